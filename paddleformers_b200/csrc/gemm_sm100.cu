@@ -1,0 +1,140 @@
+// Host launcher and torch binding for the tcgen05 bf16 GEMM family (see gemm_sm100.cuh).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "gemm_sm100.cuh"
+#include "status.h"
+#include "tma_host.h"
+
+namespace pfb {
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI, bool GROUPED>
+static void launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
+                       cudaStream_t stream) {
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, EPI, GROUPED>;
+  constexpr int smem = GemmSmem<BN, STAGES>::TOTAL;
+  static bool configured = false;
+  if (!configured) {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, p);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+template <int BN, int STAGES>
+static void dispatch(bool a_mn, bool b_mn, int epi, bool grouped, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                     const GemmParams& p, int grid, cudaStream_t s) {
+#define PFB_CASE(AMN, BMN, E, G)                                                      \
+  if (a_mn == AMN && b_mn == BMN && epi == E && grouped == G) {                       \
+    launch_one<BN, STAGES, AMN, BMN, E, G>(tmA, tmB, p, grid, s);                     \
+    return;                                                                           \
+  }
+  PFB_CASE(false, false, EPI_STORE_BF16, false)
+  PFB_CASE(false, false, EPI_STORE_F32, false)
+  PFB_CASE(false, false, EPI_ACCUM_BF16, false)
+  PFB_CASE(false, false, EPI_SWIGLU_BF16, false)
+  PFB_CASE(false, true, EPI_STORE_BF16, false)
+  PFB_CASE(false, true, EPI_ACCUM_BF16, false)
+  PFB_CASE(true, true, EPI_STORE_BF16, false)
+  PFB_CASE(true, true, EPI_STORE_F32, false)
+  PFB_CASE(true, true, EPI_ACCUM_F32, false)
+  PFB_CASE(false, false, EPI_STORE_BF16, true)
+  PFB_CASE(false, false, EPI_SWIGLU_BF16, true)
+  PFB_CASE(false, true, EPI_STORE_BF16, true)
+#undef PFB_CASE
+  TORCH_CHECK(false, "pfb200::gemm: unsupported combination a_mn=", a_mn, " b_mn=", b_mn, " epi=", epi,
+              " grouped=", grouped);
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) n = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  return n;
+}
+
+// a: [M,K] (a_mn=false) or [K,M] (a_mn=true); b: [N,K] or [K,N] (grouped: [E*N,K] or [K? no: E stacked on rows]).
+// out: [M,N] (SwiGLU: [M,N/2]); dtype decides between bf16 / fp32 epilogues.
+void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, bool b_mn, int64_t epi,
+          const c10::optional<at::Tensor>& out2, const c10::optional<at::Tensor>& block_expert,
+          int64_t n_per_expert, int64_t force_bn) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda(), "pfb200::gemm needs CUDA tensors");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "pfb200::gemm: bf16 inputs");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2, "pfb200::gemm: 2-D tensors");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1, "pfb200::gemm: inner dim contiguous");
+  const c10::cuda::CUDAGuard guard(a.device());
+  const bool grouped = block_expert.has_value();
+  const int M = a_mn ? a.size(1) : a.size(0);
+  const int K = a_mn ? a.size(0) : a.size(1);
+  const int Kb = b_mn ? b.size(0) : b.size(1);
+  const int Nb_rows = b_mn ? b.size(1) : b.size(0);
+  TORCH_CHECK(K == Kb, "pfb200::gemm: K mismatch ", K, " vs ", Kb);
+  const int N = grouped ? static_cast<int>(n_per_expert) : Nb_rows;
+  if (grouped) {
+    TORCH_CHECK(!a_mn, "grouped GEMM needs a K-major A");
+    TORCH_CHECK(Nb_rows % N == 0, "grouped GEMM: stacked B rows must be a multiple of n_per_expert");
+    TORCH_CHECK(block_expert->scalar_type() == at::kInt && block_expert->is_cuda());
+    TORCH_CHECK(block_expert->numel() * GEMM_BM >= M, "grouped GEMM: block_expert too short");
+  }
+  const bool swiglu = epi == EPI_SWIGLU_BF16;
+  const int N_out = swiglu ? N / 2 : N;
+  TORCH_CHECK(out.size(0) == M && out.size(1) == N_out, "pfb200::gemm: out shape");
+  if (epi == EPI_STORE_BF16 || epi == EPI_ACCUM_BF16 || swiglu) {
+    TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.stride(0) % 8 == 0, "bf16 out, row stride % 8");
+  } else {
+    TORCH_CHECK(out.scalar_type() == at::kFloat && out.stride(0) % 4 == 0, "fp32 out, row stride % 4");
+  }
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0, "out must be 16-byte aligned");
+  if (M == 0 || N == 0) return;
+  if (K == 0) {
+    if (epi == EPI_STORE_BF16 || epi == EPI_STORE_F32 || swiglu) out.zero_();
+    return;
+  }
+
+  // tile width: minimise waves * BN
+  int BN = 256;
+  if (force_bn == 128 || force_bn == 256) {
+    BN = static_cast<int>(force_bn);
+  } else {
+    const int sms = sm_count();
+    auto cost = [&](int bn) {
+      int nn = swiglu ? (N_out + bn / 2 - 1) / (bn / 2) : (N + bn - 1) / bn;
+      long long tiles = static_cast<long long>((M + GEMM_BM - 1) / GEMM_BM) * nn;
+      return ((tiles + sms - 1) / sms) * bn;
+    };
+    BN = cost(128) < cost(256) ? 128 : 256;
+  }
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.D = out.data_ptr(); p.ldd = out.stride(0);
+  p.D2 = nullptr; p.ldd2 = 0;
+  if (out2.has_value()) {
+    TORCH_CHECK(swiglu && out2->scalar_type() == at::kBFloat16 && out2->size(0) == M && out2->size(1) == N &&
+                out2->stride(1) == 1 && out2->stride(0) % 8 == 0, "out2: raw [M,N] bf16 for the SwiGLU epilogue");
+    p.D2 = out2->data_ptr(); p.ldd2 = out2->stride(0);
+  }
+  p.m_blocks = (M + GEMM_BM - 1) / GEMM_BM;
+  p.n_blocks = swiglu ? (N_out + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
+  p.k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
+  p.group_m = 16;
+  p.block_expert = grouped ? block_expert->data_ptr<int>() : nullptr;
+  p.n_per_expert = static_cast<int>(n_per_expert);
+  p.status = status_word();
+
+  const uint32_t b_box_rows = swiglu ? BN / 2 : BN;
+  CUtensorMap tmA = a_mn ? make_tma_2d(a.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, a.stride(0), GEMM_BK, 64)
+                         : make_tma_2d(a.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, a.stride(0), GEMM_BM, 64);
+  CUtensorMap tmB = b_mn ? make_tma_2d(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, Nb_rows, b.stride(0), GEMM_BK, 64)
+                         : make_tma_2d(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Nb_rows, K, b.stride(0), b_box_rows, 64);
+
+  const int tiles = p.m_blocks * p.n_blocks;
+  const int grid = std::min(tiles, sm_count());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  if (BN == 256) dispatch<256, 4>(a_mn, b_mn, static_cast<int>(epi), grouped, tmA, tmB, p, grid, stream);
+  else dispatch<128, 6>(a_mn, b_mn, static_cast<int>(epi), grouped, tmA, tmB, p, grid, stream);
+  count_launch();
+}
+
+}  // namespace pfb

@@ -1,0 +1,11 @@
+// Per-device error word written by kernels whose bounded waits or checked indices fail, and a host-side
+// counter of kernel launches issued by this extension.
+#pragma once
+#include <stdint.h>
+
+namespace pfb {
+int* status_word();          // device pointer to the current device's status word (allocated on first use)
+int read_status(bool reset); // synchronises the current stream; returns the status (0 = ok)
+void count_launch(int n = 1);
+int64_t launch_count(bool reset);
+}  // namespace pfb

@@ -1,0 +1,64 @@
+"""tcgen05 flash attention against an fp32 PyTorch reference (causal, GQA, document masks)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.fixture(scope="module")
+def F():
+    from paddleformers_b200.ops import functional as F
+
+    return F
+
+
+def _doc_kend(B, S, device, seed):
+    g = torch.Generator().manual_seed(seed)
+    kend = torch.empty(B, S, dtype=torch.int32)
+    for b in range(B):
+        pos = 0
+        while pos < S:
+            ln = int(torch.randint(16, 300, (1,), generator=g))
+            end = min(S, pos + ln)
+            kend[b, pos:end] = end
+            pos = end
+    return kend.to(device)
+
+
+@pytest.mark.parametrize("p_in_tmem", [True, False])
+@pytest.mark.parametrize("B,S,Hq,Hkv,docs", [(1, 128, 2, 2, False), (2, 512, 4, 2, False), (1, 640, 4, 1, True), (1, 200, 2, 1, False)])
+def test_attention_forward(F, p_in_tmem, B, S, Hq, Hkv, docs):
+    torch.manual_seed(0)
+    F.set_attention_options(p_in_tmem=p_in_tmem)
+    q = torch.randn(B, S, Hq, 128, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(B, S, Hkv, 128, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(B, S, Hkv, 128, device="cuda", dtype=torch.bfloat16)
+    kend = _doc_kend(B, S, "cuda", 1) if docs else None
+    out = F.flash_attention(q, k, v, causal=True, kend=kend)
+    F.check_kernel_status()
+    ref = F.attention_reference(q, k, v, causal=True, kend=kend)
+    F.set_attention_options(p_in_tmem=True)
+    assert _rel_err(out, ref) < 2e-2
+
+
+def test_attention_backward(F):
+    torch.manual_seed(1)
+    B, S, Hq, Hkv = 1, 384, 4, 2
+    q = torch.randn(B, S, Hq, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(B, S, Hkv, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(B, S, Hkv, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    kend = _doc_kend(B, S, "cuda", 2)
+    out = F.flash_attention(q, k, v, causal=True, kend=kend)
+    g = torch.randn_like(out)
+    out.backward(g)
+    F.check_kernel_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = F.attention_reference(qr, kr, vr, causal=True, kend=kend)
+    ref.backward(g.float())
+    assert _rel_err(out, ref) < 2e-2
+    assert _rel_err(q.grad, qr.grad) < 3e-2 and _rel_err(k.grad, kr.grad) < 3e-2 and _rel_err(v.grad, vr.grad) < 3e-2

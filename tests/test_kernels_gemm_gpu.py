@@ -1,0 +1,125 @@
+"""tcgen05 GEMM numerics against fp32 PyTorch references (all operand layouts and epilogues)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.fixture(scope="module")
+def F():
+    from paddleformers_b200.ops import functional as F
+
+    return F
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (384, 1024, 4096), (200, 328, 136), (4096, 1024, 1024)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_nt(F, M, N, K, bn):
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    out = F.gemm(a, b, force_bn=bn)
+    F.check_kernel_status()
+    ref = a.float() @ b.float().t()
+    assert _rel_err(out, ref) < 1e-2
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_dgrad_layout(F, bn):
+    torch.manual_seed(1)
+    M, N, K = 512, 384, 640  # dx[M,N] = dy[M,K] @ W[K,N]
+    dy = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+    out = F.gemm(dy, w, b_mn=True, force_bn=bn)
+    F.check_kernel_status()
+    assert _rel_err(out, dy.float() @ w.float()) < 1e-2
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_wgrad_layout_accumulate(F, bn):
+    torch.manual_seed(2)
+    T, O, I = 1024, 384, 512  # dW[O,I] = dy[T,O]^T @ x[T,I]
+    dy = torch.randn(T, O, device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(T, I, device="cuda", dtype=torch.bfloat16)
+    acc = torch.randn(O, I, device="cuda", dtype=torch.float32)
+    ref = acc + dy.float().t() @ x.float()
+    F.gemm(dy, x, out=acc, a_mn=True, b_mn=True, epi=F.EPI_ACCUM_F32, force_bn=bn)
+    F.check_kernel_status()
+    assert _rel_err(acc, ref) < 1e-3
+    out = F.gemm(dy, x, a_mn=True, b_mn=True, epi=F.EPI_STORE_BF16, force_bn=bn)
+    assert _rel_err(out, dy.float().t() @ x.float()) < 1e-2
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_swiglu_epilogue(F, bn):
+    torch.manual_seed(3)
+    T, H, I = 512, 256, 384
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(2 * I, H, device="cuda", dtype=torch.bfloat16) * 0.1
+    raw = torch.empty(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+    act = F.gemm(x, w, epi=F.EPI_SWIGLU_BF16, out2=raw, force_bn=bn)
+    F.check_kernel_status()
+    gu = x.float() @ w.float().t()
+    ref = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    assert _rel_err(raw, gu) < 1e-2
+    assert _rel_err(act, ref) < 2e-2
+
+
+def test_gemm_residual_accumulate(F):
+    torch.manual_seed(4)
+    a = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(384, 512, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(256, 384, device="cuda", dtype=torch.bfloat16)
+    ref = res.float() + a.float() @ b.float().t()
+    F.gemm(a, b, out=res, epi=F.EPI_ACCUM_BF16)
+    F.check_kernel_status()
+    assert _rel_err(res, ref) < 1e-2
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_grouped_gemm(F, bn):
+    torch.manual_seed(5)
+    E, N, K = 4, 384, 256
+    rows = [128, 0, 384, 256]  # padded-to-128 expert segments; expert 1 is empty
+    block_expert, a_parts = [], []
+    for e, r in enumerate(rows):
+        block_expert += [e] * (r // 128)
+        a_parts.append(torch.randn(r, K, device="cuda", dtype=torch.bfloat16))
+    block_expert.append(-1)  # one trailing unused block
+    a = torch.cat(a_parts + [torch.zeros(128, K, device="cuda", dtype=torch.bfloat16)])
+    w = torch.randn(E * N, K, device="cuda", dtype=torch.bfloat16)
+    be = torch.tensor(block_expert, device="cuda", dtype=torch.int32)
+    out = torch.zeros(a.shape[0], N, device="cuda", dtype=torch.bfloat16)
+    F.gemm(a, w, out=out, block_expert=be, n_per_expert=N, force_bn=bn)
+    F.check_kernel_status()
+    off = 0
+    for e, r in enumerate(rows):
+        if r:
+            ref = a[off:off + r].float() @ w[e * N:(e + 1) * N].float().t()
+            assert _rel_err(out[off:off + r], ref) < 1e-2
+        off += r
+    assert out[off:].abs().max().item() == 0.0
+
+
+def test_linear_autograd_matches_reference(F):
+    torch.manual_seed(6)
+    x = torch.randn(4, 96, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(384, 256, device="cuda", dtype=torch.bfloat16) * 0.05).requires_grad_()
+    y = F.linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    yr = torch.nn.functional.linear(xr, wr)
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2 and _rel_err(x.grad, xr.grad) < 1e-2 and _rel_err(w.grad, wr.grad) < 1e-2
+    # main_grad convention
+    w2 = w.detach().clone().requires_grad_()
+    w2.main_grad = torch.zeros(w2.shape, device="cuda", dtype=torch.float32)
+    F.linear(x.detach(), w2).backward(g)
+    assert w2.grad is None and _rel_err(w2.main_grad, wr.grad) < 1e-3
