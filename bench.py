@@ -1,0 +1,276 @@
+#!/usr/bin/env python
+"""Headline benchmark: training throughput (tokens/s, whole job) of Llama-3-8B pretraining, bf16, seq 4096,
+micro-batch 1, global batch 64 sequences, TP = number of GPUs (+ sequence parallel), sharding stage-1 optimizer,
+synthetic uniform-random tokens and random-init weights (std 0.02).
+
+    python bench.py --gpus 1 --steps 2 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29511 \
+        bench.py --gpus 8 --steps 2 --warmup 3
+    python bench.py --impl reference ...      # the unmodified reference, if it can run on this machine
+    python bench.py --model qwen3-30b-a3b ... # EP = GPUs, packed documents (needs 8 GPUs for memory)
+
+One step = 64 micro-batches of forward + backward followed by the sharded AdamW update. Two timed regions are
+reported: ``value`` is timed on the device (CUDA events, barrier + synchronize on both sides, max over ranks) with the
+inputs already resident; ``e2e`` runs the same steps through ``Trainer.train()`` with every micro-batch copied from
+pinned host memory and the loss read back to the host every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+NOMINAL_BF16_FLOPS = 2.25e15
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "qwen3-30b-a3b"])
+    ap.add_argument("--global-batch", type=int, default=64)
+    ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (the result is then marked invalid)")
+    ap.add_argument("--no-e2e", action="store_true", help="debug only: skip the end-to-end pass")
+    return ap.parse_args()
+
+
+def reference_arm(args):
+    """The reference is a PaddlePaddle library: its trainer imports paddle, paddlefleet and paddlefleet_ops."""
+    ref = os.path.join(REPO, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(os.path.join(ref, "paddleformers")):
+        why = "reference not installed under baseline/_ref"
+    else:
+        try:
+            import importlib
+
+            importlib.import_module("paddle")
+        except Exception as e:  # noqa: BLE001
+            why = f"reference needs PaddlePaddle + paddlefleet wheels which are not installable offline here (import paddle: {type(e).__name__})"
+    if why is None:
+        why = "reference launcher not wired: paddle became importable, re-check baseline/_ref"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+class ClockSampler:
+    def __init__(self, device_index: int):
+        self.proc = None
+        self.path = f"/tmp/pfb_clocks_{os.getpid()}.csv"
+        q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(device_index)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:  # noqa: BLE001
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:  # noqa: BLE001
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx.append(float(parts[1]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, parts[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.remove(self.path)
+        except Exception:  # noqa: BLE001
+            pass
+        if sm:
+            busy = [s for s in sm if s > 0]
+            out["sm_mhz"] = statistics.median(busy) if busy else None
+            out["sm_max_mhz"] = max(mx) if mx else None
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    from paddleformers_b200.data.synthetic import SyntheticCausalLMDataset
+    from paddleformers_b200.models.configuration import named_config
+    from paddleformers_b200.ops import functional as F
+    from paddleformers_b200.trainer.trainer import Trainer
+    from paddleformers_b200.trainer.trainer_callback import TrainerCallback
+    from paddleformers_b200.trainer.training_args import TrainingArguments
+    from paddleformers_b200.transformers.auto import AutoModelForCausalLM
+    from paddleformers_b200.utils.flops import model_flops_per_token
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+
+    S, GB = args.seq_len, args.global_batch
+    is_moe = args.model == "qwen3-30b-a3b"
+    over = {}
+    if args.layers:
+        over["num_hidden_layers"] = args.layers
+    cfg = named_config(args.model, **over)
+    cfg.dtype = "bfloat16"
+    if is_moe:
+        targs = dict(expert_model_parallel_size=world, sharding="stage1", tensor_model_parallel_size=1)
+        par = f"ep{world}+sharding{world}(stage1)"
+        dp_world = world
+    else:
+        targs = dict(tensor_model_parallel_size=world, sequence_parallel=world > 1, sharding="stage1")
+        par = f"tp{world}" + ("+sp" if world > 1 else "") + "+sharding1(stage1)"
+        dp_world = 1
+    accum = GB // dp_world
+    W, K = args.warmup, args.steps
+    ta = TrainingArguments(output_dir="/tmp/pfb_bench_out", per_device_train_batch_size=1, gradient_accumulation_steps=accum,
+                           max_steps=W + K, learning_rate=3e-4, lr_scheduler_type="constant", weight_decay=0.1,
+                           adam_beta2=0.95, max_grad_norm=1.0, bf16=True, logging_steps=1, save_strategy="no",
+                           max_seq_len=S, seed=0, **targs)
+    ta.setup_parallel()
+    cfg.sequence_parallel = ta.sequence_parallel
+    cfg.tensor_model_parallel_size = ta.tensor_model_parallel_size
+    torch.manual_seed(1234 + ta.parallel_state.coord["mp"] + 17 * ta.parallel_state.rank_in("ep"))
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.bfloat16, device=dev)
+    doc_range = (128, 4096) if is_moe else None
+    ds = SyntheticCausalLMDataset(cfg.vocab_size, S, num_samples=GB * (W + K), seed=7, doc_len_range=doc_range)
+
+    timings = {}
+
+    class Timing(TrainerCallback):
+        """Brackets steps W+1 .. W+K of Trainer.train() with barrier + synchronize + CUDA events."""
+
+        def on_step_begin(self, a, state, control, **kw):
+            if state.global_step == W:
+                if dist.is_initialized():
+                    dist.barrier()
+                torch.cuda.synchronize()
+                timings["e2e_start"] = torch.cuda.Event(enable_timing=True)
+                timings["e2e_end"] = torch.cuda.Event(enable_timing=True)
+                timings["e2e_start"].record()
+                timings["wall0"] = time.time()
+
+        def on_log(self, a, state, control, logs=None, **kw):
+            if state.global_step == W + K and logs and "loss" in logs and "e2e_end_done" not in timings:
+                timings["e2e_end"].record()
+                if dist.is_initialized():
+                    dist.barrier()
+                torch.cuda.synchronize()
+                timings["e2e_ms"] = timings["e2e_start"].elapsed_time(timings["e2e_end"])
+                timings["e2e_end_done"] = True
+                timings["last_loss"] = logs["loss"]
+
+    trainer = Trainer(model=model, args=ta, train_dataset=ds, callbacks=[Timing()])
+    trainer.create_optimizer_and_scheduler(W + K)
+    model.loss_accumulation_steps = accum
+
+    # ---------------- pass 1: device-timed, inputs resident on the device ----------------
+    ps = ta.parallel_state
+    def device_batch(i):
+        item = ds[(i * dp_world + ps.dataset_rank) % len(ds)]
+        return {k: v.unsqueeze(0).to(dev) for k, v in item.items()}
+    resident = [device_batch(i) for i in range(min(accum, 8))]
+
+    def one_step():
+        for mb in range(accum):
+            trainer.training_step(model, dict(resident[mb % len(resident)]))
+        trainer.optimizer_step()
+
+    for _ in range(W):
+        one_step()
+    F.check_kernel_status()
+    if dist.is_initialized():
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = F.kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        one_step()
+    e1.record()
+    if dist.is_initialized():
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches = F.kernel_launch_count() - launches0
+    clocks = sampler.stop() if sampler is not None else None
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if dist.is_initialized():
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(ms) / K
+    tokens_per_step = GB * S
+    value = tokens_per_step / (ms_per_step / 1e3)
+    F.check_kernel_status()
+
+    # ---------------- pass 2: end to end through Trainer.train() ----------------
+    e2e = None
+    if not args.no_e2e:
+        trainer._tr_loss = None
+        trainer.train()
+        e2e_ms = torch.tensor([timings.get("e2e_ms", float("nan"))], device=dev)
+        if dist.is_initialized():
+            dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+        sample = ds[0]
+        h2d = sum(v.numel() * v.element_size() for v in sample.values()) * accum
+        e2e = {"value": tokens_per_step / (float(e2e_ms) / K / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+               "d2h_bytes_per_step": 4, "ms_per_step": float(e2e_ms) / K, "last_loss": timings.get("last_loss")}
+
+    if rank == 0:
+        fpt = model_flops_per_token(cfg, S)
+        per_gpu = value / world
+        out = {
+            "metric": "train_tokens_per_second", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights (std 0.02)",
+            "config": {"model": "Llama-3-8B" if not is_moe else "Qwen3-30B-A3B", "global_batch": GB, "seq_len": S,
+                       "micro_batch": 1, "grad_accum": accum, "parallelism": par,
+                       "optimizer": "AdamW fp32 master + fp32 main_grad, sharding stage1",
+                       "l2": "no explicit flush: every step streams >= 16 GB of weights plus activations, far above the 126 MB L2",
+                       "layers": cfg.num_hidden_layers},
+            "tokens_per_second_per_gpu": per_gpu, "model_flops_per_token": fpt,
+            "model_tflops_per_gpu": per_gpu * fpt / 1e12, "mfu_vs_nominal_2.25PF": per_gpu * fpt / NOMINAL_BF16_FLOPS,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "impl": "ours",
+        }
+        if args.layers:
+            out["invalid"] = "truncated model (--layers): debug run, not a benchmark value"
+        print(json.dumps(out))
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

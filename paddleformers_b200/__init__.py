@@ -1,0 +1,38 @@
+"""B200-native LLM training framework with the capabilities of PaddleFormers.
+
+Public entry points (lazily imported so that ``import paddleformers_b200`` stays cheap, like the reference's
+``_LazyModule`` shim, paddleformers/utils/lazy_import.py):
+
+    AutoConfig, AutoModelForCausalLM, AutoTokenizer        model API
+    Trainer, TrainingArguments                             training API
+    paddleformers_b200.ops.functional                      sm_100a kernels behind torch autograd
+"""
+from __future__ import annotations
+
+import importlib
+
+__version__ = "0.1.0"
+
+_LAZY = {
+    "AutoConfig": ".transformers.auto", "AutoModelForCausalLM": ".transformers.auto", "AutoTokenizer": ".transformers.auto",
+    "AutoModelForCausalLMPipe": ".transformers.auto", "AutoProcessor": ".transformers.auto",
+    "PretrainedConfig": ".transformers.configuration_utils", "PretrainedModel": ".transformers.model_utils",
+    "Trainer": ".trainer.trainer", "TrainingArguments": ".trainer.training_args",
+    "TrainerCallback": ".trainer.trainer_callback",
+    "LlamaForCausalLM": ".models.modeling", "Qwen3ForCausalLM": ".models.modeling", "Qwen3MoeForCausalLM": ".models.modeling",
+    "DeepseekV3ForCausalLM": ".models.modeling", "Glm4MoeForCausalLM": ".models.modeling",
+    "LlamaConfig": ".models.configuration", "Qwen3Config": ".models.configuration", "Qwen3MoeConfig": ".models.configuration",
+    "DeepseekV3Config": ".models.configuration", "Glm4MoeConfig": ".models.configuration",
+    "LoRAConfig": ".peft.lora", "LoRAModel": ".peft.lora", "GenerationConfig": ".generation.utils",
+}
+
+
+def __getattr__(name):
+    if name in _LAZY:
+        mod = importlib.import_module(_LAZY[name], __name__)
+        return getattr(mod, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
+def __dir__():
+    return sorted(list(globals()) + list(_LAZY))

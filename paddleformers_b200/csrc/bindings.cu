@@ -46,6 +46,7 @@ static int64_t op_launch_count(bool reset) { return launch_count(reset); }
 void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, bool b_mn, int64_t epi,
           const c10::optional<at::Tensor>& out2, const c10::optional<at::Tensor>& block_expert, int64_t n_per_expert,
           int64_t force_bn);
+void gemm_wgrad_grouped(const at::Tensor& dy, const at::Tensor& x, at::Tensor& out, const at::Tensor& expert_rows);
 at::Tensor attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at::Tensor& out, int64_t B, int64_t S,
                     double scale, bool causal, const c10::optional<at::Tensor>& kend,
                     const c10::optional<at::Tensor>& tile_min, const c10::optional<at::Tensor>& tile_max, bool p_in_tmem);
@@ -81,6 +82,7 @@ TORCH_LIBRARY(pfb200, m) {
   m.def("launch_count(bool reset) -> int", &pfb::op_launch_count);
   m.def("gemm(Tensor a, Tensor b, Tensor(a!) out, bool a_mn, bool b_mn, int epi, Tensor? out2, Tensor? block_expert, "
         "int n_per_expert, int force_bn) -> ()", &pfb::gemm);
+  m.def("gemm_wgrad_grouped(Tensor dy, Tensor x, Tensor(a!) out, Tensor expert_rows) -> ()", &pfb::gemm_wgrad_grouped);
   m.def("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) out, int B, int S, float scale, bool causal, Tensor? kend, "
         "Tensor? tile_min, Tensor? tile_max, bool p_in_tmem) -> Tensor", &pfb::attn_fwd);
   m.def("rms_norm_fwd(Tensor x, Tensor? residual, Tensor w, float eps) -> (Tensor, Tensor, Tensor)", &pfb::rms_norm_fwd);

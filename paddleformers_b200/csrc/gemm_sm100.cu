@@ -9,10 +9,10 @@
 
 namespace pfb {
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI, bool GROUPED>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI, bool GROUPED, bool KGROUPED = false>
 static void launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
                        cudaStream_t stream) {
-  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, EPI, GROUPED>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, EPI, GROUPED, KGROUPED>;
   constexpr int smem = GemmSmem<BN, STAGES>::TOTAL;
   static bool configured = false;
   if (!configured) {
@@ -69,11 +69,16 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, 
   const int K = a_mn ? a.size(0) : a.size(1);
   const int Kb = b_mn ? b.size(0) : b.size(1);
   const int Nb_rows = b_mn ? b.size(1) : b.size(0);
-  TORCH_CHECK(K == Kb, "pfb200::gemm: K mismatch ", K, " vs ", Kb);
   const int N = grouped ? static_cast<int>(n_per_expert) : Nb_rows;
+  if (grouped && b_mn) {
+    // stacked [E*K, N]: every expert contributes K rows of an MN-major operand
+    TORCH_CHECK(Kb % K == 0 && Nb_rows == N, "grouped GEMM (MN-major B): b must be [E*K, N]");
+  } else {
+    TORCH_CHECK(K == Kb, "pfb200::gemm: K mismatch ", K, " vs ", Kb);
+  }
   if (grouped) {
     TORCH_CHECK(!a_mn, "grouped GEMM needs a K-major A");
-    TORCH_CHECK(Nb_rows % N == 0, "grouped GEMM: stacked B rows must be a multiple of n_per_expert");
+    TORCH_CHECK(b_mn || Nb_rows % N == 0, "grouped GEMM: stacked B rows must be a multiple of n_per_expert");
     TORCH_CHECK(block_expert->scalar_type() == at::kInt && block_expert->is_cuda());
     TORCH_CHECK(block_expert->numel() * GEMM_BM >= M, "grouped GEMM: block_expert too short");
   }
@@ -121,12 +126,13 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, 
   p.group_m = 16;
   p.block_expert = grouped ? block_expert->data_ptr<int>() : nullptr;
   p.n_per_expert = static_cast<int>(n_per_expert);
+  p.expert_rows = nullptr; p.tiles_per_expert = 0; p.d_expert_stride = 0;
   p.status = status_word();
 
   const uint32_t b_box_rows = swiglu ? BN / 2 : BN;
   CUtensorMap tmA = a_mn ? make_tma_2d(a.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, a.stride(0), GEMM_BK, 64)
                          : make_tma_2d(a.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, a.stride(0), GEMM_BM, 64);
-  CUtensorMap tmB = b_mn ? make_tma_2d(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, Nb_rows, b.stride(0), GEMM_BK, 64)
+  CUtensorMap tmB = b_mn ? make_tma_2d(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Kb, Nb_rows, b.stride(0), GEMM_BK, 64)
                          : make_tma_2d(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Nb_rows, K, b.stride(0), b_box_rows, 64);
 
   const int tiles = p.m_blocks * p.n_blocks;
@@ -134,6 +140,41 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, 
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   if (BN == 256) dispatch<256, 4>(a_mn, b_mn, static_cast<int>(epi), grouped, tmA, tmB, p, grid, stream);
   else dispatch<128, 6>(a_mn, b_mn, static_cast<int>(epi), grouped, tmA, tmB, p, grid, stream);
+  count_launch();
+}
+
+
+// Expert weight gradients in one launch: dW[e] (+)= dy[rows_e]^T @ x[rows_e] for every expert e.
+// dy: [R, N], x: [R, K] (expert-sorted rows, segments padded to 64-row multiples with zero rows),
+// expert_rows: int32 [E, 2] = (first row, row count); out: fp32 [E, N, K], accumulated in place.
+void gemm_wgrad_grouped(const at::Tensor& dy, const at::Tensor& x, at::Tensor& out, const at::Tensor& expert_rows) {
+  TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && x.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(dy.dim() == 2 && x.dim() == 2 && dy.stride(1) == 1 && x.stride(1) == 1 && dy.size(0) == x.size(0));
+  TORCH_CHECK(out.scalar_type() == at::kFloat && out.dim() == 3 && out.is_contiguous());
+  TORCH_CHECK(expert_rows.scalar_type() == at::kInt && expert_rows.is_contiguous() && expert_rows.is_cuda());
+  const c10::cuda::CUDAGuard guard(dy.device());
+  const int E = out.size(0), N = out.size(1), K = out.size(2), R = dy.size(0);
+  TORCH_CHECK(dy.size(1) == N && x.size(1) == K && expert_rows.numel() == 2 * E && K % 4 == 0);
+  if (E == 0 || R == 0) return;
+  constexpr int BN = 256;
+  GemmParams p;
+  p.M = N; p.N = K; p.K = R;
+  p.D = out.data_ptr(); p.ldd = K; p.D2 = nullptr; p.ldd2 = 0;
+  p.m_blocks = (N + GEMM_BM - 1) / GEMM_BM;
+  p.n_blocks = (K + BN - 1) / BN;
+  p.k_blocks = 0;
+  p.group_m = 16;
+  p.block_expert = nullptr;
+  p.n_per_expert = E;
+  p.expert_rows = expert_rows.data_ptr<int>();
+  p.tiles_per_expert = p.m_blocks * p.n_blocks;
+  p.d_expert_stride = static_cast<long long>(N) * K;
+  p.status = status_word();
+  CUtensorMap tmA = make_tma_2d(dy.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, N, dy.stride(0), GEMM_BK, 64);
+  CUtensorMap tmB = make_tma_2d(x.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, K, x.stride(0), GEMM_BK, 64);
+  const int tiles = p.tiles_per_expert * E;
+  launch_one<BN, 4, true, true, EPI_ACCUM_F32, false, true>(tmA, tmB, p, std::min(tiles, sm_count()),
+                                                           at::cuda::getCurrentCUDAStream());
   count_launch();
 }
 

@@ -39,6 +39,9 @@ struct GemmParams {
   int group_m;              // rasterisation group (m-blocks per group)
   const int* block_expert;  // grouped: expert id per 128-row block of A (-1 = skip); else nullptr
   int n_per_expert;         // grouped: rows of B per expert
+  const int* expert_rows;   // k-grouped (wgrad): [E, 2] = (first row, row count) of each expert's segment, counts % 64 == 0
+  int tiles_per_expert;     // k-grouped: m_blocks * n_blocks of one expert's [N, K] gradient
+  long long d_expert_stride;  // k-grouped: elements between consecutive experts in D
   int* status;              // error word (0 = ok)
 };
 
@@ -51,7 +54,7 @@ struct GemmSmem {
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
 };
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI, bool GROUPED>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI, bool GROUPED, bool KGROUPED = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
@@ -82,10 +85,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_tiles = p.m_blocks * p.n_blocks;
+  const int num_tiles = KGROUPED ? p.tiles_per_expert * p.n_per_expert /* = E */ : p.m_blocks * p.n_blocks;
   const int tiles_per_group = p.group_m * p.n_blocks;
 
   auto tile_coords = [&](int t, int& mb, int& nb) {
+    if constexpr (KGROUPED) t = t % p.tiles_per_expert;
     int g = t / tiles_per_group;
     int r = t - g * tiles_per_group;
     int gsz = min(p.group_m, p.m_blocks - g * p.group_m);
@@ -101,12 +105,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int mb, nb; tile_coords(t, mb, nb);
         int b_row0 = nb * BN;
+        int k_row0 = 0, k_blocks = p.k_blocks;
         if constexpr (GROUPED) {
           int e = p.block_expert[mb];
           if (e < 0) continue;
-          b_row0 += e * p.n_per_expert;
+          if constexpr (B_MN) k_row0 = e * p.K;   // stacked [E*K, N] operand: the expert offset is on the K rows
+          else b_row0 += e * p.n_per_expert;
         }
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        if constexpr (KGROUPED) {
+          const int e = t / p.tiles_per_expert;
+          k_row0 = p.expert_rows[2 * e];
+          k_blocks = p.expert_rows[2 * e + 1] / GEMM_BK;
+          if (k_blocks == 0) continue;
+        }
+        for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, PFB_ERR_WAIT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + stage * S::STAGE_BYTES;
           uint8_t* sb = sa + S::A_BYTES;
@@ -116,7 +128,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {
             #pragma unroll
             for (int j = 0; j < GEMM_BM / 64; ++j)
-              tma_load_2d(sa + j * (GEMM_BK * 128), &tmA, &full_bar[stage], mb * GEMM_BM + j * 64, kb * GEMM_BK);
+              tma_load_2d(sa + j * (GEMM_BK * 128), &tmA, &full_bar[stage], mb * GEMM_BM + j * 64,
+                          (KGROUPED ? k_row0 : 0) + kb * GEMM_BK);
           }
           if constexpr (EPI == EPI_SWIGLU_BF16) {
             // gate rows and up rows of the stacked [gate; up] weight land side by side in one tile
@@ -130,7 +143,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {
             #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * (GEMM_BK * 128), &tmB, &full_bar[stage], b_row0 + j * 64, kb * GEMM_BK);
+              tma_load_2d(sb + j * (GEMM_BK * 128), &tmB, &full_bar[stage], b_row0 + j * 64, k_row0 + kb * GEMM_BK);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -144,14 +157,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int k_blocks = p.k_blocks;
         if constexpr (GROUPED) {
           int mb, nb; tile_coords(t, mb, nb);
           if (p.block_expert[mb] < 0) continue;
         }
+        if constexpr (KGROUPED) {
+          k_blocks = p.expert_rows[2 * (t / p.tiles_per_expert) + 1] / GEMM_BK;
+          if (k_blocks == 0) continue;
+        }
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, PFB_ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
@@ -179,6 +197,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int mb, nb; tile_coords(t, mb, nb);
       if constexpr (GROUPED) { if (p.block_expert[mb] < 0) continue; }
+      long long d_off = 0;
+      if constexpr (KGROUPED) {
+        const int e = t / p.tiles_per_expert;
+        if (p.expert_rows[2 * e + 1] / GEMM_BK == 0) continue;
+        d_off = e * p.d_expert_stride;
+      }
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const int row = mb * GEMM_BM + quad * 32 + lane;
@@ -276,7 +300,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 }
               }
             } else {
-              float* dst = reinterpret_cast<float*>(p.D) + static_cast<long long>(row) * p.ldd + col;
+              float* dst = reinterpret_cast<float*>(p.D) + d_off + static_cast<long long>(row) * p.ldd + col;
               if (col + 32 <= p.N) {
                 #pragma unroll
                 for (int j = 0; j < 8; ++j) {

@@ -1,0 +1,202 @@
+"""Configurations of the supported decoder families (Hugging Face field names, so ``config.json`` files load as is).
+
+Reference counterparts: paddleformers/transformers/llama/configuration.py, qwen2, qwen3,
+qwen3_moe/configuration.py:154-226, deepseek_v3/configuration.py:136-238, glm4_moe/configuration.py:128-220.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+from ..transformers.configuration_utils import PretrainedConfig
+
+
+class DecoderConfig(PretrainedConfig):
+    """Superset of the per-family options read by the unified decoder implementation."""
+
+    model_type = "decoder"
+
+    def __init__(self, vocab_size=32000, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
+                 num_attention_heads=32, num_key_value_heads=None, head_dim=None, hidden_act="silu",
+                 max_position_embeddings=4096, rms_norm_eps=1e-6, rope_theta=10000.0, rope_scaling=None,
+                 partial_rotary_factor=1.0, attention_bias=False, mlp_bias=False, use_qk_norm=False,
+                 attention_dropout=0.0,
+                 # MoE
+                 num_experts=0, n_routed_experts=None, num_experts_per_tok=0, moe_intermediate_size=None,
+                 n_shared_experts=0, shared_expert_intermediate_size=None, first_k_dense_replace=0,
+                 decoder_sparse_step=1, mlp_only_layers=None, norm_topk_prob=True, scoring_func="softmax",
+                 topk_method="greedy", n_group=1, topk_group=1, routed_scaling_factor=1.0,
+                 router_aux_loss_coef=0.0, router_z_loss_coef=0.0, output_router_logits=False,
+                 # MLA
+                 q_lora_rank=None, kv_lora_rank=None, qk_nope_head_dim=None, qk_rope_head_dim=None, v_head_dim=None,
+                 **kwargs):
+        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, num_hidden_layers=num_hidden_layers,
+                         num_attention_heads=num_attention_heads, **kwargs)
+        self.intermediate_size = intermediate_size
+        self.num_key_value_heads = num_key_value_heads or num_attention_heads
+        self.head_dim = head_dim or hidden_size // num_attention_heads
+        self.hidden_act = hidden_act
+        self.max_position_embeddings = max_position_embeddings
+        self.rms_norm_eps = rms_norm_eps
+        self.rope_theta = rope_theta
+        self.rope_scaling = rope_scaling
+        self.partial_rotary_factor = partial_rotary_factor
+        self.attention_bias = attention_bias
+        self.mlp_bias = mlp_bias
+        self.use_qk_norm = use_qk_norm
+        self.attention_dropout = attention_dropout
+        self.num_experts = n_routed_experts if n_routed_experts is not None else num_experts
+        self.num_experts_per_tok = num_experts_per_tok
+        self.moe_intermediate_size = moe_intermediate_size
+        self.n_shared_experts = n_shared_experts or 0
+        self.shared_expert_intermediate_size = shared_expert_intermediate_size
+        self.first_k_dense_replace = first_k_dense_replace
+        self.decoder_sparse_step = decoder_sparse_step
+        self.mlp_only_layers = mlp_only_layers or []
+        self.norm_topk_prob = norm_topk_prob
+        self.scoring_func = scoring_func
+        self.topk_method = topk_method
+        self.n_group = n_group
+        self.topk_group = topk_group
+        self.routed_scaling_factor = routed_scaling_factor
+        self.router_aux_loss_coef = router_aux_loss_coef
+        self.router_z_loss_coef = router_z_loss_coef
+        self.output_router_logits = output_router_logits
+        self.q_lora_rank = q_lora_rank
+        self.kv_lora_rank = kv_lora_rank
+        self.qk_nope_head_dim = qk_nope_head_dim
+        self.qk_rope_head_dim = qk_rope_head_dim
+        self.v_head_dim = v_head_dim
+
+    @property
+    def n_routed_experts(self):
+        return self.num_experts
+
+    @property
+    def is_mla(self) -> bool:
+        return self.kv_lora_rank is not None
+
+    def is_moe_layer(self, layer_idx: int) -> bool:
+        if self.num_experts <= 0:
+            return False
+        if layer_idx in self.mlp_only_layers or layer_idx < self.first_k_dense_replace:
+            return False
+        return (layer_idx + 1) % max(self.decoder_sparse_step, 1) == 0
+
+
+class LlamaConfig(DecoderConfig):
+    model_type = "llama"
+
+    def __init__(self, **kw):
+        kw.setdefault("rms_norm_eps", 1e-6)
+        super().__init__(**kw)
+
+
+class Qwen2Config(DecoderConfig):
+    model_type = "qwen2"
+
+    def __init__(self, **kw):
+        kw.setdefault("attention_bias", True)
+        super().__init__(**kw)
+
+
+class Qwen3Config(DecoderConfig):
+    model_type = "qwen3"
+
+    def __init__(self, **kw):
+        kw.setdefault("use_qk_norm", True)
+        kw.setdefault("head_dim", 128)
+        super().__init__(**kw)
+
+
+class Qwen3MoeConfig(DecoderConfig):
+    model_type = "qwen3_moe"
+
+    def __init__(self, **kw):
+        kw.setdefault("use_qk_norm", True)
+        kw.setdefault("head_dim", 128)
+        kw.setdefault("num_experts", 128)
+        kw.setdefault("num_experts_per_tok", 8)
+        kw.setdefault("moe_intermediate_size", 768)
+        kw.setdefault("norm_topk_prob", True)
+        kw.setdefault("router_aux_loss_coef", 1e-3)
+        kw.setdefault("scoring_func", "softmax")
+        super().__init__(**kw)
+
+
+class DeepseekV3Config(DecoderConfig):
+    model_type = "deepseek_v3"
+
+    def __init__(self, **kw):
+        kw.setdefault("hidden_size", 7168)
+        kw.setdefault("intermediate_size", 18432)
+        kw.setdefault("moe_intermediate_size", 2048)
+        kw.setdefault("num_attention_heads", 128)
+        kw.setdefault("num_key_value_heads", 128)
+        kw.setdefault("n_routed_experts", 256)
+        kw.setdefault("n_shared_experts", 1)
+        kw.setdefault("num_experts_per_tok", 8)
+        kw.setdefault("first_k_dense_replace", 3)
+        kw.setdefault("scoring_func", "sigmoid")
+        kw.setdefault("topk_method", "noaux_tc")
+        kw.setdefault("n_group", 8)
+        kw.setdefault("topk_group", 4)
+        kw.setdefault("routed_scaling_factor", 2.5)
+        kw.setdefault("q_lora_rank", 1536)
+        kw.setdefault("kv_lora_rank", 512)
+        kw.setdefault("qk_nope_head_dim", 128)
+        kw.setdefault("qk_rope_head_dim", 64)
+        kw.setdefault("v_head_dim", 128)
+        kw.setdefault("head_dim", 192)
+        kw.setdefault("vocab_size", 129280)
+        kw.setdefault("num_nextn_predict_layers", 1)
+        super().__init__(**kw)
+
+
+class Glm4MoeConfig(DecoderConfig):
+    model_type = "glm4_moe"
+
+    def __init__(self, **kw):
+        kw.setdefault("partial_rotary_factor", 0.5)
+        kw.setdefault("head_dim", 128)
+        kw.setdefault("rms_norm_eps", 1e-5)
+        kw.setdefault("scoring_func", "sigmoid")
+        kw.setdefault("topk_method", "noaux_tc")
+        kw.setdefault("n_shared_experts", 1)
+        kw.setdefault("first_k_dense_replace", 1)
+        kw.setdefault("attention_bias", True)
+        kw.setdefault("norm_topk_prob", True)
+        super().__init__(**kw)
+
+
+CONFIG_MAPPING = {c.model_type: c for c in (LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
+                                            Glm4MoeConfig)}
+# families whose architecture is a strict subset of an implemented one load through it
+CONFIG_MAPPING.update({"mistral": LlamaConfig, "deepseek_v2": DeepseekV3Config, "glm4_moe_lite": Glm4MoeConfig})
+
+
+def named_config(name: str, **overrides) -> DecoderConfig:
+    """Architecture presets used by the benchmark harness and tests (no checkpoint needed)."""
+    presets = {
+        "llama3-8b": (LlamaConfig, dict(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                                        num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=500000.0,
+                                        rms_norm_eps=1e-5, max_position_embeddings=8192)),
+        "qwen3-30b-a3b": (Qwen3MoeConfig, dict(vocab_size=151936, hidden_size=2048, intermediate_size=6144,
+                                               num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4,
+                                               head_dim=128, num_experts=128, num_experts_per_tok=8,
+                                               moe_intermediate_size=768, rope_theta=1e6, rms_norm_eps=1e-6,
+                                               router_aux_loss_coef=1e-3, max_position_embeddings=40960)),
+        "deepseek-v3-4l": (DeepseekV3Config, dict(num_hidden_layers=4, first_k_dense_replace=1, num_nextn_predict_layers=1)),
+        "glm4.5-air-12l": (Glm4MoeConfig, dict(vocab_size=151552, hidden_size=4096, intermediate_size=10944,
+                                               num_hidden_layers=12, num_attention_heads=96, num_key_value_heads=8,
+                                               head_dim=128, n_routed_experts=128, num_experts_per_tok=8,
+                                               moe_intermediate_size=1408, n_shared_experts=1, first_k_dense_replace=1,
+                                               n_group=1, topk_group=1, routed_scaling_factor=1.0,
+                                               num_nextn_predict_layers=1, rope_theta=1e6)),
+        "tiny-llama": (LlamaConfig, dict(vocab_size=32000, hidden_size=256, intermediate_size=688, num_hidden_layers=2,
+                                         num_attention_heads=4, num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-6,
+                                         rope_theta=10000.0, max_position_embeddings=2048)),
+    }
+    cls, kw = presets[name]
+    kw = dict(kw)
+    kw.update(overrides)
+    return cls(**kw)

@@ -1,0 +1,541 @@
+"""Unified decoder-only transformer covering the Llama / Qwen2 / Qwen3 / Qwen3-MoE / DeepSeek-V3 / GLM-4.5 families.
+
+One implementation, configured by ``DecoderConfig``: GQA or MLA attention, optional per-head QK RMSNorm, full or
+partial rotary embedding, dense SwiGLU or MoE feed-forward (softmax / sigmoid routers, shared experts, leading dense
+layers) and multi-token-prediction (MTP) layers. Activations are kept 2-D ``[tokens, hidden]`` between blocks (token
+sharded when sequence parallel is on), exactly one fused qkv and one fused gate|up projection per layer, residual
+adds fused into the RMSNorm kernels.
+
+Reference behaviour reproduced: paddleformers/transformers/llama/modeling.py:71-642 (attention, decoder layer,
+causal LM), qwen3_moe/modeling.py:116-392 (QK-norm attention, sparse block), deepseek_v3/modeling.py:341-1128 (router,
+MLA, MTP layer), glm4_moe/modeling.py:135-385 (partial rope, router) and the criterion's loss normalisation
+(paddleformers/nn/criterion/sft_loss.py:44-57).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.utils.checkpoint
+
+from ..nn.moe import DenseMLP, MoELayer
+from ..ops import functional as F
+from ..parallel.tensor_parallel import (ColumnParallelLinear, GatherOp, RowParallelLinear, ScatterOp,
+                                        VocabParallelEmbedding, mark_as_sequence_parallel_parameter)
+from ..parallel.topology import get_parallel_state
+from ..transformers.conversion_utils import Rule, WeightMap, expand_layers
+from ..transformers.model_utils import PretrainedModel
+from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, LlamaConfig, Qwen2Config, Qwen3Config,
+                            Qwen3MoeConfig)
+
+
+@dataclass
+class BatchContext:
+    """Per-forward metadata shared by all layers."""
+
+    B: int
+    S: int
+    positions: Optional[torch.Tensor]   # [B*S] position ids (None = arange per sequence)
+    kend: Optional[torch.Tensor]        # [B, S] int32 document mask bounds (None = plain causal)
+    cos: torch.Tensor
+    sin: torch.Tensor
+
+
+@dataclass
+class CausalLMOutput:
+    loss: Optional[torch.Tensor] = None
+    logits: Optional[torch.Tensor] = None
+    hidden_states: Optional[torch.Tensor] = None
+    aux_loss: Optional[torch.Tensor] = None
+    mtp_losses: Optional[List[torch.Tensor]] = None
+    num_tokens: Optional[torch.Tensor] = None
+    past_key_values: Optional[object] = None
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, hidden_size: int, eps: float, sequence_parallel: bool = False, dtype=None, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden_size, dtype=dtype, device=device))
+        self.eps = eps
+        if sequence_parallel:
+            mark_as_sequence_parallel_parameter(self.weight)
+
+    def forward(self, x, residual=None):
+        return F.rms_norm(x, self.weight, self.eps, residual=residual)
+
+
+def _linear(in_f, out_f, bias, tp_plan, config, sections=None, dtype=None, device=None):
+    """Linear factory with a tensor-parallel plan ("colwise" | "rowwise" | None), like the reference's
+    ``Linear.create(..., tp_plan=...)`` (paddleformers/nn/linear.py:39-59)."""
+    tp = get_parallel_state().degrees.mp
+    sp = bool(getattr(config, "sequence_parallel", False))
+    if tp > 1 and tp_plan == "colwise":
+        return ColumnParallelLinear(in_f, out_f, bias=bias, sections=sections, sequence_parallel=sp, dtype=dtype, device=device)
+    if tp > 1 and tp_plan == "rowwise":
+        return RowParallelLinear(in_f, out_f, bias=bias, sequence_parallel=sp, dtype=dtype, device=device)
+    return nn.Linear(in_f, out_f, bias=bias, dtype=dtype, device=device)
+
+
+def _apply(mod, x):
+    if isinstance(mod, nn.Linear):
+        return F.linear(x, mod.weight, mod.bias)
+    return mod(x)
+
+
+class Attention(nn.Module):
+    """GQA attention with a fused qkv projection laid out as [q heads | k heads | v heads]."""
+
+    def __init__(self, config: DecoderConfig, layer_idx: int, dtype=None, device=None):
+        super().__init__()
+        tp = get_parallel_state().degrees.mp
+        self.config = config
+        self.D = config.head_dim
+        self.Hq_total, self.Hkv_total = config.num_attention_heads, config.num_key_value_heads
+        assert self.Hq_total % tp == 0 and self.Hkv_total % tp == 0, "heads must divide the tensor parallel degree"
+        self.Hq, self.Hkv = self.Hq_total // tp, self.Hkv_total // tp
+        self.rot = int(self.D * config.partial_rotary_factor)
+        H = config.hidden_size
+        secs = [self.Hq_total * self.D, self.Hkv_total * self.D, self.Hkv_total * self.D]
+        self.qkv_proj = _linear(H, sum(secs), config.attention_bias, "colwise", config, sections=secs, dtype=dtype, device=device)
+        self.o_proj = _linear(self.Hq_total * self.D, H, False, "rowwise", config, dtype=dtype, device=device)
+        self.use_qk_norm = config.use_qk_norm
+        if self.use_qk_norm:
+            self.q_norm = RMSNorm(self.D, config.rms_norm_eps, dtype=dtype, device=device)
+            self.k_norm = RMSNorm(self.D, config.rms_norm_eps, dtype=dtype, device=device)
+        self.scale = 1.0 / math.sqrt(self.D)
+
+    def forward(self, x2d: torch.Tensor, ctx: BatchContext, cache=None) -> torch.Tensor:
+        qkv = _apply(self.qkv_proj, x2d)
+        if self.use_qk_norm:
+            qkv = F.qk_norm_rope_packed(qkv, self.q_norm.weight, self.k_norm.weight, ctx.cos, ctx.sin, ctx.positions,
+                                        self.Hq, self.Hkv, self.D, self.rot, self.config.rms_norm_eps)
+        else:
+            qkv = F.rope_packed(qkv, ctx.cos, ctx.sin, ctx.positions, self.Hq, self.Hkv, self.D, self.rot)
+        if cache is not None:
+            out = cache.attend(self, qkv, ctx)
+        else:
+            out = F.flash_attention_qkvpacked(qkv, ctx.B, ctx.S, self.Hq, self.Hkv, self.D, True, ctx.kend, self.scale)
+        return _apply(self.o_proj, out)
+
+
+class MLAAttention(nn.Module):
+    """Multi-head latent attention (DeepSeek-V3), non-absorbed training form: low-rank q and kv projections with
+    RMSNorm on the latents, rotary embedding on a separate ``qk_rope_head_dim`` slice whose key part is shared by
+    all heads, q/k head dim = nope + rope, v head dim separate
+    (paddleformers/transformers/deepseek_v3/modeling.py:542-801)."""
+
+    def __init__(self, config: DecoderConfig, layer_idx: int, dtype=None, device=None):
+        super().__init__()
+        tp = get_parallel_state().degrees.mp
+        self.config = config
+        H = config.hidden_size
+        self.Hq_total = config.num_attention_heads
+        self.Hq = self.Hq_total // tp
+        self.nope, self.rope, self.vd = config.qk_nope_head_dim, config.qk_rope_head_dim, config.v_head_dim
+        self.qd = self.nope + self.rope
+        self.q_lora, self.kv_lora = config.q_lora_rank, config.kv_lora_rank
+        if self.q_lora:
+            self.q_a_proj = nn.Linear(H, self.q_lora, bias=False, dtype=dtype, device=device)
+            self.q_a_layernorm = RMSNorm(self.q_lora, config.rms_norm_eps, dtype=dtype, device=device)
+            self.q_b_proj = _linear(self.q_lora, self.Hq_total * self.qd, False, "colwise", config, dtype=dtype, device=device)
+        else:
+            self.q_proj = _linear(H, self.Hq_total * self.qd, False, "colwise", config, dtype=dtype, device=device)
+        self.kv_a_proj_with_mqa = nn.Linear(H, self.kv_lora + self.rope, bias=False, dtype=dtype, device=device)
+        self.kv_a_layernorm = RMSNorm(self.kv_lora, config.rms_norm_eps, dtype=dtype, device=device)
+        self.kv_b_proj = _linear(self.kv_lora, self.Hq_total * (self.nope + self.vd), False, "colwise", config, dtype=dtype, device=device)
+        self.o_proj = _linear(self.Hq_total * self.vd, H, False, "rowwise", config, dtype=dtype, device=device)
+        self.scale = 1.0 / math.sqrt(self.qd)
+        rs = config.rope_scaling
+        if rs and rs.get("mscale_all_dim"):
+            m = 0.1 * float(rs["mscale_all_dim"]) * math.log(float(rs.get("factor", 1.0))) + 1.0
+            self.scale = self.scale * m * m
+        self.sp = bool(getattr(config, "sequence_parallel", False)) and tp > 1
+        self.group = get_parallel_state().group("mp")
+
+    def forward(self, x2d, ctx: BatchContext, cache=None):
+        T = ctx.B * ctx.S
+        if self.q_lora:
+            qa = self.q_a_layernorm(F.linear(x2d, self.q_a_proj.weight))
+            q = _apply(self.q_b_proj, qa)
+        else:
+            q = _apply(self.q_proj, x2d)
+        ckv = F.linear(x2d, self.kv_a_proj_with_mqa.weight)
+        if self.sp:  # replicated projections ran on token shards: gather tokens for the per-head products
+            ckv = GatherOp.apply(ckv, self.group)
+        kv_lat, k_pe = ckv[:, : self.kv_lora], ckv[:, self.kv_lora:]
+        kv = _apply(self.kv_b_proj, self.kv_a_layernorm(kv_lat.contiguous()))
+        q = q.view(T, self.Hq, self.qd)
+        kv = kv.view(T, self.Hq, self.nope + self.vd)
+        q_pe = F.rope_heads(q[..., self.nope:].reshape(T, self.Hq * self.rope), ctx.cos, ctx.sin, ctx.positions,
+                            self.Hq, self.rope).view(T, self.Hq, self.rope)
+        k_pe = F.rope_heads(k_pe.contiguous(), ctx.cos, ctx.sin, ctx.positions, 1, self.rope).view(T, 1, self.rope)
+        qf = torch.cat([q[..., : self.nope], q_pe], dim=-1)
+        kf = torch.cat([kv[..., : self.nope], k_pe.expand(T, self.Hq, self.rope)], dim=-1)
+        v = kv[..., self.nope:]
+        out = F.flash_attention(qf.view(ctx.B, ctx.S, self.Hq, self.qd), kf.view(ctx.B, ctx.S, self.Hq, self.qd),
+                                v.reshape(ctx.B, ctx.S, self.Hq, self.vd), True, ctx.kend, self.scale)
+        return _apply(self.o_proj, out.reshape(T, self.Hq * self.vd))
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, config: DecoderConfig, layer_idx: int, dtype=None, device=None):
+        super().__init__()
+        sp = bool(getattr(config, "sequence_parallel", False)) and get_parallel_state().degrees.mp > 1
+        self.layer_idx = layer_idx
+        self.input_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps, sp, dtype=dtype, device=device)
+        self.post_attention_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps, sp, dtype=dtype, device=device)
+        attn_cls = MLAAttention if config.is_mla else Attention
+        self.self_attn = attn_cls(config, layer_idx, dtype=dtype, device=device)
+        if config.is_moe_layer(layer_idx):
+            self.mlp = MoELayer(config, dtype=dtype, device=device)
+        else:
+            self.mlp = DenseMLP(config.hidden_size, config.intermediate_size, config, bias=config.mlp_bias, dtype=dtype, device=device)
+
+    def forward(self, hidden, residual, ctx: BatchContext, cache=None):
+        """(branch output, residual stream) in, (branch output, residual stream) out; the add happens inside the
+        next RMSNorm kernel."""
+        if residual is None:
+            normed, residual = self.input_layernorm(hidden), hidden
+        else:
+            normed, residual = self.input_layernorm(hidden, residual)
+        attn = self.self_attn(normed, ctx, cache)
+        normed, residual = self.post_attention_layernorm(attn, residual)
+        return self.mlp(normed), residual
+
+
+class MTPLayer(nn.Module):
+    """Multi-token prediction block: h' = eh_proj([enorm(emb(tokens shifted by depth)); hnorm(h)]) -> decoder layer
+    (paddleformers/transformers/deepseek_v3/modeling.py:1032-1128)."""
+
+    def __init__(self, config: DecoderConfig, layer_idx: int, dtype=None, device=None):
+        super().__init__()
+        self.enorm = RMSNorm(config.hidden_size, config.rms_norm_eps, dtype=dtype, device=device)
+        self.hnorm = RMSNorm(config.hidden_size, config.rms_norm_eps, dtype=dtype, device=device)
+        self.eh_proj = nn.Linear(2 * config.hidden_size, config.hidden_size, bias=False, dtype=dtype, device=device)
+        self.block = DecoderLayer(config, layer_idx, dtype=dtype, device=device)
+        self.final_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps, dtype=dtype, device=device)
+
+    def forward(self, h2d, shifted_emb2d, ctx):
+        x = torch.cat([self.enorm(shifted_emb2d), self.hnorm(h2d)], dim=-1)
+        x = F.linear(x, self.eh_proj.weight)
+        out, res = self.block(x, None, ctx)
+        return self.final_layernorm(out, res)[0]
+
+
+class DecoderModel(nn.Module):
+    def __init__(self, config: DecoderConfig, dtype=None, device=None, layer_range: Optional[range] = None,
+                 with_embedding: bool = True, with_final_norm: bool = True):
+        super().__init__()
+        ps = get_parallel_state()
+        self.config = config
+        self.sp = bool(getattr(config, "sequence_parallel", False)) and ps.degrees.mp > 1
+        self.layer_range = layer_range if layer_range is not None else range(config.num_hidden_layers)
+        if with_embedding:
+            if ps.degrees.mp > 1:
+                self.embed_tokens = VocabParallelEmbedding(config.vocab_size, config.hidden_size, self.sp, dtype=dtype, device=device)
+            else:
+                self.embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size, dtype=dtype, device=device)
+        else:
+            self.embed_tokens = None
+        self.layers = nn.ModuleDict({str(i): DecoderLayer(config, i, dtype=dtype, device=device) for i in self.layer_range})
+        self.norm = RMSNorm(config.hidden_size, config.rms_norm_eps, self.sp, dtype=dtype, device=device) if with_final_norm else None
+        self._rope_cache = {}
+
+    # ------------------------------------------------------------------ helpers
+    def rope(self, device, length: int):
+        cfg = self.config
+        rot = int((cfg.qk_rope_head_dim if cfg.is_mla else cfg.head_dim * cfg.partial_rotary_factor))
+        n = max(length, 1)
+        key = (str(device), rot)
+        cached = self._rope_cache.get(key)
+        if cached is None or cached[0].shape[0] < n:
+            n = max(n, min(cfg.max_position_embeddings, 8192))
+            cached = F.rope_tables(n, rot, cfg.rope_theta, device, cfg.rope_scaling)
+            self._rope_cache[key] = cached
+        return cached
+
+    def make_context(self, input_ids, position_ids=None, kend=None) -> BatchContext:
+        B, S = input_ids.shape
+        max_pos = S if position_ids is None else max(S, int(self.config.max_position_embeddings))
+        cos, sin = self.rope(input_ids.device, max_pos)
+        pos = None
+        if position_ids is not None:
+            pos = position_ids.reshape(-1)
+        elif B > 1:
+            pos = torch.arange(S, device=input_ids.device).repeat(B)
+        return BatchContext(B, S, pos, kend, cos, sin)
+
+    def embed(self, input_ids):
+        if isinstance(self.embed_tokens, VocabParallelEmbedding):
+            h = self.embed_tokens(input_ids)
+            return h if h.dim() == 2 else h.reshape(-1, h.shape[-1])
+        h = F.embedding(input_ids, self.embed_tokens.weight).reshape(-1, self.config.hidden_size)
+        return h
+
+    def run_layers(self, hidden, residual, ctx, caches=None):
+        cfg = self.config
+        recompute = self.training and getattr(cfg, "recompute_granularity", None) == "full"
+        skip = set(getattr(cfg, "no_recompute_layers", None) or [])
+        for i in self.layer_range:
+            layer = self.layers[str(i)]
+            cache = caches[i] if caches is not None else None
+            if recompute and i not in skip and cache is None:
+                hidden, residual = torch.utils.checkpoint.checkpoint(
+                    layer, hidden, residual, ctx, None, use_reentrant=bool(getattr(cfg, "recompute_use_reentrant", False)))
+            else:
+                hidden, residual = layer(hidden, residual, ctx, cache)
+        return hidden, residual
+
+    def forward(self, input_ids, position_ids=None, kend=None, caches=None, ctx: Optional[BatchContext] = None):
+        ctx = ctx or self.make_context(input_ids, position_ids, kend)
+        h = self.embed(input_ids)
+        hidden, residual = self.run_layers(h, None, ctx, caches)
+        if self.norm is not None:
+            hidden = self.norm(hidden, residual)[0] if residual is not None else self.norm(hidden)
+        return hidden, ctx
+
+
+class DecoderForCausalLM(PretrainedModel):
+    config_class = DecoderConfig
+    base_model_prefix = "model"
+
+    def __init__(self, config: DecoderConfig, dtype=None, device=None):
+        super().__init__(config)
+        dtype = dtype if dtype is not None else _resolve_dtype(config.dtype)
+        ps = get_parallel_state()
+        self.tp = ps.degrees.mp
+        self.model = DecoderModel(config, dtype=dtype, device=device)
+        self.sp = self.model.sp
+        if config.tie_word_embeddings:
+            self.lm_head = None
+        elif self.tp > 1:
+            self.lm_head = ColumnParallelLinear(config.hidden_size, config.vocab_size, bias=False,
+                                                sequence_parallel=self.sp, dtype=dtype, device=device)
+        else:
+            self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False, dtype=dtype, device=device)
+        n_mtp = int(getattr(config, "num_nextn_predict_layers", 0) or 0)
+        self.mtp_layers = nn.ModuleList([MTPLayer(config, config.num_hidden_layers + i, dtype=dtype, device=device)
+                                         for i in range(n_mtp)])
+        self.ignore_index = -100
+        self.loss_accumulation_steps = 1   # set by the trainer: folded into the in-forward loss scale
+        self.post_init()
+
+    # ------------------------------------------------------------------ weights
+    def head_weight(self):
+        return self.model.embed_tokens.weight if self.lm_head is None else self.lm_head.weight
+
+    def _init_weights(self, module):
+        std = self.config.initializer_range
+        if isinstance(module, (nn.Linear, ColumnParallelLinear, RowParallelLinear)):
+            nn.init.normal_(module.weight, 0.0, std)
+            if getattr(module, "bias", None) is not None:
+                nn.init.zeros_(module.bias)
+        elif isinstance(module, (nn.Embedding, VocabParallelEmbedding)):
+            nn.init.normal_(module.weight, 0.0, std)
+        elif isinstance(module, RMSNorm):
+            nn.init.ones_(module.weight)
+        else:
+            from ..nn.moe import GroupedExperts, TopkRouter
+
+            if isinstance(module, GroupedExperts):
+                nn.init.normal_(module.gate_up_proj, 0.0, std)
+                nn.init.normal_(module.down_proj, 0.0, std)
+            elif isinstance(module, TopkRouter):
+                nn.init.normal_(module.weight, 0.0, std)
+
+    # ------------------------------------------------------------------ forward
+    def compute_logits(self, hidden2d):
+        w = self.head_weight()
+        if self.tp > 1 and self.lm_head is not None:
+            return self.lm_head(hidden2d)
+        return F.linear(hidden2d, w)
+
+    def _loss(self, hidden2d, labels_flat, scale):
+        """(scaled loss sum, token count) of the head + cross entropy on hidden states [T, H]."""
+        if self.tp > 1:
+            from ..parallel.vocab_parallel_loss import vocab_parallel_linear_cross_entropy
+
+            h = hidden2d
+            if self.sp:
+                h = GatherOp.apply(h, get_parallel_state().group("mp"))
+            return vocab_parallel_linear_cross_entropy(h, self.head_weight(), labels_flat, self.ignore_index, scale)
+        chunk = int(getattr(self.config, "loss_subbatch_sequence_length", -1) or -1)
+        return F.fused_linear_cross_entropy(hidden2d, self.head_weight(), labels_flat, self.ignore_index,
+                                            chunk if chunk > 0 else 2048, scale)
+
+    def forward(self, input_ids, labels=None, position_ids=None, attn_mask_startend_row_indices=None, kend=None,
+                caches=None, return_logits: Optional[bool] = None, **unused):
+        """``labels`` are next-token targets aligned with ``input_ids`` (already shifted by the data pipeline, as in
+        the reference's collators). ``attn_mask_startend_row_indices`` / ``kend``: int [B, S] FlashMask start rows."""
+        if kend is None and attn_mask_startend_row_indices is not None:
+            kend = attn_mask_startend_row_indices.reshape(input_ids.shape[0], -1)
+        hidden, ctx = self.model(input_ids, position_ids, kend, caches)
+        out = CausalLMOutput()
+        want_logits = return_logits if return_logits is not None else labels is None
+        if want_logits:
+            h = hidden
+            if self.sp:
+                h = GatherOp.apply(h, get_parallel_state().group("mp"))
+            logits = self.compute_logits(h)
+            if self.tp > 1 and self.lm_head is not None:
+                parts = [torch.empty_like(logits) for _ in range(self.tp)]
+                torch.distributed.all_gather(parts, logits.contiguous(), group=get_parallel_state().group("mp"))
+                logits = torch.cat(parts, dim=-1)
+            out.logits = logits.view(ctx.B, ctx.S, -1)
+        if labels is not None:
+            lab = labels.reshape(-1)
+            count = (lab != self.ignore_index).sum()
+            scale = 1.0 / (count.clamp(min=1).to(torch.float32) * float(self.loss_accumulation_steps))
+            loss, _ = self._loss(hidden, lab, scale)
+            out.num_tokens = count
+            if len(self.mtp_layers) > 0:
+                out.mtp_losses = self._mtp_losses(hidden, input_ids, labels, ctx, scale)
+                lam = float(getattr(self.config, "mtp_loss_scaling_factor", 0.1))
+                loss = loss + lam * torch.stack(out.mtp_losses).mean()
+            aux = [m.mlp.last_aux_loss for m in self.model.layers.values() if isinstance(m.mlp, MoELayer) and m.mlp.last_aux_loss is not None]
+            if aux:
+                out.aux_loss = torch.stack(aux).sum()
+            out.loss = loss
+        return out
+
+    def _mtp_losses(self, hidden, input_ids, labels, ctx, scale):
+        """Depth-k MTP head predicts token t+1+k from h_t and the embedding of token t+k; sequences are shifted left
+        and the tail positions are ignored (paddleformers/nn/criterion/sft_loss.py:188-247)."""
+        losses = []
+        h = hidden
+        ids, lab = input_ids, labels
+        if self.sp:
+            h = GatherOp.apply(h, get_parallel_state().group("mp"))
+        for k, layer in enumerate(self.mtp_layers, start=1):
+            ids = torch.cat([ids[:, 1:], ids[:, -1:]], dim=1)
+            lab = torch.cat([lab[:, 1:], torch.full_like(lab[:, -1:], self.ignore_index)], dim=1)
+            emb = F.embedding(ids, self.model.embed_tokens.weight).reshape(-1, self.config.hidden_size) \
+                if not isinstance(self.model.embed_tokens, VocabParallelEmbedding) else \
+                _full_tokens(self.model.embed_tokens(ids), self.sp)
+            h = layer(h, emb, ctx)
+            flat = lab.reshape(-1)
+            cnt = (flat != self.ignore_index).sum()
+            sc = 1.0 / (cnt.clamp(min=1).to(torch.float32) * float(self.loss_accumulation_steps))
+            saved_sp, self.sp = self.sp, False  # h is already token-complete
+            try:
+                l, _ = self._loss(h, flat, sc)
+            finally:
+                self.sp = saved_sp
+            losses.append(l)
+        return losses
+
+    # ------------------------------------------------------------------ checkpoint mapping
+    def weight_map(self) -> WeightMap:
+        return build_weight_map(self.config)
+
+    def get_hardware_flops_per_token(self, seq_len: int) -> float:
+        from ..utils.flops import model_flops_per_token
+
+        return model_flops_per_token(self.config, seq_len)
+
+
+def _full_tokens(x, sp):
+    if sp:
+        return GatherOp.apply(x.reshape(-1, x.shape[-1]), get_parallel_state().group("mp"))
+    return x.reshape(-1, x.shape[-1])
+
+
+def _resolve_dtype(name):
+    if isinstance(name, torch.dtype):
+        return name
+    return {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+            "float16": torch.float16, "fp16": torch.float16}.get(str(name).replace("torch.", ""), torch.float32)
+
+
+def build_weight_map(config: DecoderConfig) -> WeightMap:
+    """HF names -> fused internal parameters."""
+    L = "model.layers.{L}."
+    rules: List[Rule] = []
+    per_layer: List[Rule] = []
+    qkv_sizes = None
+    if config.is_mla:
+        pass  # MLA projections keep their HF names
+    else:
+        qkv_sizes = [config.num_attention_heads * config.head_dim, config.num_key_value_heads * config.head_dim,
+                     config.num_key_value_heads * config.head_dim]
+        per_layer.append(Rule(L + "self_attn.qkv_proj.weight", [L + "self_attn.q_proj.weight", L + "self_attn.k_proj.weight",
+                                                                 L + "self_attn.v_proj.weight"], "concat", 0, sizes=qkv_sizes))
+        if config.attention_bias:
+            per_layer.append(Rule(L + "self_attn.qkv_proj.bias", [L + "self_attn.q_proj.bias", L + "self_attn.k_proj.bias",
+                                                                   L + "self_attn.v_proj.bias"], "concat", 0, sizes=qkv_sizes))
+    dense_rule = Rule(L + "mlp.gate_up_proj.weight", [L + "mlp.gate_proj.weight", L + "mlp.up_proj.weight"], "concat", 0)
+    n_total = config.num_hidden_layers + int(getattr(config, "num_nextn_predict_layers", 0) or 0)
+    for i in range(config.num_hidden_layers):
+        rules.extend(expand_layers(per_layer, [i]))
+        if config.is_moe_layer(i):
+            E = config.num_experts
+            pre = f"model.layers.{i}.mlp."
+            rules.append(Rule(pre + "experts.gate_up_proj", [pre + "experts.{E}.gate_proj.weight", pre + "experts.{E}.up_proj.weight"],
+                              "stack_concat", 0, E, 2))
+            rules.append(Rule(pre + "experts.down_proj", [pre + "experts.{E}.down_proj.weight"], "stack", 0, E))
+            if config.n_shared_experts:
+                rules.append(Rule(pre + "shared_experts.gate_up_proj.weight",
+                                  [pre + "shared_experts.gate_proj.weight", pre + "shared_experts.up_proj.weight"], "concat", 0))
+        else:
+            rules.extend(expand_layers([dense_rule], [i]))
+    # MTP layers are stored by HF DeepSeek-V3 / GLM-4.5 as extra entries of model.layers
+    for k in range(n_total - config.num_hidden_layers):
+        i = config.num_hidden_layers + k
+        src, dst = f"model.layers.{i}.", f"mtp_layers.{k}."
+        for name in ("enorm.weight", "hnorm.weight", "eh_proj.weight"):
+            rules.append(Rule(dst + name, [src + name]))
+        rules.append(Rule(dst + "final_layernorm.weight", [src + "shared_head.norm.weight"]))
+        blk = dst + "block."
+        for name in ("input_layernorm.weight", "post_attention_layernorm.weight", "self_attn.o_proj.weight"):
+            rules.append(Rule(blk + name, [src + name]))
+        if config.is_mla:
+            for name in ("q_a_proj.weight", "q_a_layernorm.weight", "q_b_proj.weight", "kv_a_proj_with_mqa.weight",
+                         "kv_a_layernorm.weight", "kv_b_proj.weight"):
+                rules.append(Rule(blk + "self_attn." + name, [src + "self_attn." + name]))
+        else:
+            rules.append(Rule(blk + "self_attn.qkv_proj.weight", [src + "self_attn.q_proj.weight", src + "self_attn.k_proj.weight",
+                                                                 src + "self_attn.v_proj.weight"], "concat", 0, sizes=qkv_sizes))
+            if config.attention_bias:
+                rules.append(Rule(blk + "self_attn.qkv_proj.bias", [src + "self_attn.q_proj.bias", src + "self_attn.k_proj.bias",
+                                                                   src + "self_attn.v_proj.bias"], "concat", 0, sizes=qkv_sizes))
+            if config.use_qk_norm:
+                rules.append(Rule(blk + "self_attn.q_norm.weight", [src + "self_attn.q_norm.weight"]))
+                rules.append(Rule(blk + "self_attn.k_norm.weight", [src + "self_attn.k_norm.weight"]))
+        if config.is_moe_layer(i) or config.num_experts > 0:
+            E = config.num_experts
+            rules.append(Rule(blk + "mlp.gate.weight", [src + "mlp.gate.weight"]))
+            if config.topk_method == "noaux_tc":
+                rules.append(Rule(blk + "mlp.gate.e_score_correction_bias", [src + "mlp.gate.e_score_correction_bias"]))
+            rules.append(Rule(blk + "mlp.experts.gate_up_proj", [src + "mlp.experts.{E}.gate_proj.weight", src + "mlp.experts.{E}.up_proj.weight"],
+                              "stack_concat", 0, E, 2))
+            rules.append(Rule(blk + "mlp.experts.down_proj", [src + "mlp.experts.{E}.down_proj.weight"], "stack", 0, E))
+            if config.n_shared_experts:
+                rules.append(Rule(blk + "mlp.shared_experts.gate_up_proj.weight",
+                                  [src + "mlp.shared_experts.gate_proj.weight", src + "mlp.shared_experts.up_proj.weight"], "concat", 0))
+                rules.append(Rule(blk + "mlp.shared_experts.down_proj.weight", [src + "mlp.shared_experts.down_proj.weight"]))
+        else:
+            rules.append(Rule(blk + "mlp.gate_up_proj.weight", [src + "mlp.gate_proj.weight", src + "mlp.up_proj.weight"], "concat", 0))
+            rules.append(Rule(blk + "mlp.down_proj.weight", [src + "mlp.down_proj.weight"]))
+    return WeightMap(rules)
+
+
+def _family(name, cfg_cls):
+    cls = type(name, (DecoderForCausalLM,), {"config_class": cfg_cls, "__doc__": f"{cfg_cls.model_type} causal LM (unified decoder)."})
+    return cls
+
+
+LlamaForCausalLM = _family("LlamaForCausalLM", LlamaConfig)
+Qwen2ForCausalLM = _family("Qwen2ForCausalLM", Qwen2Config)
+Qwen3ForCausalLM = _family("Qwen3ForCausalLM", Qwen3Config)
+Qwen3MoeForCausalLM = _family("Qwen3MoeForCausalLM", Qwen3MoeConfig)
+DeepseekV3ForCausalLM = _family("DeepseekV3ForCausalLM", DeepseekV3Config)
+Glm4MoeForCausalLM = _family("Glm4MoeForCausalLM", Glm4MoeConfig)
+
+MODEL_MAPPING = {
+    "llama": LlamaForCausalLM, "mistral": LlamaForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
+    "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
+    "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,
+}

@@ -1,0 +1,338 @@
+"""Mixture-of-experts building blocks: routers, token permutation, expert MLPs and the MoE layer.
+
+Behaviour follows the reference's gates and layers:
+* score functions in fp32, greedy / group-limited / ``noaux_tc`` top-k with a correction bias that only affects the
+  selection, optional renormalisation and ``routed_scaling_factor``
+  (paddleformers/nn/moe_deepep/moe_gate.py:31-52, :275-362; paddleformers/transformers/deepseek_v3/modeling.py:341;
+  paddleformers/transformers/glm4_moe/modeling.py:333-385);
+* the Switch/HF load-balancing auxiliary loss (paddleformers/transformers/qwen3_moe/modeling.py:1135) and z-loss
+  (moe_gate.py:160-171), attached to the output with a pass-through autograd node
+  (paddleformers/nn/moe_deepep/modular_moe_layer.py:267-269);
+* stacked expert weights ``[E, 2I, H]`` / ``[E, H, I]`` (paddleformers/nn/experts.py:39-48), rows of every expert
+  padded to a multiple of 128 so that a single grouped GEMM covers all local experts
+  (paddleformers/cli/train/deepseek_v3_pretrain/moe_utils.py:143-262);
+* an expert-usage counter that feeds the aux-loss-free bias update callback (moe_gate.py:446-451).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as TF
+
+from ..ops import functional as F
+from ..parallel.topology import get_parallel_state
+
+
+class AddAuxiliaryLoss(torch.autograd.Function):
+    """Returns ``x`` unchanged and injects d(aux)/d(...) = scale into the graph of ``aux`` during backward."""
+
+    @staticmethod
+    def forward(ctx, x, aux):
+        ctx.save_for_backward(aux)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        (aux,) = ctx.saved_tensors
+        return g, torch.ones_like(aux)
+
+
+class TopkRouter(nn.Module):
+    def __init__(self, config, dtype=None, device=None):
+        super().__init__()
+        self.num_experts = config.num_experts
+        self.top_k = config.num_experts_per_tok
+        self.scoring = config.scoring_func
+        self.method = config.topk_method
+        self.n_group = max(int(config.n_group or 1), 1)
+        self.topk_group = max(int(config.topk_group or 1), 1)
+        self.norm_topk_prob = config.norm_topk_prob
+        self.scale = float(config.routed_scaling_factor or 1.0)
+        self.aux_coef = float(config.router_aux_loss_coef or 0.0)
+        self.z_coef = float(config.router_z_loss_coef or 0.0)
+        self.force_balance = bool(getattr(config, "moe_router_force_load_balancing", False))
+        # the router runs in fp32 like the reference's gate (weights kept fp32 regardless of the model dtype)
+        self.weight = nn.Parameter(torch.empty(self.num_experts, config.hidden_size, dtype=torch.float32, device=device))
+        self.weight.keep_fp32 = True
+        if self.method == "noaux_tc":
+            self.register_buffer("e_score_correction_bias", torch.zeros(self.num_experts, dtype=torch.float32, device=device))
+        else:
+            self.e_score_correction_bias = None
+        self.register_buffer("expert_usage", torch.zeros(self.num_experts, dtype=torch.int64, device=device), persistent=False)
+
+    def forward(self, x2d: torch.Tensor):
+        """x2d: [T, H] -> (topk_idx [T,k] int64, topk_weight [T,k] fp32, aux_loss scalar or None)."""
+        logits = TF.linear(x2d.float(), self.weight)
+        if self.scoring == "sigmoid":
+            scores = torch.sigmoid(logits)
+        else:
+            scores = torch.softmax(logits, dim=-1)
+        T, E = scores.shape
+        if self.force_balance:
+            base = torch.arange(T, device=x2d.device)[:, None] * self.top_k + torch.arange(self.top_k, device=x2d.device)[None]
+            idx = base % E
+        else:
+            sel = scores if self.e_score_correction_bias is None else scores + self.e_score_correction_bias[None]
+            if self.n_group > 1:
+                g = sel.view(T, self.n_group, E // self.n_group)
+                if self.method == "noaux_tc":
+                    gscore = g.topk(2, dim=-1)[0].sum(-1)
+                else:
+                    gscore = g.max(-1)[0]
+                gidx = gscore.topk(self.topk_group, dim=-1)[1]
+                gmask = torch.zeros_like(gscore).scatter_(1, gidx, 1.0)
+                sel = sel.masked_fill(~gmask[:, :, None].expand(-1, -1, E // self.n_group).reshape(T, E).bool(), float("-inf"))
+            idx = sel.topk(self.top_k, dim=-1)[1]
+        w = scores.gather(1, idx)
+        if self.norm_topk_prob and self.top_k > 1:
+            w = w / (w.sum(-1, keepdim=True) + 1e-20)
+        w = w * self.scale
+        with torch.no_grad():
+            self.expert_usage += torch.bincount(idx.reshape(-1), minlength=E)
+        aux = None
+        if self.training and (self.aux_coef > 0 or self.z_coef > 0):
+            aux = x2d.new_zeros((), dtype=torch.float32)
+            if self.aux_coef > 0:
+                probs = scores if self.scoring == "softmax" else scores / (scores.sum(-1, keepdim=True) + 1e-20)
+                frac = torch.zeros(E, dtype=torch.float32, device=x2d.device).scatter_add_(
+                    0, idx.reshape(-1), torch.ones(idx.numel(), dtype=torch.float32, device=x2d.device)) / max(T, 1)
+                aux = aux + self.aux_coef * E * (frac / self.top_k * probs.mean(0)).sum() * self.top_k
+            if self.z_coef > 0:
+                aux = aux + self.z_coef * torch.logsumexp(logits, dim=-1).pow(2).mean()
+        return idx, w, aux
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# permutation into expert-sorted, 128-row padded segments
+# ---------------------------------------------------------------------------------------------------------------
+def build_dispatch_plan(idx: torch.Tensor, num_local_experts: int, expert_offset: int = 0, block: int = 128):
+    """Sort (token, slot) pairs by expert and pad each expert segment to a multiple of ``block`` rows, entirely on
+    the device (no host synchronisation: the padded buffer has a static upper-bound size).
+
+    Returns (dest_row [T*k] int64 (-1 for pairs routed to non-local experts), block_expert [n_blocks] int32,
+    padded_rows int (static upper bound), counts [E_local])."""
+    T, k = idx.shape
+    flat = idx.reshape(-1) - expert_offset
+    local = (flat >= 0) & (flat < num_local_experts)
+    e = torch.where(local, flat, torch.full_like(flat, num_local_experts))
+    counts = torch.bincount(e, minlength=num_local_experts + 1)[:num_local_experts]
+    padded = (counts + block - 1) // block * block
+    seg_start = torch.cumsum(padded, 0) - padded
+    # rank of each pair inside its expert (stable): sort by expert, then position - first position of that expert
+    order = torch.argsort(e, stable=True)
+    sorted_e = e[order]
+    first = torch.cumsum(torch.bincount(sorted_e, minlength=num_local_experts + 1), 0)
+    first = torch.cat([first.new_zeros(1), first[:-1]])
+    rank_sorted = torch.arange(e.numel(), device=e.device) - first[sorted_e]
+    rank = torch.empty_like(rank_sorted)
+    rank[order] = rank_sorted
+    seg = torch.cat([seg_start, seg_start.new_zeros(1)])
+    dest = torch.where(local, seg[e] + rank, torch.full_like(e, -1))
+    max_rows = ((T * k + block - 1) // block + num_local_experts) * block
+    n_blocks = max_rows // block
+    # block -> expert table: block b belongs to expert j iff seg_start[j] <= b*block < seg_start[j] + padded[j]
+    bpos = torch.arange(n_blocks, device=e.device) * block
+    ends = seg_start + padded
+    be = torch.searchsorted(ends, bpos, right=True)
+    block_expert = torch.where(bpos < ends[-1] if num_local_experts > 0 else bpos < 0, be, torch.full_like(be, -1)).to(torch.int32)
+    return dest, block_expert, max_rows, counts
+
+
+class _PermuteFn(torch.autograd.Function):
+    """rows[dest[p]] = x[p // k] for every routed pair p with dest >= 0 (padding rows stay zero)."""
+
+    @staticmethod
+    def forward(ctx, x, dest, k, rows):
+        out = x.new_zeros((rows, x.shape[1]))
+        valid = dest >= 0
+        src_tok = torch.arange(dest.numel(), device=x.device) // k
+        out.index_copy_(0, dest[valid], x[src_tok[valid]])
+        ctx.save_for_backward(dest)
+        ctx.k, ctx.T = k, x.shape[0]
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (dest,) = ctx.saved_tensors
+        valid = dest >= 0
+        src_tok = torch.arange(dest.numel(), device=g.device) // ctx.k
+        dx = g.new_zeros((ctx.T, g.shape[1]), dtype=torch.float32)
+        dx.index_add_(0, src_tok[valid], g[dest[valid]].float())
+        return dx.to(g.dtype), None, None, None
+
+
+def unpermute_combine(y_rows: torch.Tensor, dest: torch.Tensor, weights: torch.Tensor, T: int) -> torch.Tensor:
+    """out[t] = sum_j weights[t, j] * y_rows[dest[t*k + j]] (pairs with dest < 0 contribute nothing)."""
+    k = weights.shape[1]
+    valid = (dest >= 0)
+    gathered = y_rows[dest.clamp(min=0)] * (weights.reshape(-1, 1) * valid[:, None]).to(y_rows.dtype)
+    return gathered.view(T, k, -1).sum(1)
+
+
+class GroupedExperts(nn.Module):
+    """Stacked SwiGLU experts; local experts only (E_local = E / ep)."""
+
+    def __init__(self, config, dtype=None, device=None):
+        super().__init__()
+        ps = get_parallel_state()
+        self.ep = ps.degrees.ep
+        self.num_experts = config.num_experts
+        assert self.num_experts % self.ep == 0
+        self.num_local = self.num_experts // self.ep
+        self.expert_offset = ps.rank_in("ep") * self.num_local if self.ep > 1 else 0
+        H, I = config.hidden_size, config.moe_intermediate_size
+        self.hidden, self.inter = H, I
+        self.gate_up_proj = nn.Parameter(torch.empty(self.num_local, 2 * I, H, dtype=dtype, device=device))
+        self.down_proj = nn.Parameter(torch.empty(self.num_local, H, I, dtype=dtype, device=device))
+        for p in (self.gate_up_proj, self.down_proj):
+            p.is_expert = True           # gradients are reduced over the moe_sharding group only
+            p.shard_spec = ("ep", 0, None)
+
+    def forward(self, rows: torch.Tensor, block_expert: torch.Tensor, counts: Optional[torch.Tensor] = None):
+        """rows: [R, H] expert-sorted with 128-row padded segments; returns [R, H]."""
+        if rows.is_cuda and rows.dtype == torch.bfloat16:
+            return _GroupedMlpFn.apply(rows, self.gate_up_proj, self.down_proj, block_expert)
+        out = torch.zeros_like(rows)
+        be = block_expert.tolist()
+        for b, e in enumerate(be):
+            if e < 0:
+                continue
+            seg = rows[b * 128:(b + 1) * 128]
+            gu = TF.linear(seg, self.gate_up_proj[e])
+            g, u = gu.chunk(2, -1)
+            out[b * 128:(b + 1) * 128] = TF.linear(TF.silu(g) * u, self.down_proj[e])
+        return out
+
+
+class _GroupedMlpFn(torch.autograd.Function):
+    """Two grouped tcgen05 GEMMs with the SwiGLU in the first epilogue. The backward runs grouped dgrad GEMMs and
+    per-expert wgrad GEMMs accumulating into fp32 ``main_grad`` when present."""
+
+    @staticmethod
+    def forward(ctx, rows, w_gu, w_down, block_expert):
+        E, N2, H = w_gu.shape
+        I = N2 // 2
+        R = rows.shape[0]
+        raw = torch.empty((R, N2), dtype=rows.dtype, device=rows.device)
+        act = torch.zeros((R, I), dtype=rows.dtype, device=rows.device)
+        F.gemm(rows, w_gu.view(E * N2, H), out=act, epi=F.EPI_SWIGLU_BF16, out2=raw, block_expert=block_expert, n_per_expert=N2)
+        out = torch.zeros((R, H), dtype=rows.dtype, device=rows.device)
+        F.gemm(act, w_down.view(E * H, I), out=out, block_expert=block_expert, n_per_expert=H)
+        ctx.save_for_backward(rows, w_gu, w_down, block_expert, raw)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        rows, w_gu, w_down, block_expert, raw = ctx.saved_tensors
+        E, N2, H = w_gu.shape
+        I = N2 // 2
+        R = rows.shape[0]
+        dout = dout.contiguous()
+        ops = torch.ops.pfb200
+        # d(act) = dout @ W_down[e]  (grouped, B stored [H, I] per expert = MN-major for this product)
+        dact = torch.zeros((R, I), dtype=rows.dtype, device=rows.device)
+        _grouped_dgrad(dout, w_down, dact, block_expert)
+        dgu, act = ops.swiglu_bwd(dact, raw, True)
+        drows = torch.zeros((R, H), dtype=rows.dtype, device=rows.device)
+        _grouped_dgrad(dgu, w_gu, drows, block_expert)
+        # weight gradients: one wgrad GEMM per local expert over its row segment
+        be = block_expert
+        dw_gu = _grouped_wgrad(dgu, rows, w_gu, be)
+        dw_down = _grouped_wgrad(dout, act, w_down, be)
+        return drows, dw_gu, dw_down, None
+
+
+def _grouped_dgrad(dy, w, out, block_expert):
+    """out[rows of e] = dy[rows of e] @ w[e], w: [E, N, K'] (contracts over N; the stacked weight is read MN-major,
+    no transposed copy)."""
+    E, N, Kp = w.shape
+    F.gemm(dy, w.view(E * N, Kp), out=out, b_mn=True, block_expert=block_expert, n_per_expert=Kp)
+
+
+def expert_row_table(block_expert: torch.Tensor, num_local: int) -> torch.Tensor:
+    """int32 [E, 2] = (first row, row count) of each expert's padded segment, from the block -> expert table."""
+    be = block_expert.to(torch.int64)
+    valid = be >= 0
+    cnt = torch.bincount(be[valid], minlength=num_local)[:num_local] * 128
+    start = torch.cumsum(cnt, 0) - cnt
+    return torch.stack([start, cnt], dim=1).to(torch.int32).contiguous()
+
+
+def _grouped_wgrad(dy, x, w, block_expert):
+    """dW[e] = dy[seg_e]^T @ x[seg_e] for all local experts in one launch; accumulates into w.main_grad when
+    present."""
+    E, N, K = w.shape
+    mg = getattr(w, "main_grad", None)
+    target = mg.view(E, N, K) if mg is not None else torch.zeros((E, N, K), dtype=torch.float32, device=w.device)
+    torch.ops.pfb200.gemm_wgrad_grouped(dy, x, target, expert_row_table(block_expert, E))
+    return None if mg is not None else target.to(w.dtype)
+
+
+class DenseMLP(nn.Module):
+    """SwiGLU MLP with a fused gate|up projection (paddleformers/nn/mlp.py:113-130)."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, config, bias: bool = False, tp: bool = True,
+                 dtype=None, device=None):
+        super().__init__()
+        from ..parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear
+
+        sp = bool(getattr(config, "sequence_parallel", False)) and tp
+        if tp and get_parallel_state().degrees.mp > 1:
+            self.gate_up_proj = ColumnParallelLinear(hidden_size, 2 * intermediate_size, bias=bias,
+                                                     sections=[intermediate_size, intermediate_size],
+                                                     sequence_parallel=sp, epilogue="swiglu", dtype=dtype, device=device)
+            self.down_proj = RowParallelLinear(intermediate_size, hidden_size, bias=bias, sequence_parallel=sp,
+                                               dtype=dtype, device=device)
+            self._tp = True
+        else:
+            self.gate_up_proj = nn.Linear(hidden_size, 2 * intermediate_size, bias=bias, dtype=dtype, device=device)
+            self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=bias, dtype=dtype, device=device)
+            self._tp = False
+
+    def forward(self, x):
+        if self._tp:
+            return self.down_proj(self.gate_up_proj(x))
+        if self.gate_up_proj.bias is None:
+            act = F.linear_swiglu(x, self.gate_up_proj.weight)
+        else:
+            act = F.swiglu(F.linear(x, self.gate_up_proj.weight, self.gate_up_proj.bias))
+        return F.linear(act, self.down_proj.weight, self.down_proj.bias)
+
+
+class MoELayer(nn.Module):
+    """Router -> dispatch (local permutation or expert-parallel exchange) -> grouped experts -> weighted combine,
+    plus shared experts (paddleformers/nn/moe_deepep/modular_moe_layer.py:236-278)."""
+
+    def __init__(self, config, dtype=None, device=None):
+        super().__init__()
+        self.config = config
+        self.gate = TopkRouter(config, dtype=dtype, device=device)
+        self.experts = GroupedExperts(config, dtype=dtype, device=device)
+        self.shared_experts = None
+        if config.n_shared_experts:
+            si = config.shared_expert_intermediate_size or config.moe_intermediate_size * config.n_shared_experts
+            self.shared_experts = DenseMLP(config.hidden_size, si, config, tp=False, dtype=dtype, device=device)
+        self.ep = get_parallel_state().degrees.ep
+        self.last_aux_loss = None
+
+    def forward(self, x2d: torch.Tensor) -> torch.Tensor:
+        T, H = x2d.shape
+        idx, w, aux = self.gate(x2d)
+        if self.ep > 1:
+            from ..parallel.expert_parallel import ep_moe_forward
+
+            y = ep_moe_forward(self, x2d, idx, w)
+        else:
+            dest, block_expert, rows, counts = build_dispatch_plan(idx, self.experts.num_local, 0)
+            xr = _PermuteFn.apply(x2d, dest, idx.shape[1], rows)
+            yr = self.experts(xr, block_expert, counts)
+            y = unpermute_combine(yr, dest, w, T)
+        if self.shared_experts is not None:
+            y = y + self.shared_experts(x2d)
+        self.last_aux_loss = aux.detach() if aux is not None else None
+        if aux is not None:
+            y = AddAuxiliaryLoss.apply(y, aux)
+        return y

@@ -51,6 +51,16 @@ def flash_attention_backward(dout, q, k, v, out, lse, causal, kend, kmin, kmax, 
     return _blocked_backward(dout, q, k, v, out, lse, causal, kend, scale)
 
 
+def flash_attention_backward_into(dout, q, k, v, out, lse, causal, kend, kmin, kmax, scale, dq, dk, dv):
+    """Same as ``flash_attention_backward`` but writes into caller-provided (possibly strided) dq / dk / dv views."""
+    B, S, Hq, D = q.shape
+    if q.is_cuda and D == 128 and _has_kernel("attn_bwd"):
+        torch.ops.pfb200.attn_bwd(dout.contiguous(), q, k, v, out, lse, dq, dk, dv, B, S, scale, causal, kend, kmin, kmax)
+        return
+    a, b, c = _blocked_backward(dout, q, k, v, out, lse, causal, kend, scale)
+    dq.copy_(a); dk.copy_(b); dv.copy_(c)
+
+
 def _blocked_backward(dout, q, k, v, out, lse, causal, kend, scale):
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]

@@ -1,0 +1,162 @@
+"""Kernel micro-benchmarks: ``python -m paddleformers_b200.ops.bench_kernels [--what gemm,attn,elementwise]``.
+
+Times each kernel with CUDA events on the launching stream after warm-up, flushing L2 between timed launches by
+writing a 256 MiB buffer, and prints achieved TFLOP/s or GB/s next to the library kernel of the same shape
+(torch.matmul / SDPA) and, when ``MEASURED_PEAKS.json`` sits in the working directory, the fraction of the measured
+peak.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import functional as F
+
+
+def _peaks():
+    for p in ("MEASURED_PEAKS.json", os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")):
+        if os.path.exists(p):
+            with open(p) as f:
+                return json.load(f)
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "fallback": True}
+
+
+_flush = None
+
+
+def timeit(fn, iters=10, warmup=3, flush=True):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush:
+            _flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters  # ms
+
+
+def bench_gemm(rows):
+    peaks = _peaks()
+    shapes = [
+        # (name, M, N, K, a_mn, b_mn, epi)
+        ("qkv fwd", 4096, 6144, 4096, False, False, F.EPI_STORE_BF16),
+        ("o fwd", 4096, 4096, 4096, False, False, F.EPI_STORE_BF16),
+        ("gate_up fwd", 4096, 28672, 4096, False, False, F.EPI_STORE_BF16),
+        ("gate_up+swiglu", 4096, 28672, 4096, False, False, F.EPI_SWIGLU_BF16),
+        ("down fwd", 4096, 4096, 14336, False, False, F.EPI_STORE_BF16),
+        ("gate_up dgrad", 4096, 4096, 28672, False, True, F.EPI_STORE_BF16),
+        ("down dgrad", 4096, 14336, 4096, False, True, F.EPI_STORE_BF16),
+        ("gate_up wgrad", 28672, 4096, 4096, True, True, F.EPI_ACCUM_F32),
+        ("down wgrad", 4096, 14336, 4096, True, True, F.EPI_ACCUM_F32),
+        ("lm_head 2k", 2048, 128256, 4096, False, False, F.EPI_STORE_BF16),
+        ("square 8k", 8192, 8192, 8192, False, False, F.EPI_STORE_BF16),
+    ]
+    for name, M, N, K, a_mn, b_mn, epi in shapes:
+        a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=torch.bfloat16)
+        b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
+        if epi == F.EPI_ACCUM_F32:
+            out = torch.zeros(M, N, device="cuda", dtype=torch.float32)
+        elif epi == F.EPI_SWIGLU_BF16:
+            out = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
+        else:
+            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        flops = 2.0 * M * N * K
+        res = {}
+        for bn in (128, 256):
+            ms = timeit(lambda: F.gemm(a, b, out=out, a_mn=a_mn, b_mn=b_mn, epi=epi, force_bn=bn))
+            res[bn] = flops / ms / 1e9
+        am = a.t() if a_mn else a
+        bm = b if b_mn else b.t()
+        ms_lib = timeit(lambda: torch.matmul(am, bm))
+        lib = flops / ms_lib / 1e9
+        best = max(res.values())
+        rows.append(f"gemm {name:16s} M={M} N={N} K={K}: bn128 {res[128]:7.1f} bn256 {res[256]:7.1f} TFLOP/s | "
+                    f"torch.matmul {lib:7.1f} | best/measured-peak {best / peaks['bf16_tflops']:.2f}")
+        print(rows[-1], flush=True)
+        del a, b, out
+    F.check_kernel_status()
+
+
+def bench_attn(rows):
+    for (B, S, Hq, Hkv) in [(1, 4096, 32, 8), (2, 4096, 32, 4), (1, 8192, 32, 8)]:
+        q = torch.randn(B, S, Hq, 128, device="cuda", dtype=torch.bfloat16)
+        k = torch.randn(B, S, Hkv, 128, device="cuda", dtype=torch.bfloat16)
+        v = torch.randn(B, S, Hkv, 128, device="cuda", dtype=torch.bfloat16)
+        flops = 4.0 * B * Hq * S * S * 128 / 2
+        res = {}
+        for mode in (True, False):
+            F.set_attention_options(p_in_tmem=mode)
+            ms = timeit(lambda: F.flash_attention(q, k, v, causal=True))
+            res[mode] = flops / ms / 1e9
+        F.set_attention_options(p_in_tmem=True)
+        qs, ks, vs = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+        ms_lib = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(qs, ks, vs, is_causal=True, enable_gqa=True))
+        rows.append(f"attn fwd B={B} S={S} Hq={Hq} Hkv={Hkv}: P-in-TMEM {res[True]:7.1f} P-in-smem {res[False]:7.1f} TFLOP/s | "
+                    f"torch SDPA {flops / ms_lib / 1e9:7.1f}")
+        print(rows[-1], flush=True)
+        # backward (whatever implementation is active)
+        q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
+        out = F.flash_attention(q, k, v, causal=True)
+        g = torch.randn_like(out)
+        ms_b = timeit(lambda: torch.autograd.grad(out, (q, k, v), g, retain_graph=True), iters=5)
+        rows.append(f"attn bwd B={B} S={S}: {2.5 * flops / ms_b / 1e9:7.1f} TFLOP/s ({ms_b:.2f} ms)")
+        print(rows[-1], flush=True)
+    F.check_kernel_status()
+
+
+def bench_elementwise(rows):
+    peaks = _peaks()
+    T, H, I = 8192, 4096, 14336
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: torch.ops.pfb200.rms_norm_fwd(x, None, w, 1e-5))
+    rows.append(f"rms_norm fwd [{T},{H}]: {2 * x.numel() * 2 / ms / 1e6:7.1f} GB/s ({2 * x.numel() * 2 / ms / 1e6 / peaks['hbm_gbs']:.2f} of measured copy)")
+    print(rows[-1], flush=True)
+    gu = torch.randn(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: torch.ops.pfb200.swiglu_fwd(gu))
+    rows.append(f"swiglu fwd [{T},{2 * I}]: {3 * T * I * 2 / ms / 1e6:7.1f} GB/s")
+    print(rows[-1], flush=True)
+    n = 1 << 28
+    p, m, v, g = (torch.zeros(n, device="cuda") for _ in range(4))
+    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    sc = torch.tensor([1e-3, 1.0, 0.1, 0.05, 0.0], device="cuda")
+    ms = timeit(lambda: torch.ops.pfb200.adamw_step(p, m, v, g, p16, sc, 0.9, 0.95, 1e-8, 0.1), flush=False)
+    rows.append(f"adamw {n} elems: {n * 30 / ms / 1e6:7.1f} GB/s ({n * 30 / ms / 1e6 / peaks['hbm_gbs']:.2f} of measured copy)")
+    print(rows[-1], flush=True)
+    logits = torch.randn(2048, 128256, device="cuda", dtype=torch.bfloat16)
+    labels = torch.randint(0, 128256, (2048,), device="cuda")
+    loss = torch.empty(2048, device="cuda")
+    d = torch.empty(1, device="cuda")
+    one = torch.ones(1, device="cuda")
+    ms = timeit(lambda: torch.ops.pfb200.cross_entropy(logits, labels, loss, d, d, d, one, 0, -100, 0, True))
+    rows.append(f"cross_entropy [2048,128256]: {ms:.3f} ms, {logits.numel() * 2 * 2 / ms / 1e6:7.1f} GB/s (read+write once)")
+    print(rows[-1], flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="gemm,attn,elementwise")
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args()
+    rows = []
+    for w in args.what.split(","):
+        {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise}[w](rows)
+    if args.out:
+        with open(args.out, "w") as f:
+            f.write("\n".join(rows) + "\n")
+
+
+if __name__ == "__main__":
+    main()

@@ -561,3 +561,113 @@ def fused_linear_cross_entropy(h: torch.Tensor, weight: torch.Tensor, labels: to
     if loss_scale is not None:
         loss = loss * loss_scale
     return loss, cnt
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Packed-qkv attention (no slicing in autograd: one gradient buffer for q, k and v)
+# ----------------------------------------------------------------------------------------------------------------
+def _packed_views(qkv2d, B, S, Hq, Hkv, D):
+    T = B * S
+    q = qkv2d[:, : Hq * D].view(T, Hq, D)
+    k = qkv2d[:, Hq * D: (Hq + Hkv) * D].view(T, Hkv, D)
+    v = qkv2d[:, (Hq + Hkv) * D: (Hq + 2 * Hkv) * D].view(T, Hkv, D)
+    return q, k, v
+
+
+class _FlashAttnPackedFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv2d, B, S, Hq, Hkv, D, causal, kend, scale):
+        q, k, v = _packed_views(qkv2d, B, S, Hq, Hkv, D)
+        out = torch.empty((B * S, Hq, D), dtype=qkv2d.dtype, device=qkv2d.device)
+        kmin = kmax = None
+        if kend is not None:
+            kend = kend.to(torch.int32).contiguous()
+            kmin, kmax = _kend_tiles(kend, S)
+        lse = _ops().attn_fwd(q, k, v, out, B, S, scale, causal, kend, kmin, kmax, _attn_backend["p_in_tmem"])
+        e = torch.empty(0)
+        ctx.save_for_backward(qkv2d, out, lse, kend if kend is not None else e, kmin if kmin is not None else e,
+                              kmax if kmax is not None else e)
+        ctx.meta = (B, S, Hq, Hkv, D, causal, scale, kend is not None)
+        return out.view(B * S, Hq * D)
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv2d, out, lse, kend, kmin, kmax = ctx.saved_tensors
+        B, S, Hq, Hkv, D, causal, scale, has_kend = ctx.meta
+        from . import attention_bwd
+
+        q, k, v = _packed_views(qkv2d, B, S, Hq, Hkv, D)
+        dqkv = torch.empty_like(qkv2d)
+        dq, dk, dv = _packed_views(dqkv, B, S, Hq, Hkv, D)
+        attention_bwd.flash_attention_backward_into(
+            dout.reshape(B, S, Hq, D), q.view(B, S, Hq, D), k.view(B, S, Hkv, D), v.view(B, S, Hkv, D),
+            out.view(B, S, Hq, D), lse, causal, kend if has_kend else None, kmin if has_kend else None,
+            kmax if has_kend else None, scale, dq.view(B, S, Hq, D), dk.view(B, S, Hkv, D), dv.view(B, S, Hkv, D))
+        return dqkv, None, None, None, None, None, None, None, None
+
+
+def flash_attention_qkvpacked(qkv2d, B: int, S: int, Hq: int, Hkv: int, D: int, causal: bool = True,
+                              kend: Optional[torch.Tensor] = None, scale: Optional[float] = None) -> torch.Tensor:
+    """Attention on a fused [B*S, (Hq + 2*Hkv) * D] projection (q heads | k heads | v heads). Returns [B*S, Hq*D]."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if use_cuda_kernels(qkv2d) and qkv2d.dtype == torch.bfloat16 and D == 128:
+        return _FlashAttnPackedFn.apply(qkv2d, B, S, Hq, Hkv, D, causal, kend, scale)
+    q, k, v = _packed_views(qkv2d, B, S, Hq, Hkv, D)
+    out = flash_attention(q.reshape(B, S, Hq, D), k.reshape(B, S, Hkv, D), v.reshape(B, S, Hkv, D), causal, kend, scale)
+    return out.reshape(B * S, Hq * D)
+
+
+class _QkNormRopePackedFn(torch.autograd.Function):
+    """qkv -> new packed buffer with q and k per-head RMS-normalised and rotated, v copied."""
+
+    @staticmethod
+    def forward(ctx, qkv2d, qw, kw, cos, sin, positions, Hq, Hkv, D, rot, eps):
+        ops = _ops()
+        out = torch.empty_like(qkv2d)
+        qi, ki = qkv2d[:, : Hq * D], qkv2d[:, Hq * D: (Hq + Hkv) * D]
+        qo, ko = out[:, : Hq * D], out[:, Hq * D: (Hq + Hkv) * D]
+        rq = ops.qk_norm_rope_fwd(qi, qo, qw, positions, cos, sin, Hq, D, rot, eps)
+        rk = ops.qk_norm_rope_fwd(ki, ko, kw, positions, cos, sin, Hkv, D, rot, eps)
+        out[:, (Hq + Hkv) * D:].copy_(qkv2d[:, (Hq + Hkv) * D:])
+        ctx.save_for_backward(qkv2d, qw, kw, rq, rk, cos, sin, positions if positions is not None else torch.empty(0))
+        ctx.meta = (Hq, Hkv, D, rot, positions is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv2d, qw, kw, rq, rk, cos, sin, pos = ctx.saved_tensors
+        Hq, Hkv, D, rot, has_pos = ctx.meta
+        ops = _ops()
+        pos = pos if has_pos else None
+        if dout.stride(-1) != 1:
+            dout = dout.contiguous()
+        dx = torch.empty_like(qkv2d)
+        outs = []
+        for (lo, hi, nh, w, r) in ((0, Hq * D, Hq, qw, rq), (Hq * D, (Hq + Hkv) * D, Hkv, kw, rk)):
+            mg = getattr(w, "main_grad", None)
+            dnw = mg if mg is not None else torch.zeros(D, dtype=torch.float32, device=dx.device)
+            ops.qk_norm_rope_bwd(dout[:, lo:hi], qkv2d[:, lo:hi], w, r, dx[:, lo:hi], dnw, pos, cos, sin, nh, D, rot)
+            outs.append(None if mg is not None else dnw.to(w.dtype))
+        dx[:, (Hq + Hkv) * D:].copy_(dout[:, (Hq + Hkv) * D:])
+        return dx, outs[0], outs[1], None, None, None, None, None, None, None, None
+
+
+def qk_norm_rope_packed(qkv2d, q_norm_w, k_norm_w, cos, sin, positions, Hq, Hkv, D, rot_dim=None, eps=1e-6):
+    """Per-head RMSNorm + rotary on the q and k heads of a packed qkv projection; v passes through."""
+    rot = rot_dim or D
+    if use_cuda_kernels(qkv2d) and qkv2d.dtype == torch.bfloat16:
+        pos32 = positions.to(torch.int32) if positions is not None else None
+        return _QkNormRopePackedFn.apply(qkv2d, q_norm_w, k_norm_w, cos, sin, pos32, Hq, Hkv, D, rot, eps)
+    q = qk_norm_rope(qkv2d[:, : Hq * D], q_norm_w, cos, sin, positions, Hq, D, rot, eps)
+    k = qk_norm_rope(qkv2d[:, Hq * D: (Hq + Hkv) * D], k_norm_w, cos, sin, positions, Hkv, D, rot, eps)
+    return torch.cat([q, k, qkv2d[:, (Hq + Hkv) * D:]], dim=-1)
+
+
+def rope_packed(qkv2d, cos, sin, positions, Hq, Hkv, D, rot_dim=None):
+    """Rotary embedding on the q and k heads of a packed qkv projection, in place on CUDA (the producing GEMM does
+    not need its output for its own backward)."""
+    rot = rot_dim or D
+    if use_cuda_kernels(qkv2d) and qkv2d.dtype == torch.bfloat16:
+        pos32 = positions.to(torch.int32) if positions is not None else None
+        return _RopeFn.apply(qkv2d, cos, sin, pos32, Hq + Hkv, D, rot)
+    return rope_heads(qkv2d, cos, sin, positions, Hq + Hkv, D, rot)

@@ -1,0 +1,187 @@
+"""Training checkpoints: save, completeness detection, resume, optimizer-state resharding, async writes, rotation.
+
+Directory layout of ``checkpoint-N`` (roles of the reference's formats in paddleformers/trainer/trainer.py:4730-4958,
+paddleformers/trainer/utils/sharding_io.py:267-920 and paddleformers/trainer/unified_checkpoint/):
+
+* ``model*.safetensors`` (+ index) and ``config.json`` — HF-compatible weights gathered over tp / ep
+  (``PretrainedModel.save_pretrained``);
+* ``optimizer/shard_<domain>_<rank>of<size>.pt`` — each sharding rank's fp32 master weights and Adam moments with the
+  flat-buffer layout (``offsets``) needed to re-cut them for another sharding degree (``reshard_optimizer_state``);
+* ``trainer_state.json``, ``scheduler.json``, ``rng_state_<rank>.pt`` (python / numpy / torch CPU / CUDA generators);
+* ``saved_signal_<rank>`` written last by every rank and ``.checkpoint_done`` by rank 0 once all signals exist: a
+  directory without them is an interrupted save and is skipped by ``get_last_checkpoint``.
+
+``async_save`` moves tensors to host memory on the training thread and performs file IO on a background thread; the
+next save (or the end of training) joins it first.
+"""
+from __future__ import annotations
+
+import json
+import os
+import random
+import shutil
+import threading
+import time
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..utils.log import logger
+from .trainer_utils import PREFIX_CHECKPOINT_DIR, _re_checkpoint, checkpoint_is_complete
+
+_pending: List[threading.Thread] = []
+
+
+def _barrier():
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+
+
+def wait_for_pending_saves():
+    while _pending:
+        _pending.pop().join()
+
+
+def _rng_state() -> Dict[str, object]:
+    st = {"python": random.getstate(), "numpy": np.random.get_state(), "cpu": torch.get_rng_state()}
+    if torch.cuda.is_available():
+        st["cuda"] = torch.cuda.get_rng_state()
+    return st
+
+
+def _set_rng_state(st):
+    random.setstate(st["python"])
+    np.random.set_state(st["numpy"])
+    torch.set_rng_state(st["cpu"])
+    if "cuda" in st and torch.cuda.is_available():
+        torch.cuda.set_rng_state(st["cuda"])
+
+
+def save_checkpoint(trainer, out_dir: str) -> None:
+    args, ps = trainer.args, trainer.ps
+    rank = args.process_index
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    wait_for_pending_saves()
+    os.makedirs(os.path.join(out_dir, "optimizer"), exist_ok=True)
+    # 1. model weights (collective: tp gathers)
+    trainer.model.save_pretrained(out_dir)
+    # 2. this rank's optimizer shards (moved to host now, written below or in the background)
+    opt_state = trainer.optimizer.state_dict()
+    files = {}
+    for name, dom in opt_state["domains"].items():
+        fname = f"shard_{name}_{dom['shard_rank']:03d}of{dom['shard_size']:03d}_r{rank:05d}.pt"
+        files[fname] = {"step": opt_state["step"], "lr": opt_state["lr"], "domain": name, **dom}
+    rng = _rng_state()
+    sched = trainer.lr_scheduler.state_dict()
+    state_json = None
+    if rank == 0:
+        state_json = trainer.state
+
+    def write():
+        for fname, payload in files.items():
+            tmp = os.path.join(out_dir, "optimizer", fname + ".tmp")
+            torch.save(payload, tmp)
+            os.replace(tmp, os.path.join(out_dir, "optimizer", fname))
+        torch.save(rng, os.path.join(out_dir, f"rng_state_{rank}.pt"))
+        if rank == 0:
+            state_json.save_to_json(os.path.join(out_dir, "trainer_state.json"))
+            with open(os.path.join(out_dir, "scheduler.json"), "w") as f:
+                json.dump(sched, f)
+            with open(os.path.join(out_dir, "save_meta.json"), "w") as f:
+                json.dump({"num_writers": world, "degrees": ps.degrees.__dict__, "time": time.time()}, f)
+            with open(os.path.join(out_dir, "training_args.json"), "w") as f:
+                f.write(args.to_json_string())
+        with open(os.path.join(out_dir, f"saved_signal_{rank}"), "w") as f:
+            f.write("done")
+        if rank == 0:
+            # completeness marker once every writer has signalled (polls the shared file system)
+            deadline = time.time() + 600
+            while time.time() < deadline:
+                have = len([x for x in os.listdir(out_dir) if x.startswith("saved_signal_")])
+                if have >= world:
+                    with open(os.path.join(out_dir, ".checkpoint_done"), "w") as f:
+                        f.write(str(world))
+                    break
+                time.sleep(0.05)
+
+    if args.async_save:
+        t = threading.Thread(target=write, daemon=False)
+        t.start()
+        _pending.append(t)
+    else:
+        write()
+        _barrier()
+    logger.info(f"saved checkpoint to {out_dir}")
+
+
+def load_checkpoint(trainer, path: str) -> None:
+    from .trainer_callback import TrainerState
+
+    if not checkpoint_is_complete(path):
+        raise RuntimeError(f"checkpoint {path} is incomplete (interrupted save): refusing to resume from it")
+    args, ps = trainer.args, trainer.ps
+    rank = args.process_index
+    trainer.model.load_hf_checkpoint(path)
+    opt = trainer.optimizer
+    opt_dir = os.path.join(path, "optimizer")
+    sd = {"domains": {}}
+    for dom in opt.domains:
+        want = f"shard_{dom.name}_{dom.shard_rank:03d}of{dom.shard_size:03d}_"
+        cands = sorted(f for f in os.listdir(opt_dir) if f.startswith(want) and f.endswith(".pt"))
+        if cands:
+            payload = torch.load(os.path.join(opt_dir, cands[0]), map_location="cpu", weights_only=False)
+        else:
+            payload = reshard_optimizer_state(opt_dir, dom.name, dom.shard_rank, dom.shard_size, dom.numel)
+        sd["domains"][dom.name] = payload
+        sd["step"], sd["lr"] = payload["step"], payload["lr"]
+    opt.load_state_dict(sd)
+    st_file = os.path.join(path, "trainer_state.json")
+    if os.path.exists(st_file):
+        loaded = TrainerState.load_from_json(st_file)
+        loaded.is_world_process_zero = trainer.state.is_world_process_zero
+        trainer.state = loaded
+    with open(os.path.join(path, "scheduler.json")) as f:
+        trainer.lr_scheduler.load_state_dict(json.load(f))
+    rng_file = os.path.join(path, f"rng_state_{rank}.pt")
+    if os.path.exists(rng_file):
+        _set_rng_state(torch.load(rng_file, weights_only=False))
+    logger.info(f"resumed from {path} at step {trainer.state.global_step}")
+
+
+def reshard_optimizer_state(opt_dir: str, domain: str, new_rank: int, new_size: int, numel: int) -> Dict[str, object]:
+    """Re-cut a domain saved with another sharding degree: concatenates the saved shards that overlap the new slice
+    (the flat layout is independent of the sharding degree up to tail padding)."""
+    shards = {}
+    for f in os.listdir(opt_dir):
+        if f.startswith(f"shard_{domain}_") and f.endswith(".pt"):
+            p = torch.load(os.path.join(opt_dir, f), map_location="cpu", weights_only=False)
+            shards[p["shard_rank"]] = p
+    if not shards:
+        raise FileNotFoundError(f"no optimizer shards for domain {domain} in {opt_dir}")
+    old_size = next(iter(shards.values()))["shard_size"]
+    if len(shards) != old_size:
+        raise RuntimeError(f"optimizer domain {domain}: found {len(shards)} of {old_size} shards")
+    any_p = shards[0]
+    out = {"step": any_p["step"], "lr": any_p["lr"], "domain": domain, "offsets": any_p["offsets"], "numel": numel,
+           "shard_rank": new_rank, "shard_size": new_size}
+    n_new = numel // new_size
+    lo, hi = new_rank * n_new, (new_rank + 1) * n_new
+    for key in ("master", "exp_avg", "exp_avg_sq"):
+        full = torch.cat([shards[r][key] for r in range(old_size)])
+        if full.numel() < hi:
+            full = torch.cat([full, full.new_zeros(hi - full.numel())])
+        out[key] = full[lo:hi].clone()
+    return out
+
+
+def rotate_checkpoints(output_dir: str, limit: int) -> None:
+    cands = []
+    for name in os.listdir(output_dir):
+        m = _re_checkpoint.match(name)
+        if m:
+            cands.append((int(m.group(1)), os.path.join(output_dir, name)))
+    cands.sort()
+    for _, path in cands[:-limit] if limit > 0 else []:
+        shutil.rmtree(path, ignore_errors=True)

@@ -1,0 +1,451 @@
+"""Training loop.
+
+Same user-facing shape as the reference's ``Trainer`` (paddleformers/trainer/trainer.py:282: ``train`` :1877,
+``training_step`` :4458, ``evaluate`` :5409, ``save_model``, callbacks, gradient accumulation, logging of speed
+metrics :2984-3170, checkpoint / resume :4730) with a different engine underneath:
+
+* the optimizer is the flat-buffer sharded AdamW of ``parallel.sharding`` (fp32 master weights and main grads,
+  optimizer state sharded over the sharding group, fused update kernel);
+* nothing on the step path synchronises with the host: the loss stays on the device until a logging step, a
+  non-finite gradient norm turns the update into a no-op on the device, and token counts are device scalars;
+* inputs are staged through pinned host memory with non-blocking copies.
+"""
+from __future__ import annotations
+
+import contextlib
+import json
+import math
+import os
+import time
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+from torch.utils.data import DataLoader, Dataset, IterableDataset
+
+from ..parallel.sharding import ShardedAdamW
+from ..parallel.topology import get_parallel_state
+from ..utils.log import logger
+from . import checkpoint as ckpt
+from .trainer_callback import (CallbackHandler, DefaultFlowCallback, FP8QuantWeightCallback, MetricsDumpCallback,
+                               MoECorrectionBiasAdjustCallback, PrinterCallback, ProfilerCallback, TrainerCallback,
+                               TrainerControl, TrainerState)
+from .trainer_utils import (PREFIX_CHECKPOINT_DIR, LRScheduler, TrainerMemoryTracker, get_last_checkpoint,
+                            get_scheduler_lambda, set_random_seed, speed_metrics)
+from .training_args import TrainingArguments
+
+
+class ShardedSampler(torch.utils.data.Sampler):
+    """Deterministic (seeded) epoch permutation, sliced by dataset rank; supports skipping consumed samples on
+    resume."""
+
+    def __init__(self, n: int, rank: int, world: int, batch: int, seed: int, shuffle: bool = True, drop_last=True):
+        self.n, self.rank, self.world, self.batch, self.seed, self.shuffle = n, rank, world, batch, seed, shuffle
+        self.epoch = 0
+        self.skip_batches = 0
+        self.drop_last = drop_last
+
+    def set_epoch(self, epoch: int):
+        self.epoch = epoch
+
+    def __len__(self):
+        per = self.n // (self.world * self.batch)
+        return per * self.batch
+
+    def __iter__(self):
+        g = torch.Generator().manual_seed(self.seed + self.epoch)
+        order = torch.randperm(self.n, generator=g).tolist() if self.shuffle else list(range(self.n))
+        per_rank_batches = self.n // (self.world * self.batch)
+        for b in range(self.skip_batches, per_rank_batches):
+            base = (b * self.world + self.rank) * self.batch
+            for i in range(self.batch):
+                yield order[base + i]
+        self.skip_batches = 0
+
+
+class Trainer:
+    def __init__(self, model: torch.nn.Module = None, args: TrainingArguments = None, data_collator: Callable = None,
+                 train_dataset: Dataset = None, eval_dataset: Dataset = None, tokenizer=None,
+                 callbacks: Optional[List[TrainerCallback]] = None, optimizers: Tuple[Any, Any] = (None, None),
+                 compute_metrics: Optional[Callable] = None, criterion: Optional[Callable] = None):
+        self.args = args or TrainingArguments()
+        self.ps = self.args.setup_parallel()
+        set_random_seed(self.args.seed, self.ps)
+        self.model = model
+        self.data_collator = data_collator or default_data_collator
+        self.train_dataset, self.eval_dataset = train_dataset, eval_dataset
+        self.tokenizer = tokenizer
+        self.compute_metrics = compute_metrics
+        self.criterion = criterion
+        self.optimizer, self.lr_scheduler = optimizers
+        self.state = TrainerState(is_world_process_zero=self.args.process_index == 0)
+        self.control = TrainerControl()
+        self.device = torch.device(self.args.device)
+        if self.model is not None and next(self.model.parameters()).device != self.device:
+            self.model.to(self.device)
+        default_cbs: List[TrainerCallback] = [DefaultFlowCallback(), PrinterCallback()]
+        if self.args.profile:
+            default_cbs.append(ProfilerCallback())
+        if self.args.metrics_output_path:
+            default_cbs.append(MetricsDumpCallback(self.args.metrics_output_path))
+        if self.args.moe_aux_free_bias_update_rate > 0:
+            default_cbs.append(MoECorrectionBiasAdjustCallback(self.args.moe_aux_free_bias_update_rate))
+        if getattr(getattr(model, "config", None), "fp8", None):
+            default_cbs.append(FP8QuantWeightCallback())
+        self.callback_handler = CallbackHandler(default_cbs + list(callbacks or []), self.model, self.optimizer, self.lr_scheduler)
+        self._tr_loss = None
+        self._interval_tokens = None
+        self._last_log_time = None
+        self._last_log_step = 0
+        self.pipeline_engine = None
+        self.control = self.callback_handler.on_init_end(self.args, self.state, self.control)
+
+    # ------------------------------------------------------------------ public helpers
+    def add_callback(self, cb):
+        self.callback_handler.add_callback(cb)
+
+    def remove_callback(self, cb):
+        self.callback_handler.remove_callback(cb)
+
+    # ------------------------------------------------------------------ data
+    def get_train_dataloader(self) -> DataLoader:
+        a = self.args
+        ds = self.train_dataset
+        if ds is None:
+            raise ValueError("Trainer: training requires a train_dataset")
+        if isinstance(ds, IterableDataset):
+            from ..data.dist_dataloader import IterableDatasetShard
+
+            shard = IterableDatasetShard(ds, a.per_device_train_batch_size, a.dataloader_drop_last, a.dataset_world_size,
+                                         self.ps.dataset_rank)
+            return DataLoader(shard, batch_size=a.per_device_train_batch_size, collate_fn=self.data_collator,
+                              num_workers=a.dataloader_num_workers, pin_memory=self.device.type == "cuda")
+        self._sampler = ShardedSampler(len(ds), self.ps.dataset_rank, a.dataset_world_size, a.per_device_train_batch_size,
+                                       a.data_seed if a.data_seed is not None else a.seed)
+        return DataLoader(ds, batch_size=a.per_device_train_batch_size, sampler=self._sampler, collate_fn=self.data_collator,
+                          num_workers=a.dataloader_num_workers, pin_memory=self.device.type == "cuda", drop_last=True)
+
+    def get_eval_dataloader(self, eval_dataset=None) -> DataLoader:
+        ds = eval_dataset if eval_dataset is not None else self.eval_dataset
+        a = self.args
+        sampler = ShardedSampler(len(ds), self.ps.dataset_rank, a.dataset_world_size, a.per_device_eval_batch_size, a.seed,
+                                 shuffle=False)
+        return DataLoader(ds, batch_size=a.per_device_eval_batch_size, sampler=sampler, collate_fn=self.data_collator,
+                          pin_memory=self.device.type == "cuda", drop_last=True)
+
+    def _prepare_inputs(self, inputs: Dict[str, Any]) -> Dict[str, Any]:
+        out = {}
+        for k, v in inputs.items():
+            if isinstance(v, torch.Tensor):
+                if self.device.type == "cuda" and not v.is_cuda:
+                    if not v.is_pinned():
+                        v = v.pin_memory()
+                    v = v.to(self.device, non_blocking=True)
+                out[k] = v
+            else:
+                out[k] = v
+        ps = self.ps
+        if ps.degrees.cp > 1:
+            from ..parallel.context_parallel import get_batch_on_this_cp_rank
+
+            out = get_batch_on_this_cp_rank(out, ps, getattr(self.args, "cp_balance_mode", None) or "dualchunk_allgather")
+        if ps.degrees.sep > 1:
+            from ..parallel.context_parallel import split_inputs_sequence_dim
+
+            out = split_inputs_sequence_dim(out, ps)
+        return out
+
+    # ------------------------------------------------------------------ optimizer
+    def create_optimizer_and_scheduler(self, num_training_steps: int):
+        a = self.args
+        if self.optimizer is None:
+            self.optimizer = ShardedAdamW(self.model, lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2),
+                                          eps=a.adam_epsilon, weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm,
+                                          parallel_state=self.ps, release_grads=a.release_grads)
+        if self.lr_scheduler is None:
+            min_ratio = a.min_lr / a.learning_rate if a.learning_rate > 0 else 0.0
+            fn = get_scheduler_lambda(a.lr_scheduler_type, a.get_warmup_steps(num_training_steps), num_training_steps,
+                                      min_lr_ratio=min_ratio, decay_steps=a.decay_steps)
+            self.lr_scheduler = LRScheduler(a.learning_rate, fn)
+        self.callback_handler.optimizer, self.callback_handler.lr_scheduler = self.optimizer, self.lr_scheduler
+
+    # ------------------------------------------------------------------ one micro step
+    def compute_loss(self, model, inputs: Dict[str, Any]):
+        if self.criterion is not None:
+            labels = inputs.pop("labels")
+            outputs = model(**inputs, return_logits=True)
+            return self.criterion(outputs.logits, labels), outputs
+        outputs = model(**inputs)
+        return outputs.loss, outputs
+
+    def autocast_context(self):
+        return contextlib.nullcontext()
+
+    def training_step(self, model, inputs: Dict[str, Any]) -> torch.Tensor:
+        model.train()
+        inputs = self._prepare_inputs(inputs)
+        loss, outputs = self.compute_loss(model, inputs)
+        loss.backward()
+        self.optimizer.accumulate_grads()
+        nt = getattr(outputs, "num_tokens", None)
+        if nt is not None:
+            self._interval_tokens = nt if self._interval_tokens is None else self._interval_tokens + nt
+        return loss.detach()
+
+    def training_pipeline_step(self, model, micro_batches: List[Dict[str, Any]]) -> torch.Tensor:
+        if self.pipeline_engine is None:
+            from ..parallel.pipeline import PipelineEngine
+
+            self.pipeline_engine = PipelineEngine(model, self.ps, schedule=self.args.pipeline_schedule,
+                                                  num_virtual_stages=self.args.virtual_pipeline_model_parallel_size)
+        batches = [self._prepare_inputs(mb) for mb in micro_batches]
+        loss = self.pipeline_engine.forward_backward(batches)
+        self.optimizer.accumulate_grads()
+        return loss
+
+    # ------------------------------------------------------------------ train
+    def train(self, resume_from_checkpoint: Optional[str] = None):
+        a = self.args
+        model = self.model
+        loader = self.get_train_dataloader()
+        accum = a.gradient_accumulation_steps
+        try:
+            steps_per_epoch = max(len(loader) // accum, 1)
+        except TypeError:
+            steps_per_epoch = None
+        if a.max_steps > 0:
+            max_steps = a.max_steps
+            epochs = math.ceil(max_steps / steps_per_epoch) if steps_per_epoch else 10 ** 9
+        else:
+            if steps_per_epoch is None:
+                raise ValueError("max_steps is required with an iterable dataset")
+            max_steps = int(math.ceil(a.num_train_epochs * steps_per_epoch))
+            epochs = int(math.ceil(a.num_train_epochs))
+        self.state.max_steps, self.state.num_train_epochs = max_steps, epochs
+        self.create_optimizer_and_scheduler(max_steps)
+        if hasattr(model, "loss_accumulation_steps"):
+            model.loss_accumulation_steps = accum
+
+        resume = resume_from_checkpoint if resume_from_checkpoint is not None else a.resume_from_checkpoint
+        if resume is True or resume == "auto":
+            resume = get_last_checkpoint(a.output_dir)
+        if resume:
+            self._load_from_checkpoint(resume)
+            self.state.max_steps, self.state.num_train_epochs = max_steps, epochs
+        start_step = self.state.global_step
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            # all ranks must agree on where they resume (paddleformers/trainer/trainer.py:2348-2356)
+            t = torch.tensor([start_step], device=self.device if self.device.type == "cuda" else "cpu")
+            lo, hi = t.clone(), t.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            if int(lo) != int(hi):
+                raise RuntimeError(f"ranks disagree on the resume step: min {int(lo)} max {int(hi)}")
+
+        flops_per_token = None
+        if hasattr(model, "get_hardware_flops_per_token"):
+            try:
+                flops_per_token = model.get_hardware_flops_per_token(a.max_seq_len)
+            except Exception:
+                flops_per_token = None
+        self._flops_per_token = flops_per_token
+
+        self.control = self.callback_handler.on_train_begin(a, self.state, self.control)
+        self._tr_loss = torch.zeros((), dtype=torch.float32, device=self.device)
+        self._last_log_time, self._last_log_step = time.time(), start_step
+        train_start = time.time()
+        use_pp = self.ps.degrees.pp > 1
+        start_epoch = start_step // steps_per_epoch if steps_per_epoch else 0
+        skip_batches = (start_step % steps_per_epoch) * accum if (steps_per_epoch and not a.ignore_data_skip) else 0
+        skip_intervals = [tuple(x) for x in (a.skip_data_intervals or [])]
+
+        for epoch in range(start_epoch, epochs):
+            if hasattr(self, "_sampler"):
+                self._sampler.set_epoch(epoch)
+                self._sampler.skip_batches = skip_batches if epoch == start_epoch else 0
+            self.control = self.callback_handler.on_epoch_begin(a, self.state, self.control)
+            micro: List[Dict[str, Any]] = []
+            for step, inputs in enumerate(loader):
+                self.control = self.callback_handler.on_load_data_end(a, self.state, self.control, inputs=inputs)
+                if any(lo <= self.state.global_step + 1 <= hi for lo, hi in skip_intervals) and len(micro) == 0 and (step + 1) % accum == 0:
+                    # operator-requested skip of poisonous steps (paddleformers/trainer/trainer.py:2490-2547)
+                    self.state.global_step += 1
+                    self.lr_scheduler.step()
+                    continue
+                if len(micro) == 0 and not use_pp:
+                    self.control = self.callback_handler.on_step_begin(a, self.state, self.control)
+                if use_pp:
+                    micro.append(inputs)
+                    if len(micro) < accum:
+                        continue
+                    self.control = self.callback_handler.on_step_begin(a, self.state, self.control)
+                    self._tr_loss += self.training_pipeline_step(model, micro)
+                    micro = []
+                else:
+                    self._tr_loss += self.training_step(model, inputs)
+                    micro.append(None)
+                    if len(micro) < accum:
+                        self.control = self.callback_handler.on_substep_end(a, self.state, self.control)
+                        continue
+                    micro = []
+                # ---- optimizer step boundary
+                self.control = self.callback_handler.on_optimizer_begin(a, self.state, self.control)
+                self.optimizer_step()
+                self.control = self.callback_handler.on_optimizer_end(a, self.state, self.control)
+                self.state.global_step += 1
+                self.state.consumed_samples += a.global_batch_size
+                self.state.epoch = epoch + (step + 1) / max(len(loader), 1) if steps_per_epoch else 0
+                self.control = self.callback_handler.on_step_end(a, self.state, self.control)
+                self._maybe_log_save_evaluate()
+                if self.control.should_training_stop or self.control.should_epoch_stop:
+                    break
+            self.control = self.callback_handler.on_epoch_end(a, self.state, self.control)
+            self._maybe_log_save_evaluate(epoch_end=True)
+            if self.control.should_training_stop:
+                break
+        metrics = speed_metrics("train", train_start, num_samples=(self.state.global_step - start_step) * a.global_batch_size,
+                                num_steps=self.state.global_step - start_step, seq_length=a.max_seq_len,
+                                model_flops_per_token=flops_per_token, world_size=a.world_size)
+        self.control = self.callback_handler.on_train_end(a, self.state, self.control)
+        self.log(metrics)
+        return metrics
+
+    def optimizer_step(self):
+        a = self.args
+        if a.freeze_training:
+            self.optimizer.zero_grad()
+            self.lr_scheduler.step()
+            return
+        lr = self.lr_scheduler.get_lr()
+        self._last_grad_norm = self.optimizer.step(lr=lr)
+        self.lr_scheduler.step()
+
+    # ------------------------------------------------------------------ log / save / eval
+    def _maybe_log_save_evaluate(self, epoch_end: bool = False):
+        a = self.args
+        if self.control.should_log:
+            steps = max(self.state.global_step - self._last_log_step, 1)
+            loss = self._tr_loss / steps
+            if dist.is_initialized() and self.ps.dataset_world_size > 1:
+                loss = loss.clone()
+                dist.all_reduce(loss, group=self.ps.group("data") if self.ps.size("data") > 1 else None)
+                loss = loss / self.ps.size("data")
+            loss_v = float(loss)   # the only host sync of the training loop, on logging steps
+            if not math.isfinite(loss_v):
+                raise FloatingPointError(f"LOSS_{'NAN' if math.isnan(loss_v) else 'INF'}_ERROR: loss is {loss_v} at "
+                                         f"step {self.state.global_step}")
+            now = time.time()
+            dt = max(now - self._last_log_time, 1e-9)
+            logs = {"loss": round(loss_v, 6), "learning_rate": self.lr_scheduler.get_lr(), "global_step": self.state.global_step,
+                    "epoch": round(self.state.epoch, 4)}
+            gn = getattr(self, "_last_grad_norm", None)
+            if gn is not None:
+                logs["global_norm"] = round(float(gn), 6)
+            sps = steps * a.global_batch_size / dt
+            logs["interval_runtime"] = round(dt, 4)
+            logs["interval_samples_per_second"] = round(sps, 4)
+            logs["interval_steps_per_second"] = round(steps / dt, 4)
+            tps = sps * a.max_seq_len / max(a.world_size, 1)
+            logs["interval_tokens_per_second_per_device"] = round(tps, 2)
+            if self._flops_per_token:
+                logs["interval_hardware_tflops_per_device"] = round(tps * self._flops_per_token / 2 ** 40, 3)
+            if self._interval_tokens is not None:
+                real = float(self._interval_tokens) * a.dataset_world_size / max(a.world_size, 1)
+                logs["interval_real_tokens_per_second_per_device"] = round(real / dt, 2)
+                self.state.trained_tokens += int(float(self._interval_tokens) * a.dataset_world_size)
+                self._interval_tokens = None
+            logs.update(TrainerMemoryTracker.snapshot())
+            self._tr_loss.zero_()
+            self._last_log_time, self._last_log_step = now, self.state.global_step
+            self.log(logs)
+        if self.control.should_evaluate and self.eval_dataset is not None:
+            self.evaluate()
+        if self.control.should_save:
+            self._save_checkpoint()
+            self.control = self.callback_handler.on_save(a, self.state, self.control)
+        self.control._new_step()
+
+    def log(self, logs: Dict[str, float]):
+        self.state.log_history.append(dict(logs))
+        self.control = self.callback_handler.on_log(self.args, self.state, self.control, logs=logs)
+
+    @torch.no_grad()
+    def evaluate(self, eval_dataset=None, metric_key_prefix: str = "eval") -> Dict[str, float]:
+        model = self.model
+        model.eval()
+        loader = self.get_eval_dataloader(eval_dataset)
+        tot = torch.zeros((), dtype=torch.float64, device=self.device)
+        cnt = torch.zeros((), dtype=torch.float64, device=self.device)
+        saved_accum = getattr(model, "loss_accumulation_steps", 1)
+        if hasattr(model, "loss_accumulation_steps"):
+            model.loss_accumulation_steps = 1
+        start = time.time()
+        n_batches = 0
+        for inputs in loader:
+            inputs = self._prepare_inputs(inputs)
+            out = model(**inputs)
+            n = out.num_tokens.double() if out.num_tokens is not None else torch.ones_like(cnt)
+            tot += out.loss.double() * n
+            cnt += n
+            n_batches += 1
+            self.control = self.callback_handler.on_prediction_step(self.args, self.state, self.control)
+        if hasattr(model, "loss_accumulation_steps"):
+            model.loss_accumulation_steps = saved_accum
+        if dist.is_initialized() and self.ps.size("data") > 1:
+            both = torch.stack([tot, cnt])
+            dist.all_reduce(both, group=self.ps.group("data"))
+            tot, cnt = both[0], both[1]
+        loss = float(tot / cnt.clamp(min=1))
+        metrics = {f"{metric_key_prefix}_loss": loss, f"{metric_key_prefix}_ppl": math.exp(min(loss, 50.0))}
+        metrics.update(speed_metrics(metric_key_prefix, start, num_samples=n_batches * self.args.per_device_eval_batch_size *
+                                     self.args.dataset_world_size, num_steps=n_batches))
+        self.log(metrics)
+        self.control = self.callback_handler.on_evaluate(self.args, self.state, self.control, metrics=metrics)
+        model.train()
+        return metrics
+
+    @torch.no_grad()
+    def predict(self, test_dataset, metric_key_prefix: str = "test"):
+        self.model.eval()
+        loader = self.get_eval_dataloader(test_dataset)
+        preds = []
+        for inputs in loader:
+            inputs = self._prepare_inputs(inputs)
+            inputs.pop("labels", None)
+            out = self.model(**inputs, return_logits=True)
+            preds.append(out.logits.argmax(-1).cpu())
+        self.model.train()
+        return torch.cat(preds) if preds else None
+
+    # ------------------------------------------------------------------ checkpointing
+    def save_model(self, output_dir: Optional[str] = None):
+        """Final export: HF-compatible safetensors + config (+ tokenizer files)."""
+        output_dir = output_dir or self.args.output_dir
+        self.model.save_pretrained(output_dir)
+        if self.tokenizer is not None and self.args.process_index == 0 and hasattr(self.tokenizer, "save_pretrained"):
+            self.tokenizer.save_pretrained(output_dir)
+        if self.args.process_index == 0:
+            with open(os.path.join(output_dir, "training_args.json"), "w") as f:
+                f.write(self.args.to_json_string())
+
+    def _save_checkpoint(self):
+        out = os.path.join(self.args.output_dir, f"{PREFIX_CHECKPOINT_DIR}-{self.state.global_step}")
+        ckpt.save_checkpoint(self, out)
+        if self.args.save_total_limit and self.args.process_index == 0:
+            ckpt.rotate_checkpoints(self.args.output_dir, self.args.save_total_limit)
+        if self.args.save_hf_steps > 0 and self.state.global_step % self.args.save_hf_steps == 0:
+            self.save_model(os.path.join(self.args.output_dir, f"hf_checkpoint-{self.state.global_step}"))
+
+    def _load_from_checkpoint(self, path: str):
+        ckpt.load_checkpoint(self, path)
+
+
+def default_data_collator(features: List[Dict[str, Any]]) -> Dict[str, torch.Tensor]:
+    out = {}
+    for k in features[0]:
+        vals = [f[k] for f in features]
+        if isinstance(vals[0], torch.Tensor):
+            out[k] = torch.stack(vals)
+        else:
+            out[k] = torch.as_tensor(vals)
+    return out

@@ -1,0 +1,215 @@
+"""``TrainingArguments``: every run-time flag of the trainer, and the derivation of the hybrid-parallel degrees.
+
+Mirrors the reference's dataclass (paddleformers/trainer/training_args.py:80) in naming and behaviour where it
+matters to users: the parallel degrees (``tensor_model_parallel_size``, ``pipeline_model_parallel_size``,
+``expert_model_parallel_size``, ``context_parallel_size``, ``sep_parallel_size``, ``sharding_parallel_size``,
+``sharding`` stage), the derived data-parallel degree (:2819-2947), dataset rank / world rules (:3038-3101), batch
+size arithmetic, logging / saving / evaluation strategies. Unlike the reference, building the arguments does not
+initialise the process groups as a side effect; ``setup_parallel()`` does so explicitly (the Trainer calls it).
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+import torch
+
+from ..parallel.topology import ParallelDegrees, ParallelState, get_parallel_state, initialize_parallel
+from ..transformers.configuration_utils import llmmetaclass
+from .trainer_utils import IntervalStrategy, SchedulerType
+
+
+@dataclass
+@llmmetaclass
+class TrainingArguments:
+    output_dir: str = field(default="./output", metadata={"help": "where checkpoints and logs go"})
+    overwrite_output_dir: bool = False
+    do_train: bool = True
+    do_eval: bool = False
+    do_predict: bool = False
+    # batch / steps
+    per_device_train_batch_size: int = 1
+    per_device_eval_batch_size: int = 1
+    gradient_accumulation_steps: int = 1
+    num_train_epochs: float = 1.0
+    max_steps: int = -1
+    max_seq_len: int = 2048
+    # optimisation
+    learning_rate: float = 1e-4
+    min_lr: float = 0.0
+    weight_decay: float = 0.0
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.999
+    adam_epsilon: float = 1e-8
+    max_grad_norm: float = 1.0
+    lr_scheduler_type: str = "linear"
+    warmup_steps: int = 0
+    warmup_ratio: float = 0.0
+    decay_steps: Optional[int] = None
+    optim: str = "adamw"
+    freeze_training: bool = field(default=False, metadata={"help": "lr = 0 and no updates (debugging aid)"})
+    # precision
+    bf16: bool = False
+    fp16: bool = False
+    amp_master_grad: bool = True
+    # parallelism
+    tensor_model_parallel_size: int = 1
+    pipeline_model_parallel_size: int = 1
+    virtual_pipeline_model_parallel_size: int = 1
+    expert_model_parallel_size: int = 1
+    context_parallel_size: int = 1
+    sep_parallel_size: int = 1
+    sharding_parallel_size: int = -1
+    sharding: str = field(default="", metadata={"help": "'' | stage1 | stage2"})
+    sequence_parallel: bool = False
+    hybrid_parallel_topo_order: str = "sharding_first"
+    pipeline_schedule: str = field(default="1F1B", metadata={"help": "1F1B | interleaved | FThenB"})
+    sharding_comm_buffer_size_MB: int = 256
+    sharding_overlap: bool = True
+    # logging / saving / eval
+    logging_steps: int = 1
+    logging_first_step: bool = True
+    save_strategy: str = "steps"
+    save_steps: int = 500
+    save_total_limit: Optional[int] = None
+    save_hf_steps: int = -1
+    eval_strategy: str = "no"
+    eval_steps: Optional[int] = None
+    report_to: str = "none"
+    metrics_output_path: Optional[str] = None
+    resume_from_checkpoint: Optional[str] = None
+    save_checkpoint_format: str = field(default="sharded", metadata={"help": "sharded | unified | hf"})
+    load_checkpoint_format: str = "sharded"
+    async_save: bool = False
+    skip_data_intervals: Optional[List[List[int]]] = None
+    ignore_data_skip: bool = False
+    # data
+    dataloader_num_workers: int = 0
+    dataloader_drop_last: bool = True
+    seed: int = 42
+    data_seed: Optional[int] = None
+    # misc
+    profile: bool = False
+    profile_step_start: int = 3
+    profile_step_end: int = 5
+    skip_profile_timer: bool = True
+    disable_tqdm: bool = True
+    device: Optional[str] = None
+    pg_timeout_s: int = 0
+    distributed_backend: Optional[str] = None
+    heartbeat_interval_s: float = 0.0
+    release_grads: bool = False
+    moe_aux_free_bias_update_rate: float = 0.0
+    count_trained_tokens: bool = False
+
+    def __post_init__(self):
+        self.lr_scheduler_type = SchedulerType(self.lr_scheduler_type).value
+        self.save_strategy = IntervalStrategy(self.save_strategy).value
+        self.eval_strategy = IntervalStrategy(self.eval_strategy).value
+        if self.bf16 and self.fp16:
+            raise ValueError("choose one of bf16 / fp16")
+        if self.device is None:
+            if torch.cuda.is_available():
+                self.device = f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}"
+            else:
+                self.device = "cpu"
+        self.world_size = int(os.environ.get("WORLD_SIZE", "1"))
+        self.process_index = int(os.environ.get("RANK", "0"))
+        self._post_init_parallel_degree()
+        self._state: Optional[ParallelState] = None
+
+    # ------------------------------------------------------------------ parallel degrees
+    def _post_init_parallel_degree(self):
+        """dp = world / (tp * pp * sep * cp * sharding); sharding defaults to "everything that is left" when a sharding
+        stage is requested (paddleformers/trainer/training_args.py:2819-2947)."""
+        world = self.world_size
+        tp, pp = max(self.tensor_model_parallel_size, 1), max(self.pipeline_model_parallel_size, 1)
+        sep, cp = max(self.sep_parallel_size, 1), max(self.context_parallel_size, 1)
+        if sep > 1 and cp > 1:
+            raise ValueError("sep_parallel_size and context_parallel_size are mutually exclusive")
+        model_par = tp * pp * sep * cp
+        if world % model_par != 0:
+            raise ValueError(f"world size {world} is not divisible by tp*pp*sep*cp = {model_par}")
+        rest = world // model_par
+        if self.sharding:
+            if self.sharding not in ("stage1", "stage2"):
+                raise ValueError("sharding must be '', 'stage1' or 'stage2' (stage3 / fsdp are not compatible with "
+                                 "pipeline parallel and not provided)")
+            sharding = rest if self.sharding_parallel_size in (-1, 0) else self.sharding_parallel_size
+        else:
+            sharding = 1 if self.sharding_parallel_size in (-1, 0) else self.sharding_parallel_size
+        if rest % sharding != 0:
+            raise ValueError(f"sharding_parallel_size {sharding} must divide {rest}")
+        dp = rest // sharding
+        ep = max(self.expert_model_parallel_size, 1)
+        if (world // pp) % ep != 0:
+            raise ValueError(f"expert_model_parallel_size {ep} must divide world/pp = {world // pp}")
+        if self.sequence_parallel and tp == 1:
+            self.sequence_parallel = False
+        self.data_parallel_size = dp
+        self.sharding_parallel_size = sharding
+        self.moe_sharding_parallel_size = world // (pp * ep)
+        self.degrees = ParallelDegrees(dp=dp, sharding=sharding, pp=pp, sep=sep, cp=cp, mp=tp, ep=ep,
+                                       order=self.hybrid_parallel_topo_order)
+
+    def setup_parallel(self) -> ParallelState:
+        if self._state is None:
+            if self.world_size > 1:
+                if self.pg_timeout_s:
+                    os.environ.setdefault("PFB_PG_TIMEOUT", str(self.pg_timeout_s))
+                self._state = initialize_parallel(self.degrees, backend=self.distributed_backend)
+            else:
+                from ..parallel.topology import set_parallel_state
+
+                self._state = ParallelState(self.degrees, rank=0, create_groups=False)
+                set_parallel_state(self._state)
+        return self._state
+
+    # ------------------------------------------------------------------ derived quantities
+    @property
+    def parallel_state(self) -> ParallelState:
+        return self.setup_parallel()
+
+    @property
+    def dataset_world_size(self) -> int:
+        return self.data_parallel_size * self.sharding_parallel_size
+
+    @property
+    def dataset_rank(self) -> int:
+        return self.parallel_state.dataset_rank
+
+    @property
+    def train_batch_size(self) -> int:
+        return self.per_device_train_batch_size
+
+    @property
+    def global_batch_size(self) -> int:
+        return self.per_device_train_batch_size * self.gradient_accumulation_steps * self.dataset_world_size
+
+    @property
+    def should_log(self) -> bool:
+        return self.process_index == 0
+
+    @property
+    def should_save(self) -> bool:
+        return True  # every rank writes its own shard; rank 0 writes the shared files
+
+    def get_warmup_steps(self, num_training_steps: int) -> int:
+        return self.warmup_steps if self.warmup_steps > 0 else int(num_training_steps * self.warmup_ratio)
+
+    @property
+    def compute_dtype(self) -> torch.dtype:
+        return torch.bfloat16 if self.bf16 else (torch.float16 if self.fp16 else torch.float32)
+
+    def to_dict(self) -> Dict[str, Any]:
+        out = {}
+        for f in dataclasses.fields(self):
+            v = getattr(self, f.name)
+            out[f.name] = v
+        return out
+
+    def to_json_string(self) -> str:
+        return json.dumps(self.to_dict(), indent=2, default=str)

@@ -1,0 +1,82 @@
+"""Auto classes: pick the config / model / tokenizer class from ``model_type`` in ``config.json``.
+
+Same entry points as the reference (paddleformers/transformers/auto/modeling.py:774 AutoModelForCausalLM, AutoConfig,
+AutoTokenizer). Tokenizers are thin wrappers over Hugging Face ``transformers`` tokenizers, like the reference's
+(paddleformers/transformers/llama/tokenizer.py:21-22).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+from .configuration_utils import PretrainedConfig
+
+
+class AutoConfig:
+    @staticmethod
+    def for_model(model_type: str, **kw) -> PretrainedConfig:
+        from ..models.configuration import CONFIG_MAPPING
+
+        if model_type not in CONFIG_MAPPING:
+            raise ValueError(f"unknown model_type {model_type!r}; supported: {sorted(CONFIG_MAPPING)}")
+        return CONFIG_MAPPING[model_type](**kw)
+
+    @staticmethod
+    def from_pretrained(path: str, **overrides) -> PretrainedConfig:
+        from ..models.configuration import CONFIG_MAPPING
+
+        d = PretrainedConfig.get_config_dict(path)
+        mt = d.get("model_type")
+        if mt not in CONFIG_MAPPING:
+            raise ValueError(f"unknown model_type {mt!r}; supported: {sorted(CONFIG_MAPPING)}")
+        return CONFIG_MAPPING[mt].from_dict(d, **overrides)
+
+
+class AutoModelForCausalLM:
+    @staticmethod
+    def _cls(config):
+        from ..models.modeling import MODEL_MAPPING
+
+        return MODEL_MAPPING[config.model_type]
+
+    @classmethod
+    def from_config(cls, config: PretrainedConfig, dtype=None, device=None, **kw):
+        return cls._cls(config).from_config(config, dtype=dtype, device=device, **kw)
+
+    @classmethod
+    def from_pretrained(cls, path: str, config: Optional[PretrainedConfig] = None, dtype=None, device=None, **kw):
+        config = config or AutoConfig.from_pretrained(path)
+        return cls._cls(config).from_pretrained(path, config=config, dtype=dtype, device=device, **kw)
+
+
+class AutoModelForCausalLMPipe(AutoModelForCausalLM):
+    """Pipeline-parallel variant: builds only this stage's layers (see ``parallel.pipeline``)."""
+
+    @classmethod
+    def from_config(cls, config: PretrainedConfig, dtype=None, device=None, **kw):
+        from ..parallel.pipeline import build_pipeline_model
+
+        return build_pipeline_model(config, dtype=dtype, device=device, **kw)
+
+
+class AutoTokenizer:
+    @staticmethod
+    def from_pretrained(path: str, **kw):
+        from ..utils.download import resolve_dir
+
+        try:
+            from transformers import AutoTokenizer as HFAutoTokenizer
+        except Exception as e:  # pragma: no cover
+            raise RuntimeError("AutoTokenizer needs the `transformers` package") from e
+        try:
+            path = resolve_dir(path)
+        except FileNotFoundError:
+            pass
+        return HFAutoTokenizer.from_pretrained(path, **kw)
+
+
+class AutoProcessor:
+    @staticmethod
+    def from_pretrained(path: str, **kw):
+        from transformers import AutoProcessor as HFAutoProcessor
+
+        return HFAutoProcessor.from_pretrained(path, **kw)

@@ -1,0 +1,129 @@
+"""Declarative mapping between Hugging Face checkpoint tensors and this framework's fused parameters.
+
+The reference bridges its internal layout and HF names with "AOA" statements such as
+``q,k,v -> qkv_proj.weight, fused_qkv`` (paddleformers/transformers/aoa_config_base.py:339-452,
+paddleformers/transformers/llama/modeling.py:324-353). torch linears already use HF's ``[out, in]`` layout, so only
+fusions remain here: concatenated projections (qkv, gate|up, MLA kv_a) and stacked experts. Every rule is
+invertible, which gives ``save_pretrained`` for free, and every rule knows how to cut its target for a tensor /
+expert parallel rank so that a rank only materialises its own shard.
+"""
+from __future__ import annotations
+
+import re
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+
+
+@dataclass
+class ShardSpec:
+    """How a parameter is cut over the tensor-parallel (tp) and expert-parallel (ep) groups.
+
+    ``tp_dim``: dimension split over tp (None = replicated). ``sections``: sizes of the fused sections along
+    ``tp_dim`` in the *full* tensor; each section is split separately (fused qkv / gate|up). ``ep_dim``: dimension
+    that indexes experts (split over ep)."""
+
+    tp_dim: Optional[int] = None
+    sections: Optional[List[int]] = None
+    ep_dim: Optional[int] = None
+
+    def shard(self, full: torch.Tensor, tp_rank: int, tp_size: int, ep_rank: int = 0, ep_size: int = 1) -> torch.Tensor:
+        t = full
+        if self.ep_dim is not None and ep_size > 1:
+            n = t.shape[self.ep_dim] // ep_size
+            t = t.narrow(self.ep_dim, ep_rank * n, n)
+        if self.tp_dim is not None and tp_size > 1:
+            secs = self.sections or [t.shape[self.tp_dim]]
+            parts, off = [], 0
+            for s in secs:
+                assert s % tp_size == 0, f"section {s} not divisible by tp {tp_size}"
+                n = s // tp_size
+                parts.append(t.narrow(self.tp_dim, off + tp_rank * n, n))
+                off += s
+            t = torch.cat(parts, dim=self.tp_dim) if len(parts) > 1 else parts[0]
+        return t.contiguous()
+
+    def unshard(self, shards: Sequence[torch.Tensor], tp_size: int) -> torch.Tensor:
+        """Inverse of ``shard`` over tp (``shards`` ordered by tp rank)."""
+        if self.tp_dim is None or tp_size == 1:
+            return shards[0]
+        secs = self.sections or [shards[0].shape[self.tp_dim] * tp_size]
+        out, off = [], 0
+        for s in secs:
+            n = s // tp_size
+            out.extend(sh.narrow(self.tp_dim, off, n) for sh in shards)
+            off += n
+        return torch.cat(out, dim=self.tp_dim)
+
+
+@dataclass
+class Rule:
+    """target <- op(sources). ``sources`` may contain ``{E}`` (expanded over experts for stack rules)."""
+
+    target: str
+    sources: List[str]
+    op: str = "rename"  # rename | concat | stack | stack_concat
+    dim: int = 0
+    num_experts: int = 0
+    expert_pairs: int = 1  # stack_concat: sources per expert (gate, up)
+    sizes: Optional[List[int]] = None  # concat: size of each source along ``dim`` (default: equal parts)
+
+    def source_names(self) -> List[str]:
+        if self.op in ("stack", "stack_concat"):
+            return [s.format(E=e) for e in range(self.num_experts) for s in self.sources]
+        return list(self.sources)
+
+    def forward(self, get: Callable[[str], torch.Tensor], expert_range: Optional[range] = None) -> torch.Tensor:
+        if self.op == "rename":
+            return get(self.sources[0])
+        if self.op == "concat":
+            return torch.cat([get(s) for s in self.sources], dim=self.dim)
+        er = expert_range if expert_range is not None else range(self.num_experts)
+        if self.op == "stack":
+            return torch.stack([get(self.sources[0].format(E=e)) for e in er], dim=0)
+        if self.op == "stack_concat":
+            return torch.stack([torch.cat([get(s.format(E=e)) for s in self.sources], dim=self.dim) for e in er], dim=0)
+        raise ValueError(self.op)
+
+    def inverse(self, tensor: torch.Tensor, section_sizes: Optional[List[int]] = None, expert_offset: int = 0) -> Dict[str, torch.Tensor]:
+        if self.op == "rename":
+            return {self.sources[0]: tensor}
+        if self.op == "concat":
+            sizes = section_sizes or self.sizes or [tensor.shape[self.dim] // len(self.sources)] * len(self.sources)
+            return {s: p.contiguous() for s, p in zip(self.sources, torch.split(tensor, sizes, dim=self.dim))}
+        out = {}
+        for i in range(tensor.shape[0]):
+            e = expert_offset + i
+            if self.op == "stack":
+                out[self.sources[0].format(E=e)] = tensor[i].contiguous()
+            else:
+                sizes = section_sizes or [tensor.shape[1 + self.dim] // len(self.sources)] * len(self.sources)
+                for s, p in zip(self.sources, torch.split(tensor[i], sizes, dim=self.dim)):
+                    out[s.format(E=e)] = p.contiguous()
+        return out
+
+
+class WeightMap:
+    """All rules of one model instance, indexed by internal parameter name."""
+
+    def __init__(self, rules: Iterable[Rule]):
+        self.rules: Dict[str, Rule] = {r.target: r for r in rules}
+
+    def rule_for(self, target: str) -> Rule:
+        return self.rules.get(target) or Rule(target, [target])
+
+    def hf_names(self) -> List[str]:
+        out = []
+        for r in self.rules.values():
+            out.extend(r.source_names())
+        return out
+
+
+def expand_layers(template_rules: List[Rule], layer_ids: Iterable[int]) -> List[Rule]:
+    out = []
+    for i in layer_ids:
+        for r in template_rules:
+            out.append(Rule(r.target.replace("{L}", str(i)), [s.replace("{L}", str(i)) for s in r.sources], r.op, r.dim,
+                            r.num_experts, r.expert_pairs, r.sizes))
+    return out
