@@ -83,12 +83,15 @@ class _LinearFn(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16 != 0:
             x2 = x2.contiguous()
-        y = gemm(x2, weight)
+        # allocate the result in its final shape: returning a view made inside the Function would forbid later
+        # in-place ops (rotary embedding) on it
+        y = torch.empty((*x.shape[:-1], weight.shape[0]), dtype=x.dtype, device=x.device)
+        gemm(x2, weight, out=y.view(-1, weight.shape[0]))
         if bias is not None:
-            y = y + bias
+            y += bias
         ctx.save_for_backward(x2, weight)
         ctx.has_bias = bias is not None
-        return y.view(*x.shape[:-1], weight.shape[0])
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -134,9 +137,10 @@ class _LinearSwigluFn(torch.autograd.Function):
             x2 = x2.contiguous()
         T, N = x2.shape[0], weight.shape[0]
         raw = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
-        act = gemm(x2, weight, epi=EPI_SWIGLU_BF16, out2=raw)
+        act = torch.empty((*x.shape[:-1], N // 2), dtype=torch.bfloat16, device=x.device)
+        gemm(x2, weight, out=act.view(-1, N // 2), epi=EPI_SWIGLU_BF16, out2=raw)
         ctx.save_for_backward(x2, weight, raw)
-        return act.view(*x.shape[:-1], N // 2)
+        return act
 
     @staticmethod
     def backward(ctx, dact):

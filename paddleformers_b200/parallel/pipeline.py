@@ -1,0 +1,390 @@
+"""Pipeline parallelism: stage partitioning, schedules (FThenB, 1F1B, interleaved 1F1B) and the execution engine.
+
+Roles of the reference's ``GeneralModelForCausalLMPipe`` (paddleformers/nn/pp_model.py:509-688: layer descriptions,
+``seg_method``, empty layers, virtual stages, shared embeddings) and of Fleet's ``forward_backward_pipeline`` driven by
+the trainer (paddleformers/trainer/trainer.py:4531-4580). Point-to-point traffic stays on NCCL send/recv, as two
+independent communicators (one per direction of dataflow: activations forward, gradients backward) so that messages
+of different kinds between the same pair of ranks can never be matched against each other, and on their own CUDA
+streams so that transfers overlap compute.
+
+The schedules are generated as plain lists of actions per stage; ``simulate`` checks any schedule for dependency
+order and reports the peak number of in-flight micro-batches per stage, which the CPU tests assert.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..ops import functional as F
+from .topology import ParallelState, get_parallel_state
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# partitioning
+# ---------------------------------------------------------------------------------------------------------------
+def partition_layers(num_layers: int, num_stages: int, num_virtual: int = 1, empty_head: int = 0, empty_tail: int = 0,
+                     weights: Optional[Sequence[float]] = None) -> List[List[range]]:
+    """Split ``num_layers`` decoder layers over ``num_stages * num_virtual`` virtual stages.
+
+    Returns ``parts[stage][chunk] = range of layer ids``. Empty layers count as layers of zero cost placed before the
+    first / after the last decoder layer (``num_empty_layers_add_in_head/tail``) which shifts real layers away from
+    the stages that also hold the embedding / head. ``weights`` gives a per-layer cost for non-uniform splits."""
+    n_virtual = num_stages * num_virtual
+    total = num_layers + empty_head + empty_tail
+    if weights is None:
+        base, rem = divmod(total, n_virtual)
+        sizes = [base + (1 if i < rem else 0) for i in range(n_virtual)]
+    else:
+        assert len(weights) == total
+        # greedy prefix split: close a virtual stage once its cost reaches the running average of what is left
+        sizes, start = [], 0
+        remaining_cost = float(sum(weights))
+        for v in range(n_virtual):
+            slots_left = n_virtual - v
+            if slots_left == 1:
+                sizes.append(total - start)
+                break
+            target = remaining_cost / slots_left
+            acc, cnt = 0.0, 0
+            while start + cnt < total - (slots_left - 1) and (cnt == 0 or acc + weights[start + cnt] / 2 <= target):
+                acc += weights[start + cnt]
+                cnt += 1
+            sizes.append(cnt)
+            start += cnt
+            remaining_cost -= acc
+    bounds, pos = [], 0
+    for s in sizes:
+        bounds.append((pos, pos + s))
+        pos += s
+    parts: List[List[range]] = [[None] * num_virtual for _ in range(num_stages)]
+    for v, (lo, hi) in enumerate(bounds):
+        stage, chunk = v % num_stages, v // num_stages
+        real_lo = min(max(lo - empty_head, 0), num_layers)
+        real_hi = min(max(hi - empty_head, 0), num_layers)
+        parts[stage][chunk] = range(real_lo, real_hi)
+    return parts
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# schedules
+# ---------------------------------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class Action:
+    kind: str    # "F" or "B"
+    chunk: int   # virtual chunk on this stage
+    mb: int      # micro-batch id
+
+
+def schedule_fthenb(stage: int, P: int, M: int, V: int = 1) -> List[Action]:
+    acts = [Action("F", c, m) for c in range(V) for m in range(M)]
+    acts += [Action("B", c, m) for c in reversed(range(V)) for m in range(M)]
+    return acts
+
+
+def schedule_1f1b(stage: int, P: int, M: int) -> List[Action]:
+    warm = min(P - stage - 1, M)
+    acts = [Action("F", 0, m) for m in range(warm)]
+    f, b = warm, 0
+    while f < M:
+        acts.append(Action("F", 0, f)); f += 1
+        acts.append(Action("B", 0, b)); b += 1
+    while b < M:
+        acts.append(Action("B", 0, b)); b += 1
+    return acts
+
+
+def schedule_interleaved(stage: int, P: int, M: int, V: int) -> List[Action]:
+    """Interleaved 1F1B (virtual pipeline): micro-batches advance in groups of P through the V chunks."""
+    assert M % P == 0, "interleaved schedule needs the number of micro-batches to be a multiple of the pipeline degree"
+    total = M * V
+
+    def fwd_ids(k):
+        group, within = divmod(k, P * V)
+        chunk = within // P
+        return chunk, group * P + within % P
+
+    def bwd_ids(k):
+        chunk, mb = fwd_ids(k)
+        return V - 1 - chunk, mb
+
+    warm = min((P - stage - 1) * 2 + (V - 1) * P, total)
+    acts = [Action("F", *fwd_ids(k)) for k in range(warm)]
+    f, b = warm, 0
+    while f < total:
+        acts.append(Action("F", *fwd_ids(f))); f += 1
+        acts.append(Action("B", *bwd_ids(b))); b += 1
+    while b < total:
+        acts.append(Action("B", *bwd_ids(b))); b += 1
+    return acts
+
+
+def make_schedule(name: str, stage: int, P: int, M: int, V: int = 1) -> List[Action]:
+    name = name.lower()
+    if name in ("fthenb", "f-then-b"):
+        return schedule_fthenb(stage, P, M, V)
+    if V > 1 or name in ("interleaved", "vpp"):
+        return schedule_interleaved(stage, P, M, max(V, 1))
+    return schedule_1f1b(stage, P, M)
+
+
+def simulate(schedules: List[List[Action]], P: int, V: int) -> Dict[str, object]:
+    """Runs all stages' action lists as a discrete-event simulation (unit cost per action, blocking on
+    dependencies). Raises on deadlock; returns makespan, bubble fraction and peak live activations per stage."""
+    done_f, done_b = set(), set()   # (virtual stage index, mb)
+    pos = [0] * P
+    live = [0] * P
+    peak = [0] * P
+    time = 0
+    n_actions = sum(len(s) for s in schedules)
+    finished = 0
+    last_virtual = P * V - 1
+    while finished < n_actions:
+        progressed = []
+        for s in range(P):
+            if pos[s] >= len(schedules[s]):
+                continue
+            a = schedules[s][pos[s]]
+            vs = a.chunk * P + s
+            if a.kind == "F":
+                ready = vs == 0 or (vs - 1, a.mb) in done_f
+            else:
+                ready = (vs, a.mb) in done_f and (vs == last_virtual or (vs + 1, a.mb) in done_b)
+            if ready:
+                progressed.append((s, a, vs))
+        if not progressed:
+            raise RuntimeError(f"pipeline schedule deadlocks at positions {pos}")
+        for s, a, vs in progressed:
+            if a.kind == "F":
+                done_f.add((vs, a.mb))
+                live[s] += 1
+                peak[s] = max(peak[s], live[s])
+            else:
+                done_b.add((vs, a.mb))
+                live[s] -= 1
+            pos[s] += 1
+            finished += 1
+        time += 1
+    work = max(len(s) for s in schedules)
+    return {"makespan": time, "bubble_fraction": 1.0 - work / time, "peak_live": peak}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# stage model
+# ---------------------------------------------------------------------------------------------------------------
+class PipelineStageModel(nn.Module):
+    """The chunks of a decoder that live on this pipeline stage. Chunk c of stage s is virtual stage c * P + s.
+    The embedding lives on virtual stage 0, the final norm, MTP layers and head on the last one; with tied
+    embeddings both ends hold a copy whose gradients are summed over the two owners after the backward pass
+    (the reference's SharedLayerDesc, paddleformers/nn/pp_model.py:582-594)."""
+
+    def __init__(self, config, dtype=None, device=None, ps: Optional[ParallelState] = None):
+        super().__init__()
+        from ..models.modeling import DecoderModel, MTPLayer, RMSNorm, _resolve_dtype
+
+        ps = ps or get_parallel_state()
+        self.config = config
+        self.ps = ps
+        P, V = ps.degrees.pp, max(int(getattr(config, "virtual_pipeline_model_parallel_size", 1) or 1), 1)
+        self.P, self.V, self.stage = P, V, ps.coord["pp"]
+        dtype = dtype if dtype is not None else _resolve_dtype(config.dtype)
+        parts = partition_layers(config.num_hidden_layers, P, V, int(getattr(config, "num_empty_layers_add_in_head", 0) or 0),
+                                 int(getattr(config, "num_empty_layers_add_in_tail", 0) or 0))
+        self.layer_ranges = parts[self.stage]
+        self.chunks = nn.ModuleList()
+        for c, rng in enumerate(self.layer_ranges):
+            first = self.stage == 0 and c == 0
+            last = self.stage == P - 1 and c == V - 1
+            self.chunks.append(DecoderModel(config, dtype=dtype, device=device, layer_range=rng, with_embedding=first or (last and config.tie_word_embeddings),
+                                            with_final_norm=last))
+        self.is_first = self.stage == 0
+        self.is_last = self.stage == P - 1
+        self.lm_head = None
+        self.mtp_layers = nn.ModuleList()
+        if self.is_last:
+            if not config.tie_word_embeddings:
+                self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False, dtype=dtype, device=device)
+            n_mtp = int(getattr(config, "num_nextn_predict_layers", 0) or 0)
+            self.mtp_layers = nn.ModuleList([MTPLayer(config, config.num_hidden_layers + i, dtype=dtype, device=device) for i in range(n_mtp)])
+            if n_mtp and self.chunks[-1].embed_tokens is None:
+                # MTP needs token embeddings on the last stage: a tied copy of the input embedding
+                self.chunks[-1].embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size, dtype=dtype, device=device)
+                self.chunks[-1].embed_tokens.weight.pp_shared = "embed_tokens"
+        if self.is_first and self.chunks[0].embed_tokens is not None and (config.tie_word_embeddings or getattr(config, "num_nextn_predict_layers", 0)):
+            self.chunks[0].embed_tokens.weight.pp_shared = "embed_tokens"
+        if self.is_last and config.tie_word_embeddings and self.chunks[-1].embed_tokens is not None:
+            self.chunks[-1].embed_tokens.weight.pp_shared = "embed_tokens"
+        self.loss_accumulation_steps = 1
+        self.ignore_index = -100
+        std = config.initializer_range
+        for m in self.modules():
+            if isinstance(m, (nn.Linear, nn.Embedding)):
+                nn.init.normal_(m.weight, 0.0, std)
+        from ..nn.moe import GroupedExperts, TopkRouter
+
+        for m in self.modules():
+            if isinstance(m, GroupedExperts):
+                nn.init.normal_(m.gate_up_proj, 0.0, std); nn.init.normal_(m.down_proj, 0.0, std)
+            elif isinstance(m, TopkRouter):
+                nn.init.normal_(m.weight, 0.0, std)
+
+    def head_weight(self):
+        return self.lm_head.weight if self.lm_head is not None else self.chunks[-1].embed_tokens.weight
+
+    def forward_chunk(self, c: int, x, batch, ctx):
+        model = self.chunks[c]
+        if self.is_first and c == 0:
+            x = model.embed(batch["input_ids"])
+        hidden, residual = model.run_layers(x, None, ctx)
+        last = self.is_last and c == self.V - 1
+        if last:
+            if model.norm is not None:
+                hidden = model.norm(hidden, residual)[0] if residual is not None else model.norm(hidden)
+            return hidden
+        return hidden + residual if residual is not None else hidden
+
+    def loss(self, hidden, batch, ctx):
+        labels = batch["labels"].reshape(-1)
+        count = (labels != self.ignore_index).sum()
+        scale = 1.0 / (count.clamp(min=1).float() * float(self.loss_accumulation_steps))
+        loss, _ = F.fused_linear_cross_entropy(hidden, self.head_weight(), labels, self.ignore_index, 2048, scale)
+        if len(self.mtp_layers) > 0:
+            ids, lab, h = batch["input_ids"], batch["labels"], hidden
+            extra = []
+            for layer in self.mtp_layers:
+                ids = torch.cat([ids[:, 1:], ids[:, -1:]], 1)
+                lab = torch.cat([lab[:, 1:], torch.full_like(lab[:, -1:], self.ignore_index)], 1)
+                emb = F.embedding(ids, self.chunks[-1].embed_tokens.weight).reshape(-1, self.config.hidden_size)
+                h = layer(h, emb, ctx)
+                flat = lab.reshape(-1)
+                cnt = (flat != self.ignore_index).sum()
+                sc = 1.0 / (cnt.clamp(min=1).float() * float(self.loss_accumulation_steps))
+                extra.append(F.fused_linear_cross_entropy(h, self.head_weight(), flat, self.ignore_index, 2048, sc)[0])
+            loss = loss + float(getattr(self.config, "mtp_loss_scaling_factor", 0.1)) * torch.stack(extra).mean()
+        return loss
+
+
+def build_pipeline_model(config, dtype=None, device=None, **kw):
+    return PipelineStageModel(config, dtype=dtype, device=device)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# engine
+# ---------------------------------------------------------------------------------------------------------------
+class PipelineEngine:
+    """Executes one optimizer step worth of micro-batches with the chosen schedule."""
+
+    def __init__(self, model: PipelineStageModel, ps: Optional[ParallelState] = None, schedule: str = "1F1B",
+                 num_virtual_stages: int = 1):
+        self.model = model
+        self.ps = ps or get_parallel_state()
+        self.P, self.V = self.ps.degrees.pp, model.V
+        self.stage = self.ps.coord["pp"]
+        self.schedule_name = schedule
+        ranks = self.ps.group_ranks["pp"]
+        self.prev_rank = ranks[(self.stage - 1) % self.P]
+        self.next_rank = ranks[(self.stage + 1) % self.P]
+        # two communicators: activations travel on one, gradients on the other
+        self.fwd_group, self.bwd_group, self._shared_group = _pp_comm_groups(self.ps)
+
+    # -- communication helpers (blocking semantics on the consumer side; producers are asynchronous)
+    def _send(self, t, dst, group, pending):
+        pending.append(dist.isend(t.contiguous(), dst=dst, group=group))
+
+    def _recv(self, shape, dtype, device, src, group):
+        buf = torch.empty(shape, dtype=dtype, device=device)
+        dist.recv(buf, src=src, group=group)
+        return buf
+
+    def forward_backward(self, micro_batches: List[Dict[str, torch.Tensor]]) -> torch.Tensor:
+        model, P, V, s = self.model, self.P, self.V, self.stage
+        M = len(micro_batches)
+        model.loss_accumulation_steps = M
+        acts = make_schedule(self.schedule_name, s, P, M, V)
+        H = model.config.hidden_size
+        dev = next(model.parameters()).device
+        dtype = next((p.dtype for n, p in model.named_parameters() if "gate.weight" not in n), torch.float32)
+        saved: Dict[Tuple[int, int], Tuple[Optional[torch.Tensor], torch.Tensor]] = {}
+        ctxs: Dict[int, object] = {}
+        pending: List[object] = []
+        total_loss = torch.zeros((), dtype=torch.float32, device=dev)
+        last_virtual = P * V - 1
+        for a in acts:
+            vs = a.chunk * P + s
+            batch = micro_batches[a.mb]
+            B, S = batch["input_ids"].shape
+            if a.mb not in ctxs:
+                kend = batch.get("attn_mask_startend_row_indices", batch.get("kend"))
+                ctxs[a.mb] = model.chunks[0].make_context(batch["input_ids"], batch.get("position_ids"),
+                                                          kend.reshape(B, -1) if kend is not None else None)
+            ctx = ctxs[a.mb]
+            if a.kind == "F":
+                x_in = None
+                if vs > 0:
+                    x_in = self._recv((B * S, H), dtype, dev, self.prev_rank, self.fwd_group)
+                    x_in.requires_grad_(True)
+                out = model.forward_chunk(a.chunk, x_in, batch, ctx)
+                if vs == last_virtual:
+                    loss = model.loss(out, batch, ctx)
+                    total_loss += loss.detach()
+                    saved[(a.chunk, a.mb)] = (x_in, loss)
+                else:
+                    self._send(out.detach(), self.next_rank, self.fwd_group, pending)
+                    saved[(a.chunk, a.mb)] = (x_in, out)
+            else:
+                x_in, out = saved.pop((a.chunk, a.mb))
+                if vs == last_virtual:
+                    out.backward()
+                else:
+                    g = self._recv(tuple(out.shape), out.dtype, dev, self.next_rank, self.bwd_group)
+                    torch.autograd.backward(out, g)
+                if vs > 0:
+                    self._send(x_in.grad, self.prev_rank, self.bwd_group, pending)
+        for w in pending:
+            w.wait()
+        self._sync_shared_embeddings()
+        # every stage reports the same loss: the last stage owns it
+        if P > 1:
+            src = self.ps.group_ranks["pp"][P - 1]
+            dist.broadcast(total_loss, src=src, group=self.ps.group("pp"))
+        return total_loss
+
+    def _sync_shared_embeddings(self):
+        """Sum the gradients of parameters that exist on both the first and the last stage (tied embeddings, MTP
+        embedding copy)."""
+        shared = [p for p in self.model.parameters() if getattr(p, "pp_shared", None)]
+        if not shared or self.P == 1:
+            return
+        if not (self.model.is_first or self.model.is_last):
+            return
+        for p in shared:
+            g = getattr(p, "main_grad", None)
+            if g is None:
+                g = p.grad
+            if g is not None:
+                dist.all_reduce(g, group=self._shared_group)
+
+
+_PP_GROUPS = {}
+
+
+def _pp_comm_groups(ps: ParallelState):
+    """(forward communicator, backward communicator, first+last stage group) of this rank's pipeline group. Creating
+    groups is collective over the whole job, so every rank builds every pipeline group's communicators."""
+    key = id(ps)
+    if key not in _PP_GROUPS:
+        fwd = bwd = shared = None
+        if ps.degrees.pp > 1 and dist.is_initialized():
+            for ranks in ps.topo.comm_list("pp"):
+                f = dist.new_group(ranks=ranks)
+                b = dist.new_group(ranks=ranks)
+                sh = dist.new_group(ranks=[ranks[0], ranks[-1]])
+                if ps.global_rank in ranks:
+                    fwd, bwd = f, b
+                    if ps.global_rank in (ranks[0], ranks[-1]):
+                        shared = sh
+        _PP_GROUPS[key] = (fwd, bwd, shared)
+    return _PP_GROUPS[key]

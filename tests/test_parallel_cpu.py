@@ -1,0 +1,88 @@
+"""Hybrid-parallel logic on CPU ranks (gloo): every strategy must reproduce the single-process losses."""
+import pytest
+import torch
+
+from dist_utils import run_distributed
+
+
+def _tiny_cfg(moe=False, **kw):
+    from paddleformers_b200.models.configuration import named_config
+
+    if moe:
+        return named_config("qwen3-30b-a3b", num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
+                            head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, vocab_size=128,
+                            router_aux_loss_coef=0.0, **kw)
+    return named_config("tiny-llama", num_hidden_layers=2, hidden_size=64, intermediate_size=96, num_attention_heads=4,
+                        num_key_value_heads=2, head_dim=16, vocab_size=128, **kw)
+
+
+def _data(n, S=32, vocab=128):
+    g = torch.Generator().manual_seed(11)
+    ids = torch.randint(0, vocab, (n, S + 1), generator=g)
+    return [{"input_ids": ids[i, :-1], "labels": ids[i, 1:]} for i in range(n)]
+
+
+class _DS(torch.utils.data.Dataset):
+    def __init__(self, items):
+        self.items = items
+
+    def __len__(self):
+        return len(self.items)
+
+    def __getitem__(self, i):
+        return self.items[i]
+
+
+def _train(rank, world, moe, targs, steps, full_state):
+    from paddleformers_b200 import Trainer, TrainingArguments
+    from paddleformers_b200.models.modeling import DecoderForCausalLM, MODEL_MAPPING
+    from paddleformers_b200.transformers.model_utils import param_shard_spec
+    from paddleformers_b200.transformers.conversion_utils import ShardSpec
+
+    args = TrainingArguments(output_dir="/tmp/pfb_test_unused", per_device_train_batch_size=1, max_steps=steps,
+                             learning_rate=1e-2, lr_scheduler_type="constant", logging_steps=1, save_strategy="no",
+                             max_seq_len=32, max_grad_norm=1.0, seed=3, device="cpu", **targs)
+    ps = args.setup_parallel()
+    cfg = _tiny_cfg(moe, sequence_parallel=args.sequence_parallel)
+    model = MODEL_MAPPING[cfg.model_type](cfg)
+    # load the same full weights on every configuration, cut for this rank
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            spec = param_shard_spec(p)
+            p.copy_(spec.shard(full_state[name], ps.coord["mp"], ps.degrees.mp, ps.rank_in("ep"), ps.degrees.ep))
+    ds = _DS(_data(8 * steps))
+    tr = Trainer(model=model, args=args, train_dataset=ds)
+    tr._sampler_shuffle = False
+    tr.train()
+    return [h["loss"] for h in tr.state.log_history if "loss" in h]
+
+
+def _reference(moe, steps, accum):
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+
+    torch.manual_seed(5)
+    cfg = _tiny_cfg(moe)
+    model = MODEL_MAPPING[cfg.model_type](cfg)
+    full = {k: v.detach().clone() for k, v in model.named_parameters()}
+    return full
+
+
+@pytest.mark.parametrize("name,world,moe,targs", [
+    ("tp2_sp", 2, False, dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2)),
+    ("tp2", 2, False, dict(tensor_model_parallel_size=2, gradient_accumulation_steps=2)),
+    ("sharding2", 2, False, dict(sharding="stage1", gradient_accumulation_steps=1)),
+    ("dp2", 2, False, dict(gradient_accumulation_steps=1)),
+    ("ep2", 2, True, dict(expert_model_parallel_size=2, sharding="stage1", gradient_accumulation_steps=1, moe_token_dispatcher_type="alltoall")),
+])
+def test_parallel_matches_single_process(name, world, moe, targs):
+    steps = 3
+    full = _reference(moe, steps, 2)
+    single = dict(gradient_accumulation_steps=2)
+    if moe:
+        single["moe_token_dispatcher_type"] = "alltoall"
+    ref = run_distributed(_train, 1, moe, single, steps, full)[0]
+    got = run_distributed(_train, world, moe, targs, steps, full)
+    for r in range(world):
+        assert len(got[r]) == steps
+        for a, b in zip(ref, got[r]):
+            assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (name, ref, got[r])
