@@ -20,6 +20,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from ..ops import functional as F
+from ..transformers.model_utils import PretrainedModel
 from .topology import ParallelState, get_parallel_state
 
 
@@ -175,14 +176,14 @@ def simulate(schedules: List[List[Action]], P: int, V: int) -> Dict[str, object]
 # ---------------------------------------------------------------------------------------------------------------
 # stage model
 # ---------------------------------------------------------------------------------------------------------------
-class PipelineStageModel(nn.Module):
+class PipelineStageModel(PretrainedModel):
     """The chunks of a decoder that live on this pipeline stage. Chunk c of stage s is virtual stage c * P + s.
     The embedding lives on virtual stage 0, the final norm, MTP layers and head on the last one; with tied
     embeddings both ends hold a copy whose gradients are summed over the two owners after the backward pass
     (the reference's SharedLayerDesc, paddleformers/nn/pp_model.py:582-594)."""
 
     def __init__(self, config, dtype=None, device=None, ps: Optional[ParallelState] = None):
-        super().__init__()
+        super().__init__(config)
         from ..models.modeling import DecoderModel, MTPLayer, RMSNorm, _resolve_dtype
 
         ps = ps or get_parallel_state()
@@ -233,6 +234,27 @@ class PipelineStageModel(nn.Module):
 
     def head_weight(self):
         return self.lm_head.weight if self.lm_head is not None else self.chunks[-1].embed_tokens.weight
+
+    # ---- names of this stage's parameters in the un-partitioned model (checkpoints use those)
+    def global_param_name(self, local_name: str) -> str:
+        if local_name.startswith("chunks."):
+            rest = local_name.split(".", 2)[2]
+            return "model." + rest
+        return local_name  # lm_head.*, mtp_layers.*
+
+    def owns_global_param(self, local_name: str) -> bool:
+        # the input embedding belongs to the first stage; the copy on the last stage (tied head / MTP) is not saved
+        if ".embed_tokens." in local_name and not self.is_first:
+            return False
+        return True
+
+    def weight_map(self):
+        from ..models.modeling import build_weight_map
+
+        return build_weight_map(self.config)
+
+    def _init_weights(self, module):
+        pass
 
     def forward_chunk(self, c: int, x, batch, ctx):
         model = self.chunks[c]

@@ -170,8 +170,9 @@ class PretrainedModel(nn.Module):
                 t = dequant(name, t)
             return t
 
-        targets = dict(self.named_parameters())
-        targets.update({k: v for k, v in self.named_buffers() if k in self.state_dict()})
+        local_targets = dict(self.named_parameters())
+        local_targets.update({k: v for k, v in self.named_buffers() if k in self.state_dict()})
+        targets = {self.global_param_name(k): v for k, v in local_targets.items()}
         with torch.no_grad():
             for name, p in targets.items():
                 rule = wm.rule_for(name)
@@ -207,7 +208,7 @@ class PretrainedModel(nn.Module):
                 mod_name = name.rsplit(".", 1)[0]
                 try:
                     self._init_weights(self.get_submodule(mod_name))
-                except Exception:
+                except Exception:  # noqa: BLE001 - names of pipeline stages are global, modules local
                     pass
         logger.info(f"loaded {loaded} tensors from {directory}")
 
@@ -224,8 +225,15 @@ class PretrainedModel(nn.Module):
         dense_writer = ps.dataset_rank == 0 and ps.coord["cp"] == 0 and ps.coord["sep"] == 0
         expert_writer = ps.rank_in("moe_sharding") == 0
         sd = self.state_dict()
-        for name, t in sd.items():
-            spec = param_shard_spec(self._param_or_buffer(name))
+        seen = set()
+        for local_name, t in sd.items():
+            name = self.global_param_name(local_name)
+            if name in seen:   # a parameter shared by two pipeline stages is written once
+                continue
+            seen.add(name)
+            if not self.owns_global_param(local_name):
+                continue
+            spec = param_shard_spec(self._param_or_buffer(local_name))
             is_expert = spec.ep_dim is not None
             full = t.detach()
             if spec.tp_dim is not None and tp_size > 1:
@@ -244,6 +252,14 @@ class PretrainedModel(nn.Module):
             for hf_name, ten in rule.inverse(full.cpu(), secs, offset).items():
                 yield hf_name, ten
 
+    def global_param_name(self, local_name: str) -> str:
+        """Name of a local parameter in the un-partitioned model (identity unless the model is a pipeline stage)."""
+        return local_name
+
+    def owns_global_param(self, local_name: str) -> bool:
+        """False for copies of a parameter whose primary owner is another pipeline stage."""
+        return True
+
     def _param_or_buffer(self, name: str):
         mod_name, _, leaf = name.rpartition(".")
         mod = self.get_submodule(mod_name) if mod_name else self
@@ -255,6 +271,8 @@ class PretrainedModel(nn.Module):
         ps = get_parallel_state()
         os.makedirs(save_directory, exist_ok=True)
         writer_tag = ps.weight_name_suffix() if (ps.degrees.ep > 1 or ps.degrees.pp > 1) else None
+        if writer_tag is None and ps.degrees.pp > 1:
+            writer_tag = f"pp{ps.coord['pp']:02d}"
         shards: List[Dict[str, torch.Tensor]] = [{}]
         size = 0
         for hf_name, ten in self.hf_state_dict_items():

@@ -9,11 +9,14 @@ def _tiny_cfg(moe=False, **kw):
     from paddleformers_b200.models.configuration import named_config
 
     if moe:
-        return named_config("qwen3-30b-a3b", num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
-                            head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, vocab_size=128,
-                            router_aux_loss_coef=0.0, **kw)
-    return named_config("tiny-llama", num_hidden_layers=2, hidden_size=64, intermediate_size=96, num_attention_heads=4,
-                        num_key_value_heads=2, head_dim=16, vocab_size=128, **kw)
+        base = dict(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                    num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, vocab_size=128, router_aux_loss_coef=0.0)
+        base.update(kw)
+        return named_config("qwen3-30b-a3b", **base)
+    base = dict(num_hidden_layers=2, hidden_size=64, intermediate_size=96, num_attention_heads=4, num_key_value_heads=2,
+                head_dim=16, vocab_size=128)
+    base.update(kw)
+    return named_config("tiny-llama", **base)
 
 
 def _data(n, S=32, vocab=128):
@@ -43,7 +46,10 @@ def _train(rank, world, moe, targs, steps, full_state):
                              learning_rate=1e-2, lr_scheduler_type="constant", logging_steps=1, save_strategy="no",
                              max_seq_len=32, max_grad_norm=1.0, seed=3, device="cpu", **targs)
     ps = args.setup_parallel()
-    cfg = _tiny_cfg(moe, sequence_parallel=args.sequence_parallel)
+    from paddleformers_b200.transformers.configuration_utils import LlmMetaConfig
+
+    cfg = _tiny_cfg(moe)
+    LlmMetaConfig.set_llm_config(cfg, args)
     model = MODEL_MAPPING[cfg.model_type](cfg)
     # load the same full weights on every configuration, cut for this rank
     with torch.no_grad():
@@ -84,5 +90,65 @@ def test_parallel_matches_single_process(name, world, moe, targs):
     got = run_distributed(_train, world, moe, targs, steps, full)
     for r in range(world):
         assert len(got[r]) == steps
+        for a, b in zip(ref, got[r]):
+            assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (name, ref, got[r])
+
+
+def _train_pp(rank, world, moe, targs, steps, full_state):
+    from paddleformers_b200 import Trainer, TrainingArguments
+    from paddleformers_b200.parallel.pipeline import build_pipeline_model
+    from paddleformers_b200.transformers.configuration_utils import LlmMetaConfig
+    from paddleformers_b200.transformers.model_utils import param_shard_spec
+
+    args = TrainingArguments(output_dir="/tmp/pfb_test_unused", per_device_train_batch_size=1, max_steps=steps,
+                             learning_rate=1e-2, lr_scheduler_type="constant", logging_steps=1, save_strategy="no",
+                             max_seq_len=32, max_grad_norm=1.0, seed=3, device="cpu", **targs)
+    ps = args.setup_parallel()
+    cfg = _tiny_cfg(moe, num_hidden_layers=4)
+    LlmMetaConfig.set_llm_config(cfg, args)
+    model = build_pipeline_model(cfg)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            g = model.global_param_name(name)
+            spec = param_shard_spec(p)
+            p.copy_(spec.shard(full_state[g], ps.coord["mp"], ps.degrees.mp, ps.rank_in("ep"), ps.degrees.ep))
+    tr = Trainer(model=model, args=args, train_dataset=_DS(_data(8 * steps)))
+    tr.train()
+    return [h["loss"] for h in tr.state.log_history if "loss" in h]
+
+
+def _train_single4(rank, world, moe, targs, steps, full_state):
+    from paddleformers_b200 import Trainer, TrainingArguments
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+
+    args = TrainingArguments(output_dir="/tmp/pfb_test_unused", per_device_train_batch_size=1, max_steps=steps,
+                             learning_rate=1e-2, lr_scheduler_type="constant", logging_steps=1, save_strategy="no",
+                             max_seq_len=32, max_grad_norm=1.0, seed=3, device="cpu", **targs)
+    args.setup_parallel()
+    cfg = _tiny_cfg(moe, num_hidden_layers=4)
+    model = MODEL_MAPPING[cfg.model_type](cfg)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            p.copy_(full_state[name])
+    tr = Trainer(model=model, args=args, train_dataset=_DS(_data(8 * steps)))
+    tr.train()
+    return [h["loss"] for h in tr.state.log_history if "loss" in h]
+
+
+@pytest.mark.parametrize("name,targs", [
+    ("pp2_1f1b", dict(pipeline_model_parallel_size=2, gradient_accumulation_steps=4)),
+    ("pp2_interleaved", dict(pipeline_model_parallel_size=2, virtual_pipeline_model_parallel_size=2, gradient_accumulation_steps=4,
+                             pipeline_schedule="interleaved")),
+])
+def test_pipeline_matches_single_process(name, targs):
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+
+    steps = 2
+    torch.manual_seed(5)
+    cfg = _tiny_cfg(False, num_hidden_layers=4)
+    full = {k: v.detach().clone() for k, v in MODEL_MAPPING[cfg.model_type](cfg).named_parameters()}
+    ref = run_distributed(_train_single4, 1, False, dict(gradient_accumulation_steps=4), steps, full)[0]
+    got = run_distributed(_train_pp, 2, False, targs, steps, full)
+    for r in range(2):
         for a, b in zip(ref, got[r]):
             assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (name, ref, got[r])
