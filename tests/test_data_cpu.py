@@ -1,0 +1,121 @@
+"""Data pipeline: templates, packing, collators and their mask semantics, mmap datasets."""
+import json
+import os
+
+import numpy as np
+import torch
+
+from paddleformers_b200.datasets.collate import (calc_padding_size, collate_fn, dpo_collate_fn,
+                                                 gen_attn_mask_startend_row_indices, gen_self_attn_mask)
+from paddleformers_b200.datasets.sft_dataset import (IGNORE_INDEX, Sequence, create_dataset, encode_example, pack_sequences)
+from paddleformers_b200.datasets.template import get_template
+from paddleformers_b200.ops.functional import dense_mask_from_kend
+
+
+class _Tok:
+    """Whitespace tokenizer with a growing vocabulary (enough for dataflow tests)."""
+
+    eos_token, eos_token_id, pad_token_id = "</s>", 1, 0
+
+    def __init__(self):
+        self.vocab = {"<pad>": 0, "</s>": 1}
+
+    def encode(self, text, add_special_tokens=False):
+        out = []
+        for w in text.replace("</s>", " </s> ").split():
+            out.append(self.vocab.setdefault(w, len(self.vocab)))
+        return out
+
+
+def _seq(n, start=0):
+    return Sequence(list(range(start, start + n)), list(range(start + 1, start + n + 1)), list(range(n)))
+
+
+def test_row_indices_match_dense_mask_and_reference_semantics():
+    kend = gen_attn_mask_startend_row_indices([3, 2], 7)
+    assert kend.tolist() == [3, 3, 3, 5, 5, 5, 6]  # documents end at 3 and 5, pad keys mask themselves
+    dense = gen_self_attn_mask([3, 2], 7)[0]
+    ref = dense_mask_from_kend(torch.from_numpy(kend)[None], 7, True, "cpu")[0].numpy()
+    assert (dense == ref).all()
+    assert dense[4, 3] and not dense[4, 2] and not dense[5, 3] and not dense[6, 6]
+    assert gen_attn_mask_startend_row_indices([3, 2], 7, use_global_causal_attn=True).tolist() == [5, 5, 5, 5, 5, 5, 6]
+
+
+def test_packing_strategies():
+    seqs = [_seq(n) for n in (5, 3, 6, 2, 4)]
+    greedy = list(pack_sequences(seqs, 8, "greedy"))
+    assert [[len(s) for s in b] for b in greedy] == [[5, 3], [6, 2], [4]]
+    bins = list(pack_sequences(seqs, 8, "binpacking"))
+    assert all(sum(len(s) for s in b) <= 8 for b in bins) and len(bins) == 3
+    assert sorted(len(s) for b in bins for s in b) == [2, 3, 4, 5, 6]
+    assert len(list(pack_sequences(seqs, 8, "truncate"))) == 5
+
+
+def test_collate_padding_free_and_padded():
+    class A:
+        context_parallel_size, tensor_model_parallel_size, sequence_parallel, fp8 = 2, 2, True, None
+
+    assert calc_padding_size(13, A) == 16
+    batch = [[_seq(3), _seq(2, 10)], [_seq(4, 20)]]
+    out = collate_fn(batch, _Tok(), None, max_seq_len=6)
+    assert out["input_ids"].shape == (2, 6) and out["labels"][0, 5] == IGNORE_INDEX
+    assert out["attn_mask_startend_row_indices"][0].tolist() == [3, 3, 3, 5, 5, 5]
+    assert out["position_ids"][0].tolist() == [0, 1, 2, 0, 1, 0]
+    flat = collate_fn(batch, _Tok(), None, padding_free=True)
+    assert flat["input_ids"].shape == (1, 9)
+    assert flat["attn_mask_startend_row_indices"][0].tolist() == [3, 3, 3, 5, 5, 9, 9, 9, 9]
+
+
+def test_template_masks_prompt_and_dataset_roundtrip(tmp_path):
+    tok = _Tok()
+    ex = {"messages": [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi there"},
+                       {"role": "assistant", "content": "hello friend"}]}
+    s = encode_example(ex, tok, get_template("default"), 64)
+    trained = [l for l in s.labels if l != IGNORE_INDEX]
+    assert trained == tok.encode("hello friend </s>")
+    # tool call rendering
+    pairs = get_template("qwen").render_turns(
+        [{"role": "user", "content": "weather?"}, {"role": "assistant", "content": "", "tool_calls": [{"name": "get", "arguments": {"c": 1}}]},
+         {"role": "tool", "content": "sunny"}, {"role": "assistant", "content": "It is sunny"}], tools=[{"name": "get"}])
+    assert "<tool_call>" in pairs[0][1] and "<tool_response>" in pairs[1][0] and "# Tools" in pairs[0][0]
+    p = tmp_path / "a.jsonl"
+    with open(p, "w") as f:
+        for i in range(10):
+            f.write(json.dumps({"src": [f"question {i}"], "tgt": [f"answer {i} " * (i + 1)]}) + "\n")
+    ds = create_dataset(str(p), tok, 32, template="default", packing="greedy")
+    assert len(ds) >= 2 and all(sum(len(s) for s in sample) <= 32 for sample in ds.samples)
+    mixed = create_dataset(f"{p},{p}", tok, 32, dataset_prob="0.5,0.5", template="default", mix_strategy="interleave", streaming=True)
+    assert sum(len(sample) for sample in mixed) == 20
+
+
+def test_dpo_collate_layout():
+    out = dpo_collate_fn([{"prompt_ids": [5, 6, 7], "chosen_ids": [8, 9], "rejected_ids": [10, 11, 12]}], max_seq_len=12)
+    assert out["input_ids"][0, :11].tolist() == [5, 6, 7, 8, 9, 5, 6, 7, 10, 11, 12]
+    assert out["response_indexs"][0].tolist() == [0, 2, 4, 7, 10]
+    assert out["chosen_labels"][0, 2:4].tolist() == [8, 9] and out["rejected_labels"][0, 7:10].tolist() == [10, 11, 12]
+    assert out["attn_mask_startend_row_indices"][0, :11].tolist() == [5] * 5 + [11] * 6
+
+
+def test_mmap_dataset_and_gpt_samples(tmp_path):
+    from paddleformers_b200.data.indexed_dataset import (BlendableDataset, GPTDataset, MMapIndexedDataset,
+                                                         MMapIndexedDatasetBuilder, build_train_valid_test_datasets)
+
+    prefix = str(tmp_path / "corpus")
+    b = MMapIndexedDatasetBuilder(prefix, dtype=np.uint16)
+    docs = [np.arange(10 * i, 10 * i + 7 + i) for i in range(12)]
+    for d in docs:
+        b.add_document(d)
+    b.finalize()
+    ds = MMapIndexedDataset(prefix)
+    assert len(ds) == 12 and (ds[3] == docs[3]).all() and (ds.get(3, 2, 3) == docs[3][2:5]).all()
+    g = GPTDataset(ds, None, num_samples=8, seq_length=16, seed=1, shuffle=False)
+    stream = np.concatenate(docs)
+    item = g[2]
+    assert item["input_ids"].tolist() == stream[32:48].tolist() and item["labels"].tolist() == stream[33:49].tolist()
+    g2 = GPTDataset(ds, None, num_samples=8, seq_length=16, seed=1, shuffle=True)
+    g3 = GPTDataset(ds, None, num_samples=8, seq_length=16, seed=1, shuffle=True)
+    assert all(torch.equal(g2[i]["input_ids"], g3[i]["input_ids"]) for i in range(len(g2)))
+    blend = BlendableDataset([g, g2], [0.75, 0.25], 16)
+    assert (blend.dataset_index == 0).sum() == 12
+    tr, va, te = build_train_valid_test_datasets([prefix], "8,2,2", 16, [4, 1, 1], seed=3)
+    assert tr is not None and len(tr) >= 4 and va is not None
