@@ -1,0 +1,1 @@
+from .utils import GenerationConfig, GenerationMixin, KVCache, generate  # noqa: F401

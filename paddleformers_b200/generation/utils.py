@@ -1,0 +1,179 @@
+"""Text generation: greedy, sampling (temperature / top-k / top-p / repetition penalty) and beam search with a
+key/value cache, stopping criteria and a streamer hook.
+
+Counterpart: paddleformers/generation/utils.py:347 (``GenerationMixin``), :818 (``generate``), the logits processors
+and stopping criteria of paddleformers/generation/.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+from dataclasses import asdict, dataclass, field
+from typing import Callable, List, Optional
+
+import torch
+import torch.nn.functional as TF
+
+
+@dataclass
+class GenerationConfig:
+    max_new_tokens: int = 64
+    do_sample: bool = False
+    temperature: float = 1.0
+    top_k: int = 0
+    top_p: float = 1.0
+    repetition_penalty: float = 1.0
+    num_beams: int = 1
+    length_penalty: float = 1.0
+    eos_token_id: Optional[int] = None
+    pad_token_id: Optional[int] = None
+    stop_token_ids: List[int] = field(default_factory=list)
+
+    def save_pretrained(self, d: str):
+        os.makedirs(d, exist_ok=True)
+        with open(os.path.join(d, "generation_config.json"), "w") as f:
+            json.dump(asdict(self), f, indent=2)
+
+    @classmethod
+    def from_pretrained(cls, d: str):
+        p = os.path.join(d, "generation_config.json")
+        if not os.path.exists(p):
+            return cls()
+        with open(p) as f:
+            raw = json.load(f)
+        return cls(**{k: v for k, v in raw.items() if k in cls.__dataclass_fields__})
+
+
+class KVCache:
+    """Per-layer key / value store for incremental decoding (GQA layers of the unified decoder)."""
+
+    def __init__(self):
+        self.k: Optional[torch.Tensor] = None   # [B, S, Hkv, D]
+        self.v: Optional[torch.Tensor] = None
+
+    def attend(self, attn, qkv2d, ctx):
+        B, S, Hq, Hkv, D = ctx.B, ctx.S, attn.Hq, attn.Hkv, attn.D
+        q = qkv2d[:, : Hq * D].reshape(B, S, Hq, D)
+        k = qkv2d[:, Hq * D:(Hq + Hkv) * D].reshape(B, S, Hkv, D)
+        v = qkv2d[:, (Hq + Hkv) * D:].reshape(B, S, Hkv, D)
+        self.k = k if self.k is None else torch.cat([self.k, k], 1)
+        self.v = v if self.v is None else torch.cat([self.v, v], 1)
+        Sk = self.k.shape[1]
+        qf = q.permute(0, 2, 1, 3).float()
+        kf = self.k.permute(0, 2, 1, 3).float().repeat_interleave(Hq // Hkv, 1)
+        vf = self.v.permute(0, 2, 1, 3).float().repeat_interleave(Hq // Hkv, 1)
+        s = qf @ kf.transpose(-1, -2) * attn.scale
+        i = torch.arange(Sk - S, Sk, device=q.device)[:, None]
+        j = torch.arange(Sk, device=q.device)[None]
+        s = s.masked_fill(~(j <= i)[None, None], float("-inf"))
+        o = torch.softmax(s, -1) @ vf
+        return o.permute(0, 2, 1, 3).reshape(B * S, Hq * D).to(qkv2d.dtype)
+
+    def reorder(self, idx):
+        self.k, self.v = self.k.index_select(0, idx), self.v.index_select(0, idx)
+
+
+def _process_logits(logits, generated, cfg: GenerationConfig):
+    if cfg.repetition_penalty != 1.0 and generated.numel():
+        score = logits.gather(1, generated)
+        score = torch.where(score < 0, score * cfg.repetition_penalty, score / cfg.repetition_penalty)
+        logits = logits.scatter(1, generated, score)
+    if cfg.do_sample:
+        if cfg.temperature != 1.0:
+            logits = logits / max(cfg.temperature, 1e-5)
+        if cfg.top_k > 0:
+            kth = logits.topk(min(cfg.top_k, logits.shape[-1]), dim=-1)[0][:, -1:]
+            logits = logits.masked_fill(logits < kth, float("-inf"))
+        if cfg.top_p < 1.0:
+            sl, si = logits.sort(dim=-1, descending=True)
+            cp = torch.softmax(sl, -1).cumsum(-1)
+            remove = cp - torch.softmax(sl, -1) > cfg.top_p
+            sl = sl.masked_fill(remove, float("-inf"))
+            logits = torch.full_like(logits, float("-inf")).scatter(1, si, sl)
+    return logits
+
+
+@torch.no_grad()
+def generate(model, input_ids: torch.Tensor, generation_config: Optional[GenerationConfig] = None,
+             streamer: Optional[Callable[[torch.Tensor], None]] = None, **kw) -> torch.Tensor:
+    cfg = generation_config or GenerationConfig()
+    for k, v in kw.items():
+        setattr(cfg, k, v)
+    if cfg.eos_token_id is None:
+        cfg.eos_token_id = getattr(model.config, "eos_token_id", None)
+    if cfg.num_beams > 1:
+        return _beam_search(model, input_ids, cfg)
+    stops = set(cfg.stop_token_ids) | ({cfg.eos_token_id} if cfg.eos_token_id is not None else set())
+    layers = list(model.model.layer_range)
+    use_cache = not model.config.is_mla
+    caches = {i: KVCache() for i in layers} if use_cache else None
+    B = input_ids.shape[0]
+    seq = input_ids
+    done = torch.zeros(B, dtype=torch.bool, device=input_ids.device)
+    cur, past = input_ids, 0
+    for _ in range(cfg.max_new_tokens):
+        pos = torch.arange(past, past + cur.shape[1], device=cur.device)[None].expand(B, -1)
+        out = model(cur if use_cache else seq, position_ids=pos if use_cache else None, caches=caches, return_logits=True)
+        logits = _process_logits(out.logits[:, -1].float(), seq, cfg)
+        nxt = torch.multinomial(torch.softmax(logits, -1), 1) if cfg.do_sample else logits.argmax(-1, keepdim=True)
+        if cfg.pad_token_id is not None:
+            nxt = torch.where(done[:, None], torch.full_like(nxt, cfg.pad_token_id), nxt)
+        seq = torch.cat([seq, nxt], 1)
+        if streamer is not None:
+            streamer(nxt)
+        for s in stops:
+            done |= nxt[:, 0] == s
+        if bool(done.all()):
+            break
+        past += cur.shape[1]
+        cur = nxt
+    return seq
+
+
+def _beam_search(model, input_ids, cfg: GenerationConfig):
+    B, nb = input_ids.shape[0], cfg.num_beams
+    dev = input_ids.device
+    seq = input_ids.repeat_interleave(nb, 0)
+    scores = torch.zeros(B, nb, device=dev)
+    scores[:, 1:] = -1e9
+    finished: List[List] = [[] for _ in range(B)]
+    L0 = input_ids.shape[1]
+    for step in range(cfg.max_new_tokens):
+        out = model(seq, return_logits=True)
+        lp = torch.log_softmax(out.logits[:, -1].float(), -1)
+        V = lp.shape[-1]
+        cand = (scores.view(-1, 1) + lp).view(B, nb * V)
+        top, idx = cand.topk(2 * nb, dim=-1)
+        beam, tok = idx // V, idx % V
+        new_seq, new_scores = [], []
+        for b in range(B):
+            keep = []
+            for sc, bm, tk in zip(top[b].tolist(), beam[b].tolist(), tok[b].tolist()):
+                cand_seq = torch.cat([seq[b * nb + bm], torch.tensor([tk], device=dev)])
+                if cfg.eos_token_id is not None and tk == cfg.eos_token_id:
+                    finished[b].append((sc / ((cand_seq.numel() - L0) ** cfg.length_penalty), cand_seq))
+                else:
+                    keep.append((sc, cand_seq))
+                if len(keep) == nb:
+                    break
+            while len(keep) < nb:
+                keep.append((-1e9, keep[-1][1] if keep else seq[b * nb]))
+            new_seq += [k[1] for k in keep]
+            new_scores.append([k[0] for k in keep])
+        seq = torch.stack(new_seq)
+        scores = torch.tensor(new_scores, device=dev)
+        if all(len(f) >= nb for f in finished):
+            break
+    outs = []
+    for b in range(B):
+        pool = finished[b] + [(scores[b, i].item() / max(seq.shape[1] - L0, 1) ** cfg.length_penalty, seq[b * nb + i]) for i in range(nb)]
+        outs.append(max(pool, key=lambda x: x[0])[1])
+    n = max(o.numel() for o in outs)
+    pad = cfg.pad_token_id if cfg.pad_token_id is not None else (cfg.eos_token_id or 0)
+    return torch.stack([torch.cat([o, o.new_full((n - o.numel(),), pad)]) for o in outs])
+
+
+class GenerationMixin:
+    def generate(self, input_ids, generation_config=None, **kw):
+        return generate(self, input_ids, generation_config, **kw)

@@ -158,11 +158,11 @@ class MLAAttention(nn.Module):
     def forward(self, x2d, ctx: BatchContext, cache=None):
         T = ctx.B * ctx.S
         if self.q_lora:
-            qa = self.q_a_layernorm(F.linear(x2d, self.q_a_proj.weight))
+            qa = self.q_a_layernorm(_apply(self.q_a_proj, x2d))
             q = _apply(self.q_b_proj, qa)
         else:
             q = _apply(self.q_proj, x2d)
-        ckv = F.linear(x2d, self.kv_a_proj_with_mqa.weight)
+        ckv = _apply(self.kv_a_proj_with_mqa, x2d)
         if self.sp:  # replicated projections ran on token shards: gather tokens for the per-head products
             ckv = GatherOp.apply(ckv, self.group)
         kv_lat, k_pe = ckv[:, : self.kv_lora], ckv[:, self.kv_lora:]
@@ -220,7 +220,7 @@ class MTPLayer(nn.Module):
 
     def forward(self, h2d, shifted_emb2d, ctx):
         x = torch.cat([self.enorm(shifted_emb2d), self.hnorm(h2d)], dim=-1)
-        x = F.linear(x, self.eh_proj.weight)
+        x = _apply(self.eh_proj, x)
         out, res = self.block(x, None, ctx)
         return self.final_layernorm(out, res)[0]
 

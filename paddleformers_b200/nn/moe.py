@@ -295,11 +295,14 @@ class DenseMLP(nn.Module):
     def forward(self, x):
         if self._tp:
             return self.down_proj(self.gate_up_proj(x))
-        if self.gate_up_proj.bias is None:
-            act = F.linear_swiglu(x, self.gate_up_proj.weight)
+        gu, dn = self.gate_up_proj, self.down_proj
+        if not isinstance(gu, nn.Linear):          # wrapped (e.g. LoRA): the wrapper owns the projection
+            act = F.swiglu(gu(x))
+        elif gu.bias is None:
+            act = F.linear_swiglu(x, gu.weight)
         else:
-            act = F.swiglu(F.linear(x, self.gate_up_proj.weight, self.gate_up_proj.bias))
-        return F.linear(act, self.down_proj.weight, self.down_proj.bias)
+            act = F.swiglu(F.linear(x, gu.weight, gu.bias))
+        return F.linear(act, dn.weight, dn.bias) if isinstance(dn, nn.Linear) else dn(act)
 
 
 class MoELayer(nn.Module):

@@ -1,0 +1,1 @@
+from .lora import LoRAConfig, LoRALinear, LoRAModel, LoRAMoeExperts  # noqa: F401
