@@ -1,0 +1,133 @@
+"""Block-scaled fp8 (e4m3) quantisation: 1x128 activation blocks, 128x128 weight blocks, fp32 or power-of-two (UE8M0)
+scales; reference math for the CUDA quantisation kernels and the fp8 linear layers.
+
+Counterparts: paddleformers/transformers/fp8_utils.py:105-131, 262-268 (block shapes), the Triton
+``act_quant_kernel`` / ``weight_dequant_kernel`` (paddleformers/cli/train/deepseek_v3_pretrain/kernel.py:29-125) and
+the UE8M0 flag (paddleformers/transformers/configuration_utils.py:454-459).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+FP8_MAX = 448.0
+BLOCK = 128
+
+
+def _pow2_scale(s: torch.Tensor) -> torch.Tensor:
+    """Round scales up to the next power of two (the value an UE8M0 byte can hold)."""
+    return torch.exp2(torch.ceil(torch.log2(s.clamp(min=2.0 ** -127))))
+
+
+def quant_act_1x128(x: torch.Tensor, ue8m0: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """x: [T, K] -> (e4m3 [T, K], scales fp32 [T, ceil(K/128)]) with x ~= q * scale per 1x128 block."""
+    T, K = x.shape
+    nb = (K + BLOCK - 1) // BLOCK
+    pad = nb * BLOCK - K
+    xf = torch.nn.functional.pad(x.float(), (0, pad)).view(T, nb, BLOCK)
+    amax = xf.abs().amax(-1).clamp(min=1e-12)
+    scale = amax / FP8_MAX
+    if ue8m0:
+        scale = _pow2_scale(scale)
+    q = (xf / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).view(T, nb * BLOCK)[:, :K].to(torch.float8_e4m3fn)
+    return q, scale
+
+
+def quant_weight_128x128(w: torch.Tensor, ue8m0: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """w: [N, K] -> (e4m3 [N, K], scales fp32 [ceil(N/128), ceil(K/128)])."""
+    N, K = w.shape
+    nn_, nk = (N + BLOCK - 1) // BLOCK, (K + BLOCK - 1) // BLOCK
+    wf = torch.nn.functional.pad(w.float(), (0, nk * BLOCK - K, 0, nn_ * BLOCK - N)).view(nn_, BLOCK, nk, BLOCK)
+    amax = wf.abs().amax(dim=(1, 3)).clamp(min=1e-12)
+    scale = amax / FP8_MAX
+    if ue8m0:
+        scale = _pow2_scale(scale)
+    q = (wf / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).view(nn_ * BLOCK, nk * BLOCK)[:N, :K].to(torch.float8_e4m3fn)
+    return q, scale
+
+
+def dequant_act(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    T, K = q.shape
+    s = scale.repeat_interleave(BLOCK, dim=1)[:, :K]
+    return q.float() * s
+
+
+def dequant_weight(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    N, K = q.shape
+    s = scale.repeat_interleave(BLOCK, dim=0)[:N].repeat_interleave(BLOCK, dim=1)[:, :K]
+    return q.float() * s
+
+
+def fp8_gemm_reference(xq, xs, wq, ws) -> torch.Tensor:
+    """Block-scaled product x @ w^T in fp32: per 128-wide K block, partial products are scaled by
+    act_scale[t, kb] * weight_scale[n // 128, kb] (the math of the reference's Triton fp8 GEMM,
+    paddleformers/cli/train/deepseek_v3_pretrain/kernel.py:129-186)."""
+    return dequant_act(xq, xs) @ dequant_weight(wq, ws).t()
+
+
+class _FP8LinearFn(torch.autograd.Function):
+    """fp8 forward and input-gradient products with bf16 master weights; the weight gradient stays in bf16 inputs
+    (quantised activations are not precise enough to be re-used for wgrad at 1x128 granularity along tokens)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, wq, ws, ue8m0):
+        x2 = x.reshape(-1, x.shape[-1])
+        xq, xs = quant_act_1x128(x2, ue8m0)
+        y = fp8_gemm_reference(xq, xs, wq, ws).to(x.dtype)
+        ctx.save_for_backward(x2, weight, wq, ws)
+        ctx.ue8m0, ctx.shape = ue8m0, x.shape
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, wq, ws = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dq, ds = quant_act_1x128(dy2, ctx.ue8m0)
+        dx = (dequant_act(dq, ds) @ dequant_weight(wq, ws)).to(dy.dtype).view(ctx.shape)
+        mg = getattr(weight, "main_grad", None)
+        dw = dy2.float().t() @ x2.float()
+        if mg is not None:
+            mg.add_(dw)
+            return dx, None, None, None, None
+        return dx, dw.to(weight.dtype), None, None, None
+
+
+class FP8Linear(nn.Module):
+    """Linear layer computing in block-scaled fp8 with a cached quantised copy of the bf16 master weight; the cache is
+    refreshed after each optimizer step by ``FP8QuantWeightCallback``."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, ue8m0: bool = True, dtype=None, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
+        self.ue8m0 = ue8m0
+        self._wq = self._ws = None
+        nn.init.normal_(self.weight, std=0.02)
+
+    def refresh_fp8_weight_cache(self):
+        with torch.no_grad():
+            self._wq, self._ws = quant_weight_128x128(self.weight.detach(), self.ue8m0)
+
+    def forward(self, x):
+        if self._wq is None or self._wq.device != self.weight.device:
+            self.refresh_fp8_weight_cache()
+        y = _FP8LinearFn.apply(x, self.weight, self._wq, self._ws, self.ue8m0)
+        return y + self.bias if self.bias is not None else y
+
+
+def convert_linears_to_fp8(model: nn.Module, skip=("lm_head", "gate")) -> int:
+    """Replace ``nn.Linear`` modules by ``FP8Linear`` sharing the same parameters; returns the number converted."""
+    n = 0
+    for name, mod in list(model.named_modules()):
+        if isinstance(mod, nn.Linear) and not any(s in name for s in skip):
+            parent_name, _, leaf = name.rpartition(".")
+            parent = model.get_submodule(parent_name) if parent_name else model
+            new = FP8Linear(mod.in_features, mod.out_features, mod.bias is not None, dtype=mod.weight.dtype, device=mod.weight.device)
+            new.weight = mod.weight
+            new.bias = mod.bias
+            setattr(parent, leaf, new)
+            n += 1
+    return n

@@ -1,0 +1,83 @@
+"""Quantisation, checkpoint de-quantisation and model merging."""
+import os
+
+import torch
+
+from paddleformers_b200.quantization.checkpoint_dequant import dequant_fp8_block, dequant_mxfp4, quant_mxfp4
+from paddleformers_b200.quantization.fp8 import (FP8Linear, dequant_act, dequant_weight, fp8_gemm_reference, quant_act_1x128,
+                                                 quant_weight_128x128)
+from paddleformers_b200.quantization.weight_only import QuantizationLinear
+
+
+def test_fp8_block_quant_roundtrip_and_gemm():
+    torch.manual_seed(0)
+    x, w = torch.randn(37, 300), torch.randn(200, 300)
+    for ue8m0 in (False, True):
+        xq, xs = quant_act_1x128(x, ue8m0)
+        wq, ws = quant_weight_128x128(w, ue8m0)
+        assert xs.shape == (37, 3) and ws.shape == (2, 3)
+        if ue8m0:
+            assert torch.equal(torch.log2(xs), torch.log2(xs).round())
+        assert ((dequant_act(xq, xs) - x).norm() / x.norm()) < 0.05
+        assert ((dequant_weight(wq, ws) - w).norm() / w.norm()) < 0.05
+        y = fp8_gemm_reference(xq, xs, wq, ws)
+        assert ((y - x @ w.t()).norm() / (x @ w.t()).norm()) < 0.06
+    assert torch.allclose(dequant_fp8_block(wq, ws).float(), dequant_weight(wq, ws), atol=0.05, rtol=0.02)
+
+
+def test_fp8_linear_trains():
+    torch.manual_seed(1)
+    lin = FP8Linear(256, 128, dtype=torch.float32)
+    x = torch.randn(16, 256, requires_grad=True)
+    y = lin(x)
+    y.sum().backward()
+    ref = torch.nn.functional.linear(x, lin.weight)
+    assert ((y - ref).norm() / ref.norm()) < 0.06 and lin.weight.grad is not None and x.grad is not None
+
+
+def test_mxfp4_roundtrip():
+    torch.manual_seed(2)
+    x = torch.randn(4, 64)
+    blocks, scales = quant_mxfp4(x)
+    assert blocks.shape == (4, 2, 16) and scales.shape == (4, 2)
+    back = dequant_mxfp4(blocks, scales, torch.float32)
+    assert ((back - x).norm() / x.norm()) < 0.25
+    b2, s2 = quant_mxfp4(back)
+    assert torch.equal(dequant_mxfp4(b2, s2, torch.float32), back)   # representable values are fixed points
+
+
+def test_weight_only_linears():
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(128, 64)
+    x = torch.randn(5, 128)
+    for algo, tol in (("wint8", 0.02), ("wint4", 0.2), ("nf4", 0.15)):
+        q = QuantizationLinear(lin, algo)
+        assert ((q(x) - lin(x)).norm() / lin(x).norm()) < tol
+
+
+def test_merge_methods(tmp_path):
+    from safetensors.torch import load_file, save_file
+
+    from paddleformers_b200.mergekit import MergeConfig, MergeModel
+
+    torch.manual_seed(4)
+    base = {"a.weight": torch.randn(8, 8), "b.weight": torch.randn(4)}
+    m1 = {k: v + 0.1 * torch.randn_like(v) for k, v in base.items()}
+    m2 = {k: v + 0.1 * torch.randn_like(v) for k, v in base.items()}
+    for name, sd in (("base", base), ("m1", m1), ("m2", m2)):
+        os.makedirs(tmp_path / name)
+        save_file(sd, str(tmp_path / name / "model.safetensors"))
+        (tmp_path / name / "config.json").write_text("{}")
+    paths = [str(tmp_path / "m1"), str(tmp_path / "m2")]
+    out = MergeModel(MergeConfig("linear", paths, weight_list=[1, 3], output_path=str(tmp_path / "lin"))).merge()
+    got = load_file(os.path.join(out, "model.safetensors"))
+    assert torch.allclose(got["a.weight"], 0.25 * m1["a.weight"] + 0.75 * m2["a.weight"], atol=1e-6)
+    out = MergeModel(MergeConfig("slerp", paths, slerp_t=0.0, output_path=str(tmp_path / "sl"))).merge()
+    assert torch.allclose(load_file(os.path.join(out, "model.safetensors"))["a.weight"], m1["a.weight"], atol=1e-5)
+    out = MergeModel(MergeConfig("ties", paths, base_model_path=str(tmp_path / "base"), reserve_p=1.0, sparsify_type="trim",
+                                 output_path=str(tmp_path / "ties"))).merge()
+    t = load_file(os.path.join(out, "model.safetensors"))["a.weight"]
+    d1, d2 = m1["a.weight"] - base["a.weight"], m2["a.weight"] - base["a.weight"]
+    same = torch.sign(d1) == torch.sign(d2)
+    assert torch.allclose(t[same], (base["a.weight"] + (d1 + d2) / 2)[same], atol=1e-5)
+    assert os.path.exists(os.path.join(out, "config.json"))
