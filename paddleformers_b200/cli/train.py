@@ -1,0 +1,157 @@
+"""Stage router and workflows: ``stage`` in {SFT, PT, DPO} -> build config, model, tokenizer, datasets, collator,
+trainer; train; export the final HF checkpoint.
+
+Counterparts: paddleformers/cli/train/tuner.py:33-68 (router), paddleformers/cli/train/sft/workflow.py:196
+(``run_sft``) and paddleformers/cli/train/dpo/workflow.py:65 (``run_dpo``).
+"""
+from __future__ import annotations
+
+import functools
+import os
+from typing import Optional
+
+import torch
+
+from ..transformers.auto import AutoConfig, AutoModelForCausalLM, AutoTokenizer
+from ..transformers.configuration_utils import LlmMetaConfig
+from ..utils.log import logger
+from .hparams import get_train_args
+
+
+def _build_model(model_args, train_args, dtype):
+    if model_args.model_name_or_path and os.path.isdir(model_args.model_name_or_path) or (model_args.model_name_or_path and not model_args.from_scratch and not model_args.model_type):
+        config = AutoConfig.from_pretrained(model_args.model_name_or_path, **(model_args.config_overrides or {}))
+    else:
+        from ..models.configuration import CONFIG_MAPPING, named_config
+
+        over = model_args.config_overrides or {}
+        try:
+            config = named_config(model_args.model_type, **over)
+        except KeyError:
+            config = CONFIG_MAPPING[model_args.model_type](**over)
+    LlmMetaConfig.set_llm_config(config, train_args)
+    config.dtype = str(dtype).replace("torch.", "")
+    device = torch.device(train_args.device)
+    if model_args.from_scratch or not model_args.model_name_or_path:
+        model = AutoModelForCausalLM.from_config(config, dtype=dtype, device=device)
+    else:
+        model = AutoModelForCausalLM.from_pretrained(model_args.model_name_or_path, config=config, dtype=dtype, device=device)
+    if train_args.weight_quantize_algo:
+        from ..quantization.weight_only import quantize_model
+
+        n = quantize_model(model, train_args.weight_quantize_algo)
+        logger.info(f"quantised {n} linear layers to {train_args.weight_quantize_algo}")
+    if model_args.lora:
+        from ..peft.lora import LoRAConfig, LoRAModel
+
+        if model_args.lora_path:
+            model = LoRAModel.from_pretrained(model, model_args.lora_path)
+        else:
+            cfg = LoRAConfig(r=model_args.lora_rank, lora_alpha=model_args.lora_alpha, lora_dropout=model_args.lora_dropout,
+                             rslora=model_args.rslora, lora_plus_scale=model_args.lora_plus_scale)
+            if model_args.lora_target_modules:
+                cfg.target_modules = model_args.lora_target_modules
+            model = LoRAModel(model, cfg)
+        logger.info(model.print_trainable_parameters())
+    return model, config
+
+
+def _tokenizer(model_args):
+    if model_args.model_name_or_path:
+        try:
+            return AutoTokenizer.from_pretrained(model_args.model_name_or_path)
+        except Exception as e:  # noqa: BLE001
+            logger.warning(f"no tokenizer loaded from {model_args.model_name_or_path}: {e}")
+    return None
+
+
+def run_sft(model_args, data_args, gen_args, train_args, pretrain: bool = False):
+    from ..datasets.collate import collate_fn
+    from ..datasets.sft_dataset import create_dataset
+    from ..trainer.sft_trainer import SFTTrainer
+
+    train_args.setup_parallel()
+    dtype = train_args.compute_dtype
+    model, config = _build_model(model_args, train_args, dtype)
+    tokenizer = _tokenizer(model_args)
+    if pretrain and data_args.input_dir:
+        from ..data.indexed_dataset import build_train_valid_test_datasets
+        from ..trainer.trainer import default_data_collator
+
+        prefix = data_args.input_dir.split()
+        n_train = max(train_args.max_steps, 1) * train_args.global_batch_size
+        train_ds, eval_ds, _ = build_train_valid_test_datasets(prefix, data_args.split, train_args.max_seq_len,
+                                                               [n_train, max(n_train // 100, 1), 0], seed=train_args.seed,
+                                                               eos_token_id=getattr(tokenizer, "eos_token_id", None),
+                                                               build_masks=model_args.use_attn_mask_startend_row_indices)
+        collator = default_data_collator
+    else:
+        if tokenizer is None:
+            raise ValueError("SFT needs a tokenizer (model_name_or_path with tokenizer files)")
+        packing = data_args.packing_strategy if data_args.packing else "truncate"
+        train_ds = create_dataset(data_args.train_dataset_path, tokenizer, train_args.max_seq_len, data_args.train_dataset_prob,
+                                  template=data_args.template, packing=packing, mix_strategy=data_args.mix_strategy,
+                                  streaming=data_args.streaming, train_on_prompt=data_args.train_on_prompt or pretrain,
+                                  seed=train_args.seed)
+        eval_ds = None
+        if data_args.eval_dataset_path:
+            eval_ds = create_dataset(data_args.eval_dataset_path, tokenizer, train_args.max_seq_len, data_args.eval_dataset_prob,
+                                     template=data_args.template, packing=packing)
+        collator = functools.partial(collate_fn, tokenizer=tokenizer, training_args=train_args,
+                                     max_seq_len=None if data_args.padding_free else train_args.max_seq_len,
+                                     padding_free=data_args.padding_free,
+                                     use_attn_mask_startend_row_indices=model_args.use_attn_mask_startend_row_indices,
+                                     use_global_causal_attn=model_args.use_global_causal_attn)
+    trainer = SFTTrainer(model=model, args=train_args, data_collator=collator, train_dataset=train_ds, eval_dataset=eval_ds,
+                         tokenizer=tokenizer)
+    metrics = None
+    if train_args.do_train:
+        metrics = trainer.train(resume_from_checkpoint=train_args.resume_from_checkpoint)
+        tokens = train_args.max_seq_len * train_args.global_batch_size * trainer.state.global_step
+        rt = metrics.get("train_runtime", 0) or 1e-9
+        logger.info(f"Total_Tokens_per_second_per_gpu: {tokens / rt / max(train_args.world_size, 1):.2f}")
+        trainer.save_model(train_args.output_dir)
+    if train_args.do_eval and eval_ds is not None:
+        trainer.evaluate()
+    return trainer, metrics
+
+
+def run_dpo(model_args, data_args, gen_args, train_args):
+    from ..datasets.collate import dpo_collate_fn
+    from ..datasets.dpo_dataset import create_dpo_dataset
+    from ..trainer.dpo_trainer import DPOTrainer
+
+    train_args.setup_parallel()
+    dtype = train_args.compute_dtype
+    model, config = _build_model(model_args, train_args, dtype)
+    tokenizer = _tokenizer(model_args)
+    if tokenizer is None:
+        raise ValueError("DPO needs a tokenizer")
+    ref = None
+    if not model_args.lora and train_args.dpo_loss_type not in ("or", "simpo"):
+        ref_path = train_args.ref_model_name_or_path or model_args.model_name_or_path
+        ref = AutoModelForCausalLM.from_pretrained(ref_path, dtype=dtype, device=torch.device(train_args.device))
+    ds = create_dpo_dataset(data_args.train_dataset_path, tokenizer, train_args.max_seq_len, data_args.template)
+    collator = functools.partial(dpo_collate_fn, tokenizer=tokenizer, training_args=train_args, max_seq_len=train_args.max_seq_len)
+    trainer = DPOTrainer(model=model, args=train_args, data_collator=collator, train_dataset=ds, tokenizer=tokenizer, ref_model=ref,
+                         dpo_beta=train_args.dpo_beta, dpo_loss_type=train_args.dpo_loss_type,
+                         dpo_label_smoothing=train_args.dpo_label_smoothing, sft_loss_ratio=train_args.sft_loss_ratio)
+    metrics = trainer.train(resume_from_checkpoint=train_args.resume_from_checkpoint)
+    trainer.save_model(train_args.output_dir)
+    return trainer, metrics
+
+
+def run_tuner(argv: Optional[list] = None):
+    model_args, data_args, gen_args, export_args, train_args = get_train_args(argv)
+    stage = model_args.stage.upper()
+    if stage in ("SFT", "VL-SFT"):
+        return run_sft(model_args, data_args, gen_args, train_args)
+    if stage in ("PT", "CPT", "VL-PT"):
+        return run_sft(model_args, data_args, gen_args, train_args, pretrain=True)
+    if stage in ("DPO", "VL-DPO"):
+        return run_dpo(model_args, data_args, gen_args, train_args)
+    raise ValueError(f"unknown stage {model_args.stage!r}; expected SFT | PT | DPO")
+
+
+if __name__ == "__main__":
+    run_tuner()
