@@ -41,6 +41,7 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (the result is then marked invalid)")
     ap.add_argument("--no-e2e", action="store_true", help="debug only: skip the end-to-end pass")
+    ap.add_argument("--cuda-graph", type=int, default=-1, help="1/0: replay each micro-batch from a CUDA graph (default: on for dense models)")
     return ap.parse_args()
 
 
@@ -158,7 +159,7 @@ def main():
     ta = TrainingArguments(output_dir="/tmp/pfb_bench_out", per_device_train_batch_size=1, gradient_accumulation_steps=accum,
                            max_steps=W + K, learning_rate=3e-4, lr_scheduler_type="constant", weight_decay=0.1,
                            adam_beta2=0.95, max_grad_norm=1.0, bf16=True, logging_steps=1, save_strategy="no",
-                           max_seq_len=S, seed=0, **targs)
+                           max_seq_len=S, seed=0, cuda_graph=(args.cuda_graph == 1 or (args.cuda_graph < 0 and not is_moe)), **targs)
     ta.setup_parallel()
     cfg.sequence_parallel = ta.sequence_parallel
     cfg.tensor_model_parallel_size = ta.tensor_model_parallel_size
@@ -258,18 +259,27 @@ def main():
                        "micro_batch": 1, "grad_accum": accum, "parallelism": par,
                        "optimizer": "AdamW fp32 master + fp32 main_grad, sharding stage1",
                        "l2": "no explicit flush: every step streams >= 16 GB of weights plus activations, far above the 126 MB L2",
-                       "layers": cfg.num_hidden_layers},
+                       "layers": cfg.num_hidden_layers, "cuda_graph": bool(ta.cuda_graph),
+                       "fused_tp_collectives": os.environ.get("PFB_FUSED_TP", "1") != "0" and world > 1 and not is_moe},
             "tokens_per_second_per_gpu": per_gpu, "model_flops_per_token": fpt,
             "model_tflops_per_gpu": per_gpu * fpt / 1e12, "mfu_vs_nominal_2.25PF": per_gpu * fpt / NOMINAL_BF16_FLOPS,
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "impl": "ours",
         }
+        if world > 1:
+            from paddleformers_b200.parallel import fused_collectives as fc
+
+            out["fused_collective_calls"] = dict(fc.STATS)
         if args.layers:
             out["invalid"] = "truncated model (--layers): debug run, not a benchmark value"
         print(json.dumps(out))
     if dist.is_initialized():
         dist.barrier()
-        dist.destroy_process_group()
-    return 0
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    # Captured CUDA graphs keep references to communicator state; tearing the process group down with them alive can
+    # block forever. The result is already printed, so leave without running the teardown.
+    os._exit(0)
 
 
 if __name__ == "__main__":

@@ -54,10 +54,25 @@ def check_kernel_status(reset: bool = True) -> int:
     return code
 
 
+_replayed_launches = 0
+
+
+def add_replayed_launches(n: int) -> None:
+    """Kernels launched by replaying a captured CUDA graph never pass through the host-side launchers; the owner of
+    the graph reports how many of this library's kernels one replay contains."""
+    global _replayed_launches
+    _replayed_launches += int(n)
+
+
 def kernel_launch_count(reset: bool = False) -> int:
+    """Number of this library's kernels launched so far (eager launches + kernels inside replayed graphs)."""
+    global _replayed_launches
     if not _build.is_loaded() and not _build.load_extension():
         return 0
-    return int(torch.ops.pfb200.launch_count(reset))
+    n = int(torch.ops.pfb200.launch_count(reset)) + _replayed_launches
+    if reset:
+        _replayed_launches = 0
+    return n
 
 
 # ----------------------------------------------------------------------------------------------------------------

@@ -176,6 +176,11 @@ class ColumnParallelLinear(nn.Module):
             self.bias.shard_spec = ("tp", 0, sections)
 
     def forward(self, x):
+        if self.sequence_parallel and self.bias is None and not self.gather_output:
+            from . import fused_collectives as fc
+
+            if x.dim() == 2 and fc.get_tp_workspace() is not None and fc.can_fuse(x, self.weight, self.tp, x.shape[0] * self.tp):
+                return fc.fused_column_parallel(x, self.weight, self, swiglu=self.epilogue == "swiglu")
         if self.tp > 1:
             x = AllGatherOp.apply(x, self.group) if self.sequence_parallel else CopyToTP.apply(x, self.group)
         if self.epilogue == "swiglu":
@@ -209,6 +214,13 @@ class RowParallelLinear(nn.Module):
             mark_as_sequence_parallel_parameter(self.bias)
 
     def forward(self, x):
+        if self.sequence_parallel and x.dim() == 2:
+            from . import fused_collectives as fc
+
+            if (fc.get_tp_workspace() is not None and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[0] % (self.tp * 128) == 0
+                    and self.out_features % 128 == 0 and x.shape[1] % 8 == 0):
+                y = fc.fused_row_parallel(x, self.weight)
+                return y + self.bias if self.bias is not None else y
         y = F.linear(x, self.weight)
         if self.tp > 1:
             y = ReduceScatterOp.apply(y, self.group) if self.sequence_parallel else ReduceFromTP.apply(y, self.group)

@@ -184,6 +184,8 @@ class Trainer:
     def training_step(self, model, inputs: Dict[str, Any]) -> torch.Tensor:
         model.train()
         inputs = self._prepare_inputs(inputs)
+        if self.args.cuda_graph and self.device.type == "cuda":
+            return self._graphed_training_step(model, inputs)
         loss, outputs = self.compute_loss(model, inputs)
         loss.backward()
         self.optimizer.accumulate_grads()
@@ -191,6 +193,58 @@ class Trainer:
         if nt is not None:
             self._interval_tokens = nt if self._interval_tokens is None else self._interval_tokens + nt
         return loss.detach()
+
+    def _graphed_training_step(self, model, inputs: Dict[str, Any]) -> torch.Tensor:
+        """One micro-batch of forward + backward as a CUDA graph replay. At tensor-parallel degree 8 a decoder layer
+        is a few dozen kernels of 10-100 us each, far less than the host needs to launch them through autograd; the
+        graph removes the host from the loop. The first ``cuda_graph_warmup`` calls per input signature run eagerly
+        (they create workspaces, scratch buffers and function attributes), the next one captures."""
+        from ..ops import functional as F
+
+        tensors = {k: v for k, v in inputs.items() if isinstance(v, torch.Tensor)}
+        key = tuple(sorted((k, tuple(v.shape), str(v.dtype)) for k, v in tensors.items()))
+        graphs = self.__dict__.setdefault("_graphs", {})
+        st = graphs.setdefault(key, {"warm": 0})
+        if st["warm"] < self.args.cuda_graph_warmup:
+            st["warm"] += 1
+            loss, outputs = self.compute_loss(model, inputs)
+            loss.backward()
+            self.optimizer.accumulate_grads()
+            nt = getattr(outputs, "num_tokens", None)
+            if nt is not None:
+                self._interval_tokens = nt if self._interval_tokens is None else self._interval_tokens + nt
+            return loss.detach()
+        if "graph" not in st:
+            static_in = {k: v.clone() for k, v in tensors.items()}
+            others = {k: v for k, v in inputs.items() if not isinstance(v, torch.Tensor)}
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+            g = torch.cuda.CUDAGraph()
+            n0 = F.kernel_launch_count()
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                loss, outputs = self.compute_loss(model, dict(static_in, **others))
+                loss.backward()
+                self.optimizer.accumulate_grads()
+                static_loss = loss.detach()
+                ntok = getattr(outputs, "num_tokens", None)
+            st.update(graph=g, inputs=static_in, loss=static_loss, ntok=ntok, launches=F.kernel_launch_count() - n0)
+        for k, v in tensors.items():
+            st["inputs"][k].copy_(v, non_blocking=True)
+        st["graph"].replay()
+        F.add_replayed_launches(st["launches"])
+        if st["ntok"] is not None:
+            self._interval_tokens = st["ntok"].clone() if self._interval_tokens is None else self._interval_tokens + st["ntok"]
+        return st["loss"].clone()
+
+    def release_graphs(self) -> None:
+        """Drop captured CUDA graphs (call before destroying the process group: graphs that captured collectives keep
+        communicator resources alive)."""
+        import gc
+
+        self.__dict__.pop("_graphs", None)
+        gc.collect()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
 
     def training_pipeline_step(self, model, micro_batches: List[Dict[str, Any]]) -> torch.Tensor:
         if self.pipeline_engine is None:

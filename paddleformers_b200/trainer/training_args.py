@@ -104,6 +104,9 @@ class TrainingArguments:
     release_grads: bool = False
     moe_aux_free_bias_update_rate: float = 0.0
     count_trained_tokens: bool = False
+    cuda_graph: bool = field(default=False, metadata={"help": "capture one micro-batch of forward + backward in a CUDA graph "
+                                                          "and replay it (static shapes, dense models)"})
+    cuda_graph_warmup: int = 2
 
     def __post_init__(self):
         self.lr_scheduler_type = SchedulerType(self.lr_scheduler_type).value
