@@ -47,6 +47,13 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
   p.lse = lse.data_ptr<float>(); p.delta = delta.data_ptr<float>(); p.dq_acc = dq_acc.data_ptr<float>();
   p.dk = reinterpret_cast<__nv_bfloat16*>(dk3.data_ptr()); p.dv = reinterpret_cast<__nv_bfloat16*>(dv3.data_ptr());
   p.dk_row_stride = dk3.stride(0); p.dv_row_stride = dv3.stride(0);
+  at::Tensor dk_part, dv_part;
+  p.dk_part = nullptr; p.dv_part = nullptr;
+  if (Hq != Hkv) {
+    dk_part = at::empty({T, Hq, ATT_D}, lse.options());
+    dv_part = at::empty({T, Hq, ATT_D}, lse.options());
+    p.dk_part = dk_part.data_ptr<float>(); p.dv_part = dv_part.data_ptr<float>();
+  }
   p.kend = nullptr; p.tile_min_end = nullptr; p.tile_max_end = nullptr;
   const int kv_tiles = (S + ATTB_BKV - 1) / ATTB_BKV;
   if (kend.has_value()) {
@@ -64,7 +71,7 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
     C10_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem::TOTAL));
     cfg = true;
   }
-  dim3 grid(kv_tiles, Hkv, B);
+  dim3 grid(kv_tiles, Hq, B);
   attn_bwd_kernel<<<grid, ATTB_THREADS, AttnBwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmdO, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   {
@@ -74,7 +81,18 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
                                                           T, Hq * ATT_D, dq3.stride(0));
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   }
-  count_launch(3);
+  int launches = 3;
+  if (Hq != Hkv) {
+    const long long work = T * (Hkv * ATT_D / 4);
+    const int blocks = static_cast<int>(std::min<long long>((work + 255) / 256, 148LL * 16));
+    attn_bwd_dkv_reduce_kernel<<<blocks, 256, 0, stream>>>(dk_part.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(dk3.data_ptr()),
+                                                          T, Hq, Hkv, dk3.stride(0));
+    attn_bwd_dkv_reduce_kernel<<<blocks, 256, 0, stream>>>(dv_part.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(dv3.data_ptr()),
+                                                          T, Hq, Hkv, dv3.stride(0));
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    launches += 2;
+  }
+  count_launch(launches);
 }
 
 }  // namespace pfb

@@ -1,7 +1,8 @@
 // Flash attention backward for sm_100a (head_dim 128, GQA, causal + document masks), tcgen05 + TMEM.
 //
-// One CTA owns one 128-key tile of one KV head and walks over the query tiles (64 rows) of every query head of the
-// group. All five products of the backward pass run on the tensor cores with the key dimension on the TMEM lanes:
+// One CTA owns one 128-key tile and one query head and walks over that head's query tiles (64 rows); with grouped
+// queries the G heads of a KV head run as G CTAs whose fp32 dK / dV partials are summed by a small second kernel, so
+// that the grid stays large when tensor parallelism leaves a rank a single KV head. All five products of the backward pass run on the tensor cores with the key dimension on the TMEM lanes:
 //
 //   S^T  = K  Q^T            (128 keys x 64 queries, fp32 in TMEM)
 //   dP^T = V  dO^T
@@ -29,6 +30,8 @@ struct AttnBwdParams {
   float* dq_acc;         // [B*S, Hq, 128] fp32, zero-initialised
   __nv_bfloat16* dk;     // [B*S, Hkv, 128] views (row strides below, head stride 128)
   __nv_bfloat16* dv;
+  float* dk_part;        // [B*S, Hq, 128] fp32 per-query-head partials (nullptr when Hq == Hkv)
+  float* dv_part;
   long long dk_row_stride, dv_row_stride;
   const int* kend;           // [B, S] or nullptr
   const int* tile_min_end;   // [B, kv_tiles]
@@ -68,8 +71,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int jt = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int jt = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
   const int G = p.Hq / p.Hkv;
+  const int kvh = head / G;
   const int k0 = jt * ATTB_BKV;
   const int row_base = b * p.S;
   const int kv_tiles = (p.S + ATTB_BKV - 1) / ATTB_BKV;
@@ -97,7 +101,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     i_hi = min(i_hi, (tmax - 1) / ATTB_BQ);
   }
   const int n_q = max(i_hi - i_lo + 1, 0);
-  const int n_it = n_q * G;
+  const int n_it = n_q;
 
   if (warp == 4) {
     if (lane == 0 && n_it > 0) {
@@ -105,8 +109,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_dkv = make_idesc(128, ATT_D, false, true, 1);     // TMEM A x MN-major B
       constexpr uint32_t idesc_dq = make_idesc(128, ATTB_BQ, true, true, 1);     // MN-major x MN-major
       auto load_q = [&](int it) {
-        const int g = it / n_q, i = i_lo + (it - g * n_q);
-        const int head = kvh * G + g;
+        const int i = i_lo + it;
         const int st = it & 1;
         uint8_t* sq = smem + SM::Q_OFF + st * 2 * SM::Q_TILE;
         uint8_t* sdo = sq + SM::Q_TILE;
@@ -184,8 +187,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
       const uint32_t ph = it & 1;
-      const int g = it / n_q, i = i_lo + (it - g * n_q);
-      const int head = kvh * G + g;
+      const int i = i_lo + it;
       const int q0 = i * ATTB_BQ;
       // stage this tile's lse (in log2 units) and delta: every warp keeps a private copy
       __syncwarp();
@@ -290,7 +292,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           #pragma unroll
           for (int x = 0; x < 32; ++x) { a[x] = 0u; bb[x] = 0u; }
         }
-        if (kj < p.S) {
+        if (kj < p.S && p.dk_part != nullptr) {
+          float* pk = p.dk_part + (static_cast<long long>(row_base + kj) * p.Hq + head) * ATT_D + c;
+          float* pv2 = p.dv_part + (static_cast<long long>(row_base + kj) * p.Hq + head) * ATT_D + c;
+          #pragma unroll
+          for (int x = 0; x < 32; x += 4) {
+            *reinterpret_cast<float4*>(pk + x) = make_float4(__uint_as_float(a[x]), __uint_as_float(a[x + 1]), __uint_as_float(a[x + 2]), __uint_as_float(a[x + 3]));
+            *reinterpret_cast<float4*>(pv2 + x) = make_float4(__uint_as_float(bb[x]), __uint_as_float(bb[x + 1]), __uint_as_float(bb[x + 2]), __uint_as_float(bb[x + 3]));
+          }
+        } else if (kj < p.S) {
           #pragma unroll
           for (int x = 0; x < 32; x += 8) {
             *reinterpret_cast<uint4*>(dkp + c + x) = make_uint4(
@@ -332,6 +342,28 @@ __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ dO, cons
   for (int o2 = 16; o2 > 0; o2 >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o2);
   const long long b = t / S, si = t - b * S;
   if (lane == 0) delta[(b * Hq + h) * S + si] = s;
+}
+
+// dk / dv (bf16, strided rows) = sum over the G query heads of a group of the fp32 partials [T, Hq, 128]
+__global__ void attn_bwd_dkv_reduce_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, long long T,
+                                           int Hq, int Hkv, long long out_row_stride) {
+  const int G = Hq / Hkv;
+  const int nv = Hkv * (ATT_D / 4);
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < T * nv;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = idx / nv;
+    const int r = static_cast<int>(idx - t * nv);
+    const int kvh = r / (ATT_D / 4), d4 = r - kvh * (ATT_D / 4);
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int g = 0; g < G; ++g) {
+      const float4 v = reinterpret_cast<const float4*>(part + (t * Hq + kvh * G + g) * ATT_D)[d4];
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    uint2 o;
+    o.x = pack_bf16x2(s.x, s.y);
+    o.y = pack_bf16x2(s.z, s.w);
+    reinterpret_cast<uint2*>(out + t * out_row_stride + kvh * ATT_D)[d4] = o;
+  }
 }
 
 // dq (bf16, strided rows) = dq_acc (fp32, contiguous [T, Hq*128])
