@@ -80,7 +80,9 @@ class TPWorkspace:
         self.arena = SymmetricArena(self.group)
         self._rs: Dict[Tuple[int, int], dict] = {}
         self._bwd_ag: Dict[Tuple[int, int], dict] = {}
-        self.n_copy_ctas = int(os.environ.get("PFB_AG_COPY_CTAS", "8"))
+        # copy CTAs of the all-gather: 8 keep ~1.5 MB in flight (enough for one or three peers); with 7 peers 16 measured
+        # 4 % faster end to end
+        self.n_copy_ctas = int(os.environ.get("PFB_AG_COPY_CTAS", "16" if self.tp >= 8 else "8"))
 
     def layer_gather_buffers(self, T: int, K: int) -> dict:
         """Persistent buffers of one column-parallel layer."""
