@@ -91,7 +91,7 @@ class TopkRouter(nn.Module):
             w = w / (w.sum(-1, keepdim=True) + 1e-20)
         w = w * self.scale
         with torch.no_grad():
-            self.expert_usage += torch.bincount(idx.reshape(-1), minlength=E)
+            self.expert_usage.scatter_add_(0, idx.reshape(-1), torch.ones_like(idx.reshape(-1)))
         aux = None
         if self.training and (self.aux_coef > 0 or self.z_coef > 0):
             aux = x2d.new_zeros((), dtype=torch.float32)
@@ -108,6 +108,11 @@ class TopkRouter(nn.Module):
 # ---------------------------------------------------------------------------------------------------------------
 # permutation into expert-sorted, 128-row padded segments
 # ---------------------------------------------------------------------------------------------------------------
+def count_ids(ids: torch.Tensor, n: int) -> torch.Tensor:
+    """Histogram of ``ids`` (all in [0, n)) as int64 [n] without the host read-back that ``torch.bincount`` does."""
+    return torch.zeros(n, dtype=torch.int64, device=ids.device).scatter_add_(0, ids, torch.ones_like(ids))
+
+
 def build_dispatch_plan(idx: torch.Tensor, num_local_experts: int, expert_offset: int = 0, block: int = 128):
     """Sort (token, slot) pairs by expert and pad each expert segment to a multiple of ``block`` rows, entirely on
     the device (no host synchronisation: the padded buffer has a static upper-bound size).
@@ -118,13 +123,14 @@ def build_dispatch_plan(idx: torch.Tensor, num_local_experts: int, expert_offset
     flat = idx.reshape(-1) - expert_offset
     local = (flat >= 0) & (flat < num_local_experts)
     e = torch.where(local, flat, torch.full_like(flat, num_local_experts))
-    counts = torch.bincount(e, minlength=num_local_experts + 1)[:num_local_experts]
+    counts_all = count_ids(e, num_local_experts + 1)
+    counts = counts_all[:num_local_experts]
     padded = (counts + block - 1) // block * block
     seg_start = torch.cumsum(padded, 0) - padded
     # rank of each pair inside its expert (stable): sort by expert, then position - first position of that expert
     order = torch.argsort(e, stable=True)
     sorted_e = e[order]
-    first = torch.cumsum(torch.bincount(sorted_e, minlength=num_local_experts + 1), 0)
+    first = torch.cumsum(counts_all, 0)
     first = torch.cat([first.new_zeros(1), first[:-1]])
     rank_sorted = torch.arange(e.numel(), device=e.device) - first[sorted_e]
     rank = torch.empty_like(rank_sorted)
@@ -191,10 +197,13 @@ class GroupedExperts(nn.Module):
             p.is_expert = True           # gradients are reduced over the moe_sharding group only
             p.shard_spec = ("ep", 0, None)
 
-    def forward(self, rows: torch.Tensor, block_expert: torch.Tensor, counts: Optional[torch.Tensor] = None):
-        """rows: [R, H] expert-sorted with 128-row padded segments; returns [R, H]."""
+    def forward(self, rows: torch.Tensor, block_expert: torch.Tensor, counts: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None, expert_rows: Optional[torch.Tensor] = None):
+        """rows: [R, H] expert-sorted with 128-row padded segments; returns [R, H] (written into ``out`` when given,
+        e.g. a peer-visible buffer). ``expert_rows`` int32 [E, 2] = (first row, padded rows) per expert, if already
+        known."""
         if rows.is_cuda and rows.dtype == torch.bfloat16:
-            return _GroupedMlpFn.apply(rows, self.gate_up_proj, self.down_proj, block_expert)
+            return _GroupedMlpFn.apply(rows, self.gate_up_proj, self.down_proj, block_expert, out, expert_rows)
         out = torch.zeros_like(rows)
         be = block_expert.tolist()
         for b, e in enumerate(be):
@@ -212,16 +221,20 @@ class _GroupedMlpFn(torch.autograd.Function):
     per-expert wgrad GEMMs accumulating into fp32 ``main_grad`` when present."""
 
     @staticmethod
-    def forward(ctx, rows, w_gu, w_down, block_expert):
+    def forward(ctx, rows, w_gu, w_down, block_expert, out=None, expert_rows=None):
         E, N2, H = w_gu.shape
         I = N2 // 2
         R = rows.shape[0]
         raw = torch.empty((R, N2), dtype=rows.dtype, device=rows.device)
         act = torch.zeros((R, I), dtype=rows.dtype, device=rows.device)
         F.gemm(rows, w_gu.view(E * N2, H), out=act, epi=F.EPI_SWIGLU_BF16, out2=raw, block_expert=block_expert, n_per_expert=N2)
-        out = torch.zeros((R, H), dtype=rows.dtype, device=rows.device)
+        if out is None:
+            out = torch.zeros((R, H), dtype=rows.dtype, device=rows.device)
+        else:
+            ctx.mark_dirty(out)
         F.gemm(act, w_down.view(E * H, I), out=out, block_expert=block_expert, n_per_expert=H)
         ctx.save_for_backward(rows, w_gu, w_down, block_expert, raw)
+        ctx.expert_rows = expert_rows
         return out
 
     @staticmethod
@@ -239,10 +252,10 @@ class _GroupedMlpFn(torch.autograd.Function):
         drows = torch.zeros((R, H), dtype=rows.dtype, device=rows.device)
         _grouped_dgrad(dgu, w_gu, drows, block_expert)
         # weight gradients: one wgrad GEMM per local expert over its row segment
-        be = block_expert
-        dw_gu = _grouped_wgrad(dgu, rows, w_gu, be)
-        dw_down = _grouped_wgrad(dout, act, w_down, be)
-        return drows, dw_gu, dw_down, None
+        table = ctx.expert_rows if ctx.expert_rows is not None else expert_row_table(block_expert, E)
+        dw_gu = _grouped_wgrad(dgu, rows, w_gu, table)
+        dw_down = _grouped_wgrad(dout, act, w_down, table)
+        return drows, dw_gu, dw_down, None, None, None
 
 
 def _grouped_dgrad(dy, w, out, block_expert):
@@ -255,19 +268,18 @@ def _grouped_dgrad(dy, w, out, block_expert):
 def expert_row_table(block_expert: torch.Tensor, num_local: int) -> torch.Tensor:
     """int32 [E, 2] = (first row, row count) of each expert's padded segment, from the block -> expert table."""
     be = block_expert.to(torch.int64)
-    valid = be >= 0
-    cnt = torch.bincount(be[valid], minlength=num_local)[:num_local] * 128
+    cnt = count_ids(torch.where(be >= 0, be, torch.full_like(be, num_local)), num_local + 1)[:num_local] * 128
     start = torch.cumsum(cnt, 0) - cnt
     return torch.stack([start, cnt], dim=1).to(torch.int32).contiguous()
 
 
-def _grouped_wgrad(dy, x, w, block_expert):
-    """dW[e] = dy[seg_e]^T @ x[seg_e] for all local experts in one launch; accumulates into w.main_grad when
-    present."""
+def _grouped_wgrad(dy, x, w, table):
+    """dW[e] = dy[seg_e]^T @ x[seg_e] for all local experts in one launch (``table``: int32 [E, 2] row segments);
+    accumulates into w.main_grad when present."""
     E, N, K = w.shape
     mg = getattr(w, "main_grad", None)
     target = mg.view(E, N, K) if mg is not None else torch.zeros((E, N, K), dtype=torch.float32, device=w.device)
-    torch.ops.pfb200.gemm_wgrad_grouped(dy, x, target, expert_row_table(block_expert, E))
+    torch.ops.pfb200.gemm_wgrad_grouped(dy, x, target, table)
     return None if mg is not None else target.to(w.dtype)
 
 

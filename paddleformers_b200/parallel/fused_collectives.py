@@ -229,7 +229,7 @@ def can_fuse(x, weight, tp: int, tokens_total: int) -> bool:
 def get_ep_workspace(ps, x2d, layer):
     """Symmetric workspace of the fused dispatch / combine kernels, or None when they are not available (CPU ranks,
     extension built without them): the caller then uses the NCCL all-to-all path."""
-    if not x2d.is_cuda or not hasattr(torch.ops.pfb200, "ep_dispatch"):
+    if not x2d.is_cuda or not hasattr(torch.ops.pfb200, "ep_exchange"):
         return None
     from . import fused_ep
 

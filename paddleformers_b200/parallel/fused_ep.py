@@ -1,0 +1,182 @@
+"""Expert-parallel MoE exchange over NVLink peer memory: dispatch and combine without NCCL and without host reads.
+
+The NCCL path (``parallel.expert_parallel._alltoall_moe_forward``) reads the split sizes back to the host once per
+layer, which serialises the step and cannot be captured in a CUDA graph. Here the receive buffer has a static capacity
+and the whole exchange is stream-ordered device work (the role DeepEP's ``Buffer.dispatch`` / ``combine`` play for the
+reference, paddleformers/transformers/fused_a2a.py:81-178 and paddleformers/nn/moe_deepep/moe_communication.py:31-137):
+
+1. ``ep_exchange``   counts -> every destination; receive-side layout (expert segments padded to 128 rows, block ->
+                     expert table, per-expert row table) and per-source slot offsets -> every source.
+2. ``ep_push_rows``  each routed pair's row goes straight into its slot of the destination's receive buffer.
+3. grouped expert GEMMs on the receive buffer, output written into a peer-visible buffer.
+4. ``ep_pull_rows``  each source reads its k rows back and forms the weighted sum.
+
+The backward pass mirrors it: the combine's backward pushes ``w * dout`` rows and reads the expert outputs again for
+the routing-weight gradient; the dispatch's backward pulls the expert input gradients.
+
+Buffers. Per MoE layer: the receive buffer (it is the saved activation of the expert GEMMs) and the expert output
+buffer (read again in the backward pass). Per workspace: one gradient receive buffer and one input-gradient buffer;
+they can be shared by all layers because a rank cannot start the next layer's exchange before every peer has finished
+reading this layer's buffers (each step of the protocol waits for a flag from every peer). Flags are epoch-valued.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict
+
+import torch
+
+from .fused_collectives import SymmetricArena, _Region
+
+FLAG_COUNTS, FLAG_OFFSETS, FLAG_ROWS, FLAG_Y, FLAG_DY, FLAG_DX = 0, 1, 2, 3, 4, 5
+_MAX_RANKS = 8
+STATS = {"dispatch": 0, "combine": 0}
+
+
+def capacity_rows(tokens: int, top_k: int, ep: int, num_local: int, factor: float) -> int:
+    """Rows of the receive buffer: ``factor`` x the balanced share (every rank sends tokens*top_k pairs, so a balanced
+    rank receives tokens*top_k) plus one padding block per local expert."""
+    body = int(tokens * top_k * factor)
+    return ((body + 127) // 128 + num_local) * 128
+
+
+class EPWorkspace:
+    def __init__(self, ps, T: int, H: int, top_k: int, num_local: int):
+        self.ps = ps
+        self.group = ps.group("ep")
+        self.ep = ps.degrees.ep
+        self.rank = ps.rank_in("ep")
+        self.EL = num_local
+        self.T, self.H, self.k = T, H, top_k
+        assert self.ep <= _MAX_RANKS and num_local <= 64
+        self.factor = float(os.environ.get("PFB_EP_CAPACITY", "1.5"))
+        self.cap = capacity_rows(T, top_k, self.ep, num_local, self.factor)
+        self.arena = SymmetricArena(self.group)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.table = _Region(self.arena, (2 * self.ep * num_local + 8 * _MAX_RANKS,), torch.int32)
+        self.dy = _Region(self.arena, (self.cap, H), torch.bfloat16)
+        self.dxr = _Region(self.arena, (self.cap, H), torch.bfloat16)
+        self.fwd_epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.bwd_epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.done = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.total_rows = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def layer_buffers(self) -> dict:
+        return {"x_recv": _Region(self.arena, (self.cap, self.H), torch.bfloat16),
+                "y": _Region(self.arena, (self.cap, self.H), torch.bfloat16)}
+
+    # thin wrappers -------------------------------------------------------------------------------------------
+    def wait(self, slot: int, epoch):
+        torch.ops.pfb200.ep_wait_flag(self.table.peer_ptrs, self.rank, self.ep, self.EL, slot, epoch)
+
+    def signal(self, slot: int, epoch):
+        torch.ops.pfb200.ep_signal_flag(self.table.peer_ptrs, self.rank, self.ep, self.EL, slot, epoch)
+
+    def push(self, x, plan, scale, region: _Region, slot: int, epoch, slots_from_table: bool):
+        torch.ops.pfb200.ep_push_rows(x, plan["idx"], plan["rank_in_expert"], scale, self.table.peer_ptrs, plan["pair_slot"],
+                                      region.peer_ptrs, self.k, self.EL, self.ep, self.cap, self.rank, slot, epoch, self.done,
+                                      slots_from_table)
+
+    def pull(self, out, plan, w, g, dots, region: _Region):
+        torch.ops.pfb200.ep_pull_rows(out, plan["idx"], plan["pair_slot"], w, g, dots, region.peer_ptrs, self.table.peer_ptrs,
+                                      self.T, self.k, self.H, self.EL, self.ep, self.cap)
+
+
+_WS: Dict[tuple, EPWorkspace] = {}
+
+
+def get_workspace(ps, x2d, layer):
+    if x2d.dtype != torch.bfloat16 or x2d.shape[1] % 8 != 0 or ps.degrees.ep > _MAX_RANKS or os.environ.get("PFB_FUSED_EP", "1") == "0":
+        return None
+    T, H = x2d.shape
+    k = layer.gate.top_k
+    key = (id(ps), T, H, k, layer.experts.num_local)
+    if key not in _WS:
+        _WS[key] = EPWorkspace(ps, T, H, k, layer.experts.num_local)
+    return _WS[key]
+
+
+def make_plan(ws: EPWorkspace, idx: torch.Tensor) -> dict:
+    """Device-side bookkeeping of one exchange: per-expert pair counts and every pair's rank inside its expert (stable
+    in pair order), with no host read."""
+    from ..nn.moe import count_ids
+
+    E = ws.ep * ws.EL
+    flat = idx.reshape(-1).contiguous()
+    counts = count_ids(flat, E)
+    order = torch.argsort(flat, stable=True)
+    first = torch.cumsum(counts, 0) - counts
+    rank_sorted = torch.arange(flat.numel(), device=flat.device) - first[flat[order]]
+    rank_in_expert = torch.empty_like(rank_sorted)
+    rank_in_expert[order] = rank_sorted
+    dev = flat.device
+    return {"idx": flat, "counts": counts.to(torch.int32), "rank_in_expert": rank_in_expert.to(torch.int32),
+            "pair_slot": torch.empty(flat.numel(), dtype=torch.int32, device=dev),
+            "block_expert": torch.empty(ws.cap // 128, dtype=torch.int32, device=dev),
+            "expert_rows": torch.empty((ws.EL, 2), dtype=torch.int32, device=dev)}
+
+
+class _Dispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x2d, ws, bufs, plan):
+        ws.push(x2d.contiguous(), plan, None, bufs["x_recv"], FLAG_ROWS, ws.fwd_epoch, True)
+        ws.wait(FLAG_ROWS, ws.fwd_epoch)
+        ctx.ws, ctx.plan = ws, plan
+        ctx.shape = x2d.shape
+        STATS["dispatch"] += 1
+        return bufs["x_recv"].tensor.detach()      # a fresh tensor object per call: autograd attaches this call's graph to it
+
+    @staticmethod
+    def backward(ctx, g):
+        ws, plan = ctx.ws, ctx.plan
+        # g: gradient of the receive buffer rows, produced by the expert backward which has consumed ws.dy by now
+        ws.dxr.tensor.copy_(g)
+        ws.dy.tensor.zero_()        # padding rows of the next exchange must read as zero in the weight-gradient GEMMs
+        ws.signal(FLAG_DX, ws.bwd_epoch)
+        ws.wait(FLAG_DX, ws.bwd_epoch)
+        dx = torch.empty(ctx.shape, dtype=torch.bfloat16, device=g.device)
+        ws.pull(dx, plan, None, None, None, ws.dxr)
+        return dx, None, None, None
+
+
+class _Combine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y_rows, w, ws, bufs, plan):
+        # y_rows is bufs["y"].tensor, written by the expert GEMM that precedes this call in stream order
+        ws.signal(FLAG_Y, ws.fwd_epoch)
+        ws.wait(FLAG_Y, ws.fwd_epoch)
+        out = torch.empty((ws.T, ws.H), dtype=torch.bfloat16, device=y_rows.device)
+        wf = w.reshape(-1).float().contiguous()
+        ws.pull(out, plan, wf, None, None, bufs["y"])
+        ctx.ws, ctx.plan, ctx.bufs = ws, plan, bufs
+        ctx.save_for_backward(wf)
+        ctx.w_shape, ctx.w_dtype = w.shape, w.dtype
+        STATS["combine"] += 1
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        ws, plan, bufs = ctx.ws, ctx.plan, ctx.bufs
+        (wf,) = ctx.saved_tensors
+        dout = dout.contiguous()
+        ws.bwd_epoch.add_(1)
+        ws.push(dout, plan, wf, ws.dy, FLAG_DY, ws.bwd_epoch, False)   # reuses the slots recorded in the forward pass
+        dots = torch.empty(wf.numel(), dtype=torch.float32, device=dout.device)
+        ws.pull(None, plan, None, dout, dots, bufs["y"])
+        ws.wait(FLAG_DY, ws.bwd_epoch)
+        return ws.dy.tensor.detach(), dots.view(ctx.w_shape).to(ctx.w_dtype), None, None, None
+
+
+def moe_forward(ws: EPWorkspace, layer, x2d, idx, w):
+    """Routed-expert output [T, H] of ``layer`` for tokens x2d with routing (idx, w), experts spread over the ep group."""
+    bufs = getattr(layer, "_ep_bufs", None)
+    if bufs is None or bufs["x_recv"].tensor.shape != (ws.cap, ws.H):
+        bufs = ws.layer_buffers()
+        layer._ep_bufs = bufs
+    plan = make_plan(ws, idx)
+    ws.fwd_epoch.add_(1)
+    torch.ops.pfb200.ep_exchange(ws.table.peer_ptrs, plan["counts"], plan["block_expert"], plan["expert_rows"], ws.total_rows,
+                                 ws.rank, ws.ep, ws.EL, ws.fwd_epoch)
+    x_recv = _Dispatch.apply(x2d, ws, bufs, plan)
+    y_rows = layer.experts(x_recv, plan["block_expert"], None, out=bufs["y"].tensor.detach(), expert_rows=plan["expert_rows"])
+    return _Combine.apply(y_rows, w, ws, bufs, plan)

@@ -25,16 +25,20 @@ class SymmetricBuffer:
         self.group = group
         self.nbytes = int((nbytes + 255) // 256 * 256)
         self.device = device or torch.device("cuda", torch.cuda.current_device())
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
+        # a one-rank group (or no process group at all): the only peer is this rank itself, nothing to exchange
+        self._solo = not dist.is_initialized() or not isinstance(group, (dist.ProcessGroup, type(None)))
+        self.world = 1 if self._solo else dist.get_world_size(group)
+        self.rank = 0 if self._solo else dist.get_rank(group)
         self.local_ptr, handle = ops.symm_alloc(self.nbytes)
         handles: List[Optional[torch.Tensor]] = [None] * self.world
-        dist.all_gather_object(handles, handle, group=group)
+        if not self._solo:
+            dist.all_gather_object(handles, handle, group=group)
         self.peer_ptrs: List[int] = []
         for r, h in enumerate(handles):
             self.peer_ptrs.append(self.local_ptr if r == self.rank else int(ops.symm_open(h)))
         self.peer_ptrs_tensor = torch.tensor(self.peer_ptrs, dtype=torch.int64, device=self.device)
-        dist.barrier(group=group)
+        if not self._solo:
+            dist.barrier(group=group)
 
     def tensor(self, shape: Sequence[int], dtype: torch.dtype, byte_offset: int = 0) -> torch.Tensor:
         """View of the LOCAL copy."""
@@ -49,7 +53,8 @@ class SymmetricBuffer:
         for r, p in enumerate(self.peer_ptrs):
             if r != self.rank:
                 ops.symm_close(p)
-        dist.barrier(group=self.group)
+        if not self._solo:
+            dist.barrier(group=self.group)
         ops.symm_free(self.local_ptr)
 
 
