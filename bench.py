@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (the result is then marked invalid)")
     ap.add_argument("--no-e2e", action="store_true", help="debug only: skip the end-to-end pass")
+    ap.add_argument("--ep-dispatch", default="fused", choices=["fused", "alltoall"],
+                    help="MoE token exchange: peer-memory kernels or the NCCL all-to-all baseline")
     ap.add_argument("--cuda-graph", type=int, default=-1, help="1/0: replay each micro-batch from a CUDA graph (default: on for dense models)")
     return ap.parse_args()
 
@@ -146,6 +148,7 @@ def main():
         over["num_hidden_layers"] = args.layers
     cfg = named_config(args.model, **over)
     cfg.dtype = "bfloat16"
+    cfg.moe_token_dispatcher_type = args.ep_dispatch
     if is_moe:
         targs = dict(expert_model_parallel_size=world, sharding="stage1", tensor_model_parallel_size=1)
         par = f"ep{world}+sharding{world}(stage1)"
@@ -269,6 +272,11 @@ def main():
             from paddleformers_b200.parallel import fused_collectives as fc
 
             out["fused_collective_calls"] = dict(fc.STATS)
+            if is_moe:
+                from paddleformers_b200.parallel import fused_ep
+
+                out["config"]["ep_dispatch"] = args.ep_dispatch
+                out["fused_ep_calls"] = dict(fused_ep.STATS)
         if args.layers:
             out["invalid"] = "truncated model (--layers): debug run, not a benchmark value"
         print(json.dumps(out))

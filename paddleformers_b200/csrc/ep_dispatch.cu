@@ -27,7 +27,7 @@
 namespace pfb {
 
 constexpr int EP_MAX_RANKS = 8;
-constexpr int EP_MAX_LOCAL_EXPERTS = 64;
+constexpr int EP_MAX_LOCAL_EXPERTS = 128;
 
 struct EpTables {
   // symmetric int32 region per rank (see layout in fused_ep.py):

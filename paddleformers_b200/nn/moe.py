@@ -198,12 +198,14 @@ class GroupedExperts(nn.Module):
             p.shard_spec = ("ep", 0, None)
 
     def forward(self, rows: torch.Tensor, block_expert: torch.Tensor, counts: Optional[torch.Tensor] = None,
-                out: Optional[torch.Tensor] = None, expert_rows: Optional[torch.Tensor] = None):
+                out: Optional[torch.Tensor] = None, expert_rows: Optional[torch.Tensor] = None,
+                grad_rows_out: Optional[torch.Tensor] = None):
         """rows: [R, H] expert-sorted with 128-row padded segments; returns [R, H] (written into ``out`` when given,
         e.g. a peer-visible buffer). ``expert_rows`` int32 [E, 2] = (first row, padded rows) per expert, if already
-        known."""
+        known; ``grad_rows_out``: buffer that receives the gradient of ``rows`` in the backward pass. Rows of blocks
+        that belong to no expert are left unwritten in every output."""
         if rows.is_cuda and rows.dtype == torch.bfloat16:
-            return _GroupedMlpFn.apply(rows, self.gate_up_proj, self.down_proj, block_expert, out, expert_rows)
+            return _GroupedMlpFn.apply(rows, self.gate_up_proj, self.down_proj, block_expert, out, expert_rows, grad_rows_out)
         out = torch.zeros_like(rows)
         be = block_expert.tolist()
         for b, e in enumerate(be):
@@ -221,12 +223,13 @@ class _GroupedMlpFn(torch.autograd.Function):
     per-expert wgrad GEMMs accumulating into fp32 ``main_grad`` when present."""
 
     @staticmethod
-    def forward(ctx, rows, w_gu, w_down, block_expert, out=None, expert_rows=None):
+    def forward(ctx, rows, w_gu, w_down, block_expert, out=None, expert_rows=None, grad_rows_out=None):
         E, N2, H = w_gu.shape
         I = N2 // 2
         R = rows.shape[0]
+        # intermediate rows of unowned blocks are never read by the grouped kernels, so they need no initial value
         raw = torch.empty((R, N2), dtype=rows.dtype, device=rows.device)
-        act = torch.zeros((R, I), dtype=rows.dtype, device=rows.device)
+        act = torch.empty((R, I), dtype=rows.dtype, device=rows.device)
         F.gemm(rows, w_gu.view(E * N2, H), out=act, epi=F.EPI_SWIGLU_BF16, out2=raw, block_expert=block_expert, n_per_expert=N2)
         if out is None:
             out = torch.zeros((R, H), dtype=rows.dtype, device=rows.device)
@@ -235,6 +238,7 @@ class _GroupedMlpFn(torch.autograd.Function):
         F.gemm(act, w_down.view(E * H, I), out=out, block_expert=block_expert, n_per_expert=H)
         ctx.save_for_backward(rows, w_gu, w_down, block_expert, raw)
         ctx.expert_rows = expert_rows
+        ctx.grad_rows_out = grad_rows_out
         return out
 
     @staticmethod
@@ -246,16 +250,16 @@ class _GroupedMlpFn(torch.autograd.Function):
         dout = dout.contiguous()
         ops = torch.ops.pfb200
         # d(act) = dout @ W_down[e]  (grouped, B stored [H, I] per expert = MN-major for this product)
-        dact = torch.zeros((R, I), dtype=rows.dtype, device=rows.device)
+        dact = torch.empty((R, I), dtype=rows.dtype, device=rows.device)
         _grouped_dgrad(dout, w_down, dact, block_expert)
         dgu, act = ops.swiglu_bwd(dact, raw, True)
-        drows = torch.zeros((R, H), dtype=rows.dtype, device=rows.device)
+        drows = ctx.grad_rows_out if ctx.grad_rows_out is not None else torch.zeros((R, H), dtype=rows.dtype, device=rows.device)
         _grouped_dgrad(dgu, w_gu, drows, block_expert)
         # weight gradients: one wgrad GEMM per local expert over its row segment
         table = ctx.expert_rows if ctx.expert_rows is not None else expert_row_table(block_expert, E)
         dw_gu = _grouped_wgrad(dgu, rows, w_gu, table)
         dw_down = _grouped_wgrad(dout, act, w_down, table)
-        return drows, dw_gu, dw_down, None, None, None
+        return drows, dw_gu, dw_down, None, None, None, None
 
 
 def _grouped_dgrad(dy, w, out, block_expert):

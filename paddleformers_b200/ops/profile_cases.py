@@ -1,6 +1,6 @@
 """Small fixed workloads of each hot kernel for profiler captures:
 
-    python -m paddleformers_b200.ops.profile_cases --case gemm|attn_fwd|attn_bwd|gemm_swiglu|gemm_wgrad
+    python -m paddleformers_b200.ops.profile_cases --case gemm|attn_fwd|attn_bwd|gemm_swiglu|gemm_wgrad|moe_layer|moe_layer_local
 
 Each case launches its kernel a few times on inputs larger than the L2 cache but well under a few GB, so that an
 ``ncu --set full -k regex:<kernel> -c 1`` capture finishes in about a minute.
@@ -48,11 +48,47 @@ def case_attn(kind: str):
             out.backward(torch.ones_like(out))
 
 
+def case_moe_layer(kind: str):
+    """One MoE layer forward + backward with the per-rank shape of Qwen3-30B-A3B under 8-way expert parallelism
+    (16 local experts, 4096 tokens x top-8, hidden 2048, expert width 768). ``moe_layer`` exchanges tokens through the
+    peer-memory dispatch / combine kernels (a one-rank group: the rank exchanges with itself), ``moe_layer_local``
+    through the local permutation."""
+    from ..models.configuration import Qwen3MoeConfig
+    from ..nn.moe import MoELayer
+    from ..parallel import fused_ep
+    from ..parallel.topology import get_parallel_state
+
+    cfg = Qwen3MoeConfig(hidden_size=2048, num_experts=16, num_experts_per_tok=8, moe_intermediate_size=768, intermediate_size=768,
+                         num_hidden_layers=1, num_attention_heads=16, num_key_value_heads=4, vocab_size=128)
+    layer = MoELayer(cfg, dtype=torch.bfloat16, device="cuda")
+    for p in layer.parameters():
+        torch.nn.init.normal_(p, std=0.02)
+    x = torch.randn(4096, 2048, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn_like(x)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for it in range(4):
+        if it == 3:
+            start.record()
+        if kind == "moe_layer":
+            idx, w, _ = layer.gate(x)
+            ws = fused_ep.get_workspace(get_parallel_state(), x, layer)
+            y = fused_ep.moe_forward(ws, layer, x, idx, w)
+        else:
+            y = layer(x)
+        y.backward(g)
+    end.record()
+    torch.cuda.synchronize()
+    print(f"{kind}: forward+backward {start.elapsed_time(end):.3f} ms")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["gemm", "gemm_swiglu", "gemm_wgrad", "attn_fwd", "attn_bwd"])
+    ap.add_argument("--case", required=True, choices=["gemm", "gemm_swiglu", "gemm_wgrad", "attn_fwd", "attn_bwd", "moe_layer",
+                                                      "moe_layer_local"])
     args = ap.parse_args()
-    if args.case.startswith("gemm"):
+    if args.case.startswith("moe"):
+        case_moe_layer(args.case)
+    elif args.case.startswith("gemm"):
         case_gemm(args.case)
     else:
         case_attn(args.case)

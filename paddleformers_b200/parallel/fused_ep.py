@@ -48,7 +48,7 @@ class EPWorkspace:
         self.rank = ps.rank_in("ep")
         self.EL = num_local
         self.T, self.H, self.k = T, H, top_k
-        assert self.ep <= _MAX_RANKS and num_local <= 64
+        assert self.ep <= _MAX_RANKS and num_local <= 128
         self.factor = float(os.environ.get("PFB_EP_CAPACITY", "1.5"))
         self.cap = capacity_rows(T, top_k, self.ep, num_local, self.factor)
         self.arena = SymmetricArena(self.group)
@@ -130,7 +130,8 @@ class _Dispatch(torch.autograd.Function):
     def backward(ctx, g):
         ws, plan = ctx.ws, ctx.plan
         # g: gradient of the receive buffer rows, produced by the expert backward which has consumed ws.dy by now
-        ws.dxr.tensor.copy_(g)
+        if g.data_ptr() != ws.dxr.tensor.data_ptr():     # the expert backward normally writes straight into the buffer
+            ws.dxr.tensor.copy_(g)
         ws.dy.tensor.zero_()        # padding rows of the next exchange must read as zero in the weight-gradient GEMMs
         ws.signal(FLAG_DX, ws.bwd_epoch)
         ws.wait(FLAG_DX, ws.bwd_epoch)
@@ -178,5 +179,6 @@ def moe_forward(ws: EPWorkspace, layer, x2d, idx, w):
     torch.ops.pfb200.ep_exchange(ws.table.peer_ptrs, plan["counts"], plan["block_expert"], plan["expert_rows"], ws.total_rows,
                                  ws.rank, ws.ep, ws.EL, ws.fwd_epoch)
     x_recv = _Dispatch.apply(x2d, ws, bufs, plan)
-    y_rows = layer.experts(x_recv, plan["block_expert"], None, out=bufs["y"].tensor.detach(), expert_rows=plan["expert_rows"])
+    y_rows = layer.experts(x_recv, plan["block_expert"], None, out=bufs["y"].tensor.detach(), expert_rows=plan["expert_rows"],
+                          grad_rows_out=ws.dxr.tensor)
     return _Combine.apply(y_rows, w, ws, bufs, plan)
