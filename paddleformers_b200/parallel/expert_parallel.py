@@ -47,7 +47,9 @@ def ep_moe_forward(layer, x2d: torch.Tensor, idx: torch.Tensor, w: torch.Tensor)
     """Routed-expert part of an MoE layer under expert parallelism. x2d: [T, H]; idx, w: [T, k]."""
     ps = get_parallel_state()
     dispatcher = getattr(layer.config, "moe_token_dispatcher_type", "fused")
-    if dispatcher == "fused":
+    # the fused path keeps one micro-batch per layer in its peer-visible buffers: pipeline schedules, which hold several
+    # micro-batches in flight, stay on the all-to-all path
+    if dispatcher == "fused" and ps.degrees.pp == 1:
         from . import fused_collectives as fc
 
         ws = fc.get_ep_workspace(ps, x2d, layer)
