@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: ``python -m paddleformers_b200.ops.bench_kernels [--what gemm,attn,elementwise]``.
+"""Kernel micro-benchmarks: ``python -m paddleformers_b200.ops.bench_kernels [--what gemm,attn,elementwise,fp8]``.
 
 Times each kernel with CUDA events on the launching stream after warm-up, flushing L2 between timed launches by
 writing a 256 MiB buffer, and prints achieved TFLOP/s or GB/s next to the library kernel of the same shape
@@ -145,6 +145,35 @@ def bench_elementwise(rows):
     print(rows[-1], flush=True)
 
 
+def bench_fp8(rows):
+    """Block-scaled e4m3 GEMM and its quantisation kernels; beside them the bf16 tcgen05 GEMM of the same shape and
+    ``torch._scaled_mm`` with the same 1x128 / 128x128 scales where this torch build offers it."""
+    from ..quantization import fp8 as Q
+
+    for name, M, N, K in (("dsv3 gate_up", 4096, 4096, 7168), ("dsv3 down", 4096, 7168, 2048), ("square", 8192, 8192, 8192)):
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        xq, xs_t = Q.quant_act_kernel(x)
+        wq, ws = Q.quant_weight_kernel(w)
+        ms = timeit(lambda: Q.fp8_gemm(xq, xs_t, wq, ws, out=out))
+        ms_bf16 = timeit(lambda: F.gemm(x, w, out=out))
+        ms_qa = timeit(lambda: Q.quant_act_kernel(x))
+        ms_qw = timeit(lambda: Q.quant_weight_kernel(w))
+        fl = 2.0 * M * N * K
+        lib = float("nan")
+        try:
+            xs = xs_t.t().contiguous()
+            lib_ms = timeit(lambda: torch._scaled_mm(xq, wq.t(), scale_a=xs, scale_b=ws.t(), out_dtype=torch.bfloat16))
+            lib = fl / lib_ms / 1e9
+        except Exception:  # this torch build has no 1x128 / 128x128 scaled matmul
+            pass
+        rows.append(f"fp8 gemm {name:13s} M={M} N={N} K={K}: {fl / ms / 1e9:7.1f} TFLOP/s (bf16 kernel {fl / ms_bf16 / 1e9:7.1f}, "
+                    f"torch._scaled_mm {lib:7.1f}) | quant act {x.numel() * 3 / ms_qa / 1e6:6.0f} GB/s, "
+                    f"quant weight {w.numel() * 3 / ms_qw / 1e6:6.0f} GB/s")
+        print(rows[-1], flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", default="gemm,attn,elementwise")
@@ -152,7 +181,7 @@ def main():
     args = ap.parse_args()
     rows = []
     for w in args.what.split(","):
-        {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise}[w](rows)
+        {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise, "fp8": bench_fp8}[w](rows)
     if args.out:
         with open(args.out, "w") as f:
             f.write("\n".join(rows) + "\n")

@@ -61,6 +61,39 @@ def dequant_weight(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     return q.float() * s
 
 
+def _use_kernels(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16
+
+
+def quant_act_kernel(x: torch.Tensor, ue8m0: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """CUDA 1x128 quantisation of a bf16 [T, K] tensor (K % 128 == 0): (e4m3 [T, K], scales fp32 TRANSPOSED
+    [K/128, T], the layout the fp8 GEMM epilogue reads with coalesced loads)."""
+    from ..ops import functional as F
+
+    return F._ops().fp8_quant_act(x.contiguous(), ue8m0)
+
+
+def quant_weight_kernel(w: torch.Tensor, ue8m0: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """CUDA 128x128 quantisation of a bf16 [N, K] weight (K % 128 == 0): (e4m3 [N, K], scales fp32 [ceil(N/128), K/128])."""
+    from ..ops import functional as F
+
+    return F._ops().fp8_quant_weight(w.contiguous(), ue8m0)
+
+
+def fp8_gemm(xq, xs_t, wq, ws, block_expert=None, n_per_expert: int = 0, out=None) -> torch.Tensor:
+    """Block-scaled e4m3 product on the tcgen05 tensor cores: out[M, N] (bf16) = dequant(xq, xs_t^T) @ dequant(wq, ws)^T.
+    With ``block_expert`` (int32, one entry per 128 rows of xq, -1 = skip) ``wq`` holds E stacked [n_per_expert, K]
+    matrices and each row block is multiplied by its expert's matrix."""
+    from ..ops import functional as F
+
+    M = xq.shape[0]
+    N = n_per_expert if block_expert is not None else wq.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=xq.device)
+    F._ops().gemm_fp8(xq, xs_t, wq, ws, out, block_expert, n_per_expert)
+    return out
+
+
 def fp8_gemm_reference(xq, xs, wq, ws) -> torch.Tensor:
     """Block-scaled product x @ w^T in fp32: per 128-wide K block, partial products are scaled by
     act_scale[t, kb] * weight_scale[n // 128, kb] (the math of the reference's Triton fp8 GEMM,
@@ -73,26 +106,38 @@ class _FP8LinearFn(torch.autograd.Function):
     (quantised activations are not precise enough to be re-used for wgrad at 1x128 granularity along tokens)."""
 
     @staticmethod
-    def forward(ctx, x, weight, wq, ws, ue8m0):
+    def forward(ctx, x, weight, wq, ws, wq_t, ws_t, ue8m0):
         x2 = x.reshape(-1, x.shape[-1])
-        xq, xs = quant_act_1x128(x2, ue8m0)
-        y = fp8_gemm_reference(xq, xs, wq, ws).to(x.dtype)
-        ctx.save_for_backward(x2, weight, wq, ws)
+        ctx.kernels = _use_kernels(x2) and wq_t is not None
+        if ctx.kernels:
+            xq, xs_t = quant_act_kernel(x2, ue8m0)
+            y = fp8_gemm(xq, xs_t, wq, ws)
+        else:
+            xq, xs = quant_act_1x128(x2, ue8m0)
+            y = fp8_gemm_reference(xq, xs, wq, ws).to(x.dtype)
+        ctx.save_for_backward(x2, weight, wq, ws, wq_t if wq_t is not None else wq, ws_t if ws_t is not None else ws)
         ctx.ue8m0, ctx.shape = ue8m0, x.shape
         return y.view(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
-        x2, weight, wq, ws = ctx.saved_tensors
+        x2, weight, wq, ws, wq_t, ws_t = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
+        if ctx.kernels:
+            from ..ops import functional as F
+
+            dq, ds_t = quant_act_kernel(dy2, ctx.ue8m0)
+            dx = fp8_gemm(dq, ds_t, wq_t, ws_t).view(ctx.shape)       # dy @ W with the transposed fp8 weight copy
+            dw = F._weight_grad(dy2.contiguous(), x2, weight)         # bf16 tcgen05 wgrad (into main_grad when present)
+            return dx, dw, None, None, None, None, None
         dq, ds = quant_act_1x128(dy2, ctx.ue8m0)
         dx = (dequant_act(dq, ds) @ dequant_weight(wq, ws)).to(dy.dtype).view(ctx.shape)
         mg = getattr(weight, "main_grad", None)
         dw = dy2.float().t() @ x2.float()
         if mg is not None:
             mg.add_(dw)
-            return dx, None, None, None, None
-        return dx, dw.to(weight.dtype), None, None, None
+            return dx, None, None, None, None, None, None
+        return dx, dw.to(weight.dtype), None, None, None, None, None
 
 
 class FP8Linear(nn.Module):
@@ -104,17 +149,24 @@ class FP8Linear(nn.Module):
         self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=dtype, device=device))
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
         self.ue8m0 = ue8m0
-        self._wq = self._ws = None
+        self._wq = self._ws = self._wq_t = self._ws_t = None
         nn.init.normal_(self.weight, std=0.02)
 
     def refresh_fp8_weight_cache(self):
+        """Quantise the bf16 master weight (and, on the GPU, its transpose for the input-gradient product)."""
         with torch.no_grad():
-            self._wq, self._ws = quant_weight_128x128(self.weight.detach(), self.ue8m0)
+            w = self.weight.detach()
+            if _use_kernels(w) and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0:
+                self._wq, self._ws = quant_weight_kernel(w, self.ue8m0)
+                self._wq_t, self._ws_t = quant_weight_kernel(w.t().contiguous(), self.ue8m0)
+            else:
+                self._wq, self._ws = quant_weight_128x128(w, self.ue8m0)
+                self._wq_t = self._ws_t = None
 
     def forward(self, x):
         if self._wq is None or self._wq.device != self.weight.device:
             self.refresh_fp8_weight_cache()
-        y = _FP8LinearFn.apply(x, self.weight, self._wq, self._ws, self.ue8m0)
+        y = _FP8LinearFn.apply(x, self.weight, self._wq, self._ws, self._wq_t, self._ws_t, self.ue8m0)
         return y + self.bias if self.bias is not None else y
 
 

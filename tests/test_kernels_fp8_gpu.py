@@ -1,0 +1,81 @@
+"""Block-scaled fp8 kernels (quantisation, tcgen05 e4m3 GEMM, grouped variant, FP8Linear) against fp32 PyTorch math."""
+import pytest
+import torch
+
+from paddleformers_b200.quantization import fp8 as Q
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("ue8m0", [True, False])
+def test_quant_kernels_match_reference(ue8m0):
+    torch.manual_seed(0)
+    x = (torch.randn(300, 512, device="cuda") * torch.rand(300, 1, device="cuda") * 4).to(torch.bfloat16)
+    x[5] = 0                                                       # an all-zero block
+    q, s_t = Q.quant_act_kernel(x, ue8m0)
+    q_ref, s_ref = Q.quant_act_1x128(x, ue8m0)
+    assert q.shape == (300, 512) and s_t.shape == (4, 300)
+    torch.testing.assert_close(s_t.t(), s_ref, rtol=1e-6, atol=0)
+    assert (q.view(torch.uint8) != q_ref.view(torch.uint8)).float().mean().item() < 1e-3   # division rounding at ties only
+    torch.testing.assert_close(Q.dequant_act(q, s_t.t()), Q.dequant_act(q_ref, s_ref), rtol=0.13, atol=1e-6)   # where they differ it is by one e4m3 step
+
+    w = (torch.randn(200, 384, device="cuda") * 0.05).to(torch.bfloat16)     # 200 rows: a ragged last block
+    wq, ws = Q.quant_weight_kernel(w, ue8m0)
+    wq_ref, ws_ref = Q.quant_weight_128x128(w, ue8m0)
+    assert ws.shape == (2, 3)
+    torch.testing.assert_close(ws, ws_ref, rtol=1e-6, atol=0)
+    assert (wq.view(torch.uint8) != wq_ref.view(torch.uint8)).float().mean().item() < 1e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 384, 512), (128, 128, 128), (1024, 1536, 7168), (77, 200, 256)])
+def test_fp8_gemm_matches_reference(M, N, K):
+    torch.manual_seed(1)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    xq, xs_t = Q.quant_act_kernel(x)
+    wq, ws = Q.quant_weight_kernel(w)
+    out = Q.fp8_gemm(xq, xs_t, wq, ws)
+    ref = Q.fp8_gemm_reference(xq, xs_t.t(), wq, ws)
+    assert _rel(out, ref) < 6e-3                                   # bf16 rounding of the output
+    assert _rel(out, x.float() @ w.float().t()) < 6e-2             # and the quantisation error itself stays small
+    from paddleformers_b200.ops import functional as F
+
+    F.check_kernel_status()
+
+
+def test_fp8_grouped_gemm():
+    torch.manual_seed(2)
+    E, N, K = 4, 256, 512
+    block_expert = torch.tensor([2, 0, -1, 3, 3, 1], dtype=torch.int32, device="cuda")
+    M = block_expert.numel() * 128
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(E * N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    xq, xs_t = Q.quant_act_kernel(x)
+    wq, ws = Q.quant_weight_kernel(w)
+    out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    Q.fp8_gemm(xq, xs_t, wq, ws, block_expert=block_expert, n_per_expert=N, out=out)
+    xd = Q.dequant_act(xq, xs_t.t())
+    wd = Q.dequant_weight(wq, ws)
+    for b, e in enumerate(block_expert.tolist()):
+        rows = slice(b * 128, (b + 1) * 128)
+        if e < 0:
+            assert out[rows].abs().max().item() == 0
+        else:
+            assert _rel(out[rows], xd[rows] @ wd[e * N:(e + 1) * N].t()) < 6e-3
+
+
+def test_fp8_linear_forward_backward():
+    torch.manual_seed(3)
+    lin = Q.FP8Linear(512, 384, dtype=torch.bfloat16, device="cuda")
+    x = torch.randn(4, 64, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = lin(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    w = lin.weight.detach().float()
+    assert _rel(y, x.detach().float() @ w.t()) < 6e-2
+    assert _rel(x.grad, g.float() @ w) < 6e-2
+    assert _rel(lin.weight.grad, g.float().reshape(-1, 384).t() @ x.detach().float().reshape(-1, 512)) < 2e-2
