@@ -9,7 +9,8 @@
 //
 // Structure: the persistent TMA / MMA / epilogue split of the bf16 kernel with 128 x 128 x 128 tiles. Each K block is
 // multiplied into a FRESH TMEM accumulator (four 128-column buffers rotate), committed to the epilogue warps, and
-// those read it back with tcgen05.ld, multiply by the block's scale product and add into fp32 registers: the
+// (eight of them: two per TMEM lane quadrant, 64 columns each) read it back with tcgen05.ld, multiply by the block's
+// scale product and add into fp32 registers: the
 // promotion that a 1x128 / 128x128 scaled format needs, with the tensor core never waiting for it as long as the
 // epilogue keeps up (four buffers of slack).
 //
@@ -26,7 +27,8 @@ namespace pfb {
 constexpr int F8_BM = 128, F8_BN = 128, F8_BK = 128;   // 128 e4m3 = one 128-byte swizzle row
 constexpr int F8_UMMA_K = 32;
 constexpr int F8_ACC_BUFS = 4;
-constexpr int F8_THREADS = 192;
+constexpr int F8_EPI_WARPS = 8;            // two warps per TMEM lane quadrant, 64 accumulator columns each
+constexpr int F8_THREADS = 64 + 32 * F8_EPI_WARPS;
 
 struct Fp8GemmParams {
   int M, N, K;
@@ -70,7 +72,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < F8_ACC_BUFS; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4); }
+    for (int a = 0; a < F8_ACC_BUFS; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], F8_EPI_WARPS); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -145,7 +147,9 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
       }
     }
   } else {
-    const int quad = warp & 3;
+    const int quad = warp & 3;                 // TMEM lanes this warp may read
+    const int half = (warp - 2) >> 2;          // which 64 of the tile's 128 columns it accumulates
+    constexpr int COLS = F8_BN / 2;
     int buf = 0; uint32_t buf_phase = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
@@ -160,9 +164,9 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
       const int row_c = min(row, p.M - 1);
       const float* sa_col = p.sa_t + row_c;
       const float* sb_rowp = p.sb + static_cast<long long>(sb_row) * p.k_blocks;
-      float acc[F8_BN];
+      float acc[COLS];
       #pragma unroll
-      for (int j = 0; j < F8_BN; ++j) acc[j] = 0.f;
+      for (int j = 0; j < COLS; ++j) acc[j] = 0.f;
       float s_ring[4];
       #pragma unroll
       for (int u = 0; u < 4; ++u)
@@ -177,18 +181,19 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             s_ring[u] = sa_col[static_cast<long long>(kb + 4) * p.sa_ld] * sb_rowp[kb + 4];
           if (!mbar_wait(&tfull_bar[buf], buf_phase, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * F8_BN;
-          #pragma unroll
-          for (int c = 0; c < F8_BN / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32(taddr + c * 32, v);
-            tmem_ld_wait();
-            #pragma unroll
-            for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(s, __uint_as_float(v[j]), acc[c * 32 + j]);
-          }
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * F8_BN + half * COLS;
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32(taddr, v0);
+          tmem_ld_32x32(taddr + 32, v1);
+          tmem_ld_wait();
+          // the partial sums are in registers: hand the buffer back before the arithmetic
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+          #pragma unroll
+          for (int j = 0; j < 32; ++j) acc[j] = fmaf(s, __uint_as_float(v0[j]), acc[j]);
+          #pragma unroll
+          for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(s, __uint_as_float(v1[j]), acc[32 + j]);
           if (++buf == F8_ACC_BUFS) { buf = 0; buf_phase ^= 1; }
         }
       }
@@ -196,8 +201,8 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
       if (row < p.M) {
         __nv_bfloat16* drow = p.D + static_cast<long long>(row) * p.ldd;
         #pragma unroll
-        for (int c = 0; c < F8_BN / 32; ++c) {
-          const int col = nb * F8_BN + c * 32;
+        for (int c = 0; c < COLS / 32; ++c) {
+          const int col = nb * F8_BN + half * COLS + c * 32;
           if (col + 32 <= p.N) {
             #pragma unroll
             for (int j = 0; j < 4; ++j)
