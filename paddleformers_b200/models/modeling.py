@@ -42,6 +42,9 @@ class BatchContext:
     kend: Optional[torch.Tensor]        # [B, S] int32 document mask bounds (None = plain causal)
     cos: torch.Tensor
     sin: torch.Tensor
+    cp_positions: Optional[torch.Tensor] = None   # context parallel: global positions of the local tokens
+    S_full: int = 0                               # context / segment parallel: length of the whole sequence
+    kend_full: Optional[torch.Tensor] = None      # [B, S_full] document bounds of all keys (cp / sep)
 
 
 @dataclass
@@ -85,6 +88,37 @@ def _apply(mod, x):
     return mod(x)
 
 
+def long_sequence_attention(q, k, v, ctx: "BatchContext", scale: float, config) -> Optional[torch.Tensor]:
+    """Attention when the sequence is split over ranks. q, k, v: [B, S_local, H, D].
+
+    * context parallel (``cp`` axis): keys / values are all-gathered over the group and the local queries attend by
+      global position (``context_parallel_algo = "ring"`` selects the K/V ring instead, plain causal masks only);
+    * Ulysses (``sep`` axis): all-to-all to [B, S, H / sep, D], ordinary attention on whole sequences, all-to-all back
+      (paddleformers/transformers/segment_parallel_utils.py:69-137).
+
+    Returns None when neither axis is active."""
+    ps = get_parallel_state()
+    if ps.degrees.cp > 1 and ctx.cp_positions is not None:
+        from ..parallel.context_parallel import cp_attention, ring_attention
+
+        mode = getattr(config, "cp_balance_mode", None) or "dualchunk_allgather"
+        if getattr(config, "context_parallel_algo", "allgather") == "ring" and ctx.kend_full is None:
+            return ring_attention(q, k, v, ps.group("cp"), ctx.S_full, mode, scale)
+        return cp_attention(q, k, v, ctx.cp_positions, ctx.S_full, mode, ps.group("cp"), scale, ctx.kend_full)
+    if ps.degrees.sep > 1:
+        from ..parallel.context_parallel import ReshardLayer
+
+        n, g = ps.degrees.sep, ps.group("sep")
+        assert q.shape[2] % n == 0, "segment parallel needs the query heads (per tensor-parallel rank) to divide sep"
+        if k.shape[2] % n != 0:     # fewer key/value heads than ranks: replicate them so that every rank owns one
+            rep = n // math.gcd(n, k.shape[2])
+            k, v = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
+        qh, kh, vh = (ReshardLayer.apply(t.contiguous(), g, True) for t in (q, k, v))
+        out = F.flash_attention(qh, kh, vh, True, ctx.kend_full if ctx.kend_full is not None else None, scale)
+        return ReshardLayer.apply(out.contiguous(), g, False)
+    return None
+
+
 class Attention(nn.Module):
     """GQA attention with a fused qkv projection laid out as [q heads | k heads | v heads]."""
 
@@ -116,6 +150,12 @@ class Attention(nn.Module):
             qkv = F.rope_packed(qkv, ctx.cos, ctx.sin, ctx.positions, self.Hq, self.Hkv, self.D, self.rot)
         if cache is not None:
             out = cache.attend(self, qkv, ctx)
+        elif ctx.S_full:
+            B, S, D = ctx.B, ctx.S, self.D
+            q, k, v = qkv.view(B, S, -1).split([self.Hq * D, self.Hkv * D, self.Hkv * D], dim=-1)
+            out = long_sequence_attention(q.reshape(B, S, self.Hq, D), k.reshape(B, S, self.Hkv, D),
+                                          v.reshape(B, S, self.Hkv, D), ctx, self.scale, self.config)
+            out = out.reshape(B * S, self.Hq * D)
         else:
             out = F.flash_attention_qkvpacked(qkv, ctx.B, ctx.S, self.Hq, self.Hkv, self.D, True, ctx.kend, self.scale)
         return _apply(self.o_proj, out)
@@ -175,8 +215,12 @@ class MLAAttention(nn.Module):
         qf = torch.cat([q[..., : self.nope], q_pe], dim=-1)
         kf = torch.cat([kv[..., : self.nope], k_pe.expand(T, self.Hq, self.rope)], dim=-1)
         v = kv[..., self.nope:]
-        out = F.flash_attention(qf.view(ctx.B, ctx.S, self.Hq, self.qd), kf.view(ctx.B, ctx.S, self.Hq, self.qd),
-                                v.reshape(ctx.B, ctx.S, self.Hq, self.vd), True, ctx.kend, self.scale)
+        q4, k4 = qf.view(ctx.B, ctx.S, self.Hq, self.qd), kf.view(ctx.B, ctx.S, self.Hq, self.qd)
+        v4 = v.reshape(ctx.B, ctx.S, self.Hq, self.vd)
+        if ctx.S_full and cache is None:
+            out = long_sequence_attention(q4, k4, v4, ctx, self.scale, self.config)
+        else:
+            out = F.flash_attention(q4, k4, v4, True, ctx.kend, self.scale)
         return _apply(self.o_proj, out.reshape(T, self.Hq * self.vd))
 
 
@@ -257,7 +301,8 @@ class DecoderModel(nn.Module):
             self._rope_cache[key] = cached
         return cached
 
-    def make_context(self, input_ids, position_ids=None, kend=None) -> BatchContext:
+    def make_context(self, input_ids, position_ids=None, kend=None, cp_positions=None, full_seq_len=None,
+                     kend_full=None) -> BatchContext:
         B, S = input_ids.shape
         max_pos = S if position_ids is None else max(S, int(self.config.max_position_embeddings))
         cos, sin = self.rope(input_ids.device, max_pos)
@@ -266,7 +311,15 @@ class DecoderModel(nn.Module):
             pos = position_ids.reshape(-1)
         elif B > 1:
             pos = torch.arange(S, device=input_ids.device).repeat(B)
-        return BatchContext(B, S, pos, kend, cos, sin)
+        ps = get_parallel_state()
+        S_full = 0
+        if ps.degrees.cp > 1 and cp_positions is not None:
+            S_full = int(full_seq_len or S * ps.degrees.cp)
+        elif ps.degrees.sep > 1:
+            S_full = int(full_seq_len or S * ps.degrees.sep)
+        if S_full:
+            cos, sin = self.rope(input_ids.device, max(max_pos, S_full))
+        return BatchContext(B, S, pos, kend, cos, sin, cp_positions if S_full else None, S_full, kend_full if S_full else None)
 
     def embed(self, input_ids):
         if isinstance(self.embed_tokens, VocabParallelEmbedding):
@@ -289,8 +342,9 @@ class DecoderModel(nn.Module):
                 hidden, residual = layer(hidden, residual, ctx, cache)
         return hidden, residual
 
-    def forward(self, input_ids, position_ids=None, kend=None, caches=None, ctx: Optional[BatchContext] = None):
-        ctx = ctx or self.make_context(input_ids, position_ids, kend)
+    def forward(self, input_ids, position_ids=None, kend=None, caches=None, ctx: Optional[BatchContext] = None,
+                cp_positions=None, full_seq_len=None, kend_full=None):
+        ctx = ctx or self.make_context(input_ids, position_ids, kend, cp_positions, full_seq_len, kend_full)
         h = self.embed(input_ids)
         hidden, residual = self.run_layers(h, None, ctx, caches)
         if self.norm is not None:
@@ -367,12 +421,16 @@ class DecoderForCausalLM(PretrainedModel):
                                             chunk if chunk > 0 else 2048, scale)
 
     def forward(self, input_ids, labels=None, position_ids=None, attn_mask_startend_row_indices=None, kend=None,
-                caches=None, return_logits: Optional[bool] = None, **unused):
+                caches=None, return_logits: Optional[bool] = None, cp_global_positions=None, cp_full_seq_len=None,
+                full_attn_mask_startend_row_indices=None, **unused):
         """``labels`` are next-token targets aligned with ``input_ids`` (already shifted by the data pipeline, as in
         the reference's collators). ``attn_mask_startend_row_indices`` / ``kend``: int [B, S] FlashMask start rows."""
         if kend is None and attn_mask_startend_row_indices is not None:
             kend = attn_mask_startend_row_indices.reshape(input_ids.shape[0], -1)
-        hidden, ctx = self.model(input_ids, position_ids, kend, caches)
+        kend_full = full_attn_mask_startend_row_indices
+        if kend_full is not None:
+            kend_full = kend_full.reshape(input_ids.shape[0], -1)
+        hidden, ctx = self.model(input_ids, position_ids, kend, caches, None, cp_global_positions, cp_full_seq_len, kend_full)
         out = CausalLMOutput()
         want_logits = return_logits if return_logits is not None else labels is None
         if want_logits:

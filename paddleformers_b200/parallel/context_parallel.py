@@ -50,6 +50,8 @@ def get_batch_on_this_cp_rank(batch: Dict[str, torch.Tensor], ps: Optional[Paral
     S = batch["input_ids"].shape[1]
     assert S % (2 * cp) == 0, f"sequence length {S} must be a multiple of 2*cp = {2 * cp}"
     idx = cp_positions(S, cp, rank, mode, batch["input_ids"].device)
+    if batch.get("attn_mask_startend_row_indices") is not None:     # every rank needs the bounds of ALL key columns
+        out["full_attn_mask_startend_row_indices"] = batch["attn_mask_startend_row_indices"]
     for k in _SEQ_KEYS:
         if k in batch and isinstance(batch[k], torch.Tensor) and batch[k].dim() >= 2 and batch[k].shape[1] == S:
             out[k] = batch[k].index_select(1, idx)
@@ -70,6 +72,9 @@ def split_inputs_sequence_dim(batch: Dict[str, torch.Tensor], ps: Optional[Paral
     S = batch["input_ids"].shape[1]
     assert S % n == 0
     per = S // n
+    if batch.get("attn_mask_startend_row_indices") is not None:
+        out["full_attn_mask_startend_row_indices"] = batch["attn_mask_startend_row_indices"]
+    out["cp_full_seq_len"] = S
     for k in _SEQ_KEYS:
         if k in batch and isinstance(batch[k], torch.Tensor) and batch[k].dim() >= 2 and batch[k].shape[1] == S:
             out[k] = batch[k][:, r * per:(r + 1) * per].contiguous()

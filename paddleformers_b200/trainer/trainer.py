@@ -380,10 +380,12 @@ class Trainer:
         if self.control.should_log:
             steps = max(self.state.global_step - self._last_log_step, 1)
             loss = self._tr_loss / steps
-            if dist.is_initialized() and self.ps.dataset_world_size > 1:
+            # ranks that saw different samples, or different slices of one sequence (cp / sep), each hold a partial mean
+            n_parts = self.ps.size("dp_sharding_cp")
+            if dist.is_initialized() and n_parts > 1:
                 loss = loss.clone()
-                dist.all_reduce(loss, group=self.ps.group("data") if self.ps.size("data") > 1 else None)
-                loss = loss / self.ps.size("data")
+                dist.all_reduce(loss, group=self.ps.group("dp_sharding_cp"))
+                loss = loss / n_parts
             loss_v = float(loss)   # the only host sync of the training loop, on logging steps
             if not math.isfinite(loss_v):
                 raise FloatingPointError(f"LOSS_{'NAN' if math.isnan(loss_v) else 'INF'}_ERROR: loss is {loss_v} at "

@@ -39,6 +39,7 @@ class LlmMetaConfig:
         ("expert_model_parallel_size", int, 1, "expert parallel degree"),
         ("context_parallel_size", int, 1, "context parallel degree"),
         ("cp_balance_mode", str, "dualchunk_allgather", "dualchunk_allgather (zig-zag) or contiguous_allgather"),
+        ("context_parallel_algo", str, "allgather", "allgather (gather K/V over the cp group) | ring (K/V ring with log-sum-exp merging)"),
         ("sep_parallel_size", int, 1, "Ulysses (segment) parallel degree"),
         ("sequence_parallel", bool, False, "Megatron sequence parallel inside the tensor parallel group"),
         ("fuse_sequence_parallel_allreduce", bool, False, "fuse SP parameter gradient all-reduces"),

@@ -79,6 +79,10 @@ def _reference(moe, steps, accum):
     ("sharding2", 2, False, dict(sharding="stage1", gradient_accumulation_steps=1)),
     ("dp2", 2, False, dict(gradient_accumulation_steps=1)),
     ("ep2", 2, True, dict(expert_model_parallel_size=2, sharding="stage1", gradient_accumulation_steps=1, moe_token_dispatcher_type="alltoall")),
+    ("cp2", 2, False, dict(context_parallel_size=2, gradient_accumulation_steps=2)),
+    ("cp2_contiguous", 2, False, dict(context_parallel_size=2, cp_balance_mode="contiguous_allgather", gradient_accumulation_steps=2)),
+    ("cp2_ring", 2, False, dict(context_parallel_size=2, context_parallel_algo="ring", gradient_accumulation_steps=2)),
+    ("sep2", 2, False, dict(sep_parallel_size=2, gradient_accumulation_steps=2)),
 ])
 def test_parallel_matches_single_process(name, world, moe, targs):
     steps = 3
