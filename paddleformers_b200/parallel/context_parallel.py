@@ -105,10 +105,13 @@ class _AllGatherSeq(torch.autograd.Function):
         return out, None
 
 
-def cp_attention(q, k, v, q_positions: torch.Tensor, S_full: int, mode: str, group, scale=None, kend_full=None):
+def cp_attention(q, k, v, q_positions: torch.Tensor, S_full: int, mode: str, group, scale=None, kend_full=None,
+                 block: int = 4096):
     """q, k, v: [B, S_local, H, D] of this cp rank; ``q_positions``: global positions of the local tokens.
     Keys / values of all ranks are gathered and re-ordered to global order; the local queries attend causally by
-    global position."""
+    global position (and inside ``kend_full[b, j]`` document bounds when given). The keys are visited in blocks with
+    log-sum-exp merging, so the score matrix never exceeds [S_local, block] per head, and blocks that lie entirely in
+    the future of every local query are skipped."""
     cp = group.size()
     kg = _AllGatherSeq.apply(k, group)
     vg = _AllGatherSeq.apply(v, group)
@@ -117,22 +120,28 @@ def cp_attention(q, k, v, q_positions: torch.Tensor, S_full: int, mode: str, gro
     pos_all = torch.cat([cp_positions(S_full, cp, r, mode, dev) for r in range(cp)])
     order = torch.argsort(pos_all)
     kg, vg = kg.index_select(1, order), vg.index_select(1, order)
-    B, Sl, Hq, D = q.shape
-    Hkv = kg.shape[2]
-    scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    qf = q.permute(0, 2, 1, 3).float()
-    kf = kg.permute(0, 2, 1, 3).float().repeat_interleave(Hq // Hkv, dim=1)
-    vf = vg.permute(0, 2, 1, 3).float().repeat_interleave(Hq // Hkv, dim=1)
-    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
-    j = torch.arange(S_full, device=dev)[None, :]
-    vis = j <= q_positions[:, None]
-    if kend_full is not None:
-        vis = vis[None] & (q_positions[None, :, None] < kend_full[:, None, :])
-        s = s.masked_fill(~vis[:, None], float("-inf"))
-    else:
-        s = s.masked_fill(~vis[None, None], float("-inf"))
-    p = torch.softmax(s, dim=-1)
-    return torch.matmul(p, vf).permute(0, 2, 1, 3).to(q.dtype)
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    out = torch.zeros(q.shape[:3] + (v.shape[-1],), dtype=torch.float32, device=dev)
+    lse = torch.full(q.shape[:3], -1e30, dtype=torch.float32, device=dev)
+    # the local positions are known on the host from (S_full, cp, rank, mode): no device read is needed for the skip
+    q_max = int(max(_host_positions(S_full, cp, dist.get_rank(group), mode)))
+    for j0 in range(0, S_full, block):
+        if j0 > q_max:
+            break
+        j1 = min(j0 + block, S_full)
+        k_pos = torch.arange(j0, j1, device=dev)
+        kend_blk = kend_full[:, j0:j1] if kend_full is not None else None
+        blk_out, blk_lse = _block_attention(q, kg[:, j0:j1], vg[:, j0:j1], q_positions, k_pos, scale, kend_blk)
+        out, lse = _merge(out, lse, blk_out, blk_lse)
+    return out.to(q.dtype)
+
+
+def _host_positions(S: int, cp: int, rank: int, mode: str):
+    if mode == "contiguous_allgather":
+        per = S // cp
+        return range(rank * per, (rank + 1) * per)
+    c = S // (2 * cp)
+    return list(range(rank * c, (rank + 1) * c)) + list(range((2 * cp - 1 - rank) * c, (2 * cp - rank) * c))
 
 
 def _merge(out, lse, blk_out, blk_lse):
@@ -143,8 +152,9 @@ def _merge(out, lse, blk_out, blk_lse):
     return out * w_old + blk_out * w_new, new_lse
 
 
-def _block_attention(q, k, v, q_pos, k_pos, scale):
-    """Returns (out [B,Sq,H,D] fp32, lse [B,Sq,H]) of q against one K/V block with causal masking by position."""
+def _block_attention(q, k, v, q_pos, k_pos, scale, kend=None):
+    """Returns (out [B,Sq,H,D] fp32, lse [B,Sq,H]) of q against one K/V block with causal masking by position
+    (``kend``: [B, Sk] document bounds of the block's keys: key j is visible to query positions < kend[b, j])."""
     B, Sq, Hq, D = q.shape
     Hkv = k.shape[2]
     qf = q.permute(0, 2, 1, 3).float()
@@ -152,7 +162,11 @@ def _block_attention(q, k, v, q_pos, k_pos, scale):
     vf = v.permute(0, 2, 1, 3).float().repeat_interleave(Hq // Hkv, dim=1)
     s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
     vis = k_pos[None, :] <= q_pos[:, None]
-    s = s.masked_fill(~vis[None, None], float("-inf"))
+    if kend is not None:
+        vis = vis[None] & (q_pos[None, :, None] < kend[:, None, :])
+        s = s.masked_fill(~vis[:, None], float("-inf"))
+    else:
+        s = s.masked_fill(~vis[None, None], float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
     p = torch.exp(s - lse.unsqueeze(-1)).nan_to_num(0.0)
     lse = torch.where(torch.isinf(lse), torch.full_like(lse, -1e30), lse)
