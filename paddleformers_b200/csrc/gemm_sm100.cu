@@ -108,7 +108,9 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, 
       long long tiles = static_cast<long long>((M + GEMM_BM - 1) / GEMM_BM) * nn;
       return ((tiles + sms - 1) / sms) * bn;
     };
-    BN = cost(128) < cost(256) ? 128 : 256;
+    // a 256-wide tile moves 1.33x fewer operand bytes per FLOP and measured 1.4-1.5x the rate of a 128-wide one on
+    // every model shape, so the narrow tile is chosen only when it saves more than that in wave quantisation
+    BN = cost(128) * 3 < cost(256) * 2 ? 128 : 256;
   }
 
   GemmParams p;
