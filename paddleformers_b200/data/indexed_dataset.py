@@ -97,9 +97,53 @@ class MMapIndexedDataset(Dataset):
         return self.get(i)
 
 
-def build_sample_index(sizes: np.ndarray, doc_order: np.ndarray, seq_length: int, num_samples: int) -> np.ndarray:
+_HOST = None
+
+
+def _host():
+    """The compiled index helpers (``csrc_host/data_index.cpp``), built on first use; None if no compiler is there."""
+    global _HOST
+    if _HOST is None:
+        import ctypes
+
+        from ..ops import _build
+
+        try:
+            _build.build_host_library()
+            lib = _build.load_host_library()
+            i64p, i32p, f64p = (ctypes.POINTER(t) for t in (ctypes.c_int64, ctypes.c_int32, ctypes.c_double))
+            lib.pfb_build_sample_index.restype = ctypes.c_int64
+            lib.pfb_build_sample_index.argtypes = [i32p, i64p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, i64p]
+            lib.pfb_build_blend_index.restype = None
+            lib.pfb_build_blend_index.argtypes = [f64p, ctypes.c_int32, ctypes.c_int64, i32p, i64p]
+            lib.pfb_build_doc_bounds.restype = None
+            lib.pfb_build_doc_bounds.argtypes = [i64p, ctypes.c_int64, ctypes.c_int64, i32p, i64p]
+            _HOST = lib
+        except Exception:  # noqa: BLE001 - no compiler / read-only tree: the numpy paths below are equivalent
+            _HOST = False
+    return _HOST or None
+
+
+def _ptr(a: np.ndarray, ctype):
+    import ctypes
+
+    return a.ctypes.data_as(ctypes.POINTER(ctype))
+
+
+def build_sample_index(sizes: np.ndarray, doc_order: np.ndarray, seq_length: int, num_samples: int,
+                       use_native: bool = True) -> np.ndarray:
     """sample_idx[k] = (position in doc_order, token offset in that document) where sample k starts; sample k covers
     seq_length + 1 tokens (inputs + shifted labels) and may span documents."""
+    lib = _host() if use_native else None
+    if lib is not None and len(doc_order) > 0:
+        import ctypes
+
+        sz = np.ascontiguousarray(sizes, dtype=np.int32)
+        order = np.ascontiguousarray(doc_order, dtype=np.int64)
+        out = np.zeros((num_samples + 1, 2), dtype=np.int64)
+        n = lib.pfb_build_sample_index(_ptr(sz, ctypes.c_int32), _ptr(order, ctypes.c_int64), len(order), seq_length,
+                                       num_samples, _ptr(out, ctypes.c_int64))
+        return out[:n + 1]
     lens = sizes[doc_order].astype(np.int64)
     cum = np.concatenate([[0], np.cumsum(lens)])
     total = cum[-1]
@@ -167,6 +211,17 @@ class GPTDataset(Dataset):
             # document-causal packing: a document ends after every eos token
             ids = toks[:-1]
             S = len(ids)
+            lib = _host()
+            if lib is not None:
+                import ctypes
+
+                ids_c = np.ascontiguousarray(ids, dtype=np.int64)
+                kend, pos = np.empty(S, dtype=np.int32), np.empty(S, dtype=np.int64)
+                lib.pfb_build_doc_bounds(_ptr(ids_c, ctypes.c_int64), S, int(self.eos), _ptr(kend, ctypes.c_int32),
+                                         _ptr(pos, ctypes.c_int64))
+                item["attn_mask_startend_row_indices"] = torch.from_numpy(kend)
+                item["position_ids"] = torch.from_numpy(pos)
+                return item
             ends = np.nonzero(ids == self.eos)[0] + 1
             bounds = np.concatenate([ends[ends < S], [S]])
             kend = np.empty(S, dtype=np.int32)
@@ -185,12 +240,19 @@ class BlendableDataset(Dataset):
     """Weighted mixture of datasets with a deterministic interleaving that keeps each dataset's share close to its
     weight at every prefix (greedy largest-deficit rule)."""
 
-    def __init__(self, datasets: Sequence[Dataset], weights: Sequence[float], size: int):
+    def __init__(self, datasets: Sequence[Dataset], weights: Sequence[float], size: int, use_native: bool = True):
         w = np.asarray(weights, dtype=np.float64)
-        w = w / w.sum()
+        w = np.ascontiguousarray(w / w.sum())
         self.datasets = list(datasets)
         self.dataset_index = np.zeros(size, dtype=np.int32)
         self.sample_index = np.zeros(size, dtype=np.int64)
+        lib = _host() if use_native else None
+        if lib is not None:
+            import ctypes
+
+            lib.pfb_build_blend_index(_ptr(w, ctypes.c_double), len(w), size, _ptr(self.dataset_index, ctypes.c_int32),
+                                      _ptr(self.sample_index, ctypes.c_int64))
+            return
         counts = np.zeros(len(w), dtype=np.int64)
         for i in range(size):
             deficit = w * (i + 1) - counts

@@ -65,6 +65,31 @@ def build_extension(verbose: bool = False) -> str:
     return ext_path()
 
 
+HOST_SRC_DIR = os.path.join(_PKG_DIR, "csrc_host")
+HOST_LIB = os.path.join(EXT_DIR, "pfb_host.so")
+
+
+def build_host_library() -> str:
+    """Compile the host-only C++ helpers (dataset index builders) into ``_ext/pfb_host.so`` with g++."""
+    import subprocess
+
+    os.makedirs(EXT_DIR, exist_ok=True)
+    srcs = sorted(os.path.join(HOST_SRC_DIR, f) for f in os.listdir(HOST_SRC_DIR) if f.endswith(".cpp"))
+    newest = max(os.path.getmtime(f) for f in srcs)
+    if not os.path.exists(HOST_LIB) or os.path.getmtime(HOST_LIB) < newest:
+        subprocess.run(["g++", "-O3", "-std=c++17", "-shared", "-fPIC", "-o", HOST_LIB] + srcs, check=True)
+    return HOST_LIB
+
+
+def load_host_library():
+    """ctypes handle of the host helpers, or None when the library has not been built."""
+    import ctypes
+
+    if not os.path.exists(HOST_LIB):
+        return None
+    return ctypes.CDLL(HOST_LIB)
+
+
 def load_extension(required: bool = False) -> bool:
     """Load the prebuilt extension if it exists. Returns True when ``torch.ops.pfb200`` is usable."""
     global _loaded
@@ -91,4 +116,5 @@ def is_loaded() -> bool:
 
 
 if __name__ == "__main__":
+    print(build_host_library())
     print(build_extension(verbose=True))

@@ -3,6 +3,7 @@ import json
 import os
 
 import numpy as np
+import pytest
 import torch
 
 from paddleformers_b200.datasets.collate import (calc_padding_size, collate_fn, dpo_collate_fn,
@@ -119,3 +120,33 @@ def test_mmap_dataset_and_gpt_samples(tmp_path):
     assert (blend.dataset_index == 0).sum() == 12
     tr, va, te = build_train_valid_test_datasets([prefix], "8,2,2", 16, [4, 1, 1], seed=3)
     assert tr is not None and len(tr) >= 4 and va is not None
+
+
+def test_native_index_helpers_match_numpy():
+    """The compiled index builders and the numpy fallbacks produce identical indices."""
+    import numpy as np
+
+    from paddleformers_b200.data import indexed_dataset as idx
+
+    if idx._host() is None:
+        pytest.skip("no C++ compiler available")
+    rng = np.random.RandomState(0)
+    sizes = rng.randint(1, 50, size=200).astype(np.int32)
+    order = rng.permutation(np.tile(np.arange(200), 3)).astype(np.int64)
+    for seq, ns in ((16, 10), (7, 10_000), (128, 50)):
+        a = idx.build_sample_index(sizes, order, seq, ns, use_native=True)
+        b = idx.build_sample_index(sizes, order, seq, ns, use_native=False)
+        assert a.shape == b.shape and (a == b).all()
+    ds = [list(range(10)), list(range(20)), list(range(5))]
+    x = idx.BlendableDataset(ds, [0.5, 0.3, 0.2], 1000, use_native=True)
+    y = idx.BlendableDataset(ds, [0.5, 0.3, 0.2], 1000, use_native=False)
+    assert (x.dataset_index == y.dataset_index).all() and (x.sample_index == y.sample_index).all()
+    share = np.bincount(x.dataset_index, minlength=3) / 1000
+    assert np.allclose(share, [0.5, 0.3, 0.2], atol=2e-3)
+    # document bounds of a packed sample: documents end after every eos (token 0 here)
+    import ctypes
+
+    ids = np.array([5, 3, 0, 7, 7, 7, 0, 0, 2, 9], dtype=np.int64)
+    kend, pos = np.empty(10, dtype=np.int32), np.empty(10, dtype=np.int64)
+    idx._host().pfb_build_doc_bounds(idx._ptr(ids, ctypes.c_int64), 10, 0, idx._ptr(kend, ctypes.c_int32), idx._ptr(pos, ctypes.c_int64))
+    assert kend.tolist() == [3, 3, 3, 7, 7, 7, 7, 8, 10, 10] and pos.tolist() == [0, 1, 2, 0, 1, 2, 3, 0, 0, 1]
