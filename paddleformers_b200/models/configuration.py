@@ -168,10 +168,87 @@ class Glm4MoeConfig(DecoderConfig):
         super().__init__(**kw)
 
 
+class MistralConfig(DecoderConfig):
+    """Llama architecture; ``sliding_window`` (when set) must cover the training sequence length, because the attention
+    kernels implement causal and document masks, not a sliding window."""
+
+    model_type = "mistral"
+
+    def __init__(self, sliding_window=None, **kw):
+        super().__init__(**kw)
+        self.sliding_window = sliding_window
+
+
+class Phi3Config(DecoderConfig):
+    """Phi-3 / Phi-4: Llama blocks whose checkpoints already store the fused ``qkv_proj`` and ``gate_up_proj``
+    matrices, which is this implementation's internal layout (paddleformers/transformers/phi3)."""
+
+    model_type = "phi3"
+
+    def __init__(self, sliding_window=None, **kw):
+        kw.setdefault("rms_norm_eps", 1e-5)
+        super().__init__(**kw)
+        self.sliding_window = sliding_window
+        self.hf_fused_qkv = True
+        self.hf_fused_gate_up = True
+
+
+class SeedOssConfig(DecoderConfig):
+    """Seed-OSS: Llama blocks with biases on q/k/v (paddleformers/transformers/seed_oss)."""
+
+    model_type = "seed_oss"
+
+    def __init__(self, **kw):
+        kw.setdefault("attention_bias", True)
+        super().__init__(**kw)
+
+
+class InternLM3Config(DecoderConfig):
+    """InternLM3: Llama blocks; ``qkv_bias`` switches the q/k/v biases (paddleformers/transformers/internlm3)."""
+
+    model_type = "internlm3"
+
+    def __init__(self, qkv_bias=False, **kw):
+        kw.setdefault("attention_bias", bool(qkv_bias))
+        super().__init__(**kw)
+        self.qkv_bias = qkv_bias
+
+
 CONFIG_MAPPING = {c.model_type: c for c in (LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
-                                            Glm4MoeConfig)}
+                                            Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config)}
+
+# Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
+# feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
+UNSUPPORTED_FAMILIES = {
+    "gpt_oss": "attention sinks, clamped SwiGLU with expert biases, mxfp4 expert checkpoints (dequantiser: quantization.checkpoint_dequant)",
+    "deepseek_v32": "sparse (indexer) attention", "deepseek_v4": "compressed sparse attention",
+    "glm_moe_dsa": "sparse (indexer) attention", "kimi_k2": "DeepSeek-V3 blocks with a different tokenizer / config schema",
+    "minimax": "lightning (linear) attention hybrid", "minimax_m2": "per-layer QK norm over the full projection",
+    "qwen3_next": "gated delta-net linear attention hybrid", "qwen3_5": "gated delta-net linear attention hybrid",
+    "qwen3_5_moe": "gated delta-net linear attention hybrid", "qwen2_moe": "sigmoid-gated shared expert",
+    "hunyuan_v1_dense": "QK norm applied after the rotary embedding", "hunyuan_v1_moe": "QK norm after rotary, shared-expert mixing",
+    "gemma3": "(1 + w) RMSNorm, GeGLU, sliding/global layer pattern", "gemma3_text": "(1 + w) RMSNorm, GeGLU, sliding/global layer pattern",
+    "ernie4_5": "interleaved (GPT-J style) rotary embedding layout", "ernie4_5_moe": "interleaved rotary layout, modality-aware experts",
+    "granite": "embedding / residual / attention / logit multipliers", "phi4_multimodal": "vision and audio towers",
+    "olmo2": "post-norm blocks with QK norm over the full projection", "cohere": "LayerNorm, parallel attention + MLP block",
+    "cohere2": "LayerNorm, parallel block, sliding-window layers", "stablelm": "LayerNorm with bias, partial rotary with per-head norm",
+    "internlm2": "interleaved fused wqkv layout", "minicpm": "depth / embedding scaling factors", "minicpm3": "MLA with scaling factors",
+    "llama4_text": "chunked attention, NoPE layers, shared-expert MoE", "diffllama": "differential attention",
+    "qwen2_vl": "vision tower and multimodal rotary embedding", "qwen2_5_vl": "vision tower and multimodal rotary embedding",
+    "qwen3_vl": "vision tower and multimodal rotary embedding", "qwen3_vl_moe": "vision tower and multimodal rotary embedding",
+    "ernie4_5_vl": "vision tower, modality-aware experts", "paddleocr_vl": "vision tower", "glm4v_moe": "vision tower",
+    "paligemma": "SigLIP vision tower", "whisper": "encoder-decoder speech model", "qwen3_omni_moe": "audio / vision towers",
+}
+
+
+def resolve_config_class(model_type: str):
+    if model_type in CONFIG_MAPPING:
+        return CONFIG_MAPPING[model_type]
+    if model_type in UNSUPPORTED_FAMILIES:
+        raise NotImplementedError(f"model_type {model_type!r} is known but not implemented: it needs {UNSUPPORTED_FAMILIES[model_type]}")
+    raise ValueError(f"unknown model_type {model_type!r}; supported: {sorted(CONFIG_MAPPING)}")
 # families whose architecture is a strict subset of an implemented one load through it
-CONFIG_MAPPING.update({"mistral": LlamaConfig, "deepseek_v2": DeepseekV3Config, "glm4_moe_lite": Glm4MoeConfig})
+CONFIG_MAPPING.update({"deepseek_v2": DeepseekV3Config, "glm4_moe_lite": Glm4MoeConfig, "phi4": Phi3Config})
 
 
 def named_config(name: str, **overrides) -> DecoderConfig:

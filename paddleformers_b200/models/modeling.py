@@ -28,8 +28,8 @@ from ..parallel.tensor_parallel import (ColumnParallelLinear, GatherOp, RowParal
 from ..parallel.topology import get_parallel_state
 from ..transformers.conversion_utils import Rule, WeightMap, expand_layers
 from ..transformers.model_utils import PretrainedModel
-from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, LlamaConfig, Qwen2Config, Qwen3Config,
-                            Qwen3MoeConfig)
+from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
+                            Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig)
 
 
 @dataclass
@@ -304,6 +304,10 @@ class DecoderModel(nn.Module):
     def make_context(self, input_ids, position_ids=None, kend=None, cp_positions=None, full_seq_len=None,
                      kend_full=None) -> BatchContext:
         B, S = input_ids.shape
+        window = getattr(self.config, "sliding_window", None)
+        if window and (full_seq_len or S) > int(window):
+            raise NotImplementedError(f"sequence length {full_seq_len or S} exceeds sliding_window={window}: the attention "
+                                      "kernels implement causal and document masks, not a sliding window")
         max_pos = S if position_ids is None else max(S, int(self.config.max_position_embeddings))
         cos, sin = self.rope(input_ids.device, max_pos)
         pos = None
@@ -519,12 +523,18 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
     else:
         qkv_sizes = [config.num_attention_heads * config.head_dim, config.num_key_value_heads * config.head_dim,
                      config.num_key_value_heads * config.head_dim]
-        per_layer.append(Rule(L + "self_attn.qkv_proj.weight", [L + "self_attn.q_proj.weight", L + "self_attn.k_proj.weight",
-                                                                 L + "self_attn.v_proj.weight"], "concat", 0, sizes=qkv_sizes))
-        if config.attention_bias:
+        if getattr(config, "hf_fused_qkv", False):      # the checkpoint already stores [q | k | v] rows in one matrix
+            per_layer.append(Rule(L + "self_attn.qkv_proj.weight", [L + "self_attn.qkv_proj.weight"]))
+        else:
+            per_layer.append(Rule(L + "self_attn.qkv_proj.weight", [L + "self_attn.q_proj.weight", L + "self_attn.k_proj.weight",
+                                                                     L + "self_attn.v_proj.weight"], "concat", 0, sizes=qkv_sizes))
+        if config.attention_bias and not getattr(config, "hf_fused_qkv", False):
             per_layer.append(Rule(L + "self_attn.qkv_proj.bias", [L + "self_attn.q_proj.bias", L + "self_attn.k_proj.bias",
                                                                    L + "self_attn.v_proj.bias"], "concat", 0, sizes=qkv_sizes))
-    dense_rule = Rule(L + "mlp.gate_up_proj.weight", [L + "mlp.gate_proj.weight", L + "mlp.up_proj.weight"], "concat", 0)
+    if getattr(config, "hf_fused_gate_up", False):  # [gate; up] rows already stacked in the checkpoint
+        dense_rule = Rule(L + "mlp.gate_up_proj.weight", [L + "mlp.gate_up_proj.weight"])
+    else:
+        dense_rule = Rule(L + "mlp.gate_up_proj.weight", [L + "mlp.gate_proj.weight", L + "mlp.up_proj.weight"], "concat", 0)
     n_total = config.num_hidden_layers + int(getattr(config, "num_nextn_predict_layers", 0) or 0)
     for i in range(config.num_hidden_layers):
         rules.extend(expand_layers(per_layer, [i]))
@@ -591,9 +601,14 @@ Qwen3ForCausalLM = _family("Qwen3ForCausalLM", Qwen3Config)
 Qwen3MoeForCausalLM = _family("Qwen3MoeForCausalLM", Qwen3MoeConfig)
 DeepseekV3ForCausalLM = _family("DeepseekV3ForCausalLM", DeepseekV3Config)
 Glm4MoeForCausalLM = _family("Glm4MoeForCausalLM", Glm4MoeConfig)
+MistralForCausalLM = _family("MistralForCausalLM", MistralConfig)
+Phi3ForCausalLM = _family("Phi3ForCausalLM", Phi3Config)
+SeedOssForCausalLM = _family("SeedOssForCausalLM", SeedOssConfig)
+InternLM3ForCausalLM = _family("InternLM3ForCausalLM", InternLM3Config)
 
 MODEL_MAPPING = {
-    "llama": LlamaForCausalLM, "mistral": LlamaForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
+    "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
+    "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,
 }

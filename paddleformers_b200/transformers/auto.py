@@ -14,21 +14,16 @@ from .configuration_utils import PretrainedConfig
 class AutoConfig:
     @staticmethod
     def for_model(model_type: str, **kw) -> PretrainedConfig:
-        from ..models.configuration import CONFIG_MAPPING
+        from ..models.configuration import resolve_config_class
 
-        if model_type not in CONFIG_MAPPING:
-            raise ValueError(f"unknown model_type {model_type!r}; supported: {sorted(CONFIG_MAPPING)}")
-        return CONFIG_MAPPING[model_type](**kw)
+        return resolve_config_class(model_type)(**kw)
 
     @staticmethod
     def from_pretrained(path: str, **overrides) -> PretrainedConfig:
-        from ..models.configuration import CONFIG_MAPPING
+        from ..models.configuration import resolve_config_class
 
         d = PretrainedConfig.get_config_dict(path)
-        mt = d.get("model_type")
-        if mt not in CONFIG_MAPPING:
-            raise ValueError(f"unknown model_type {mt!r}; supported: {sorted(CONFIG_MAPPING)}")
-        return CONFIG_MAPPING[mt].from_dict(d, **overrides)
+        return resolve_config_class(d.get("model_type")).from_dict(d, **overrides)
 
 
 class AutoModelForCausalLM:
