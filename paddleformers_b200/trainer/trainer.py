@@ -92,6 +92,9 @@ class Trainer:
             default_cbs.append(MoECorrectionBiasAdjustCallback(self.args.moe_aux_free_bias_update_rate))
         if getattr(getattr(model, "config", None), "fp8", None):
             default_cbs.append(FP8QuantWeightCallback())
+        from .integrations import callbacks_from_args
+
+        default_cbs.extend(callbacks_from_args(self.args))
         self.callback_handler = CallbackHandler(default_cbs + list(callbacks or []), self.model, self.optimizer, self.lr_scheduler)
         self._tr_loss = None
         self._interval_tokens = None
@@ -422,6 +425,10 @@ class Trainer:
         self.control._new_step()
 
     def log(self, logs: Dict[str, float]):
+        for cb in self.callback_handler.callbacks:        # callbacks that add fields (timers, memory) run before the sinks
+            aug = getattr(cb, "augment_logs", None)
+            if aug is not None:
+                aug(self.args, self.state, logs)
         self.state.log_history.append(dict(logs))
         self.control = self.callback_handler.on_log(self.args, self.state, self.control, logs=logs)
 

@@ -78,7 +78,10 @@ class TrainingArguments:
     save_hf_steps: int = -1
     eval_strategy: str = "no"
     eval_steps: Optional[int] = None
-    report_to: str = "none"
+    report_to: str = "none"            # none | comma-separated: tensorboard, visualdl, jsonl
+    logging_dir: Optional[str] = None  # scalar logs (default <output_dir>/runs)
+    enable_timer: bool = False         # per-step read-data / forward-backward / optimizer-step timers in the log record
+    log_memory: bool = False           # device memory high-water marks in the log record
     metrics_output_path: Optional[str] = None
     resume_from_checkpoint: Optional[str] = None
     save_checkpoint_format: str = field(default="sharded", metadata={"help": "sharded | unified | hf"})

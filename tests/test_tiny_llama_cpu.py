@@ -63,3 +63,39 @@ def test_resume_reproduces_uninterrupted_run(tmp_path):
     got = [h["loss"] for h in second.state.log_history if "loss" in h]
     assert second.state.global_step == 10
     assert all(abs(a - b) < 1e-5 for a, b in zip(ref[5:], got[-5:])), (ref[5:], got[-5:])
+
+
+def test_timers_and_scalar_reports(tmp_path):
+    """report_to=jsonl writes scalars; enable_timer adds per-step timer fields to the log records."""
+    import json
+
+    from paddleformers_b200 import Trainer, TrainingArguments
+    from paddleformers_b200.data.synthetic import SyntheticCausalLMDataset
+    from paddleformers_b200.models.configuration import named_config
+    from paddleformers_b200.transformers.auto import AutoModelForCausalLM
+
+    cfg = named_config("tiny-llama", vocab_size=128, hidden_size=32, intermediate_size=64, num_attention_heads=2,
+                       num_key_value_heads=1, head_dim=16)
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32)
+    args = TrainingArguments(output_dir=str(tmp_path), per_device_train_batch_size=1, gradient_accumulation_steps=2, max_steps=3,
+                             learning_rate=1e-3, logging_steps=1, save_strategy="no", max_seq_len=16, device="cpu",
+                             report_to="jsonl", enable_timer=True)
+    ds = SyntheticCausalLMDataset(128, 16, num_samples=16, seed=0)
+    tr = Trainer(model=model, args=args, train_dataset=ds)
+    tr.train()
+    recs = [h for h in tr.state.log_history if "loss" in h]
+    assert len(recs) == 3 and all(r["timer_forward_backward_ms"] > 0 and r["timer_optimizer_step_ms"] > 0 for r in recs)
+    lines = [json.loads(l) for l in open(tmp_path / "runs" / "scalars.jsonl")]
+    tags = {l["tag"] for l in lines}
+    assert {"train/loss", "train/learning_rate", "train/timer_forward_backward_ms"} <= tags
+
+
+def test_timers_accumulate_intervals():
+    from paddleformers_b200.utils.timer import Timers
+
+    t = Timers(use_cuda=False)
+    for _ in range(3):
+        with t("a"):
+            pass
+    info = t.info(normalizer=3)
+    assert set(info) == {"a"} and info["a"] >= 0 and t.info() == {}
