@@ -124,9 +124,50 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, db
 
 
+class WeightGradStore:
+    """Queue of deferred weight-gradient GEMMs, for pipeline schedules that run the input-gradient part of a backward
+    pass (which the previous stage is waiting for) before its weight-gradient part. While a group is open, linear
+    layers whose weights accumulate into ``main_grad`` enqueue their dW GEMM instead of launching it; the schedule runs
+    the group later. Only such layers can be deferred: their dW is not a value autograd has to return."""
+
+    _open = None
+    _groups: list = []
+
+    @classmethod
+    def begin_group(cls):
+        cls._open = []
+
+    @classmethod
+    def end_group(cls):
+        if cls._open is not None:
+            cls._groups.append(cls._open)
+        cls._open = None
+
+    @classmethod
+    def defer(cls, fn) -> bool:
+        if cls._open is None:
+            return False
+        cls._open.append(fn)
+        return True
+
+    @classmethod
+    def run_group(cls):
+        if cls._groups:
+            for fn in cls._groups.pop(0):
+                fn()
+
+    @classmethod
+    def run_all(cls):
+        while cls._groups:
+            cls.run_group()
+
+
 def _weight_grad(dy2, x2, weight):
     """dW = dy^T x. Accumulates into ``weight.main_grad`` (fp32) when present and returns None for autograd."""
     mg = getattr(weight, "main_grad", None)
+    if mg is not None and WeightGradStore.defer(
+            lambda: gemm(dy2, x2, out=mg.view(weight.shape), a_mn=True, b_mn=True, epi=EPI_ACCUM_F32)):
+        return None
     if mg is not None:
         gemm(dy2, x2, out=mg.view(weight.shape), a_mn=True, b_mn=True, epi=EPI_ACCUM_F32)
         return None

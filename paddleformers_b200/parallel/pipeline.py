@@ -123,54 +123,88 @@ def schedule_interleaved(stage: int, P: int, M: int, V: int) -> List[Action]:
     return acts
 
 
+def schedule_zero_bubble(stage: int, P: int, M: int) -> List[Action]:
+    """1F1B with the backward pass split into B (gradient w.r.t. the stage input: the part the previous stage waits
+    for) and W (weight gradients, needed only before the optimizer step), W running right after its B. The chain of
+    backward dependencies between stages then advances in B-sized instead of (B + W)-sized hops, which removes the W
+    share of the warm-up and cool-down bubbles: with unit costs the makespan falls from 3M + 3(P - 1) to
+    3M + 2(P - 1) at 1F1B's activation memory (checked by ``simulate`` in the tests). The reference attacks the same
+    bubble with its DualPipeV / overlapped schedule nodes
+    (paddleformers/cli/train/deepseek_v3_pretrain/modeling_pp.py:535-606)."""
+    warm = min(P - stage - 1, M)
+    acts = [Action("F", 0, m) for m in range(warm)]
+    f = warm
+    for b in range(M):
+        if f < M:
+            acts.append(Action("F", 0, f)); f += 1
+        acts.append(Action("B", 0, b))
+        acts.append(Action("W", 0, b))
+    return acts
+
+
 def make_schedule(name: str, stage: int, P: int, M: int, V: int = 1) -> List[Action]:
     name = name.lower()
     if name in ("fthenb", "f-then-b"):
         return schedule_fthenb(stage, P, M, V)
+    if name in ("zb", "zbh1", "zero_bubble", "zero-bubble"):
+        assert V == 1, "the zero-bubble schedule is defined for one chunk per stage"
+        return schedule_zero_bubble(stage, P, M)
     if V > 1 or name in ("interleaved", "vpp"):
         return schedule_interleaved(stage, P, M, max(V, 1))
     return schedule_1f1b(stage, P, M)
 
 
-def simulate(schedules: List[List[Action]], P: int, V: int) -> Dict[str, object]:
-    """Runs all stages' action lists as a discrete-event simulation (unit cost per action, blocking on
-    dependencies). Raises on deadlock; returns makespan, bubble fraction and peak live activations per stage."""
-    done_f, done_b = set(), set()   # (virtual stage index, mb)
+def simulate(schedules: List[List[Action]], P: int, V: int, cost: Optional[Dict[str, float]] = None) -> Dict[str, object]:
+    """Runs all stages' action lists as a timed simulation: every stage executes its list in order, an action starts
+    when the stage is free and its dependencies have finished. ``cost`` maps action kinds to durations; by default a
+    forward costs 1, a fused backward 2, and in schedules that split it B and W cost 1 each. Raises on deadlock;
+    returns makespan, bubble fraction (idle share of the busiest stage's timeline) and peak live activations."""
+    split = any(a.kind == "W" for sch in schedules for a in sch)
+    cost = cost or ({"F": 1.0, "B": 1.0, "W": 1.0} if split else {"F": 1.0, "B": 2.0})
+    fin_f: Dict[Tuple[int, int], float] = {}
+    fin_b: Dict[Tuple[int, int], float] = {}
     pos = [0] * P
+    free = [0.0] * P
     live = [0] * P
     peak = [0] * P
-    time = 0
     n_actions = sum(len(s) for s in schedules)
     finished = 0
     last_virtual = P * V - 1
     while finished < n_actions:
-        progressed = []
+        progressed = False
         for s in range(P):
-            if pos[s] >= len(schedules[s]):
-                continue
-            a = schedules[s][pos[s]]
-            vs = a.chunk * P + s
-            if a.kind == "F":
-                ready = vs == 0 or (vs - 1, a.mb) in done_f
-            else:
-                ready = (vs, a.mb) in done_f and (vs == last_virtual or (vs + 1, a.mb) in done_b)
-            if ready:
-                progressed.append((s, a, vs))
+            while pos[s] < len(schedules[s]):
+                a = schedules[s][pos[s]]
+                vs = a.chunk * P + s
+                if a.kind == "F":
+                    deps = [] if vs == 0 else [fin_f.get((vs - 1, a.mb))]
+                elif a.kind == "B":
+                    deps = [fin_f.get((vs, a.mb))] + ([] if vs == last_virtual else [fin_b.get((vs + 1, a.mb))])
+                else:
+                    deps = [fin_b.get((vs, a.mb))]
+                if any(d is None for d in deps):
+                    break
+                start = max([free[s]] + deps)
+                end = start + cost[a.kind]
+                free[s] = end
+                if a.kind == "F":
+                    fin_f[(vs, a.mb)] = end
+                    live[s] += 1
+                    peak[s] = max(peak[s], live[s])
+                elif a.kind == "B":
+                    fin_b[(vs, a.mb)] = end
+                    if not split:
+                        live[s] -= 1
+                else:
+                    live[s] -= 1
+                pos[s] += 1
+                finished += 1
+                progressed = True
         if not progressed:
             raise RuntimeError(f"pipeline schedule deadlocks at positions {pos}")
-        for s, a, vs in progressed:
-            if a.kind == "F":
-                done_f.add((vs, a.mb))
-                live[s] += 1
-                peak[s] = max(peak[s], live[s])
-            else:
-                done_b.add((vs, a.mb))
-                live[s] -= 1
-            pos[s] += 1
-            finished += 1
-        time += 1
-    work = max(len(s) for s in schedules)
-    return {"makespan": time, "bubble_fraction": 1.0 - work / time, "peak_live": peak}
+    makespan = max(free)
+    work = max(sum(cost[a.kind] for a in sch) for sch in schedules)
+    return {"makespan": makespan, "bubble_fraction": 1.0 - work / makespan, "peak_live": peak}
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -334,7 +368,11 @@ class PipelineEngine:
         pending: List[object] = []
         total_loss = torch.zeros((), dtype=torch.float32, device=dev)
         last_virtual = P * V - 1
+        split_w = any(a.kind == "W" for a in acts)
         for a in acts:
+            if a.kind == "W":
+                F.WeightGradStore.run_group()      # the weight-gradient GEMMs queued by the matching B
+                continue
             vs = a.chunk * P + s
             batch = micro_batches[a.mb]
             B, S = batch["input_ids"].shape
@@ -358,13 +396,20 @@ class PipelineEngine:
                     saved[(a.chunk, a.mb)] = (x_in, out)
             else:
                 x_in, out = saved.pop((a.chunk, a.mb))
-                if vs == last_virtual:
-                    out.backward()
-                else:
-                    g = self._recv(tuple(out.shape), out.dtype, dev, self.next_rank, self.bwd_group)
-                    torch.autograd.backward(out, g)
+                if split_w:
+                    F.WeightGradStore.begin_group()
+                try:
+                    if vs == last_virtual:
+                        out.backward()
+                    else:
+                        g = self._recv(tuple(out.shape), out.dtype, dev, self.next_rank, self.bwd_group)
+                        torch.autograd.backward(out, g)
+                finally:
+                    if split_w:
+                        F.WeightGradStore.end_group()
                 if vs > 0:
                     self._send(x_in.grad, self.prev_rank, self.bwd_group, pending)
+        F.WeightGradStore.run_all()
         for w in pending:
             w.wait()
         self._sync_shared_embeddings()

@@ -66,7 +66,7 @@ class TrainingArguments:
     sharding: str = field(default="", metadata={"help": "'' | stage1 | stage2"})
     sequence_parallel: bool = False
     hybrid_parallel_topo_order: str = "sharding_first"
-    pipeline_schedule: str = field(default="1F1B", metadata={"help": "1F1B | interleaved | FThenB"})
+    pipeline_schedule: str = field(default="1F1B", metadata={"help": "1F1B | interleaved | FThenB | zero_bubble (backward split into input-gradient and deferred weight-gradient parts)"})
     sharding_comm_buffer_size_MB: int = 256
     sharding_overlap: bool = True
     # logging / saving / eval
