@@ -150,7 +150,35 @@ def run_tuner(argv: Optional[list] = None):
         return run_sft(model_args, data_args, gen_args, train_args, pretrain=True)
     if stage in ("DPO", "VL-DPO"):
         return run_dpo(model_args, data_args, gen_args, train_args)
-    raise ValueError(f"unknown stage {model_args.stage!r}; expected SFT | PT | DPO")
+    if stage in ("AUTO-PARALLEL", "AUTO_PARALLEL"):
+        return run_auto_parallel(model_args, data_args, gen_args, train_args)
+    raise ValueError(f"unknown stage {model_args.stage!r}; expected SFT | PT | DPO | auto-parallel")
+
+
+def run_auto_parallel(model_args, data_args, gen_args, train_args):
+    """Pre-training with the parallel degrees chosen by ``parallel.auto_plan`` for this job's GPU count (the role of
+    the reference's auto-parallel stage, paddleformers/cli/train/auto_parallel/workflow.py): any degree the user left
+    at 1 is overwritten by the plan, then the PT workflow runs unchanged."""
+    import os
+
+    from ..models.configuration import CONFIG_MAPPING, named_config
+    from ..parallel.auto_plan import plan_parallelism
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if model_args.model_name_or_path and not model_args.from_scratch:
+        config = AutoConfig.from_pretrained(model_args.model_name_or_path)
+    else:
+        try:
+            config = named_config(model_args.model_type)
+        except KeyError:
+            config = CONFIG_MAPPING[model_args.model_type]()
+    plan = plan_parallelism(config, world, train_args.max_seq_len, train_args.per_device_train_batch_size,
+                            recompute=getattr(train_args, "recompute_granularity", None) == "full")
+    logger.info(f"auto-parallel plan for {world} GPU(s): {plan.reason}")
+    for k, v in plan.training_args().items():
+        if hasattr(train_args, k) and getattr(train_args, k) in (1, "", False, None):
+            setattr(train_args, k, v)
+    return run_sft(model_args, data_args, gen_args, train_args, pretrain=True)
 
 
 if __name__ == "__main__":

@@ -20,7 +20,8 @@ def test_parse_overrides_and_unknown_keys(tmp_path):
         get_train_args([str(cfg), "not_a_flag=1"])
 
 
-def test_pretrain_stage_end_to_end_from_yaml(tmp_path):
+@pytest.mark.parametrize("stage", ["PT", "auto-parallel"])
+def test_pretrain_stage_end_to_end_from_yaml(tmp_path, stage):
     from paddleformers_b200.cli.cli import main
     from paddleformers_b200.data.indexed_dataset import MMapIndexedDatasetBuilder
 
@@ -33,7 +34,7 @@ def test_pretrain_stage_end_to_end_from_yaml(tmp_path):
     out = tmp_path / "out"
     cfg = tmp_path / "pt.json"
     cfg.write_text(json.dumps({
-        "stage": "PT", "model_type": "tiny-llama", "from_scratch": True, "compute_type": "float32", "device": "cpu",
+        "stage": stage, "model_type": "tiny-llama", "from_scratch": True, "compute_type": "float32", "device": "cpu",
         "config_overrides": {"vocab_size": 128, "hidden_size": 32, "intermediate_size": 48, "num_attention_heads": 2,
                              "num_key_value_heads": 1, "head_dim": 16},
         "input_dir": prefix, "split": "9,1,0", "max_seq_len": 32, "max_steps": 4, "per_device_train_batch_size": 2,
