@@ -65,10 +65,22 @@ def save_checkpoint(trainer, out_dir: str) -> None:
     world = dist.get_world_size() if dist.is_initialized() else 1
     wait_for_pending_saves()
     os.makedirs(os.path.join(out_dir, "optimizer"), exist_ok=True)
-    # 1. model weights (collective: tp gathers)
-    trainer.model.save_pretrained(out_dir)
-    # 2. this rank's optimizer shards (moved to host now, written below or in the background)
-    opt_state = trainer.optimizer.state_dict()
+    zcc = getattr(trainer, "zcc", None)
+    extra = None
+    if zcc is not None:
+        # zero-cost path: the shard is copied to pinned memory on a side stream; the working weights are rebuilt from the
+        # fp32 master shards on resume, so the (collective, synchronous) HF export is skipped unless asked for
+        if getattr(args, "zcc_save_model_weights", False):
+            trainer.model.save_pretrained(out_dir)
+        else:
+            trainer.model.config.save_pretrained(out_dir)
+        opt_state = zcc.snapshot()
+        extra = zcc.extra_state()
+    else:
+        # 1. model weights (collective: tp gathers)
+        trainer.model.save_pretrained(out_dir)
+        # 2. this rank's optimizer shards (moved to host now, written below or in the background)
+        opt_state = trainer.optimizer.state_dict()
     files = {}
     for name, dom in opt_state["domains"].items():
         fname = f"shard_{name}_{dom['shard_rank']:03d}of{dom['shard_size']:03d}_r{rank:05d}.pt"
@@ -80,6 +92,9 @@ def save_checkpoint(trainer, out_dir: str) -> None:
         state_json = trainer.state
 
     def write():
+        if zcc is not None:
+            zcc.wait_host()                      # the copies into the pinned buffers have landed
+            torch.save(extra, os.path.join(out_dir, f"extra_state_{rank}.pt"))
         for fname, payload in files.items():
             tmp = os.path.join(out_dir, "optimizer", fname + ".tmp")
             torch.save(payload, tmp)
@@ -106,7 +121,7 @@ def save_checkpoint(trainer, out_dir: str) -> None:
                     break
                 time.sleep(0.05)
 
-    if args.async_save:
+    if args.async_save or zcc is not None:
         t = threading.Thread(target=write, daemon=False)
         t.start()
         _pending.append(t)
@@ -123,7 +138,14 @@ def load_checkpoint(trainer, path: str) -> None:
         raise RuntimeError(f"checkpoint {path} is incomplete (interrupted save): refusing to resume from it")
     args, ps = trainer.args, trainer.ps
     rank = args.process_index
-    trainer.model.load_hf_checkpoint(path)
+    has_weights = any(f.endswith(".safetensors") for f in os.listdir(path))
+    if has_weights:
+        trainer.model.load_hf_checkpoint(path)
+    extra_file = os.path.join(path, f"extra_state_{rank}.pt")
+    if os.path.exists(extra_file):
+        from .zero_cost_checkpoint import load_extra_state
+
+        load_extra_state(trainer.model, torch.load(extra_file, map_location="cpu", weights_only=False))
     opt = trainer.optimizer
     opt_dir = os.path.join(path, "optimizer")
     sd = {"domains": {}}

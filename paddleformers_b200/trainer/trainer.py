@@ -171,6 +171,11 @@ class Trainer:
                                       min_lr_ratio=min_ratio, decay_steps=a.decay_steps)
             self.lr_scheduler = LRScheduler(a.learning_rate, fn)
         self.callback_handler.optimizer, self.callback_handler.lr_scheduler = self.optimizer, self.lr_scheduler
+        self.zcc = None
+        if getattr(a, "enable_zero_cost_checkpoint", False) and isinstance(self.optimizer, ShardedAdamW):
+            from .zero_cost_checkpoint import ZeroCostCheckpointManager
+
+            self.zcc = ZeroCostCheckpointManager(self.optimizer, self.model)
 
     # ------------------------------------------------------------------ one micro step
     def compute_loss(self, model, inputs: Dict[str, Any]):
@@ -374,6 +379,8 @@ class Trainer:
             self.lr_scheduler.step()
             return
         lr = self.lr_scheduler.get_lr()
+        if getattr(self, "zcc", None) is not None:
+            self.zcc.before_update()
         self._last_grad_norm = self.optimizer.step(lr=lr)
         self.lr_scheduler.step()
 

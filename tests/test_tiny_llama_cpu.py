@@ -99,3 +99,24 @@ def test_timers_accumulate_intervals():
             pass
     info = t.info(normalizer=3)
     assert set(info) == {"a"} and info["a"] >= 0 and t.info() == {}
+
+
+def test_zero_cost_checkpoint_resume_matches_uninterrupted_run(tmp_path):
+    """Optimizer-shard snapshots persisted in the background, no weight export: the resumed run rebuilds the working
+    weights from the fp32 master shards and continues exactly like the uninterrupted one."""
+    _, full = _make(tmp_path / "a", 10)
+    full.train()
+    ref = [h["loss"] for h in full.state.log_history if "loss" in h]
+    _, first = _make(tmp_path / "b", 5, enable_zero_cost_checkpoint=True)
+    first.train()
+    from paddleformers_b200.trainer.checkpoint import wait_for_pending_saves
+
+    wait_for_pending_saves()
+    ck = get_last_checkpoint(str(tmp_path / "b"))
+    assert ck.endswith("checkpoint-5") and not any(f.endswith(".safetensors") for f in os.listdir(ck))
+    assert os.path.exists(os.path.join(ck, "extra_state_0.pt")) and first.zcc.snapshots == 1
+    _, second = _make(tmp_path / "b", 10, enable_zero_cost_checkpoint=True)
+    second.train(resume_from_checkpoint="auto")
+    got = [h["loss"] for h in second.state.log_history if "loss" in h]
+    assert second.state.global_step == 10
+    assert all(abs(a - b) < 1e-5 for a, b in zip(ref[5:], got[-5:])), (ref[5:], got[-5:])
