@@ -178,3 +178,77 @@ register_template("phi4", format_user="<|im_start|>user<|im_sep|>{content}<|im_e
                   stop_words=["<|im_end|>"])
 register_template("ernie", format_prefix="<|begin_of_sentence|>", format_user="User: {content}\nAssistant: ",
                   format_assistant="{content}<|end_of_sentence|>", format_system="{content}\n")
+
+# ---- further public chat formats (as published on the respective model cards) -------------------------------------------
+_CHATML = dict(format_user="<|im_start|>user\n{content}<|im_end|>\n<|im_start|>assistant\n", format_assistant="{content}<|im_end|>\n",
+               format_system="<|im_start|>system\n{content}<|im_end|>\n", stop_words=["<|im_end|>"], replace_eos=True)
+register_template("llama2", format_prefix="<s>", format_user="[INST] {content} [/INST]", format_assistant=" {content} </s><s>",
+                  format_system="<<SYS>>\n{content}\n<</SYS>>\n\n")
+register_template("llama4", format_prefix="<|begin_of_text|>",
+                  format_user="<|header_start|>user<|header_end|>\n\n{content}<|eot|><|header_start|>assistant<|header_end|>\n\n",
+                  format_assistant="{content}<|eot|>", format_system="<|header_start|>system<|header_end|>\n\n{content}<|eot|>",
+                  format_observation="<|header_start|>ipython<|header_end|>\n\n{content}<|eot|><|header_start|>assistant<|header_end|>\n\n",
+                  format_function="{content}<|eot|>", stop_words=["<|eot|>", "<|eom|>"], replace_eos=True)
+register_template("vicuna", format_user="USER: {content} ASSISTANT:", format_assistant=" {content}</s>", format_system="{content} ",
+                  default_system="A chat between a curious user and an artificial intelligence assistant. The assistant gives "
+                                 "helpful, detailed, and polite answers to the user's questions.")
+register_template("zephyr", format_user="<|user|>\n{content}</s>\n<|assistant|>\n", format_assistant="{content}</s>\n",
+                  format_system="<|system|>\n{content}</s>\n")
+register_template("yi", **_CHATML)
+register_template("qwen2_vl", default_system="You are a helpful assistant.", **_CHATML)
+register_template("qwen3_nothink", format_user="<|im_start|>user\n{content}<|im_end|>\n<|im_start|>assistant\n<think>\n\n</think>\n\n",
+                  format_assistant="{content}<|im_end|>\n", format_system="<|im_start|>system\n{content}<|im_end|>\n",
+                  stop_words=["<|im_end|>"], replace_eos=True)
+register_template("minicpm", **_CHATML)
+register_template("internlm2", format_prefix="<s>", format_observation="<|im_start|>environment\n{content}<|im_end|>\n<|im_start|>assistant\n",
+                  **_CHATML)
+register_template("internlm3", format_prefix="<s>", **_CHATML)
+register_template("seed_oss", format_prefix="<seed:bos>", format_user="user\n{content}<seed:eos><seed:bos>assistant\n",
+                  format_assistant="{content}<seed:eos>", format_system="system\n{content}<seed:eos><seed:bos>", stop_words=["<seed:eos>"])
+register_template("baichuan2", format_user="<reserved_106>{content}<reserved_107>", format_assistant="{content}", format_system="{content}",
+                  efficient_eos=True)
+register_template("deepseek", format_prefix="<｜begin▁of▁sentence｜>", format_user="User: {content}\n\nAssistant:",
+                  format_assistant=" {content}<｜end▁of▁sentence｜>", format_system="{content}\n\n")
+register_template("deepseek_coder", format_prefix="<｜begin▁of▁sentence｜>", format_user="### Instruction:\n{content}\n### Response:\n",
+                  format_assistant="{content}\n<|EOT|>\n", format_system="{content}\n", stop_words=["<|EOT|>"],
+                  default_system="You are an AI programming assistant, utilizing the DeepSeek Coder model, developed by DeepSeek "
+                                 "Company, and you only answer questions related to computer science.")
+register_template("deepseek_r1", format_prefix="<｜begin▁of▁sentence｜>", format_user="<｜User｜>{content}<｜Assistant｜>",
+                  format_assistant="{content}<｜end▁of▁sentence｜>", format_system="{content}")
+register_template("gemma3", format_prefix="<bos>", format_user="<start_of_turn>user\n{content}<end_of_turn>\n<start_of_turn>model\n",
+                  format_assistant="{content}<end_of_turn>\n", format_system="{content}\n\n", stop_words=["<end_of_turn>"], replace_eos=True)
+register_template("phi3", format_user="<|user|>\n{content}<|end|>\n<|assistant|>\n", format_assistant="{content}<|end|>\n",
+                  format_system="<|system|>\n{content}<|end|>\n", stop_words=["<|end|>"], replace_eos=True)
+register_template("cohere", format_prefix="<BOS_TOKEN>",
+                  format_user="<|START_OF_TURN_TOKEN|><|USER_TOKEN|>{content}<|END_OF_TURN_TOKEN|><|START_OF_TURN_TOKEN|><|CHATBOT_TOKEN|>",
+                  format_assistant="{content}<|END_OF_TURN_TOKEN|>",
+                  format_system="<|START_OF_TURN_TOKEN|><|SYSTEM_TOKEN|>{content}<|END_OF_TURN_TOKEN|>", stop_words=["<|END_OF_TURN_TOKEN|>"])
+register_template("falcon", format_user="User: {content}\nFalcon:", format_assistant=" {content}\n", format_system="{content}\n",
+                  efficient_eos=True)
+register_template("olmo", format_user="<|user|>\n{content}\n<|assistant|>\n", format_assistant="{content}<|endoftext|>\n",
+                  format_system="<|system|>\n{content}\n")
+register_template("granite3", format_user="<|start_of_role|>user<|end_of_role|>{content}<|end_of_text|>\n<|start_of_role|>assistant<|end_of_role|>",
+                  format_assistant="{content}<|end_of_text|>\n", format_system="<|start_of_role|>system<|end_of_role|>{content}<|end_of_text|>\n",
+                  stop_words=["<|end_of_text|>"])
+register_template("hunyuan", format_prefix="<|startoftext|>", format_user="{content}<|extra_0|>", format_assistant="{content}<|eos|>",
+                  format_system="{content}<|extra_4|>", stop_words=["<|eos|>"])
+register_template("kimi", format_user="<|im_user|>user<|im_middle|>{content}<|im_end|><|im_assistant|>assistant<|im_middle|>",
+                  format_assistant="{content}<|im_end|>", format_system="<|im_system|>system<|im_middle|>{content}<|im_end|>",
+                  stop_words=["<|im_end|>"])
+register_template("gpt_oss", format_user="<|start|>user<|message|>{content}<|end|><|start|>assistant",
+                  format_assistant="<|channel|>final<|message|>{content}<|end|>", format_system="<|start|>system<|message|>{content}<|end|>",
+                  stop_words=["<|return|>", "<|end|>"], thought_words=("<|channel|>analysis<|message|>", "<|end|><|start|>assistant"))
+register_template("ernie_nothink", format_prefix="<|begin_of_sentence|>", format_user="User: {content}\nAssistant: <think>\n\n</think>\n\n",
+                  format_assistant="{content}<|end_of_sentence|>", format_system="{content}\n")
+register_template("mistral_small", format_prefix="<s>", format_user="[INST]{content}[/INST]", format_assistant="{content}</s>",
+                  format_system="[SYSTEM_PROMPT]{content}[/SYSTEM_PROMPT]")
+register_template("minimax", format_user="<beginning_of_sentence>user name=user\n{content}<end_of_sentence>\n<beginning_of_sentence>ai name=assistant\n",
+                  format_assistant="{content}<end_of_sentence>\n", format_system="<beginning_of_sentence>system ai_setting=assistant\n{content}<end_of_sentence>\n",
+                  stop_words=["<end_of_sentence>"])
+register_template("xverse", format_user="Human: {content}\n\nAssistant: ", format_assistant="{content}", efficient_eos=True)
+register_template("openchat", format_user="GPT4 Correct User: {content}<|end_of_turn|>GPT4 Correct Assistant:",
+                  format_assistant=" {content}<|end_of_turn|>", format_system="{content}<|end_of_turn|>", stop_words=["<|end_of_turn|>"])
+register_template("solar", format_user="### User:\n{content}\n\n### Assistant:\n", format_assistant="{content}\n\n",
+                  format_system="### System:\n{content}\n\n", efficient_eos=True)
+register_template("starchat", format_user="<|user|>\n{content}<|end|>\n<|assistant|>", format_assistant="\n{content}<|end|>\n",
+                  format_system="<|system|>\n{content}<|end|>\n", stop_words=["<|end|>"])

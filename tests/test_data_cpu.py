@@ -150,3 +150,20 @@ def test_native_index_helpers_match_numpy():
     kend, pos = np.empty(10, dtype=np.int32), np.empty(10, dtype=np.int64)
     idx._host().pfb_build_doc_bounds(idx._ptr(ids, ctypes.c_int64), 10, 0, idx._ptr(kend, ctypes.c_int32), idx._ptr(pos, ctypes.c_int64))
     assert kend.tolist() == [3, 3, 3, 7, 7, 7, 7, 8, 10, 10] and pos.tolist() == [0, 1, 2, 0, 1, 2, 3, 0, 0, 1]
+
+
+def test_every_template_renders_a_multi_turn_conversation():
+    from paddleformers_b200.datasets.template import TEMPLATES
+
+    msgs = [{"role": "system", "content": "SYS"}, {"role": "user", "content": "Q1"}, {"role": "assistant", "content": "A1"},
+            {"role": "user", "content": "Q2"}, {"role": "assistant", "content": "A2"}]
+    assert len(TEMPLATES) >= 45
+    for name, t in TEMPLATES.items():
+        pairs = t.render_turns(msgs)
+        assert len(pairs) == 2, name
+        text = "".join(p + r for p, r in pairs)
+        for piece in ("Q1", "A1", "Q2", "A2"):
+            assert piece in text, (name, piece)
+        assert text.index("Q1") < text.index("A1") < text.index("Q2") < text.index("A2"), name
+        if name != "empty":
+            assert "SYS" in pairs[0][0], name
