@@ -96,7 +96,11 @@ def _process_logits(logits, generated, cfg: GenerationConfig):
 
 @torch.no_grad()
 def generate(model, input_ids: torch.Tensor, generation_config: Optional[GenerationConfig] = None,
-             streamer: Optional[Callable[[torch.Tensor], None]] = None, **kw) -> torch.Tensor:
+             streamer: Optional[Callable[[torch.Tensor], None]] = None, logits_processor=None, stopping_criteria=None,
+             **kw) -> torch.Tensor:
+    """Greedy / sampling / beam decoding with a KV cache. ``logits_processor`` (a ``LogitsProcessorList``) runs before the
+    built-in repetition penalty and sampling warpers; ``stopping_criteria`` (a ``StoppingCriteriaList``) adds to the
+    end-of-sequence and stop-token checks."""
     cfg = generation_config or GenerationConfig()
     for k, v in kw.items():
         setattr(cfg, k, v)
@@ -115,19 +119,26 @@ def generate(model, input_ids: torch.Tensor, generation_config: Optional[Generat
     for _ in range(cfg.max_new_tokens):
         pos = torch.arange(past, past + cur.shape[1], device=cur.device)[None].expand(B, -1)
         out = model(cur if use_cache else seq, position_ids=pos if use_cache else None, caches=caches, return_logits=True)
-        logits = _process_logits(out.logits[:, -1].float(), seq, cfg)
+        logits = out.logits[:, -1].float()
+        if logits_processor is not None:
+            logits = logits_processor(seq, logits)
+        logits = _process_logits(logits, seq, cfg)
         nxt = torch.multinomial(torch.softmax(logits, -1), 1) if cfg.do_sample else logits.argmax(-1, keepdim=True)
         if cfg.pad_token_id is not None:
             nxt = torch.where(done[:, None], torch.full_like(nxt, cfg.pad_token_id), nxt)
         seq = torch.cat([seq, nxt], 1)
         if streamer is not None:
-            streamer(nxt)
+            (streamer.put if hasattr(streamer, "put") else streamer)(nxt)
         for s in stops:
             done |= nxt[:, 0] == s
+        if stopping_criteria is not None:
+            done |= stopping_criteria(seq, logits)
         if bool(done.all()):
             break
         past += cur.shape[1]
         cur = nxt
+    if streamer is not None and hasattr(streamer, "end"):
+        streamer.end()
     return seq
 
 
