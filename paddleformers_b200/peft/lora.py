@@ -178,13 +178,15 @@ class LoRAModel(nn.Module):
             p.requires_grad_(False)
         pats = [re.compile(p) for p in cfg.target_modules]
         from ..nn.moe import GroupedExperts
+        from ..quantization.weight_only import QuantizationLinear
 
         for name, mod in list(model.named_modules()):
             if not any(p.fullmatch(name) or p.search(name) for p in pats):
                 continue
             parent_name, _, leaf = name.rpartition(".")
             parent = model.get_submodule(parent_name) if parent_name else model
-            if isinstance(mod, (nn.Linear, ColumnParallelLinear, RowParallelLinear)):
+            if isinstance(mod, (nn.Linear, ColumnParallelLinear, RowParallelLinear, QuantizationLinear)):
+                # a QuantizationLinear base (int8 / int4 / nf4) gives QLoRA: frozen quantised weights, bf16 adapters
                 setattr(parent, leaf, LoRALinear(mod, cfg))
             elif isinstance(mod, GroupedExperts):
                 setattr(parent, leaf, LoRAMoeExperts(mod, cfg))

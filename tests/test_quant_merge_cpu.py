@@ -81,3 +81,43 @@ def test_merge_methods(tmp_path):
     same = torch.sign(d1) == torch.sign(d2)
     assert torch.allclose(t[same], (base["a.weight"] + (d1 + d2) / 2)[same], atol=1e-5)
     assert os.path.exists(os.path.join(out, "config.json"))
+
+
+def test_qat_linears_hadamard_and_qlora():
+    import torch.nn as nn
+
+    from paddleformers_b200.peft.lora import LoRAConfig, LoRAModel
+    from paddleformers_b200.quantization.qat import (QATLinear, block_hadamard, convert_to_qat, fake_quant_per_token,
+                                                     hadamard_transform)
+    from paddleformers_b200.quantization.weight_only import quantize_model
+
+    torch.manual_seed(0)
+    x = torch.randn(7, 64)
+    # Hadamard: orthonormal and an involution
+    h = hadamard_transform(x)
+    assert torch.allclose(hadamard_transform(h), x, atol=1e-5) and torch.allclose(h.norm(dim=-1), x.norm(dim=-1), atol=1e-4)
+    assert torch.allclose(block_hadamard(block_hadamard(x, 16), 16), x, atol=1e-5)
+    # fake quantisation: at most half a step of error, gradients pass through
+    xq = fake_quant_per_token(x.clone().requires_grad_(True))
+    step = x.abs().amax(-1, keepdim=True) / 127
+    assert ((xq - x).abs() <= step / 2 + 1e-6).all()
+    lin = nn.Linear(64, 32)
+    q = QATLinear(lin, hadamard_block=16)
+    xin = x.clone().requires_grad_(True)
+    y = q(xin)
+    assert (y - lin(x)).abs().max() < 0.05
+    y.sum().backward()
+    assert lin.weight.grad is not None and xin.grad.abs().sum() > 0
+    # QLoRA: adapters on top of nf4 bases; only the adapters train
+    net = nn.Sequential()
+    net.add_module("qkv_proj", nn.Linear(64, 64))
+    net.add_module("down_proj", nn.Linear(64, 64))
+    assert quantize_model(net, "nf4") == 2
+    lora = LoRAModel(net, LoRAConfig(r=4, lora_alpha=8))
+    names = [n for n, p in lora.named_parameters() if p.requires_grad]
+    assert len(names) == 4 and all("lora_" in n for n in names)
+    out = lora(x)
+    out.sum().backward()
+    assert all(p.grad is not None for n, p in lora.named_parameters() if p.requires_grad)
+    m2 = nn.Sequential(nn.Linear(8, 8), nn.Linear(8, 8))
+    assert convert_to_qat(m2, "a8w4") == 2
