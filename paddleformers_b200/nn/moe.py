@@ -65,7 +65,7 @@ class TopkRouter(nn.Module):
 
     def forward(self, x2d: torch.Tensor):
         """x2d: [T, H] -> (topk_idx [T,k] int64, topk_weight [T,k] fp32, aux_loss scalar or None)."""
-        logits = TF.linear(x2d.float(), self.weight)
+        logits = F.router_logits(x2d, self.weight)
         if self.scoring == "sigmoid":
             scores = torch.sigmoid(logits)
         else:

@@ -124,6 +124,51 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, db
 
 
+def split_bf16(t: torch.Tensor):
+    """t (fp32) ~= hi + lo with both parts in bf16: 16 mantissa bits survive instead of 8, and products of a bf16
+    operand with (hi, lo) accumulated in fp32 on the tensor cores reproduce an fp32 matmul to ~1e-5 relative."""
+    hi = t.to(torch.bfloat16)
+    lo = (t - hi.float()).to(torch.bfloat16)
+    return hi, lo
+
+
+class _RouterLogitsFn(torch.autograd.Function):
+    """fp32-accurate router logits x @ W^T for bf16 activations and fp32 router weights on the tcgen05 GEMM: the weight
+    (and, in the backward pass, the logit gradient) is split into bf16 hi + lo parts that ride along as extra rows /
+    columns of one GEMM each, so no fp32 copy of the activations is made and no CUDA-core GEMM runs."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        E = w.shape[0]
+        hi, lo = split_bf16(w.detach())
+        out = gemm(x, torch.cat([hi, lo], 0), epi=EPI_STORE_F32)          # [T, 2E]
+        ctx.save_for_backward(x, hi, lo)
+        return out[:, :E] + out[:, E:]
+
+    @staticmethod
+    def backward(ctx, g):
+        x, hi, lo = ctx.saved_tensors
+        E = hi.shape[0]
+        ghi, glo = split_bf16(g.float())
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            # (g_hi + g_lo) @ (W_hi + W_lo), dropping the lo x lo term
+            dx = gemm(torch.cat([ghi, glo, ghi], 1), torch.cat([hi, hi, lo], 0), b_mn=True)
+        if ctx.needs_input_grad[1]:
+            both = gemm(torch.cat([ghi, glo], 1), x, a_mn=True, b_mn=True, epi=EPI_STORE_F32)   # [2E, H]
+            dw = both[:E] + both[E:]
+        return dx, dw
+
+
+def router_logits(x2d: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """Router scores in fp32 ([T, E]) from activations [T, H] and fp32 weights [E, H]
+    (paddleformers/nn/moe_deepep/moe_gate.py:464-499 computes them with an fp32 matmul)."""
+    if (use_cuda_kernels(x2d) and x2d.dtype == torch.bfloat16 and weight.dtype == torch.float32 and weight.shape[0] % 8 == 0
+            and weight.shape[1] % 8 == 0 and x2d.is_contiguous()):
+        return _RouterLogitsFn.apply(x2d, weight)
+    return torch.nn.functional.linear(x2d.float(), weight.float())
+
+
 class WeightGradStore:
     """Queue of deferred weight-gradient GEMMs, for pipeline schedules that run the input-gradient part of a backward
     pass (which the previous stage is waiting for) before its weight-gradient part. While a group is open, linear

@@ -123,3 +123,26 @@ def test_linear_autograd_matches_reference(F):
     w2.main_grad = torch.zeros(w2.shape, device="cuda", dtype=torch.float32)
     F.linear(x.detach(), w2).backward(g)
     assert w2.grad is None and _rel_err(w2.main_grad, wr.grad) < 1e-3
+
+
+def test_router_logits_fp32_accuracy_on_tensor_cores():
+    """hi/lo bf16 split of the fp32 router weight (and of the logit gradient): the tcgen05 path must match an fp32 matmul
+    far more closely than a plain bf16 cast of the weight would."""
+    from paddleformers_b200.ops import functional as F
+
+    torch.manual_seed(0)
+    T, H, E = 1000, 512, 128
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(E, H, device="cuda") * 0.05).requires_grad_(True)
+    g = torch.randn(T, E, device="cuda")
+    out = F.router_logits(x, w)
+    out.backward(g)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().clone().requires_grad_(True)
+    ref = xr @ wr.t()
+    ref.backward(g)
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    assert out.dtype == torch.float32 and rel(out, ref) < 2e-5
+    assert rel(w.grad, wr.grad) < 2e-5
+    assert rel(x.grad, xr.grad) < 5e-3          # dx is returned in bf16
+    F.check_kernel_status()
