@@ -237,6 +237,14 @@ class DecoderLayer(nn.Module):
             self.mlp = MoELayer(config, dtype=dtype, device=device)
         else:
             self.mlp = DenseMLP(config.hidden_size, config.intermediate_size, config, bias=config.mlp_bias, dtype=dtype, device=device)
+        # recompute_granularity="selective": recompute_modules names the sub-modules ("attn", "mlp") whose activations are
+        # dropped and rebuilt in the backward pass (paddleformers/transformers/configuration_utils.py:264-283)
+        mods = getattr(config, "recompute_modules", None) or []
+        if isinstance(mods, str):
+            mods = [m.strip() for m in mods.split(",") if m.strip()]
+        alias = {"self_attn": "attn", "attention": "attn", "core_attn": "attn", "moe": "mlp", "experts": "mlp"}
+        self._selective = tuple(sorted({alias.get(m, m) for m in mods})) \
+            if getattr(config, "recompute_granularity", None) == "selective" else ()
 
     def forward(self, hidden, residual, ctx: BatchContext, cache=None):
         """(branch output, residual stream) in, (branch output, residual stream) out; the add happens inside the
@@ -245,8 +253,14 @@ class DecoderLayer(nn.Module):
             normed, residual = self.input_layernorm(hidden), hidden
         else:
             normed, residual = self.input_layernorm(hidden, residual)
-        attn = self.self_attn(normed, ctx, cache)
+        sel = self._selective if (self.training and cache is None) else ()
+        if "attn" in sel:       # selective recompute: keep only this sub-module's input, rebuild its internals in backward
+            attn = torch.utils.checkpoint.checkpoint(self.self_attn, normed, ctx, None, use_reentrant=False)
+        else:
+            attn = self.self_attn(normed, ctx, cache)
         normed, residual = self.post_attention_layernorm(attn, residual)
+        if "mlp" in sel:
+            return torch.utils.checkpoint.checkpoint(self.mlp, normed, use_reentrant=False), residual
         return self.mlp(normed), residual
 
 
@@ -336,6 +350,25 @@ class DecoderModel(nn.Module):
         cfg = self.config
         recompute = self.training and getattr(cfg, "recompute_granularity", None) == "full"
         skip = set(getattr(cfg, "no_recompute_layers", None) or [])
+        # recompute_method: "uniform" recomputes every layer (in chunks of recompute_num_layers, one checkpoint each);
+        # "block" recomputes only the first recompute_num_layers layers of this stage and keeps the rest
+        method = getattr(cfg, "recompute_method", None) or "uniform"
+        n_rc = int(getattr(cfg, "recompute_num_layers", 1) or 1)
+        layer_ids = list(self.layer_range)
+        if recompute and method == "block":
+            skip |= set(layer_ids[n_rc:])
+        if recompute and method == "uniform" and n_rc > 1 and caches is None:
+            for j in range(0, len(layer_ids), n_rc):
+                chunk = [self.layers[str(i)] for i in layer_ids[j:j + n_rc]]
+
+                def run_chunk(h, r, chunk=chunk):
+                    for lyr in chunk:
+                        h, r = lyr(h, r, ctx, None)
+                    return h, r
+
+                hidden, residual = torch.utils.checkpoint.checkpoint(
+                    run_chunk, hidden, residual, use_reentrant=bool(getattr(cfg, "recompute_use_reentrant", False)))
+            return hidden, residual
         for i in self.layer_range:
             layer = self.layers[str(i)]
             cache = caches[i] if caches is not None else None

@@ -338,6 +338,20 @@ class MoELayer(nn.Module):
         self.last_aux_loss = None
 
     def forward(self, x2d: torch.Tensor) -> torch.Tensor:
+        # moe_subbatch_token_num_before_dispatch > 0: route and run the experts on slices of the tokens, one after the other, which bounds
+        # the size of the permuted / exchanged buffers (paddleformers/transformers/qwen3_moe/modeling.py:447-540)
+        sub = int(getattr(self.config, "moe_subbatch_token_num_before_dispatch", 0) or 0)
+        if sub > 0 and x2d.shape[0] > sub:
+            outs, auxes = [], []
+            for piece in x2d.split(sub, dim=0):
+                outs.append(self._forward_tokens(piece))
+                if self.last_aux_loss is not None:
+                    auxes.append(self.last_aux_loss)
+            self.last_aux_loss = torch.stack(auxes).mean() if auxes else None
+            return torch.cat(outs, dim=0)
+        return self._forward_tokens(x2d)
+
+    def _forward_tokens(self, x2d: torch.Tensor) -> torch.Tensor:
         T, H = x2d.shape
         idx, w, aux = self.gate(x2d)
         if self.ep > 1:
