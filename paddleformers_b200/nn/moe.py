@@ -196,6 +196,29 @@ class GroupedExperts(nn.Module):
         for p in (self.gate_up_proj, self.down_proj):
             p.is_expert = True           # gradients are reduced over the moe_sharding group only
             p.shard_spec = ("ep", 0, None)
+        # config.fp8 = "e4m3": expert GEMMs of the forward and input-gradient passes run block-scaled fp8 on quantised
+        # weight copies that are refreshed once per optimizer step; weight gradients stay in bf16
+        self.use_fp8 = bool(getattr(config, "fp8", None)) and H % 128 == 0 and I % 128 == 0
+        self._fp8_cache = None
+
+    def refresh_fp8_weight_cache(self):
+        """Quantise the expert weights (128x128 blocks) and their per-expert transposes for the input-gradient GEMMs
+        (the cached ``fp8_weight`` / ``fp8_weight_transpose`` of paddleformers/transformers/fp8_utils.py:913-1009)."""
+        if not (self.use_fp8 and self.gate_up_proj.is_cuda):
+            self._fp8_cache = None
+            return
+        from ..quantization.fp8 import quant_weight_kernel
+
+        E, N2, H = self.gate_up_proj.shape
+        I = N2 // 2
+        with torch.no_grad():
+            gu, dn = self.gate_up_proj.detach(), self.down_proj.detach()
+            c = {}
+            c["gu_q"], c["gu_s"] = quant_weight_kernel(gu.reshape(E * N2, H))
+            c["dn_q"], c["dn_s"] = quant_weight_kernel(dn.reshape(E * H, I))
+            c["guT_q"], c["guT_s"] = quant_weight_kernel(gu.transpose(1, 2).contiguous().reshape(E * H, N2))
+            c["dnT_q"], c["dnT_s"] = quant_weight_kernel(dn.transpose(1, 2).contiguous().reshape(E * I, H))
+        self._fp8_cache = c
 
     def forward(self, rows: torch.Tensor, block_expert: torch.Tensor, counts: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None, expert_rows: Optional[torch.Tensor] = None,
@@ -204,6 +227,11 @@ class GroupedExperts(nn.Module):
         e.g. a peer-visible buffer). ``expert_rows`` int32 [E, 2] = (first row, padded rows) per expert, if already
         known; ``grad_rows_out``: buffer that receives the gradient of ``rows`` in the backward pass. Rows of blocks
         that belong to no expert are left unwritten in every output."""
+        if rows.is_cuda and rows.dtype == torch.bfloat16 and self.use_fp8:
+            if self._fp8_cache is None:
+                self.refresh_fp8_weight_cache()
+            return _GroupedMlpFp8Fn.apply(rows, self.gate_up_proj, self.down_proj, block_expert, self._fp8_cache, out,
+                                          expert_rows, grad_rows_out)
         if rows.is_cuda and rows.dtype == torch.bfloat16:
             return _GroupedMlpFn.apply(rows, self.gate_up_proj, self.down_proj, block_expert, out, expert_rows, grad_rows_out)
         out = torch.zeros_like(rows)
@@ -260,6 +288,55 @@ class _GroupedMlpFn(torch.autograd.Function):
         dw_gu = _grouped_wgrad(dgu, rows, w_gu, table)
         dw_down = _grouped_wgrad(dout, act, w_down, table)
         return drows, dw_gu, dw_down, None, None, None, None
+
+
+class _GroupedMlpFp8Fn(torch.autograd.Function):
+    """Expert MLP with block-scaled e4m3 GEMMs: activations are quantised per 1x128 block on the fly, weights come from
+    the per-step cache; the SwiGLU runs in bf16 between the two GEMMs. Backward: input gradients through fp8 GEMMs on the
+    transposed weight copies, weight gradients through the bf16 K-grouped kernel
+    (paddleformers/transformers/fp8_utils.py:913-1190, FP8GroupGemmMlpFunctionNode)."""
+
+    @staticmethod
+    def forward(ctx, rows, w_gu, w_down, block_expert, cache, out=None, expert_rows=None, grad_rows_out=None):
+        from ..quantization.fp8 import fp8_gemm, quant_act_kernel
+
+        E, N2, H = w_gu.shape
+        R = rows.shape[0]
+        xq, xs_t = quant_act_kernel(rows)
+        raw = torch.empty((R, N2), dtype=rows.dtype, device=rows.device)
+        fp8_gemm(xq, xs_t, cache["gu_q"], cache["gu_s"], block_expert, N2, out=raw)
+        act = torch.ops.pfb200.swiglu_fwd(raw)
+        aq, as_t = quant_act_kernel(act)
+        if out is None:
+            out = torch.zeros((R, H), dtype=rows.dtype, device=rows.device)
+        else:
+            ctx.mark_dirty(out)
+        fp8_gemm(aq, as_t, cache["dn_q"], cache["dn_s"], block_expert, H, out=out)
+        ctx.save_for_backward(rows, w_gu, w_down, block_expert, raw)
+        ctx.cache, ctx.expert_rows, ctx.grad_rows_out = cache, expert_rows, grad_rows_out
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from ..quantization.fp8 import fp8_gemm, quant_act_kernel
+
+        rows, w_gu, w_down, block_expert, raw = ctx.saved_tensors
+        cache = ctx.cache
+        E, N2, H = w_gu.shape
+        I = N2 // 2
+        R = rows.shape[0]
+        dout = dout.contiguous()
+        dq, ds_t = quant_act_kernel(dout)
+        dact = torch.empty((R, I), dtype=rows.dtype, device=rows.device)
+        fp8_gemm(dq, ds_t, cache["dnT_q"], cache["dnT_s"], block_expert, I, out=dact)
+        dgu, act = torch.ops.pfb200.swiglu_bwd(dact, raw, True)
+        gq, gs_t = quant_act_kernel(dgu)
+        drows = ctx.grad_rows_out if ctx.grad_rows_out is not None else torch.zeros((R, H), dtype=rows.dtype, device=rows.device)
+        fp8_gemm(gq, gs_t, cache["guT_q"], cache["guT_s"], block_expert, H, out=drows)
+        table = ctx.expert_rows if ctx.expert_rows is not None else expert_row_table(block_expert, E)
+        dw_gu = _grouped_wgrad(dgu, rows, w_gu, table)
+        dw_down = _grouped_wgrad(dout, act, w_down, table)
+        return drows, dw_gu, dw_down, None, None, None, None, None
 
 
 def _grouped_dgrad(dy, w, out, block_expert):

@@ -79,3 +79,42 @@ def test_fp8_linear_forward_backward():
     assert _rel(y, x.detach().float() @ w.t()) < 6e-2
     assert _rel(x.grad, g.float() @ w) < 6e-2
     assert _rel(lin.weight.grad, g.float().reshape(-1, 384).t() @ x.detach().float().reshape(-1, 512)) < 2e-2
+
+
+def test_fp8_grouped_experts_match_bf16_experts():
+    """Expert MLP on block-scaled fp8 GEMMs (forward and input gradients) against the bf16 grouped kernels."""
+    from paddleformers_b200.models.configuration import Qwen3MoeConfig
+    from paddleformers_b200.nn.moe import GroupedExperts
+
+    torch.manual_seed(4)
+    kw = dict(hidden_size=256, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=128, intermediate_size=128,
+              num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=2, vocab_size=64)
+    ref = GroupedExperts(Qwen3MoeConfig(**kw), dtype=torch.bfloat16, device="cuda")
+    cfg8 = Qwen3MoeConfig(**kw)
+    cfg8.fp8 = "e4m3"
+    low = GroupedExperts(cfg8, dtype=torch.bfloat16, device="cuda")
+    assert low.use_fp8 and not ref.use_fp8
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.normal_(0, 0.05)
+        low.gate_up_proj.copy_(ref.gate_up_proj)
+        low.down_proj.copy_(ref.down_proj)
+    block_expert = torch.tensor([1, 1, 0, 3, -1, 2], dtype=torch.int32, device="cuda")
+    R = block_expert.numel() * 128
+    x = torch.randn(R, 256, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(R, 256, device="cuda", dtype=torch.bfloat16)
+    g[4 * 128:5 * 128] = 0                                     # rows of the unowned block carry no gradient
+    outs = []
+    for mod in (ref, low):
+        xi = x.clone().requires_grad_(True)
+        y = mod(xi, block_expert)
+        y.backward(g)
+        outs.append((y.detach(), xi.grad.detach(), mod.gate_up_proj.grad.detach().clone(), mod.down_proj.grad.detach().clone()))
+    live = torch.cat([torch.arange(b * 128, (b + 1) * 128) for b, e in enumerate(block_expert.tolist()) if e >= 0]).cuda()
+    for name, a, b in zip(("y", "dx"), outs[1][:2], outs[0][:2]):
+        assert _rel(a[live], b[live]) < 8e-2, name
+    for name, a, b in zip(("dw_gate_up", "dw_down"), outs[1][2:], outs[0][2:]):
+        assert _rel(a, b) < 8e-2, name
+    from paddleformers_b200.ops import functional as F
+
+    F.check_kernel_status()
