@@ -166,6 +166,13 @@ def load_checkpoint(trainer, path: str) -> None:
         trainer.state = loaded
     with open(os.path.join(path, "scheduler.json")) as f:
         trainer.lr_scheduler.load_state_dict(json.load(f))
+    ema_file = os.path.join(path, f"ema_state_{rank}.pt")
+    if os.path.exists(ema_file):
+        from .ema import EMACallback
+
+        for cb in trainer.callback_handler.callbacks:
+            if isinstance(cb, EMACallback):
+                cb.load_state_dict(torch.load(ema_file, map_location="cpu", weights_only=False))
     rng_file = os.path.join(path, f"rng_state_{rank}.pt")
     if os.path.exists(rng_file):
         _set_rng_state(torch.load(rng_file, weights_only=False))

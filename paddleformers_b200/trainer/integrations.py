@@ -159,6 +159,10 @@ def callbacks_from_args(args) -> List[TrainerCallback]:
             out.append(VisualDLCallback())
         else:
             raise ValueError(f"report_to: unknown logger {n!r} (tensorboard, visualdl, jsonl, none)")
+    if float(getattr(args, "ema_decay", 0.0) or 0.0) > 0:
+        from .ema import EMACallback
+
+        out.append(EMACallback(float(args.ema_decay), int(getattr(args, "ema_start_step", 0) or 0)))
     if getattr(args, "enable_timer", False):
         out.append(TimerCallback())
     if getattr(args, "log_memory", False):

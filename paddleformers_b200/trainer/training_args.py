@@ -82,6 +82,8 @@ class TrainingArguments:
     logging_dir: Optional[str] = None  # scalar logs (default <output_dir>/runs)
     enable_zero_cost_checkpoint: bool = False   # snapshot the optimizer shard on a side stream, persist in the background
     zcc_save_model_weights: bool = False        # also export HF weights at every save (collective and synchronous)
+    ema_decay: float = 0.0                      # > 0: keep an exponential moving average of the fp32 master shards
+    ema_start_step: int = 0
     enable_timer: bool = False         # per-step read-data / forward-backward / optimizer-step timers in the log record
     log_memory: bool = False           # device memory high-water marks in the log record
     metrics_output_path: Optional[str] = None

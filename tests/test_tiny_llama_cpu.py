@@ -120,3 +120,23 @@ def test_zero_cost_checkpoint_resume_matches_uninterrupted_run(tmp_path):
     got = [h["loss"] for h in second.state.log_history if "loss" in h]
     assert second.state.global_step == 10
     assert all(abs(a - b) < 1e-5 for a, b in zip(ref[5:], got[-5:])), (ref[5:], got[-5:])
+
+
+def test_ema_tracks_master_weights_and_exports(tmp_path):
+    from paddleformers_b200.trainer.ema import EMACallback, export_ema_weights
+
+    model, tr = _make(tmp_path, 6, ema_decay=0.5, save_strategy="no")
+    ema = next(cb for cb in tr.callback_handler.callbacks if isinstance(cb, EMACallback))
+    tr.train()
+    assert ema.num_updates == 6
+    dom = tr.optimizer.domains[0]
+    shadow = ema.shadow[dom.name]
+    # the average lags the live weights but stays between them and the initial weights
+    assert not torch.equal(shadow, dom.master) and (shadow - dom.master).abs().max() < 1e-2
+    live = {k: v.clone() for k, v in model.state_dict().items()}
+    out = export_ema_weights(tr, ema, str(tmp_path / "ema"))
+    for k, v in model.state_dict().items():          # the live weights are restored after the export
+        assert torch.equal(v, live[k]), k
+    m2 = AutoModelForCausalLM.from_pretrained(out)
+    diffs = [(m2.state_dict()[k].float() - live[k].float()).abs().max().item() for k in live]
+    assert max(diffs) > 0 and max(diffs) < 1e-2
