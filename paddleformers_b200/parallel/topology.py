@@ -110,7 +110,10 @@ class ParallelState:
     AXES = ("dp", "sharding", "pp", "sep", "cp", "mp")
 
     def __init__(self, degrees: Optional[ParallelDegrees] = None, rank: Optional[int] = None, backend: Optional[str] = None,
-                 create_groups: bool = True):
+                 create_groups: bool = True, nccl_config=None):
+        from .nccl_config import load_nccl_config
+
+        self.nccl_config = load_nccl_config(nccl_config)
         self.degrees = degrees or ParallelDegrees()
         d = self.degrees
         self.world_size = d.world
@@ -150,7 +153,12 @@ class ParallelState:
             for ranks in groups:
                 g = None
                 if make and len(ranks) > 1:
-                    g = dist.new_group(ranks=ranks, backend=backend)
+                    from .nccl_config import make_pg_options
+
+                    eff = backend or ("nccl" if torch.cuda.is_available() else "gloo")
+                    opts = make_pg_options(self.nccl_config, name, eff)
+                    g = dist.new_group(ranks=ranks, backend=backend, pg_options=opts) if opts is not None else \
+                        dist.new_group(ranks=ranks, backend=backend)
                 if self.global_rank in ranks:
                     mine = ranks
                     self.groups[name] = g if g is not None else _SingleGroup()
@@ -255,10 +263,10 @@ def init_distributed(backend: Optional[str] = None, timeout_s: Optional[int] = N
     dist.init_process_group(backend=backend, **kw)
 
 
-def initialize_parallel(degrees: ParallelDegrees, backend: Optional[str] = None) -> ParallelState:
+def initialize_parallel(degrees: ParallelDegrees, backend: Optional[str] = None, nccl_config=None) -> ParallelState:
     init_distributed(backend)
     world = dist.get_world_size() if dist.is_initialized() else 1
     assert degrees.world == world, f"parallel degrees {degrees} need {degrees.world} ranks, job has {world}"
-    state = ParallelState(degrees, backend=backend)
+    state = ParallelState(degrees, backend=backend, nccl_config=nccl_config)
     set_parallel_state(state)
     return state

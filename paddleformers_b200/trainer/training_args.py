@@ -82,6 +82,7 @@ class TrainingArguments:
     logging_dir: Optional[str] = None  # scalar logs (default <output_dir>/runs)
     enable_zero_cost_checkpoint: bool = False   # snapshot the optimizer shard on a side stream, persist in the background
     zcc_save_model_weights: bool = False        # also export HF weights at every save (collective and synchronous)
+    nccl_comm_group_config: Optional[str] = None   # JSON file / string: per-group NCCL communicator options
     ema_decay: float = 0.0                      # > 0: keep an exponential moving average of the fp32 master shards
     ema_start_step: int = 0
     enable_timer: bool = False         # per-step read-data / forward-backward / optimizer-step timers in the log record
@@ -170,7 +171,8 @@ class TrainingArguments:
             if self.world_size > 1:
                 if self.pg_timeout_s:
                     os.environ.setdefault("PFB_PG_TIMEOUT", str(self.pg_timeout_s))
-                self._state = initialize_parallel(self.degrees, backend=self.distributed_backend)
+                self._state = initialize_parallel(self.degrees, backend=self.distributed_backend,
+                                                   nccl_config=getattr(self, "nccl_comm_group_config", None))
             else:
                 from ..parallel.topology import set_parallel_state
 

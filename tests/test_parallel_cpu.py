@@ -200,3 +200,21 @@ def test_zero_bubble_schedule_shortens_the_pipeline(P, M):
     assert zb["makespan"] == 3 * M + 2 * (P - 1)
     assert zb["peak_live"] == base["peak_live"] == list(range(P, 0, -1))
     assert zb["bubble_fraction"] < base["bubble_fraction"]
+
+
+def test_nccl_group_config_parsing_and_options():
+    import torch.distributed as dist
+
+    from paddleformers_b200.parallel.nccl_config import group_options, load_nccl_config, make_pg_options
+
+    cfg = load_nccl_config('{"default": {"cga_cluster_size": 2}, "mp": {"high_priority": true, "max_ctas": 16}}')
+    assert group_options(cfg, "mp") == {"cga_cluster_size": 2, "high_priority": True, "max_ctas": 16}
+    assert group_options(cfg, "pp") == {"cga_cluster_size": 2}
+    assert make_pg_options(cfg, "mp", "gloo") is None and make_pg_options({}, "mp", "nccl") is None
+    if hasattr(dist, "ProcessGroupNCCL"):
+        o = make_pg_options(cfg, "mp", "nccl")
+        assert o.is_high_priority_stream and o.config.max_ctas == 16 and o.config.cga_cluster_size == 2
+    with pytest.raises(ValueError, match="unknown option"):
+        load_nccl_config({"mp": {"ctas": 3}})
+    with pytest.raises(ValueError, match="unknown group"):
+        load_nccl_config({"tp": {"max_ctas": 3}})
