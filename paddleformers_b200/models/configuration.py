@@ -214,7 +214,56 @@ class InternLM3Config(DecoderConfig):
         self.qkv_bias = qkv_bias
 
 
-CONFIG_MAPPING = {c.model_type: c for c in (LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
+class Ernie4_5Config(DecoderConfig):
+    """ERNIE-4.5 dense: Llama blocks with tied embeddings whose checkpoints store q / k rows in the interleaved rotary
+    order; the weight map permutes them to the half-split order on load and back on save
+    (paddleformers/transformers/ernie4_5)."""
+
+    model_type = "ernie4_5"
+
+    def __init__(self, use_bias=False, **kw):
+        kw.setdefault("rms_norm_eps", 1e-5)
+        kw.setdefault("rope_theta", 500000.0)
+        kw.setdefault("tie_word_embeddings", True)
+        kw.setdefault("attention_bias", bool(use_bias))
+        kw.setdefault("mlp_bias", bool(use_bias))
+        super().__init__(**kw)
+        self.use_bias = use_bias
+        self.rope_interleaved_checkpoint = True
+
+
+class Ernie4_5MoeConfig(Ernie4_5Config):
+    """ERNIE-4.5 MoE (text): softmax router whose top-k selection adds a correction bias (``moe_statics``), weights
+    renormalised over the selected experts, shared experts next to the routed ones, dense layers before
+    ``moe_layer_start_index`` (paddleformers/transformers/ernie4_5_moe). The Hugging Face field names are accepted and
+    translated."""
+
+    model_type = "ernie4_5_moe"
+
+    def __init__(self, moe_num_experts=None, moe_k=None, moe_num_shared_experts=None, moe_layer_start_index=None,
+                 moe_layer_interval=None, moe_use_aux_free=True, moe_norm_min=1e-12, **kw):
+        if moe_num_experts is not None:
+            kw.setdefault("num_experts", int(moe_num_experts))
+        if moe_k is not None:
+            kw.setdefault("num_experts_per_tok", int(moe_k))
+        if moe_num_shared_experts is not None:
+            kw.setdefault("n_shared_experts", int(moe_num_shared_experts))
+        if moe_layer_start_index is not None:
+            kw.setdefault("first_k_dense_replace", int(moe_layer_start_index))
+        if moe_layer_interval is not None:
+            kw.setdefault("decoder_sparse_step", int(moe_layer_interval))
+        kw.setdefault("scoring_func", "softmax")
+        kw.setdefault("topk_method", "noaux_tc" if moe_use_aux_free else "greedy")
+        kw.setdefault("norm_topk_prob", True)
+        kw.setdefault("router_aux_loss_coef", 1e-3)
+        super().__init__(**kw)
+        self.moe_num_experts, self.moe_k = self.num_experts, self.num_experts_per_tok
+        self.moe_num_shared_experts, self.moe_layer_start_index = self.n_shared_experts, self.first_k_dense_replace
+        self.moe_layer_interval, self.moe_use_aux_free, self.moe_norm_min = self.decoder_sparse_step, moe_use_aux_free, moe_norm_min
+        self.router_bias_name = "mlp.moe_statics.e_score_correction_bias"
+
+
+CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
                                             Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config)}
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
@@ -228,7 +277,6 @@ UNSUPPORTED_FAMILIES = {
     "qwen3_5_moe": "gated delta-net linear attention hybrid", "qwen2_moe": "sigmoid-gated shared expert",
     "hunyuan_v1_dense": "QK norm applied after the rotary embedding", "hunyuan_v1_moe": "QK norm after rotary, shared-expert mixing",
     "gemma3": "(1 + w) RMSNorm, GeGLU, sliding/global layer pattern", "gemma3_text": "(1 + w) RMSNorm, GeGLU, sliding/global layer pattern",
-    "ernie4_5": "interleaved (GPT-J style) rotary embedding layout", "ernie4_5_moe": "interleaved rotary layout, modality-aware experts",
     "granite": "embedding / residual / attention / logit multipliers", "phi4_multimodal": "vision and audio towers",
     "olmo2": "post-norm blocks with QK norm over the full projection", "cohere": "LayerNorm, parallel attention + MLP block",
     "cohere2": "LayerNorm, parallel block, sliding-window layers", "stablelm": "LayerNorm with bias, partial rotary with per-head norm",

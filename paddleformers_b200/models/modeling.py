@@ -29,7 +29,7 @@ from ..parallel.topology import get_parallel_state
 from ..transformers.conversion_utils import Rule, WeightMap, expand_layers
 from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
-                            Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig)
+                            Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig)
 
 
 @dataclass
@@ -551,6 +551,8 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
     rules: List[Rule] = []
     per_layer: List[Rule] = []
     qkv_sizes = None
+    # checkpoints trained with interleaved rotary pairs: q and k rows (sources 0 and 1) are permuted per head on load
+    rope_perm = {0: config.head_dim, 1: config.head_dim} if getattr(config, "rope_interleaved_checkpoint", False) else None
     if config.is_mla:
         pass  # MLA projections keep their HF names
     else:
@@ -560,10 +562,12 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
             per_layer.append(Rule(L + "self_attn.qkv_proj.weight", [L + "self_attn.qkv_proj.weight"]))
         else:
             per_layer.append(Rule(L + "self_attn.qkv_proj.weight", [L + "self_attn.q_proj.weight", L + "self_attn.k_proj.weight",
-                                                                     L + "self_attn.v_proj.weight"], "concat", 0, sizes=qkv_sizes))
+                                                                     L + "self_attn.v_proj.weight"], "concat", 0, sizes=qkv_sizes,
+                                  rope_deinterleave=rope_perm))
         if config.attention_bias and not getattr(config, "hf_fused_qkv", False):
             per_layer.append(Rule(L + "self_attn.qkv_proj.bias", [L + "self_attn.q_proj.bias", L + "self_attn.k_proj.bias",
-                                                                   L + "self_attn.v_proj.bias"], "concat", 0, sizes=qkv_sizes))
+                                                                   L + "self_attn.v_proj.bias"], "concat", 0, sizes=qkv_sizes,
+                                  rope_deinterleave=rope_perm))
     if getattr(config, "hf_fused_gate_up", False):  # [gate; up] rows already stacked in the checkpoint
         dense_rule = Rule(L + "mlp.gate_up_proj.weight", [L + "mlp.gate_up_proj.weight"])
     else:
@@ -577,6 +581,9 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
             rules.append(Rule(pre + "experts.gate_up_proj", [pre + "experts.{E}.gate_proj.weight", pre + "experts.{E}.up_proj.weight"],
                               "stack_concat", 0, E, 2))
             rules.append(Rule(pre + "experts.down_proj", [pre + "experts.{E}.down_proj.weight"], "stack", 0, E))
+            if getattr(config, "router_bias_name", None) and config.topk_method == "noaux_tc":
+                # stored outside the gate module and with a leading unit dimension
+                rules.append(Rule(pre + "gate.e_score_correction_bias", [f"model.layers.{i}." + config.router_bias_name], flatten=True))
             if config.n_shared_experts:
                 rules.append(Rule(pre + "shared_experts.gate_up_proj.weight",
                                   [pre + "shared_experts.gate_proj.weight", pre + "shared_experts.up_proj.weight"], "concat", 0))
@@ -638,10 +645,12 @@ MistralForCausalLM = _family("MistralForCausalLM", MistralConfig)
 Phi3ForCausalLM = _family("Phi3ForCausalLM", Phi3Config)
 SeedOssForCausalLM = _family("SeedOssForCausalLM", SeedOssConfig)
 InternLM3ForCausalLM = _family("InternLM3ForCausalLM", InternLM3Config)
+Ernie4_5ForCausalLM = _family("Ernie4_5ForCausalLM", Ernie4_5Config)
+Ernie4_5MoeForCausalLM = _family("Ernie4_5MoeForCausalLM", Ernie4_5MoeConfig)
 
 MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
-    "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
+    "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,
 }

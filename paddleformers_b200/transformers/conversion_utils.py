@@ -57,6 +57,23 @@ class ShardSpec:
         return torch.cat(out, dim=self.tp_dim)
 
 
+def deinterleave_rope_rows(t: torch.Tensor, head_dim: int) -> torch.Tensor:
+    """Reorder the rows of a q / k projection (or bias) from the interleaved rotary layout, where the pair rotated
+    together sits at rows (2i, 2i + 1) of each head, to the half-split layout (i, i + head_dim / 2) that the rotary
+    kernels use. Attention scores are invariant under a common permutation of q and k features, so a checkpoint
+    trained with interleaved rotation computes the same function after this permutation with half-split rotation."""
+    nh = t.shape[0] // head_dim
+    rest = t.shape[1:]
+    return t.reshape(nh, head_dim // 2, 2, *rest).transpose(1, 2).reshape(t.shape)
+
+
+def interleave_rope_rows(t: torch.Tensor, head_dim: int) -> torch.Tensor:
+    """Inverse of ``deinterleave_rope_rows``."""
+    nh = t.shape[0] // head_dim
+    rest = t.shape[1:]
+    return t.reshape(nh, 2, head_dim // 2, *rest).transpose(1, 2).reshape(t.shape)
+
+
 @dataclass
 class Rule:
     """target <- op(sources). ``sources`` may contain ``{E}`` (expanded over experts for stack rules)."""
@@ -68,6 +85,18 @@ class Rule:
     num_experts: int = 0
     expert_pairs: int = 1  # stack_concat: sources per expert (gate, up)
     sizes: Optional[List[int]] = None  # concat: size of each source along ``dim`` (default: equal parts)
+    rope_deinterleave: Optional[Dict[int, int]] = None  # source index -> head_dim: rows stored in interleaved rotary order
+    flatten: bool = False              # rename: the checkpoint stores the tensor with a leading unit dimension
+
+    def _load(self, i: int, t: torch.Tensor) -> torch.Tensor:
+        if self.rope_deinterleave and i in self.rope_deinterleave:
+            t = deinterleave_rope_rows(t, self.rope_deinterleave[i])
+        return t
+
+    def _store(self, i: int, t: torch.Tensor) -> torch.Tensor:
+        if self.rope_deinterleave and i in self.rope_deinterleave:
+            t = interleave_rope_rows(t, self.rope_deinterleave[i])
+        return t
 
     def source_names(self) -> List[str]:
         if self.op in ("stack", "stack_concat"):
@@ -76,9 +105,10 @@ class Rule:
 
     def forward(self, get: Callable[[str], torch.Tensor], expert_range: Optional[range] = None) -> torch.Tensor:
         if self.op == "rename":
-            return get(self.sources[0])
+            t = self._load(0, get(self.sources[0]))
+            return t.reshape(-1) if self.flatten else t
         if self.op == "concat":
-            return torch.cat([get(s) for s in self.sources], dim=self.dim)
+            return torch.cat([self._load(i, get(s)) for i, s in enumerate(self.sources)], dim=self.dim)
         er = expert_range if expert_range is not None else range(self.num_experts)
         if self.op == "stack":
             return torch.stack([get(self.sources[0].format(E=e)) for e in er], dim=0)
@@ -88,10 +118,12 @@ class Rule:
 
     def inverse(self, tensor: torch.Tensor, section_sizes: Optional[List[int]] = None, expert_offset: int = 0) -> Dict[str, torch.Tensor]:
         if self.op == "rename":
-            return {self.sources[0]: tensor}
+            t = self._store(0, tensor)
+            return {self.sources[0]: t.reshape(1, -1) if self.flatten else t}
         if self.op == "concat":
             sizes = section_sizes or self.sizes or [tensor.shape[self.dim] // len(self.sources)] * len(self.sources)
-            return {s: p.contiguous() for s, p in zip(self.sources, torch.split(tensor, sizes, dim=self.dim))}
+            return {s: self._store(i, p).contiguous()
+                    for i, (s, p) in enumerate(zip(self.sources, torch.split(tensor, sizes, dim=self.dim)))}
         out = {}
         for i in range(tensor.shape[0]):
             e = expert_offset + i
@@ -125,5 +157,5 @@ def expand_layers(template_rules: List[Rule], layer_ids: Iterable[int]) -> List[
     for i in layer_ids:
         for r in template_rules:
             out.append(Rule(r.target.replace("{L}", str(i)), [s.replace("{L}", str(i)) for s in r.sources], r.op, r.dim,
-                            r.num_experts, r.expert_pairs, r.sizes))
+                            r.num_experts, r.expert_pairs, r.sizes, r.rope_deinterleave, r.flatten))
     return out

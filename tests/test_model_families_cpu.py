@@ -102,3 +102,66 @@ def test_moe_subbatching_matches_single_pass():
     assert loss0 == pytest.approx(loss1, rel=1e-5)
     for k in g0:
         torch.testing.assert_close(g0[k], g1[k], rtol=1e-4, atol=1e-6)
+
+
+def _interleaved_rope(x, pos, theta):
+    """Rotary embedding on adjacent pairs (2i, 2i + 1) of the last dim; x: [S, heads, D]."""
+    D = x.shape[-1]
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2).float() / D))
+    ang = pos[:, None].float() * inv[None]                       # [S, D/2]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    x1, x2 = x[..., 0::2], x[..., 1::2]
+    return torch.stack([x1 * cos - x2 * sin, x1 * sin + x2 * cos], dim=-1).flatten(-2)
+
+
+def test_ernie_rope_row_permutation_preserves_attention_scores():
+    """Interleaved rotation with the checkpoint's rows == half-split rotation with the permuted rows."""
+    from paddleformers_b200.ops import functional as F
+    from paddleformers_b200.transformers.conversion_utils import deinterleave_rope_rows, interleave_rope_rows
+
+    torch.manual_seed(0)
+    S, H, nh, D, theta = 12, 32, 2, 16, 10000.0
+    x = torch.randn(S, H)
+    wq, wk = torch.randn(nh * D, H), torch.randn(nh * D, H)
+    pos = torch.arange(S)
+    q = _interleaved_rope((x @ wq.t()).view(S, nh, D), pos, theta)
+    k = _interleaved_rope((x @ wk.t()).view(S, nh, D), pos, theta)
+    ref = torch.einsum("shd,thd->hst", q, k)
+    wq2, wk2 = deinterleave_rope_rows(wq, D), deinterleave_rope_rows(wk, D)
+    assert torch.equal(interleave_rope_rows(wq2, D), wq)
+    cos, sin = F.rope_tables(S, D, theta, x.device)
+    q2 = F.rope_heads((x @ wq2.t()).contiguous(), cos, sin, pos, nh, D).view(S, nh, D)
+    k2 = F.rope_heads((x @ wk2.t()).contiguous(), cos, sin, pos, nh, D).view(S, nh, D)
+    got = torch.einsum("shd,thd->hst", q2, k2)
+    torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-4)
+
+
+def test_ernie45_moe_config_translation_and_checkpoint_names(tmp_path):
+    cfg = AutoConfig.for_model("ernie4_5_moe", vocab_size=96, hidden_size=32, intermediate_size=48, num_hidden_layers=3,
+                               num_attention_heads=4, num_key_value_heads=2, head_dim=8, moe_num_experts=4, moe_k=2,
+                               moe_num_shared_experts=1, moe_layer_start_index=1, moe_intermediate_size=16)
+    assert (cfg.num_experts, cfg.num_experts_per_tok, cfg.n_shared_experts, cfg.first_k_dense_replace) == (4, 2, 1, 1)
+    assert cfg.topk_method == "noaux_tc" and cfg.scoring_func == "softmax" and cfg.tie_word_embeddings
+    assert not cfg.is_moe_layer(0) and cfg.is_moe_layer(1)
+    torch.manual_seed(0)
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32)
+    with torch.no_grad():
+        model.model.layers["1"].mlp.gate.e_score_correction_bias.copy_(torch.tensor([0.1, -0.2, 0.3, 0.0]))
+    model.save_pretrained(str(tmp_path))
+    names = _hf_names(str(tmp_path))
+    assert "model.layers.1.mlp.moe_statics.e_score_correction_bias" in names
+    assert "model.layers.1.mlp.experts.3.down_proj.weight" in names and "model.layers.1.mlp.shared_experts.up_proj.weight" in names
+    assert "model.layers.0.mlp.gate_proj.weight" in names and "lm_head.weight" not in names
+    from safetensors import safe_open
+
+    with safe_open(str(tmp_path / "model.safetensors"), "pt") as sf:
+        assert tuple(sf.get_tensor("model.layers.1.mlp.moe_statics.e_score_correction_bias").shape) == (1, 4)
+        q_saved = sf.get_tensor("model.layers.0.self_attn.q_proj.weight")
+    # saved rows are in the interleaved order: permuting them back gives the internal q section
+    from paddleformers_b200.transformers.conversion_utils import deinterleave_rope_rows
+
+    internal_q = model.model.layers["0"].self_attn.qkv_proj.weight[:32].detach()
+    torch.testing.assert_close(deinterleave_rope_rows(q_saved, 8), internal_q, rtol=0, atol=0)
+    again = AutoModelForCausalLM.from_pretrained(str(tmp_path), dtype=torch.float32)
+    ids = torch.randint(0, 96, (2, 16))
+    torch.testing.assert_close(model(ids, return_logits=True).logits, again(ids, return_logits=True).logits, rtol=0, atol=0)
