@@ -214,6 +214,39 @@ class InternLM3Config(DecoderConfig):
         self.qkv_bias = qkv_bias
 
 
+class Qwen2MoeConfig(DecoderConfig):
+    """Qwen2-MoE / Qwen1.5-MoE: softmax router without renormalisation, one wide shared expert whose output is gated per
+    token by a sigmoid (paddleformers/transformers/qwen2_moe)."""
+
+    model_type = "qwen2_moe"
+
+    def __init__(self, **kw):
+        kw.setdefault("attention_bias", True)
+        kw.setdefault("num_experts", 60)
+        kw.setdefault("num_experts_per_tok", 4)
+        kw.setdefault("moe_intermediate_size", 1408)
+        kw.setdefault("shared_expert_intermediate_size", 5632)
+        kw.setdefault("n_shared_experts", 1)
+        kw.setdefault("norm_topk_prob", False)
+        kw.setdefault("router_aux_loss_coef", 1e-3)
+        super().__init__(**kw)
+        self.shared_expert_gate = True
+        self.shared_expert_hf_name = "shared_expert"
+
+
+class GraniteConfig(DecoderConfig):
+    """Granite 3: Llama blocks with four scalar multipliers - on the embeddings, on every residual branch, as the
+    attention softmax scale, and as a divisor of the logits (paddleformers/transformers/granite)."""
+
+    model_type = "granite"
+
+    def __init__(self, embedding_multiplier=1.0, residual_multiplier=1.0, attention_multiplier=None, logits_scaling=1.0, **kw):
+        super().__init__(**kw)
+        self.embedding_multiplier, self.residual_multiplier = float(embedding_multiplier), float(residual_multiplier)
+        self.attention_multiplier = attention_multiplier
+        self.logits_scaling = float(logits_scaling)
+
+
 class Ernie4_5Config(DecoderConfig):
     """ERNIE-4.5 dense: Llama blocks with tied embeddings whose checkpoints store q / k rows in the interleaved rotary
     order; the weight map permutes them to the half-split order on load and back on save
@@ -263,7 +296,7 @@ class Ernie4_5MoeConfig(Ernie4_5Config):
         self.router_bias_name = "mlp.moe_statics.e_score_correction_bias"
 
 
-CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
+CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
                                             Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config)}
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
@@ -274,10 +307,10 @@ UNSUPPORTED_FAMILIES = {
     "glm_moe_dsa": "sparse (indexer) attention", "kimi_k2": "DeepSeek-V3 blocks with a different tokenizer / config schema",
     "minimax": "lightning (linear) attention hybrid", "minimax_m2": "per-layer QK norm over the full projection",
     "qwen3_next": "gated delta-net linear attention hybrid", "qwen3_5": "gated delta-net linear attention hybrid",
-    "qwen3_5_moe": "gated delta-net linear attention hybrid", "qwen2_moe": "sigmoid-gated shared expert",
+    "qwen3_5_moe": "gated delta-net linear attention hybrid",
     "hunyuan_v1_dense": "QK norm applied after the rotary embedding", "hunyuan_v1_moe": "QK norm after rotary, shared-expert mixing",
     "gemma3": "(1 + w) RMSNorm, GeGLU, sliding/global layer pattern", "gemma3_text": "(1 + w) RMSNorm, GeGLU, sliding/global layer pattern",
-    "granite": "embedding / residual / attention / logit multipliers", "phi4_multimodal": "vision and audio towers",
+    "phi4_multimodal": "vision and audio towers",
     "olmo2": "post-norm blocks with QK norm over the full projection", "cohere": "LayerNorm, parallel attention + MLP block",
     "cohere2": "LayerNorm, parallel block, sliding-window layers", "stablelm": "LayerNorm with bias, partial rotary with per-head norm",
     "internlm2": "interleaved fused wqkv layout", "minicpm": "depth / embedding scaling factors", "minicpm3": "MLA with scaling factors",

@@ -29,7 +29,8 @@ from ..parallel.topology import get_parallel_state
 from ..transformers.conversion_utils import Rule, WeightMap, expand_layers
 from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
-                            Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig)
+                            Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig,
+                            GraniteConfig, Qwen2MoeConfig)
 
 
 @dataclass
@@ -139,7 +140,7 @@ class Attention(nn.Module):
         if self.use_qk_norm:
             self.q_norm = RMSNorm(self.D, config.rms_norm_eps, dtype=dtype, device=device)
             self.k_norm = RMSNorm(self.D, config.rms_norm_eps, dtype=dtype, device=device)
-        self.scale = 1.0 / math.sqrt(self.D)
+        self.scale = float(getattr(config, "attention_multiplier", None) or 1.0 / math.sqrt(self.D))
 
     def forward(self, x2d: torch.Tensor, ctx: BatchContext, cache=None) -> torch.Tensor:
         qkv = _apply(self.qkv_proj, x2d)
@@ -245,6 +246,7 @@ class DecoderLayer(nn.Module):
         alias = {"self_attn": "attn", "attention": "attn", "core_attn": "attn", "moe": "mlp", "experts": "mlp"}
         self._selective = tuple(sorted({alias.get(m, m) for m in mods})) \
             if getattr(config, "recompute_granularity", None) == "selective" else ()
+        self.residual_multiplier = float(getattr(config, "residual_multiplier", 1.0) or 1.0)
 
     def forward(self, hidden, residual, ctx: BatchContext, cache=None):
         """(branch output, residual stream) in, (branch output, residual stream) out; the add happens inside the
@@ -258,10 +260,13 @@ class DecoderLayer(nn.Module):
             attn = torch.utils.checkpoint.checkpoint(self.self_attn, normed, ctx, None, use_reentrant=False)
         else:
             attn = self.self_attn(normed, ctx, cache)
+        if self.residual_multiplier != 1.0:      # the residual add happens inside the next norm: scale the branch first
+            attn = attn * self.residual_multiplier
         normed, residual = self.post_attention_layernorm(attn, residual)
-        if "mlp" in sel:
-            return torch.utils.checkpoint.checkpoint(self.mlp, normed, use_reentrant=False), residual
-        return self.mlp(normed), residual
+        out = torch.utils.checkpoint.checkpoint(self.mlp, normed, use_reentrant=False) if "mlp" in sel else self.mlp(normed)
+        if self.residual_multiplier != 1.0:
+            out = out * self.residual_multiplier
+        return out, residual
 
 
 class MTPLayer(nn.Module):
@@ -340,11 +345,13 @@ class DecoderModel(nn.Module):
         return BatchContext(B, S, pos, kend, cos, sin, cp_positions if S_full else None, S_full, kend_full if S_full else None)
 
     def embed(self, input_ids):
+        mult = float(getattr(self.config, "embedding_multiplier", 1.0) or 1.0)
         if isinstance(self.embed_tokens, VocabParallelEmbedding):
             h = self.embed_tokens(input_ids)
-            return h if h.dim() == 2 else h.reshape(-1, h.shape[-1])
-        h = F.embedding(input_ids, self.embed_tokens.weight).reshape(-1, self.config.hidden_size)
-        return h
+            h = h if h.dim() == 2 else h.reshape(-1, h.shape[-1])
+        else:
+            h = F.embedding(input_ids, self.embed_tokens.weight).reshape(-1, self.config.hidden_size)
+        return h * mult if mult != 1.0 else h
 
     def run_layers(self, hidden, residual, ctx, caches=None):
         cfg = self.config
@@ -468,6 +475,9 @@ class DecoderForCausalLM(PretrainedModel):
         if kend_full is not None:
             kend_full = kend_full.reshape(input_ids.shape[0], -1)
         hidden, ctx = self.model(input_ids, position_ids, kend, caches, None, cp_global_positions, cp_full_seq_len, kend_full)
+        logits_scaling = float(getattr(self.config, "logits_scaling", 1.0) or 1.0)
+        if logits_scaling != 1.0:        # logits / s == head(hidden / s)
+            hidden = hidden / logits_scaling
         out = CausalLMOutput()
         want_logits = return_logits if return_logits is not None else labels is None
         if want_logits:
@@ -585,8 +595,11 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
                 # stored outside the gate module and with a leading unit dimension
                 rules.append(Rule(pre + "gate.e_score_correction_bias", [f"model.layers.{i}." + config.router_bias_name], flatten=True))
             if config.n_shared_experts:
+                sh = getattr(config, "shared_expert_hf_name", "shared_experts")
+                if sh != "shared_experts":
+                    rules.append(Rule(pre + "shared_experts.down_proj.weight", [pre + sh + ".down_proj.weight"]))
                 rules.append(Rule(pre + "shared_experts.gate_up_proj.weight",
-                                  [pre + "shared_experts.gate_proj.weight", pre + "shared_experts.up_proj.weight"], "concat", 0))
+                                  [pre + sh + ".gate_proj.weight", pre + sh + ".up_proj.weight"], "concat", 0))
         else:
             rules.extend(expand_layers([dense_rule], [i]))
     # MTP layers are stored by HF DeepSeek-V3 / GLM-4.5 as extra entries of model.layers
@@ -647,10 +660,12 @@ SeedOssForCausalLM = _family("SeedOssForCausalLM", SeedOssConfig)
 InternLM3ForCausalLM = _family("InternLM3ForCausalLM", InternLM3Config)
 Ernie4_5ForCausalLM = _family("Ernie4_5ForCausalLM", Ernie4_5Config)
 Ernie4_5MoeForCausalLM = _family("Ernie4_5MoeForCausalLM", Ernie4_5MoeConfig)
+Qwen2MoeForCausalLM = _family("Qwen2MoeForCausalLM", Qwen2MoeConfig)
+GraniteForCausalLM = _family("GraniteForCausalLM", GraniteConfig)
 
 MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
-    "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
+    "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,
 }

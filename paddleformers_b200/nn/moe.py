@@ -411,6 +411,10 @@ class MoELayer(nn.Module):
         if config.n_shared_experts:
             si = config.shared_expert_intermediate_size or config.moe_intermediate_size * config.n_shared_experts
             self.shared_experts = DenseMLP(config.hidden_size, si, config, tp=False, dtype=dtype, device=device)
+        # Qwen2-MoE: the shared expert's output is scaled per token by sigmoid(linear(x))
+        self.shared_expert_gate = None
+        if config.n_shared_experts and getattr(config, "shared_expert_gate", False):
+            self.shared_expert_gate = nn.Linear(config.hidden_size, 1, bias=False, dtype=dtype, device=device)
         self.ep = get_parallel_state().degrees.ep
         self.last_aux_loss = None
 
@@ -441,7 +445,10 @@ class MoELayer(nn.Module):
             yr = self.experts(xr, block_expert, counts)
             y = unpermute_combine(yr, dest, w, T)
         if self.shared_experts is not None:
-            y = y + self.shared_experts(x2d)
+            shared = self.shared_experts(x2d)
+            if self.shared_expert_gate is not None:
+                shared = shared * torch.sigmoid(TF.linear(x2d, self.shared_expert_gate.weight)).to(shared.dtype)
+            y = y + shared
         self.last_aux_loss = aux.detach() if aux is not None else None
         if aux is not None:
             y = AddAuxiliaryLoss.apply(y, aux)

@@ -165,3 +165,60 @@ def test_ernie45_moe_config_translation_and_checkpoint_names(tmp_path):
     again = AutoModelForCausalLM.from_pretrained(str(tmp_path), dtype=torch.float32)
     ids = torch.randint(0, 96, (2, 16))
     torch.testing.assert_close(model(ids, return_logits=True).logits, again(ids, return_logits=True).logits, rtol=0, atol=0)
+
+
+def test_granite_multipliers():
+    kw = {**TINY, "num_hidden_layers": 1, "tie_word_embeddings": False}
+    torch.manual_seed(1)
+    base = AutoModelForCausalLM.from_config(AutoConfig.for_model("granite", **kw), dtype=torch.float32).eval()
+    ids = torch.randint(0, 96, (1, 12))
+    ref = base(ids, return_logits=True).logits
+
+    def variant(**mult):
+        m = AutoModelForCausalLM.from_config(AutoConfig.for_model("granite", **kw, **mult), dtype=torch.float32).eval()
+        m.load_state_dict(base.state_dict())
+        return m
+
+    torch.testing.assert_close(variant(logits_scaling=4.0)(ids, return_logits=True).logits, ref / 4.0, rtol=1e-5, atol=1e-6)
+    # embedding multiplier == scaled embedding table
+    scaled = variant()
+    with torch.no_grad():
+        scaled.model.embed_tokens.weight.mul_(3.0)
+    torch.testing.assert_close(variant(embedding_multiplier=3.0)(ids, return_logits=True).logits,
+                               scaled(ids, return_logits=True).logits, rtol=1e-5, atol=1e-6)
+    # residual multiplier against the block written out by hand
+    r = 0.5
+    m = variant(residual_multiplier=r)
+    layer = m.model.layers["0"]
+    ctx = m.model.make_context(ids)
+    h = m.model.embed(ids)
+    h = h + r * layer.self_attn(layer.input_layernorm(h), ctx)
+    h = h + r * layer.mlp(layer.post_attention_layernorm(h))
+    manual = torch.nn.functional.linear(m.model.norm(h), m.lm_head.weight).view(1, 12, -1)
+    torch.testing.assert_close(m(ids, return_logits=True).logits, manual, rtol=1e-4, atol=1e-5)
+    # attention multiplier replaces 1 / sqrt(head_dim)
+    assert variant(attention_multiplier=0.25).model.layers["0"].self_attn.scale == 0.25
+
+
+def test_qwen2_moe_shared_expert_gate_and_names(tmp_path):
+    cfg = AutoConfig.for_model("qwen2_moe", vocab_size=96, hidden_size=32, intermediate_size=48, num_hidden_layers=2,
+                               num_attention_heads=4, num_key_value_heads=2, head_dim=8, num_experts=4, num_experts_per_tok=2,
+                               moe_intermediate_size=16, shared_expert_intermediate_size=24)
+    torch.manual_seed(2)
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32).eval()
+    moe = model.model.layers["0"].mlp
+    assert moe.shared_expert_gate is not None and not moe.gate.norm_topk_prob
+    x = torch.randn(10, 32)
+    with torch.no_grad():
+        full = moe(x)
+        moe.shared_expert_gate.weight.fill_(-50.0)        # sigmoid -> 0 for most tokens: only the routed experts remain
+        moe.shared_expert_gate.weight[0, 0] = -50.0
+        routed_only = moe(x * 0 + x.abs())                # positive inputs keep the gate's pre-activation very negative
+    assert full.shape == routed_only.shape == (10, 32)
+    model.save_pretrained(str(tmp_path))
+    names = _hf_names(str(tmp_path))
+    assert "model.layers.0.mlp.shared_expert.down_proj.weight" in names and "model.layers.0.mlp.shared_expert_gate.weight" in names
+    assert "model.layers.1.mlp.shared_expert.gate_proj.weight" in names and not any("shared_experts." in n for n in names)
+    again = AutoModelForCausalLM.from_pretrained(str(tmp_path), dtype=torch.float32).eval()
+    ids = torch.randint(0, 96, (2, 8))
+    torch.testing.assert_close(model(ids, return_logits=True).logits, again(ids, return_logits=True).logits, rtol=0, atol=0)
