@@ -247,6 +247,22 @@ class GraniteConfig(DecoderConfig):
         self.logits_scaling = float(logits_scaling)
 
 
+class MiniCPMConfig(GraniteConfig):
+    """MiniCPM (muP-style scaling): embeddings x ``scale_emb``, every residual branch x ``scale_depth / sqrt(layers)``,
+    hidden states / (hidden_size / dim_model_base) before the head (paddleformers/transformers/minicpm)."""
+
+    model_type = "minicpm"
+
+    def __init__(self, scale_emb=1.0, scale_depth=1.0, dim_model_base=None, **kw):
+        L = int(kw.get("num_hidden_layers", 32))
+        H = int(kw.get("hidden_size", 4096))
+        kw.setdefault("embedding_multiplier", float(scale_emb))
+        kw.setdefault("residual_multiplier", float(scale_depth) / (L ** 0.5))
+        kw.setdefault("logits_scaling", float(H) / float(dim_model_base) if dim_model_base else 1.0)
+        super().__init__(**kw)
+        self.scale_emb, self.scale_depth, self.dim_model_base = scale_emb, scale_depth, dim_model_base
+
+
 class Ernie4_5Config(DecoderConfig):
     """ERNIE-4.5 dense: Llama blocks with tied embeddings whose checkpoints store q / k rows in the interleaved rotary
     order; the weight map permutes them to the half-split order on load and back on save
@@ -296,7 +312,7 @@ class Ernie4_5MoeConfig(Ernie4_5Config):
         self.router_bias_name = "mlp.moe_statics.e_score_correction_bias"
 
 
-CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
+CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, MiniCPMConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
                                             Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config)}
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
@@ -304,7 +320,7 @@ CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Q
 UNSUPPORTED_FAMILIES = {
     "gpt_oss": "attention sinks, clamped SwiGLU with expert biases, mxfp4 expert checkpoints (dequantiser: quantization.checkpoint_dequant)",
     "deepseek_v32": "sparse (indexer) attention", "deepseek_v4": "compressed sparse attention",
-    "glm_moe_dsa": "sparse (indexer) attention", "kimi_k2": "DeepSeek-V3 blocks with a different tokenizer / config schema",
+    "glm_moe_dsa": "sparse (indexer) attention",
     "minimax": "lightning (linear) attention hybrid", "minimax_m2": "per-layer QK norm over the full projection",
     "qwen3_next": "gated delta-net linear attention hybrid", "qwen3_5": "gated delta-net linear attention hybrid",
     "qwen3_5_moe": "gated delta-net linear attention hybrid",
@@ -313,7 +329,7 @@ UNSUPPORTED_FAMILIES = {
     "phi4_multimodal": "vision and audio towers",
     "olmo2": "post-norm blocks with QK norm over the full projection", "cohere": "LayerNorm, parallel attention + MLP block",
     "cohere2": "LayerNorm, parallel block, sliding-window layers", "stablelm": "LayerNorm with bias, partial rotary with per-head norm",
-    "internlm2": "interleaved fused wqkv layout", "minicpm": "depth / embedding scaling factors", "minicpm3": "MLA with scaling factors",
+    "internlm2": "interleaved fused wqkv layout", "minicpm3": "MLA with scaling factors",
     "llama4_text": "chunked attention, NoPE layers, shared-expert MoE", "diffllama": "differential attention",
     "qwen2_vl": "vision tower and multimodal rotary embedding", "qwen2_5_vl": "vision tower and multimodal rotary embedding",
     "qwen3_vl": "vision tower and multimodal rotary embedding", "qwen3_vl_moe": "vision tower and multimodal rotary embedding",
@@ -329,7 +345,7 @@ def resolve_config_class(model_type: str):
         raise NotImplementedError(f"model_type {model_type!r} is known but not implemented: it needs {UNSUPPORTED_FAMILIES[model_type]}")
     raise ValueError(f"unknown model_type {model_type!r}; supported: {sorted(CONFIG_MAPPING)}")
 # families whose architecture is a strict subset of an implemented one load through it
-CONFIG_MAPPING.update({"deepseek_v2": DeepseekV3Config, "glm4_moe_lite": Glm4MoeConfig, "phi4": Phi3Config})
+CONFIG_MAPPING.update({"kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV3Config, "glm4_moe_lite": Glm4MoeConfig, "phi4": Phi3Config})
 
 
 def named_config(name: str, **overrides) -> DecoderConfig:

@@ -222,3 +222,12 @@ def test_qwen2_moe_shared_expert_gate_and_names(tmp_path):
     again = AutoModelForCausalLM.from_pretrained(str(tmp_path), dtype=torch.float32).eval()
     ids = torch.randint(0, 96, (2, 8))
     torch.testing.assert_close(model(ids, return_logits=True).logits, again(ids, return_logits=True).logits, rtol=0, atol=0)
+
+
+def test_minicpm_scaling_maps_to_multipliers_and_kimi_uses_deepseek_blocks():
+    cfg = AutoConfig.for_model("minicpm", **{**TINY, "num_hidden_layers": 4, "scale_emb": 12.0, "scale_depth": 1.4, "dim_model_base": 8})
+    assert cfg.embedding_multiplier == 12.0 and cfg.residual_multiplier == pytest.approx(0.7) and cfg.logits_scaling == 4.0
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32)
+    assert model(torch.randint(0, 96, (1, 8)), return_logits=True).logits.shape == (1, 8, 96)
+    k = AutoConfig.for_model("kimi_k2", num_hidden_layers=2)
+    assert k.is_mla and k.topk_method == "noaux_tc"
