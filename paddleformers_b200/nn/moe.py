@@ -424,10 +424,16 @@ class MoELayer(nn.Module):
         sub = int(getattr(self.config, "moe_subbatch_token_num_before_dispatch", 0) or 0)
         if sub > 0 and x2d.shape[0] > sub:
             outs, auxes = [], []
-            for piece in x2d.split(sub, dim=0):
-                outs.append(self._forward_tokens(piece))
-                if self.last_aux_loss is not None:
-                    auxes.append(self.last_aux_loss)
+            # the peer-memory exchange keeps ONE exchange per layer alive for the backward pass; several sub-batches per
+            # layer therefore go through the all-to-all path
+            self._single_exchange_buffers_busy = True
+            try:
+                for piece in x2d.split(sub, dim=0):
+                    outs.append(self._forward_tokens(piece))
+                    if self.last_aux_loss is not None:
+                        auxes.append(self.last_aux_loss)
+            finally:
+                self._single_exchange_buffers_busy = False
             self.last_aux_loss = torch.stack(auxes).mean() if auxes else None
             return torch.cat(outs, dim=0)
         return self._forward_tokens(x2d)
