@@ -183,3 +183,117 @@ def test_checker_detects_a_removed_synchronisation(broken):
         except Hazard:
             caught += 1
     assert caught > 0
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# tensor-parallel fused collectives: all-gather -> GEMM (pull from peers' gather buffers) and GEMM -> reduce-scatter
+# (push partial tiles into the owner's staging slots), parallel/fused_collectives.py
+# ---------------------------------------------------------------------------------------------------------------
+def tp_rank_program(w: World, me: int, layers: int, steps: int, staging_buffers: int = 2, bwd_gather_buffers: int = 2,
+                    back_to_back: bool = False):
+    n = w.n
+    peers = range(n)
+    epochs = {}
+    rs_calls = 0
+    ag_bwd_calls = 0
+
+    def write(owner, buf, tag):
+        w.begin_write(me, owner, buf, tag)
+        yield ("op", None)
+        w.end_write(me, owner, buf, tag)
+        yield ("op", None)
+
+    def read(owner, buf, tag, writers):
+        w.begin_read(me, owner, buf, tag, writers)
+        yield ("op", None)
+        w.end_read(me, owner, buf, tag)
+        yield ("op", None)
+
+    def ag_gemm(buf, tag):
+        epochs[buf] = epochs.get(buf, 0) + 1
+        e = epochs[buf]
+        yield from write(me, buf, tag)                           # own token slice into the gather buffer
+        for p in peers:
+            w.flags[(p, ("ready", buf), me)] = e
+        yield ("op", None)
+        for p in peers:                                          # copy CTAs: wait for the peer's slice, then pull it
+            if p == me:
+                continue
+            yield ("wait", lambda p=p: w.flag(me, ("ready", buf), p) >= e)
+            yield from read(p, buf, tag, [p])
+
+    def gemm_rs(tag):
+        nonlocal rs_calls
+        par = rs_calls % staging_buffers
+        rs_calls += 1
+        buf = f"stage{par}"
+        epochs[buf] = epochs.get(buf, 0) + 1
+        e = epochs[buf]
+        for p in peers:                                          # partial tiles into the owner's slot, then its counter
+            yield from write(p, buf, tag)
+            w.flags[(p, ("cnt", buf), me)] = e
+            yield ("op", None)
+        yield ("wait", lambda: all(w.flag(me, ("cnt", buf), s) >= e for s in peers))
+        yield from read(me, buf, tag, peers)                     # owner sums the slots in rank order
+
+    for step in range(steps):
+        for L in range(layers):
+            yield from ag_gemm(f"G_attn{L}", ("f", step, L, "qkv"))
+            yield from gemm_rs(("f", step, L, "o"))
+            if back_to_back:          # two row-parallel products in a row (no gather in between to order the ranks)
+                yield from gemm_rs(("f", step, L, "o2"))
+                yield from gemm_rs(("f", step, L, "o3"))
+            yield from ag_gemm(f"G_mlp{L}", ("f", step, L, "gate_up"))
+            yield from gemm_rs(("f", step, L, "down"))
+        for L in reversed(range(layers)):
+            for name in ("down", "o"):
+                par = ag_bwd_calls % bwd_gather_buffers          # row-parallel backward: gather dy, shared buffers
+                ag_bwd_calls += 1
+                yield from ag_gemm(f"G_bwd{par}", ("b", step, L, name))
+                if back_to_back:
+                    par = ag_bwd_calls % bwd_gather_buffers
+                    ag_bwd_calls += 1
+                    yield from ag_gemm(f"G_bwd{par}", ("b", step, L, name + "2"))
+                yield from gemm_rs(("b", step, L, name + "_dx"))  # column-parallel backward: dgrad + reduce-scatter
+
+
+def run_tp(n, layers, steps, seed, **kw):
+    rng = random.Random(seed)
+    w = World(n)
+    progs = [tp_rank_program(w, r, layers, steps, **kw) for r in range(n)]
+    blocked = [None] * n
+    alive = set(range(n))
+    while alive:
+        runnable = [r for r in alive if blocked[r] is None or blocked[r]()]
+        if not runnable:
+            raise AssertionError(f"deadlock: ranks {sorted(alive)} all wait")
+        r = rng.choice(runnable)
+        blocked[r] = None
+        try:
+            kind, pred = next(progs[r])
+        except StopIteration:
+            alive.discard(r)
+            continue
+        if kind == "wait" and not pred():
+            blocked[r] = pred
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("back_to_back", [False, True])
+def test_tensor_parallel_fused_collectives_have_no_races(n, back_to_back):
+    for seed in range(100):
+        run_tp(n, layers=2, steps=2, seed=seed, back_to_back=back_to_back)
+
+
+@pytest.mark.parametrize("kw", [dict(staging_buffers=1), dict(bwd_gather_buffers=1)])
+def test_single_buffering_of_shared_tp_buffers_is_caught(kw):
+    """Why the shared buffers alternate: when two calls of the same kind follow each other directly, a fast rank would
+    overwrite, in a single buffer, data that a slow peer still reads. (With a call of the other kind in between, which
+    needs a signal from every peer, one buffer would do; two cover every call order.)"""
+    caught = 0
+    for seed in range(300):
+        try:
+            run_tp(4, layers=2, steps=2, seed=seed, back_to_back=True, **kw)
+        except Hazard:
+            caught += 1
+    assert caught > 0
