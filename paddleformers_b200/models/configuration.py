@@ -71,6 +71,13 @@ class DecoderConfig(PretrainedConfig):
     def n_routed_experts(self):
         return self.num_experts
 
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if self.num_experts and self.model_type in ("deepseek_v3", "deepseek_v2", "glm4_moe", "glm4_moe_lite", "kimi_k2"):
+            d["n_routed_experts"] = self.num_experts      # the field name these families use in config.json
+            d.pop("num_experts", None)
+        return d
+
     @property
     def is_mla(self) -> bool:
         return self.kv_lora_rank is not None
@@ -132,7 +139,8 @@ class DeepseekV3Config(DecoderConfig):
         kw.setdefault("moe_intermediate_size", 2048)
         kw.setdefault("num_attention_heads", 128)
         kw.setdefault("num_key_value_heads", 128)
-        kw.setdefault("n_routed_experts", 256)
+        if "num_experts" not in kw:
+            kw.setdefault("n_routed_experts", 256)
         kw.setdefault("n_shared_experts", 1)
         kw.setdefault("num_experts_per_tok", 8)
         kw.setdefault("first_k_dense_replace", 3)

@@ -1,0 +1,125 @@
+"""End-to-end CPU checks of the fine-tuning workflows and of the MLA / MTP / GLM model variants."""
+import os
+
+import pytest
+import torch
+
+from paddleformers_b200 import Trainer, TrainingArguments
+from paddleformers_b200.datasets.collate import dpo_collate_fn
+from paddleformers_b200.models.configuration import named_config
+from paddleformers_b200.transformers.auto import AutoConfig, AutoModelForCausalLM
+
+
+def _tiny(**kw):
+    cfg = named_config("tiny-llama", vocab_size=64, hidden_size=32, intermediate_size=64, num_attention_heads=2,
+                       num_key_value_heads=1, head_dim=16, **kw)
+    torch.manual_seed(0)
+    return AutoModelForCausalLM.from_config(cfg, dtype=torch.float32)
+
+
+class _Pairs(torch.utils.data.Dataset):
+    """The chosen answer continues with token 7, the rejected one with token 9."""
+
+    def __len__(self):
+        return 64
+
+    def __getitem__(self, i):
+        g = torch.Generator().manual_seed(i)
+        p = torch.randint(10, 60, (6,), generator=g).tolist()
+        return {"prompt_ids": p, "chosen_ids": [7, 7, 7, 1], "rejected_ids": [9, 9, 9, 1]}
+
+
+@pytest.mark.parametrize("loss_type", ["sigmoid", "ipo", "simpo"])
+def test_dpo_training_raises_the_reward_margin(tmp_path, loss_type):
+    from paddleformers_b200.trainer.dpo_trainer import DPOTrainer
+
+    policy, ref = _tiny(), _tiny()
+    args = TrainingArguments(output_dir=str(tmp_path), per_device_train_batch_size=4, max_steps=12, learning_rate=5e-3,
+                             logging_steps=1, save_strategy="no", max_seq_len=32, device="cpu", lr_scheduler_type="constant")
+    tr = DPOTrainer(model=policy, ref_model=ref, args=args, train_dataset=_Pairs(), data_collator=lambda b: dpo_collate_fn(b, max_seq_len=32),
+                    dpo_loss_type=loss_type, dpo_beta=0.5)
+    tr.train()
+    recs = [h for h in tr.state.log_history if "loss" in h]
+    assert recs[-1]["loss"] < recs[0]["loss"]
+    batch = dpo_collate_fn([_Pairs()[i] for i in range(8)], max_seq_len=32)
+    with torch.no_grad():
+        c, r, _ = tr._logps(policy, batch)
+    assert (c > r).all()                                    # the policy now prefers the chosen continuation
+
+
+def test_lora_finetune_trains_only_adapters_and_merges(tmp_path):
+    from paddleformers_b200.data.synthetic import SyntheticCausalLMDataset
+    from paddleformers_b200.peft.lora import LoRAConfig, LoRAModel
+
+    base = _tiny()
+    before = {k: v.clone() for k, v in base.state_dict().items()}
+    model = LoRAModel(base, LoRAConfig(r=4, lora_alpha=8))
+    args = TrainingArguments(output_dir=str(tmp_path), per_device_train_batch_size=2, max_steps=8, learning_rate=1e-2,
+                             logging_steps=1, save_strategy="no", max_seq_len=16, device="cpu", lr_scheduler_type="constant")
+
+    class Fixed(torch.utils.data.Dataset):
+        ds = SyntheticCausalLMDataset(64, 16, num_samples=2, seed=0)
+
+        def __len__(self):
+            return 32
+
+        def __getitem__(self, i):
+            return self.ds[i % 2]
+
+    tr = Trainer(model=model, args=args, train_dataset=Fixed())
+    tr.train()
+    losses = [h["loss"] for h in tr.state.log_history if "loss" in h]
+    assert losses[-1] < losses[0]
+    for k, v in base.state_dict().items():
+        if "lora_" not in k and k in before:
+            assert torch.equal(v, before[k]), k              # frozen base weights did not move
+    ids = torch.randint(0, 64, (2, 16))
+    with torch.no_grad():
+        with_adapters = model(ids, return_logits=True).logits
+        merged = model.merge_and_unload() if hasattr(model, "merge_and_unload") else None
+    if merged is not None:
+        with torch.no_grad():
+            torch.testing.assert_close(merged(ids, return_logits=True).logits, with_adapters, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("preset,over", [
+    ("deepseek-v3-4l", dict(hidden_size=64, intermediate_size=96, moe_intermediate_size=32, num_attention_heads=4,
+                            num_key_value_heads=4, n_routed_experts=8, num_experts_per_tok=2, n_group=2, topk_group=1,
+                            q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, head_dim=24,
+                            vocab_size=96, num_hidden_layers=3, first_k_dense_replace=1)),
+    ("glm4.5-air-12l", dict(hidden_size=64, intermediate_size=96, moe_intermediate_size=32, num_attention_heads=4,
+                            num_key_value_heads=2, head_dim=16, n_routed_experts=4, num_experts_per_tok=2, vocab_size=96,
+                            num_hidden_layers=3)),
+])
+def test_mla_mtp_and_glm_variants_train_and_roundtrip(tmp_path, preset, over):
+    torch.manual_seed(0)
+    cfg = named_config(preset, **over)
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32)
+    assert len(model.mtp_layers) == 1
+    ids = torch.randint(0, 96, (2, 16))
+    labels = torch.roll(ids, -1, 1)
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3)
+    first = last = None
+    for _ in range(8):
+        out = model(ids, labels=labels)
+        assert out.mtp_losses is not None and len(out.mtp_losses) == 1
+        opt.zero_grad()
+        out.loss.backward()
+        opt.step()
+        first = first if first is not None else out.loss.item()
+        last = out.loss.item()
+    assert last < first
+    model.eval()
+    model.save_pretrained(str(tmp_path))
+    again = AutoModelForCausalLM.from_pretrained(str(tmp_path), dtype=torch.float32).eval()
+    with torch.no_grad():
+        torch.testing.assert_close(model(ids, return_logits=True).logits, again(ids, return_logits=True).logits, rtol=0, atol=0)
+    # the MTP block is stored as an extra entry of model.layers, like the Hugging Face checkpoints
+    from safetensors import safe_open
+
+    names = []
+    for f in os.listdir(tmp_path):
+        if f.endswith(".safetensors"):
+            with safe_open(str(tmp_path / f), "pt") as sf:
+                names += list(sf.keys())
+    assert any(n.startswith(f"model.layers.{cfg.num_hidden_layers}.") and "eh_proj" in n for n in names)
