@@ -218,3 +218,52 @@ def test_nccl_group_config_parsing_and_options():
         load_nccl_config({"mp": {"ctas": 3}})
     with pytest.raises(ValueError, match="unknown group"):
         load_nccl_config({"tp": {"max_ctas": 3}})
+
+
+def _train_and_save(rank, world, targs, steps, full_state, out_dir, resume):
+    from paddleformers_b200 import Trainer, TrainingArguments
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+    from paddleformers_b200.transformers.configuration_utils import LlmMetaConfig
+    from paddleformers_b200.transformers.model_utils import param_shard_spec
+
+    args = TrainingArguments(output_dir=out_dir, per_device_train_batch_size=1, max_steps=steps, learning_rate=1e-2,
+                             lr_scheduler_type="constant", logging_steps=1, save_steps=2, max_seq_len=32, max_grad_norm=1.0,
+                             seed=3, device="cpu", **targs)
+    ps = args.setup_parallel()
+    cfg = _tiny_cfg(False)
+    LlmMetaConfig.set_llm_config(cfg, args)
+    model = MODEL_MAPPING[cfg.model_type](cfg)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            p.copy_(param_shard_spec(p).shard(full_state[name], ps.coord["mp"], ps.degrees.mp, ps.rank_in("ep"), ps.degrees.ep))
+    tr = Trainer(model=model, args=args, train_dataset=_DS(_data(8 * 4)))
+    tr._sampler_shuffle = False
+    tr.train(resume_from_checkpoint="auto" if resume else None)
+    return [h["loss"] for h in tr.state.log_history if "loss" in h]
+
+
+def test_resume_with_a_different_sharding_degree(tmp_path):
+    """Optimizer shards written by 2 sharding ranks are re-cut for 1 rank; the run continues like an uninterrupted one."""
+    full = _reference(False, 4, 2)
+    ref = run_distributed(_train_and_save, 1, dict(gradient_accumulation_steps=2), 4, full, str(tmp_path / "ref"), False)[0]
+    run_distributed(_train_and_save, 2, dict(sharding="stage1", gradient_accumulation_steps=1), 2, full, str(tmp_path / "run"), False)
+    got = run_distributed(_train_and_save, 1, dict(gradient_accumulation_steps=2), 4, full, str(tmp_path / "run"), True)[0]
+    assert len(got) >= 2
+    for a, b in zip(ref[2:], got[-2:]):
+        assert abs(a - b) < 3e-4 * max(1.0, abs(a)), (ref, got)
+
+
+def test_tensor_parallel_checkpoint_loads_in_one_process(tmp_path):
+    """Weights saved by 2 tensor-parallel ranks form one Hugging Face checkpoint that a single process loads."""
+    from paddleformers_b200.transformers.auto import AutoModelForCausalLM
+
+    full = _reference(False, 2, 2)
+    run_distributed(_train_and_save, 2, dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2),
+                    2, full, str(tmp_path / "tp"), False)
+    ref_losses = run_distributed(_train_and_save, 1, dict(gradient_accumulation_steps=2), 2, full, str(tmp_path / "one"), False)[0]
+    a = AutoModelForCausalLM.from_pretrained(str(tmp_path / "tp" / "checkpoint-2"), dtype=torch.float32)
+    b = AutoModelForCausalLM.from_pretrained(str(tmp_path / "one" / "checkpoint-2"), dtype=torch.float32)
+    assert len(ref_losses) == 2
+    for (n1, p1), (n2, p2) in zip(a.state_dict().items(), b.state_dict().items()):
+        assert n1 == n2
+        torch.testing.assert_close(p1, p2, rtol=2e-3, atol=2e-4)
