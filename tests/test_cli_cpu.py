@@ -57,3 +57,66 @@ def test_launch_command_uses_loopback_rendezvous(monkeypatch):
     monkeypatch.delenv("MASTER_ADDR", raising=False)
     cmd = build_launch_command(["cfg.yaml", "a=1"], 8)
     assert "--nproc-per-node=8" in cmd and "--master-addr=127.0.0.1" in cmd and cmd[-2:] == ["cfg.yaml", "a=1"]
+
+
+def _tiny_tokenizer_dir(tmp_path):
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    words = ["<pad>", "<s>", "</s>", "<unk>", "Human:", "Assistant:", "System:"] + [f"w{i}" for i in range(60)]
+    tok = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    fast = PreTrainedTokenizerFast(tokenizer_object=tok, pad_token="<pad>", bos_token="<s>", eos_token="</s>", unk_token="<unk>")
+    d = tmp_path / "tok"
+    fast.save_pretrained(str(d))
+    return str(d), len(words)
+
+
+def test_sft_lora_stage_then_export_merges_adapters(tmp_path):
+    """SFT stage with LoRA from a jsonl of conversations, then the export command merges the adapters into a
+    Hugging Face directory that loads as a plain model."""
+    from paddleformers_b200.cli.cli import main
+    from paddleformers_b200.transformers.auto import AutoModelForCausalLM
+
+    tok_dir, vocab = _tiny_tokenizer_dir(tmp_path)
+    data = tmp_path / "sft.jsonl"
+    rng = np.random.RandomState(0)
+    with open(data, "w") as f:
+        for _ in range(32):
+            q = " ".join(f"w{i}" for i in rng.randint(0, 60, size=5))
+            a = " ".join(f"w{i}" for i in rng.randint(0, 60, size=4))
+            f.write(json.dumps({"messages": [{"role": "user", "content": q}, {"role": "assistant", "content": a}]}) + "\n")
+    # a base model directory that also holds the tokenizer
+    base_dir = tmp_path / "base"
+    from paddleformers_b200.models.configuration import named_config
+
+    cfg = named_config("tiny-llama", vocab_size=vocab, hidden_size=32, intermediate_size=48, num_attention_heads=2,
+                       num_key_value_heads=1, head_dim=16)
+    AutoModelForCausalLM.from_config(cfg, dtype=torch.float32).save_pretrained(str(base_dir))
+    for fn in os.listdir(tok_dir):
+        with open(os.path.join(tok_dir, fn), "rb") as src, open(base_dir / fn, "wb") as dst:
+            dst.write(src.read())
+    out = tmp_path / "lora_out"
+    cfg_file = tmp_path / "sft.json"
+    cfg_file.write_text(json.dumps({
+        "stage": "SFT", "model_name_or_path": str(base_dir), "compute_type": "float32", "device": "cpu", "lora": True,
+        "lora_rank": 4, "train_dataset_path": str(data), "template": "default", "max_seq_len": 32, "max_steps": 3,
+        "per_device_train_batch_size": 2, "learning_rate": 1e-3, "logging_steps": 1, "save_strategy": "no", "output_dir": str(out)}))
+    env = os.environ.get("CUDA_VISIBLE_DEVICES")
+    os.environ["CUDA_VISIBLE_DEVICES"] = ""
+    try:
+        assert main(["train", str(cfg_file)]) == 0
+        merged = tmp_path / "merged"
+        exp_file = tmp_path / "export.json"
+        exp_file.write_text(json.dumps({"model_name_or_path": str(base_dir), "lora_path": str(out), "output_dir": str(merged),
+                                        "compute_type": "float32", "device": "cpu"}))
+        assert main(["export", str(exp_file)]) == 0
+    finally:
+        if env is None:
+            os.environ.pop("CUDA_VISIBLE_DEVICES", None)
+        else:
+            os.environ["CUDA_VISIBLE_DEVICES"] = env
+    final = merged / "export"                  # the export command writes into <output_dir>/export, like the reference's
+    model = AutoModelForCausalLM.from_pretrained(str(final), dtype=torch.float32)
+    assert not any("lora_" in n for n, _ in model.named_parameters())
+    assert os.path.exists(final / "tokenizer.json")
