@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Headline benchmark: training throughput (tokens/s, whole job) of Llama-3-8B pretraining, bf16, seq 4096,
-micro-batch 1, global batch 64 sequences, TP = number of GPUs (+ sequence parallel), sharding stage-1 optimizer,
-synthetic uniform-random tokens and random-init weights (std 0.02).
+global batch 64 sequences (micro-batch 2 on one GPU, 1 otherwise; see --micro-batch), TP = number of GPUs (+ sequence
+parallel), sharding stage-1 optimizer, synthetic uniform-random tokens and random-init weights (std 0.02).
 
     python bench.py --gpus 1 --steps 2 --warmup 3
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29511 \
@@ -9,7 +9,7 @@ synthetic uniform-random tokens and random-init weights (std 0.02).
     python bench.py --impl reference ...      # the unmodified reference, if it can run on this machine
     python bench.py --model qwen3-30b-a3b ... # EP = GPUs, packed documents (needs 8 GPUs for memory)
 
-One step = 64 micro-batches of forward + backward followed by the sharded AdamW update. Two timed regions are
+One step = 64 sequences of forward + backward (in micro-batches) followed by the sharded AdamW update. Two timed regions are
 reported: ``value`` is timed on the device (CUDA events, barrier + synchronize on both sides, max over ranks) with the
 inputs already resident; ``e2e`` runs the same steps through ``Trainer.train()`` with every micro-batch copied from
 pinned host memory and the loss read back to the host every step.
