@@ -21,7 +21,7 @@ class DecoderConfig(PretrainedConfig):
                  partial_rotary_factor=1.0, attention_bias=False, mlp_bias=False, use_qk_norm=False,
                  attention_dropout=0.0,
                  # MoE
-                 num_experts=0, n_routed_experts=None, num_experts_per_tok=0, moe_intermediate_size=None,
+                 num_experts=0, n_routed_experts=None, num_local_experts=None, num_experts_per_tok=0, moe_intermediate_size=None,
                  n_shared_experts=0, shared_expert_intermediate_size=None, first_k_dense_replace=0,
                  decoder_sparse_step=1, mlp_only_layers=None, norm_topk_prob=True, scoring_func="softmax",
                  topk_method="greedy", n_group=1, topk_group=1, routed_scaling_factor=1.0,
@@ -44,6 +44,8 @@ class DecoderConfig(PretrainedConfig):
         self.mlp_bias = mlp_bias
         self.use_qk_norm = use_qk_norm
         self.attention_dropout = attention_dropout
+        if num_local_experts is not None and not num_experts:      # the name recent Hugging Face configs serialise
+            num_experts = num_local_experts
         self.num_experts = n_routed_experts if n_routed_experts is not None else num_experts
         self.num_experts_per_tok = num_experts_per_tok
         self.moe_intermediate_size = moe_intermediate_size
@@ -115,10 +117,17 @@ class Qwen3Config(DecoderConfig):
         super().__init__(**kw)
 
 
+def _expert_count_alias(kw):
+    """Recent Hugging Face releases serialise the expert count of these families as ``num_local_experts``."""
+    if "num_local_experts" in kw and "num_experts" not in kw:
+        kw["num_experts"] = kw["num_local_experts"]
+
+
 class Qwen3MoeConfig(DecoderConfig):
     model_type = "qwen3_moe"
 
     def __init__(self, **kw):
+        _expert_count_alias(kw)
         kw.setdefault("use_qk_norm", True)
         kw.setdefault("head_dim", 128)
         kw.setdefault("num_experts", 128)
@@ -229,6 +238,7 @@ class Qwen2MoeConfig(DecoderConfig):
     model_type = "qwen2_moe"
 
     def __init__(self, **kw):
+        _expert_count_alias(kw)
         kw.setdefault("attention_bias", True)
         kw.setdefault("num_experts", 60)
         kw.setdefault("num_experts_per_tok", 4)

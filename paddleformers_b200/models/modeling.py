@@ -563,8 +563,20 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
     qkv_sizes = None
     # checkpoints trained with interleaved rotary pairs: q and k rows (sources 0 and 1) are permuted per head on load
     rope_perm = {0: config.head_dim, 1: config.head_dim} if getattr(config, "rope_interleaved_checkpoint", False) else None
+    mla_q_name = mla_q_perm = mla_kv_perm = None
     if config.is_mla:
-        pass  # MLA projections keep their HF names
+        # MLA projections keep their HF names. DeepSeek checkpoints store the rotary slice of every query head and of the
+        # compressed kv projection with interleaved pairs (the published model code rotates (2i, 2i + 1)); the rows are
+        # permuted to the half-split order of the rotary kernels on load and back on save
+        # (paddleformers/transformers/deepseek_v3/modeling.py:229-233 does the same permutation on activations).
+        if getattr(config, "rope_interleave", True):
+            qd = config.qk_nope_head_dim + config.qk_rope_head_dim
+            mla_q_name = "q_b_proj.weight" if config.q_lora_rank else "q_proj.weight"
+            mla_q_perm = {0: (qd, config.qk_nope_head_dim, config.qk_rope_head_dim)}
+            mla_kv_perm = {0: (config.kv_lora_rank + config.qk_rope_head_dim, config.kv_lora_rank, config.qk_rope_head_dim)}
+            per_layer.append(Rule(L + "self_attn." + mla_q_name, [L + "self_attn." + mla_q_name], rope_deinterleave=mla_q_perm))
+            per_layer.append(Rule(L + "self_attn.kv_a_proj_with_mqa.weight", [L + "self_attn.kv_a_proj_with_mqa.weight"],
+                                  rope_deinterleave=mla_kv_perm))
     else:
         qkv_sizes = [config.num_attention_heads * config.head_dim, config.num_key_value_heads * config.head_dim,
                      config.num_key_value_heads * config.head_dim]
@@ -615,7 +627,8 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
         if config.is_mla:
             for name in ("q_a_proj.weight", "q_a_layernorm.weight", "q_b_proj.weight", "kv_a_proj_with_mqa.weight",
                          "kv_a_layernorm.weight", "kv_b_proj.weight"):
-                rules.append(Rule(blk + "self_attn." + name, [src + "self_attn." + name]))
+                perm = mla_q_perm if name == mla_q_name else mla_kv_perm if name == "kv_a_proj_with_mqa.weight" else None
+                rules.append(Rule(blk + "self_attn." + name, [src + "self_attn." + name], rope_deinterleave=perm))
         else:
             rules.append(Rule(blk + "self_attn.qkv_proj.weight", [src + "self_attn.q_proj.weight", src + "self_attn.k_proj.weight",
                                                                  src + "self_attn.v_proj.weight"], "concat", 0, sizes=qkv_sizes))

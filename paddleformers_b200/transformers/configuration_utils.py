@@ -159,6 +159,8 @@ class PretrainedConfig:
                 continue
             if hasattr(v, "to_dict"):
                 v = v.to_dict()
+            if saving and v is None:
+                continue          # absent == None on load; an explicit null breaks other loaders (quantization_config)
             out[k] = v
         out["model_type"] = self.model_type
         if saving:

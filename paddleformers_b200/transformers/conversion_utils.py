@@ -57,6 +57,21 @@ class ShardSpec:
         return torch.cat(out, dim=self.tp_dim)
 
 
+def _rope_rows(t: torch.Tensor, spec, inverse: bool) -> torch.Tensor:
+    """``spec`` = head_dim (whole heads are rotary) or (head_size, rope_offset, rope_dim): inside every chunk of
+    ``head_size`` rows only rows [rope_offset, rope_offset + rope_dim) carry the rotary embedding (MLA: each query head is
+    [nope | rope]; the compressed kv projection is [latent | rope])."""
+    fn = interleave_rope_rows if inverse else deinterleave_rope_rows
+    if isinstance(spec, int):
+        return fn(t, spec)
+    head, off, rd = spec
+    nh = t.shape[0] // head
+    v = t.reshape(nh, head, *t.shape[1:]).clone()
+    part = v[:, off:off + rd].reshape(nh * rd, *t.shape[1:])
+    v[:, off:off + rd] = fn(part, rd).reshape(nh, rd, *t.shape[1:])
+    return v.reshape(t.shape)
+
+
 def deinterleave_rope_rows(t: torch.Tensor, head_dim: int) -> torch.Tensor:
     """Reorder the rows of a q / k projection (or bias) from the interleaved rotary layout, where the pair rotated
     together sits at rows (2i, 2i + 1) of each head, to the half-split layout (i, i + head_dim / 2) that the rotary
@@ -85,17 +100,18 @@ class Rule:
     num_experts: int = 0
     expert_pairs: int = 1  # stack_concat: sources per expert (gate, up)
     sizes: Optional[List[int]] = None  # concat: size of each source along ``dim`` (default: equal parts)
-    rope_deinterleave: Optional[Dict[int, int]] = None  # source index -> head_dim: rows stored in interleaved rotary order
+    rope_deinterleave: Optional[Dict[int, object]] = None  # source index -> head_dim | (head_size, rope_offset, rope_dim):
+    #                                                          rows stored in interleaved rotary order
     flatten: bool = False              # rename: the checkpoint stores the tensor with a leading unit dimension
 
     def _load(self, i: int, t: torch.Tensor) -> torch.Tensor:
         if self.rope_deinterleave and i in self.rope_deinterleave:
-            t = deinterleave_rope_rows(t, self.rope_deinterleave[i])
+            t = _rope_rows(t, self.rope_deinterleave[i], inverse=False)
         return t
 
     def _store(self, i: int, t: torch.Tensor) -> torch.Tensor:
         if self.rope_deinterleave and i in self.rope_deinterleave:
-            t = interleave_rope_rows(t, self.rope_deinterleave[i])
+            t = _rope_rows(t, self.rope_deinterleave[i], inverse=True)
         return t
 
     def source_names(self) -> List[str]:

@@ -181,6 +181,10 @@ class PretrainedModel(nn.Module):
                 if not all(reader.has(s) for s in srcs):
                     if name == "lm_head.weight" and reader.has("model.embed_tokens.weight"):
                         full = get("model.embed_tokens.weight")
+                    elif reader.has(name):
+                        # the checkpoint already stores this tensor in the fused internal layout (stacked experts
+                        # [E, 2I, H] / [E, H, I] as written by recent Hugging Face releases)
+                        full = get(name)
                     else:
                         missing.append(name)
                         continue

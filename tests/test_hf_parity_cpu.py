@@ -1,0 +1,84 @@
+"""Parity with the Hugging Face ``transformers`` PyTorch implementations, used as an independent oracle: a tiny randomly
+initialised HF model is saved as safetensors, loaded through this framework's weight maps, and must produce the same
+logits (fp32, CPU). This pins the rotary conventions, fused-projection layouts, router rules, MLA and the per-family
+multipliers to an implementation that shares no code with this repository."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from paddleformers_b200.transformers.auto import AutoModelForCausalLM  # noqa: E402
+
+BASE = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+            num_key_value_heads=2, max_position_embeddings=128, tie_word_embeddings=False)
+
+CASES = {
+    "llama": ("LlamaConfig", "LlamaForCausalLM", dict(rope_theta=10000.0, rms_norm_eps=1e-5)),
+    "mistral": ("MistralConfig", "MistralForCausalLM", dict(sliding_window=None)),
+    "qwen2": ("Qwen2Config", "Qwen2ForCausalLM", dict()),
+    "qwen3": ("Qwen3Config", "Qwen3ForCausalLM", dict(head_dim=16)),
+    "phi3": ("Phi3Config", "Phi3ForCausalLM", dict(pad_token_id=0)),
+    "seed_oss": ("SeedOssConfig", "SeedOssForCausalLM", dict(head_dim=16)),
+    "granite": ("GraniteConfig", "GraniteForCausalLM", dict(embedding_multiplier=3.0, residual_multiplier=0.5, attention_multiplier=0.2,
+                                                           logits_scaling=2.0)),
+    "qwen3_moe": ("Qwen3MoeConfig", "Qwen3MoeForCausalLM", dict(head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
+                                                               norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[])),
+    "qwen2_moe": ("Qwen2MoeConfig", "Qwen2MoeForCausalLM", dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
+                                                               shared_expert_intermediate_size=48, norm_topk_prob=False,
+                                                               decoder_sparse_step=1, mlp_only_layers=[])),
+    "ernie4_5": ("Ernie4_5Config", "Ernie4_5ForCausalLM", dict(head_dim=16, tie_word_embeddings=True)),
+    "ernie4_5_moe": ("Ernie4_5_MoeConfig", "Ernie4_5_MoeForCausalLM", dict(head_dim=16, tie_word_embeddings=True, moe_num_experts=4, moe_k=2,
+                                                                         moe_intermediate_size=32, moe_num_shared_experts=1,
+                                                                         moe_layer_start_index=1, moe_layer_interval=1)),
+    "deepseek_v3": ("DeepseekV3Config", "DeepseekV3ForCausalLM", dict(num_key_value_heads=4, moe_intermediate_size=32, n_routed_experts=8,
+                                                                     num_experts_per_tok=2, n_group=2, topk_group=1, n_shared_experts=1,
+                                                                     first_k_dense_replace=1, q_lora_rank=24, kv_lora_rank=16,
+                                                                     qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                                                                     routed_scaling_factor=2.5, norm_topk_prob=True)),
+    "glm4_moe": ("Glm4MoeConfig", "Glm4MoeForCausalLM", dict(head_dim=16, moe_intermediate_size=32, n_routed_experts=4, num_experts_per_tok=2,
+                                                             n_group=1, topk_group=1, n_shared_experts=1, first_k_dense_replace=1,
+                                                             partial_rotary_factor=0.5, use_qk_norm=True, routed_scaling_factor=1.5,
+                                                             norm_topk_prob=True)),
+}
+
+
+@pytest.mark.parametrize("family", sorted(CASES))
+def test_logits_match_hugging_face_implementation(tmp_path, family):
+    cfg_name, cls_name, extra = CASES[family]
+    if not (hasattr(transformers, cfg_name) and hasattr(transformers, cls_name)):
+        pytest.skip(f"transformers has no {cls_name}")
+    torch.manual_seed(0)
+    hf_cfg = getattr(transformers, cfg_name)(**{**BASE, **extra})
+    hf = getattr(transformers, cls_name)(hf_cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():          # non-trivial values everywhere (norm weights, router biases)
+            if p.dim() == 1:
+                p.normal_(1.0 if "norm" in n else 0.0, 0.1)
+        for n, b in hf.named_buffers():
+            if "e_score_correction_bias" in n:
+                b.normal_(0.0, 0.1)
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    mine = AutoModelForCausalLM.from_pretrained(str(tmp_path), dtype=torch.float32).eval()
+    ids = torch.randint(0, 128, (2, 24))
+    with torch.no_grad():
+        want = hf(input_ids=ids).logits
+        got = mine(ids, return_logits=True).logits
+    torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
+
+
+@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3"])
+def test_hugging_face_loads_what_this_framework_saves(tmp_path, family):
+    """The other direction: a checkpoint written by ``save_pretrained`` here (per-expert tensors, interleaved rotary rows
+    restored, HF config field names) loads in ``transformers`` and gives the same logits."""
+    cfg_name, cls_name, extra = CASES[family]
+    torch.manual_seed(1)
+    hf_cfg = getattr(transformers, cfg_name)(**{**BASE, **extra})
+    src = tmp_path / "src"
+    getattr(transformers, cls_name)(hf_cfg).save_pretrained(str(src), safe_serialization=True)
+    mine = AutoModelForCausalLM.from_pretrained(str(src), dtype=torch.float32).eval()
+    out = tmp_path / "out"
+    mine.save_pretrained(str(out))
+    back = getattr(transformers, cls_name).from_pretrained(str(out), torch_dtype=torch.float32).eval()
+    ids = torch.randint(0, 128, (2, 24))
+    with torch.no_grad():
+        torch.testing.assert_close(back(input_ids=ids).logits, mine(ids, return_logits=True).logits, rtol=2e-4, atol=2e-4)
