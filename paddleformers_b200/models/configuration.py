@@ -17,7 +17,7 @@ class DecoderConfig(PretrainedConfig):
 
     def __init__(self, vocab_size=32000, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
                  num_attention_heads=32, num_key_value_heads=None, head_dim=None, hidden_act="silu",
-                 max_position_embeddings=4096, rms_norm_eps=1e-6, rope_theta=10000.0, rope_scaling=None,
+                 max_position_embeddings=4096, rms_norm_eps=1e-6, rope_theta=10000.0, rope_scaling=None, rope_parameters=None,
                  partial_rotary_factor=1.0, attention_bias=False, mlp_bias=False, use_qk_norm=False,
                  attention_dropout=0.0,
                  # MoE
@@ -37,6 +37,13 @@ class DecoderConfig(PretrainedConfig):
         self.hidden_act = hidden_act
         self.max_position_embeddings = max_position_embeddings
         self.rms_norm_eps = rms_norm_eps
+        if rope_parameters:          # recent Hugging Face configs: base and scaling rule in one dict
+            rope_theta = rope_parameters.get("rope_theta", rope_theta)
+            kind = rope_parameters.get("rope_type", rope_parameters.get("type", "default"))
+            if kind not in (None, "default") and rope_scaling is None:
+                rope_scaling = {k: v for k, v in rope_parameters.items() if k != "rope_theta"}
+            if "partial_rotary_factor" in rope_parameters and partial_rotary_factor == 1.0:
+                partial_rotary_factor = rope_parameters["partial_rotary_factor"]
         self.rope_theta = rope_theta
         self.rope_scaling = rope_scaling
         self.partial_rotary_factor = partial_rotary_factor

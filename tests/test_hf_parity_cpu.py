@@ -14,6 +14,10 @@ BASE = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_lay
 
 CASES = {
     "llama": ("LlamaConfig", "LlamaForCausalLM", dict(rope_theta=10000.0, rms_norm_eps=1e-5)),
+    "llama_theta": ("LlamaConfig", "LlamaForCausalLM", dict(rope_theta=500000.0)),
+    "llama3_scaling": ("LlamaConfig", "LlamaForCausalLM", dict(rope_theta=500000.0, rope_scaling={
+        "rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 16})),
+    "llama_linear_scaling": ("LlamaConfig", "LlamaForCausalLM", dict(rope_scaling={"rope_type": "linear", "factor": 4.0})),
     "mistral": ("MistralConfig", "MistralForCausalLM", dict(sliding_window=None)),
     "qwen2": ("Qwen2Config", "Qwen2ForCausalLM", dict()),
     "qwen3": ("Qwen3Config", "Qwen3ForCausalLM", dict(head_dim=16)),
@@ -35,6 +39,12 @@ CASES = {
                                                                      first_k_dense_replace=1, q_lora_rank=24, kv_lora_rank=16,
                                                                      qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
                                                                      routed_scaling_factor=2.5, norm_topk_prob=True)),
+    "deepseek_v3_yarn": ("DeepseekV3Config", "DeepseekV3ForCausalLM", dict(
+        num_key_value_heads=4, moe_intermediate_size=32, n_routed_experts=8, num_experts_per_tok=2, n_group=2, topk_group=1,
+        n_shared_experts=1, first_k_dense_replace=1, q_lora_rank=None, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8,
+        v_head_dim=16, routed_scaling_factor=2.5, norm_topk_prob=True, max_position_embeddings=128,
+        rope_scaling={"rope_type": "yarn", "factor": 4.0, "beta_fast": 32, "beta_slow": 1, "mscale": 1.0, "mscale_all_dim": 0.707,
+                      "original_max_position_embeddings": 32})),
     "glm4_moe": ("Glm4MoeConfig", "Glm4MoeForCausalLM", dict(head_dim=16, moe_intermediate_size=32, n_routed_experts=4, num_experts_per_tok=2,
                                                              n_group=1, topk_group=1, n_shared_experts=1, first_k_dense_replace=1,
                                                              partial_rotary_factor=0.5, use_qk_norm=True, routed_scaling_factor=1.5,
@@ -82,3 +92,33 @@ def test_hugging_face_loads_what_this_framework_saves(tmp_path, family):
     ids = torch.randint(0, 128, (2, 24))
     with torch.no_grad():
         torch.testing.assert_close(back(input_ids=ids).logits, mine(ids, return_logits=True).logits, rtol=2e-4, atol=2e-4)
+
+
+def test_loss_gradients_and_greedy_generation_match_hugging_face(tmp_path):
+    """Loss convention (targets shifted by the data pipeline here, inside the model there), gradients of the fused qkv /
+    gate|up parameters against the concatenated Hugging Face gradients, and cached greedy decoding."""
+    from paddleformers_b200.generation.utils import GenerationConfig, generate
+
+    torch.manual_seed(3)
+    hf_cfg = transformers.LlamaConfig(**{**BASE, "rope_theta": 10000.0})
+    hf = transformers.LlamaForCausalLM(hf_cfg).float()
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    mine = AutoModelForCausalLM.from_pretrained(str(tmp_path), dtype=torch.float32)
+    ids = torch.randint(1, 128, (2, 20))        # 0 is the pad id below: transformers masks pad tokens found in a prompt
+    labels = torch.cat([ids[:, 1:], torch.full((2, 1), -100)], dim=1)          # next-token targets, last position ignored
+    out = mine(ids, labels=labels)
+    want = hf(input_ids=ids, labels=ids)
+    assert out.loss.item() == pytest.approx(want.loss.item(), rel=1e-5)
+    out.loss.backward()
+    want.loss.backward()
+    layer, hl = mine.model.layers["0"], hf.model.layers[0]
+    g_qkv = torch.cat([hl.self_attn.q_proj.weight.grad, hl.self_attn.k_proj.weight.grad, hl.self_attn.v_proj.weight.grad])
+    torch.testing.assert_close(layer.self_attn.qkv_proj.weight.grad, g_qkv, rtol=1e-4, atol=1e-6)
+    g_gu = torch.cat([hl.mlp.gate_proj.weight.grad, hl.mlp.up_proj.weight.grad])
+    torch.testing.assert_close(layer.mlp.gate_up_proj.weight.grad, g_gu, rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(mine.model.embed_tokens.weight.grad, hf.model.embed_tokens.weight.grad, rtol=1e-4, atol=1e-6)
+    prompt = ids[:, :6]
+    mine.eval(); hf.eval()
+    got = generate(mine, prompt, GenerationConfig(max_new_tokens=8))
+    ref = hf.generate(prompt, max_new_tokens=8, do_sample=False, pad_token_id=0)
+    assert torch.equal(got, ref)
