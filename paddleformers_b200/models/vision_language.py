@@ -1,0 +1,313 @@
+"""Qwen2-VL style vision-language model: a ViT with 2-D rotary embedding and a 2x2 patch merger in front of the unified
+decoder, multimodal rotary positions (temporal / height / width sections of the rotary frequencies) in the decoder.
+
+Roles of paddleformers/transformers/qwen2_vl (vision tower, merger, ``get_rope_index``) and of the multimodal collator
+(paddleformers/datasets/collate.py:755 ``mm_collate_fn``). The language model is the ordinary ``DecoderForCausalLM`` with
+Qwen2 settings; multimodal rotary embedding needs no new kernel: the three position streams are folded into one
+per-token cos / sin table, which the rotary kernels index by token number.
+
+Inputs follow the Hugging Face processor: ``pixel_values`` [patches, C * T * P * P] with the patches of every image
+ordered merge-block by merge-block, ``image_grid_thw`` [images, 3], and ``input_ids`` holding one ``image_token_id`` per
+merged patch.
+"""
+from __future__ import annotations
+
+import itertools
+from typing import List, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as TF
+
+from ..ops import functional as F
+from ..transformers.configuration_utils import PretrainedConfig
+from ..transformers.conversion_utils import Rule, WeightMap
+from ..transformers.model_utils import PretrainedModel
+from .configuration import Qwen2Config
+from .modeling import BatchContext, CausalLMOutput, DecoderForCausalLM, build_weight_map
+
+
+class Qwen2VLConfig(PretrainedConfig):
+    model_type = "qwen2_vl"
+
+    def __init__(self, text_config=None, vision_config=None, image_token_id=151655, video_token_id=151656,
+                 vision_start_token_id=151652, vision_end_token_id=151653, **kwargs):
+        text = dict(text_config or {})
+        # older checkpoints keep the text fields at the top level
+        for k in ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
+                  "num_key_value_heads", "max_position_embeddings", "rms_norm_eps", "rope_theta", "rope_scaling",
+                  "rope_parameters", "tie_word_embeddings", "hidden_act"):
+            if k in kwargs and k not in text:
+                text[k] = kwargs.pop(k)
+        tie = bool(text.get("tie_word_embeddings", kwargs.get("tie_word_embeddings", False)))
+        kwargs.setdefault("tie_word_embeddings", tie)
+        kwargs.pop("model_type", None)
+        super().__init__(**{k: v for k, v in kwargs.items() if k not in ("text_config", "vision_config")})
+        text.pop("model_type", None)
+        text.setdefault("tie_word_embeddings", tie)
+        self.text_config = text if isinstance(text, Qwen2Config) else Qwen2Config(**text)
+        rs = self.text_config.rope_scaling or {}
+        rp = text.get("rope_parameters") or {}
+        self.mrope_section = list(rs.get("mrope_section") or rp.get("mrope_section") or [])
+        if rs.get("rope_type", rs.get("type")) in ("mrope", "default"):
+            self.text_config.rope_scaling = None           # the sections only select positions; frequencies are plain
+        v = dict(vision_config or {})
+        v.pop("model_type", None)
+        self.vision_config = {"depth": 32, "embed_dim": 1280, "hidden_size": self.text_config.hidden_size, "hidden_act": "quick_gelu",
+                              "mlp_ratio": 4, "num_heads": 16, "in_channels": 3, "patch_size": 14, "spatial_merge_size": 2,
+                              "temporal_patch_size": 2, **v}
+        self.image_token_id, self.video_token_id = image_token_id, video_token_id
+        self.vision_start_token_id, self.vision_end_token_id = vision_start_token_id, vision_end_token_id
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        text = self.text_config.to_dict(saving)
+        text["model_type"] = "qwen2_vl_text"
+        text["rope_scaling"] = {"type": "mrope", "mrope_section": self.mrope_section}
+        d["text_config"] = text
+        d["vision_config"] = dict(self.vision_config, model_type="qwen2_vl")
+        d.pop("mrope_section", None)
+        return d
+
+
+def _quick_gelu(x):
+    return x * torch.sigmoid(1.702 * x)
+
+
+class _VisionBlock(nn.Module):
+    def __init__(self, dim: int, heads: int, mlp_hidden: int, act: str, dtype=None, device=None):
+        super().__init__()
+        kw = dict(dtype=dtype, device=device)
+        self.norm1 = nn.LayerNorm(dim, eps=1e-6, **kw)
+        self.norm2 = nn.LayerNorm(dim, eps=1e-6, **kw)
+        self.qkv = nn.Linear(dim, 3 * dim, **kw)
+        self.proj = nn.Linear(dim, dim, **kw)
+        self.fc1 = nn.Linear(dim, mlp_hidden, **kw)
+        self.fc2 = nn.Linear(mlp_hidden, dim, **kw)
+        self.heads, self.hd = heads, dim // heads
+        self.act = _quick_gelu if act == "quick_gelu" else getattr(TF, act)
+
+    def forward(self, x, cos, sin, lengths: List[int]):
+        N = x.shape[0]
+        q, k, v = self.qkv(self.norm1(x)).view(N, 3, self.heads, self.hd).unbind(1)
+        half = self.hd // 2
+
+        def rot(t):                                    # 2-D rotary: first half of the pairs from the row, second from the column
+            t1, t2 = t[..., :half].float(), t[..., half:].float()
+            return torch.cat([t1 * cos - t2 * sin, t2 * cos + t1 * sin], dim=-1).to(t.dtype)
+
+        q, k = rot(q), rot(k)
+        outs, off = [], 0
+        for n in lengths:                              # full (non-causal) attention inside each image / frame
+            sl = slice(off, off + n)
+            outs.append(F.flash_attention(q[sl][None], k[sl][None], v[sl][None], causal=False)[0])
+            off += n
+        a = torch.cat(outs, dim=0).reshape(N, -1)
+        x = x + self.proj(a)
+        return x + self.fc2(self.act(self.fc1(self.norm2(x))))
+
+
+class VisionTower(nn.Module):
+    def __init__(self, vc: dict, dtype=None, device=None):
+        super().__init__()
+        kw = dict(dtype=dtype, device=device)
+        self.vc = vc
+        dim = vc["embed_dim"]
+        self.patch_dim = vc["in_channels"] * vc["temporal_patch_size"] * vc["patch_size"] ** 2
+        self.patch_embed = nn.Linear(self.patch_dim, dim, bias=False, **kw)      # the strided Conv3d as one GEMM
+        self.blocks = nn.ModuleList([_VisionBlock(dim, vc["num_heads"], int(dim * vc["mlp_ratio"]), vc["hidden_act"], **kw)
+                                     for _ in range(vc["depth"])])
+        m = vc["spatial_merge_size"] ** 2
+        self.ln_q = nn.LayerNorm(dim, eps=1e-6, **kw)
+        self.merge_fc1 = nn.Linear(dim * m, dim * m, **kw)
+        self.merge_fc2 = nn.Linear(dim * m, vc["hidden_size"], **kw)
+        self.head_dim = dim // vc["num_heads"]
+
+    def rotary(self, grid_thw: torch.Tensor, device):
+        """cos / sin [patches, head_dim / 2]: row position drives the first quarter of the frequencies, column position
+        the second, in the merge-block patch order of the processor."""
+        ms = self.vc["spatial_merge_size"]
+        quarter = self.head_dim // 4
+        inv = 1.0 / (10000.0 ** (torch.arange(0, self.head_dim // 2, 2, dtype=torch.float32, device=device) / (self.head_dim // 2)))
+        out = []
+        for t, h, w in grid_thw.tolist():
+            hp = torch.arange(h, device=device)[:, None].expand(h, w).reshape(h // ms, ms, w // ms, ms).permute(0, 2, 1, 3).flatten()
+            wp = torch.arange(w, device=device)[None, :].expand(h, w).reshape(h // ms, ms, w // ms, ms).permute(0, 2, 1, 3).flatten()
+            ang = torch.cat([hp[:, None].float() * inv[None], wp[:, None].float() * inv[None]], dim=-1)
+            assert ang.shape[1] == 2 * quarter
+            out.append(ang.repeat(t, 1))
+        ang = torch.cat(out, dim=0)[:, None, :]
+        return ang.cos(), ang.sin()
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
+        x = self.patch_embed(pixel_values.to(self.patch_embed.weight.dtype))
+        cos, sin = self.rotary(grid_thw, x.device)
+        lengths = [h * w for t, h, w in grid_thw.tolist() for _ in range(t)]
+        for blk in self.blocks:
+            x = blk(x, cos, sin, lengths)
+        m = self.vc["spatial_merge_size"] ** 2
+        x = self.ln_q(x).view(-1, x.shape[-1] * m)
+        return self.merge_fc2(TF.gelu(self.merge_fc1(x)))
+
+
+def multimodal_position_ids(input_ids: torch.Tensor, image_token_id: int, video_token_id: int, image_grid_thw, video_grid_thw,
+                            merge: int) -> torch.Tensor:
+    """[3, B, S] temporal / height / width positions: text tokens advance all three together; the tokens of an image keep
+    the temporal position fixed and count rows and columns of the merged grid; the next text token continues after the
+    larger of the two extents (the rule of the published Qwen2-VL model code)."""
+    B, S = input_ids.shape
+    pos = torch.zeros(3, B, S, dtype=torch.long, device=input_ids.device)
+    grids = {image_token_id: iter(image_grid_thw.tolist()) if image_grid_thw is not None else iter(()),
+             video_token_id: iter(video_grid_thw.tolist()) if video_grid_thw is not None else iter(())}
+    for b in range(B):
+        row = input_ids[b].tolist()
+        cur, parts = 0, []
+        for is_vis, group in itertools.groupby(range(S), key=lambda i: row[i] if row[i] in grids else -1):
+            idx = list(group)
+            if is_vis == -1:
+                parts.append(torch.arange(cur, cur + len(idx))[None].expand(3, -1))
+                cur += len(idx)
+                continue
+            done = 0
+            while done < len(idx):                     # consecutive images without text in between
+                t, h, w = next(grids[is_vis])
+                gh, gw = h // merge, w // merge
+                n = t * gh * gw
+                wpos = torch.arange(cur, cur + gw).repeat(gh * t)
+                hpos = torch.arange(cur, cur + gh).repeat_interleave(gw * t)
+                tpos = torch.full((n,), cur, dtype=torch.long)
+                parts.append(torch.stack([tpos, hpos, wpos]))
+                cur += max(gh, gw)
+                done += n
+        pos[:, b] = torch.cat(parts, dim=1).to(pos.device)
+    return pos
+
+
+class Qwen2VLForConditionalGeneration(PretrainedModel):
+    config_class = Qwen2VLConfig
+
+    def __init__(self, config: Qwen2VLConfig, dtype=None, device=None):
+        super().__init__(config)
+        self.visual = VisionTower(config.vision_config, dtype=dtype, device=device)
+        self.language = DecoderForCausalLM(config.text_config, dtype=dtype, device=device)
+        # tensor names differ between generations of checkpoints: the vision tower is stored as "visual.*" or
+        # "model.visual.*", the decoder as "model.*" or "model.language_model.*"; both are probed on load, and the writer
+        # uses "model.visual.*" + "model.*", which current and older readers of the format accept
+        self._vision_prefix, self._text_nested = "model.visual.", False
+
+    # ------------------------------------------------------------------ rotary tables
+    def _context(self, input_ids, position_ids3) -> BatchContext:
+        B, S = input_ids.shape
+        lm = self.language.model
+        D = self.config.text_config.head_dim
+        cos_t, sin_t = lm.rope(input_ids.device, int(position_ids3.max().item()) + 1)
+        sections = self.config.mrope_section or [D // 2]
+        axis = torch.repeat_interleave(torch.arange(len(sections), device=input_ids.device) % 3,
+                                       torch.tensor(sections, device=input_ids.device))           # [D / 2] -> t / h / w
+        flat = position_ids3.reshape(3, B * S)
+        sel = flat[axis]                                                                            # [D / 2, B * S]
+        col = torch.arange(D // 2, device=input_ids.device)[:, None]
+        cos = cos_t[sel, col].t().contiguous()                                                      # [B * S, D / 2]
+        sin = sin_t[sel, col].t().contiguous()
+        return BatchContext(B, S, torch.arange(B * S, device=input_ids.device), None, cos, sin)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, input_ids, pixel_values=None, image_grid_thw=None, pixel_values_videos=None, video_grid_thw=None, labels=None,
+                position_ids=None, return_logits: Optional[bool] = None, **unused):
+        cfg, lm = self.config, self.language
+        h = lm.model.embed(input_ids)
+        for pv, grid, tok in ((pixel_values, image_grid_thw, cfg.image_token_id), (pixel_values_videos, video_grid_thw, cfg.video_token_id)):
+            if pv is not None:
+                feats = self.visual(pv, grid).to(h.dtype)
+                mask = (input_ids.reshape(-1) == tok)
+                assert int(mask.sum()) == feats.shape[0], "one placeholder token per merged patch is required"
+                h = h.masked_scatter(mask[:, None], feats)
+        if position_ids is None:
+            position_ids = multimodal_position_ids(input_ids, cfg.image_token_id, cfg.video_token_id, image_grid_thw, video_grid_thw,
+                                                   cfg.vision_config["spatial_merge_size"])
+        ctx = self._context(input_ids, position_ids)
+        hidden, residual = lm.model.run_layers(h, None, ctx)
+        hidden = lm.model.norm(hidden, residual)[0] if residual is not None else lm.model.norm(hidden)
+        out = CausalLMOutput()
+        if return_logits if return_logits is not None else labels is None:
+            out.logits = lm.compute_logits(hidden).view(ctx.B, ctx.S, -1)
+        if labels is not None:
+            lab = labels.reshape(-1)
+            count = (lab != lm.ignore_index).sum()
+            scale = 1.0 / (count.clamp(min=1).to(torch.float32) * float(lm.loss_accumulation_steps))
+            out.loss, _ = lm._loss(hidden, lab, scale)
+            out.num_tokens = count
+        return out
+
+    @property
+    def loss_accumulation_steps(self):
+        return self.language.loss_accumulation_steps
+
+    @loss_accumulation_steps.setter
+    def loss_accumulation_steps(self, v):
+        self.language.loss_accumulation_steps = v
+
+    # ------------------------------------------------------------------ checkpoint names
+    def load_hf_checkpoint(self, directory: str, strict: bool = False) -> None:
+        from ..transformers.model_utils import _CheckpointReader
+
+        reader = _CheckpointReader(directory)
+        saved = (self._vision_prefix, self._text_nested)
+        self._vision_prefix = "visual." if reader.has("visual.patch_embed.proj.weight") else "model.visual."
+        self._text_nested = reader.has("model.language_model.embed_tokens.weight")
+        try:
+            super().load_hf_checkpoint(directory, strict)
+        finally:
+            self._vision_prefix, self._text_nested = saved
+
+    def weight_map(self) -> WeightMap:
+        vis = self._vision_prefix
+
+        def text_name(s: str) -> str:
+            if s.startswith("lm_head.") or not self._text_nested:
+                return s
+            return s.replace("model.", "model.language_model.", 1)
+
+        rules = []
+        for r in build_weight_map(self.config.text_config).rules.values():
+            rules.append(Rule("language." + r.target, [text_name(s) for s in r.sources], r.op, r.dim, r.num_experts, r.expert_pairs,
+                              r.sizes, r.rope_deinterleave, r.flatten))
+        known = {r.target for r in rules}
+        for name, _ in self.language.named_parameters():                 # parameters without a fusion rule: renamed only
+            t = "language." + name
+            if t not in known:
+                rules.append(Rule(t, [text_name(name)]))
+        vc = self.config.vision_config
+        conv_shape = [vc["embed_dim"], vc["in_channels"], vc["temporal_patch_size"], vc["patch_size"], vc["patch_size"]]
+        rules.append(Rule("visual.patch_embed.weight", [vis + "patch_embed.proj.weight"], reshape=[vc["embed_dim"], -1],
+                          source_shape=conv_shape))
+        for i in range(vc["depth"]):
+            a, b = f"visual.blocks.{i}.", vis + f"blocks.{i}."
+            for mine, theirs in (("norm1", "norm1"), ("norm2", "norm2"), ("qkv", "attn.qkv"), ("proj", "attn.proj"),
+                                 ("fc1", "mlp.fc1"), ("fc2", "mlp.fc2")):
+                for leaf in ("weight", "bias"):
+                    rules.append(Rule(a + f"{mine}.{leaf}", [b + f"{theirs}.{leaf}"]))
+        for mine, theirs in (("ln_q", "merger.ln_q"), ("merge_fc1", "merger.mlp.0"), ("merge_fc2", "merger.mlp.2")):
+            for leaf in ("weight", "bias"):
+                rules.append(Rule(f"visual.{mine}.{leaf}", [vis + f"{theirs}.{leaf}"]))
+        return WeightMap(rules)
+
+
+def mm_collate_fn(examples: List[dict], pad_token_id: int = 0, ignore_index: int = -100) -> dict:
+    """Batch multimodal examples: ``input_ids`` / ``labels`` are padded to the longest row, the patch tensors of all
+    images are concatenated in example order with their grids (the layout ``Qwen2VLForConditionalGeneration`` expects)."""
+    S = max(len(e["input_ids"]) for e in examples)
+    ids = torch.full((len(examples), S), pad_token_id, dtype=torch.long)
+    labels = torch.full((len(examples), S), ignore_index, dtype=torch.long)
+    for i, e in enumerate(examples):
+        n = len(e["input_ids"])
+        ids[i, :n] = torch.as_tensor(e["input_ids"])
+        if "labels" in e:
+            labels[i, :n] = torch.as_tensor(e["labels"])
+    out = {"input_ids": ids, "labels": labels}
+    pv = [torch.as_tensor(e["pixel_values"]) for e in examples if e.get("pixel_values") is not None]
+    if pv:
+        out["pixel_values"] = torch.cat(pv, dim=0)
+        out["image_grid_thw"] = torch.cat([torch.as_tensor(e["image_grid_thw"]).reshape(-1, 3) for e in examples
+                                           if e.get("image_grid_thw") is not None], dim=0)
+    return out

@@ -43,6 +43,29 @@ class AutoModelForCausalLM:
         return cls._cls(config).from_pretrained(path, config=config, dtype=dtype, device=device, **kw)
 
 
+class AutoModelForConditionalGeneration:
+    """Vision-language models (image / video placeholders in the token stream)."""
+
+    @staticmethod
+    def _classes(model_type: str):
+        from ..models.vision_language import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+
+        table = {"qwen2_vl": (Qwen2VLConfig, Qwen2VLForConditionalGeneration)}
+        if model_type not in table:
+            raise ValueError(f"unknown vision-language model_type {model_type!r}; supported: {sorted(table)}")
+        return table[model_type]
+
+    @classmethod
+    def from_config(cls, config, dtype=None, device=None, **kw):
+        return cls._classes(config.model_type)[1].from_config(config, dtype=dtype, device=device, **kw)
+
+    @classmethod
+    def from_pretrained(cls, path: str, dtype=None, device=None, **kw):
+        mt = PretrainedConfig.get_config_dict(path).get("model_type")
+        cfg_cls, model_cls = cls._classes(mt)
+        return model_cls.from_pretrained(path, config=cfg_cls.from_pretrained(path), dtype=dtype, device=device, **kw)
+
+
 class AutoModelForCausalLMPipe(AutoModelForCausalLM):
     """Pipeline-parallel variant: builds only this stage's layers (see ``parallel.pipeline``)."""
 

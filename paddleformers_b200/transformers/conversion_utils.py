@@ -103,6 +103,8 @@ class Rule:
     rope_deinterleave: Optional[Dict[int, object]] = None  # source index -> head_dim | (head_size, rope_offset, rope_dim):
     #                                                          rows stored in interleaved rotary order
     flatten: bool = False              # rename: the checkpoint stores the tensor with a leading unit dimension
+    reshape: Optional[List[int]] = None        # rename: shape of the internal parameter (e.g. a Conv3d kernel used as a matrix)
+    source_shape: Optional[List[int]] = None   # rename: shape of the tensor in the checkpoint, for the way back
 
     def _load(self, i: int, t: torch.Tensor) -> torch.Tensor:
         if self.rope_deinterleave and i in self.rope_deinterleave:
@@ -122,6 +124,8 @@ class Rule:
     def forward(self, get: Callable[[str], torch.Tensor], expert_range: Optional[range] = None) -> torch.Tensor:
         if self.op == "rename":
             t = self._load(0, get(self.sources[0]))
+            if self.reshape is not None:
+                return t.reshape(self.reshape)
             return t.reshape(-1) if self.flatten else t
         if self.op == "concat":
             return torch.cat([self._load(i, get(s)) for i, s in enumerate(self.sources)], dim=self.dim)
@@ -135,6 +139,8 @@ class Rule:
     def inverse(self, tensor: torch.Tensor, section_sizes: Optional[List[int]] = None, expert_offset: int = 0) -> Dict[str, torch.Tensor]:
         if self.op == "rename":
             t = self._store(0, tensor)
+            if self.source_shape is not None:
+                return {self.sources[0]: t.reshape(self.source_shape)}
             return {self.sources[0]: t.reshape(1, -1) if self.flatten else t}
         if self.op == "concat":
             sizes = section_sizes or self.sizes or [tensor.shape[self.dim] // len(self.sources)] * len(self.sources)

@@ -1,0 +1,84 @@
+"""Image pre-processing for the vision-language models: dynamic-resolution resize, normalisation and patch extraction in
+the order the vision tower expects (roles of paddleformers/transformers/image_processing_utils.py and the Qwen2-VL
+image processor of the reference).
+
+``Qwen2VLImageProcessor.__call__(images)`` returns ``pixel_values`` [patches, C * T * P * P] and ``image_grid_thw``
+[images, 3]: every image is resized so that both sides are multiples of ``patch_size * merge_size`` with the number of
+pixels inside [min_pixels, max_pixels], scaled to [0, 1], normalised, repeated along time to ``temporal_patch_size``
+frames, and cut into patches ordered merge-block by merge-block (the 2 x 2 patches that the merger fuses are adjacent).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+OPENAI_CLIP_MEAN = (0.48145466, 0.4578275, 0.40821073)
+OPENAI_CLIP_STD = (0.26862954, 0.26130258, 0.27577711)
+
+
+def smart_resize(height: int, width: int, factor: int = 28, min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 1280):
+    """Target size: both sides multiples of ``factor``, area within the pixel budget, aspect ratio kept as far as the
+    rounding allows."""
+    if max(height, width) / min(height, width) > 200:
+        raise ValueError("aspect ratio above 200 is not supported")
+    h = max(factor, round(height / factor) * factor)
+    w = max(factor, round(width / factor) * factor)
+    if h * w > max_pixels:
+        beta = math.sqrt(height * width / max_pixels)
+        h = max(factor, math.floor(height / beta / factor) * factor)
+        w = max(factor, math.floor(width / beta / factor) * factor)
+    elif h * w < min_pixels:
+        beta = math.sqrt(min_pixels / (height * width))
+        h = math.ceil(height * beta / factor) * factor
+        w = math.ceil(width * beta / factor) * factor
+    return h, w
+
+
+def _resize(img: np.ndarray, h: int, w: int) -> np.ndarray:
+    try:
+        from PIL import Image
+
+        return np.asarray(Image.fromarray(img).resize((w, h), resample=Image.BICUBIC))
+    except ImportError:
+        t = torch.from_numpy(img).permute(2, 0, 1)[None].float()
+        t = torch.nn.functional.interpolate(t, size=(h, w), mode="bicubic", align_corners=False, antialias=True)
+        return t[0].permute(1, 2, 0).round().clamp(0, 255).to(torch.uint8).numpy()
+
+
+class Qwen2VLImageProcessor:
+    def __init__(self, patch_size: int = 14, merge_size: int = 2, temporal_patch_size: int = 2, min_pixels: int = 56 * 56,
+                 max_pixels: int = 28 * 28 * 1280, image_mean: Sequence[float] = OPENAI_CLIP_MEAN,
+                 image_std: Sequence[float] = OPENAI_CLIP_STD, rescale_factor: float = 1.0 / 255.0):
+        self.patch_size, self.merge_size, self.temporal_patch_size = patch_size, merge_size, temporal_patch_size
+        self.min_pixels, self.max_pixels = min_pixels, max_pixels
+        self.mean = np.asarray(image_mean, dtype=np.float32)
+        self.std = np.asarray(image_std, dtype=np.float32)
+        self.rescale_factor = rescale_factor
+
+    def preprocess_one(self, img: np.ndarray):
+        """img: uint8 [H, W, 3]. Returns (patches [grid_h * grid_w, C * T * P * P] float32, (1, grid_h, grid_w))."""
+        P, m, T = self.patch_size, self.merge_size, self.temporal_patch_size
+        h, w = smart_resize(img.shape[0], img.shape[1], P * m, self.min_pixels, self.max_pixels)
+        x = _resize(np.ascontiguousarray(img), h, w).astype(np.float32) * self.rescale_factor
+        x = (x - self.mean) / self.std
+        x = np.transpose(x, (2, 0, 1))[None].repeat(T, axis=0)               # [T, C, H, W]: a still image fills every frame
+        gh, gw = h // P, w // P
+        C = x.shape[1]
+        x = x.reshape(1, T, C, gh // m, m, P, gw // m, m, P)
+        x = x.transpose(0, 3, 6, 4, 7, 2, 1, 5, 8)                          # [1, gh/m, gw/m, m, m, C, T, P, P]
+        return x.reshape(gh * gw, C * T * P * P), (1, gh, gw)
+
+    def __call__(self, images: List[np.ndarray], return_tensors: str = "pt"):
+        patches, grids = zip(*(self.preprocess_one(np.asarray(im)) for im in images))
+        pv = np.concatenate(patches, axis=0)
+        grid = np.asarray(grids, dtype=np.int64)
+        if return_tensors == "pt":
+            return {"pixel_values": torch.from_numpy(pv), "image_grid_thw": torch.from_numpy(grid)}
+        return {"pixel_values": pv, "image_grid_thw": grid}
+
+    def num_image_tokens(self, grid_thw) -> int:
+        t, h, w = (int(v) for v in grid_thw)
+        return t * h * w // (self.merge_size ** 2)
