@@ -57,6 +57,7 @@ class _Domain:
     offsets: Dict[str, Tuple[int, int]] = field(default_factory=dict)
     numel: int = 0
     is_expert: bool = False
+    is_muon: bool = False          # matrices updated by the orthogonalised-momentum rule (see ShardedMuon)
 
     @property
     def shard_numel(self) -> int:
@@ -94,24 +95,29 @@ class ShardedAdamW:
         for name, p in model.named_parameters():
             if not p.requires_grad:
                 continue
-            key = (bool(getattr(p, "is_expert", False)), bool(no_decay_fn(name)), p.dtype)
+            key = (bool(getattr(p, "is_expert", False)), bool(no_decay_fn(name)), p.dtype, bool(self._is_muon_param(name, p)))
             groups.setdefault(key, []).append((name, p))
         expert_scale = float(d.mp * d.cp) / float(d.ep) if d.ep > 1 else 1.0
-        for (is_expert, no_decay, dtype), plist in sorted(groups.items(), key=lambda kv: (kv[0][0], kv[0][1], str(kv[0][2]))):
+        for (is_expert, no_decay, dtype, is_muon), plist in sorted(groups.items(),
+                                                                   key=lambda kv: (kv[0][0], kv[0][1], str(kv[0][2]), kv[0][3])):
             if is_expert and d.ep > 1:
                 sg, ssz, srk, extra = ps.group("moe_sharding"), ps.size("moe_sharding"), ps.rank_in("moe_sharding"), None
             else:
                 sg, ssz, srk = ps.group("sharding"), d.sharding, ps.coord["sharding"]
                 extra = ps.group("dp_sep_cp") if d.dp * d.sep * d.cp > 1 else None
-            dom = _Domain(name=f"{'expert' if is_expert else 'dense'}_{'nodecay' if no_decay else 'decay'}_{str(dtype)[6:]}",
+            dom = _Domain(name=f"{'expert' if is_expert else 'dense'}_{'nodecay' if no_decay else 'decay'}_{str(dtype)[6:]}"
+                               + ("_muon" if is_muon else ""),
                           params=plist, weight_decay=0.0 if no_decay else weight_decay, shard_group=sg if ssz > 1 else None,
                           shard_size=ssz, shard_rank=srk, extra_reduce_group=extra,
-                          grad_scale=expert_scale if is_expert else 1.0, is_expert=is_expert)
+                          grad_scale=expert_scale if is_expert else 1.0, is_expert=is_expert, is_muon=is_muon)
             self._build_domain(dom, dtype)
             self.domains.append(dom)
         dev = self.domains[0].flat_param.device if self.domains else torch.device("cpu")
         self._scalars = torch.zeros(8, dtype=torch.float32, device=dev)
         self._norm_acc = torch.zeros(1, dtype=torch.float32, device=dev)
+
+    def _is_muon_param(self, name: str, p) -> bool:
+        return False
 
     # ------------------------------------------------------------------ construction
     def _build_domain(self, dom: _Domain, dtype):
@@ -250,7 +256,9 @@ class ShardedAdamW:
         sc[4] = (~finite).to(torch.float32)   # non-finite gradient: skip the update
         for dom, g in zip(self.domains, shards):
             pslice = dom.shard_slice(dom.flat_param)
-            if g.is_cuda:
+            if dom.is_muon:
+                self._muon_update(dom, g, pslice, sc)
+            elif g.is_cuda:
                 p16 = pslice if pslice.dtype == torch.bfloat16 else None
                 torch.ops.pfb200.adamw_step(dom.master, dom.exp_avg, dom.exp_avg_sq, g, p16, sc, b1, b2, self.eps,
                                             dom.weight_decay)
@@ -263,6 +271,9 @@ class ShardedAdamW:
                 dist.all_gather_into_tensor(dom.flat_param, pslice.clone(), group=dom.shard_group)
             dom.flat_grad.zero_()
         return gnorm
+
+    def _muon_update(self, dom, g, pslice, sc):
+        raise NotImplementedError
 
     def _adamw_cpu(self, dom, g, pslice, sc):
         if float(sc[4]) != 0.0:
@@ -306,3 +317,63 @@ class ShardedAdamW:
         for dom in self.domains:
             tot += dom.flat_param.numel() * dom.flat_param.element_size() + dom.flat_grad.numel() * 4 + dom.master.numel() * 12
         return tot
+
+
+def newton_schulz_orthogonalize(G: torch.Tensor, steps: int = 5) -> torch.Tensor:
+    """Approximate U V^T of G = U S V^T with the quintic Newton-Schulz iteration (coefficients 3.4445, -4.7750, 2.0315) on
+    the Frobenius-normalised matrix, in bf16 on GPUs: singular values end up in roughly [0.7, 1.2], which is all the
+    Muon update needs."""
+    a, b, c = 3.4445, -4.7750, 2.0315
+    X = G.to(torch.bfloat16 if G.is_cuda else torch.float32)
+    transposed = X.shape[-2] > X.shape[-1]
+    if transposed:
+        X = X.transpose(-2, -1)
+    X = X / (X.norm(dim=(-2, -1), keepdim=True) + 1e-7)
+    for _ in range(steps):
+        A = X @ X.transpose(-2, -1)
+        B = b * A + c * (A @ A)
+        X = a * X + B @ X
+    if transposed:
+        X = X.transpose(-2, -1)
+    return X.to(torch.float32)
+
+
+class ShardedMuon(ShardedAdamW):
+    """Muon for the hidden weight matrices, AdamW for everything else (embeddings, head, norms, biases, routers), over
+    the same flat buffers and with the same gradient reduction and clipping. A matrix's update is its Nesterov momentum,
+    orthogonalised by Newton-Schulz and scaled by 0.2 * sqrt(max(rows, cols)) so that one learning rate and one weight
+    decay serve both rules. Stacked expert weights [E, N, K] are treated as E matrices. The reference exposes the same
+    choice through Paddle's optimizer (paddleformers/trainer/trainer.py:3897).
+
+    The orthogonalisation needs whole matrices: Muon domains must not be split over a sharding group (each rank then
+    repeats the same update on its replica), which the constructor enforces."""
+
+    def __init__(self, *args, momentum: float = 0.95, nesterov: bool = True, ns_steps: int = 5, **kw):
+        self.momentum, self.nesterov, self.ns_steps = momentum, nesterov, ns_steps
+        super().__init__(*args, **kw)
+        for dom in self.domains:
+            if dom.is_muon and dom.shard_size > 1:
+                raise ValueError("ShardedMuon: hidden matrices cannot be sharded over the optimizer-sharding group; use "
+                                 "sharding degree 1 (data parallel replicas repeat the update) or AdamW")
+
+    def _is_muon_param(self, name: str, p) -> bool:
+        if p.dim() < 2 or "embed" in name or "lm_head" in name or name.endswith("gate.weight"):
+            return False
+        return True
+
+    def _muon_update(self, dom, g, pslice, sc):
+        lr, gmul, skip = sc[0], sc[1], sc[4]
+        dom.exp_avg.mul_(self.momentum).add_(g * gmul)                    # momentum buffer lives where Adam's first moment does
+        upd = torch.zeros_like(dom.master)
+        for name, p in dom.params:
+            off, n = dom.offsets[name]
+            m = dom.exp_avg[off:off + n].view(p.shape)
+            gr = (g[off:off + n].view(p.shape) * gmul)
+            d = gr + self.momentum * m if self.nesterov else m
+            mats = d.reshape(-1, d.shape[-2], d.shape[-1])
+            o = newton_schulz_orthogonalize(mats, self.ns_steps)
+            scale = 0.2 * math.sqrt(max(d.shape[-2], d.shape[-1]))
+            upd[off:off + n] = (o * scale).reshape(-1)
+        keep = 1.0 - skip                                                  # non-finite gradients: leave the weights alone
+        dom.master.mul_(1.0 - lr * dom.weight_decay * keep).add_(upd * (-(lr * keep)))
+        pslice.copy_(dom.master)

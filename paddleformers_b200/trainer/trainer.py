@@ -162,7 +162,14 @@ class Trainer:
     def create_optimizer_and_scheduler(self, num_training_steps: int):
         a = self.args
         if self.optimizer is None:
-            self.optimizer = ShardedAdamW(self.model, lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2),
+            opt_cls = ShardedAdamW
+            if str(getattr(a, "optim", "adamw")).lower() == "muon":
+                from ..parallel.sharding import ShardedMuon
+
+                opt_cls = ShardedMuon
+            elif str(getattr(a, "optim", "adamw")).lower() not in ("adamw", "adamw_torch", "adamw_fused"):
+                raise ValueError(f"optim={a.optim!r}: expected adamw or muon")
+            self.optimizer = opt_cls(self.model, lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2),
                                           eps=a.adam_epsilon, weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm,
                                           parallel_state=self.ps, release_grads=a.release_grads)
         if self.lr_scheduler is None:

@@ -28,8 +28,10 @@ def _make(tmp, steps, **kw):
             cfg.intermediate_size, cfg.vocab_size) == (2, 256, 4, 2, 64, 688, 32000)
     model = AutoModelForCausalLM.from_config(cfg)
     ds = _Fixed(SyntheticCausalLMDataset(32000, 128, 8, seed=0), 64)
-    args = TrainingArguments(output_dir=str(tmp), per_device_train_batch_size=2, max_steps=steps, learning_rate=1e-4,
-                             logging_steps=1, save_steps=5, max_seq_len=128, lr_scheduler_type="constant", **kw)
+    base = dict(output_dir=str(tmp), per_device_train_batch_size=2, max_steps=steps, learning_rate=1e-4, logging_steps=1,
+                save_steps=5, max_seq_len=128, lr_scheduler_type="constant")
+    base.update(kw)
+    args = TrainingArguments(**base)
     return model, Trainer(model=model, args=args, train_dataset=ds)
 
 
@@ -140,3 +142,22 @@ def test_ema_tracks_master_weights_and_exports(tmp_path):
     m2 = AutoModelForCausalLM.from_pretrained(out)
     diffs = [(m2.state_dict()[k].float() - live[k].float()).abs().max().item() for k in live]
     assert max(diffs) > 0 and max(diffs) < 1e-2
+
+
+def test_muon_orthogonalises_matrix_updates_and_trains(tmp_path):
+    from paddleformers_b200.parallel.sharding import ShardedMuon, newton_schulz_orthogonalize
+
+    torch.manual_seed(0)
+    G = torch.randn(48, 80)
+    sv = torch.linalg.svdvals(newton_schulz_orthogonalize(G))
+    assert sv.min() > 0.5 and sv.max() < 1.3                       # all singular values pushed towards one
+    _, tr = _make(tmp_path, 8, optim="muon", save_strategy="no", learning_rate=2e-3)
+    tr.train()
+    assert isinstance(tr.optimizer, ShardedMuon)
+    names = {d.name: [n for n, _ in d.params] for d in tr.optimizer.domains}
+    muon = [n for k, v in names.items() if k.endswith("_muon") for n in v]
+    adam = [n for k, v in names.items() if not k.endswith("_muon") for n in v]
+    assert any("qkv_proj" in n for n in muon) and any("down_proj" in n for n in muon)
+    assert any("embed_tokens" in n for n in adam) and any("norm" in n for n in adam) and not any("embed" in n for n in muon)
+    losses = [h["loss"] for h in tr.state.log_history if "loss" in h]
+    assert losses[-1] < losses[0] - 0.05
