@@ -54,6 +54,8 @@ class DataArguments:
     streaming: bool = False
     train_on_prompt: bool = False
     num_samples_each_epoch: int = 0
+    min_pixels: Optional[int] = field(default=None, metadata={"help": "VL stages: lower bound of the resized image area"})
+    max_pixels: Optional[int] = field(default=None, metadata={"help": "VL stages: upper bound of the resized image area"})
 
 
 @dataclass

@@ -144,7 +144,9 @@ def run_dpo(model_args, data_args, gen_args, train_args):
 def run_tuner(argv: Optional[list] = None):
     model_args, data_args, gen_args, export_args, train_args = get_train_args(argv)
     stage = model_args.stage.upper()
-    if stage in ("SFT", "VL-SFT"):
+    if stage == "VL-SFT":
+        return run_vl_sft(model_args, data_args, gen_args, train_args)
+    if stage == "SFT":
         return run_sft(model_args, data_args, gen_args, train_args)
     if stage in ("PT", "CPT", "VL-PT"):
         return run_sft(model_args, data_args, gen_args, train_args, pretrain=True)
@@ -153,6 +155,42 @@ def run_tuner(argv: Optional[list] = None):
     if stage in ("AUTO-PARALLEL", "AUTO_PARALLEL"):
         return run_auto_parallel(model_args, data_args, gen_args, train_args)
     raise ValueError(f"unknown stage {model_args.stage!r}; expected SFT | PT | DPO | auto-parallel")
+
+
+def run_vl_sft(model_args, data_args, gen_args, train_args):
+    """Supervised fine-tuning of a vision-language model on conversations with images
+    (paddleformers/cli/train/tuner.py:33-68 routes VL-SFT to the same workflow with multimodal data plugins)."""
+    import functools as ft
+
+    from ..datasets.mm_dataset import MMSFTDataset
+    from ..models.vision_language import mm_collate_fn
+    from ..trainer.trainer import Trainer
+    from ..transformers.auto import AutoModelForConditionalGeneration
+    from ..transformers.image_processing import Qwen2VLImageProcessor
+
+    train_args.setup_parallel()
+    dtype = train_args.compute_dtype
+    model = AutoModelForConditionalGeneration.from_pretrained(model_args.model_name_or_path, dtype=dtype,
+                                                              device=torch.device(train_args.device))
+    tokenizer = _tokenizer(model_args)
+    if tokenizer is None:
+        raise ValueError("VL-SFT needs a tokenizer (model_name_or_path with tokenizer files)")
+    vc = model.config.vision_config
+    proc_kw = dict(patch_size=vc["patch_size"], merge_size=vc["spatial_merge_size"], temporal_patch_size=vc["temporal_patch_size"])
+    for k in ("min_pixels", "max_pixels"):
+        if getattr(data_args, k, None):
+            proc_kw[k] = getattr(data_args, k)
+    proc = Qwen2VLImageProcessor(**proc_kw)
+    names = dict(image_token=tokenizer.convert_ids_to_tokens(model.config.image_token_id),
+                 vision_start_token=tokenizer.convert_ids_to_tokens(model.config.vision_start_token_id),
+                 vision_end_token=tokenizer.convert_ids_to_tokens(model.config.vision_end_token_id))
+    train_ds = MMSFTDataset(data_args.train_dataset_path, tokenizer, proc, data_args.template, train_args.max_seq_len, **names)
+    pad = tokenizer.pad_token_id if tokenizer.pad_token_id is not None else 0
+    trainer = Trainer(model=model, args=train_args, train_dataset=train_ds, data_collator=ft.partial(mm_collate_fn, pad_token_id=pad),
+                      tokenizer=tokenizer)
+    metrics = trainer.train(resume_from_checkpoint=train_args.resume_from_checkpoint)
+    trainer.save_model(train_args.output_dir)
+    return trainer, metrics
 
 
 def run_auto_parallel(model_args, data_args, gen_args, train_args):

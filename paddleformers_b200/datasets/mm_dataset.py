@@ -1,0 +1,83 @@
+"""Multimodal SFT examples: chat messages with ``<image>`` markers plus image files -> token ids with one placeholder
+token per merged patch, labels, pixel patches and grids (the job of the reference's multimodal plugins,
+paddleformers/datasets/template/mm_plugin.py, and ``mm_collate_fn``, paddleformers/datasets/collate.py:755).
+
+Every ``<image>`` in a message is replaced by ``vision_start + image_pad * n + vision_end`` where n is the number of
+merged patches of the corresponding image after pre-processing; the expansion is done on token ids, so the tokenizer
+only has to know the three special tokens.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import numpy as np
+import torch
+from torch.utils.data import Dataset
+
+from .sft_dataset import IGNORE_INDEX, read_examples, to_messages
+from .template import get_template
+
+IMAGE_MARKER = "<image>"
+
+
+def _load_image(path_or_array) -> np.ndarray:
+    if isinstance(path_or_array, np.ndarray):
+        return path_or_array
+    from PIL import Image
+
+    return np.asarray(Image.open(path_or_array).convert("RGB"))
+
+
+class MMSFTDataset(Dataset):
+    def __init__(self, path_or_examples, tokenizer, image_processor, template: Optional[str], max_seq_len: int,
+                 image_token: str = "<|image_pad|>", vision_start_token: str = "<|vision_start|>",
+                 vision_end_token: str = "<|vision_end|>"):
+        self.examples = list(read_examples(path_or_examples)) if isinstance(path_or_examples, str) else list(path_or_examples)
+        self.tok, self.proc, self.template, self.max_seq_len = tokenizer, image_processor, get_template(template), max_seq_len
+        ids = tokenizer.convert_tokens_to_ids([image_token, vision_start_token, vision_end_token])
+        if any(i is None or i == tokenizer.unk_token_id for i in ids):
+            raise ValueError("the tokenizer must know the image placeholder and vision start / end tokens")
+        self.image_id, self.start_id, self.end_id = ids
+        self.marker_ids = tokenizer.encode(IMAGE_MARKER, add_special_tokens=False)
+
+    def __len__(self):
+        return len(self.examples)
+
+    def _expand(self, ids: List[int], mask: List[int], counts: List[int]):
+        """Replace every occurrence of the marker's token sequence by the placeholder run of the next image."""
+        out_ids, out_mask, k, i, m = [], [], 0, 0, len(self.marker_ids)
+        while i < len(ids):
+            if m and ids[i:i + m] == self.marker_ids and k < len(counts):
+                run = [self.start_id] + [self.image_id] * counts[k] + [self.end_id]
+                out_ids += run
+                out_mask += [0] * len(run)            # image tokens are context, never targets
+                k += 1
+                i += m
+            else:
+                out_ids.append(ids[i])
+                out_mask.append(mask[i])
+                i += 1
+        if k != len(counts):
+            raise ValueError(f"{len(counts)} images but {k} {IMAGE_MARKER} markers in the conversation")
+        return out_ids, out_mask
+
+    def __getitem__(self, i):
+        ex = self.examples[i]
+        images = [_load_image(p) for p in ex.get("images", [])]
+        item = {}
+        counts: List[int] = []
+        if images:
+            pre = self.proc(images)
+            item["pixel_values"], item["image_grid_thw"] = pre["pixel_values"], pre["image_grid_thw"]
+            counts = [self.proc.num_image_tokens(g) for g in pre["image_grid_thw"].tolist()]
+        norm = to_messages(ex)
+        ids, mask = [], []
+        for p_ids, r_ids in self.template.encode_multiturn(self.tok, norm["messages"], norm["system"], norm["tools"]):
+            ids += p_ids + r_ids
+            mask += [0] * len(p_ids) + [1] * len(r_ids)
+        ids, mask = self._expand(ids, mask, counts)
+        if len(ids) > self.max_seq_len + 1:
+            raise ValueError(f"example {i} needs {len(ids)} tokens (images are not truncated); raise max_seq_len")
+        item["input_ids"] = torch.tensor(ids[:-1])
+        item["labels"] = torch.tensor([t if m else IGNORE_INDEX for t, m in zip(ids[1:], mask[1:])])
+        return item

@@ -120,3 +120,54 @@ def test_sft_lora_stage_then_export_merges_adapters(tmp_path):
     model = AutoModelForCausalLM.from_pretrained(str(final), dtype=torch.float32)
     assert not any("lora_" in n for n, _ in model.named_parameters())
     assert os.path.exists(final / "tokenizer.json")
+
+
+def test_vl_sft_stage_trains_on_images(tmp_path):
+    """VL-SFT stage: conversations with <image> markers and image files, a Qwen2-VL directory with tokenizer files."""
+    from PIL import Image
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    from paddleformers_b200.cli.cli import main
+    from paddleformers_b200.models.vision_language import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    words = ["<pad>", "<s>", "</s>", "<unk>", "Human:", "Assistant:", "System:", "<image>", "<|image_pad|>", "<|vision_start|>",
+             "<|vision_end|>"] + [f"w{i}" for i in range(40)]
+    tok = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    fast = PreTrainedTokenizerFast(tokenizer_object=tok, pad_token="<pad>", bos_token="<s>", eos_token="</s>", unk_token="<unk>")
+    base = tmp_path / "base"
+    cfg = Qwen2VLConfig(text_config=dict(vocab_size=len(words), hidden_size=32, intermediate_size=48, num_hidden_layers=1,
+                                         num_attention_heads=2, num_key_value_heads=1, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}),
+                        vision_config=dict(depth=1, embed_dim=16, hidden_size=32, mlp_ratio=2, num_heads=2, patch_size=4),
+                        image_token_id=words.index("<|image_pad|>"), vision_start_token_id=words.index("<|vision_start|>"),
+                        vision_end_token_id=words.index("<|vision_end|>"))
+    torch.manual_seed(0)
+    Qwen2VLForConditionalGeneration(cfg, dtype=torch.float32).save_pretrained(str(base))
+    fast.save_pretrained(str(base))
+    rng = np.random.RandomState(0)
+    data = tmp_path / "vl.jsonl"
+    with open(data, "w") as f:
+        for i in range(8):
+            img = tmp_path / f"img{i}.png"
+            Image.fromarray((rng.rand(20 + 4 * (i % 3), 24, 3) * 255).astype("uint8")).save(img)
+            f.write(json.dumps({"images": [str(img)], "messages": [{"role": "user", "content": "<image> w1 w2"},
+                                                                     {"role": "assistant", "content": f"w{3 + i % 5} w9"}]}) + "\n")
+    out = tmp_path / "out"
+    cfg_file = tmp_path / "vl.json"
+    cfg_file.write_text(json.dumps({
+        "stage": "VL-SFT", "model_name_or_path": str(base), "compute_type": "float32", "device": "cpu", "train_dataset_path": str(data),
+        "template": "default", "max_seq_len": 64, "max_steps": 4, "per_device_train_batch_size": 1, "learning_rate": 5e-3,
+        "logging_steps": 1, "save_strategy": "no", "output_dir": str(out), "min_pixels": 256, "max_pixels": 4096}))
+    env = os.environ.get("CUDA_VISIBLE_DEVICES")
+    os.environ["CUDA_VISIBLE_DEVICES"] = ""
+    try:
+        assert main(["train", str(cfg_file)]) == 0
+    finally:
+        if env is None:
+            os.environ.pop("CUDA_VISIBLE_DEVICES", None)
+        else:
+            os.environ["CUDA_VISIBLE_DEVICES"] = env
+    model = AutoModelForConditionalGeneration.from_pretrained(str(out), dtype=torch.float32)
+    assert model.visual.patch_embed.weight.shape == (16, 3 * 2 * 4 * 4) and os.path.exists(out / "tokenizer.json")
