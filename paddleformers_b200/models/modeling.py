@@ -151,6 +151,14 @@ class Attention(nn.Module):
             qkv = F.rope_packed(qkv, ctx.cos, ctx.sin, ctx.positions, self.Hq, self.Hkv, self.D, self.rot)
         if cache is not None:
             out = cache.attend(self, qkv, ctx)
+        elif getattr(self.config, "_attn_implementation", None) in ("eager", "sdpa") and not ctx.S_full:
+            from ..nn.attention import AttentionInterface      # reference back-ends, selectable like the reference's
+
+            B, S, D = ctx.B, ctx.S, self.D
+            q, k, v = qkv.view(B, S, -1).split([self.Hq * D, self.Hkv * D, self.Hkv * D], dim=-1)
+            out = AttentionInterface.get(self.config._attn_implementation)(
+                q.reshape(B, S, self.Hq, D), k.reshape(B, S, self.Hkv, D), v.reshape(B, S, self.Hkv, D), ctx.kend, self.scale)
+            out = out.reshape(B * S, self.Hq * D)
         elif ctx.S_full:
             B, S, D = ctx.B, ctx.S, self.D
             q, k, v = qkv.view(B, S, -1).split([self.Hq * D, self.Hkv * D, self.Hkv * D], dim=-1)

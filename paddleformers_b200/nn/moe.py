@@ -41,6 +41,25 @@ class AddAuxiliaryLoss(torch.autograd.Function):
 
 
 class TopkRouter(nn.Module):
+    def _capacity_mask(self, idx: torch.Tensor, w: torch.Tensor, T: int, E: int) -> torch.Tensor:
+        """1 for routed pairs inside their expert's capacity, 0 for dropped ones; no host synchronisation."""
+        cap = int(math.ceil(self.capacity_factor * T * self.top_k / E))
+        flat_e = idx.reshape(-1)
+        n = flat_e.numel()
+        if self.drop_policy == "position":
+            prio = torch.arange(n, device=idx.device, dtype=torch.float32)              # earlier pairs first
+        else:
+            prio = -w.reshape(-1).float()                                               # larger probability first
+        # rank of every pair inside its expert by priority: sort by (expert, priority)
+        order = torch.argsort(prio, stable=True)
+        order = order[torch.argsort(flat_e[order], stable=True)]
+        counts = count_ids(flat_e, E)
+        first = torch.cumsum(counts, 0) - counts
+        rank_sorted = torch.arange(n, device=idx.device) - first[flat_e[order]]
+        rank = torch.empty_like(rank_sorted)
+        rank[order] = rank_sorted
+        return (rank < cap).view_as(idx)
+
     def __init__(self, config, dtype=None, device=None):
         super().__init__()
         self.num_experts = config.num_experts
@@ -54,6 +73,11 @@ class TopkRouter(nn.Module):
         self.aux_coef = float(config.router_aux_loss_coef or 0.0)
         self.z_coef = float(config.router_z_loss_coef or 0.0)
         self.force_balance = bool(getattr(config, "moe_router_force_load_balancing", False))
+        # capacity: every expert serves at most ceil(factor * tokens * top_k / experts) routed pairs; the rest are dropped
+        # (their combine weight becomes zero) by position in the batch or by routing probability
+        # (paddleformers/nn/moe_deepep/moe_gate.py:75-97, :183-273)
+        self.capacity_factor = float(getattr(config, "moe_capacity_factor", 0.0) or 0.0)
+        self.drop_policy = str(getattr(config, "moe_drop_policy", "probs") or "probs")
         # the router runs in fp32 like the reference's gate (weights kept fp32 regardless of the model dtype)
         self.weight = nn.Parameter(torch.empty(self.num_experts, config.hidden_size, dtype=torch.float32, device=device))
         self.weight.keep_fp32 = True
@@ -90,6 +114,8 @@ class TopkRouter(nn.Module):
         if self.norm_topk_prob and self.top_k > 1:
             w = w / (w.sum(-1, keepdim=True) + 1e-20)
         w = w * self.scale
+        if self.capacity_factor > 0:
+            w = w * self._capacity_mask(idx, w.detach(), T, E).to(w.dtype)
         with torch.no_grad():
             self.expert_usage.scatter_add_(0, idx.reshape(-1), torch.ones_like(idx.reshape(-1)))
         aux = None

@@ -231,3 +231,82 @@ def test_minicpm_scaling_maps_to_multipliers_and_kimi_uses_deepseek_blocks():
     assert model(torch.randint(0, 96, (1, 8)), return_logits=True).logits.shape == (1, 8, 96)
     k = AutoConfig.for_model("kimi_k2", num_hidden_layers=2)
     assert k.is_mla and k.topk_method == "noaux_tc"
+
+
+def test_attention_backends_agree_and_sinks_absorb_probability():
+    from paddleformers_b200.nn.attention import AttentionInterface
+
+    torch.manual_seed(0)
+    B, S, Hq, Hkv, D = 2, 16, 4, 2, 8
+    q, k, v = torch.randn(B, S, Hq, D), torch.randn(B, S, Hkv, D), torch.randn(B, S, Hkv, D)
+    rows = torch.full((B, S), S, dtype=torch.int32)
+    rows[0, :6] = 6                                              # two packed documents in the first row
+    outs = {n: AttentionInterface.get(n)(q, k, v, rows) for n in ("flashmask", "sdpa", "eager")}
+    torch.testing.assert_close(outs["sdpa"], outs["eager"], rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(outs["flashmask"], outs["eager"], rtol=1e-4, atol=1e-5)
+    assert set(AttentionInterface.valid_keys()) >= {"eager", "sdpa", "flashmask"}
+    # sinks: a very negative sink changes nothing, a large one drains the attention output towards zero
+    none = AttentionInterface.get("eager")(q, k, v, rows, sinks=torch.full((Hq,), -1e4))
+    torch.testing.assert_close(none, outs["eager"], rtol=1e-5, atol=1e-6)
+    drained = AttentionInterface.get("eager")(q, k, v, rows, sinks=torch.full((Hq,), 30.0))
+    assert drained.abs().max() < 1e-3 * outs["eager"].abs().max() + 1e-6
+    with pytest.raises(NotImplementedError):
+        AttentionInterface.get("sdpa")(q, k, v, sinks=torch.zeros(Hq))
+
+
+def test_layer_factories_follow_the_tensor_parallel_plan():
+    import torch.nn as nn
+
+    from paddleformers_b200.nn.layers import Embedding, Linear, LMHead, MLP, Norm
+
+    cfg = AutoConfig.for_model("llama", **TINY)
+    assert isinstance(Linear.create(8, 16, tp_plan="colwise"), nn.Linear)            # tensor-parallel degree 1: plain layers
+    assert isinstance(Embedding.create(32, 8), nn.Embedding)
+    assert type(Norm.create(8)).__name__ == "RMSNorm" and isinstance(Norm.create(8, norm_type="layer_norm"), nn.LayerNorm)
+    mlp = MLP.create(cfg, dtype=torch.float32)
+    assert mlp(torch.randn(3, cfg.hidden_size)).shape == (3, cfg.hidden_size)
+    assert LMHead.create(cfg).weight.shape == (cfg.vocab_size, cfg.hidden_size)
+    with pytest.raises(KeyError):
+        Norm.create(8, norm_type="nope")
+
+
+@pytest.mark.parametrize("policy", ["probs", "position"])
+def test_router_capacity_drops_overflow_pairs(policy):
+    from paddleformers_b200.models.configuration import Qwen3MoeConfig
+    from paddleformers_b200.nn.moe import TopkRouter
+
+    torch.manual_seed(0)
+    cfg = Qwen3MoeConfig(hidden_size=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=8, intermediate_size=8,
+                         num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=2, vocab_size=32, norm_topk_prob=False)
+    cfg.moe_capacity_factor, cfg.moe_drop_policy = 0.5, policy
+    router = TopkRouter(cfg)
+    with torch.no_grad():
+        router.weight.normal_(0, 1.0)
+        router.weight[0] *= 4                                      # expert 0 is over-subscribed
+    x = torch.randn(32, 16)
+    idx, w, _ = router(x)
+    cap = 8                                                        # ceil(0.5 * 32 * 2 / 4)
+    kept = w > 0
+    for e in range(4):
+        on_e = idx == e
+        assert int((kept & on_e).sum()) == min(cap, int(on_e.sum()))
+    assert int((idx == 0).sum()) > cap                             # something was actually dropped
+    if policy == "position":
+        pairs = torch.nonzero(idx == 0)                            # row-major: earliest tokens first
+        assert kept[idx == 0][:cap].all() and not kept[idx == 0][cap:].any() and len(pairs) > cap
+    else:
+        router.capacity_factor = 0.0                               # same router without the cap: the original weights
+        _, w_full, _ = router(x)
+        on0 = idx == 0
+        assert w_full[on0 & kept].min() >= w_full[on0 & ~kept].max()       # the most probable pairs survive
+
+
+def test_attention_implementation_switch_matches_default_path():
+    cfg = AutoConfig.for_model("llama", **TINY)
+    torch.manual_seed(0)
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32).eval()
+    ids = torch.randint(0, 96, (2, 12))
+    ref = model(ids, return_logits=True).logits
+    for impl in ("eager", "sdpa"):
+        model.config._attn_implementation = impl
+        torch.testing.assert_close(model(ids, return_logits=True).logits, ref, rtol=1e-4, atol=1e-5)
