@@ -24,6 +24,13 @@ _LAZY = {
     "LlamaConfig": ".models.configuration", "Qwen3Config": ".models.configuration", "Qwen3MoeConfig": ".models.configuration",
     "DeepseekV3Config": ".models.configuration", "Glm4MoeConfig": ".models.configuration",
     "LoRAConfig": ".peft.lora", "LoRAModel": ".peft.lora", "GenerationConfig": ".generation.utils",
+    "AutoModelForConditionalGeneration": ".transformers.auto", "Qwen2VLForConditionalGeneration": ".models.vision_language",
+    "Qwen2VLConfig": ".models.vision_language", "Qwen2VLImageProcessor": ".transformers.image_processing",
+    "Qwen2ForCausalLM": ".models.modeling", "MistralForCausalLM": ".models.modeling", "Phi3ForCausalLM": ".models.modeling",
+    "Ernie4_5ForCausalLM": ".models.modeling", "Ernie4_5MoeForCausalLM": ".models.modeling", "Qwen2MoeForCausalLM": ".models.modeling",
+    "GraniteForCausalLM": ".models.modeling", "SFTTrainer": ".trainer.sft_trainer", "DPOTrainer": ".trainer.dpo_trainer",
+    "ShardedAdamW": ".parallel.sharding", "ShardedMuon": ".parallel.sharding", "EMACallback": ".trainer.ema",
+    "plan_parallelism": ".parallel.auto_plan",
 }
 
 
