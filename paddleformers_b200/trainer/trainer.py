@@ -84,7 +84,11 @@ class Trainer:
         if self.model is not None and next(self.model.parameters()).device != self.device:
             self.model.to(self.device)
         default_cbs: List[TrainerCallback] = [DefaultFlowCallback(), PrinterCallback()]
-        if self.args.profile:
+        if self.args.profile and getattr(self.args, "profile_backend", "cuda_api") == "torch":
+            from ..utils.profiler import TorchProfilerCallback
+
+            default_cbs.append(TorchProfilerCallback(self.args.profile_step_start, self.args.profile_step_end))
+        elif self.args.profile:
             default_cbs.append(ProfilerCallback())
         if self.args.metrics_output_path:
             default_cbs.append(MetricsDumpCallback(self.args.metrics_output_path))

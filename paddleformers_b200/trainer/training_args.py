@@ -104,6 +104,7 @@ class TrainingArguments:
     profile_step_start: int = 3
     profile_step_end: int = 5
     skip_profile_timer: bool = True
+    profile_backend: str = "cuda_api"   # cuda_api: cudaProfilerStart/Stop window for an external profiler | torch: torch.profiler trace
     disable_tqdm: bool = True
     device: Optional[str] = None
     pg_timeout_s: int = 0

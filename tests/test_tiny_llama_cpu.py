@@ -161,3 +161,15 @@ def test_muon_orthogonalises_matrix_updates_and_trains(tmp_path):
     assert any("embed_tokens" in n for n in adam) and any("norm" in n for n in adam) and not any("embed" in n for n in muon)
     losses = [h["loss"] for h in tr.state.log_history if "loss" in h]
     assert losses[-1] < losses[0] - 0.05
+
+
+def test_torch_profiler_window_writes_trace(tmp_path):
+    from paddleformers_b200.utils.profiler import StartupTimer
+
+    _, tr = _make(tmp_path, 4, save_strategy="no", profile=True, profile_backend="torch", profile_step_start=1, profile_step_end=3)
+    tr.train()
+    prof_dir = tmp_path / "profile"
+    assert (prof_dir / "trace_rank0.json").stat().st_size > 1000 and "Name" in (prof_dir / "top_ops_rank0.txt").read_text()
+    st = StartupTimer()
+    st.mark("imports"); st.mark("model")
+    assert "imports" in st.report()
