@@ -25,7 +25,8 @@ _LAZY = {
     "DeepseekV3Config": ".models.configuration", "Glm4MoeConfig": ".models.configuration",
     "LoRAConfig": ".peft.lora", "LoRAModel": ".peft.lora", "GenerationConfig": ".generation.utils",
     "AutoModelForConditionalGeneration": ".transformers.auto", "Qwen2VLForConditionalGeneration": ".models.vision_language",
-    "Qwen2VLConfig": ".models.vision_language", "Qwen2VLImageProcessor": ".transformers.image_processing",
+    "Qwen2VLConfig": ".models.vision_language", "Qwen2_5_VLConfig": ".models.vision_language",
+    "Qwen2_5_VLForConditionalGeneration": ".models.vision_language", "Qwen2VLImageProcessor": ".transformers.image_processing",
     "Qwen2ForCausalLM": ".models.modeling", "MistralForCausalLM": ".models.modeling", "Phi3ForCausalLM": ".models.modeling",
     "Ernie4_5ForCausalLM": ".models.modeling", "Ernie4_5MoeForCausalLM": ".models.modeling", "Qwen2MoeForCausalLM": ".models.modeling",
     "GraniteForCausalLM": ".models.modeling", "SFTTrainer": ".trainer.sft_trainer", "DPOTrainer": ".trainer.dpo_trainer",

@@ -356,7 +356,7 @@ UNSUPPORTED_FAMILIES = {
     "cohere2": "LayerNorm, parallel block, sliding-window layers", "stablelm": "LayerNorm with bias, partial rotary with per-head norm",
     "internlm2": "interleaved fused wqkv layout", "minicpm3": "MLA with scaling factors",
     "llama4_text": "chunked attention, NoPE layers, shared-expert MoE", "diffllama": "differential attention",
-    "qwen2_5_vl": "windowed vision attention and RMSNorm vision blocks (Qwen2-VL itself is implemented: models/vision_language.py)",
+
     "qwen3_vl": "vision tower and multimodal rotary embedding", "qwen3_vl_moe": "vision tower and multimodal rotary embedding",
     "ernie4_5_vl": "vision tower, modality-aware experts", "paddleocr_vl": "vision tower", "glm4v_moe": "vision tower",
     "paligemma": "SigLIP vision tower", "whisper": "encoder-decoder speech model", "qwen3_omni_moe": "audio / vision towers",

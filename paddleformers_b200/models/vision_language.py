@@ -70,22 +70,68 @@ class Qwen2VLConfig(PretrainedConfig):
         return d
 
 
+class Qwen2_5_VLConfig(Qwen2VLConfig):
+    """Qwen2.5-VL: the vision blocks use RMSNorm and a biased SwiGLU MLP, most of them attend inside windows of
+    ``window_size`` pixels (``fullatt_block_indexes`` lists the blocks that see the whole image), and the merger normalises
+    with RMSNorm (paddleformers/transformers/qwen2_5_vl)."""
+
+    model_type = "qwen2_5_vl"
+
+    def __init__(self, vision_config=None, **kwargs):
+        v = dict(vision_config or {})
+        if "in_chans" in v:
+            v.setdefault("in_channels", v.pop("in_chans"))
+        defaults = {"depth": 32, "hidden_size": 1280, "intermediate_size": 3420, "num_heads": 16, "in_channels": 3, "out_hidden_size": 3584,
+                    "patch_size": 14, "spatial_merge_size": 2, "temporal_patch_size": 2, "window_size": 112,
+                    "fullatt_block_indexes": [7, 15, 23, 31], "hidden_act": "silu", "tokens_per_second": 4}
+        super().__init__(vision_config={}, **kwargs)
+        self.vision_config = {**defaults, **{k: v[k] for k in v if k != "model_type"}}
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        d["text_config"]["model_type"] = "qwen2_5_vl_text"
+        d["vision_config"]["model_type"] = "qwen2_5_vl"
+        return d
+
+
 def _quick_gelu(x):
     return x * torch.sigmoid(1.702 * x)
 
 
+class _RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float = 1e-6, dtype=None, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device))
+        self.eps = eps
+
+    def forward(self, x):
+        return F.rms_norm(x, self.weight, self.eps)
+
+
 class _VisionBlock(nn.Module):
-    def __init__(self, dim: int, heads: int, mlp_hidden: int, act: str, dtype=None, device=None):
+    def __init__(self, dim: int, heads: int, mlp_hidden: int, act: str, dtype=None, device=None, rms_norm: bool = False,
+                 swiglu: bool = False):
         super().__init__()
         kw = dict(dtype=dtype, device=device)
-        self.norm1 = nn.LayerNorm(dim, eps=1e-6, **kw)
-        self.norm2 = nn.LayerNorm(dim, eps=1e-6, **kw)
+        norm = (lambda: _RMSNorm(dim, 1e-6, **kw)) if rms_norm else (lambda: nn.LayerNorm(dim, eps=1e-6, **kw))
+        self.norm1, self.norm2 = norm(), norm()
         self.qkv = nn.Linear(dim, 3 * dim, **kw)
         self.proj = nn.Linear(dim, dim, **kw)
-        self.fc1 = nn.Linear(dim, mlp_hidden, **kw)
-        self.fc2 = nn.Linear(mlp_hidden, dim, **kw)
+        self.swiglu = swiglu
+        if swiglu:
+            self.gate_proj = nn.Linear(dim, mlp_hidden, **kw)
+            self.up_proj = nn.Linear(dim, mlp_hidden, **kw)
+            self.down_proj = nn.Linear(mlp_hidden, dim, **kw)
+        else:
+            self.fc1 = nn.Linear(dim, mlp_hidden, **kw)
+            self.fc2 = nn.Linear(mlp_hidden, dim, **kw)
         self.heads, self.hd = heads, dim // heads
         self.act = _quick_gelu if act == "quick_gelu" else getattr(TF, act)
+
+    def mlp(self, x):
+        if self.swiglu:
+            return self.down_proj(self.act(self.gate_proj(x)) * self.up_proj(x))
+        return self.fc2(self.act(self.fc1(x)))
 
     def forward(self, x, cos, sin, lengths: List[int]):
         N = x.shape[0]
@@ -104,7 +150,7 @@ class _VisionBlock(nn.Module):
             off += n
         a = torch.cat(outs, dim=0).reshape(N, -1)
         x = x + self.proj(a)
-        return x + self.fc2(self.act(self.fc1(self.norm2(x))))
+        return x + self.mlp(self.norm2(x))
 
 
 class VisionTower(nn.Module):
@@ -150,6 +196,65 @@ class VisionTower(nn.Module):
         return self.merge_fc2(TF.gelu(self.merge_fc1(x)))
 
 
+class WindowedVisionTower(VisionTower):
+    """Qwen2.5-VL tower: merged-patch groups are re-ordered window by window so that windowed blocks attend inside
+    contiguous runs; full-attention blocks use the per-image runs on the same ordering; the merged output is put back
+    into the processor's order."""
+
+    def __init__(self, vc: dict, dtype=None, device=None):
+        nn.Module.__init__(self)
+        kw = dict(dtype=dtype, device=device)
+        self.vc = vc
+        dim = vc["hidden_size"]
+        self.patch_dim = vc["in_channels"] * vc["temporal_patch_size"] * vc["patch_size"] ** 2
+        self.patch_embed = nn.Linear(self.patch_dim, dim, bias=False, **kw)
+        self.blocks = nn.ModuleList([_VisionBlock(dim, vc["num_heads"], vc["intermediate_size"], vc["hidden_act"], rms_norm=True,
+                                                  swiglu=True, **kw) for _ in range(vc["depth"])])
+        m = vc["spatial_merge_size"] ** 2
+        self.ln_q = _RMSNorm(dim, 1e-6, **kw)
+        self.merge_fc1 = nn.Linear(dim * m, dim * m, **kw)
+        self.merge_fc2 = nn.Linear(dim * m, vc["out_hidden_size"], **kw)
+        self.head_dim = dim // vc["num_heads"]
+
+    def window_order(self, grid_thw: torch.Tensor):
+        ms, unit = self.vc["spatial_merge_size"], self.vc["spatial_merge_size"] ** 2
+        win = self.vc["window_size"] // ms // self.vc["patch_size"]
+        index, lengths, base = [], [], 0
+        for t, h, w in grid_thw.tolist():
+            gh, gw = h // ms, w // ms
+            idx = torch.arange(t * gh * gw).reshape(t, gh, gw)
+            ph, pw = win - gh % win, win - gw % win                 # (a full extra window of padding when already aligned)
+            nh, nw = (gh + ph) // win, (gw + pw) // win
+            padded = TF.pad(idx, (0, pw, 0, ph), value=-100).reshape(t, nh, win, nw, win).permute(0, 1, 3, 2, 4)
+            padded = padded.reshape(t, nh * nw, win, win)
+            per_window = (padded != -100).sum([2, 3]).reshape(-1)
+            flat = padded.reshape(-1)
+            index.append(flat[flat != -100] + base)
+            lengths += [int(n) * unit for n in per_window.tolist() if n > 0]
+            base += t * gh * gw
+        return torch.cat(index), lengths
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
+        unit = self.vc["spatial_merge_size"] ** 2
+        x = self.patch_embed(pixel_values.to(self.patch_embed.weight.dtype))
+        cos, sin = self.rotary(grid_thw, x.device)
+        order, window_lengths = self.window_order(grid_thw)
+        order = order.to(x.device)
+        N = x.shape[0]
+
+        def regroup(t):
+            return t.reshape(N // unit, unit, *t.shape[1:])[order].reshape(N, *t.shape[1:])
+
+        x, cos, sin = regroup(x), regroup(cos), regroup(sin)
+        image_lengths = [h * w for t, h, w in grid_thw.tolist() for _ in range(t)]
+        full = set(self.vc["fullatt_block_indexes"])
+        for i, blk in enumerate(self.blocks):
+            x = blk(x, cos, sin, image_lengths if i in full else window_lengths)
+        x = self.ln_q(x).view(-1, x.shape[-1] * unit)
+        x = self.merge_fc2(TF.gelu(self.merge_fc1(x)))
+        return x[torch.argsort(order)]
+
+
 def multimodal_position_ids(input_ids: torch.Tensor, image_token_id: int, video_token_id: int, image_grid_thw, video_grid_thw,
                             merge: int) -> torch.Tensor:
     """[3, B, S] temporal / height / width positions: text tokens advance all three together; the tokens of an image keep
@@ -184,11 +289,14 @@ def multimodal_position_ids(input_ids: torch.Tensor, image_token_id: int, video_
 
 
 class Qwen2VLForConditionalGeneration(PretrainedModel):
+    """Qwen2-VL and (with a ``Qwen2_5_VLConfig``) Qwen2.5-VL."""
+
     config_class = Qwen2VLConfig
 
     def __init__(self, config: Qwen2VLConfig, dtype=None, device=None):
         super().__init__(config)
-        self.visual = VisionTower(config.vision_config, dtype=dtype, device=device)
+        tower = WindowedVisionTower if isinstance(config, Qwen2_5_VLConfig) else VisionTower
+        self.visual = tower(config.vision_config, dtype=dtype, device=device)
         self.language = DecoderForCausalLM(config.text_config, dtype=dtype, device=device)
         # tensor names differ between generations of checkpoints: the vision tower is stored as "visual.*" or
         # "model.visual.*", the decoder as "model.*" or "model.language_model.*"; both are probed on load, and the writer
@@ -278,18 +386,23 @@ class Qwen2VLForConditionalGeneration(PretrainedModel):
             if t not in known:
                 rules.append(Rule(t, [text_name(name)]))
         vc = self.config.vision_config
-        conv_shape = [vc["embed_dim"], vc["in_channels"], vc["temporal_patch_size"], vc["patch_size"], vc["patch_size"]]
-        rules.append(Rule("visual.patch_embed.weight", [vis + "patch_embed.proj.weight"], reshape=[vc["embed_dim"], -1],
-                          source_shape=conv_shape))
+        windowed = isinstance(self.config, Qwen2_5_VLConfig)
+        width = vc["hidden_size"] if windowed else vc["embed_dim"]
+        conv_shape = [width, vc["in_channels"], vc["temporal_patch_size"], vc["patch_size"], vc["patch_size"]]
+        rules.append(Rule("visual.patch_embed.weight", [vis + "patch_embed.proj.weight"], reshape=[width, -1], source_shape=conv_shape))
+        mlp_names = (("gate_proj", "mlp.gate_proj"), ("up_proj", "mlp.up_proj"), ("down_proj", "mlp.down_proj")) if windowed else \
+            (("fc1", "mlp.fc1"), ("fc2", "mlp.fc2"))
+        own = dict(self.visual.named_parameters())
         for i in range(vc["depth"]):
             a, b = f"visual.blocks.{i}.", vis + f"blocks.{i}."
-            for mine, theirs in (("norm1", "norm1"), ("norm2", "norm2"), ("qkv", "attn.qkv"), ("proj", "attn.proj"),
-                                 ("fc1", "mlp.fc1"), ("fc2", "mlp.fc2")):
+            for mine, theirs in (("norm1", "norm1"), ("norm2", "norm2"), ("qkv", "attn.qkv"), ("proj", "attn.proj")) + mlp_names:
                 for leaf in ("weight", "bias"):
-                    rules.append(Rule(a + f"{mine}.{leaf}", [b + f"{theirs}.{leaf}"]))
+                    if f"blocks.{i}.{mine}.{leaf}" in own:              # RMSNorm has no bias
+                        rules.append(Rule(a + f"{mine}.{leaf}", [b + f"{theirs}.{leaf}"]))
         for mine, theirs in (("ln_q", "merger.ln_q"), ("merge_fc1", "merger.mlp.0"), ("merge_fc2", "merger.mlp.2")):
             for leaf in ("weight", "bias"):
-                rules.append(Rule(f"visual.{mine}.{leaf}", [vis + f"{theirs}.{leaf}"]))
+                if f"{mine}.{leaf}" in own:
+                    rules.append(Rule(f"visual.{mine}.{leaf}", [vis + f"{theirs}.{leaf}"]))
         return WeightMap(rules)
 
 
@@ -311,3 +424,7 @@ def mm_collate_fn(examples: List[dict], pad_token_id: int = 0, ignore_index: int
         out["image_grid_thw"] = torch.cat([torch.as_tensor(e["image_grid_thw"]).reshape(-1, 3) for e in examples
                                            if e.get("image_grid_thw") is not None], dim=0)
     return out
+
+
+class Qwen2_5_VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
+    config_class = Qwen2_5_VLConfig

@@ -48,9 +48,11 @@ class AutoModelForConditionalGeneration:
 
     @staticmethod
     def _classes(model_type: str):
-        from ..models.vision_language import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+        from ..models.vision_language import (Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration, Qwen2VLConfig,
+                                              Qwen2VLForConditionalGeneration)
 
-        table = {"qwen2_vl": (Qwen2VLConfig, Qwen2VLForConditionalGeneration)}
+        table = {"qwen2_vl": (Qwen2VLConfig, Qwen2VLForConditionalGeneration),
+                 "qwen2_5_vl": (Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration)}
         if model_type not in table:
             raise ValueError(f"unknown vision-language model_type {model_type!r}; supported: {sorted(table)}")
         return table[model_type]

@@ -207,3 +207,32 @@ def test_image_processor_matches_hugging_face_and_vl_training_step():
         losses.append(total)
     assert losses[-1] < losses[0]
     assert model.visual.patch_embed.weight.grad is not None and model.visual.patch_embed.weight.grad.abs().sum() > 0
+
+
+def test_qwen2_5_vl_matches_hugging_face(tmp_path):
+    """Windowed vision attention (window re-ordering and its inverse), RMSNorm / SwiGLU vision blocks."""
+    if not hasattr(transformers, "Qwen2_5_VLForConditionalGeneration"):
+        pytest.skip("transformers has no Qwen2.5-VL")
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    torch.manual_seed(6)
+    vc = dict(depth=3, hidden_size=32, intermediate_size=48, num_heads=2, in_chans=3, out_hidden_size=64, patch_size=4,
+              spatial_merge_size=2, temporal_patch_size=2, window_size=16, fullatt_block_indexes=[1], hidden_act="silu",
+              tokens_per_second=1)      # still images: the temporal position of an image is the position where it starts
+    tc = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              max_position_embeddings=128, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}, tie_word_embeddings=False)
+    cfg = transformers.Qwen2_5_VLConfig(text_config=tc, vision_config=vc, image_token_id=120, video_token_id=121,
+                                        vision_start_token_id=118, vision_end_token_id=119)
+    hf = transformers.Qwen2_5_VLForConditionalGeneration(cfg).eval().float()
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path), dtype=torch.float32).eval()
+    grid = torch.tensor([[1, 6, 10], [1, 4, 4]])                      # 60 and 16 patches -> 15 and 4 tokens; windows of 2 x 2 groups
+    pixels = torch.randn(int(grid.prod(-1).sum()), 3 * 2 * 4 * 4)
+    with torch.no_grad():
+        torch.testing.assert_close(mine.visual(pixels, grid), hf.model.visual(pixels, grid_thw=grid).pooler_output, rtol=1e-4, atol=1e-5)
+    ids = torch.tensor([[5, 118] + [120] * 15 + [119, 7, 8, 118] + [120] * 4 + [119, 10, 11]])
+    types = (ids == 120).int()
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=types).logits
+        got = mine(ids, pixel_values=pixels, image_grid_thw=grid, return_logits=True).logits
+    torch.testing.assert_close(got, want, rtol=3e-4, atol=3e-4)
