@@ -171,3 +171,30 @@ def test_vl_sft_stage_trains_on_images(tmp_path):
             os.environ["CUDA_VISIBLE_DEVICES"] = env
     model = AutoModelForConditionalGeneration.from_pretrained(str(out), dtype=torch.float32)
     assert model.visual.patch_embed.weight.shape == (16, 3 * 2 * 4 * 4) and os.path.exists(out / "tokenizer.json")
+
+
+def test_example_configs_parse(monkeypatch):
+    """Every file under examples/config is accepted by the argument parser (no unknown keys, right types, parallel
+    degrees that divide a 64-GPU job)."""
+    import glob
+
+    monkeypatch.setenv("WORLD_SIZE", "64")
+    monkeypatch.setenv("RANK", "0")
+
+    from paddleformers_b200.cli.hparams import read_args
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "config")
+    files = sorted(glob.glob(os.path.join(root, "*.yaml")))
+    assert len(files) >= 8
+    for f in files:
+        flat = read_args([f])
+        if "export" in os.path.basename(f):
+            from paddleformers_b200.cli.hparams import ExportArguments
+
+            known = {x.name for x in __import__("dataclasses").fields(ExportArguments)} | {"model_name_or_path", "compute_type", "device"}
+            assert set(flat) <= known | {"lora_path", "output_dir"}, (f, set(flat) - known)
+            continue
+        from paddleformers_b200.cli.hparams import parse_dict
+
+        model_args, data_args, gen_args, export_args, train_args = parse_dict(dict(flat, device="cpu"))
+        assert model_args.stage and train_args.output_dir, f
