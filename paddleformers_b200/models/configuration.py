@@ -288,6 +288,66 @@ class MiniCPMConfig(GraniteConfig):
         self.scale_emb, self.scale_depth, self.dim_model_base = scale_emb, scale_depth, dim_model_base
 
 
+class Olmo2Config(DecoderConfig):
+    """OLMo 2: normalisation AFTER each branch (x + norm(branch(x))) and one RMSNorm over all heads' query / key features
+    (paddleformers/transformers/olmo2)."""
+
+    model_type = "olmo2"
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.block_style, self.qk_norm_full = "post", True
+
+
+class GemmaConfig(DecoderConfig):
+    """Gemma (first generation): RMSNorm weights stored as (w - 1), GELU-gated MLP, embeddings scaled by sqrt(hidden),
+    tied head (paddleformers/transformers/gemma)."""
+
+    model_type = "gemma"
+
+    def __init__(self, hidden_activation=None, **kw):
+        kw.setdefault("tie_word_embeddings", True)
+        kw.setdefault("head_dim", 256)
+        kw["hidden_act"] = hidden_activation or kw.get("hidden_act") or "gelu_pytorch_tanh"
+        if kw["hidden_act"] == "gelu":
+            kw["hidden_act"] = "gelu_pytorch_tanh"          # the released checkpoints were trained with the tanh form
+        super().__init__(**kw)
+        self.hidden_activation = self.hidden_act
+        self.embedding_multiplier = float(self.hidden_size) ** 0.5
+        self.norm_weight_offset = 1.0
+
+
+class CohereConfig(DecoderConfig):
+    """Command-R: bias-free LayerNorm, attention and MLP in parallel on one normed input, interleaved rotary pairs in the
+    checkpoint, logits multiplied by ``logit_scale`` (paddleformers/transformers/cohere)."""
+
+    model_type = "cohere"
+
+    def __init__(self, layer_norm_eps=1e-5, logit_scale=0.0625, **kw):
+        kw.setdefault("rms_norm_eps", layer_norm_eps)
+        kw.setdefault("tie_word_embeddings", True)
+        super().__init__(**kw)
+        self.layer_norm_eps, self.logit_scale = layer_norm_eps, logit_scale
+        self.norm_type, self.block_style = "layernorm_nobias", "parallel"
+        self.rope_interleaved_checkpoint = True
+        self.logits_scaling = 1.0 / float(logit_scale)
+
+
+class StableLmConfig(DecoderConfig):
+    """StableLM 2: LayerNorm with bias, rotary embedding on the first quarter of each head, optional q/k/v biases
+    (paddleformers/transformers/stablelm)."""
+
+    model_type = "stablelm"
+
+    def __init__(self, layer_norm_eps=1e-5, use_qkv_bias=False, **kw):
+        kw.setdefault("rms_norm_eps", layer_norm_eps)
+        kw.setdefault("attention_bias", bool(use_qkv_bias))
+        kw.setdefault("partial_rotary_factor", 0.25)
+        super().__init__(**kw)
+        self.layer_norm_eps, self.use_qkv_bias = layer_norm_eps, use_qkv_bias
+        self.norm_type = "layernorm"
+
+
 class Ernie4_5Config(DecoderConfig):
     """ERNIE-4.5 dense: Llama blocks with tied embeddings whose checkpoints store q / k rows in the interleaved rotary
     order; the weight map permutes them to the half-split order on load and back on save
@@ -337,7 +397,8 @@ class Ernie4_5MoeConfig(Ernie4_5Config):
         self.router_bias_name = "mlp.moe_statics.e_score_correction_bias"
 
 
-CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, MiniCPMConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
+CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, MiniCPMConfig, Olmo2Config,
+                                            GemmaConfig, CohereConfig, StableLmConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
                                             Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config)}
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
@@ -352,8 +413,7 @@ UNSUPPORTED_FAMILIES = {
     "hunyuan_v1_dense": "QK norm applied after the rotary embedding", "hunyuan_v1_moe": "QK norm after rotary, shared-expert mixing",
     "gemma3": "(1 + w) RMSNorm, GeGLU, sliding/global layer pattern", "gemma3_text": "(1 + w) RMSNorm, GeGLU, sliding/global layer pattern",
     "phi4_multimodal": "vision and audio towers",
-    "olmo2": "post-norm blocks with QK norm over the full projection", "cohere": "LayerNorm, parallel attention + MLP block",
-    "cohere2": "LayerNorm, parallel block, sliding-window layers", "stablelm": "LayerNorm with bias, partial rotary with per-head norm",
+    "cohere2": "LayerNorm, parallel block, sliding-window layers", "gemma2": "soft-capping, sliding / global layer pattern, post norms",
     "internlm2": "interleaved fused wqkv layout", "minicpm3": "MLA with scaling factors",
     "llama4_text": "chunked attention, NoPE layers, shared-expert MoE", "diffllama": "differential attention",
 

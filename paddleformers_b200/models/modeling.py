@@ -30,7 +30,7 @@ from ..transformers.conversion_utils import Rule, WeightMap, expand_layers
 from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
                             Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig,
-                            GraniteConfig, MiniCPMConfig, Qwen2MoeConfig)
+                            GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, CohereConfig, StableLmConfig)
 
 
 @dataclass
@@ -69,6 +69,38 @@ class RMSNorm(nn.Module):
 
     def forward(self, x, residual=None):
         return F.rms_norm(x, self.weight, self.eps, residual=residual)
+
+
+class LayerNormAdapter(nn.Module):
+    """LayerNorm (optionally without bias) behind the call convention of ``RMSNorm``: ``norm(x)`` or
+    ``norm(x, residual) -> (normed(x + residual), x + residual)``. Statistics are computed in fp32."""
+
+    def __init__(self, hidden_size: int, eps: float, bias: bool = True, dtype=None, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden_size, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(hidden_size, dtype=dtype, device=device)) if bias else None
+        self.eps = eps
+
+    def _ln(self, x):
+        y = torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), None, None, self.eps) * self.weight.float()
+        if self.bias is not None:
+            y = y + self.bias.float()
+        return y.to(x.dtype)
+
+    def forward(self, x, residual=None):
+        if residual is None:
+            return self._ln(x)
+        s = x + residual
+        return self._ln(s), s
+
+
+def make_norm(config, hidden_size: int, sequence_parallel: bool = False, dtype=None, device=None):
+    """RMSNorm (fused kernel) unless the family asks for LayerNorm (``norm_type``: rms | layernorm | layernorm_nobias)."""
+    kind = getattr(config, "norm_type", "rms") or "rms"
+    if kind == "rms":
+        return RMSNorm(hidden_size, config.rms_norm_eps, sequence_parallel, dtype=dtype, device=device)
+    assert get_parallel_state().degrees.mp == 1, "LayerNorm families are implemented for tensor-parallel degree 1"
+    return LayerNormAdapter(hidden_size, config.rms_norm_eps, bias=kind == "layernorm", dtype=dtype, device=device)
 
 
 def _linear(in_f, out_f, bias, tp_plan, config, sections=None, dtype=None, device=None):
@@ -137,13 +169,22 @@ class Attention(nn.Module):
         self.qkv_proj = _linear(H, sum(secs), config.attention_bias, "colwise", config, sections=secs, dtype=dtype, device=device)
         self.o_proj = _linear(self.Hq_total * self.D, H, False, "rowwise", config, dtype=dtype, device=device)
         self.use_qk_norm = config.use_qk_norm
-        if self.use_qk_norm:
+        self.qk_norm_full = bool(getattr(config, "qk_norm_full", False))      # one RMSNorm over all heads' features (OLMo2)
+        if self.qk_norm_full:
+            assert tp == 1, "full-width QK norm is implemented for tensor-parallel degree 1"
+            self.use_qk_norm = False
+            self.q_norm = RMSNorm(self.Hq * self.D, config.rms_norm_eps, dtype=dtype, device=device)
+            self.k_norm = RMSNorm(self.Hkv * self.D, config.rms_norm_eps, dtype=dtype, device=device)
+        elif self.use_qk_norm:
             self.q_norm = RMSNorm(self.D, config.rms_norm_eps, dtype=dtype, device=device)
             self.k_norm = RMSNorm(self.D, config.rms_norm_eps, dtype=dtype, device=device)
         self.scale = float(getattr(config, "attention_multiplier", None) or 1.0 / math.sqrt(self.D))
 
     def forward(self, x2d: torch.Tensor, ctx: BatchContext, cache=None) -> torch.Tensor:
         qkv = _apply(self.qkv_proj, x2d)
+        if self.qk_norm_full:
+            nq, nk = self.Hq * self.D, self.Hkv * self.D
+            qkv = torch.cat([self.q_norm(qkv[:, :nq].contiguous()), self.k_norm(qkv[:, nq:nq + nk].contiguous()), qkv[:, nq + nk:]], dim=-1)
         if self.use_qk_norm:
             qkv = F.qk_norm_rope_packed(qkv, self.q_norm.weight, self.k_norm.weight, ctx.cos, ctx.sin, ctx.positions,
                                         self.Hq, self.Hkv, self.D, self.rot, self.config.rms_norm_eps)
@@ -238,8 +279,17 @@ class DecoderLayer(nn.Module):
         super().__init__()
         sp = bool(getattr(config, "sequence_parallel", False)) and get_parallel_state().degrees.mp > 1
         self.layer_idx = layer_idx
-        self.input_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps, sp, dtype=dtype, device=device)
-        self.post_attention_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps, sp, dtype=dtype, device=device)
+        # block_style: "pre" (norm -> branch -> add, the default), "post" (branch -> norm -> add: OLMo2) or "parallel"
+        # (attention and MLP read the same normed input and are added together: Cohere)
+        self.block_style = getattr(config, "block_style", "pre") or "pre"
+        if self.block_style != "parallel":
+            self.input_layernorm = make_norm(config, config.hidden_size, sp, dtype=dtype, device=device) \
+                if self.block_style == "pre" else None
+            self.post_attention_layernorm = make_norm(config, config.hidden_size, sp, dtype=dtype, device=device)
+            if self.block_style == "post":
+                self.post_feedforward_layernorm = make_norm(config, config.hidden_size, sp, dtype=dtype, device=device)
+        else:
+            self.input_layernorm = make_norm(config, config.hidden_size, sp, dtype=dtype, device=device)
         attn_cls = MLAAttention if config.is_mla else Attention
         self.self_attn = attn_cls(config, layer_idx, dtype=dtype, device=device)
         if config.is_moe_layer(layer_idx):
@@ -259,6 +309,13 @@ class DecoderLayer(nn.Module):
     def forward(self, hidden, residual, ctx: BatchContext, cache=None):
         """(branch output, residual stream) in, (branch output, residual stream) out; the add happens inside the
         next RMSNorm kernel."""
+        if self.block_style != "pre":
+            x = hidden if residual is None else hidden + residual
+            if self.block_style == "post":
+                x = x + self.post_attention_layernorm(self.self_attn(x, ctx, cache))
+                return x + self.post_feedforward_layernorm(self.mlp(x)), None
+            normed = self.input_layernorm(x)
+            return x + self.self_attn(normed, ctx, cache) + self.mlp(normed), None
         if residual is None:
             normed, residual = self.input_layernorm(hidden), hidden
         else:
@@ -312,7 +369,7 @@ class DecoderModel(nn.Module):
         else:
             self.embed_tokens = None
         self.layers = nn.ModuleDict({str(i): DecoderLayer(config, i, dtype=dtype, device=device) for i in self.layer_range})
-        self.norm = RMSNorm(config.hidden_size, config.rms_norm_eps, self.sp, dtype=dtype, device=device) if with_final_norm else None
+        self.norm = make_norm(config, config.hidden_size, self.sp, dtype=dtype, device=device) if with_final_norm else None
         self._rope_cache = {}
 
     # ------------------------------------------------------------------ helpers
@@ -602,6 +659,11 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
         dense_rule = Rule(L + "mlp.gate_up_proj.weight", [L + "mlp.gate_up_proj.weight"])
     else:
         dense_rule = Rule(L + "mlp.gate_up_proj.weight", [L + "mlp.gate_proj.weight", L + "mlp.up_proj.weight"], "concat", 0)
+    off = float(getattr(config, "norm_weight_offset", 0.0) or 0.0)
+    if off:                                         # checkpoints that store (w - offset) for every RMSNorm weight
+        rules.append(Rule("model.norm.weight", ["model.norm.weight"], offset=off))
+        for nm in ("input_layernorm.weight", "post_attention_layernorm.weight"):
+            per_layer.append(Rule(L + nm, [L + nm], offset=off))
     n_total = config.num_hidden_layers + int(getattr(config, "num_nextn_predict_layers", 0) or 0)
     for i in range(config.num_hidden_layers):
         rules.extend(expand_layers(per_layer, [i]))
@@ -684,10 +746,15 @@ Ernie4_5MoeForCausalLM = _family("Ernie4_5MoeForCausalLM", Ernie4_5MoeConfig)
 Qwen2MoeForCausalLM = _family("Qwen2MoeForCausalLM", Qwen2MoeConfig)
 GraniteForCausalLM = _family("GraniteForCausalLM", GraniteConfig)
 MiniCPMForCausalLM = _family("MiniCPMForCausalLM", MiniCPMConfig)
+Olmo2ForCausalLM = _family("Olmo2ForCausalLM", Olmo2Config)
+GemmaForCausalLM = _family("GemmaForCausalLM", GemmaConfig)
+CohereForCausalLM = _family("CohereForCausalLM", CohereConfig)
+StableLmForCausalLM = _family("StableLmForCausalLM", StableLmConfig)
 
 MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
-    "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
+    "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "cohere": CohereForCausalLM,
+    "stablelm": StableLmForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,
 }

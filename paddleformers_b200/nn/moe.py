@@ -410,8 +410,27 @@ class DenseMLP(nn.Module):
             self.gate_up_proj = nn.Linear(hidden_size, 2 * intermediate_size, bias=bias, dtype=dtype, device=device)
             self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=bias, dtype=dtype, device=device)
             self._tp = False
+        # gate activation: "silu" runs in the fused SwiGLU kernels; the GELU variants (GeGLU families) use the unfused path
+        self.act_name = str(getattr(config, "hidden_act", "silu") or "silu")
+        if self.act_name not in ("silu", "swish"):
+            assert not self._tp, "non-SiLU gated MLPs are implemented for tensor-parallel degree 1"
+
+    def _gated_generic(self, x):
+        gu = self.gate_up_proj(x) if not isinstance(self.gate_up_proj, nn.Linear) else \
+            F.linear(x, self.gate_up_proj.weight, self.gate_up_proj.bias)
+        g, u = gu.chunk(2, dim=-1)
+        if self.act_name in ("gelu_pytorch_tanh", "gelu_tanh"):
+            a = TF.gelu(g, approximate="tanh")
+        elif self.act_name == "gelu":
+            a = TF.gelu(g)
+        else:
+            a = getattr(TF, self.act_name)(g)
+        dn = self.down_proj
+        return F.linear(a * u, dn.weight, dn.bias) if isinstance(dn, nn.Linear) else dn(a * u)
 
     def forward(self, x):
+        if self.act_name not in ("silu", "swish"):
+            return self._gated_generic(x)
         if self._tp:
             return self.down_proj(self.gate_up_proj(x))
         gu, dn = self.gate_up_proj, self.down_proj

@@ -105,6 +105,7 @@ class Rule:
     flatten: bool = False              # rename: the checkpoint stores the tensor with a leading unit dimension
     reshape: Optional[List[int]] = None        # rename: shape of the internal parameter (e.g. a Conv3d kernel used as a matrix)
     source_shape: Optional[List[int]] = None   # rename: shape of the tensor in the checkpoint, for the way back
+    offset: float = 0.0                        # rename: internal = checkpoint + offset ((1 + w) norm weights)
 
     def _load(self, i: int, t: torch.Tensor) -> torch.Tensor:
         if self.rope_deinterleave and i in self.rope_deinterleave:
@@ -124,6 +125,8 @@ class Rule:
     def forward(self, get: Callable[[str], torch.Tensor], expert_range: Optional[range] = None) -> torch.Tensor:
         if self.op == "rename":
             t = self._load(0, get(self.sources[0]))
+            if self.offset:
+                t = t + self.offset
             if self.reshape is not None:
                 return t.reshape(self.reshape)
             return t.reshape(-1) if self.flatten else t
@@ -139,6 +142,8 @@ class Rule:
     def inverse(self, tensor: torch.Tensor, section_sizes: Optional[List[int]] = None, expert_offset: int = 0) -> Dict[str, torch.Tensor]:
         if self.op == "rename":
             t = self._store(0, tensor)
+            if self.offset:
+                t = t - self.offset
             if self.source_shape is not None:
                 return {self.sources[0]: t.reshape(self.source_shape)}
             return {self.sources[0]: t.reshape(1, -1) if self.flatten else t}
@@ -179,5 +184,5 @@ def expand_layers(template_rules: List[Rule], layer_ids: Iterable[int]) -> List[
     for i in layer_ids:
         for r in template_rules:
             out.append(Rule(r.target.replace("{L}", str(i)), [s.replace("{L}", str(i)) for s in r.sources], r.op, r.dim,
-                            r.num_experts, r.expert_pairs, r.sizes, r.rope_deinterleave, r.flatten))
+                            r.num_experts, r.expert_pairs, r.sizes, r.rope_deinterleave, r.flatten, r.reshape, r.source_shape, r.offset))
     return out

@@ -45,6 +45,10 @@ CASES = {
         v_head_dim=16, routed_scaling_factor=2.5, norm_topk_prob=True, max_position_embeddings=128,
         rope_scaling={"rope_type": "yarn", "factor": 4.0, "beta_fast": 32, "beta_slow": 1, "mscale": 1.0, "mscale_all_dim": 0.707,
                       "original_max_position_embeddings": 32})),
+    "olmo2": ("Olmo2Config", "Olmo2ForCausalLM", dict()),
+    "gemma": ("GemmaConfig", "GemmaForCausalLM", dict(head_dim=16, tie_word_embeddings=True, hidden_activation="gelu_pytorch_tanh")),
+    "cohere": ("CohereConfig", "CohereForCausalLM", dict(tie_word_embeddings=True, logit_scale=0.25, use_qk_norm=False)),
+    "stablelm": ("StableLmConfig", "StableLmForCausalLM", dict(use_qkv_bias=True, partial_rotary_factor=0.25)),
     "glm4_moe": ("Glm4MoeConfig", "Glm4MoeForCausalLM", dict(head_dim=16, moe_intermediate_size=32, n_routed_experts=4, num_experts_per_tok=2,
                                                              n_group=1, topk_group=1, n_shared_experts=1, first_k_dense_replace=1,
                                                              partial_rotary_factor=0.5, use_qk_norm=True, routed_scaling_factor=1.5,
@@ -76,7 +80,8 @@ def test_logits_match_hugging_face_implementation(tmp_path, family):
     torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3"])
+@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "cohere", "olmo2",
+                                    "stablelm", "granite", "qwen2_moe", "ernie4_5_moe"])
 def test_hugging_face_loads_what_this_framework_saves(tmp_path, family):
     """The other direction: a checkpoint written by ``save_pretrained`` here (per-expert tensors, interleaved rotary rows
     restored, HF config field names) loads in ``transformers`` and gives the same logits."""
