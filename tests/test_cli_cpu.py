@@ -198,3 +198,25 @@ def test_example_configs_parse(monkeypatch):
 
         model_args, data_args, gen_args, export_args, train_args = parse_dict(dict(flat, device="cpu"))
         assert model_args.stage and train_args.output_dir, f
+
+
+def test_preprocess_tool_writes_a_corpus_that_gpt_dataset_reads(tmp_path):
+    from paddleformers_b200.data.indexed_dataset import GPTDataset, MMapIndexedDataset
+    from paddleformers_b200.data.preprocess import main as preprocess_main
+
+    tok_dir, vocab = _tiny_tokenizer_dir(tmp_path)
+    src = tmp_path / "corpus.jsonl"
+    rng = np.random.RandomState(0)
+    docs = [" ".join(f"w{i}" for i in rng.randint(0, 60, size=rng.randint(5, 30))) for _ in range(40)]
+    with open(src, "w") as f:
+        for d in docs:
+            f.write(json.dumps({"text": d}) + "\n")
+    prefix = str(tmp_path / "out" / "corpus")
+    assert preprocess_main(["--input", str(src), "--tokenizer", tok_dir, "--output-prefix", prefix, "--append-eos"]) == 0
+    ds = MMapIndexedDataset(prefix)
+    assert len(ds) == 40 and ds.dtype == np.uint16
+    first = ds[0]
+    assert first[-1] == 2 and len(first) == len(docs[0].split()) + 1             # eos appended
+    g = GPTDataset(ds, None, num_samples=10, seq_length=16, seed=1)
+    item = g[0]
+    assert item["input_ids"].shape == (16,) and torch.equal(item["input_ids"][1:], item["labels"][:-1])
