@@ -54,7 +54,7 @@ def _documents(path: str, key: str) -> Iterator[str]:
         with open(path, encoding="utf-8") as f:
             for line in f:
                 if line.strip():
-                    yield line.rstrip("\\n")
+                    yield line.rstrip("\n")
 
 
 def preprocess(input_path: str, tokenizer_dir: str, output_prefix: str, json_key: str = "text", append_eos: bool = True,
@@ -88,7 +88,7 @@ def preprocess(input_path: str, tokenizer_dir: str, output_prefix: str, json_key
 
 
 def main(argv=None):
-    ap = argparse.ArgumentParser(description=__doc__.split("\\n")[0])
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--input", required=True)
     ap.add_argument("--tokenizer", required=True)
     ap.add_argument("--output-prefix", required=True)
