@@ -63,7 +63,9 @@ class TrainingArguments:
     context_parallel_size: int = 1
     sep_parallel_size: int = 1
     sharding_parallel_size: int = -1
-    sharding: str = field(default="", metadata={"help": "'' | stage1 | stage2"})
+    sharding: str = field(default="", metadata={"help": "'' | stage1 | stage2 (optimizer-state sharding; stage2 is accepted for "
+                                                        "configuration compatibility and runs the stage1 plan: gradients stay in the "
+                                                        "full fp32 accumulation buffer that the weight-gradient GEMMs write)"})
     sequence_parallel: bool = False
     hybrid_parallel_topo_order: str = "sharding_first"
     pipeline_schedule: str = field(default="1F1B", metadata={"help": "1F1B | interleaved | FThenB | zero_bubble (backward split into input-gradient and deferred weight-gradient parts)"})
