@@ -312,6 +312,49 @@ class ShardedAdamW:
             if dom.shard_group is not None:
                 dist.all_gather_into_tensor(dom.flat_param, dom.shard_slice(dom.flat_param).clone(), group=dom.shard_group)
 
+    # ------------------------------------------------------------------ parallelism-independent state
+    def gather_full_state(self, kind: str) -> Dict[int, torch.Tensor]:
+        """``kind`` in {master, exp_avg, exp_avg_sq}: for every parameter, an fp32 tensor of the parameter's (local) shape
+        holding that state, assembled from the sharding group's slices (collective over each domain's sharding group).
+        Keys are ``id(param)``. Together with the tensor-parallel gathers of the model writer this yields optimizer state
+        that does not depend on the parallel layout."""
+        out: Dict[int, torch.Tensor] = {}
+        for dom in self.domains:
+            local = getattr(dom, kind)
+            if dom.shard_group is not None:
+                full = torch.empty(dom.numel, dtype=local.dtype, device=local.device)
+                dist.all_gather_into_tensor(full, local.contiguous(), group=dom.shard_group)
+            else:
+                full = local
+            for name, p in dom.params:
+                off, n = dom.offsets[name]
+                out[id(p)] = full[off:off + n].view(p.shape)
+        return out
+
+    def full_state_buffers(self) -> Dict[str, Dict[int, torch.Tensor]]:
+        """Writable fp32 staging tensors (one per parameter and state kind) plus a commit step: see ``commit_full_state``."""
+        self._staging = {}
+        views: Dict[str, Dict[int, torch.Tensor]] = {}
+        for kind in ("master", "exp_avg", "exp_avg_sq"):
+            views[kind] = {}
+            for dom in self.domains:
+                full = torch.zeros(dom.numel, dtype=torch.float32, device=dom.master.device)
+                self._staging[(kind, dom.name)] = full
+                for name, p in dom.params:
+                    off, n = dom.offsets[name]
+                    views[kind][id(p)] = full[off:off + n].view(p.shape)
+        return views
+
+    def commit_full_state(self, step: int, lr: Optional[float] = None) -> None:
+        """Cut this rank's slices out of the staging tensors filled through ``full_state_buffers`` and rebuild the working
+        weights from the master slices."""
+        sd = {"step": step, "lr": self.lr if lr is None else lr, "domains": {}}
+        for dom in self.domains:
+            sd["domains"][dom.name] = {k: dom.shard_slice(self._staging[(k, dom.name)]) for k in ("master", "exp_avg", "exp_avg_sq")}
+            sd["domains"][dom.name].update(shard_size=dom.shard_size, numel=dom.numel)
+        self.load_state_dict(sd)
+        self._staging = {}
+
     def memory_bytes(self) -> int:
         tot = 0
         for dom in self.domains:

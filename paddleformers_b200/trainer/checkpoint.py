@@ -79,6 +79,8 @@ def save_checkpoint(trainer, out_dir: str) -> None:
     else:
         # 1. model weights (collective: tp gathers)
         trainer.model.save_pretrained(out_dir)
+        if getattr(args, "save_checkpoint_format", "sharded") == "unified":
+            save_unified_optimizer(trainer, out_dir)
         # 2. this rank's optimizer shards (moved to host now, written below or in the background)
         opt_state = trainer.optimizer.state_dict()
     files = {}
@@ -131,6 +133,34 @@ def save_checkpoint(trainer, out_dir: str) -> None:
     logger.info(f"saved checkpoint to {out_dir}")
 
 
+UNIFIED_DIR = "unified_optimizer"
+
+
+def save_unified_optimizer(trainer, out_dir: str) -> None:
+    """Optimizer state under parameter names in safetensors, independent of the tensor / sharding / expert layout that
+    wrote it: fp32 master weights and both Adam moments go through the same gathers and weight-map rules as the model
+    weights (the reference's unified checkpoint, paddleformers/trainer/unified_checkpoint/unified_checkpoint.py:92)."""
+    opt = trainer.optimizer
+    for kind in ("master", "exp_avg", "exp_avg_sq"):
+        state = opt.gather_full_state(kind)
+        trainer.model.save_pretrained(os.path.join(out_dir, UNIFIED_DIR, kind), save_config=False,
+                                      tensor_for=lambda obj, state=state: state.get(id(obj)))
+    if trainer.args.process_index == 0:
+        with open(os.path.join(out_dir, UNIFIED_DIR, "meta.json"), "w") as f:
+            json.dump({"step": opt.step_count, "lr": opt.lr}, f)
+
+
+def load_unified_optimizer(trainer, path: str) -> None:
+    opt = trainer.optimizer
+    views = opt.full_state_buffers()
+    for kind in ("master", "exp_avg", "exp_avg_sq"):
+        trainer.model.load_hf_checkpoint(os.path.join(path, UNIFIED_DIR, kind),
+                                         target_for=lambda p, v=views[kind]: v.get(id(p)))
+    with open(os.path.join(path, UNIFIED_DIR, "meta.json")) as f:
+        meta = json.load(f)
+    opt.commit_full_state(int(meta["step"]), float(meta["lr"]))
+
+
 def load_checkpoint(trainer, path: str) -> None:
     from .trainer_callback import TrainerState
 
@@ -149,6 +179,18 @@ def load_checkpoint(trainer, path: str) -> None:
     opt = trainer.optimizer
     opt_dir = os.path.join(path, "optimizer")
     sd = {"domains": {}}
+    unified = os.path.isdir(os.path.join(path, UNIFIED_DIR))
+    saved_degrees = None
+    meta_file = os.path.join(path, "save_meta.json")
+    if os.path.exists(meta_file):
+        with open(meta_file) as f:
+            saved_degrees = json.load(f).get("degrees")
+    layout_changed = saved_degrees is not None and any(
+        int(saved_degrees.get(k, 1)) != int(getattr(ps.degrees, k)) for k in ("mp", "pp", "ep"))
+    if unified and (layout_changed or getattr(args, "load_checkpoint_format", "sharded") == "unified"):
+        load_unified_optimizer(trainer, path)          # tensor / pipeline / expert degrees differ: shards cannot be re-cut
+        _finish_load(trainer, path, rank)
+        return
     for dom in opt.domains:
         want = f"shard_{dom.name}_{dom.shard_rank:03d}of{dom.shard_size:03d}_"
         cands = sorted(f for f in os.listdir(opt_dir) if f.startswith(want) and f.endswith(".pt"))
@@ -159,6 +201,12 @@ def load_checkpoint(trainer, path: str) -> None:
         sd["domains"][dom.name] = payload
         sd["step"], sd["lr"] = payload["step"], payload["lr"]
     opt.load_state_dict(sd)
+    _finish_load(trainer, path, rank)
+
+
+def _finish_load(trainer, path: str, rank: int) -> None:
+    from .trainer_callback import TrainerState
+
     st_file = os.path.join(path, "trainer_state.json")
     if os.path.exists(st_file):
         loaded = TrainerState.load_from_json(st_file)

@@ -149,7 +149,10 @@ class PretrainedModel(nn.Module):
         return model
 
     # ------------------------------------------------------------------ loading
-    def load_hf_checkpoint(self, directory: str, strict: bool = False) -> None:
+    def load_hf_checkpoint(self, directory: str, strict: bool = False, target_for=None) -> None:
+        """``target_for(param) -> tensor | None`` redirects the copy: the loaded (and sharded) value of every parameter goes
+        into the returned tensor instead of the parameter, parameters mapped to None are skipped. Used to read optimizer
+        state stored under parameter names."""
         reader = _CheckpointReader(directory)
         wm = self.weight_map()
         ps = get_parallel_state()
@@ -173,6 +176,8 @@ class PretrainedModel(nn.Module):
         local_targets = dict(self.named_parameters())
         local_targets.update({k: v for k, v in self.named_buffers() if k in self.state_dict()})
         targets = {self.global_param_name(k): v for k, v in local_targets.items()}
+        if target_for is not None:
+            targets = {k: v for k, v in targets.items() if target_for(v) is not None}
         with torch.no_grad():
             for name, p in targets.items():
                 rule = wm.rule_for(name)
@@ -200,7 +205,9 @@ class PretrainedModel(nn.Module):
                 shard = spec.shard(full, tp_rank, tp_size, ep_rank, ep_size)
                 if tuple(shard.shape) != tuple(p.shape):
                     raise ValueError(f"shape mismatch for {name}: checkpoint {tuple(shard.shape)} vs model {tuple(p.shape)}")
-                p.copy_(shard.to(p.dtype))
+                dst = p if target_for is None else target_for(p)
+                if dst is not None:
+                    dst.copy_(shard.to(dst.dtype))
                 loaded += 1
         missing = [m for m in missing if not any(re.search(pat, m) for pat in self._keys_to_ignore_on_load_missing)]
         if missing:
@@ -217,8 +224,10 @@ class PretrainedModel(nn.Module):
         logger.info(f"loaded {loaded} tensors from {directory}")
 
     # ------------------------------------------------------------------ saving
-    def hf_state_dict_items(self):
+    def hf_state_dict_items(self, tensor_for=None):
         """Yields (hf_name, full tensor on CPU) for every parameter this rank is responsible for writing.
+        ``tensor_for(param_or_buffer) -> tensor | None`` substitutes the value that is written (same shape as the local
+        parameter; None skips it): optimizer state saved under parameter names goes through the same gathers and rules.
 
         Tensor-parallel shards are all-gathered inside the tp group (rank 0 of the group writes); expert-parallel
         ranks each write their own experts (HF names carry the global expert id)."""
@@ -237,8 +246,13 @@ class PretrainedModel(nn.Module):
             seen.add(name)
             if not self.owns_global_param(local_name):
                 continue
-            spec = param_shard_spec(self._param_or_buffer(local_name))
+            obj = self._param_or_buffer(local_name)
+            spec = param_shard_spec(obj)
             is_expert = spec.ep_dim is not None
+            if tensor_for is not None:
+                t = tensor_for(obj)
+                if t is None:
+                    continue
             full = t.detach()
             if spec.tp_dim is not None and tp_size > 1:
                 # every tensor-parallel rank takes part in the gather; one of them keeps the result
@@ -269,7 +283,8 @@ class PretrainedModel(nn.Module):
         mod = self.get_submodule(mod_name) if mod_name else self
         return getattr(mod, leaf)
 
-    def save_pretrained(self, save_directory: str, max_shard_size: int = 5 * 1024 ** 3, save_config: bool = True) -> None:
+    def save_pretrained(self, save_directory: str, max_shard_size: int = 5 * 1024 ** 3, save_config: bool = True,
+                        tensor_for=None) -> None:
         from safetensors.torch import save_file
 
         ps = get_parallel_state()
@@ -279,7 +294,7 @@ class PretrainedModel(nn.Module):
             writer_tag = f"pp{ps.coord['pp']:02d}"
         shards: List[Dict[str, torch.Tensor]] = [{}]
         size = 0
-        for hf_name, ten in self.hf_state_dict_items():
+        for hf_name, ten in self.hf_state_dict_items(tensor_for):
             nbytes = ten.numel() * ten.element_size()
             if size + nbytes > max_shard_size and shards[-1]:
                 shards.append({})

@@ -267,3 +267,21 @@ def test_tensor_parallel_checkpoint_loads_in_one_process(tmp_path):
     for (n1, p1), (n2, p2) in zip(a.state_dict().items(), b.state_dict().items()):
         assert n1 == n2
         torch.testing.assert_close(p1, p2, rtol=2e-3, atol=2e-4)
+
+
+def test_unified_checkpoint_resumes_under_a_different_tensor_parallel_degree(tmp_path):
+    """Optimizer state written under parameter names by 2 tensor-parallel ranks restores a 1-rank run that continues
+    like an uninterrupted one (and the other way round: 1 rank -> 2 tensor-parallel ranks)."""
+    full = _reference(False, 4, 2)
+    single = dict(gradient_accumulation_steps=2, save_checkpoint_format="unified")
+    tp2 = dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2, save_checkpoint_format="unified")
+    ref = run_distributed(_train_and_save, 1, dict(gradient_accumulation_steps=2), 4, full, str(tmp_path / "ref"), False)[0]
+    run_distributed(_train_and_save, 2, tp2, 2, full, str(tmp_path / "a"), False)
+    got = run_distributed(_train_and_save, 1, single, 4, full, str(tmp_path / "a"), True)[0]
+    for a, b in zip(ref[2:], got[-2:]):
+        assert abs(a - b) < 3e-4 * max(1.0, abs(a)), (ref, got)
+    run_distributed(_train_and_save, 1, single, 2, full, str(tmp_path / "b"), False)
+    got2 = run_distributed(_train_and_save, 2, tp2, 4, full, str(tmp_path / "b"), True)
+    for r in range(2):
+        for a, b in zip(ref[2:], got2[r][-2:]):
+            assert abs(a - b) < 3e-4 * max(1.0, abs(a)), (ref, got2[r])
