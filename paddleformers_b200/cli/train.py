@@ -36,6 +36,13 @@ def _build_model(model_args, train_args, dtype):
         model = AutoModelForCausalLM.from_config(config, dtype=dtype, device=device)
     else:
         model = AutoModelForCausalLM.from_pretrained(model_args.model_name_or_path, config=config, dtype=dtype, device=device)
+    if getattr(config, "fp8", None):
+        # block-scaled fp8 forward / input-gradient GEMMs for the dense projections (experts switch on config.fp8 themselves);
+        # the vocabulary head and the routers stay in bf16 / fp32
+        from ..quantization.fp8 import convert_linears_to_fp8
+
+        n = convert_linears_to_fp8(model)
+        logger.info(f"fp8 ({config.fp8}): {n} dense linear layers run block-scaled e4m3 GEMMs")
     if train_args.weight_quantize_algo:
         from ..quantization.weight_only import quantize_model
 

@@ -220,3 +220,23 @@ def test_preprocess_tool_writes_a_corpus_that_gpt_dataset_reads(tmp_path):
     g = GPTDataset(ds, None, num_samples=10, seq_length=16, seed=1)
     item = g[0]
     assert item["input_ids"].shape == (16,) and torch.equal(item["input_ids"][1:], item["labels"][:-1])
+
+
+def test_fp8_flag_converts_dense_linears_in_the_workflow(tmp_path):
+    from paddleformers_b200.cli.hparams import parse_dict
+    from paddleformers_b200.cli.train import _build_model
+    from paddleformers_b200.quantization.fp8 import FP8Linear
+
+    flat = {"stage": "PT", "model_type": "tiny-llama", "from_scratch": True, "compute_type": "float32", "device": "cpu", "fp8": "e4m3",
+            "config_overrides": {"vocab_size": 128, "hidden_size": 128, "intermediate_size": 256, "num_attention_heads": 2,
+                                 "num_key_value_heads": 1, "head_dim": 64}, "output_dir": str(tmp_path)}
+    model_args, _, _, _, train_args = parse_dict(flat)
+    train_args.setup_parallel()
+    model, cfg = _build_model(model_args, train_args, torch.float32)
+    layer = model.model.layers["0"]
+    assert isinstance(layer.self_attn.qkv_proj, FP8Linear) and isinstance(layer.mlp.down_proj, FP8Linear)
+    assert not isinstance(model.lm_head, FP8Linear)
+    ids = torch.randint(0, 128, (2, 16))
+    out = model(ids, labels=torch.roll(ids, -1, 1))
+    out.loss.backward()
+    assert torch.isfinite(out.loss) and layer.self_attn.qkv_proj.weight.grad is not None
