@@ -105,6 +105,7 @@ class LlamaConfig(DecoderConfig):
     def __init__(self, **kw):
         kw.setdefault("rms_norm_eps", 1e-6)
         super().__init__(**kw)
+        self.attention_out_bias = bool(self.attention_bias)      # Llama's switch covers the output projection too
 
 
 class Qwen2Config(DecoderConfig):
@@ -222,9 +223,10 @@ class SeedOssConfig(DecoderConfig):
 
     model_type = "seed_oss"
 
-    def __init__(self, **kw):
+    def __init__(self, attention_out_bias=False, **kw):
         kw.setdefault("attention_bias", True)
         super().__init__(**kw)
+        self.attention_out_bias = bool(attention_out_bias)
 
 
 class InternLM3Config(DecoderConfig):
@@ -232,10 +234,12 @@ class InternLM3Config(DecoderConfig):
 
     model_type = "internlm3"
 
-    def __init__(self, qkv_bias=False, **kw):
+    def __init__(self, qkv_bias=False, bias=False, **kw):
         kw.setdefault("attention_bias", bool(qkv_bias))
+        kw.setdefault("mlp_bias", bool(bias))
         super().__init__(**kw)
-        self.qkv_bias = qkv_bias
+        self.qkv_bias, self.bias = qkv_bias, bias
+        self.attention_out_bias = bool(bias)
 
 
 class Qwen2MoeConfig(DecoderConfig):

@@ -167,7 +167,8 @@ class Attention(nn.Module):
         H = config.hidden_size
         secs = [self.Hq_total * self.D, self.Hkv_total * self.D, self.Hkv_total * self.D]
         self.qkv_proj = _linear(H, sum(secs), config.attention_bias, "colwise", config, sections=secs, dtype=dtype, device=device)
-        self.o_proj = _linear(self.Hq_total * self.D, H, False, "rowwise", config, dtype=dtype, device=device)
+        self.o_proj = _linear(self.Hq_total * self.D, H, bool(getattr(config, "attention_out_bias", False)), "rowwise", config,
+                              dtype=dtype, device=device)
         self.use_qk_norm = config.use_qk_norm
         self.qk_norm_full = bool(getattr(config, "qk_norm_full", False))      # one RMSNorm over all heads' features (OLMo2)
         if self.qk_norm_full:
@@ -664,6 +665,9 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
         rules.append(Rule("model.norm.weight", ["model.norm.weight"], offset=off))
         for nm in ("input_layernorm.weight", "post_attention_layernorm.weight"):
             per_layer.append(Rule(L + nm, [L + nm], offset=off))
+    dense_rules = [dense_rule]
+    if config.mlp_bias and not getattr(config, "hf_fused_gate_up", False):
+        dense_rules.append(Rule(L + "mlp.gate_up_proj.bias", [L + "mlp.gate_proj.bias", L + "mlp.up_proj.bias"], "concat", 0))
     n_total = config.num_hidden_layers + int(getattr(config, "num_nextn_predict_layers", 0) or 0)
     for i in range(config.num_hidden_layers):
         rules.extend(expand_layers(per_layer, [i]))
@@ -683,7 +687,7 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
                 rules.append(Rule(pre + "shared_experts.gate_up_proj.weight",
                                   [pre + sh + ".gate_proj.weight", pre + sh + ".up_proj.weight"], "concat", 0))
         else:
-            rules.extend(expand_layers([dense_rule], [i]))
+            rules.extend(expand_layers(dense_rules, [i]))
     # MTP layers are stored by HF DeepSeek-V3 / GLM-4.5 as extra entries of model.layers
     for k in range(n_total - config.num_hidden_layers):
         i = config.num_hidden_layers + k

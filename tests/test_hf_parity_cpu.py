@@ -18,6 +18,7 @@ CASES = {
     "llama3_scaling": ("LlamaConfig", "LlamaForCausalLM", dict(rope_theta=500000.0, rope_scaling={
         "rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 16})),
     "llama_linear_scaling": ("LlamaConfig", "LlamaForCausalLM", dict(rope_scaling={"rope_type": "linear", "factor": 4.0})),
+    "llama_biases_tied": ("LlamaConfig", "LlamaForCausalLM", dict(attention_bias=True, mlp_bias=True, tie_word_embeddings=True, head_dim=32)),
     "mistral": ("MistralConfig", "MistralForCausalLM", dict(sliding_window=None)),
     "qwen2": ("Qwen2Config", "Qwen2ForCausalLM", dict()),
     "qwen3": ("Qwen3Config", "Qwen3ForCausalLM", dict(head_dim=16)),
