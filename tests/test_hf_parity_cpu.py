@@ -28,6 +28,17 @@ CASES = {
                                                            logits_scaling=2.0)),
     "qwen3_moe": ("Qwen3MoeConfig", "Qwen3MoeForCausalLM", dict(head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
                                                                norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[])),
+    "qwen3_moe_mixed_layers": ("Qwen3MoeConfig", "Qwen3MoeForCausalLM", dict(
+        head_dim=16, num_hidden_layers=4, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, norm_topk_prob=False,
+        decoder_sparse_step=2, mlp_only_layers=[1])),
+    "deepseek_v3_groups": ("DeepseekV3Config", "DeepseekV3ForCausalLM", dict(
+        num_hidden_layers=3, num_key_value_heads=4, moe_intermediate_size=32, n_routed_experts=16, num_experts_per_tok=4, n_group=4,
+        topk_group=2, n_shared_experts=2, first_k_dense_replace=2, q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=16,
+        qk_rope_head_dim=8, v_head_dim=16, routed_scaling_factor=1.0, norm_topk_prob=False)),
+    "glm4_moe_plain": ("Glm4MoeConfig", "Glm4MoeForCausalLM", dict(
+        head_dim=16, moe_intermediate_size=32, n_routed_experts=8, num_experts_per_tok=2, n_group=2, topk_group=1, n_shared_experts=1,
+        first_k_dense_replace=0, partial_rotary_factor=0.5, use_qk_norm=False, attention_bias=True, routed_scaling_factor=1.0,
+        norm_topk_prob=True)),
     "qwen2_moe": ("Qwen2MoeConfig", "Qwen2MoeForCausalLM", dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
                                                                shared_expert_intermediate_size=48, norm_topk_prob=False,
                                                                decoder_sparse_step=1, mlp_only_layers=[])),
