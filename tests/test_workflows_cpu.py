@@ -123,3 +123,39 @@ def test_mla_mtp_and_glm_variants_train_and_roundtrip(tmp_path, preset, over):
             with safe_open(str(tmp_path / f), "pt") as sf:
                 names += list(sf.keys())
     assert any(n.startswith(f"model.layers.{cfg.num_hidden_layers}.") and "eh_proj" in n for n in names)
+
+
+def test_peft_adapter_export_and_import_preserve_the_function(tmp_path):
+    """Fused-layer adapters written in the Hugging Face PEFT layout (per-projection pairs), read back into fused layers of
+    a larger rank with block-diagonal B: same logits; and the per-projection tensors reproduce the delta by hand."""
+    from safetensors.torch import load_file
+
+    from paddleformers_b200.peft.hf_format import export_peft_adapter, import_peft_adapter
+    from paddleformers_b200.peft.lora import LoRAConfig, LoRAModel
+
+    base = _tiny()
+    ref_state = {k: v.clone() for k, v in base.state_dict().items()}
+    model = LoRAModel(base, LoRAConfig(r=4, lora_alpha=8))
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "lora_B" in n:
+                p.normal_(0, 0.05)                         # B starts at zero: make the adapters matter
+    ids = torch.randint(0, 64, (2, 12))
+    with torch.no_grad():
+        want = model(ids, return_logits=True).logits
+    export_peft_adapter(model, str(tmp_path))
+    sd = load_file(str(tmp_path / "adapter_model.safetensors"))
+    assert "base_model.model.model.layers.0.self_attn.k_proj.lora_B.weight" in sd
+    assert "base_model.model.model.layers.1.mlp.up_proj.lora_A.weight" in sd and not any("qkv_proj" in k for k in sd)
+    # the per-projection pair reproduces the fused delta rows of that projection
+    lin = model.model.model.layers["0"].self_attn.qkv_proj
+    q_rows = base.config.num_attention_heads * base.config.head_dim
+    delta_k = sd["base_model.model.model.layers.0.self_attn.k_proj.lora_B.weight"] @ sd["base_model.model.model.layers.0.self_attn.k_proj.lora_A.weight"]
+    torch.testing.assert_close(delta_k * model.lora_config.scaling, lin.delta()[q_rows:q_rows + delta_k.shape[0]], rtol=1e-5, atol=1e-6)
+    # a fresh copy of the base model + the PEFT directory == the adapted model
+    fresh = _tiny()
+    fresh.load_state_dict(ref_state)
+    again = import_peft_adapter(fresh, str(tmp_path))
+    assert again.lora_config.r == 12                        # q, k, v pairs stacked
+    with torch.no_grad():
+        torch.testing.assert_close(again(ids, return_logits=True).logits, want, rtol=1e-4, atol=1e-5)
