@@ -30,7 +30,7 @@ from . import checkpoint as ckpt
 from .trainer_callback import (CallbackHandler, DefaultFlowCallback, FP8QuantWeightCallback, MetricsDumpCallback,
                                MoECorrectionBiasAdjustCallback, PrinterCallback, ProfilerCallback, TrainerCallback,
                                TrainerControl, TrainerState)
-from .trainer_utils import (PREFIX_CHECKPOINT_DIR, LRScheduler, TrainerMemoryTracker, get_last_checkpoint,
+from .trainer_utils import (PREFIX_CHECKPOINT_DIR, LRScheduler, TrainerMemoryTracker, get_last_checkpoint, tensor_md5,
                             get_scheduler_lambda, set_random_seed, speed_metrics)
 from .training_args import TrainingArguments
 
@@ -415,6 +415,10 @@ class Trainer:
             dt = max(now - self._last_log_time, 1e-9)
             logs = {"loss": round(loss_v, 6), "learning_rate": self.lr_scheduler.get_lr(), "global_step": self.state.global_step,
                     "epoch": round(self.state.epoch, 4)}
+            if a.log_loss_md5 or os.environ.get("LOG_LOSS_MD5", "0") == "1":
+                # digest of the fp32 bit pattern: two runs (or two frameworks) agree bit for bit iff the digests match
+                # (paddleformers/trainer/trainer.py:3006-3015)
+                logs["loss_md5"] = tensor_md5(loss.detach().float().reshape(1))
             gn = getattr(self, "_last_grad_norm", None)
             if gn is not None:
                 logs["global_norm"] = round(float(gn), 6)

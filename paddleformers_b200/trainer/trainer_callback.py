@@ -218,6 +218,11 @@ class ProfilerCallback(TrainerCallback):
         step = state.global_step
         if step == args.profile_step_start:
             torch.cuda.cudart().cudaProfilerStart()
+            depth = int(getattr(args, "profile_nvtx_depth", 0) or 0)
+            if depth > 0 and kw.get("model") is not None:
+                from ..utils.profiler import NvtxModuleRanges
+
+                self._ranges = NvtxModuleRanges(kw["model"], depth=depth)   # one range per sub-module, forward and backward
         if args.profile_step_start <= step < args.profile_step_end:
             torch.cuda.nvtx.range_push(f"step_{step}")
 
@@ -229,3 +234,6 @@ class ProfilerCallback(TrainerCallback):
             torch.cuda.nvtx.range_pop()
         if step + 1 == args.profile_step_end:
             torch.cuda.cudart().cudaProfilerStop()
+            if getattr(self, "_ranges", None) is not None:
+                self._ranges.remove()
+                self._ranges = None

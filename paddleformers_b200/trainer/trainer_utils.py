@@ -131,6 +131,28 @@ def speed_metrics(split: str, start_time: float, num_samples=None, num_steps=Non
     return out
 
 
+def tensor_md5(t: torch.Tensor) -> str:
+    """Hex md5 of a tensor's bytes (bf16 is widened to fp32 first, which is exact). Used to compare runs bit for bit:
+    loss values, batches, parameters after a resume."""
+    import hashlib
+
+    t = t.detach()
+    if t.dtype == torch.bfloat16:
+        t = t.float()
+    return hashlib.md5(t.contiguous().cpu().numpy().tobytes()).hexdigest()
+
+
+def state_digest(tensors) -> str:
+    """One md5 over an ordered ``name -> tensor`` mapping (names included, so a renamed or reordered entry changes it)."""
+    import hashlib
+
+    h = hashlib.md5()
+    for k, v in tensors.items():
+        h.update(k.encode())
+        h.update(tensor_md5(v).encode())
+    return h.hexdigest()
+
+
 def set_seed(seed: int):
     random.seed(seed)
     np.random.seed(seed % (2 ** 32))

@@ -88,6 +88,7 @@ class TrainingArguments:
     ema_decay: float = 0.0                      # > 0: keep an exponential moving average of the fp32 master shards
     ema_start_step: int = 0
     enable_timer: bool = False         # per-step read-data / forward-backward / optimizer-step timers in the log record
+    log_loss_md5: bool = False         # md5 of the logged loss's fp32 bytes in the log record (also: LOG_LOSS_MD5=1)
     log_memory: bool = False           # device memory high-water marks in the log record
     metrics_output_path: Optional[str] = None
     resume_from_checkpoint: Optional[str] = None
@@ -106,6 +107,7 @@ class TrainingArguments:
     profile_step_start: int = 3
     profile_step_end: int = 5
     skip_profile_timer: bool = True
+    profile_nvtx_depth: int = 0         # > 0: inside the profile window, one NVTX range per sub-module down to this depth
     profile_backend: str = "cuda_api"   # cuda_api: cudaProfilerStart/Stop window for an external profiler | torch: torch.profiler trace
     disable_tqdm: bool = True
     device: Optional[str] = None

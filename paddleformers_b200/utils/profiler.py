@@ -20,20 +20,59 @@ from ..trainer.trainer_callback import TrainerCallback
 from .log import logger
 
 _profiling = False
+_open_step_range = False
 
 
 def switch_profile(step: int, start: int, end: int, enable_nvtx: bool = True) -> None:
-    global _profiling
+    """Call once at the top of every step. Each step inside the window is one NVTX range ``step_<n>``; the range of the
+    previous step is closed before the next one opens, and the last one before the profiler stops."""
+    global _profiling, _open_step_range
     if not torch.cuda.is_available():
         return
+    if _open_step_range:
+        torch.cuda.nvtx.range_pop()
+        _open_step_range = False
     if step == start and not _profiling:
         torch.cuda.cudart().cudaProfilerStart()
         _profiling = True
-    if _profiling and enable_nvtx and start <= step < end:
-        torch.cuda.nvtx.range_push(f"step_{step}")
     if step == end and _profiling:
         torch.cuda.cudart().cudaProfilerStop()
         _profiling = False
+    if _profiling and enable_nvtx and start <= step < end:
+        torch.cuda.nvtx.range_push(f"step_{step}")
+        _open_step_range = True
+
+
+class NvtxModuleRanges:
+    """Forward pre / post hooks that wrap every sub-module down to ``depth`` levels in an NVTX range named by its
+    qualified name and class, plus full-backward hooks with a ``bwd:`` prefix, so that a timeline shows which layer a
+    kernel belongs to (the reference registers such hooks when its profiler is on: paddleformers/utils/perf_utils.py).
+    ``push`` / ``pop`` are injectable for tests; by default they are ``torch.cuda.nvtx.range_push`` / ``range_pop``."""
+
+    def __init__(self, model: torch.nn.Module, depth: int = 3, backward: bool = True, push=None, pop=None):
+        self.push = push or torch.cuda.nvtx.range_push
+        self.pop = pop or torch.cuda.nvtx.range_pop
+        self.handles = []
+        for name, mod in model.named_modules():
+            if name == "" or name.count(".") >= depth:
+                continue
+            label = f"{name}:{type(mod).__name__}"
+            self.handles.append(mod.register_forward_pre_hook(lambda m, a, _l=label: self.push(_l)))
+            self.handles.append(mod.register_forward_hook(lambda m, a, o, _l=label: self.pop(), always_call=True))
+            if backward:
+                self.handles.append(mod.register_full_backward_pre_hook(lambda m, g, _l=label: self.push("bwd:" + _l)))
+                self.handles.append(mod.register_full_backward_hook(lambda m, gi, go, _l=label: self.pop()))
+
+    def remove(self) -> None:
+        for h in self.handles:
+            h.remove()
+        self.handles = []
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.remove()
 
 
 class TorchProfilerCallback(TrainerCallback):

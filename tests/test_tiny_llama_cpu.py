@@ -173,3 +173,59 @@ def test_torch_profiler_window_writes_trace(tmp_path):
     st = StartupTimer()
     st.mark("imports"); st.mark("model")
     assert "imports" in st.report()
+
+
+def test_two_runs_with_one_seed_agree_bit_for_bit(tmp_path, monkeypatch):
+    """Run-to-run determinism, checked through the loss digests of the log records; a different seed changes them."""
+    from paddleformers_b200.trainer.trainer_utils import state_digest, tensor_md5
+
+    def run(sub, seed):
+        m, tr = _make(tmp_path / sub, 4, save_strategy="no", log_loss_md5=True, seed=seed)
+        tr.train()
+        return [h["loss_md5"] for h in tr.state.log_history if "loss_md5" in h], state_digest(dict(m.state_dict()))
+
+    a, da = run("a", 1)
+    b, db = run("b", 1)
+    assert len(a) == 4 and all(len(x) == 32 for x in a)
+    assert a == b and da == db
+    # the digest is of the fp32 bit pattern, so the smallest change shows
+    x = torch.tensor([1.0])
+    assert tensor_md5(x) != tensor_md5(torch.nextafter(x, torch.tensor([2.0])))
+    assert tensor_md5(x.bfloat16()) == tensor_md5(x)
+    # the environment switch does the same as the argument
+    monkeypatch.setenv("LOG_LOSS_MD5", "1")
+    _, tr = _make(tmp_path / "c", 1, save_strategy="no")
+    tr.train()
+    assert "loss_md5" in tr.state.log_history[0]
+
+
+def test_module_ranges_nest_and_balance_in_forward_and_backward():
+    from paddleformers_b200.utils.profiler import NvtxModuleRanges
+
+    torch.manual_seed(0)
+    model = AutoModelForCausalLM.from_config(named_config("tiny-llama"))
+    events, stack = [], []
+
+    def push(label):
+        stack.append(label)
+        events.append(("push", label, len(stack)))
+
+    def pop():
+        events.append(("pop", stack.pop(), len(stack)))
+
+    ids = torch.randint(0, 32000, (1, 16))
+    with NvtxModuleRanges(model, depth=3, push=push, pop=pop) as ranges:
+        assert ranges.handles
+        out = model(input_ids=ids, labels=ids)
+        loss = out[0] if isinstance(out, tuple) else out.loss
+        assert not stack                     # every forward range closed
+        loss.backward()
+        assert not stack                     # every backward range closed
+    pushed = [e[1] for e in events if e[0] == "push"]
+    assert any(l.startswith("model.layers.0:") for l in pushed) and any(l.startswith("model.layers.1:") for l in pushed)
+    assert any(l.startswith("bwd:model.layers.0:") for l in pushed)
+    assert max(e[2] for e in events) >= 2     # children open inside their parent's range
+    assert not any(l.count(".") >= 3 for l in (x.split(":")[-2] if x.startswith("bwd:") else x.split(":")[0] for x in pushed))
+    n = len(events)
+    model(input_ids=ids)                      # hooks removed on exit
+    assert len(events) == n
