@@ -1,5 +1,5 @@
-"""Text generation: greedy, sampling (temperature / top-k / top-p / repetition penalty) and beam search with a
-key/value cache, stopping criteria and a streamer hook.
+"""Text generation: greedy, sampling (temperature / top-k / top-p / repetition penalty), beam search and diverse
+(group) beam search, with a key/value cache, stopping criteria and a streamer hook.
 
 Counterpart: paddleformers/generation/utils.py:347 (``GenerationMixin``), :818 (``generate``), the logits processors
 and stopping criteria of paddleformers/generation/.
@@ -25,6 +25,9 @@ class GenerationConfig:
     top_p: float = 1.0
     repetition_penalty: float = 1.0
     num_beams: int = 1
+    num_beam_groups: int = 1
+    diversity_penalty: float = 0.0
+    num_return_sequences: int = 1
     length_penalty: float = 1.0
     eos_token_id: Optional[int] = None
     pad_token_id: Optional[int] = None
@@ -143,43 +146,73 @@ def generate(model, input_ids: torch.Tensor, generation_config: Optional[Generat
 
 
 def _beam_search(model, input_ids, cfg: GenerationConfig):
+    """Beam search; with ``num_beam_groups`` > 1 the beams are split into groups that are advanced one after the other
+    inside every step, and a token already chosen by an earlier group in that step costs ``diversity_penalty`` per use
+    (Hamming diversity), so that the groups explore different continuations
+    (paddleformers/generation/utils.py: ``group_beam_search``). ``num_return_sequences`` best hypotheses are returned per
+    input, [B * num_return_sequences, L]."""
     B, nb = input_ids.shape[0], cfg.num_beams
+    ng = max(int(getattr(cfg, "num_beam_groups", 1) or 1), 1)
+    if nb % ng != 0:
+        raise ValueError(f"num_beams {nb} must be a multiple of num_beam_groups {ng}")
+    if ng > 1 and float(getattr(cfg, "diversity_penalty", 0.0) or 0.0) <= 0.0:
+        raise ValueError("group beam search needs diversity_penalty > 0 (otherwise every group finds the same beams)")
+    gs = nb // ng
+    nret = max(int(getattr(cfg, "num_return_sequences", 1) or 1), 1)
+    if nret > nb:
+        raise ValueError("num_return_sequences must not exceed num_beams")
     dev = input_ids.device
     seq = input_ids.repeat_interleave(nb, 0)
-    scores = torch.zeros(B, nb, device=dev)
-    scores[:, 1:] = -1e9
+    scores = torch.full((B, nb), -1e9, device=dev)
+    scores[:, ::gs] = 0.0                           # one live beam per group at the start
     finished: List[List] = [[] for _ in range(B)]
     L0 = input_ids.shape[1]
     for step in range(cfg.max_new_tokens):
         out = model(seq, return_logits=True)
-        lp = torch.log_softmax(out.logits[:, -1].float(), -1)
-        V = lp.shape[-1]
-        cand = (scores.view(-1, 1) + lp).view(B, nb * V)
-        top, idx = cand.topk(2 * nb, dim=-1)
-        beam, tok = idx // V, idx % V
-        new_seq, new_scores = [], []
-        for b in range(B):
-            keep = []
-            for sc, bm, tk in zip(top[b].tolist(), beam[b].tolist(), tok[b].tolist()):
-                cand_seq = torch.cat([seq[b * nb + bm], torch.tensor([tk], device=dev)])
-                if cfg.eos_token_id is not None and tk == cfg.eos_token_id:
-                    finished[b].append((sc / ((cand_seq.numel() - L0) ** cfg.length_penalty), cand_seq))
-                else:
-                    keep.append((sc, cand_seq))
-                if len(keep) == nb:
-                    break
-            while len(keep) < nb:
-                keep.append((-1e9, keep[-1][1] if keep else seq[b * nb]))
-            new_seq += [k[1] for k in keep]
-            new_scores.append([k[0] for k in keep])
-        seq = torch.stack(new_seq)
+        lp_all = torch.log_softmax(out.logits[:, -1].float(), -1).view(B, nb, -1)
+        V = lp_all.shape[-1]
+        new_seq = [[None] * nb for _ in range(B)]
+        new_scores = [[-1e9] * nb for _ in range(B)]
+        chosen = torch.zeros(B, V, device=dev)       # tokens taken by earlier groups in this step
+        for g in range(ng):
+            lo = g * gs
+            lp = lp_all[:, lo:lo + gs]
+            if g > 0:
+                lp = lp - cfg.diversity_penalty * chosen[:, None, :]
+            cand = (scores[:, lo:lo + gs, None] + lp).reshape(B, gs * V)
+            top, idx = cand.topk(2 * gs, dim=-1)
+            beam, tok = idx // V, idx % V
+            for b in range(B):
+                keep = []
+                for sc, bm, tk in zip(top[b].tolist(), beam[b].tolist(), tok[b].tolist()):
+                    cand_seq = torch.cat([seq[b * nb + lo + bm], torch.tensor([tk], device=dev)])
+                    if cfg.eos_token_id is not None and tk == cfg.eos_token_id:
+                        finished[b].append((sc / ((cand_seq.numel() - L0) ** cfg.length_penalty), cand_seq))
+                    else:
+                        keep.append((sc, cand_seq))
+                    if len(keep) == gs:
+                        break
+                while len(keep) < gs:
+                    keep.append((-1e9, keep[-1][1] if keep else torch.cat([seq[b * nb + lo], seq.new_zeros(1)])))
+                for i, (sc, cs) in enumerate(keep):
+                    new_seq[b][lo + i], new_scores[b][lo + i] = cs, sc
+                    if sc > -1e8:
+                        chosen[b, cs[-1]] += 1
+        seq = torch.stack([x for row in new_seq for x in row])
         scores = torch.tensor(new_scores, device=dev)
         if all(len(f) >= nb for f in finished):
             break
     outs = []
     for b in range(B):
-        pool = finished[b] + [(scores[b, i].item() / max(seq.shape[1] - L0, 1) ** cfg.length_penalty, seq[b * nb + i]) for i in range(nb)]
-        outs.append(max(pool, key=lambda x: x[0])[1])
+        pool = finished[b] + [(scores[b, i].item() / max(seq.shape[1] - L0, 1) ** cfg.length_penalty, seq[b * nb + i])
+                              for i in range(nb) if scores[b, i].item() > -1e8]
+        pool.sort(key=lambda x: -x[0])
+        uniq = []
+        for sc, cs in pool:                           # groups may converge on one hypothesis: return distinct ones first
+            if not any(cs.numel() == u.numel() and torch.equal(cs, u) for u in uniq):
+                uniq.append(cs)
+        uniq += [p[1] for p in pool]
+        outs += uniq[:nret]
     n = max(o.numel() for o in outs)
     pad = cfg.pad_token_id if cfg.pad_token_id is not None else (cfg.eos_token_id or 0)
     return torch.stack([torch.cat([o, o.new_full((n - o.numel(),), pad)]) for o in outs])

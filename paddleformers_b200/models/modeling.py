@@ -455,6 +455,11 @@ class DecoderModel(nn.Module):
     def forward(self, input_ids, position_ids=None, kend=None, caches=None, ctx: Optional[BatchContext] = None,
                 cp_positions=None, full_seq_len=None, kend_full=None):
         ctx = ctx or self.make_context(input_ids, position_ids, kend, cp_positions, full_seq_len, kend_full)
+        if getattr(self.config, "moe_router_load_balancing_type", "aux_loss") == "seq_aux_loss":
+            for layer in self.layers.values():       # per-sequence balance loss: the router needs the rows-per-sequence of this batch
+                gate = getattr(getattr(layer, "mlp", None), "gate", None)
+                if gate is not None:
+                    gate.tokens_per_seq = 0 if self.sp else ctx.S
         h = self.embed(input_ids)
         hidden, residual = self.run_layers(h, None, ctx, caches)
         if self.norm is not None:

@@ -73,6 +73,10 @@ class TopkRouter(nn.Module):
         self.aux_coef = float(config.router_aux_loss_coef or 0.0)
         self.z_coef = float(config.router_z_loss_coef or 0.0)
         self.force_balance = bool(getattr(config, "moe_router_force_load_balancing", False))
+        # "seq_aux_loss": the balance term is computed per sequence and averaged, which also balances experts inside every
+        # sequence rather than only over the batch (paddleformers/nn/moe_deepep/moe_gate.py:126-158)
+        self.balance_type = str(getattr(config, "moe_router_load_balancing_type", "aux_loss") or "aux_loss")
+        self.tokens_per_seq = 0      # set by the decoder model when rows are laid out sequence after sequence
         # capacity: every expert serves at most ceil(factor * tokens * top_k / experts) routed pairs; the rest are dropped
         # (their combine weight becomes zero) by position in the batch or by routing probability
         # (paddleformers/nn/moe_deepep/moe_gate.py:75-97, :183-273)
@@ -121,7 +125,16 @@ class TopkRouter(nn.Module):
         aux = None
         if self.training and (self.aux_coef > 0 or self.z_coef > 0):
             aux = x2d.new_zeros((), dtype=torch.float32)
-            if self.aux_coef > 0:
+            S = int(self.tokens_per_seq or 0)
+            if self.aux_coef > 0 and self.balance_type == "seq_aux_loss" and 0 < S < T and T % S == 0:
+                probs = scores if self.scoring == "softmax" else scores / (scores.sum(-1, keepdim=True) + 1e-20)
+                nseq = T // S
+                seq_of = (torch.arange(T, device=x2d.device) // S)[:, None].expand_as(idx)
+                frac = torch.zeros(nseq * E, dtype=torch.float32, device=x2d.device).scatter_add_(
+                    0, (seq_of * E + idx).reshape(-1), torch.ones(idx.numel(), dtype=torch.float32, device=x2d.device))
+                frac = frac.view(nseq, E) / S
+                aux = aux + self.aux_coef * E * (frac * probs.view(nseq, S, E).mean(1)).sum(-1).mean()
+            elif self.aux_coef > 0 and self.balance_type != "none":
                 probs = scores if self.scoring == "softmax" else scores / (scores.sum(-1, keepdim=True) + 1e-20)
                 frac = torch.zeros(E, dtype=torch.float32, device=x2d.device).scatter_add_(
                     0, idx.reshape(-1), torch.ones(idx.numel(), dtype=torch.float32, device=x2d.device)) / max(T, 1)

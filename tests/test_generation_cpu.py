@@ -67,3 +67,35 @@ def test_generate_with_processors_criteria_and_streamer():
     generate(m, ids, GenerationConfig(max_new_tokens=3), streamer=st)
     text = "".join(st)
     assert len(text.split()) == 3
+
+
+def _seq_logprob(m, seq, L0):
+    lp = torch.log_softmax(m(seq[:, :-1], return_logits=True).logits.float(), -1)
+    return lp[:, L0 - 1:].gather(-1, seq[:, L0:, None]).squeeze(-1).sum(-1)
+
+
+def test_beam_search_beats_greedy_and_groups_diversify():
+    import pytest
+
+    m = _model()
+    ids = torch.randint(0, 64, (2, 5))
+    n = 5
+    greedy = generate(m, ids, GenerationConfig(max_new_tokens=n))
+    beams = generate(m, ids, GenerationConfig(max_new_tokens=n, num_beams=4, length_penalty=0.0))
+    assert beams.shape == greedy.shape
+    assert (_seq_logprob(m, beams, 5) >= _seq_logprob(m, greedy, 5) - 1e-5).all()
+    # several hypotheses per input, best first
+    many = generate(m, ids, GenerationConfig(max_new_tokens=n, num_beams=4, num_return_sequences=3, length_penalty=0.0))
+    assert many.shape == (6, 10) and torch.equal(many[0], beams[0]) and torch.equal(many[3], beams[1])
+    lp = _seq_logprob(m, many, 5).view(2, 3)
+    assert (lp[:, :-1] >= lp[:, 1:] - 1e-5).all()
+    # diverse beam search: a large penalty forces every group onto its own first token
+    div = generate(m, ids, GenerationConfig(max_new_tokens=n, num_beams=4, num_beam_groups=4, diversity_penalty=100.0,
+                                            num_return_sequences=4, length_penalty=0.0))
+    first = div[:, 5].view(2, 4)
+    assert all(len(set(row.tolist())) == 4 for row in first)
+    # plain beams of the same width share first tokens more often than not on a peaked model; at the least they are legal
+    with pytest.raises(ValueError):
+        generate(m, ids, GenerationConfig(max_new_tokens=2, num_beams=4, num_beam_groups=3, diversity_penalty=1.0))
+    with pytest.raises(ValueError):
+        generate(m, ids, GenerationConfig(max_new_tokens=2, num_beams=4, num_beam_groups=2))

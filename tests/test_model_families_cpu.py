@@ -310,3 +310,36 @@ def test_attention_implementation_switch_matches_default_path():
     for impl in ("eager", "sdpa"):
         model.config._attn_implementation = impl
         torch.testing.assert_close(model(ids, return_logits=True).logits, ref, rtol=1e-4, atol=1e-5)
+
+
+def test_sequence_level_balance_loss_is_the_mean_of_per_sequence_losses():
+    from paddleformers_b200.models.configuration import Qwen3MoeConfig
+    from paddleformers_b200.nn.moe import TopkRouter
+
+    torch.manual_seed(0)
+    cfg = Qwen3MoeConfig(hidden_size=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=8, intermediate_size=8,
+                         num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=2, vocab_size=32,
+                         router_aux_loss_coef=0.01)
+    router = TopkRouter(cfg).train()
+    with torch.no_grad():
+        router.weight.normal_(0, 1.0)
+    x = torch.randn(3 * 8, 16)
+    per_seq = torch.stack([router(x[i * 8:(i + 1) * 8])[2] for i in range(3)]).mean()
+    batch = router(x)[2]
+    router.balance_type, router.tokens_per_seq = "seq_aux_loss", 8
+    seq = router(x)[2]
+    assert torch.allclose(seq, per_seq, rtol=1e-5, atol=1e-8)
+    assert not torch.allclose(seq, batch, rtol=1e-4, atol=0)
+    router.tokens_per_seq = 0                               # unknown layout: falls back to the batch-level term
+    assert torch.allclose(router(x)[2], batch)
+    router.balance_type = "none"
+    assert float(router(x)[2]) == 0.0
+    # end to end: the model sets the rows per sequence and the loss back-propagates into the router
+    mcfg = AutoConfig.for_model("qwen3_moe", **dict(TINY, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
+                                                    router_aux_loss_coef=0.01, moe_router_load_balancing_type="seq_aux_loss"))
+    model = AutoModelForCausalLM.from_config(mcfg, dtype=torch.float32).train()
+    ids = torch.randint(0, 96, (2, 12))
+    out = model(ids, labels=ids)
+    (out[0] if isinstance(out, tuple) else out.loss).backward()
+    gate = model.model.layers["0"].mlp.gate
+    assert gate.tokens_per_seq == 12 and gate.weight.grad.abs().sum() > 0
