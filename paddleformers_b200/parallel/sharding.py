@@ -73,7 +73,11 @@ def default_no_decay(name: str) -> bool:
 
 
 class ShardedAdamW:
-    """AdamW over flat buffers; works for world size 1 (no sharding) up to any sharding / moe_sharding degree."""
+    """AdamW over flat buffers; works for world size 1 (no sharding) up to any sharding / moe_sharding degree.
+    Subclasses that set ``custom_update`` replace the update rule of a shard by their own ``_update`` (the gradient
+    reduction, clipping and parameter all-gather stay the same)."""
+
+    custom_update = False
 
     def __init__(self, model: torch.nn.Module, lr: float = 1e-4, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.0, max_grad_norm: float = 0.0, parallel_state: Optional[ParallelState] = None,
@@ -258,6 +262,8 @@ class ShardedAdamW:
             pslice = dom.shard_slice(dom.flat_param)
             if dom.is_muon:
                 self._muon_update(dom, g, pslice, sc)
+            elif self.custom_update:
+                self._update(dom, g, pslice, sc)
             elif g.is_cuda:
                 p16 = pslice if pslice.dtype == torch.bfloat16 else None
                 torch.ops.pfb200.adamw_step(dom.master, dom.exp_avg, dom.exp_avg_sq, g, p16, sc, b1, b2, self.eps,

@@ -166,16 +166,27 @@ class Trainer:
     def create_optimizer_and_scheduler(self, num_training_steps: int):
         a = self.args
         if self.optimizer is None:
-            opt_cls = ShardedAdamW
-            if str(getattr(a, "optim", "adamw")).lower() == "muon":
+            opt_cls, extra = ShardedAdamW, {}
+            name = str(getattr(a, "optim", "adamw")).lower()
+            if name == "muon":
                 from ..parallel.sharding import ShardedMuon
 
                 opt_cls = ShardedMuon
-            elif str(getattr(a, "optim", "adamw")).lower() not in ("adamw", "adamw_torch", "adamw_fused"):
-                raise ValueError(f"optim={a.optim!r}: expected adamw or muon")
+            elif name == "adamw_mini":
+                from ..utils.optimizer import AdamWMini
+
+                opt_cls = AdamWMini
+            elif name == "adamw_custom" or a.use_lowprecision_moment or a.tensorwise_offload_optimizer or a.hf_bitexact:
+                from ..utils.optimizer import AdamWCustom
+
+                opt_cls = AdamWCustom
+                extra = dict(moment_dtype=torch.bfloat16 if a.use_lowprecision_moment else torch.float32,
+                             offload_moments=a.tensorwise_offload_optimizer, hf_bitexact=a.hf_bitexact)
+            elif name not in ("adamw", "adamw_torch", "adamw_fused"):
+                raise ValueError(f"optim={a.optim!r}: expected adamw, adamw_mini, adamw_custom or muon")
             self.optimizer = opt_cls(self.model, lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2),
                                           eps=a.adam_epsilon, weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm,
-                                          parallel_state=self.ps, release_grads=a.release_grads)
+                                          parallel_state=self.ps, release_grads=a.release_grads, **extra)
         if self.lr_scheduler is None:
             min_ratio = a.min_lr / a.learning_rate if a.learning_rate > 0 else 0.0
             fn = get_scheduler_lambda(a.lr_scheduler_type, a.get_warmup_steps(num_training_steps), num_training_steps,

@@ -29,6 +29,15 @@ class SchedulerType(str, enum.Enum):
     WSD = "warmup_stable_decay"
 
 
+class OptimizerNames(str, enum.Enum):
+    """Accepted values of ``TrainingArguments.optim`` (paddleformers/trainer/trainer_utils.py:528-537)."""
+
+    ADAMW = "adamw"
+    ADAMW_MINI = "adamw_mini"
+    ADAMW_CUSTOM = "adamw_custom"
+    MUON = "muon"
+
+
 class ShardingOption(str, enum.Enum):
     SHARD_OP = "stage1"
     SHARD_GRAD_OP = "stage2"

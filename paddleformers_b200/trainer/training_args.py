@@ -49,7 +49,10 @@ class TrainingArguments:
     warmup_steps: int = 0
     warmup_ratio: float = 0.0
     decay_steps: Optional[int] = None
-    optim: str = "adamw"
+    optim: str = field(default="adamw", metadata={"help": "adamw | adamw_mini (one second moment per row) | adamw_custom | muon"})
+    use_lowprecision_moment: bool = False        # adamw_custom: Adam moments stored in bf16
+    tensorwise_offload_optimizer: bool = False   # adamw_custom: Adam moments live in host memory, streamed through the device
+    hf_bitexact: bool = False                    # adamw_custom: torch.optim.AdamW / clip_grad_norm_ operation order (one process)
     freeze_training: bool = field(default=False, metadata={"help": "lr = 0 and no updates (debugging aid)"})
     # precision
     bf16: bool = False

@@ -77,6 +77,8 @@ def _reference(moe, steps, accum):
     ("tp2_sp", 2, False, dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2)),
     ("tp2", 2, False, dict(tensor_model_parallel_size=2, gradient_accumulation_steps=2)),
     ("sharding2", 2, False, dict(sharding="stage1", gradient_accumulation_steps=1)),
+    ("sharding2_custom_adamw", 2, False, dict(sharding="stage1", gradient_accumulation_steps=1, optim="adamw_custom",
+                                              tensorwise_offload_optimizer=True)),
     ("dp2", 2, False, dict(gradient_accumulation_steps=1)),
     ("ep2", 2, True, dict(expert_model_parallel_size=2, sharding="stage1", gradient_accumulation_steps=1, moe_token_dispatcher_type="alltoall")),
     ("cp2", 2, False, dict(context_parallel_size=2, gradient_accumulation_steps=2)),
