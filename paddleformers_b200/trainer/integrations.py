@@ -163,6 +163,12 @@ def callbacks_from_args(args) -> List[TrainerCallback]:
         from .ema import EMACallback
 
         out.append(EMACallback(float(args.ema_decay), int(getattr(args, "ema_start_step", 0) or 0)))
+    if int(getattr(args, "internal_medicine_monitor_interval", 0) or 0) > 0:
+        from .health_monitor import HealthMonitorCallback
+
+        out.append(HealthMonitorCallback(getattr(args, "internal_medicine_monitors", None) or "all",
+                                         int(args.internal_medicine_monitor_interval),
+                                         log_dir=getattr(args, "logging_dir", None) or os.path.join(args.output_dir, "runs")))
     if getattr(args, "enable_timer", False):
         out.append(TimerCallback())
     if getattr(args, "log_memory", False):

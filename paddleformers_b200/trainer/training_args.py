@@ -93,6 +93,8 @@ class TrainingArguments:
     enable_timer: bool = False         # per-step read-data / forward-backward / optimizer-step timers in the log record
     log_loss_md5: bool = False         # md5 of the logged loss's fp32 bytes in the log record (also: LOG_LOSS_MD5=1)
     log_memory: bool = False           # device memory high-water marks in the log record
+    internal_medicine_monitors: Optional[str] = None   # "all" or a comma list of activations,router,grads,weights
+    internal_medicine_monitor_interval: int = 0       # sample the monitors every N steps (0 = off)
     metrics_output_path: Optional[str] = None
     resume_from_checkpoint: Optional[str] = None
     save_checkpoint_format: str = field(default="sharded", metadata={"help": "sharded | unified | hf"})

@@ -159,3 +159,45 @@ def test_peft_adapter_export_and_import_preserve_the_function(tmp_path):
     assert again.lora_config.r == 12                        # q, k, v pairs stacked
     with torch.no_grad():
         torch.testing.assert_close(again(ids, return_logits=True).logits, want, rtol=1e-4, atol=1e-5)
+
+
+def test_health_monitors_sample_and_truncate_on_resume(tmp_path):
+    import json
+
+    from paddleformers_b200 import AutoModelForCausalLM, Trainer, TrainingArguments
+    from paddleformers_b200.data.synthetic import SyntheticCausalLMDataset
+    from paddleformers_b200.models.configuration import named_config
+    from paddleformers_b200.trainer.health_monitor import HealthMonitorCallback
+
+    def run(steps, resume=None):
+        torch.manual_seed(0)
+        from paddleformers_b200.models.configuration import Qwen3MoeConfig
+
+        cfg = Qwen3MoeConfig(vocab_size=128, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=2,
+                             num_attention_heads=2, num_key_value_heads=2, head_dim=32, num_experts=4, num_experts_per_tok=2)
+        model = AutoModelForCausalLM.from_config(cfg)
+        args = TrainingArguments(output_dir=str(tmp_path), per_device_train_batch_size=2, max_steps=steps, learning_rate=1e-3,
+                                 save_steps=4, max_seq_len=32, lr_scheduler_type="constant",
+                                 internal_medicine_monitor_interval=2)
+        tr = Trainer(model=model, args=args, train_dataset=SyntheticCausalLMDataset(128, 32, 64, seed=0))
+        tr.train(resume_from_checkpoint=resume)
+        return tr
+
+    tr = run(6)
+    cb = [c for c in tr.callback_handler.callbacks if isinstance(c, HealthMonitorCallback)][0]
+    assert [r["global_step"] for r in cb.records] == [2, 4, 6]
+    rec = cb.records[0]
+    assert rec["act_rms/layer0"] > 0 and rec["act_absmax/layer1"] >= rec["act_rms/layer1"]
+    assert rec["grad_norm/all"] > 0 and rec["weight_norm/layer0"] > 0
+    assert 1.0 <= rec["router_max_share/layer0"] and 0.0 <= rec["router_entropy/layer0"] <= 1.0 + 1e-6
+    assert any(k.startswith("expert_weight_norm/layer0/") for k in rec)
+    path = tmp_path / "runs" / "internal_medicine.jsonl"
+    assert [json.loads(l)["global_step"] for l in path.read_text().splitlines()] == [2, 4, 6]
+    # resume from step 4: rows past the checkpoint are dropped, the first resumed step is not sampled
+    tr2 = run(8, resume=str(tmp_path / "checkpoint-4"))
+    steps = [json.loads(l)["global_step"] for l in path.read_text().splitlines()]
+    assert steps == [2, 4, 6, 8] and tr2.state.global_step == 8
+    # a fresh start moves the old file aside
+    run(2)
+    assert [json.loads(l)["global_step"] for l in path.read_text().splitlines()] == [2]
+    assert any(p.name.startswith("internal_medicine.jsonl.bak.") for p in path.parent.iterdir())
