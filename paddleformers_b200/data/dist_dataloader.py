@@ -1,6 +1,7 @@
 """Sharding of iterable datasets over data ranks and broadcast of batches inside model-parallel groups.
 
 ``IterableDatasetShard`` plays the role of paddleformers/trainer/trainer_utils.py's class of the same name;
+``StreamDistDataLoader`` (one reader for the whole job, batches scattered to the data ranks) that of :257;
 ``DistDataLoader`` the role of paddleformers/data/dist_dataloader.py:42 (only the first rank of each tensor /
 pipeline group reads data, the batch is broadcast to the others).
 """
@@ -83,3 +84,100 @@ class DistDataLoader:
                 dist.broadcast(t, src=self.src_global, group=self.group)
                 out[k] = t
             yield out
+
+
+class StreamDistDataLoader:
+    """Loader for a stream (an iterable dataset) that only ONE process reads: the first rank of ``stream_group`` pulls
+    ``group size`` batches per step from the stream and scatters one to every data rank; each data rank then shares its
+    batch with its tensor / pipeline / context-parallel peers through ``DistDataLoader``'s broadcast. Compared with
+    ``IterableDatasetShard`` no rank reads and throws away the other ranks' samples, and a source that cannot be opened
+    twice (a socket, a queue) works (paddleformers/data/dist_dataloader.py:257).
+
+    ``dataset`` may be None on every rank but the reader. A background thread keeps ``reader_buffer_size`` global batches
+    ready on the reader. An incomplete last global batch is dropped, so that all data ranks stop together."""
+
+    def __init__(self, dataset, batch_size: int = 1, collate_fn=None, stream_group=None, model_parallel_group=None,
+                 reader_buffer_size: int = 2, device: Optional[torch.device] = None):
+        self.dataset, self.batch_size, self.collate_fn = dataset, int(batch_size), collate_fn or (lambda x: x)
+        self.group, self.mp_group, self.device = stream_group, model_parallel_group, device
+        self.buffer = max(int(reader_buffer_size), 1)
+        on = dist.is_initialized()
+        self.n = dist.get_world_size(stream_group) if on else 1
+        self.rank = dist.get_rank(stream_group) if on else 0
+        self.in_stream_group = self.rank >= 0
+        self.src_global = dist.get_global_rank(stream_group, 0) if (on and stream_group is not None) else 0
+
+    def _global_batches(self):
+        """Reader side: lists of ``n`` collated batches."""
+        items, batches = [], []
+        for el in self.dataset:
+            items.append(el)
+            if len(items) == self.batch_size:
+                batches.append(self.collate_fn(items))
+                items = []
+                if len(batches) == self.n:
+                    yield batches
+                    batches = []
+
+    def _prefetched(self):
+        import queue
+        import threading
+
+        q: "queue.Queue" = queue.Queue(maxsize=self.buffer)
+        end = object()
+
+        def work():
+            try:
+                for gb in self._global_batches():
+                    q.put(gb)
+                q.put(end)
+            except BaseException as e:  # noqa: BLE001 - re-raised on the consumer side
+                q.put(e)
+
+        threading.Thread(target=work, daemon=True).start()
+        while True:
+            x = q.get()
+            if x is end:
+                return
+            if isinstance(x, BaseException):
+                raise x
+            yield x
+
+    def _scattered(self):
+        if self.n == 1:
+            for gb in self._prefetched():
+                yield gb[0]
+            return
+        src = self._prefetched() if self.rank == 0 else None
+        while True:
+            recv = [None]
+            send = None
+            if self.rank == 0:
+                gb = next(src, None)
+                send = list(gb) if gb is not None else ["stop"] * self.n
+            dist.scatter_object_list(recv, send, src=self.src_global, group=self.group)
+            if isinstance(recv[0], str) and recv[0] == "stop":
+                return
+            yield recv[0]
+
+    def __iter__(self):
+        class _Once:                        # DistDataLoader wants an iterable; only the data rank of each group has one
+            def __init__(s, gen):
+                s.gen = gen
+
+            def __iter__(s):
+                return s.gen
+
+        multi_mp = self.mp_group is not None and dist.is_initialized() and dist.get_world_size(self.mp_group) > 1
+        if not multi_mp:
+            for b in self._scattered():
+                yield self._to_device(b)
+            return
+        is_data_rank = dist.get_rank(self.mp_group) == 0
+        inner = DistDataLoader(_Once(self._scattered() if is_data_rank else iter(())), self.mp_group, 0, self.device)
+        yield from inner
+
+    def _to_device(self, b):
+        if self.device is None or not isinstance(b, dict):
+            return b
+        return {k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in b.items()}

@@ -167,3 +167,41 @@ def test_every_template_renders_a_multi_turn_conversation():
         assert text.index("Q1") < text.index("A1") < text.index("Q2") < text.index("A2"), name
         if name != "empty":
             assert "SYS" in pairs[0][0], name
+
+
+def _stream_worker(rank, world):
+    import torch
+    import torch.distributed as dist
+
+    from paddleformers_b200.data.dist_dataloader import StreamDistDataLoader
+
+    class Stream(torch.utils.data.IterableDataset):
+        reads = 0
+
+        def __iter__(self):
+            for i in range(11):            # 11 samples, batch 2, 2 ranks: two global batches, the rest is dropped
+                Stream.reads += 1
+                yield {"input_ids": torch.full((4,), i)}
+
+    def collate(items):
+        return {"input_ids": torch.stack([x["input_ids"] for x in items])}
+
+    ds = Stream() if rank == 0 else None
+    loader = StreamDistDataLoader(ds, batch_size=2, collate_fn=collate, stream_group=dist.group.WORLD)
+    got = [b["input_ids"][:, 0].tolist() for b in loader]
+    return got, (Stream.reads if rank == 0 else 0)
+
+
+def test_stream_loader_reads_on_one_rank_and_scatters():
+    from dist_utils import run_distributed
+
+    res = run_distributed(_stream_worker, 2)
+    assert res[0][0] == [[0, 1], [4, 5]] and res[1][0] == [[2, 3], [6, 7]]
+    assert res[0][1] >= 8 and res[1][1] == 0
+    # one process: plain batching of the stream
+    import torch
+
+    from paddleformers_b200.data.dist_dataloader import StreamDistDataLoader
+
+    out = list(StreamDistDataLoader(iter(range(5)) and list(range(5)), batch_size=2, collate_fn=lambda x: torch.tensor(x)))
+    assert [o.tolist() for o in out] == [[0, 1], [2, 3]]
