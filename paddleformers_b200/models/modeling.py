@@ -522,13 +522,45 @@ class DecoderForCausalLM(PretrainedModel):
             return self.lm_head(hidden2d)
         return F.linear(hidden2d, w)
 
-    def _loss(self, hidden2d, labels_flat, scale):
+    def _label_norm(self, count):
+        """Number of labelled tokens the loss is divided by. Ranks of a context / segment parallel group hold slices of ONE
+        sequence: they normalise by the labelled tokens of the whole sequence (their mean per rank), so that averaging the
+        ranks' losses and gradients gives the loss of the unsplit sequence even when labels are spread unevenly."""
+        norm = count.clamp(min=1).to(torch.float32)
+        ps = get_parallel_state()
+        for axis in ("cp", "sep"):
+            n_slices = getattr(ps.degrees, axis)
+            if n_slices > 1 and torch.distributed.is_initialized():
+                total = count.to(torch.float32)
+                torch.distributed.all_reduce(total, group=ps.group(axis))
+                norm = (total / n_slices).clamp(min=1.0)
+        return norm
+
+    def _filter_labelled_rows(self, hidden2d, labels_flat):
+        """use_filtered_label_loss: only the rows whose label is not ignored go through the head GEMM and the loss (a large
+        saving for SFT, where prompt tokens carry no label). Under sequence parallelism every rank filters its own token
+        slice and the survivors are all-gathered with their varying counts. The row count depends on the data, so this
+        reads it on the host (paddleformers/nn/criterion/sft_loss.py:138-157)."""
+        keep = labels_flat != self.ignore_index
+        if self.sp:
+            from ..parallel.tensor_parallel import AllGatherVarlenOp
+
+            g = get_parallel_state().group("mp")
+            per = hidden2d.shape[0]
+            r = torch.distributed.get_rank(g)
+            local = keep[r * per:(r + 1) * per]
+            rows = AllGatherVarlenOp.apply(hidden2d[local.nonzero(as_tuple=True)[0]], g)
+        else:
+            rows = hidden2d[keep.nonzero(as_tuple=True)[0]]
+        return rows, labels_flat[keep]
+
+    def _loss(self, hidden2d, labels_flat, scale, tokens_complete: bool = False):
         """(scaled loss sum, token count) of the head + cross entropy on hidden states [T, H]."""
         if self.tp > 1:
             from ..parallel.vocab_parallel_loss import vocab_parallel_linear_cross_entropy
 
             h = hidden2d
-            if self.sp:
+            if self.sp and not tokens_complete:
                 h = GatherOp.apply(h, get_parallel_state().group("mp"))
             return vocab_parallel_linear_cross_entropy(h, self.head_weight(), labels_flat, self.ignore_index, scale)
         chunk = int(getattr(self.config, "loss_subbatch_sequence_length", -1) or -1)
@@ -564,8 +596,13 @@ class DecoderForCausalLM(PretrainedModel):
         if labels is not None:
             lab = labels.reshape(-1)
             count = (lab != self.ignore_index).sum()
-            scale = 1.0 / (count.clamp(min=1).to(torch.float32) * float(self.loss_accumulation_steps))
-            loss, _ = self._loss(hidden, lab, scale)
+            norm = self._label_norm(count)
+            scale = 1.0 / (norm * float(self.loss_accumulation_steps))
+            if getattr(self.config, "use_filtered_label_loss", False):
+                rows, lab_kept = self._filter_labelled_rows(hidden, lab)
+                loss, _ = self._loss(rows, lab_kept, scale, tokens_complete=True)
+            else:
+                loss, _ = self._loss(hidden, lab, scale)
             out.num_tokens = count
             if len(self.mtp_layers) > 0:
                 out.mtp_losses = self._mtp_losses(hidden, input_ids, labels, ctx, scale)
@@ -594,7 +631,7 @@ class DecoderForCausalLM(PretrainedModel):
             h = layer(h, emb, ctx)
             flat = lab.reshape(-1)
             cnt = (flat != self.ignore_index).sum()
-            sc = 1.0 / (cnt.clamp(min=1).to(torch.float32) * float(self.loss_accumulation_steps))
+            sc = 1.0 / (self._label_norm(cnt) * float(self.loss_accumulation_steps))
             saved_sp, self.sp = self.sp, False  # h is already token-complete
             try:
                 l, _ = self._loss(h, flat, sc)

@@ -110,6 +110,40 @@ class GatherOp(torch.autograd.Function):
         return g[r * per:(r + 1) * per].contiguous(), None
 
 
+class AllGatherVarlenOp(torch.autograd.Function):
+    """All-gather of token rows when every rank holds a different number of them (the rows that survive a label filter):
+    the counts are exchanged first, rows are padded to the largest count for the collective and the padding is dropped.
+    Output rows are ordered by rank. Backward keeps this rank's rows, like ``GatherOp``
+    (paddleformers/transformers/sequence_parallel_utils.py:68-121)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        n = _group_size(group)
+        ctx.group = group
+        if n == 1:
+            ctx.span = None
+            return x
+        cnt = torch.tensor([x.shape[0]], dtype=torch.int64, device=x.device)
+        cnts = torch.empty(n, dtype=torch.int64, device=x.device)
+        dist.all_gather_into_tensor(cnts, cnt, group=group)
+        counts = cnts.tolist()
+        m = max(max(counts), 1)
+        pad = torch.zeros((m,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        pad[:x.shape[0]] = x
+        out = torch.empty((n * m,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, pad, group=group)
+        r = dist.get_rank(group)
+        ctx.span = (sum(counts[:r]), counts[r])
+        return torch.cat([out[i * m:i * m + c] for i, c in enumerate(counts)], dim=0)
+
+    @staticmethod
+    def backward(ctx, g):
+        if ctx.span is None:
+            return g, None
+        lo, c = ctx.span
+        return g[lo:lo + c].contiguous(), None
+
+
 class CopyToTP(torch.autograd.Function):
     """Identity forward, all-reduce backward (input of a column-parallel linear without SP)."""
 

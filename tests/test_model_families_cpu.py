@@ -76,7 +76,10 @@ def _grads(cfg_over, moe=False):
     model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32).train()
     g = torch.Generator().manual_seed(9)
     ids = torch.randint(0, 96, (2, 16), generator=g)
-    out = model(ids, labels=torch.roll(ids, -1, 1))
+    labels = torch.roll(ids, -1, 1)
+    labels[:, :5] = -100                 # prompt positions carry no label
+    labels[1, 9] = -100
+    out = model(ids, labels=labels)
     out.loss.backward()
     return out.loss.item(), {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}
 
@@ -87,6 +90,8 @@ def _grads(cfg_over, moe=False):
     dict(recompute_granularity="full", recompute_method="block", recompute_num_layers=1),
     dict(recompute_granularity="selective", recompute_modules=["attn"]),
     dict(recompute_granularity="selective", recompute_modules="core_attn,mlp"),
+    dict(use_filtered_label_loss=True),
+    dict(loss_subbatch_sequence_length=8),
 ])
 def test_recompute_variants_leave_loss_and_gradients_unchanged(over):
     loss0, g0 = _grads({})

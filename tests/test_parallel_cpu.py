@@ -22,7 +22,10 @@ def _tiny_cfg(moe=False, **kw):
 def _data(n, S=32, vocab=128):
     g = torch.Generator().manual_seed(11)
     ids = torch.randint(0, vocab, (n, S + 1), generator=g)
-    return [{"input_ids": ids[i, :-1], "labels": ids[i, 1:]} for i in range(n)]
+    labels = ids[:, 1:].clone()
+    labels[:, :3] = -100                  # prompt positions without a label
+    labels[::2, 17] = -100
+    return [{"input_ids": ids[i, :-1], "labels": labels[i]} for i in range(n)]
 
 
 class _DS(torch.utils.data.Dataset):
@@ -76,6 +79,8 @@ def _reference(moe, steps, accum):
 @pytest.mark.parametrize("name,world,moe,targs", [
     ("tp2_sp", 2, False, dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2)),
     ("tp2", 2, False, dict(tensor_model_parallel_size=2, gradient_accumulation_steps=2)),
+    ("tp2_sp_filtered_loss", 2, False, dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2,
+                                            use_filtered_label_loss=True)),
     ("sharding2", 2, False, dict(sharding="stage1", gradient_accumulation_steps=1)),
     ("sharding2_custom_adamw", 2, False, dict(sharding="stage1", gradient_accumulation_steps=1, optim="adamw_custom",
                                               tensorwise_offload_optimizer=True)),
