@@ -161,7 +161,57 @@ def run_tuner(argv: Optional[list] = None):
         return run_dpo(model_args, data_args, gen_args, train_args)
     if stage in ("AUTO-PARALLEL", "AUTO_PARALLEL"):
         return run_auto_parallel(model_args, data_args, gen_args, train_args)
-    raise ValueError(f"unknown stage {model_args.stage!r}; expected SFT | PT | DPO | auto-parallel")
+    if stage in RECIPES:
+        return run_recipe_pretrain(stage, model_args, data_args, gen_args, train_args)
+    raise ValueError(f"unknown stage {model_args.stage!r}; expected SFT | PT | DPO | VL-SFT | auto-parallel | "
+                     f"{' | '.join(sorted(RECIPES)).lower()}")
+
+
+# Pre-training recipes: what the reference ships as separate, hand-tuned workflows for one model family each
+# (paddleformers/cli/train/deepseek_v3_pretrain/workflow.py:340, paddleformers/cli/train/ernie_pretrain/workflow.py) is here the
+# ordinary pre-training workflow with that recipe's switches turned on; every switch the user set explicitly wins.
+RECIPES = {
+    # MLA + fp8 linears and experts + peer-memory expert exchange + aux-loss-free balancing + overlapped pipeline schedule
+    "DSV3_PRETRAIN": dict(fp8="e4m3", moe_token_dispatcher_type="fused", moe_aux_free_bias_update_rate=0.001,
+                          recompute_granularity="selective", recompute_modules=["attn"], _pp_schedule="zero_bubble",
+                          _model_types=("deepseek_v3", "deepseek_v2", "kimi_k2", "deepseek-v3-4l")),
+    # sequence-parallel linears with the all-gather / reduce-scatter fused into the GEMMs + fp8 experts
+    "ERNIE_PRETRAIN": dict(fp8="e4m3", moe_token_dispatcher_type="fused", _sequence_parallel=True,
+                           _model_types=("ernie4_5", "ernie4_5_moe")),
+}
+RECIPES["DEEPSEEK_V3_PRETRAIN"] = RECIPES["DSV3_PRETRAIN"]
+
+
+def apply_recipe(stage: str, model_args, train_args) -> dict:
+    """Turns on the recipe's switches that are still at their defaults; returns what was changed."""
+    import dataclasses
+
+    recipe = RECIPES[stage.upper()]
+    defaults = {f.name: (f.default if f.default is not dataclasses.MISSING else None) for f in dataclasses.fields(train_args)}
+    changed = {}
+
+    def put(name, value):
+        if name in defaults and getattr(train_args, name) == defaults[name] and value != defaults[name]:
+            setattr(train_args, name, value)
+            changed[name] = value
+
+    for k, v in recipe.items():
+        if not k.startswith("_"):
+            put(k, v)
+    if recipe.get("_pp_schedule") and train_args.pipeline_model_parallel_size > 1:
+        put("pipeline_schedule", recipe["_pp_schedule"])
+    if train_args.tensor_model_parallel_size > 1:
+        put("sequence_parallel", True)
+    mt = (model_args.model_type or "").lower()
+    if mt and not model_args.model_name_or_path and mt not in recipe["_model_types"]:
+        logger.warning(f"stage {stage}: model_type {mt!r} is not one of {recipe['_model_types']}; the recipe's switches still apply")
+    return changed
+
+
+def run_recipe_pretrain(stage, model_args, data_args, gen_args, train_args):
+    changed = apply_recipe(stage, model_args, train_args)
+    logger.info(f"stage {stage}: recipe switches {changed}")
+    return run_sft(model_args, data_args, gen_args, train_args, pretrain=True)
 
 
 def run_vl_sft(model_args, data_args, gen_args, train_args):

@@ -240,3 +240,49 @@ def test_fp8_flag_converts_dense_linears_in_the_workflow(tmp_path):
     out = model(ids, labels=torch.roll(ids, -1, 1))
     out.loss.backward()
     assert torch.isfinite(out.loss) and layer.self_attn.qkv_proj.weight.grad is not None
+
+
+def test_recipe_stages_turn_on_their_switches_and_train(tmp_path):
+    from paddleformers_b200.cli.cli import main
+    from paddleformers_b200.cli.hparams import parse_dict
+    from paddleformers_b200.cli.train import apply_recipe
+    from paddleformers_b200.data.indexed_dataset import MMapIndexedDatasetBuilder
+
+    base = {"model_type": "deepseek_v3", "from_scratch": True, "compute_type": "float32", "device": "cpu", "output_dir": str(tmp_path)}
+    margs, _, _, _, targs = parse_dict(dict(base, stage="dsv3_pretrain"))
+    changed = apply_recipe("dsv3_pretrain", margs, targs)
+    assert targs.fp8 == "e4m3" and targs.moe_token_dispatcher_type == "fused" and targs.moe_aux_free_bias_update_rate == 0.001
+    assert targs.recompute_granularity == "selective" and "pipeline_schedule" not in changed      # one pipeline stage
+    # what the user set explicitly stays
+    margs, _, _, _, targs = parse_dict(dict(base, stage="ernie_pretrain", moe_token_dispatcher_type="alltoall"))
+    apply_recipe("ernie_pretrain", margs, targs)
+    assert targs.moe_token_dispatcher_type == "alltoall" and targs.fp8 == "e4m3"
+
+    prefix = str(tmp_path / "corpus")
+    b = MMapIndexedDatasetBuilder(prefix, dtype=np.uint16)
+    rng = np.random.RandomState(0)
+    for _ in range(64):
+        b.add_document(rng.randint(2, 120, size=rng.randint(20, 60)))
+    b.finalize()
+    out = tmp_path / "out"
+    cfg = tmp_path / "dsv3.json"
+    cfg.write_text(json.dumps(dict(base, stage="dsv3_pretrain", output_dir=str(out), input_dir=prefix, split="9,1,0", max_seq_len=32,
+                                   max_steps=3, per_device_train_batch_size=2, learning_rate=1e-3, logging_steps=1, save_strategy="no",
+                                   config_overrides={"vocab_size": 128, "hidden_size": 128, "intermediate_size": 256,
+                                                     "moe_intermediate_size": 128, "num_hidden_layers": 2, "first_k_dense_replace": 1,
+                                                     "num_attention_heads": 2, "n_routed_experts": 4, "num_experts_per_tok": 2,
+                                                     "n_group": 1, "topk_group": 1, "q_lora_rank": 32, "kv_lora_rank": 32,
+                                                     "qk_nope_head_dim": 16, "qk_rope_head_dim": 16, "v_head_dim": 16,
+                                                     "num_nextn_predict_layers": 1})))
+    env = os.environ.get("CUDA_VISIBLE_DEVICES")
+    os.environ["CUDA_VISIBLE_DEVICES"] = ""
+    try:
+        assert main(["train", str(cfg)]) == 0
+    finally:
+        if env is None:
+            os.environ.pop("CUDA_VISIBLE_DEVICES", None)
+        else:
+            os.environ["CUDA_VISIBLE_DEVICES"] = env
+    assert os.path.exists(out / "model.safetensors")
+    saved = json.loads((out / "config.json").read_text())
+    assert saved["model_type"] == "deepseek_v3"
