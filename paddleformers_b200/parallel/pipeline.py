@@ -1,4 +1,5 @@
-"""Pipeline parallelism: stage partitioning, schedules (FThenB, 1F1B, interleaved 1F1B) and the execution engine.
+"""Pipeline parallelism: stage partitioning, schedules (FThenB, 1F1B, interleaved 1F1B, zero-bubble, and the V placement
+with split backward) and the execution engine.
 
 Roles of the reference's ``GeneralModelForCausalLMPipe`` (paddleformers/nn/pp_model.py:509-688: layer descriptions,
 ``seg_method``, empty layers, virtual stages, shared embeddings) and of Fleet's ``forward_backward_pipeline`` driven by
@@ -27,8 +28,31 @@ from .topology import ParallelState, get_parallel_state
 # ---------------------------------------------------------------------------------------------------------------
 # partitioning
 # ---------------------------------------------------------------------------------------------------------------
+V_SCHEDULES = ("zbv", "zb-v", "zb_v", "dualpipev", "dual_pipe_v")
+
+
+def is_v_schedule(name: Optional[str]) -> bool:
+    return str(name or "").lower() in V_SCHEDULES
+
+
+def virtual_stage(stage: int, chunk: int, P: int, v_shape: bool = False) -> int:
+    """Position of (stage, chunk) in the model's layer order. Interleaved placement walks the stages once per chunk
+    (chunk * P + stage); the V placement walks them down with chunk 0 and back up with chunk 1, so that the first and the
+    last part of the model share stage 0 and the turn at the last stage needs no communication."""
+    if v_shape:
+        return stage if chunk == 0 else 2 * P - 1 - stage
+    return chunk * P + stage
+
+
+def stage_of_virtual(vs: int, P: int, v_shape: bool = False) -> Tuple[int, int]:
+    """Inverse of ``virtual_stage``: (stage, chunk)."""
+    if v_shape:
+        return (vs, 0) if vs < P else (2 * P - 1 - vs, 1)
+    return vs % P, vs // P
+
+
 def partition_layers(num_layers: int, num_stages: int, num_virtual: int = 1, empty_head: int = 0, empty_tail: int = 0,
-                     weights: Optional[Sequence[float]] = None) -> List[List[range]]:
+                     weights: Optional[Sequence[float]] = None, v_shape: bool = False) -> List[List[range]]:
     """Split ``num_layers`` decoder layers over ``num_stages * num_virtual`` virtual stages.
 
     Returns ``parts[stage][chunk] = range of layer ids``. Empty layers count as layers of zero cost placed before the
@@ -63,7 +87,7 @@ def partition_layers(num_layers: int, num_stages: int, num_virtual: int = 1, emp
         pos += s
     parts: List[List[range]] = [[None] * num_virtual for _ in range(num_stages)]
     for v, (lo, hi) in enumerate(bounds):
-        stage, chunk = v % num_stages, v // num_stages
+        stage, chunk = stage_of_virtual(v, num_stages, v_shape)
         real_lo = min(max(lo - empty_head, 0), num_layers)
         real_hi = min(max(hi - empty_head, 0), num_layers)
         parts[stage][chunk] = range(real_lo, real_hi)
@@ -142,8 +166,101 @@ def schedule_zero_bubble(stage: int, P: int, M: int) -> List[Action]:
     return acts
 
 
+def schedule_zbv(stage: int, P: int, M: int) -> List[Action]:
+    """Schedule for the V placement (two chunks per stage, chunk 0 running down the stages and chunk 1 back up) with the
+    backward pass split into B and W: the family the reference reaches through ``use_dualpipev`` and its overlapped schedule
+    nodes (paddleformers/trainer/training_args.py:2073-2087, paddleformers/cli/train/deepseek_v3_pretrain/modeling_pp.py:
+    535-606). Built by list scheduling on unit costs: every stage runs, at each step, the first ready action in the priority
+    order B (which the neighbour waits for), then forward of chunk 1, forward of chunk 0, and W only when nothing else is
+    ready; forwards of chunk 0 are admitted while fewer than P + 1 micro-batch chunks are alive on the stage, which keeps every
+    stage at about 2P half-size chunks: the activation memory of 1F1B's first stage, but the same on all stages. (A larger
+    cap trades memory for a smaller bubble; ``_zbv_all`` takes it as a parameter.) The loss and the embedding sit on the same
+    stage, so the backward of a micro-batch can start right after its forward returns to stage 0."""
+    return _zbv_all(P, M)[stage]
+
+
+def ZBV_LIVE_CAP(P: int) -> int:
+    """Chunk-0 forwards are admitted while fewer than this many chunks are alive on a stage."""
+    return P + 1
+
+
+_ZBV_CACHE: Dict[Tuple[int, int, int], List[List[Action]]] = {}
+
+
+def _zbv_all(P: int, M: int, max_live: Optional[int] = None) -> List[List[Action]]:
+    cap = int(max_live) if max_live else ZBV_LIVE_CAP(P)
+    if (P, M, cap) in _ZBV_CACHE:
+        return _ZBV_CACHE[(P, M, cap)]
+    last = 2 * P - 1
+    done_f: Dict[Tuple[int, int], int] = {}       # (virtual stage, micro-batch) -> finish time
+    done_b: Dict[Tuple[int, int], int] = {}
+    out: List[List[Action]] = [[] for _ in range(P)]
+    nf = [[0, 0] for _ in range(P)]                # next micro-batch to run forward, per chunk
+    nb = [[0, 0] for _ in range(P)]
+    wq: List[List[Tuple[int, int]]] = [[] for _ in range(P)]
+    live = [0] * P
+    t, total, emitted = 0, P * M * 2 * 3, 0
+    while emitted < total:
+        step = []
+        for s in range(P):
+            choice = None
+            # B: chunk 1 first (it is earlier in the backward order)
+            for c in (1, 0):
+                m = nb[s][c]
+                if m >= M:
+                    continue
+                vs = virtual_stage(s, c, P, True)
+                ready = done_f.get((vs, m), 1 << 30) <= t and (vs == last or done_b.get((vs + 1, m), 1 << 30) <= t)
+                if ready:
+                    choice = ("B", c, m)
+                    break
+            if choice is None:
+                for c in (1, 0):
+                    m = nf[s][c]
+                    if m >= M:
+                        continue
+                    vs = virtual_stage(s, c, P, True)
+                    if vs > 0 and done_f.get((vs - 1, m), 1 << 30) > t:
+                        continue
+                    if c == 0 and live[s] >= cap:
+                        continue
+                    choice = ("F", c, m)
+                    break
+            if choice is None and wq[s]:
+                c, m = wq[s][0]
+                choice = ("W", c, m)
+            if choice is not None:
+                step.append((s, choice))
+        if not step and emitted < total:
+            t += 1
+            if t > 16 * (total + P):
+                raise RuntimeError("zbv schedule construction did not terminate")
+            continue
+        for s, (kind, c, m) in step:
+            vs = virtual_stage(s, c, P, True)
+            out[s].append(Action(kind, c, m))
+            emitted += 1
+            if kind == "F":
+                done_f[(vs, m)] = t + 1
+                nf[s][c] += 1
+                live[s] += 1
+            elif kind == "B":
+                done_b[(vs, m)] = t + 1
+                nb[s][c] += 1
+                wq[s].append((c, m))
+            else:
+                wq[s].pop(0)
+                live[s] -= 1
+        t += 1
+    _ZBV_CACHE[(P, M, cap)] = out
+    return out
+
+
 def make_schedule(name: str, stage: int, P: int, M: int, V: int = 1) -> List[Action]:
     name = name.lower()
+    if name in V_SCHEDULES:
+        assert V == 2, "the V placement has exactly two chunks per stage"
+        return schedule_zbv(stage, P, M)
     if name in ("fthenb", "f-then-b"):
         return schedule_fthenb(stage, P, M, V)
     if name in ("zb", "zbh1", "zero_bubble", "zero-bubble"):
@@ -154,7 +271,8 @@ def make_schedule(name: str, stage: int, P: int, M: int, V: int = 1) -> List[Act
     return schedule_1f1b(stage, P, M)
 
 
-def simulate(schedules: List[List[Action]], P: int, V: int, cost: Optional[Dict[str, float]] = None) -> Dict[str, object]:
+def simulate(schedules: List[List[Action]], P: int, V: int, cost: Optional[Dict[str, float]] = None,
+             v_shape: bool = False) -> Dict[str, object]:
     """Runs all stages' action lists as a timed simulation: every stage executes its list in order, an action starts
     when the stage is free and its dependencies have finished. ``cost`` maps action kinds to durations; by default a
     forward costs 1, a fused backward 2, and in schedules that split it B and W cost 1 each. Raises on deadlock;
@@ -175,7 +293,7 @@ def simulate(schedules: List[List[Action]], P: int, V: int, cost: Optional[Dict[
         for s in range(P):
             while pos[s] < len(schedules[s]):
                 a = schedules[s][pos[s]]
-                vs = a.chunk * P + s
+                vs = virtual_stage(s, a.chunk, P, v_shape)
                 if a.kind == "F":
                     deps = [] if vs == 0 else [fin_f.get((vs - 1, a.mb))]
                 elif a.kind == "B":
@@ -224,19 +342,29 @@ class PipelineStageModel(PretrainedModel):
         self.config = config
         self.ps = ps
         P, V = ps.degrees.pp, max(int(getattr(config, "virtual_pipeline_model_parallel_size", 1) or 1), 1)
+        # V placement (schedule "zbv"): two chunks per stage, the model runs down the stages and back up, so that stage 0
+        # holds both the embedding and the head
+        self.v_shape = is_v_schedule(getattr(config, "pipeline_schedule", None)) and P > 1
+        if self.v_shape:
+            V = 2
         self.P, self.V, self.stage = P, V, ps.coord["pp"]
         dtype = dtype if dtype is not None else _resolve_dtype(config.dtype)
         parts = partition_layers(config.num_hidden_layers, P, V, int(getattr(config, "num_empty_layers_add_in_head", 0) or 0),
-                                 int(getattr(config, "num_empty_layers_add_in_tail", 0) or 0))
+                                 int(getattr(config, "num_empty_layers_add_in_tail", 0) or 0), v_shape=self.v_shape)
         self.layer_ranges = parts[self.stage]
         self.chunks = nn.ModuleList()
+        last_stage = 0 if self.v_shape else P - 1
         for c, rng in enumerate(self.layer_ranges):
             first = self.stage == 0 and c == 0
-            last = self.stage == P - 1 and c == V - 1
-            self.chunks.append(DecoderModel(config, dtype=dtype, device=device, layer_range=rng, with_embedding=first or (last and config.tie_word_embeddings),
+            last = self.stage == last_stage and c == V - 1
+            # with the V placement a tied / MTP embedding on the last chunk is the first chunk's own parameter (set below)
+            self.chunks.append(DecoderModel(config, dtype=dtype, device=device, layer_range=rng,
+                                            with_embedding=first or (last and config.tie_word_embeddings and not self.v_shape),
                                             with_final_norm=last))
         self.is_first = self.stage == 0
-        self.is_last = self.stage == P - 1
+        self.is_last = self.stage == last_stage
+        if self.v_shape and self.is_last and (config.tie_word_embeddings or int(getattr(config, "num_nextn_predict_layers", 0) or 0)):
+            self.chunks[-1].embed_tokens = self.chunks[0].embed_tokens       # one parameter, two users: autograd sums the gradients
         self.lm_head = None
         self.mtp_layers = nn.ModuleList()
         if self.is_last:
@@ -244,14 +372,15 @@ class PipelineStageModel(PretrainedModel):
                 self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False, dtype=dtype, device=device)
             n_mtp = int(getattr(config, "num_nextn_predict_layers", 0) or 0)
             self.mtp_layers = nn.ModuleList([MTPLayer(config, config.num_hidden_layers + i, dtype=dtype, device=device) for i in range(n_mtp)])
-            if n_mtp and self.chunks[-1].embed_tokens is None:
+            if n_mtp and self.chunks[-1].embed_tokens is None and not self.v_shape:
                 # MTP needs token embeddings on the last stage: a tied copy of the input embedding
                 self.chunks[-1].embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size, dtype=dtype, device=device)
                 self.chunks[-1].embed_tokens.weight.pp_shared = "embed_tokens"
-        if self.is_first and self.chunks[0].embed_tokens is not None and (config.tie_word_embeddings or getattr(config, "num_nextn_predict_layers", 0)):
-            self.chunks[0].embed_tokens.weight.pp_shared = "embed_tokens"
-        if self.is_last and config.tie_word_embeddings and self.chunks[-1].embed_tokens is not None:
-            self.chunks[-1].embed_tokens.weight.pp_shared = "embed_tokens"
+        if not self.v_shape:
+            if self.is_first and self.chunks[0].embed_tokens is not None and (config.tie_word_embeddings or getattr(config, "num_nextn_predict_layers", 0)):
+                self.chunks[0].embed_tokens.weight.pp_shared = "embed_tokens"
+            if self.is_last and config.tie_word_embeddings and self.chunks[-1].embed_tokens is not None:
+                self.chunks[-1].embed_tokens.weight.pp_shared = "embed_tokens"
         self.loss_accumulation_steps = 1
         self.ignore_index = -100
         std = config.initializer_range
@@ -341,6 +470,11 @@ class PipelineEngine:
         self.stage = self.ps.coord["pp"]
         self.schedule_name = schedule
         ranks = self.ps.group_ranks["pp"]
+        self.ranks = ranks
+        self.v_shape = bool(getattr(model, "v_shape", False))
+        if is_v_schedule(schedule) != self.v_shape and self.P > 1:
+            raise ValueError(f"schedule {schedule!r} and the model's chunk placement disagree: build the model with the same "
+                             "pipeline_schedule in its configuration")
         self.prev_rank = ranks[(self.stage - 1) % self.P]
         self.next_rank = ranks[(self.stage + 1) % self.P]
         # two communicators: activations travel on one, gradients on the other
@@ -354,6 +488,10 @@ class PipelineEngine:
         buf = torch.empty(shape, dtype=dtype, device=device)
         dist.recv(buf, src=src, group=group)
         return buf
+
+    def _owner(self, vs: int) -> int:
+        """Stage that holds virtual stage ``vs``."""
+        return stage_of_virtual(vs, self.P, self.v_shape)[0]
 
     def forward_backward(self, micro_batches: List[Dict[str, torch.Tensor]]) -> torch.Tensor:
         model, P, V, s = self.model, self.P, self.V, self.stage
@@ -369,11 +507,13 @@ class PipelineEngine:
         total_loss = torch.zeros((), dtype=torch.float32, device=dev)
         last_virtual = P * V - 1
         split_w = any(a.kind == "W" for a in acts)
+        local_fwd: Dict[Tuple[int, int], torch.Tensor] = {}     # hand-over between two chunks of this stage (V placement)
+        local_bwd: Dict[Tuple[int, int], torch.Tensor] = {}
         for a in acts:
             if a.kind == "W":
                 F.WeightGradStore.run_group()      # the weight-gradient GEMMs queued by the matching B
                 continue
-            vs = a.chunk * P + s
+            vs = virtual_stage(s, a.chunk, P, self.v_shape)
             batch = micro_batches[a.mb]
             B, S = batch["input_ids"].shape
             if a.mb not in ctxs:
@@ -381,10 +521,16 @@ class PipelineEngine:
                 ctxs[a.mb] = model.chunks[0].make_context(batch["input_ids"], batch.get("position_ids"),
                                                           kend.reshape(B, -1) if kend is not None else None)
             ctx = ctxs[a.mb]
+            # neighbours in the model's layer order; with the V placement the turn at the last stage stays on this rank
+            src_stage = self._owner(vs - 1) if vs > 0 else None
+            dst_stage = self._owner(vs + 1) if vs < last_virtual else None
             if a.kind == "F":
                 x_in = None
                 if vs > 0:
-                    x_in = self._recv((B * S, H), dtype, dev, self.prev_rank, self.fwd_group)
+                    if src_stage == s:
+                        x_in = local_fwd.pop((vs - 1, a.mb))
+                    else:
+                        x_in = self._recv((B * S, H), dtype, dev, self.ranks[src_stage], self.fwd_group)
                     x_in.requires_grad_(True)
                 out = model.forward_chunk(a.chunk, x_in, batch, ctx)
                 if vs == last_virtual:
@@ -392,7 +538,10 @@ class PipelineEngine:
                     total_loss += loss.detach()
                     saved[(a.chunk, a.mb)] = (x_in, loss)
                 else:
-                    self._send(out.detach(), self.next_rank, self.fwd_group, pending)
+                    if dst_stage == s:
+                        local_fwd[(vs, a.mb)] = out.detach()
+                    else:
+                        self._send(out.detach(), self.ranks[dst_stage], self.fwd_group, pending)
                     saved[(a.chunk, a.mb)] = (x_in, out)
             else:
                 x_in, out = saved.pop((a.chunk, a.mb))
@@ -402,20 +551,26 @@ class PipelineEngine:
                     if vs == last_virtual:
                         out.backward()
                     else:
-                        g = self._recv(tuple(out.shape), out.dtype, dev, self.next_rank, self.bwd_group)
+                        if dst_stage == s:
+                            g = local_bwd.pop((vs + 1, a.mb))
+                        else:
+                            g = self._recv(tuple(out.shape), out.dtype, dev, self.ranks[dst_stage], self.bwd_group)
                         torch.autograd.backward(out, g)
                 finally:
                     if split_w:
                         F.WeightGradStore.end_group()
                 if vs > 0:
-                    self._send(x_in.grad, self.prev_rank, self.bwd_group, pending)
+                    if src_stage == s:
+                        local_bwd[(vs, a.mb)] = x_in.grad
+                    else:
+                        self._send(x_in.grad, self.ranks[src_stage], self.bwd_group, pending)
         F.WeightGradStore.run_all()
         for w in pending:
             w.wait()
         self._sync_shared_embeddings()
         # every stage reports the same loss: the last stage owns it
         if P > 1:
-            src = self.ps.group_ranks["pp"][P - 1]
+            src = self.ps.group_ranks["pp"][self._owner(last_virtual)]
             dist.broadcast(total_loss, src=src, group=self.ps.group("pp"))
         return total_loss
 
@@ -423,7 +578,7 @@ class PipelineEngine:
         """Sum the gradients of parameters that exist on both the first and the last stage (tied embeddings, MTP
         embedding copy)."""
         shared = [p for p in self.model.parameters() if getattr(p, "pp_shared", None)]
-        if not shared or self.P == 1:
+        if not shared or self.P == 1 or self.v_shape:
             return
         if not (self.model.is_first or self.model.is_last):
             return

@@ -71,7 +71,7 @@ class TrainingArguments:
                                                         "full fp32 accumulation buffer that the weight-gradient GEMMs write)"})
     sequence_parallel: bool = False
     hybrid_parallel_topo_order: str = "sharding_first"
-    pipeline_schedule: str = field(default="1F1B", metadata={"help": "1F1B | interleaved | FThenB | zero_bubble (backward split into input-gradient and deferred weight-gradient parts)"})
+    pipeline_schedule: str = field(default="1F1B", metadata={"help": "1F1B | interleaved | FThenB | zero_bubble (backward split into input-gradient and deferred weight-gradient parts) | zbv (zero_bubble on a V-shaped placement with two chunks per stage)"})
     sharding_comm_buffer_size_MB: int = 256
     sharding_overlap: bool = True
     # logging / saving / eval

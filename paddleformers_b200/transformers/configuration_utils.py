@@ -34,6 +34,7 @@ class LlmMetaConfig:
         ("tensor_parallel_output", bool, True, "keep lm_head logits vocabulary-sharded"),
         ("pipeline_model_parallel_size", int, 1, "pipeline parallel degree"),
         ("virtual_pipeline_model_parallel_size", int, 1, "interleaved pipeline chunks per stage"),
+        ("pipeline_schedule", str, "1F1B", "1F1B | interleaved | FThenB | zero_bubble | zbv (V-shaped placement, two chunks per stage)"),
         ("num_empty_layers_add_in_head", int, 0, "empty layers inserted before the first decoder layer"),
         ("num_empty_layers_add_in_tail", int, 0, "empty layers appended after the last decoder layer"),
         ("expert_model_parallel_size", int, 1, "expert parallel degree"),

@@ -151,6 +151,7 @@ def _train_single4(rank, world, moe, targs, steps, full_state):
     ("pp2_interleaved", dict(pipeline_model_parallel_size=2, virtual_pipeline_model_parallel_size=2, gradient_accumulation_steps=4,
                              pipeline_schedule="interleaved")),
     ("pp2_zero_bubble", dict(pipeline_model_parallel_size=2, gradient_accumulation_steps=4, pipeline_schedule="zero_bubble")),
+    ("pp2_zbv", dict(pipeline_model_parallel_size=2, gradient_accumulation_steps=4, pipeline_schedule="zbv")),
 ])
 def test_pipeline_matches_single_process(name, targs):
     from paddleformers_b200.models.modeling import MODEL_MAPPING
@@ -207,6 +208,29 @@ def test_zero_bubble_schedule_shortens_the_pipeline(P, M):
     assert zb["makespan"] == 3 * M + 2 * (P - 1)
     assert zb["peak_live"] == base["peak_live"] == list(range(P, 0, -1))
     assert zb["bubble_fraction"] < base["bubble_fraction"]
+
+
+@pytest.mark.parametrize("P,M", [(2, 4), (4, 8), (8, 16), (8, 32)])
+def test_v_placement_schedule_is_valid_and_nearly_bubble_free(P, M):
+    from paddleformers_b200.parallel.pipeline import (make_schedule, partition_layers, simulate, stage_of_virtual,
+                                                      virtual_stage)
+
+    # placement: down the stages with chunk 0, back up with chunk 1; first and last part of the model on stage 0
+    order = [stage_of_virtual(v, P, True) for v in range(2 * P)]
+    assert order[0] == (0, 0) and order[P - 1] == (P - 1, 0) and order[P] == (P - 1, 1) and order[-1] == (0, 1)
+    assert all(virtual_stage(s, c, P, True) == v for v, (s, c) in enumerate(order))
+    parts = partition_layers(4 * P, P, 2, v_shape=True)
+    assert parts[0][0] == range(0, 2) and parts[0][1] == range(4 * P - 2, 4 * P) and parts[P - 1][0].stop == parts[P - 1][1].start
+    sch = [make_schedule("zbv", s, P, M, 2) for s in range(P)]
+    for s in range(P):                       # every chunk of every micro-batch runs F, B and W exactly once
+        assert sorted((a.kind, a.chunk, a.mb) for a in sch[s]) == sorted((k, c, m) for k in "FBW" for c in (0, 1) for m in range(M))
+    unit = {"F": 1.0, "B": 1.0, "W": 1.0}    # one half-size chunk = one unit per pass
+    r = simulate(sch, P, 2, unit, v_shape=True)
+    one = simulate([make_schedule("1f1b", s, P, M, 1) for s in range(P)], P, 1, {"F": 2.0, "B": 4.0})
+    zb = simulate([make_schedule("zero_bubble", s, P, M, 1) for s in range(P)], P, 1, {"F": 2.0, "B": 2.0, "W": 2.0})
+    assert r["makespan"] < zb["makespan"] < one["makespan"]
+    assert r["bubble_fraction"] < 0.6 * one["bubble_fraction"]
+    assert max(r["peak_live"]) <= 2 * P + 1       # half-size chunks: about the activation memory of 1F1B's first stage
 
 
 def test_nccl_group_config_parsing_and_options():
