@@ -70,14 +70,14 @@ HOST_LIB = os.path.join(EXT_DIR, "pfb_host.so")
 
 
 def build_host_library() -> str:
-    """Compile the host-only C++ helpers (dataset index builders) into ``_ext/pfb_host.so`` with g++."""
+    """Compile the host-only C++ helpers (dataset index builders, block-scaled checkpoint converters) into ``_ext/pfb_host.so`` with g++."""
     import subprocess
 
     os.makedirs(EXT_DIR, exist_ok=True)
     srcs = sorted(os.path.join(HOST_SRC_DIR, f) for f in os.listdir(HOST_SRC_DIR) if f.endswith(".cpp"))
     newest = max(os.path.getmtime(f) for f in srcs)
     if not os.path.exists(HOST_LIB) or os.path.getmtime(HOST_LIB) < newest:
-        subprocess.run(["g++", "-O3", "-std=c++17", "-shared", "-fPIC", "-o", HOST_LIB] + srcs, check=True)
+        subprocess.run(["g++", "-O3", "-std=c++17", "-pthread", "-shared", "-fPIC", "-o", HOST_LIB] + srcs, check=True)
     return HOST_LIB
 
 

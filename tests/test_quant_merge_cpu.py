@@ -121,3 +121,44 @@ def test_qat_linears_hadamard_and_qlora():
     assert all(p.grad is not None for n, p in lora.named_parameters() if p.requires_grad)
     m2 = nn.Sequential(nn.Linear(8, 8), nn.Linear(8, 8))
     assert convert_to_qat(m2, "a8w4") == 2
+
+
+def test_native_block_scaled_converters_match_the_tensor_implementations():
+    """The compiled host converters against the tensor-op specification: bit-identical codes, scales and values."""
+    from paddleformers_b200.ops._build import build_host_library
+    from paddleformers_b200.quantization import checkpoint_dequant as cd
+
+    build_host_library()
+    cd._host = None
+    assert cd._host_lib() is not None
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(64, 256, generator=g) * torch.logspace(-6, 4, 64).unsqueeze(1)      # many magnitudes
+    x[3, :32] = 0.0
+    x[5, 7] = 6.0 * 2.0 ** 3                                                             # exactly on a scale boundary
+    # mxfp4
+    bn, sn = cd.quant_mxfp4(x, native=True)
+    bt, st = cd.quant_mxfp4(x, native=False)
+    assert torch.equal(sn, st) and torch.equal(bn, bt)
+    assert torch.equal(cd.dequant_mxfp4(bn, sn, torch.float32, native=True), cd.dequant_mxfp4(bn, sn, torch.float32, native=False))
+    # mxfp8
+    qn, s8n = cd.quant_mxfp8(x, native=True)
+    qt, s8t = cd.quant_mxfp8(x, native=False)
+    assert torch.equal(s8n, s8t) and torch.equal(qn.view(torch.uint8), qt.view(torch.uint8))
+    back = cd.dequant_mxfp8(qn, s8n, torch.float32, native=True)
+    assert torch.equal(back, cd.dequant_mxfp8(qn, s8n, torch.float32, native=False))
+    nz = x.abs() > 1e-3 * x.abs().amax(-1, keepdim=True)
+    assert ((back - x).abs()[nz] / x.abs()[nz]).max() < 0.07                              # e4m3: 3 mantissa bits
+    # every e4m3 byte decodes like torch's own conversion
+    allb = torch.arange(256, dtype=torch.uint8).repeat(1, 1)
+    sc = torch.full((1, 8), 127, dtype=torch.uint8)
+    mine = cd.dequant_mxfp8(allb, sc, torch.float32, native=True)
+    ref = allb.view(torch.float8_e4m3fn).float()
+    ok = ~ref.isnan()
+    assert torch.equal(mine[ok], ref[ok]) and mine[~ok].isnan().all()
+    # names of the reference's converters
+    v, s = cd.downcast_to_mxfp(x, "mxfp4")
+    assert torch.equal(cd.upcast_from_mxfp(v, s, "mxfp4", torch.float32), cd.dequant_mxfp4(bn, sn, torch.float32))
+    # fp8 128x128 block checkpoints
+    w = (torch.randn(200, 300, generator=g)).to(torch.float8_e4m3fn)
+    scale = torch.rand(2, 3, generator=g) + 0.5
+    assert torch.equal(cd.dequant_fp8_block(w, scale, 128, native=True), cd.dequant_fp8_block(w, scale, 128, native=False))
