@@ -32,6 +32,9 @@ class ModelArguments:
     lora_plus_scale: float = 1.0
     lora_target_modules: Optional[List[str]] = None
     lora_path: Optional[str] = None
+    loraga: bool = False                 # initialise the adapters from full-weight gradients (LoRA-GA)
+    loraga_init_iters: int = 8           # batches used for the gradient estimate
+    loraga_stable_gamma: float = 16.0    # -1: scale the factors by 1 / lora scaling instead
     use_attn_mask_startend_row_indices: bool = True
     use_global_causal_attn: bool = False
     config_overrides: Optional[Dict[str, Any]] = None

@@ -111,6 +111,16 @@ def run_sft(model_args, data_args, gen_args, train_args, pretrain: bool = False)
                                      use_global_causal_attn=model_args.use_global_causal_attn)
     trainer = SFTTrainer(model=model, args=train_args, data_collator=collator, train_dataset=train_ds, eval_dataset=eval_ds,
                          tokenizer=tokenizer)
+    if model_args.lora and getattr(model_args, "loraga", False) and not model_args.lora_path and not train_args.resume_from_checkpoint:
+        import itertools
+
+        from ..peft.lora_ga import lora_ga_init
+
+        ps = train_args.parallel_state
+        batches = (trainer._prepare_inputs(b) for b in itertools.islice(iter(trainer.get_train_dataloader()), model_args.loraga_init_iters))
+        lora_ga_init(model, batches, model_args.loraga_stable_gamma,
+                     dp_group=ps.group("data") if ps.size("data") > 1 else None)
+        logger.info(f"LoRA-GA: adapters initialised from {model_args.loraga_init_iters} batches of full-weight gradients")
     metrics = None
     if train_args.do_train:
         metrics = trainer.train(resume_from_checkpoint=train_args.resume_from_checkpoint)

@@ -242,8 +242,27 @@ class LoRAModel(nn.Module):
         from safetensors.torch import save_file
 
         os.makedirs(d, exist_ok=True)
-        self.lora_config.save_pretrained(d)
-        save_file({k: v.contiguous() for k, v in self.lora_state_dict().items()}, os.path.join(d, LORA_WEIGHTS_NAME))
+        sd = self.lora_state_dict()
+        cfg = self.lora_config
+        init = getattr(self, "loraga_init_dict", None)
+        if init:
+            # LoRA-GA shifted the frozen weights by -scaling * B0 A0 at initialisation. Saved adapters must apply to the
+            # ORIGINAL base weights, so the saved pair is the rank-2r factorisation of B A - B0 A0:
+            # [B | B0] @ [A ; -A0], with alpha doubled so that the scaling alpha / r stays what it was.
+            import copy
+
+            for name, t0 in init.items():
+                # names recorded on the wrapper carry its own attribute prefix
+                key = next((k for k in sd if name == k or name.endswith("." + k) or k.endswith("." + name)), None)
+                if key is None:
+                    continue
+                t0 = t0.detach().cpu().to(sd[key].dtype)
+                sd[key] = torch.cat([sd[key], -t0], dim=0) if name.endswith("lora_A") else torch.cat([sd[key], t0], dim=1)
+            cfg = copy.copy(cfg)
+            cfg.lora_alpha = cfg.lora_alpha * (math.sqrt(2.0) if cfg.rslora else 2.0)
+            cfg.r = cfg.r * 2
+        cfg.save_pretrained(d)
+        save_file({k: v.contiguous() for k, v in sd.items()}, os.path.join(d, LORA_WEIGHTS_NAME))
 
     @classmethod
     def from_pretrained(cls, model: nn.Module, d: str) -> "LoRAModel":

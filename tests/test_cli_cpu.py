@@ -100,7 +100,7 @@ def test_sft_lora_stage_then_export_merges_adapters(tmp_path):
     cfg_file = tmp_path / "sft.json"
     cfg_file.write_text(json.dumps({
         "stage": "SFT", "model_name_or_path": str(base_dir), "compute_type": "float32", "device": "cpu", "lora": True,
-        "lora_rank": 4, "train_dataset_path": str(data), "template": "default", "max_seq_len": 32, "max_steps": 3,
+        "lora_rank": 4, "loraga": True, "loraga_init_iters": 2, "train_dataset_path": str(data), "template": "default", "max_seq_len": 32, "max_steps": 3,
         "per_device_train_batch_size": 2, "learning_rate": 1e-3, "logging_steps": 1, "save_strategy": "no", "output_dir": str(out)}))
     env = os.environ.get("CUDA_VISIBLE_DEVICES")
     os.environ["CUDA_VISIBLE_DEVICES"] = ""

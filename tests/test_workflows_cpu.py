@@ -201,3 +201,88 @@ def test_health_monitors_sample_and_truncate_on_resume(tmp_path):
     run(2)
     assert [json.loads(l)["global_step"] for l in path.read_text().splitlines()] == [2]
     assert any(p.name.startswith("internal_medicine.jsonl.bak.") for p in path.parent.iterdir())
+
+
+def test_lora_ga_initialisation_keeps_the_function_and_follows_the_gradient():
+    from paddleformers_b200 import AutoModelForCausalLM
+    from paddleformers_b200.models.configuration import named_config
+    from paddleformers_b200.peft.lora import LoRAConfig, LoRALinear, LoRAModel
+    from paddleformers_b200.peft.lora_ga import estimate_gradients, lora_ga_reinit
+
+    torch.manual_seed(0)
+    cfg = named_config("tiny-llama", vocab_size=128, hidden_size=64, intermediate_size=128, num_attention_heads=2,
+                       num_key_value_heads=2, head_dim=32)
+    base = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32)
+    model = LoRAModel(base, LoRAConfig(r=4, lora_alpha=8))
+    g = torch.Generator().manual_seed(1)
+    batches = [dict(input_ids=(ids := torch.randint(0, 128, (2, 16), generator=g)), labels=torch.roll(ids, -1, 1)) for _ in range(3)]
+    model.eval()
+    before = model(input_ids=batches[0]["input_ids"], return_logits=True).logits.detach().clone()
+    loss_before = float(model(**batches[0]).loss)
+    grads = estimate_gradients(model, batches)
+    layers = {n: m for n, m in model.named_modules() if isinstance(m, LoRALinear)}
+    assert set(grads) == set(layers) and all(g.abs().sum() > 0 for g in grads.values())
+    assert not any(m.base.weight.requires_grad or m.disabled for m in layers.values())
+    lora_ga_reinit(model, grads, stable_gamma=16)
+    # the function is unchanged at step 0 although the adapters are no longer zero
+    after = model(input_ids=batches[0]["input_ids"], return_logits=True).logits
+    assert torch.allclose(before, after, rtol=1e-4, atol=1e-4)
+    name, layer = next(iter(layers.items()))
+    assert layer.lora_B.abs().sum() > 0
+    # B spans the top left singular directions of the gradient, A the next input-side directions
+    U, S, Vh = torch.linalg.svd(grads[name], full_matrices=False)
+    Bn = layer.lora_B / layer.lora_B.norm(dim=0, keepdim=True)
+    assert (U[:, :4].T @ Bn).abs().diagonal().min() > 0.9
+    An = layer.lora_A / layer.lora_A.norm(dim=1, keepdim=True)
+    assert (An @ Vh[4:8].T).abs().diagonal().min() > 0.9
+    # one SGD step on the adapters lowers the loss at least as fast as from the default initialisation
+    def one_step(m, lr=0.05):
+        m.train()
+        loss = m(**batches[0]).loss
+        loss.backward()
+        with torch.no_grad():
+            for p in m.parameters():
+                if p.requires_grad and p.grad is not None:
+                    p -= lr * p.grad
+        m.eval()
+        return float(m(**batches[0]).loss)
+
+    ga = one_step(model)
+    torch.manual_seed(0)
+    plain = LoRAModel(AutoModelForCausalLM.from_config(cfg, dtype=torch.float32), LoRAConfig(r=4, lora_alpha=8))
+    pl = one_step(plain)
+    assert ga < loss_before and ga < pl
+
+
+def test_lora_ga_adapters_saved_relative_to_the_original_weights(tmp_path):
+    from paddleformers_b200 import AutoModelForCausalLM
+    from paddleformers_b200.models.configuration import named_config
+    from paddleformers_b200.peft.lora import LoRAConfig, LoRAModel
+    from paddleformers_b200.peft.lora_ga import lora_ga_init
+
+    torch.manual_seed(0)
+    cfg = named_config("tiny-llama", vocab_size=128, hidden_size=64, intermediate_size=128, num_attention_heads=2,
+                       num_key_value_heads=2, head_dim=32)
+    base = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32)
+    base.save_pretrained(str(tmp_path / "base"))
+    model = LoRAModel(base, LoRAConfig(r=4, lora_alpha=8))
+    ids = torch.randint(0, 128, (2, 16))
+    batch = dict(input_ids=ids, labels=torch.roll(ids, -1, 1))
+    lora_ga_init(model, [batch])
+    model.train()
+    model(**batch).loss.backward()                       # one update so that B A differs from B0 A0
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.requires_grad and p.grad is not None:
+                p -= 0.05 * p.grad
+    model.eval()
+    want = model(input_ids=ids, return_logits=True).logits.detach()
+    model.save_pretrained(str(tmp_path / "adapter"))
+    saved = LoRAConfig.from_pretrained(str(tmp_path / "adapter"))
+    assert saved.r == 8 and saved.lora_alpha == 16 and saved.scaling == model.lora_config.scaling
+    fresh = LoRAModel.from_pretrained(AutoModelForCausalLM.from_pretrained(str(tmp_path / "base"), dtype=torch.float32),
+                                      str(tmp_path / "adapter")).eval()
+    got = fresh(input_ids=ids, return_logits=True).logits
+    assert torch.allclose(got, want, rtol=1e-4, atol=1e-4)
+    merged = fresh.merged_model()
+    assert torch.allclose(merged(input_ids=ids, return_logits=True).logits, want, rtol=1e-4, atol=1e-4)
