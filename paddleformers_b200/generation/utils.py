@@ -69,7 +69,11 @@ class KVCache:
         s = qf @ kf.transpose(-1, -2) * attn.scale
         i = torch.arange(Sk - S, Sk, device=q.device)[:, None]
         j = torch.arange(Sk, device=q.device)[None]
-        s = s.masked_fill(~(j <= i)[None, None], float("-inf"))
+        vis = j <= i
+        w = int(getattr(attn, "window", 0) or 0)
+        if w:
+            vis = vis & (i - j < w)           # sliding-window layer: only the last ``w`` keys
+        s = s.masked_fill(~vis[None, None], float("-inf"))
         o = torch.softmax(s, -1) @ vf
         return o.permute(0, 2, 1, 3).reshape(B * S, Hq * D).to(qkv2d.dtype)
 

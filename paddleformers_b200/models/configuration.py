@@ -91,6 +91,20 @@ class DecoderConfig(PretrainedConfig):
     def is_mla(self) -> bool:
         return self.kv_lora_rank is not None
 
+    def layer_window(self, layer_idx: int) -> int:
+        """Sliding-window width of a layer (0 = full causal attention): query i sees keys j with i - j < window. All layers
+        use ``sliding_window`` unless ``layer_types`` names the kind of each layer ("sliding_attention" / "full_attention")
+        or, Qwen2 style, ``use_sliding_window`` with ``max_window_layers`` (layers from that index on slide)."""
+        w = int(getattr(self, "sliding_window", 0) or 0)
+        if w <= 0:
+            return 0
+        types = getattr(self, "layer_types", None)
+        if types:
+            return w if types[layer_idx] == "sliding_attention" else 0
+        if getattr(self, "use_sliding_window", None) is not None:
+            return w if (self.use_sliding_window and layer_idx >= int(getattr(self, "max_window_layers", 0) or 0)) else 0
+        return w
+
     def is_moe_layer(self, layer_idx: int) -> bool:
         if self.num_experts <= 0:
             return False
@@ -194,8 +208,8 @@ class Glm4MoeConfig(DecoderConfig):
 
 
 class MistralConfig(DecoderConfig):
-    """Llama architecture; ``sliding_window`` (when set) must cover the training sequence length, because the attention
-    kernels implement causal and document masks, not a sliding window."""
+    """Llama architecture with optional sliding-window attention, which is expressed through the attention kernels' per-key
+    "first masked row" bound (key j is masked from row j + window on)."""
 
     model_type = "mistral"
 
@@ -321,6 +335,49 @@ class GemmaConfig(DecoderConfig):
         self.norm_weight_offset = 1.0
 
 
+class Gemma3TextConfig(GemmaConfig):
+    """Gemma 3 (text): Gemma's (w - 1) norms, GeGLU and scaled embeddings, plus per-head QK norm, four norms per block (the
+    branch output is normed before it joins the residual stream), a repeating pattern of sliding-window layers and global
+    layers that use different rotary bases, and a query scale of ``query_pre_attn_scalar ** -0.5``
+    (paddleformers/transformers/gemma3_text). Logit soft-capping is not provided (the released text models leave it off)."""
+
+    model_type = "gemma3_text"
+
+    def __init__(self, sliding_window=4096, layer_types=None, sliding_window_pattern=6, query_pre_attn_scalar=256,
+                 rope_local_base_freq=10000.0, rope_parameters=None, final_logit_softcapping=None, attn_logit_softcapping=None,
+                 **kw):
+        local_theta = float(rope_local_base_freq)
+        if rope_parameters and "full_attention" in rope_parameters:      # recent Hugging Face configs: one entry per layer kind
+            local_theta = float(rope_parameters.get("sliding_attention", {}).get("rope_theta", local_theta))
+            rope_parameters = dict(rope_parameters["full_attention"])
+        kw.setdefault("rope_theta", 1000000.0)
+        kw.setdefault("use_qk_norm", True)
+        kw.setdefault("max_position_embeddings", 131072)
+        super().__init__(rope_parameters=rope_parameters, **kw)
+        if final_logit_softcapping or attn_logit_softcapping:
+            raise NotImplementedError("logit soft-capping is not implemented")
+        self.sliding_window = sliding_window
+        n = self.num_hidden_layers
+        self.layer_types = list(layer_types) if layer_types else [
+            "full_attention" if (i + 1) % int(sliding_window_pattern) == 0 else "sliding_attention" for i in range(n)]
+        self.query_pre_attn_scalar = query_pre_attn_scalar
+        self.attention_multiplier = float(query_pre_attn_scalar) ** -0.5
+        self.rope_local_theta = local_theta
+        self.block_style = "sandwich"
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if saving:
+            full = {"rope_type": "default", "rope_theta": self.rope_theta}
+            if self.rope_scaling:
+                full = {**self.rope_scaling, "rope_theta": self.rope_theta}
+            d["rope_parameters"] = {"sliding_attention": {"rope_type": "default", "rope_theta": self.rope_local_theta},
+                                    "full_attention": full}
+            for k in ("rope_theta", "rope_scaling", "rope_local_theta", "attention_multiplier", "block_style"):
+                d.pop(k, None)
+        return d
+
+
 class CohereConfig(DecoderConfig):
     """Command-R: bias-free LayerNorm, attention and MLP in parallel on one normed input, interleaved rotary pairs in the
     checkpoint, logits multiplied by ``logit_scale`` (paddleformers/transformers/cohere)."""
@@ -335,6 +392,22 @@ class CohereConfig(DecoderConfig):
         self.norm_type, self.block_style = "layernorm_nobias", "parallel"
         self.rope_interleaved_checkpoint = True
         self.logits_scaling = 1.0 / float(logit_scale)
+
+
+class Cohere2Config(CohereConfig):
+    """Command-R7B / Command-A: Cohere blocks with a repeating pattern of sliding-window layers, which rotate q and k, and
+    global layers, which use no positional embedding at all (paddleformers/transformers/cohere2)."""
+
+    model_type = "cohere2"
+
+    def __init__(self, sliding_window=4096, layer_types=None, sliding_window_pattern=4, **kw):
+        kw.setdefault("use_qk_norm", False)
+        super().__init__(**kw)
+        self.sliding_window = sliding_window
+        n = self.num_hidden_layers
+        self.layer_types = list(layer_types) if layer_types else [
+            "full_attention" if (i + 1) % int(sliding_window_pattern) == 0 else "sliding_attention" for i in range(n)]
+        self.rope_on_window_layers_only = True
 
 
 class StableLmConfig(DecoderConfig):
@@ -402,7 +475,7 @@ class Ernie4_5MoeConfig(Ernie4_5Config):
 
 
 CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, MiniCPMConfig, Olmo2Config,
-                                            GemmaConfig, CohereConfig, StableLmConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
+                                            GemmaConfig, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
                                             Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config)}
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
@@ -415,9 +488,9 @@ UNSUPPORTED_FAMILIES = {
     "qwen3_next": "gated delta-net linear attention hybrid", "qwen3_5": "gated delta-net linear attention hybrid",
     "qwen3_5_moe": "gated delta-net linear attention hybrid",
     "hunyuan_v1_dense": "QK norm applied after the rotary embedding", "hunyuan_v1_moe": "QK norm after rotary, shared-expert mixing",
-    "gemma3": "(1 + w) RMSNorm, GeGLU, sliding/global layer pattern", "gemma3_text": "(1 + w) RMSNorm, GeGLU, sliding/global layer pattern",
+    "gemma3": "SigLIP vision tower (the text decoder is available as gemma3_text)",
     "phi4_multimodal": "vision and audio towers",
-    "cohere2": "LayerNorm, parallel block, sliding-window layers", "gemma2": "soft-capping, sliding / global layer pattern, post norms",
+    "gemma2": "soft-capping, sliding / global layer pattern, post norms",
     "internlm2": "interleaved fused wqkv layout", "minicpm3": "MLA with scaling factors",
     "llama4_text": "chunked attention, NoPE layers, shared-expert MoE", "diffllama": "differential attention",
 

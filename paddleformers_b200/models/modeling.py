@@ -30,7 +30,7 @@ from ..transformers.conversion_utils import Rule, WeightMap, expand_layers
 from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
                             Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig,
-                            GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, CohereConfig, StableLmConfig)
+                            GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig)
 
 
 @dataclass
@@ -46,6 +46,10 @@ class BatchContext:
     cp_positions: Optional[torch.Tensor] = None   # context parallel: global positions of the local tokens
     S_full: int = 0                               # context / segment parallel: length of the whole sequence
     kend_full: Optional[torch.Tensor] = None      # [B, S_full] document bounds of all keys (cp / sep)
+    kend_window: Optional[torch.Tensor] = None    # [B, S] bounds of sliding-window layers: min(kend, key index + window)
+    window: int = 0
+    cos_local: Optional[torch.Tensor] = None      # rotary tables of sliding-window layers when they use their own base
+    sin_local: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -180,17 +184,23 @@ class Attention(nn.Module):
             self.q_norm = RMSNorm(self.D, config.rms_norm_eps, dtype=dtype, device=device)
             self.k_norm = RMSNorm(self.D, config.rms_norm_eps, dtype=dtype, device=device)
         self.scale = float(getattr(config, "attention_multiplier", None) or 1.0 / math.sqrt(self.D))
+        self.window = config.layer_window(layer_idx)
+        self.local_rope = bool(self.window and getattr(config, "rope_local_theta", None))
+        # families whose global layers carry no positional embedding (Cohere2): only window layers rotate
+        self.use_rope = bool(self.window) or not getattr(config, "rope_on_window_layers_only", False)
 
     def forward(self, x2d: torch.Tensor, ctx: BatchContext, cache=None) -> torch.Tensor:
         qkv = _apply(self.qkv_proj, x2d)
+        kend = ctx.kend_window if (self.window and ctx.kend_window is not None) else ctx.kend
+        cos, sin = (ctx.cos_local, ctx.sin_local) if (self.local_rope and ctx.cos_local is not None) else (ctx.cos, ctx.sin)
         if self.qk_norm_full:
             nq, nk = self.Hq * self.D, self.Hkv * self.D
             qkv = torch.cat([self.q_norm(qkv[:, :nq].contiguous()), self.k_norm(qkv[:, nq:nq + nk].contiguous()), qkv[:, nq + nk:]], dim=-1)
         if self.use_qk_norm:
-            qkv = F.qk_norm_rope_packed(qkv, self.q_norm.weight, self.k_norm.weight, ctx.cos, ctx.sin, ctx.positions,
+            qkv = F.qk_norm_rope_packed(qkv, self.q_norm.weight, self.k_norm.weight, cos, sin, ctx.positions,
                                         self.Hq, self.Hkv, self.D, self.rot, self.config.rms_norm_eps)
-        else:
-            qkv = F.rope_packed(qkv, ctx.cos, ctx.sin, ctx.positions, self.Hq, self.Hkv, self.D, self.rot)
+        elif self.use_rope:
+            qkv = F.rope_packed(qkv, cos, sin, ctx.positions, self.Hq, self.Hkv, self.D, self.rot)
         if cache is not None:
             out = cache.attend(self, qkv, ctx)
         elif getattr(self.config, "_attn_implementation", None) in ("eager", "sdpa") and not ctx.S_full:
@@ -199,7 +209,7 @@ class Attention(nn.Module):
             B, S, D = ctx.B, ctx.S, self.D
             q, k, v = qkv.view(B, S, -1).split([self.Hq * D, self.Hkv * D, self.Hkv * D], dim=-1)
             out = AttentionInterface.get(self.config._attn_implementation)(
-                q.reshape(B, S, self.Hq, D), k.reshape(B, S, self.Hkv, D), v.reshape(B, S, self.Hkv, D), ctx.kend, self.scale)
+                q.reshape(B, S, self.Hq, D), k.reshape(B, S, self.Hkv, D), v.reshape(B, S, self.Hkv, D), kend, self.scale)
             out = out.reshape(B * S, self.Hq * D)
         elif ctx.S_full:
             B, S, D = ctx.B, ctx.S, self.D
@@ -208,7 +218,7 @@ class Attention(nn.Module):
                                           v.reshape(B, S, self.Hkv, D), ctx, self.scale, self.config)
             out = out.reshape(B * S, self.Hq * D)
         else:
-            out = F.flash_attention_qkvpacked(qkv, ctx.B, ctx.S, self.Hq, self.Hkv, self.D, True, ctx.kend, self.scale)
+            out = F.flash_attention_qkvpacked(qkv, ctx.B, ctx.S, self.Hq, self.Hkv, self.D, True, kend, self.scale)
         return _apply(self.o_proj, out)
 
 
@@ -282,8 +292,12 @@ class DecoderLayer(nn.Module):
         self.layer_idx = layer_idx
         # block_style: "pre" (norm -> branch -> add, the default), "post" (branch -> norm -> add: OLMo2) or "parallel"
         # (attention and MLP read the same normed input and are added together: Cohere)
+        # or "sandwich" (norm -> branch -> norm -> add, four norms per block: Gemma 3)
         self.block_style = getattr(config, "block_style", "pre") or "pre"
-        if self.block_style != "parallel":
+        if self.block_style == "sandwich":
+            for nm in ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm"):
+                setattr(self, nm, make_norm(config, config.hidden_size, sp, dtype=dtype, device=device))
+        elif self.block_style != "parallel":
             self.input_layernorm = make_norm(config, config.hidden_size, sp, dtype=dtype, device=device) \
                 if self.block_style == "pre" else None
             self.post_attention_layernorm = make_norm(config, config.hidden_size, sp, dtype=dtype, device=device)
@@ -312,6 +326,9 @@ class DecoderLayer(nn.Module):
         next RMSNorm kernel."""
         if self.block_style != "pre":
             x = hidden if residual is None else hidden + residual
+            if self.block_style == "sandwich":
+                x = x + self.post_attention_layernorm(self.self_attn(self.input_layernorm(x), ctx, cache))
+                return x + self.post_feedforward_layernorm(self.mlp(self.pre_feedforward_layernorm(x))), None
             if self.block_style == "post":
                 x = x + self.post_attention_layernorm(self.self_attn(x, ctx, cache))
                 return x + self.post_feedforward_layernorm(self.mlp(x)), None
@@ -374,25 +391,38 @@ class DecoderModel(nn.Module):
         self._rope_cache = {}
 
     # ------------------------------------------------------------------ helpers
-    def rope(self, device, length: int):
+    def rope(self, device, length: int, local: bool = False):
+        """(cos, sin) tables; ``local``: the tables of sliding-window layers with their own base and no scaling rule."""
         cfg = self.config
         rot = int((cfg.qk_rope_head_dim if cfg.is_mla else cfg.head_dim * cfg.partial_rotary_factor))
         n = max(length, 1)
-        key = (str(device), rot)
+        key = (str(device), rot, local)
         cached = self._rope_cache.get(key)
         if cached is None or cached[0].shape[0] < n:
             n = max(n, min(cfg.max_position_embeddings, 8192))
-            cached = F.rope_tables(n, rot, cfg.rope_theta, device, cfg.rope_scaling)
+            if local:
+                cached = F.rope_tables(n, rot, float(cfg.rope_local_theta), device, None)
+            else:
+                cached = F.rope_tables(n, rot, cfg.rope_theta, device, cfg.rope_scaling)
             self._rope_cache[key] = cached
         return cached
 
     def make_context(self, input_ids, position_ids=None, kend=None, cp_positions=None, full_seq_len=None,
                      kend_full=None) -> BatchContext:
         B, S = input_ids.shape
-        window = getattr(self.config, "sliding_window", None)
-        if window and (full_seq_len or S) > int(window):
-            raise NotImplementedError(f"sequence length {full_seq_len or S} exceeds sliding_window={window}: the attention "
-                                      "kernels implement causal and document masks, not a sliding window")
+        window = int(getattr(self.config, "sliding_window", None) or 0)
+        if not any(self.config.layer_window(i) for i in self.layer_range):
+            window = 0
+        kend_window = None
+        if window and (full_seq_len or S) > window:
+            if full_seq_len and full_seq_len != S:
+                raise NotImplementedError("sliding-window attention is not combined with context / segment parallelism")
+            # key j stops being visible at row j + window; together with the causal rule this is the sliding window, and it
+            # composes with document bounds by taking the smaller of the two
+            kend_window = (torch.arange(S, device=input_ids.device, dtype=torch.int32) + window).clamp(max=S)[None].expand(B, S)
+            if kend is not None:
+                kend_window = torch.minimum(kend_window, kend.to(torch.int32).reshape(B, S))
+            kend_window = kend_window.contiguous()
         max_pos = S if position_ids is None else max(S, int(self.config.max_position_embeddings))
         cos, sin = self.rope(input_ids.device, max_pos)
         pos = None
@@ -408,7 +438,11 @@ class DecoderModel(nn.Module):
             S_full = int(full_seq_len or S * ps.degrees.sep)
         if S_full:
             cos, sin = self.rope(input_ids.device, max(max_pos, S_full))
-        return BatchContext(B, S, pos, kend, cos, sin, cp_positions if S_full else None, S_full, kend_full if S_full else None)
+        cos_l = sin_l = None
+        if getattr(self.config, "rope_local_theta", None):
+            cos_l, sin_l = self.rope(input_ids.device, max(max_pos, S_full), local=True)
+        return BatchContext(B, S, pos, kend, cos, sin, cp_positions if S_full else None, S_full, kend_full if S_full else None,
+                            kend_window, window, cos_l, sin_l)
 
     def embed(self, input_ids):
         mult = float(getattr(self.config, "embedding_multiplier", 1.0) or 1.0)
@@ -705,7 +739,12 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
     off = float(getattr(config, "norm_weight_offset", 0.0) or 0.0)
     if off:                                         # checkpoints that store (w - offset) for every RMSNorm weight
         rules.append(Rule("model.norm.weight", ["model.norm.weight"], offset=off))
-        for nm in ("input_layernorm.weight", "post_attention_layernorm.weight"):
+        norm_names = ["input_layernorm.weight", "post_attention_layernorm.weight"]
+        if getattr(config, "block_style", "pre") == "sandwich":
+            norm_names += ["pre_feedforward_layernorm.weight", "post_feedforward_layernorm.weight"]
+        if config.use_qk_norm and not config.is_mla:
+            norm_names += ["self_attn.q_norm.weight", "self_attn.k_norm.weight"]
+        for nm in norm_names:
             per_layer.append(Rule(L + nm, [L + nm], offset=off))
     dense_rules = [dense_rule]
     if config.mlp_bias and not getattr(config, "hf_fused_gate_up", False):
@@ -794,12 +833,14 @@ GraniteForCausalLM = _family("GraniteForCausalLM", GraniteConfig)
 MiniCPMForCausalLM = _family("MiniCPMForCausalLM", MiniCPMConfig)
 Olmo2ForCausalLM = _family("Olmo2ForCausalLM", Olmo2Config)
 GemmaForCausalLM = _family("GemmaForCausalLM", GemmaConfig)
+Gemma3ForCausalLM = _family("Gemma3ForCausalLM", Gemma3TextConfig)
 CohereForCausalLM = _family("CohereForCausalLM", CohereConfig)
+Cohere2ForCausalLM = _family("Cohere2ForCausalLM", Cohere2Config)
 StableLmForCausalLM = _family("StableLmForCausalLM", StableLmConfig)
 
 MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
-    "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "cohere": CohereForCausalLM,
+    "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
     "stablelm": StableLmForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,

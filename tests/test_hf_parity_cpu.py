@@ -20,7 +20,10 @@ CASES = {
     "llama_linear_scaling": ("LlamaConfig", "LlamaForCausalLM", dict(rope_scaling={"rope_type": "linear", "factor": 4.0})),
     "llama_biases_tied": ("LlamaConfig", "LlamaForCausalLM", dict(attention_bias=True, mlp_bias=True, tie_word_embeddings=True, head_dim=32)),
     "mistral": ("MistralConfig", "MistralForCausalLM", dict(sliding_window=None)),
+    "mistral_sliding_window": ("MistralConfig", "MistralForCausalLM", dict(sliding_window=8)),
     "qwen2": ("Qwen2Config", "Qwen2ForCausalLM", dict()),
+    "qwen2_sliding_upper_layers": ("Qwen2Config", "Qwen2ForCausalLM", dict(num_hidden_layers=3, use_sliding_window=True, sliding_window=6,
+                                                                          max_window_layers=1)),
     "qwen3": ("Qwen3Config", "Qwen3ForCausalLM", dict(head_dim=16)),
     "phi3": ("Phi3Config", "Phi3ForCausalLM", dict(pad_token_id=0)),
     "seed_oss": ("SeedOssConfig", "SeedOssForCausalLM", dict(head_dim=16)),
@@ -59,7 +62,13 @@ CASES = {
                       "original_max_position_embeddings": 32})),
     "olmo2": ("Olmo2Config", "Olmo2ForCausalLM", dict()),
     "gemma": ("GemmaConfig", "GemmaForCausalLM", dict(head_dim=16, tie_word_embeddings=True, hidden_activation="gelu_pytorch_tanh")),
+    "gemma3_text": ("Gemma3TextConfig", "Gemma3ForCausalLM", dict(head_dim=16, num_hidden_layers=4, sliding_window=8, query_pre_attn_scalar=24,
+                                                                  layer_types=["sliding_attention", "sliding_attention", "full_attention",
+                                                                               "sliding_attention"], tie_word_embeddings=True)),
     "cohere": ("CohereConfig", "CohereForCausalLM", dict(tie_word_embeddings=True, logit_scale=0.25, use_qk_norm=False)),
+    "cohere2": ("Cohere2Config", "Cohere2ForCausalLM", dict(tie_word_embeddings=True, logit_scale=0.25, num_hidden_layers=4, sliding_window=8,
+                                                          layer_types=["sliding_attention", "full_attention", "sliding_attention",
+                                                                       "full_attention"])),
     "stablelm": ("StableLmConfig", "StableLmForCausalLM", dict(use_qkv_bias=True, partial_rotary_factor=0.25)),
     "glm4_moe": ("Glm4MoeConfig", "Glm4MoeForCausalLM", dict(head_dim=16, moe_intermediate_size=32, n_routed_experts=4, num_experts_per_tok=2,
                                                              n_group=1, topk_group=1, n_shared_experts=1, first_k_dense_replace=1,
@@ -92,7 +101,7 @@ def test_logits_match_hugging_face_implementation(tmp_path, family):
     torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "cohere", "olmo2",
+@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma3_text", "cohere", "cohere2", "olmo2",
                                     "stablelm", "granite", "qwen2_moe", "ernie4_5_moe"])
 def test_hugging_face_loads_what_this_framework_saves(tmp_path, family):
     """The other direction: a checkpoint written by ``save_pretrained`` here (per-expert tensors, interleaved rotary rows

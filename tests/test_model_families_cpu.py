@@ -48,11 +48,40 @@ def test_family_checkpoint_roundtrip(tmp_path, model_type, extra, expect, absent
     torch.testing.assert_close(a, b, rtol=0, atol=0)
 
 
-def test_mistral_sliding_window_shorter_than_sequence_is_refused():
+def test_sliding_window_is_expressed_through_the_mask_bounds():
+    """Window layers see the last ``window`` keys only; the window composes with packed-document bounds; cached decoding
+    applies the same rule; context parallelism with a window is refused."""
+    from paddleformers_b200.generation.utils import GenerationConfig, generate
+
     cfg = AutoConfig.for_model("mistral", **{**TINY, "sliding_window": 8})
-    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32)
-    with pytest.raises(NotImplementedError, match="sliding_window"):
-        model(torch.randint(0, 96, (1, 16)), return_logits=True)
+    torch.manual_seed(0)
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32).eval()
+    ids = torch.randint(0, 96, (2, 20))
+    ctx = model.model.make_context(ids)
+    assert ctx.kend_window.tolist()[0] == [min(j + 8, 20) for j in range(20)]
+    kend = torch.full((2, 20), 20, dtype=torch.int32)
+    kend[:, :5] = 5                                                      # a first document of 5 tokens
+    assert model.model.make_context(ids, kend=kend).kend_window.tolist()[0][:6] == [5, 5, 5, 5, 5, 13]
+    # a change more than ``window`` tokens back cannot reach a later position through ONE layer, and a sequence no longer than
+    # the window is plain causal attention
+    assert model.model.make_context(ids[:, :8]).kend_window is None
+    with torch.no_grad():
+        full = model(ids, return_logits=True).logits
+        # greedy decoding with the cache agrees with a full forward under the same window rule
+        out = generate(model, ids[:, :12], GenerationConfig(max_new_tokens=5))
+        again = model(out[:, :-1], return_logits=True).logits
+    assert torch.equal(again[:, 11:].argmax(-1), out[:, 12:])
+    wide = AutoConfig.for_model("mistral", **{**TINY, "sliding_window": 64})
+    torch.manual_seed(0)
+    ref = AutoModelForCausalLM.from_config(wide, dtype=torch.float32).eval()
+    with torch.no_grad():
+        assert not torch.allclose(ref(ids, return_logits=True).logits[:, -1], full[:, -1], atol=1e-5)   # the window matters
+        torch.testing.assert_close(ref(ids[:, :8], return_logits=True).logits, model(ids[:, :8], return_logits=True).logits)
+    assert [cfg.layer_window(i) for i in range(2)] == [8, 8]
+    q2 = AutoConfig.for_model("qwen2", **{**TINY, "sliding_window": 8, "use_sliding_window": True, "max_window_layers": 1})
+    assert [q2.layer_window(i) for i in range(2)] == [0, 8]
+    q3 = AutoConfig.for_model("qwen2", **{**TINY, "sliding_window": 8, "use_sliding_window": False})
+    assert [q3.layer_window(i) for i in range(2)] == [0, 0]
 
 
 def test_registry_names_known_but_unimplemented_families():
