@@ -256,6 +256,116 @@ class InternLM3Config(DecoderConfig):
         self.attention_out_bias = bool(bias)
 
 
+class HunYuanDenseV1Config(DecoderConfig):
+    """Hunyuan dense: Llama blocks whose per-head QK RMSNorm runs AFTER the rotary embedding, and whose "dynamic" rotary rule
+    with ``alpha`` is a plain change of base, theta * alpha ** (d / (d - 2)) (paddleformers/transformers/hunyuan)."""
+
+    model_type = "hunyuan_v1_dense"
+
+    def __init__(self, rope_parameters=None, **kw):
+        kw.setdefault("rms_norm_eps", 1e-5)
+        kw["use_qk_norm"] = True
+        rp = dict(rope_parameters or {})
+        alpha = rp.get("alpha") if rp.get("rope_type") == "dynamic" else None
+        if alpha:
+            rope_parameters = {"rope_type": "default", "rope_theta": rp.get("rope_theta", kw.get("rope_theta", 10000.0))}
+        super().__init__(rope_parameters=rope_parameters, **kw)
+        self.rope_alpha = float(alpha) if alpha else None
+        if alpha:
+            self.rope_base_theta = float(self.rope_theta)
+            self.rope_theta = self.rope_base_theta * float(alpha) ** (self.head_dim / (self.head_dim - 2))
+        self.qk_norm_after_rope = True
+        self.qk_norm_hf_names = ("query_layernorm", "key_layernorm")
+        self.attention_out_bias = bool(self.attention_bias)
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if saving:
+            if self.rope_alpha:
+                d["rope_parameters"] = {"rope_type": "dynamic", "alpha": self.rope_alpha, "factor": 1.0, "rope_theta": self.rope_base_theta}
+                d.pop("rope_theta", None)
+            for k in ("rope_alpha", "rope_base_theta", "qk_norm_after_rope", "qk_norm_hf_names"):
+                d.pop(k, None)
+        return d
+
+
+class HunYuanMoEV1Config(HunYuanDenseV1Config):
+    """Hunyuan MoE: every layer routes with softmax top-k (renormalised) over experts of the dense width and adds one shared
+    expert of the same width (paddleformers/transformers/hunyuan)."""
+
+    model_type = "hunyuan_v1_moe"
+
+    def __init__(self, moe_topk=1, num_experts=1, **kw):
+        if not isinstance(num_experts, int) or not isinstance(moe_topk, int):
+            raise NotImplementedError("per-layer expert counts / top-k lists are not implemented")
+        kw.setdefault("num_experts_per_tok", moe_topk)
+        kw.setdefault("norm_topk_prob", True)
+        kw.setdefault("scoring_func", "softmax")
+        kw.setdefault("n_shared_experts", 1)
+        super().__init__(num_experts=num_experts, **kw)
+        self.moe_topk = self.num_experts_per_tok
+        self.moe_intermediate_size = self.moe_intermediate_size or self.intermediate_size
+        self.shared_expert_intermediate_size = self.shared_expert_intermediate_size or self.intermediate_size
+        self.shared_expert_hf_name = "shared_mlp"
+        self.router_weight_hf_name = "gate.wg.weight"
+
+
+class MixtralConfig(DecoderConfig):
+    """Mixtral: Mistral attention (optional sliding window), every layer a softmax top-k router with renormalised weights over
+    experts of the dense width; checkpoints name the block ``block_sparse_moe`` and the projections w1 / w3 / w2."""
+
+    model_type = "mixtral"
+
+    def __init__(self, sliding_window=None, **kw):
+        kw.setdefault("norm_topk_prob", True)
+        kw.setdefault("num_experts_per_tok", 2)
+        kw.setdefault("router_aux_loss_coef", 0.001)
+        kw.setdefault("rms_norm_eps", 1e-5)
+        super().__init__(**kw)
+        self.sliding_window = sliding_window
+        self.moe_intermediate_size = self.moe_intermediate_size or self.intermediate_size
+        self.moe_block_hf_name = "block_sparse_moe"
+        self.expert_proj_hf_names = ("w1", "w3", "w2")
+        self.num_local_experts = self.num_experts
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if saving:
+            d["num_local_experts"] = self.num_experts
+            d.pop("num_experts", None)
+        return d
+
+
+class MiniMaxM2Config(DecoderConfig):
+    """MiniMax-M2: one RMSNorm over all heads' query / key features before the rotary embedding, every layer a sigmoid
+    router with a selection-only correction bias and renormalised top-k weights, experts of the dense width, no shared
+    expert (paddleformers/transformers/minimax_m2)."""
+
+    model_type = "minimax_m2"
+
+    def __init__(self, **kw):
+        kw.setdefault("scoring_func", "sigmoid")
+        kw.setdefault("topk_method", "noaux_tc")
+        kw.setdefault("norm_topk_prob", True)
+        kw.setdefault("router_aux_loss_coef", 0.001)
+        kw.setdefault("rope_theta", 5000000.0)
+        super().__init__(**kw)
+        self.qk_norm_full = True
+        self.moe_intermediate_size = self.moe_intermediate_size or self.intermediate_size
+        self.moe_block_hf_name = "block_sparse_moe"            # checkpoints use Mixtral's names: w1 = gate, w3 = up, w2 = down
+        self.expert_proj_hf_names = ("w1", "w3", "w2")
+        self.router_bias_name = "block_sparse_moe.e_score_correction_bias"
+        self.router_bias_leading_dim = False
+        self.num_local_experts = self.num_experts
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if saving:
+            d["num_local_experts"] = self.num_experts
+            d.pop("num_experts", None)
+        return d
+
+
 class Qwen2MoeConfig(DecoderConfig):
     """Qwen2-MoE / Qwen1.5-MoE: softmax router without renormalisation, one wide shared expert whose output is gated per
     token by a sigmoid (paddleformers/transformers/qwen2_moe)."""
@@ -476,7 +586,8 @@ class Ernie4_5MoeConfig(Ernie4_5Config):
 
 CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, MiniCPMConfig, Olmo2Config,
                                             GemmaConfig, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
-                                            Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config)}
+                                            Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config, HunYuanDenseV1Config,
+                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig)}
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
 # feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
@@ -484,10 +595,9 @@ UNSUPPORTED_FAMILIES = {
     "gpt_oss": "attention sinks, clamped SwiGLU with expert biases, mxfp4 expert checkpoints (dequantiser: quantization.checkpoint_dequant)",
     "deepseek_v32": "sparse (indexer) attention", "deepseek_v4": "compressed sparse attention",
     "glm_moe_dsa": "sparse (indexer) attention",
-    "minimax": "lightning (linear) attention hybrid", "minimax_m2": "per-layer QK norm over the full projection",
+    "minimax": "lightning (linear) attention hybrid",
     "qwen3_next": "gated delta-net linear attention hybrid", "qwen3_5": "gated delta-net linear attention hybrid",
     "qwen3_5_moe": "gated delta-net linear attention hybrid",
-    "hunyuan_v1_dense": "QK norm applied after the rotary embedding", "hunyuan_v1_moe": "QK norm after rotary, shared-expert mixing",
     "gemma3": "SigLIP vision tower (the text decoder is available as gemma3_text)",
     "phi4_multimodal": "vision and audio towers",
     "gemma2": "soft-capping, sliding / global layer pattern, post norms",

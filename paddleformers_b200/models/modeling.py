@@ -30,7 +30,8 @@ from ..transformers.conversion_utils import Rule, WeightMap, expand_layers
 from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
                             Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig,
-                            GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig)
+                            GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig,
+                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig)
 
 
 @dataclass
@@ -183,6 +184,7 @@ class Attention(nn.Module):
         elif self.use_qk_norm:
             self.q_norm = RMSNorm(self.D, config.rms_norm_eps, dtype=dtype, device=device)
             self.k_norm = RMSNorm(self.D, config.rms_norm_eps, dtype=dtype, device=device)
+        self.qk_norm_after_rope = bool(self.use_qk_norm and getattr(config, "qk_norm_after_rope", False))   # Hunyuan
         self.scale = float(getattr(config, "attention_multiplier", None) or 1.0 / math.sqrt(self.D))
         self.window = config.layer_window(layer_idx)
         self.local_rope = bool(self.window and getattr(config, "rope_local_theta", None))
@@ -196,7 +198,13 @@ class Attention(nn.Module):
         if self.qk_norm_full:
             nq, nk = self.Hq * self.D, self.Hkv * self.D
             qkv = torch.cat([self.q_norm(qkv[:, :nq].contiguous()), self.k_norm(qkv[:, nq:nq + nk].contiguous()), qkv[:, nq + nk:]], dim=-1)
-        if self.use_qk_norm:
+        if self.qk_norm_after_rope:
+            qkv = F.rope_packed(qkv, cos, sin, ctx.positions, self.Hq, self.Hkv, self.D, self.rot)
+            nq, nk = self.Hq * self.D, self.Hkv * self.D
+            qn = self.q_norm(qkv[:, :nq].reshape(-1, self.D)).reshape(-1, nq)
+            kn = self.k_norm(qkv[:, nq:nq + nk].reshape(-1, self.D)).reshape(-1, nk)
+            qkv = torch.cat([qn, kn, qkv[:, nq + nk:]], dim=-1)
+        elif self.use_qk_norm:
             qkv = F.qk_norm_rope_packed(qkv, self.q_norm.weight, self.k_norm.weight, cos, sin, ctx.positions,
                                         self.Hq, self.Hkv, self.D, self.rot, self.config.rms_norm_eps)
         elif self.use_rope:
@@ -746,6 +754,10 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
             norm_names += ["self_attn.q_norm.weight", "self_attn.k_norm.weight"]
         for nm in norm_names:
             per_layer.append(Rule(L + nm, [L + nm], offset=off))
+    qk_names = getattr(config, "qk_norm_hf_names", None)
+    if qk_names and config.use_qk_norm and not config.is_mla:
+        per_layer.append(Rule(L + "self_attn.q_norm.weight", [L + "self_attn." + qk_names[0] + ".weight"], offset=off))
+        per_layer.append(Rule(L + "self_attn.k_norm.weight", [L + "self_attn." + qk_names[1] + ".weight"], offset=off))
     dense_rules = [dense_rule]
     if config.mlp_bias and not getattr(config, "hf_fused_gate_up", False):
         dense_rules.append(Rule(L + "mlp.gate_up_proj.bias", [L + "mlp.gate_proj.bias", L + "mlp.up_proj.bias"], "concat", 0))
@@ -755,18 +767,25 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
         if config.is_moe_layer(i):
             E = config.num_experts
             pre = f"model.layers.{i}.mlp."
-            rules.append(Rule(pre + "experts.gate_up_proj", [pre + "experts.{E}.gate_proj.weight", pre + "experts.{E}.up_proj.weight"],
+            # checkpoint-side names: the block ("mlp" unless the family says otherwise, e.g. Mixtral's "block_sparse_moe") and
+            # the three expert projections (gate, up, down)
+            src = f"model.layers.{i}." + (getattr(config, "moe_block_hf_name", None) or "mlp") + "."
+            g_n, u_n, d_n = getattr(config, "expert_proj_hf_names", None) or ("gate_proj", "up_proj", "down_proj")
+            rules.append(Rule(pre + "experts.gate_up_proj", [src + "experts.{E}." + g_n + ".weight", src + "experts.{E}." + u_n + ".weight"],
                               "stack_concat", 0, E, 2))
-            rules.append(Rule(pre + "experts.down_proj", [pre + "experts.{E}.down_proj.weight"], "stack", 0, E))
+            rules.append(Rule(pre + "experts.down_proj", [src + "experts.{E}." + d_n + ".weight"], "stack", 0, E))
+            if getattr(config, "router_weight_hf_name", None) or src != pre:
+                rules.append(Rule(pre + "gate.weight", [src + (getattr(config, "router_weight_hf_name", None) or "gate.weight")]))
             if getattr(config, "router_bias_name", None) and config.topk_method == "noaux_tc":
-                # stored outside the gate module and with a leading unit dimension
-                rules.append(Rule(pre + "gate.e_score_correction_bias", [f"model.layers.{i}." + config.router_bias_name], flatten=True))
+                # stored outside the gate module (and, in some families, with a leading unit dimension)
+                rules.append(Rule(pre + "gate.e_score_correction_bias", [f"model.layers.{i}." + config.router_bias_name],
+                                  flatten=bool(getattr(config, "router_bias_leading_dim", True))))
             if config.n_shared_experts:
                 sh = getattr(config, "shared_expert_hf_name", "shared_experts")
-                if sh != "shared_experts":
-                    rules.append(Rule(pre + "shared_experts.down_proj.weight", [pre + sh + ".down_proj.weight"]))
+                if sh != "shared_experts" or src != pre:
+                    rules.append(Rule(pre + "shared_experts.down_proj.weight", [src + sh + ".down_proj.weight"]))
                 rules.append(Rule(pre + "shared_experts.gate_up_proj.weight",
-                                  [pre + sh + ".gate_proj.weight", pre + sh + ".up_proj.weight"], "concat", 0))
+                                  [src + sh + ".gate_proj.weight", src + sh + ".up_proj.weight"], "concat", 0))
         else:
             rules.extend(expand_layers(dense_rules, [i]))
     # MTP layers are stored by HF DeepSeek-V3 / GLM-4.5 as extra entries of model.layers
@@ -837,11 +856,15 @@ Gemma3ForCausalLM = _family("Gemma3ForCausalLM", Gemma3TextConfig)
 CohereForCausalLM = _family("CohereForCausalLM", CohereConfig)
 Cohere2ForCausalLM = _family("Cohere2ForCausalLM", Cohere2Config)
 StableLmForCausalLM = _family("StableLmForCausalLM", StableLmConfig)
+HunYuanDenseV1ForCausalLM = _family("HunYuanDenseV1ForCausalLM", HunYuanDenseV1Config)
+HunYuanMoEV1ForCausalLM = _family("HunYuanMoEV1ForCausalLM", HunYuanMoEV1Config)
+MiniMaxM2ForCausalLM = _family("MiniMaxM2ForCausalLM", MiniMaxM2Config)
+MixtralForCausalLM = _family("MixtralForCausalLM", MixtralConfig)
 
 MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
     "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
-    "stablelm": StableLmForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
+    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,
 }

@@ -69,6 +69,11 @@ CASES = {
     "cohere2": ("Cohere2Config", "Cohere2ForCausalLM", dict(tie_word_embeddings=True, logit_scale=0.25, num_hidden_layers=4, sliding_window=8,
                                                           layer_types=["sliding_attention", "full_attention", "sliding_attention",
                                                                        "full_attention"])),
+    "hunyuan_v1_dense": ("HunYuanDenseV1Config", "HunYuanDenseV1ForCausalLM", dict(head_dim=16, rope_parameters={
+        "rope_type": "dynamic", "alpha": 50.0, "factor": 1.0, "rope_theta": 10000.0})),
+    "hunyuan_v1_moe": ("HunYuanMoEV1Config", "HunYuanMoEV1ForCausalLM", dict(head_dim=16, num_experts=4, moe_topk=2)),
+    "minimax_m2": ("MiniMaxM2Config", "MiniMaxM2ForCausalLM", dict(head_dim=16, num_local_experts=4, num_experts_per_tok=2)),
+    "mixtral": ("MixtralConfig", "MixtralForCausalLM", dict(num_local_experts=4, num_experts_per_tok=2, sliding_window=8)),
     "stablelm": ("StableLmConfig", "StableLmForCausalLM", dict(use_qkv_bias=True, partial_rotary_factor=0.25)),
     "glm4_moe": ("Glm4MoeConfig", "Glm4MoeForCausalLM", dict(head_dim=16, moe_intermediate_size=32, n_routed_experts=4, num_experts_per_tok=2,
                                                              n_group=1, topk_group=1, n_shared_experts=1, first_k_dense_replace=1,
@@ -101,7 +106,7 @@ def test_logits_match_hugging_face_implementation(tmp_path, family):
     torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma3_text", "cohere", "cohere2", "olmo2",
+@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma3_text", "cohere", "cohere2", "olmo2", "hunyuan_v1_dense", "hunyuan_v1_moe", "minimax_m2", "mixtral",
                                     "stablelm", "granite", "qwen2_moe", "ernie4_5_moe"])
 def test_hugging_face_loads_what_this_framework_saves(tmp_path, family):
     """The other direction: a checkpoint written by ``save_pretrained`` here (per-expert tensors, interleaved rotary rows
