@@ -191,6 +191,26 @@ class DeepseekV3Config(DecoderConfig):
         super().__init__(**kw)
 
 
+class DeepseekV2Config(DeepseekV3Config):
+    """DeepSeek-V2 / V2-Lite: MLA with a softmax router (greedy or group-limited), no multi-token-prediction layer, the query
+    projected directly when ``q_lora_rank`` is null (paddleformers/transformers/deepseek_v3 serves both generations)."""
+
+    model_type = "deepseek_v2"
+
+    def __init__(self, **kw):
+        kw.setdefault("scoring_func", "softmax")
+        kw.setdefault("topk_method", "greedy")
+        kw.setdefault("norm_topk_prob", False)
+        kw.setdefault("routed_scaling_factor", 1.0)
+        kw.setdefault("num_nextn_predict_layers", 0)
+        kw.setdefault("first_k_dense_replace", 1)
+        if "num_experts" not in kw:
+            kw.setdefault("n_routed_experts", 64)
+        kw.setdefault("num_experts_per_tok", 6)
+        kw.setdefault("n_shared_experts", 2)
+        super().__init__(**kw)
+
+
 class Glm4MoeConfig(DecoderConfig):
     model_type = "glm4_moe"
 
@@ -617,7 +637,7 @@ def resolve_config_class(model_type: str):
         raise NotImplementedError(f"model_type {model_type!r} is known but not implemented: it needs {UNSUPPORTED_FAMILIES[model_type]}")
     raise ValueError(f"unknown model_type {model_type!r}; supported: {sorted(CONFIG_MAPPING)}")
 # families whose architecture is a strict subset of an implemented one load through it
-CONFIG_MAPPING.update({"kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV3Config, "glm4_moe_lite": Glm4MoeConfig, "phi4": Phi3Config})
+CONFIG_MAPPING.update({"kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV2Config, "glm4_moe_lite": Glm4MoeConfig, "phi4": Phi3Config})
 
 
 def named_config(name: str, **overrides) -> DecoderConfig:

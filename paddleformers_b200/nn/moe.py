@@ -67,6 +67,8 @@ class TopkRouter(nn.Module):
         self.scoring = config.scoring_func
         self.method = config.topk_method
         self.n_group = max(int(config.n_group or 1), 1)
+        if self.method == "greedy":
+            self.n_group = 1          # plain top-k ignores the expert groups (only the group-limited methods use them)
         self.topk_group = max(int(config.topk_group or 1), 1)
         self.norm_topk_prob = config.norm_topk_prob
         self.scale = float(config.routed_scaling_factor or 1.0)

@@ -122,6 +122,8 @@ def llmmetaclass(cls):
 
 class PretrainedConfig:
     model_type: str = ""
+    # fields whose null is a value of its own and differs from other loaders' defaults (no low-rank query projection, no window)
+    keep_null_keys = ("q_lora_rank", "sliding_window")
     attribute_map: Dict[str, str] = {}
 
     def __init__(self, **kwargs):
@@ -160,7 +162,7 @@ class PretrainedConfig:
                 continue
             if hasattr(v, "to_dict"):
                 v = v.to_dict()
-            if saving and v is None:
+            if saving and v is None and k not in self.keep_null_keys:
                 continue          # absent == None on load; an explicit null breaks other loaders (quantization_config)
             out[k] = v
         out["model_type"] = self.model_type

@@ -60,6 +60,10 @@ CASES = {
         v_head_dim=16, routed_scaling_factor=2.5, norm_topk_prob=True, max_position_embeddings=128,
         rope_scaling={"rope_type": "yarn", "factor": 4.0, "beta_fast": 32, "beta_slow": 1, "mscale": 1.0, "mscale_all_dim": 0.707,
                       "original_max_position_embeddings": 32})),
+    "deepseek_v2": ("DeepseekV2Config", "DeepseekV2ForCausalLM", dict(
+        num_key_value_heads=4, moe_intermediate_size=32, n_routed_experts=8, num_experts_per_tok=2, n_group=2, topk_group=1,
+        n_shared_experts=1, first_k_dense_replace=1, q_lora_rank=None, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8,
+        v_head_dim=16, routed_scaling_factor=1.0, topk_method="greedy", norm_topk_prob=False)),
     "olmo2": ("Olmo2Config", "Olmo2ForCausalLM", dict()),
     "gemma": ("GemmaConfig", "GemmaForCausalLM", dict(head_dim=16, tie_word_embeddings=True, hidden_activation="gelu_pytorch_tanh")),
     "gemma3_text": ("Gemma3TextConfig", "Gemma3ForCausalLM", dict(head_dim=16, num_hidden_layers=4, sliding_window=8, query_pre_attn_scalar=24,
@@ -106,7 +110,7 @@ def test_logits_match_hugging_face_implementation(tmp_path, family):
     torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma3_text", "cohere", "cohere2", "olmo2", "hunyuan_v1_dense", "hunyuan_v1_moe", "minimax_m2", "mixtral",
+@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma3_text", "cohere", "cohere2", "olmo2", "hunyuan_v1_dense", "hunyuan_v1_moe", "minimax_m2", "mixtral", "deepseek_v2",
                                     "stablelm", "granite", "qwen2_moe", "ernie4_5_moe"])
 def test_hugging_face_loads_what_this_framework_saves(tmp_path, family):
     """The other direction: a checkpoint written by ``save_pretrained`` here (per-expert tensors, interleaved rotary rows
