@@ -436,6 +436,22 @@ class MiniCPMConfig(GraniteConfig):
         self.scale_emb, self.scale_depth, self.dim_model_base = scale_emb, scale_depth, dim_model_base
 
 
+class MiniCPM3Config(MiniCPMConfig):
+    """MiniCPM3: MiniCPM's scaling rules on multi-head latent attention (low-rank q and kv projections, a rotary slice shared
+    by all heads' keys) with half-split rotary pairs in the checkpoint and dense SwiGLU MLPs
+    (paddleformers/transformers/minicpm3)."""
+
+    model_type = "minicpm3"
+
+    def __init__(self, qk_nope_head_dim=64, qk_rope_head_dim=32, q_lora_rank=768, kv_lora_rank=256, v_head_dim=None, **kw):
+        kw.setdefault("tie_word_embeddings", True)
+        kw["head_dim"] = qk_nope_head_dim + qk_rope_head_dim
+        super().__init__(qk_nope_head_dim=qk_nope_head_dim, qk_rope_head_dim=qk_rope_head_dim, q_lora_rank=q_lora_rank,
+                         kv_lora_rank=kv_lora_rank, v_head_dim=v_head_dim or qk_nope_head_dim, **kw)
+        self.rope_interleave = False          # rotate_half convention: no row permutation on load
+        self.num_key_value_heads = self.num_attention_heads
+
+
 class Olmo2Config(DecoderConfig):
     """OLMo 2: normalisation AFTER each branch (x + norm(branch(x))) and one RMSNorm over all heads' query / key features
     (paddleformers/transformers/olmo2)."""
@@ -607,7 +623,7 @@ class Ernie4_5MoeConfig(Ernie4_5Config):
 CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, MiniCPMConfig, Olmo2Config,
                                             GemmaConfig, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
                                             Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config, HunYuanDenseV1Config,
-                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig)}
+                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config)}
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
 # feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
@@ -621,7 +637,7 @@ UNSUPPORTED_FAMILIES = {
     "gemma3": "SigLIP vision tower (the text decoder is available as gemma3_text)",
     "phi4_multimodal": "vision and audio towers",
     "gemma2": "soft-capping, sliding / global layer pattern, post norms",
-    "internlm2": "interleaved fused wqkv layout", "minicpm3": "MLA with scaling factors",
+    "internlm2": "interleaved fused wqkv layout",
     "llama4_text": "chunked attention, NoPE layers, shared-expert MoE", "diffllama": "differential attention",
 
     "qwen3_vl": "vision tower and multimodal rotary embedding", "qwen3_vl_moe": "vision tower and multimodal rotary embedding",

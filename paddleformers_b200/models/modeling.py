@@ -31,7 +31,7 @@ from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
                             Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig,
                             GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig,
-                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig)
+                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config)
 
 
 @dataclass
@@ -404,14 +404,21 @@ class DecoderModel(nn.Module):
         cfg = self.config
         rot = int((cfg.qk_rope_head_dim if cfg.is_mla else cfg.head_dim * cfg.partial_rotary_factor))
         n = max(length, 1)
-        key = (str(device), rot, local)
+        kind = (cfg.rope_scaling or {}).get("rope_type", (cfg.rope_scaling or {}).get("type")) if not local else None
+        # rules that depend on the sequence length get one table per regime (longrope: short / long factors) or per length
+        # (dynamic NTK beyond the trained context)
+        regime = F.rope_uses_long_factors(cfg.rope_scaling, n) if kind in ("longrope", "su") else \
+            (n if kind == "dynamic" and n > cfg.max_position_embeddings else 0)
+        key = (str(device), rot, local, regime)
         cached = self._rope_cache.get(key)
         if cached is None or cached[0].shape[0] < n:
-            n = max(n, min(cfg.max_position_embeddings, 8192))
+            seq = n
+            n = max(n, min(cfg.max_position_embeddings, 8192)) if kind != "dynamic" else n
             if local:
                 cached = F.rope_tables(n, rot, float(cfg.rope_local_theta), device, None)
             else:
-                cached = F.rope_tables(n, rot, cfg.rope_theta, device, cfg.rope_scaling)
+                cached = F.rope_tables(n, rot, cfg.rope_theta, device, cfg.rope_scaling, seq_len=seq,
+                                       max_position_embeddings=cfg.max_position_embeddings)
             self._rope_cache[key] = cached
         return cached
 
@@ -860,11 +867,12 @@ HunYuanDenseV1ForCausalLM = _family("HunYuanDenseV1ForCausalLM", HunYuanDenseV1C
 HunYuanMoEV1ForCausalLM = _family("HunYuanMoEV1ForCausalLM", HunYuanMoEV1Config)
 MiniMaxM2ForCausalLM = _family("MiniMaxM2ForCausalLM", MiniMaxM2Config)
 MixtralForCausalLM = _family("MixtralForCausalLM", MixtralConfig)
+MiniCPM3ForCausalLM = _family("MiniCPM3ForCausalLM", MiniCPM3Config)
 
 MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
     "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
-    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
+    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,
 }

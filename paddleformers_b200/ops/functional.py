@@ -350,15 +350,40 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 # ----------------------------------------------------------------------------------------------------------------
 # Rotary embedding (+ per-head QK RMSNorm)
 # ----------------------------------------------------------------------------------------------------------------
-def rope_tables(positions_max: int, rot_dim: int, theta: float, device, scaling: Optional[dict] = None):
-    """fp32 cos/sin tables [positions_max, rot_dim/2]; supports the 'llama3', 'linear' and 'yarn' scaling rules of
-    paddleformers/transformers/modeling_rope_utils.py."""
+def rope_uses_long_factors(scaling: Optional[dict], seq_len: int) -> bool:
+    """'longrope' keeps two sets of per-frequency factors; the long set applies once the sequence exceeds the original
+    context length."""
+    if not scaling or scaling.get("rope_type", scaling.get("type")) not in ("longrope", "su"):
+        return False
+    return int(seq_len) > int(scaling.get("original_max_position_embeddings", 0) or 0)
+
+
+def rope_tables(positions_max: int, rot_dim: int, theta: float, device, scaling: Optional[dict] = None,
+                seq_len: Optional[int] = None, max_position_embeddings: Optional[int] = None):
+    """fp32 cos/sin tables [positions_max, rot_dim/2]; supports the 'llama3', 'linear', 'yarn', 'longrope' and 'dynamic'
+    scaling rules of paddleformers/transformers/modeling_rope_utils.py. ``seq_len`` (default: the table length) is the
+    sequence length the rules that depend on it see: 'longrope' switches to its long factors beyond the original context,
+    'dynamic' grows the base beyond ``max_position_embeddings``."""
     inv_freq = 1.0 / (theta ** (torch.arange(0, rot_dim, 2, dtype=torch.float64) / rot_dim))
     attn_factor = 1.0
+    cur = int(seq_len or positions_max)
     if scaling:
         kind = scaling.get("rope_type", scaling.get("type", "default"))
         factor = float(scaling.get("factor", 1.0))
-        if kind == "linear":
+        if kind in ("longrope", "su"):
+            orig = int(scaling.get("original_max_position_embeddings", 0) or max_position_embeddings or positions_max)
+            ext = scaling["long_factor"] if cur > orig else scaling["short_factor"]
+            inv_freq = inv_freq / torch.tensor(ext, dtype=torch.float64)
+            full = float(max_position_embeddings or orig)
+            ratio = float(scaling["factor"]) if scaling.get("factor") else full / orig
+            attn_factor = float(scaling.get("attention_factor") or
+                                (1.0 if ratio <= 1.0 else math.sqrt(1.0 + math.log(ratio) / math.log(orig))))
+        elif kind == "dynamic":
+            mp = int(max_position_embeddings or scaling.get("original_max_position_embeddings") or positions_max)
+            if cur > mp:
+                base = theta * ((factor * cur / mp) - (factor - 1)) ** (rot_dim / (rot_dim - 2))
+                inv_freq = 1.0 / (base ** (torch.arange(0, rot_dim, 2, dtype=torch.float64) / rot_dim))
+        elif kind == "linear":
             inv_freq = inv_freq / factor
         elif kind == "llama3":
             low = float(scaling.get("low_freq_factor", 1.0))

@@ -26,6 +26,10 @@ CASES = {
                                                                           max_window_layers=1)),
     "qwen3": ("Qwen3Config", "Qwen3ForCausalLM", dict(head_dim=16)),
     "phi3": ("Phi3Config", "Phi3ForCausalLM", dict(pad_token_id=0)),
+    "phi3_longrope": ("Phi3Config", "Phi3ForCausalLM", dict(pad_token_id=0, original_max_position_embeddings=16, rope_scaling={
+        "rope_type": "longrope", "short_factor": [1.0, 1.1, 1.2, 1.3, 1.4, 1.5, 1.6, 1.7],
+        "long_factor": [1.5, 2.0, 2.5, 3.0, 3.5, 4.0, 4.5, 5.0]})),
+    "llama_dynamic_ntk": ("LlamaConfig", "LlamaForCausalLM", dict(max_position_embeddings=16, rope_scaling={"rope_type": "dynamic", "factor": 2.0})),
     "seed_oss": ("SeedOssConfig", "SeedOssForCausalLM", dict(head_dim=16)),
     "granite": ("GraniteConfig", "GraniteForCausalLM", dict(embedding_multiplier=3.0, residual_multiplier=0.5, attention_multiplier=0.2,
                                                            logits_scaling=2.0)),

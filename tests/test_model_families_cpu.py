@@ -267,6 +267,37 @@ def test_minicpm_scaling_maps_to_multipliers_and_kimi_uses_deepseek_blocks():
     assert k.is_mla and k.topk_method == "noaux_tc"
 
 
+def test_minicpm3_is_latent_attention_with_minicpm_scaling_and_half_split_rotary_rows(tmp_path):
+    from safetensors.torch import load_file
+
+    from paddleformers_b200.models.modeling import build_weight_map
+
+    cfg = AutoConfig.for_model("minicpm3", vocab_size=96, hidden_size=32, intermediate_size=48, num_hidden_layers=2,
+                               num_attention_heads=4, qk_nope_head_dim=8, qk_rope_head_dim=4, q_lora_rank=16, kv_lora_rank=8,
+                               scale_emb=12.0, scale_depth=1.4, dim_model_base=8)
+    assert cfg.is_mla and cfg.head_dim == 12 and cfg.v_head_dim == 8 and cfg.num_experts == 0
+    assert cfg.embedding_multiplier == 12.0 and cfg.residual_multiplier == pytest.approx(1.4 / 2 ** 0.5) and cfg.logits_scaling == 4.0
+    # rotate-half checkpoints: no row permutation anywhere in the weight map (DeepSeek checkpoints get one)
+    assert not any(r.rope_deinterleave for r in build_weight_map(cfg).rules.values())
+    ds = AutoConfig.for_model("deepseek_v2", vocab_size=96, hidden_size=32, num_hidden_layers=1, num_attention_heads=4,
+                              qk_nope_head_dim=8, qk_rope_head_dim=4, q_lora_rank=16, kv_lora_rank=8, v_head_dim=8)
+    assert any(r.rope_deinterleave for r in build_weight_map(ds).rules.values())
+    torch.manual_seed(0)
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32).eval()
+    ids = torch.randint(0, 96, (2, 10))
+    want = model(ids, return_logits=True).logits
+    model.save_pretrained(str(tmp_path))
+    names = set(load_file(str(tmp_path / "model.safetensors")))
+    assert {"model.layers.0.self_attn.q_a_proj.weight", "model.layers.0.self_attn.kv_a_proj_with_mqa.weight",
+            "model.layers.1.self_attn.kv_b_proj.weight", "model.layers.0.mlp.gate_proj.weight"} <= names
+    assert "lm_head.weight" not in names                                      # tied head
+    back = AutoModelForCausalLM.from_pretrained(str(tmp_path), dtype=torch.float32).eval()
+    torch.testing.assert_close(back(ids, return_logits=True).logits, want)
+    # stored rows equal the live parameter: nothing was permuted on the way out
+    stored = load_file(str(tmp_path / "model.safetensors"))["model.layers.0.self_attn.q_b_proj.weight"]
+    assert torch.equal(stored, model.model.layers["0"].self_attn.q_b_proj.weight.detach())
+
+
 def test_attention_backends_agree_and_sinks_absorb_probability():
     from paddleformers_b200.nn.attention import AttentionInterface
 
