@@ -386,6 +386,27 @@ class MiniMaxM2Config(DecoderConfig):
         return d
 
 
+class InternLM2Config(DecoderConfig):
+    """InternLM2 / InternLM2.5: Llama blocks stored under their own names (``tok_embeddings``, ``attention.wqkv`` / ``wo``,
+    ``feed_forward.w1`` / ``w3`` / ``w2``, ``attention_norm``, ``ffn_norm``, ``output``) with the fused ``wqkv`` rows grouped
+    by kv head (paddleformers/transformers/intern_lm2, intern_lm2_5)."""
+
+    model_type = "internlm2"
+
+    def __init__(self, bias=False, **kw):
+        if bias:
+            raise NotImplementedError("InternLM2 checkpoints with projection biases are not handled")
+        super().__init__(**kw)
+        self.bias = False
+        self.hf_fused_qkv = True
+        self.qkv_grouped_by_kv_head = True
+        self.hf_name_translation = [["model.embed_tokens.", "model.tok_embeddings."], ["lm_head.", "output."],
+                                    ["self_attn.qkv_proj.", "attention.wqkv."], ["self_attn.o_proj.", "attention.wo."],
+                                    ["input_layernorm.", "attention_norm."], ["post_attention_layernorm.", "ffn_norm."],
+                                    ["mlp.gate_proj.", "feed_forward.w1."], ["mlp.up_proj.", "feed_forward.w3."],
+                                    ["mlp.down_proj.", "feed_forward.w2."]]
+
+
 class Qwen2MoeConfig(DecoderConfig):
     """Qwen2-MoE / Qwen1.5-MoE: softmax router without renormalisation, one wide shared expert whose output is gated per
     token by a sigmoid (paddleformers/transformers/qwen2_moe)."""
@@ -623,7 +644,7 @@ class Ernie4_5MoeConfig(Ernie4_5Config):
 CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, MiniCPMConfig, Olmo2Config,
                                             GemmaConfig, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
                                             Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config, HunYuanDenseV1Config,
-                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config)}
+                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config)}
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
 # feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
@@ -637,7 +658,7 @@ UNSUPPORTED_FAMILIES = {
     "gemma3": "SigLIP vision tower (the text decoder is available as gemma3_text)",
     "phi4_multimodal": "vision and audio towers",
     "gemma2": "soft-capping, sliding / global layer pattern, post norms",
-    "internlm2": "interleaved fused wqkv layout",
+
     "llama4_text": "chunked attention, NoPE layers, shared-expert MoE", "diffllama": "differential attention",
 
     "qwen3_vl": "vision tower and multimodal rotary embedding", "qwen3_vl_moe": "vision tower and multimodal rotary embedding",

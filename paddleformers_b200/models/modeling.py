@@ -31,7 +31,7 @@ from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
                             Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig,
                             GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig,
-                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config)
+                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config)
 
 
 @dataclass
@@ -738,7 +738,10 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
         qkv_sizes = [config.num_attention_heads * config.head_dim, config.num_key_value_heads * config.head_dim,
                      config.num_key_value_heads * config.head_dim]
         if getattr(config, "hf_fused_qkv", False):      # the checkpoint already stores [q | k | v] rows in one matrix
-            per_layer.append(Rule(L + "self_attn.qkv_proj.weight", [L + "self_attn.qkv_proj.weight"]))
+            groups = None
+            if getattr(config, "qkv_grouped_by_kv_head", False):
+                groups = (config.num_key_value_heads, config.num_attention_heads // config.num_key_value_heads, config.head_dim)
+            per_layer.append(Rule(L + "self_attn.qkv_proj.weight", [L + "self_attn.qkv_proj.weight"], qkv_groups=groups))
         else:
             per_layer.append(Rule(L + "self_attn.qkv_proj.weight", [L + "self_attn.q_proj.weight", L + "self_attn.k_proj.weight",
                                                                      L + "self_attn.v_proj.weight"], "concat", 0, sizes=qkv_sizes,
@@ -834,6 +837,26 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
         else:
             rules.append(Rule(blk + "mlp.gate_up_proj.weight", [src + "mlp.gate_proj.weight", src + "mlp.up_proj.weight"], "concat", 0))
             rules.append(Rule(blk + "mlp.down_proj.weight", [src + "mlp.down_proj.weight"]))
+    translation = getattr(config, "hf_name_translation", None)
+    if translation:
+        # families that store the same tensors under other names: parameters that would keep their name get an explicit
+        # rule, then every checkpoint-side name is rewritten
+        have = {r.target for r in rules}
+        same = ["model.embed_tokens.weight", "model.norm.weight"] + ([] if config.tie_word_embeddings else ["lm_head.weight"])
+        for i in range(config.num_hidden_layers):
+            pre = f"model.layers.{i}."
+            same += [pre + "self_attn.o_proj.weight", pre + "input_layernorm.weight", pre + "post_attention_layernorm.weight"]
+            if not config.is_moe_layer(i):
+                same.append(pre + "mlp.down_proj.weight")
+        rules += [Rule(n, [n]) for n in same if n not in have]
+
+        def rewrite(name):
+            for a, b in translation:
+                name = name.replace(a, b)
+            return name
+
+        for r in rules:
+            r.sources = [rewrite(x) for x in r.sources]
     return WeightMap(rules)
 
 
@@ -868,11 +891,12 @@ HunYuanMoEV1ForCausalLM = _family("HunYuanMoEV1ForCausalLM", HunYuanMoEV1Config)
 MiniMaxM2ForCausalLM = _family("MiniMaxM2ForCausalLM", MiniMaxM2Config)
 MixtralForCausalLM = _family("MixtralForCausalLM", MixtralConfig)
 MiniCPM3ForCausalLM = _family("MiniCPM3ForCausalLM", MiniCPM3Config)
+InternLM2ForCausalLM = _family("InternLM2ForCausalLM", InternLM2Config)
 
 MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
     "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
-    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
+    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,
 }

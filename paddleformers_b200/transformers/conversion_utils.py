@@ -89,6 +89,26 @@ def interleave_rope_rows(t: torch.Tensor, head_dim: int) -> torch.Tensor:
     return t.reshape(nh, 2, head_dim // 2, *rest).transpose(1, 2).reshape(t.shape)
 
 
+def ungroup_qkv_rows(t: torch.Tensor, n_kv: int, q_per_kv: int, head_dim: int) -> torch.Tensor:
+    """Rows stored per kv head as [q_0 .. q_{g-1}, k, v] (InternLM2's ``wqkv``) -> [all q heads | all k heads | all v heads]."""
+    rest = t.shape[1:]
+    v = t.reshape(n_kv, q_per_kv + 2, head_dim, *rest)
+    q = v[:, :q_per_kv].reshape(n_kv * q_per_kv * head_dim, *rest)
+    k = v[:, q_per_kv].reshape(n_kv * head_dim, *rest)
+    val = v[:, q_per_kv + 1].reshape(n_kv * head_dim, *rest)
+    return torch.cat([q, k, val], dim=0)
+
+
+def group_qkv_rows(t: torch.Tensor, n_kv: int, q_per_kv: int, head_dim: int) -> torch.Tensor:
+    """Inverse of ``ungroup_qkv_rows``."""
+    rest = t.shape[1:]
+    nq = n_kv * q_per_kv * head_dim
+    q = t[:nq].reshape(n_kv, q_per_kv, head_dim, *rest)
+    k = t[nq:nq + n_kv * head_dim].reshape(n_kv, 1, head_dim, *rest)
+    v = t[nq + n_kv * head_dim:].reshape(n_kv, 1, head_dim, *rest)
+    return torch.cat([q, k, v], dim=1).reshape(t.shape)
+
+
 @dataclass
 class Rule:
     """target <- op(sources). ``sources`` may contain ``{E}`` (expanded over experts for stack rules)."""
@@ -106,6 +126,8 @@ class Rule:
     reshape: Optional[List[int]] = None        # rename: shape of the internal parameter (e.g. a Conv3d kernel used as a matrix)
     source_shape: Optional[List[int]] = None   # rename: shape of the tensor in the checkpoint, for the way back
     offset: float = 0.0                        # rename: internal = checkpoint + offset ((1 + w) norm weights)
+    qkv_groups: Optional[Tuple[int, int, int]] = None   # rename: (kv heads, q heads per kv head, head dim) of a checkpoint that
+    #                                                     stores the fused projection grouped by kv head: [q.. q k v] per group
 
     def _load(self, i: int, t: torch.Tensor) -> torch.Tensor:
         if self.rope_deinterleave and i in self.rope_deinterleave:
@@ -125,6 +147,8 @@ class Rule:
     def forward(self, get: Callable[[str], torch.Tensor], expert_range: Optional[range] = None) -> torch.Tensor:
         if self.op == "rename":
             t = self._load(0, get(self.sources[0]))
+            if self.qkv_groups is not None:
+                t = ungroup_qkv_rows(t, *self.qkv_groups)
             if self.offset:
                 t = t + self.offset
             if self.reshape is not None:
@@ -142,6 +166,8 @@ class Rule:
     def inverse(self, tensor: torch.Tensor, section_sizes: Optional[List[int]] = None, expert_offset: int = 0) -> Dict[str, torch.Tensor]:
         if self.op == "rename":
             t = self._store(0, tensor)
+            if self.qkv_groups is not None:
+                t = group_qkv_rows(t, *self.qkv_groups)
             if self.offset:
                 t = t - self.offset
             if self.source_shape is not None:
@@ -184,5 +210,6 @@ def expand_layers(template_rules: List[Rule], layer_ids: Iterable[int]) -> List[
     for i in layer_ids:
         for r in template_rules:
             out.append(Rule(r.target.replace("{L}", str(i)), [s.replace("{L}", str(i)) for s in r.sources], r.op, r.dim,
-                            r.num_experts, r.expert_pairs, r.sizes, r.rope_deinterleave, r.flatten, r.reshape, r.source_shape, r.offset))
+                            r.num_experts, r.expert_pairs, r.sizes, r.rope_deinterleave, r.flatten, r.reshape, r.source_shape, r.offset,
+                            r.qkv_groups))
     return out

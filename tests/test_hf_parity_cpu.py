@@ -275,3 +275,47 @@ def test_qwen2_5_vl_matches_hugging_face(tmp_path):
         want = hf(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=types).logits
         got = mine(ids, pixel_values=pixels, image_grid_thw=grid, return_logits=True).logits
     torch.testing.assert_close(got, want, rtol=3e-4, atol=3e-4)
+
+
+def test_internlm2_checkpoint_layout_against_a_llama_oracle(tmp_path):
+    """InternLM2 is a Llama whose checkpoint uses other names and a fused ``wqkv`` grouped by kv head. A Hugging Face Llama is
+    rewritten into that format by hand (independently of the framework's rules); loading it must reproduce the Llama's logits,
+    and saving must reproduce the rewritten tensors exactly."""
+    import json
+
+    from safetensors.torch import load_file, save_file
+
+    torch.manual_seed(0)
+    hf_cfg = transformers.LlamaConfig(**{**BASE, "rope_theta": 10000.0})
+    hf = transformers.LlamaForCausalLM(hf_cfg).eval().float()
+    sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
+    Hq, Hkv, D = 4, 2, 16
+    out = {"model.tok_embeddings.weight": sd["model.embed_tokens.weight"], "model.norm.weight": sd["model.norm.weight"],
+           "output.weight": sd["lm_head.weight"]}
+    for i in range(2):
+        p, q = f"model.layers.{i}.", f"model.layers.{i}."
+        wq = sd[p + "self_attn.q_proj.weight"].view(Hkv, Hq // Hkv, D, -1)
+        wk = sd[p + "self_attn.k_proj.weight"].view(Hkv, 1, D, -1)
+        wv = sd[p + "self_attn.v_proj.weight"].view(Hkv, 1, D, -1)
+        out[q + "attention.wqkv.weight"] = torch.cat([wq, wk, wv], dim=1).reshape(-1, wq.shape[-1]).contiguous()
+        out[q + "attention.wo.weight"] = sd[p + "self_attn.o_proj.weight"]
+        out[q + "attention_norm.weight"] = sd[p + "input_layernorm.weight"]
+        out[q + "ffn_norm.weight"] = sd[p + "post_attention_layernorm.weight"]
+        out[q + "feed_forward.w1.weight"] = sd[p + "mlp.gate_proj.weight"]
+        out[q + "feed_forward.w3.weight"] = sd[p + "mlp.up_proj.weight"]
+        out[q + "feed_forward.w2.weight"] = sd[p + "mlp.down_proj.weight"]
+    src = tmp_path / "src"
+    src.mkdir()
+    save_file({k: v.contiguous() for k, v in out.items()}, str(src / "model.safetensors"), metadata={"format": "pt"})
+    cfg = {k: v for k, v in hf_cfg.to_dict().items() if k in BASE or k in ("rms_norm_eps", "rope_theta", "head_dim", "hidden_act")}
+    cfg.update(model_type="internlm2", bias=False, rope_theta=10000.0)
+    (src / "config.json").write_text(json.dumps(cfg))
+    mine = AutoModelForCausalLM.from_pretrained(str(src), dtype=torch.float32).eval()
+    ids = torch.randint(0, 128, (2, 24))
+    with torch.no_grad():
+        torch.testing.assert_close(mine(ids, return_logits=True).logits, hf(input_ids=ids).logits, rtol=2e-4, atol=2e-4)
+    mine.save_pretrained(str(tmp_path / "out"))
+    back = load_file(str(tmp_path / "out" / "model.safetensors"))
+    assert set(back) == set(out)
+    for k in out:
+        assert torch.equal(back[k], out[k]), k
