@@ -247,6 +247,8 @@ def run_vl_sft(model_args, data_args, gen_args, train_args):
     for k in ("min_pixels", "max_pixels"):
         if getattr(data_args, k, None):
             proc_kw[k] = getattr(data_args, k)
+    if model.config.model_type == "qwen3_vl":       # this generation normalises pixels to [-1, 1]
+        proc_kw.update(image_mean=(0.5, 0.5, 0.5), image_std=(0.5, 0.5, 0.5))
     proc = Qwen2VLImageProcessor(**proc_kw)
     names = dict(image_token=tokenizer.convert_ids_to_tokens(model.config.image_token_id),
                  vision_start_token=tokenizer.convert_ids_to_tokens(model.config.vision_start_token_id),

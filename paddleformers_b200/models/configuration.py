@@ -661,7 +661,7 @@ UNSUPPORTED_FAMILIES = {
 
     "llama4_text": "chunked attention, NoPE layers, shared-expert MoE", "diffllama": "differential attention",
 
-    "qwen3_vl": "vision tower and multimodal rotary embedding", "qwen3_vl_moe": "vision tower and multimodal rotary embedding",
+
     "ernie4_5_vl": "vision tower, modality-aware experts", "paddleocr_vl": "vision tower", "glm4v_moe": "vision tower",
     "paligemma": "SigLIP vision tower", "whisper": "encoder-decoder speech model", "qwen3_omni_moe": "audio / vision towers",
 }

@@ -781,9 +781,13 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
             # the three expert projections (gate, up, down)
             src = f"model.layers.{i}." + (getattr(config, "moe_block_hf_name", None) or "mlp") + "."
             g_n, u_n, d_n = getattr(config, "expert_proj_hf_names", None) or ("gate_proj", "up_proj", "down_proj")
-            rules.append(Rule(pre + "experts.gate_up_proj", [src + "experts.{E}." + g_n + ".weight", src + "experts.{E}." + u_n + ".weight"],
-                              "stack_concat", 0, E, 2))
-            rules.append(Rule(pre + "experts.down_proj", [src + "experts.{E}." + d_n + ".weight"], "stack", 0, E))
+            if getattr(config, "hf_fused_experts", False):     # the checkpoint stores the stacked [E, 2I, H] / [E, H, I] tensors
+                rules.append(Rule(pre + "experts.gate_up_proj", [src + "experts.gate_up_proj"]))
+                rules.append(Rule(pre + "experts.down_proj", [src + "experts.down_proj"]))
+            else:
+                rules.append(Rule(pre + "experts.gate_up_proj", [src + "experts.{E}." + g_n + ".weight", src + "experts.{E}." + u_n + ".weight"],
+                                  "stack_concat", 0, E, 2))
+                rules.append(Rule(pre + "experts.down_proj", [src + "experts.{E}." + d_n + ".weight"], "stack", 0, E))
             if getattr(config, "router_weight_hf_name", None) or src != pre:
                 rules.append(Rule(pre + "gate.weight", [src + (getattr(config, "router_weight_hf_name", None) or "gate.weight")]))
             if getattr(config, "router_bias_name", None) and config.topk_method == "noaux_tc":

@@ -126,7 +126,8 @@ class _VisionBlock(nn.Module):
             self.fc1 = nn.Linear(dim, mlp_hidden, **kw)
             self.fc2 = nn.Linear(mlp_hidden, dim, **kw)
         self.heads, self.hd = heads, dim // heads
-        self.act = _quick_gelu if act == "quick_gelu" else getattr(TF, act)
+        self.act = _quick_gelu if act == "quick_gelu" else (lambda x: TF.gelu(x, approximate="tanh")) if act == "gelu_pytorch_tanh" \
+            else getattr(TF, act)
 
     def mlp(self, x):
         if self.swiglu:
@@ -428,3 +429,263 @@ def mm_collate_fn(examples: List[dict], pad_token_id: int = 0, ignore_index: int
 
 class Qwen2_5_VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
     config_class = Qwen2_5_VLConfig
+
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Qwen3-VL
+# ---------------------------------------------------------------------------------------------------------------
+class Qwen3VLConfig(Qwen2VLConfig):
+    """Qwen3-VL: a Qwen3 decoder (per-head QK norm) whose rotary frequencies take the temporal / height / width position in
+    an interleaved pattern, a vision tower with learned position embeddings interpolated to the image grid, and "deepstack":
+    features of intermediate vision blocks are added to the visual tokens after the first decoder layers
+    (paddleformers/transformers/qwen3_vl)."""
+
+    model_type = "qwen3_vl"
+    text_model_type = "qwen3_vl_text"
+
+    def _text_class(self):
+        from .configuration import Qwen3Config
+
+        return Qwen3Config
+
+    def __init__(self, text_config=None, vision_config=None, **kwargs):
+
+        text = dict(text_config or {})
+        text.pop("model_type", None)
+        rp = dict(text.get("rope_parameters") or text.get("rope_scaling") or {})
+        section = list(rp.pop("mrope_section", None) or [24, 20, 20])
+        rp.pop("mrope_interleaved", None)
+        if "rope_parameters" in text:
+            text["rope_parameters"] = rp
+        elif "rope_scaling" in text:
+            text["rope_scaling"] = rp if rp.get("rope_type", rp.get("type", "default")) not in ("default", "mrope") else None
+        tie = bool(text.get("tie_word_embeddings", kwargs.get("tie_word_embeddings", False)))
+        text.setdefault("tie_word_embeddings", tie)
+        text.setdefault("use_qk_norm", True)
+        text.setdefault("rope_theta", 5000000.0)
+        super().__init__(text_config={"num_hidden_layers": 1}, vision_config={}, **{**kwargs, "tie_word_embeddings": tie})
+        self.text_config = self._text_class()(**text)
+        self.mrope_section, self.mrope_interleaved = section, True
+        v = dict(vision_config or {})
+        v.pop("model_type", None)
+        self.vision_config = {"depth": 27, "hidden_size": 1152, "hidden_act": "gelu_pytorch_tanh", "intermediate_size": 4304,
+                              "num_heads": 16, "in_channels": 3, "patch_size": 16, "spatial_merge_size": 2, "temporal_patch_size": 2,
+                              "out_hidden_size": self.text_config.hidden_size, "num_position_embeddings": 2304,
+                              "deepstack_visual_indexes": [8, 16, 24], **v}
+
+    def to_dict(self, saving: bool = False):
+        d = PretrainedConfig.to_dict(self, saving)
+        text = self.text_config.to_dict(saving)
+        text["model_type"] = self.text_model_type
+        scaling = text.pop("rope_scaling", None) or {}
+        text["rope_parameters"] = {"rope_type": "default", **scaling, "rope_theta": text.pop("rope_theta", self.text_config.rope_theta),
+                                   "mrope_section": self.mrope_section, "mrope_interleaved": True}
+        d["text_config"] = text
+        d["vision_config"] = dict(self.vision_config, model_type=self.model_type)
+        d.pop("mrope_section", None)
+        d.pop("mrope_interleaved", None)
+        return d
+
+
+class Qwen3VLMoeConfig(Qwen3VLConfig):
+    """Qwen3-VL with the Qwen3-MoE decoder (paddleformers/transformers/qwen3_vl_moe)."""
+
+    model_type = "qwen3_vl_moe"
+    text_model_type = "qwen3_vl_moe_text"
+
+    def _text_class(self):
+        from .configuration import Qwen3MoeConfig
+
+        def make(**kw):
+            cfg = Qwen3MoeConfig(**kw)
+            cfg.hf_fused_experts = True        # this family's checkpoints hold the experts as stacked tensors
+            return cfg
+
+        return make
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if saving and "num_experts" in d["text_config"]:
+            d["text_config"]["num_local_experts"] = d["text_config"]["num_experts"]
+        return d
+
+
+class _Merger(nn.Module):
+    """LayerNorm (before or after the merge-block shuffle) -> linear -> GELU -> linear to the decoder width."""
+
+    def __init__(self, dim: int, unit: int, out_dim: int, post_shuffle_norm: bool, dtype=None, device=None):
+        super().__init__()
+        kw = dict(dtype=dtype, device=device)
+        self.width, self.post = dim * unit, post_shuffle_norm
+        self.norm = nn.LayerNorm(self.width if post_shuffle_norm else dim, eps=1e-6, **kw)
+        self.fc1 = nn.Linear(self.width, self.width, **kw)
+        self.fc2 = nn.Linear(self.width, out_dim, **kw)
+
+    def forward(self, x):
+        x = self.norm(x.view(-1, self.width)) if self.post else self.norm(x).view(-1, self.width)
+        return self.fc2(TF.gelu(self.fc1(x)))
+
+
+class Qwen3VisionTower(VisionTower):
+    def __init__(self, vc: dict, dtype=None, device=None):
+        nn.Module.__init__(self)
+        kw = dict(dtype=dtype, device=device)
+        self.vc = vc
+        dim = vc["hidden_size"]
+        self.patch_dim = vc["in_channels"] * vc["temporal_patch_size"] * vc["patch_size"] ** 2
+        self.patch_embed = nn.Linear(self.patch_dim, dim, bias=True, **kw)
+        self.pos_embed = nn.Embedding(vc["num_position_embeddings"], dim, **kw)
+        self.side = int(vc["num_position_embeddings"] ** 0.5)
+        self.blocks = nn.ModuleList([_VisionBlock(dim, vc["num_heads"], vc["intermediate_size"], vc["hidden_act"], **kw)
+                                     for _ in range(vc["depth"])])
+        unit = vc["spatial_merge_size"] ** 2
+        self.merger = _Merger(dim, unit, vc["out_hidden_size"], False, **kw)
+        self.deepstack_indexes = list(vc["deepstack_visual_indexes"])
+        self.deepstack_mergers = nn.ModuleList([_Merger(dim, unit, vc["out_hidden_size"], True, **kw) for _ in self.deepstack_indexes])
+        self.head_dim = dim // vc["num_heads"]
+
+    def position_embeddings(self, grid_thw: torch.Tensor) -> torch.Tensor:
+        """The learned side x side table, bilinearly interpolated to every image's patch grid (corners aligned), repeated
+        over frames and put in the processor's merge-block patch order."""
+        ms, side = self.vc["spatial_merge_size"], self.side
+        table = self.pos_embed.weight
+        out = []
+        for t, h, w in grid_thw.tolist():
+            hs = torch.linspace(0, side - 1, h, device=table.device)
+            ws = torch.linspace(0, side - 1, w, device=table.device)
+            h0, w0 = hs.long(), ws.long()
+            h1, w1 = (h0 + 1).clamp(max=side - 1), (w0 + 1).clamp(max=side - 1)
+            dh, dw = (hs - h0)[:, None].to(table.dtype), (ws - w0)[None, :].to(table.dtype)
+
+            def at(r, c):
+                return table[(r[:, None] * side + c[None, :]).reshape(-1)].view(h, w, -1)
+
+            e = at(h0, w0) * ((1 - dh) * (1 - dw))[..., None] + at(h0, w1) * ((1 - dh) * dw)[..., None] \
+                + at(h1, w0) * (dh * (1 - dw))[..., None] + at(h1, w1) * (dh * dw)[..., None]
+            e = e.view(h // ms, ms, w // ms, ms, -1).permute(0, 2, 1, 3, 4).reshape(h * w, -1)
+            out.append(e.repeat(t, 1))
+        return torch.cat(out, dim=0)
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor):
+        x = self.patch_embed(pixel_values.to(self.patch_embed.weight.dtype))
+        x = x + self.position_embeddings(grid_thw).to(x.dtype)
+        cos, sin = self.rotary(grid_thw, x.device)
+        lengths = [h * w for t, h, w in grid_thw.tolist() for _ in range(t)]
+        deep = []
+        for i, blk in enumerate(self.blocks):
+            x = blk(x, cos, sin, lengths)
+            if i in self.deepstack_indexes:
+                deep.append(self.deepstack_mergers[self.deepstack_indexes.index(i)](x))
+        return self.merger(x), deep
+
+
+class Qwen3VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
+    config_class = Qwen3VLConfig
+
+    def __init__(self, config: Qwen3VLConfig, dtype=None, device=None):
+        PretrainedModel.__init__(self, config)
+        self.visual = Qwen3VisionTower(config.vision_config, dtype=dtype, device=device)
+        self.language = DecoderForCausalLM(config.text_config, dtype=dtype, device=device)
+        self._vision_prefix, self._text_nested = "model.visual.", True
+
+    def _context(self, input_ids, position_ids3) -> BatchContext:
+        B, S = input_ids.shape
+        lm = self.language.model
+        D = self.config.text_config.head_dim
+        cos_t, sin_t = lm.rope(input_ids.device, int(position_ids3.max().item()) + 1)
+        # interleaved sections: frequency i follows the temporal position unless i = 1 (mod 3) below 3 * section[1] (height)
+        # or i = 2 (mod 3) below 3 * section[2] (width)
+        axis = torch.zeros(D // 2, dtype=torch.long, device=input_ids.device)
+        sec = self.config.mrope_section
+        axis[1:sec[1] * 3:3] = 1
+        axis[2:sec[2] * 3:3] = 2
+        flat = position_ids3.reshape(3, B * S)
+        sel = flat[axis]
+        col = torch.arange(D // 2, device=input_ids.device)[:, None]
+        return BatchContext(B, S, torch.arange(B * S, device=input_ids.device), None, cos_t[sel, col].t().contiguous(),
+                            sin_t[sel, col].t().contiguous())
+
+    def forward(self, input_ids, pixel_values=None, image_grid_thw=None, pixel_values_videos=None, video_grid_thw=None, labels=None,
+                position_ids=None, return_logits: Optional[bool] = None, **unused):
+        cfg, lm = self.config, self.language
+        h = lm.model.embed(input_ids)
+        flat_ids = input_ids.reshape(-1)
+        visual_rows, deep_feats = [], None
+        frames_grid = None
+        if video_grid_thw is not None:          # every frame of a video is placed like an image (text may sit between frames)
+            frames_grid = torch.repeat_interleave(video_grid_thw, video_grid_thw[:, 0], dim=0).clone()
+            frames_grid[:, 0] = 1
+        for pv, grid, tok in ((pixel_values, image_grid_thw, cfg.image_token_id), (pixel_values_videos, video_grid_thw, cfg.video_token_id)):
+            if pv is None:
+                continue
+            feats, deep = self.visual(pv, grid)
+            rows = (flat_ids == tok).nonzero(as_tuple=True)[0]
+            assert rows.numel() == feats.shape[0], "one placeholder token per merged patch is required"
+            h = h.index_copy(0, rows, feats.to(h.dtype))
+            visual_rows.append(rows)
+            deep_feats = deep if deep_feats is None else [torch.cat([a, b], dim=0) for a, b in zip(deep_feats, deep)]
+        if position_ids is None:
+            position_ids = multimodal_position_ids(input_ids, cfg.image_token_id, cfg.video_token_id, image_grid_thw, frames_grid,
+                                                   cfg.vision_config["spatial_merge_size"])
+        ctx = self._context(input_ids, position_ids)
+        hidden, residual = h, None
+        rows = torch.cat(visual_rows) if visual_rows else None
+        for i, layer in enumerate(lm.model.layers.values()):
+            hidden, residual = layer(hidden, residual, ctx)
+            if deep_feats is not None and i < len(deep_feats):
+                # the layer's output is hidden + residual (the add runs inside the next norm): adding to either term adds to it
+                add = deep_feats[i].to(hidden.dtype)
+                if residual is None:
+                    hidden = hidden.index_add(0, rows, add)
+                else:
+                    residual = residual.index_add(0, rows, add)
+        hidden = lm.model.norm(hidden, residual)[0] if residual is not None else lm.model.norm(hidden)
+        out = CausalLMOutput()
+        if return_logits if return_logits is not None else labels is None:
+            out.logits = lm.compute_logits(hidden).view(ctx.B, ctx.S, -1)
+        if labels is not None:
+            lab = labels.reshape(-1)
+            count = (lab != lm.ignore_index).sum()
+            scale = 1.0 / (count.clamp(min=1).to(torch.float32) * float(lm.loss_accumulation_steps))
+            out.loss, _ = lm._loss(hidden, lab, scale)
+            out.num_tokens = count
+        return out
+
+    def load_hf_checkpoint(self, directory: str, strict: bool = False) -> None:
+        PretrainedModel.load_hf_checkpoint(self, directory, strict)
+
+    def weight_map(self) -> WeightMap:
+        vis = "model.visual."
+        rules = []
+        for r in build_weight_map(self.config.text_config).rules.values():
+            src = [s if s.startswith("lm_head.") else s.replace("model.", "model.language_model.", 1) for s in r.sources]
+            rules.append(Rule("language." + r.target, src, r.op, r.dim, r.num_experts, r.expert_pairs, r.sizes, r.rope_deinterleave,
+                              r.flatten, r.reshape, r.source_shape, r.offset, r.qkv_groups))
+        known = {r.target for r in rules}
+        for name, _ in self.language.named_parameters():
+            if "language." + name not in known:
+                rules.append(Rule("language." + name, [name if name.startswith("lm_head.") else name.replace("model.", "model.language_model.", 1)]))
+        vc = self.config.vision_config
+        width = vc["hidden_size"]
+        conv_shape = [width, vc["in_channels"], vc["temporal_patch_size"], vc["patch_size"], vc["patch_size"]]
+        rules.append(Rule("visual.patch_embed.weight", [vis + "patch_embed.proj.weight"], reshape=[width, -1], source_shape=conv_shape))
+        rules.append(Rule("visual.patch_embed.bias", [vis + "patch_embed.proj.bias"]))
+        rules.append(Rule("visual.pos_embed.weight", [vis + "pos_embed.weight"]))
+        for i in range(vc["depth"]):
+            a, b = f"visual.blocks.{i}.", vis + f"blocks.{i}."
+            for mine, theirs in (("norm1", "norm1"), ("norm2", "norm2"), ("qkv", "attn.qkv"), ("proj", "attn.proj"),
+                                 ("fc1", "mlp.linear_fc1"), ("fc2", "mlp.linear_fc2")):
+                for leaf in ("weight", "bias"):
+                    rules.append(Rule(a + f"{mine}.{leaf}", [b + f"{theirs}.{leaf}"]))
+        mergers = [("visual.merger.", vis + "merger.")] + [(f"visual.deepstack_mergers.{k}.", vis + f"deepstack_merger_list.{k}.")
+                                                           for k in range(len(vc["deepstack_visual_indexes"]))]
+        for a, b in mergers:
+            for mine, theirs in (("norm", "norm"), ("fc1", "linear_fc1"), ("fc2", "linear_fc2")):
+                for leaf in ("weight", "bias"):
+                    rules.append(Rule(a + f"{mine}.{leaf}", [b + f"{theirs}.{leaf}"]))
+        return WeightMap(rules)
+
+
+class Qwen3VLMoeForConditionalGeneration(Qwen3VLForConditionalGeneration):
+    config_class = Qwen3VLMoeConfig

@@ -190,6 +190,10 @@ class PretrainedModel(nn.Module):
                         # the checkpoint already stores this tensor in the fused internal layout (stacked experts
                         # [E, 2I, H] / [E, H, I] as written by recent Hugging Face releases)
                         full = get(name)
+                    elif rule.op in ("stack", "stack_concat") and "{E}" in rule.sources[0] and \
+                            reader.has(rule.sources[0].split("{E}")[0] + name.rsplit(".", 1)[-1]):
+                        # the same, under the checkpoint's own prefix (a decoder nested inside a larger model)
+                        full = get(rule.sources[0].split("{E}")[0] + name.rsplit(".", 1)[-1])
                     else:
                         missing.append(name)
                         continue

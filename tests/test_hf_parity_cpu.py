@@ -319,3 +319,54 @@ def test_internlm2_checkpoint_layout_against_a_llama_oracle(tmp_path):
     assert set(back) == set(out)
     for k in out:
         assert torch.equal(back[k], out[k]), k
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_qwen3_vl_matches_hugging_face(tmp_path, moe):
+    """Interpolated position embeddings, deepstack features added after the first decoder layers, interleaved multimodal rotary
+    sections and per-head QK norm against ``transformers``' Qwen3-VL, on two images of different sizes between text tokens."""
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    names = ("Qwen3VLMoeConfig", "Qwen3VLMoeForConditionalGeneration") if moe else ("Qwen3VLConfig", "Qwen3VLForConditionalGeneration")
+    if not all(hasattr(transformers, n) for n in names):
+        pytest.skip("transformers has no Qwen3-VL")
+    HFConfig, HFModel = (getattr(transformers, n) for n in names)
+    torch.manual_seed(7)
+    vc = dict(depth=3, hidden_size=32, intermediate_size=48, num_heads=2, in_channels=3, patch_size=4, spatial_merge_size=2,
+              temporal_patch_size=2, out_hidden_size=64, num_position_embeddings=36, deepstack_visual_indexes=[0, 2])
+    tc = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=16, max_position_embeddings=128, tie_word_embeddings=False,
+              rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [4, 2, 2], "mrope_interleaved": True})
+    if moe:
+        tc.update(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=24, decoder_sparse_step=1, mlp_only_layers=[1])
+    cfg = HFConfig(text_config=tc, vision_config=vc, image_token_id=120, video_token_id=121,
+                                     vision_start_token_id=118, vision_end_token_id=119)
+    hf = HFModel(cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.dim() == 1:
+                p.normal_(1.0 if "norm" in n and "bias" not in n else 0.0, 0.1)
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path), dtype=torch.float32).eval()
+    grid = torch.tensor([[1, 4, 6], [1, 2, 2]])
+    pixels = torch.randn(int(grid.prod(-1).sum()), 3 * 2 * 4 * 4)
+    ids = torch.tensor([[5, 6, 118] + [120] * 6 + [119, 7, 8, 9, 118, 120, 119, 10, 11]])
+    types = (ids == 120).int()
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=types).logits
+        got = mine(ids, pixel_values=pixels, image_grid_thw=grid, return_logits=True).logits
+    torch.testing.assert_close(got, want, rtol=3e-4, atol=3e-4)
+    text = torch.randint(0, 100, (2, 12))
+    with torch.no_grad():
+        torch.testing.assert_close(mine(text, return_logits=True).logits, hf(input_ids=text).logits, rtol=3e-4, atol=3e-4)
+    out = tmp_path / "out"
+    mine.save_pretrained(str(out))
+    back = HFModel.from_pretrained(str(out), torch_dtype=torch.float32).eval()
+    with torch.no_grad():
+        torch.testing.assert_close(back(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=types).logits, want,
+                                   rtol=3e-4, atol=3e-4)
+    # gradients reach the vision tower, its position table and the deepstack mergers
+    mine.train()
+    mine(ids, pixel_values=pixels, image_grid_thw=grid, labels=torch.roll(ids, -1, 1)).loss.backward()
+    for name in ("visual.pos_embed.weight", "visual.deepstack_mergers.1.fc2.weight", "visual.blocks.0.qkv.weight"):
+        assert dict(mine.named_parameters())[name].grad.abs().sum() > 0, name
