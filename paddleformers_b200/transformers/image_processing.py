@@ -82,3 +82,67 @@ class Qwen2VLImageProcessor:
     def num_image_tokens(self, grid_thw) -> int:
         t, h, w = (int(v) for v in grid_thw)
         return t * h * w // (self.merge_size ** 2)
+
+
+class Qwen2VLVideoProcessor(Qwen2VLImageProcessor):
+    """Video pre-processing (roles of paddleformers/transformers/video_processing_utils.py and the Qwen2-VL video processor):
+    ``__call__(videos)`` takes clips as uint8 arrays [frames, H, W, 3], optionally samples frames uniformly
+    (``num_frames`` or ``fps`` with the clip's own ``source_fps``), resizes all frames of a clip to one size whose per-clip
+    pixel count (frames x H x W) stays within the budget, pads the clip to a multiple of ``temporal_patch_size`` by repeating
+    its last frame, and cuts it into spatio-temporal patches in the tower's merge-block order. Returns
+    ``pixel_values_videos`` [patches, C * T * P * P] and ``video_grid_thw`` [clips, 3]."""
+
+    def __init__(self, *args, min_frames: int = 4, max_frames: int = 768, **kw):
+        kw.setdefault("min_pixels", 128 * 28 * 28)
+        kw.setdefault("max_pixels", 28 * 28 * 768)
+        super().__init__(*args, **kw)
+        self.min_frames, self.max_frames = min_frames, max_frames
+
+    def sample_indices(self, total: int, num_frames: int = None, fps: float = None, source_fps: float = None) -> np.ndarray:
+        """Uniformly spaced frame indices: ``num_frames`` of them, or ``fps`` per second of a clip recorded at ``source_fps``
+        (rounded to a multiple of the temporal patch size and clamped to [min_frames, max_frames])."""
+        T = self.temporal_patch_size
+        if num_frames is None and fps is not None:
+            if not source_fps:
+                raise ValueError("sampling by fps needs the clip's source_fps")
+            n = total / source_fps * fps
+            n = min(max(n, self.min_frames), self.max_frames, total)
+            num_frames = max(int(math.floor(n / T) * T), T)
+        if num_frames is None:
+            return np.arange(total)
+        if num_frames > total:
+            raise ValueError(f"cannot sample {num_frames} frames from a clip of {total}")
+        return np.linspace(0, total - 1, num_frames).round().astype(np.int64)
+
+    def preprocess_clip(self, frames: np.ndarray):
+        """frames: uint8 [F, H, W, 3] -> (patches [grid_t * grid_h * grid_w, C * T * P * P], (grid_t, grid_h, grid_w))."""
+        P, m, T = self.patch_size, self.merge_size, self.temporal_patch_size
+        F = frames.shape[0]
+        # the pixel budget of a clip is shared by its frames
+        h, w = smart_resize(frames.shape[1], frames.shape[2], P * m, self.min_pixels // max(F, 1) if F > 1 else self.min_pixels,
+                            max(self.max_pixels // max(F, 1), (P * m) ** 2))
+        x = np.stack([_resize(np.ascontiguousarray(f), h, w) for f in frames]).astype(np.float32) * self.rescale_factor
+        x = (x - self.mean) / self.std
+        x = np.transpose(x, (0, 3, 1, 2))                                    # [F, C, H, W]
+        if F % T:
+            x = np.concatenate([x, np.repeat(x[-1:], T - F % T, axis=0)], axis=0)
+        gt, gh, gw = x.shape[0] // T, h // P, w // P
+        C = x.shape[1]
+        x = x.reshape(gt, T, C, gh // m, m, P, gw // m, m, P)
+        x = x.transpose(0, 3, 6, 4, 7, 2, 1, 5, 8)                          # [gt, gh/m, gw/m, m, m, C, T, P, P]
+        return x.reshape(gt * gh * gw, C * T * P * P), (gt, gh, gw)
+
+    def __call__(self, videos: List[np.ndarray], num_frames: int = None, fps: float = None, source_fps=None, return_tensors: str = "pt"):
+        patches, grids = [], []
+        for i, clip in enumerate(videos):
+            clip = np.asarray(clip)
+            sf = source_fps[i] if isinstance(source_fps, (list, tuple)) else source_fps
+            idx = self.sample_indices(clip.shape[0], num_frames, fps, sf)
+            p, g = self.preprocess_clip(clip[idx])
+            patches.append(p)
+            grids.append(g)
+        pv = np.concatenate(patches, axis=0)
+        grid = np.asarray(grids, dtype=np.int64)
+        if return_tensors == "pt":
+            return {"pixel_values_videos": torch.from_numpy(pv), "video_grid_thw": torch.from_numpy(grid)}
+        return {"pixel_values_videos": pv, "video_grid_thw": grid}

