@@ -205,3 +205,59 @@ def test_stream_loader_reads_on_one_rank_and_scatters():
 
     out = list(StreamDistDataLoader(iter(range(5)) and list(range(5)), batch_size=2, collate_fn=lambda x: torch.tensor(x)))
     assert [o.tolist() for o in out] == [[0, 1], [2, 3]]
+
+
+def test_rl_prompt_dataset_left_pads_and_batch_container_operations(tmp_path):
+    import json
+
+    import numpy as np
+    import pytest
+    import torch
+
+    from paddleformers_b200.datasets.rl_dataset import DataProto, RLHFDataset, left_padding, rl_collate_fn
+
+    class Tok:
+        chat_template = None
+        pad_token_id = 0
+
+        def __call__(self, text, add_special_tokens=True):
+            return {"input_ids": ([1] if add_special_tokens else []) + [2 + (ord(c) % 50) for c in text]}
+
+    path = tmp_path / "prompts.jsonl"
+    path.write_text("\n".join(json.dumps({"src": s, "tgt": t}) for s, t in
+                              [("hi", "a"), ("what is 2+2", "4"), ("x" * 40, "long"), ("bye now", "ok")]))
+    ds = RLHFDataset(str(path), Tok(), max_prompt_len=16, requires_label=True, response_key="tgt")
+    assert len(ds) == 3                                              # the 40-character prompt is dropped, not cut
+    batch = rl_collate_fn([ds[i] for i in range(3)], pad_token_id=0, requires_label=True)
+    ids, mask = batch["input_ids"], batch["attention_mask"]
+    assert ids.shape == (3, 12) and ids[0, :9].eq(0).all() and ids[0, 9] == 1 and mask[0].tolist() == [0] * 9 + [1] * 3
+    assert batch["position_ids"][0].tolist() == [0] * 9 + [0, 1, 2] and batch["position_ids"][1].tolist() == list(range(12))
+    assert batch["label_ids"].shape[0] == 3
+    assert left_padding([torch.tensor([1, 2, 3])], 0, 2).tolist() == [[2, 3]]
+
+    dp = DataProto.from_dict({"input_ids": ids, "attention_mask": mask}, {"uid": ["a", "b", "c"]}, {"temperature": 0.7})
+    assert len(dp) == 3 and dp[1]["uid"] == "b"
+    padded, pad = dp.pad_to_divisor(2)
+    assert len(padded) == 4 and pad == 1 and padded[3]["uid"] == "a"
+    parts = padded.chunk(2)
+    assert [len(p) for p in parts] == [2, 2] and parts[1].non_tensor_batch["uid"].tolist() == ["c", "a"]
+    back = DataProto.concat(parts).unpad(pad)
+    assert torch.equal(back.batch["input_ids"], ids) and back.non_tensor_batch["uid"].tolist() == ["a", "b", "c"]
+    rep = dp.repeat(2, interleave=True)
+    assert rep.non_tensor_batch["uid"].tolist() == ["a", "a", "b", "b", "c", "c"] and torch.equal(rep.batch["input_ids"][1], ids[0])
+    assert dp.repeat(2, interleave=False).non_tensor_batch["uid"].tolist() == ["a", "b", "c", "a", "b", "c"]
+    sel = dp.select(batch_keys=["input_ids"])
+    assert set(sel.batch) == {"input_ids"} and "uid" in sel.non_tensor_batch
+    scores = DataProto.from_dict({"reward": torch.tensor([1.0, 0.0, 0.5])})
+    dp.union(scores)
+    assert "reward" in dp.batch
+    with pytest.raises(ValueError):
+        dp.union(DataProto.from_dict({"reward": torch.zeros(3)}))
+    popped = dp.pop(batch_keys=["reward"])
+    assert "reward" not in dp.batch and popped.batch["reward"].tolist() == [1.0, 0.0, 0.5]
+    dp.reorder(torch.tensor([2, 0, 1]))
+    assert dp.non_tensor_batch["uid"].tolist() == ["c", "a", "b"] and torch.equal(dp.batch["input_ids"][1], ids[0])
+    seen = [m.non_tensor_batch["uid"].tolist() for m in dp.select().pad_to_divisor(1)[0].make_iterator(1, epochs=2, seed=0)]
+    assert len(seen) == 6 and sorted(x[0] for x in seen[:3]) == ["a", "b", "c"]
+    with pytest.raises(ValueError):
+        DataProto.from_dict({"a": torch.zeros(2)}, {"b": np.zeros(3)})
