@@ -168,7 +168,13 @@ class Trainer:
         if self.optimizer is None:
             opt_cls, extra = ShardedAdamW, {}
             name = str(getattr(a, "optim", "adamw")).lower()
-            if name == "muon":
+            if a.sharding == "stage3":
+                from ..parallel.fsdp import FullyShardedOptimizer
+
+                if name not in ("adamw", "adamw_torch", "adamw_fused"):
+                    raise ValueError("sharding stage3 is implemented for optim=adamw")
+                opt_cls = FullyShardedOptimizer
+            elif name == "muon":
                 from ..parallel.sharding import ShardedMuon
 
                 opt_cls = ShardedMuon

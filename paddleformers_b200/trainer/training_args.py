@@ -68,7 +68,9 @@ class TrainingArguments:
     sharding_parallel_size: int = -1
     sharding: str = field(default="", metadata={"help": "'' | stage1 | stage2 (optimizer-state sharding; stage2 is accepted for "
                                                         "configuration compatibility and runs the stage1 plan: gradients stay in the "
-                                                        "full fp32 accumulation buffer that the weight-gradient GEMMs write)"})
+                                                        "full fp32 accumulation buffer that the weight-gradient GEMMs write) | stage3 "
+                                                        "(alias fsdp: parameters, gradients and optimizer state sharded per decoder "
+                                                        "layer over the data ranks, with per-layer recompute)"})
     sequence_parallel: bool = False
     hybrid_parallel_topo_order: str = "sharding_first"
     pipeline_schedule: str = field(default="1F1B", metadata={"help": "1F1B | interleaved | FThenB | zero_bubble (backward split into input-gradient and deferred weight-gradient parts) | zbv (zero_bubble on a V-shaped placement with two chunks per stage)"})
@@ -156,9 +158,13 @@ class TrainingArguments:
             raise ValueError(f"world size {world} is not divisible by tp*pp*sep*cp = {model_par}")
         rest = world // model_par
         if self.sharding:
-            if self.sharding not in ("stage1", "stage2"):
-                raise ValueError("sharding must be '', 'stage1' or 'stage2' (stage3 / fsdp are not compatible with "
-                                 "pipeline parallel and not provided)")
+            if self.sharding in ("fsdp", "p_g_os"):
+                self.sharding = "stage3"
+            if self.sharding not in ("stage1", "stage2", "stage3"):
+                raise ValueError("sharding must be '', 'stage1', 'stage2' or 'stage3' (alias fsdp)")
+            if self.sharding == "stage3" and (tp > 1 or pp > 1 or max(self.expert_model_parallel_size, 1) > 1 or sep > 1 or cp > 1):
+                raise ValueError("sharding stage3 shards over the data ranks only: tensor / pipeline / expert / context "
+                                 "parallel degrees must be 1")
             sharding = rest if self.sharding_parallel_size in (-1, 0) else self.sharding_parallel_size
         else:
             sharding = 1 if self.sharding_parallel_size in (-1, 0) else self.sharding_parallel_size

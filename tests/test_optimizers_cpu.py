@@ -134,3 +134,52 @@ def test_trainer_selects_optimizer_variants(tmp_path):
         assert type(tr.optimizer) is cls
         losses = [h["loss"] for h in tr.state.log_history if "loss" in h]
         assert len(losses) == 3 and all(l == l for l in losses)
+
+
+def test_stage3_units_share_one_working_buffer_and_match_the_flat_optimizer():
+    """One process: per-layer units with recompute reproduce the flat optimizer's trajectory on a MoE model; layer parameters
+    are views of ONE buffer of the size of the largest layer; evaluation without a graph gathers too."""
+    from paddleformers_b200.models.configuration import Qwen3MoeConfig
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+    from paddleformers_b200.parallel.fsdp import FullyShardedOptimizer
+
+    ps = _state()
+    cfg = Qwen3MoeConfig(vocab_size=96, hidden_size=32, intermediate_size=48, moe_intermediate_size=16, num_hidden_layers=3,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=8, num_experts=4, num_experts_per_tok=2,
+                         router_aux_loss_coef=0.01, mlp_only_layers=[1])
+    kw = dict(lr=5e-3, weight_decay=0.1, max_grad_norm=1.0, parallel_state=ps)
+
+    def run(make):
+        torch.manual_seed(0)
+        model = MODEL_MAPPING[cfg.model_type](cfg).float().train()
+        opt = make(model)
+        g = torch.Generator().manual_seed(1)
+        losses = []
+        for _ in range(3):
+            for _ in range(2):                                   # two micro-batches per step
+                ids = torch.randint(0, 96, (2, 12), generator=g)
+                out = model(ids, labels=torch.roll(ids, -1, 1))
+                out.loss.backward()
+                opt.accumulate_grads()
+                losses.append(float(out.loss))
+            opt.step()
+        return model, opt, losses
+
+    base, bopt, l0 = run(lambda m: ShardedAdamW(m, **kw))
+    s3m, s3, l1 = run(lambda m: FullyShardedOptimizer(m, **kw))
+    assert l0 == pytest.approx(l1, rel=1e-5, abs=1e-6)
+    ref = dict(base.named_parameters())
+    for n, p in s3m.named_parameters():
+        torch.testing.assert_close(s3.full_tensor(p), ref[n].detach(), rtol=1e-5, atol=1e-6, msg=n)
+    assert len(s3.units) == 3 and s3.root is not None
+    biggest = max(u.numel for u in s3.units)
+    assert s3._pbuf.numel() == biggest
+    ptrs = {p.data_ptr() for u in s3.units for _, p in u.params}
+    lo, hi = s3._pbuf.data_ptr(), s3._pbuf.data_ptr() + biggest * s3._pbuf.element_size()
+    assert all(lo <= x < hi for x in ptrs)
+    # without a graph (evaluation, generation) the layers gather their parameters as well
+    ids = torch.randint(0, 96, (1, 8))
+    with torch.no_grad():
+        got = s3m.eval()(ids, return_logits=True).logits
+        want = base.eval()(ids, return_logits=True).logits
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)

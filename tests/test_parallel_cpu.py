@@ -85,6 +85,7 @@ def _reference(moe, steps, accum):
     ("sharding2_custom_adamw", 2, False, dict(sharding="stage1", gradient_accumulation_steps=1, optim="adamw_custom",
                                               tensorwise_offload_optimizer=True)),
     ("dp2", 2, False, dict(gradient_accumulation_steps=1)),
+    ("stage3_fsdp2", 2, False, dict(sharding="stage3", gradient_accumulation_steps=1)),
     ("ep2", 2, True, dict(expert_model_parallel_size=2, sharding="stage1", gradient_accumulation_steps=1, moe_token_dispatcher_type="alltoall")),
     ("cp2", 2, False, dict(context_parallel_size=2, gradient_accumulation_steps=2)),
     ("cp2_contiguous", 2, False, dict(context_parallel_size=2, cp_balance_mode="contiguous_allgather", gradient_accumulation_steps=2)),
@@ -282,6 +283,31 @@ def test_resume_with_a_different_sharding_degree(tmp_path):
     assert len(got) >= 2
     for a, b in zip(ref[2:], got[-2:]):
         assert abs(a - b) < 3e-4 * max(1.0, abs(a)), (ref, got)
+
+
+def test_stage3_checkpoint_resumes_on_the_same_and_on_another_number_of_ranks(tmp_path):
+    """Parameters, gradients and optimizer state sharded per layer over 2 ranks: the exported weights are whole, and the run
+    resumes from its per-unit slices on 2 ranks and (re-cut) on 1 rank like an uninterrupted single-process run."""
+    from paddleformers_b200.transformers.auto import AutoModelForCausalLM
+
+    full = _reference(False, 4, 2)
+    ref = run_distributed(_train_and_save, 1, dict(gradient_accumulation_steps=2), 4, full, str(tmp_path / "ref"), False)[0]
+    s3 = dict(sharding="stage3", gradient_accumulation_steps=1)
+    run_distributed(_train_and_save, 2, s3, 2, full, str(tmp_path / "run"), False)
+    # the checkpoint's Hugging Face weights equal those of the single-process run at the same step
+    a = AutoModelForCausalLM.from_pretrained(str(tmp_path / "run" / "checkpoint-2"), dtype=torch.float32)
+    b = AutoModelForCausalLM.from_pretrained(str(tmp_path / "ref" / "checkpoint-2"), dtype=torch.float32)
+    for (n, p), (_, q) in zip(a.named_parameters(), b.named_parameters()):
+        torch.testing.assert_close(p, q, rtol=1e-4, atol=1e-5, msg=n)
+    import shutil
+
+    shutil.copytree(str(tmp_path / "run"), str(tmp_path / "run1"))
+    got2 = run_distributed(_train_and_save, 2, s3, 4, full, str(tmp_path / "run"), True)[0]
+    got1 = run_distributed(_train_and_save, 1, dict(sharding="stage3", gradient_accumulation_steps=2), 4, full, str(tmp_path / "run1"), True)[0]
+    for got in (got2, got1):
+        assert len(got) >= 2
+        for x, y in zip(ref[2:], got[-2:]):
+            assert abs(x - y) < 3e-4 * max(1.0, abs(x)), (ref, got)
 
 
 def test_tensor_parallel_checkpoint_loads_in_one_process(tmp_path):
