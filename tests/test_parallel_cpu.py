@@ -310,6 +310,28 @@ def test_stage3_checkpoint_resumes_on_the_same_and_on_another_number_of_ranks(tm
             assert abs(x - y) < 3e-4 * max(1.0, abs(x)), (ref, got)
 
 
+def test_offline_resharding_tool_prepares_a_checkpoint_for_more_ranks(tmp_path):
+    """A checkpoint written by one process is re-cut offline for 2 sharding ranks; they find their own shard files and continue
+    like the uninterrupted run."""
+    from paddleformers_b200.trainer import ckpt_converter as cc
+
+    full = _reference(False, 4, 2)
+    ref = run_distributed(_train_and_save, 1, dict(gradient_accumulation_steps=2), 4, full, str(tmp_path / "ref"), False)[0]
+    run_distributed(_train_and_save, 1, dict(gradient_accumulation_steps=2), 2, full, str(tmp_path / "one"), False)
+    src = str(tmp_path / "one" / "checkpoint-2")
+    info = cc.inspect(src)
+    assert info["complete"] and info["global_step"] == 2 and all(d["shard_size"] == 1 for d in info["optimizer_domains"].values())
+    dst = tmp_path / "two" / "checkpoint-2"
+    files = cc.reshard(src, str(dst), 2)
+    assert len(files) == 2 * len(info["optimizer_domains"]) and all("of002" in f for f in files)
+    after = cc.inspect(str(dst))
+    assert after["complete"] and all(d["shard_size"] == 2 and d["files"] == 2 for d in after["optimizer_domains"].values())
+    assert cc.main(["inspect", str(dst)]) == 0
+    got = run_distributed(_train_and_save, 2, dict(sharding="stage1", gradient_accumulation_steps=1), 4, full, str(tmp_path / "two"), True)[0]
+    for a, b in zip(ref[2:], got[-2:]):
+        assert abs(a - b) < 3e-4 * max(1.0, abs(a)), (ref, got)
+
+
 def test_tensor_parallel_checkpoint_loads_in_one_process(tmp_path):
     """Weights saved by 2 tensor-parallel ranks form one Hugging Face checkpoint that a single process loads."""
     from paddleformers_b200.transformers.auto import AutoModelForCausalLM
