@@ -67,6 +67,9 @@ class KVCache:
         kf = self.k.permute(0, 2, 1, 3).float().repeat_interleave(Hq // Hkv, 1)
         vf = self.v.permute(0, 2, 1, 3).float().repeat_interleave(Hq // Hkv, 1)
         s = qf @ kf.transpose(-1, -2) * attn.scale
+        cap = float(getattr(attn, "softcap", 0.0) or 0.0)
+        if cap:
+            s = torch.tanh(s / cap) * cap
         i = torch.arange(Sk - S, Sk, device=q.device)[:, None]
         j = torch.arange(Sk, device=q.device)[None]
         vis = j <= i

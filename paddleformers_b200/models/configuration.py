@@ -502,11 +502,40 @@ class GemmaConfig(DecoderConfig):
         self.norm_weight_offset = 1.0
 
 
+class Gemma2Config(GemmaConfig):
+    """Gemma 2: Gemma with four norms per block, alternating sliding-window and global layers, a query scale of
+    ``query_pre_attn_scalar ** -0.5`` and soft-capped attention scores and output logits. The flash kernels have no soft cap:
+    attention runs in the eager back-end and the loss outside the fused head kernel (paddleformers/transformers lists the
+    family through its Gemma support)."""
+
+    model_type = "gemma2"
+
+    def __init__(self, sliding_window=4096, layer_types=None, query_pre_attn_scalar=256, attn_logit_softcapping=50.0,
+                 final_logit_softcapping=30.0, **kw):
+        kw.setdefault("max_position_embeddings", 8192)
+        super().__init__(**kw)
+        self.sliding_window = sliding_window
+        n = self.num_hidden_layers
+        self.layer_types = list(layer_types) if layer_types else [
+            "sliding_attention" if i % 2 == 0 else "full_attention" for i in range(n)]
+        self.query_pre_attn_scalar = query_pre_attn_scalar
+        self.attention_multiplier = float(query_pre_attn_scalar) ** -0.5
+        self.attn_logit_softcapping, self.final_logit_softcapping = attn_logit_softcapping, final_logit_softcapping
+        self.block_style = "sandwich"
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if saving:
+            for k in ("attention_multiplier", "block_style"):
+                d.pop(k, None)
+        return d
+
+
 class Gemma3TextConfig(GemmaConfig):
     """Gemma 3 (text): Gemma's (w - 1) norms, GeGLU and scaled embeddings, plus per-head QK norm, four norms per block (the
     branch output is normed before it joins the residual stream), a repeating pattern of sliding-window layers and global
     layers that use different rotary bases, and a query scale of ``query_pre_attn_scalar ** -0.5``
-    (paddleformers/transformers/gemma3_text). Logit soft-capping is not provided (the released text models leave it off)."""
+    (paddleformers/transformers/gemma3_text). Logit soft-capping, when a configuration sets it, takes the eager attention back-end like Gemma 2."""
 
     model_type = "gemma3_text"
 
@@ -521,8 +550,7 @@ class Gemma3TextConfig(GemmaConfig):
         kw.setdefault("use_qk_norm", True)
         kw.setdefault("max_position_embeddings", 131072)
         super().__init__(rope_parameters=rope_parameters, **kw)
-        if final_logit_softcapping or attn_logit_softcapping:
-            raise NotImplementedError("logit soft-capping is not implemented")
+        self.attn_logit_softcapping, self.final_logit_softcapping = attn_logit_softcapping, final_logit_softcapping
         self.sliding_window = sliding_window
         n = self.num_hidden_layers
         self.layer_types = list(layer_types) if layer_types else [
@@ -642,7 +670,7 @@ class Ernie4_5MoeConfig(Ernie4_5Config):
 
 
 CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, MiniCPMConfig, Olmo2Config,
-                                            GemmaConfig, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
+                                            GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
                                             Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config, HunYuanDenseV1Config,
                                             HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config)}
 
@@ -657,7 +685,7 @@ UNSUPPORTED_FAMILIES = {
     "qwen3_5_moe": "gated delta-net linear attention hybrid",
     "gemma3": "SigLIP vision tower (the text decoder is available as gemma3_text)",
     "phi4_multimodal": "vision and audio towers",
-    "gemma2": "soft-capping, sliding / global layer pattern, post norms",
+
 
     "llama4_text": "chunked attention, NoPE layers, shared-expert MoE", "diffllama": "differential attention",
 

@@ -30,7 +30,7 @@ from ..transformers.conversion_utils import Rule, WeightMap, expand_layers
 from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
                             Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig,
-                            GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig,
+                            GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig,
                             HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config)
 
 
@@ -186,6 +186,8 @@ class Attention(nn.Module):
             self.k_norm = RMSNorm(self.D, config.rms_norm_eps, dtype=dtype, device=device)
         self.qk_norm_after_rope = bool(self.use_qk_norm and getattr(config, "qk_norm_after_rope", False))   # Hunyuan
         self.scale = float(getattr(config, "attention_multiplier", None) or 1.0 / math.sqrt(self.D))
+        # soft-capped attention scores are not in the flash kernels: such families run the eager back-end
+        self.softcap = float(getattr(config, "attn_logit_softcapping", None) or 0.0)
         self.window = config.layer_window(layer_idx)
         self.local_rope = bool(self.window and getattr(config, "rope_local_theta", None))
         # families whose global layers carry no positional embedding (Cohere2): only window layers rotate
@@ -211,14 +213,18 @@ class Attention(nn.Module):
             qkv = F.rope_packed(qkv, cos, sin, ctx.positions, self.Hq, self.Hkv, self.D, self.rot)
         if cache is not None:
             out = cache.attend(self, qkv, ctx)
-        elif getattr(self.config, "_attn_implementation", None) in ("eager", "sdpa") and not ctx.S_full:
+        elif (self.softcap or getattr(self.config, "_attn_implementation", None) in ("eager", "sdpa")) and not ctx.S_full:
             from ..nn.attention import AttentionInterface      # reference back-ends, selectable like the reference's
 
             B, S, D = ctx.B, ctx.S, self.D
             q, k, v = qkv.view(B, S, -1).split([self.Hq * D, self.Hkv * D, self.Hkv * D], dim=-1)
-            out = AttentionInterface.get(self.config._attn_implementation)(
-                q.reshape(B, S, self.Hq, D), k.reshape(B, S, self.Hkv, D), v.reshape(B, S, self.Hkv, D), kend, self.scale)
+            impl = "eager" if self.softcap else self.config._attn_implementation
+            extra = {"softcap": self.softcap} if self.softcap else {}
+            out = AttentionInterface.get(impl)(
+                q.reshape(B, S, self.Hq, D), k.reshape(B, S, self.Hkv, D), v.reshape(B, S, self.Hkv, D), kend, self.scale, **extra)
             out = out.reshape(B * S, self.Hq * D)
+        elif self.softcap:
+            raise NotImplementedError("soft-capped attention scores are not combined with context / segment parallelism")
         elif ctx.S_full:
             B, S, D = ctx.B, ctx.S, self.D
             q, k, v = qkv.view(B, S, -1).split([self.Hq * D, self.Hkv * D, self.Hkv * D], dim=-1)
@@ -568,8 +574,13 @@ class DecoderForCausalLM(PretrainedModel):
     def compute_logits(self, hidden2d):
         w = self.head_weight()
         if self.tp > 1 and self.lm_head is not None:
-            return self.lm_head(hidden2d)
-        return F.linear(hidden2d, w)
+            logits = self.lm_head(hidden2d)
+        else:
+            logits = F.linear(hidden2d, w)
+        cap = float(getattr(self.config, "final_logit_softcapping", None) or 0.0)
+        if cap:
+            logits = (torch.tanh(logits.float() / cap) * cap).to(logits.dtype)
+        return logits
 
     def _label_norm(self, count):
         """Number of labelled tokens the loss is divided by. Ranks of a context / segment parallel group hold slices of ONE
@@ -605,6 +616,16 @@ class DecoderForCausalLM(PretrainedModel):
 
     def _loss(self, hidden2d, labels_flat, scale, tokens_complete: bool = False):
         """(scaled loss sum, token count) of the head + cross entropy on hidden states [T, H]."""
+        if getattr(self.config, "final_logit_softcapping", None):
+            # capped logits cannot go through the fused head + loss kernel: head GEMM, cap and cross entropy run as separate
+            # operations, in token chunks so that only a slice of the [tokens, vocabulary] logits is alive at a time
+            assert self.tp == 1, "final logit soft-capping is implemented for tensor-parallel degree 1"
+            total = hidden2d.new_zeros((), dtype=torch.float32)
+            for lo in range(0, hidden2d.shape[0], 2048):
+                lg = self.compute_logits(hidden2d[lo:lo + 2048]).float()
+                total = total + torch.nn.functional.cross_entropy(lg, labels_flat[lo:lo + 2048], ignore_index=self.ignore_index,
+                                                                  reduction="sum")
+            return total * scale, (labels_flat != self.ignore_index).sum()
         if self.tp > 1:
             from ..parallel.vocab_parallel_loss import vocab_parallel_linear_cross_entropy
 
@@ -886,6 +907,7 @@ GraniteForCausalLM = _family("GraniteForCausalLM", GraniteConfig)
 MiniCPMForCausalLM = _family("MiniCPMForCausalLM", MiniCPMConfig)
 Olmo2ForCausalLM = _family("Olmo2ForCausalLM", Olmo2Config)
 GemmaForCausalLM = _family("GemmaForCausalLM", GemmaConfig)
+Gemma2ForCausalLM = _family("Gemma2ForCausalLM", Gemma2Config)
 Gemma3ForCausalLM = _family("Gemma3ForCausalLM", Gemma3TextConfig)
 CohereForCausalLM = _family("CohereForCausalLM", CohereConfig)
 Cohere2ForCausalLM = _family("Cohere2ForCausalLM", Cohere2Config)
@@ -899,7 +921,7 @@ InternLM2ForCausalLM = _family("InternLM2ForCausalLM", InternLM2Config)
 
 MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
-    "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
+    "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma2": Gemma2ForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
     "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,

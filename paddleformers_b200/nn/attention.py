@@ -7,8 +7,9 @@ returns [B, S, Hq, Dv]:
 
 * ``flashmask`` - the tcgen05 flash kernels on the GPU (causal + document masks with tile skipping);
 * ``sdpa``      - ``torch.nn.functional.scaled_dot_product_attention`` with a dense mask rebuilt from the row indices;
-* ``eager``     - matmul + softmax in fp32; the only back-end that supports attention sinks: one learned logit per head
-  that joins the softmax denominator and absorbs probability mass without contributing a value.
+* ``eager``     - matmul + softmax in fp32; the only back-end that supports attention sinks (one learned logit per head
+  that joins the softmax denominator and absorbs probability mass without contributing a value) and soft-capped scores
+  (``softcap * tanh(score / softcap)``).
 """
 from __future__ import annotations
 
@@ -55,11 +56,13 @@ def sdpa_attention(q, k, v, attn_mask_startend_row_indices=None, scale=None, cau
     return out.transpose(1, 2)
 
 
-def eager_attention(q, k, v, attn_mask_startend_row_indices=None, scale=None, causal=True, sinks=None):
+def eager_attention(q, k, v, attn_mask_startend_row_indices=None, scale=None, causal=True, sinks=None, softcap=None):
     B, S, Hq, D = q.shape
     rep = Hq // k.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     s = torch.einsum("bshd,bthd->bhst", q.float(), k.float().repeat_interleave(rep, 2)) * scale
+    if softcap:                                         # Gemma 2: scores squashed into (-cap, cap) before the softmax
+        s = torch.tanh(s / softcap) * softcap
     vis = _dense_mask(_kend(attn_mask_startend_row_indices, B, S), B, S, causal, q.device)[:, None]
     s = s.masked_fill(~vis, float("-inf"))
     if sinks is not None:                               # [Hq] logits: an extra column that takes part in the softmax only

@@ -70,6 +70,8 @@ CASES = {
         v_head_dim=16, routed_scaling_factor=1.0, topk_method="greedy", norm_topk_prob=False)),
     "olmo2": ("Olmo2Config", "Olmo2ForCausalLM", dict()),
     "gemma": ("GemmaConfig", "GemmaForCausalLM", dict(head_dim=16, tie_word_embeddings=True, hidden_activation="gelu_pytorch_tanh")),
+    "gemma2": ("Gemma2Config", "Gemma2ForCausalLM", dict(head_dim=16, num_hidden_layers=4, sliding_window=8, query_pre_attn_scalar=24,
+                                                        attn_logit_softcapping=5.0, final_logit_softcapping=3.0, tie_word_embeddings=True)),
     "gemma3_text": ("Gemma3TextConfig", "Gemma3ForCausalLM", dict(head_dim=16, num_hidden_layers=4, sliding_window=8, query_pre_attn_scalar=24,
                                                                   layer_types=["sliding_attention", "sliding_attention", "full_attention",
                                                                                "sliding_attention"], tie_word_embeddings=True)),
@@ -114,7 +116,7 @@ def test_logits_match_hugging_face_implementation(tmp_path, family):
     torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma3_text", "cohere", "cohere2", "olmo2", "hunyuan_v1_dense", "hunyuan_v1_moe", "minimax_m2", "mixtral", "deepseek_v2",
+@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma2", "gemma3_text", "cohere", "cohere2", "olmo2", "hunyuan_v1_dense", "hunyuan_v1_moe", "minimax_m2", "mixtral", "deepseek_v2",
                                     "stablelm", "granite", "qwen2_moe", "ernie4_5_moe"])
 def test_hugging_face_loads_what_this_framework_saves(tmp_path, family):
     """The other direction: a checkpoint written by ``save_pretrained`` here (per-expert tensors, interleaved rotary rows
@@ -415,3 +417,28 @@ def test_video_processor_patch_layout_and_model_consumes_it():
     out = model(ids, pixel_values_videos=o5["pixel_values_videos"], video_grid_thw=o5["video_grid_thw"], labels=torch.roll(ids, -1, 1))
     out.loss.backward()
     assert torch.isfinite(out.loss) and model.visual.patch_embed.weight.grad.abs().sum() > 0
+
+
+def test_gemma2_capped_loss_and_cached_decoding_match_hugging_face(tmp_path):
+    """Soft-capped scores and logits take the unfused paths: the loss (head, cap, cross entropy in token chunks) and greedy
+    decoding with the key / value cache still agree with ``transformers``."""
+    from paddleformers_b200.generation.utils import GenerationConfig, generate
+
+    torch.manual_seed(2)
+    cfg = transformers.Gemma2Config(**{**BASE, "head_dim": 16, "num_hidden_layers": 2, "sliding_window": 6, "query_pre_attn_scalar": 24,
+                                       "attn_logit_softcapping": 5.0, "final_logit_softcapping": 3.0, "tie_word_embeddings": True})
+    hf = transformers.Gemma2ForCausalLM(cfg).float()
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    mine = AutoModelForCausalLM.from_pretrained(str(tmp_path), dtype=torch.float32)
+    ids = torch.randint(1, 128, (2, 20))
+    labels = torch.cat([ids[:, 1:], torch.full((2, 1), -100)], dim=1)
+    out = mine(ids, labels=labels)
+    want = hf(input_ids=ids, labels=ids)
+    assert out.loss.item() == pytest.approx(want.loss.item(), rel=1e-5)
+    out.loss.backward()
+    want.loss.backward()
+    torch.testing.assert_close(mine.model.embed_tokens.weight.grad, hf.model.embed_tokens.weight.grad, rtol=1e-4, atol=1e-6)
+    mine.eval(); hf.eval()
+    got = generate(mine, ids[:, :8], GenerationConfig(max_new_tokens=6))
+    ref = hf.generate(ids[:, :8], max_new_tokens=6, do_sample=False, pad_token_id=0)
+    assert torch.equal(got, ref[:, :got.shape[1]])
