@@ -77,6 +77,11 @@ class KVCache:
         if w:
             vis = vis & (i - j < w)           # sliding-window layer: only the last ``w`` keys
         s = s.masked_fill(~vis[None, None], float("-inf"))
+        sinks = getattr(attn, "sinks", None)
+        if sinks is not None:             # one extra logit per head in the softmax denominator
+            sink = sinks.float().view(1, -1, 1, 1).expand(s.shape[0], -1, s.shape[2], 1)
+            o = torch.softmax(torch.cat([s, sink], -1), -1)[..., :-1] @ vf
+            return o.permute(0, 2, 1, 3).reshape(B * S, Hq * D).to(qkv2d.dtype)
         o = torch.softmax(s, -1) @ vf
         return o.permute(0, 2, 1, 3).reshape(B * S, Hq * D).to(qkv2d.dtype)
 

@@ -356,6 +356,49 @@ class MixtralConfig(DecoderConfig):
         return d
 
 
+class GptOssConfig(DecoderConfig):
+    """gpt-oss: attention with one learned sink logit per head, biases on all attention projections, alternating
+    sliding-window and global layers, yarn rotary scaling; every layer routes with a biased router whose combine weights are a
+    softmax over the selected logits, to experts with biases and a clamped gate (paddleformers/transformers/gpt_oss). Sinks
+    and biased experts have no fused kernels here: attention runs in the eager back-end, the experts in tensor operations."""
+
+    model_type = "gpt_oss"
+
+    def __init__(self, sliding_window=128, layer_types=None, swiglu_limit=7.0, **kw):
+        kw.setdefault("attention_bias", True)
+        kw.setdefault("num_experts_per_tok", 4)
+        kw.setdefault("rms_norm_eps", 1e-5)
+        kw.setdefault("rope_theta", 150000.0)
+        kw.setdefault("head_dim", 64)
+        kw.setdefault("router_aux_loss_coef", 0.9)
+        kw["scoring_func"] = "softmax_topk"
+        super().__init__(**kw)
+        self.sliding_window = sliding_window
+        n = self.num_hidden_layers
+        self.layer_types = list(layer_types) if layer_types else [
+            "sliding_attention" if i % 2 == 0 else "full_attention" for i in range(n)]
+        self.swiglu_limit = swiglu_limit
+        self.attention_out_bias = True
+        self.attention_sinks = True
+        self.router_bias = True
+        self.expert_bias = True
+        self.hf_experts_style = "gpt_oss"
+        self.moe_intermediate_size = self.moe_intermediate_size or self.intermediate_size
+        self.moe_token_dispatcher_type = "alltoall"
+        self.num_local_experts = self.num_experts
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if saving:
+            d["num_local_experts"] = self.num_experts
+            d.pop("num_experts", None)
+            rp = {"rope_type": "default", **(self.rope_scaling or {}), "rope_theta": self.rope_theta}
+            d["rope_parameters"] = rp
+            for k in ("rope_theta", "rope_scaling", "scoring_func", "attention_sinks", "router_bias", "expert_bias", "hf_experts_style"):
+                d.pop(k, None)
+        return d
+
+
 class MiniMaxM2Config(DecoderConfig):
     """MiniMax-M2: one RMSNorm over all heads' query / key features before the rotary embedding, every layer a sigmoid
     router with a selection-only correction bias and renormalised top-k weights, experts of the dense width, no shared
@@ -672,12 +715,11 @@ class Ernie4_5MoeConfig(Ernie4_5Config):
 CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, MiniCPMConfig, Olmo2Config,
                                             GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
                                             Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config, HunYuanDenseV1Config,
-                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config)}
+                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig)}
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
 # feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
 UNSUPPORTED_FAMILIES = {
-    "gpt_oss": "attention sinks, clamped SwiGLU with expert biases, mxfp4 expert checkpoints (dequantiser: quantization.checkpoint_dequant)",
     "deepseek_v32": "sparse (indexer) attention", "deepseek_v4": "compressed sparse attention",
     "glm_moe_dsa": "sparse (indexer) attention",
     "minimax": "lightning (linear) attention hybrid",

@@ -31,7 +31,7 @@ from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
                             Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig,
                             GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig,
-                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config)
+                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig)
 
 
 @dataclass
@@ -186,8 +186,11 @@ class Attention(nn.Module):
             self.k_norm = RMSNorm(self.D, config.rms_norm_eps, dtype=dtype, device=device)
         self.qk_norm_after_rope = bool(self.use_qk_norm and getattr(config, "qk_norm_after_rope", False))   # Hunyuan
         self.scale = float(getattr(config, "attention_multiplier", None) or 1.0 / math.sqrt(self.D))
-        # soft-capped attention scores are not in the flash kernels: such families run the eager back-end
+        # soft-capped attention scores and attention sinks are not in the flash kernels: such families run the eager back-end
         self.softcap = float(getattr(config, "attn_logit_softcapping", None) or 0.0)
+        self.sinks = nn.Parameter(torch.zeros(self.Hq, dtype=dtype, device=device)) if getattr(config, "attention_sinks", False) else None
+        if self.sinks is not None and tp > 1:
+            self.sinks.shard_spec = ("tp", 0, None)
         self.window = config.layer_window(layer_idx)
         self.local_rope = bool(self.window and getattr(config, "rope_local_theta", None))
         # families whose global layers carry no positional embedding (Cohere2): only window layers rotate
@@ -213,18 +216,21 @@ class Attention(nn.Module):
             qkv = F.rope_packed(qkv, cos, sin, ctx.positions, self.Hq, self.Hkv, self.D, self.rot)
         if cache is not None:
             out = cache.attend(self, qkv, ctx)
-        elif (self.softcap or getattr(self.config, "_attn_implementation", None) in ("eager", "sdpa")) and not ctx.S_full:
+        elif (self.softcap or self.sinks is not None or getattr(self.config, "_attn_implementation", None) in ("eager", "sdpa")) \
+                and not ctx.S_full:
             from ..nn.attention import AttentionInterface      # reference back-ends, selectable like the reference's
 
             B, S, D = ctx.B, ctx.S, self.D
             q, k, v = qkv.view(B, S, -1).split([self.Hq * D, self.Hkv * D, self.Hkv * D], dim=-1)
-            impl = "eager" if self.softcap else self.config._attn_implementation
+            impl = "eager" if (self.softcap or self.sinks is not None) else self.config._attn_implementation
             extra = {"softcap": self.softcap} if self.softcap else {}
+            if self.sinks is not None:
+                extra["sinks"] = self.sinks
             out = AttentionInterface.get(impl)(
                 q.reshape(B, S, self.Hq, D), k.reshape(B, S, self.Hkv, D), v.reshape(B, S, self.Hkv, D), kend, self.scale, **extra)
             out = out.reshape(B * S, self.Hq * D)
-        elif self.softcap:
-            raise NotImplementedError("soft-capped attention scores are not combined with context / segment parallelism")
+        elif self.softcap or self.sinks is not None:
+            raise NotImplementedError("soft-capped scores / attention sinks are not combined with context / segment parallelism")
         elif ctx.S_full:
             B, S, D = ctx.B, ctx.S, self.D
             q, k, v = qkv.view(B, S, -1).split([self.Hq * D, self.Hkv * D, self.Hkv * D], dim=-1)
@@ -802,6 +808,24 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
             # the three expert projections (gate, up, down)
             src = f"model.layers.{i}." + (getattr(config, "moe_block_hf_name", None) or "mlp") + "."
             g_n, u_n, d_n = getattr(config, "expert_proj_hf_names", None) or ("gate_proj", "up_proj", "down_proj")
+            if getattr(config, "hf_experts_style", None) == "gpt_oss":
+                # stacked [E, H, 2I] with gate / up columns interleaved, [E, I, H], and biases; router under "router"
+                def split_cols(t):        # [..., 2I] interleaved -> [gate | up]
+                    return torch.cat([t[..., 0::2], t[..., 1::2]], dim=-1)
+
+                def join_cols(t):
+                    g, u = t.chunk(2, dim=-1)
+                    return torch.stack([g, u], dim=-1).flatten(-2)
+
+                rules.append(Rule(pre + "experts.gate_up_proj", [src + "experts.gate_up_proj"],
+                                  fn=(lambda t: split_cols(t).transpose(1, 2).contiguous(), lambda t: join_cols(t.transpose(1, 2)).contiguous())))
+                rules.append(Rule(pre + "experts.gate_up_bias", [src + "experts.gate_up_proj_bias"], fn=(split_cols, join_cols)))
+                rules.append(Rule(pre + "experts.down_proj", [src + "experts.down_proj"],
+                                  fn=(lambda t: t.transpose(1, 2).contiguous(), lambda t: t.transpose(1, 2).contiguous())))
+                rules.append(Rule(pre + "experts.down_bias", [src + "experts.down_proj_bias"]))
+                rules.append(Rule(pre + "gate.weight", [src + "router.weight"]))
+                rules.append(Rule(pre + "gate.bias", [src + "router.bias"]))
+                continue
             if getattr(config, "hf_fused_experts", False):     # the checkpoint stores the stacked [E, 2I, H] / [E, H, I] tensors
                 rules.append(Rule(pre + "experts.gate_up_proj", [src + "experts.gate_up_proj"]))
                 rules.append(Rule(pre + "experts.down_proj", [src + "experts.down_proj"]))
@@ -918,11 +942,12 @@ MiniMaxM2ForCausalLM = _family("MiniMaxM2ForCausalLM", MiniMaxM2Config)
 MixtralForCausalLM = _family("MixtralForCausalLM", MixtralConfig)
 MiniCPM3ForCausalLM = _family("MiniCPM3ForCausalLM", MiniCPM3Config)
 InternLM2ForCausalLM = _family("InternLM2ForCausalLM", InternLM2Config)
+GptOssForCausalLM = _family("GptOssForCausalLM", GptOssConfig)
 
 MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
     "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma2": Gemma2ForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
-    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
+    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "gpt_oss": GptOssForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,
 }

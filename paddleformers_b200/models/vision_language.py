@@ -661,7 +661,7 @@ class Qwen3VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
         for r in build_weight_map(self.config.text_config).rules.values():
             src = [s if s.startswith("lm_head.") else s.replace("model.", "model.language_model.", 1) for s in r.sources]
             rules.append(Rule("language." + r.target, src, r.op, r.dim, r.num_experts, r.expert_pairs, r.sizes, r.rope_deinterleave,
-                              r.flatten, r.reshape, r.source_shape, r.offset, r.qkv_groups))
+                              r.flatten, r.reshape, r.source_shape, r.offset, fn=r.fn, qkv_groups=r.qkv_groups))
         known = {r.target for r in rules}
         for name, _ in self.language.named_parameters():
             if "language." + name not in known:

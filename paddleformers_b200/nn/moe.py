@@ -87,6 +87,11 @@ class TopkRouter(nn.Module):
         # the router runs in fp32 like the reference's gate (weights kept fp32 regardless of the model dtype)
         self.weight = nn.Parameter(torch.empty(self.num_experts, config.hidden_size, dtype=torch.float32, device=device))
         self.weight.keep_fp32 = True
+        # gpt-oss: the router has a bias and the combine weights are a softmax over the k selected LOGITS
+        self.bias = nn.Parameter(torch.zeros(self.num_experts, dtype=torch.float32, device=device)) \
+            if getattr(config, "router_bias", False) else None
+        if self.bias is not None:
+            self.bias.keep_fp32 = True
         if self.method == "noaux_tc":
             self.register_buffer("e_score_correction_bias", torch.zeros(self.num_experts, dtype=torch.float32, device=device))
         else:
@@ -96,6 +101,21 @@ class TopkRouter(nn.Module):
     def forward(self, x2d: torch.Tensor):
         """x2d: [T, H] -> (topk_idx [T,k] int64, topk_weight [T,k] fp32, aux_loss scalar or None)."""
         logits = F.router_logits(x2d, self.weight)
+        if self.bias is not None:
+            logits = logits + self.bias
+        if self.scoring == "softmax_topk":
+            top, idx = logits.topk(self.top_k, dim=-1)
+            w = torch.softmax(top, dim=-1) * self.scale
+            with torch.no_grad():
+                self.expert_usage.scatter_add_(0, idx.reshape(-1), torch.ones_like(idx.reshape(-1)))
+            aux = None
+            if self.training and self.aux_coef > 0 and self.balance_type != "none":
+                T, E = logits.shape
+                probs = torch.softmax(logits, dim=-1)
+                frac = torch.zeros(E, dtype=torch.float32, device=x2d.device).scatter_add_(
+                    0, idx.reshape(-1), torch.ones(idx.numel(), dtype=torch.float32, device=x2d.device)) / max(T, 1)
+                aux = self.aux_coef * E * (frac * probs.mean(0)).sum()
+            return idx, w, aux
         if self.scoring == "sigmoid":
             scores = torch.sigmoid(logits)
         else:
@@ -287,6 +307,39 @@ class GroupedExperts(nn.Module):
         return out
 
 
+class BiasedGluExperts(GroupedExperts):
+    """Experts with biases on both projections and gpt-oss's clamped gate: gate <= limit, |up| <= limit,
+    out = (up + 1) * gate * sigmoid(alpha * gate). The grouped tcgen05 kernels fuse plain SwiGLU without biases, so these
+    experts run block by block in tensor operations on every device: functional support, not a tuned path."""
+
+    def __init__(self, config, dtype=None, device=None):
+        super().__init__(config, dtype=dtype, device=device)
+        self.gate_up_bias = nn.Parameter(torch.zeros(self.num_local, 2 * self.inter, dtype=dtype, device=device))
+        self.down_bias = nn.Parameter(torch.zeros(self.num_local, self.hidden, dtype=dtype, device=device))
+        for p in (self.gate_up_bias, self.down_bias):
+            p.is_expert = True
+            p.shard_spec = ("ep", 0, None)
+        self.alpha = float(getattr(config, "glu_alpha", 1.702))
+        self.limit = float(getattr(config, "swiglu_limit", 7.0))
+        self.use_fp8 = False
+
+    def forward(self, rows, block_expert, counts=None, out=None, expert_rows=None, grad_rows_out=None):
+        if out is not None or grad_rows_out is not None:
+            raise NotImplementedError("experts with biases take the all-to-all dispatcher (moe_token_dispatcher_type: alltoall)")
+        pieces = []
+        for b, e in enumerate(block_expert.tolist()):
+            seg = rows[b * 128:(b + 1) * 128]
+            if e < 0:
+                pieces.append(torch.zeros_like(seg))
+                continue
+            gu = TF.linear(seg, self.gate_up_proj[e], self.gate_up_bias[e])
+            g, u = gu.chunk(2, -1)
+            g = g.clamp(max=self.limit)
+            u = u.clamp(min=-self.limit, max=self.limit)
+            pieces.append(TF.linear((u + 1) * g * torch.sigmoid(g * self.alpha), self.down_proj[e], self.down_bias[e]))
+        return torch.cat(pieces, dim=0) if pieces else torch.zeros_like(rows)
+
+
 class _GroupedMlpFn(torch.autograd.Function):
     """Two grouped tcgen05 GEMMs with the SwiGLU in the first epilogue. The backward runs grouped dgrad GEMMs and
     per-expert wgrad GEMMs accumulating into fp32 ``main_grad`` when present."""
@@ -466,7 +519,8 @@ class MoELayer(nn.Module):
         super().__init__()
         self.config = config
         self.gate = TopkRouter(config, dtype=dtype, device=device)
-        self.experts = GroupedExperts(config, dtype=dtype, device=device)
+        experts_cls = BiasedGluExperts if getattr(config, "expert_bias", False) else GroupedExperts
+        self.experts = experts_cls(config, dtype=dtype, device=device)
         self.shared_experts = None
         if config.n_shared_experts:
             si = config.shared_expert_intermediate_size or config.moe_intermediate_size * config.n_shared_experts

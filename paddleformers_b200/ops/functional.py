@@ -402,8 +402,10 @@ def rope_tables(positions_max: int, rot_dim: int, theta: float, device, scaling:
             def corr_dim(n_rot):
                 return (rot_dim * math.log(old / (n_rot * 2 * math.pi))) / (2 * math.log(theta))
 
-            lo = max(math.floor(corr_dim(beta_fast)), 0)
-            hi = min(math.ceil(corr_dim(beta_slow)), rot_dim - 1)
+            lo, hi = corr_dim(beta_fast), corr_dim(beta_slow)
+            if scaling.get("truncate", True):          # some families keep the fractional correction range
+                lo, hi = math.floor(lo), math.ceil(hi)
+            lo, hi = max(lo, 0), min(hi, rot_dim - 1)
             ramp = ((torch.arange(rot_dim // 2, dtype=torch.float64) - lo) / max(hi - lo, 1e-3)).clamp(0, 1)
             mask = 1 - ramp
             inv_freq = inv_freq / factor * (1 - mask) + inv_freq * mask

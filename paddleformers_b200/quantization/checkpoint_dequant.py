@@ -150,6 +150,29 @@ def upcast_from_mxfp(values: torch.Tensor, scales: torch.Tensor, fmt: str = "mxf
     raise ValueError(f"unknown micro-scaled format {fmt!r} (mxfp4, mxfp8)")
 
 
+class MXFP4Reader:
+    """Checkpoint reader view for MXFP4 checkpoints (gpt-oss): a tensor stored as ``<name>_blocks`` (uint8
+    [..., rows, groups, 16]) with ``<name>_scales`` ([..., rows, groups]) appears under ``<name>`` as the de-quantised bf16
+    tensor. The quantised axis is the input dimension of each projection and is stored last, while the unquantised format
+    of these tensors is [experts, in, out]: the de-quantised tensor is therefore transposed to that layout
+    (paddleformers/quantization/checkpoint_dequant.py:295-355)."""
+
+    def __init__(self, reader):
+        self.reader = reader
+
+    def __getattr__(self, name):
+        return getattr(self.reader, name)
+
+    def has(self, name: str) -> bool:
+        return self.reader.has(name) or (self.reader.has(name + "_blocks") and self.reader.has(name + "_scales"))
+
+    def get(self, name: str) -> torch.Tensor:
+        if self.reader.has(name):
+            return self.reader.get(name)
+        full = dequant_mxfp4(self.reader.get(name + "_blocks"), self.reader.get(name + "_scales"))   # [..., rows, in]
+        return full.transpose(-1, -2).contiguous() if full.dim() >= 3 else full
+
+
 def build_dequantizer(quantization_config, reader) -> Optional[Callable[[str, torch.Tensor], torch.Tensor]]:
     """Returns ``f(name, tensor) -> tensor`` applied to every tensor read from the checkpoint."""
     qc = quantization_config if isinstance(quantization_config, dict) else getattr(quantization_config, "__dict__", {})

@@ -126,6 +126,8 @@ class Rule:
     reshape: Optional[List[int]] = None        # rename: shape of the internal parameter (e.g. a Conv3d kernel used as a matrix)
     source_shape: Optional[List[int]] = None   # rename: shape of the tensor in the checkpoint, for the way back
     offset: float = 0.0                        # rename: internal = checkpoint + offset ((1 + w) norm weights)
+    fn: Optional[Tuple[Callable, Callable]] = None      # rename: (checkpoint -> internal, internal -> checkpoint) for layouts
+    #                                                     that no declarative field covers
     qkv_groups: Optional[Tuple[int, int, int]] = None   # rename: (kv heads, q heads per kv head, head dim) of a checkpoint that
     #                                                     stores the fused projection grouped by kv head: [q.. q k v] per group
 
@@ -149,6 +151,8 @@ class Rule:
             t = self._load(0, get(self.sources[0]))
             if self.qkv_groups is not None:
                 t = ungroup_qkv_rows(t, *self.qkv_groups)
+            if self.fn is not None:
+                t = self.fn[0](t)
             if self.offset:
                 t = t + self.offset
             if self.reshape is not None:
@@ -168,6 +172,8 @@ class Rule:
             t = self._store(0, tensor)
             if self.qkv_groups is not None:
                 t = group_qkv_rows(t, *self.qkv_groups)
+            if self.fn is not None:
+                t = self.fn[1](t)
             if self.offset:
                 t = t - self.offset
             if self.source_shape is not None:
@@ -211,5 +217,5 @@ def expand_layers(template_rules: List[Rule], layer_ids: Iterable[int]) -> List[
         for r in template_rules:
             out.append(Rule(r.target.replace("{L}", str(i)), [s.replace("{L}", str(i)) for s in r.sources], r.op, r.dim,
                             r.num_experts, r.expert_pairs, r.sizes, r.rope_deinterleave, r.flatten, r.reshape, r.source_shape, r.offset,
-                            r.qkv_groups))
+                            r.fn, r.qkv_groups))
     return out

@@ -164,6 +164,11 @@ class PretrainedModel(nn.Module):
             from ..quantization.checkpoint_dequant import build_dequantizer
 
             dequant = build_dequantizer(qcfg, reader)
+            qc = qcfg if isinstance(qcfg, dict) else getattr(qcfg, "__dict__", {})
+            if qc.get("quant_method") == "mxfp4":
+                from ..quantization.checkpoint_dequant import MXFP4Reader
+
+                reader = MXFP4Reader(reader)          # "<name>" is served from "<name>_blocks" + "<name>_scales"
         missing, loaded = [], 0
         tied = bool(getattr(self.config, "tie_word_embeddings", False))
 

@@ -83,6 +83,10 @@ CASES = {
         "rope_type": "dynamic", "alpha": 50.0, "factor": 1.0, "rope_theta": 10000.0})),
     "hunyuan_v1_moe": ("HunYuanMoEV1Config", "HunYuanMoEV1ForCausalLM", dict(head_dim=16, num_experts=4, moe_topk=2)),
     "minimax_m2": ("MiniMaxM2Config", "MiniMaxM2ForCausalLM", dict(head_dim=16, num_local_experts=4, num_experts_per_tok=2)),
+    "gpt_oss": ("GptOssConfig", "GptOssForCausalLM", dict(
+        head_dim=16, intermediate_size=48, num_hidden_layers=4, num_local_experts=4, num_experts_per_tok=2, sliding_window=8,
+        rope_parameters={"rope_type": "yarn", "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0, "truncate": False,
+                         "original_max_position_embeddings": 32, "rope_theta": 10000.0})),
     "mixtral": ("MixtralConfig", "MixtralForCausalLM", dict(num_local_experts=4, num_experts_per_tok=2, sliding_window=8)),
     "stablelm": ("StableLmConfig", "StableLmForCausalLM", dict(use_qkv_bias=True, partial_rotary_factor=0.25)),
     "glm4_moe": ("Glm4MoeConfig", "Glm4MoeForCausalLM", dict(head_dim=16, moe_intermediate_size=32, n_routed_experts=4, num_experts_per_tok=2,
@@ -102,7 +106,7 @@ def test_logits_match_hugging_face_implementation(tmp_path, family):
     hf = getattr(transformers, cls_name)(hf_cfg).eval().float()
     with torch.no_grad():
         for n, p in hf.named_parameters():          # non-trivial values everywhere (norm weights, router biases)
-            if p.dim() == 1:
+            if p.dim() == 1 or n.endswith("bias"):
                 p.normal_(1.0 if "norm" in n else 0.0, 0.1)
         for n, b in hf.named_buffers():
             if "e_score_correction_bias" in n:
@@ -116,7 +120,7 @@ def test_logits_match_hugging_face_implementation(tmp_path, family):
     torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma2", "gemma3_text", "cohere", "cohere2", "olmo2", "hunyuan_v1_dense", "hunyuan_v1_moe", "minimax_m2", "mixtral", "deepseek_v2",
+@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma2", "gemma3_text", "cohere", "cohere2", "olmo2", "hunyuan_v1_dense", "hunyuan_v1_moe", "minimax_m2", "mixtral", "deepseek_v2", "gpt_oss",
                                     "stablelm", "granite", "qwen2_moe", "ernie4_5_moe"])
 def test_hugging_face_loads_what_this_framework_saves(tmp_path, family):
     """The other direction: a checkpoint written by ``save_pretrained`` here (per-expert tensors, interleaved rotary rows
@@ -442,3 +446,43 @@ def test_gemma2_capped_loss_and_cached_decoding_match_hugging_face(tmp_path):
     got = generate(mine, ids[:, :8], GenerationConfig(max_new_tokens=6))
     ref = hf.generate(ids[:, :8], max_new_tokens=6, do_sample=False, pad_token_id=0)
     assert torch.equal(got, ref[:, :got.shape[1]])
+
+
+def test_gpt_oss_mxfp4_checkpoint_loads_through_the_virtual_tensors(tmp_path):
+    """The released gpt-oss checkpoints keep the expert matrices as MXFP4 blocks + scales. A Hugging Face model whose expert
+    weights are exactly representable in MXFP4 is rewritten into that format; loading it must reproduce the logits."""
+    import json
+
+    from safetensors.torch import load_file, save_file
+
+    from paddleformers_b200.quantization.checkpoint_dequant import dequant_mxfp4, quant_mxfp4
+
+    torch.manual_seed(4)
+    cfg = transformers.GptOssConfig(**{**BASE, "head_dim": 16, "intermediate_size": 32, "num_hidden_layers": 2, "num_local_experts": 4,
+                                       "num_experts_per_tok": 2, "sliding_window": 8,
+                                       "rope_parameters": {"rope_type": "default", "rope_theta": 10000.0}})
+    hf = transformers.GptOssForCausalLM(cfg).eval().float()
+    with torch.no_grad():                       # snap the expert matrices onto the MXFP4 grid (quantised along the input dimension)
+        for n, p in hf.named_parameters():
+            if n.endswith("experts.gate_up_proj") or n.endswith("experts.down_proj"):
+                t = (p * 8).transpose(1, 2).contiguous()                         # [E, out, in]
+                p.copy_(dequant_mxfp4(*quant_mxfp4(t), torch.float32).transpose(1, 2))
+    hf.save_pretrained(str(tmp_path / "plain"), safe_serialization=True)
+    sd = load_file(str(tmp_path / "plain" / "model.safetensors"))
+    out = {}
+    for k, v in sd.items():
+        if k.endswith("experts.gate_up_proj") or k.endswith("experts.down_proj"):
+            blocks, scales = quant_mxfp4(v.float().transpose(1, 2).contiguous())
+            out[k + "_blocks"], out[k + "_scales"] = blocks, scales
+        else:
+            out[k] = v
+    q = tmp_path / "mxfp4"
+    q.mkdir()
+    save_file({k: v.contiguous() for k, v in out.items()}, str(q / "model.safetensors"), metadata={"format": "pt"})
+    conf = json.loads((tmp_path / "plain" / "config.json").read_text())
+    conf["quantization_config"] = {"quant_method": "mxfp4", "modules_to_not_convert": ["model.layers.*.self_attn", "lm_head"]}
+    (q / "config.json").write_text(json.dumps(conf))
+    mine = AutoModelForCausalLM.from_pretrained(str(q), dtype=torch.float32).eval()
+    ids = torch.randint(0, 128, (2, 20))
+    with torch.no_grad():
+        torch.testing.assert_close(mine(ids, return_logits=True).logits, hf(input_ids=ids).logits, rtol=2e-4, atol=2e-4)

@@ -408,3 +408,26 @@ def test_sequence_level_balance_loss_is_the_mean_of_per_sequence_losses():
     (out[0] if isinstance(out, tuple) else out.loss).backward()
     gate = model.model.layers["0"].mlp.gate
     assert gate.tokens_per_seq == 12 and gate.weight.grad.abs().sum() > 0
+
+
+def test_gpt_oss_trains_sinks_router_bias_and_expert_biases():
+    from paddleformers_b200.generation.utils import GenerationConfig, generate
+
+    cfg = AutoConfig.for_model("gpt_oss", **{**TINY, "num_hidden_layers": 2, "num_local_experts": 4, "num_experts_per_tok": 2,
+                                            "intermediate_size": 24, "sliding_window": 6, "router_aux_loss_coef": 0.01})
+    assert [cfg.layer_window(i) for i in range(2)] == [6, 0] and cfg.scoring_func == "softmax_topk"
+    torch.manual_seed(0)
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32).train()
+    ids = torch.randint(0, 96, (2, 14))
+    out = model(ids, labels=torch.roll(ids, -1, 1))
+    out.loss.backward()
+    layer = model.model.layers["0"]
+    for p in (layer.self_attn.sinks, layer.mlp.gate.bias, layer.mlp.experts.gate_up_bias, layer.mlp.experts.down_bias,
+              layer.mlp.experts.gate_up_proj, layer.self_attn.o_proj.bias):
+        assert p.grad is not None and p.grad.abs().sum() > 0
+    assert out.aux_loss is not None
+    model.eval()
+    with torch.no_grad():
+        seq = generate(model, ids[:, :8], GenerationConfig(max_new_tokens=4))
+        again = model(seq[:, :-1], return_logits=True).logits
+    assert torch.equal(again[:, 7:].argmax(-1), seq[:, 8:])          # cached decoding applies sinks and windows too
