@@ -100,7 +100,7 @@ class DecoderConfig(PretrainedConfig):
             return 0
         types = getattr(self, "layer_types", None)
         if types:
-            return w if types[layer_idx] == "sliding_attention" else 0
+            return w if (layer_idx < len(types) and types[layer_idx] == "sliding_attention") else 0
         if getattr(self, "use_sliding_window", None) is not None:
             return w if (self.use_sliding_window and layer_idx >= int(getattr(self, "max_window_layers", 0) or 0)) else 0
         return w

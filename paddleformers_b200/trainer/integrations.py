@@ -169,6 +169,10 @@ def callbacks_from_args(args) -> List[TrainerCallback]:
         out.append(HealthMonitorCallback(getattr(args, "internal_medicine_monitors", None) or "all",
                                          int(args.internal_medicine_monitor_interval),
                                          log_dir=getattr(args, "logging_dir", None) or os.path.join(args.output_dir, "runs")))
+    if getattr(args, "flash_device_path", None):
+        from ..utils.ckpt_mirror import MirrorCallback
+
+        out.append(MirrorCallback(args.flash_device_path))
     if getattr(args, "enable_timer", False):
         out.append(TimerCallback())
     if getattr(args, "log_memory", False):

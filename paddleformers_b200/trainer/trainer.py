@@ -318,6 +318,14 @@ class Trainer:
 
         resume = resume_from_checkpoint if resume_from_checkpoint is not None else a.resume_from_checkpoint
         if resume is True or resume == "auto":
+            if getattr(a, "flash_device_path", None):
+                # newest checkpoint that verifies, the fast device first; rank 0 copies it under output_dir if it is not there
+                from ..utils.ckpt_mirror import restore_latest
+
+                if a.process_index == 0:
+                    restore_latest([a.flash_device_path, a.output_dir], a.output_dir)
+                if dist.is_initialized() and dist.get_world_size() > 1:
+                    dist.barrier()
             resume = get_last_checkpoint(a.output_dir)
         if resume:
             self._load_from_checkpoint(resume)

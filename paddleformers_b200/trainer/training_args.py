@@ -99,6 +99,8 @@ class TrainingArguments:
     internal_medicine_monitor_interval: int = 0       # sample the monitors every N steps (0 = off)
     metrics_output_path: Optional[str] = None
     resume_from_checkpoint: Optional[str] = None
+    flash_device_path: Optional[str] = None     # fast local device: every checkpoint is mirrored there (verified copy, newest
+    #                                             kept) and resume_from_checkpoint=auto looks there first
     save_checkpoint_format: str = field(default="sharded", metadata={"help": "sharded | unified | hf"})
     load_checkpoint_format: str = "sharded"
     async_save: bool = False

@@ -110,3 +110,75 @@ def test_nonfinite_loss_raises_named_error(tmp_path):
                  train_dataset=SyntheticCausalLMDataset(64, 16, 8))
     with pytest.raises(FloatingPointError, match="LOSS_NAN_ERROR"):
         tr.train()
+
+
+def test_checkpoint_mirror_verifies_copies_and_restores_the_newest_good_one(tmp_path):
+    import json
+    import os
+
+    import torch
+
+    from paddleformers_b200.utils import ckpt_mirror as cm
+
+    def make(root, step, payload):
+        d = root / f"checkpoint-{step}"
+        (d / "optimizer").mkdir(parents=True)
+        torch.save({"x": torch.full((64,), payload)}, d / "optimizer" / "shard.pt")
+        (d / "trainer_state.json").write_text(json.dumps({"global_step": step}))
+        return d
+
+    store, fast, local = tmp_path / "store", tmp_path / "fast", tmp_path / "local"
+    c2, c4 = make(store, 2, 2.0), make(store, 4, 4.0)
+    assert cm.verify(str(c2))[0] is cm.MirrorStatus.CHECKSUM_MISSING
+    cm.write_manifest(str(c2)); cm.write_manifest(str(c4))
+    assert cm.verify(str(c4)) == (cm.MirrorStatus.SUCCESS, [])
+    # the fast device keeps the newest verified copy only
+    assert cm.backup_to_fast_device(str(c2), str(fast)) is cm.MirrorStatus.SUCCESS
+    assert cm.backup_to_fast_device(str(c4), str(fast)) is cm.MirrorStatus.SUCCESS
+    assert [s for s, _ in cm.list_checkpoints(str(fast))] == [4] and not os.path.exists(str(fast / "checkpoint-4.incoming"))
+    # a corrupted source is refused and leaves no checkpoint behind (the copy is set aside)
+    with open(c2 / "optimizer" / "shard.pt", "r+b") as f:
+        f.seek(200); f.write(b"\\x00\\x01\\x02\\x03")
+    st, problems = cm.verify(str(c2))
+    assert st is cm.MirrorStatus.CHECKSUM_MISMATCH and "digest differs" in problems[0]
+    assert cm.mirror(str(c2), str(tmp_path / "bad" / "checkpoint-2")) is cm.MirrorStatus.CHECKSUM_MISMATCH
+    assert not os.path.exists(tmp_path / "bad" / "checkpoint-2") and os.path.exists(tmp_path / "bad" / "checkpoint-2.failed")
+    # restore: the fast device's copy of step 4 wins; if it is damaged the persistent copy is taken; step 2 is never chosen
+    st, path = cm.restore_latest([str(fast), str(store)], str(local))
+    assert st is cm.MirrorStatus.SUCCESS and path == str(local / "checkpoint-4")
+    assert torch.load(local / "checkpoint-4" / "optimizer" / "shard.pt")["x"][0] == 4.0
+    os.remove(fast / "checkpoint-4" / "trainer_state.json")
+    import shutil
+    shutil.rmtree(local)
+    st, path = cm.restore_latest([str(fast), str(store)], str(local))
+    assert st is cm.MirrorStatus.SUCCESS and cm.verify(path)[0] is cm.MirrorStatus.SUCCESS
+    shutil.rmtree(store / "checkpoint-4"); shutil.rmtree(fast)
+    assert cm.restore_latest([str(fast), str(store)], str(tmp_path / "none")) == (cm.MirrorStatus.NOTHING_TO_RESTORE, None)
+
+
+def test_trainer_mirrors_checkpoints_to_the_fast_device_and_resumes_from_it(tmp_path):
+    import shutil
+
+    import torch
+
+    from paddleformers_b200 import AutoModelForCausalLM, Trainer, TrainingArguments
+    from paddleformers_b200.data.synthetic import SyntheticCausalLMDataset
+    from paddleformers_b200.models.configuration import named_config
+    from paddleformers_b200.utils import ckpt_mirror as cm
+
+    def run(steps):
+        torch.manual_seed(0)
+        model = AutoModelForCausalLM.from_config(named_config("tiny-llama", vocab_size=128, hidden_size=32, intermediate_size=48,
+                                                              num_attention_heads=2, num_key_value_heads=1, head_dim=16))
+        args = TrainingArguments(output_dir=str(tmp_path / "out"), per_device_train_batch_size=2, max_steps=steps, learning_rate=1e-3,
+                                 save_steps=2, max_seq_len=32, lr_scheduler_type="constant", flash_device_path=str(tmp_path / "flash"))
+        tr = Trainer(model=model, args=args, train_dataset=SyntheticCausalLMDataset(128, 32, 64, seed=0))
+        tr.train(resume_from_checkpoint="auto")
+        return tr
+
+    run(4)
+    assert [s for s, _ in cm.list_checkpoints(str(tmp_path / "flash"))] == [4]
+    assert cm.verify(str(tmp_path / "flash" / "checkpoint-4"))[0] is cm.MirrorStatus.SUCCESS
+    shutil.rmtree(tmp_path / "out")                       # the shared store is gone: the fast device still has step 4
+    tr = run(6)
+    assert tr.state.global_step == 6 and [h["global_step"] for h in tr.state.log_history if "loss" in h][-2:] == [5, 6]
