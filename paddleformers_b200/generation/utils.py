@@ -76,6 +76,9 @@ class KVCache:
         w = int(getattr(attn, "window", 0) or 0)
         if w:
             vis = vis & (i - j < w)           # sliding-window layer: only the last ``w`` keys
+        c = int(getattr(attn, "chunk", 0) or 0)
+        if c:
+            vis = vis & (i // c == j // c)    # chunked layer: keys of the query's own chunk
         s = s.masked_fill(~vis[None, None], float("-inf"))
         sinks = getattr(attn, "sinks", None)
         if sinks is not None:             # one extra logit per head in the softmax denominator

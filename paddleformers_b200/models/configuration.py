@@ -105,7 +105,18 @@ class DecoderConfig(PretrainedConfig):
             return w if (self.use_sliding_window and layer_idx >= int(getattr(self, "max_window_layers", 0) or 0)) else 0
         return w
 
+    def layer_chunk(self, layer_idx: int) -> int:
+        """Chunk length of a chunked-attention layer (0 = none): a query sees the keys of its own chunk of ``attention_chunk_size``
+        consecutive positions only (Llama 4's local layers)."""
+        c = int(getattr(self, "attention_chunk_size", 0) or 0)
+        types = getattr(self, "layer_types", None)
+        if c <= 0 or not types or layer_idx >= len(types):
+            return 0
+        return c if types[layer_idx] == "chunked_attention" else 0
+
     def is_moe_layer(self, layer_idx: int) -> bool:
+        if getattr(self, "moe_layers", None) is not None and self.num_experts > 0:
+            return layer_idx in self.moe_layers
         if self.num_experts <= 0:
             return False
         if layer_idx in self.mlp_only_layers or layer_idx < self.first_k_dense_replace:
@@ -353,6 +364,56 @@ class MixtralConfig(DecoderConfig):
         if saving:
             d["num_local_experts"] = self.num_experts
             d.pop("num_experts", None)
+        return d
+
+
+class Llama4TextConfig(DecoderConfig):
+    """Llama 4 (text): local layers attend inside chunks of ``attention_chunk_size`` positions and rotate q / k (interleaved
+    pairs in the checkpoint), followed by a weightless L2 norm of q and k; every ``no_rope_layer_interval``-th layer is global,
+    uses no positional embedding and scales its queries with the logarithm of the position ("temperature tuning"). MoE layers
+    (``moe_layers``) pick top-k experts by logit, multiply the expert INPUT by the sigmoid of that logit, and add a shared
+    expert; dense layers use ``intermediate_size_mlp`` (paddleformers/transformers/llama4)."""
+
+    model_type = "llama4_text"
+
+    def __init__(self, intermediate_size_mlp=16384, attention_chunk_size=8192, layer_types=None, no_rope_layers=None,
+                 no_rope_layer_interval=4, moe_layers=None, interleave_moe_layer_step=1, attn_temperature_tuning=True, attn_scale=0.1,
+                 floor_scale=8192, use_qk_norm=True, **kw):
+        kw.setdefault("num_experts_per_tok", 1)
+        kw.setdefault("rms_norm_eps", 1e-5)
+        kw.setdefault("rope_theta", 500000.0)
+        kw.setdefault("n_shared_experts", 1)
+        kw["scoring_func"] = "sigmoid_topk_logits"
+        expert_size = kw.pop("intermediate_size", 8192)
+        super().__init__(intermediate_size=intermediate_size_mlp, moe_intermediate_size=expert_size, use_qk_norm=False, **kw)
+        n = self.num_hidden_layers
+        self.intermediate_size_mlp, self.expert_intermediate_size = intermediate_size_mlp, expert_size
+        self.shared_expert_intermediate_size = expert_size
+        self.attention_chunk_size = attention_chunk_size
+        self.no_rope_layer_interval = no_rope_layer_interval
+        self.no_rope_layers = list(no_rope_layers) if no_rope_layers else [int((i + 1) % no_rope_layer_interval != 0) for i in range(n)]
+        self.layer_types = list(layer_types) if layer_types else ["chunked_attention" if r else "full_attention" for r in self.no_rope_layers]
+        self.interleave_moe_layer_step = interleave_moe_layer_step
+        self.moe_layers = list(moe_layers) if moe_layers is not None else list(range(interleave_moe_layer_step - 1, n, interleave_moe_layer_step))
+        self.attn_temperature_tuning, self.attn_scale, self.floor_scale = attn_temperature_tuning, attn_scale, floor_scale
+        self.qk_l2_norm = bool(use_qk_norm)
+        self.rope_interleaved_checkpoint = True
+        self.moe_scale_expert_input = True
+        self.hf_experts_style = "llama4"
+        self.shared_expert_hf_name = "shared_expert"
+        self.router_weight_hf_name = "router.weight"
+        self.hf_name_translation = [[".mlp.", ".feed_forward."]]
+        self.num_local_experts = self.num_experts
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if saving:
+            d["intermediate_size"] = self.expert_intermediate_size
+            d["num_local_experts"] = self.num_experts
+            d["use_qk_norm"] = self.qk_l2_norm
+            for k in ("num_experts", "moe_intermediate_size", "scoring_func", "expert_intermediate_size", "qk_l2_norm",
+                      "hf_experts_style", "hf_name_translation", "moe_scale_expert_input"):
+                d.pop(k, None)
         return d
 
 
@@ -715,7 +776,7 @@ class Ernie4_5MoeConfig(Ernie4_5Config):
 CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, MiniCPMConfig, Olmo2Config,
                                             GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
                                             Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config, HunYuanDenseV1Config,
-                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig)}
+                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig)}
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
 # feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
@@ -726,10 +787,7 @@ UNSUPPORTED_FAMILIES = {
     "qwen3_next": "gated delta-net linear attention hybrid", "qwen3_5": "gated delta-net linear attention hybrid",
     "qwen3_5_moe": "gated delta-net linear attention hybrid",
     "gemma3": "SigLIP vision tower (the text decoder is available as gemma3_text)",
-    "phi4_multimodal": "vision and audio towers",
-
-
-    "llama4_text": "chunked attention, NoPE layers, shared-expert MoE", "diffllama": "differential attention",
+    "phi4_multimodal": "vision and audio towers", "diffllama": "differential attention",
 
 
     "ernie4_5_vl": "vision tower, modality-aware experts", "paddleocr_vl": "vision tower", "glm4v_moe": "vision tower",

@@ -31,7 +31,7 @@ from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
                             Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig,
                             GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig,
-                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig)
+                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig)
 
 
 @dataclass
@@ -195,10 +195,18 @@ class Attention(nn.Module):
         self.local_rope = bool(self.window and getattr(config, "rope_local_theta", None))
         # families whose global layers carry no positional embedding (Cohere2): only window layers rotate
         self.use_rope = bool(self.window) or not getattr(config, "rope_on_window_layers_only", False)
+        # Llama 4: chunked local layers; listed layers without rotary embedding; a weightless L2 norm of q and k after the
+        # rotation on the rotating layers; position-dependent query scale on the others
+        self.chunk = config.layer_chunk(layer_idx)
+        nope = getattr(config, "no_rope_layers", None)
+        if nope is not None and layer_idx < len(nope):
+            self.use_rope = bool(nope[layer_idx])
+        self.qk_l2 = bool(getattr(config, "qk_l2_norm", False)) and self.use_rope
+        self.temp_tuning = bool(getattr(config, "attn_temperature_tuning", False)) and not self.use_rope
 
     def forward(self, x2d: torch.Tensor, ctx: BatchContext, cache=None) -> torch.Tensor:
         qkv = _apply(self.qkv_proj, x2d)
-        kend = ctx.kend_window if (self.window and ctx.kend_window is not None) else ctx.kend
+        kend = ctx.kend_window if ((self.window or self.chunk) and ctx.kend_window is not None) else ctx.kend
         cos, sin = (ctx.cos_local, ctx.sin_local) if (self.local_rope and ctx.cos_local is not None) else (ctx.cos, ctx.sin)
         if self.qk_norm_full:
             nq, nk = self.Hq * self.D, self.Hkv * self.D
@@ -214,6 +222,22 @@ class Attention(nn.Module):
                                         self.Hq, self.Hkv, self.D, self.rot, self.config.rms_norm_eps)
         elif self.use_rope:
             qkv = F.rope_packed(qkv, cos, sin, ctx.positions, self.Hq, self.Hkv, self.D, self.rot)
+        if self.qk_l2 or self.temp_tuning:
+            nq, nk = self.Hq * self.D, self.Hkv * self.D
+            q, k = qkv[:, :nq], qkv[:, nq:nq + nk]
+            if self.qk_l2:
+                eps = self.config.rms_norm_eps
+
+                def l2(t):
+                    t = t.reshape(-1, self.D).float()
+                    return (t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps)).reshape(x2d.shape[0], -1)
+
+                q, k = l2(q).to(qkv.dtype), l2(k).to(qkv.dtype)
+            if self.temp_tuning:
+                pos = ctx.positions if ctx.positions is not None else torch.arange(ctx.S, device=qkv.device).repeat(ctx.B)
+                sc = torch.log1p(torch.floor((pos.float() + 1.0) / float(self.config.floor_scale))) * float(self.config.attn_scale) + 1.0
+                q = (q.float() * sc[:, None]).to(qkv.dtype)
+            qkv = torch.cat([q, k, qkv[:, nq + nk:]], dim=-1)
         if cache is not None:
             out = cache.attend(self, qkv, ctx)
         elif (self.softcap or self.sinks is not None or getattr(self.config, "_attn_implementation", None) in ("eager", "sdpa")) \
@@ -440,8 +464,18 @@ class DecoderModel(nn.Module):
         window = int(getattr(self.config, "sliding_window", None) or 0)
         if not any(self.config.layer_window(i) for i in self.layer_range):
             window = 0
+        chunk = max([self.config.layer_chunk(i) for i in self.layer_range] or [0])
         kend_window = None
-        if window and (full_seq_len or S) > window:
+        if chunk and (full_seq_len or S) > chunk:
+            if full_seq_len and full_seq_len != S:
+                raise NotImplementedError("chunked attention is not combined with context / segment parallelism")
+            # chunked layers: key j is visible up to the end of its own chunk (the same bound as a packed document of that length)
+            j = torch.arange(S, device=input_ids.device, dtype=torch.int32)
+            kend_window = ((j // chunk + 1) * chunk).clamp(max=S)[None].expand(B, S)
+            if kend is not None:
+                kend_window = torch.minimum(kend_window, kend.to(torch.int32).reshape(B, S))
+            kend_window = kend_window.contiguous()
+        elif window and (full_seq_len or S) > window:
             if full_seq_len and full_seq_len != S:
                 raise NotImplementedError("sliding-window attention is not combined with context / segment parallelism")
             # key j stops being visible at row j + window; together with the causal rule this is the sliding window, and it
@@ -808,6 +842,17 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
             # the three expert projections (gate, up, down)
             src = f"model.layers.{i}." + (getattr(config, "moe_block_hf_name", None) or "mlp") + "."
             g_n, u_n, d_n = getattr(config, "expert_proj_hf_names", None) or ("gate_proj", "up_proj", "down_proj")
+            if getattr(config, "hf_experts_style", None) == "llama4":
+                # stacked [E, H, 2I] ([in, out], gate columns then up columns) and [E, I, H]
+                tr = (lambda t: t.transpose(1, 2).contiguous(), lambda t: t.transpose(1, 2).contiguous())
+                rules.append(Rule(pre + "experts.gate_up_proj", [src + "experts.gate_up_proj"], fn=tr))
+                rules.append(Rule(pre + "experts.down_proj", [src + "experts.down_proj"], fn=tr))
+                rules.append(Rule(pre + "gate.weight", [src + config.router_weight_hf_name]))
+                sh = config.shared_expert_hf_name
+                rules.append(Rule(pre + "shared_experts.down_proj.weight", [src + sh + ".down_proj.weight"]))
+                rules.append(Rule(pre + "shared_experts.gate_up_proj.weight", [src + sh + ".gate_proj.weight", src + sh + ".up_proj.weight"],
+                                  "concat", 0))
+                continue
             if getattr(config, "hf_experts_style", None) == "gpt_oss":
                 # stacked [E, H, 2I] with gate / up columns interleaved, [E, I, H], and biases; router under "router"
                 def split_cols(t):        # [..., 2I] interleaved -> [gate | up]
@@ -943,11 +988,12 @@ MixtralForCausalLM = _family("MixtralForCausalLM", MixtralConfig)
 MiniCPM3ForCausalLM = _family("MiniCPM3ForCausalLM", MiniCPM3Config)
 InternLM2ForCausalLM = _family("InternLM2ForCausalLM", InternLM2Config)
 GptOssForCausalLM = _family("GptOssForCausalLM", GptOssConfig)
+Llama4ForCausalLM = _family("Llama4ForCausalLM", Llama4TextConfig)
 
 MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
     "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma2": Gemma2ForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
-    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "gpt_oss": GptOssForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
+    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "gpt_oss": GptOssForCausalLM, "llama4_text": Llama4ForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,
 }

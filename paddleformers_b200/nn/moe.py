@@ -103,6 +103,11 @@ class TopkRouter(nn.Module):
         logits = F.router_logits(x2d, self.weight)
         if self.bias is not None:
             logits = logits + self.bias
+        if self.scoring == "sigmoid_topk_logits":        # Llama 4: experts by logit, weight = sigmoid of the selected logit
+            top, idx = logits.topk(self.top_k, dim=-1)
+            with torch.no_grad():
+                self.expert_usage.scatter_add_(0, idx.reshape(-1), torch.ones_like(idx.reshape(-1)))
+            return idx, torch.sigmoid(top) * self.scale, None
         if self.scoring == "softmax_topk":
             top, idx = logits.topk(self.top_k, dim=-1)
             w = torch.softmax(top, dim=-1) * self.scale
@@ -558,7 +563,17 @@ class MoELayer(nn.Module):
         if self.ep > 1:
             from ..parallel.expert_parallel import ep_moe_forward
 
+            assert not getattr(self.config, "moe_scale_expert_input", False), \
+                "routing weights on the expert input are implemented for expert-parallel degree 1"
             y = ep_moe_forward(self, x2d, idx, w)
+        elif getattr(self.config, "moe_scale_expert_input", False):
+            # the routing weight multiplies what the expert READS (Llama 4): every (token, slot) pair becomes its own scaled
+            # row, and the outputs are summed with weight one
+            dest, block_expert, rows, counts = build_dispatch_plan(idx, self.experts.num_local, 0)
+            pairs = (x2d[:, None, :] * w[:, :, None].to(x2d.dtype)).reshape(T * idx.shape[1], H)
+            xr = _PermuteFn.apply(pairs, dest, 1, rows)
+            yr = self.experts(xr, block_expert, counts)
+            y = unpermute_combine(yr, dest, torch.ones_like(w), T)
         else:
             dest, block_expert, rows, counts = build_dispatch_plan(idx, self.experts.num_local, 0)
             xr = _PermuteFn.apply(x2d, dest, idx.shape[1], rows)

@@ -431,3 +431,27 @@ def test_gpt_oss_trains_sinks_router_bias_and_expert_biases():
         seq = generate(model, ids[:, :8], GenerationConfig(max_new_tokens=4))
         again = model(seq[:, :-1], return_logits=True).logits
     assert torch.equal(again[:, 7:].argmax(-1), seq[:, 8:])          # cached decoding applies sinks and windows too
+
+
+def test_llama4_chunked_layers_and_cached_decoding():
+    from paddleformers_b200.generation.utils import GenerationConfig, generate
+
+    cfg = AutoConfig.for_model("llama4_text", **{**TINY, "intermediate_size": 24, "intermediate_size_mlp": 48, "num_hidden_layers": 4,
+                                                 "num_local_experts": 4, "attention_chunk_size": 6, "interleave_moe_layer_step": 2,
+                                                 "floor_scale": 4})
+    assert cfg.no_rope_layers == [1, 1, 1, 0] and [cfg.layer_chunk(i) for i in range(4)] == [6, 6, 6, 0] and cfg.moe_layers == [1, 3]
+    assert [cfg.is_moe_layer(i) for i in range(4)] == [False, True, False, True]
+    torch.manual_seed(0)
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32)
+    ids = torch.randint(0, 96, (2, 15))
+    ctx = model.model.make_context(ids)
+    assert ctx.kend_window.tolist()[0] == [6] * 6 + [12] * 6 + [15] * 3
+    out = model.train()(ids, labels=torch.roll(ids, -1, 1))
+    out.loss.backward()
+    moe = model.model.layers["1"].mlp
+    assert moe.gate.weight.grad.abs().sum() > 0 and moe.experts.gate_up_proj.grad.abs().sum() > 0     # weights on the expert input
+    model.eval()
+    with torch.no_grad():
+        seq = generate(model, ids[:, :9], GenerationConfig(max_new_tokens=5))
+        again = model(seq[:, :-1], return_logits=True).logits
+    assert torch.equal(again[:, 8:].argmax(-1), seq[:, 9:])
