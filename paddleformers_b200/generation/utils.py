@@ -128,7 +128,7 @@ def generate(model, input_ids: torch.Tensor, generation_config: Optional[Generat
         return _beam_search(model, input_ids, cfg)
     stops = set(cfg.stop_token_ids) | ({cfg.eos_token_id} if cfg.eos_token_id is not None else set())
     layers = list(model.model.layer_range)
-    use_cache = not model.config.is_mla
+    use_cache = not model.config.is_mla and not getattr(model.config, "no_kv_cache", False)
     caches = {i: KVCache() for i in layers} if use_cache else None
     B = input_ids.shape[0]
     seq = input_ids

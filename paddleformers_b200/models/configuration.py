@@ -367,6 +367,47 @@ class MixtralConfig(DecoderConfig):
         return d
 
 
+class Qwen3NextConfig(DecoderConfig):
+    """Qwen3-Next: three of four layers mix tokens with a gated delta-rule linear attention (``nn.linear_attention``), the
+    fourth with softmax attention whose output is gated by a sigmoid computed from the query projection; rotary embedding on a
+    quarter of each head, per-head QK norm, zero-centred RMSNorm weights ((1 + w), stored as w), MoE layers with a gated
+    shared expert (paddleformers/transformers/qwen3_next). The linear-attention layers run as tensor operations and keep no
+    decoding state: generation recomputes the prefix."""
+
+    model_type = "qwen3_next"
+
+    def __init__(self, layer_types=None, full_attention_interval=4, linear_num_value_heads=32, linear_num_key_heads=16,
+                 linear_key_head_dim=128, linear_value_head_dim=128, linear_conv_kernel_dim=4, **kw):
+        _expert_count_alias(kw)
+        kw.setdefault("partial_rotary_factor", 0.25)
+        kw.setdefault("use_qk_norm", True)
+        kw.setdefault("head_dim", 256)
+        kw.setdefault("norm_topk_prob", True)
+        kw.setdefault("router_aux_loss_coef", 1e-3)
+        if kw.get("num_experts") and kw.get("shared_expert_intermediate_size", 1):
+            kw.setdefault("n_shared_experts", 1)
+        super().__init__(**kw)
+        n = self.num_hidden_layers
+        self.full_attention_interval = full_attention_interval
+        self.layer_types = list(layer_types) if layer_types else [
+            "full_attention" if (i + 1) % full_attention_interval == 0 else "linear_attention" for i in range(n)]
+        self.linear_num_value_heads, self.linear_num_key_heads = linear_num_value_heads, linear_num_key_heads
+        self.linear_key_head_dim, self.linear_value_head_dim = linear_key_head_dim, linear_value_head_dim
+        self.linear_conv_kernel_dim = linear_conv_kernel_dim
+        self.attention_output_gate = True
+        self.norm_weight_offset = 1.0
+        self.no_kv_cache = True
+        self.shared_expert_gate = bool(self.n_shared_experts)
+        self.shared_expert_hf_name = "shared_expert"
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if saving:
+            for k in ("attention_output_gate", "norm_weight_offset", "no_kv_cache", "shared_expert_gate", "shared_expert_hf_name"):
+                d.pop(k, None)
+        return d
+
+
 class Llama4TextConfig(DecoderConfig):
     """Llama 4 (text): local layers attend inside chunks of ``attention_chunk_size`` positions and rotate q / k (interleaved
     pairs in the checkpoint), followed by a weightless L2 norm of q and k; every ``no_rope_layer_interval``-th layer is global,
@@ -776,15 +817,14 @@ class Ernie4_5MoeConfig(Ernie4_5Config):
 CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, MiniCPMConfig, Olmo2Config,
                                             GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
                                             Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config, HunYuanDenseV1Config,
-                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig)}
+                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig)}
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
 # feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
 UNSUPPORTED_FAMILIES = {
     "deepseek_v32": "sparse (indexer) attention", "deepseek_v4": "compressed sparse attention",
     "glm_moe_dsa": "sparse (indexer) attention",
-    "minimax": "lightning (linear) attention hybrid",
-    "qwen3_next": "gated delta-net linear attention hybrid", "qwen3_5": "gated delta-net linear attention hybrid",
+    "minimax": "lightning (linear) attention hybrid", "qwen3_5": "gated delta-net linear attention hybrid",
     "qwen3_5_moe": "gated delta-net linear attention hybrid",
     "gemma3": "SigLIP vision tower (the text decoder is available as gemma3_text)",
     "phi4_multimodal": "vision and audio towers", "diffllama": "differential attention",

@@ -31,7 +31,7 @@ from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
                             Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig,
                             GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig,
-                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig)
+                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig)
 
 
 @dataclass
@@ -171,7 +171,17 @@ class Attention(nn.Module):
         self.rot = int(self.D * config.partial_rotary_factor)
         H = config.hidden_size
         secs = [self.Hq_total * self.D, self.Hkv_total * self.D, self.Hkv_total * self.D]
-        self.qkv_proj = _linear(H, sum(secs), config.attention_bias, "colwise", config, sections=secs, dtype=dtype, device=device)
+        # attention_output_gate (Qwen3-Next): the query projection also produces one gate value per output feature, stored per
+        # head as [q | gate]; the attention output is multiplied by sigmoid(gate). Such layers keep q / k / v projections apart.
+        self.output_gate = bool(getattr(config, "attention_output_gate", False))
+        if self.output_gate:
+            assert tp == 1, "gated attention is implemented for tensor-parallel degree 1"
+            self.q_proj = nn.Linear(H, 2 * secs[0], bias=config.attention_bias, dtype=dtype, device=device)
+            self.k_proj = nn.Linear(H, secs[1], bias=config.attention_bias, dtype=dtype, device=device)
+            self.v_proj = nn.Linear(H, secs[2], bias=config.attention_bias, dtype=dtype, device=device)
+            self.qkv_proj = None
+        else:
+            self.qkv_proj = _linear(H, sum(secs), config.attention_bias, "colwise", config, sections=secs, dtype=dtype, device=device)
         self.o_proj = _linear(self.Hq_total * self.D, H, bool(getattr(config, "attention_out_bias", False)), "rowwise", config,
                               dtype=dtype, device=device)
         self.use_qk_norm = config.use_qk_norm
@@ -205,7 +215,13 @@ class Attention(nn.Module):
         self.temp_tuning = bool(getattr(config, "attn_temperature_tuning", False)) and not self.use_rope
 
     def forward(self, x2d: torch.Tensor, ctx: BatchContext, cache=None) -> torch.Tensor:
-        qkv = _apply(self.qkv_proj, x2d)
+        gate = None
+        if self.output_gate:
+            qg = _apply(self.q_proj, x2d).view(x2d.shape[0], self.Hq, 2 * self.D)
+            gate = qg[..., self.D:].reshape(x2d.shape[0], self.Hq * self.D)
+            qkv = torch.cat([qg[..., :self.D].reshape(x2d.shape[0], self.Hq * self.D), _apply(self.k_proj, x2d), _apply(self.v_proj, x2d)], dim=-1)
+        else:
+            qkv = _apply(self.qkv_proj, x2d)
         kend = ctx.kend_window if ((self.window or self.chunk) and ctx.kend_window is not None) else ctx.kend
         cos, sin = (ctx.cos_local, ctx.sin_local) if (self.local_rope and ctx.cos_local is not None) else (ctx.cos, ctx.sin)
         if self.qk_norm_full:
@@ -263,6 +279,8 @@ class Attention(nn.Module):
             out = out.reshape(B * S, self.Hq * D)
         else:
             out = F.flash_attention_qkvpacked(qkv, ctx.B, ctx.S, self.Hq, self.Hkv, self.D, True, kend, self.scale)
+        if gate is not None:
+            out = out * torch.sigmoid(gate.float()).to(out.dtype)
         return _apply(self.o_proj, out)
 
 
@@ -350,7 +368,15 @@ class DecoderLayer(nn.Module):
         else:
             self.input_layernorm = make_norm(config, config.hidden_size, sp, dtype=dtype, device=device)
         attn_cls = MLAAttention if config.is_mla else Attention
-        self.self_attn = attn_cls(config, layer_idx, dtype=dtype, device=device)
+        types = getattr(config, "layer_types", None)
+        if types and layer_idx < len(types) and types[layer_idx] == "linear_attention":
+            from ..nn.linear_attention import GatedDeltaNet
+
+            # gated delta-rule token mixer instead of softmax attention (Qwen3-Next); called like an attention module
+            self.linear_attn = GatedDeltaNet(config, layer_idx, dtype=dtype, device=device)
+            self.self_attn = self.linear_attn.forward
+        else:
+            self.self_attn = attn_cls(config, layer_idx, dtype=dtype, device=device)
         if config.is_moe_layer(layer_idx):
             self.mlp = MoELayer(config, dtype=dtype, device=device)
         else:
@@ -798,7 +824,9 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
     else:
         qkv_sizes = [config.num_attention_heads * config.head_dim, config.num_key_value_heads * config.head_dim,
                      config.num_key_value_heads * config.head_dim]
-        if getattr(config, "hf_fused_qkv", False):      # the checkpoint already stores [q | k | v] rows in one matrix
+        if getattr(config, "attention_output_gate", False):
+            pass                                        # q (with its gate rows), k and v stay separate parameters under the same names
+        elif getattr(config, "hf_fused_qkv", False):      # the checkpoint already stores [q | k | v] rows in one matrix
             groups = None
             if getattr(config, "qkv_grouped_by_kv_head", False):
                 groups = (config.num_key_value_heads, config.num_attention_heads // config.num_key_value_heads, config.head_dim)
@@ -807,7 +835,7 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
             per_layer.append(Rule(L + "self_attn.qkv_proj.weight", [L + "self_attn.q_proj.weight", L + "self_attn.k_proj.weight",
                                                                      L + "self_attn.v_proj.weight"], "concat", 0, sizes=qkv_sizes,
                                   rope_deinterleave=rope_perm))
-        if config.attention_bias and not getattr(config, "hf_fused_qkv", False):
+        if config.attention_bias and not getattr(config, "hf_fused_qkv", False) and not getattr(config, "attention_output_gate", False):
             per_layer.append(Rule(L + "self_attn.qkv_proj.bias", [L + "self_attn.q_proj.bias", L + "self_attn.k_proj.bias",
                                                                    L + "self_attn.v_proj.bias"], "concat", 0, sizes=qkv_sizes,
                                   rope_deinterleave=rope_perm))
@@ -989,11 +1017,12 @@ MiniCPM3ForCausalLM = _family("MiniCPM3ForCausalLM", MiniCPM3Config)
 InternLM2ForCausalLM = _family("InternLM2ForCausalLM", InternLM2Config)
 GptOssForCausalLM = _family("GptOssForCausalLM", GptOssConfig)
 Llama4ForCausalLM = _family("Llama4ForCausalLM", Llama4TextConfig)
+Qwen3NextForCausalLM = _family("Qwen3NextForCausalLM", Qwen3NextConfig)
 
 MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
     "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma2": Gemma2ForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
-    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "gpt_oss": GptOssForCausalLM, "llama4_text": Llama4ForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
+    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "gpt_oss": GptOssForCausalLM, "llama4_text": Llama4ForCausalLM, "qwen3_next": Qwen3NextForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,
 }

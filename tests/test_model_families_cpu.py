@@ -455,3 +455,46 @@ def test_llama4_chunked_layers_and_cached_decoding():
         seq = generate(model, ids[:, :9], GenerationConfig(max_new_tokens=5))
         again = model(seq[:, :-1], return_logits=True).logits
     assert torch.equal(again[:, 8:].argmax(-1), seq[:, 9:])
+
+
+def test_gated_delta_rule_chunked_form_and_qwen3_next_training_step():
+    from paddleformers_b200.generation.utils import GenerationConfig, generate
+    from paddleformers_b200.nn.linear_attention import gated_delta_rule, gated_delta_rule_reference
+
+    torch.manual_seed(0)
+    B, S, H, dk, dv = 2, 37, 3, 8, 6
+    q = torch.nn.functional.normalize(torch.randn(B, S, H, dk), dim=-1).requires_grad_(True)
+    k = torch.nn.functional.normalize(torch.randn(B, S, H, dk), dim=-1).requires_grad_(True)
+    v = torch.randn(B, S, H, dv, requires_grad=True)
+    g, beta = -torch.rand(B, S, H) * 0.5, torch.rand(B, S, H)
+    ref, s_ref = gated_delta_rule_reference(q, k, v, g, beta)
+    grads_ref = torch.autograd.grad(ref.square().sum(), (q, k, v))
+    for chunk in (4, 16, 64):                                    # ragged last chunk, one chunk, several chunks
+        out, s_out = gated_delta_rule(q, k, v, g, beta, chunk=chunk)
+        torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(s_out, s_ref, rtol=1e-4, atol=1e-5)
+        for a, b in zip(torch.autograd.grad(out.square().sum(), (q, k, v)), grads_ref):
+            torch.testing.assert_close(a, b, rtol=1e-3, atol=1e-4)
+    # the state carries over: two halves with the state passed on equal one pass
+    o1, st = gated_delta_rule(q[:, :20], k[:, :20], v[:, :20], g[:, :20], beta[:, :20], chunk=8)
+    o2, _ = gated_delta_rule(q[:, 20:], k[:, 20:], v[:, 20:], g[:, 20:], beta[:, 20:], chunk=8, state=st)
+    torch.testing.assert_close(torch.cat([o1, o2], 1), ref, rtol=1e-4, atol=1e-5)
+
+    cfg = AutoConfig.for_model("qwen3_next", **{**TINY, "num_hidden_layers": 4, "linear_num_value_heads": 4, "linear_num_key_heads": 2,
+                                               "linear_key_head_dim": 8, "linear_value_head_dim": 8, "num_experts": 4,
+                                               "num_experts_per_tok": 2, "moe_intermediate_size": 16,
+                                               "shared_expert_intermediate_size": 24})
+    assert cfg.layer_types == ["linear_attention"] * 3 + ["full_attention"]
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32).train()
+    ids = torch.randint(0, 96, (2, 13))
+    out = model(ids, labels=torch.roll(ids, -1, 1))
+    out.loss.backward()
+    lin, full = model.model.layers["0"].linear_attn, model.model.layers["3"].self_attn
+    for p in (lin.A_log, lin.dt_bias, lin.conv1d.weight, lin.in_proj_ba.weight, lin.norm.weight, full.q_proj.weight,
+              model.model.layers["0"].mlp.shared_expert_gate.weight):
+        assert p.grad is not None and p.grad.abs().sum() > 0
+    model.eval()
+    with torch.no_grad():
+        seq = generate(model, ids[:, :7], GenerationConfig(max_new_tokens=3))
+        again = model(seq[:, :-1], return_logits=True).logits
+    assert torch.equal(again[:, 6:].argmax(-1), seq[:, 7:])
