@@ -408,6 +408,41 @@ class Qwen3NextConfig(DecoderConfig):
         return d
 
 
+class Qwen3_5TextConfig(Qwen3NextConfig):
+    """Qwen3.5 (text decoder): Qwen3-Next's layer pattern with dense MLPs, four separate input projections in the
+    linear-attention layers, and tensors stored under ``model.language_model`` because the released models are multimodal
+    (paddleformers/transformers/qwen3_5). A multimodal configuration is reduced to its ``text_config``; the vision tower
+    of the multimodal model is not provided."""
+
+    model_type = "qwen3_5_text"
+
+    def __init__(self, text_config=None, vision_config=None, **kw):
+        if text_config:                                   # a multimodal config.json: keep the decoder's fields
+            kw = {**{k: v for k, v in dict(text_config).items() if k != "model_type"},
+                  **{k: v for k, v in kw.items() if k in ("tie_word_embeddings", "dtype", "torch_dtype", "architectures")}}
+        rp = dict(kw.get("rope_parameters") or {})
+        for k in ("mrope_section", "mrope_interleaved"):     # text-only use: the three position streams coincide
+            rp.pop(k, None)
+        if rp:
+            kw["rope_parameters"] = rp
+        super().__init__(**kw)
+        self.linear_attn_split_projections = True
+        self.hf_name_translation = [["model.", "model.language_model."]]
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if saving:
+            d.pop("linear_attn_split_projections", None)
+            d.pop("hf_name_translation", None)
+        return d
+
+
+class Qwen3_5MoeTextConfig(Qwen3_5TextConfig):
+    """Qwen3.5-MoE (text decoder): Qwen3.5 with Qwen3-Next's MoE layers (paddleformers/transformers/qwen3_5_moe)."""
+
+    model_type = "qwen3_5_moe_text"
+
+
 class Llama4TextConfig(DecoderConfig):
     """Llama 4 (text): local layers attend inside chunks of ``attention_chunk_size`` positions and rotate q / k (interleaved
     pairs in the checkpoint), followed by a weightless L2 norm of q and k; every ``no_rope_layer_interval``-th layer is global,
@@ -817,15 +852,14 @@ class Ernie4_5MoeConfig(Ernie4_5Config):
 CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, MiniCPMConfig, Olmo2Config,
                                             GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
                                             Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config, HunYuanDenseV1Config,
-                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig)}
+                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig, Qwen3_5TextConfig, Qwen3_5MoeTextConfig)}
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
 # feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
 UNSUPPORTED_FAMILIES = {
     "deepseek_v32": "sparse (indexer) attention", "deepseek_v4": "compressed sparse attention",
     "glm_moe_dsa": "sparse (indexer) attention",
-    "minimax": "lightning (linear) attention hybrid", "qwen3_5": "gated delta-net linear attention hybrid",
-    "qwen3_5_moe": "gated delta-net linear attention hybrid",
+    "minimax": "lightning (linear) attention hybrid",
     "gemma3": "SigLIP vision tower (the text decoder is available as gemma3_text)",
     "phi4_multimodal": "vision and audio towers", "diffllama": "differential attention",
 
@@ -842,7 +876,7 @@ def resolve_config_class(model_type: str):
         raise NotImplementedError(f"model_type {model_type!r} is known but not implemented: it needs {UNSUPPORTED_FAMILIES[model_type]}")
     raise ValueError(f"unknown model_type {model_type!r}; supported: {sorted(CONFIG_MAPPING)}")
 # families whose architecture is a strict subset of an implemented one load through it
-CONFIG_MAPPING.update({"kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV2Config, "glm4_moe_lite": Glm4MoeConfig, "phi4": Phi3Config})
+CONFIG_MAPPING.update({"qwen3_5": Qwen3_5TextConfig, "qwen3_5_moe": Qwen3_5MoeTextConfig, "kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV2Config, "glm4_moe_lite": Glm4MoeConfig, "phi4": Phi3Config})
 
 
 def named_config(name: str, **overrides) -> DecoderConfig:

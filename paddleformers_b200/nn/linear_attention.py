@@ -86,8 +86,16 @@ class GatedDeltaNet(nn.Module):
         self.kernel = config.linear_conv_kernel_dim
         self.eps = config.rms_norm_eps
         conv_dim = 2 * self.key_dim + self.value_dim
-        self.in_proj_qkvz = nn.Linear(H, 2 * self.key_dim + 2 * self.value_dim, bias=False, **kw)
-        self.in_proj_ba = nn.Linear(H, 2 * self.nv, bias=False, **kw)
+        # Qwen3-Next fuses the input projections per key head; Qwen3.5 keeps four flat ones
+        self.split_proj = bool(getattr(config, "linear_attn_split_projections", False))
+        if self.split_proj:
+            self.in_proj_qkv = nn.Linear(H, conv_dim, bias=False, **kw)
+            self.in_proj_z = nn.Linear(H, self.value_dim, bias=False, **kw)
+            self.in_proj_b = nn.Linear(H, self.nv, bias=False, **kw)
+            self.in_proj_a = nn.Linear(H, self.nv, bias=False, **kw)
+        else:
+            self.in_proj_qkvz = nn.Linear(H, 2 * self.key_dim + 2 * self.value_dim, bias=False, **kw)
+            self.in_proj_ba = nn.Linear(H, 2 * self.nv, bias=False, **kw)
         self.conv1d = nn.Conv1d(conv_dim, conv_dim, self.kernel, groups=conv_dim, bias=False, padding=self.kernel - 1, **kw)
         self.dt_bias = nn.Parameter(torch.ones(self.nv, **kw))
         self.A_log = nn.Parameter(torch.log(torch.empty(self.nv, dtype=torch.float32, device=device).uniform_(1, 16)).to(dtype or torch.float32))
@@ -100,12 +108,16 @@ class GatedDeltaNet(nn.Module):
             raise NotImplementedError("incremental decoding state for linear-attention layers is not kept: decode without a cache")
         B, S = ctx.B, ctx.S
         r = self.nv // self.nk
-        # projections are laid out per key head: [q (dk) | k (dk) | v (r dv) | z (r dv)] and [b (r) | a (r)]
-        qkvz = self.in_proj_qkvz(x2d).view(B, S, self.nk, 2 * self.dk + 2 * r * self.dv)
-        ba = self.in_proj_ba(x2d).view(B, S, self.nk, 2 * r)
-        q, k, v, z = qkvz.split([self.dk, self.dk, r * self.dv, r * self.dv], dim=-1)
-        b, a = ba.split([r, r], dim=-1)
-        mixed = torch.cat([q.reshape(B, S, -1), k.reshape(B, S, -1), v.reshape(B, S, -1)], dim=-1).transpose(1, 2)
+        if self.split_proj:
+            mixed = self.in_proj_qkv(x2d).view(B, S, -1).transpose(1, 2)
+            z, b, a = self.in_proj_z(x2d), self.in_proj_b(x2d), self.in_proj_a(x2d)
+        else:
+            # projections are laid out per key head: [q (dk) | k (dk) | v (r dv) | z (r dv)] and [b (r) | a (r)]
+            qkvz = self.in_proj_qkvz(x2d).view(B, S, self.nk, 2 * self.dk + 2 * r * self.dv)
+            ba = self.in_proj_ba(x2d).view(B, S, self.nk, 2 * r)
+            q, k, v, z = qkvz.split([self.dk, self.dk, r * self.dv, r * self.dv], dim=-1)
+            b, a = ba.split([r, r], dim=-1)
+            mixed = torch.cat([q.reshape(B, S, -1), k.reshape(B, S, -1), v.reshape(B, S, -1)], dim=-1).transpose(1, 2)
         mixed = TF.silu(self.conv1d(mixed)[:, :, :S]).transpose(1, 2)          # causal: left padding, right part dropped
         q, k, v = mixed.split([self.key_dim, self.key_dim, self.value_dim], dim=-1)
         q, k = q.reshape(B, S, self.nk, self.dk), k.reshape(B, S, self.nk, self.dk)

@@ -198,11 +198,18 @@ class Rule:
 class WeightMap:
     """All rules of one model instance, indexed by internal parameter name."""
 
-    def __init__(self, rules: Iterable[Rule]):
+    def __init__(self, rules: Iterable[Rule], translation: Optional[Sequence[Sequence[str]]] = None):
         self.rules: Dict[str, Rule] = {r.target: r for r in rules}
+        self.translation = [tuple(x) for x in (translation or [])]
+
+    def translate(self, name: str) -> str:
+        """Checkpoint-side spelling of a name for families that store the same tensors under other names."""
+        for a, b in self.translation:
+            name = name.replace(a, b)
+        return name
 
     def rule_for(self, target: str) -> Rule:
-        return self.rules.get(target) or Rule(target, [target])
+        return self.rules.get(target) or Rule(target, [self.translate(target)])
 
     def hf_names(self) -> List[str]:
         out = []
