@@ -202,6 +202,52 @@ class DeepseekV3Config(DecoderConfig):
         super().__init__(**kw)
 
 
+class Glm4MoeLiteConfig(DeepseekV3Config):
+    """GLM-4.7-Flash class models (``glm4_moe_lite``): DeepSeek-V3's blocks (multi-head latent attention with interleaved rotary
+    rows, sigmoid ``noaux_tc`` routing, shared expert) at other sizes, without a multi-token-prediction layer; ``mlp_layer_types``
+    lists which layers are dense."""
+
+    model_type = "glm4_moe_lite"
+
+    def __init__(self, mlp_layer_types=None, **kw):
+        kw.setdefault("hidden_size", 2048)
+        kw.setdefault("intermediate_size", 10240)
+        kw.setdefault("moe_intermediate_size", 1536)
+        kw.setdefault("num_attention_heads", 20)
+        kw.setdefault("num_key_value_heads", kw["num_attention_heads"])
+        if "num_experts" not in kw:
+            kw.setdefault("n_routed_experts", 64)
+        kw.setdefault("num_experts_per_tok", 4)
+        kw.setdefault("n_group", 1)
+        kw.setdefault("topk_group", 1)
+        kw.setdefault("routed_scaling_factor", 1.8)
+        kw.setdefault("q_lora_rank", 768)
+        kw.setdefault("kv_lora_rank", 512)
+        kw.setdefault("qk_nope_head_dim", 192)
+        kw.setdefault("qk_rope_head_dim", 64)
+        kw.setdefault("v_head_dim", 256)
+        kw["head_dim"] = kw["qk_nope_head_dim"] + kw["qk_rope_head_dim"]
+        kw.setdefault("rms_norm_eps", 1e-5)
+        kw.setdefault("vocab_size", 154880)
+        kw.setdefault("num_nextn_predict_layers", 0)
+        if mlp_layer_types:
+            dense = [i for i, t in enumerate(mlp_layer_types) if t == "dense"]
+            if dense != list(range(len(dense))):
+                raise NotImplementedError("dense layers are expected at the start of the stack")
+            kw["first_k_dense_replace"] = len(dense)
+        else:
+            kw.setdefault("first_k_dense_replace", 1)
+        super().__init__(**kw)
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if saving:
+            d["mlp_layer_types"] = ["dense" if i < self.first_k_dense_replace else "sparse" for i in range(self.num_hidden_layers)]
+            d["qk_head_dim"] = self.qk_nope_head_dim + self.qk_rope_head_dim
+            d.pop("head_dim", None)          # other loaders read it as the rotary width of the latent attention
+        return d
+
+
 class DeepseekV2Config(DeepseekV3Config):
     """DeepSeek-V2 / V2-Lite: MLA with a softmax router (greedy or group-limited), no multi-token-prediction layer, the query
     projected directly when ``q_lora_rank`` is null (paddleformers/transformers/deepseek_v3 serves both generations)."""
@@ -876,7 +922,7 @@ def resolve_config_class(model_type: str):
         raise NotImplementedError(f"model_type {model_type!r} is known but not implemented: it needs {UNSUPPORTED_FAMILIES[model_type]}")
     raise ValueError(f"unknown model_type {model_type!r}; supported: {sorted(CONFIG_MAPPING)}")
 # families whose architecture is a strict subset of an implemented one load through it
-CONFIG_MAPPING.update({"qwen3_5": Qwen3_5TextConfig, "qwen3_5_moe": Qwen3_5MoeTextConfig, "kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV2Config, "glm4_moe_lite": Glm4MoeConfig, "phi4": Phi3Config})
+CONFIG_MAPPING.update({"qwen3_5": Qwen3_5TextConfig, "qwen3_5_moe": Qwen3_5MoeTextConfig, "kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV2Config, "glm4_moe_lite": Glm4MoeLiteConfig, "phi4": Phi3Config})
 
 
 def named_config(name: str, **overrides) -> DecoderConfig:

@@ -1025,7 +1025,7 @@ MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
     "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma2": Gemma2ForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
     "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "gpt_oss": GptOssForCausalLM, "llama4_text": Llama4ForCausalLM, "qwen3_next": Qwen3NextForCausalLM, "qwen3_5_text": Qwen3_5ForCausalLM, "qwen3_5_moe_text": Qwen3_5MoeForCausalLM,
-    "qwen3_5": Qwen3_5ForCausalLM, "qwen3_5_moe": Qwen3_5MoeForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": Glm4MoeForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
+    "qwen3_5": Qwen3_5ForCausalLM, "qwen3_5_moe": Qwen3_5MoeForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": DeepseekV3ForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,
 }

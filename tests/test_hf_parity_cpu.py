@@ -102,6 +102,10 @@ CASES = {
     "qwen3_5_moe_text": ("Qwen3_5MoeTextConfig", "Qwen3_5MoeForCausalLM", dict(
         head_dim=16, num_hidden_layers=4, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=8, linear_value_head_dim=8,
         num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=48)),
+    "glm4_moe_lite": ("Glm4MoeLiteConfig", "Glm4MoeLiteForCausalLM", dict(
+        num_hidden_layers=3, num_key_value_heads=4, moe_intermediate_size=32, n_routed_experts=8, num_experts_per_tok=2, n_group=1,
+        topk_group=1, n_shared_experts=1, mlp_layer_types=["dense", "sparse", "sparse"], q_lora_rank=24, kv_lora_rank=16,
+        qk_nope_head_dim=24, qk_rope_head_dim=8, v_head_dim=32, routed_scaling_factor=1.8, norm_topk_prob=True)),
     "mixtral": ("MixtralConfig", "MixtralForCausalLM", dict(num_local_experts=4, num_experts_per_tok=2, sliding_window=8)),
     "stablelm": ("StableLmConfig", "StableLmForCausalLM", dict(use_qkv_bias=True, partial_rotary_factor=0.25)),
     "glm4_moe": ("Glm4MoeConfig", "Glm4MoeForCausalLM", dict(head_dim=16, moe_intermediate_size=32, n_routed_experts=4, num_experts_per_tok=2,
@@ -135,7 +139,7 @@ def test_logits_match_hugging_face_implementation(tmp_path, family):
     torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma2", "gemma3_text", "cohere", "cohere2", "olmo2", "hunyuan_v1_dense", "hunyuan_v1_moe", "minimax_m2", "mixtral", "deepseek_v2", "gpt_oss", "llama4_text", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text",
+@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma2", "gemma3_text", "cohere", "cohere2", "olmo2", "hunyuan_v1_dense", "hunyuan_v1_moe", "minimax_m2", "mixtral", "deepseek_v2", "gpt_oss", "llama4_text", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "glm4_moe_lite",
                                     "stablelm", "granite", "qwen2_moe", "ernie4_5_moe"])
 def test_hugging_face_loads_what_this_framework_saves(tmp_path, family):
     """The other direction: a checkpoint written by ``save_pretrained`` here (per-expert tensors, interleaved rotary rows
