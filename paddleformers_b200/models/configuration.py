@@ -82,7 +82,7 @@ class DecoderConfig(PretrainedConfig):
 
     def to_dict(self, saving: bool = False):
         d = super().to_dict(saving)
-        if self.num_experts and self.model_type in ("deepseek_v3", "deepseek_v2", "glm4_moe", "glm4_moe_lite", "kimi_k2"):
+        if self.num_experts and self.model_type in ("deepseek_v3", "deepseek_v2", "deepseek_v32", "glm4_moe", "glm4_moe_lite", "glm_moe_dsa", "kimi_k2"):
             d["n_routed_experts"] = self.num_experts      # the field name these families use in config.json
             d.pop("num_experts", None)
         return d
@@ -246,6 +246,32 @@ class Glm4MoeLiteConfig(DeepseekV3Config):
             d["qk_head_dim"] = self.qk_nope_head_dim + self.qk_rope_head_dim
             d.pop("head_dim", None)          # other loaders read it as the rotary width of the latent attention
         return d
+
+
+class GlmMoeDsaConfig(Glm4MoeLiteConfig):
+    """GLM with DeepSeek sparse attention (``glm_moe_dsa``): latent attention whose queries attend to the ``index_topk`` keys
+    picked by a light indexer (``index_n_heads`` x ``index_head_dim``); sequences no longer than ``index_topk`` are plain
+    latent attention."""
+
+    model_type = "glm_moe_dsa"
+
+    def __init__(self, index_topk=2048, index_n_heads=32, index_head_dim=128, **kw):
+        kw.setdefault("routed_scaling_factor", 2.5)
+        super().__init__(**kw)
+        self.index_topk, self.index_n_heads, self.index_head_dim = index_topk, index_n_heads, index_head_dim
+        self.no_kv_cache = True
+        self.rope_interleave = False          # checkpoints of this family store half-split rotary rows
+
+
+class DeepseekV32Config(DeepseekV3Config):
+    """DeepSeek-V3.2: DeepSeek-V3 with the sparse-attention indexer (paddleformers/transformers/deepseek_v32)."""
+
+    model_type = "deepseek_v32"
+
+    def __init__(self, index_topk=2048, index_n_heads=64, index_head_dim=128, **kw):
+        super().__init__(**kw)
+        self.index_topk, self.index_n_heads, self.index_head_dim = index_topk, index_n_heads, index_head_dim
+        self.no_kv_cache = True
 
 
 class DeepseekV2Config(DeepseekV3Config):
@@ -902,9 +928,7 @@ CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Q
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
 # feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
-UNSUPPORTED_FAMILIES = {
-    "deepseek_v32": "sparse (indexer) attention", "deepseek_v4": "compressed sparse attention",
-    "glm_moe_dsa": "sparse (indexer) attention",
+UNSUPPORTED_FAMILIES = { "deepseek_v4": "compressed sparse attention",
     "minimax": "lightning (linear) attention hybrid",
     "gemma3": "SigLIP vision tower (the text decoder is available as gemma3_text)",
     "phi4_multimodal": "vision and audio towers", "diffllama": "differential attention",
@@ -922,7 +946,7 @@ def resolve_config_class(model_type: str):
         raise NotImplementedError(f"model_type {model_type!r} is known but not implemented: it needs {UNSUPPORTED_FAMILIES[model_type]}")
     raise ValueError(f"unknown model_type {model_type!r}; supported: {sorted(CONFIG_MAPPING)}")
 # families whose architecture is a strict subset of an implemented one load through it
-CONFIG_MAPPING.update({"qwen3_5": Qwen3_5TextConfig, "qwen3_5_moe": Qwen3_5MoeTextConfig, "kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV2Config, "glm4_moe_lite": Glm4MoeLiteConfig, "phi4": Phi3Config})
+CONFIG_MAPPING.update({"qwen3_5": Qwen3_5TextConfig, "qwen3_5_moe": Qwen3_5MoeTextConfig, "kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV2Config, "glm4_moe_lite": Glm4MoeLiteConfig, "glm_moe_dsa": GlmMoeDsaConfig, "deepseek_v32": DeepseekV32Config, "phi4": Phi3Config})
 
 
 def named_config(name: str, **overrides) -> DecoderConfig:

@@ -31,7 +31,7 @@ from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
                             Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig,
                             GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig,
-                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig, Qwen3_5TextConfig, Qwen3_5MoeTextConfig)
+                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig, Qwen3_5TextConfig, Qwen3_5MoeTextConfig, GlmMoeDsaConfig, DeepseekV32Config)
 
 
 @dataclass
@@ -284,6 +284,40 @@ class Attention(nn.Module):
         return _apply(self.o_proj, out)
 
 
+class SparseIndexer(nn.Module):
+    """Token selector of DeepSeek sparse attention (DSA): a light multi-head scorer, score[s, t] = sum_h w[s, h] *
+    relu(q[s, h] . k[t]) / sqrt(d), with its own projections (queries from the latent query, one shared key per token, rotary
+    embedding on the first ``qk_rope_head_dim`` features in half-split order) picks the ``index_topk`` keys a query may attend
+    to (paddleformers/transformers/deepseek_v32, glm_moe_dsa). Selection is not differentiated through."""
+
+    def __init__(self, config, dtype=None, device=None):
+        super().__init__()
+        kw = dict(dtype=dtype, device=device)
+        self.H, self.D, self.rope = config.index_n_heads, config.index_head_dim, config.qk_rope_head_dim
+        self.topk = int(config.index_topk)
+        self.wq_b = nn.Linear(config.q_lora_rank, self.H * self.D, bias=False, **kw)
+        self.wk = nn.Linear(config.hidden_size, self.D, bias=False, **kw)
+        self.k_norm = nn.LayerNorm(self.D, eps=1e-6, **kw)
+        self.weights_proj = nn.Linear(config.hidden_size, self.H, bias=False, **kw)
+
+    @torch.no_grad()
+    def visible(self, x2d, q_latent, ctx: "BatchContext", allowed: torch.Tensor) -> torch.Tensor:
+        """allowed: bool [B, S, S] (causal / document mask). Returns bool [B, S, S]: the selected keys among the allowed ones."""
+        B, S = ctx.B, ctx.S
+        T = B * S
+        q = self.wq_b(q_latent).view(T, self.H, self.D)
+        k = self.k_norm(self.wk(x2d))
+        q_pe = F.rope_heads(q[..., :self.rope].reshape(T, self.H * self.rope), ctx.cos, ctx.sin, ctx.positions, self.H, self.rope)
+        k_pe = F.rope_heads(k[:, :self.rope].contiguous(), ctx.cos, ctx.sin, ctx.positions, 1, self.rope)
+        q = torch.cat([q_pe.view(T, self.H, self.rope), q[..., self.rope:]], dim=-1).view(B, S, self.H, self.D)
+        k = torch.cat([k_pe.view(T, self.rope), k[:, self.rope:]], dim=-1).view(B, S, self.D)
+        w = self.weights_proj(x2d).float().view(B, S, self.H) * self.H ** -0.5
+        sc = torch.relu(torch.einsum("bshd,btd->bsht", q.float(), k.float()) * self.D ** -0.5)
+        score = torch.einsum("bsht,bsh->bst", sc, w).masked_fill(~allowed, float("-inf"))
+        idx = score.topk(min(self.topk, S), dim=-1).indices
+        return torch.zeros_like(allowed).scatter_(-1, idx, True) & allowed
+
+
 class MLAAttention(nn.Module):
     """Multi-head latent attention (DeepSeek-V3), non-absorbed training form: low-rank q and kv projections with
     RMSNorm on the latents, rotary embedding on a separate ``qk_rope_head_dim`` slice whose key part is shared by
@@ -317,9 +351,14 @@ class MLAAttention(nn.Module):
             self.scale = self.scale * m * m
         self.sp = bool(getattr(config, "sequence_parallel", False)) and tp > 1
         self.group = get_parallel_state().group("mp")
+        self.indexer = None
+        if getattr(config, "index_topk", None):
+            assert tp == 1 and self.q_lora, "sparse (indexer) attention needs the latent query and tensor-parallel degree 1"
+            self.indexer = SparseIndexer(config, dtype=dtype, device=device)
 
     def forward(self, x2d, ctx: BatchContext, cache=None):
         T = ctx.B * ctx.S
+        qa = None
         if self.q_lora:
             qa = self.q_a_layernorm(_apply(self.q_a_proj, x2d))
             q = _apply(self.q_b_proj, qa)
@@ -340,7 +379,19 @@ class MLAAttention(nn.Module):
         v = kv[..., self.nope:]
         q4, k4 = qf.view(ctx.B, ctx.S, self.Hq, self.qd), kf.view(ctx.B, ctx.S, self.Hq, self.qd)
         v4 = v.reshape(ctx.B, ctx.S, self.Hq, self.vd)
-        if ctx.S_full and cache is None:
+        if self.indexer is not None and ctx.S > self.indexer.topk:
+            # more keys than the selector keeps: every query attends to its selected keys only. The mask is arbitrary per
+            # query, which the flash kernels cannot express: scores and softmax run as tensor operations here.
+            if ctx.S_full:
+                raise NotImplementedError("sparse (indexer) attention is not combined with context / segment parallelism")
+            from ..nn.attention import _dense_mask
+
+            allowed = _dense_mask(ctx.kend, ctx.B, ctx.S, True, x2d.device)
+            vis = self.indexer.visible(x2d, qa, ctx, allowed)
+            sc = torch.einsum("bshd,bthd->bhst", q4.float(), k4.float()) * self.scale
+            p = torch.softmax(sc.masked_fill(~vis[:, None], float("-inf")), dim=-1)
+            out = torch.einsum("bhst,bthd->bshd", p, v4.float()).to(x2d.dtype)
+        elif ctx.S_full and cache is None:
             out = long_sequence_attention(q4, k4, v4, ctx, self.scale, self.config)
         else:
             out = F.flash_attention(q4, k4, v4, True, ctx.kend, self.scale)
@@ -1025,7 +1076,8 @@ MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
     "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma2": Gemma2ForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
     "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "gpt_oss": GptOssForCausalLM, "llama4_text": Llama4ForCausalLM, "qwen3_next": Qwen3NextForCausalLM, "qwen3_5_text": Qwen3_5ForCausalLM, "qwen3_5_moe_text": Qwen3_5MoeForCausalLM,
-    "qwen3_5": Qwen3_5ForCausalLM, "qwen3_5_moe": Qwen3_5MoeForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": DeepseekV3ForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
+    "qwen3_5": Qwen3_5ForCausalLM, "qwen3_5_moe": Qwen3_5MoeForCausalLM,
+    "glm_moe_dsa": DeepseekV3ForCausalLM, "deepseek_v32": DeepseekV3ForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": DeepseekV3ForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,
 }

@@ -106,6 +106,10 @@ CASES = {
         num_hidden_layers=3, num_key_value_heads=4, moe_intermediate_size=32, n_routed_experts=8, num_experts_per_tok=2, n_group=1,
         topk_group=1, n_shared_experts=1, mlp_layer_types=["dense", "sparse", "sparse"], q_lora_rank=24, kv_lora_rank=16,
         qk_nope_head_dim=24, qk_rope_head_dim=8, v_head_dim=32, routed_scaling_factor=1.8, norm_topk_prob=True)),
+    "glm_moe_dsa": ("GlmMoeDsaConfig", "GlmMoeDsaForCausalLM", dict(
+        num_hidden_layers=2, num_key_value_heads=4, moe_intermediate_size=32, n_routed_experts=4, num_experts_per_tok=2, n_group=1,
+        topk_group=1, mlp_layer_types=["dense", "sparse"], q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8,
+        v_head_dim=16, index_topk=8, index_n_heads=2, index_head_dim=16)),
     "mixtral": ("MixtralConfig", "MixtralForCausalLM", dict(num_local_experts=4, num_experts_per_tok=2, sliding_window=8)),
     "stablelm": ("StableLmConfig", "StableLmForCausalLM", dict(use_qkv_bias=True, partial_rotary_factor=0.25)),
     "glm4_moe": ("Glm4MoeConfig", "Glm4MoeForCausalLM", dict(head_dim=16, moe_intermediate_size=32, n_routed_experts=4, num_experts_per_tok=2,
@@ -122,6 +126,8 @@ def test_logits_match_hugging_face_implementation(tmp_path, family):
         pytest.skip(f"transformers has no {cls_name}")
     torch.manual_seed(0)
     hf_cfg = getattr(transformers, cfg_name)(**{**BASE, **extra})
+    if family == "glm_moe_dsa":
+        hf_cfg._attn_implementation = "eager"      # its default attention path drops the causal mask when no mask tensor is passed
     hf = getattr(transformers, cls_name)(hf_cfg).eval().float()
     with torch.no_grad():
         for n, p in hf.named_parameters():          # non-trivial values everywhere (norm weights, router biases)
@@ -139,7 +145,7 @@ def test_logits_match_hugging_face_implementation(tmp_path, family):
     torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma2", "gemma3_text", "cohere", "cohere2", "olmo2", "hunyuan_v1_dense", "hunyuan_v1_moe", "minimax_m2", "mixtral", "deepseek_v2", "gpt_oss", "llama4_text", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "glm4_moe_lite",
+@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma2", "gemma3_text", "cohere", "cohere2", "olmo2", "hunyuan_v1_dense", "hunyuan_v1_moe", "minimax_m2", "mixtral", "deepseek_v2", "gpt_oss", "llama4_text", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "glm4_moe_lite", "glm_moe_dsa",
                                     "stablelm", "granite", "qwen2_moe", "ernie4_5_moe"])
 def test_hugging_face_loads_what_this_framework_saves(tmp_path, family):
     """The other direction: a checkpoint written by ``save_pretrained`` here (per-expert tensors, interleaved rotary rows
@@ -152,7 +158,8 @@ def test_hugging_face_loads_what_this_framework_saves(tmp_path, family):
     mine = AutoModelForCausalLM.from_pretrained(str(src), dtype=torch.float32).eval()
     out = tmp_path / "out"
     mine.save_pretrained(str(out))
-    back = getattr(transformers, cls_name).from_pretrained(str(out), torch_dtype=torch.float32).eval()
+    back = getattr(transformers, cls_name).from_pretrained(str(out), torch_dtype=torch.float32,
+                                                           **({"attn_implementation": "eager"} if family == "glm_moe_dsa" else {})).eval()
     ids = torch.randint(0, 128, (2, 24))
     with torch.no_grad():
         torch.testing.assert_close(back(input_ids=ids).logits, mine(ids, return_logits=True).logits, rtol=2e-4, atol=2e-4)

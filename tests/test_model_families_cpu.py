@@ -87,7 +87,7 @@ def test_sliding_window_is_expressed_through_the_mask_bounds():
 def test_registry_names_known_but_unimplemented_families():
     assert not set(CONFIG_MAPPING) & set(UNSUPPORTED_FAMILIES)
     with pytest.raises(NotImplementedError, match="sparse"):
-        AutoConfig.for_model("deepseek_v32")
+        AutoConfig.for_model("deepseek_v4")
     with pytest.raises(ValueError, match="unknown model_type"):
         AutoConfig.for_model("no_such_family")
 
@@ -498,3 +498,31 @@ def test_gated_delta_rule_chunked_form_and_qwen3_next_training_step():
         seq = generate(model, ids[:, :7], GenerationConfig(max_new_tokens=3))
         again = model(seq[:, :-1], return_logits=True).logits
     assert torch.equal(again[:, 6:].argmax(-1), seq[:, 7:])
+
+
+def test_sparse_indexer_attention_selects_keys_only_beyond_its_budget():
+    kw = dict(vocab_size=96, hidden_size=32, intermediate_size=48, moe_intermediate_size=16, num_hidden_layers=2, num_attention_heads=2,
+              n_routed_experts=4, num_experts_per_tok=2, n_group=1, topk_group=1, first_k_dense_replace=1, q_lora_rank=16, kv_lora_rank=8,
+              qk_nope_head_dim=8, qk_rope_head_dim=4, v_head_dim=8, num_nextn_predict_layers=0, index_n_heads=2, index_head_dim=8)
+    torch.manual_seed(0)
+    sparse = AutoModelForCausalLM.from_config(AutoConfig.for_model("deepseek_v32", index_topk=6, **kw), dtype=torch.float32)
+    dense_cfg = AutoConfig.for_model("deepseek_v32", index_topk=64, **kw)
+    dense = AutoModelForCausalLM.from_config(dense_cfg, dtype=torch.float32)
+    dense.load_state_dict(sparse.state_dict())
+    ids = torch.randint(0, 96, (2, 14))
+    with torch.no_grad():
+        a = sparse.eval()(ids, return_logits=True).logits
+        b = dense.eval()(ids, return_logits=True).logits
+    # the first 6 positions have at most 6 visible keys: nothing to drop; later positions lose keys
+    torch.testing.assert_close(a[:, :6], b[:, :6], rtol=1e-4, atol=1e-5)
+    assert not torch.allclose(a[:, 8:], b[:, 8:], atol=1e-4)
+    att = sparse.model.layers["0"].self_attn
+    ctx = sparse.model.make_context(ids)
+    x = sparse.model.embed(ids)
+    qa = att.q_a_layernorm(att.q_a_proj(x))
+    allowed = torch.ones(14, 14, dtype=torch.bool).tril()[None].expand(2, 14, 14)
+    vis = att.indexer.visible(x, qa, ctx, allowed)
+    assert (vis.sum(-1) == torch.arange(1, 15).clamp(max=6)[None]).all() and not (vis & ~allowed).any()
+    out = sparse.train()(ids, labels=torch.roll(ids, -1, 1))
+    out.loss.backward()
+    assert att.kv_b_proj.weight.grad.abs().sum() > 0 and att.indexer.wk.weight.grad is None      # selection is not differentiated
