@@ -608,6 +608,35 @@ class GptOssConfig(DecoderConfig):
         return d
 
 
+class MiniMaxConfig(MixtralConfig):
+    """MiniMax-Text-01: Mixtral's MoE blocks, alternating softmax attention and fixed-decay "lightning" linear attention
+    (``layer_types``), and a block whose residual stream continues from the normed input with per-branch alpha / beta factors
+    (paddleformers/transformers/minimax)."""
+
+    model_type = "minimax"
+
+    def __init__(self, layer_types=None, block_size=256, full_attn_alpha_factor=1, full_attn_beta_factor=1, linear_attn_alpha_factor=1,
+                 linear_attn_beta_factor=1, mlp_alpha_factor=1, mlp_beta_factor=1, **kw):
+        kw.setdefault("rope_theta", 1000000.0)
+        super().__init__(**kw)
+        n = self.num_hidden_layers
+        self.layer_types = list(layer_types) if layer_types else ["full_attention" if (i + 1) % 2 else "linear_attention" for i in range(n)]
+        self.block_size = block_size
+        self.full_attn_alpha_factor, self.full_attn_beta_factor = full_attn_alpha_factor, full_attn_beta_factor
+        self.linear_attn_alpha_factor, self.linear_attn_beta_factor = linear_attn_alpha_factor, linear_attn_beta_factor
+        self.mlp_alpha_factor, self.mlp_beta_factor = mlp_alpha_factor, mlp_beta_factor
+        self.block_style = "normed_residual"
+        self.linear_attention_kind = "lightning"
+        self.no_kv_cache = True
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if saving:
+            for k in ("block_style", "linear_attention_kind", "no_kv_cache"):
+                d.pop(k, None)
+        return d
+
+
 class MiniMaxM2Config(DecoderConfig):
     """MiniMax-M2: one RMSNorm over all heads' query / key features before the rotary embedding, every layer a sigmoid
     router with a selection-only correction bias and renormalised top-k weights, experts of the dense width, no shared
@@ -924,12 +953,11 @@ class Ernie4_5MoeConfig(Ernie4_5Config):
 CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, MiniCPMConfig, Olmo2Config,
                                             GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
                                             Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config, HunYuanDenseV1Config,
-                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig, Qwen3_5TextConfig, Qwen3_5MoeTextConfig)}
+                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig, Qwen3_5TextConfig, Qwen3_5MoeTextConfig, MiniMaxConfig)}
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
 # feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
 UNSUPPORTED_FAMILIES = { "deepseek_v4": "compressed sparse attention",
-    "minimax": "lightning (linear) attention hybrid",
     "gemma3": "SigLIP vision tower (the text decoder is available as gemma3_text)",
     "phi4_multimodal": "vision and audio towers", "diffllama": "differential attention",
 

@@ -31,7 +31,7 @@ from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
                             Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig,
                             GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig,
-                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig, Qwen3_5TextConfig, Qwen3_5MoeTextConfig, GlmMoeDsaConfig, DeepseekV32Config)
+                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig, Qwen3_5TextConfig, Qwen3_5MoeTextConfig, GlmMoeDsaConfig, DeepseekV32Config, MiniMaxConfig)
 
 
 @dataclass
@@ -407,7 +407,15 @@ class DecoderLayer(nn.Module):
         # (attention and MLP read the same normed input and are added together: Cohere)
         # or "sandwich" (norm -> branch -> norm -> add, four norms per block: Gemma 3)
         self.block_style = getattr(config, "block_style", "pre") or "pre"
-        if self.block_style == "sandwich":
+        # or "normed_residual" (MiniMax-Text: the residual stream continues from the NORMED input, x <- a * norm(x) + b * branch)
+        if self.block_style == "normed_residual":
+            self.input_layernorm = make_norm(config, config.hidden_size, sp, dtype=dtype, device=device)
+            self.post_attention_layernorm = make_norm(config, config.hidden_size, sp, dtype=dtype, device=device)
+            lin = bool(getattr(config, "layer_types", None)) and config.layer_types[layer_idx] == "linear_attention"
+            self.attn_ab = (float(getattr(config, "linear_attn_alpha_factor" if lin else "full_attn_alpha_factor", 1.0)),
+                            float(getattr(config, "linear_attn_beta_factor" if lin else "full_attn_beta_factor", 1.0)))
+            self.mlp_ab = (float(getattr(config, "mlp_alpha_factor", 1.0)), float(getattr(config, "mlp_beta_factor", 1.0)))
+        elif self.block_style == "sandwich":
             for nm in ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm"):
                 setattr(self, nm, make_norm(config, config.hidden_size, sp, dtype=dtype, device=device))
         elif self.block_style != "parallel":
@@ -421,10 +429,12 @@ class DecoderLayer(nn.Module):
         attn_cls = MLAAttention if config.is_mla else Attention
         types = getattr(config, "layer_types", None)
         if types and layer_idx < len(types) and types[layer_idx] == "linear_attention":
-            from ..nn.linear_attention import GatedDeltaNet
+            from ..nn.linear_attention import GatedDeltaNet, LightningAttention
 
-            # gated delta-rule token mixer instead of softmax attention (Qwen3-Next); called like an attention module
-            self.linear_attn = GatedDeltaNet(config, layer_idx, dtype=dtype, device=device)
+            # a linear-attention token mixer instead of softmax attention: gated delta rule (Qwen3-Next) or fixed-decay
+            # "lightning" attention (MiniMax-Text); called like an attention module
+            mixer = LightningAttention if getattr(config, "linear_attention_kind", "gated_delta") == "lightning" else GatedDeltaNet
+            self.linear_attn = mixer(config, layer_idx, dtype=dtype, device=device)
             self.self_attn = self.linear_attn.forward
         else:
             self.self_attn = attn_cls(config, layer_idx, dtype=dtype, device=device)
@@ -447,6 +457,11 @@ class DecoderLayer(nn.Module):
         next RMSNorm kernel."""
         if self.block_style != "pre":
             x = hidden if residual is None else hidden + residual
+            if self.block_style == "normed_residual":
+                h = self.input_layernorm(x)
+                x = h * self.attn_ab[0] + self.self_attn(h, ctx, cache) * self.attn_ab[1]
+                h = self.post_attention_layernorm(x)
+                return h * self.mlp_ab[0] + self.mlp(h) * self.mlp_ab[1], None
             if self.block_style == "sandwich":
                 x = x + self.post_attention_layernorm(self.self_attn(self.input_layernorm(x), ctx, cache))
                 return x + self.post_feedforward_layernorm(self.mlp(self.pre_feedforward_layernorm(x))), None
@@ -914,6 +929,10 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
     n_total = config.num_hidden_layers + int(getattr(config, "num_nextn_predict_layers", 0) or 0)
     for i in range(config.num_hidden_layers):
         rules.extend(expand_layers(per_layer, [i]))
+        if getattr(config, "linear_attention_kind", None) == "lightning" and config.layer_types[i] == "linear_attention":
+            a, b = f"model.layers.{i}.linear_attn.", f"model.layers.{i}.self_attn."
+            rules += [Rule(a + "qkv.weight", [b + "qkv_proj.weight"]), Rule(a + "gate.weight", [b + "output_gate.weight"]),
+                      Rule(a + "out.weight", [b + "out_proj.weight"]), Rule(a + "norm.weight", [b + "norm.weight"])]
         if config.is_moe_layer(i):
             E = config.num_experts
             pre = f"model.layers.{i}.mlp."
@@ -1063,6 +1082,7 @@ StableLmForCausalLM = _family("StableLmForCausalLM", StableLmConfig)
 HunYuanDenseV1ForCausalLM = _family("HunYuanDenseV1ForCausalLM", HunYuanDenseV1Config)
 HunYuanMoEV1ForCausalLM = _family("HunYuanMoEV1ForCausalLM", HunYuanMoEV1Config)
 MiniMaxM2ForCausalLM = _family("MiniMaxM2ForCausalLM", MiniMaxM2Config)
+MiniMaxForCausalLM = _family("MiniMaxForCausalLM", MiniMaxConfig)
 MixtralForCausalLM = _family("MixtralForCausalLM", MixtralConfig)
 MiniCPM3ForCausalLM = _family("MiniCPM3ForCausalLM", MiniCPM3Config)
 InternLM2ForCausalLM = _family("InternLM2ForCausalLM", InternLM2Config)
@@ -1075,7 +1095,7 @@ Qwen3_5MoeForCausalLM = _family("Qwen3_5MoeForCausalLM", Qwen3_5MoeTextConfig)
 MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
     "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma2": Gemma2ForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
-    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "gpt_oss": GptOssForCausalLM, "llama4_text": Llama4ForCausalLM, "qwen3_next": Qwen3NextForCausalLM, "qwen3_5_text": Qwen3_5ForCausalLM, "qwen3_5_moe_text": Qwen3_5MoeForCausalLM,
+    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "minimax": MiniMaxForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "gpt_oss": GptOssForCausalLM, "llama4_text": Llama4ForCausalLM, "qwen3_next": Qwen3NextForCausalLM, "qwen3_5_text": Qwen3_5ForCausalLM, "qwen3_5_moe_text": Qwen3_5MoeForCausalLM,
     "qwen3_5": Qwen3_5ForCausalLM, "qwen3_5_moe": Qwen3_5MoeForCausalLM,
     "glm_moe_dsa": DeepseekV3ForCausalLM, "deepseek_v32": DeepseekV3ForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": DeepseekV3ForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,

@@ -136,3 +136,58 @@ class GatedDeltaNet(nn.Module):
         o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + self.eps)
         o = (self.norm.weight * o.to(x2d.dtype)) * TF.silu(z.float())
         return self.out_proj(o.to(x2d.dtype).reshape(B * S, self.value_dim))
+
+
+def decayed_linear_attention(q, k, v, slope, chunk: int = 64, state=None):
+    """Causal linear attention with a fixed exponential decay per head ("lightning attention", MiniMax-Text):
+    o_t = sum_{i <= t} exp(-slope_h (t - i)) (q_t . k_i) v_i. q, k, v: [B, S, H, D]; slope: [H] (> 0).
+    Inside a chunk the decayed score matrix is formed explicitly; across chunks a [D, D] state per head carries the sum of
+    decayed k v^T. Returns (o [B, S, H, D], final state [B, H, D, D])."""
+    B, S, H, D = q.shape
+    dtype = v.dtype
+    q, k, v = (x.float().transpose(1, 2) for x in (q, k, v))                       # [B, H, S, D]
+    slope = slope.float().view(1, H, 1, 1)
+    St = torch.zeros(B, H, D, v.shape[-1], dtype=torch.float32, device=q.device) if state is None else state.float()
+    outs = []
+    for lo in range(0, S, chunk):
+        qc, kc, vc = q[:, :, lo:lo + chunk], k[:, :, lo:lo + chunk], v[:, :, lo:lo + chunk]
+        n = qc.shape[2]
+        pos = torch.arange(n, device=q.device, dtype=torch.float32)
+        dist = pos[:, None] - pos[None, :]
+        decay = torch.where(dist >= 0, torch.exp(-slope * dist.clamp(min=0)), torch.zeros((), device=q.device))   # [1, H, n, n]
+        intra = ((qc @ kc.transpose(-1, -2)) * decay) @ vc
+        inter = (qc * torch.exp(-slope * (pos + 1).view(1, 1, n, 1))) @ St          # the state is "one step before the chunk"
+        outs.append(intra + inter)
+        St = St * torch.exp(-slope * n) + (kc * torch.exp(-slope * (n - 1 - pos).view(1, 1, n, 1))).transpose(-1, -2) @ vc
+    return torch.cat(outs, dim=2).transpose(1, 2).to(dtype), St
+
+
+class LightningAttention(nn.Module):
+    """MiniMax-Text's linear-attention mixer (paddleformers/transformers/minimax): SiLU on the fused q | k | v projection (laid out
+    per head), decayed linear attention with head- and depth-dependent slopes, RMSNorm over all heads, a sigmoid output gate
+    computed from the layer input, output projection."""
+
+    def __init__(self, config, layer_idx: int, dtype=None, device=None):
+        super().__init__()
+        kw = dict(dtype=dtype, device=device)
+        H, self.nh, self.hd = config.hidden_size, config.num_attention_heads, config.head_dim
+        self.chunk = int(getattr(config, "block_size", 64) or 64)
+        self.qkv = nn.Linear(H, 3 * self.nh * self.hd, bias=False, **kw)
+        self.gate = nn.Linear(H, self.nh * self.hd, bias=False, **kw)
+        self.out = nn.Linear(self.nh * self.hd, H, bias=False, **kw)
+        self.norm = nn.Module()
+        self.norm.weight = nn.Parameter(torch.ones(self.nh * self.hd, **kw))
+        self.eps = 1e-6
+        base = 1.0 / (2.0 ** (8.0 / self.nh))
+        depth = 1.0 - layer_idx / (config.num_hidden_layers - 1 + 1e-5) + 1e-5
+        self.register_buffer("slope", (base ** (torch.arange(self.nh, dtype=torch.float32, device=device) + 1)) * depth, persistent=False)
+
+    def forward(self, x2d, ctx, cache=None):
+        if cache is not None:
+            raise NotImplementedError("incremental decoding state for linear-attention layers is not kept: decode without a cache")
+        B, S = ctx.B, ctx.S
+        q, k, v = TF.silu(self.qkv(x2d)).view(B, S, self.nh, 3 * self.hd).split(self.hd, dim=-1)
+        o, _ = decayed_linear_attention(q, k, v, self.slope, self.chunk)
+        o = o.reshape(B * S, self.nh * self.hd).float()
+        o = (o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + self.eps)).to(x2d.dtype) * self.norm.weight
+        return self.out(torch.sigmoid(self.gate(x2d)) * o)

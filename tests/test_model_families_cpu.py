@@ -526,3 +526,22 @@ def test_sparse_indexer_attention_selects_keys_only_beyond_its_budget():
     out = sparse.train()(ids, labels=torch.roll(ids, -1, 1))
     out.loss.backward()
     assert att.kv_b_proj.weight.grad.abs().sum() > 0 and att.indexer.wk.weight.grad is None      # selection is not differentiated
+
+
+def test_decayed_linear_attention_matches_the_double_sum():
+    from paddleformers_b200.nn.linear_attention import decayed_linear_attention
+
+    torch.manual_seed(0)
+    B, S, H, D = 2, 21, 3, 4
+    q, k, v = (torch.randn(B, S, H, D) for _ in range(3))
+    slope = torch.tensor([0.5, 0.1, 0.02])
+    ref = torch.zeros(B, S, H, D)
+    for t in range(S):
+        for i in range(t + 1):
+            ref[:, t] += torch.exp(-slope * (t - i))[None, :, None] * (q[:, t] * k[:, i]).sum(-1, keepdim=True) * v[:, i]
+    for chunk in (4, 8, 64):
+        out, state = decayed_linear_attention(q, k, v, slope, chunk)
+        torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-5)
+    first, st = decayed_linear_attention(q[:, :9], k[:, :9], v[:, :9], slope, 4)
+    rest, _ = decayed_linear_attention(q[:, 9:], k[:, 9:], v[:, 9:], slope, 4, state=st)
+    torch.testing.assert_close(torch.cat([first, rest], 1), ref, rtol=1e-4, atol=1e-5)
