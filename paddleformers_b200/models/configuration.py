@@ -608,6 +608,28 @@ class GptOssConfig(DecoderConfig):
         return d
 
 
+class DiffLlamaConfig(DecoderConfig):
+    """Differential Transformer on Llama blocks: attention heads work in pairs and subtract a learned multiple of the second
+    head's attention from the first (paddleformers/transformers/diff_transformer)."""
+
+    model_type = "diffllama"
+
+    def __init__(self, lambda_std_dev=0.1, **kw):
+        kw.setdefault("rms_norm_eps", 1e-5)
+        super().__init__(**kw)
+        self.lambda_std_dev = lambda_std_dev
+        self.differential_attention = True
+        self.attention_out_bias = bool(self.attention_bias)
+        self.no_kv_cache = True
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if saving:
+            for k in ("differential_attention", "no_kv_cache"):
+                d.pop(k, None)
+        return d
+
+
 class MiniMaxConfig(MixtralConfig):
     """MiniMax-Text-01: Mixtral's MoE blocks, alternating softmax attention and fixed-decay "lightning" linear attention
     (``layer_types``), and a block whose residual stream continues from the normed input with per-branch alpha / beta factors
@@ -953,13 +975,13 @@ class Ernie4_5MoeConfig(Ernie4_5Config):
 CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Qwen2MoeConfig, GraniteConfig, MiniCPMConfig, Olmo2Config,
                                             GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig, LlamaConfig, Qwen2Config, Qwen3Config, Qwen3MoeConfig, DeepseekV3Config,
                                             Glm4MoeConfig, MistralConfig, Phi3Config, SeedOssConfig, InternLM3Config, HunYuanDenseV1Config,
-                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig, Qwen3_5TextConfig, Qwen3_5MoeTextConfig, MiniMaxConfig)}
+                                            HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig, Qwen3_5TextConfig, Qwen3_5MoeTextConfig, MiniMaxConfig, DiffLlamaConfig)}
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
 # feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
 UNSUPPORTED_FAMILIES = { "deepseek_v4": "compressed sparse attention",
     "gemma3": "SigLIP vision tower (the text decoder is available as gemma3_text)",
-    "phi4_multimodal": "vision and audio towers", "diffllama": "differential attention",
+    "phi4_multimodal": "vision and audio towers",
 
 
     "ernie4_5_vl": "vision tower, modality-aware experts", "paddleocr_vl": "vision tower", "glm4v_moe": "vision tower",

@@ -31,7 +31,7 @@ from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
                             Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig,
                             GraniteConfig, MiniCPMConfig, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig,
-                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig, Qwen3_5TextConfig, Qwen3_5MoeTextConfig, GlmMoeDsaConfig, DeepseekV32Config, MiniMaxConfig)
+                            HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig, Qwen3_5TextConfig, Qwen3_5MoeTextConfig, GlmMoeDsaConfig, DeepseekV32Config, MiniMaxConfig, DiffLlamaConfig)
 
 
 @dataclass
@@ -207,6 +207,15 @@ class Attention(nn.Module):
         self.use_rope = bool(self.window) or not getattr(config, "rope_on_window_layers_only", False)
         # Llama 4: chunked local layers; listed layers without rotary embedding; a weightless L2 norm of q and k after the
         # rotation on the rotating layers; position-dependent query scale on the others
+        # differential attention (DiffLlama): heads work in pairs (j, j + H/2); the pair's output is softmax_j V - lambda *
+        # softmax_{j+H/2} V on a value twice as wide (both halves' values side by side), RMS-normalised without weights
+        self.differential = bool(getattr(config, "differential_attention", False))
+        if self.differential:
+            assert tp == 1 and self.Hq % 2 == 0, "differential attention: even head count, tensor-parallel degree 1"
+            std = float(getattr(config, "lambda_std_dev", 0.1))
+            for nm in ("lambda_q1", "lambda_k1", "lambda_q2", "lambda_k2"):
+                setattr(self, nm, nn.Parameter(torch.randn(self.D, dtype=dtype, device=device) * std))
+            self.lambda_init = 0.8 - 0.6 * math.exp(-0.3 * layer_idx)
         self.chunk = config.layer_chunk(layer_idx)
         nope = getattr(config, "no_rope_layers", None)
         if nope is not None and layer_idx < len(nope):
@@ -254,6 +263,22 @@ class Attention(nn.Module):
                 sc = torch.log1p(torch.floor((pos.float() + 1.0) / float(self.config.floor_scale))) * float(self.config.attn_scale) + 1.0
                 q = (q.float() * sc[:, None]).to(qkv.dtype)
             qkv = torch.cat([q, k, qkv[:, nq + nk:]], dim=-1)
+        if self.differential:
+            if cache is not None or ctx.S_full:
+                raise NotImplementedError("differential attention: no incremental cache, no context / segment parallelism")
+            B, S, D, half = ctx.B, ctx.S, self.D, self.Hq // 2
+            rep = self.Hq // self.Hkv
+            q, k, v = qkv.view(B, S, -1).split([self.Hq * D, self.Hkv * D, self.Hkv * D], dim=-1)
+            q = q.reshape(B, S, self.Hq, D)
+            k = k.reshape(B, S, self.Hkv, D).repeat_interleave(rep, dim=2)
+            v = v.reshape(B, S, self.Hkv, D).repeat_interleave(rep, dim=2)
+            v2 = torch.cat([v[:, :, :half], v[:, :, half:]], dim=-1).repeat(1, 1, 2, 1)          # [B, S, Hq, 2D]
+            o = F.flash_attention(q, k.contiguous(), v2.contiguous(), True, kend, self.scale)
+            lam = torch.exp((self.lambda_q1.float() * self.lambda_k1.float()).sum()) \
+                - torch.exp((self.lambda_q2.float() * self.lambda_k2.float()).sum()) + self.lambda_init
+            o = o[:, :, :half].float() - lam * o[:, :, half:].float()
+            o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + self.config.rms_norm_eps) * (1.0 - self.lambda_init)
+            return _apply(self.o_proj, o.to(x2d.dtype).reshape(B * S, self.Hq * D))
         if cache is not None:
             out = cache.attend(self, qkv, ctx)
         elif (self.softcap or self.sinks is not None or getattr(self.config, "_attn_implementation", None) in ("eager", "sdpa")) \
@@ -1083,6 +1108,7 @@ HunYuanDenseV1ForCausalLM = _family("HunYuanDenseV1ForCausalLM", HunYuanDenseV1C
 HunYuanMoEV1ForCausalLM = _family("HunYuanMoEV1ForCausalLM", HunYuanMoEV1Config)
 MiniMaxM2ForCausalLM = _family("MiniMaxM2ForCausalLM", MiniMaxM2Config)
 MiniMaxForCausalLM = _family("MiniMaxForCausalLM", MiniMaxConfig)
+DiffLlamaForCausalLM = _family("DiffLlamaForCausalLM", DiffLlamaConfig)
 MixtralForCausalLM = _family("MixtralForCausalLM", MixtralConfig)
 MiniCPM3ForCausalLM = _family("MiniCPM3ForCausalLM", MiniCPM3Config)
 InternLM2ForCausalLM = _family("InternLM2ForCausalLM", InternLM2Config)
@@ -1095,7 +1121,7 @@ Qwen3_5MoeForCausalLM = _family("Qwen3_5MoeForCausalLM", Qwen3_5MoeTextConfig)
 MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
     "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma2": Gemma2ForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
-    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "minimax": MiniMaxForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "gpt_oss": GptOssForCausalLM, "llama4_text": Llama4ForCausalLM, "qwen3_next": Qwen3NextForCausalLM, "qwen3_5_text": Qwen3_5ForCausalLM, "qwen3_5_moe_text": Qwen3_5MoeForCausalLM,
+    "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "minimax": MiniMaxForCausalLM, "diffllama": DiffLlamaForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "gpt_oss": GptOssForCausalLM, "llama4_text": Llama4ForCausalLM, "qwen3_next": Qwen3NextForCausalLM, "qwen3_5_text": Qwen3_5ForCausalLM, "qwen3_5_moe_text": Qwen3_5MoeForCausalLM,
     "qwen3_5": Qwen3_5ForCausalLM, "qwen3_5_moe": Qwen3_5MoeForCausalLM,
     "glm_moe_dsa": DeepseekV3ForCausalLM, "deepseek_v32": DeepseekV3ForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": DeepseekV3ForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,

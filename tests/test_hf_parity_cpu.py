@@ -114,6 +114,7 @@ CASES = {
         head_dim=16, intermediate_size=48, num_hidden_layers=4, num_local_experts=4, num_experts_per_tok=2, block_size=8,
         full_attn_alpha_factor=1.5, full_attn_beta_factor=0.8, linear_attn_alpha_factor=1.2, linear_attn_beta_factor=0.9,
         mlp_alpha_factor=1.1, mlp_beta_factor=0.7)),
+    "diffllama": ("DiffLlamaConfig", "DiffLlamaForCausalLM", dict(num_hidden_layers=3)),
     "mixtral": ("MixtralConfig", "MixtralForCausalLM", dict(num_local_experts=4, num_experts_per_tok=2, sliding_window=8)),
     "stablelm": ("StableLmConfig", "StableLmForCausalLM", dict(use_qkv_bias=True, partial_rotary_factor=0.25)),
     "glm4_moe": ("Glm4MoeConfig", "Glm4MoeForCausalLM", dict(head_dim=16, moe_intermediate_size=32, n_routed_experts=4, num_experts_per_tok=2,
@@ -149,7 +150,7 @@ def test_logits_match_hugging_face_implementation(tmp_path, family):
     torch.testing.assert_close(got, want, rtol=2e-4, atol=2e-4)
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma2", "gemma3_text", "cohere", "cohere2", "olmo2", "hunyuan_v1_dense", "hunyuan_v1_moe", "minimax_m2", "mixtral", "deepseek_v2", "gpt_oss", "llama4_text", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "glm4_moe_lite", "glm_moe_dsa", "minimax",
+@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3_moe", "deepseek_v3", "glm4_moe", "ernie4_5", "phi3", "gemma", "gemma2", "gemma3_text", "cohere", "cohere2", "olmo2", "hunyuan_v1_dense", "hunyuan_v1_moe", "minimax_m2", "mixtral", "deepseek_v2", "gpt_oss", "llama4_text", "qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "glm4_moe_lite", "glm_moe_dsa", "minimax", "diffllama",
                                     "stablelm", "granite", "qwen2_moe", "ernie4_5_moe"])
 def test_hugging_face_loads_what_this_framework_saves(tmp_path, family):
     """The other direction: a checkpoint written by ``save_pretrained`` here (per-expert tensors, interleaved rotary rows
