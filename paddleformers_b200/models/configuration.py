@@ -443,8 +443,7 @@ class Qwen3NextConfig(DecoderConfig):
     """Qwen3-Next: three of four layers mix tokens with a gated delta-rule linear attention (``nn.linear_attention``), the
     fourth with softmax attention whose output is gated by a sigmoid computed from the query projection; rotary embedding on a
     quarter of each head, per-head QK norm, zero-centred RMSNorm weights ((1 + w), stored as w), MoE layers with a gated
-    shared expert (paddleformers/transformers/qwen3_next). The linear-attention layers run as tensor operations and keep no
-    decoding state: generation recomputes the prefix."""
+    shared expert (paddleformers/transformers/qwen3_next). The linear-attention layers run as tensor operations."""
 
     model_type = "qwen3_next"
 
@@ -468,7 +467,6 @@ class Qwen3NextConfig(DecoderConfig):
         self.linear_conv_kernel_dim = linear_conv_kernel_dim
         self.attention_output_gate = True
         self.norm_weight_offset = 1.0
-        self.no_kv_cache = True
         self.shared_expert_gate = bool(self.n_shared_experts)
         self.shared_expert_hf_name = "shared_expert"
 
@@ -649,7 +647,6 @@ class MiniMaxConfig(MixtralConfig):
         self.mlp_alpha_factor, self.mlp_beta_factor = mlp_alpha_factor, mlp_beta_factor
         self.block_style = "normed_residual"
         self.linear_attention_kind = "lightning"
-        self.no_kv_cache = True
 
     def to_dict(self, saving: bool = False):
         d = super().to_dict(saving)

@@ -17,7 +17,8 @@ token-by-token recurrence above, used by the tests.
 ``GatedDeltaNet`` is the full mixer (paddleformers/transformers/qwen3_next): fused input projections grouped by key head
 (q, k, v, output gate z; write strength and decay inputs), a causal depth-wise convolution with SiLU over q | k | v, L2-normalised
 q and k, decay a_t = exp(-exp(A_log) softplus(x_a + dt_bias)), a per-head RMSNorm of the read-out gated by SiLU(z), and the
-output projection. It runs as tensor operations on every device.
+output projection. It runs as tensor operations on every device; with a cache object it continues from the stored
+convolution tail and recurrent state (incremental decoding).
 """
 from __future__ import annotations
 
@@ -104,8 +105,8 @@ class GatedDeltaNet(nn.Module):
         self.out_proj = nn.Linear(self.value_dim, H, bias=False, **kw)
 
     def forward(self, x2d: torch.Tensor, ctx, cache=None) -> torch.Tensor:
-        if cache is not None:
-            raise NotImplementedError("incremental decoding state for linear-attention layers is not kept: decode without a cache")
+        """``cache`` (any object; attributes are added to it) keeps what incremental decoding needs between calls: the last
+        ``kernel - 1`` inputs of the convolution and the recurrent state."""
         B, S = ctx.B, ctx.S
         r = self.nv // self.nk
         if self.split_proj:
@@ -118,7 +119,15 @@ class GatedDeltaNet(nn.Module):
             q, k, v, z = qkvz.split([self.dk, self.dk, r * self.dv, r * self.dv], dim=-1)
             b, a = ba.split([r, r], dim=-1)
             mixed = torch.cat([q.reshape(B, S, -1), k.reshape(B, S, -1), v.reshape(B, S, -1)], dim=-1).transpose(1, 2)
-        mixed = TF.silu(self.conv1d(mixed)[:, :, :S]).transpose(1, 2)          # causal: left padding, right part dropped
+        if cache is None:
+            mixed = TF.silu(self.conv1d(mixed)[:, :, :S]).transpose(1, 2)      # causal: left padding, right part dropped
+        else:
+            tail = getattr(cache, "conv_tail", None)
+            if tail is None:
+                tail = mixed.new_zeros(B, mixed.shape[1], self.kernel - 1)
+            padded = torch.cat([tail, mixed], dim=-1)
+            cache.conv_tail = padded[:, :, -(self.kernel - 1):].detach()
+            mixed = TF.silu(TF.conv1d(padded, self.conv1d.weight, None, groups=padded.shape[1])).transpose(1, 2)
         q, k, v = mixed.split([self.key_dim, self.key_dim, self.value_dim], dim=-1)
         q, k = q.reshape(B, S, self.nk, self.dk), k.reshape(B, S, self.nk, self.dk)
         v, z = v.reshape(B, S, self.nv, self.dv), z.reshape(B, S, self.nv, self.dv)
@@ -131,7 +140,10 @@ class GatedDeltaNet(nn.Module):
             t = t.float()
             return t * torch.rsqrt(t.pow(2).sum(-1, keepdim=True) + 1e-6)
 
-        o, _ = gated_delta_rule(l2(q) * self.dk ** -0.5, l2(k), v, log_decay, beta)
+        o, state = gated_delta_rule(l2(q) * self.dk ** -0.5, l2(k), v, log_decay, beta,
+                                    state=getattr(cache, "linear_state", None) if cache is not None else None)
+        if cache is not None:
+            cache.linear_state = state.detach()
         o = o.float()
         o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + self.eps)
         o = (self.norm.weight * o.to(x2d.dtype)) * TF.silu(z.float())
@@ -183,11 +195,12 @@ class LightningAttention(nn.Module):
         self.register_buffer("slope", (base ** (torch.arange(self.nh, dtype=torch.float32, device=device) + 1)) * depth, persistent=False)
 
     def forward(self, x2d, ctx, cache=None):
-        if cache is not None:
-            raise NotImplementedError("incremental decoding state for linear-attention layers is not kept: decode without a cache")
         B, S = ctx.B, ctx.S
         q, k, v = TF.silu(self.qkv(x2d)).view(B, S, self.nh, 3 * self.hd).split(self.hd, dim=-1)
-        o, _ = decayed_linear_attention(q, k, v, self.slope, self.chunk)
+        o, state = decayed_linear_attention(q, k, v, self.slope, self.chunk,
+                                            state=getattr(cache, "linear_state", None) if cache is not None else None)
+        if cache is not None:               # incremental decoding: the decayed sum of k v^T so far
+            cache.linear_state = state.detach()
         o = o.reshape(B * S, self.nh * self.hd).float()
         o = (o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + self.eps)).to(x2d.dtype) * self.norm.weight
         return self.out(torch.sigmoid(self.gate(x2d)) * o)

@@ -547,3 +547,27 @@ def test_decayed_linear_attention_matches_the_double_sum():
     first, st = decayed_linear_attention(q[:, :9], k[:, :9], v[:, :9], slope, 4)
     rest, _ = decayed_linear_attention(q[:, 9:], k[:, 9:], v[:, 9:], slope, 4, state=st)
     torch.testing.assert_close(torch.cat([first, rest], 1), ref, rtol=1e-4, atol=1e-5)
+
+
+def test_linear_attention_layers_decode_incrementally():
+    """Generation keeps the convolution tail and the recurrent state of linear-attention layers (and the keys / values of the
+    softmax layers): the tokens equal those of a full forward over the generated prefix, for both mixer kinds."""
+    from paddleformers_b200.generation.utils import GenerationConfig, KVCache, generate
+
+    mm = AutoConfig.for_model("minimax", **{**TINY, "num_hidden_layers": 4, "num_local_experts": 4, "num_experts_per_tok": 2,
+                                            "intermediate_size": 24, "block_size": 4})
+    nx = AutoConfig.for_model("qwen3_next", **{**TINY, "num_hidden_layers": 4, "linear_num_value_heads": 4, "linear_num_key_heads": 2,
+                                              "linear_key_head_dim": 8, "linear_value_head_dim": 8})
+    for cfg in (mm, nx):
+        torch.manual_seed(0)
+        model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32).eval()
+        ids = torch.randint(0, 96, (2, 9))
+        with torch.no_grad():
+            seq = generate(model, ids, GenerationConfig(max_new_tokens=6))
+            full = model(seq[:, :-1], return_logits=True).logits
+            assert torch.equal(full[:, 8:].argmax(-1), seq[:, 9:])
+            # the cached path itself: prefix, then one token at a time, against the full forward
+            caches = {i: KVCache() for i in model.model.layer_range}
+            a = model(seq[:, :9], position_ids=torch.arange(9)[None].expand(2, -1), caches=caches, return_logits=True).logits
+            b = model(seq[:, 9:10], position_ids=torch.full((2, 1), 9), caches=caches, return_logits=True).logits
+            torch.testing.assert_close(torch.cat([a, b], 1), model(seq[:, :10], return_logits=True).logits, rtol=1e-4, atol=1e-4)
