@@ -981,7 +981,7 @@ UNSUPPORTED_FAMILIES = { "deepseek_v4": "compressed sparse attention",
     "phi4_multimodal": "vision and audio towers",
 
 
-    "ernie4_5_vl": "vision tower, modality-aware experts", "paddleocr_vl": "vision tower", "glm4v_moe": "vision tower",
+    "ernie4_5_vl": "vision tower, modality-aware experts", "paddleocr_vl": "vision tower",
     "paligemma": "SigLIP vision tower", "whisper": "encoder-decoder speech model", "qwen3_omni_moe": "audio / vision towers",
 }
 

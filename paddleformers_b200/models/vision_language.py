@@ -110,18 +110,19 @@ class _RMSNorm(nn.Module):
 
 class _VisionBlock(nn.Module):
     def __init__(self, dim: int, heads: int, mlp_hidden: int, act: str, dtype=None, device=None, rms_norm: bool = False,
-                 swiglu: bool = False):
+                 swiglu: bool = False, bias: bool = True, eps: float = 1e-6, mlp_bias: Optional[bool] = None):
         super().__init__()
         kw = dict(dtype=dtype, device=device)
-        norm = (lambda: _RMSNorm(dim, 1e-6, **kw)) if rms_norm else (lambda: nn.LayerNorm(dim, eps=1e-6, **kw))
+        mlp_bias = bias if mlp_bias is None else mlp_bias
+        norm = (lambda: _RMSNorm(dim, eps, **kw)) if rms_norm else (lambda: nn.LayerNorm(dim, eps=eps, **kw))
         self.norm1, self.norm2 = norm(), norm()
-        self.qkv = nn.Linear(dim, 3 * dim, **kw)
-        self.proj = nn.Linear(dim, dim, **kw)
+        self.qkv = nn.Linear(dim, 3 * dim, bias=bias, **kw)
+        self.proj = nn.Linear(dim, dim, bias=bias, **kw)
         self.swiglu = swiglu
         if swiglu:
-            self.gate_proj = nn.Linear(dim, mlp_hidden, **kw)
-            self.up_proj = nn.Linear(dim, mlp_hidden, **kw)
-            self.down_proj = nn.Linear(mlp_hidden, dim, **kw)
+            self.gate_proj = nn.Linear(dim, mlp_hidden, bias=mlp_bias, **kw)
+            self.up_proj = nn.Linear(dim, mlp_hidden, bias=mlp_bias, **kw)
+            self.down_proj = nn.Linear(mlp_hidden, dim, bias=mlp_bias, **kw)
         else:
             self.fc1 = nn.Linear(dim, mlp_hidden, **kw)
             self.fc2 = nn.Linear(mlp_hidden, dim, **kw)
@@ -689,3 +690,173 @@ class Qwen3VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
 
 class Qwen3VLMoeForConditionalGeneration(Qwen3VLForConditionalGeneration):
     config_class = Qwen3VLMoeConfig
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# GLM-4.5V
+# ---------------------------------------------------------------------------------------------------------------
+class Glm4vMoeConfig(Qwen2VLConfig):
+    """GLM-4.5V: the GLM-4.5 MoE decoder with multimodal rotary sections on its rotated half of each head, and a vision tower
+    with RMSNorm / bias-free SwiGLU blocks, bicubically interpolated position embeddings, a strided-convolution merge of
+    2 x 2 patches and a gated merger MLP (paddleformers/transformers/glm4v_moe)."""
+
+    model_type = "glm4v_moe"
+
+    def __init__(self, text_config=None, vision_config=None, image_token_id=151363, video_token_id=151364, image_start_token_id=151339,
+                 image_end_token_id=151340, **kwargs):
+        from .configuration import Glm4MoeConfig
+
+        text = dict(text_config or {})
+        text.pop("model_type", None)
+        rp = dict(text.get("rope_parameters") or {})
+        section = list(rp.pop("mrope_section", None) or [8, 12, 12])
+        if "rope_parameters" in text:
+            text["rope_parameters"] = rp
+        tie = bool(text.get("tie_word_embeddings", kwargs.get("tie_word_embeddings", False)))
+        text.setdefault("tie_word_embeddings", tie)
+        text.setdefault("attention_bias", True)
+        text.setdefault("use_qk_norm", False)
+        for k in ("video_start_token_id", "video_end_token_id"):
+            kwargs.pop(k, None)
+        super().__init__(text_config={"num_hidden_layers": 1}, vision_config={}, image_token_id=image_token_id,
+                         video_token_id=video_token_id, vision_start_token_id=image_start_token_id,
+                         vision_end_token_id=image_end_token_id, **{**kwargs, "tie_word_embeddings": tie})
+        self.text_config = Glm4MoeConfig(**text)
+        self.mrope_section = section
+        self.image_start_token_id, self.image_end_token_id = image_start_token_id, image_end_token_id
+        v = dict(vision_config or {})
+        v.pop("model_type", None)
+        self.vision_config = {"depth": 24, "hidden_size": 1536, "hidden_act": "silu", "attention_bias": False, "num_heads": 12,
+                              "in_channels": 3, "image_size": 336, "patch_size": 14, "rms_norm_eps": 1e-5, "spatial_merge_size": 2,
+                              "temporal_patch_size": 2, "out_hidden_size": self.text_config.hidden_size, "intermediate_size": 13696, **v}
+
+    def to_dict(self, saving: bool = False):
+        d = PretrainedConfig.to_dict(self, saving)
+        text = self.text_config.to_dict(saving)
+        text["model_type"] = "glm4v_moe_text"
+        scaling = text.pop("rope_scaling", None) or {}
+        text["rope_parameters"] = {"rope_type": "default", **scaling, "rope_theta": text.pop("rope_theta", self.text_config.rope_theta),
+                                   "partial_rotary_factor": self.text_config.partial_rotary_factor, "mrope_section": self.mrope_section}
+        d["text_config"] = text
+        d["vision_config"] = dict(self.vision_config, model_type="glm4v_moe_vision")
+        for k in ("mrope_section", "vision_start_token_id", "vision_end_token_id"):
+            d.pop(k, None)
+        return d
+
+
+class Glm4vVisionTower(VisionTower):
+    def __init__(self, vc: dict, dtype=None, device=None):
+        nn.Module.__init__(self)
+        kw = dict(dtype=dtype, device=device)
+        self.vc = vc
+        dim, out, eps, ms = vc["hidden_size"], vc["out_hidden_size"], vc["rms_norm_eps"], vc["spatial_merge_size"]
+        self.patch_dim = vc["in_channels"] * vc["temporal_patch_size"] * vc["patch_size"] ** 2
+        self.patch_embed = nn.Linear(self.patch_dim, dim, bias=True, **kw)
+        self.post_conv_layernorm = _RMSNorm(dim, eps, **kw)
+        self.side = vc["image_size"] // vc["patch_size"]
+        self.position_embedding = nn.Embedding(self.side ** 2, dim, **kw)
+        # the blocks' MLP width is the OUTPUT width of the tower; ``intermediate_size`` belongs to the merger
+        self.blocks = nn.ModuleList([_VisionBlock(dim, vc["num_heads"], out, vc["hidden_act"], rms_norm=True, swiglu=True,
+                                                  bias=bool(vc.get("attention_bias", False)), mlp_bias=False, eps=eps, **kw) for _ in range(vc["depth"])])
+        self.post_layernorm = _RMSNorm(dim, eps, **kw)
+        self.downsample = nn.Linear(dim * ms * ms, out, bias=True, **kw)          # the stride-ms convolution over one merge block
+        self.merge_proj = nn.Linear(out, out, bias=False, **kw)
+        self.merge_norm = nn.LayerNorm(out, **kw)
+        self.merge_gate = nn.Linear(out, vc["intermediate_size"], bias=False, **kw)
+        self.merge_up = nn.Linear(out, vc["intermediate_size"], bias=False, **kw)
+        self.merge_down = nn.Linear(vc["intermediate_size"], out, bias=False, **kw)
+        self.head_dim = dim // vc["num_heads"]
+
+    def position_embeddings(self, grid_thw: torch.Tensor) -> torch.Tensor:
+        """Bicubic samples of the learned side x side table at the centre of every patch (coordinates relative to the image's own
+        grid), in the processor's merge-block patch order."""
+        ms, side = self.vc["spatial_merge_size"], self.side
+        table = self.position_embedding.weight
+        table2d = table.view(side, side, -1).permute(2, 0, 1)[None].float()
+        out = []
+        for t, h, w in grid_thw.tolist():
+            hp = torch.arange(h, device=table.device)[:, None].expand(h, w).reshape(h // ms, ms, w // ms, ms).permute(0, 2, 1, 3).flatten()
+            wp = torch.arange(w, device=table.device)[None, :].expand(h, w).reshape(h // ms, ms, w // ms, ms).permute(0, 2, 1, 3).flatten()
+            grid = torch.stack([(wp.float() + 0.5) / w * 2 - 1, (hp.float() + 0.5) / h * 2 - 1], dim=-1)[None, :, None, :]
+            e = TF.grid_sample(table2d, grid, mode="bicubic", align_corners=False, padding_mode="border")[0, :, :, 0].t()
+            out.append(e.to(table.dtype).repeat(t, 1))
+        return torch.cat(out, dim=0)
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
+        ms = self.vc["spatial_merge_size"]
+        x = self.post_conv_layernorm(self.patch_embed(pixel_values.to(self.patch_embed.weight.dtype)))
+        x = x + self.position_embeddings(grid_thw).to(x.dtype)
+        cos, sin = self.rotary(grid_thw, x.device)
+        lengths = [h * w for t, h, w in grid_thw.tolist() for _ in range(t)]
+        for blk in self.blocks:
+            x = blk(x, cos, sin, lengths)
+        x = self.post_layernorm(x)
+        # a merge block's ms x ms patches are consecutive rows: channel-major flattening matches the convolution's weight layout
+        x = x.view(-1, ms, ms, x.shape[-1]).permute(0, 3, 1, 2).reshape(-1, x.shape[-1] * ms * ms)
+        x = self.merge_proj(self.downsample(x))
+        x = TF.gelu(self.merge_norm(x))
+        return self.merge_down(TF.silu(self.merge_gate(x)) * self.merge_up(x))
+
+
+class Glm4vMoeForConditionalGeneration(Qwen2VLForConditionalGeneration):
+    config_class = Glm4vMoeConfig
+
+    def __init__(self, config: Glm4vMoeConfig, dtype=None, device=None):
+        PretrainedModel.__init__(self, config)
+        self.visual = Glm4vVisionTower(config.vision_config, dtype=dtype, device=device)
+        self.language = DecoderForCausalLM(config.text_config, dtype=dtype, device=device)
+        self._vision_prefix, self._text_nested = "model.visual.", True
+
+    def _context(self, input_ids, position_ids3) -> BatchContext:
+        B, S = input_ids.shape
+        lm = self.language.model
+        half = int(self.config.text_config.head_dim * self.config.text_config.partial_rotary_factor) // 2     # rotated frequencies
+        cos_t, sin_t = lm.rope(input_ids.device, int(position_ids3.max().item()) + 1)
+        sections = self.config.mrope_section
+        assert sum(sections) == half, "mrope sections must cover the rotated half of the head"
+        axis = torch.repeat_interleave(torch.arange(len(sections), device=input_ids.device) % 3,
+                                       torch.tensor(sections, device=input_ids.device))
+        sel = position_ids3.reshape(3, B * S)[axis]
+        col = torch.arange(half, device=input_ids.device)[:, None]
+        return BatchContext(B, S, torch.arange(B * S, device=input_ids.device), None, cos_t[sel, col].t().contiguous(),
+                            sin_t[sel, col].t().contiguous())
+
+    def load_hf_checkpoint(self, directory: str, strict: bool = False) -> None:
+        PretrainedModel.load_hf_checkpoint(self, directory, strict)
+
+    def weight_map(self) -> WeightMap:
+        vis = "model.visual."
+        rules = []
+        for r in build_weight_map(self.config.text_config).rules.values():
+            src = [x if x.startswith("lm_head.") else x.replace("model.", "model.language_model.", 1) for x in r.sources]
+            rules.append(Rule("language." + r.target, src, r.op, r.dim, r.num_experts, r.expert_pairs, r.sizes, r.rope_deinterleave,
+                              r.flatten, r.reshape, r.source_shape, r.offset, fn=r.fn, qkv_groups=r.qkv_groups))
+        known = {r.target for r in rules}
+        for name, _ in list(self.language.named_parameters()) + [(k, None) for k, _ in self.language.named_buffers()]:
+            if "language." + name not in known and (name in dict(self.language.named_parameters()) or name in self.language.state_dict()):
+                rules.append(Rule("language." + name, [name if name.startswith("lm_head.") else name.replace("model.", "model.language_model.", 1)]))
+        vc = self.config.vision_config
+        dim, out, ms = vc["hidden_size"], vc["out_hidden_size"], vc["spatial_merge_size"]
+        conv_shape = [dim, vc["in_channels"], vc["temporal_patch_size"], vc["patch_size"], vc["patch_size"]]
+        rules += [Rule("visual.patch_embed.weight", [vis + "patch_embed.proj.weight"], reshape=[dim, -1], source_shape=conv_shape),
+                  Rule("visual.patch_embed.bias", [vis + "patch_embed.proj.bias"]),
+                  Rule("visual.post_conv_layernorm.weight", [vis + "post_conv_layernorm.weight"]),
+                  Rule("visual.position_embedding.weight", [vis + "embeddings.position_embedding.weight"]),
+                  Rule("visual.post_layernorm.weight", [vis + "post_layernorm.weight"]),
+                  Rule("visual.downsample.weight", [vis + "downsample.weight"], reshape=[out, -1], source_shape=[out, dim, ms, ms]),
+                  Rule("visual.downsample.bias", [vis + "downsample.bias"]),
+                  Rule("visual.merge_proj.weight", [vis + "merger.proj.weight"]),
+                  Rule("visual.merge_norm.weight", [vis + "merger.post_projection_norm.weight"]),
+                  Rule("visual.merge_norm.bias", [vis + "merger.post_projection_norm.bias"]),
+                  Rule("visual.merge_gate.weight", [vis + "merger.gate_proj.weight"]),
+                  Rule("visual.merge_up.weight", [vis + "merger.up_proj.weight"]),
+                  Rule("visual.merge_down.weight", [vis + "merger.down_proj.weight"])]
+        own = dict(self.visual.named_parameters())
+        for i in range(vc["depth"]):
+            a, b = f"visual.blocks.{i}.", vis + f"blocks.{i}."
+            for mine, theirs in (("norm1", "norm1"), ("norm2", "norm2"), ("qkv", "attn.qkv"), ("proj", "attn.proj"),
+                                 ("gate_proj", "mlp.gate_proj"), ("up_proj", "mlp.up_proj"), ("down_proj", "mlp.down_proj")):
+                for leaf in ("weight", "bias"):
+                    if f"blocks.{i}.{mine}.{leaf}" in own:
+                        rules.append(Rule(a + f"{mine}.{leaf}", [b + f"{theirs}.{leaf}"]))
+        return WeightMap(rules)

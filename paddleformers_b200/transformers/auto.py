@@ -50,12 +50,14 @@ class AutoModelForConditionalGeneration:
     def _classes(model_type: str):
         from ..models.vision_language import (Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration, Qwen2VLConfig,
                                               Qwen2VLForConditionalGeneration, Qwen3VLConfig, Qwen3VLForConditionalGeneration,
-                                              Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration)
+                                              Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration, Glm4vMoeConfig,
+                                              Glm4vMoeForConditionalGeneration)
 
         table = {"qwen2_vl": (Qwen2VLConfig, Qwen2VLForConditionalGeneration),
                  "qwen2_5_vl": (Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration),
                  "qwen3_vl": (Qwen3VLConfig, Qwen3VLForConditionalGeneration),
-                 "qwen3_vl_moe": (Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration)}
+                 "qwen3_vl_moe": (Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration),
+                 "glm4v_moe": (Glm4vMoeConfig, Glm4vMoeForConditionalGeneration)}
         if model_type not in table:
             raise ValueError(f"unknown vision-language model_type {model_type!r}; supported: {sorted(table)}")
         return table[model_type]

@@ -517,3 +517,45 @@ def test_gpt_oss_mxfp4_checkpoint_loads_through_the_virtual_tensors(tmp_path):
     ids = torch.randint(0, 128, (2, 20))
     with torch.no_grad():
         torch.testing.assert_close(mine(ids, return_logits=True).logits, hf(input_ids=ids).logits, rtol=2e-4, atol=2e-4)
+
+
+def test_glm4v_moe_matches_hugging_face(tmp_path):
+    """GLM-4.5V: bicubic position-embedding samples, strided-convolution patch merge, gated merger, multimodal rotary sections on
+    the rotated half of each head, GLM-4.5 MoE decoder with biases, against ``transformers`` on two images between text tokens."""
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    if not hasattr(transformers, "Glm4vMoeForConditionalGeneration"):
+        pytest.skip("transformers has no GLM-4.5V")
+    torch.manual_seed(11)
+    vc = dict(depth=2, hidden_size=32, intermediate_size=48, num_heads=2, in_channels=3, image_size=24, patch_size=4, spatial_merge_size=2,
+              temporal_patch_size=2, out_hidden_size=64)
+    tc = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=16, max_position_embeddings=128, tie_word_embeddings=False, moe_intermediate_size=32, n_routed_experts=4,
+              num_experts_per_tok=2, n_shared_experts=1, first_k_dense_replace=1, n_group=1, topk_group=1,
+              rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5, "mrope_section": [2, 1, 1]})
+    cfg = transformers.Glm4vMoeConfig(text_config=tc, vision_config=vc, image_token_id=120, video_token_id=121,
+                                      image_start_token_id=118, image_end_token_id=119)
+    hf = transformers.Glm4vMoeForConditionalGeneration(cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.dim() == 1:
+                p.normal_(1.0 if "norm" in n and "bias" not in n else 0.0, 0.1)
+        for n, b in hf.named_buffers():
+            if "e_score_correction_bias" in n:
+                b.normal_(0.0, 0.1)
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path), dtype=torch.float32).eval()
+    grid = torch.tensor([[1, 4, 6], [1, 2, 2]])
+    pixels = torch.randn(int(grid.prod(-1).sum()), 3 * 2 * 4 * 4)
+    ids = torch.tensor([[5, 6, 118] + [120] * 6 + [119, 7, 8, 9, 118, 120, 119, 10, 11]])
+    types = (ids == 120).int()
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=types).logits
+        got = mine(ids, pixel_values=pixels, image_grid_thw=grid, return_logits=True).logits
+    torch.testing.assert_close(got, want, rtol=3e-4, atol=3e-4)
+    out = tmp_path / "out"
+    mine.save_pretrained(str(out))
+    back = transformers.Glm4vMoeForConditionalGeneration.from_pretrained(str(out), torch_dtype=torch.float32).eval()
+    with torch.no_grad():
+        torch.testing.assert_close(back(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=types).logits, want,
+                                   rtol=3e-4, atol=3e-4)
