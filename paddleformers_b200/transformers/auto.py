@@ -73,6 +73,29 @@ class AutoModelForConditionalGeneration:
         return model_cls.from_pretrained(path, config=cfg_cls.from_pretrained(path), dtype=dtype, device=device, **kw)
 
 
+class AutoModel:
+    """Encoders without a language-model head (image towers)."""
+
+    @staticmethod
+    def _classes(model_type: str):
+        from ..models.siglip import SiglipVisionConfig, SiglipVisionModel
+
+        table = {"siglip_vision_model": (SiglipVisionConfig, SiglipVisionModel)}
+        if model_type not in table:
+            raise ValueError(f"unknown encoder model_type {model_type!r}; supported: {sorted(table)}")
+        return table[model_type]
+
+    @classmethod
+    def from_config(cls, config, dtype=None, device=None, **kw):
+        return cls._classes(config.model_type)[1].from_config(config, dtype=dtype, device=device, **kw)
+
+    @classmethod
+    def from_pretrained(cls, path: str, dtype=None, device=None, **kw):
+        mt = PretrainedConfig.get_config_dict(path).get("model_type")
+        cfg_cls, model_cls = cls._classes(mt)
+        return model_cls.from_pretrained(path, config=cfg_cls.from_pretrained(path), dtype=dtype, device=device, **kw)
+
+
 class AutoModelForCausalLMPipe(AutoModelForCausalLM):
     """Pipeline-parallel variant: builds only this stage's layers (see ``parallel.pipeline``)."""
 

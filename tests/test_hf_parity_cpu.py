@@ -559,3 +559,32 @@ def test_glm4v_moe_matches_hugging_face(tmp_path):
     with torch.no_grad():
         torch.testing.assert_close(back(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=types).logits, want,
                                    rtol=3e-4, atol=3e-4)
+
+
+@pytest.mark.parametrize("use_head", [True, False])
+def test_siglip_vision_tower_matches_hugging_face(tmp_path, use_head):
+    """Hidden states and the probe-attention pooled vector, loaded from a checkpoint written by transformers; a checkpoint
+    written here loads back into transformers with identical outputs."""
+    from transformers import SiglipVisionConfig as HFConfig, SiglipVisionModel as HFModel
+
+    from paddleformers_b200.transformers.auto import AutoModel
+
+    torch.manual_seed(0)
+    hf = HFModel(HFConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, image_size=32,
+                          patch_size=8, vision_use_head=use_head)).eval()
+    hf.save_pretrained(tmp_path / "hf")
+    mine = AutoModel.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).eval()
+    x = torch.randn(2, 3, 32, 32)
+    with torch.no_grad():
+        want = hf(pixel_values=x)
+        hidden, pooled = mine(x)
+    assert (want.last_hidden_state - hidden).abs().max() < 1e-4
+    if use_head:
+        assert (want.pooler_output - pooled).abs().max() < 1e-4
+    else:
+        assert pooled is None
+    mine.save_pretrained(str(tmp_path / "mine"))
+    back = HFModel.from_pretrained(tmp_path / "mine").eval()
+    with torch.no_grad():
+        again = back(pixel_values=x)
+    assert (again.last_hidden_state - want.last_hidden_state).abs().max() < 1e-5
