@@ -51,6 +51,7 @@ class BatchContext:
     window: int = 0
     cos_local: Optional[torch.Tensor] = None      # rotary tables of sliding-window layers when they use their own base
     sin_local: Optional[torch.Tensor] = None
+    kstart: Optional[torch.Tensor] = None         # [B, S] first row that sees key j (blocks with two-way attention); None = causal
 
 
 @dataclass
@@ -281,21 +282,24 @@ class Attention(nn.Module):
             return _apply(self.o_proj, o.to(x2d.dtype).reshape(B * S, self.Hq * D))
         if cache is not None:
             out = cache.attend(self, qkv, ctx)
-        elif (self.softcap or self.sinks is not None or getattr(self.config, "_attn_implementation", None) in ("eager", "sdpa")) \
-                and not ctx.S_full:
+        elif (self.softcap or self.sinks is not None or ctx.kstart is not None
+              or getattr(self.config, "_attn_implementation", None) in ("eager", "sdpa")) and not ctx.S_full:
             from ..nn.attention import AttentionInterface      # reference back-ends, selectable like the reference's
 
             B, S, D = ctx.B, ctx.S, self.D
             q, k, v = qkv.view(B, S, -1).split([self.Hq * D, self.Hkv * D, self.Hkv * D], dim=-1)
-            impl = "eager" if (self.softcap or self.sinks is not None) else self.config._attn_implementation
+            impl = "eager" if (self.softcap or self.sinks is not None) else (getattr(self.config, "_attn_implementation", None) or "sdpa")
+            impl = impl if impl in ("eager", "sdpa") else "sdpa"
             extra = {"softcap": self.softcap} if self.softcap else {}
+            if ctx.kstart is not None:                    # two-way blocks: the flash kernels take the upper bound only
+                extra["kstart"] = ctx.kstart
             if self.sinks is not None:
                 extra["sinks"] = self.sinks
             out = AttentionInterface.get(impl)(
                 q.reshape(B, S, self.Hq, D), k.reshape(B, S, self.Hkv, D), v.reshape(B, S, self.Hkv, D), kend, self.scale, **extra)
             out = out.reshape(B * S, self.Hq * D)
-        elif self.softcap or self.sinks is not None:
-            raise NotImplementedError("soft-capped scores / attention sinks are not combined with context / segment parallelism")
+        elif self.softcap or self.sinks is not None or ctx.kstart is not None:
+            raise NotImplementedError("soft-capped scores / attention sinks / two-way blocks are not combined with context / segment parallelism")
         elif ctx.S_full:
             B, S, D = ctx.B, ctx.S, self.D
             q, k, v = qkv.view(B, S, -1).split([self.Hq * D, self.Hkv * D, self.Hkv * D], dim=-1)

@@ -1,0 +1,187 @@
+"""PaliGemma: a SigLIP image encoder, one linear projector and a Gemma decoder that reads the image tokens and the prompt
+with two-way attention and writes the answer causally (paddleformers/transformers/paligemma).
+
+The prefix (image placeholders + prompt, ``token_type_ids == 0``) attends to itself in both directions; the suffix
+(``token_type_ids == 1``) is causal and sees the whole prefix. This is expressed as a per-key lower bound ``kstart[j]`` = first
+row of j's prefix block (j itself for suffix keys), next to the per-key upper bound used for packed documents; the attention
+runs through the tensor-operation back-ends, because the flash kernels take the upper bound only. Without ``token_type_ids``
+the whole input is one prefix (a prompt being encoded for generation).
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from ..transformers.configuration_utils import PretrainedConfig
+from ..transformers.conversion_utils import Rule, WeightMap
+from ..transformers.model_utils import PretrainedModel
+from .modeling import BatchContext, CausalLMOutput, DecoderForCausalLM, build_weight_map
+from .siglip import SiglipVisionConfig, SiglipVisionModel
+
+
+def two_way_block_starts(two_way: torch.Tensor) -> torch.Tensor:
+    """two_way: bool [B, S], True on tokens of blocks that attend in both directions (runs of True are one block each).
+    Returns int32 [B, S]: for a key inside a block, the first position of its block; for any other key, its own position."""
+    B, S = two_way.shape
+    idx = torch.arange(S, device=two_way.device)[None].expand(B, S)
+    prev = torch.nn.functional.pad(two_way, (1, 0), value=False)[:, :-1]
+    start_here = torch.where(two_way & ~prev, idx, torch.zeros_like(idx))      # block starts carry their index
+    block_start = torch.cummax(start_here, dim=1).values
+    return torch.where(two_way, block_start, idx).to(torch.int32).contiguous()
+
+
+def two_way_block_ends(two_way: torch.Tensor) -> torch.Tensor:
+    """int32 [B, S]: for a key inside a two-way block, one past the last position of its block; 0 for any other key. Layers
+    with a sliding window keep a block whole: the upper bound of a block key is at least this."""
+    B, S = two_way.shape
+    rev = torch.flip(two_way, dims=[1])
+    starts_rev = two_way_block_starts(rev).long()                     # first position of the block in the reversed order
+    ends = S - torch.flip(starts_rev, dims=[1])
+    return torch.where(two_way, ends, torch.zeros_like(ends)).to(torch.int32).contiguous()
+
+
+class PaliGemmaConfig(PretrainedConfig):
+    model_type = "paligemma"
+
+    def __init__(self, text_config=None, vision_config=None, image_token_id=None, image_token_index=None, projection_dim=None,
+                 hidden_size=None, **kwargs):
+        from ..transformers.auto import AutoConfig
+
+        kwargs.pop("model_type", None)
+        text = dict(text_config or {}) if not isinstance(text_config, PretrainedConfig) else text_config
+        if isinstance(text, dict):
+            text.setdefault("tie_word_embeddings", True)
+            text.pop("use_bidirectional_attention", None)
+            text = AutoConfig.for_model(text.pop("model_type", "gemma"), **text)
+        kwargs.setdefault("tie_word_embeddings", bool(text.tie_word_embeddings))
+        super().__init__(**{k: v for k, v in kwargs.items() if k != "vocab_size"})
+        self.text_config = text
+        vis = dict(vision_config or {}) if not isinstance(vision_config, PretrainedConfig) else vision_config.to_dict()
+        vis.pop("model_type", None)
+        self.projection_dim = int(projection_dim or vis.get("projection_dim") or text.hidden_size)
+        vis.pop("projection_dim", None)
+        vis["vision_use_head"] = False
+        self.vision_config = SiglipVisionConfig(**vis)
+        tok = image_token_id if image_token_id is not None else image_token_index
+        self.image_token_id = int(tok if tok is not None else 257152)
+        self.hidden_size = int(hidden_size or text.hidden_size)
+        self.vocab_size = text.vocab_size
+
+    @property
+    def num_image_tokens(self) -> int:
+        return (self.vision_config.image_size // self.vision_config.patch_size) ** 2
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        text = self.text_config.to_dict(saving)
+        text["model_type"] = self.text_config.model_type
+        text["num_image_tokens"] = self.num_image_tokens
+        vis = self.vision_config.to_dict(saving)
+        vis.update(model_type="siglip_vision_model", projection_dim=self.projection_dim)
+        d.update(text_config=text, vision_config=vis, image_token_index=self.image_token_id)
+        d.pop("image_token_id", None)
+        return d
+
+
+class PaliGemmaForConditionalGeneration(PretrainedModel):
+    config_class = PaliGemmaConfig
+
+    def __init__(self, config: PaliGemmaConfig, dtype=None, device=None):
+        super().__init__(config)
+        self.vision_tower = SiglipVisionModel(config.vision_config, dtype=dtype, device=device)
+        self.projector = nn.Linear(config.vision_config.hidden_size, config.projection_dim, dtype=dtype, device=device)
+        self.language = DecoderForCausalLM(config.text_config, dtype=dtype, device=device)
+        self._layout = "nested"                     # tensor-name generation of the checkpoint being read / written
+
+    def _init_weights(self, module):
+        if module is self.projector:
+            nn.init.normal_(module.weight, 0.0, self.config.text_config.initializer_range)
+            nn.init.zeros_(module.bias)
+
+    def image_features(self, pixel_values: torch.Tensor) -> torch.Tensor:
+        """[B, C, H, W] -> [B * tokens, text hidden]. The decoder multiplies embeddings by sqrt(hidden) when it looks tokens
+        up; image rows enter after that step and therefore stay unscaled."""
+        hidden, _ = self.vision_tower(pixel_values)
+        return self.projector(hidden).reshape(-1, self.config.projection_dim)
+
+    def forward(self, input_ids, pixel_values=None, token_type_ids=None, labels=None, kend=None,
+                return_logits: Optional[bool] = None, **unused):
+        cfg, lm = self.config, self.language
+        B, S = input_ids.shape
+        is_image = input_ids == cfg.image_token_id
+        ids = input_ids.masked_fill(is_image, 0) if cfg.image_token_id >= cfg.text_config.vocab_size else input_ids
+        h = lm.model.embed(ids)
+        if pixel_values is not None:
+            feats = self.image_features(pixel_values).to(h.dtype)
+            assert int(is_image.sum()) == feats.shape[0], "one placeholder token per image patch is required"
+            h = h.masked_scatter(is_image.reshape(-1)[:, None], feats)
+        two_way = (token_type_ids == 0) if token_type_ids is not None else torch.ones_like(input_ids, dtype=torch.bool)
+        ctx = lm.model.make_context(input_ids, None, kend)
+        ctx.kstart = two_way_block_starts(two_way)
+        if ctx.kend_window is not None:               # a window never cuts through a two-way block
+            ctx.kend_window = torch.maximum(ctx.kend_window, two_way_block_ends(two_way))
+        hidden, residual = lm.model.run_layers(h, None, ctx)
+        hidden = lm.model.norm(hidden, residual)[0] if residual is not None else lm.model.norm(hidden)
+        out = CausalLMOutput()
+        if return_logits if return_logits is not None else labels is None:
+            out.logits = lm.compute_logits(hidden).view(B, S, -1)
+        if labels is not None:
+            lab = labels.reshape(-1)
+            count = (lab != lm.ignore_index).sum()
+            scale = 1.0 / (count.clamp(min=1).to(torch.float32) * float(lm.loss_accumulation_steps))
+            out.loss, _ = lm._loss(hidden, lab, scale)
+            out.num_tokens = count
+        return out
+
+    @property
+    def loss_accumulation_steps(self):
+        return self.language.loss_accumulation_steps
+
+    @loss_accumulation_steps.setter
+    def loss_accumulation_steps(self, v):
+        self.language.loss_accumulation_steps = v
+
+    # ------------------------------------------------------------------ checkpoint names
+    _LAYOUTS = {                                   # (decoder "model." ->, vision / projector prefix)
+        "legacy": ("language_model.model.", ""),                   # published checkpoints
+        "flat": ("model.language_model.", "model."),
+        "nested": ("model.language_model.model.", "model."),
+    }
+
+    def load_hf_checkpoint(self, directory: str, strict: bool = False) -> None:
+        from ..transformers.model_utils import _CheckpointReader
+
+        reader = _CheckpointReader(directory)
+        saved = self._layout
+        for name, (text, _) in self._LAYOUTS.items():
+            if reader.has(text + "embed_tokens.weight"):
+                self._layout = name
+                break
+        try:
+            super().load_hf_checkpoint(directory, strict)
+        finally:
+            self._layout = saved
+
+    def weight_map(self) -> WeightMap:
+        text_prefix, other = self._LAYOUTS[self._layout]
+
+        def text_name(s: str) -> str:
+            if s.startswith("lm_head."):
+                return ("language_model." if self._layout == "legacy" else "") + s
+            return text_prefix + s[len("model."):] if s.startswith("model.") else s
+
+        rules = []
+        for r in build_weight_map(self.config.text_config).rules.values():
+            rules.append(dataclasses.replace(r, target="language." + r.target, sources=[text_name(s) for s in r.sources]))
+        known = {r.target for r in rules}
+        for name, _ in self.language.named_parameters():                 # parameters without a fusion rule: renamed only
+            if "language." + name not in known:
+                rules.append(Rule("language." + name, [text_name(name)]))
+        for r in self.vision_tower.weight_map().rules.values():
+            rules.append(dataclasses.replace(r, target="vision_tower." + r.target, sources=[other + "vision_tower." + s for s in r.sources]))
+        rules += [Rule("projector.weight", [other + "multi_modal_projector.linear.weight"]),
+                  Rule("projector.bias", [other + "multi_modal_projector.linear.bias"])]
+        return WeightMap(rules)

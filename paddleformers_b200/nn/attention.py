@@ -35,35 +35,41 @@ def flashmask_attention(q, k, v, attn_mask_startend_row_indices=None, scale=None
     return F.flash_attention(q, k, v, causal, _kend(attn_mask_startend_row_indices, B, S), scale)
 
 
-def _dense_mask(kend, B, S, causal, device):
+def _dense_mask(kend, B, S, causal, device, kstart=None):
+    """bool [B, S(query), S(key)]. ``kstart`` [B, S]: first query row that sees key j; it replaces the causal triangle
+    (``kstart[j] = j``) and lets a block of keys be visible to the earlier rows of the same block (prefix-LM and image
+    blocks: ``kstart[j]`` = first position of j's block)."""
     i = torch.arange(S, device=device)
-    vis = (i[None, :] <= i[:, None]) if causal else torch.ones(S, S, dtype=torch.bool, device=device)
-    vis = vis[None].expand(B, S, S)
+    if kstart is not None:
+        vis = i[None, :, None] >= kstart[:, None, :].to(i.dtype)
+    else:
+        vis = (i[None, :] <= i[:, None]) if causal else torch.ones(S, S, dtype=torch.bool, device=device)
+        vis = vis[None].expand(B, S, S)
     if kend is not None:
         vis = vis & (i[None, :, None] < kend[:, None, :])
     return vis
 
 
-def sdpa_attention(q, k, v, attn_mask_startend_row_indices=None, scale=None, causal=True, sinks=None):
+def sdpa_attention(q, k, v, attn_mask_startend_row_indices=None, scale=None, causal=True, sinks=None, kstart=None):
     if sinks is not None:
         raise NotImplementedError("attention sinks are only available in the eager back-end")
     B, S, Hq, D = q.shape
     rep = Hq // k.shape[2]
-    mask = _dense_mask(_kend(attn_mask_startend_row_indices, B, S), B, S, causal, q.device)[:, None]
+    mask = _dense_mask(_kend(attn_mask_startend_row_indices, B, S), B, S, causal, q.device, kstart)[:, None]
     out = torch.nn.functional.scaled_dot_product_attention(
         q.transpose(1, 2), k.transpose(1, 2).repeat_interleave(rep, 1), v.transpose(1, 2).repeat_interleave(rep, 1),
         attn_mask=mask, scale=scale if scale is not None else 1.0 / math.sqrt(D))
     return out.transpose(1, 2)
 
 
-def eager_attention(q, k, v, attn_mask_startend_row_indices=None, scale=None, causal=True, sinks=None, softcap=None):
+def eager_attention(q, k, v, attn_mask_startend_row_indices=None, scale=None, causal=True, sinks=None, softcap=None, kstart=None):
     B, S, Hq, D = q.shape
     rep = Hq // k.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     s = torch.einsum("bshd,bthd->bhst", q.float(), k.float().repeat_interleave(rep, 2)) * scale
     if softcap:                                         # Gemma 2: scores squashed into (-cap, cap) before the softmax
         s = torch.tanh(s / softcap) * softcap
-    vis = _dense_mask(_kend(attn_mask_startend_row_indices, B, S), B, S, causal, q.device)[:, None]
+    vis = _dense_mask(_kend(attn_mask_startend_row_indices, B, S), B, S, causal, q.device, kstart)[:, None]
     s = s.masked_fill(~vis, float("-inf"))
     if sinks is not None:                               # [Hq] logits: an extra column that takes part in the softmax only
         sink = sinks.float().view(1, Hq, 1, 1).expand(B, Hq, S, 1)

@@ -52,8 +52,10 @@ class AutoModelForConditionalGeneration:
                                               Qwen2VLForConditionalGeneration, Qwen3VLConfig, Qwen3VLForConditionalGeneration,
                                               Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration, Glm4vMoeConfig,
                                               Glm4vMoeForConditionalGeneration)
+        from ..models.paligemma import PaliGemmaConfig, PaliGemmaForConditionalGeneration
 
-        table = {"qwen2_vl": (Qwen2VLConfig, Qwen2VLForConditionalGeneration),
+        table = {"paligemma": (PaliGemmaConfig, PaliGemmaForConditionalGeneration),
+                 "qwen2_vl": (Qwen2VLConfig, Qwen2VLForConditionalGeneration),
                  "qwen2_5_vl": (Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration),
                  "qwen3_vl": (Qwen3VLConfig, Qwen3VLForConditionalGeneration),
                  "qwen3_vl_moe": (Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration),

@@ -588,3 +588,77 @@ def test_siglip_vision_tower_matches_hugging_face(tmp_path, use_head):
     with torch.no_grad():
         again = back(pixel_values=x)
     assert (again.last_hidden_state - want.last_hidden_state).abs().max() < 1e-5
+
+
+def test_paligemma_matches_hugging_face(tmp_path):
+    """SigLIP tower + projector + Gemma decoder with two-way attention on the prefix: logits under the training mask
+    (prefix from ``token_type_ids``, different prefix lengths per row) and under the prompt mask (everything two-way), the loss on
+    the suffix, and a checkpoint written here read back by transformers."""
+    from transformers import PaliGemmaConfig as HFConfig, PaliGemmaForConditionalGeneration as HFModel
+
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    torch.manual_seed(0)
+    hf = HFModel(HFConfig(
+        vision_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, image_size=16, patch_size=8,
+                           projection_dim=64, vision_use_head=False),
+        text_config=dict(model_type="gemma", hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=1, head_dim=16, vocab_size=300),
+        image_token_id=299, hidden_size=64, projection_dim=64))
+    hf.save_pretrained(tmp_path / "hf")
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).eval()
+    ids = torch.tensor([[299] * 4 + [2, 5, 6, 7, 8, 9, 10, 11], [299] * 4 + [2, 15, 16, 17, 18, 19, 20, 21]])
+    types = torch.tensor([[0] * 8 + [1] * 4, [0] * 6 + [1] * 6])
+    pixels = torch.randn(2, 3, 16, 16)
+    labels = torch.where(types == 1, ids, torch.full_like(ids, -100))
+    shifted = torch.cat([labels[:, 1:], torch.full_like(labels[:, :1], -100)], dim=1)     # transformers shifts inside the model
+    with torch.no_grad():
+        hf.train()                                   # the training mask is only built in training mode
+        want = hf(input_ids=ids, pixel_values=pixels, token_type_ids=types, labels=labels)
+        hf.eval()
+        got = mine(ids, pixel_values=pixels, token_type_ids=types, labels=shifted, return_logits=True)
+        assert (want.logits - got.logits).abs().max() < 1e-4
+        assert abs(want.loss.item() - got.loss.item()) < 1e-4
+        causal = mine.language(ids).logits           # the same decoder without the two-way prefix must differ on prefix rows
+        assert (causal[:, 4:6] - got.logits[:, 4:6]).abs().max() > 1e-3
+        want_prompt = hf(input_ids=ids, pixel_values=pixels)
+        got_prompt = mine(ids, pixel_values=pixels)
+        assert (want_prompt.logits - got_prompt.logits).abs().max() < 1e-4
+    out = mine(ids, pixel_values=pixels, token_type_ids=types, labels=shifted)
+    out.loss.backward()
+    assert mine.projector.weight.grad.abs().sum() > 0 and mine.vision_tower.patch_embedding.weight.grad.abs().sum() > 0
+    mine.save_pretrained(str(tmp_path / "mine"))
+    back = HFModel.from_pretrained(tmp_path / "mine").eval()
+    with torch.no_grad():
+        again = back(input_ids=ids, pixel_values=pixels)
+    assert (again.logits - want_prompt.logits).abs().max() < 1e-5
+
+
+def test_paligemma2_window_layers_keep_the_prefix_whole(tmp_path):
+    """Gemma 2 decoder (soft-capped scores, alternating sliding-window layers) under a prefix longer than the window: a
+    window never cuts through the two-way prefix, and suffix rows see the usual window."""
+    from transformers import PaliGemmaConfig as HFConfig, PaliGemmaForConditionalGeneration as HFModel
+
+    from paddleformers_b200.models.paligemma import two_way_block_ends, two_way_block_starts
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    blocks = torch.tensor([[1, 1, 1, 0, 0, 1, 1, 0], [0, 1, 1, 1, 1, 0, 0, 0]]).bool()
+    assert two_way_block_starts(blocks).tolist() == [[0, 0, 0, 3, 4, 5, 5, 7], [0, 1, 1, 1, 1, 5, 6, 7]]
+    assert two_way_block_ends(blocks).tolist() == [[3, 3, 3, 0, 0, 7, 7, 0], [0, 5, 5, 5, 5, 0, 0, 0]]
+    torch.manual_seed(0)
+    hf = HFModel(HFConfig(
+        vision_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, image_size=16, patch_size=8,
+                           projection_dim=64, vision_use_head=False),
+        text_config=dict(model_type="gemma2", hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=1, head_dim=16, vocab_size=300, sliding_window=4, query_pre_attn_scalar=16),
+        image_token_id=299, hidden_size=64, projection_dim=64))
+    hf.save_pretrained(tmp_path)
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path), dtype=torch.float32).eval()
+    ids = torch.tensor([[299] * 4 + [2, 5, 6, 7, 8, 9, 10, 11, 12, 13], [299] * 4 + [2, 15, 16, 17, 18, 19, 20, 21, 22, 23]])
+    types = torch.tensor([[0] * 8 + [1] * 6, [0] * 6 + [1] * 8])
+    pixels = torch.randn(2, 3, 16, 16)
+    with torch.no_grad():
+        hf.train()
+        want = hf(input_ids=ids, pixel_values=pixels, token_type_ids=types, labels=ids).logits
+        got = mine(ids, pixel_values=pixels, token_type_ids=types).logits
+    assert (want - got).abs().max() < 5e-4
