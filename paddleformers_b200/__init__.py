@@ -32,6 +32,7 @@ _LAZY = {
     "GraniteForCausalLM": ".models.modeling", "SFTTrainer": ".trainer.sft_trainer", "DPOTrainer": ".trainer.dpo_trainer",
     "ShardedAdamW": ".parallel.sharding", "ShardedMuon": ".parallel.sharding", "EMACallback": ".trainer.ema",
     "plan_parallelism": ".parallel.auto_plan",
+    "PaliGemmaForConditionalGeneration": ".models.paligemma", "Gemma3ForConditionalGeneration": ".models.paligemma",
     "AutoModel": ".transformers.auto", "SiglipVisionModel": ".models.siglip", "SiglipVisionConfig": ".models.siglip",
     "Qwen3VLForConditionalGeneration": ".models.vision_language", "Qwen3VLMoeForConditionalGeneration": ".models.vision_language",
     "Glm4vMoeForConditionalGeneration": ".models.vision_language", "FullyShardedOptimizer": ".parallel.fsdp",

@@ -977,7 +977,6 @@ CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Q
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
 # feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
 UNSUPPORTED_FAMILIES = { "deepseek_v4": "compressed sparse attention",
-    "gemma3": "image-token pooling projector and processor (the text decoder is available as gemma3_text, the tower as siglip_vision_model)",
     "phi4_multimodal": "vision and audio towers",
 
 

@@ -1,4 +1,4 @@
-"""PaliGemma: a SigLIP image encoder, one linear projector and a Gemma decoder that reads the image tokens and the prompt
+"""PaliGemma and Gemma 3 with images. PaliGemma: a SigLIP image encoder, one linear projector and a Gemma decoder that reads the image tokens and the prompt
 with two-way attention and writes the answer causally (paddleformers/transformers/paligemma).
 
 The prefix (image placeholders + prompt, ``token_type_ids == 0``) attends to itself in both directions; the suffix
@@ -92,12 +92,16 @@ class PaliGemmaForConditionalGeneration(PretrainedModel):
     def __init__(self, config: PaliGemmaConfig, dtype=None, device=None):
         super().__init__(config)
         self.vision_tower = SiglipVisionModel(config.vision_config, dtype=dtype, device=device)
-        self.projector = nn.Linear(config.vision_config.hidden_size, config.projection_dim, dtype=dtype, device=device)
+        self.build_projector(config, dtype, device)
         self.language = DecoderForCausalLM(config.text_config, dtype=dtype, device=device)
         self._layout = "nested"                     # tensor-name generation of the checkpoint being read / written
+        self.post_init()
+
+    def build_projector(self, config, dtype, device):
+        self.projector = nn.Linear(config.vision_config.hidden_size, config.projection_dim, dtype=dtype, device=device)
 
     def _init_weights(self, module):
-        if module is self.projector:
+        if module is getattr(self, "projector", None):
             nn.init.normal_(module.weight, 0.0, self.config.text_config.initializer_range)
             nn.init.zeros_(module.bias)
 
@@ -105,7 +109,19 @@ class PaliGemmaForConditionalGeneration(PretrainedModel):
         """[B, C, H, W] -> [B * tokens, text hidden]. The decoder multiplies embeddings by sqrt(hidden) when it looks tokens
         up; image rows enter after that step and therefore stay unscaled."""
         hidden, _ = self.vision_tower(pixel_values)
+        return self.project(hidden)
+
+    def project(self, hidden: torch.Tensor) -> torch.Tensor:
         return self.projector(hidden).reshape(-1, self.config.projection_dim)
+
+    def two_way_tokens(self, input_ids, token_type_ids) -> torch.Tensor:
+        """bool [B, S]: tokens inside blocks that attend in both directions. Here: the prefix (type 0); everything when no types
+        are given."""
+        return (token_type_ids == 0) if token_type_ids is not None else torch.ones_like(input_ids, dtype=torch.bool)
+
+    def projector_rules(self, prefix: str):
+        return [Rule("projector.weight", [prefix + "multi_modal_projector.linear.weight"]),
+                Rule("projector.bias", [prefix + "multi_modal_projector.linear.bias"])]
 
     def forward(self, input_ids, pixel_values=None, token_type_ids=None, labels=None, kend=None,
                 return_logits: Optional[bool] = None, **unused):
@@ -118,7 +134,7 @@ class PaliGemmaForConditionalGeneration(PretrainedModel):
             feats = self.image_features(pixel_values).to(h.dtype)
             assert int(is_image.sum()) == feats.shape[0], "one placeholder token per image patch is required"
             h = h.masked_scatter(is_image.reshape(-1)[:, None], feats)
-        two_way = (token_type_ids == 0) if token_type_ids is not None else torch.ones_like(input_ids, dtype=torch.bool)
+        two_way = self.two_way_tokens(input_ids, token_type_ids)
         ctx = lm.model.make_context(input_ids, None, kend)
         ctx.kstart = two_way_block_starts(two_way)
         if ctx.kend_window is not None:               # a window never cuts through a two-way block
@@ -182,6 +198,68 @@ class PaliGemmaForConditionalGeneration(PretrainedModel):
                 rules.append(Rule("language." + name, [text_name(name)]))
         for r in self.vision_tower.weight_map().rules.values():
             rules.append(dataclasses.replace(r, target="vision_tower." + r.target, sources=[other + "vision_tower." + s for s in r.sources]))
-        rules += [Rule("projector.weight", [other + "multi_modal_projector.linear.weight"]),
-                  Rule("projector.bias", [other + "multi_modal_projector.linear.bias"])]
-        return WeightMap(rules)
+        return WeightMap(rules + self.projector_rules(other))
+
+
+class Gemma3Config(PaliGemmaConfig):
+    """Gemma 3 with images (paddleformers/transformers/gemma3): the SigLIP patch grid is average-pooled to
+    ``mm_tokens_per_image`` tokens per image, normalised and projected by one matrix; the tokens of one image attend to each
+    other in both directions inside the otherwise causal Gemma 3 text decoder."""
+
+    model_type = "gemma3"
+
+    def __init__(self, text_config=None, vision_config=None, mm_tokens_per_image=256, boi_token_index=255999, eoi_token_index=256000,
+                 image_token_index=262144, **kwargs):
+        text = text_config
+        if not isinstance(text, PretrainedConfig):
+            text = dict(text_config or {})
+            text["model_type"] = "gemma3_text"
+        super().__init__(text_config=text, vision_config=vision_config, image_token_index=kwargs.pop("image_token_id", image_token_index),
+                         **kwargs)
+        self.mm_tokens_per_image = int(mm_tokens_per_image)
+        self.boi_token_index, self.eoi_token_index = boi_token_index, eoi_token_index
+        self.projection_dim = self.text_config.hidden_size
+
+    @property
+    def num_image_tokens(self) -> int:
+        return self.mm_tokens_per_image
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        d["text_config"].pop("num_image_tokens", None)
+        d["vision_config"].pop("projection_dim", None)
+        d.pop("projection_dim", None)
+        return d
+
+
+class Gemma3ForConditionalGeneration(PaliGemmaForConditionalGeneration):
+    config_class = Gemma3Config
+
+    def build_projector(self, config, dtype, device):
+        kw = dict(dtype=dtype, device=device)
+        self.mm_input_projection_weight = nn.Parameter(torch.zeros(config.vision_config.hidden_size, config.text_config.hidden_size, **kw))
+        self.mm_soft_emb_norm = nn.Parameter(torch.zeros(config.vision_config.hidden_size, **kw))    # stored as (scale - 1)
+
+    def _init_weights(self, module):
+        if module is self:
+            nn.init.normal_(self.mm_input_projection_weight, 0.0, self.config.text_config.initializer_range)
+
+    def project(self, hidden: torch.Tensor) -> torch.Tensor:
+        cfg = self.config
+        B, N, H = hidden.shape
+        side = int(N ** 0.5)
+        out_side = int(cfg.mm_tokens_per_image ** 0.5)
+        k = side // out_side
+        pooled = hidden.view(B, out_side, k, out_side, k, H).float().mean(dim=(2, 4)).reshape(B, out_side * out_side, H)
+        normed = pooled * torch.rsqrt(pooled.pow(2).mean(-1, keepdim=True) + cfg.vision_config.layer_norm_eps)
+        normed = (normed * (1.0 + self.mm_soft_emb_norm.float())).to(hidden.dtype)
+        return (normed @ self.mm_input_projection_weight).reshape(-1, cfg.text_config.hidden_size)
+
+    def two_way_tokens(self, input_ids, token_type_ids) -> torch.Tensor:
+        """The tokens of each image (type 1, or the image placeholder when no types are given); consecutive images are told
+        apart by the end-of-image / begin-of-image tokens between them."""
+        return (token_type_ids == 1) if token_type_ids is not None else (input_ids == self.config.image_token_id)
+
+    def projector_rules(self, prefix: str):
+        return [Rule("mm_input_projection_weight", [prefix + "multi_modal_projector.mm_input_projection_weight"]),
+                Rule("mm_soft_emb_norm", [prefix + "multi_modal_projector.mm_soft_emb_norm.weight"])]

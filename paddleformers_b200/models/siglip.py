@@ -116,6 +116,7 @@ class SiglipVisionModel(PretrainedModel):
         self.layers = nn.ModuleList([_Block(config, **kw) for _ in range(config.num_hidden_layers)])
         self.post_layernorm = nn.LayerNorm(H, eps=config.layer_norm_eps, **kw)
         self.head = _PoolingHead(config, **kw) if config.vision_use_head else None
+        self.post_init()
 
     def _init_weights(self, module):
         if isinstance(module, (nn.Linear, nn.Embedding)):

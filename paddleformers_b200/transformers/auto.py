@@ -52,9 +52,11 @@ class AutoModelForConditionalGeneration:
                                               Qwen2VLForConditionalGeneration, Qwen3VLConfig, Qwen3VLForConditionalGeneration,
                                               Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration, Glm4vMoeConfig,
                                               Glm4vMoeForConditionalGeneration)
-        from ..models.paligemma import PaliGemmaConfig, PaliGemmaForConditionalGeneration
+        from ..models.paligemma import (Gemma3Config, Gemma3ForConditionalGeneration, PaliGemmaConfig,
+                                        PaliGemmaForConditionalGeneration)
 
         table = {"paligemma": (PaliGemmaConfig, PaliGemmaForConditionalGeneration),
+                 "gemma3": (Gemma3Config, Gemma3ForConditionalGeneration),
                  "qwen2_vl": (Qwen2VLConfig, Qwen2VLForConditionalGeneration),
                  "qwen2_5_vl": (Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration),
                  "qwen3_vl": (Qwen3VLConfig, Qwen3VLForConditionalGeneration),

@@ -662,3 +662,42 @@ def test_paligemma2_window_layers_keep_the_prefix_whole(tmp_path):
         want = hf(input_ids=ids, pixel_values=pixels, token_type_ids=types, labels=ids).logits
         got = mine(ids, pixel_values=pixels, token_type_ids=types).logits
     assert (want - got).abs().max() < 5e-4
+
+
+def test_gemma3_with_images_matches_hugging_face(tmp_path):
+    """Two images in one row: pooled + normalised + projected SigLIP features, two-way attention inside each image on global and
+    on sliding-window layers (window shorter than an image block), causal text."""
+    from transformers import Gemma3Config as HFConfig, Gemma3ForConditionalGeneration as HFModel
+
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    torch.manual_seed(0)
+    hf = HFModel(HFConfig(
+        vision_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, image_size=32, patch_size=8,
+                           vision_use_head=False),
+        text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=1,
+                         head_dim=16, vocab_size=300, sliding_window=3, query_pre_attn_scalar=16,
+                         layer_types=["sliding_attention", "full_attention", "sliding_attention"]),
+        mm_tokens_per_image=4, image_token_index=299, boi_token_index=297, eoi_token_index=298)).eval()
+    with torch.no_grad():
+        hf.model.multi_modal_projector.mm_input_projection_weight.normal_(0, 0.1)
+        hf.model.multi_modal_projector.mm_soft_emb_norm.weight.normal_(0, 0.1)
+    hf.save_pretrained(tmp_path / "hf")
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).eval()
+    ids = torch.tensor([[2, 5, 297] + [299] * 4 + [298, 6, 297] + [299] * 4 + [298, 7, 8, 9, 10]])
+    types = (ids == 299).long()
+    pixels = torch.randn(2, 3, 32, 32)
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pixels, token_type_ids=types).logits
+        got = mine(ids, pixel_values=pixels).logits                      # types default to the image placeholders
+        assert (want - got).abs().max() < 1e-4
+        assert (mine(ids, pixel_values=pixels, token_type_ids=types).logits - got).abs().max() == 0
+    labels = torch.cat([ids[:, 1:], torch.full_like(ids[:, :1], -100)], dim=1).masked_fill(ids.roll(-1, 1) >= 297, -100)
+    mine(ids, pixel_values=pixels, labels=labels).loss.backward()
+    assert mine.mm_input_projection_weight.grad.abs().sum() > 0
+    mine.save_pretrained(str(tmp_path / "mine"))
+    back = HFModel.from_pretrained(tmp_path / "mine").eval()
+    with torch.no_grad():
+        assert (back(input_ids=ids, pixel_values=pixels, token_type_ids=types).logits - want).abs().max() < 1e-5
+    fresh = AutoModelForConditionalGeneration.from_config(mine.config, dtype=torch.float32)
+    assert fresh.mm_input_projection_weight.abs().sum() > 0
