@@ -136,9 +136,10 @@ class PaliGemmaForConditionalGeneration(PretrainedModel):
             h = h.masked_scatter(is_image.reshape(-1)[:, None], feats)
         two_way = self.two_way_tokens(input_ids, token_type_ids)
         ctx = lm.model.make_context(input_ids, None, kend)
-        ctx.kstart = two_way_block_starts(two_way)
-        if ctx.kend_window is not None:               # a window never cuts through a two-way block
-            ctx.kend_window = torch.maximum(ctx.kend_window, two_way_block_ends(two_way))
+        if two_way is not None:
+            ctx.kstart = two_way_block_starts(two_way)
+            if ctx.kend_window is not None:           # a window never cuts through a two-way block
+                ctx.kend_window = torch.maximum(ctx.kend_window, two_way_block_ends(two_way))
         hidden, residual = lm.model.run_layers(h, None, ctx)
         hidden = lm.model.norm(hidden, residual)[0] if residual is not None else lm.model.norm(hidden)
         out = CausalLMOutput()
@@ -185,8 +186,8 @@ class PaliGemmaForConditionalGeneration(PretrainedModel):
         text_prefix, other = self._LAYOUTS[self._layout]
 
         def text_name(s: str) -> str:
-            if s.startswith("lm_head."):
-                return ("language_model." if self._layout == "legacy" else "") + s
+            if s.startswith("lm_head."):                       # beside the decoder's "model." in every layout
+                return (text_prefix if self._layout == "legacy" else other)[:-len("model.")] + s
             return text_prefix + s[len("model."):] if s.startswith("model.") else s
 
         rules = []
@@ -263,3 +264,104 @@ class Gemma3ForConditionalGeneration(PaliGemmaForConditionalGeneration):
     def projector_rules(self, prefix: str):
         return [Rule("mm_input_projection_weight", [prefix + "multi_modal_projector.mm_input_projection_weight"]),
                 Rule("mm_soft_emb_norm", [prefix + "multi_modal_projector.mm_soft_emb_norm.weight"])]
+
+
+class AyaVisionConfig(PaliGemmaConfig):
+    """Aya Vision (paddleformers/transformers/aya_vision): SigLIP features of one encoder layer, neighbouring patches folded
+    into the channel dimension (``downsample_factor`` per side), LayerNorm + SwiGLU projector, Cohere 2 decoder; causal."""
+
+    model_type = "aya_vision"
+
+    def __init__(self, text_config=None, vision_config=None, downsample_factor=2, alignment_intermediate_size=36864,
+                 adapter_layer_norm_eps=1e-6, vision_feature_layer=-1, vision_feature_select_strategy="full", image_token_index=255036,
+                 **kwargs):
+        text = text_config
+        if not isinstance(text, PretrainedConfig):
+            text = dict(text_config or {})
+            text.setdefault("model_type", "cohere2")
+        super().__init__(text_config=text, vision_config=vision_config, image_token_index=kwargs.pop("image_token_id", image_token_index),
+                         **kwargs)
+        self.downsample_factor, self.alignment_intermediate_size = int(downsample_factor), int(alignment_intermediate_size)
+        self.adapter_layer_norm_eps, self.vision_feature_layer = adapter_layer_norm_eps, int(vision_feature_layer)
+        self.vision_feature_select_strategy = vision_feature_select_strategy
+        self.projection_dim = self.text_config.hidden_size
+
+    @property
+    def num_image_tokens(self) -> int:
+        return (self.vision_config.image_size // self.vision_config.patch_size // self.downsample_factor) ** 2
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        d["text_config"].pop("num_image_tokens", None)
+        d["vision_config"].pop("projection_dim", None)
+        d.pop("projection_dim", None)
+        return d
+
+
+class AyaVisionForConditionalGeneration(PaliGemmaForConditionalGeneration):
+    config_class = AyaVisionConfig
+
+    def build_projector(self, config, dtype, device):
+        kw = dict(dtype=dtype, device=device)
+        width = config.vision_config.hidden_size * config.downsample_factor ** 2
+        self.layernorm = nn.LayerNorm(width, eps=config.adapter_layer_norm_eps, **kw)
+        self.linear_1 = nn.Linear(width, config.alignment_intermediate_size, **kw)
+        self.linear_2 = nn.Linear(config.alignment_intermediate_size // 2, config.text_config.hidden_size, **kw)
+
+    def _init_weights(self, module):
+        if module is getattr(self, "linear_1", None) or module is getattr(self, "linear_2", None):
+            nn.init.normal_(module.weight, 0.0, self.config.text_config.initializer_range)
+            nn.init.zeros_(module.bias)
+
+    def image_features(self, pixel_values: torch.Tensor) -> torch.Tensor:
+        hidden, _ = self.vision_tower(pixel_values, feature_layer=self.config.vision_feature_layer)
+        return self.project(hidden)
+
+    def project(self, hidden: torch.Tensor) -> torch.Tensor:
+        B, N, C = hidden.shape
+        side, f = int(N ** 0.5), self.config.downsample_factor
+        # fold f x f neighbouring patches into the channels; the element order follows the published checkpoints: first f
+        # neighbours along the second grid axis, then f along the first, and the folded grid is stored second axis first
+        x = hidden.reshape(B, side, side // f, C * f).permute(0, 2, 1, 3)
+        x = x.reshape(B, side // f, side // f, C * f * f).permute(0, 2, 1, 3)
+        x = self.linear_1(self.layernorm(x))
+        val, gate = x.chunk(2, dim=-1)
+        return self.linear_2(torch.nn.functional.silu(gate) * val).reshape(-1, self.config.text_config.hidden_size)
+
+    def two_way_tokens(self, input_ids, token_type_ids):
+        return None
+
+    def projector_rules(self, prefix: str):
+        return [Rule(f"{m}.{leaf}", [prefix + f"multi_modal_projector.{m}.{leaf}"])
+                for m in ("layernorm", "linear_1", "linear_2") for leaf in ("weight", "bias")]
+
+
+class ShieldGemma2Config(Gemma3Config):
+    model_type = "shieldgemma2"
+
+    def __init__(self, yes_token_index=10784, no_token_index=3771, **kwargs):
+        super().__init__(**kwargs)
+        self.yes_token_index, self.no_token_index = int(yes_token_index), int(no_token_index)
+
+
+@dataclasses.dataclass
+class ImageClassifierOutput:
+    logits: torch.Tensor            # [B, 2]: the "yes" and "no" logits at the last position
+    probabilities: torch.Tensor     # softmax over the two
+
+
+class ShieldGemma2ForImageClassification(Gemma3ForConditionalGeneration):
+    """Image policy classifier (paddleformers/transformers/shieldgemma2): Gemma 3 reads the image and a policy prompt; the
+    answer is the probability of "yes" against "no" as the next token."""
+
+    config_class = ShieldGemma2Config
+    _LAYOUTS = {
+        "legacy": ("model.language_model.model.", "model."),
+        "flat": ("model.model.language_model.", "model.model."),
+        "nested": ("model.model.language_model.model.", "model.model."),
+    }
+
+    def forward(self, input_ids, pixel_values=None, token_type_ids=None, **kw):
+        out = super().forward(input_ids, pixel_values=pixel_values, token_type_ids=token_type_ids, return_logits=True)
+        picked = out.logits[:, -1, [self.config.yes_token_index, self.config.no_token_index]].float()
+        return ImageClassifierOutput(picked, torch.softmax(picked, dim=-1))

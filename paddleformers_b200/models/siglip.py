@@ -131,10 +131,17 @@ class SiglipVisionModel(PretrainedModel):
         x = pixel_values.view(B, C, Hh // P, P, Ww // P, P).permute(0, 2, 4, 1, 3, 5)
         return x.reshape(B, (Hh // P) * (Ww // P), C * P * P)
 
-    def forward(self, pixel_values: torch.Tensor):
-        """Returns (last_hidden_state [B, N, H], pooled [B, H] or None)."""
+    def forward(self, pixel_values: torch.Tensor, feature_layer: Optional[int] = None):
+        """Returns (last_hidden_state [B, N, H], pooled [B, H] or None). With ``feature_layer`` (an index into [embeddings,
+        block 1, ..., block N], negative from the end) the first element is that intermediate state, without the final
+        LayerNorm, and nothing is pooled."""
         x = self.patch_embedding(self.patches(pixel_values.to(self.patch_embedding.weight.dtype)))
         x = x + self.position_embedding.weight[None, :x.shape[1]]
+        if feature_layer is not None:
+            stop = feature_layer if feature_layer >= 0 else len(self.layers) + 1 + feature_layer
+            for blk in self.layers[:stop]:
+                x = blk(x)
+            return x, None
         for blk in self.layers:
             x = blk(x)
         x = self.post_layernorm(x)

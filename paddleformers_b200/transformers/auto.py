@@ -52,11 +52,14 @@ class AutoModelForConditionalGeneration:
                                               Qwen2VLForConditionalGeneration, Qwen3VLConfig, Qwen3VLForConditionalGeneration,
                                               Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration, Glm4vMoeConfig,
                                               Glm4vMoeForConditionalGeneration)
-        from ..models.paligemma import (Gemma3Config, Gemma3ForConditionalGeneration, PaliGemmaConfig,
-                                        PaliGemmaForConditionalGeneration)
+        from ..models.paligemma import (AyaVisionConfig, AyaVisionForConditionalGeneration, Gemma3Config,
+                                        Gemma3ForConditionalGeneration, PaliGemmaConfig, PaliGemmaForConditionalGeneration,
+                                        ShieldGemma2Config, ShieldGemma2ForImageClassification)
 
         table = {"paligemma": (PaliGemmaConfig, PaliGemmaForConditionalGeneration),
                  "gemma3": (Gemma3Config, Gemma3ForConditionalGeneration),
+                 "aya_vision": (AyaVisionConfig, AyaVisionForConditionalGeneration),
+                 "shieldgemma2": (ShieldGemma2Config, ShieldGemma2ForImageClassification),
                  "qwen2_vl": (Qwen2VLConfig, Qwen2VLForConditionalGeneration),
                  "qwen2_5_vl": (Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration),
                  "qwen3_vl": (Qwen3VLConfig, Qwen3VLForConditionalGeneration),

@@ -701,3 +701,59 @@ def test_gemma3_with_images_matches_hugging_face(tmp_path):
         assert (back(input_ids=ids, pixel_values=pixels, token_type_ids=types).logits - want).abs().max() < 1e-5
     fresh = AutoModelForConditionalGeneration.from_config(mine.config, dtype=torch.float32)
     assert fresh.mm_input_projection_weight.abs().sum() > 0
+
+
+def test_aya_vision_matches_hugging_face(tmp_path):
+    """SigLIP features of the last encoder block (no final LayerNorm), 2 x 2 patches folded into channels, LayerNorm + SwiGLU
+    projector, Cohere 2 decoder with sliding-window layers."""
+    from transformers import AyaVisionConfig as HFConfig, AyaVisionForConditionalGeneration as HFModel
+
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    torch.manual_seed(0)
+    hf = HFModel(HFConfig(
+        vision_config=dict(model_type="siglip_vision_model", hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                           num_attention_heads=2, image_size=32, patch_size=8, vision_use_head=False),
+        text_config=dict(model_type="cohere2", hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=1, head_dim=16, vocab_size=300, sliding_window=4),
+        downsample_factor=2, alignment_intermediate_size=96, image_token_index=299)).eval()
+    hf.save_pretrained(tmp_path / "hf")
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).eval()
+    ids = torch.tensor([[2, 5] + [299] * 4 + [6, 7, 8, 9, 10], [2] + [299] * 4 + [6, 7, 8, 9, 10, 11]])
+    pixels = torch.randn(2, 3, 32, 32)
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pixels).logits
+        assert (want - mine(ids, pixel_values=pixels).logits).abs().max() < 1e-4
+    mine.save_pretrained(str(tmp_path / "mine"))
+    back = HFModel.from_pretrained(tmp_path / "mine").eval()
+    with torch.no_grad():
+        assert (back(input_ids=ids, pixel_values=pixels).logits - want).abs().max() < 1e-5
+
+
+def test_shieldgemma2_classifier_matches_hugging_face(tmp_path):
+    from transformers import ShieldGemma2Config as HFConfig, ShieldGemma2ForImageClassification as HFModel
+
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    torch.manual_seed(0)
+    hf = HFModel(HFConfig(
+        vision_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2, image_size=32, patch_size=8,
+                           vision_use_head=False),
+        text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1,
+                         head_dim=16, vocab_size=300, sliding_window=3, query_pre_attn_scalar=16),
+        mm_tokens_per_image=4, image_token_index=299, boi_token_index=297, eoi_token_index=298, yes_token_index=11, no_token_index=12)).eval()
+    with torch.no_grad():
+        hf.model.model.multi_modal_projector.mm_input_projection_weight.normal_(0, 0.1)
+    hf.save_pretrained(tmp_path / "hf")
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).eval()
+    ids = torch.tensor([[2, 297] + [299] * 4 + [298, 6, 7, 8, 9]])
+    pixels = torch.randn(1, 3, 32, 32)
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pixels, token_type_ids=(ids == 299).long())
+        got = mine(ids, pixel_values=pixels)
+    assert (want.probabilities - got.probabilities).abs().max() < 1e-5 and (want.logits - got.logits).abs().max() < 1e-4
+    mine.save_pretrained(str(tmp_path / "mine"))
+    back = HFModel.from_pretrained(tmp_path / "mine").eval()
+    with torch.no_grad():
+        again = back(input_ids=ids, pixel_values=pixels, token_type_ids=(ids == 299).long())
+    assert (again.logits - want.logits).abs().max() < 1e-5
