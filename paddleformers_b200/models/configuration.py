@@ -981,7 +981,7 @@ UNSUPPORTED_FAMILIES = { "deepseek_v4": "compressed sparse attention",
 
 
     "ernie4_5_vl": "vision tower, modality-aware experts", "paddleocr_vl": "vision tower",
-    "whisper": "encoder-decoder speech model", "qwen3_omni_moe": "audio / vision towers",
+    "qwen3_omni_moe": "audio / vision towers",
 }
 
 

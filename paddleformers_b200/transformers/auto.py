@@ -103,6 +103,19 @@ class AutoModel:
         return model_cls.from_pretrained(path, config=cfg_cls.from_pretrained(path), dtype=dtype, device=device, **kw)
 
 
+class AutoModelForSpeechSeq2Seq(AutoModel):
+    """Encoder-decoder speech models."""
+
+    @staticmethod
+    def _classes(model_type: str):
+        from ..models.whisper import WhisperConfig, WhisperForConditionalGeneration
+
+        table = {"whisper": (WhisperConfig, WhisperForConditionalGeneration)}
+        if model_type not in table:
+            raise ValueError(f"unknown speech model_type {model_type!r}; supported: {sorted(table)}")
+        return table[model_type]
+
+
 class AutoModelForCausalLMPipe(AutoModelForCausalLM):
     """Pipeline-parallel variant: builds only this stage's layers (see ``parallel.pipeline``)."""
 

@@ -757,3 +757,56 @@ def test_shieldgemma2_classifier_matches_hugging_face(tmp_path):
     with torch.no_grad():
         again = back(input_ids=ids, pixel_values=pixels, token_type_ids=(ids == 299).long())
     assert (again.logits - want.logits).abs().max() < 1e-5
+
+
+def test_whisper_matches_hugging_face(tmp_path):
+    """Encoder-decoder speech model: logits and loss under teacher forcing (decoder fed the labels shifted right), checkpoint
+    round trip, and greedy decoding consistent with the teacher-forced argmax."""
+    from transformers import WhisperConfig as HFConfig, WhisperForConditionalGeneration as HFModel
+
+    from paddleformers_b200.transformers.auto import AutoModelForSpeechSeq2Seq
+
+    torch.manual_seed(0)
+    hf = HFModel(HFConfig(vocab_size=120, num_mel_bins=8, encoder_layers=2, encoder_attention_heads=2, decoder_layers=2,
+                          decoder_attention_heads=2, decoder_ffn_dim=64, encoder_ffn_dim=64, d_model=32, max_source_positions=20,
+                          max_target_positions=24, decoder_start_token_id=1, pad_token_id=0, bos_token_id=2, eos_token_id=3,
+                          suppress_tokens=None, begin_suppress_tokens=None)).eval()
+    hf.save_pretrained(tmp_path / "hf")
+    mine = AutoModelForSpeechSeq2Seq.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).eval()
+    feats = torch.randn(2, 8, 40)
+    labels = torch.randint(4, 120, (2, 9))
+    labels[1, 6:] = -100
+    with torch.no_grad():
+        want = hf(input_features=feats, labels=labels)
+        got = mine(feats, labels=labels, return_logits=True)
+    assert (want.logits - got.logits).abs().max() < 1e-4 and abs(want.loss.item() - got.loss.item()) < 1e-4
+    mine(feats, labels=labels).loss.backward()
+    assert mine.model.encoder.conv1.weight.grad.abs().sum() > 0 and mine.model.encoder.embed_positions.weight.grad is None
+    out = mine.generate(feats, max_new_tokens=5)
+    with torch.no_grad():
+        step = hf(input_features=feats, decoder_input_ids=out[:, :-1]).logits.argmax(-1)
+    assert out.shape == (2, 6) and torch.equal(step[:, -1], out[:, -1]) and torch.equal(step[:, 0], out[:, 1])
+    mine.save_pretrained(str(tmp_path / "mine"))
+    back = HFModel.from_pretrained(tmp_path / "mine").eval()
+    with torch.no_grad():
+        assert (back(input_features=feats, labels=labels).logits - want.logits).abs().max() < 1e-5
+
+
+def test_log_mel_features_match_hugging_face(tmp_path):
+    import numpy as np
+    from transformers import WhisperFeatureExtractor as HFExtractor
+
+    from paddleformers_b200.transformers.audio_processing import LogMelFeatureExtractor
+
+    hf, mine = HFExtractor(feature_size=80, chunk_length=2), LogMelFeatureExtractor(feature_size=80, chunk_length=2)
+    assert np.abs(hf.mel_filters - mine.mel_filters.numpy()).max() < 1e-6
+    rng = np.random.default_rng(0)
+    waves = [rng.standard_normal(20000).astype(np.float32) * 0.1, np.sin(np.arange(40000) * 0.05).astype(np.float32)]
+    want = hf(waves, sampling_rate=16000, return_tensors="pt")["input_features"]
+    got = mine(waves, sampling_rate=16000)["input_features"]
+    assert got.shape == want.shape == (2, 80, 200) and (want - got).abs().max() < 1e-4
+    mine.save_pretrained(str(tmp_path))
+    again = LogMelFeatureExtractor.from_pretrained(str(tmp_path))
+    assert again.nb_max_frames == 200 and torch.equal(again(waves)["input_features"], got)
+    with pytest.raises(ValueError, match="resample"):
+        mine(waves, sampling_rate=8000)

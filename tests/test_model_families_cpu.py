@@ -88,8 +88,8 @@ def test_registry_names_known_but_unimplemented_families():
     assert not set(CONFIG_MAPPING) & set(UNSUPPORTED_FAMILIES)
     with pytest.raises(NotImplementedError, match="sparse"):
         AutoConfig.for_model("deepseek_v4")
-    with pytest.raises(NotImplementedError, match="speech"):
-        AutoConfig.for_model("whisper")
+    with pytest.raises(NotImplementedError, match="audio"):
+        AutoConfig.for_model("qwen3_omni_moe")
     with pytest.raises(ValueError, match="unknown model_type"):
         AutoConfig.for_model("no_such_family")
 
