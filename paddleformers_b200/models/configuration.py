@@ -757,6 +757,20 @@ class MiniCPMConfig(GraniteConfig):
         self.scale_emb, self.scale_depth, self.dim_model_base = scale_emb, scale_depth, dim_model_base
 
 
+class MiniCPM4_1Config(MiniCPMConfig):
+    """MiniCPM 4.1 (paddleformers/transformers/minicpm4_1): MiniCPM's scaling rules with long-rope frequency factors. The
+    checkpoint's ``sparse_config`` describes a block-sparse key selection that the reference applies only to long prompts on
+    the GPU; it is kept in the configuration and attention stays dense, which is exact up to ``sparse_config["dense_len"]``
+    tokens and an approximation-free (more expensive) evaluation beyond it."""
+
+    model_type = "minicpm4_1"
+
+    def __init__(self, sparse_config=None, mup_denominator=32, **kw):
+        kw.setdefault("tie_word_embeddings", True)
+        super().__init__(**kw)
+        self.sparse_config, self.mup_denominator = sparse_config, mup_denominator
+
+
 class MiniCPM3Config(MiniCPMConfig):
     """MiniCPM3: MiniCPM's scaling rules on multi-head latent attention (low-rank q and kv projections, a rotary slice shared
     by all heads' keys) with half-split rotary pairs in the checkpoint and dense SwiGLU MLPs
@@ -992,7 +1006,7 @@ def resolve_config_class(model_type: str):
         raise NotImplementedError(f"model_type {model_type!r} is known but not implemented: it needs {UNSUPPORTED_FAMILIES[model_type]}")
     raise ValueError(f"unknown model_type {model_type!r}; supported: {sorted(CONFIG_MAPPING)}")
 # families whose architecture is a strict subset of an implemented one load through it
-CONFIG_MAPPING.update({"qwen3_5": Qwen3_5TextConfig, "qwen3_5_moe": Qwen3_5MoeTextConfig, "kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV2Config, "glm4_moe_lite": Glm4MoeLiteConfig, "glm_moe_dsa": GlmMoeDsaConfig, "deepseek_v32": DeepseekV32Config, "phi4": Phi3Config})
+CONFIG_MAPPING.update({"minicpm4_1": MiniCPM4_1Config, "qwen3_5": Qwen3_5TextConfig, "qwen3_5_moe": Qwen3_5MoeTextConfig, "kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV2Config, "glm4_moe_lite": Glm4MoeLiteConfig, "glm_moe_dsa": GlmMoeDsaConfig, "deepseek_v32": DeepseekV32Config, "phi4": Phi3Config})
 
 
 def named_config(name: str, **overrides) -> DecoderConfig:

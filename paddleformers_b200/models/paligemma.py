@@ -86,6 +86,18 @@ class PaliGemmaConfig(PretrainedConfig):
         return d
 
 
+class PaliGemma2Config(PaliGemmaConfig):
+    """The same composite with the Gemma 2 decoder as the default text model (paddleformers/transformers/paligemma2)."""
+
+    model_type = "paligemma2"
+
+    def __init__(self, text_config=None, **kwargs):
+        if not isinstance(text_config, PretrainedConfig):
+            text_config = dict(text_config or {})
+            text_config.setdefault("model_type", "gemma2")
+        super().__init__(text_config=text_config, **kwargs)
+
+
 class PaliGemmaForConditionalGeneration(PretrainedModel):
     config_class = PaliGemmaConfig
 

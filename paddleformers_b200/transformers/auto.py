@@ -53,10 +53,11 @@ class AutoModelForConditionalGeneration:
                                               Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration, Glm4vMoeConfig,
                                               Glm4vMoeForConditionalGeneration)
         from ..models.paligemma import (AyaVisionConfig, AyaVisionForConditionalGeneration, Gemma3Config,
-                                        Gemma3ForConditionalGeneration, PaliGemmaConfig, PaliGemmaForConditionalGeneration,
-                                        ShieldGemma2Config, ShieldGemma2ForImageClassification)
+                                        Gemma3ForConditionalGeneration, PaliGemma2Config, PaliGemmaConfig,
+                                        PaliGemmaForConditionalGeneration, ShieldGemma2Config, ShieldGemma2ForImageClassification)
 
         table = {"paligemma": (PaliGemmaConfig, PaliGemmaForConditionalGeneration),
+                 "paligemma2": (PaliGemma2Config, PaliGemmaForConditionalGeneration),
                  "gemma3": (Gemma3Config, Gemma3ForConditionalGeneration),
                  "aya_vision": (AyaVisionConfig, AyaVisionForConditionalGeneration),
                  "shieldgemma2": (ShieldGemma2Config, ShieldGemma2ForImageClassification),

@@ -571,3 +571,42 @@ def test_linear_attention_layers_decode_incrementally():
             a = model(seq[:, :9], position_ids=torch.arange(9)[None].expand(2, -1), caches=caches, return_logits=True).logits
             b = model(seq[:, 9:10], position_ids=torch.full((2, 1), 9), caches=caches, return_logits=True).logits
             torch.testing.assert_close(torch.cat([a, b], 1), model(seq[:, :10], return_logits=True).logits, rtol=1e-4, atol=1e-4)
+
+
+def test_minicpm4_1_and_paligemma2_registrations(tmp_path):
+    """Families that reuse an implemented architecture under their own ``model_type``: MiniCPM 4.1 (MiniCPM scaling + long-rope
+    factors; the sparse-prefill description is carried in the configuration, attention stays dense) and PaliGemma 2 (the PaliGemma
+    composite with a Gemma 2 decoder by default)."""
+    from paddleformers_b200.transformers.auto import AutoModelForCausalLM, AutoModelForConditionalGeneration
+
+    short, long = [1.0 + 0.05 * i for i in range(8)], [1.5 + 0.2 * i for i in range(8)]
+    cfg = AutoConfig.for_model(
+        "minicpm4_1", vocab_size=200, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=16, scale_emb=12, scale_depth=1.4, dim_model_base=32, max_position_embeddings=64,
+        rope_scaling={"rope_type": "longrope", "short_factor": short, "long_factor": long, "original_max_position_embeddings": 32},
+        sparse_config={"kernel_size": 32, "kernel_stride": 16, "block_size": 64, "topk": 64, "dense_len": 8192})
+    torch.manual_seed(0)
+    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.float32)
+    ids = torch.randint(0, 200, (2, 16))
+    model(ids, labels=ids).loss.backward()
+    model.save_pretrained(str(tmp_path / "m"))
+    again = AutoModelForCausalLM.from_pretrained(str(tmp_path / "m"), dtype=torch.float32)
+    assert type(again).__name__ == "MiniCPM4_1ForCausalLM" and again.config.sparse_config["dense_len"] == 8192
+    assert torch.equal(again(ids).logits, model(ids).logits)
+
+    from paddleformers_b200.models.paligemma import PaliGemma2Config
+
+    pg = PaliGemma2Config(
+        vision_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2, image_size=16, patch_size=8),
+        text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1,
+                         head_dim=16, vocab_size=300, sliding_window=4, query_pre_attn_scalar=16),
+        image_token_index=299, projection_dim=64)
+    assert pg.text_config.model_type == "gemma2" and pg.num_image_tokens == 4
+    vl = AutoModelForConditionalGeneration.from_config(pg, dtype=torch.float32)
+    vl.save_pretrained(str(tmp_path / "pg"))
+    back = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path / "pg"), dtype=torch.float32)
+    ids = torch.tensor([[299] * 4 + [2, 5, 6, 7, 8, 9]])
+    pixels = torch.randn(1, 3, 16, 16)
+    types = torch.tensor([[0] * 6 + [1] * 4])
+    assert back.config.model_type == "paligemma2"
+    assert torch.equal(back(ids, pixel_values=pixels, token_type_ids=types).logits, vl(ids, pixel_values=pixels, token_type_ids=types).logits)
