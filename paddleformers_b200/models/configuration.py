@@ -990,12 +990,16 @@ CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Q
 
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
 # feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
-UNSUPPORTED_FAMILIES = { "deepseek_v4": "compressed sparse attention",
-    "phi4_multimodal": "vision and audio towers",
-
-
-    "ernie4_5_vl": "vision tower, modality-aware experts", "paddleocr_vl": "vision tower",
-    "qwen3_omni_moe": "audio / vision towers",
+UNSUPPORTED_FAMILIES = {
+    "deepseek_v4": "compressed sparse attention",
+    "gemma4_text": "per-layer-type head geometry (global layers with their own head size and shared key / value projection)",
+    "gemma4": "per-layer-type head geometry (global layers with their own head size and shared key / value projection)",
+    "kimi_k3": "delta-rule linear attention with per-channel decay, vision tower", "kimi_linear": "delta-rule linear attention with per-channel decay",
+    "kimi_k25": "vision tower", "hyperencoder": "encoder stack of its own",
+    "phi4_multimodal": "vision and audio towers", "molmo": "vision tower with pooled multi-crop features",
+    "llama4": "vision tower (the text decoder is available as llama4_text)", "glm_ocr": "vision tower variant, dense GLM-4V text decoder",
+    "ernie4_5_vl": "vision tower, modality-aware experts", "ernie4_5_moe_vl": "vision tower, modality-aware experts",
+    "paddleocr_vl": "vision tower", "qwen3_omni_moe": "audio / vision towers",
 }
 
 
