@@ -335,6 +335,32 @@ class Phi3Config(DecoderConfig):
         self.hf_fused_gate_up = True
 
 
+class Glm4Config(DecoderConfig):
+    """GLM-4 dense (paddleformers/transformers/glm_ocr text decoder, GLM-4-0414): a norm before and after both the attention
+    and the MLP of every block, rotary embedding on the first half of each head with interleaved pairs in the checkpoint, fused
+    ``gate_up_proj`` in the checkpoint."""
+
+    model_type = "glm4"
+
+    def __init__(self, **kw):
+        kw.setdefault("partial_rotary_factor", 0.5)
+        kw.setdefault("rms_norm_eps", 1e-5)
+        super().__init__(**kw)
+        self.block_style = "sandwich"
+        self.hf_fused_gate_up = True
+        self.rope_interleaved_checkpoint = True
+        self.hf_name_translation = [["post_attention_layernorm", "post_self_attn_layernorm"],
+                                    ["pre_feedforward_layernorm", "post_attention_layernorm"],
+                                    ["post_feedforward_layernorm", "post_mlp_layernorm"]]
+
+    def to_dict(self, saving: bool = False):
+        d = super().to_dict(saving)
+        if saving:
+            for k in ("block_style", "hf_fused_gate_up", "rope_interleaved_checkpoint", "hf_name_translation"):
+                d.pop(k, None)
+        return d
+
+
 class SeedOssConfig(DecoderConfig):
     """Seed-OSS: Llama blocks with biases on q/k/v (paddleformers/transformers/seed_oss)."""
 
@@ -997,7 +1023,7 @@ UNSUPPORTED_FAMILIES = {
     "kimi_k3": "delta-rule linear attention with per-channel decay, vision tower", "kimi_linear": "delta-rule linear attention with per-channel decay",
     "kimi_k25": "vision tower", "hyperencoder": "encoder stack of its own",
     "phi4_multimodal": "vision and audio towers", "molmo": "vision tower with pooled multi-crop features",
-    "llama4": "vision tower (the text decoder is available as llama4_text)", "glm_ocr": "vision tower variant, dense GLM-4V text decoder",
+    "llama4": "vision tower (the text decoder is available as llama4_text)",
     "ernie4_5_vl": "vision tower, modality-aware experts", "ernie4_5_moe_vl": "vision tower, modality-aware experts",
     "paddleocr_vl": "vision tower", "qwen3_omni_moe": "audio / vision towers",
 }
@@ -1010,7 +1036,7 @@ def resolve_config_class(model_type: str):
         raise NotImplementedError(f"model_type {model_type!r} is known but not implemented: it needs {UNSUPPORTED_FAMILIES[model_type]}")
     raise ValueError(f"unknown model_type {model_type!r}; supported: {sorted(CONFIG_MAPPING)}")
 # families whose architecture is a strict subset of an implemented one load through it
-CONFIG_MAPPING.update({"minicpm4_1": MiniCPM4_1Config, "qwen3_5": Qwen3_5TextConfig, "qwen3_5_moe": Qwen3_5MoeTextConfig, "kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV2Config, "glm4_moe_lite": Glm4MoeLiteConfig, "glm_moe_dsa": GlmMoeDsaConfig, "deepseek_v32": DeepseekV32Config, "phi4": Phi3Config})
+CONFIG_MAPPING.update({"glm4": Glm4Config, "minicpm4_1": MiniCPM4_1Config, "qwen3_5": Qwen3_5TextConfig, "qwen3_5_moe": Qwen3_5MoeTextConfig, "kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV2Config, "glm4_moe_lite": Glm4MoeLiteConfig, "glm_moe_dsa": GlmMoeDsaConfig, "deepseek_v32": DeepseekV32Config, "phi4": Phi3Config})
 
 
 def named_config(name: str, **overrides) -> DecoderConfig:

@@ -30,7 +30,7 @@ from ..transformers.conversion_utils import Rule, WeightMap, expand_layers
 from ..transformers.model_utils import PretrainedModel
 from .configuration import (DecoderConfig, DeepseekV3Config, Glm4MoeConfig, InternLM3Config, LlamaConfig, MistralConfig,
                             Phi3Config, Qwen2Config, Qwen3Config, Qwen3MoeConfig, SeedOssConfig, Ernie4_5Config, Ernie4_5MoeConfig,
-                            GraniteConfig, MiniCPMConfig, MiniCPM4_1Config, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig,
+                            GraniteConfig, MiniCPMConfig, MiniCPM4_1Config, Glm4Config, Qwen2MoeConfig, Olmo2Config, GemmaConfig, Gemma2Config, Gemma3TextConfig, CohereConfig, Cohere2Config, StableLmConfig,
                             HunYuanDenseV1Config, HunYuanMoEV1Config, MiniMaxM2Config, MixtralConfig, MiniCPM3Config, InternLM2Config, GptOssConfig, Llama4TextConfig, Qwen3NextConfig, Qwen3_5TextConfig, Qwen3_5MoeTextConfig, GlmMoeDsaConfig, DeepseekV32Config, MiniMaxConfig, DiffLlamaConfig)
 
 
@@ -901,7 +901,11 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
     per_layer: List[Rule] = []
     qkv_sizes = None
     # checkpoints trained with interleaved rotary pairs: q and k rows (sources 0 and 1) are permuted per head on load
-    rope_perm = {0: config.head_dim, 1: config.head_dim} if getattr(config, "rope_interleaved_checkpoint", False) else None
+    rope_perm = None
+    if getattr(config, "rope_interleaved_checkpoint", False):
+        rot = int(config.head_dim * float(getattr(config, "partial_rotary_factor", 1.0) or 1.0))
+        spec = config.head_dim if rot == config.head_dim else (config.head_dim, 0, rot)       # only the rotated rows are paired
+        rope_perm = {0: spec, 1: spec}
     mla_q_name = mla_q_perm = mla_kv_perm = None
     if config.is_mla:
         # MLA projections keep their HF names. DeepSeek checkpoints store the rotary slice of every query head and of the
@@ -1102,6 +1106,7 @@ Qwen2MoeForCausalLM = _family("Qwen2MoeForCausalLM", Qwen2MoeConfig)
 GraniteForCausalLM = _family("GraniteForCausalLM", GraniteConfig)
 MiniCPMForCausalLM = _family("MiniCPMForCausalLM", MiniCPMConfig)
 MiniCPM4_1ForCausalLM = _family("MiniCPM4_1ForCausalLM", MiniCPM4_1Config)
+Glm4ForCausalLM = _family("Glm4ForCausalLM", Glm4Config)
 Olmo2ForCausalLM = _family("Olmo2ForCausalLM", Olmo2Config)
 GemmaForCausalLM = _family("GemmaForCausalLM", GemmaConfig)
 Gemma2ForCausalLM = _family("Gemma2ForCausalLM", Gemma2Config)
@@ -1125,7 +1130,7 @@ Qwen3_5MoeForCausalLM = _family("Qwen3_5MoeForCausalLM", Qwen3_5MoeTextConfig)
 
 MODEL_MAPPING = {
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
-    "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "minicpm4_1": MiniCPM4_1ForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma2": Gemma2ForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
+    "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "minicpm4_1": MiniCPM4_1ForCausalLM, "glm4": Glm4ForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma2": Gemma2ForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
     "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "minimax": MiniMaxForCausalLM, "diffllama": DiffLlamaForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "gpt_oss": GptOssForCausalLM, "llama4_text": Llama4ForCausalLM, "qwen3_next": Qwen3NextForCausalLM, "qwen3_5_text": Qwen3_5ForCausalLM, "qwen3_5_moe_text": Qwen3_5MoeForCausalLM,
     "qwen3_5": Qwen3_5ForCausalLM, "qwen3_5_moe": Qwen3_5MoeForCausalLM,
     "glm_moe_dsa": DeepseekV3ForCausalLM, "deepseek_v32": DeepseekV3ForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": DeepseekV3ForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,

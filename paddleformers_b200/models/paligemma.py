@@ -203,12 +203,13 @@ class PaliGemmaForConditionalGeneration(PretrainedModel):
             return text_prefix + s[len("model."):] if s.startswith("model.") else s
 
         rules = []
-        for r in build_weight_map(self.config.text_config).rules.values():
+        text_map = build_weight_map(self.config.text_config)
+        for r in text_map.rules.values():
             rules.append(dataclasses.replace(r, target="language." + r.target, sources=[text_name(s) for s in r.sources]))
         known = {r.target for r in rules}
         for name, _ in self.language.named_parameters():                 # parameters without a fusion rule: renamed only
             if "language." + name not in known:
-                rules.append(Rule("language." + name, [text_name(name)]))
+                rules.append(Rule("language." + name, [text_name(text_map.translate(name))]))
         for r in self.vision_tower.weight_map().rules.values():
             rules.append(dataclasses.replace(r, target="vision_tower." + r.target, sources=[other + "vision_tower." + s for s in r.sources]))
         return WeightMap(rules + self.projector_rules(other))

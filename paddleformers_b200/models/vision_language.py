@@ -110,9 +110,12 @@ class _RMSNorm(nn.Module):
 
 class _VisionBlock(nn.Module):
     def __init__(self, dim: int, heads: int, mlp_hidden: int, act: str, dtype=None, device=None, rms_norm: bool = False,
-                 swiglu: bool = False, bias: bool = True, eps: float = 1e-6, mlp_bias: Optional[bool] = None):
+                 swiglu: bool = False, bias: bool = True, eps: float = 1e-6, mlp_bias: Optional[bool] = None, qk_norm: bool = False):
         super().__init__()
         kw = dict(dtype=dtype, device=device)
+        if qk_norm:                                    # per-head RMSNorm on queries and keys before the rotary embedding
+            self.q_norm, self.k_norm = _RMSNorm(dim // heads, eps, **kw), _RMSNorm(dim // heads, eps, **kw)
+        self.qk_norm = qk_norm
         mlp_bias = bias if mlp_bias is None else mlp_bias
         norm = (lambda: _RMSNorm(dim, eps, **kw)) if rms_norm else (lambda: nn.LayerNorm(dim, eps=eps, **kw))
         self.norm1, self.norm2 = norm(), norm()
@@ -144,6 +147,8 @@ class _VisionBlock(nn.Module):
             t1, t2 = t[..., :half].float(), t[..., half:].float()
             return torch.cat([t1 * cos - t2 * sin, t2 * cos + t1 * sin], dim=-1).to(t.dtype)
 
+        if self.qk_norm:
+            q, k = self.q_norm(q.contiguous()), self.k_norm(k.contiguous())
         q, k = rot(q), rot(k)
         outs, off = [], 0
         for n in lengths:                              # full (non-causal) attention inside each image / frame
@@ -704,8 +709,6 @@ class Glm4vMoeConfig(Qwen2VLConfig):
 
     def __init__(self, text_config=None, vision_config=None, image_token_id=151363, video_token_id=151364, image_start_token_id=151339,
                  image_end_token_id=151340, **kwargs):
-        from .configuration import Glm4MoeConfig
-
         text = dict(text_config or {})
         text.pop("model_type", None)
         rp = dict(text.get("rope_parameters") or {})
@@ -714,31 +717,42 @@ class Glm4vMoeConfig(Qwen2VLConfig):
             text["rope_parameters"] = rp
         tie = bool(text.get("tie_word_embeddings", kwargs.get("tie_word_embeddings", False)))
         text.setdefault("tie_word_embeddings", tie)
-        text.setdefault("attention_bias", True)
-        text.setdefault("use_qk_norm", False)
+        for k, v in self._text_defaults.items():
+            text.setdefault(k, v)
         for k in ("video_start_token_id", "video_end_token_id"):
             kwargs.pop(k, None)
         super().__init__(text_config={"num_hidden_layers": 1}, vision_config={}, image_token_id=image_token_id,
                          video_token_id=video_token_id, vision_start_token_id=image_start_token_id,
                          vision_end_token_id=image_end_token_id, **{**kwargs, "tie_word_embeddings": tie})
-        self.text_config = Glm4MoeConfig(**text)
+        self.text_config = self._text_class()(**text)
         self.mrope_section = section
         self.image_start_token_id, self.image_end_token_id = image_start_token_id, image_end_token_id
         v = dict(vision_config or {})
         v.pop("model_type", None)
         self.vision_config = {"depth": 24, "hidden_size": 1536, "hidden_act": "silu", "attention_bias": False, "num_heads": 12,
                               "in_channels": 3, "image_size": 336, "patch_size": 14, "rms_norm_eps": 1e-5, "spatial_merge_size": 2,
-                              "temporal_patch_size": 2, "out_hidden_size": self.text_config.hidden_size, "intermediate_size": 13696, **v}
+                              "temporal_patch_size": 2, "out_hidden_size": self.text_config.hidden_size, "intermediate_size": 13696,
+                              **self._vision_defaults, **v}
+
+    _text_defaults = {"attention_bias": True, "use_qk_norm": False}
+    _vision_defaults: dict = {}
+    _text_type, _vision_type = "glm4v_moe_text", "glm4v_moe_vision"
+
+    @staticmethod
+    def _text_class():
+        from .configuration import Glm4MoeConfig
+
+        return Glm4MoeConfig
 
     def to_dict(self, saving: bool = False):
         d = PretrainedConfig.to_dict(self, saving)
         text = self.text_config.to_dict(saving)
-        text["model_type"] = "glm4v_moe_text"
+        text["model_type"] = self._text_type
         scaling = text.pop("rope_scaling", None) or {}
         text["rope_parameters"] = {"rope_type": "default", **scaling, "rope_theta": text.pop("rope_theta", self.text_config.rope_theta),
                                    "partial_rotary_factor": self.text_config.partial_rotary_factor, "mrope_section": self.mrope_section}
         d["text_config"] = text
-        d["vision_config"] = dict(self.vision_config, model_type="glm4v_moe_vision")
+        d["vision_config"] = dict(self.vision_config, model_type=self._vision_type)
         for k in ("mrope_section", "vision_start_token_id", "vision_end_token_id"):
             d.pop(k, None)
         return d
@@ -827,14 +841,16 @@ class Glm4vMoeForConditionalGeneration(Qwen2VLForConditionalGeneration):
     def weight_map(self) -> WeightMap:
         vis = "model.visual."
         rules = []
-        for r in build_weight_map(self.config.text_config).rules.values():
+        text_map = build_weight_map(self.config.text_config)
+        for r in text_map.rules.values():
             src = [x if x.startswith("lm_head.") else x.replace("model.", "model.language_model.", 1) for x in r.sources]
             rules.append(Rule("language." + r.target, src, r.op, r.dim, r.num_experts, r.expert_pairs, r.sizes, r.rope_deinterleave,
                               r.flatten, r.reshape, r.source_shape, r.offset, fn=r.fn, qkv_groups=r.qkv_groups))
         known = {r.target for r in rules}
         for name, _ in list(self.language.named_parameters()) + [(k, None) for k, _ in self.language.named_buffers()]:
             if "language." + name not in known and (name in dict(self.language.named_parameters()) or name in self.language.state_dict()):
-                rules.append(Rule("language." + name, [name if name.startswith("lm_head.") else name.replace("model.", "model.language_model.", 1)]))
+                theirs = text_map.translate(name)            # the text family's own spelling of plainly renamed tensors
+                rules.append(Rule("language." + name, [theirs if theirs.startswith("lm_head.") else theirs.replace("model.", "model.language_model.", 1)]))
         vc = self.config.vision_config
         dim, out, ms = vc["hidden_size"], vc["out_hidden_size"], vc["spatial_merge_size"]
         conv_shape = [dim, vc["in_channels"], vc["temporal_patch_size"], vc["patch_size"], vc["patch_size"]]
@@ -859,4 +875,79 @@ class Glm4vMoeForConditionalGeneration(Qwen2VLForConditionalGeneration):
                 for leaf in ("weight", "bias"):
                     if f"blocks.{i}.{mine}.{leaf}" in own:
                         rules.append(Rule(a + f"{mine}.{leaf}", [b + f"{theirs}.{leaf}"]))
+        return WeightMap(rules)
+
+
+class GlmOcrConfig(Glm4vMoeConfig):
+    """GLM-OCR (paddleformers/transformers/glm_ocr): the dense GLM-4 decoder with multimodal rotary sections, and the GLM-4.5V
+    vision tower without learned position embeddings, with per-head RMSNorm on queries and keys, biased projections and a
+    merger three times the output width."""
+
+    model_type = "glm_ocr"
+    _text_defaults = {"attention_bias": False}
+    _vision_defaults = {"hidden_size": 1024, "attention_bias": True, "num_heads": 16, "out_hidden_size": 1536, "intermediate_size": 4096}
+    _text_type, _vision_type = "glm_ocr_text", "glm_ocr_vision"
+
+    def __init__(self, image_token_id=59280, video_token_id=59281, image_start_token_id=59256, image_end_token_id=59257, **kwargs):
+        super().__init__(image_token_id=image_token_id, video_token_id=video_token_id, image_start_token_id=image_start_token_id,
+                         image_end_token_id=image_end_token_id, **kwargs)
+
+    @staticmethod
+    def _text_class():
+        from .configuration import Glm4Config
+
+        return Glm4Config
+
+
+class GlmOcrVisionTower(Glm4vVisionTower):
+    def __init__(self, vc: dict, dtype=None, device=None):
+        nn.Module.__init__(self)
+        kw = dict(dtype=dtype, device=device)
+        self.vc = vc
+        dim, out, eps, ms = vc["hidden_size"], vc["out_hidden_size"], vc["rms_norm_eps"], vc["spatial_merge_size"]
+        bias = bool(vc.get("attention_bias", True))
+        self.patch_dim = vc["in_channels"] * vc["temporal_patch_size"] * vc["patch_size"] ** 2
+        self.patch_embed = nn.Linear(self.patch_dim, dim, bias=True, **kw)
+        self.blocks = nn.ModuleList([_VisionBlock(dim, vc["num_heads"], vc["intermediate_size"], vc["hidden_act"], rms_norm=True, swiglu=True,
+                                                  bias=bias, mlp_bias=bias, eps=eps, qk_norm=True, **kw) for _ in range(vc["depth"])])
+        self.post_layernorm = _RMSNorm(dim, eps, **kw)
+        self.downsample = nn.Linear(dim * ms * ms, out, bias=True, **kw)
+        wide = out * vc["in_channels"]
+        self.merge_proj = nn.Linear(out, out, bias=False, **kw)
+        self.merge_norm = nn.LayerNorm(out, **kw)
+        self.merge_gate = nn.Linear(out, wide, bias=False, **kw)
+        self.merge_up = nn.Linear(out, wide, bias=False, **kw)
+        self.merge_down = nn.Linear(wide, out, bias=False, **kw)
+        self.head_dim = dim // vc["num_heads"]
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
+        ms = self.vc["spatial_merge_size"]
+        x = self.patch_embed(pixel_values.to(self.patch_embed.weight.dtype))
+        cos, sin = self.rotary(grid_thw, x.device)
+        lengths = [h * w for t, h, w in grid_thw.tolist() for _ in range(t)]
+        for blk in self.blocks:
+            x = blk(x, cos, sin, lengths)
+        x = self.post_layernorm(x)
+        x = x.view(-1, ms, ms, x.shape[-1]).permute(0, 3, 1, 2).reshape(-1, x.shape[-1] * ms * ms)
+        x = self.merge_proj(self.downsample(x))
+        x = TF.gelu(self.merge_norm(x))
+        return self.merge_down(TF.silu(self.merge_gate(x)) * self.merge_up(x))
+
+
+class GlmOcrForConditionalGeneration(Glm4vMoeForConditionalGeneration):
+    config_class = GlmOcrConfig
+
+    def __init__(self, config: GlmOcrConfig, dtype=None, device=None):
+        PretrainedModel.__init__(self, config)
+        self.visual = GlmOcrVisionTower(config.vision_config, dtype=dtype, device=device)
+        self.language = DecoderForCausalLM(config.text_config, dtype=dtype, device=device)
+        self._vision_prefix, self._text_nested = "model.visual.", True
+
+    def weight_map(self) -> WeightMap:
+        base = super().weight_map()
+        own = dict(self.named_parameters())
+        rules = [r for r in base.rules.values() if r.target in own]        # no position table, no norm after the patch projection
+        for i in range(self.config.vision_config["depth"]):
+            for n in ("q_norm", "k_norm"):
+                rules.append(Rule(f"visual.blocks.{i}.{n}.weight", [f"model.visual.blocks.{i}.attn.{n}.weight"]))
         return WeightMap(rules)

@@ -51,7 +51,7 @@ class AutoModelForConditionalGeneration:
         from ..models.vision_language import (Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration, Qwen2VLConfig,
                                               Qwen2VLForConditionalGeneration, Qwen3VLConfig, Qwen3VLForConditionalGeneration,
                                               Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration, Glm4vMoeConfig,
-                                              Glm4vMoeForConditionalGeneration)
+                                              Glm4vMoeForConditionalGeneration, GlmOcrConfig, GlmOcrForConditionalGeneration)
         from ..models.paligemma import (AyaVisionConfig, AyaVisionForConditionalGeneration, Gemma3Config,
                                         Gemma3ForConditionalGeneration, PaliGemma2Config, PaliGemmaConfig,
                                         PaliGemmaForConditionalGeneration, ShieldGemma2Config, ShieldGemma2ForImageClassification)
@@ -65,7 +65,8 @@ class AutoModelForConditionalGeneration:
                  "qwen2_5_vl": (Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration),
                  "qwen3_vl": (Qwen3VLConfig, Qwen3VLForConditionalGeneration),
                  "qwen3_vl_moe": (Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration),
-                 "glm4v_moe": (Glm4vMoeConfig, Glm4vMoeForConditionalGeneration)}
+                 "glm4v_moe": (Glm4vMoeConfig, Glm4vMoeForConditionalGeneration),
+                 "glm_ocr": (GlmOcrConfig, GlmOcrForConditionalGeneration)}
         if model_type not in table:
             raise ValueError(f"unknown vision-language model_type {model_type!r}; supported: {sorted(table)}")
         return table[model_type]

@@ -810,3 +810,52 @@ def test_log_mel_features_match_hugging_face(tmp_path):
     assert again.nb_max_frames == 200 and torch.equal(again(waves)["input_features"], got)
     with pytest.raises(ValueError, match="resample"):
         mine(waves, sampling_rate=8000)
+
+
+def test_glm4_dense_and_glm_ocr_match_hugging_face(tmp_path):
+    """GLM-4 dense text (four norms per block, interleaved partial rotary rows, fused gate_up in the checkpoint) and GLM-OCR on top
+    of it (vision tower with per-head q / k norms and no position table), against ``transformers`` both ways."""
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    torch.manual_seed(3)
+    hf_text = transformers.Glm4ForCausalLM(transformers.Glm4Config(
+        vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+        attention_bias=True, pad_token_id=0)).eval()
+    hf_text.save_pretrained(str(tmp_path / "glm4"))
+    text = AutoModelForCausalLM.from_pretrained(str(tmp_path / "glm4"), dtype=torch.float32).eval()
+    tokens = torch.randint(0, 300, (2, 12))
+    with torch.no_grad():
+        torch.testing.assert_close(text(tokens).logits, hf_text(tokens).logits, rtol=1e-4, atol=1e-4)
+    text.save_pretrained(str(tmp_path / "glm4_back"))
+    with torch.no_grad():
+        torch.testing.assert_close(transformers.Glm4ForCausalLM.from_pretrained(str(tmp_path / "glm4_back")).eval()(tokens).logits,
+                                   hf_text(tokens).logits, rtol=1e-5, atol=1e-5)
+
+    if not hasattr(transformers, "GlmOcrForConditionalGeneration"):
+        pytest.skip("transformers has no GLM-OCR")
+    vc = dict(hidden_size=32, depth=2, num_heads=2, out_hidden_size=48, intermediate_size=64, image_size=32, patch_size=4,
+              spatial_merge_size=2, temporal_patch_size=2)
+    tc = dict(vocab_size=300, hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=16, rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [2, 1, 1],
+                                            "partial_rotary_factor": 0.5})
+    hf = transformers.GlmOcrForConditionalGeneration(transformers.GlmOcrConfig(
+        vision_config=vc, text_config=tc, image_token_id=299, video_token_id=298, image_start_token_id=297, image_end_token_id=296)).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.dim() == 1:
+                p.normal_(1.0 if "norm" in n and "bias" not in n else 0.0, 0.1)
+    hf.save_pretrained(str(tmp_path / "ocr"))
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path / "ocr"), dtype=torch.float32).eval()
+    grid = torch.tensor([[1, 4, 6], [1, 2, 2]])
+    pixels = torch.randn(int(grid.prod(-1).sum()), 3 * 2 * 4 * 4)
+    ids = torch.tensor([[5, 6, 297] + [299] * 6 + [296, 7, 8, 9, 297, 299, 296, 10, 11]])
+    types = (ids == 299).int()
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=types).logits
+        got = mine(ids, pixel_values=pixels, image_grid_thw=grid, return_logits=True).logits
+    torch.testing.assert_close(got, want, rtol=3e-4, atol=3e-4)
+    mine.save_pretrained(str(tmp_path / "ocr_back"))
+    back = transformers.GlmOcrForConditionalGeneration.from_pretrained(str(tmp_path / "ocr_back")).eval()
+    with torch.no_grad():
+        torch.testing.assert_close(back(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=types).logits, want,
+                                   rtol=1e-5, atol=1e-5)
