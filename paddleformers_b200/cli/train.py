@@ -243,16 +243,26 @@ def run_vl_sft(model_args, data_args, gen_args, train_args):
     if tokenizer is None:
         raise ValueError("VL-SFT needs a tokenizer (model_name_or_path with tokenizer files)")
     vc = model.config.vision_config
-    proc_kw = dict(patch_size=vc["patch_size"], merge_size=vc["spatial_merge_size"], temporal_patch_size=vc["temporal_patch_size"])
-    for k in ("min_pixels", "max_pixels"):
-        if getattr(data_args, k, None):
-            proc_kw[k] = getattr(data_args, k)
-    if model.config.model_type == "qwen3_vl":       # this generation normalises pixels to [-1, 1]
-        proc_kw.update(image_mean=(0.5, 0.5, 0.5), image_std=(0.5, 0.5, 0.5))
-    proc = Qwen2VLImageProcessor(**proc_kw)
-    names = dict(image_token=tokenizer.convert_ids_to_tokens(model.config.image_token_id),
-                 vision_start_token=tokenizer.convert_ids_to_tokens(model.config.vision_start_token_id),
-                 vision_end_token=tokenizer.convert_ids_to_tokens(model.config.vision_end_token_id))
+    if not isinstance(vc, dict):                    # SigLIP towers: fixed image size, a fixed number of tokens per image
+        from ..transformers.image_processing import SiglipImageProcessor
+
+        proc = SiglipImageProcessor(image_size=vc.image_size, tokens_per_image=model.config.num_image_tokens)
+        start, end = getattr(model.config, "boi_token_index", None), getattr(model.config, "eoi_token_index", None)
+        names = dict(image_token=tokenizer.convert_ids_to_tokens(model.config.image_token_id),
+                     vision_start_token=None if start is None else tokenizer.convert_ids_to_tokens(start),
+                     vision_end_token=None if end is None else tokenizer.convert_ids_to_tokens(end),
+                     emit_token_types=model.config.model_type in ("paligemma", "paligemma2"))      # prompt two-way, answer causal
+    else:
+        proc_kw = dict(patch_size=vc["patch_size"], merge_size=vc["spatial_merge_size"], temporal_patch_size=vc["temporal_patch_size"])
+        for k in ("min_pixels", "max_pixels"):
+            if getattr(data_args, k, None):
+                proc_kw[k] = getattr(data_args, k)
+        if model.config.model_type == "qwen3_vl":       # this generation normalises pixels to [-1, 1]
+            proc_kw.update(image_mean=(0.5, 0.5, 0.5), image_std=(0.5, 0.5, 0.5))
+        proc = Qwen2VLImageProcessor(**proc_kw)
+        names = dict(image_token=tokenizer.convert_ids_to_tokens(model.config.image_token_id),
+                     vision_start_token=tokenizer.convert_ids_to_tokens(model.config.vision_start_token_id),
+                     vision_end_token=tokenizer.convert_ids_to_tokens(model.config.vision_end_token_id))
     train_ds = MMSFTDataset(data_args.train_dataset_path, tokenizer, proc, data_args.template, train_args.max_seq_len, **names)
     pad = tokenizer.pad_token_id if tokenizer.pad_token_id is not None else 0
     trainer = Trainer(model=model, args=train_args, train_dataset=train_ds, data_collator=ft.partial(mm_collate_fn, pad_token_id=pad),

@@ -30,14 +30,16 @@ def _load_image(path_or_array) -> np.ndarray:
 
 class MMSFTDataset(Dataset):
     def __init__(self, path_or_examples, tokenizer, image_processor, template: Optional[str], max_seq_len: int,
-                 image_token: str = "<|image_pad|>", vision_start_token: str = "<|vision_start|>",
-                 vision_end_token: str = "<|vision_end|>"):
+                 image_token: str = "<|image_pad|>", vision_start_token: Optional[str] = "<|vision_start|>",
+                 vision_end_token: Optional[str] = "<|vision_end|>", emit_token_types: bool = False):
         self.examples = list(read_examples(path_or_examples)) if isinstance(path_or_examples, str) else list(path_or_examples)
         self.tok, self.proc, self.template, self.max_seq_len = tokenizer, image_processor, get_template(template), max_seq_len
-        ids = tokenizer.convert_tokens_to_ids([image_token, vision_start_token, vision_end_token])
-        if any(i is None or i == tokenizer.unk_token_id for i in ids):
+        ids = [None if t is None else tokenizer.convert_tokens_to_ids(t) for t in (image_token, vision_start_token, vision_end_token)]
+        if any(t is not None and (i is None or i == tokenizer.unk_token_id)
+               for t, i in zip((image_token, vision_start_token, vision_end_token), ids)):
             raise ValueError("the tokenizer must know the image placeholder and vision start / end tokens")
-        self.image_id, self.start_id, self.end_id = ids
+        self.image_id, self.start_id, self.end_id = ids               # families without start / end tokens pass None for them
+        self.emit_token_types = emit_token_types                       # prefix-LM families: 0 on context tokens, 1 on answer tokens
         self.marker_ids = tokenizer.encode(IMAGE_MARKER, add_special_tokens=False)
 
     def __len__(self):
@@ -48,7 +50,8 @@ class MMSFTDataset(Dataset):
         out_ids, out_mask, k, i, m = [], [], 0, 0, len(self.marker_ids)
         while i < len(ids):
             if m and ids[i:i + m] == self.marker_ids and k < len(counts):
-                run = [self.start_id] + [self.image_id] * counts[k] + [self.end_id]
+                run = ([self.start_id] if self.start_id is not None else []) + [self.image_id] * counts[k] \
+                    + ([self.end_id] if self.end_id is not None else [])
                 out_ids += run
                 out_mask += [0] * len(run)            # image tokens are context, never targets
                 k += 1
@@ -68,8 +71,12 @@ class MMSFTDataset(Dataset):
         counts: List[int] = []
         if images:
             pre = self.proc(images)
-            item["pixel_values"], item["image_grid_thw"] = pre["pixel_values"], pre["image_grid_thw"]
-            counts = [self.proc.num_image_tokens(g) for g in pre["image_grid_thw"].tolist()]
+            item["pixel_values"] = pre["pixel_values"]
+            if "image_grid_thw" in pre:                 # variable-resolution towers: one grid per image
+                item["image_grid_thw"] = pre["image_grid_thw"]
+                counts = [self.proc.num_image_tokens(g) for g in pre["image_grid_thw"].tolist()]
+            else:                                       # fixed-size towers: the same number of tokens for every image
+                counts = [self.proc.num_image_tokens()] * len(images)
         norm = to_messages(ex)
         ids, mask = [], []
         for p_ids, r_ids in self.template.encode_multiturn(self.tok, norm["messages"], norm["system"], norm["tools"]):
@@ -80,4 +87,6 @@ class MMSFTDataset(Dataset):
             raise ValueError(f"example {i} needs {len(ids)} tokens (images are not truncated); raise max_seq_len")
         item["input_ids"] = torch.tensor(ids[:-1])
         item["labels"] = torch.tensor([t if m else IGNORE_INDEX for t, m in zip(ids[1:], mask[1:])])
+        if self.emit_token_types:
+            item["token_type_ids"] = torch.tensor(mask[:-1])
         return item

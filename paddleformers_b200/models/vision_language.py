@@ -428,8 +428,14 @@ def mm_collate_fn(examples: List[dict], pad_token_id: int = 0, ignore_index: int
     pv = [torch.as_tensor(e["pixel_values"]) for e in examples if e.get("pixel_values") is not None]
     if pv:
         out["pixel_values"] = torch.cat(pv, dim=0)
-        out["image_grid_thw"] = torch.cat([torch.as_tensor(e["image_grid_thw"]).reshape(-1, 3) for e in examples
-                                           if e.get("image_grid_thw") is not None], dim=0)
+        grids = [torch.as_tensor(e["image_grid_thw"]).reshape(-1, 3) for e in examples if e.get("image_grid_thw") is not None]
+        if grids:                                      # fixed-size towers have no grids
+            out["image_grid_thw"] = torch.cat(grids, dim=0)
+    if any("token_type_ids" in e for e in examples):   # prefix-LM families; padding counts as (causal) answer positions
+        types = torch.ones((len(examples), S), dtype=torch.long)
+        for i, e in enumerate(examples):
+            types[i, :len(e["token_type_ids"])] = torch.as_tensor(e["token_type_ids"])
+        out["token_type_ids"] = types
     return out
 
 

@@ -146,3 +146,29 @@ class Qwen2VLVideoProcessor(Qwen2VLImageProcessor):
         if return_tensors == "pt":
             return {"pixel_values_videos": torch.from_numpy(pv), "video_grid_thw": torch.from_numpy(grid)}
         return {"pixel_values_videos": pv, "video_grid_thw": grid}
+
+
+class SiglipImageProcessor:
+    """Fixed-size pre-processing of the SigLIP towers (PaliGemma, Gemma 3, Aya Vision; paddleformers/transformers/paligemma2/
+    image_processor.py): every image is resized to ``image_size`` x ``image_size`` (bicubic, antialiased), scaled to [0, 1] and
+    normalised. Returns ``pixel_values`` float32 [images, 3, size, size]; each image stands for ``tokens_per_image``
+    placeholder tokens."""
+
+    def __init__(self, image_size: int = 224, image_mean=(0.5, 0.5, 0.5), image_std=(0.5, 0.5, 0.5), tokens_per_image: int = 256,
+                 rescale_factor: float = 1.0 / 255.0):
+        self.image_size, self.tokens_per_image, self.rescale_factor = int(image_size), int(tokens_per_image), rescale_factor
+        self.image_mean, self.image_std = tuple(image_mean), tuple(image_std)
+
+    def num_image_tokens(self, grid=None) -> int:
+        return self.tokens_per_image
+
+    def __call__(self, images: List[np.ndarray], return_tensors: str = "pt"):
+        mean = torch.tensor(self.image_mean, dtype=torch.float32).view(1, 3, 1, 1)
+        std = torch.tensor(self.image_std, dtype=torch.float32).view(1, 3, 1, 1)
+        out = []
+        for img in images:
+            t = torch.as_tensor(np.ascontiguousarray(img)).permute(2, 0, 1)[None].float()
+            t = torch.nn.functional.interpolate(t, size=(self.image_size, self.image_size), mode="bicubic", align_corners=False,
+                                                antialias=True).clamp(0.0, 255.0)
+            out.append((t * self.rescale_factor - mean) / std)
+        return {"pixel_values": torch.cat(out, dim=0)}

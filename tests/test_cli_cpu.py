@@ -286,3 +286,75 @@ def test_recipe_stages_turn_on_their_switches_and_train(tmp_path):
     assert os.path.exists(out / "model.safetensors")
     saved = json.loads((out / "config.json").read_text())
     assert saved["model_type"] == "deepseek_v3"
+
+
+@pytest.mark.parametrize("family", ["gemma3", "paligemma"])
+def test_vl_sft_stage_trains_the_siglip_families(tmp_path, family):
+    """VL-SFT on fixed-size-image families: Gemma 3 (begin / end-of-image tokens around a fixed run of placeholders, two-way attention
+    inside each image) and PaliGemma (placeholders only, token types mark the two-way prompt)."""
+    from PIL import Image
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    from paddleformers_b200.cli.cli import main
+    from paddleformers_b200.datasets.mm_dataset import MMSFTDataset
+    from paddleformers_b200.models.paligemma import Gemma3Config, PaliGemmaConfig
+    from paddleformers_b200.models.vision_language import mm_collate_fn
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+    from paddleformers_b200.transformers.image_processing import SiglipImageProcessor
+
+    words = ["<pad>", "<s>", "</s>", "<unk>", "Human:", "Assistant:", "System:", "<image>", "<image_soft_token>", "<start_of_image>",
+             "<end_of_image>"] + [f"w{i}" for i in range(40)]
+    tok = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    fast = PreTrainedTokenizerFast(tokenizer_object=tok, pad_token="<pad>", bos_token="<s>", eos_token="</s>", unk_token="<unk>")
+    vision = dict(hidden_size=16, intermediate_size=32, num_hidden_layers=1, num_attention_heads=2, image_size=16, patch_size=4)
+    text = dict(vocab_size=len(words), hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1,
+                head_dim=16)
+    if family == "gemma3":
+        cfg = Gemma3Config(text_config=dict(text, sliding_window=8, query_pre_attn_scalar=16), vision_config=vision, mm_tokens_per_image=4,
+                           image_token_index=words.index("<image_soft_token>"), boi_token_index=words.index("<start_of_image>"),
+                           eoi_token_index=words.index("<end_of_image>"))
+    else:
+        cfg = PaliGemmaConfig(text_config=dict(text, model_type="gemma"), vision_config=vision, image_token_index=words.index("<image>"),
+                              projection_dim=32)
+    base = tmp_path / "base"
+    torch.manual_seed(0)
+    AutoModelForConditionalGeneration.from_config(cfg, dtype=torch.float32).save_pretrained(str(base))
+    fast.save_pretrained(str(base))
+    rng = np.random.RandomState(0)
+    data = tmp_path / "vl.jsonl"
+    with open(data, "w") as f:
+        for i in range(8):
+            img = tmp_path / f"img{i}.png"
+            Image.fromarray((rng.rand(20 + 4 * (i % 3), 24, 3) * 255).astype("uint8")).save(img)
+            f.write(json.dumps({"images": [str(img)], "messages": [{"role": "user", "content": "<image> w1 w2"},
+                                                                     {"role": "assistant", "content": f"w{3 + i % 5} w9"}]}) + "\n")
+    proc = SiglipImageProcessor(image_size=16, tokens_per_image=cfg.num_image_tokens)
+    ds = MMSFTDataset(str(data), fast, proc, "default", 64, image_token=words[cfg.image_token_id],
+                      vision_start_token="<start_of_image>" if family == "gemma3" else None,
+                      vision_end_token="<end_of_image>" if family == "gemma3" else None, emit_token_types=family == "paligemma")
+    batch = mm_collate_fn([ds[0], ds[1]])
+    assert batch["pixel_values"].shape == (2, 3, 16, 16) and "image_grid_thw" not in batch
+    assert int((batch["input_ids"] == cfg.image_token_id).sum()) == 2 * cfg.num_image_tokens
+    if family == "paligemma":
+        assert batch["token_type_ids"].shape == batch["input_ids"].shape and int(batch["token_type_ids"][0, 0]) == 0
+        answered = batch["labels"][0] != -100
+        assert bool((batch["token_type_ids"][0][answered.roll(1, 0)][1:] == 1).all())     # answer tokens are fed back causally
+    out = tmp_path / "out"
+    cfg_file = tmp_path / "vl.json"
+    cfg_file.write_text(json.dumps({
+        "stage": "VL-SFT", "model_name_or_path": str(base), "compute_type": "float32", "device": "cpu", "train_dataset_path": str(data),
+        "template": "default", "max_seq_len": 64, "max_steps": 4, "per_device_train_batch_size": 2, "learning_rate": 5e-3,
+        "logging_steps": 1, "save_strategy": "no", "output_dir": str(out)}))
+    env = os.environ.get("CUDA_VISIBLE_DEVICES")
+    os.environ["CUDA_VISIBLE_DEVICES"] = ""
+    try:
+        assert main(["train", str(cfg_file)]) == 0
+    finally:
+        if env is None:
+            os.environ.pop("CUDA_VISIBLE_DEVICES", None)
+        else:
+            os.environ["CUDA_VISIBLE_DEVICES"] = env
+    model = AutoModelForConditionalGeneration.from_pretrained(str(out), dtype=torch.float32)
+    assert model.config.model_type == family and os.path.exists(out / "tokenizer.json")
