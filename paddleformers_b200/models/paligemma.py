@@ -136,14 +136,14 @@ class PaliGemmaForConditionalGeneration(PretrainedModel):
                 Rule("projector.bias", [prefix + "multi_modal_projector.linear.bias"])]
 
     def forward(self, input_ids, pixel_values=None, token_type_ids=None, labels=None, kend=None,
-                return_logits: Optional[bool] = None, **unused):
+                return_logits: Optional[bool] = None, image_embeds=None, **unused):
         cfg, lm = self.config, self.language
         B, S = input_ids.shape
         is_image = input_ids == cfg.image_token_id
         ids = input_ids.masked_fill(is_image, 0) if cfg.image_token_id >= cfg.text_config.vocab_size else input_ids
         h = lm.model.embed(ids)
-        if pixel_values is not None:
-            feats = self.image_features(pixel_values).to(h.dtype)
+        if pixel_values is not None or image_embeds is not None:
+            feats = (image_embeds if image_embeds is not None else self.image_features(pixel_values)).to(h.dtype)
             assert int(is_image.sum()) == feats.shape[0], "one placeholder token per image patch is required"
             h = h.masked_scatter(is_image.reshape(-1)[:, None], feats)
         two_way = self.two_way_tokens(input_ids, token_type_ids)
@@ -164,6 +164,34 @@ class PaliGemmaForConditionalGeneration(PretrainedModel):
             out.loss, _ = lm._loss(hidden, lab, scale)
             out.num_tokens = count
         return out
+
+    def generation_token_types(self, prompt_len: int, total_len: int, batch: int, device) -> Optional[torch.Tensor]:
+        """Token types while decoding: the prompt stays a two-way prefix, generated tokens are causal."""
+        types = torch.ones(batch, total_len, dtype=torch.long, device=device)
+        types[:, :prompt_len] = 0
+        return types
+
+    @torch.no_grad()
+    def generate(self, input_ids, pixel_values=None, max_new_tokens: int = 32, eos_token_id: Optional[int] = None):
+        """Greedy decoding. Every step re-reads the whole sequence (no key / value cache): the image features are computed once
+        and the decoder sees the same masks as in training, so the result equals cached decoding."""
+        cfg, lm = self.config, self.language
+        eos = eos_token_id if eos_token_id is not None else getattr(cfg.text_config, "eos_token_id", None)
+        eos_ids = set(eos) if isinstance(eos, (list, tuple)) else ({eos} if eos is not None else set())
+        feats = self.image_features(pixel_values) if pixel_values is not None else None
+        ids, prompt_len = input_ids, input_ids.shape[1]
+        done = torch.zeros(ids.shape[0], dtype=torch.bool, device=ids.device)
+        pad = getattr(cfg.text_config, "pad_token_id", None) or 0
+        for _ in range(max_new_tokens):
+            types = self.generation_token_types(prompt_len, ids.shape[1], ids.shape[0], ids.device)
+            logits = self.forward(ids, token_type_ids=types, image_embeds=feats).logits[:, -1]
+            nxt = torch.where(done, torch.full_like(logits.argmax(-1), pad), logits.argmax(-1))
+            ids = torch.cat([ids, nxt[:, None]], dim=1)
+            for e in eos_ids:
+                done |= nxt == e
+            if bool(done.all()):
+                break
+        return ids
 
     @property
     def loss_accumulation_steps(self):
@@ -269,6 +297,9 @@ class Gemma3ForConditionalGeneration(PaliGemmaForConditionalGeneration):
         normed = (normed * (1.0 + self.mm_soft_emb_norm.float())).to(hidden.dtype)
         return (normed @ self.mm_input_projection_weight).reshape(-1, cfg.text_config.hidden_size)
 
+    def generation_token_types(self, prompt_len, total_len, batch, device):
+        return None                                    # the image blocks are found from the placeholder tokens
+
     def two_way_tokens(self, input_ids, token_type_ids) -> torch.Tensor:
         """The tokens of each image (type 1, or the image placeholder when no types are given); consecutive images are told
         apart by the end-of-image / begin-of-image tokens between them."""
@@ -342,6 +373,9 @@ class AyaVisionForConditionalGeneration(PaliGemmaForConditionalGeneration):
         return self.linear_2(torch.nn.functional.silu(gate) * val).reshape(-1, self.config.text_config.hidden_size)
 
     def two_way_tokens(self, input_ids, token_type_ids):
+        return None
+
+    def generation_token_types(self, prompt_len, total_len, batch, device):
         return None
 
     def projector_rules(self, prefix: str):

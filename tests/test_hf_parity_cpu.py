@@ -859,3 +859,38 @@ def test_glm4_dense_and_glm_ocr_match_hugging_face(tmp_path):
     with torch.no_grad():
         torch.testing.assert_close(back(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=types).logits, want,
                                    rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("family", ["paligemma", "gemma3"])
+def test_greedy_generation_of_siglip_composites_matches_hugging_face(tmp_path, family):
+    """Decoding without a cache under the training masks (two-way prompt / image blocks, causal continuation) gives the tokens
+    that transformers produces with its cache."""
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    torch.manual_seed(5)
+    vision = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, image_size=16, patch_size=8, vision_use_head=False)
+    text = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1, head_dim=16,
+                vocab_size=300, initializer_range=0.3)
+    if family == "paligemma":
+        hf = transformers.PaliGemmaForConditionalGeneration(transformers.PaliGemmaConfig(
+            vision_config=dict(vision, projection_dim=64), text_config=dict(text, model_type="gemma"), image_token_id=299, hidden_size=64,
+            projection_dim=64)).eval()
+        ids = torch.tensor([[299] * 4 + [2, 5, 6, 7]])
+        extra = {}
+    else:
+        hf = transformers.Gemma3ForConditionalGeneration(transformers.Gemma3Config(
+            vision_config=vision, text_config=dict(text, sliding_window=4, query_pre_attn_scalar=16), mm_tokens_per_image=4,
+            image_token_index=299, boi_token_index=297, eoi_token_index=298)).eval()
+        with torch.no_grad():
+            hf.model.multi_modal_projector.mm_input_projection_weight.normal_(0, 0.3)
+        ids = torch.tensor([[2, 297] + [299] * 4 + [298, 5, 6, 7]])
+        extra = {"token_type_ids": (ids == 299).long()}
+    hf.generation_config.eos_token_id = None
+    hf.save_pretrained(str(tmp_path))
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path), dtype=torch.float32).eval()
+    pixels = torch.randn(1, 3, 16, 16)
+    want = hf.generate(input_ids=ids, pixel_values=pixels, max_new_tokens=6, do_sample=False, **extra)
+    got = mine.generate(ids, pixel_values=pixels, max_new_tokens=6, eos_token_id=-1)
+    assert got.tolist() == want.tolist()
+    if family == "gemma3":                                       # (tied tiny Gemma repeats its last token)
+        assert len(set(got[0, ids.shape[1]:].tolist())) > 1      # not a degenerate repetition
