@@ -202,6 +202,7 @@ class PaliGemmaForConditionalGeneration(PretrainedModel):
         self.language.loss_accumulation_steps = v
 
     # ------------------------------------------------------------------ checkpoint names
+    _vision_name = "vision_tower."
     _LAYOUTS = {                                   # (decoder "model." ->, vision / projector prefix)
         "legacy": ("language_model.model.", ""),                   # published checkpoints
         "flat": ("model.language_model.", "model."),
@@ -239,7 +240,7 @@ class PaliGemmaForConditionalGeneration(PretrainedModel):
             if "language." + name not in known:
                 rules.append(Rule("language." + name, [text_name(text_map.translate(name))]))
         for r in self.vision_tower.weight_map().rules.values():
-            rules.append(dataclasses.replace(r, target="vision_tower." + r.target, sources=[other + "vision_tower." + s for s in r.sources]))
+            rules.append(dataclasses.replace(r, target="vision_tower." + r.target, sources=[other + self._vision_name + s for s in r.sources]))
         return WeightMap(rules + self.projector_rules(other))
 
 

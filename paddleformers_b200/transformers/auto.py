@@ -56,7 +56,10 @@ class AutoModelForConditionalGeneration:
                                         Gemma3ForConditionalGeneration, PaliGemma2Config, PaliGemmaConfig,
                                         PaliGemmaForConditionalGeneration, ShieldGemma2Config, ShieldGemma2ForImageClassification)
 
-        table = {"paligemma": (PaliGemmaConfig, PaliGemmaForConditionalGeneration),
+        from ..models.llama4_vision import Llama4Config, Llama4ForConditionalGeneration
+
+        table = {"llama4": (Llama4Config, Llama4ForConditionalGeneration),
+                 "paligemma": (PaliGemmaConfig, PaliGemmaForConditionalGeneration),
                  "paligemma2": (PaliGemma2Config, PaliGemmaForConditionalGeneration),
                  "gemma3": (Gemma3Config, Gemma3ForConditionalGeneration),
                  "aya_vision": (AyaVisionConfig, AyaVisionForConditionalGeneration),

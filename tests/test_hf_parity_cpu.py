@@ -900,3 +900,35 @@ def test_greedy_generation_of_siglip_composites_matches_hugging_face(tmp_path, f
         hf.eval()
         mine_types = types if family == "paligemma" else {}
         torch.testing.assert_close(mine(want, pixel_values=pixels, **mine_types).logits[:, -1], ref, rtol=1e-4, atol=1e-4)
+
+
+def test_llama4_with_images_matches_hugging_face(tmp_path):
+    """Vision tower (class token last, interleaved 2-D rotary pairs, 2 x 2 patch folding adapter), bias-free projector and the
+    Llama 4 text decoder with chunked local layers and experts; checkpoint round trip."""
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    if not hasattr(transformers, "Llama4ForConditionalGeneration"):
+        pytest.skip("transformers has no Llama 4")
+    torch.manual_seed(0)
+    tc = dict(vocab_size=128, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=48,
+              intermediate_size_mlp=96, num_hidden_layers=2, num_local_experts=4, num_experts_per_tok=1, attention_chunk_size=8,
+              interleave_moe_layer_step=2, floor_scale=4, attn_scale=0.3, max_position_embeddings=128, pad_token_id=0)
+    vc = dict(hidden_size=32, num_hidden_layers=2, num_attention_heads=2, intermediate_size=128, image_size=16, patch_size=4, num_channels=3,
+              vision_output_dim=48, projector_input_dim=48, projector_output_dim=48, pixel_shuffle_ratio=0.5)
+    hf = transformers.Llama4ForConditionalGeneration(transformers.Llama4Config(
+        text_config=tc, vision_config=vc, image_token_index=127, boi_token_index=125, eoi_token_index=126)).eval()
+    hf.save_pretrained(str(tmp_path / "hf"))
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).eval()
+    assert mine.config.num_image_tokens == 4
+    ids = torch.tensor([[1, 5, 125] + [127] * 4 + [126, 6, 7, 8, 9, 10], [1, 125] + [127] * 4 + [126, 16, 17, 18, 19, 20, 21]])
+    pixels = torch.randn(2, 3, 16, 16)
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pixels).logits
+        torch.testing.assert_close(mine(ids, pixel_values=pixels).logits, want, rtol=1e-4, atol=1e-4)
+    labels = torch.cat([ids[:, 1:], torch.full_like(ids[:, :1], -100)], 1).masked_fill(ids.roll(-1, 1) >= 125, -100)
+    mine(ids, pixel_values=pixels, labels=labels).loss.backward()
+    assert mine.vision_tower.class_embedding.grad.abs().sum() > 0 and mine.projector.weight.grad.abs().sum() > 0
+    mine.save_pretrained(str(tmp_path / "mine"))
+    back = transformers.Llama4ForConditionalGeneration.from_pretrained(str(tmp_path / "mine")).eval()
+    with torch.no_grad():
+        torch.testing.assert_close(back(input_ids=ids, pixel_values=pixels).logits, want, rtol=1e-5, atol=1e-5)
