@@ -243,10 +243,11 @@ def run_vl_sft(model_args, data_args, gen_args, train_args):
     if tokenizer is None:
         raise ValueError("VL-SFT needs a tokenizer (model_name_or_path with tokenizer files)")
     vc = model.config.vision_config
-    if not isinstance(vc, dict):                    # SigLIP towers: fixed image size, a fixed number of tokens per image
+    if not isinstance(vc, dict) or "spatial_merge_size" not in vc:    # fixed image size, a fixed number of tokens per image
         from ..transformers.image_processing import SiglipImageProcessor
 
-        proc = SiglipImageProcessor(image_size=vc.image_size, tokens_per_image=model.config.num_image_tokens)
+        size = vc["image_size"] if isinstance(vc, dict) else vc.image_size
+        proc = SiglipImageProcessor(image_size=size, tokens_per_image=model.config.num_image_tokens)
         start, end = getattr(model.config, "boi_token_index", None), getattr(model.config, "eoi_token_index", None)
         names = dict(image_token=tokenizer.convert_ids_to_tokens(model.config.image_token_id),
                      vision_start_token=None if start is None else tokenizer.convert_ids_to_tokens(start),
