@@ -1024,7 +1024,7 @@ UNSUPPORTED_FAMILIES = {
     "kimi_k25": "vision tower", "hyperencoder": "encoder stack of its own",
     "phi4_multimodal": "vision and audio towers", "molmo": "vision tower with pooled multi-crop features",
     "ernie4_5_vl": "vision tower, modality-aware experts", "ernie4_5_moe_vl": "vision tower, modality-aware experts",
-    "paddleocr_vl": "vision tower", "qwen3_omni_moe": "audio / vision towers",
+    "qwen3_omni_moe": "audio / vision towers",
 }
 
 

@@ -58,7 +58,10 @@ class AutoModelForConditionalGeneration:
 
         from ..models.llama4_vision import Llama4Config, Llama4ForConditionalGeneration
 
+        from ..models.paddleocr_vl import PaddleOCRVLConfig, PaddleOCRVLForConditionalGeneration
+
         table = {"llama4": (Llama4Config, Llama4ForConditionalGeneration),
+                 "paddleocr_vl": (PaddleOCRVLConfig, PaddleOCRVLForConditionalGeneration),
                  "paligemma": (PaliGemmaConfig, PaliGemmaForConditionalGeneration),
                  "paligemma2": (PaliGemma2Config, PaliGemmaForConditionalGeneration),
                  "gemma3": (Gemma3Config, Gemma3ForConditionalGeneration),

@@ -932,3 +932,37 @@ def test_llama4_with_images_matches_hugging_face(tmp_path):
     back = transformers.Llama4ForConditionalGeneration.from_pretrained(str(tmp_path / "mine")).eval()
     with torch.no_grad():
         torch.testing.assert_close(back(input_ids=ids, pixel_values=pixels).logits, want, rtol=1e-5, atol=1e-5)
+
+
+def test_paddleocr_vl_matches_hugging_face(tmp_path):
+    """Variable-resolution SigLIP-style tower (bilinearly resampled positions, 2-D rotary, raster-order 2 x 2 merge) and the dense
+    decoder with multimodal rotary sections, two images of different sizes in one row; checkpoint round trip."""
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    if not hasattr(transformers, "PaddleOCRVLForConditionalGeneration"):
+        pytest.skip("transformers has no PaddleOCR-VL")
+    torch.manual_seed(0)
+    hf = transformers.PaddleOCRVLForConditionalGeneration(transformers.PaddleOCRVLConfig(
+        vision_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2, image_size=16, patch_size=4,
+                           spatial_merge_size=2),
+        text_config=dict(vocab_size=300, hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=16, max_position_embeddings=256,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [4, 2, 2]}),
+        image_token_id=299, video_token_id=298, vision_start_token_id=297, vision_end_token_id=296)).eval()
+    hf.save_pretrained(str(tmp_path / "hf"))
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).eval()
+    grid = torch.tensor([[1, 4, 6], [1, 2, 2]])
+    pixels = torch.randn(int(grid.prod(-1).sum()), 3, 4, 4)
+    ids = torch.tensor([[5, 6, 297] + [299] * 6 + [296, 7, 8, 9, 297, 299, 296, 10, 11]])
+    types = (ids == 299).int()
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=types).logits
+        torch.testing.assert_close(mine(ids, pixel_values=pixels, image_grid_thw=grid).logits, want, rtol=1e-4, atol=1e-4)
+    labels = torch.cat([ids[:, 1:], torch.full_like(ids[:, :1], -100)], 1).masked_fill(ids.roll(-1, 1) >= 296, -100)
+    mine(ids, pixel_values=pixels, image_grid_thw=grid, labels=labels).loss.backward()
+    assert mine.visual.position_embedding.weight.grad.abs().sum() > 0
+    mine.save_pretrained(str(tmp_path / "mine"))
+    back = transformers.PaddleOCRVLForConditionalGeneration.from_pretrained(str(tmp_path / "mine")).eval()
+    with torch.no_grad():
+        torch.testing.assert_close(back(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=types).logits, want,
+                                   rtol=1e-5, atol=1e-5)
