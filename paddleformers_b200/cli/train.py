@@ -254,7 +254,9 @@ def run_vl_sft(model_args, data_args, gen_args, train_args):
                      vision_end_token=None if end is None else tokenizer.convert_ids_to_tokens(end),
                      emit_token_types=model.config.model_type in ("paligemma", "paligemma2"))      # prompt two-way, answer causal
     else:
-        proc_kw = dict(patch_size=vc["patch_size"], merge_size=vc["spatial_merge_size"], temporal_patch_size=vc["temporal_patch_size"])
+        proc_kw = dict(patch_size=vc["patch_size"], merge_size=vc["spatial_merge_size"], temporal_patch_size=vc.get("temporal_patch_size", 1))
+        if model.config.model_type == "paddleocr_vl":   # single-frame patches in raster order, pixels in [-1, 1]
+            proc_kw.update(raster_order=True, image_mean=(0.5, 0.5, 0.5), image_std=(0.5, 0.5, 0.5))
         for k in ("min_pixels", "max_pixels"):
             if getattr(data_args, k, None):
                 proc_kw[k] = getattr(data_args, k)

@@ -51,8 +51,9 @@ def _resize(img: np.ndarray, h: int, w: int) -> np.ndarray:
 class Qwen2VLImageProcessor:
     def __init__(self, patch_size: int = 14, merge_size: int = 2, temporal_patch_size: int = 2, min_pixels: int = 56 * 56,
                  max_pixels: int = 28 * 28 * 1280, image_mean: Sequence[float] = OPENAI_CLIP_MEAN,
-                 image_std: Sequence[float] = OPENAI_CLIP_STD, rescale_factor: float = 1.0 / 255.0):
+                 image_std: Sequence[float] = OPENAI_CLIP_STD, rescale_factor: float = 1.0 / 255.0, raster_order: bool = False):
         self.patch_size, self.merge_size, self.temporal_patch_size = patch_size, merge_size, temporal_patch_size
+        self.raster_order = raster_order           # towers that merge after the encoder read patches row by row (PaddleOCR-VL)
         self.min_pixels, self.max_pixels = min_pixels, max_pixels
         self.mean = np.asarray(image_mean, dtype=np.float32)
         self.std = np.asarray(image_std, dtype=np.float32)
@@ -67,6 +68,9 @@ class Qwen2VLImageProcessor:
         x = np.transpose(x, (2, 0, 1))[None].repeat(T, axis=0)               # [T, C, H, W]: a still image fills every frame
         gh, gw = h // P, w // P
         C = x.shape[1]
+        if self.raster_order:
+            x = x.reshape(T, C, gh, P, gw, P).transpose(2, 4, 1, 0, 3, 5)       # [gh, gw, C, T, P, P]
+            return x.reshape(gh * gw, C * T * P * P), (1, gh, gw)
         x = x.reshape(1, T, C, gh // m, m, P, gw // m, m, P)
         x = x.transpose(0, 3, 6, 4, 7, 2, 1, 5, 8)                          # [1, gh/m, gw/m, m, m, C, T, P, P]
         return x.reshape(gh * gw, C * T * P * P), (1, gh, gw)

@@ -358,3 +358,54 @@ def test_vl_sft_stage_trains_the_siglip_families(tmp_path, family):
             os.environ["CUDA_VISIBLE_DEVICES"] = env
     model = AutoModelForConditionalGeneration.from_pretrained(str(out), dtype=torch.float32)
     assert model.config.model_type == family and os.path.exists(out / "tokenizer.json")
+
+
+def test_vl_sft_stage_trains_paddleocr_vl(tmp_path):
+    """Variable-resolution tower fed with raster-order single-frame patches from the image processor."""
+    from PIL import Image
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    from paddleformers_b200.cli.cli import main
+    from paddleformers_b200.models.paddleocr_vl import PaddleOCRVLConfig
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    words = ["<pad>", "<s>", "</s>", "<unk>", "Human:", "Assistant:", "System:", "<image>", "<|image_pad|>", "<|vision_start|>",
+             "<|vision_end|>"] + [f"w{i}" for i in range(40)]
+    tok = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    fast = PreTrainedTokenizerFast(tokenizer_object=tok, pad_token="<pad>", bos_token="<s>", eos_token="</s>", unk_token="<unk>")
+    cfg = PaddleOCRVLConfig(
+        text_config=dict(vocab_size=len(words), hidden_size=32, intermediate_size=48, num_hidden_layers=1, num_attention_heads=2,
+                         num_key_value_heads=1, head_dim=16, rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [4, 2, 2]}),
+        vision_config=dict(hidden_size=16, intermediate_size=32, num_hidden_layers=1, num_attention_heads=2, image_size=16, patch_size=4),
+        image_token_id=words.index("<|image_pad|>"), vision_start_token_id=words.index("<|vision_start|>"),
+        vision_end_token_id=words.index("<|vision_end|>"))
+    base = tmp_path / "base"
+    torch.manual_seed(0)
+    AutoModelForConditionalGeneration.from_config(cfg, dtype=torch.float32).save_pretrained(str(base))
+    fast.save_pretrained(str(base))
+    rng = np.random.RandomState(0)
+    data = tmp_path / "vl.jsonl"
+    with open(data, "w") as f:
+        for i in range(6):
+            img = tmp_path / f"img{i}.png"
+            Image.fromarray((rng.rand(20 + 4 * (i % 3), 24, 3) * 255).astype("uint8")).save(img)
+            f.write(json.dumps({"images": [str(img)], "messages": [{"role": "user", "content": "<image> w1 w2"},
+                                                                     {"role": "assistant", "content": f"w{3 + i % 5} w9"}]}) + "\n")
+    out = tmp_path / "out"
+    cfg_file = tmp_path / "vl.json"
+    cfg_file.write_text(json.dumps({
+        "stage": "VL-SFT", "model_name_or_path": str(base), "compute_type": "float32", "device": "cpu", "train_dataset_path": str(data),
+        "template": "default", "max_seq_len": 64, "max_steps": 3, "per_device_train_batch_size": 2, "learning_rate": 5e-3,
+        "logging_steps": 1, "save_strategy": "no", "output_dir": str(out), "min_pixels": 256, "max_pixels": 1024}))
+    env = os.environ.get("CUDA_VISIBLE_DEVICES")
+    os.environ["CUDA_VISIBLE_DEVICES"] = ""
+    try:
+        assert main(["train", str(cfg_file)]) == 0
+    finally:
+        if env is None:
+            os.environ.pop("CUDA_VISIBLE_DEVICES", None)
+        else:
+            os.environ["CUDA_VISIBLE_DEVICES"] = env
+    assert AutoModelForConditionalGeneration.from_pretrained(str(out), dtype=torch.float32).config.model_type == "paddleocr_vl"

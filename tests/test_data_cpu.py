@@ -261,3 +261,26 @@ def test_rl_prompt_dataset_left_pads_and_batch_container_operations(tmp_path):
     assert len(seen) == 6 and sorted(x[0] for x in seen[:3]) == ["a", "b", "c"]
     with pytest.raises(ValueError):
         DataProto.from_dict({"a": torch.zeros(2)}, {"b": np.zeros(3)})
+
+
+def test_image_processor_raster_order_matches_plain_patch_cutting():
+    """Towers that merge patches after the encoder read them row by row: the processor's raster layout equals cutting the
+    normalised image into P x P tiles in reading order, and holds the same patches as the merge-block layout."""
+    import numpy as np
+    import torch
+
+    from paddleformers_b200.transformers.image_processing import Qwen2VLImageProcessor
+
+    rng = np.random.RandomState(0)
+    img = (rng.rand(40, 56, 3) * 255).astype("uint8")
+    kw = dict(patch_size=4, merge_size=2, temporal_patch_size=1, min_pixels=64, max_pixels=4096, image_mean=(0.5,) * 3, image_std=(0.5,) * 3)
+    raster = Qwen2VLImageProcessor(raster_order=True, **kw)([img])
+    blocks = Qwen2VLImageProcessor(**kw)([img])
+    t, gh, gw = raster["image_grid_thw"][0].tolist()
+    assert raster["pixel_values"].shape == (gh * gw, 3 * 4 * 4) and torch.equal(raster["image_grid_thw"], blocks["image_grid_thw"])
+    tiles = raster["pixel_values"].view(gh, gw, 3, 4, 4)
+    full = tiles.permute(2, 0, 3, 1, 4).reshape(3, gh * 4, gw * 4)                 # stitch the tiles back into the image
+    again = full.view(3, gh, 4, gw, 4).permute(1, 3, 0, 2, 4).reshape(gh * gw, -1)
+    assert torch.equal(again, raster["pixel_values"])
+    reordered = blocks["pixel_values"].view(gh // 2, gw // 2, 2, 2, -1).permute(0, 2, 1, 3, 4).reshape(gh * gw, -1)
+    assert torch.equal(reordered, raster["pixel_values"])
