@@ -175,3 +175,37 @@ def test_families_on_tensor_operation_paths_train_in_bf16_on_the_device(F, famil
     g = getattr(emb_g, "main_grad", None)
     g = g if g is not None and g.abs().sum() > 0 else emb_g.grad
     assert g is not None and torch.isfinite(g.float()).all()
+
+
+def test_paligemma_two_way_prefix_on_the_device(F):
+    """SigLIP tower (head size 64: the generic attention path), projector and a Gemma decoder under the two-way prefix mask: the bf16
+    device run stays close to the fp32 host run of the same weights, and gradients reach the tower."""
+    from paddleformers_b200.models.paligemma import PaliGemmaConfig
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    def config():
+        return PaliGemmaConfig(
+            vision_config=dict(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2, image_size=64, patch_size=16),
+            text_config=dict(model_type="gemma", hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
+                             num_key_value_heads=1, head_dim=128, vocab_size=4096),
+            image_token_index=4095, projection_dim=512)
+
+    torch.manual_seed(0)
+    ref = AutoModelForConditionalGeneration.from_config(config(), dtype=torch.float32)
+    gpu = AutoModelForConditionalGeneration.from_config(config(), dtype=torch.bfloat16, device="cuda")
+    sd = {k: v.to(torch.bfloat16) for k, v in ref.state_dict().items()}
+    gpu.load_state_dict(sd)
+    ref.load_state_dict({k: v.float() for k, v in sd.items()})
+    n_img = ref.config.num_image_tokens
+    ids = torch.cat([torch.full((2, n_img), 4095), torch.randint(0, 4000, (2, 48))], dim=1)
+    types = torch.cat([torch.zeros(2, n_img + 16, dtype=torch.long), torch.ones(2, 32, dtype=torch.long)], dim=1)
+    labels = torch.where(types == 1, ids, torch.full_like(ids, -100)).roll(-1, 1)
+    labels[:, -1] = -100
+    pixels = torch.randn(2, 3, 64, 64)
+    a = ref(ids, pixel_values=pixels, token_type_ids=types, labels=labels)
+    b = gpu(ids.cuda(), pixel_values=pixels.cuda().to(torch.bfloat16), token_type_ids=types.cuda(), labels=labels.cuda())
+    b.loss.backward()
+    F.check_kernel_status()
+    assert abs(a.loss.item() - b.loss.item()) / a.loss.item() < 0.05
+    g = gpu.vision_tower.patch_embedding.weight.grad
+    assert g is not None and torch.isfinite(g.float()).all() and g.abs().sum() > 0
