@@ -34,6 +34,7 @@ _LAZY = {
     "plan_parallelism": ".parallel.auto_plan",
     "PaliGemmaForConditionalGeneration": ".models.paligemma", "Gemma3ForConditionalGeneration": ".models.paligemma",
     "AutoModelForSpeechSeq2Seq": ".transformers.auto", "WhisperForConditionalGeneration": ".models.whisper",
+    "AutoModelForSequenceClassification": ".transformers.auto", "AutoModelForTokenClassification": ".transformers.auto",
     "AutoModel": ".transformers.auto", "SiglipVisionModel": ".models.siglip", "SiglipVisionConfig": ".models.siglip",
     "Qwen3VLForConditionalGeneration": ".models.vision_language", "Qwen3VLMoeForConditionalGeneration": ".models.vision_language",
     "Glm4vMoeForConditionalGeneration": ".models.vision_language", "FullyShardedOptimizer": ".parallel.fsdp",

@@ -111,6 +111,33 @@ class AutoModel:
         return model_cls.from_pretrained(path, config=cfg_cls.from_pretrained(path), dtype=dtype, device=device, **kw)
 
 
+class AutoModelForSequenceClassification:
+    """Any supported decoder family with one label (or score) per sequence."""
+
+    _kind = "DecoderForSequenceClassification"
+
+    @classmethod
+    def _cls(cls):
+        from ..models import classification
+
+        return getattr(classification, cls._kind)
+
+    @classmethod
+    def from_config(cls, config, dtype=None, device=None, **kw):
+        return cls._cls().from_config(config, dtype=dtype, device=device, **kw)
+
+    @classmethod
+    def from_pretrained(cls, path: str, config=None, dtype=None, device=None, num_labels: Optional[int] = None, **kw):
+        config = config or AutoConfig.from_pretrained(path)
+        if num_labels is not None:
+            config.num_labels = int(num_labels)
+        return cls._cls().from_pretrained(path, config=config, dtype=dtype, device=device, **kw)
+
+
+class AutoModelForTokenClassification(AutoModelForSequenceClassification):
+    _kind = "DecoderForTokenClassification"
+
+
 class AutoModelForSpeechSeq2Seq(AutoModel):
     """Encoder-decoder speech models."""
 

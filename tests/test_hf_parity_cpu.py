@@ -966,3 +966,46 @@ def test_paddleocr_vl_matches_hugging_face(tmp_path):
     with torch.no_grad():
         torch.testing.assert_close(back(input_ids=ids, pixel_values=pixels, image_grid_thw=grid, mm_token_type_ids=types).logits, want,
                                    rtol=1e-5, atol=1e-5)
+
+
+def test_classification_heads_match_hugging_face(tmp_path):
+    """Sequence classification (last non-padding token, bias-free score) and token classification (biased score) on the unified
+    decoder against transformers, checkpoint round trip, and a one-score reward head started from a causal-LM checkpoint."""
+    from paddleformers_b200.transformers.auto import AutoModelForSequenceClassification, AutoModelForTokenClassification
+
+    torch.manual_seed(0)
+    kw = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=16, pad_token_id=0)
+    ids = torch.randint(1, 128, (3, 10))
+    ids[0, 7:] = 0
+    ids[2, 4:] = 0
+    hf = transformers.Qwen3ForSequenceClassification(transformers.Qwen3Config(num_labels=3, **kw)).eval()
+    hf.save_pretrained(str(tmp_path / "seq"))
+    mine = AutoModelForSequenceClassification.from_pretrained(str(tmp_path / "seq"), dtype=torch.float32).eval()
+    labels = torch.tensor([0, 2, 1])
+    with torch.no_grad():
+        want, got = hf(input_ids=ids, labels=labels), mine(ids, labels=labels)
+    assert mine.num_labels == 3 and (want.logits - got.logits).abs().max() < 1e-5 and abs(want.loss.item() - got.loss.item()) < 1e-5
+    mine.save_pretrained(str(tmp_path / "seq_back"))
+    back = transformers.Qwen3ForSequenceClassification.from_pretrained(str(tmp_path / "seq_back")).eval()
+    with torch.no_grad():
+        assert (back(input_ids=ids).logits - want.logits).abs().max() < 1e-5
+
+    hf_tok = transformers.LlamaForTokenClassification(transformers.LlamaConfig(num_labels=5, **kw)).eval()
+    hf_tok.save_pretrained(str(tmp_path / "tok"))
+    tok = AutoModelForTokenClassification.from_pretrained(str(tmp_path / "tok"), dtype=torch.float32).eval()
+    tags = torch.randint(0, 5, (3, 10))
+    tags[0, 7:] = -100
+    with torch.no_grad():
+        want, got = hf_tok(input_ids=ids, labels=tags), tok(ids, labels=tags)
+    assert (want.logits - got.logits).abs().max() < 1e-5 and abs(want.loss.item() - got.loss.item()) < 1e-5
+
+    lm = transformers.LlamaForCausalLM(transformers.LlamaConfig(**kw)).eval()
+    lm.save_pretrained(str(tmp_path / "lm"))
+    reward = AutoModelForSequenceClassification.from_pretrained(str(tmp_path / "lm"), dtype=torch.float32, num_labels=1)
+    out = reward(ids, labels=torch.tensor([0.5, -1.0, 2.0]))
+    out.loss.backward()
+    assert out.logits.shape == (3, 1) and reward.score.weight.grad.abs().sum() > 0
+    with torch.no_grad():                            # the decoder really came from the causal-LM checkpoint
+        hidden = lm.model(input_ids=ids).last_hidden_state
+    assert (reward.hidden(ids) - hidden).abs().max() < 1e-4
