@@ -8,7 +8,12 @@
 #include "status.h"
 #include "tma_host.h"
 
+#include <cstdlib>
+#include <string>
+
 namespace pfb {
+
+static at::Tensor g_prof_buf;  // TEMP
 
 static CUtensorMap map3(const at::Tensor& t, int box_rows) {
   TORCH_CHECK(t.dim() == 3 && t.stride(2) == 1 && t.scalar_type() == at::kBFloat16 && t.size(2) == ATT_D);
@@ -21,7 +26,7 @@ static CUtensorMap map3(const at::Tensor& t, int box_rows) {
 void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& out,
               const at::Tensor& lse, at::Tensor& dq, at::Tensor& dk, at::Tensor& dv, int64_t B, int64_t S, double scale,
               bool causal, const c10::optional<at::Tensor>& kend, const c10::optional<at::Tensor>& tile_min,
-              const c10::optional<at::Tensor>& tile_max) {
+              const c10::optional<at::Tensor>& tile_max, bool deterministic, int64_t heads_per_cta_override) {
   TORCH_CHECK(q.is_cuda() && q.size(-1) == ATT_D, "attn_bwd: head_dim 128");
   const c10::cuda::CUDAGuard guard(q.device());
   const int Hq = q.size(-2), Hkv = k.size(-2);
@@ -33,6 +38,7 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
   TORCH_CHECK(dq3.stride(2) == 1 && dq3.stride(1) == ATT_D && dk3.stride(1) == ATT_D && dv3.stride(1) == ATT_D);
   TORCH_CHECK(lse.is_contiguous() && lse.scalar_type() == at::kFloat);
   if (T == 0) return;
+  bool group_mode = false;
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   at::Tensor delta = at::empty({B, Hq, S}, lse.options());
   at::Tensor dq_acc = at::zeros({T, Hq, ATT_D}, lse.options());
@@ -49,7 +55,16 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
   p.dk_row_stride = dk3.stride(0); p.dv_row_stride = dv3.stride(0);
   at::Tensor dk_part, dv_part;
   p.dk_part = nullptr; p.dv_part = nullptr;
-  if (Hq != Hkv) {
+  static const bool use_v1 = [] { const char* e = std::getenv("PFB_ATTN_BWD"); return e != nullptr && std::string(e) == "v1"; }();
+  // one CTA per (key tile, KV head), walking the group's query heads, when that still fills the GPU about twice over;
+  // otherwise one CTA per query head with fp32 dK / dV partials that a second kernel sums
+  const int G = Hq / Hkv;
+  const long long group_ctas = ((S + ATTB_BKV - 1) / ATTB_BKV) * static_cast<long long>(Hkv) * B;
+  int heads_per_cta = (G > 1 && group_ctas >= 2LL * at::cuda::getCurrentDeviceProperties()->multiProcessorCount) ? G : 1;
+  if (heads_per_cta_override > 0) heads_per_cta = heads_per_cta_override == 1 ? 1 : G;
+  if (use_v1) heads_per_cta = 1;
+  group_mode = heads_per_cta != 1;
+  if (Hq != Hkv && !group_mode) {
     dk_part = at::empty({T, Hq, ATT_D}, lse.options());
     dv_part = at::empty({T, Hq, ATT_D}, lse.options());
     p.dk_part = dk_part.data_ptr<float>(); p.dv_part = dv_part.data_ptr<float>();
@@ -66,25 +81,61 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
   p.causal = causal ? 1 : 0;
   p.status = status_word();
   CUtensorMap tmQ = map3(q3, ATTB_BQ), tmK = map3(k3, ATTB_BKV), tmV = map3(v3, ATTB_BKV), tmdO = map3(do3, ATTB_BQ);
-  static bool cfg = false;
-  if (!cfg) {
-    C10_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem::TOTAL));
-    cfg = true;
+  if (use_v1) {
+    static bool cfg = false;
+    if (!cfg) {
+      C10_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem::TOTAL));
+      cfg = true;
+    }
+    dim3 grid(kv_tiles, Hq, B);
+    attn_bwd_kernel<<<grid, ATTB_THREADS, AttnBwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmdO, p);
+  } else {
+    AttnBwd2Params pp;
+    pp.base = p;
+    pp.deterministic = deterministic ? 1 : 0;
+    pp.dq_turn = nullptr;
+    { const char* e = std::getenv("PFB_DEBUG_BWD"); pp.debug_flags = e ? atoi(e) : 0; }
+    pp.prof = nullptr;
+    if (std::getenv("PFB_PROF_BWD")) {
+      if (!g_prof_buf.defined()) g_prof_buf = at::zeros({32}, lse.options().dtype(at::kLong));
+      pp.prof = reinterpret_cast<long long*>(g_prof_buf.data_ptr<int64_t>());
+    }
+    at::Tensor turns;
+    if (deterministic) {
+      turns = at::zeros({B, Hq, (S + ATTB_BQ - 1) / ATTB_BQ}, lse.options().dtype(at::kInt));
+      pp.dq_turn = turns.data_ptr<int>();
+    }
+    pp.heads_per_cta = heads_per_cta;
+    CUtensorMap tmdQ = make_tma_3d(dq_acc.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, T, Hq, ATT_D,
+                                   static_cast<uint64_t>(Hq) * ATT_D, ATT_D, 32, 1, ATT_D, CU_TENSOR_MAP_SWIZZLE_NONE);
+    static bool cfg = false;
+    if (!cfg) {
+      C10_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwd2Smem::TOTAL));
+      cfg = true;
+    }
+    dim3 grid(kv_tiles, pp.heads_per_cta == 1 ? Hq : Hkv, B);
+    attn_bwd2_kernel<<<grid, AB2_THREADS, AttnBwd2Smem::TOTAL, stream>>>(tmQ, tmK, tmV, tmdO, tmdQ, pp);
   }
-  dim3 grid(kv_tiles, Hq, B);
-  attn_bwd_kernel<<<grid, ATTB_THREADS, AttnBwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmdO, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
+  if (std::getenv("PFB_PROF_BWD") && !use_v1) {
+    cudaStreamSynchronize(stream);
+    at::Tensor h = g_prof_buf.cpu();
+    const int64_t* v = h.data_ptr<int64_t>();
+    printf("bwd2 prof CTA0: n_it %lld total %lld | mma waits: q_full %lld dq_read %lld bar_p %lld bar_ds %lld | compute: total %lld wait_s %lld wait_dp %lld | dq: total %lld wait_dq %lld\n",
+           (long long)v[5], (long long)v[4], (long long)v[0], (long long)v[1], (long long)v[2], (long long)v[3], (long long)v[10], (long long)v[8], (long long)v[9], (long long)v[13], (long long)v[12]);
+    printf("   compute segments: ldS %lld exp %lld stP %lld lddP %lld dS %lld st_dS %lld\n", (long long)v[16], (long long)v[17], (long long)v[18], (long long)v[19], (long long)v[20], (long long)v[21]);
+  }
   {
     const long long work = T * (Hq * ATT_D / 4);
-    const int blocks = static_cast<int>(std::min<long long>((work + 255) / 256, 148LL * 16));
+    const int blocks = static_cast<int>(std::min<long long>((work + 255) / 256, static_cast<long long>(at::cuda::getCurrentDeviceProperties()->multiProcessorCount) * 16));
     attn_bwd_dq_convert_kernel<<<blocks, 256, 0, stream>>>(dq_acc.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(dq3.data_ptr()),
                                                           T, Hq * ATT_D, dq3.stride(0));
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   }
   int launches = 3;
-  if (Hq != Hkv) {
+  if (Hq != Hkv && !group_mode) {
     const long long work = T * (Hkv * ATT_D / 4);
-    const int blocks = static_cast<int>(std::min<long long>((work + 255) / 256, 148LL * 16));
+    const int blocks = static_cast<int>(std::min<long long>((work + 255) / 256, static_cast<long long>(at::cuda::getCurrentDeviceProperties()->multiProcessorCount) * 16));
     attn_bwd_dkv_reduce_kernel<<<blocks, 256, 0, stream>>>(dk_part.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(dk3.data_ptr()),
                                                           T, Hq, Hkv, dk3.stride(0));
     attn_bwd_dkv_reduce_kernel<<<blocks, 256, 0, stream>>>(dv_part.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(dv3.data_ptr()),
@@ -99,6 +150,7 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
 
 TORCH_LIBRARY_FRAGMENT(pfb200, m) {
   m.def("attn_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor out, Tensor lse, Tensor(a!) dq, Tensor(b!) dk, "
-        "Tensor(c!) dv, int B, int S, float scale, bool causal, Tensor? kend, Tensor? tile_min, Tensor? tile_max) -> ()",
+        "Tensor(c!) dv, int B, int S, float scale, bool causal, Tensor? kend, Tensor? tile_min, Tensor? tile_max, "
+        "bool deterministic=False, int heads_per_cta=0) -> ()",
         &pfb::attn_bwd);
 }

@@ -20,6 +20,8 @@
 
 namespace pfb {
 
+__device__ __forceinline__ void fence_proxy_async_all_bwd() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 constexpr int ATTB_BKV = 128;
 constexpr int ATTB_BQ = 64;
 constexpr int ATTB_THREADS = 160;
@@ -318,6 +320,499 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   if (warp == 4) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Pipelined backward (the default). Same mathematics and operand layouts as attn_bwd_kernel above, but the work of a
+// query tile is spread over four roles that run concurrently on two tiles:
+//
+//   warp 8     TMA loader: K, V once; Q / dO tiles through a three-stage ring
+//   warp 9     MMA issuer: S^T and dP^T of tile i+1 are issued BEFORE it waits for P(i) / dS(i), so the tensor pipe works
+//              on tile i+1's products and tile i-1's dV / dK / dQ while the compute warps handle tile i
+//   warps 0-3  compute: P^T = exp2(S^T - lse), dS^T = P^T (dP^T - delta) scale; both are written back to TMEM as bf16
+//              (A operands of the dV / dK products) and dS^T also to swizzled shared memory (B operand of dQ^T)
+//   warps 4-7  dQ: read dQ^T from TMEM, transpose through shared memory, and add it to the fp32 accumulator with one
+//              TMA reduce-add per 32 query rows (instead of per-element atomics). With `deterministic` the adds of one
+//              query tile happen in a fixed order (descending key tile): every CTA takes its turn on a per-tile counter.
+//
+// TMEM (512 columns): two stages of [S^T 64 | dP^T 64], dV 128, dK 128. Within a stage P^T (bf16) overwrites columns
+// 0-31 and dS^T (bf16) columns 96-127; the 64 columns in between are dead by then and receive dQ^T, so no separate
+// dQ accumulator is needed. With `heads_per_cta` = G the CTA walks all query heads of its KV head and dK / dV accumulate
+// over them in TMEM (no fp32 partials); with 1 it owns one query head (keeps the grid large when a rank has few KV heads).
+#define PFB_PROF_WAIT(slot, expr) do { long long _t0 = clock64(); bool _r = (expr); _prof[slot] += clock64() - _t0; if (!_r) { _fail = true; } } while (0)
+constexpr int AB2_THREADS = 320;
+constexpr int AB2_QSTAGES = 3;
+
+struct AttnBwd2Params {
+  AttnBwdParams base;
+  int heads_per_cta;     // Hq / Hkv, or 1
+  int deterministic;     // 1: ordered dQ accumulation
+  int* dq_turn;          // [B, Hq, q_tiles] zero-initialised counters (deterministic mode)
+  int debug_flags;       // TEMP: 1 = skip the dQ reduce-add, 2 = skip staging too
+  long long* prof;       // TEMP: per-role wait cycles of CTA (0,0,0)
+};
+
+struct AttnBwd2Smem {
+  static constexpr int KV_TILE = ATTB_BKV * ATT_D * 2;   // 32 KB
+  static constexpr int Q_TILE = ATTB_BQ * ATT_D * 2;     // 16 KB
+  static constexpr int K_OFF = 0, V_OFF = KV_TILE;
+  static constexpr int Q_OFF = 2 * KV_TILE;                               // QSTAGES x (Q, dO)
+  static constexpr int DS_OFF = Q_OFF + AB2_QSTAGES * 2 * Q_TILE;         // 2 x dS^T [128 keys x 64 q] bf16
+  static constexpr int DQ_OFF = DS_OFF + 2 * ATTB_BKV * ATTB_BQ * 2;      // fp32 [32 q x 128 d] staging for the reduce-add
+  static constexpr int STAT_OFF = DQ_OFF + 32 * ATT_D * 4;                // per compute warp: lse[64], delta[64]
+  static constexpr int BAR_OFF = STAT_OFF + 4 * 2 * 64 * 4;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__global__ void __launch_bounds__(AB2_THREADS, 1)
+attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                 const __grid_constant__ CUtensorMap tmdQ, const AttnBwd2Params pp) {
+  using SM = AttnBwd2Smem;
+  const AttnBwdParams& p = pp.base;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + SM::K_OFF; uint8_t* sV = smem + SM::V_OFF;
+  float* sDQ = reinterpret_cast<float*>(smem + SM::DQ_OFF);
+  float* s_stat_all = reinterpret_cast<float*>(smem + SM::STAT_OFF);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
+  uint64_t* bar_kv = bars;                 // 1
+  uint64_t* q_full = bars + 1;             // [3]
+  uint64_t* q_empty = bars + 4;            // [3]
+  uint64_t* bar_s = bars + 7;              // [2]
+  uint64_t* bar_dp = bars + 9;             // [2]
+  uint64_t* bar_p = bars + 11;             // [2]
+  uint64_t* bar_ds = bars + 13;            // [2]
+  uint64_t* bar_dq = bars + 15;            // [2]
+  uint64_t* dq_read = bars + 17;           // [2]
+  uint64_t* bar_done = bars + 19;          // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_tiles = (p.S + ATTB_BKV - 1) / ATTB_BKV;
+  // deterministic mode: a CTA waits for the CTA of the next key tile, which must therefore have the lower block index;
+  // otherwise the heavy (early) key tiles of a causal mask start first
+  const int jt = pp.deterministic ? kv_tiles - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
+  const int b = blockIdx.z;
+  const int G = p.Hq / p.Hkv;
+  const int HPC = pp.heads_per_cta;
+  const int head0 = HPC == 1 ? static_cast<int>(blockIdx.y) : static_cast<int>(blockIdx.y) * G;
+  const int kvh = head0 / G;
+  const int k0 = jt * ATTB_BKV;
+  const int row_base = b * p.S;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_kv, 1);
+    for (int s = 0; s < AB2_QSTAGES; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar_s[s], 1); mbar_init(&bar_dp[s], 1); mbar_init(&bar_p[s], 4); mbar_init(&bar_ds[s], 4);
+      mbar_init(&bar_dq[s], 1); mbar_init(&dq_read[s], 4);
+    }
+    mbar_init(bar_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); tc_fence_before(); }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tdV = tmem_base + 256, tdK = tmem_base + 384;
+
+  // query tile range visible to this key tile
+  const int q_tiles = (p.S + ATTB_BQ - 1) / ATTB_BQ;
+  const int i_lo = p.causal ? k0 / ATTB_BQ : 0;
+  int i_hi = q_tiles - 1;
+  int tmin_end = 0x7fffffff;
+  if (p.kend) {
+    const int tmax = p.tile_max_end[b * kv_tiles + jt];
+    tmin_end = p.tile_min_end[b * kv_tiles + jt];
+    i_hi = min(i_hi, (tmax - 1) / ATTB_BQ);
+  }
+  const int n_q = max(i_hi - i_lo + 1, 0);
+  const int n_it = n_q * HPC;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------ TMA loader
+    if (lane == 0 && n_it > 0) {
+      mbar_expect_tx(bar_kv, 2 * SM::KV_TILE);
+      tma_load_3d(sK, &tmK, bar_kv, 0, kvh, row_base + k0);
+      tma_load_3d(sK + SM::KV_TILE / 2, &tmK, bar_kv, 64, kvh, row_base + k0);
+      tma_load_3d(sV, &tmV, bar_kv, 0, kvh, row_base + k0);
+      tma_load_3d(sV + SM::KV_TILE / 2, &tmV, bar_kv, 64, kvh, row_base + k0);
+      int st = 0; uint32_t ph = 0;
+      for (int it = 0; it < n_it; ++it) {
+        const int g = it / n_q, i = i_lo + (it - g * n_q);
+        if (!mbar_wait(&q_empty[st], ph ^ 1, abort_flag, p.status, PFB_ERR_WAIT_EMPTY)) break;
+        uint8_t* sq = smem + SM::Q_OFF + st * 2 * SM::Q_TILE;
+        uint8_t* sdo = sq + SM::Q_TILE;
+        mbar_expect_tx(&q_full[st], 2 * SM::Q_TILE);
+        tma_load_3d(sq, &tmQ, &q_full[st], 0, head0 + g, row_base + i * ATTB_BQ);
+        tma_load_3d(sq + SM::Q_TILE / 2, &tmQ, &q_full[st], 64, head0 + g, row_base + i * ATTB_BQ);
+        tma_load_3d(sdo, &tmdO, &q_full[st], 0, head0 + g, row_base + i * ATTB_BQ);
+        tma_load_3d(sdo + SM::Q_TILE / 2, &tmdO, &q_full[st], 64, head0 + g, row_base + i * ATTB_BQ);
+        if (++st == AB2_QSTAGES) { st = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idesc_s = make_idesc(128, ATTB_BQ, false, false, 1);   // K-major x K-major
+      constexpr uint32_t idesc_dkv = make_idesc(128, ATT_D, false, true, 1);     // TMEM A x MN-major B
+      constexpr uint32_t idesc_dq = make_idesc(128, ATTB_BQ, true, true, 1);     // MN-major x MN-major
+      bool ok = mbar_wait(bar_kv, 0, abort_flag, p.status, PFB_ERR_WAIT_FULL);
+      long long _prof[8] = {0, 0, 0, 0, 0, 0, 0, 0}; bool _fail = false; const long long _tstart = clock64();
+      auto issue_s_dp = [&](int it) -> bool {
+        const int qs = it % AB2_QSTAGES, st = it & 1;
+        PFB_PROF_WAIT(0, mbar_wait(&q_full[qs], (it / AB2_QSTAGES) & 1, abort_flag, p.status, PFB_ERR_WAIT_FULL));
+        if (_fail) return false;
+        tc_fence_after();
+        const uint32_t sq = smem_u32(smem + SM::Q_OFF + qs * 2 * SM::Q_TILE);
+        const uint32_t sdo = sq + SM::Q_TILE;
+        const uint32_t tS = tmem_base + st * 128, tdP = tS + 64;
+        if (pp.debug_flags & 32) {
+          #pragma unroll
+          for (int k = 0; k < ATT_D / 16; ++k) {
+            const uint32_t offk = (k >> 2) * (SM::KV_TILE / 2) + (k & 3) * 32;
+            const uint32_t offq = (k >> 2) * (SM::Q_TILE / 2) + (k & 3) * 32;
+            tc_mma_f16_ss(tS, make_smem_desc_sw128(smem_u32(sK) + offk, 16, 1024), make_smem_desc_sw128(sq + offq, 16, 1024),
+                          idesc_s, k != 0);
+            tc_mma_f16_ss(tdP, make_smem_desc_sw128(smem_u32(sV) + offk, 16, 1024), make_smem_desc_sw128(sdo + offq, 16, 1024),
+                          idesc_s, k != 0);
+          }
+          tc_commit(&bar_s[st]);
+        } else {
+          #pragma unroll
+          for (int k = 0; k < ATT_D / 16; ++k) {
+            const uint32_t offk = (k >> 2) * (SM::KV_TILE / 2) + (k & 3) * 32;
+            const uint32_t offq = (k >> 2) * (SM::Q_TILE / 2) + (k & 3) * 32;
+            tc_mma_f16_ss(tS, make_smem_desc_sw128(smem_u32(sK) + offk, 16, 1024), make_smem_desc_sw128(sq + offq, 16, 1024),
+                          idesc_s, k != 0);
+          }
+          tc_commit(&bar_s[st]);
+          #pragma unroll
+          for (int k = 0; k < ATT_D / 16; ++k) {
+            const uint32_t offk = (k >> 2) * (SM::KV_TILE / 2) + (k & 3) * 32;
+            const uint32_t offq = (k >> 2) * (SM::Q_TILE / 2) + (k & 3) * 32;
+            tc_mma_f16_ss(tdP, make_smem_desc_sw128(smem_u32(sV) + offk, 16, 1024), make_smem_desc_sw128(sdo + offq, 16, 1024),
+                          idesc_s, k != 0);
+          }
+        }
+        tc_commit(&bar_dp[st]);
+        return true;
+      };
+      if (ok) ok = issue_s_dp(0);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it & 1, qs = it % AB2_QSTAGES;
+        const uint32_t ph2 = (it >> 1) & 1;
+        const uint32_t stage = tmem_base + st * 128;
+        const uint32_t sq = smem_u32(smem + SM::Q_OFF + qs * 2 * SM::Q_TILE);
+        const uint32_t sdo = sq + SM::Q_TILE;
+        if (it + 1 < n_it && !(pp.debug_flags & 16)) {
+          // the other stage still holds dQ^T of tile it-1 until the dQ warps have read it
+          if (it >= 1) { PFB_PROF_WAIT(1, mbar_wait(&dq_read[st ^ 1], ((it - 1) >> 1) & 1, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)); if (_fail) break; }
+          tc_fence_after();
+          if (!issue_s_dp(it + 1)) break;
+        }
+        PFB_PROF_WAIT(2, mbar_wait(&bar_p[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)); if (_fail) break;
+        tc_fence_after();
+        #pragma unroll
+        for (int k = 0; k < ATTB_BQ / 16; ++k)
+          tc_mma_f16_ts(tdV, stage + k * 8, make_smem_desc_sw128(sdo + k * 16 * 128, SM::Q_TILE / 2, 1024), idesc_dkv,
+                        (it | k) != 0);
+        PFB_PROF_WAIT(3, mbar_wait(&bar_ds[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)); if (_fail) break;
+        tc_fence_after();
+        #pragma unroll
+        for (int k = 0; k < ATTB_BQ / 16; ++k)
+          tc_mma_f16_ts(tdK, stage + 96 + k * 8, make_smem_desc_sw128(sq + k * 16 * 128, SM::Q_TILE / 2, 1024), idesc_dkv,
+                        (it | k) != 0);
+        tc_commit(&q_empty[qs]);   // Q / dO of this tile are no longer read once everything issued so far has run
+        const uint32_t sds = smem_u32(smem + SM::DS_OFF + st * (ATTB_BKV * ATTB_BQ * 2));
+        #pragma unroll
+        for (int k = 0; k < ATTB_BKV / 16; ++k)
+          tc_mma_f16_ss(stage + 32, make_smem_desc_sw128(smem_u32(sK) + k * 16 * 128, SM::KV_TILE / 2, 1024),
+                        make_smem_desc_sw128(sds + k * 16 * 128, 16, 1024), idesc_dq, k != 0);
+        tc_commit(&bar_dq[st]);
+        if (it + 1 < n_it && (pp.debug_flags & 16)) {
+          if (it >= 1) { PFB_PROF_WAIT(1, mbar_wait(&dq_read[st ^ 1], ((it - 1) >> 1) & 1, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)); if (_fail) break; }
+          tc_fence_after();
+          if (!issue_s_dp(it + 1)) break;
+        }
+      }
+      tc_commit(bar_done);
+      if (pp.prof && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        for (int i = 0; i < 4; ++i) pp.prof[i] = _prof[i];
+        pp.prof[4] = clock64() - _tstart; pp.prof[5] = n_it;
+      }
+    }
+  } else if (warp < 4) {
+    // ------------------------------------------------------------ compute warps: thread r owns key row k0 + r
+    const int r = threadIdx.x;
+    const int kj = k0 + r;
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    float* s_lse = s_stat_all + warp * 128;
+    float* s_delta = s_lse + 64;
+    const int my_kend = (p.kend && kj < p.S) ? p.kend[b * p.S + kj] : 0x7fffffff;
+    bool ok = true;
+    // statistics of the first tile; those of tile it+1 are fetched while tile it is being processed
+    float nl[2], nd[2];
+    auto fetch_stats = [&](int it) {
+      const int g = it / n_q, i = i_lo + (it - g * n_q);
+      const long long base = (static_cast<long long>(b) * p.Hq + head0 + g) * p.S;
+      #pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int qi = i * ATTB_BQ + lane + 32 * c;
+        nl[c] = qi < p.S ? p.lse[base + qi] * 1.4426950408889634f : 0.f;
+        nd[c] = qi < p.S ? p.delta[base + qi] : 0.f;
+      }
+    };
+    if (n_it > 0) fetch_stats(0);
+    long long _prof[8] = {0, 0, 0, 0, 0, 0, 0, 0}; bool _fail = false; const long long _tstart = clock64();
+    for (int it = 0; it < n_it; ++it) {
+      const int st = it & 1;
+      const uint32_t ph2 = (it >> 1) & 1;
+      const int g = it / n_q, i = i_lo + (it - g * n_q);
+      const int q0 = i * ATTB_BQ;
+      const uint32_t tS = tmem_base + st * 128 + lane_off, tdP = tS + 64;
+      __syncwarp();
+      s_lse[lane] = nl[0]; s_lse[lane + 32] = nl[1];
+      s_delta[lane] = nd[0]; s_delta[lane + 32] = nd[1];
+      __syncwarp();
+      if (it + 1 < n_it) fetch_stats(it + 1);
+      const bool need_mask = (p.causal && q0 < k0 + ATTB_BKV) || (q0 + ATTB_BQ > p.S) || (k0 + ATTB_BKV > p.S) ||
+                             (q0 + ATTB_BQ > tmin_end);
+      // the 64 row statistics go to registers with a few vector loads BEFORE the wait: while the tensor pipe streams
+      // its operands out of shared memory, every further shared-memory read of this warp would queue behind them
+      if (pp.debug_flags & 64) {   // TEMP: no compute at all, only the barrier hand-shakes
+        PFB_PROF_WAIT(0, mbar_wait(&bar_s[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)); if (_fail) { ok = false; break; }
+        tc_fence_after(); tc_fence_before(); __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_p[st]);
+        PFB_PROF_WAIT(1, mbar_wait(&bar_dp[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)); if (_fail) { ok = false; break; }
+        tc_fence_after(); tc_fence_before(); __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_ds[st]);
+        continue;
+      }
+      float ls[ATTB_BQ];
+      #pragma unroll
+      for (int x = 0; x < ATTB_BQ; x += 4) {
+        const float4 t4 = *reinterpret_cast<const float4*>(s_lse + x);
+        ls[x] = t4.x; ls[x + 1] = t4.y; ls[x + 2] = t4.z; ls[x + 3] = t4.w;
+      }
+      PFB_PROF_WAIT(0, mbar_wait(&bar_s[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)); if (_fail) { ok = false; break; }
+      tc_fence_after();
+      float pv[ATTB_BQ];
+      long long _ta = clock64();
+      #pragma unroll
+      for (int c = 0; c < ATTB_BQ; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tS + c, v);
+        tmem_ld_wait();
+        asm volatile("" :: "r"(v[0]), "r"(v[15]), "r"(v[31]) : "memory");
+        { long long _tb = clock64(); _prof[2] += _tb - _ta; _ta = _tb; }
+        #pragma unroll
+        for (int x = 0; x < 32; x += 2) {
+          float p0, p1;
+          if (pp.debug_flags & 4) {
+            p0 = __uint_as_float(v[x]) * p.scale_log2 - ls[c + x];
+            p1 = __uint_as_float(v[x + 1]) * p.scale_log2 - ls[c + x + 1];
+          } else {
+            p0 = fast_exp2(__uint_as_float(v[x]) * p.scale_log2 - ls[c + x]);
+            p1 = fast_exp2(__uint_as_float(v[x + 1]) * p.scale_log2 - ls[c + x + 1]);
+          }
+          if (need_mask && !(pp.debug_flags & 8)) {
+            const int qi = q0 + c + x;
+            const bool v0 = qi < p.S && kj < p.S && (!p.causal || kj <= qi) && qi < my_kend;
+            const bool v1 = qi + 1 < p.S && kj < p.S && (!p.causal || kj <= qi + 1) && qi + 1 < my_kend;
+            p0 = v0 ? p0 : 0.f; p1 = v1 ? p1 : 0.f;
+          }
+          pv[c + x] = p0; pv[c + x + 1] = p1;
+        }
+        { long long _tb = clock64(); _prof[3] += _tb - _ta; _ta = _tb; }
+      }
+      // all 64 raw scores of this lane have been read: P^T (bf16) may overwrite columns 0-31
+      #pragma unroll
+      for (int c = 0; c < ATTB_BQ; c += 32) {
+        uint32_t pk[16];
+        #pragma unroll
+        for (int x = 0; x < 32; x += 2) pk[x >> 1] = pack_bf16x2(pv[c + x], pv[c + x + 1]);
+        tmem_st_32x16(tS + (c >> 1), pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_p[st]);
+      { long long _tb = clock64(); _prof[4] += _tb - _ta; _ta = _tb; }
+      // dS^T = P^T * (dP^T - delta) * scale
+      #pragma unroll
+      for (int x = 0; x < ATTB_BQ; x += 4) {
+        const float4 t4 = *reinterpret_cast<const float4*>(s_delta + x);
+        ls[x] = t4.x; ls[x + 1] = t4.y; ls[x + 2] = t4.z; ls[x + 3] = t4.w;
+      }
+      PFB_PROF_WAIT(1, mbar_wait(&bar_dp[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)); if (_fail) { ok = false; break; }
+      tc_fence_after();
+      uint32_t dsk[ATTB_BQ / 2];
+      _ta = clock64();
+      #pragma unroll
+      for (int c = 0; c < ATTB_BQ; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tdP + c, v);
+        tmem_ld_wait();
+        asm volatile("" :: "r"(v[0]), "r"(v[15]), "r"(v[31]) : "memory");
+        { long long _tb = clock64(); _prof[5] += _tb - _ta; _ta = _tb; }
+        #pragma unroll
+        for (int x = 0; x < 32; x += 2) {
+          const float d0 = pv[c + x] * (__uint_as_float(v[x]) - ls[c + x]) * p.scale;
+          const float d1 = pv[c + x + 1] * (__uint_as_float(v[x + 1]) - ls[c + x + 1]) * p.scale;
+          dsk[(c + x) >> 1] = pack_bf16x2(d0, d1);
+        }
+        { long long _tb = clock64(); _prof[6] += _tb - _ta; _ta = _tb; }
+      }
+      uint8_t* rowp = smem + SM::DS_OFF + st * (ATTB_BKV * ATTB_BQ * 2) + r * 128;
+      #pragma unroll
+      for (int c = 0; c < ATTB_BQ; c += 32) {
+        uint32_t pk[16];
+        #pragma unroll
+        for (int x = 0; x < 16; ++x) pk[x] = dsk[(c >> 1) + x];
+        tmem_st_32x16(tS + 96 + (c >> 1), pk);
+        #pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = (c >> 3) + q4;
+          *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+        }
+      }
+      tmem_st_wait();
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_ds[st]);
+      { long long _tb = clock64(); _prof[7] += _tb - _ta; _ta = _tb; }
+    }
+    if (pp.prof && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+      pp.prof[8] = _prof[0]; pp.prof[9] = _prof[1]; pp.prof[10] = clock64() - _tstart; for (int i = 2; i < 8; ++i) pp.prof[14 + i] = _prof[i];
+    }
+    // dK, dV: one key row per thread
+    if (ok && n_it > 0) ok = mbar_wait(bar_done, 0, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL);
+    if (ok) {
+      if (n_it > 0) tc_fence_after();
+      const bool partial = p.dk_part != nullptr && HPC == 1;
+      __nv_bfloat16* dkp = p.dk + static_cast<long long>(row_base + kj) * p.dk_row_stride + kvh * ATT_D;
+      __nv_bfloat16* dvp = p.dv + static_cast<long long>(row_base + kj) * p.dv_row_stride + kvh * ATT_D;
+      #pragma unroll 1
+      for (int c = 0; c < ATT_D; c += 32) {
+        uint32_t a[32], bb[32];
+        if (n_it > 0) {
+          tmem_ld_32x32(tdK + lane_off + c, a);
+          tmem_ld_32x32(tdV + lane_off + c, bb);
+          tmem_ld_wait();
+        } else {
+          #pragma unroll
+          for (int x = 0; x < 32; ++x) { a[x] = 0u; bb[x] = 0u; }
+        }
+        if (kj < p.S && partial) {
+          float* pk = p.dk_part + (static_cast<long long>(row_base + kj) * p.Hq + head0) * ATT_D + c;
+          float* pv2 = p.dv_part + (static_cast<long long>(row_base + kj) * p.Hq + head0) * ATT_D + c;
+          #pragma unroll
+          for (int x = 0; x < 32; x += 4) {
+            *reinterpret_cast<float4*>(pk + x) = make_float4(__uint_as_float(a[x]), __uint_as_float(a[x + 1]), __uint_as_float(a[x + 2]), __uint_as_float(a[x + 3]));
+            *reinterpret_cast<float4*>(pv2 + x) = make_float4(__uint_as_float(bb[x]), __uint_as_float(bb[x + 1]), __uint_as_float(bb[x + 2]), __uint_as_float(bb[x + 3]));
+          }
+        } else if (kj < p.S) {
+          #pragma unroll
+          for (int x = 0; x < 32; x += 8) {
+            *reinterpret_cast<uint4*>(dkp + c + x) = make_uint4(
+                pack_bf16x2(__uint_as_float(a[x]), __uint_as_float(a[x + 1])), pack_bf16x2(__uint_as_float(a[x + 2]), __uint_as_float(a[x + 3])),
+                pack_bf16x2(__uint_as_float(a[x + 4]), __uint_as_float(a[x + 5])), pack_bf16x2(__uint_as_float(a[x + 6]), __uint_as_float(a[x + 7])));
+            *reinterpret_cast<uint4*>(dvp + c + x) = make_uint4(
+                pack_bf16x2(__uint_as_float(bb[x]), __uint_as_float(bb[x + 1])), pack_bf16x2(__uint_as_float(bb[x + 2]), __uint_as_float(bb[x + 3])),
+                pack_bf16x2(__uint_as_float(bb[x + 4]), __uint_as_float(bb[x + 5])), pack_bf16x2(__uint_as_float(bb[x + 6]), __uint_as_float(bb[x + 7])));
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ dQ warps (4-7): thread d owns head dim d of dQ^T
+    const int d = threadIdx.x - 128;
+    const uint32_t lane_off = static_cast<uint32_t>((warp - 4) * 32) << 16;
+    const bool leader = d == 0;
+    bool ok = true;
+    long long _prof[8] = {0, 0, 0, 0, 0, 0, 0, 0}; bool _fail = false; const long long _tstart = clock64();
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int st = it & 1;
+      const uint32_t ph2 = (it >> 1) & 1;
+      const int g = it / n_q, i = i_lo + (it - g * n_q);
+      const int q0 = i * ATTB_BQ;
+      PFB_PROF_WAIT(0, mbar_wait(&bar_dq[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)); if (_fail) break;
+      tc_fence_after();
+      uint32_t dq0[32], dq1[32];
+      tmem_ld_32x32(tmem_base + st * 128 + 32 + lane_off, dq0);
+      tmem_ld_32x32(tmem_base + st * 128 + 64 + lane_off, dq1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&dq_read[st]);
+      int my_turn = 0;
+      if (pp.deterministic && warp == 4) {
+        // contributors of this query tile are taken in descending key-tile order: count those above this CTA's tile
+        const int j_top = p.causal ? min(kv_tiles - 1, (q0 + ATTB_BQ - 1) / ATTB_BKV) : kv_tiles - 1;
+        int cnt = 0;
+        for (int j2 = jt + 1 + lane; j2 <= j_top; j2 += 32)
+          cnt += (p.kend == nullptr || p.tile_max_end[b * kv_tiles + j2] > q0) ? 1 : 0;
+        #pragma unroll
+        for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+        my_turn = cnt;
+      }
+      #pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        // the previous reduce-add has finished reading the staging tile
+        if (leader) tma_store_wait_read<0>();
+        named_bar_sync(1, 128);
+        const uint32_t* src = half == 0 ? dq0 : dq1;
+        if (!(pp.debug_flags & 2)) {
+        #pragma unroll
+        for (int x = 0; x < 32; ++x) sDQ[x * ATT_D + d] = __uint_as_float(src[x]);
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1, 128);
+        if (leader) {
+          int* turn = pp.dq_turn + (static_cast<long long>(b) * p.Hq + head0 + g) * q_tiles + i;
+          if (pp.deterministic && half == 0) {
+            const long long t0 = global_ns(), budget = wait_budget_ns(p.status);
+            while (*reinterpret_cast<volatile int*>(turn) < my_turn) {
+              if (*abort_flag) { ok = false; break; }
+              if (global_ns() - t0 > budget) { *abort_flag = 1; atomicCAS(p.status, 0, PFB_ERR_WAIT_PEER); ok = false; break; }
+            }
+            __threadfence();
+          }
+          if (ok && !(pp.debug_flags & 1)) {
+            tma_reduce_add_3d(&tmdQ, sDQ, 0, head0 + g, row_base + q0 + half * 32);
+            tma_store_commit();
+            if (pp.deterministic && half == 1) {
+              tma_store_wait<0>();          // both halves are in memory: pass the turn on
+              fence_proxy_async_all_bwd();
+              __threadfence();
+              atomicExch(turn, my_turn + 1);
+            }
+          }
+        }
+      }
+      ok = ok && !*abort_flag;
+    }
+    if (leader) tma_store_wait<0>();
+    if (pp.prof && leader && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { pp.prof[12] = _prof[0]; pp.prof[13] = clock64() - _tstart; }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 // delta[b, h, s] = sum_d dO * O ; one warp per (token, head).

@@ -7,6 +7,9 @@
 #include "status.h"
 #include "tma_host.h"
 
+#include <cstdlib>
+#include <string>
+
 namespace pfb {
 
 static CUtensorMap qkv_map(const at::Tensor& t, int box_rows) {
@@ -49,21 +52,20 @@ at::Tensor attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& 
   p.causal = causal ? 1 : 0;
   p.status = status_word();
   CUtensorMap tmQ = qkv_map(q, ATT_BQ), tmK = qkv_map(k, ATT_BKV), tmV = qkv_map(v, ATT_BKV);
-  dim3 grid((S + ATT_BQ - 1) / ATT_BQ, Hq, B);
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
-  if (p_in_tmem) {
-    auto kern = attn_fwd_kernel<true>;
-    constexpr int smem = AttnFwdSmem<true>::TOTAL;
+  static const bool use_v1 = [] { const char* e = std::getenv("PFB_ATTN_FWD"); return e != nullptr && std::string(e) == "v1"; }();
+  if (!use_v1) {
+    // two query tiles per CTA, softmax of one tile under the products of the other
+    constexpr int smem = AttnFwd2Smem::TOTAL;
     static bool cfg = false;
-    if (!cfg) { C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); cfg = true; }
-    kern<<<grid, ATT_THREADS, smem, stream>>>(tmQ, tmK, tmV, p);
-  } else {
-    auto kern = attn_fwd_kernel<false>;
-    constexpr int smem = AttnFwdSmem<false>::TOTAL;
-    static bool cfg = false;
-    if (!cfg) { C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); cfg = true; }
-    kern<<<grid, ATT_THREADS, smem, stream>>>(tmQ, tmK, tmV, p);
+    if (!cfg) { C10_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); cfg = true; }
+    dim3 grid2((S + 2 * ATT_BQ - 1) / (2 * ATT_BQ), Hq, B);
+    attn_fwd2_kernel<<<grid2, AF2_THREADS, smem, stream>>>(tmQ, tmK, tmV, p);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    count_launch();
+    return lse;
   }
+  dim3 grid((S + ATT_BQ - 1) / ATT_BQ, Hq, B);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
   return lse;

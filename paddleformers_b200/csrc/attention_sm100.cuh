@@ -268,4 +268,289 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 4) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Two-tile ("ping-pong") forward, the default. One CTA owns two consecutive 128-row query tiles of one head, so that
+// the tensor pipe always has the other tile's product to run while one tile is in its softmax:
+//
+//   warp 8      TMA loader: both Q tiles once, K and V tiles through two-stage rings
+//   warp 9      MMA issuer:  S_t = Q_t K_j^T and O_t += P_t V_j for t = 0, 1, the S product of step j+1 issued right after
+//               the PV product of step j of the same tile (the pipe executes in order, so it cannot overtake the read of P)
+//   warps 0-3   softmax of tile 0, warps 4-7 softmax of tile 1: ONE pass over S (the 128 scores of a row stay in
+//               registers), P written back over S as bf16. O stays in TMEM for the whole walk: it is rescaled only when
+//               a row maximum has grown by more than 2^8 since the scale last used (the lazy rescale), which after the
+//               first tiles is rare; the final 1/l normalisation absorbs the stale scale exactly.
+//
+// TMEM: S_0, S_1, O_0, O_1 at 128 columns each (all 512). Same masks, layouts and outputs as attn_fwd_kernel.
+constexpr int AF2_THREADS = 320;
+constexpr float AF2_RESCALE_LOG2 = 8.f;
+
+struct AttnFwd2Smem {
+  static constexpr int TILE = ATT_BQ * ATT_D * 2;  // 32 KB
+  static constexpr int Q_OFF = 0;                  // 2 tiles
+  static constexpr int K_OFF = 2 * TILE;           // 2 stages
+  static constexpr int V_OFF = 4 * TILE;           // 2 stages
+  static constexpr int KEND_OFF = 6 * TILE;        // per softmax warp: 128 ints
+  static constexpr int BAR_OFF = KEND_OFF + 8 * 128 * 4;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+static __global__ void __launch_bounds__(AF2_THREADS, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
+  using SM = AttnFwd2Smem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* k_full = bars + 1;      // [2]
+  uint64_t* k_empty = bars + 3;     // [2]
+  uint64_t* v_full = bars + 5;      // [2]
+  uint64_t* v_empty = bars + 7;     // [2]
+  uint64_t* s_full = bars + 9;      // [2] per tile
+  uint64_t* p_full = bars + 11;     // [2] per tile
+  uint64_t* o_full = bars + 13;     // [2] per tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pair = gridDim.x - 1 - blockIdx.x;     // heavy (late) causal tiles first
+  const int head = blockIdx.y, b = blockIdx.z;
+  const int kvh = head / (p.Hq / p.Hkv);
+  const int q0 = pair * 2 * ATT_BQ;
+  const int row_base = b * p.S;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 4); mbar_init(&o_full[s], 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); tc_fence_before(); }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // kv tile ranges: common lower end, one upper end per query tile
+  const int kv_tiles = (p.S + ATT_BKV - 1) / ATT_BKV;
+  int j_lo = 0;
+  if (p.kend) {
+    const int* tmax = p.tile_max_end + b * kv_tiles;
+    const int top = p.causal ? min(kv_tiles - 1, (q0 + ATT_BQ - 1) / ATT_BKV) : kv_tiles - 1;
+    while (j_lo < top && tmax[j_lo] <= q0) ++j_lo;
+  }
+  int n_t[2];
+  #pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qt0 = q0 + t * ATT_BQ;
+    const int j_hi = p.causal ? min(kv_tiles - 1, (qt0 + ATT_BQ - 1) / ATT_BKV) : kv_tiles - 1;
+    n_t[t] = qt0 < p.S ? max(j_hi - j_lo + 1, 0) : 0;
+  }
+  const int n = max(n_t[0], n_t[1]);
+
+  if (warp == 8) {
+    // ------------------------------------------------------------ TMA loader
+    if (lane == 0 && n > 0) {
+      uint8_t* sQ = smem + SM::Q_OFF;
+      mbar_expect_tx(q_full, 2 * SM::TILE);
+      #pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        tma_load_3d(sQ + t * SM::TILE, &tmQ, q_full, 0, head, row_base + q0 + t * ATT_BQ);
+        tma_load_3d(sQ + t * SM::TILE + SM::TILE / 2, &tmQ, q_full, 64, head, row_base + q0 + t * ATT_BQ);
+      }
+      for (int jj = 0; jj < n; ++jj) {
+        const int st = jj & 1;
+        const uint32_t ph = (jj >> 1) & 1;
+        const int row = row_base + (j_lo + jj) * ATT_BKV;
+        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status, PFB_ERR_WAIT_EMPTY)) break;
+        uint8_t* sK = smem + SM::K_OFF + st * SM::TILE;
+        mbar_expect_tx(&k_full[st], SM::TILE);
+        tma_load_3d(sK, &tmK, &k_full[st], 0, kvh, row);
+        tma_load_3d(sK + SM::TILE / 2, &tmK, &k_full[st], 64, kvh, row);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status, PFB_ERR_WAIT_EMPTY)) break;
+        uint8_t* sV = smem + SM::V_OFF + st * SM::TILE;
+        mbar_expect_tx(&v_full[st], SM::TILE);
+        tma_load_3d(sV, &tmV, &v_full[st], 0, kvh, row);
+        tma_load_3d(sV + SM::TILE / 2, &tmV, &v_full[st], 64, kvh, row);
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t idesc_s = make_idesc(ATT_BQ, ATT_BKV, false, false, 1);
+      constexpr uint32_t idesc_o = make_idesc(ATT_BQ, ATT_D, false, true, 1);
+      auto issue_s = [&](int t, int jj) {
+        const uint32_t sq = smem_u32(smem + SM::Q_OFF + t * SM::TILE);
+        const uint32_t sk = smem_u32(smem + SM::K_OFF + (jj & 1) * SM::TILE);
+        #pragma unroll
+        for (int k = 0; k < ATT_D / 16; ++k) {
+          const uint32_t off = (k >> 2) * (SM::TILE / 2) + (k & 3) * 32;
+          tc_mma_f16_ss(tmem_base + t * 128, make_smem_desc_sw128(sq + off, 16, 1024), make_smem_desc_sw128(sk + off, 16, 1024),
+                        idesc_s, k != 0);
+        }
+        tc_commit(&s_full[t]);
+      };
+      auto issue_pv = [&](int t, int jj) {
+        const uint32_t sv = smem_u32(smem + SM::V_OFF + (jj & 1) * SM::TILE);
+        #pragma unroll
+        for (int k = 0; k < ATT_BKV / 16; ++k)
+          tc_mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
+                        make_smem_desc_sw128(sv + k * 16 * 128, SM::TILE / 2, 1024), idesc_o, (jj | k) != 0);
+        tc_commit(&o_full[t]);
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, PFB_ERR_WAIT_FULL);
+      ok = ok && mbar_wait(&k_full[0], 0, abort_flag, p.status, PFB_ERR_WAIT_FULL);
+      if (ok) {
+        tc_fence_after();
+        if (n_t[0] > 0) issue_s(0, 0);
+        if (n_t[1] > 0) issue_s(1, 0);
+        tc_commit(&k_empty[0]);
+      }
+      for (int jj = 0; jj < n && ok; ++jj) {
+        const uint32_t ph = jj & 1, ph2 = (jj >> 1) & 1, ph2n = ((jj + 1) >> 1) & 1;
+        if (!mbar_wait(&v_full[jj & 1], ph2, abort_flag, p.status, PFB_ERR_WAIT_FULL)) break;
+        const bool more = jj + 1 < n;
+        if (more && !mbar_wait(&k_full[(jj + 1) & 1], ph2n, abort_flag, p.status, PFB_ERR_WAIT_FULL)) break;
+        #pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (jj < n_t[t]) {
+            if (!mbar_wait(&p_full[t], ph, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv(t, jj);
+          }
+          if (jj + 1 < n_t[t]) issue_s(t, jj + 1);
+        }
+        if (!ok) break;
+        tc_commit(&v_empty[jj & 1]);
+        if (more) tc_commit(&k_empty[(jj + 1) & 1]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax: warps 0-3 tile 0, warps 4-7 tile 1
+    const int t = warp >> 2;
+    const int r = threadIdx.x & 127;
+    const int qt0 = q0 + t * ATT_BQ;
+    const int qi = qt0 + r;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem_base + t * 128 + lane_off, tO = tmem_base + 256 + t * 128 + lane_off;
+    int* s_kend = reinterpret_cast<int*>(smem + SM::KEND_OFF) + warp * 128;
+    const int nt = n_t[t];
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int jj = 0; jj < nt; ++jj) {
+      const uint32_t ph = jj & 1;
+      const int j = j_lo + jj;
+      const int k0 = j * ATT_BKV;
+      bool need_mask = (p.causal && k0 + ATT_BKV - 1 > qt0) || (k0 + ATT_BKV > p.S);
+      const bool need_kend = p.kend && p.tile_min_end[b * kv_tiles + j] < qt0 + ATT_BQ;
+      if (need_kend) {
+        __syncwarp();
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int kk = lane + 32 * i;
+          s_kend[kk] = (k0 + kk < p.S) ? p.kend[b * p.S + k0 + kk] : 0;
+        }
+        __syncwarp();
+        need_mask = true;
+      }
+      if (!mbar_wait(&s_full[t], ph, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t v[128];
+      #pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&v[32 * c]));
+      tmem_ld_wait();
+      float mx = -INFINITY;
+      if (need_mask) {
+        #pragma unroll
+        for (int i = 0; i < 128; ++i) {
+          const int kj = k0 + i;
+          bool vis = kj < p.S && (!p.causal || kj <= qi);
+          if (need_kend) vis = vis && qi < s_kend[i];
+          const float x = vis ? __uint_as_float(v[i]) : -INFINITY;
+          v[i] = __float_as_uint(x);
+          mx = fmaxf(mx, x);
+        }
+      } else {
+        #pragma unroll
+        for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+      }
+      const float m_new = fmaxf(m_used, mx * p.scale_log2);
+      // lazy rescale: keep the old reference maximum unless some row of this warp has outgrown it by 2^8
+      const bool grow = m_new > m_used + AF2_RESCALE_LOG2 || (m_used == -INFINITY && m_new != -INFINITY);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m_used - m_new);   // m_used = -inf -> 0
+        if (jj > 0) {
+          // O of this tile holds sums scaled by the old reference: wait for the last PV product, then rescale in place
+          if (!mbar_wait(&o_full[t], (jj - 1) & 1, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+          tc_fence_after();
+          #pragma unroll 1
+          for (int c = 0; c < ATT_D; c += 32) {
+            uint32_t o[32];
+            tmem_ld_32x32(tO + c, o);
+            tmem_ld_wait();
+            #pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x16(tO + c, *reinterpret_cast<uint32_t(*)[16]>(&o[0]));
+            tmem_st_32x16(tO + c + 16, *reinterpret_cast<uint32_t(*)[16]>(&o[16]));
+          }
+        }
+        l *= alpha;
+        m_used = m_new;
+      }
+      const float m_sub = m_used == -INFINITY ? 0.f : m_used;
+      float lt = 0.f;
+      #pragma unroll
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t pk[16];
+        #pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fast_exp2(__uint_as_float(v[c + i]) * p.scale_log2 - m_sub);     // masked: exp2(-inf) = 0
+          const float p1 = fast_exp2(__uint_as_float(v[c + i + 1]) * p.scale_log2 - m_sub);
+          lt += p0 + p1;
+          pk[i >> 1] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_32x16(tS + (c >> 1), pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
+      l += lt;
+    }
+    if (ok && nt > 0) ok = mbar_wait(&o_full[t], (nt - 1) & 1, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL);
+    if (ok && qt0 < p.S) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = p.O + static_cast<long long>(row_base + qi) * p.o_row_stride + head * ATT_D;
+      #pragma unroll 1
+      for (int c = 0; c < ATT_D; c += 32) {
+        uint32_t o[32];
+        if (nt > 0) { tmem_ld_32x32(tO + c, o); tmem_ld_wait(); }
+        else {
+          #pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (qi < p.S) {
+          #pragma unroll
+          for (int i = 0; i < 32; i += 8)
+            *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(
+                pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv),
+                pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv),
+                pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv),
+                pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv));
+        }
+      }
+      if (qi < p.S)
+        p.lse[(static_cast<long long>(b) * p.Hq + head) * p.S + qi] =
+            l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
 }  // namespace pfb

@@ -22,11 +22,19 @@ int* status_word() {
   std::lock_guard<std::mutex> lk(g_mu);
   auto it = g_status.find(dev);
   if (it != g_status.end()) return it->second;
+  // 16-byte block: [0] status, [1] reserved, [2..3] wait budget in ns (0 = the kernels' default of one second)
   int* p = nullptr;
-  C10_CUDA_CHECK(cudaMalloc(&p, sizeof(int)));
-  C10_CUDA_CHECK(cudaMemset(p, 0, sizeof(int)));
+  C10_CUDA_CHECK(cudaMalloc(&p, 4 * sizeof(int)));
+  C10_CUDA_CHECK(cudaMemset(p, 0, 4 * sizeof(int)));
   g_status[dev] = p;
   return p;
+}
+// Budget of every bounded device-side wait launched from now on (stream-ordered with respect to the current stream).
+void set_wait_budget(double seconds) {
+  int* p = status_word();
+  const long long ns = seconds > 0 ? static_cast<long long>(seconds * 1e9) : 0;
+  C10_CUDA_CHECK(cudaMemcpyAsync(p + 2, &ns, sizeof(ns), cudaMemcpyHostToDevice, at::cuda::getCurrentCUDAStream()));
+  C10_CUDA_CHECK(cudaStreamSynchronize(at::cuda::getCurrentCUDAStream()));
 }
 int read_status(bool reset) {
   int* p = status_word();
@@ -40,6 +48,7 @@ void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 int64_t launch_count(bool reset) { return reset ? g_launches.exchange(0) : g_launches.load(); }
 
 static int64_t op_read_status(bool reset) { return read_status(reset); }
+static void op_set_wait_budget(double seconds) { set_wait_budget(seconds); }
 static int64_t op_launch_count(bool reset) { return launch_count(reset); }
 
 // ---- declarations of the ops implemented in the other translation units ---------------------------------------
@@ -79,6 +88,7 @@ void cast_scale(const at::Tensor& src, at::Tensor& dst, double scale, bool accum
 
 TORCH_LIBRARY(pfb200, m) {
   m.def("read_status(bool reset) -> int", &pfb::op_read_status);
+  m.def("set_wait_budget(float seconds) -> ()", &pfb::op_set_wait_budget);
   m.def("launch_count(bool reset) -> int", &pfb::op_launch_count);
   m.def("gemm(Tensor a, Tensor b, Tensor(a!) out, bool a_mn, bool b_mn, int epi, Tensor? out2, Tensor? block_expert, "
         "int n_per_expert, int force_bn) -> ()", &pfb::gemm);

@@ -61,9 +61,9 @@ __global__ void ep_exchange_kernel(EpTables tabs, const int* __restrict__ my_cou
   if (tid < ep) st_release_sys_i32(tabs.peer_base[tid] + FL + 0 * EP_MAX_RANKS + rank, epoch);
   // phase B: wait for all sources' counts
   if (tid < ep) {
-    const long long t0 = clock64();
+    const long long t0 = global_ns(), budget = wait_budget_ns(status);
     while (ld_acquire_sys_i32(tabs.base + FL + 0 * EP_MAX_RANKS + tid) < epoch) {
-      if (clock64() - t0 > kWaitCycles) { atomicCAS(status, 0, PFB_ERR_WAIT_PEER); s_ok = 0; break; }
+      if (global_ns() - t0 > budget) { atomicCAS(status, 0, PFB_ERR_WAIT_PEER); s_ok = 0; break; }
       __nanosleep(64);
     }
   }
@@ -113,9 +113,9 @@ __global__ void ep_exchange_kernel(EpTables tabs, const int* __restrict__ my_cou
   if (tid < ep) st_release_sys_i32(tabs.peer_base[tid] + FL + 1 * EP_MAX_RANKS + rank, epoch);
   // phase D: wait for the offsets from every destination
   if (tid < ep) {
-    const long long t0 = clock64();
+    const long long t0 = global_ns(), budget = wait_budget_ns(status);
     while (ld_acquire_sys_i32(tabs.base + FL + 1 * EP_MAX_RANKS + tid) < epoch) {
-      if (clock64() - t0 > kWaitCycles) { atomicCAS(status, 0, PFB_ERR_WAIT_PEER); break; }
+      if (global_ns() - t0 > budget) { atomicCAS(status, 0, PFB_ERR_WAIT_PEER); break; }
       __nanosleep(64);
     }
   }
@@ -288,7 +288,7 @@ void ep_push_rows(const at::Tensor& x, const at::Tensor& idx, const at::Tensor& 
   const int n_pairs = idx.numel(), H = x.size(1);
   TORCH_CHECK(x.size(0) * k == n_pairs);
   int* tab = reinterpret_cast<int*>(peer_tab_ptrs.data_ptr<int64_t>()[rank]);
-  const int blocks = std::max(1, std::min((n_pairs * 32 + 255) / 256, 148 * 8));
+  const int blocks = std::max(1, std::min((n_pairs * 32 + 255) / 256, at::cuda::getCurrentDeviceProperties()->multiProcessorCount * 8));
   ep_push_rows_kernel<<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
       reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), reinterpret_cast<const long long*>(idx.data_ptr<int64_t>()),
       rank_in_expert.data_ptr<int>(), scale.has_value() ? scale->data_ptr<float>() : nullptr, slots_from_table ? tab + ep * EL : nullptr,
@@ -305,9 +305,9 @@ __global__ void ep_wait_flag_kernel(const int* __restrict__ flags, int ep, const
   const int tid = threadIdx.x;
   if (tid >= ep) return;
   const int epoch = *epoch_ptr;
-  const long long t0 = clock64();
+  const long long t0 = global_ns(), budget = wait_budget_ns(status);
   while (ld_acquire_sys_i32(flags + tid) < epoch) {
-    if (clock64() - t0 > kWaitCycles) { atomicCAS(status, 0, PFB_ERR_WAIT_PEER); return; }
+    if (global_ns() - t0 > budget) { atomicCAS(status, 0, PFB_ERR_WAIT_PEER); return; }
     __nanosleep(64);
   }
 }
@@ -339,7 +339,7 @@ void ep_pull_rows(c10::optional<at::Tensor> out, const at::Tensor& idx, const at
                   const at::Tensor& peer_tab_ptrs, int64_t T, int64_t k, int64_t H, int64_t EL, int64_t ep, int64_t capacity_rows) {
   const c10::cuda::CUDAGuard guard(idx.device());
   TORCH_CHECK(H % 8 == 0 && idx.numel() == T * k);
-  const int blocks = std::max<int64_t>(1, std::min<int64_t>((T * 32 + 255) / 256, 148 * 8));
+  const int blocks = std::max<int64_t>(1, std::min<int64_t>((T * 32 + 255) / 256, at::cuda::getCurrentDeviceProperties()->multiProcessorCount * 8));
   ep_pull_rows_kernel<<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
       out.has_value() ? reinterpret_cast<__nv_bfloat16*>(out->data_ptr()) : nullptr, reinterpret_cast<const long long*>(idx.data_ptr<int64_t>()),
       pair_slot.data_ptr<int>(), w.has_value() ? w->data_ptr<float>() : nullptr,

@@ -22,8 +22,22 @@ enum : int {
   PFB_ERR_BOUNDS = 6,          // a checked index was outside its buffer
 };
 
-// About one second at 2 GHz. Waits in healthy kernels finish in microseconds.
-constexpr long long kWaitCycles = 2000000000LL;
+// Wait budget. The status word handed to every kernel is the first int of a 16-byte block
+//   [0] status code   [1] reserved   [2..3] budget of one wait in nanoseconds (64 bit, 0 = default)
+// so that the host can shorten or lengthen the budget at run time (pfb200::set_wait_budget) without touching a kernel
+// signature. Waits in healthy kernels finish in microseconds; the default is one second of %globaltimer.
+constexpr long long kDefaultWaitNs = 1000000000LL;
+
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ long long wait_budget_ns(const int* status) {
+  if (status == nullptr) return kDefaultWaitNs;
+  const long long b = *reinterpret_cast<const volatile long long*>(status + 2);
+  return b > 0 ? b : kDefaultWaitNs;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -59,14 +73,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int err_code) {
   if (mbar_try_wait(bar, parity)) return true;
-  long long t0 = clock64();
+  const long long t0 = global_ns();
+  const long long budget = wait_budget_ns(status);
   while (true) {
     #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
     }
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (global_ns() - t0 > budget) {
       *abort_flag = 1;
       if (status) atomicCAS(status, 0, err_code);
       return false;

@@ -34,13 +34,16 @@ __global__ void peer_signal_kernel(const long long* __restrict__ peer_pads, int 
   }
 }
 
-// Wait until pad[slot0 + i] >= value for i < n, with a cycle budget.
-__global__ void peer_wait_kernel(const int* __restrict__ pad, int slot0, int n, int value, long long max_cycles, int* status) {
+// Wait until pad[slot0 + i] >= value for i < n, for at most max_ns nanoseconds of %globaltimer.
+__global__ void peer_wait_kernel(const int* __restrict__ pad, int slot0, int n, int value, long long max_ns, int* status) {
   const int i = threadIdx.x;
   if (i >= n) return;
-  const long long t0 = clock64();
+  long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
   while (ld_acquire_sys(pad + slot0 + i) < value) {
-    if (clock64() - t0 > max_cycles) {
+    long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (t1 - t0 > max_ns) {
       atomicCAS(status, 0, PFB_ERR_WAIT_PEER);
       return;
     }
@@ -94,7 +97,7 @@ void peer_signal(const at::Tensor& peer_pads, int64_t slot, int64_t value) {
 
 void peer_wait(int64_t pad_ptr, int64_t slot0, int64_t n, int64_t value, double timeout_s) {
   TORCH_CHECK(n <= 32);
-  const long long cycles = static_cast<long long>(timeout_s * 1.8e9);
+  const long long cycles = static_cast<long long>(timeout_s * 1e9);  // nanoseconds
   peer_wait_kernel<<<1, 32, 0, at::cuda::getCurrentCUDAStream()>>>(reinterpret_cast<const int*>(pad_ptr), static_cast<int>(slot0),
                                                                   static_cast<int>(n), static_cast<int>(value), cycles, status_word());
   C10_CUDA_KERNEL_LAUNCH_CHECK();

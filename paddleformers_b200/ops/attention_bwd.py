@@ -25,6 +25,12 @@ def _has_kernel(name: str) -> bool:
         return False
 
 
+def _bwd_options():
+    from . import functional as F
+
+    return bool(F._attn_backend.get("deterministic", False)), int(F._attn_backend.get("bwd_heads_per_cta", 0))
+
+
 def _block_visibility(q0, q1, S_k, causal, kend_b, device):
     """[q1-q0, S_k] boolean visibility for query rows q0..q1 of one batch element."""
     i = torch.arange(q0, q1, device=device)[:, None]
@@ -46,7 +52,8 @@ def flash_attention_backward(dout, q, k, v, out, lse, causal, kend, kmin, kmax, 
         dq = torch.empty_like(q)
         dk = torch.empty_like(k)
         dv = torch.empty_like(v)
-        torch.ops.pfb200.attn_bwd(dout.contiguous(), q, k, v, out, lse, dq, dk, dv, B, S, scale, causal, kend, kmin, kmax)
+        torch.ops.pfb200.attn_bwd(dout.contiguous(), q, k, v, out, lse, dq, dk, dv, B, S, scale, causal, kend, kmin, kmax,
+                                  *_bwd_options())
         return dq, dk, dv
     return _blocked_backward(dout, q, k, v, out, lse, causal, kend, scale)
 
@@ -55,7 +62,8 @@ def flash_attention_backward_into(dout, q, k, v, out, lse, causal, kend, kmin, k
     """Same as ``flash_attention_backward`` but writes into caller-provided (possibly strided) dq / dk / dv views."""
     B, S, Hq, D = q.shape
     if q.is_cuda and D == 128 and _has_kernel("attn_bwd"):
-        torch.ops.pfb200.attn_bwd(dout.contiguous(), q, k, v, out, lse, dq, dk, dv, B, S, scale, causal, kend, kmin, kmax)
+        torch.ops.pfb200.attn_bwd(dout.contiguous(), q, k, v, out, lse, dq, dk, dv, B, S, scale, causal, kend, kmin, kmax,
+                                  *_bwd_options())
         return
     a, b, c = _blocked_backward(dout, q, k, v, out, lse, causal, kend, scale)
     dq.copy_(a); dk.copy_(b); dv.copy_(c)

@@ -89,30 +89,50 @@ def bench_gemm(rows):
     F.check_kernel_status()
 
 
+def _doc_kend(B, S, lo=128, hi=4096, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    kend = torch.empty(B, S, dtype=torch.int32)
+    for b in range(B):
+        pos = 0
+        while pos < S:
+            end = min(S, pos + int(torch.randint(lo, hi + 1, (1,), generator=g)))
+            kend[b, pos:end] = end
+            pos = end
+    return kend.cuda()
+
+
 def bench_attn(rows):
-    for (B, S, Hq, Hkv) in [(1, 4096, 32, 8), (2, 4096, 32, 4), (1, 8192, 32, 8)]:
-        q = torch.randn(B, S, Hq, 128, device="cuda", dtype=torch.bfloat16)
-        k = torch.randn(B, S, Hkv, 128, device="cuda", dtype=torch.bfloat16)
-        v = torch.randn(B, S, Hkv, 128, device="cuda", dtype=torch.bfloat16)
-        flops = 4.0 * B * Hq * S * S * 128 / 2
-        res = {}
-        for mode in (True, False):
-            F.set_attention_options(p_in_tmem=mode)
-            ms = timeit(lambda: F.flash_attention(q, k, v, causal=True))
-            res[mode] = flops / ms / 1e9
-        F.set_attention_options(p_in_tmem=True)
-        qs, ks, vs = (t.permute(0, 2, 1, 3) for t in (q, k, v))
-        ms_lib = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(qs, ks, vs, is_causal=True, enable_gqa=True))
-        rows.append(f"attn fwd B={B} S={S} Hq={Hq} Hkv={Hkv}: P-in-TMEM {res[True]:7.1f} P-in-smem {res[False]:7.1f} TFLOP/s | "
-                    f"torch SDPA {flops / ms_lib / 1e9:7.1f}")
-        print(rows[-1], flush=True)
-        # backward (whatever implementation is active)
-        q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
-        out = F.flash_attention(q, k, v, causal=True)
+    """Forward and backward against torch SDPA on the same line (model FLOPs of the causal half; the packed-document
+    case counts the visible (query, key) pairs)."""
+    cases = [(1, 4096, 32, 8, False), (1, 4096, 4, 1, False), (2, 4096, 32, 4, True), (1, 8192, 32, 8, False)]
+    for (B, S, Hq, Hkv, docs) in cases:
+        q = torch.randn(B, S, Hq, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        k = torch.randn(B, S, Hkv, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        v = torch.randn(B, S, Hkv, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        kend = _doc_kend(B, S) if docs else None
+        if docs:
+            i = torch.arange(S, device="cuda")
+            pairs = float(sum(int(((i[None, :] <= i[:, None]) & (i[:, None] < kend[b][None, :])).sum()) for b in range(B)))
+        else:
+            pairs = B * S * (S + 1) / 2.0
+        flops = 4.0 * Hq * 128 * pairs
+        ms = timeit(lambda: F.flash_attention(q, k, v, causal=True, kend=kend))
+        out = F.flash_attention(q, k, v, causal=True, kend=kend)
         g = torch.randn_like(out)
         ms_b = timeit(lambda: torch.autograd.grad(out, (q, k, v), g, retain_graph=True), iters=5)
-        rows.append(f"attn bwd B={B} S={S}: {2.5 * flops / ms_b / 1e9:7.1f} TFLOP/s ({ms_b:.2f} ms)")
-        print(rows[-1], flush=True)
+        line = (f"attn B={B} S={S} Hq={Hq} Hkv={Hkv}{' packed docs' if docs else ''}: fwd {flops / ms / 1e9:7.1f} TFLOP/s ({ms * 1e3:.0f} us), "
+                f"bwd {2.5 * flops / ms_b / 1e9:7.1f} TFLOP/s ({ms_b * 1e3:.0f} us)")
+        if not docs:
+            qs, ks, vs = (t.detach().permute(0, 2, 1, 3).requires_grad_() for t in (q, k, v))
+            sd = lambda: torch.nn.functional.scaled_dot_product_attention(qs, ks, vs, is_causal=True, enable_gqa=True)
+            ms_lib = timeit(sd)
+            o2 = sd()
+            g2 = torch.randn_like(o2)
+            ms_lib_b = timeit(lambda: torch.autograd.grad(o2, (qs, ks, vs), g2, retain_graph=True), iters=5)
+            line += f" | torch SDPA fwd {flops / ms_lib / 1e9:7.1f}, bwd {2.5 * flops / ms_lib_b / 1e9:7.1f}"
+        rows.append(line)
+        print(line, flush=True)
+        del q, k, v, out, g
     F.check_kernel_status()
 
 

@@ -13,6 +13,8 @@ sees no ``.grad`` for that parameter.
 """
 from __future__ import annotations
 
+import os
+
 import math
 from typing import Optional, Tuple
 
@@ -569,7 +571,10 @@ def attention_reference(q, k, v, causal=True, kend=None, scale=None):
     return torch.matmul(p, vf).permute(0, 2, 1, 3).to(q.dtype)
 
 
-_attn_backend = {"bwd": "auto", "p_in_tmem": True}
+# "deterministic": dQ contributions of the key tiles are added in a fixed order (bit-identical runs);
+# "bwd_heads_per_cta": 0 = chosen from the grid size, 1 = one CTA per query head, 2 = one CTA per KV head (walks its group)
+_attn_backend = {"bwd": "auto", "p_in_tmem": True, "deterministic": os.environ.get("PFB_ATTN_DETERMINISTIC", "0") == "1",
+                 "bwd_heads_per_cta": 0}
 
 
 def set_attention_options(**kw):

@@ -3,7 +3,8 @@
     python -m paddleformers_b200.ops.profile_cases --case gemm|attn_fwd|attn_bwd|gemm_swiglu|gemm_wgrad|moe_layer|moe_layer_local
 
 Each case launches its kernel a few times on inputs larger than the L2 cache but well under a few GB, so that an
-``ncu --set full -k regex:<kernel> -c 1`` capture finishes in about a minute.
+``ncu --set full --clock-control none -k regex:<kernel> -s 1 -c 1`` capture finishes in about a minute (always pass
+``--clock-control none``: without it the profiler locks the GPU clocks, which other users of a shared machine inherit).
 """
 from __future__ import annotations
 

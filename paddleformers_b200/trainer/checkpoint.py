@@ -5,8 +5,10 @@ paddleformers/trainer/utils/sharding_io.py:267-920 and paddleformers/trainer/uni
 
 * ``model*.safetensors`` (+ index) and ``config.json`` — HF-compatible weights gathered over tp / ep
   (``PretrainedModel.save_pretrained``);
-* ``optimizer/shard_<domain>_<rank>of<size>.pt`` — each sharding rank's fp32 master weights and Adam moments with the
-  flat-buffer layout (``offsets``) needed to re-cut them for another sharding degree (``reshard_optimizer_state``);
+* ``optimizer/shard_<domain>_<rank>of<size>_m<tp>p<pp>e<ep>_r<writer>.pt`` — each sharding rank's fp32 master weights
+  and Adam moments with the flat-buffer layout (``offsets``) needed to re-cut them for another sharding degree
+  (``reshard_optimizer_state``). The ``m..p..e..`` tag is the writer's tensor / pipeline / expert coordinate: ranks
+  that share a sharding coordinate but hold different model shards must never read each other's files;
 * ``trainer_state.json``, ``scheduler.json``, ``rng_state_<rank>.pt`` (python / numpy / torch CPU / CUDA generators);
 * ``saved_signal_<rank>`` written last by every rank and ``.checkpoint_done`` by rank 0 once all signals exist: a
   directory without them is an interrupted save and is skipped by ``get_last_checkpoint``.
@@ -19,6 +21,7 @@ from __future__ import annotations
 import json
 import os
 import random
+import re
 import shutil
 import threading
 import time
@@ -32,6 +35,16 @@ from ..utils.log import logger
 from .trainer_utils import PREFIX_CHECKPOINT_DIR, _re_checkpoint, checkpoint_is_complete
 
 _pending: List[threading.Thread] = []
+_pending_lock = threading.Lock()
+
+
+def model_parallel_tag(ps) -> str:
+    """Tensor / pipeline / expert coordinate of a rank as it appears in optimizer shard file names."""
+    try:
+        ep = ps.rank_in("ep")
+    except Exception:  # noqa: BLE001
+        ep = 0
+    return f"m{ps.coord.get('mp', 0):02d}p{ps.coord.get('pp', 0):02d}e{ep:02d}"
 
 
 def _barrier():
@@ -40,8 +53,16 @@ def _barrier():
 
 
 def wait_for_pending_saves():
-    while _pending:
-        _pending.pop().join()
+    """Join the background writers. Threads are joined first and removed afterwards under a lock, so that a second
+    caller (the mirror worker) never makes the list look empty while a writer still reads the pinned snapshot."""
+    with _pending_lock:
+        threads = list(_pending)
+    for t in threads:
+        t.join()
+    with _pending_lock:
+        for t in threads:
+            if t in _pending:
+                _pending.remove(t)
 
 
 def _rng_state() -> Dict[str, object]:
@@ -65,6 +86,15 @@ def save_checkpoint(trainer, out_dir: str) -> None:
     world = dist.get_world_size() if dist.is_initialized() else 1
     wait_for_pending_saves()
     os.makedirs(os.path.join(out_dir, "optimizer"), exist_ok=True)
+    # markers of an interrupted save of the same step must not count towards this one
+    for stale in (f"saved_signal_{rank}",) + ((".checkpoint_done",) if rank == 0 else ()):
+        try:
+            os.remove(os.path.join(out_dir, stale))
+        except FileNotFoundError:
+            pass
+    _barrier()
+    tag = model_parallel_tag(ps)
+    rotate_limit = int(getattr(args, "save_total_limit", 0) or 0)
     zcc = getattr(trainer, "zcc", None)
     extra = None
     if zcc is not None:
@@ -85,8 +115,8 @@ def save_checkpoint(trainer, out_dir: str) -> None:
         opt_state = trainer.optimizer.state_dict()
     files = {}
     for name, dom in opt_state["domains"].items():
-        fname = f"shard_{name}_{dom['shard_rank']:03d}of{dom['shard_size']:03d}_r{rank:05d}.pt"
-        files[fname] = {"step": opt_state["step"], "lr": opt_state["lr"], "domain": name, **dom}
+        fname = f"shard_{name}_{dom['shard_rank']:03d}of{dom['shard_size']:03d}_{tag}_r{rank:05d}.pt"
+        files[fname] = {"step": opt_state["step"], "lr": opt_state["lr"], "domain": name, "mp_tag": tag, **dom}
     rng = _rng_state()
     sched = trainer.lr_scheduler.state_dict()
     state_json = None
@@ -120,13 +150,17 @@ def save_checkpoint(trainer, out_dir: str) -> None:
                 if have >= world:
                     with open(os.path.join(out_dir, ".checkpoint_done"), "w") as f:
                         f.write(str(world))
+                    # older checkpoints go only now that this one is complete
+                    if rotate_limit > 0:
+                        rotate_checkpoints(os.path.dirname(os.path.abspath(out_dir)), rotate_limit)
                     break
                 time.sleep(0.05)
 
     if args.async_save or zcc is not None:
         t = threading.Thread(target=write, daemon=False)
         t.start()
-        _pending.append(t)
+        with _pending_lock:
+            _pending.append(t)
     else:
         write()
         _barrier()
@@ -191,13 +225,21 @@ def load_checkpoint(trainer, path: str) -> None:
         load_unified_optimizer(trainer, path)          # tensor / pipeline / expert degrees differ: shards cannot be re-cut
         _finish_load(trainer, path, rank)
         return
+    tag = model_parallel_tag(ps)
+    solo_model = all(int(getattr(ps.degrees, k)) == 1 for k in ("mp", "pp", "ep"))
     for dom in opt.domains:
         want = f"shard_{dom.name}_{dom.shard_rank:03d}of{dom.shard_size:03d}_"
-        cands = sorted(f for f in os.listdir(opt_dir) if f.startswith(want) and f.endswith(".pt"))
-        if cands:
-            payload = torch.load(os.path.join(opt_dir, cands[0]), map_location="cpu", weights_only=False)
+        names = sorted(f for f in os.listdir(opt_dir) if f.startswith(want) and f.endswith(".pt"))
+        # this rank's own model shard; files without a tag come from checkpoints of a job without model parallelism
+        cands = [f for f in names if f"_{tag}_" in f[len(want) - 1:]]
+        if not cands and solo_model:
+            cands = [f for f in names if _re_tag.search(f) is None]
+        exact = [f for f in cands if f.endswith(f"_r{rank:05d}.pt")]
+        if exact or cands:
+            payload = torch.load(os.path.join(opt_dir, (exact or cands)[0]), map_location="cpu", weights_only=False)
         else:
-            payload = reshard_optimizer_state(opt_dir, dom.name, dom.shard_rank, dom.shard_size, dom.numel)
+            payload = reshard_optimizer_state(opt_dir, dom.name, dom.shard_rank, dom.shard_size, dom.numel,
+                                              mp_tag=None if solo_model else tag)
         sd["domains"][dom.name] = payload
         sd["step"], sd["lr"] = payload["step"], payload["lr"]
     opt.load_state_dict(sd)
@@ -227,13 +269,24 @@ def _finish_load(trainer, path: str, rank: int) -> None:
     logger.info(f"resumed from {path} at step {trainer.state.global_step}")
 
 
-def reshard_optimizer_state(opt_dir: str, domain: str, new_rank: int, new_size: int, numel: int) -> Dict[str, object]:
+_re_tag = re.compile(r"_m\d+p\d+e\d+_")
+
+
+def reshard_optimizer_state(opt_dir: str, domain: str, new_rank: int, new_size: int, numel: int,
+                            mp_tag: Optional[str] = None) -> Dict[str, object]:
     """Re-cut a domain saved with another sharding degree: concatenates the saved shards that overlap the new slice
-    (the flat layout is independent of the sharding degree up to tail padding)."""
+    (the flat layout is independent of the sharding degree up to tail padding). ``mp_tag`` restricts the shards to
+    those written by one tensor / pipeline / expert coordinate (``model_parallel_tag``); shards of different model
+    shards have the same sizes and must not be mixed."""
     shards = {}
-    for f in os.listdir(opt_dir):
+    for f in sorted(os.listdir(opt_dir)):
         if f.startswith(f"shard_{domain}_") and f.endswith(".pt"):
+            if mp_tag is not None and f"_{mp_tag}_" not in f:
+                continue
             p = torch.load(os.path.join(opt_dir, f), map_location="cpu", weights_only=False)
+            if mp_tag is None and p["shard_rank"] in shards and p.get("mp_tag") != shards[p["shard_rank"]].get("mp_tag"):
+                raise RuntimeError(f"optimizer domain {domain}: shards of several model-parallel coordinates found; "
+                                   "pass mp_tag to choose one")
             shards[p["shard_rank"]] = p
     if not shards:
         raise FileNotFoundError(f"no optimizer shards for domain {domain} in {opt_dir}")
@@ -242,7 +295,7 @@ def reshard_optimizer_state(opt_dir: str, domain: str, new_rank: int, new_size: 
         raise RuntimeError(f"optimizer domain {domain}: found {len(shards)} of {old_size} shards")
     any_p = shards[0]
     out = {"step": any_p["step"], "lr": any_p["lr"], "domain": domain, "offsets": any_p["offsets"], "numel": numel,
-           "shard_rank": new_rank, "shard_size": new_size}
+           "shard_rank": new_rank, "shard_size": new_size, "mp_tag": any_p.get("mp_tag")}
     n_new = numel // new_size
     lo, hi = new_rank * n_new, (new_rank + 1) * n_new
     for key in ("master", "exp_avg", "exp_avg_sq"):
@@ -254,10 +307,12 @@ def reshard_optimizer_state(opt_dir: str, domain: str, new_rank: int, new_size: 
 
 
 def rotate_checkpoints(output_dir: str, limit: int) -> None:
+    """Keep the newest ``limit`` COMPLETE checkpoints. Directories of saves that are still being written (or were
+    interrupted) are neither counted nor deleted here, so the last complete checkpoint always survives."""
     cands = []
     for name in os.listdir(output_dir):
         m = _re_checkpoint.match(name)
-        if m:
+        if m and checkpoint_is_complete(os.path.join(output_dir, name)):
             cands.append((int(m.group(1)), os.path.join(output_dir, name)))
     cands.sort()
     for _, path in cands[:-limit] if limit > 0 else []:

@@ -35,8 +35,11 @@ def list_domains(opt_dir: str) -> Dict[str, Dict[str, int]]:
             continue
         p = torch.load(os.path.join(opt_dir, f), map_location="cpu", weights_only=False)
         d = out.setdefault(p["domain"], {"shard_size": int(p["shard_size"]), "numel": int(p["numel"]), "files": 0,
-                                         "step": int(p["step"])})
+                                         "step": int(p["step"]), "mp_tags": []})
         d["files"] += 1
+        tag = p.get("mp_tag")
+        if tag not in d["mp_tags"]:
+            d["mp_tags"].append(tag)
     return out
 
 
@@ -85,11 +88,15 @@ def reshard(path: str, out: str, sharding: int) -> List[str]:
         used = max((off + (cnt + _ALIGN - 1) // _ALIGN * _ALIGN) for off, cnt in offsets.values()) if offsets else d["numel"]
         unit = _ALIGN * sharding
         numel = (used + unit - 1) // unit * unit
-        for r in range(sharding):
-            payload = reshard_optimizer_state(opt_dir, name, r, sharding, numel)
-            fname = f"shard_{name}_{r:03d}of{sharding:03d}_r{r:05d}.pt"
-            torch.save(payload, os.path.join(out, "optimizer", fname))
-            written.append(fname)
+        # one re-cut per tensor / pipeline / expert coordinate that wrote this domain: their shards have equal sizes
+        # and different contents
+        for ti, tag in enumerate(d["mp_tags"]):
+            for r in range(sharding):
+                payload = reshard_optimizer_state(opt_dir, name, r, sharding, numel, mp_tag=tag)
+                mid = f"_{tag}" if tag else ""
+                fname = f"shard_{name}_{r:03d}of{sharding:03d}{mid}_r{ti * sharding + r:05d}.pt"
+                torch.save(payload, os.path.join(out, "optimizer", fname))
+                written.append(fname)
     # random-number states belong to the old ranks: rank 0's is kept for every new rank so that a resume is deterministic
     rng0 = os.path.join(path, "rng_state_0.pt")
     for r in range(sharding):

@@ -363,12 +363,23 @@ class Trainer:
                 self._sampler.skip_batches = skip_batches if epoch == start_epoch else 0
             self.control = self.callback_handler.on_epoch_begin(a, self.state, self.control)
             micro: List[Dict[str, Any]] = []
+            skip_left = 0
             for step, inputs in enumerate(loader):
                 self.control = self.callback_handler.on_load_data_end(a, self.state, self.control, inputs=inputs)
-                if any(lo <= self.state.global_step + 1 <= hi for lo, hi in skip_intervals) and len(micro) == 0 and (step + 1) % accum == 0:
-                    # operator-requested skip of poisonous steps (paddleformers/trainer/trainer.py:2490-2547)
-                    self.state.global_step += 1
-                    self.lr_scheduler.step()
+                if skip_left == 0 and len(micro) == 0 and any(lo <= self.state.global_step + 1 <= hi for lo, hi in skip_intervals):
+                    # operator-requested skip of poisonous steps (paddleformers/trainer/trainer.py:2490-2547): the whole
+                    # global batch of the step (all of its micro-batches) is read and dropped, then the step counter, the
+                    # sample counter and the scheduler advance once
+                    skip_left = accum
+                if skip_left > 0:
+                    skip_left -= 1
+                    if skip_left == 0:
+                        self.state.global_step += 1
+                        self.state.consumed_samples += a.global_batch_size
+                        self.lr_scheduler.step()
+                        if a.max_steps > 0 and self.state.global_step >= max_steps:
+                            self.control.should_training_stop = True
+                            break
                     continue
                 if len(micro) == 0 and not use_pp:
                     self.control = self.callback_handler.on_step_begin(a, self.state, self.control)
@@ -433,6 +444,12 @@ class Trainer:
                 dist.all_reduce(loss, group=self.ps.group("dp_sharding_cp"))
                 loss = loss / n_parts
             loss_v = float(loss)   # the only host sync of the training loop, on logging steps
+            if self.device.type == "cuda":
+                # a bounded device wait that ran out, an expert-parallel receive buffer that overflowed or a failed bounds
+                # check leaves a code in the device status word; stop here instead of training on wrong numbers
+                from ..ops import functional as F
+
+                F.check_kernel_status()
             if not math.isfinite(loss_v):
                 raise FloatingPointError(f"LOSS_{'NAN' if math.isnan(loss_v) else 'INF'}_ERROR: loss is {loss_v} at "
                                          f"step {self.state.global_step}")
@@ -540,9 +557,11 @@ class Trainer:
 
     def _save_checkpoint(self):
         out = os.path.join(self.args.output_dir, f"{PREFIX_CHECKPOINT_DIR}-{self.state.global_step}")
-        ckpt.save_checkpoint(self, out)
-        if self.args.save_total_limit and self.args.process_index == 0:
-            ckpt.rotate_checkpoints(self.args.output_dir, self.args.save_total_limit)
+        from ..ops import functional as F
+
+        if self.device.type == "cuda":
+            F.check_kernel_status()      # never persist a state produced after a kernel reported an error
+        ckpt.save_checkpoint(self, out)  # rotation happens inside, once the new checkpoint is complete
         if self.args.save_hf_steps > 0 and self.state.global_step % self.args.save_hf_steps == 0:
             self.save_model(os.path.join(self.args.output_dir, f"hf_checkpoint-{self.state.global_step}"))
 

@@ -46,19 +46,56 @@ def test_attention_forward(F, p_in_tmem, B, S, Hq, Hkv, docs):
     assert _rel_err(out, ref) < 2e-2
 
 
-def test_attention_backward(F):
-    torch.manual_seed(1)
-    B, S, Hq, Hkv = 1, 384, 4, 2
+def _backward_case(F, B, S, Hq, Hkv, causal, docs, seed=1):
+    torch.manual_seed(seed)
     q = torch.randn(B, S, Hq, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     k = torch.randn(B, S, Hkv, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     v = torch.randn(B, S, Hkv, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
-    kend = _doc_kend(B, S, "cuda", 2)
-    out = F.flash_attention(q, k, v, causal=True, kend=kend)
+    kend = _doc_kend(B, S, "cuda", 2) if docs else None
+    out = F.flash_attention(q, k, v, causal=causal, kend=kend)
     g = torch.randn_like(out)
     out.backward(g)
     F.check_kernel_status()
+    return q, k, v, kend, out, g
+
+
+# heads_per_cta: 1 = one CTA per query head (fp32 dK / dV partials), 2 = one CTA per KV head walking its query heads
+@pytest.mark.parametrize("hpc", [1, 2])
+@pytest.mark.parametrize("B,S,Hq,Hkv,causal,docs", [
+    (1, 384, 4, 2, True, True),      # documents, G = 2
+    (2, 512, 4, 4, True, False),     # batch 2, G = 1
+    (1, 456, 4, 1, True, False),     # S not a multiple of 64, G = 4
+    (1, 320, 8, 1, False, False),    # not causal, G = 8
+    (2, 200, 2, 1, False, True),     # not causal + documents, ragged, batch 2
+    (1, 1024, 8, 2, True, True),     # many tiles per CTA: exercises every ring wrap
+])
+def test_attention_backward(F, hpc, B, S, Hq, Hkv, causal, docs):
+    F.set_attention_options(bwd_heads_per_cta=hpc)
+    try:
+        q, k, v, kend, out, g = _backward_case(F, B, S, Hq, Hkv, causal, docs)
+    finally:
+        F.set_attention_options(bwd_heads_per_cta=0)
     qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
-    ref = F.attention_reference(qr, kr, vr, causal=True, kend=kend)
+    ref = F.attention_reference(qr, kr, vr, causal=causal, kend=kend)
     ref.backward(g.float())
     assert _rel_err(out, ref) < 2e-2
     assert _rel_err(q.grad, qr.grad) < 3e-2 and _rel_err(k.grad, kr.grad) < 3e-2 and _rel_err(v.grad, vr.grad) < 3e-2
+
+
+def test_attention_backward_deterministic_mode_is_bitwise_reproducible(F):
+    """With ordered dQ accumulation two runs on the same inputs give identical bits (the default adds the key tiles'
+    contributions in arrival order)."""
+    F.set_attention_options(deterministic=True)
+    try:
+        runs = []
+        for _ in range(2):
+            q, k, v, kend, out, g = _backward_case(F, 2, 1024, 8, 2, True, True, seed=5)
+            runs.append((q.grad.clone(), k.grad.clone(), v.grad.clone()))
+        qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+        ref = F.attention_reference(qr, kr, vr, causal=True, kend=kend)
+        ref.backward(g.float())
+    finally:
+        F.set_attention_options(deterministic=False)
+    for a, b in zip(*runs):
+        assert torch.equal(a, b)
+    assert _rel_err(runs[0][0], qr.grad) < 3e-2 and _rel_err(runs[0][1], kr.grad) < 3e-2

@@ -1,4 +1,6 @@
 """Hybrid-parallel logic on CPU ranks (gloo): every strategy must reproduce the single-process losses."""
+import os
+
 import pytest
 import torch
 
@@ -330,6 +332,24 @@ def test_offline_resharding_tool_prepares_a_checkpoint_for_more_ranks(tmp_path):
     got = run_distributed(_train_and_save, 2, dict(sharding="stage1", gradient_accumulation_steps=1), 4, full, str(tmp_path / "two"), True)[0]
     for a, b in zip(ref[2:], got[-2:]):
         assert abs(a - b) < 3e-4 * max(1.0, abs(a)), (ref, got)
+
+
+@pytest.mark.parametrize("extra", [dict(), dict(enable_zero_cost_checkpoint=True)], ids=["sharded", "zcc"])
+def test_sharded_checkpoint_resumes_under_tensor_parallelism(tmp_path, extra):
+    """Two tensor-parallel ranks share the sharding coordinate 0: each must get back its OWN master weights and
+    moments (the shard files carry the tensor / pipeline / expert coordinate), so the resumed run continues like the
+    uninterrupted one."""
+    full = _reference(False, 4, 2)
+    tp2 = dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2, **extra)
+    ref = run_distributed(_train_and_save, 2, dict(tp2), 4, full, str(tmp_path / "ref"), False)
+    run_distributed(_train_and_save, 2, dict(tp2), 2, full, str(tmp_path / "run"), False)
+    files = os.listdir(str(tmp_path / "run" / "checkpoint-2" / "optimizer"))
+    assert any("_m00p00e00_" in f for f in files) and any("_m01p00e00_" in f for f in files), files
+    got = run_distributed(_train_and_save, 2, dict(tp2), 4, full, str(tmp_path / "run"), True)
+    for r in range(2):
+        assert len(got[r]) >= 2
+        for a, b in zip(ref[r][2:], got[r][-2:]):
+            assert abs(a - b) < 3e-4 * max(1.0, abs(a)), (ref[r], got[r])
 
 
 def test_tensor_parallel_checkpoint_loads_in_one_process(tmp_path):

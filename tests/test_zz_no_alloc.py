@@ -4,8 +4,8 @@ Some users drive these kernels from C / C++ in processes that cannot call cudaMa
 handed out in full, or a section where cudaMalloc's device-wide synchronisation is not acceptable); for them the
 library keeps the weight-gradient scratch in a static device array. This test calls the C symbol with raw device
 pointers twice in a row (the second call re-uses the scratch that the first one left behind, once overwriting and once
-accumulating into dw) and checks both results against the regular entry point, then checks that an over-long row is
-refused with a message instead of being run. The file name sorts last so that a run that stops at the first failure
+accumulating into dw) and checks both results against the regular entry point and against the same gradients
+written as plain fp32 PyTorch expressions, then checks that an over-long row is refused with a message instead of being run. The file name sorts last so that a run that stops at the first failure
 has already executed every other test.
 """
 import ctypes
@@ -69,6 +69,16 @@ def test_noalloc_rms_norm_bwd_matches_regular_entry_point():
             assert torch.cuda.mem_get_info()[0] >= free_before
         assert _rel_err(dx, dx_ref) < 1e-2
         assert _rel_err(dw, dw_ref) < 2e-2
+        # fp32 oracle: y = x * rstd * w  =>  dx = rstd * (g - xhat * mean(g * xhat)) with g = dy * w, dw = sum_t dy * xhat
+        xf, dyf, wf = x.float(), dy.float(), w.float()
+        xhat = xf * rstd[:, None]
+        g = dyf * wf
+        dx_o = rstd[:, None] * (g - xhat * (g * xhat).mean(-1, keepdim=True))
+        if dres is not None:
+            dx_o = dx_o + dres.float()
+        dw_o = start + (dyf * xhat).sum(0)
+        assert _rel_err(dx, dx_o) < 1e-2
+        assert _rel_err(dw, dw_o) < 2e-2
 
 
 def test_noalloc_rejects_rows_beyond_the_static_scratch():
