@@ -13,8 +13,6 @@
 
 namespace pfb {
 
-static at::Tensor g_prof_buf;  // TEMP
-
 static CUtensorMap map3(const at::Tensor& t, int box_rows) {
   TORCH_CHECK(t.dim() == 3 && t.stride(2) == 1 && t.scalar_type() == at::kBFloat16 && t.size(2) == ATT_D);
   return make_tma_3d(t.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t.size(0), t.size(1), t.size(2), t.stride(0),
@@ -94,12 +92,6 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
     pp.base = p;
     pp.deterministic = deterministic ? 1 : 0;
     pp.dq_turn = nullptr;
-    { const char* e = std::getenv("PFB_DEBUG_BWD"); pp.debug_flags = e ? atoi(e) : 0; }
-    pp.prof = nullptr;
-    if (std::getenv("PFB_PROF_BWD")) {
-      if (!g_prof_buf.defined()) g_prof_buf = at::zeros({32}, lse.options().dtype(at::kLong));
-      pp.prof = reinterpret_cast<long long*>(g_prof_buf.data_ptr<int64_t>());
-    }
     at::Tensor turns;
     if (deterministic) {
       turns = at::zeros({B, Hq, (S + ATTB_BQ - 1) / ATTB_BQ}, lse.options().dtype(at::kInt));
@@ -117,14 +109,6 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
     attn_bwd2_kernel<<<grid, AB2_THREADS, AttnBwd2Smem::TOTAL, stream>>>(tmQ, tmK, tmV, tmdO, tmdQ, pp);
   }
   C10_CUDA_KERNEL_LAUNCH_CHECK();
-  if (std::getenv("PFB_PROF_BWD") && !use_v1) {
-    cudaStreamSynchronize(stream);
-    at::Tensor h = g_prof_buf.cpu();
-    const int64_t* v = h.data_ptr<int64_t>();
-    printf("bwd2 prof CTA0: n_it %lld total %lld | mma waits: q_full %lld dq_read %lld bar_p %lld bar_ds %lld | compute: total %lld wait_s %lld wait_dp %lld | dq: total %lld wait_dq %lld\n",
-           (long long)v[5], (long long)v[4], (long long)v[0], (long long)v[1], (long long)v[2], (long long)v[3], (long long)v[10], (long long)v[8], (long long)v[9], (long long)v[13], (long long)v[12]);
-    printf("   compute segments: ldS %lld exp %lld stP %lld lddP %lld dS %lld st_dS %lld\n", (long long)v[16], (long long)v[17], (long long)v[18], (long long)v[19], (long long)v[20], (long long)v[21]);
-  }
   {
     const long long work = T * (Hq * ATT_D / 4);
     const int blocks = static_cast<int>(std::min<long long>((work + 255) / 256, static_cast<long long>(at::cuda::getCurrentDeviceProperties()->multiProcessorCount) * 16));

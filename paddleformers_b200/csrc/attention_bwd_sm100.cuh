@@ -324,23 +324,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
 // ------------------------------------------------------------------------------------------------------------------
 // Pipelined backward (the default). Same mathematics and operand layouts as attn_bwd_kernel above, but the work of a
-// query tile is spread over four roles that run concurrently on two tiles:
+// query tile is spread over four roles that run concurrently on several tiles:
 //
-//   warp 8     TMA loader: K, V once; Q / dO tiles through a three-stage ring
-//   warp 9     MMA issuer: S^T and dP^T of tile i+1 are issued BEFORE it waits for P(i) / dS(i), so the tensor pipe works
-//              on tile i+1's products and tile i-1's dV / dK / dQ while the compute warps handle tile i
-//   warps 0-3  compute: P^T = exp2(S^T - lse), dS^T = P^T (dP^T - delta) scale; both are written back to TMEM as bf16
-//              (A operands of the dV / dK products) and dS^T also to swizzled shared memory (B operand of dQ^T)
-//   warps 4-7  dQ: read dQ^T from TMEM, transpose through shared memory, and add it to the fp32 accumulator with one
+//   warp 12    TMA loader: K, V once; Q / dO tiles through a three-stage ring
+//   warp 13    MMA issuer: S^T and dP^T run TWO tiles ahead of the dV / dK / dQ products, so the tensor pipe always has
+//              queued work while the compute warps handle a tile, and no product waits for a round trip through
+//              another warp except dP^T(i+2), which needs the dQ warps to have emptied the columns it reuses
+//   warps 0-7  compute: P^T = exp2(S^T - lse), dS^T = P^T (dP^T - delta) scale; both are written back to TMEM as bf16
+//              (A operands of the dV / dK products) and dS^T also to swizzled shared memory (B operand of dQ^T).
+//              Two warps share a TMEM lane quadrant (32 key rows) and split the 64 query columns, so that every
+//              scheduler has two compute warps to interleave: one warp per scheduler leaves the ALU latencies exposed
+//   warps 8-11 dQ: read dQ^T from TMEM, transpose through shared memory, and add it to the fp32 accumulator with one
 //              TMA reduce-add per 32 query rows (instead of per-element atomics). With `deterministic` the adds of one
 //              query tile happen in a fixed order (descending key tile): every CTA takes its turn on a per-tile counter.
 //
-// TMEM (512 columns): two stages of [S^T 64 | dP^T 64], dV 128, dK 128. Within a stage P^T (bf16) overwrites columns
-// 0-31 and dS^T (bf16) columns 96-127; the 64 columns in between are dead by then and receive dQ^T, so no separate
-// dQ accumulator is needed. With `heads_per_cta` = G the CTA walks all query heads of its KV head and dK / dV accumulate
-// over them in TMEM (no fp32 partials); with 1 it owns one query head (keeps the grid large when a rank has few KV heads).
-#define PFB_PROF_WAIT(slot, expr) do { long long _t0 = clock64(); bool _r = (expr); _prof[slot] += clock64() - _t0; if (!_r) { _fail = true; } } while (0)
-constexpr int AB2_THREADS = 320;
+// TMEM (512 columns): two stages of [S^T 64 | dP^T 64], dV 128, dK 128. Each half-warp group overwrites its OWN 32 raw
+// score columns: P^T (bf16) the first 16 of them, dS^T (bf16) the last 16, so the two groups never touch each other's
+// columns and need no barrier; the dP^T columns 64-127 are dead once dS^T exists and receive dQ^T, so no separate dQ accumulator is needed, and S^T(i+2) can be issued into columns 0-63 as
+// soon as the products that read P^T(i) / dS^T(i) have been issued (the tensor pipe executes in order).
+// With `heads_per_cta` = G the CTA walks all query heads of its KV head and dK / dV accumulate over them in TMEM (no
+// fp32 partials); with 1 it owns one query head (keeps the grid large when a rank has few KV heads).
+constexpr int AB2_THREADS = 448;
 constexpr int AB2_QSTAGES = 3;
 
 struct AttnBwd2Params {
@@ -348,8 +352,6 @@ struct AttnBwd2Params {
   int heads_per_cta;     // Hq / Hkv, or 1
   int deterministic;     // 1: ordered dQ accumulation
   int* dq_turn;          // [B, Hq, q_tiles] zero-initialised counters (deterministic mode)
-  int debug_flags;       // TEMP: 1 = skip the dQ reduce-add, 2 = skip staging too
-  long long* prof;       // TEMP: per-role wait cycles of CTA (0,0,0)
 };
 
 struct AttnBwd2Smem {
@@ -359,8 +361,8 @@ struct AttnBwd2Smem {
   static constexpr int Q_OFF = 2 * KV_TILE;                               // QSTAGES x (Q, dO)
   static constexpr int DS_OFF = Q_OFF + AB2_QSTAGES * 2 * Q_TILE;         // 2 x dS^T [128 keys x 64 q] bf16
   static constexpr int DQ_OFF = DS_OFF + 2 * ATTB_BKV * ATTB_BQ * 2;      // fp32 [32 q x 128 d] staging for the reduce-add
-  static constexpr int STAT_OFF = DQ_OFF + 32 * ATT_D * 4;                // per compute warp: lse[64], delta[64]
-  static constexpr int BAR_OFF = STAT_OFF + 4 * 2 * 64 * 4;
+  static constexpr int STAT_OFF = DQ_OFF + 32 * ATT_D * 4;                // per compute warp: lse[32], delta[32]
+  static constexpr int BAR_OFF = STAT_OFF + 8 * 2 * 32 * 4;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -415,14 +417,14 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(bar_kv, 1);
     for (int s = 0; s < AB2_QSTAGES; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&bar_s[s], 1); mbar_init(&bar_dp[s], 1); mbar_init(&bar_p[s], 4); mbar_init(&bar_ds[s], 4);
+      mbar_init(&bar_s[s], 1); mbar_init(&bar_dp[s], 1); mbar_init(&bar_p[s], 8); mbar_init(&bar_ds[s], 8);
       mbar_init(&bar_dq[s], 1); mbar_init(&dq_read[s], 4);
     }
     mbar_init(bar_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); tc_fence_before(); }
+  if (warp == 13) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); tc_fence_before(); }
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
@@ -441,7 +443,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int n_q = max(i_hi - i_lo + 1, 0);
   const int n_it = n_q * HPC;
 
-  if (warp == 8) {
+  if (warp == 12) {
     // ------------------------------------------------------------ TMA loader
     if (lane == 0 && n_it > 0) {
       mbar_expect_tx(bar_kv, 2 * SM::KV_TILE);
@@ -463,243 +465,188 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (++st == AB2_QSTAGES) { st = 0; ph ^= 1; }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 13) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0 && n_it > 0) {
       constexpr uint32_t idesc_s = make_idesc(128, ATTB_BQ, false, false, 1);   // K-major x K-major
       constexpr uint32_t idesc_dkv = make_idesc(128, ATT_D, false, true, 1);     // TMEM A x MN-major B
       constexpr uint32_t idesc_dq = make_idesc(128, ATTB_BQ, true, true, 1);     // MN-major x MN-major
       bool ok = mbar_wait(bar_kv, 0, abort_flag, p.status, PFB_ERR_WAIT_FULL);
-      long long _prof[8] = {0, 0, 0, 0, 0, 0, 0, 0}; bool _fail = false; const long long _tstart = clock64();
-      auto issue_s_dp = [&](int it) -> bool {
+      auto issue_s = [&](int it) -> bool {
         const int qs = it % AB2_QSTAGES, st = it & 1;
-        PFB_PROF_WAIT(0, mbar_wait(&q_full[qs], (it / AB2_QSTAGES) & 1, abort_flag, p.status, PFB_ERR_WAIT_FULL));
-        if (_fail) return false;
+        if (!mbar_wait(&q_full[qs], (it / AB2_QSTAGES) & 1, abort_flag, p.status, PFB_ERR_WAIT_FULL)) return false;
         tc_fence_after();
         const uint32_t sq = smem_u32(smem + SM::Q_OFF + qs * 2 * SM::Q_TILE);
-        const uint32_t sdo = sq + SM::Q_TILE;
-        const uint32_t tS = tmem_base + st * 128, tdP = tS + 64;
-        if (pp.debug_flags & 32) {
-          #pragma unroll
-          for (int k = 0; k < ATT_D / 16; ++k) {
-            const uint32_t offk = (k >> 2) * (SM::KV_TILE / 2) + (k & 3) * 32;
-            const uint32_t offq = (k >> 2) * (SM::Q_TILE / 2) + (k & 3) * 32;
-            tc_mma_f16_ss(tS, make_smem_desc_sw128(smem_u32(sK) + offk, 16, 1024), make_smem_desc_sw128(sq + offq, 16, 1024),
-                          idesc_s, k != 0);
-            tc_mma_f16_ss(tdP, make_smem_desc_sw128(smem_u32(sV) + offk, 16, 1024), make_smem_desc_sw128(sdo + offq, 16, 1024),
-                          idesc_s, k != 0);
-          }
-          tc_commit(&bar_s[st]);
-        } else {
-          #pragma unroll
-          for (int k = 0; k < ATT_D / 16; ++k) {
-            const uint32_t offk = (k >> 2) * (SM::KV_TILE / 2) + (k & 3) * 32;
-            const uint32_t offq = (k >> 2) * (SM::Q_TILE / 2) + (k & 3) * 32;
-            tc_mma_f16_ss(tS, make_smem_desc_sw128(smem_u32(sK) + offk, 16, 1024), make_smem_desc_sw128(sq + offq, 16, 1024),
-                          idesc_s, k != 0);
-          }
-          tc_commit(&bar_s[st]);
-          #pragma unroll
-          for (int k = 0; k < ATT_D / 16; ++k) {
-            const uint32_t offk = (k >> 2) * (SM::KV_TILE / 2) + (k & 3) * 32;
-            const uint32_t offq = (k >> 2) * (SM::Q_TILE / 2) + (k & 3) * 32;
-            tc_mma_f16_ss(tdP, make_smem_desc_sw128(smem_u32(sV) + offk, 16, 1024), make_smem_desc_sw128(sdo + offq, 16, 1024),
-                          idesc_s, k != 0);
-          }
+        #pragma unroll
+        for (int k = 0; k < ATT_D / 16; ++k) {
+          const uint32_t offk = (k >> 2) * (SM::KV_TILE / 2) + (k & 3) * 32;
+          const uint32_t offq = (k >> 2) * (SM::Q_TILE / 2) + (k & 3) * 32;
+          tc_mma_f16_ss(tmem_base + st * 128, make_smem_desc_sw128(smem_u32(sK) + offk, 16, 1024),
+                        make_smem_desc_sw128(sq + offq, 16, 1024), idesc_s, k != 0);
         }
-        tc_commit(&bar_dp[st]);
+        tc_commit(&bar_s[st]);
         return true;
       };
-      if (ok) ok = issue_s_dp(0);
+      auto issue_dp = [&](int it) {
+        const int qs = it % AB2_QSTAGES, st = it & 1;
+        const uint32_t sdo = smem_u32(smem + SM::Q_OFF + qs * 2 * SM::Q_TILE) + SM::Q_TILE;
+        #pragma unroll
+        for (int k = 0; k < ATT_D / 16; ++k) {
+          const uint32_t offk = (k >> 2) * (SM::KV_TILE / 2) + (k & 3) * 32;
+          const uint32_t offq = (k >> 2) * (SM::Q_TILE / 2) + (k & 3) * 32;
+          tc_mma_f16_ss(tmem_base + st * 128 + 64, make_smem_desc_sw128(smem_u32(sV) + offk, 16, 1024),
+                        make_smem_desc_sw128(sdo + offq, 16, 1024), idesc_s, k != 0);
+        }
+        tc_commit(&bar_dp[st]);
+      };
+      // both stages start empty: the first two tiles' S^T / dP^T need no hand-shake
+      for (int it = 0; it < 2 && it < n_it && ok; ++it) {
+        ok = issue_s(it);
+        if (ok) issue_dp(it);
+      }
       for (int it = 0; it < n_it && ok; ++it) {
         const int st = it & 1, qs = it % AB2_QSTAGES;
         const uint32_t ph2 = (it >> 1) & 1;
         const uint32_t stage = tmem_base + st * 128;
         const uint32_t sq = smem_u32(smem + SM::Q_OFF + qs * 2 * SM::Q_TILE);
         const uint32_t sdo = sq + SM::Q_TILE;
-        if (it + 1 < n_it && !(pp.debug_flags & 16)) {
-          // the other stage still holds dQ^T of tile it-1 until the dQ warps have read it
-          if (it >= 1) { PFB_PROF_WAIT(1, mbar_wait(&dq_read[st ^ 1], ((it - 1) >> 1) & 1, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)); if (_fail) break; }
-          tc_fence_after();
-          if (!issue_s_dp(it + 1)) break;
-        }
-        PFB_PROF_WAIT(2, mbar_wait(&bar_p[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)); if (_fail) break;
+        if (!mbar_wait(&bar_p[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
         #pragma unroll
         for (int k = 0; k < ATTB_BQ / 16; ++k)
-          tc_mma_f16_ts(tdV, stage + k * 8, make_smem_desc_sw128(sdo + k * 16 * 128, SM::Q_TILE / 2, 1024), idesc_dkv,
+          tc_mma_f16_ts(tdV, stage + (k >> 1) * 32 + (k & 1) * 8, make_smem_desc_sw128(sdo + k * 16 * 128, SM::Q_TILE / 2, 1024), idesc_dkv,
                         (it | k) != 0);
-        PFB_PROF_WAIT(3, mbar_wait(&bar_ds[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)); if (_fail) break;
+        if (!mbar_wait(&bar_ds[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
-        #pragma unroll
-        for (int k = 0; k < ATTB_BQ / 16; ++k)
-          tc_mma_f16_ts(tdK, stage + 96 + k * 8, make_smem_desc_sw128(sq + k * 16 * 128, SM::Q_TILE / 2, 1024), idesc_dkv,
-                        (it | k) != 0);
-        tc_commit(&q_empty[qs]);   // Q / dO of this tile are no longer read once everything issued so far has run
+        // dQ^T first: its consumers (the dQ warps) get a head start while dK runs
         const uint32_t sds = smem_u32(smem + SM::DS_OFF + st * (ATTB_BKV * ATTB_BQ * 2));
         #pragma unroll
         for (int k = 0; k < ATTB_BKV / 16; ++k)
-          tc_mma_f16_ss(stage + 32, make_smem_desc_sw128(smem_u32(sK) + k * 16 * 128, SM::KV_TILE / 2, 1024),
+          tc_mma_f16_ss(stage + 64, make_smem_desc_sw128(smem_u32(sK) + k * 16 * 128, SM::KV_TILE / 2, 1024),
                         make_smem_desc_sw128(sds + k * 16 * 128, 16, 1024), idesc_dq, k != 0);
         tc_commit(&bar_dq[st]);
-        if (it + 1 < n_it && (pp.debug_flags & 16)) {
-          if (it >= 1) { PFB_PROF_WAIT(1, mbar_wait(&dq_read[st ^ 1], ((it - 1) >> 1) & 1, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)); if (_fail) break; }
+        #pragma unroll
+        for (int k = 0; k < ATTB_BQ / 16; ++k)
+          tc_mma_f16_ts(tdK, stage + (k >> 1) * 32 + 16 + (k & 1) * 8, make_smem_desc_sw128(sq + k * 16 * 128, SM::Q_TILE / 2, 1024), idesc_dkv,
+                        (it | k) != 0);
+        tc_commit(&q_empty[qs]);   // Q / dO of this tile are no longer read once everything issued so far has run
+        if (it + 2 < n_it) {
+          // columns 0-63 of this stage: P^T / dS^T of tile it are read by products issued above (in-order pipe)
+          if (!issue_s(it + 2)) break;
+          // columns 64-127 hold dQ^T of tile it until the dQ warps have read it
+          if (!mbar_wait(&dq_read[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)) break;
           tc_fence_after();
-          if (!issue_s_dp(it + 1)) break;
+          issue_dp(it + 2);
         }
       }
       tc_commit(bar_done);
-      if (pp.prof && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-        for (int i = 0; i < 4; ++i) pp.prof[i] = _prof[i];
-        pp.prof[4] = clock64() - _tstart; pp.prof[5] = n_it;
-      }
     }
-  } else if (warp < 4) {
-    // ------------------------------------------------------------ compute warps: thread r owns key row k0 + r
-    const int r = threadIdx.x;
+  } else if (warp < 8) {
+    // ------------------------------------------------------------ compute warps: thread owns key row k0 + r and the
+    // 32 query columns of its half
+    const int quad = warp & 3, half = warp >> 2;
+    const int r = quad * 32 + lane;
     const int kj = k0 + r;
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    float* s_lse = s_stat_all + warp * 128;
-    float* s_delta = s_lse + 64;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    float* s_lse = s_stat_all + warp * 64;
+    float* s_delta = s_lse + 32;
     const int my_kend = (p.kend && kj < p.S) ? p.kend[b * p.S + kj] : 0x7fffffff;
     bool ok = true;
     // statistics of the first tile; those of tile it+1 are fetched while tile it is being processed
-    float nl[2], nd[2];
+    float nl, nd;
     auto fetch_stats = [&](int it) {
       const int g = it / n_q, i = i_lo + (it - g * n_q);
       const long long base = (static_cast<long long>(b) * p.Hq + head0 + g) * p.S;
-      #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int qi = i * ATTB_BQ + lane + 32 * c;
-        nl[c] = qi < p.S ? p.lse[base + qi] * 1.4426950408889634f : 0.f;
-        nd[c] = qi < p.S ? p.delta[base + qi] : 0.f;
-      }
+      const int qi = i * ATTB_BQ + half * 32 + lane;
+      nl = qi < p.S ? p.lse[base + qi] * 1.4426950408889634f : 0.f;
+      nd = qi < p.S ? p.delta[base + qi] : 0.f;
     };
     if (n_it > 0) fetch_stats(0);
-    long long _prof[8] = {0, 0, 0, 0, 0, 0, 0, 0}; bool _fail = false; const long long _tstart = clock64();
     for (int it = 0; it < n_it; ++it) {
       const int st = it & 1;
       const uint32_t ph2 = (it >> 1) & 1;
       const int g = it / n_q, i = i_lo + (it - g * n_q);
-      const int q0 = i * ATTB_BQ;
-      const uint32_t tS = tmem_base + st * 128 + lane_off, tdP = tS + 64;
+      const int q0 = i * ATTB_BQ + half * 32;            // first query of this thread's 32 columns
+      const uint32_t tS = tmem_base + st * 128 + half * 32 + lane_off, tdP = tS + 64;
       __syncwarp();
-      s_lse[lane] = nl[0]; s_lse[lane + 32] = nl[1];
-      s_delta[lane] = nd[0]; s_delta[lane + 32] = nd[1];
+      s_lse[lane] = nl;
+      s_delta[lane] = nd;
       __syncwarp();
       if (it + 1 < n_it) fetch_stats(it + 1);
-      const bool need_mask = (p.causal && q0 < k0 + ATTB_BKV) || (q0 + ATTB_BQ > p.S) || (k0 + ATTB_BKV > p.S) ||
-                             (q0 + ATTB_BQ > tmin_end);
-      // the 64 row statistics go to registers with a few vector loads BEFORE the wait: while the tensor pipe streams
-      // its operands out of shared memory, every further shared-memory read of this warp would queue behind them
-      if (pp.debug_flags & 64) {   // TEMP: no compute at all, only the barrier hand-shakes
-        PFB_PROF_WAIT(0, mbar_wait(&bar_s[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)); if (_fail) { ok = false; break; }
-        tc_fence_after(); tc_fence_before(); __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_p[st]);
-        PFB_PROF_WAIT(1, mbar_wait(&bar_dp[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)); if (_fail) { ok = false; break; }
-        tc_fence_after(); tc_fence_before(); __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_ds[st]);
-        continue;
-      }
-      float ls[ATTB_BQ];
+      const bool need_mask = (p.causal && q0 < k0 + ATTB_BKV) || (q0 + 32 > p.S) || (k0 + ATTB_BKV > p.S) || (q0 + 32 > tmin_end);
+      // the row statistics go to registers with a few vector loads before the wait: while the tensor pipe streams its
+      // operands out of shared memory, scalar shared-memory reads inside the loops below would queue behind them
+      float ls[32];
       #pragma unroll
-      for (int x = 0; x < ATTB_BQ; x += 4) {
+      for (int x = 0; x < 32; x += 4) {
         const float4 t4 = *reinterpret_cast<const float4*>(s_lse + x);
         ls[x] = t4.x; ls[x + 1] = t4.y; ls[x + 2] = t4.z; ls[x + 3] = t4.w;
       }
-      PFB_PROF_WAIT(0, mbar_wait(&bar_s[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)); if (_fail) { ok = false; break; }
+      if (!mbar_wait(&bar_s[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      float pv[ATTB_BQ];
-      long long _ta = clock64();
-      #pragma unroll
-      for (int c = 0; c < ATTB_BQ; c += 32) {
+      float pv[32];
+      {
         uint32_t v[32];
-        tmem_ld_32x32(tS + c, v);
+        tmem_ld_32x32(tS, v);
         tmem_ld_wait();
-        asm volatile("" :: "r"(v[0]), "r"(v[15]), "r"(v[31]) : "memory");
-        { long long _tb = clock64(); _prof[2] += _tb - _ta; _ta = _tb; }
         #pragma unroll
         for (int x = 0; x < 32; x += 2) {
-          float p0, p1;
-          if (pp.debug_flags & 4) {
-            p0 = __uint_as_float(v[x]) * p.scale_log2 - ls[c + x];
-            p1 = __uint_as_float(v[x + 1]) * p.scale_log2 - ls[c + x + 1];
-          } else {
-            p0 = fast_exp2(__uint_as_float(v[x]) * p.scale_log2 - ls[c + x]);
-            p1 = fast_exp2(__uint_as_float(v[x + 1]) * p.scale_log2 - ls[c + x + 1]);
-          }
-          if (need_mask && !(pp.debug_flags & 8)) {
-            const int qi = q0 + c + x;
+          float p0 = fast_exp2(__uint_as_float(v[x]) * p.scale_log2 - ls[x]);
+          float p1 = fast_exp2(__uint_as_float(v[x + 1]) * p.scale_log2 - ls[x + 1]);
+          if (need_mask) {
+            const int qi = q0 + x;
             const bool v0 = qi < p.S && kj < p.S && (!p.causal || kj <= qi) && qi < my_kend;
             const bool v1 = qi + 1 < p.S && kj < p.S && (!p.causal || kj <= qi + 1) && qi + 1 < my_kend;
             p0 = v0 ? p0 : 0.f; p1 = v1 ? p1 : 0.f;
           }
-          pv[c + x] = p0; pv[c + x + 1] = p1;
+          pv[x] = p0; pv[x + 1] = p1;
         }
-        { long long _tb = clock64(); _prof[3] += _tb - _ta; _ta = _tb; }
       }
-      // all 64 raw scores of this lane have been read: P^T (bf16) may overwrite columns 0-31
-      #pragma unroll
-      for (int c = 0; c < ATTB_BQ; c += 32) {
+      {
+        // the 32 raw scores of this thread have been read: P^T (bf16) overwrites the first 16 of their columns
         uint32_t pk[16];
         #pragma unroll
-        for (int x = 0; x < 32; x += 2) pk[x >> 1] = pack_bf16x2(pv[c + x], pv[c + x + 1]);
-        tmem_st_32x16(tS + (c >> 1), pk);
+        for (int x = 0; x < 32; x += 2) pk[x >> 1] = pack_bf16x2(pv[x], pv[x + 1]);
+        tmem_st_32x16(tS, pk);
       }
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_p[st]);
-      { long long _tb = clock64(); _prof[4] += _tb - _ta; _ta = _tb; }
       // dS^T = P^T * (dP^T - delta) * scale
       #pragma unroll
-      for (int x = 0; x < ATTB_BQ; x += 4) {
+      for (int x = 0; x < 32; x += 4) {
         const float4 t4 = *reinterpret_cast<const float4*>(s_delta + x);
         ls[x] = t4.x; ls[x + 1] = t4.y; ls[x + 2] = t4.z; ls[x + 3] = t4.w;
       }
-      PFB_PROF_WAIT(1, mbar_wait(&bar_dp[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)); if (_fail) { ok = false; break; }
+      if (!mbar_wait(&bar_dp[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      uint32_t dsk[ATTB_BQ / 2];
-      _ta = clock64();
-      #pragma unroll
-      for (int c = 0; c < ATTB_BQ; c += 32) {
+      uint32_t pk[16];
+      {
         uint32_t v[32];
-        tmem_ld_32x32(tdP + c, v);
+        tmem_ld_32x32(tdP, v);
         tmem_ld_wait();
-        asm volatile("" :: "r"(v[0]), "r"(v[15]), "r"(v[31]) : "memory");
-        { long long _tb = clock64(); _prof[5] += _tb - _ta; _ta = _tb; }
         #pragma unroll
         for (int x = 0; x < 32; x += 2) {
-          const float d0 = pv[c + x] * (__uint_as_float(v[x]) - ls[c + x]) * p.scale;
-          const float d1 = pv[c + x + 1] * (__uint_as_float(v[x + 1]) - ls[c + x + 1]) * p.scale;
-          dsk[(c + x) >> 1] = pack_bf16x2(d0, d1);
+          const float d0 = pv[x] * (__uint_as_float(v[x]) - ls[x]) * p.scale;
+          const float d1 = pv[x + 1] * (__uint_as_float(v[x + 1]) - ls[x + 1]) * p.scale;
+          pk[x >> 1] = pack_bf16x2(d0, d1);
         }
-        { long long _tb = clock64(); _prof[6] += _tb - _ta; _ta = _tb; }
       }
+      tmem_st_32x16(tS + 16, pk);       // dS^T: the last 16 of this thread's raw score columns
       uint8_t* rowp = smem + SM::DS_OFF + st * (ATTB_BKV * ATTB_BQ * 2) + r * 128;
       #pragma unroll
-      for (int c = 0; c < ATTB_BQ; c += 32) {
-        uint32_t pk[16];
-        #pragma unroll
-        for (int x = 0; x < 16; ++x) pk[x] = dsk[(c >> 1) + x];
-        tmem_st_32x16(tS + 96 + (c >> 1), pk);
-        #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = (c >> 3) + q4;
-          *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-        }
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const int chunk = half * 4 + q4;
+        *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
       }
       tmem_st_wait();
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_ds[st]);
-      { long long _tb = clock64(); _prof[7] += _tb - _ta; _ta = _tb; }
     }
-    if (pp.prof && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-      pp.prof[8] = _prof[0]; pp.prof[9] = _prof[1]; pp.prof[10] = clock64() - _tstart; for (int i = 2; i < 8; ++i) pp.prof[14 + i] = _prof[i];
-    }
-    // dK, dV: one key row per thread
+    // dK, dV: one key row per thread, the two halves take 64 head dims each
     if (ok && n_it > 0) ok = mbar_wait(bar_done, 0, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL);
     if (ok) {
       if (n_it > 0) tc_fence_after();
@@ -707,7 +654,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       __nv_bfloat16* dkp = p.dk + static_cast<long long>(row_base + kj) * p.dk_row_stride + kvh * ATT_D;
       __nv_bfloat16* dvp = p.dv + static_cast<long long>(row_base + kj) * p.dv_row_stride + kvh * ATT_D;
       #pragma unroll 1
-      for (int c = 0; c < ATT_D; c += 32) {
+      for (int c = half * 64; c < half * 64 + 64; c += 32) {
         uint32_t a[32], bb[32];
         if (n_it > 0) {
           tmem_ld_32x32(tdK + lane_off + c, a);
@@ -739,28 +686,27 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------ dQ warps (4-7): thread d owns head dim d of dQ^T
-    const int d = threadIdx.x - 128;
-    const uint32_t lane_off = static_cast<uint32_t>((warp - 4) * 32) << 16;
+    // ------------------------------------------------------------ dQ warps (8-11): thread d owns head dim d of dQ^T
+    const int d = threadIdx.x - 256;
+    const uint32_t lane_off = static_cast<uint32_t>((warp - 8) * 32) << 16;
     const bool leader = d == 0;
     bool ok = true;
-    long long _prof[8] = {0, 0, 0, 0, 0, 0, 0, 0}; bool _fail = false; const long long _tstart = clock64();
     for (int it = 0; it < n_it && ok; ++it) {
       const int st = it & 1;
       const uint32_t ph2 = (it >> 1) & 1;
       const int g = it / n_q, i = i_lo + (it - g * n_q);
       const int q0 = i * ATTB_BQ;
-      PFB_PROF_WAIT(0, mbar_wait(&bar_dq[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)); if (_fail) break;
+      if (!mbar_wait(&bar_dq[st], ph2, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       uint32_t dq0[32], dq1[32];
-      tmem_ld_32x32(tmem_base + st * 128 + 32 + lane_off, dq0);
-      tmem_ld_32x32(tmem_base + st * 128 + 64 + lane_off, dq1);
+      tmem_ld_32x32(tmem_base + st * 128 + 64 + lane_off, dq0);
+      tmem_ld_32x32(tmem_base + st * 128 + 96 + lane_off, dq1);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&dq_read[st]);
       int my_turn = 0;
-      if (pp.deterministic && warp == 4) {
+      if (pp.deterministic && warp == 8) {
         // contributors of this query tile are taken in descending key-tile order: count those above this CTA's tile
         const int j_top = p.causal ? min(kv_tiles - 1, (q0 + ATTB_BQ - 1) / ATTB_BKV) : kv_tiles - 1;
         int cnt = 0;
@@ -776,10 +722,8 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (leader) tma_store_wait_read<0>();
         named_bar_sync(1, 128);
         const uint32_t* src = half == 0 ? dq0 : dq1;
-        if (!(pp.debug_flags & 2)) {
         #pragma unroll
         for (int x = 0; x < 32; ++x) sDQ[x * ATT_D + d] = __uint_as_float(src[x]);
-        }
         fence_proxy_async_smem();
         named_bar_sync(1, 128);
         if (leader) {
@@ -792,7 +736,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             __threadfence();
           }
-          if (ok && !(pp.debug_flags & 1)) {
+          if (ok) {
             tma_reduce_add_3d(&tmdQ, sDQ, 0, head0 + g, row_base + q0 + half * 32);
             tma_store_commit();
             if (pp.deterministic && half == 1) {
@@ -807,12 +751,11 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = ok && !*abort_flag;
     }
     if (leader) tma_store_wait<0>();
-    if (pp.prof && leader && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { pp.prof[12] = _prof[0]; pp.prof[13] = clock64() - _tstart; }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == 13) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 // delta[b, h, s] = sum_d dO * O ; one warp per (token, head).

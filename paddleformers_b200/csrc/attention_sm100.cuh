@@ -461,7 +461,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&v[32 * c]));
       tmem_ld_wait();
-      float mx = -INFINITY;
+      // four independent running maxima (and sums below): one serial chain over 128 values would leave this warp
+      // waiting on its own ALU latency most of the time
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
         #pragma unroll
         for (int i = 0; i < 128; ++i) {
@@ -470,12 +472,13 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (need_kend) vis = vis && qi < s_kend[i];
           const float x = vis ? __uint_as_float(v[i]) : -INFINITY;
           v[i] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
+          mx4[i & 3] = fmaxf(mx4[i & 3], x);
         }
       } else {
         #pragma unroll
-        for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        for (int i = 0; i < 128; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       // lazy rescale: keep the old reference maximum unless some row of this warp has outgrown it by 2^8
       const bool grow = m_new > m_used + AF2_RESCALE_LOG2 || (m_used == -INFINITY && m_new != -INFINITY);
@@ -500,7 +503,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         m_used = m_new;
       }
       const float m_sub = m_used == -INFINITY ? 0.f : m_used;
-      float lt = 0.f;
+      float lt4[4] = {0.f, 0.f, 0.f, 0.f};
       #pragma unroll
       for (int c = 0; c < 128; c += 32) {
         uint32_t pk[16];
@@ -508,11 +511,12 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < 32; i += 2) {
           const float p0 = fast_exp2(__uint_as_float(v[c + i]) * p.scale_log2 - m_sub);     // masked: exp2(-inf) = 0
           const float p1 = fast_exp2(__uint_as_float(v[c + i + 1]) * p.scale_log2 - m_sub);
-          lt += p0 + p1;
+          lt4[(i >> 1) & 3] += p0 + p1;
           pk[i >> 1] = pack_bf16x2(p0, p1);
         }
         tmem_st_32x16(tS + (c >> 1), pk);
       }
+      const float lt = (lt4[0] + lt4[1]) + (lt4[2] + lt4[3]);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();

@@ -56,36 +56,27 @@ static int pick_bn(int M, int N, bool swiglu, int ctas) {
   return cost(128) * 3 < cost(256) * 2 ? 128 : 256;   // 256-wide tiles measured 1.4-1.5x the rate of 128-wide ones
 }
 
-// out[T, N] (SwiGLU: [T, N/2]) = gather(x_local)[T, K] @ B^T with B = weight [N, K] or (b_mn) [K, N]. x_local holds this
-// rank's R = T / tp rows; G is this rank's symmetric gathered buffer (every rank's rows end up in it, this rank's own
-// included, written by the kernel's push CTAs); blk counters are a symmetric int32 array [T / 128] per rank.
-void ag_gemm(const at::Tensor& x_local, const at::Tensor& G, const at::Tensor& peer_G_ptrs, const at::Tensor& weight, at::Tensor& out,
-             const c10::optional<at::Tensor>& out2, int64_t epi, bool b_mn, const at::Tensor& peer_blk_ptrs,
-             const at::Tensor& epoch, int64_t rank, int64_t tp, int64_t n_copy) {
+// out[T, N] (SwiGLU: [T, N/2]) = gather(G)[T, K] @ B^T with B = weight [N, K] or (b_mn) [K, N]. G is this rank's
+// symmetric gathered buffer whose own slice (rows rank*R .. +R) has already been written on the current stream.
+void ag_gemm(const at::Tensor& G, const at::Tensor& peer_G_ptrs, const at::Tensor& weight, at::Tensor& out,
+             const c10::optional<at::Tensor>& out2, int64_t epi, bool b_mn, int64_t ready_ptr,
+             const at::Tensor& peer_ready_ptrs, at::Tensor& blk_flags, const at::Tensor& epoch, int64_t rank, int64_t tp, int64_t n_copy) {
   TORCH_CHECK(G.is_cuda() && G.dim() == 2 && G.is_contiguous() && G.scalar_type() == at::kBFloat16);
-  TORCH_CHECK(x_local.is_cuda() && x_local.dim() == 2 && x_local.is_contiguous() && x_local.scalar_type() == at::kBFloat16);
   TORCH_CHECK(weight.scalar_type() == at::kBFloat16 && weight.dim() == 2 && weight.stride(1) == 1);
-  TORCH_CHECK(tp >= 2 && tp <= COMM_MAX_RANKS && peer_G_ptrs.numel() == tp && peer_blk_ptrs.numel() == tp);
-  TORCH_CHECK(!peer_G_ptrs.is_cuda() && !peer_blk_ptrs.is_cuda() && peer_G_ptrs.scalar_type() == at::kLong);
+  TORCH_CHECK(tp >= 2 && tp <= COMM_MAX_RANKS && peer_G_ptrs.numel() == tp && peer_ready_ptrs.numel() == tp);
+  TORCH_CHECK(!peer_G_ptrs.is_cuda() && !peer_ready_ptrs.is_cuda() && peer_G_ptrs.scalar_type() == at::kLong);
   const c10::cuda::CUDAGuard guard(G.device());
   const int T = G.size(0), K = G.size(1);
   TORCH_CHECK(T % (tp * GEMM_BM) == 0, "ag_gemm: tokens must be a multiple of tp * 128");
   TORCH_CHECK(K % 128 == 0, "ag_gemm: K must be a multiple of 128");
-  TORCH_CHECK(x_local.size(0) == T / tp && x_local.size(1) == K, "ag_gemm: x_local must be [T / tp, K]");
-  TORCH_CHECK((reinterpret_cast<uintptr_t>(x_local.data_ptr()) & 15) == 0);
   const int Kb = b_mn ? weight.size(0) : weight.size(1);
   const int N = b_mn ? weight.size(1) : weight.size(0);
   TORCH_CHECK(K == Kb);
   const bool swiglu = epi == EPI_SWIGLU_BF16;
   TORCH_CHECK(epi == EPI_STORE_BF16 || swiglu);
   TORCH_CHECK(out.size(0) == T && out.size(1) == (swiglu ? N / 2 : N) && out.stride(1) == 1 && out.scalar_type() == at::kBFloat16);
-  const int blocks_per_rank = T / tp / GEMM_BM;
-  int ncopy = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(n_copy, 32)));
-  // a 128-row block is pushed in `parts` pieces so that every push CTA has work; a piece is a whole number of 32 KB chunks
-  int parts = 1;
-  while (parts * 2 * blocks_per_rank <= ncopy && (GEMM_BM / (parts * 2)) * static_cast<long long>(K) * 2 % COPY_CHUNK == 0 && parts < 8)
-    parts *= 2;
-  ncopy = std::min(ncopy, blocks_per_rank * parts);
+  TORCH_CHECK(blk_flags.scalar_type() == at::kInt && blk_flags.numel() >= T / GEMM_BM && blk_flags.is_cuda());
+  const int ncopy = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(n_copy, 32)));
   const int gemm_ctas = sms() - ncopy;
   const int BN = pick_bn(T, N, swiglu, gemm_ctas);
   GemmParams p;
@@ -96,19 +87,18 @@ void ag_gemm(const at::Tensor& x_local, const at::Tensor& G, const at::Tensor& p
   p.m_blocks = T / GEMM_BM;
   p.n_blocks = swiglu ? (N / 2 + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
   p.k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
-  p.group_m = static_cast<int>(tp);    // one rasterisation group = the same block index of every source rank
+  p.group_m = 4;
   p.block_expert = nullptr; p.n_per_expert = 0; p.expert_rows = nullptr; p.tiles_per_expert = 0; p.d_expert_stride = 0;
   p.status = status_word();
   CommParams c{};
   c.mode = MODE_AG; c.rank = rank; c.tp = tp; c.rows_per_rank = T / tp; c.epoch_ptr = epoch.data_ptr<int>(); c.n_copy_ctas = ncopy;
   for (int q = 0; q < tp; ++q) {
-    c.peer_G[q] = reinterpret_cast<__nv_bfloat16*>(peer_G_ptrs.data_ptr<int64_t>()[q]);
-    c.peer_blk[q] = reinterpret_cast<int*>(peer_blk_ptrs.data_ptr<int64_t>()[q]);
+    c.peer_G[q] = reinterpret_cast<const __nv_bfloat16*>(peer_G_ptrs.data_ptr<int64_t>()[q]);
+    c.peer_ready[q] = reinterpret_cast<int*>(peer_ready_ptrs.data_ptr<int64_t>()[q]);
   }
-  TORCH_CHECK(reinterpret_cast<void*>(c.peer_G[rank]) == G.data_ptr(), "ag_gemm: peer_G_ptrs[rank] must be G");
-  c.src = reinterpret_cast<const __nv_bfloat16*>(x_local.data_ptr());
-  c.blk_cnt = c.peer_blk[rank];
-  c.blk_parts = parts;
+  c.G = reinterpret_cast<__nv_bfloat16*>(G.data_ptr());
+  c.ready = reinterpret_cast<int*>(ready_ptr);
+  c.blk_flags = blk_flags.data_ptr<int>();
   c.row_bytes = static_cast<long long>(K) * 2;
   const uint32_t b_box_rows = swiglu ? BN / 2 : BN;
   CUtensorMap tmA = make_tma_2d(G.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, K, K, GEMM_BM, 64);
@@ -167,8 +157,8 @@ void gemm_rs(const at::Tensor& x, const at::Tensor& weight, bool b_mn, const at:
 }  // namespace pfb
 
 TORCH_LIBRARY_FRAGMENT(pfb200, m) {
-  m.def("ag_gemm(Tensor x_local, Tensor(b!) G, Tensor peer_G_ptrs, Tensor weight, Tensor(a!) out, Tensor? out2, int epi, bool b_mn, "
-        "Tensor peer_blk_ptrs, Tensor epoch, int rank, int tp, int n_copy) -> ()", &pfb::ag_gemm);
+  m.def("ag_gemm(Tensor G, Tensor peer_G_ptrs, Tensor weight, Tensor(a!) out, Tensor? out2, int epi, bool b_mn, int ready_ptr, "
+        "Tensor peer_ready_ptrs, Tensor(b!) blk_flags, Tensor epoch, int rank, int tp, int n_copy) -> ()", &pfb::ag_gemm);
   m.def("gemm_rs(Tensor x, Tensor weight, bool b_mn, Tensor peer_stage_ptrs, Tensor peer_count_ptrs, Tensor(a!) out, Tensor epoch, "
         "int rank, int tp) -> ()", &pfb::gemm_rs);
 }

@@ -1,18 +1,15 @@
 // Tensor-parallel GEMMs fused with their collective over NVLink peer memory (sm_100a).
 //
 //   MODE_AG  (all-gather -> GEMM, column-parallel linear with sequence-parallel input):
-//     every rank owns R rows of the activation A[T, K]; the gathered A lives in a symmetric buffer G on every rank. A few
-//     "push" CTAs read this rank's rows once (bulk copy global -> shared) and store each chunk into the G of EVERY rank,
-//     its own included (bulk copies shared -> peer global over NVLink, no multicast). Stores are posted: nothing waits
-//     for a round trip and a rank's rows start travelling the moment its kernel starts, whether or not the receiver
-//     has launched yet. When a 128-row block (or a part of it) is complete everywhere the push CTA bumps that block's
-//     arrival counter on every rank (release, system scope). The GEMM CTAs walk the row blocks in arrival order
-//     (block 0 of every source, then block 1, ...) and their TMA producer waits for a block's counter before loading
-//     it, so the transfer of later blocks overlaps the tensor-core work on earlier ones. The gathered A stays in G for
-//     the weight-gradient GEMM of the backward pass.
-//     Writing into a peer's G is safe when that peer has finished reading what G held before. Callers guarantee it by
-//     ordering: every reader of G is launched before the rank's next fused call on the same stream, and a fused call
-//     completes only after every peer has started the same call.
+//     every rank owns R rows of the activation A[T, K] inside a symmetric buffer G. A few "copy" CTAs pull the other
+//     ranks' row blocks into the local G with bulk async copies (cp.async.bulk, no multicast) staged through a ring in
+//     shared memory (192 KB in flight per CTA, which is what it takes to cover the link latency) and publish one flag
+//     per 128-row block; the GEMM CTAs walk the row blocks starting with the local ones and their TMA producer waits
+//     for the flag of a block before loading it, so the transfer of block i+1 overlaps the tensor-core work on block i.
+//     The gathered A stays in G for the weight-gradient GEMM of the backward pass. (A variant in which every rank
+//     pushed its rows into all peers' buffers, with bulk stores or with plain vector stores from the copy CTAs,
+//     measured 1.5-2.5x slower on two GPUs: a handful of CTAs keeps too few posted bytes in flight, and every
+//     completion wait before a flag costs a link round trip.)
 //
 //   MODE_RS  (GEMM -> reduce-scatter, row-parallel linear with sequence-parallel output):
 //     the epilogue writes each bf16 partial tile straight into the owner rank's staging slot [src_rank][R][N] with
@@ -37,11 +34,11 @@ struct CommParams {
                          // the launch, so that a captured CUDA graph advances it on every replay)
   int n_copy_ctas;
   // AG
-  __nv_bfloat16* peer_G[COMM_MAX_RANKS];        // every rank's gathered buffer [T, K]
-  const __nv_bfloat16* src;                      // this rank's rows [R, K], contiguous
-  int* peer_blk[COMM_MAX_RANKS];                 // arrival counters [m_blocks] at every rank
-  int* blk_cnt;                                  // local ones
-  int blk_parts;                                 // pieces a 128-row block is pushed in (counter target = epoch * parts)
+  const __nv_bfloat16* peer_G[COMM_MAX_RANKS];  // every rank's gathered buffer [T, K]
+  __nv_bfloat16* G;                              // local one
+  int* peer_ready[COMM_MAX_RANKS];               // ready pads [tp] at every rank (slot = source rank)
+  int* ready;                                    // local ready pad
+  int* blk_flags;                                // local [m_blocks]
   long long row_bytes;                           // K * 2
   // RS
   __nv_bfloat16* peer_stage[COMM_MAX_RANKS];     // staging [tp][R][N] at every rank
@@ -104,6 +101,7 @@ __device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uin
 
 constexpr int COPY_CHUNK = 32768;  // bytes per bulk copy
 constexpr int COPY_STAGES = 6;
+constexpr int COPY_AHEAD = 5;        // loads in flight per copy CTA (160 KB)
 
 struct StageMaps { CUtensorMap m[COMM_MAX_RANKS]; };  // RS: one store map per owner rank's staging buffer [tp*R, N]
 constexpr int RS_STAGING_BYTES = 4 * 2 * 4096;      // per epilogue warp: two 32-row x 128-byte slabs
@@ -143,54 +141,57 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int epoch = *c.epoch_ptr;
 
   if (is_copy_cta) {
-    // ------------------------------------------------------------------ all-gather push CTAs
+    // ------------------------------------------------------------------ all-gather copy CTAs
     if (threadIdx.x == 0) {
-      constexpr int LOOKAHEAD = 3;   // loads in flight ahead of the stores; COPY_STAGES - LOOKAHEAD - 1 store groups may
-                                     // still be reading shared memory when a slot is reused (see wait_read below)
-      const int part_rows = GEMM_BM / c.blk_parts;
-      const long long part_bytes = static_cast<long long>(part_rows) * c.row_bytes;
-      const int chunks = static_cast<int>(part_bytes / COPY_CHUNK);   // part_bytes % 32 KB == 0 (checked by the host)
-      const int items = blocks_per_rank * c.blk_parts;
-      int lslot = 0, sslot = 0;
-      uint32_t sphase = 0;
+      if (blockIdx.x == 0) {
+        // this rank's own slice of G was written by earlier work on this stream: tell everyone
+        __threadfence_system();
+        for (int q = 0; q < c.tp; ++q) st_release_sys_i32(c.peer_ready[q] + c.rank, epoch);
+      }
+      const long long blk_bytes = static_cast<long long>(GEMM_BM) * c.row_bytes;
+      const int chunks_per_blk = static_cast<int>(blk_bytes / COPY_CHUNK);  // row_bytes*128 is a multiple of 32 KB for K % 128 == 0
+      int issue_stage = 0, done_stage = 0;
+      uint32_t done_phase = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < items && ok; item += c.n_copy_ctas) {
-        const int blk = item / c.blk_parts, part = item - blk * c.blk_parts;
-        const long long src_off = (static_cast<long long>(blk) * GEMM_BM + part * part_rows) * c.row_bytes;
-        const long long dst_off = static_cast<long long>(c.rank) * c.rows_per_rank * c.row_bytes + src_off;
-        const uint8_t* gsrc = reinterpret_cast<const uint8_t*>(c.src) + src_off;
-        for (int i = 0; i < chunks + LOOKAHEAD && ok; ++i) {
-          if (i < chunks) {
-            // the slot's previous occupant was stored COPY_STAGES chunks ago: all but the newest
-            // COPY_STAGES - LOOKAHEAD - 1 store groups have been read out of shared memory after this wait
-            tma_store_wait_read<COPY_STAGES - LOOKAHEAD - 1>();
-            mbar_expect_tx(&copy_bar[lslot], COPY_CHUNK);
-            bulk_load(smem + lslot * COPY_CHUNK, gsrc + static_cast<long long>(i) * COPY_CHUNK, COPY_CHUNK, &copy_bar[lslot]);
-            if (++lslot == COPY_STAGES) lslot = 0;
-          }
-          if (i >= LOOKAHEAD) {
-            const int ch = i - LOOKAHEAD;
-            if (!mbar_wait(&copy_bar[sslot], sphase, abort_flag, p.status, PFB_ERR_WAIT_FULL)) { ok = false; break; }
-            for (int d = 1; d <= c.tp; ++d) {      // peers first, this rank's own copy last
-              const int q = (c.rank + d) % c.tp;
-              bulk_store(reinterpret_cast<uint8_t*>(c.peer_G[q]) + dst_off + static_cast<long long>(ch) * COPY_CHUNK,
-                         smem + sslot * COPY_CHUNK, COPY_CHUNK);
+      int item = 0;
+      for (int d = 1; d < c.tp && ok; ++d) {
+        const int src = (c.rank + d) % c.tp;
+        for (int b = 0; b < blocks_per_rank && ok; ++b, ++item) {
+          if (item % c.n_copy_ctas != static_cast<int>(blockIdx.x)) continue;
+          if (!wait_flag_ge<true>(c.ready + src, epoch, abort_flag, p.status)) { ok = false; break; }
+          const int mb = src * blocks_per_rank + b;
+          const uint8_t* gsrc = reinterpret_cast<const uint8_t*>(c.peer_G[src]) + mb * blk_bytes;
+          uint8_t* gdst = reinterpret_cast<uint8_t*>(c.G) + mb * blk_bytes;
+          int issued = 0, stored = 0;
+          while (stored < chunks_per_blk && ok) {
+            // keep up to COPY_AHEAD loads in flight. The slot of load n held chunk n - COPY_STAGES; at least
+            // n - COPY_AHEAD + 1 stores have been committed by now, so that chunk's store is followed by at most
+            // COPY_STAGES - COPY_AHEAD newer ones: waiting until no more than that many are still reading frees it
+            while (issued < chunks_per_blk && issued - stored < COPY_AHEAD) {
+              tma_store_wait_read<COPY_STAGES - COPY_AHEAD>();
+              mbar_expect_tx(&copy_bar[issue_stage], COPY_CHUNK);
+              bulk_load(smem + issue_stage * COPY_CHUNK, gsrc + static_cast<long long>(issued) * COPY_CHUNK, COPY_CHUNK,
+                        &copy_bar[issue_stage]);
+              issue_stage = (issue_stage + 1) % COPY_STAGES;
+              ++issued;
             }
+            if (!mbar_wait(&copy_bar[done_stage], done_phase, abort_flag, p.status, PFB_ERR_WAIT_PEER)) { ok = false; break; }
+            bulk_store(gdst + static_cast<long long>(stored) * COPY_CHUNK, smem + done_stage * COPY_CHUNK, COPY_CHUNK);
             tma_store_commit();
-            if (++sslot == COPY_STAGES) { sslot = 0; sphase ^= 1; }
+            if (++done_stage == COPY_STAGES) { done_stage = 0; done_phase ^= 1; }
+            ++stored;
           }
-        }
-        if (ok) {
-          tma_store_wait<0>();          // this part has landed everywhere
-          fence_proxy_async_all();
-          __threadfence_system();
-          const int mb = c.rank * blocks_per_rank + blk;
-          for (int d = 1; d <= c.tp; ++d) red_release_sys_add(c.peer_blk[(c.rank + d) % c.tp] + mb, 1);
+          if (ok) {
+            tma_store_wait<0>();          // the block is in local memory
+            fence_proxy_async_all();
+            __threadfence();
+            st_release_gpu_i32(c.blk_flags + mb, epoch);
+          }
         }
       }
       tma_store_wait<0>();
     }
-    return;  // push CTAs allocate no TMEM
+    return;  // copy CTAs allocate no TMEM
   }
 
   const uint32_t tmem_base = *tmem_slot;
@@ -199,21 +200,15 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int my_cta = blockIdx.x - first_cta;
   const int num_tiles = p.m_blocks * p.n_blocks;
   const int tiles_per_group = p.group_m * p.n_blocks;
-  // RS starts with the next rank's rows (own rows last); AG takes the row blocks in arrival order (below)
-  const int m_shift = ((c.rank + 1) % c.tp) * blocks_per_rank;
+  // AG walks row blocks starting at this rank's own rows; RS starts with the next rank's rows (own rows last)
+  const int m_shift = (MODE == MODE_AG ? c.rank : (c.rank + 1) % c.tp) * blocks_per_rank;
 
   auto tile_coords = [&](int t, int& mb, int& nb) {
     int g = t / tiles_per_group;
     int r = t - g * tiles_per_group;
     int gsz = min(p.group_m, p.m_blocks - g * p.group_m);
     int mlog = g * p.group_m + (r % gsz);
-    if constexpr (MODE == MODE_AG) {
-      // block b of every source (this rank first), then block b + 1, ...: the order in which the pushes complete
-      const int bb = mlog / c.tp, sidx = mlog - bb * c.tp;
-      mb = ((c.rank + sidx) % c.tp) * blocks_per_rank + bb;
-    } else {
-      mb = (mlog + m_shift) % p.m_blocks;
-    }
+    mb = (mlog + m_shift) % p.m_blocks;
     nb = r / gsz;
   };
 
@@ -224,9 +219,10 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int t = my_cta; t < num_tiles && ok; t += n_ctas) {
         int mb, nb; tile_coords(t, mb, nb);
         if constexpr (MODE == MODE_AG) {
-          // written by a push CTA of the source rank (generic proxy at the peer -> async proxy here)
-          if (!wait_flag_ge<true>(c.blk_cnt + mb, epoch * c.blk_parts, abort_flag, p.status)) break;
-          fence_proxy_async_all();
+          if (mb / blocks_per_rank != c.rank) {
+            if (!wait_flag_ge<false>(c.blk_flags + mb, epoch, abort_flag, p.status)) break;
+            fence_proxy_async_all();
+          }
         }
         const int b_row0 = nb * BN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {

@@ -8,8 +8,7 @@ A/B baseline (``PFB_FUSED_TP=0``).
 
 Buffers (all symmetric, carved from ``SymmetricArena`` chunks so that one handle exchange serves many layers):
 
-* per column-parallel layer: gathered input G [T, K] (doubles as the saved activation) and its per-block arrival
-  counters, which the peers' push CTAs bump;
+* per column-parallel layer: gathered input G [T, K] (doubles as the saved activation), a ready pad [tp], block flags;
 * per tensor-parallel group and shape: two reduce-scatter staging buffers [tp, T/tp, N] with their counters, and two
   gathered-gradient buffers for the backward all-gather, used alternately (a rank can never be two fused calls ahead
   of a peer, because finishing a call needs every peer's signal of that call).
@@ -81,12 +80,13 @@ class TPWorkspace:
         self.arena = SymmetricArena(self.group)
         self._rs: Dict[Tuple[int, int], dict] = {}
         self._bwd_ag: Dict[Tuple[int, int], dict] = {}
-        # push CTAs of the all-gather (each keeps three 32 KB chunks in flight towards every rank)
+        # copy CTAs of the all-gather (each keeps five 32 KB chunks in flight)
         self.n_copy_ctas = int(os.environ.get("PFB_AG_COPY_CTAS", "16" if self.tp >= 8 else "8"))
 
     def layer_gather_buffers(self, T: int, K: int) -> dict:
         """Persistent buffers of one column-parallel layer."""
-        return {"G": _Region(self.arena, (T, K), torch.bfloat16), "blk": _Region(self.arena, (max(T // 128, 8),), torch.int32),
+        return {"G": _Region(self.arena, (T, K), torch.bfloat16), "ready": _Region(self.arena, (max(self.tp, 8),), torch.int32),
+                "blk": torch.zeros(T // 128, dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device())),
                 "epoch": torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()))}
 
     def rs_buffers(self, T: int, N: int) -> dict:
@@ -143,14 +143,16 @@ def release_workspaces() -> None:
 def _ag_gemm(ws: TPWorkspace, bufs: dict, x_local, weight, b_mn: bool, swiglu: bool):
     G = bufs["G"].tensor
     T, K = G.shape
+    R = T // ws.tp
+    G[ws.rank * R:(ws.rank + 1) * R].copy_(x_local)
     bufs["epoch"].add_(1)   # device-side counter: a captured graph advances it on every replay
     STATS["ag_gemm"] += 1
     N = weight.shape[1] if b_mn else weight.shape[0]
     out = torch.empty((T, N // 2 if swiglu else N), dtype=torch.bfloat16, device=x_local.device)
     raw = torch.empty((T, N), dtype=torch.bfloat16, device=x_local.device) if swiglu else None
-    torch.ops.pfb200.ag_gemm(x_local.contiguous(), G, bufs["G"].peer_ptrs, weight, out, raw,
-                             F.EPI_SWIGLU_BF16 if swiglu else F.EPI_STORE_BF16, b_mn, bufs["blk"].peer_ptrs, bufs["epoch"], ws.rank,
-                             ws.tp, ws.n_copy_ctas)
+    torch.ops.pfb200.ag_gemm(G, bufs["G"].peer_ptrs, weight, out, raw, F.EPI_SWIGLU_BF16 if swiglu else F.EPI_STORE_BF16, b_mn,
+                             bufs["ready"].local_ptr, bufs["ready"].peer_ptrs, bufs["blk"], bufs["epoch"], ws.rank, ws.tp,
+                             ws.n_copy_ctas)
     return out, raw, G
 
 
