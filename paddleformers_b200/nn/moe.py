@@ -16,6 +16,7 @@ Behaviour follows the reference's gates and layers:
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -38,6 +39,39 @@ class AddAuxiliaryLoss(torch.autograd.Function):
     def backward(ctx, g):
         (aux,) = ctx.saved_tensors
         return g, torch.ones_like(aux)
+
+
+class _FusedRouteFn(torch.autograd.Function):
+    """Scores, top-k, combine weights, per-expert counts, stable ranks and balance loss in two kernel launches
+    (``csrc/moe_route.cu``); the backward pass recomputes the scores and returns d(logits) in one launch."""
+
+    @staticmethod
+    def forward(ctx, logits, sel_bias, k, sigmoid, n_group, topk_group, group_top2, norm_topk, scale, aux_coef, usage):
+        T, E = logits.shape
+        prob_sums = torch.zeros(E, dtype=torch.float32, device=logits.device) if aux_coef > 0 else None
+        idx, w, rank, counts = torch.ops.pfb200.moe_route_fwd(logits, sel_bias, k, sigmoid, n_group, topk_group, group_top2,
+                                                              norm_topk, scale, prob_sums, usage)
+        aux = logits.new_zeros(())
+        frac = None
+        if aux_coef > 0:
+            frac = counts.float() / max(T, 1)
+            aux = aux_coef * E * (frac * (prob_sums / max(T, 1))).sum()
+        ctx.save_for_backward(logits, idx, frac if frac is not None else logits.new_zeros(0))
+        ctx.cfg = (sigmoid, norm_topk, scale, aux_coef, T, E)
+        ctx.mark_non_differentiable(idx, rank, counts)
+        return idx, w, aux, rank, counts
+
+    @staticmethod
+    def backward(ctx, d_idx, dw, daux, d_rank, d_counts):
+        logits, idx, frac = ctx.saved_tensors
+        sigmoid, norm_topk, scale, aux_coef, T, E = ctx.cfg
+        aux_vec = None
+        if aux_coef > 0 and daux is not None:
+            aux_vec = (daux.float() * (aux_coef * E / max(T, 1))) * frac
+        if dw is None:
+            dw = torch.zeros(idx.shape, dtype=torch.float32, device=logits.device)
+        dlogits = torch.ops.pfb200.moe_route_bwd(logits, None, idx, dw.float().contiguous(), aux_vec, sigmoid, norm_topk, scale)
+        return (dlogits,) + (None,) * 10
 
 
 class TopkRouter(nn.Module):
@@ -98,9 +132,35 @@ class TopkRouter(nn.Module):
             self.e_score_correction_bias = None
         self.register_buffer("expert_usage", torch.zeros(self.num_experts, dtype=torch.int64, device=device), persistent=False)
 
+    def _fused_ok(self, logits: torch.Tensor) -> bool:
+        """The routing kernel covers softmax / sigmoid scores with plain, group-limited or bias-corrected top-k and the
+        batch-level balance loss; capacity dropping, per-sequence balance, z-loss and the biased / logit-scored routers
+        stay on the tensor-operation path below."""
+        E = self.num_experts
+        if not (logits.is_cuda and os.environ.get("PFB_FUSED_ROUTER", "1") != "0" and F.use_cuda_kernels(logits)
+                and hasattr(torch.ops.pfb200, "moe_route_fwd")):
+            return False
+        if self.scoring not in ("softmax", "sigmoid") or self.bias is not None or self.force_balance or self.capacity_factor > 0:
+            return False
+        if self.z_coef > 0 or self.balance_type not in ("aux_loss", "none") or E % 32 != 0 or E > 256 or self.top_k > 32:
+            return False
+        if self.n_group > 1 and ((E // 32) % self.n_group != 0 or self.topk_group > self.n_group):
+            return False
+        return True
+
     def forward(self, x2d: torch.Tensor):
         """x2d: [T, H] -> (topk_idx [T,k] int64, topk_weight [T,k] fp32, aux_loss scalar or None)."""
         logits = F.router_logits(x2d, self.weight)
+        self.last_plan = None
+        if self._fused_ok(logits):
+            want_aux = self.training and self.aux_coef > 0 and self.balance_type != "none"
+            idx, w, aux, rank, counts = _FusedRouteFn.apply(
+                logits.contiguous(), self.e_score_correction_bias, self.top_k, self.scoring == "sigmoid", self.n_group,
+                self.topk_group, self.method == "noaux_tc", bool(self.norm_topk_prob and self.top_k > 1), self.scale,
+                self.aux_coef if want_aux else 0.0, self.expert_usage)
+            # the dispatcher reuses the kernel's per-expert counts and stable ranks instead of sorting the pairs again
+            self.last_plan = {"idx": idx, "rank_in_expert": rank, "counts": counts}
+            return idx, w, (aux if want_aux else None)
         if self.bias is not None:
             logits = logits + self.bias
         if self.scoring == "sigmoid_topk_logits":        # Llama 4: experts by logit, weight = sigmoid of the selected logit

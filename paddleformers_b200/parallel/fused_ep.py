@@ -96,20 +96,24 @@ def get_workspace(ps, x2d, layer):
     return _WS[key]
 
 
-def make_plan(ws: EPWorkspace, idx: torch.Tensor) -> dict:
+def make_plan(ws: EPWorkspace, idx: torch.Tensor, routed: dict = None) -> dict:
     """Device-side bookkeeping of one exchange: per-expert pair counts and every pair's rank inside its expert (stable
-    in pair order), with no host read."""
+    in pair order), with no host read. ``routed`` is what the routing kernel already produced for these indices
+    (``TopkRouter.last_plan``); without it the ranks come from a stable sort."""
     from ..nn.moe import count_ids
 
     E = ws.ep * ws.EL
     flat = idx.reshape(-1).contiguous()
-    counts = count_ids(flat, E)
-    order = torch.argsort(flat, stable=True)
-    first = torch.cumsum(counts, 0) - counts
-    rank_sorted = torch.arange(flat.numel(), device=flat.device) - first[flat[order]]
-    rank_in_expert = torch.empty_like(rank_sorted)
-    rank_in_expert[order] = rank_sorted
     dev = flat.device
+    if routed is not None and routed.get("idx") is idx and routed["counts"].numel() == E:
+        counts, rank_in_expert = routed["counts"], routed["rank_in_expert"]
+    else:
+        counts = count_ids(flat, E)
+        order = torch.argsort(flat, stable=True)
+        first = torch.cumsum(counts, 0) - counts
+        rank_sorted = torch.arange(flat.numel(), device=flat.device) - first[flat[order]]
+        rank_in_expert = torch.empty_like(rank_sorted)
+        rank_in_expert[order] = rank_sorted
     return {"idx": flat, "counts": counts.to(torch.int32), "rank_in_expert": rank_in_expert.to(torch.int32),
             "pair_slot": torch.empty(flat.numel(), dtype=torch.int32, device=dev),
             "block_expert": torch.empty(ws.cap // 128, dtype=torch.int32, device=dev),
@@ -174,7 +178,7 @@ def moe_forward(ws: EPWorkspace, layer, x2d, idx, w):
     if bufs is None or bufs["x_recv"].tensor.shape != (ws.cap, ws.H):
         bufs = ws.layer_buffers()
         layer._ep_bufs = bufs
-    plan = make_plan(ws, idx)
+    plan = make_plan(ws, idx, getattr(layer.gate, "last_plan", None))
     ws.fwd_epoch.add_(1)
     torch.ops.pfb200.ep_exchange(ws.table.peer_ptrs, plan["counts"], plan["block_expert"], plan["expert_rows"], ws.total_rows,
                                  ws.rank, ws.ep, ws.EL, ws.fwd_epoch)
