@@ -54,6 +54,128 @@ struct GemmSmem {
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
 };
 
+// Epilogue of one accumulator tile: the calling thread owns TMEM lane (row) `row` of a 128 x BN fp32 tile at `taddr`
+// and writes / accumulates its BN columns into D (see GemmEpilogue). Shared by the one-CTA and the CTA-pair kernels.
+template <int BN, int EPI>
+__device__ __forceinline__ void gemm_store_tile(uint32_t taddr, int row, int nb, const GemmParams& p, long long d_off) {
+  if constexpr (EPI == EPI_SWIGLU_BF16) {
+    // tile columns [0,BN/2) hold gate, [BN/2,BN) hold up for output columns nb*BN/2 ...
+    __nv_bfloat16* Dp = reinterpret_cast<__nv_bfloat16*>(p.D);
+    const int n_out = p.N / 2;
+    #pragma unroll 1
+    for (int c = 0; c < BN / 2; c += 32) {
+      uint32_t g[32], u[32];
+      tmem_ld_32x32(taddr + c, g);
+      tmem_ld_32x32(taddr + BN / 2 + c, u);
+      tmem_ld_wait();
+      const int col = nb * (BN / 2) + c;
+      if (row < p.M && p.D2 != nullptr && col < n_out) {
+        __nv_bfloat16* r0 = reinterpret_cast<__nv_bfloat16*>(p.D2) + static_cast<long long>(row) * p.ldd2 + col;
+        __nv_bfloat16* r1 = r0 + n_out;
+        if (col + 32 <= n_out) {
+          #pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            reinterpret_cast<uint4*>(r0)[j] = make_uint4(pack_bf16x2(__uint_as_float(g[8 * j]), __uint_as_float(g[8 * j + 1])),
+                pack_bf16x2(__uint_as_float(g[8 * j + 2]), __uint_as_float(g[8 * j + 3])),
+                pack_bf16x2(__uint_as_float(g[8 * j + 4]), __uint_as_float(g[8 * j + 5])),
+                pack_bf16x2(__uint_as_float(g[8 * j + 6]), __uint_as_float(g[8 * j + 7])));
+            reinterpret_cast<uint4*>(r1)[j] = make_uint4(pack_bf16x2(__uint_as_float(u[8 * j]), __uint_as_float(u[8 * j + 1])),
+                pack_bf16x2(__uint_as_float(u[8 * j + 2]), __uint_as_float(u[8 * j + 3])),
+                pack_bf16x2(__uint_as_float(u[8 * j + 4]), __uint_as_float(u[8 * j + 5])),
+                pack_bf16x2(__uint_as_float(u[8 * j + 6]), __uint_as_float(u[8 * j + 7])));
+          }
+        } else {
+          for (int j = 0; j < 32 && col + j < n_out; ++j) {
+            r0[j] = __float2bfloat16(__uint_as_float(g[j]));
+            r1[j] = __float2bfloat16(__uint_as_float(u[j]));
+          }
+        }
+      }
+      if (row < p.M && col < n_out) {
+        uint32_t o[16];
+        #pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+          float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+          float a0 = g0 / (1.f + __expf(-g0)) * u0;
+          float a1 = g1 / (1.f + __expf(-g1)) * u1;
+          o[j] = pack_bf16x2(a0, a1);
+        }
+        __nv_bfloat16* dst = Dp + static_cast<long long>(row) * p.ldd + col;
+        if (col + 32 <= n_out) {
+          #pragma unroll
+          for (int j = 0; j < 4; ++j)
+            reinterpret_cast<uint4*>(dst)[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+        } else {
+          for (int j = 0; j < 32 && col + j < n_out; ++j)
+            dst[j] = reinterpret_cast<__nv_bfloat16*>(o)[j];
+        }
+      }
+    }
+  } else {
+    #pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      uint32_t v[32];
+      tmem_ld_32x32(taddr + c, v);
+      tmem_ld_wait();
+      const int col = nb * BN + c;
+      if (row < p.M && col < p.N) {
+        if constexpr (EPI == EPI_STORE_BF16 || EPI == EPI_ACCUM_BF16) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + col;
+          if (col + 32 <= p.N) {
+            #pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 o;
+              if constexpr (EPI == EPI_ACCUM_BF16) {
+                uint4 old = reinterpret_cast<const uint4*>(dst)[j];
+                const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+                uint32_t* oo = reinterpret_cast<uint32_t*>(&o);
+                #pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  float2 f = __bfloat1622float2(ob[q]);
+                  oo[q] = pack_bf16x2(__uint_as_float(v[8 * j + 2 * q]) + f.x, __uint_as_float(v[8 * j + 2 * q + 1]) + f.y);
+                }
+              } else {
+                o = make_uint4(pack_bf16x2(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1])),
+                               pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3])),
+                               pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5])),
+                               pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7])));
+              }
+              reinterpret_cast<uint4*>(dst)[j] = o;
+            }
+          } else {
+            for (int j = 0; j < 32 && col + j < p.N; ++j) {
+              float x = __uint_as_float(v[j]);
+              if constexpr (EPI == EPI_ACCUM_BF16) x += __bfloat162float(dst[j]);
+              dst[j] = __float2bfloat16(x);
+            }
+          }
+        } else {
+          float* dst = reinterpret_cast<float*>(p.D) + d_off + static_cast<long long>(row) * p.ldd + col;
+          if (col + 32 <= p.N) {
+            #pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 o = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                     __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+              if constexpr (EPI == EPI_ACCUM_F32) {
+                float4 old = reinterpret_cast<const float4*>(dst)[j];
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              reinterpret_cast<float4*>(dst)[j] = o;
+            }
+          } else {
+            for (int j = 0; j < 32 && col + j < p.N; ++j) {
+              float x = __uint_as_float(v[j]);
+              if constexpr (EPI == EPI_ACCUM_F32) x += dst[j];
+              dst[j] = x;
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI, bool GROUPED, bool KGROUPED = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -207,122 +329,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int row = mb * GEMM_BM + quad * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-      if constexpr (EPI == EPI_SWIGLU_BF16) {
-        // tile columns [0,BN/2) hold gate, [BN/2,BN) hold up for output columns nb*BN/2 ...
-        __nv_bfloat16* Dp = reinterpret_cast<__nv_bfloat16*>(p.D);
-        const int n_out = p.N / 2;
-        #pragma unroll 1
-        for (int c = 0; c < BN / 2; c += 32) {
-          uint32_t g[32], u[32];
-          tmem_ld_32x32(taddr + c, g);
-          tmem_ld_32x32(taddr + BN / 2 + c, u);
-          tmem_ld_wait();
-          const int col = nb * (BN / 2) + c;
-          if (row < p.M && p.D2 != nullptr && col < n_out) {
-            __nv_bfloat16* r0 = reinterpret_cast<__nv_bfloat16*>(p.D2) + static_cast<long long>(row) * p.ldd2 + col;
-            __nv_bfloat16* r1 = r0 + n_out;
-            if (col + 32 <= n_out) {
-              #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                reinterpret_cast<uint4*>(r0)[j] = make_uint4(pack_bf16x2(__uint_as_float(g[8 * j]), __uint_as_float(g[8 * j + 1])),
-                    pack_bf16x2(__uint_as_float(g[8 * j + 2]), __uint_as_float(g[8 * j + 3])),
-                    pack_bf16x2(__uint_as_float(g[8 * j + 4]), __uint_as_float(g[8 * j + 5])),
-                    pack_bf16x2(__uint_as_float(g[8 * j + 6]), __uint_as_float(g[8 * j + 7])));
-                reinterpret_cast<uint4*>(r1)[j] = make_uint4(pack_bf16x2(__uint_as_float(u[8 * j]), __uint_as_float(u[8 * j + 1])),
-                    pack_bf16x2(__uint_as_float(u[8 * j + 2]), __uint_as_float(u[8 * j + 3])),
-                    pack_bf16x2(__uint_as_float(u[8 * j + 4]), __uint_as_float(u[8 * j + 5])),
-                    pack_bf16x2(__uint_as_float(u[8 * j + 6]), __uint_as_float(u[8 * j + 7])));
-              }
-            } else {
-              for (int j = 0; j < 32 && col + j < n_out; ++j) {
-                r0[j] = __float2bfloat16(__uint_as_float(g[j]));
-                r1[j] = __float2bfloat16(__uint_as_float(u[j]));
-              }
-            }
-          }
-          if (row < p.M && col < n_out) {
-            uint32_t o[16];
-            #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
-              float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
-              float a0 = g0 / (1.f + __expf(-g0)) * u0;
-              float a1 = g1 / (1.f + __expf(-g1)) * u1;
-              o[j] = pack_bf16x2(a0, a1);
-            }
-            __nv_bfloat16* dst = Dp + static_cast<long long>(row) * p.ldd + col;
-            if (col + 32 <= n_out) {
-              #pragma unroll
-              for (int j = 0; j < 4; ++j)
-                reinterpret_cast<uint4*>(dst)[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-            } else {
-              for (int j = 0; j < 32 && col + j < n_out; ++j)
-                dst[j] = reinterpret_cast<__nv_bfloat16*>(o)[j];
-            }
-          }
-        }
-      } else {
-        #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c, v);
-          tmem_ld_wait();
-          const int col = nb * BN + c;
-          if (row < p.M && col < p.N) {
-            if constexpr (EPI == EPI_STORE_BF16 || EPI == EPI_ACCUM_BF16) {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + col;
-              if (col + 32 <= p.N) {
-                #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  uint4 o;
-                  if constexpr (EPI == EPI_ACCUM_BF16) {
-                    uint4 old = reinterpret_cast<const uint4*>(dst)[j];
-                    const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
-                    uint32_t* oo = reinterpret_cast<uint32_t*>(&o);
-                    #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                      float2 f = __bfloat1622float2(ob[q]);
-                      oo[q] = pack_bf16x2(__uint_as_float(v[8 * j + 2 * q]) + f.x, __uint_as_float(v[8 * j + 2 * q + 1]) + f.y);
-                    }
-                  } else {
-                    o = make_uint4(pack_bf16x2(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1])),
-                                   pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3])),
-                                   pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5])),
-                                   pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7])));
-                  }
-                  reinterpret_cast<uint4*>(dst)[j] = o;
-                }
-              } else {
-                for (int j = 0; j < 32 && col + j < p.N; ++j) {
-                  float x = __uint_as_float(v[j]);
-                  if constexpr (EPI == EPI_ACCUM_BF16) x += __bfloat162float(dst[j]);
-                  dst[j] = __float2bfloat16(x);
-                }
-              }
-            } else {
-              float* dst = reinterpret_cast<float*>(p.D) + d_off + static_cast<long long>(row) * p.ldd + col;
-              if (col + 32 <= p.N) {
-                #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  float4 o = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                         __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                  if constexpr (EPI == EPI_ACCUM_F32) {
-                    float4 old = reinterpret_cast<const float4*>(dst)[j];
-                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                  }
-                  reinterpret_cast<float4*>(dst)[j] = o;
-                }
-              } else {
-                for (int j = 0; j < 32 && col + j < p.N; ++j) {
-                  float x = __uint_as_float(v[j]);
-                  if constexpr (EPI == EPI_ACCUM_F32) x += dst[j];
-                  dst[j] = x;
-                }
-              }
-            }
-          }
-        }
-      }
+      gemm_store_tile<BN, EPI>(taddr, row, nb, p, d_off);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);

@@ -74,7 +74,7 @@ def bench_gemm(rows):
             out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         flops = 2.0 * M * N * K
         res = {}
-        for bn in (128, 256):
+        for bn in (128, 256, 0):       # 0 = automatic choice: CTA pairs (256 x 256 tiles) on these shapes
             ms = timeit(lambda: F.gemm(a, b, out=out, a_mn=a_mn, b_mn=b_mn, epi=epi, force_bn=bn))
             res[bn] = flops / ms / 1e9
         am = a.t() if a_mn else a
@@ -82,7 +82,7 @@ def bench_gemm(rows):
         ms_lib = timeit(lambda: torch.matmul(am, bm))
         lib = flops / ms_lib / 1e9
         best = max(res.values())
-        rows.append(f"gemm {name:16s} M={M} N={N} K={K}: bn128 {res[128]:7.1f} bn256 {res[256]:7.1f} TFLOP/s | "
+        rows.append(f"gemm {name:16s} M={M} N={N} K={K}: bn128 {res[128]:7.1f} bn256 {res[256]:7.1f} pair {res[0]:7.1f} TFLOP/s | "
                     f"torch.matmul {lib:7.1f} | best/measured-peak {best / peaks['bf16_tflops']:.2f}")
         print(rows[-1], flush=True)
         del a, b, out

@@ -17,8 +17,9 @@ def F():
     return F
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (384, 1024, 4096), (200, 328, 136), (4096, 1024, 1024)])
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (384, 1024, 4096), (200, 328, 136), (4096, 1024, 1024),
+                                   (1000, 1304, 520), (4096, 6144, 4096)])
+@pytest.mark.parametrize("bn", [128, 256, 0])   # 0 = automatic: the CTA-pair kernel when the shape has 256 x 256 tiles
 def test_gemm_nt(F, M, N, K, bn):
     torch.manual_seed(0)
     a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
@@ -29,7 +30,7 @@ def test_gemm_nt(F, M, N, K, bn):
     assert _rel_err(out, ref) < 1e-2
 
 
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 256, 0])   # 0 = automatic: the CTA-pair kernel when the shape has 256 x 256 tiles
 def test_gemm_dgrad_layout(F, bn):
     torch.manual_seed(1)
     M, N, K = 512, 384, 640  # dx[M,N] = dy[M,K] @ W[K,N]
@@ -40,7 +41,7 @@ def test_gemm_dgrad_layout(F, bn):
     assert _rel_err(out, dy.float() @ w.float()) < 1e-2
 
 
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 256, 0])   # 0 = automatic: the CTA-pair kernel when the shape has 256 x 256 tiles
 def test_gemm_wgrad_layout_accumulate(F, bn):
     torch.manual_seed(2)
     T, O, I = 1024, 384, 512  # dW[O,I] = dy[T,O]^T @ x[T,I]
@@ -55,7 +56,7 @@ def test_gemm_wgrad_layout_accumulate(F, bn):
     assert _rel_err(out, dy.float().t() @ x.float()) < 1e-2
 
 
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 256, 0])   # 0 = automatic: the CTA-pair kernel when the shape has 256 x 256 tiles
 def test_gemm_swiglu_epilogue(F, bn):
     torch.manual_seed(3)
     T, H, I = 512, 256, 384
@@ -81,7 +82,7 @@ def test_gemm_residual_accumulate(F):
     assert _rel_err(res, ref) < 1e-2
 
 
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 256, 0])   # 0 = automatic: the CTA-pair kernel when the shape has 256 x 256 tiles
 def test_grouped_gemm(F, bn):
     torch.manual_seed(5)
     E, N, K = 4, 384, 256
