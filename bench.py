@@ -46,6 +46,7 @@ def parse():
     ap.add_argument("--no-second", action="store_true", help="8 GPUs: skip the Qwen3-30B-A3B EP8 block")
     ap.add_argument("--second-steps", type=int, default=3, help="timed steps of the Qwen3-30B-A3B EP8 block")
     ap.add_argument("--second-budget-s", type=float, default=330.0, help="wall-clock limit of the second block")
+    ap.add_argument("--force-second", action="store_true", help="debug only: run the second block at any GPU count / layer count")
     ap.add_argument("--global-batch", type=int, default=64)
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (the result is then marked invalid)")
@@ -188,7 +189,9 @@ def run_config(args, model_name, W, K, do_e2e, dev, world, rank, local_rank):
     MB = args.micro_batch or 1
     assert GB % (dp_world * MB) == 0, "global batch must be a multiple of data ranks x micro batch"
     accum = GB // (dp_world * MB)
-    use_graph = args.cuda_graph == 1 or (args.cuda_graph < 0 and not is_moe)
+    # MoE models replay from a graph too when their token exchange runs on the peer-memory kernels (no host read-back)
+    use_graph = args.cuda_graph == 1 or (args.cuda_graph < 0 and (not is_moe or (cfg.moe_token_dispatcher_type == "fused" and world > 1
+                                                                                 and model_name != "glm4.5-air-12l")))
     ta = TrainingArguments(output_dir="/tmp/pfb_bench_out", per_device_train_batch_size=MB, gradient_accumulation_steps=accum,
                            max_steps=W + K, learning_rate=3e-4, lr_scheduler_type="constant", weight_decay=0.1,
                            adam_beta2=0.95, max_grad_norm=1.0, bf16=True, logging_steps=1, save_strategy="no",
@@ -293,7 +296,7 @@ def run_config(args, model_name, W, K, do_e2e, dev, world, rank, local_rank):
                 r[0] += 1
                 r[1] += ev.device_time_total
             tot = sum(v[1] for v in rows.values())
-            with open(args.kernel_table, "w") as f:
+            with open(args.kernel_table.replace(".txt", f"_{model_name}.txt"), "w") as f:
                 f.write(f"# {model_name} {par}: {n_mb} micro-batches (forward + backward), device time per kernel, rank 0; "
                         f"total {tot / n_mb / 1e3:.2f} ms per micro-batch\n")
                 for name, (cnt, us) in sorted(rows.items(), key=lambda kv: -kv[1][1]):
@@ -400,7 +403,7 @@ def main():
     out = run_config(args, args.model, args.warmup, args.steps, not args.no_e2e, dev, world, rank, local_rank)
 
     # The other half of the headline metric: Qwen3-30B-A3B at EP8 with the peer-memory dispatch / combine kernels.
-    if world == 8 and args.model == "llama3-8b" and not args.no_second and not args.layers:
+    if (world == 8 and args.model == "llama3-8b" and not args.no_second and not args.layers) or (args.force_second and world > 1):
         printed = threading.Event()
 
         def give_up():

@@ -15,12 +15,19 @@ Design (the reference's sharding stage-1 "V2" / split_param semantics, paddlefor
   tp*cp/ep relative to dense parameters (paddleformers/trainer/training_args.py:2808-2815); the gradient norm is
   combined across domains and model-parallel groups like the reference's MoE-aware clip
   (paddleformers/utils/moe_hybrid_parallel_optimizer.py:60-160).
+* On GPUs the flat buffers of a sharded domain live in symmetric (peer-mapped) memory and the step uses two fused
+  kernels instead of three library collectives (``csrc/shard_comm.cu``): ``shard_reduce`` reads this rank's gradient
+  slice out of every peer's buffer, sums in rank order, scales and accumulates the squared norm in one pass;
+  ``adamw_push`` updates the slice and stores the bf16 weights into every rank's parameter buffer, which is the
+  all-gather. ``PFB_FUSED_SHARDING=0`` keeps the NCCL reduce-scatter / all-gather path (the A/B baseline, and the path of
+  CPU ranks).
 * Weight decay follows the reference's name rule: parameters whose name contains "bias" or "norm" are not decayed
   (paddleformers/trainer/trainer.py:3645-3656).
 """
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Callable, Dict, Iterable, List, Optional, Tuple
 
@@ -58,6 +65,7 @@ class _Domain:
     numel: int = 0
     is_expert: bool = False
     is_muon: bool = False          # matrices updated by the orthogonalised-momentum rule (see ShardedMuon)
+    symm: Optional[dict] = None    # peer-memory state of the fused reduce / update kernels (None: library collectives)
 
     @property
     def shard_numel(self) -> int:
@@ -134,8 +142,23 @@ class ShardedAdamW:
         total = (total + unit - 1) // unit * unit
         dom.numel = total
         dev = dom.params[0][1].device
-        dom.flat_param = torch.zeros(total, dtype=dtype, device=dev)
-        dom.flat_grad = torch.zeros(total, dtype=torch.float32, device=dev)
+        if self._fused_sharding_ok(dom, dtype, dev):
+            from .symmetric_memory import SymmetricBuffer
+
+            pbuf = SymmetricBuffer(total * 2, dom.shard_group, dev)
+            gbuf = SymmetricBuffer(total * 4, dom.shard_group, dev)
+            fbuf = SymmetricBuffer(2 * 8 * 4, dom.shard_group, dev)
+            dom.flat_param = pbuf.tensor((total,), dtype)
+            dom.flat_grad = gbuf.tensor((total,), torch.float32)
+            dom.flat_param.zero_()
+            dom.flat_grad.zero_()
+            dom.symm = {"bufs": (pbuf, gbuf, fbuf), "param_ptrs": torch.tensor(pbuf.peer_ptrs, dtype=torch.int64),
+                        "grad_ptrs": torch.tensor(gbuf.peer_ptrs, dtype=torch.int64),
+                        "flag_ptrs": torch.tensor(fbuf.peer_ptrs, dtype=torch.int64),
+                        "epoch": torch.zeros(1, dtype=torch.int32, device=dev)}
+        else:
+            dom.flat_param = torch.zeros(total, dtype=dtype, device=dev)
+            dom.flat_grad = torch.zeros(total, dtype=torch.float32, device=dev)
         for name, p in dom.params:
             off, n = dom.offsets[name]
             view = dom.flat_param[off:off + n].view(p.shape)
@@ -145,6 +168,16 @@ class ShardedAdamW:
         dom.master = dom.shard_slice(dom.flat_param).float().clone()
         dom.exp_avg = torch.zeros_like(dom.master)
         dom.exp_avg_sq = torch.zeros_like(dom.master)
+
+    def _fused_sharding_ok(self, dom: _Domain, dtype, dev) -> bool:
+        if dom.shard_group is None or dev.type != "cuda" or dtype != torch.bfloat16 or dom.shard_size > 8:
+            return False
+        if os.environ.get("PFB_FUSED_SHARDING", "1") == "0" or dom.is_muon or self.custom_update:
+            return False
+        try:
+            return F._build.load_extension() and hasattr(torch.ops.pfb200, "shard_reduce")
+        except Exception:  # noqa: BLE001
+            return False
 
     # ------------------------------------------------------------------ gradient handling
     def accumulate_grads(self):
@@ -181,6 +214,20 @@ class ShardedAdamW:
             world = dom.shard_size * (_group_size(dom.extra_reduce_group))
             scale = dom.grad_scale / world
             local = dom.shard_slice(dom.flat_grad)
+            if dom.symm is not None:
+                # one pass: peer loads of this rank's slice from every rank's buffer, fixed-order sum, scale, squared norm
+                sy = dom.symm
+                sy["epoch"].add_(1)
+                ops = torch.ops.pfb200
+                ops.shard_signal(sy["grad_ptrs"], sy["param_ptrs"], sy["flag_ptrs"], dom.shard_rank, 0, sy["epoch"])
+                sy["norm"] = torch.zeros(1, dtype=torch.float32, device=local.device)
+                ops.shard_reduce(dom.flat_grad, sy["grad_ptrs"], sy["param_ptrs"], sy["flag_ptrs"], dom.shard_rank, dom.shard_rank * n, n,
+                                 scale, sy["norm"], sy["epoch"])
+                if dom.extra_reduce_group is not None:
+                    dist.all_reduce(local, group=dom.extra_reduce_group)
+                    sy["norm"] = None          # the slice changed after the kernel's norm: recomputed below
+                shards.append(local)
+                continue
             if dom.shard_group is not None:
                 dist.reduce_scatter_tensor(local, dom.flat_grad, group=dom.shard_group)
             if dom.extra_reduce_group is not None:
@@ -196,7 +243,9 @@ class ShardedAdamW:
         acc_expert = torch.zeros_like(acc_dense)
         for dom, g in zip(self.domains, shards):
             acc = acc_expert if dom.is_expert else acc_dense
-            if g.is_cuda:
+            if dom.symm is not None and dom.symm.get("norm") is not None:
+                acc += dom.symm["norm"]             # accumulated by the reduce kernel
+            elif g.is_cuda:
                 ops = torch.ops.pfb200
                 scratch = F._get_scratch(g.device, int(ops.sq_norm_scratch_elems()))
                 ops.sq_norm_accum(g, acc, scratch)
@@ -264,6 +313,19 @@ class ShardedAdamW:
                 self._muon_update(dom, g, pslice, sc)
             elif self.custom_update:
                 self._update(dom, g, pslice, sc)
+            elif dom.symm is not None:
+                # update + all-gather in one kernel: the bf16 weights are stored into every rank's parameter buffer
+                sy = dom.symm
+                ops = torch.ops.pfb200
+                n = dom.shard_numel
+                ops.adamw_push(dom.master, dom.exp_avg, dom.exp_avg_sq, dom.flat_grad, sy["grad_ptrs"], sy["param_ptrs"], sy["flag_ptrs"],
+                               dom.shard_rank, dom.shard_rank * n, sc, b1, b2, self.eps, dom.weight_decay)
+                ops.shard_signal(sy["grad_ptrs"], sy["param_ptrs"], sy["flag_ptrs"], dom.shard_rank, 1, sy["epoch"])
+                # every rank has pushed (and therefore finished reading this rank's gradients): the buffer may be cleared and
+                # the next forward pass may read the parameters
+                ops.shard_wait(sy["flag_ptrs"], dom.shard_rank, 1, sy["epoch"])
+                dom.flat_grad.zero_()
+                continue
             elif g.is_cuda:
                 p16 = pslice if pslice.dtype == torch.bfloat16 else None
                 torch.ops.pfb200.adamw_step(dom.master, dom.exp_avg, dom.exp_avg_sq, g, p16, sc, b1, b2, self.eps,

@@ -164,6 +164,13 @@ class TrainingArguments:
                 self.sharding = "stage3"
             if self.sharding not in ("stage1", "stage2", "stage3"):
                 raise ValueError("sharding must be '', 'stage1', 'stage2' or 'stage3' (alias fsdp)")
+            if self.sharding == "stage2":
+                # gradients stay whole per rank: the fp32 main_grad buffers that the weight-gradient GEMMs accumulate into
+                # are the gradient store of this design, so stage 2 runs the stage-1 plan (stage 3 shards them per layer)
+                import warnings
+
+                warnings.warn("sharding stage2 runs the stage1 plan here (optimizer state sharded, fp32 gradients kept whole "
+                              "per rank); use stage3 to shard gradients and parameters too", stacklevel=2)
             if self.sharding == "stage3" and (tp > 1 or pp > 1 or max(self.expert_model_parallel_size, 1) > 1 or sep > 1 or cp > 1):
                 raise ValueError("sharding stage3 shards over the data ranks only: tensor / pipeline / expert / context "
                                  "parallel degrees must be 1")
