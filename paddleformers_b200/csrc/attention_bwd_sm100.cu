@@ -14,7 +14,7 @@
 namespace pfb {
 
 static CUtensorMap map3(const at::Tensor& t, int box_rows) {
-  TORCH_CHECK(t.dim() == 3 && t.stride(2) == 1 && t.scalar_type() == at::kBFloat16 && t.size(2) == ATT_D);
+  TORCH_CHECK(t.dim() == 3 && t.stride(2) == 1 && t.scalar_type() == at::kBFloat16 && (t.size(2) == ATT_D || t.size(2) == 192));
   return make_tma_3d(t.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t.size(0), t.size(1), t.size(2), t.stride(0),
                      t.stride(1), box_rows, 1, 64);
 }
@@ -25,21 +25,24 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
               const at::Tensor& lse, at::Tensor& dq, at::Tensor& dk, at::Tensor& dv, int64_t B, int64_t S, double scale,
               bool causal, const c10::optional<at::Tensor>& kend, const c10::optional<at::Tensor>& tile_min,
               const c10::optional<at::Tensor>& tile_max, bool deterministic, int64_t heads_per_cta_override) {
-  TORCH_CHECK(q.is_cuda() && q.size(-1) == ATT_D, "attn_bwd: head_dim 128");
+  const int DQK = q.size(-1);
+  TORCH_CHECK(q.is_cuda() && (DQK == ATT_D || DQK == 192) && k.size(-1) == DQK && v.size(-1) == ATT_D,
+              "attn_bwd: queries / keys 128 or 192 wide, values 128 wide");
   const c10::cuda::CUDAGuard guard(q.device());
   const int Hq = q.size(-2), Hkv = k.size(-2);
+  TORCH_CHECK(DQK == ATT_D || Hq == Hkv, "attn_bwd: 192-wide heads need as many key heads as query heads");
   const long long T = B * S;
-  at::Tensor q3 = q.view({T, Hq, ATT_D}), k3 = k.view({T, Hkv, ATT_D}), v3 = v.view({T, Hkv, ATT_D});
+  at::Tensor q3 = q.view({T, Hq, DQK}), k3 = k.view({T, Hkv, DQK}), v3 = v.view({T, Hkv, ATT_D});
   at::Tensor do3 = dout.contiguous().view({T, Hq, ATT_D});
   at::Tensor o3 = out.contiguous().view({T, Hq, ATT_D});
-  at::Tensor dq3 = dq.view({T, Hq, ATT_D}), dk3 = dk.view({T, Hkv, ATT_D}), dv3 = dv.view({T, Hkv, ATT_D});
-  TORCH_CHECK(dq3.stride(2) == 1 && dq3.stride(1) == ATT_D && dk3.stride(1) == ATT_D && dv3.stride(1) == ATT_D);
+  at::Tensor dq3 = dq.view({T, Hq, DQK}), dk3 = dk.view({T, Hkv, DQK}), dv3 = dv.view({T, Hkv, ATT_D});
+  TORCH_CHECK(dq3.stride(2) == 1 && dq3.stride(1) == DQK && dk3.stride(1) == DQK && dv3.stride(1) == ATT_D);
   TORCH_CHECK(lse.is_contiguous() && lse.scalar_type() == at::kFloat);
   if (T == 0) return;
   bool group_mode = false;
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   at::Tensor delta = at::empty({B, Hq, S}, lse.options());
-  at::Tensor dq_acc = at::zeros({T, Hq, ATT_D}, lse.options());
+  at::Tensor dq_acc = at::zeros({T, Hq, DQK}, lse.options());
   {
     const long long warps = T * Hq;
     attn_bwd_delta_kernel<<<static_cast<int>((warps * 32 + 255) / 256), 256, 0, stream>>>(
@@ -60,7 +63,7 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
   const long long group_ctas = ((S + ATTB_BKV - 1) / ATTB_BKV) * static_cast<long long>(Hkv) * B;
   int heads_per_cta = (G > 1 && group_ctas >= 2LL * at::cuda::getCurrentDeviceProperties()->multiProcessorCount) ? G : 1;
   if (heads_per_cta_override > 0) heads_per_cta = heads_per_cta_override == 1 ? 1 : G;
-  if (use_v1) heads_per_cta = 1;
+  if (use_v1 || DQK != ATT_D) heads_per_cta = 1;
   group_mode = heads_per_cta != 1;
   if (Hq != Hkv && !group_mode) {
     dk_part = at::empty({T, Hq, ATT_D}, lse.options());
@@ -79,14 +82,23 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
   p.causal = causal ? 1 : 0;
   p.status = status_word();
   CUtensorMap tmQ = map3(q3, ATTB_BQ), tmK = map3(k3, ATTB_BKV), tmV = map3(v3, ATTB_BKV), tmdO = map3(do3, ATTB_BQ);
-  if (use_v1) {
+  if (DQK == 192) {
+    // multi-head latent attention: the one-tile-at-a-time kernel (dK alone takes 192 TMEM columns)
     static bool cfg = false;
     if (!cfg) {
-      C10_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem::TOTAL));
+      C10_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_kernel<192>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmemT<192>::TOTAL));
       cfg = true;
     }
     dim3 grid(kv_tiles, Hq, B);
-    attn_bwd_kernel<<<grid, ATTB_THREADS, AttnBwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmdO, p);
+    attn_bwd_kernel<192><<<grid, ATTB_THREADS, AttnBwdSmemT<192>::TOTAL, stream>>>(tmQ, tmK, tmV, tmdO, p);
+  } else if (use_v1) {
+    static bool cfg = false;
+    if (!cfg) {
+      C10_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem::TOTAL));
+      cfg = true;
+    }
+    dim3 grid(kv_tiles, Hq, B);
+    attn_bwd_kernel<128><<<grid, ATTB_THREADS, AttnBwdSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmdO, p);
   } else {
     AttnBwd2Params pp;
     pp.base = p;
@@ -113,7 +125,7 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
     const long long work = T * (Hq * ATT_D / 4);
     const int blocks = static_cast<int>(std::min<long long>((work + 255) / 256, static_cast<long long>(at::cuda::getCurrentDeviceProperties()->multiProcessorCount) * 16));
     attn_bwd_dq_convert_kernel<<<blocks, 256, 0, stream>>>(dq_acc.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(dq3.data_ptr()),
-                                                          T, Hq * ATT_D, dq3.stride(0));
+                                                          T, Hq * DQK, dq3.stride(0));
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   }
   int launches = 3;

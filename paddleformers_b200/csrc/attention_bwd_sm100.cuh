@@ -44,22 +44,37 @@ struct AttnBwdParams {
   int* status;
 };
 
-struct AttnBwdSmem {
-  static constexpr int KV_TILE = ATTB_BKV * ATT_D * 2;   // 32 KB
-  static constexpr int Q_TILE = ATTB_BQ * ATT_D * 2;     // 16 KB
-  static constexpr int K_OFF = 0, V_OFF = KV_TILE;
-  static constexpr int Q_OFF = 2 * KV_TILE;               // 2 stages x (Q, dO)
-  static constexpr int DS_OFF = Q_OFF + 4 * Q_TILE;       // dS^T [128 keys x 64 q] bf16 = 16 KB
+// DQK: width of queries / keys (128, or 192 for multi-head latent attention; values and dO stay 128 wide).
+template <int DQK>
+struct AttnBwdSmemT {
+  static constexpr int KSLABS = DQK == 128 ? 2 : 4;       // 192: a fourth, zero-filled slab pads K^T to 256 rows for dQ^T
+  static constexpr int K_SLAB = ATTB_BKV * 64 * 2;        // 16 KB: [128 keys x 64 columns]
+  static constexpr int Q_SLAB = ATTB_BQ * 64 * 2;         // 8 KB:  [64 queries x 64 columns]
+  static constexpr int K_TILE = KSLABS * K_SLAB;
+  static constexpr int V_TILE = 2 * K_SLAB;
+  static constexpr int Q_TILE = (DQK / 64) * Q_SLAB;
+  static constexpr int DO_TILE = 2 * Q_SLAB;
+  static constexpr int K_OFF = 0, V_OFF = K_TILE;
+  static constexpr int Q_OFF = K_TILE + V_TILE;            // 2 stages x (Q, dO)
+  static constexpr int DS_OFF = Q_OFF + 2 * (Q_TILE + DO_TILE);   // dS^T [128 keys x 64 q] bf16 = 16 KB
   static constexpr int STAT_OFF = DS_OFF + ATTB_BKV * ATTB_BQ * 2;  // per-warp lse / delta copies: 4 x 2 x 64 floats
   static constexpr int BAR_OFF = STAT_OFF + 4 * 2 * 64 * 4;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
+using AttnBwdSmem = AttnBwdSmemT<128>;
 
+// One tile at a time (no overlap between the products and the element-wise work): the simple schedule. It is the only
+// kernel for DQK = 192, where dK alone takes 192 TMEM columns and no second [S^T | dP^T] stage fits.
+// TMEM: [S^T 0-63][dP^T 64-127][dQ^T(d < 128) 128-191][dV 192-319][dK 320-...]; P^T (bf16) over S^T columns 0-31, dS^T
+// (bf16) over dP^T columns 96-127; for DQK = 192 the second half of dQ^T (head dims 128-191, computed as a 128-row
+// product against the zero-padded K^T) goes to the dead columns 32-95 in between.
+template <int DQK>
 __global__ void __launch_bounds__(ATTB_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                 const AttnBwdParams p) {
-  using SM = AttnBwdSmem;
+  using SM = AttnBwdSmemT<DQK>;
+  constexpr bool MLA = DQK != 128;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem + SM::K_OFF; uint8_t* sV = smem + SM::V_OFF;
@@ -90,7 +105,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tdP = tmem_base + 64, tdV = tmem_base + 128, tdK = tmem_base + 256, tdQ = tmem_base + 384;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 64, tdQ = tmem_base + 128, tdV = tmem_base + 192, tdK = tmem_base + 320;
+  const uint32_t tdQb = tmem_base + 32;     // DQK = 192 only
 
   // query tile range visible to this key tile
   const int q_tiles = (p.S + ATTB_BQ - 1) / ATTB_BQ;
@@ -108,44 +124,50 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 4) {
     if (lane == 0 && n_it > 0) {
       constexpr uint32_t idesc_s = make_idesc(128, ATTB_BQ, false, false, 1);   // K-major x K-major
-      constexpr uint32_t idesc_dkv = make_idesc(128, ATT_D, false, true, 1);     // TMEM A x MN-major B
+      constexpr uint32_t idesc_dv = make_idesc(128, ATT_D, false, true, 1);      // TMEM A x MN-major B
+      constexpr uint32_t idesc_dk = make_idesc(128, DQK, false, true, 1);
       constexpr uint32_t idesc_dq = make_idesc(128, ATTB_BQ, true, true, 1);     // MN-major x MN-major
       auto load_q = [&](int it) {
         const int i = i_lo + it;
         const int st = it & 1;
-        uint8_t* sq = smem + SM::Q_OFF + st * 2 * SM::Q_TILE;
+        uint8_t* sq = smem + SM::Q_OFF + st * (SM::Q_TILE + SM::DO_TILE);
         uint8_t* sdo = sq + SM::Q_TILE;
-        mbar_expect_tx(&bar_q[st], 2 * SM::Q_TILE);
-        tma_load_3d(sq, &tmQ, &bar_q[st], 0, head, row_base + i * ATTB_BQ);
-        tma_load_3d(sq + SM::Q_TILE / 2, &tmQ, &bar_q[st], 64, head, row_base + i * ATTB_BQ);
+        mbar_expect_tx(&bar_q[st], SM::Q_TILE + SM::DO_TILE);
+        #pragma unroll
+        for (int sl = 0; sl < DQK / 64; ++sl) tma_load_3d(sq + sl * SM::Q_SLAB, &tmQ, &bar_q[st], 64 * sl, head, row_base + i * ATTB_BQ);
         tma_load_3d(sdo, &tmdO, &bar_q[st], 0, head, row_base + i * ATTB_BQ);
-        tma_load_3d(sdo + SM::Q_TILE / 2, &tmdO, &bar_q[st], 64, head, row_base + i * ATTB_BQ);
+        tma_load_3d(sdo + SM::Q_SLAB, &tmdO, &bar_q[st], 64, head, row_base + i * ATTB_BQ);
       };
-      mbar_expect_tx(bar_kv, 2 * SM::KV_TILE);
-      tma_load_3d(sK, &tmK, bar_kv, 0, kvh, row_base + k0);
-      tma_load_3d(sK + SM::KV_TILE / 2, &tmK, bar_kv, 64, kvh, row_base + k0);
+      mbar_expect_tx(bar_kv, SM::K_TILE + SM::V_TILE);
+      #pragma unroll
+      for (int sl = 0; sl < SM::KSLABS; ++sl)       // a slab that starts at or beyond column DQK reads as zeros
+        tma_load_3d(sK + sl * SM::K_SLAB, &tmK, bar_kv, 64 * sl, kvh, row_base + k0);
       tma_load_3d(sV, &tmV, bar_kv, 0, kvh, row_base + k0);
-      tma_load_3d(sV + SM::KV_TILE / 2, &tmV, bar_kv, 64, kvh, row_base + k0);
+      tma_load_3d(sV + SM::K_SLAB, &tmV, bar_kv, 64, kvh, row_base + k0);
       load_q(0);
       bool ok = mbar_wait(bar_kv, 0, abort_flag, p.status, PFB_ERR_WAIT_FULL);
       for (int it = 0; it < n_it && ok; ++it) {
         const int st = it & 1;
         const uint32_t ph = it & 1, qph = (it >> 1) & 1;
-        const uint32_t sq = smem_u32(smem + SM::Q_OFF + st * 2 * SM::Q_TILE);
+        const uint32_t sq = smem_u32(smem + SM::Q_OFF + st * (SM::Q_TILE + SM::DO_TILE));
         const uint32_t sdo = sq + SM::Q_TILE;
         if (!mbar_wait(&bar_q[st], qph, abort_flag, p.status, PFB_ERR_WAIT_FULL)) break;
+        if constexpr (MLA) {
+          // the second half of dQ^T of the previous tile sits in columns that S^T / dP^T are about to overwrite
+          if (it > 0 && !mbar_wait(bar_dqread, (it - 1) & 1, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)) break;
+        }
         tc_fence_after();
         #pragma unroll
-        for (int k = 0; k < ATT_D / 16; ++k) {
-          const uint32_t offk = (k >> 2) * (SM::KV_TILE / 2) + (k & 3) * 32;
-          const uint32_t offq = (k >> 2) * (SM::Q_TILE / 2) + (k & 3) * 32;
+        for (int k = 0; k < DQK / 16; ++k) {
+          const uint32_t offk = (k >> 2) * SM::K_SLAB + (k & 3) * 32;
+          const uint32_t offq = (k >> 2) * SM::Q_SLAB + (k & 3) * 32;
           tc_mma_f16_ss(tS, make_smem_desc_sw128(smem_u32(sK) + offk, 16, 1024), make_smem_desc_sw128(sq + offq, 16, 1024),
                         idesc_s, k != 0);
         }
         #pragma unroll
         for (int k = 0; k < ATT_D / 16; ++k) {
-          const uint32_t offk = (k >> 2) * (SM::KV_TILE / 2) + (k & 3) * 32;
-          const uint32_t offq = (k >> 2) * (SM::Q_TILE / 2) + (k & 3) * 32;
+          const uint32_t offk = (k >> 2) * SM::K_SLAB + (k & 3) * 32;
+          const uint32_t offq = (k >> 2) * SM::Q_SLAB + (k & 3) * 32;
           tc_mma_f16_ss(tdP, make_smem_desc_sw128(smem_u32(sV) + offk, 16, 1024), make_smem_desc_sw128(sdo + offq, 16, 1024),
                         idesc_s, k != 0);
         }
@@ -159,22 +181,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after();
         #pragma unroll
         for (int k = 0; k < ATTB_BQ / 16; ++k)
-          tc_mma_f16_ts(tdV, tS + k * 8, make_smem_desc_sw128(sdo + k * 16 * 128, SM::Q_TILE / 2, 1024), idesc_dkv,
-                        (it | k) != 0);
+          tc_mma_f16_ts(tdV, tS + k * 8, make_smem_desc_sw128(sdo + k * 16 * 128, SM::Q_SLAB, 1024), idesc_dv, (it | k) != 0);
         if (!mbar_wait(bar_ds, ph, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
         #pragma unroll
         for (int k = 0; k < ATTB_BQ / 16; ++k)
-          tc_mma_f16_ts(tdK, tdP + k * 8, make_smem_desc_sw128(sq + k * 16 * 128, SM::Q_TILE / 2, 1024), idesc_dkv,
-                        (it | k) != 0);
+          tc_mma_f16_ts(tdK, tdP + 32 + k * 8, make_smem_desc_sw128(sq + k * 16 * 128, SM::Q_SLAB, 1024), idesc_dk, (it | k) != 0);
         if (it > 0) {
           if (!mbar_wait(bar_dqread, (it - 1) & 1, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)) break;
           tc_fence_after();
         }
         #pragma unroll
         for (int k = 0; k < ATTB_BKV / 16; ++k)
-          tc_mma_f16_ss(tdQ, make_smem_desc_sw128(smem_u32(sK) + k * 16 * 128, SM::KV_TILE / 2, 1024),
+          tc_mma_f16_ss(tdQ, make_smem_desc_sw128(smem_u32(sK) + k * 16 * 128, SM::K_SLAB, 1024),
                         make_smem_desc_sw128(smem_u32(sdS) + k * 16 * 128, 16, 1024), idesc_dq, k != 0);
+        if constexpr (MLA) {
+          // head dims 128-255 of K^T (192-255 are the zero slab): its own 128-row product into the dead columns
+          #pragma unroll
+          for (int k = 0; k < ATTB_BKV / 16; ++k)
+            tc_mma_f16_ss(tdQb, make_smem_desc_sw128(smem_u32(sK) + 2 * SM::K_SLAB + k * 16 * 128, SM::K_SLAB, 1024),
+                          make_smem_desc_sw128(smem_u32(sdS) + k * 16 * 128, 16, 1024), idesc_dq, k != 0);
+        }
         tc_commit(bar_dq);
       }
     }
@@ -213,7 +240,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t v[32];
         tmem_ld_32x32(tS + lane_off + c, v);
         tmem_ld_wait();
-        uint32_t pk[16];
         #pragma unroll
         for (int x = 0; x < 32; x += 2) {
           float p0 = fast_exp2(__uint_as_float(v[x]) * p.scale_log2 - s_lse[c + x]);
@@ -225,8 +251,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             p0 = v0 ? p0 : 0.f; p1 = v1 ? p1 : 0.f;
           }
           pv[c + x] = p0; pv[c + x + 1] = p1;
-          pk[x >> 1] = pack_bf16x2(p0, p1);
         }
+      }
+      #pragma unroll
+      for (int c = 0; c < ATTB_BQ; c += 32) {       // after ALL raw scores of this lane have been read
+        uint32_t pk[16];
+        #pragma unroll
+        for (int x = 0; x < 32; x += 2) pk[x >> 1] = pack_bf16x2(pv[c + x], pv[c + x + 1]);
         tmem_st_32x16(tS + lane_off + (c >> 1), pk);
       }
       tmem_st_wait();
@@ -234,20 +265,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p);
       // dS^T = P^T * (dP^T - delta) * scale
+      uint32_t dsk[ATTB_BQ / 2];
       #pragma unroll
       for (int c = 0; c < ATTB_BQ; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32(tdP + lane_off + c, v);
         tmem_ld_wait();
-        uint32_t pk[16];
         #pragma unroll
         for (int x = 0; x < 32; x += 2) {
           const float d0 = pv[c + x] * (__uint_as_float(v[x]) - s_delta[c + x]) * p.scale;
           const float d1 = pv[c + x + 1] * (__uint_as_float(v[x + 1]) - s_delta[c + x + 1]) * p.scale;
-          pk[x >> 1] = pack_bf16x2(d0, d1);
+          dsk[(c + x) >> 1] = pack_bf16x2(d0, d1);
         }
-        tmem_st_32x16(tdP + lane_off + (c >> 1), pk);
-        uint8_t* rowp = sdS + r * 128;
+      }
+      uint8_t* rowp = sdS + r * 128;
+      #pragma unroll
+      for (int c = 0; c < ATTB_BQ; c += 32) {
+        uint32_t pk[16];
+        #pragma unroll
+        for (int x = 0; x < 16; ++x) pk[x] = dsk[(c >> 1) + x];
+        tmem_st_32x16(tdP + lane_off + 32 + (c >> 1), pk);
         #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const int chunk = (c >> 3) + q4;
@@ -259,58 +296,72 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_ds);
-      // dQ^T tile: lane (TMEM) index = head dim r, columns = the 64 queries
+      // dQ^T tile(s): lane (TMEM) index = head dim, columns = the 64 queries
       if (!mbar_wait(bar_dq, ph, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      uint32_t dq0[32], dq1[32];
-      tmem_ld_32x32(tdQ + lane_off, dq0);
-      tmem_ld_32x32(tdQ + lane_off + 32, dq1);
-      tmem_ld_wait();
+      const long long qstride = static_cast<long long>(p.Hq) * DQK;
+      #pragma unroll 1
+      for (int hb = 0; hb < (MLA ? 2 : 1); ++hb) {
+        uint32_t dq0[32], dq1[32];
+        const uint32_t src = hb == 0 ? tdQ : tdQb;
+        tmem_ld_32x32(src + lane_off, dq0);
+        tmem_ld_32x32(src + lane_off + 32, dq1);
+        tmem_ld_wait();
+        const int d = hb * 128 + r;
+        if (d < DQK) {
+          float* acc = p.dq_acc + (static_cast<long long>(row_base + q0) * p.Hq + head) * DQK + d;
+          #pragma unroll
+          for (int x = 0; x < 32; ++x)
+            if (q0 + x < p.S) atomicAdd(acc + x * qstride, __uint_as_float(dq0[x]));
+          #pragma unroll
+          for (int x = 0; x < 32; ++x)
+            if (q0 + 32 + x < p.S) atomicAdd(acc + (32 + x) * qstride, __uint_as_float(dq1[x]));
+        }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_dqread);
-      float* acc = p.dq_acc + (static_cast<long long>(row_base + q0) * p.Hq + head) * ATT_D + r;
-      const long long qstride = static_cast<long long>(p.Hq) * ATT_D;
-      #pragma unroll
-      for (int x = 0; x < 32; ++x)
-        if (q0 + x < p.S) atomicAdd(acc + x * qstride, __uint_as_float(dq0[x]));
-      #pragma unroll
-      for (int x = 0; x < 32; ++x)
-        if (q0 + 32 + x < p.S) atomicAdd(acc + (32 + x) * qstride, __uint_as_float(dq1[x]));
     }
     // dK, dV: one key row per thread
     if (ok) {
       if (n_it > 0) tc_fence_after();
-      __nv_bfloat16* dkp = p.dk + static_cast<long long>(row_base + kj) * p.dk_row_stride + kvh * ATT_D;
+      __nv_bfloat16* dkp = p.dk + static_cast<long long>(row_base + kj) * p.dk_row_stride + kvh * DQK;
       __nv_bfloat16* dvp = p.dv + static_cast<long long>(row_base + kj) * p.dv_row_stride + kvh * ATT_D;
       #pragma unroll 1
-      for (int c = 0; c < ATT_D; c += 32) {
+      for (int c = 0; c < DQK; c += 32) {
         uint32_t a[32], bb[32];
+        const bool has_v = c < ATT_D;
         if (n_it > 0) {
           tmem_ld_32x32(tdK + lane_off + c, a);
-          tmem_ld_32x32(tdV + lane_off + c, bb);
+          if (has_v) tmem_ld_32x32(tdV + lane_off + c, bb);
           tmem_ld_wait();
         } else {
           #pragma unroll
           for (int x = 0; x < 32; ++x) { a[x] = 0u; bb[x] = 0u; }
         }
         if (kj < p.S && p.dk_part != nullptr) {
-          float* pk = p.dk_part + (static_cast<long long>(row_base + kj) * p.Hq + head) * ATT_D + c;
-          float* pv2 = p.dv_part + (static_cast<long long>(row_base + kj) * p.Hq + head) * ATT_D + c;
+          float* pk = p.dk_part + (static_cast<long long>(row_base + kj) * p.Hq + head) * DQK + c;
           #pragma unroll
-          for (int x = 0; x < 32; x += 4) {
+          for (int x = 0; x < 32; x += 4)
             *reinterpret_cast<float4*>(pk + x) = make_float4(__uint_as_float(a[x]), __uint_as_float(a[x + 1]), __uint_as_float(a[x + 2]), __uint_as_float(a[x + 3]));
-            *reinterpret_cast<float4*>(pv2 + x) = make_float4(__uint_as_float(bb[x]), __uint_as_float(bb[x + 1]), __uint_as_float(bb[x + 2]), __uint_as_float(bb[x + 3]));
+          if (has_v) {
+            float* pv2 = p.dv_part + (static_cast<long long>(row_base + kj) * p.Hq + head) * ATT_D + c;
+            #pragma unroll
+            for (int x = 0; x < 32; x += 4)
+              *reinterpret_cast<float4*>(pv2 + x) = make_float4(__uint_as_float(bb[x]), __uint_as_float(bb[x + 1]), __uint_as_float(bb[x + 2]), __uint_as_float(bb[x + 3]));
           }
         } else if (kj < p.S) {
           #pragma unroll
-          for (int x = 0; x < 32; x += 8) {
+          for (int x = 0; x < 32; x += 8)
             *reinterpret_cast<uint4*>(dkp + c + x) = make_uint4(
                 pack_bf16x2(__uint_as_float(a[x]), __uint_as_float(a[x + 1])), pack_bf16x2(__uint_as_float(a[x + 2]), __uint_as_float(a[x + 3])),
                 pack_bf16x2(__uint_as_float(a[x + 4]), __uint_as_float(a[x + 5])), pack_bf16x2(__uint_as_float(a[x + 6]), __uint_as_float(a[x + 7])));
-            *reinterpret_cast<uint4*>(dvp + c + x) = make_uint4(
-                pack_bf16x2(__uint_as_float(bb[x]), __uint_as_float(bb[x + 1])), pack_bf16x2(__uint_as_float(bb[x + 2]), __uint_as_float(bb[x + 3])),
-                pack_bf16x2(__uint_as_float(bb[x + 4]), __uint_as_float(bb[x + 5])), pack_bf16x2(__uint_as_float(bb[x + 6]), __uint_as_float(bb[x + 7])));
+          if (has_v) {
+            #pragma unroll
+            for (int x = 0; x < 32; x += 8)
+              *reinterpret_cast<uint4*>(dvp + c + x) = make_uint4(
+                  pack_bf16x2(__uint_as_float(bb[x]), __uint_as_float(bb[x + 1])), pack_bf16x2(__uint_as_float(bb[x + 2]), __uint_as_float(bb[x + 3])),
+                  pack_bf16x2(__uint_as_float(bb[x + 4]), __uint_as_float(bb[x + 5])), pack_bf16x2(__uint_as_float(bb[x + 6]), __uint_as_float(bb[x + 7])));
           }
         }
       }

@@ -26,7 +26,9 @@ at::Tensor attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& 
                     int64_t S, double scale, bool causal, const c10::optional<at::Tensor>& kend,
                     const c10::optional<at::Tensor>& tile_min, const c10::optional<at::Tensor>& tile_max,
                     bool p_in_tmem) {
-  TORCH_CHECK(q.is_cuda() && q.size(2) == ATT_D && k.size(2) == ATT_D && v.size(2) == ATT_D, "attn_fwd: head_dim 128");
+  const int DQK = q.size(2);
+  TORCH_CHECK(q.is_cuda() && (DQK == ATT_D || DQK == 192) && k.size(2) == DQK && v.size(2) == ATT_D,
+              "attn_fwd: queries / keys 128 or 192 wide, values 128 wide");
   TORCH_CHECK(q.size(0) == B * S && k.size(0) == B * S && v.size(0) == B * S);
   TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.dim() == 3 && out.stride(2) == 1 && out.stride(1) == ATT_D);
   const c10::cuda::CUDAGuard guard(q.device());
@@ -54,6 +56,18 @@ at::Tensor attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& 
   CUtensorMap tmQ = qkv_map(q, ATT_BQ), tmK = qkv_map(k, ATT_BKV), tmV = qkv_map(v, ATT_BKV);
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   static const bool use_v1 = [] { const char* e = std::getenv("PFB_ATTN_FWD"); return e != nullptr && std::string(e) == "v1"; }();
+  if (DQK == 192) {
+    // multi-head latent attention (192-wide queries / keys, 128-wide values): one query tile per CTA
+    auto kern = attn_fwd_kernel<true, 192>;
+    constexpr int smem = AttnFwdSmem<true, 192>::TOTAL;
+    static bool cfg = false;
+    if (!cfg) { C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); cfg = true; }
+    dim3 grid1((S + ATT_BQ - 1) / ATT_BQ, Hq, B);
+    kern<<<grid1, ATT_THREADS, smem, stream>>>(tmQ, tmK, tmV, p);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    count_launch();
+    return lse;
+  }
   if (!use_v1) {
     // two query tiles per CTA, softmax of one tile under the products of the other
     constexpr int smem = AttnFwd2Smem::TOTAL;

@@ -39,19 +39,24 @@ struct AttnFwdParams {
   int* status;
 };
 
-template <bool P_TMEM>
+// DQK is the width of queries and keys (128, or 192 for multi-head latent attention whose values stay 128 wide: the
+// reference's call sites are paddleformers/transformers/deepseek_v3/modeling.py:542-801); Q and K tiles are stored as
+// DQK / 64 slabs of [128 rows x 64 columns] (128-byte swizzle), V as two.
+template <bool P_TMEM, int DQK = ATT_D>
 struct AttnFwdSmem {
-  static constexpr int TILE = ATT_BQ * ATT_D * 2;  // 32 KB
-  static constexpr int Q_OFF = 0, K_OFF = TILE, V_OFF = 2 * TILE, P_OFF = 3 * TILE;
-  static constexpr int AUX_OFF = P_TMEM ? 3 * TILE : 4 * TILE;
+  static constexpr int TILE = ATT_BQ * ATT_D * 2;      // 32 KB: V, P
+  static constexpr int SLAB = ATT_BQ * 64 * 2;         // 16 KB
+  static constexpr int QK_TILE = (DQK / 64) * SLAB;
+  static constexpr int Q_OFF = 0, K_OFF = QK_TILE, V_OFF = 2 * QK_TILE, P_OFF = 2 * QK_TILE + TILE;
+  static constexpr int AUX_OFF = P_TMEM ? P_OFF : P_OFF + TILE;
   static constexpr int TOTAL = AUX_OFF + 2048 + 256 + 1024;
 };
 
-template <bool P_TMEM>
-__global__ void __launch_bounds__(ATT_THREADS, P_TMEM ? 2 : 1)
+template <bool P_TMEM, int DQK = ATT_D>
+__global__ void __launch_bounds__(ATT_THREADS, (P_TMEM && DQK == ATT_D) ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
-  using SM = AttnFwdSmem<P_TMEM>;
+  using SM = AttnFwdSmem<P_TMEM, DQK>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem + SM::Q_OFF; uint8_t* sK = smem + SM::K_OFF; uint8_t* sV = smem + SM::V_OFF;
@@ -96,12 +101,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(ATT_BQ, ATT_BKV, false, false, 1);
       constexpr uint32_t idesc_o = make_idesc(ATT_BQ, ATT_D, false, true, 1);
-      mbar_expect_tx(bar_q, SM::TILE);
-      tma_load_3d(sQ, &tmQ, bar_q, 0, head, row_base + q0);
-      tma_load_3d(sQ + SM::TILE / 2, &tmQ, bar_q, 64, head, row_base + q0);
-      mbar_expect_tx(bar_k, SM::TILE);
-      tma_load_3d(sK, &tmK, bar_k, 0, kvh, row_base + j_lo * ATT_BKV);
-      tma_load_3d(sK + SM::TILE / 2, &tmK, bar_k, 64, kvh, row_base + j_lo * ATT_BKV);
+      mbar_expect_tx(bar_q, SM::QK_TILE);
+      #pragma unroll
+      for (int sl = 0; sl < DQK / 64; ++sl) tma_load_3d(sQ + sl * SM::SLAB, &tmQ, bar_q, 64 * sl, head, row_base + q0);
+      mbar_expect_tx(bar_k, SM::QK_TILE);
+      #pragma unroll
+      for (int sl = 0; sl < DQK / 64; ++sl) tma_load_3d(sK + sl * SM::SLAB, &tmK, bar_k, 64 * sl, kvh, row_base + j_lo * ATT_BKV);
       mbar_expect_tx(bar_v, SM::TILE);
       tma_load_3d(sV, &tmV, bar_v, 0, kvh, row_base + j_lo * ATT_BKV);
       tma_load_3d(sV + SM::TILE / 2, &tmV, bar_v, 64, kvh, row_base + j_lo * ATT_BKV);
@@ -111,17 +116,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(bar_k, ph, abort_flag, p.status, PFB_ERR_WAIT_FULL)) break;
         tc_fence_after();
         #pragma unroll
-        for (int k = 0; k < ATT_D / 16; ++k) {
-          const uint32_t off = (k >> 2) * (SM::TILE / 2) + (k & 3) * 32;
+        for (int k = 0; k < DQK / 16; ++k) {
+          const uint32_t off = (k >> 2) * SM::SLAB + (k & 3) * 32;
           tc_mma_f16_ss(tS, make_smem_desc_sw128(smem_u32(sQ) + off, 16, 1024),
                         make_smem_desc_sw128(smem_u32(sK) + off, 16, 1024), idesc_s, k != 0);
         }
         tc_commit(bar_s);
         if (!mbar_wait(bar_s, ph, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)) break;
         if (j < j_hi) {
-          mbar_expect_tx(bar_k, SM::TILE);
-          tma_load_3d(sK, &tmK, bar_k, 0, kvh, row_base + (j + 1) * ATT_BKV);
-          tma_load_3d(sK + SM::TILE / 2, &tmK, bar_k, 64, kvh, row_base + (j + 1) * ATT_BKV);
+          mbar_expect_tx(bar_k, SM::QK_TILE);
+          #pragma unroll
+          for (int sl = 0; sl < DQK / 64; ++sl) tma_load_3d(sK + sl * SM::SLAB, &tmK, bar_k, 64 * sl, kvh, row_base + (j + 1) * ATT_BKV);
         }
         if (!mbar_wait(bar_p, ph, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)) break;
         if (!mbar_wait(bar_v, ph, abort_flag, p.status, PFB_ERR_WAIT_FULL)) break;

@@ -46,9 +46,10 @@ def flash_attention_backward(dout, q, k, v, out, lse, causal, kend, kmin, kmax, 
     k/v [B,S,Hkv,D], lse [B,Hq,S] (natural log)."""
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]
-    dout = dout.reshape(B, S, Hq, D)
-    out = out.reshape(B, S, Hq, D)
-    if q.is_cuda and D == 128 and _has_kernel("attn_bwd"):
+    Dv = v.shape[-1]
+    dout = dout.reshape(B, S, Hq, Dv)
+    out = out.reshape(B, S, Hq, Dv)
+    if q.is_cuda and Dv == 128 and (D == 128 or (D == 192 and Hq == Hkv)) and _has_kernel("attn_bwd"):
         dq = torch.empty_like(q)
         dk = torch.empty_like(k)
         dv = torch.empty_like(v)

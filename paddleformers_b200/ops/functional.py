@@ -596,8 +596,9 @@ class _FlashAttnFn(torch.autograd.Function):
     def forward(ctx, q, k, v, causal, kend, scale):
         B, S, Hq, D = q.shape
         Hkv = k.shape[2]
-        q3, k3, v3 = q.reshape(B * S, Hq, D), k.reshape(B * S, Hkv, D), v.reshape(B * S, Hkv, D)
-        out = torch.empty((B * S, Hq, D), dtype=q.dtype, device=q.device)
+        Dv = v.shape[-1]
+        q3, k3, v3 = q.reshape(B * S, Hq, D), k.reshape(B * S, Hkv, D), v.reshape(B * S, Hkv, Dv)
+        out = torch.empty((B * S, Hq, Dv), dtype=q.dtype, device=q.device)
         kmin = kmax = None
         if kend is not None:
             kend = kend.to(torch.int32).contiguous()
@@ -605,7 +606,7 @@ class _FlashAttnFn(torch.autograd.Function):
         lse = _ops().attn_fwd(q3, k3, v3, out, B, S, scale, causal, kend, kmin, kmax, _attn_backend["p_in_tmem"])
         ctx.save_for_backward(q, k, v, out, lse, kend if kend is not None else torch.empty(0), kmin if kmin is not None else torch.empty(0), kmax if kmax is not None else torch.empty(0))
         ctx.meta = (causal, scale, kend is not None)
-        return out.view(B, S, Hq, D)
+        return out.view(B, S, Hq, Dv)
 
     @staticmethod
     def backward(ctx, dout):
@@ -624,7 +625,9 @@ def flash_attention(q, k, v, causal: bool = True, kend: Optional[torch.Tensor] =
     visible to query rows i with j <= i < kend[b, j])."""
     D = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if use_cuda_kernels(q) and q.dtype == torch.bfloat16 and D == 128 and v.shape[-1] == 128:
+    # 128-wide heads, or multi-head latent attention (192-wide queries / keys with as many key heads as query heads)
+    if use_cuda_kernels(q) and q.dtype == torch.bfloat16 and v.shape[-1] == 128 and (
+            D == 128 or (D == 192 and q.shape[2] == k.shape[2] and os.environ.get("PFB_MLA_KERNEL", "1") != "0")):
         return _FlashAttnFn.apply(q, k, v, causal, kend, scale)
     if use_cuda_kernels(q) and q.dtype == torch.bfloat16:
         from . import attention_bwd

@@ -99,3 +99,24 @@ def test_attention_backward_deterministic_mode_is_bitwise_reproducible(F):
     for a, b in zip(*runs):
         assert torch.equal(a, b)
     assert _rel_err(runs[0][0], qr.grad) < 3e-2 and _rel_err(runs[0][1], kr.grad) < 3e-2
+
+
+@pytest.mark.parametrize("B,S,H,causal,docs", [(1, 384, 4, True, False), (2, 200, 2, True, True), (1, 520, 3, False, False)])
+def test_latent_attention_192_wide_keys_128_wide_values(F, B, S, H, causal, docs):
+    """Multi-head latent attention shapes (queries / keys 192 wide, values 128 wide) on the tcgen05 kernels, forward and
+    backward, against the fp32 reference."""
+    torch.manual_seed(4)
+    q = torch.randn(B, S, H, 192, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(B, S, H, 192, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(B, S, H, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    kend = _doc_kend(B, S, "cuda", 3) if docs else None
+    out = F.flash_attention(q, k, v, causal=causal, kend=kend)
+    assert out.shape == (B, S, H, 128)
+    g = torch.randn_like(out)
+    out.backward(g)
+    F.check_kernel_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = F.attention_reference(qr, kr, vr, causal=causal, kend=kend)
+    ref.backward(g.float())
+    assert _rel_err(out, ref) < 2e-2
+    assert _rel_err(q.grad, qr.grad) < 3e-2 and _rel_err(k.grad, kr.grad) < 3e-2 and _rel_err(v.grad, vr.grad) < 3e-2
