@@ -61,11 +61,36 @@ __global__ void shard_wait_kernel(const int* __restrict__ flags, int kind, int n
   shard_wait_all(flags, kind, n, *epoch_ptr, status);
 }
 
-// out slice (local gradient buffer, elements [lo, lo + cnt)) = scale * sum_q grad_q[lo + i]; norm_acc += sum of squares.
+// Sum of a value over the block in a fixed order (warp butterflies, then the warp sums): the same tree as the squared
+// norm kernel of the unfused path, so that both paths give the same bits for the same slice.
+__device__ __forceinline__ float shard_block_sum(float v, float* red) {
+  #pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float r = l < nw ? red[l] : 0.f;
+  #pragma unroll
+  for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  return r;
+}
+
+// norm_acc[0] += sum of the per-block partials, in index order
+__global__ void shard_norm_finish_kernel(const float* __restrict__ partial, int P, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < P; i += blockDim.x) s += partial[i];
+  s = shard_block_sum(s, red);
+  if (threadIdx.x == 0) out[0] += s;
+}
+
+// out slice (local gradient buffer, elements [lo, lo + cnt)) = scale * sum_q grad_q[lo + i]; partial[blockIdx.x] = this
+// block's share of the slice's squared norm (no atomics: the sum is the same on every run).
 __global__ void __launch_bounds__(256) shard_reduce_kernel(ShardPeers peers, int n, int rank, long long lo, long long cnt, float scale,
-                                                           float* __restrict__ out, float* __restrict__ norm_acc,
+                                                           float* __restrict__ out, float* __restrict__ partial,
                                                            const int* __restrict__ epoch_ptr, int* status) {
-  if (!shard_wait_all(peers.flags[rank], 0, n, *epoch_ptr, status)) return;
+  if (!shard_wait_all(peers.flags[rank], 0, n, *epoch_ptr, status)) { if (threadIdx.x == 0) partial[blockIdx.x] = 0.f; return; }
   const long long nv = cnt >> 2;
   float sq = 0.f;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nv;
@@ -82,17 +107,9 @@ __global__ void __launch_bounds__(256) shard_reduce_kernel(ShardPeers peers, int
     reinterpret_cast<float4*>(out + lo)[i] = acc;
     sq += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
   }
-  // block reduction of the squared norm, one atomic per block
-  __shared__ float s_part[8];
-  #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = sq;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float t = 0.f;
-    for (int w = 0; w < 8; ++w) t += s_part[w];
-    atomicAdd(norm_acc, t);
-  }
+  __shared__ float red[32];
+  sq = shard_block_sum(sq, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = sq;
 }
 
 // AdamW on the slice; the bf16 weights go to elements [lo, lo + cnt) of every rank's parameter buffer.
@@ -142,9 +159,10 @@ static ShardPeers make_shard_peers(const at::Tensor& grad_ptrs, const at::Tensor
   return sp;
 }
 
+// the grid of the squared-norm kernel of the unfused path (same partition of the slice -> same partial sums)
 static int shard_grid(long long cnt) {
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-  return static_cast<int>(std::max<long long>(1, std::min<long long>((cnt / 4 + 255) / 256, static_cast<long long>(sms) * 8)));
+  return static_cast<int>(std::max<long long>(1, std::min<long long>((cnt / 4 + 255) / 256 + 1, static_cast<long long>(sms) * 8)));
 }
 
 void shard_signal(const at::Tensor& grad_ptrs, const at::Tensor& param_ptrs, const at::Tensor& flag_ptrs, int64_t rank, int64_t kind,
@@ -172,11 +190,16 @@ void shard_reduce(at::Tensor& local_grad, const at::Tensor& grad_ptrs, const at:
   TORCH_CHECK(norm_acc.scalar_type() == at::kFloat && norm_acc.numel() >= 1);
   const c10::cuda::CUDAGuard guard(local_grad.device());
   const int n = grad_ptrs.numel();
-  shard_reduce_kernel<<<shard_grid(cnt), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+  const int P = shard_grid(cnt);
+  at::Tensor partial = at::empty({P}, norm_acc.options());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  shard_reduce_kernel<<<P, 256, 0, stream>>>(
       make_shard_peers(grad_ptrs, param_ptrs, flag_ptrs, n), n, static_cast<int>(rank), lo, cnt, static_cast<float>(scale),
-      local_grad.data_ptr<float>(), norm_acc.data_ptr<float>(), epoch.data_ptr<int>(), status_word());
+      local_grad.data_ptr<float>(), partial.data_ptr<float>(), epoch.data_ptr<int>(), status_word());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
-  count_launch();
+  shard_norm_finish_kernel<<<1, 256, 0, stream>>>(partial.data_ptr<float>(), P, norm_acc.data_ptr<float>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch(2);
 }
 
 void adamw_push(at::Tensor& master, at::Tensor& m, at::Tensor& v, const at::Tensor& local_grad, const at::Tensor& grad_ptrs,
