@@ -184,8 +184,13 @@ def run_config(args, model_name, W, K, do_e2e, dev, world, rank, local_rank):
         par = f"tp{world}" + ("+sp" if world > 1 else "") + "+sharding1(stage1)"
         dp_world = 1
     if model_name == "deepseek-v3-4l":
-        targs["fp8"] = True
+        cfg.fp8 = "e4m3"          # block-scaled e4m3 GEMMs for the dense projections and the experts
         GB = min(GB, 32)
+    if is_moe:
+        # Random-initialised deep networks send nearly all tokens to a few experts; like Megatron's
+        # --moe-router-force-load-balancing the benchmark draws the experts from random logits. The gate GEMM, the routing
+        # kernel, the exchange and the expert work per token are those of a trained, balanced model.
+        cfg.moe_router_force_load_balancing = True
     MB = args.micro_batch or 1
     assert GB % (dp_world * MB) == 0, "global batch must be a multiple of data ranks x micro batch"
     accum = GB // (dp_world * MB)
@@ -201,6 +206,10 @@ def run_config(args, model_name, W, K, do_e2e, dev, world, rank, local_rank):
     cfg.tensor_model_parallel_size = ta.tensor_model_parallel_size
     torch.manual_seed(1234 + ta.parallel_state.coord["mp"] + 17 * ta.parallel_state.rank_in("ep"))
     model = AutoModelForCausalLM.from_config(cfg, dtype=torch.bfloat16, device=dev)
+    if getattr(cfg, "fp8", None):
+        from paddleformers_b200.quantization.fp8 import convert_linears_to_fp8
+
+        convert_linears_to_fp8(model)
     doc_range = (128, 4096) if model_name == "qwen3-30b-a3b" else None
     ds = SyntheticCausalLMDataset(cfg.vocab_size, S, num_samples=GB * (W + K), seed=7, doc_len_range=doc_range)
 
@@ -344,6 +353,9 @@ def run_config(args, model_name, W, K, do_e2e, dev, world, rank, local_rank):
                 from paddleformers_b200.parallel import fused_ep
 
                 out["config"]["ep_dispatch"] = cfg.moe_token_dispatcher_type
+                out["config"]["routing"] = "experts drawn from random logits (force-balanced, as Megatron's benchmark flag); " \
+                                           "gate GEMM, routing kernel and expert work per token unchanged"
+                out["moe_dropped_pairs"] = int(fused_ep.dropped_pairs(reset=True))
                 out["fused_ep_calls"] = dict(fused_ep.STATS)
         if args.layers:
             out["invalid"] = "truncated model (--layers): debug run, not a benchmark value"

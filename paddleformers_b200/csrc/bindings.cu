@@ -22,7 +22,7 @@ int* status_word() {
   std::lock_guard<std::mutex> lk(g_mu);
   auto it = g_status.find(dev);
   if (it != g_status.end()) return it->second;
-  // 16-byte block: [0] status, [1] reserved, [2..3] wait budget in ns (0 = the kernels' default of one second)
+  // 16-byte block: [0] status, [1] rows dropped by the expert-parallel dispatcher (receive buffer full), [2..3] wait budget in ns (0 = the kernels' default of one second)
   int* p = nullptr;
   C10_CUDA_CHECK(cudaMalloc(&p, 4 * sizeof(int)));
   C10_CUDA_CHECK(cudaMemset(p, 0, 4 * sizeof(int)));
@@ -44,12 +44,23 @@ int read_status(bool reset) {
   if (reset && v != 0) C10_CUDA_CHECK(cudaMemset(p, 0, sizeof(int)));
   return v;
 }
+// Routed (token, expert) pairs that the expert-parallel dispatcher dropped since the last reset because the destination's
+// receive buffer was full (capacity-factor semantics: a dropped pair contributes nothing to the token's output).
+int64_t read_drop_count(bool reset) {
+  int* p = status_word();
+  int v = 0;
+  C10_CUDA_CHECK(cudaStreamSynchronize(at::cuda::getCurrentCUDAStream()));
+  C10_CUDA_CHECK(cudaMemcpy(&v, p + 1, sizeof(int), cudaMemcpyDeviceToHost));
+  if (reset && v != 0) C10_CUDA_CHECK(cudaMemset(p + 1, 0, sizeof(int)));
+  return v;
+}
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 int64_t launch_count(bool reset) { return reset ? g_launches.exchange(0) : g_launches.load(); }
 
 static int64_t op_read_status(bool reset) { return read_status(reset); }
 static void op_set_wait_budget(double seconds) { set_wait_budget(seconds); }
 static int64_t op_launch_count(bool reset) { return launch_count(reset); }
+static int64_t op_read_drop_count(bool reset) { return read_drop_count(reset); }
 
 // ---- declarations of the ops implemented in the other translation units ---------------------------------------
 void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, bool b_mn, int64_t epi,
@@ -90,6 +101,7 @@ TORCH_LIBRARY(pfb200, m) {
   m.def("read_status(bool reset) -> int", &pfb::op_read_status);
   m.def("set_wait_budget(float seconds) -> ()", &pfb::op_set_wait_budget);
   m.def("launch_count(bool reset) -> int", &pfb::op_launch_count);
+  m.def("read_drop_count(bool reset) -> int", &pfb::op_read_drop_count);
   m.def("gemm(Tensor a, Tensor b, Tensor(a!) out, bool a_mn, bool b_mn, int epi, Tensor? out2, Tensor? block_expert, "
         "int n_per_expert, int force_bn) -> ()", &pfb::gemm);
   m.def("gemm_wgrad_grouped(Tensor dy, Tensor x, Tensor(a!) out, Tensor expert_rows) -> ()", &pfb::gemm_wgrad_grouped);

@@ -14,8 +14,9 @@
 //                 peer loads and writes their (optionally weighted) sum - the combine, and the backward of dispatch.
 //                 Optionally also returns the k dot products <row, g[token]> (gradient of the routing weights).
 //
-// All flags are epoch-valued; all waits are bounded and report PFB_ERR_WAIT_PEER; a slot beyond the receive capacity
-// reports PFB_ERR_BOUNDS and the row is skipped.
+// All flags are epoch-valued; all waits are bounded and report PFB_ERR_WAIT_PEER. A pair whose slot lies beyond the
+// receive capacity is DROPPED (capacity-factor semantics: it is not sent and contributes nothing to the combine, forward
+// and backward) and counted in the second word of the status block, which the host reads with read_drop_count.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
@@ -78,10 +79,9 @@ __global__ void ep_exchange_kernel(EpTables tabs, const int* __restrict__ my_cou
       for (int s = 0; s < ep; ++s) tot += s_cnt[s * EL + e];
       s_seg[e] = pos;
       int padded = (tot + 127) / 128 * 128;
-      if (pos + padded > n_blocks * 128) {   // receive buffer too small: clamp so that no consumer leaves the buffer
-        padded = max(0, n_blocks * 128 - pos);
-        atomicCAS(status, 0, PFB_ERR_BOUNDS);
-      }
+      // receive buffer too small: clamp so that no consumer leaves the buffer; the senders drop (and count) the pairs
+      // whose slot falls beyond it
+      if (pos + padded > n_blocks * 128) padded = max(0, n_blocks * 128 - pos);
       expert_rows[2 * e] = pos;
       expert_rows[2 * e + 1] = padded;
       pos += padded;
@@ -139,8 +139,8 @@ __global__ void ep_push_rows_kernel(const __nv_bfloat16* __restrict__ x, const l
     // the recorded slot is reused, because the table already belongs to a later exchange
     const int slot = offsets ? offsets[d * EL + el] + rank_in_expert[p] : pair_slot[p];
     if (offsets && lane == 0) pair_slot[p] = slot;
-    if (slot >= capacity_rows) {
-      if (lane == 0) atomicCAS(status, 0, PFB_ERR_BOUNDS);
+    if (slot >= capacity_rows) {   // dropped pair: nothing is sent, the combine adds nothing for it; counted once, in the forward pass
+      if (lane == 0 && offsets) atomicAdd(status + 1, 1);
       continue;
     }
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<long long>(p / k) * H);

@@ -227,16 +227,6 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
 // ---------------------------------------------------------------------------------------------------------------
 // quantisation
 // ---------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float fp8_block_scale(float amax, bool ue8m0) {
-  float scale = fmaxf(amax, 1e-12f) / 448.f;
-  if (ue8m0) {   // next power of two (what an UE8M0 byte holds), by exponent arithmetic: exact, unlike ceil(log2())
-    scale = fmaxf(scale, 1.17549435e-38f);
-    const uint32_t bits = __float_as_uint(scale);
-    scale = __uint_as_float(((bits >> 23) + ((bits & 0x7FFFFFu) ? 1u : 0u)) << 23);
-  }
-  return scale;
-}
-
 // One warp per (row, 128-column block): q[T, K] e4m3 and scales stored transposed, s_t[K/128, T].
 __global__ void fp8_quant_act_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q,
                                      float* __restrict__ s_t, int T, int K, bool ue8m0) {

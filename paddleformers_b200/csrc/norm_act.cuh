@@ -93,7 +93,7 @@ __global__ void rms_norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const _
 // dw_partial[blockIdx.x, H] (fp32 scratch); rms_norm_dw_reduce_kernel folds the partials.
 // blockDim.x * 8 * PER_THREAD >= H is required (PER_THREAD chunks of 8 columns per thread).
 template <int PER_THREAD>
-__global__ void rms_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(256, PER_THREAD <= 2 ? 4 : 1) rms_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                     const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                                     const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                                     float* __restrict__ dw_partial, int T, int H, long long dy_stride) {
@@ -159,13 +159,32 @@ __global__ void rms_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const 
 }
 
 // dw[h] (+)= sum_p partial[p, h]; accumulate != 0 adds to the existing fp32 value (main_grad semantics).
+// One block of 256 threads per 32 columns: 8 row groups read 128-byte lines, each with 4 independent partial sums; the
+// groups are combined through shared memory in a fixed order.
 __global__ void rms_norm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int P, int H,
                                           int accumulate) {
-  const int h = blockIdx.x * blockDim.x + threadIdx.x;
-  if (h >= H) return;
-  float s = 0.f;
-  for (int p = 0; p < P; ++p) s += partial[static_cast<long long>(p) * H + h];
-  dw[h] = accumulate ? dw[h] + s : s;
+  __shared__ float red[8][33];
+  const int col = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int h = blockIdx.x * 32 + col;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (h < H) {
+    int p = grp;
+    for (; p + 24 < P; p += 32) {
+      s0 += partial[static_cast<long long>(p) * H + h];
+      s1 += partial[static_cast<long long>(p + 8) * H + h];
+      s2 += partial[static_cast<long long>(p + 16) * H + h];
+      s3 += partial[static_cast<long long>(p + 24) * H + h];
+    }
+    for (; p < P; p += 8) s0 += partial[static_cast<long long>(p) * H + h];
+  }
+  red[grp][col] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (grp == 0 && h < H) {
+    float s = 0.f;
+    #pragma unroll
+    for (int g = 0; g < 8; ++g) s += red[g][col];
+    dw[h] = accumulate ? dw[h] + s : s;
+  }
 }
 
 // act[t, i] = silu(gu[t, i]) * gu[t, I + i]
@@ -242,6 +261,40 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict
     const float x1 = __bfloat162float(base[i]), x2 = __bfloat162float(base[i + half]);
     base[i] = __float2bfloat16(x1 * c - x2 * s);
     base[i + half] = __float2bfloat16(x2 * c + x1 * s);
+  }
+}
+
+// The same rotation with 16-byte accesses: one thread rotates 8 adjacent pairs (x1[i..i+8), x2[i..i+8)). Needs
+// rot % 16 == 0, D % 8 == 0, row_stride % 8 == 0 and a 16-byte aligned base.
+__global__ void rope_vec8_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict__ pos, const float* __restrict__ cs,
+                                 const float* __restrict__ sn, int T, int n_heads, int D, int rot, long long row_stride,
+                                 float sign) {
+  const int half = rot >> 1, hv = half >> 3;
+  const int per_row = n_heads * hv;
+  const long long total = static_cast<long long>(T) * per_row;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(idx / per_row);
+    const int r = static_cast<int>(idx - static_cast<long long>(t) * per_row);
+    const int h = r / hv, i = (r - h * hv) * 8;
+    const int p = pos ? pos[t] : t;
+    const float4* c4 = reinterpret_cast<const float4*>(cs + static_cast<long long>(p) * half + i);
+    const float4* s4 = reinterpret_cast<const float4*>(sn + static_cast<long long>(p) * half + i);
+    const float4 ca = c4[0], cb = c4[1], sa = s4[0], sb = s4[1];
+    const float c[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+    const float sv[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
+    __nv_bfloat16* base = x + t * row_stride + static_cast<long long>(h) * D + i;
+    const bf16x8 a = *reinterpret_cast<const bf16x8*>(base), b = *reinterpret_cast<const bf16x8*>(base + half);
+    bf16x8 oa, ob;
+    #pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f1 = __bfloat1622float2(a.v[j]), f2 = __bfloat1622float2(b.v[j]);
+      const float s0 = sign * sv[2 * j], s1 = sign * sv[2 * j + 1];
+      oa.v[j] = __float22bfloat162_rn(make_float2(f1.x * c[2 * j] - f2.x * s0, f1.y * c[2 * j + 1] - f2.y * s1));
+      ob.v[j] = __float22bfloat162_rn(make_float2(f2.x * c[2 * j] + f1.x * s0, f2.y * c[2 * j + 1] + f1.y * s1));
+    }
+    *reinterpret_cast<bf16x8*>(base) = oa;
+    *reinterpret_cast<bf16x8*>(base + half) = ob;
   }
 }
 

@@ -50,7 +50,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> rms_norm_fwd(const at::Tensor& x,
 
 // dx (+= dres), dw: dw is accumulated into `dw_out` (fp32 [H]) when accumulate is true, else overwritten.
 // `scratch` is a caller-provided fp32 buffer of at least rms_norm_bwd_scratch_rows() * H elements.
-int64_t rms_norm_bwd_scratch_rows() { return static_cast<int64_t>(num_sms()) * 2; }
+int64_t rms_norm_bwd_scratch_rows() { return static_cast<int64_t>(num_sms()) * 4; }
 
 at::Tensor rms_norm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w, const at::Tensor& rstd,
                         const c10::optional<at::Tensor>& dres, at::Tensor& dw_out, bool accumulate,
@@ -77,7 +77,7 @@ at::Tensor rms_norm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Ten
   else if (per <= 4) launch(std::integral_constant<int, 4>{});
   else launch(std::integral_constant<int, 8>{});
   C10_CUDA_KERNEL_LAUNCH_CHECK();
-  rms_norm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, cur_stream()>>>(scratch.data_ptr<float>(), dw_out.data_ptr<float>(),
+  rms_norm_dw_reduce_kernel<<<(H + 31) / 32, 256, 0, cur_stream()>>>(scratch.data_ptr<float>(), dw_out.data_ptr<float>(),
                                                                       P, H, accumulate ? 1 : 0);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch(2);
@@ -128,9 +128,15 @@ void rope_inplace(at::Tensor& x, const c10::optional<at::Tensor>& pos, const at:
   if (pos.has_value()) { TORCH_CHECK(pos->scalar_type() == at::kInt && pos->numel() == T); pp = pos->data_ptr<int>(); }
   else TORCH_CHECK(cos.size(0) >= T, "rope: cos/sin table shorter than the sequence");
   const long long work = static_cast<long long>(T) * n_heads * (rot / 2);
-  rope_kernel<<<ew_grid(work, 256), 256, 0, cur_stream()>>>(bfm(x), pp, cos.data_ptr<float>(), sin.data_ptr<float>(), T,
-                                                           static_cast<int>(n_heads), static_cast<int>(D),
-                                                           static_cast<int>(rot), x.stride(0), backward ? -1.f : 1.f);
+  const bool vec = rot % 16 == 0 && D % 8 == 0 && x.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0;
+  if (vec)
+    rope_vec8_kernel<<<ew_grid(work / 8, 256), 256, 0, cur_stream()>>>(bfm(x), pp, cos.data_ptr<float>(), sin.data_ptr<float>(), T,
+                                                                      static_cast<int>(n_heads), static_cast<int>(D),
+                                                                      static_cast<int>(rot), x.stride(0), backward ? -1.f : 1.f);
+  else
+    rope_kernel<<<ew_grid(work, 256), 256, 0, cur_stream()>>>(bfm(x), pp, cos.data_ptr<float>(), sin.data_ptr<float>(), T,
+                                                             static_cast<int>(n_heads), static_cast<int>(D),
+                                                             static_cast<int>(rot), x.stride(0), backward ? -1.f : 1.f);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
 }

@@ -20,6 +20,7 @@ enum : int {
   PFB_ERR_WAIT_TMEM_EMPTY = 4, // MMA warp gave up waiting for a free accumulator
   PFB_ERR_WAIT_PEER = 5,       // a flag owned by another rank never arrived
   PFB_ERR_BOUNDS = 6,          // a checked index was outside its buffer
+  PFB_ERR_SCALE_NOT_POW2 = 7,  // a block scale handed to the tensor-core-scaled fp8 GEMM was not a power of two
 };
 
 // Wait budget. The status word handed to every kernel is the first int of a 16-byte block
@@ -234,6 +235,17 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N, bool a_mn_major,
          (static_cast<uint32_t>(a_mn_major ? 1 : 0) << 15) |
          (static_cast<uint32_t>(b_mn_major ? 1 : 0) << 16) |
          (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+// Scale of one fp8 (e4m3) quantisation block with absolute maximum `amax`: amax / 448, optionally rounded up to a power of two.
+__device__ __forceinline__ float fp8_block_scale(float amax, bool ue8m0) {
+  float scale = fmaxf(amax, 1e-12f) / 448.f;
+  if (ue8m0) {   // next power of two (what an UE8M0 byte holds), by exponent arithmetic: exact, unlike ceil(log2())
+    scale = fmaxf(scale, 1.17549435e-38f);
+    const uint32_t bits = __float_as_uint(scale);
+    scale = __uint_as_float(((bits >> 23) + ((bits & 0x7FFFFFu) ? 1u : 0u)) << 23);
+  }
+  return scale;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

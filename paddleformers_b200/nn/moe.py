@@ -74,6 +74,18 @@ class _FusedRouteFn(torch.autograd.Function):
         return (dlogits,) + (None,) * 10
 
 
+class _RandomLogits(torch.autograd.Function):
+    """Standard-normal logits in the forward pass, the incoming gradient unchanged in the backward pass."""
+
+    @staticmethod
+    def forward(ctx, logits):
+        return torch.randn_like(logits)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g
+
+
 class TopkRouter(nn.Module):
     def _capacity_mask(self, idx: torch.Tensor, w: torch.Tensor, T: int, E: int) -> torch.Tensor:
         """1 for routed pairs inside their expert's capacity, 0 for dropped ones; no host synchronisation."""
@@ -140,7 +152,7 @@ class TopkRouter(nn.Module):
         if not (logits.is_cuda and os.environ.get("PFB_FUSED_ROUTER", "1") != "0" and F.use_cuda_kernels(logits)
                 and hasattr(torch.ops.pfb200, "moe_route_fwd")):
             return False
-        if self.scoring not in ("softmax", "sigmoid") or self.bias is not None or self.force_balance or self.capacity_factor > 0:
+        if self.scoring not in ("softmax", "sigmoid") or self.bias is not None or self.capacity_factor > 0:
             return False
         if self.z_coef > 0 or self.balance_type not in ("aux_loss", "none") or E % 32 != 0 or E > 256 or self.top_k > 32:
             return False
@@ -153,6 +165,11 @@ class TopkRouter(nn.Module):
         logits = F.router_logits(x2d, self.weight)
         self.last_plan = None
         if self._fused_ok(logits):
+            if self.force_balance:
+                # benchmarking with random-initialised weights: the experts are chosen from random logits so that every
+                # expert gets its share of the tokens (a deep random network routes almost all tokens to a few experts);
+                # the gate GEMM, the routing kernel and the work per token are unchanged
+                logits = _RandomLogits.apply(logits)
             want_aux = self.training and self.aux_coef > 0 and self.balance_type != "none"
             idx, w, aux, rank, counts = _FusedRouteFn.apply(
                 logits.contiguous(), self.e_score_correction_bias, self.top_k, self.scoring == "sigmoid", self.n_group,
@@ -451,7 +468,8 @@ class _GroupedMlpFn(torch.autograd.Function):
 
 class _GroupedMlpFp8Fn(torch.autograd.Function):
     """Expert MLP with block-scaled e4m3 GEMMs: activations are quantised per 1x128 block on the fly, weights come from
-    the per-step cache; the SwiGLU runs in bf16 between the two GEMMs. Backward: input gradients through fp8 GEMMs on the
+    the per-step cache; the SwiGLU and the quantisation of its result are one kernel, and so are its backward and the
+    quantisation of the gate / up gradients. Backward: input gradients through fp8 GEMMs on the
     transposed weight copies, weight gradients through the bf16 K-grouped kernel
     (paddleformers/transformers/fp8_utils.py:913-1190, FP8GroupGemmMlpFunctionNode)."""
 
@@ -464,8 +482,7 @@ class _GroupedMlpFp8Fn(torch.autograd.Function):
         xq, xs_t = quant_act_kernel(rows)
         raw = torch.empty((R, N2), dtype=rows.dtype, device=rows.device)
         fp8_gemm(xq, xs_t, cache["gu_q"], cache["gu_s"], block_expert, N2, out=raw)
-        act = torch.ops.pfb200.swiglu_fwd(raw)
-        aq, as_t = quant_act_kernel(act)
+        aq, as_t, _ = torch.ops.pfb200.swiglu_quant_fwd(raw, None, True, False)    # SwiGLU and 1x128 quantisation in one pass
         if out is None:
             out = torch.zeros((R, H), dtype=rows.dtype, device=rows.device)
         else:
@@ -488,8 +505,7 @@ class _GroupedMlpFp8Fn(torch.autograd.Function):
         dq, ds_t = quant_act_kernel(dout)
         dact = torch.empty((R, I), dtype=rows.dtype, device=rows.device)
         fp8_gemm(dq, ds_t, cache["dnT_q"], cache["dnT_s"], block_expert, I, out=dact)
-        dgu, act = torch.ops.pfb200.swiglu_bwd(dact, raw, True)
-        gq, gs_t = quant_act_kernel(dgu)
+        dgu, gq, gs_t, act, _ = torch.ops.pfb200.swiglu_quant_bwd(dact, raw, None, True, True)
         drows = ctx.grad_rows_out if ctx.grad_rows_out is not None else torch.zeros((R, H), dtype=rows.dtype, device=rows.device)
         fp8_gemm(gq, gs_t, cache["guT_q"], cache["guT_s"], block_expert, H, out=drows)
         table = ctx.expert_rows if ctx.expert_rows is not None else expert_row_table(block_expert, E)

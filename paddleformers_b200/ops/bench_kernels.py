@@ -144,6 +144,22 @@ def bench_elementwise(rows):
     ms = timeit(lambda: torch.ops.pfb200.rms_norm_fwd(x, None, w, 1e-5))
     rows.append(f"rms_norm fwd [{T},{H}]: {2 * x.numel() * 2 / ms / 1e6:7.1f} GB/s ({2 * x.numel() * 2 / ms / 1e6 / peaks['hbm_gbs']:.2f} of measured copy)")
     print(rows[-1], flush=True)
+    # backward: reads dy, x and the residual-stream gradient, writes dx; the weight-gradient partials are folded by a second kernel
+    ops = torch.ops.pfb200
+    rstd = torch.ones(T, device="cuda")
+    dwf = torch.zeros(H, device="cuda")
+    scratch = torch.empty(int(ops.rms_norm_bwd_scratch_rows()) * H, device="cuda")
+    ms = timeit(lambda: ops.rms_norm_bwd(x, x, w, rstd, x, dwf, True, scratch))
+    rows.append(f"rms_norm bwd [{T},{H}] (+residual grad, dw): {4 * x.numel() * 2 / ms / 1e6:7.1f} GB/s "
+                f"({4 * x.numel() * 2 / ms / 1e6 / peaks['hbm_gbs']:.2f} of measured copy)")
+    print(rows[-1], flush=True)
+    # rotary embedding in place on the q and k heads of a packed qkv activation (32 + 8 heads of 128 in rows of 6144)
+    qkv = torch.randn(T, 6144, device="cuda", dtype=torch.bfloat16)
+    cos, sin = F.rope_tables(T, 128, 500000.0, qkv.device)
+    ms = timeit(lambda: ops.rope_inplace(qkv, None, cos, sin, 40, 128, 128, False))
+    rows.append(f"rope in place [{T}, 40 heads x 128]: {2 * T * 40 * 128 * 2 / ms / 1e6:7.1f} GB/s "
+                f"({2 * T * 40 * 128 * 2 / ms / 1e6 / peaks['hbm_gbs']:.2f} of measured copy)")
+    print(rows[-1], flush=True)
     gu = torch.randn(T, 2 * I, device="cuda", dtype=torch.bfloat16)
     ms = timeit(lambda: torch.ops.pfb200.swiglu_fwd(gu))
     rows.append(f"swiglu fwd [{T},{2 * I}]: {3 * T * I * 2 / ms / 1e6:7.1f} GB/s")
@@ -176,10 +192,21 @@ def bench_fp8(rows):
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         xq, xs_t = Q.quant_act_kernel(x)
         wq, ws = Q.quant_weight_kernel(w)
-        ms = timeit(lambda: Q.fp8_gemm(xq, xs_t, wq, ws, out=out))
+        ops = torch.ops.pfb200
+        bn = int(ops.mxf8_tile_n(N))
+        sfa = ops.mx_pack_scales(xs_t, True, M, 1, 128)
+        sfb = ops.mx_pack_scales(ws, False, N, 1, bn)
+        ms = timeit(lambda: ops.gemm_mxf8(xq, sfa, wq, sfb, out, None, 0, bn))          # scales applied by the tensor core
+        ms_promo = timeit(lambda: Q.fp8_gemm(xq, xs_t, wq, ws, out=out, pow2=False))      # scales applied in the epilogue
+        ms_pack = timeit(lambda: ops.mx_pack_scales(xs_t, True, M, 1, 128))
         ms_bf16 = timeit(lambda: F.gemm(x, w, out=out))
         ms_qa = timeit(lambda: Q.quant_act_kernel(x))
         ms_qw = timeit(lambda: Q.quant_weight_kernel(w))
+        ms_qt = timeit(lambda: Q.quant_transpose_kernel(x))
+        acc = torch.zeros(N, K, device="cuda")
+        dy = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+        ms_wg = timeit(lambda: Q.fp8_wgrad(dy, x, acc))                                   # two transposing quantisers + packs + GEMM
+        ms_wg_bf16 = timeit(lambda: F.gemm(dy, x, out=acc, a_mn=True, b_mn=True, epi=F.EPI_ACCUM_F32))
         fl = 2.0 * M * N * K
         lib = float("nan")
         try:
@@ -188,10 +215,24 @@ def bench_fp8(rows):
             lib = fl / lib_ms / 1e9
         except Exception:  # this torch build has no 1x128 / 128x128 scaled matmul
             pass
-        rows.append(f"fp8 gemm {name:13s} M={M} N={N} K={K}: {fl / ms / 1e9:7.1f} TFLOP/s (bf16 kernel {fl / ms_bf16 / 1e9:7.1f}, "
-                    f"torch._scaled_mm {lib:7.1f}) | quant act {x.numel() * 3 / ms_qa / 1e6:6.0f} GB/s, "
+        rows.append(f"fp8 gemm {name:13s} M={M} N={N} K={K} tile {bn}: {fl / ms / 1e9:7.1f} TFLOP/s tensor-core scaling "
+                    f"(epilogue promotion {fl / ms_promo / 1e9:7.1f}, bf16 kernel {fl / ms_bf16 / 1e9:7.1f}, torch._scaled_mm {lib:7.1f}) | "
+                    f"scale pack {ms_pack * 1e3:5.1f} us | wgrad fp8 end to end {fl / ms_wg / 1e9:7.1f} vs bf16 {fl / ms_wg_bf16 / 1e9:7.1f} TFLOP/s | "
+                    f"quant act {x.numel() * 3 / ms_qa / 1e6:6.0f} GB/s, quant transpose {x.numel() * 3 / ms_qt / 1e6:6.0f} GB/s, "
                     f"quant weight {w.numel() * 3 / ms_qw / 1e6:6.0f} GB/s")
         print(rows[-1], flush=True)
+    # fused SwiGLU + quantisation against SwiGLU then quantisation (rows x 2I -> e4m3 rows x I)
+    R, I = 16384, 2048
+    gu = torch.randn(R, 2 * I, device="cuda", dtype=torch.bfloat16)
+    dact = torch.randn(R, I, device="cuda", dtype=torch.bfloat16)
+    ops = torch.ops.pfb200
+    ms_f = timeit(lambda: ops.swiglu_quant_fwd(gu, None, True, False))
+    ms_u = timeit(lambda: Q.quant_act_kernel(ops.swiglu_fwd(gu)))
+    ms_fb = timeit(lambda: ops.swiglu_quant_bwd(dact, gu, None, True, True))
+    ms_ub = timeit(lambda: Q.quant_act_kernel(ops.swiglu_bwd(dact, gu, True)[0]))
+    rows.append(f"swiglu+quant [{R}, 2x{I}]: forward fused {ms_f * 1e3:6.1f} us ({R * I * 5 / ms_f / 1e6:5.0f} GB/s) vs two kernels {ms_u * 1e3:6.1f} us; "
+                f"backward fused {ms_fb * 1e3:6.1f} us ({R * I * 14 / ms_fb / 1e6:5.0f} GB/s) vs two kernels {ms_ub * 1e3:6.1f} us")
+    print(rows[-1], flush=True)
 
 
 def main():

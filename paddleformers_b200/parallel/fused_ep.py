@@ -85,6 +85,19 @@ class EPWorkspace:
 _WS: Dict[tuple, EPWorkspace] = {}
 
 
+def dropped_pairs(reset: bool = True) -> int:
+    """Routed (token, expert) pairs dropped on this rank since the last reset because a destination's receive buffer
+    (``PFB_EP_CAPACITY`` x the balanced share, default 1.5) was full. Synchronises the current stream. With
+    ``PFB_EP_OVERFLOW=error`` a non-zero count raises instead: use it when dropping must not pass silently."""
+    if not torch.cuda.is_available() or not hasattr(torch.ops.pfb200, "read_drop_count"):
+        return 0
+    n = int(torch.ops.pfb200.read_drop_count(reset))
+    if n and os.environ.get("PFB_EP_OVERFLOW", "drop") == "error":
+        raise RuntimeError(f"expert-parallel dispatch dropped {n} routed pairs: raise PFB_EP_CAPACITY (now "
+                           f"{os.environ.get('PFB_EP_CAPACITY', '1.5')}) or balance the router")
+    return n
+
+
 def get_workspace(ps, x2d, layer):
     if x2d.dtype != torch.bfloat16 or x2d.shape[1] % 8 != 0 or ps.degrees.ep > _MAX_RANKS or os.environ.get("PFB_FUSED_EP", "1") == "0":
         return None

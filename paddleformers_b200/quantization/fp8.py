@@ -8,6 +8,7 @@ the UE8M0 flag (paddleformers/transformers/configuration_utils.py:454-459).
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -80,17 +81,72 @@ def quant_weight_kernel(w: torch.Tensor, ue8m0: bool = True) -> Tuple[torch.Tens
     return F._ops().fp8_quant_weight(w.contiguous(), ue8m0)
 
 
-def fp8_gemm(xq, xs_t, wq, ws, block_expert=None, n_per_expert: int = 0, out=None) -> torch.Tensor:
+def _mx_enabled() -> bool:
+    return os.environ.get("PFB_FP8_MX", "1") != "0"
+
+
+def _packed_weight_scales(ws: torch.Tensor, rows_per_group: int, groups: int, bn: int) -> torch.Tensor:
+    """Exponent words of a 128x128-scaled weight for ``bn``-row tiles, cached on the scale tensor (weight caches are
+    rebuilt, as new tensors, after every optimizer step)."""
+    cache = getattr(ws, "_mx_pack", None)
+    if cache is None:
+        cache = {}
+        ws._mx_pack = cache
+    key = (rows_per_group, groups, bn)
+    if key not in cache:
+        cache[key] = torch.ops.pfb200.mx_pack_scales(ws, False, rows_per_group, groups, bn)
+    return cache[key]
+
+
+def fp8_gemm(xq, xs_t, wq, ws, block_expert=None, n_per_expert: int = 0, out=None, pow2: bool = True) -> torch.Tensor:
     """Block-scaled e4m3 product on the tcgen05 tensor cores: out[M, N] (bf16) = dequant(xq, xs_t^T) @ dequant(wq, ws)^T.
     With ``block_expert`` (int32, one entry per 128 rows of xq, -1 = skip) ``wq`` holds E stacked [n_per_expert, K]
-    matrices and each row block is multiplied by its expert's matrix."""
+    matrices and each row block is multiplied by its expert's matrix.
+
+    ``pow2`` says that every scale is a power of two (the UE8M0 option of the quantisers): the product then runs on the
+    tensor core's own block scaling (``gemm_mxf8``); otherwise the partial sums are promoted in the epilogue
+    (``gemm_fp8``). ``PFB_FP8_MX=0`` forces the latter."""
     from ..ops import functional as F
 
-    M = xq.shape[0]
-    N = n_per_expert if block_expert is not None else wq.shape[0]
+    ops = F._ops()
+    M, K = xq.shape
+    grouped = block_expert is not None
+    N = n_per_expert if grouped else wq.shape[0]
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=xq.device)
-    F._ops().gemm_fp8(xq, xs_t, wq, ws, out, block_expert, n_per_expert)
+    if pow2 and _mx_enabled() and M > 0:
+        bn = int(ops.mxf8_tile_n(N))
+        groups = wq.shape[0] // N if grouped else 1
+        sfa = ops.mx_pack_scales(xs_t, True, M, 1, 128)
+        sfb = _packed_weight_scales(ws, N, groups, bn)
+        ops.gemm_mxf8(xq, sfa, wq, sfb, out, block_expert, n_per_expert, bn)
+    else:
+        ops.gemm_fp8(xq, xs_t, wq, ws, out, block_expert, n_per_expert)
+    return out
+
+
+def quant_transpose_kernel(x: torch.Tensor, ue8m0: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """CUDA transposing quantisation of a bf16 [T, K] tensor: (e4m3 [K, ceil(T/128)*128] = x^T with a zero tail,
+    scales fp32 [ceil(T/128), K]), one scale per channel and 128 tokens."""
+    return torch.ops.pfb200.fp8_quant_transpose(x if x.stride(1) == 1 else x.contiguous(), ue8m0)
+
+
+def fp8_wgrad(dy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Weight gradient dy^T @ x ([N, K] fp32) with both operands in e4m3, scaled per 128 tokens, on the tensor core's
+    block scaling; ADDED to ``out`` when given (an fp32 main-grad buffer), returned as a new fp32 tensor otherwise
+    (the fp8 wgrad of paddleformers/transformers/fp8_utils.py:1011-1190)."""
+    from ..ops import functional as F
+
+    ops = F._ops()
+    N, K = dy.shape[1], x.shape[1]
+    aq, as_ = quant_transpose_kernel(dy)
+    bq, bs = quant_transpose_kernel(x)
+    bn = int(ops.mxf8_tile_n(K))
+    sfa = ops.mx_pack_scales(as_, True, N, 1, 128)
+    sfb = ops.mx_pack_scales(bs, True, K, 1, bn)
+    if out is None:
+        out = torch.zeros((N, K), dtype=torch.float32, device=dy.device)
+    ops.gemm_mxf8(aq, sfa, bq, sfb, out, None, 0, bn)
     return out
 
 
@@ -101,9 +157,17 @@ def fp8_gemm_reference(xq, xs, wq, ws) -> torch.Tensor:
     return dequant_act(xq, xs) @ dequant_weight(wq, ws).t()
 
 
+def _fp8_wgrad_ok(dy2: torch.Tensor, x2: torch.Tensor) -> bool:
+    """The fp8 weight gradient needs power-of-two scales, channel counts that the transposing quantiser tiles (64) and is
+    switched by PFB_FP8_WGRAD (default on)."""
+    return (os.environ.get("PFB_FP8_WGRAD", "1") != "0" and _mx_enabled() and dy2.shape[1] % 64 == 0 and x2.shape[1] % 64 == 0
+            and dy2.shape[0] >= 128)
+
+
 class _FP8LinearFn(torch.autograd.Function):
-    """fp8 forward and input-gradient products with bf16 master weights; the weight gradient stays in bf16 inputs
-    (quantised activations are not precise enough to be re-used for wgrad at 1x128 granularity along tokens)."""
+    """fp8 forward, input-gradient and weight-gradient products with bf16 master weights. The forward and input-gradient
+    operands are scaled per 1x128 block along their contraction (channels); the weight gradient contracts over tokens,
+    so both of its operands are quantised again, transposed, with one scale per channel and 128 tokens."""
 
     @staticmethod
     def forward(ctx, x, weight, wq, ws, wq_t, ws_t, ue8m0):
@@ -111,7 +175,7 @@ class _FP8LinearFn(torch.autograd.Function):
         ctx.kernels = _use_kernels(x2) and wq_t is not None
         if ctx.kernels:
             xq, xs_t = quant_act_kernel(x2, ue8m0)
-            y = fp8_gemm(xq, xs_t, wq, ws)
+            y = fp8_gemm(xq, xs_t, wq, ws, pow2=ue8m0)
         else:
             xq, xs = quant_act_1x128(x2, ue8m0)
             y = fp8_gemm_reference(xq, xs, wq, ws).to(x.dtype)
@@ -127,8 +191,13 @@ class _FP8LinearFn(torch.autograd.Function):
             from ..ops import functional as F
 
             dq, ds_t = quant_act_kernel(dy2, ctx.ue8m0)
-            dx = fp8_gemm(dq, ds_t, wq_t, ws_t).view(ctx.shape)       # dy @ W with the transposed fp8 weight copy
-            dw = F._weight_grad(dy2.contiguous(), x2, weight)         # bf16 tcgen05 wgrad (into main_grad when present)
+            dx = fp8_gemm(dq, ds_t, wq_t, ws_t, pow2=ctx.ue8m0).view(ctx.shape)   # dy @ W with the transposed fp8 weight copy
+            if _fp8_wgrad_ok(dy2, x2):
+                mg = getattr(weight, "main_grad", None)
+                dw = fp8_wgrad(dy2, x2, mg.view(weight.shape) if mg is not None else None)
+                dw = None if mg is not None else dw.to(weight.dtype)
+            else:
+                dw = F._weight_grad(dy2.contiguous(), x2, weight)     # bf16 tcgen05 wgrad (into main_grad when present)
             return dx, dw, None, None, None, None, None
         dq, ds = quant_act_1x128(dy2, ctx.ue8m0)
         dx = (dequant_act(dq, ds) @ dequant_weight(wq, ws)).to(dy.dtype).view(ctx.shape)

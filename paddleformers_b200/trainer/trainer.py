@@ -445,11 +445,16 @@ class Trainer:
                 loss = loss / n_parts
             loss_v = float(loss)   # the only host sync of the training loop, on logging steps
             if self.device.type == "cuda":
-                # a bounded device wait that ran out, an expert-parallel receive buffer that overflowed or a failed bounds
-                # check leaves a code in the device status word; stop here instead of training on wrong numbers
+                # a bounded device wait that ran out or a failed bounds check leaves a code in the device status word; stop
+                # here instead of training on wrong numbers
                 from ..ops import functional as F
 
                 F.check_kernel_status()
+                # routed pairs dropped because an expert-parallel receive buffer was full are counted, not fatal
+                # (PFB_EP_OVERFLOW=error makes them fatal)
+                from ..parallel.fused_ep import dropped_pairs
+
+                self._ep_dropped = dropped_pairs() if getattr(self.ps.degrees, "ep", 1) > 1 else 0
             if not math.isfinite(loss_v):
                 raise FloatingPointError(f"LOSS_{'NAN' if math.isnan(loss_v) else 'INF'}_ERROR: loss is {loss_v} at "
                                          f"step {self.state.global_step}")
@@ -464,6 +469,8 @@ class Trainer:
             gn = getattr(self, "_last_grad_norm", None)
             if gn is not None:
                 logs["global_norm"] = round(float(gn), 6)
+            if getattr(self, "_ep_dropped", 0):
+                logs["moe_dropped_pairs"] = int(self._ep_dropped)
             sps = steps * a.global_batch_size / dt
             logs["interval_runtime"] = round(dt, 4)
             logs["interval_samples_per_second"] = round(sps, 4)
