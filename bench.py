@@ -50,6 +50,7 @@ def parse():
     ap.add_argument("--global-batch", type=int, default=64)
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (the result is then marked invalid)")
+    ap.add_argument("--experts", type=int, default=0, help="debug only: number of routed experts (the result is then marked invalid)")
     ap.add_argument("--no-e2e", action="store_true", help="debug only: skip the end-to-end pass")
     ap.add_argument("--micro-batch", type=int, default=0,
                     help="sequences per micro-batch; global batch and sequence length stay fixed. 0 = 1, the configuration's value "
@@ -157,6 +158,7 @@ def run_config(args, model_name, W, K, do_e2e, dev, world, rank, local_rank):
     from paddleformers_b200.trainer.trainer_callback import TrainerCallback
     from paddleformers_b200.trainer.training_args import TrainingArguments
     from paddleformers_b200.transformers.auto import AutoModelForCausalLM
+    from paddleformers_b200.transformers.configuration_utils import LlmMetaConfig
     from paddleformers_b200.utils.flops import model_flops_per_token
 
     S, GB = args.seq_len, args.global_batch
@@ -164,6 +166,8 @@ def run_config(args, model_name, W, K, do_e2e, dev, world, rank, local_rank):
     over = {}
     if args.layers:
         over["num_hidden_layers"] = args.layers
+    if args.experts and is_moe:
+        over["num_experts" if model_name == "qwen3-30b-a3b" else "n_routed_experts"] = args.experts
     cfg = named_config(model_name, **over)
     cfg.dtype = "bfloat16"
     cfg.moe_token_dispatcher_type = args.ep_dispatch
@@ -172,7 +176,6 @@ def run_config(args, model_name, W, K, do_e2e, dev, world, rank, local_rank):
         ep = world // pp
         targs = dict(pipeline_model_parallel_size=pp, expert_model_parallel_size=ep, sharding="stage1",
                      virtual_pipeline_model_parallel_size=2, pipeline_schedule="interleaved")
-        cfg.moe_token_dispatcher_type = "alltoall"      # several micro-batches are in flight per stage
         par = f"pp{pp}(interleaved)+ep{ep}+sharding{ep}(stage1)"
         dp_world = world // pp
     elif is_moe:
@@ -205,7 +208,13 @@ def run_config(args, model_name, W, K, do_e2e, dev, world, rank, local_rank):
     cfg.sequence_parallel = ta.sequence_parallel
     cfg.tensor_model_parallel_size = ta.tensor_model_parallel_size
     torch.manual_seed(1234 + ta.parallel_state.coord["mp"] + 17 * ta.parallel_state.rank_in("ep"))
-    model = AutoModelForCausalLM.from_config(cfg, dtype=torch.bfloat16, device=dev)
+    if ta.pipeline_model_parallel_size > 1:
+        from paddleformers_b200.transformers.auto import AutoModelForCausalLMPipe
+
+        LlmMetaConfig.set_llm_config(cfg, ta)      # the stage model reads the schedule and the virtual stages from the config
+        model = AutoModelForCausalLMPipe.from_config(cfg, dtype=torch.bfloat16, device=dev)
+    else:
+        model = AutoModelForCausalLM.from_config(cfg, dtype=torch.bfloat16, device=dev)
     if getattr(cfg, "fp8", None):
         from paddleformers_b200.quantization.fp8 import convert_linears_to_fp8
 
@@ -357,8 +366,8 @@ def run_config(args, model_name, W, K, do_e2e, dev, world, rank, local_rank):
                                            "gate GEMM, routing kernel and expert work per token unchanged"
                 out["moe_dropped_pairs"] = int(fused_ep.dropped_pairs(reset=True))
                 out["fused_ep_calls"] = dict(fused_ep.STATS)
-        if args.layers:
-            out["invalid"] = "truncated model (--layers): debug run, not a benchmark value"
+        if args.layers or (args.experts and is_moe):
+            out["invalid"] = "truncated model (--layers / --experts): debug run, not a benchmark value"
 
     # ---------------- release: graphs first (they pin communicator state), then the model and its workspaces ----------------
     trainer.release_graphs()

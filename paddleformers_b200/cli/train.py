@@ -32,10 +32,14 @@ def _build_model(model_args, train_args, dtype):
     LlmMetaConfig.set_llm_config(config, train_args)
     config.dtype = str(dtype).replace("torch.", "")
     device = torch.device(train_args.device)
+    # under pipeline parallelism every rank builds (and loads) only the layers of its own stage
+    auto_cls = AutoModelForCausalLM
+    if train_args.pipeline_model_parallel_size > 1:
+        from ..transformers.auto import AutoModelForCausalLMPipe as auto_cls
     if model_args.from_scratch or not model_args.model_name_or_path:
-        model = AutoModelForCausalLM.from_config(config, dtype=dtype, device=device)
+        model = auto_cls.from_config(config, dtype=dtype, device=device)
     else:
-        model = AutoModelForCausalLM.from_pretrained(model_args.model_name_or_path, config=config, dtype=dtype, device=device)
+        model = auto_cls.from_pretrained(model_args.model_name_or_path, config=config, dtype=dtype, device=device)
     if getattr(config, "fp8", None):
         # block-scaled fp8 forward / input-gradient GEMMs for the dense projections (experts switch on config.fp8 themselves);
         # the vocabulary head and the routers stay in bf16 / fp32

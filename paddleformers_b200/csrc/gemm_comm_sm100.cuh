@@ -11,11 +11,15 @@
 //     measured 1.5-2.5x slower on two GPUs: a handful of CTAs keeps too few posted bytes in flight, and every
 //     completion wait before a flag costs a link round trip.)
 //
-//   MODE_RS  (GEMM -> reduce-scatter, row-parallel linear with sequence-parallel output):
-//     the epilogue writes each bf16 partial tile straight into the owner rank's staging slot [src_rank][R][N] with
-//     peer stores and bumps a per-source counter at the owner (release, system scope); tiles of remote owners are
-//     computed first. When a CTA runs out of tiles it waits (bounded) for all sources' counters and sums the tp
-//     staging slots of its share of the local rows in fp32 (fixed order: deterministic).
+//   MODE_RS  (GEMM -> reduce-scatter, row-parallel linear with sequence-parallel output), two transports:
+//     pull (default): the epilogue TMA-stores each bf16 partial tile into THIS rank's staging buffer, slot [owner][R][N],
+//       and bumps a per-source counter at the owner (release, system scope); tiles of remote owners are computed first.
+//       When a CTA runs out of tiles it waits (bounded) for all sources' counters and sums its share of the local rows
+//       in fp32, reading slot [this rank] of every peer's staging with plain 16-byte peer loads (all tp loads of a
+//       vector in flight together, summed in rank order: deterministic). Partial sums cross NVLink as loads, which
+//       pipeline per thread; remote TMA stores of 4 KB slabs measured a quarter of the link rate at eight ranks.
+//     push: the epilogue stores the tile into the OWNER's staging slot [src_rank][R][N] with peer TMA stores; the owner
+//       sums its own staging.
 //
 // Flags and counters are epoch-valued and never reset. Every wait is bounded and reports PFB_ERR_WAIT_PEER.
 // Dataflow precedent in the reference: Flux all_gather_gemm / gemm_reduce_scatter
@@ -47,6 +51,7 @@ struct CommParams {
   __nv_bfloat16* stage;                          // local staging
   __nv_bfloat16* out;                            // local result [R, N]
   int tiles_per_source;                          // (R / 128) * n_blocks
+  int pull;                                      // RS: 1 = partial tiles stay in the producer's staging and the owner reads them
 };
 
 __device__ __forceinline__ void st_release_sys_i32(int* p, int v) {
@@ -291,7 +296,9 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // Each warp moves its 32 rows through two private 4 KB swizzled slabs and TMA-stores them into the owner's
         // staging slot (full 128-byte lines over NVLink); only __syncwarp is needed, never a cross-warp barrier.
         const int owner = mb / blocks_per_rank;
-        const int srow0 = c.rank * c.rows_per_rank + (mb * GEMM_BM + quad * 32 - owner * c.rows_per_rank);
+        const int slot_idx = c.pull ? owner : c.rank;            // slot inside the staging buffer that receives the tile
+        const int srow0 = slot_idx * c.rows_per_rank + (mb * GEMM_BM + quad * 32 - owner * c.rows_per_rank);
+        const CUtensorMap* store_map = &stage_maps.m[c.pull ? c.rank : owner];
         uint8_t* my_stg = rs_staging + (warp - 2) * 8192;
         #pragma unroll 1
         for (int cc = 0; cc < BN; cc += 64) {
@@ -319,7 +326,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0 && nb * BN + cc < p.N) {
-            tma_store_2d(&stage_maps.m[owner], slab, nb * BN + cc, srow0);
+            tma_store_2d(store_map, slab, nb * BN + cc, srow0);
             tma_store_commit();
           }
         }
@@ -427,8 +434,44 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const long long nvec = static_cast<long long>(c.rows_per_rank) * p.N / 8;
           const long long slot = static_cast<long long>(c.rows_per_rank) * p.N;
           const int tid = (warp - 2) * 32 + lane;
-          // four independent vectors per thread and iteration: tp * 4 loads in flight hide the DRAM latency
           const long long stride = static_cast<long long>(n_ctas) * 128;
+          if (c.pull) {
+            // two vectors per thread and iteration, the tp loads of both issued before any is used: 2 * tp peer loads
+            // (16 bytes each) in flight per thread cover the link latency
+            const long long mine = static_cast<long long>(c.rank) * slot;
+            for (long long i0 = static_cast<long long>(my_cta) * 128 + tid; i0 < nvec; i0 += 2 * stride) {
+              const long long i1 = i0 + stride;
+              uint4 ra[COMM_MAX_RANKS], rb[COMM_MAX_RANKS];
+              #pragma unroll
+              for (int q = 0; q < COMM_MAX_RANKS; ++q) {
+                ra[q] = make_uint4(0, 0, 0, 0); rb[q] = make_uint4(0, 0, 0, 0);
+                if (q < c.tp) {
+                  const __nv_bfloat16* src = c.peer_stage[q] + mine;
+                  ra[q] = *reinterpret_cast<const uint4*>(src + i0 * 8);
+                  if (i1 < nvec) rb[q] = *reinterpret_cast<const uint4*>(src + i1 * 8);
+                }
+              }
+              float sa[8], sb[8];
+              #pragma unroll
+              for (int j = 0; j < 8; ++j) { sa[j] = 0.f; sb[j] = 0.f; }
+              #pragma unroll
+              for (int q = 0; q < COMM_MAX_RANKS; ++q) {
+                const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&ra[q]);
+                const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&rb[q]);
+                #pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 fa = __bfloat1622float2(ha[j]), fb = __bfloat1622float2(hb[j]);
+                  sa[2 * j] += fa.x; sa[2 * j + 1] += fa.y; sb[2 * j] += fb.x; sb[2 * j + 1] += fb.y;
+                }
+              }
+              *reinterpret_cast<uint4*>(c.out + i0 * 8) = make_uint4(pack_bf16x2(sa[0], sa[1]), pack_bf16x2(sa[2], sa[3]),
+                                                                     pack_bf16x2(sa[4], sa[5]), pack_bf16x2(sa[6], sa[7]));
+              if (i1 < nvec)
+                *reinterpret_cast<uint4*>(c.out + i1 * 8) = make_uint4(pack_bf16x2(sb[0], sb[1]), pack_bf16x2(sb[2], sb[3]),
+                                                                       pack_bf16x2(sb[4], sb[5]), pack_bf16x2(sb[6], sb[7]));
+            }
+          } else {
+          // four independent vectors per thread and iteration: tp * 4 loads in flight hide the DRAM latency
           for (long long i0 = static_cast<long long>(my_cta) * 128 + tid; i0 < nvec; i0 += 4 * stride) {
             float accv[4][8];
             #pragma unroll
@@ -456,6 +499,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 *reinterpret_cast<uint4*>(c.out + i * 8) = make_uint4(pack_bf16x2(accv[u][0], accv[u][1]), pack_bf16x2(accv[u][2], accv[u][3]),
                                                                      pack_bf16x2(accv[u][4], accv[u][5]), pack_bf16x2(accv[u][6], accv[u][7]));
             }
+          }
           }
         }
       }

@@ -47,9 +47,9 @@ def ep_moe_forward(layer, x2d: torch.Tensor, idx: torch.Tensor, w: torch.Tensor)
     """Routed-expert part of an MoE layer under expert parallelism. x2d: [T, H]; idx, w: [T, k]."""
     ps = get_parallel_state()
     dispatcher = getattr(layer.config, "moe_token_dispatcher_type", "fused")
-    # the fused path keeps one micro-batch per layer in its peer-visible buffers: pipeline schedules, which hold several
-    # micro-batches in flight, stay on the all-to-all path
-    if dispatcher == "fused" and ps.degrees.pp == 1 and not getattr(layer, "_single_exchange_buffers_busy", False):
+    # the fused path keeps the receive and output buffers of a layer per micro-batch slot; the pipeline engine assigns the
+    # slots (parallel.fused_ep.SlotAllocator), without pipeline parallelism there is one
+    if dispatcher == "fused" and not getattr(layer, "_single_exchange_buffers_busy", False):
         from . import fused_collectives as fc
 
         ws = fc.get_ep_workspace(ps, x2d, layer)

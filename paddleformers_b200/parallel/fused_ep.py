@@ -14,8 +14,10 @@ reference, paddleformers/transformers/fused_a2a.py:81-178 and paddleformers/nn/m
 The backward pass mirrors it: the combine's backward pushes ``w * dout`` rows and reads the expert outputs again for
 the routing-weight gradient; the dispatch's backward pulls the expert input gradients.
 
-Buffers. Per MoE layer: the receive buffer (it is the saved activation of the expert GEMMs) and the expert output
-buffer (read again in the backward pass). Per workspace: one gradient receive buffer and one input-gradient buffer;
+Buffers. Per MoE layer and micro-batch in flight: the receive buffer (it is the saved activation of the expert GEMMs) and
+the expert output buffer (read again in the backward pass). Without pipeline parallelism one micro-batch is in flight;
+a pipeline schedule keeps several between their forward and backward passes, so the engine gives every micro-batch a
+slot (``set_micro_batch_slot``, ``SlotAllocator``) and a layer keeps one buffer pair per slot. Per workspace: one gradient receive buffer and one input-gradient buffer;
 they can be shared by all layers because a rank cannot start the next layer's exchange before every peer has finished
 reading this layer's buffers (each step of the protocol waits for a flag from every peer). Flags are epoch-valued.
 """
@@ -83,6 +85,39 @@ class EPWorkspace:
 
 
 _WS: Dict[tuple, EPWorkspace] = {}
+_SLOT = 0
+
+
+def set_micro_batch_slot(slot: int) -> None:
+    """Buffer slot of the micro-batch whose forward (or recomputing backward) pass runs next on this rank."""
+    global _SLOT
+    _SLOT = int(slot)
+
+
+class SlotAllocator:
+    """Hands every micro-batch a buffer slot for the time between its first forward and its last backward chunk on this
+    stage; freed slots are reused, so the number of slots equals the schedule's maximum of micro-batches in flight."""
+
+    def __init__(self, chunks_per_micro_batch: int = 1):
+        self.chunks = chunks_per_micro_batch
+        self.free: list = []
+        self.slot_of: Dict[int, int] = {}
+        self.left: Dict[int, int] = {}
+        self.high_water = 0
+
+    def acquire(self, mb: int) -> int:
+        if mb not in self.slot_of:
+            self.slot_of[mb] = self.free.pop() if self.free else self.high_water
+            if self.slot_of[mb] == self.high_water:
+                self.high_water += 1
+            self.left[mb] = self.chunks
+        return self.slot_of[mb]
+
+    def backward_done(self, mb: int) -> None:
+        self.left[mb] -= 1
+        if self.left[mb] == 0:
+            self.free.append(self.slot_of.pop(mb))
+            del self.left[mb]
 
 
 def dropped_pairs(reset: bool = True) -> int:
@@ -187,10 +222,12 @@ class _Combine(torch.autograd.Function):
 
 def moe_forward(ws: EPWorkspace, layer, x2d, idx, w):
     """Routed-expert output [T, H] of ``layer`` for tokens x2d with routing (idx, w), experts spread over the ep group."""
-    bufs = getattr(layer, "_ep_bufs", None)
+    by_slot = getattr(layer, "_ep_bufs", None)
+    if by_slot is None:
+        by_slot = layer._ep_bufs = {}
+    bufs = by_slot.get(_SLOT)
     if bufs is None or bufs["x_recv"].tensor.shape != (ws.cap, ws.H):
-        bufs = ws.layer_buffers()
-        layer._ep_bufs = bufs
+        bufs = by_slot[_SLOT] = ws.layer_buffers()
     plan = make_plan(ws, idx, getattr(layer.gate, "last_plan", None))
     ws.fwd_epoch.add_(1)
     torch.ops.pfb200.ep_exchange(ws.table.peer_ptrs, plan["counts"], plan["block_expert"], plan["expert_rows"], ws.total_rows,

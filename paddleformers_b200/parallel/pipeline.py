@@ -509,6 +509,10 @@ class PipelineEngine:
         split_w = any(a.kind == "W" for a in acts)
         local_fwd: Dict[Tuple[int, int], torch.Tensor] = {}     # hand-over between two chunks of this stage (V placement)
         local_bwd: Dict[Tuple[int, int], torch.Tensor] = {}
+        # expert-parallel exchange buffers are kept per micro-batch in flight (forward done, backward pending)
+        from .fused_ep import SlotAllocator, set_micro_batch_slot
+
+        slots = SlotAllocator(chunks_per_micro_batch=V)
         for a in acts:
             if a.kind == "W":
                 F.WeightGradStore.run_group()      # the weight-gradient GEMMs queued by the matching B
@@ -524,6 +528,7 @@ class PipelineEngine:
             # neighbours in the model's layer order; with the V placement the turn at the last stage stays on this rank
             src_stage = self._owner(vs - 1) if vs > 0 else None
             dst_stage = self._owner(vs + 1) if vs < last_virtual else None
+            set_micro_batch_slot(slots.acquire(a.mb))
             if a.kind == "F":
                 x_in = None
                 if vs > 0:
@@ -559,12 +564,14 @@ class PipelineEngine:
                 finally:
                     if split_w:
                         F.WeightGradStore.end_group()
+                slots.backward_done(a.mb)
                 if vs > 0:
                     if src_stage == s:
                         local_bwd[(vs, a.mb)] = x_in.grad
                     else:
                         self._send(x_in.grad, self.ranks[src_stage], self.bwd_group, pending)
         F.WeightGradStore.run_all()
+        set_micro_batch_slot(0)
         for w in pending:
             w.wait()
         self._sync_shared_embeddings()

@@ -155,8 +155,9 @@ class CopyToTP(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         if _group_size(ctx.group) > 1:
-            g = g.contiguous()
-            dist.all_reduce(g, group=ctx.group)
+            from . import nvls
+
+            g = nvls.all_reduce_(g.contiguous(), ctx.group)      # NVSwitch multicast kernel for bf16, NCCL otherwise
         return g, None
 
 
@@ -166,8 +167,9 @@ class ReduceFromTP(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
         if _group_size(group) > 1:
-            x = x.contiguous()
-            dist.all_reduce(x, group=group)
+            from . import nvls
+
+            x = nvls.all_reduce_(x.contiguous(), group)          # NVSwitch multicast kernel for bf16, NCCL otherwise
         return x
 
     @staticmethod

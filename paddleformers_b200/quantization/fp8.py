@@ -243,7 +243,10 @@ def convert_linears_to_fp8(model: nn.Module, skip=("lm_head", "gate")) -> int:
     """Replace ``nn.Linear`` modules by ``FP8Linear`` sharing the same parameters; returns the number converted."""
     n = 0
     for name, mod in list(model.named_modules()):
-        if isinstance(mod, nn.Linear) and not any(s in name for s in skip):
+        # the GEMM kernels tile both weight dimensions by 128 (the forward product and its transposed copy for the input
+        # gradient); other layers (e.g. DeepSeek's 576-wide compressed key/value projection) stay in bf16
+        if isinstance(mod, nn.Linear) and not any(s in name for s in skip) and mod.in_features % 128 == 0 \
+                and mod.out_features % 128 == 0:
             parent_name, _, leaf = name.rpartition(".")
             parent = model.get_submodule(parent_name) if parent_name else model
             new = FP8Linear(mod.in_features, mod.out_features, mod.bias is not None, dtype=mod.weight.dtype, device=mod.weight.device)

@@ -160,6 +160,13 @@ class AutoModelForCausalLMPipe(AutoModelForCausalLM):
 
         return build_pipeline_model(config, dtype=dtype, device=device, **kw)
 
+    @classmethod
+    def from_pretrained(cls, path: str, config: Optional[PretrainedConfig] = None, dtype=None, device=None, **kw):
+        from ..parallel.pipeline import PipelineStageModel
+
+        config = config or AutoConfig.from_pretrained(path)
+        return PipelineStageModel.from_pretrained(path, config=config, dtype=dtype, device=device, **kw)
+
 
 class AutoTokenizer:
     @staticmethod

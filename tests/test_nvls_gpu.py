@@ -1,0 +1,64 @@
+"""All-reduce through NVSwitch multicast memory (multimem.ld_reduce / multimem.st) on 2 GPUs against the fp32 sum of the
+gathered inputs. The ranks leave together, after a barrier and after dropping the multicast-bound buffers."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["PFB_REPO"])
+from paddleformers_b200.parallel.topology import ParallelDegrees, initialize_parallel
+from paddleformers_b200.parallel import nvls
+from paddleformers_b200.ops import functional as F
+
+world = int(os.environ["WORLD_SIZE"])
+ps = initialize_parallel(ParallelDegrees(mp=world))
+group, rank = ps.group("mp"), ps.coord["mp"]
+dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+F._ops()
+bad = []
+for n in (8, 1000, 4096 * 4096, 3 * 1024 * 1024 + 24, 5):
+    torch.manual_seed(100 + rank)
+    x = torch.randn(n, device=dev).bfloat16()
+    parts = [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(parts, x, group=group)
+    ref = torch.stack([p.float() for p in parts]).sum(0)
+    for it in range(3):                       # repeated calls: epochs advance, the buffer is reused
+        y = x.clone()
+        nvls.all_reduce_(y, group)
+        err = ((y.float() - ref).norm() / (ref.norm() + 1e-9)).item()
+        ys = [torch.empty_like(y) for _ in range(world)]
+        dist.all_gather(ys, y, group=group)
+        same = all(torch.equal(ys[0], t) for t in ys)      # every rank holds the same bits
+        if not (err < 1e-2 and same):
+            bad.append((n, it, err, same))
+F.check_kernel_status()
+st = nvls._get(group)
+print("RESULT", "OK" if not bad else f"BAD {bad}", "multicast" if st is not None else "nccl", nvls.STATS["nvls_all_reduce"], flush=True)
+nvls.release()
+dist.barrier(); dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_multicast_all_reduce_matches_fp32_sum(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER)
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PFB_REPO=repo)
+    env.pop("NCCL_NVLS_ENABLE", None)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr=127.0.0.1",
+           "--master-port=29577", str(script)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    lines = [l.split() for l in res.stdout.splitlines() if l.startswith("RESULT")]
+    assert len(lines) == 2 and all(l[1] == "OK" for l in lines), res.stdout[-3000:]
+    # where the fabric offers multicast the kernel must have carried the calls (15 per rank); NCCL is only the fallback
+    for l in lines:
+        assert l[2] == "nccl" or int(l[3]) == 15, lines
+    print("transport:", lines[0][2])

@@ -117,6 +117,7 @@ def test_parallel_strategies_match_single_gpu(tmp_path):
         "dense2": (False, 2, False, dict(gradient_accumulation_steps=2)),
         "dense4": (False, 4, False, acc4),
         "moe2": (True, 2, False, dict(gradient_accumulation_steps=2, moe_token_dispatcher_type="alltoall")),
+        "moe4": (True, 4, False, dict(moe_token_dispatcher_type="alltoall", **acc4)),
     }, tmp_path / "ref.json", 29571)
     cases = {
         "pp2_1f1b": (False, 4, True, dict(pipeline_model_parallel_size=2, **acc4)),
@@ -130,9 +131,11 @@ def test_parallel_strategies_match_single_gpu(tmp_path):
         "sep2": (False, 2, False, dict(sep_parallel_size=2, gradient_accumulation_steps=2)),
         "ep2_fused": (True, 2, False, dict(expert_model_parallel_size=2, sharding="stage1", gradient_accumulation_steps=1,
                                            moe_token_dispatcher_type="fused")),
+        # several micro-batches in flight per stage: the peer-memory exchange keeps one buffer slot per micro-batch
+        "ppm_moe_fused": (True, 4, True, dict(pipeline_model_parallel_size=2, moe_token_dispatcher_type="fused", **acc4)),
     }
     got = _launch(tmp_path, 2, cases, tmp_path / "got.json", 29572)
-    base = {"pp2": "dense4", "ep2": "moe2"}
+    base = {"pp2": "dense4", "ep2": "moe2", "ppm": "moe4"}
     bad = {}
     for name, losses in got.items():
         want = ref[base.get(name[:3], "dense2")]

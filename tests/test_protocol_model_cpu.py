@@ -187,13 +187,14 @@ def test_checker_detects_a_removed_synchronisation(broken):
 
 # ---------------------------------------------------------------------------------------------------------------
 # tensor-parallel fused collectives: all-gather -> GEMM (pull from peers' gather buffers) and GEMM -> reduce-scatter
-# (push partial tiles into the owner's staging slots), parallel/fused_collectives.py. The gathered buffers are read again
+# (partial tiles stay in the producer's staging and the owner pulls them, or are pushed into the owner's staging slots),
+# parallel/fused_collectives.py. The gathered buffers are read again
 # by the weight-gradient GEMMs of the backward pass; the next write of a buffer (by its owner) and the peers' pulls of
 # the new contents may only happen after those reads, which the call order (weight gradient BEFORE the layer's next
 # fused call) guarantees.
 # ---------------------------------------------------------------------------------------------------------------
 def tp_rank_program(w: World, me: int, layers: int, steps: int, staging_buffers: int = 2, bwd_gather_buffers: int = 2,
-                    back_to_back: bool = False, wgrad_late: bool = False):
+                    back_to_back: bool = False, wgrad_late: bool = False, rs_pull: bool = True):
     n = w.n
     peers = range(n)
     epochs = {}
@@ -232,6 +233,17 @@ def tp_rank_program(w: World, me: int, layers: int, steps: int, staging_buffers:
         buf = f"stage{par}"
         epochs[buf] = epochs.get(buf, 0) + 1
         e = epochs[buf]
+        if rs_pull:
+            # partial tiles of every owner into this rank's own staging, a counter at the owner per finished share; the
+            # owner then reads its slot of every producer's staging (peer loads) and sums in rank order
+            for p in peers:                                      # slot p of my staging holds owner p's rows
+                yield from write(me, (buf, p), tag)
+                w.flags[(p, ("cnt", buf), me)] = e
+                yield ("op", None)
+            yield ("wait", lambda: all(w.flag(me, ("cnt", buf), s) >= e for s in peers))
+            for p in peers:
+                yield from read(p, (buf, me), tag, [p])
+            return
         for p in peers:                                          # partial tiles into the owner's slot, then its counter
             yield from write(p, buf, tag)
             w.flags[(p, ("cnt", buf), me)] = e
@@ -291,12 +303,13 @@ def run_tp(n, layers, steps, seed, **kw):
 
 @pytest.mark.parametrize("n", [2, 4, 8])
 @pytest.mark.parametrize("back_to_back", [False, True])
-def test_tensor_parallel_fused_collectives_have_no_races(n, back_to_back):
+@pytest.mark.parametrize("rs_pull", [True, False])
+def test_tensor_parallel_fused_collectives_have_no_races(n, back_to_back, rs_pull):
     for seed in range(100):
-        run_tp(n, layers=2, steps=2, seed=seed, back_to_back=back_to_back)
+        run_tp(n, layers=2, steps=2, seed=seed, back_to_back=back_to_back, rs_pull=rs_pull)
 
 
-@pytest.mark.parametrize("kw", [dict(staging_buffers=1), dict(bwd_gather_buffers=1)])
+@pytest.mark.parametrize("kw", [dict(staging_buffers=1), dict(bwd_gather_buffers=1), dict(staging_buffers=1, rs_pull=False)])
 def test_single_buffering_of_shared_tp_buffers_is_caught(kw):
     """Why the shared buffers alternate: when two calls of the same kind follow each other directly, a fast rank would
     overwrite, in a single buffer, data that a slow peer still reads. (With a call of the other kind in between, which
