@@ -144,9 +144,9 @@ void gemm_rs(const at::Tensor& x, const at::Tensor& weight, bool b_mn, const at:
   c.count = c.peer_count[rank];
   c.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
   c.tiles_per_source = (c.rows_per_rank / GEMM_BM) * p.n_blocks;
-  // transport of the partial tiles: the owner pulls them from the producers' staging (default) or the producers push
-  // them into the owner's staging (PFB_RS_PULL=0); every rank of a group must use the same setting
-  static const bool pull = [] { const char* e = std::getenv("PFB_RS_PULL"); return !(e && e[0] == '0'); }();
+  // transport of the partial tiles: the producers push them into the owner's staging (default) or the owner pulls them
+  // from the producers' staging (PFB_RS_PULL=1); every rank of a group must use the same setting
+  static const bool pull = [] { const char* e = std::getenv("PFB_RS_PULL"); return e && e[0] == '1'; }();
   c.pull = pull ? 1 : 0;
   CUtensorMap tmA = make_tma_2d(x.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, K, x.stride(0), GEMM_BM, 64);
   CUtensorMap tmB = b_mn ? make_tma_2d(weight.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, weight.stride(0), GEMM_BK, 64)

@@ -12,14 +12,14 @@
 //     completion wait before a flag costs a link round trip.)
 //
 //   MODE_RS  (GEMM -> reduce-scatter, row-parallel linear with sequence-parallel output), two transports:
-//     pull (default): the epilogue TMA-stores each bf16 partial tile into THIS rank's staging buffer, slot [owner][R][N],
-//       and bumps a per-source counter at the owner (release, system scope); tiles of remote owners are computed first.
-//       When a CTA runs out of tiles it waits (bounded) for all sources' counters and sums its share of the local rows
-//       in fp32, reading slot [this rank] of every peer's staging with plain 16-byte peer loads (all tp loads of a
-//       vector in flight together, summed in rank order: deterministic). Partial sums cross NVLink as loads, which
-//       pipeline per thread; remote TMA stores of 4 KB slabs measured a quarter of the link rate at eight ranks.
-//     push: the epilogue stores the tile into the OWNER's staging slot [src_rank][R][N] with peer TMA stores; the owner
-//       sums its own staging.
+//     push (default): the epilogue TMA-stores each bf16 partial tile into the OWNER's staging slot [src_rank][R][N] with
+//       peer stores and bumps a per-source counter at the owner (release, system scope); tiles of remote owners are
+//       computed first. When a CTA runs out of tiles it waits (bounded) for all sources' counters and sums the tp staging
+//       slots of its share of the local rows in fp32 (fixed order: deterministic). The transfer overlaps the tensor work.
+//     pull (PFB_RS_PULL=1): the tile goes into THIS rank's staging, slot [owner][R][N]; the owner reads slot [its rank]
+//       of every peer's staging with plain 16-byte peer loads (all tp loads of a vector in flight together) and sums in
+//       rank order. The transfer starts only after the producers' tiles are done: on two GPUs, where the GEMMs are
+//       long (K = 2048 ... 7168 per rank), it measured 236 / 344 us per call against 176 / 294 us for push.
 //
 // Flags and counters are epoch-valued and never reset. Every wait is bounded and reports PFB_ERR_WAIT_PEER.
 // Dataflow precedent in the reference: Flux all_gather_gemm / gemm_reduce_scatter

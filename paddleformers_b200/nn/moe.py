@@ -74,6 +74,23 @@ class _FusedRouteFn(torch.autograd.Function):
         return (dlogits,) + (None,) * 10
 
 
+def _global_balance_stats(frac: torch.Tensor, pmean: torch.Tensor):
+    """Mean of the per-rank expert loads and mean routing probabilities over the data ranks; the result keeps the
+    gradient of this rank's own probabilities (the other ranks' enter as constants)."""
+    import torch.distributed as dist
+
+    from ..parallel.topology import get_parallel_state
+
+    ps = get_parallel_state()
+    n = ps.size("dp_sharding_cp") if dist.is_initialized() else 1
+    if n <= 1:
+        return frac, pmean
+    group = ps.group("dp_sharding_cp")
+    both = torch.stack([frac.detach(), pmean.detach()])
+    dist.all_reduce(both, group=group)
+    return both[0] / n, (both[1] - pmean.detach() + pmean) / n
+
+
 class _RandomLogits(torch.autograd.Function):
     """Standard-normal logits in the forward pass, the incoming gradient unchanged in the backward pass."""
 
@@ -121,6 +138,10 @@ class TopkRouter(nn.Module):
         self.aux_coef = float(config.router_aux_loss_coef or 0.0)
         self.z_coef = float(config.router_z_loss_coef or 0.0)
         self.force_balance = bool(getattr(config, "moe_router_force_load_balancing", False))
+        # global_aux_loss: the balance term uses the expert load and mean probability of ALL data ranks (one small
+        # all-reduce each), not of this rank's tokens only; the gradient flows through the local probabilities
+        # (examples/experiments/ernie_pretrain/models/moe/top2_gate.py:61-72)
+        self.global_aux = bool(getattr(config, "global_aux_loss", False))
         # "seq_aux_loss": the balance term is computed per sequence and averaged, which also balances experts inside every
         # sequence rather than only over the batch (paddleformers/nn/moe_deepep/moe_gate.py:126-158)
         self.balance_type = str(getattr(config, "moe_router_load_balancing_type", "aux_loss") or "aux_loss")
@@ -153,6 +174,8 @@ class TopkRouter(nn.Module):
                 and hasattr(torch.ops.pfb200, "moe_route_fwd")):
             return False
         if self.scoring not in ("softmax", "sigmoid") or self.bias is not None or self.capacity_factor > 0:
+            return False
+        if self.global_aux and self.training and self.aux_coef > 0:
             return False
         if self.z_coef > 0 or self.balance_type not in ("aux_loss", "none") or E % 32 != 0 or E > 256 or self.top_k > 32:
             return False
@@ -242,7 +265,10 @@ class TopkRouter(nn.Module):
                 probs = scores if self.scoring == "softmax" else scores / (scores.sum(-1, keepdim=True) + 1e-20)
                 frac = torch.zeros(E, dtype=torch.float32, device=x2d.device).scatter_add_(
                     0, idx.reshape(-1), torch.ones(idx.numel(), dtype=torch.float32, device=x2d.device)) / max(T, 1)
-                aux = aux + self.aux_coef * E * (frac / self.top_k * probs.mean(0)).sum() * self.top_k
+                pmean = probs.mean(0)
+                if self.global_aux:
+                    frac, pmean = _global_balance_stats(frac, pmean)
+                aux = aux + self.aux_coef * E * (frac / self.top_k * pmean).sum() * self.top_k
             if self.z_coef > 0:
                 aux = aux + self.z_coef * torch.logsumexp(logits, dim=-1).pow(2).mean()
         return idx, w, aux
@@ -636,7 +662,10 @@ class MoELayer(nn.Module):
     def _forward_tokens(self, x2d: torch.Tensor) -> torch.Tensor:
         T, H = x2d.shape
         idx, w, aux = self.gate(x2d)
-        if self.ep > 1:
+        # PFB_FUSED_EP_SINGLE=1 sends a single expert-parallel rank through the peer-memory exchange as well (the kernels then
+        # exchange with themselves): the way to exercise the exchange, its buffers and their pipeline slots on few GPUs
+        if self.ep > 1 or (x2d.is_cuda and os.environ.get("PFB_FUSED_EP_SINGLE", "0") == "1"
+                           and getattr(self.config, "moe_token_dispatcher_type", "fused") == "fused"):
             from ..parallel.expert_parallel import ep_moe_forward
 
             assert not getattr(self.config, "moe_scale_expert_input", False), \

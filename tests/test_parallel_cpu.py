@@ -384,3 +384,43 @@ def test_unified_checkpoint_resumes_under_a_different_tensor_parallel_degree(tmp
     for r in range(2):
         for a, b in zip(ref[2:], got2[r][-2:]):
             assert abs(a - b) < 3e-4 * max(1.0, abs(a)), (ref, got2[r])
+
+
+def _global_aux_worker(rank, world):
+    """Balance loss from the expert loads and mean probabilities of all data ranks (``global_aux_loss``)."""
+    from paddleformers_b200.models.configuration import Qwen3MoeConfig
+    from paddleformers_b200.nn.moe import TopkRouter
+    from paddleformers_b200.parallel.topology import ParallelDegrees, initialize_parallel
+
+    initialize_parallel(ParallelDegrees(sharding=world), backend="gloo")
+    cfg = Qwen3MoeConfig(hidden_size=32, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=16, intermediate_size=16,
+                         num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=2, vocab_size=64, router_aux_loss_coef=0.01)
+    cfg.global_aux_loss = True
+    torch.manual_seed(3)
+    gate = TopkRouter(cfg)
+    torch.nn.init.normal_(gate.weight, std=0.5)
+    gate.train()
+    x_all = torch.randn(world * 24, 32, generator=torch.Generator().manual_seed(9))
+    _, _, aux = gate(x_all[rank * 24:(rank + 1) * 24])
+    aux.backward()
+    return float(aux), gate.weight.grad.clone()
+
+
+def test_global_aux_loss_uses_the_statistics_of_all_data_ranks():
+    from paddleformers_b200.models.configuration import Qwen3MoeConfig
+    from paddleformers_b200.nn.moe import TopkRouter
+
+    res = run_distributed(_global_aux_worker, 2)
+    cfg = Qwen3MoeConfig(hidden_size=32, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=16, intermediate_size=16,
+                         num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=2, vocab_size=64, router_aux_loss_coef=0.01)
+    torch.manual_seed(3)
+    gate = TopkRouter(cfg)
+    torch.nn.init.normal_(gate.weight, std=0.5)
+    gate.train()
+    x_all = torch.randn(48, 32, generator=torch.Generator().manual_seed(9))
+    _, _, aux = gate(x_all)
+    aux.backward()
+    for a, _ in res:
+        assert abs(a - float(aux)) < 1e-6                              # every rank reports the loss of the whole batch
+    # each rank differentiates through its own probabilities only: the ranks' gradients add up to the whole-batch gradient
+    torch.testing.assert_close(res[0][1] + res[1][1], gate.weight.grad, rtol=1e-4, atol=1e-7)

@@ -59,6 +59,8 @@ def full_weights(moe, layers):
     return {k: v.detach().clone() for k, v in m.named_parameters()}
 
 def train(moe, layers, pipeline, targs):
+    targs = dict(targs)
+    os.environ.update(targs.pop("_env", {}))
     args = TrainingArguments(output_dir="/tmp/pfb_test_unused", per_device_train_batch_size=1, max_steps=STEPS, learning_rate=1e-3,
                              lr_scheduler_type="constant", logging_steps=1, save_strategy="no", max_seq_len=S, max_grad_norm=1.0,
                              seed=3, bf16=ON_GPU, device=str(dev), **targs)
@@ -91,6 +93,8 @@ for name, (moe, layers, pipeline, targs) in CASES.items():
     out[name] = train(moe, layers, pipeline, targs)
     if dist.is_initialized(): dist.barrier()
 if rank == 0:
+    from paddleformers_b200.parallel import fused_ep
+    out["_fused_ep_dispatches"] = fused_ep.STATS["dispatch"]
     json.dump(out, open(os.environ["PFB_OUT"], "w"))
 if dist.is_initialized():
     dist.barrier(); dist.destroy_process_group()
@@ -117,7 +121,6 @@ def test_parallel_strategies_match_single_gpu(tmp_path):
         "dense2": (False, 2, False, dict(gradient_accumulation_steps=2)),
         "dense4": (False, 4, False, acc4),
         "moe2": (True, 2, False, dict(gradient_accumulation_steps=2, moe_token_dispatcher_type="alltoall")),
-        "moe4": (True, 4, False, dict(moe_token_dispatcher_type="alltoall", **acc4)),
     }, tmp_path / "ref.json", 29571)
     cases = {
         "pp2_1f1b": (False, 4, True, dict(pipeline_model_parallel_size=2, **acc4)),
@@ -131,15 +134,37 @@ def test_parallel_strategies_match_single_gpu(tmp_path):
         "sep2": (False, 2, False, dict(sep_parallel_size=2, gradient_accumulation_steps=2)),
         "ep2_fused": (True, 2, False, dict(expert_model_parallel_size=2, sharding="stage1", gradient_accumulation_steps=1,
                                            moe_token_dispatcher_type="fused")),
-        # several micro-batches in flight per stage: the peer-memory exchange keeps one buffer slot per micro-batch
-        "ppm_moe_fused": (True, 4, True, dict(pipeline_model_parallel_size=2, moe_token_dispatcher_type="fused", **acc4)),
     }
     got = _launch(tmp_path, 2, cases, tmp_path / "got.json", 29572)
-    base = {"pp2": "dense4", "ep2": "moe2", "ppm": "moe4"}
+    base = {"pp2": "dense4", "ep2": "moe2"}
     bad = {}
+    got.pop("_fused_ep_dispatches", None)
     for name, losses in got.items():
         want = ref[base.get(name[:3], "dense2")]
         for a, b in zip(want, losses):
             if not abs(a - b) < 3e-2 * max(1.0, abs(a)):        # bf16 forward and backward, different reduction orders
                 bad[name] = (want, losses)
     assert not bad, bad
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_pipeline_stages_use_the_peer_memory_expert_exchange(tmp_path):
+    """Several micro-batches are in flight per pipeline stage: the exchange keeps one buffer slot per micro-batch. With two
+    GPUs both are pipeline stages, so each stage's expert-parallel group has one rank and PFB_FUSED_EP_SINGLE sends it
+    through the exchange kernels all the same."""
+    acc4 = dict(gradient_accumulation_steps=4)
+    ref = _launch(tmp_path, 1, {"moe4": (True, 4, False, dict(moe_token_dispatcher_type="alltoall", **acc4))},
+                  tmp_path / "ref.json", 29573)
+    got = _launch(tmp_path, 2, {
+        "pp2_moe_fused_1f1b": (True, 4, True, dict(pipeline_model_parallel_size=2, moe_token_dispatcher_type="fused",
+                                                   _env={"PFB_FUSED_EP_SINGLE": "1"}, **acc4)),
+        "pp2_moe_fused_interleaved": (True, 4, True, dict(pipeline_model_parallel_size=2, virtual_pipeline_model_parallel_size=2,
+                                                          pipeline_schedule="interleaved", moe_token_dispatcher_type="fused",
+                                                          _env={"PFB_FUSED_EP_SINGLE": "1"}, **acc4)),
+    }, tmp_path / "got.json", 29574)
+    for name, losses in got.items():
+        if name.startswith("_"):
+            continue
+        for a, b in zip(ref["moe4"], losses):
+            assert abs(a - b) < 3e-2 * max(1.0, abs(a)), (name, ref["moe4"], losses)
+    assert got["_fused_ep_dispatches"] > 0, got
