@@ -150,6 +150,10 @@ def read_args(argv: Optional[List[str]] = None) -> Dict[str, Any]:
 
 
 def parse_dict(cfg: Dict[str, Any], classes=ARG_CLASSES) -> Tuple:
+    # keys that only the reference's trainer knows are translated, accepted without effect or refused with a pointer
+    from .reference_flags import translate
+
+    cfg = translate(cfg, {f.name for cls in classes for f in dataclasses.fields(cls)})
     used = set()
     outs = []
     hints_cache = {}

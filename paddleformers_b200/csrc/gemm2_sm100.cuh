@@ -24,17 +24,29 @@
 
 namespace pfb {
 
-constexpr int G2_STAGES = 7;
+constexpr int G2_STAGES = 7;          // six when the epilogue stages its tiles in shared memory (EPI_REDUCE_F32)
+constexpr int G2_STAGING_BYTES = 4 * 2 * 4096;   // per epilogue warp: two 32-row x 128-byte slabs
 constexpr int G2_BN = 256;            // accumulator columns per CTA (= tile N)
 constexpr int G2_HALF = 128;          // B rows loaded by each CTA
 
-struct Gemm2Smem {
+template <int STAGES, int STAGING>
+struct Gemm2SmemT {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;     // 16 KB
   static constexpr int B_BYTES = G2_HALF * GEMM_BK * 2;     // 16 KB
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = G2_STAGES * STAGE_BYTES;
+  static constexpr int STAGING_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFFSET = STAGING_OFFSET + STAGING;
   static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;
 };
+template <int EPI>
+using Gemm2SmemFor = Gemm2SmemT<(EPI == EPI_REDUCE_F32 ? G2_STAGES - 1 : G2_STAGES), (EPI == EPI_REDUCE_F32 ? G2_STAGING_BYTES : 0)>;
+using Gemm2Smem = Gemm2SmemFor<EPI_STORE_BF16>;
+
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+               : "memory");
+}
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -112,13 +124,15 @@ __device__ __forceinline__ void tc_mma2_f16_ss(uint32_t tmem_d, uint64_t desc_a,
 
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
-  using S = Gemm2Smem;
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
+  using S = Gemm2SmemFor<EPI>;
+  constexpr int STAGES = (EPI == EPI_REDUCE_F32) ? G2_STAGES - 1 : G2_STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);   // [STAGES] leader only: both CTAs' loads have landed
-  uint64_t* empty_bar = full_bar + G2_STAGES;                               // [STAGES] the products that read a stage are done
-  uint64_t* tfull_bar = empty_bar + G2_STAGES;                              // [2] accumulator complete
+  uint64_t* empty_bar = full_bar + STAGES;                               // [STAGES] the products that read a stage are done
+  uint64_t* tfull_bar = empty_bar + STAGES;                              // [2] accumulator complete
   uint64_t* tempty_bar = tfull_bar + 2;                                     // [2] leader only: drained by both CTAs
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -129,7 +143,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const bool leader = cta == 0;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < G2_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 8); }
     *abort_flag = 0;
     mbar_fence_init();
@@ -189,7 +203,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             for (int j = 0; j < G2_HALF / 64; ++j)
               tma_load_2d_pair(sb + j * (GEMM_BK * 128), &tmB, fb, b_row0 + j * 64, kb * GEMM_BK);
           }
-          if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -224,7 +238,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             // the stage is free in BOTH CTAs once these products have read it
             tc_commit2(smem_u32(&empty_bar[stage]));
             tc_commit2(peer_empty0 + stage * 8);
-            if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
           if (ok) { tc_commit2(smem_u32(&tfull_bar[acc])); tc_commit2(peer_tfull0 + acc * 8); }
           if (++acc == 2) { acc = 0; acc_phase ^= 1; }
@@ -242,11 +256,40 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tc_fence_after();
       const int row = mp * 2 * GEMM_BM + static_cast<int>(cta) * GEMM_BM + quad * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * G2_BN;
-      gemm_store_tile<G2_BN, EPI>(taddr, row, nb, p, 0);
+      if constexpr (EPI == EPI_REDUCE_F32) {
+        // each warp moves its 32 rows through two private 4 KB slabs (32 fp32 columns = one 128-byte swizzle row per
+        // row) and hands them to the TMA unit as reduce-add operations: D += tile is formed in L2
+        uint8_t* my_stg = smem + S::STAGING_OFFSET + (warp - 2) * 8192;
+        const int row0 = row - lane;
+        #pragma unroll 1
+        for (int c = 0; c < G2_BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+          uint8_t* slab = my_stg + ((c >> 5) & 1) * 4096;
+          if (lane == 0) tma_store_wait_read<1>();   // the slab used two steps ago has been read out
+          __syncwarp();
+          uint8_t* rowp = slab + lane * 128;
+          #pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < p.M && nb * G2_BN + c < p.N) {
+            tma_reduce_add_2d(&tmD, slab, nb * G2_BN + c, row0);
+            tma_store_commit();
+          }
+        }
+      } else {
+        gemm_store_tile<G2_BN, EPI>(taddr, row, nb, p, 0);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_tempty0 + acc * 8);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if constexpr (EPI == EPI_REDUCE_F32) {
+      if (lane == 0) tma_store_wait<0>();      // the staging slabs stay valid until the last reduction has read them
     }
   }
 

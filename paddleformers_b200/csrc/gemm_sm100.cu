@@ -54,9 +54,10 @@ static void dispatch(bool a_mn, bool b_mn, int epi, bool grouped, const CUtensor
 
 // ---- CTA-pair kernel (gemm2_sm100.cuh): launched as clusters of two CTAs
 template <bool A_MN, bool B_MN, int EPI>
-static void launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int n_clusters, cudaStream_t stream) {
+static void launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const GemmParams& p, int n_clusters,
+                        cudaStream_t stream) {
   auto kern = gemm2_bf16_kernel<A_MN, B_MN, EPI>;
-  constexpr int smem = Gemm2Smem::TOTAL;
+  constexpr int smem = Gemm2SmemFor<EPI>::TOTAL;
   static bool configured = false;
   if (!configured) {
     C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -72,13 +73,13 @@ static void launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Ge
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  C10_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p));
+  C10_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmD, p));
 }
 
-static bool dispatch_pair(bool a_mn, bool b_mn, int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                          int n_clusters, cudaStream_t s) {
+static bool dispatch_pair(bool a_mn, bool b_mn, int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD,
+                          const GemmParams& p, int n_clusters, cudaStream_t s) {
 #define PFB_PAIR(AMN, BMN, E)                                                                       \
-  if (a_mn == AMN && b_mn == BMN && epi == E) { launch_pair<AMN, BMN, E>(tmA, tmB, p, n_clusters, s); return true; }
+  if (a_mn == AMN && b_mn == BMN && epi == E) { launch_pair<AMN, BMN, E>(tmA, tmB, tmD, p, n_clusters, s); return true; }
   PFB_PAIR(false, false, EPI_STORE_BF16)
   PFB_PAIR(false, false, EPI_STORE_F32)
   PFB_PAIR(false, false, EPI_ACCUM_BF16)
@@ -88,6 +89,7 @@ static bool dispatch_pair(bool a_mn, bool b_mn, int epi, const CUtensorMap& tmA,
   PFB_PAIR(true, true, EPI_STORE_BF16)
   PFB_PAIR(true, true, EPI_STORE_F32)
   PFB_PAIR(true, true, EPI_ACCUM_F32)
+  PFB_PAIR(true, true, EPI_REDUCE_F32)
 #undef PFB_PAIR
   return false;
 }
@@ -95,6 +97,13 @@ static bool dispatch_pair(bool a_mn, bool b_mn, int epi, const CUtensorMap& tmA,
 // PFB_GEMM_PAIR=0 keeps every product on the one-CTA kernel (A/B switch)
 static bool pair_enabled() {
   static const bool on = [] { const char* e = std::getenv("PFB_GEMM_PAIR"); return e == nullptr || std::string(e) != "0"; }();
+  return on;
+}
+
+// PFB_GEMM_TMA_REDUCE=1: the fp32-accumulating weight-gradient product adds its tiles through TMA reduce operations (the
+// sum is formed in L2) instead of reading the old values into the epilogue warps
+static bool tma_reduce_enabled() {
+  static const bool on = [] { const char* e = std::getenv("PFB_GEMM_TMA_REDUCE"); return e != nullptr && std::string(e) == "1"; }();
   return on;
 }
 
@@ -208,7 +217,14 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, 
       CUtensorMap tmB2 = b_mn ? make_tma_2d(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Kb, Nb_rows, b.stride(0), GEMM_BK, 64)
                               : make_tma_2d(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Nb_rows, K, b.stride(0), G2_HALF, 64);
       const int n_clusters = static_cast<int>(std::min<long long>(tiles2, pairs));
-      if (dispatch_pair(a_mn, b_mn, static_cast<int>(epi), tmA2, tmB2, p2, n_clusters, stream)) {
+      int epi2 = static_cast<int>(epi);
+      CUtensorMap tmD2 = tmA2;     // only the reduce-add epilogue reads it
+      if (epi2 == EPI_ACCUM_F32 && a_mn && b_mn && tma_reduce_enabled() && out.stride(0) % 4 == 0 &&
+          (reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0) {
+        epi2 = EPI_REDUCE_F32;
+        tmD2 = make_tma_2d(out.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, out.stride(0), 32, 32);
+      }
+      if (dispatch_pair(a_mn, b_mn, epi2, tmA2, tmB2, tmD2, p2, n_clusters, stream)) {
         count_launch();
         return;
       }

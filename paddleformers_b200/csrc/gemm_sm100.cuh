@@ -27,6 +27,7 @@ enum GemmEpilogue : int {
   EPI_ACCUM_F32 = 2,    // D(fp32) += acc            (wgrad into fp32 main_grad)
   EPI_SWIGLU_BF16 = 3,  // D(bf16)[.., N/2]: silu(acc[:, j]) * acc[:, j + BN/2] per tile (gate|up interleaved by tile)
   EPI_ACCUM_BF16 = 4,   // D(bf16) = D + acc          (residual add fused)
+  EPI_REDUCE_F32 = 5,   // D(fp32) += acc through TMA reduce-add (CTA-pair kernel only): the add happens in L2, nothing is read back
 };
 
 struct GemmParams {

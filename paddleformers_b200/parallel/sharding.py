@@ -196,14 +196,39 @@ class ShardedAdamW:
 
     def sync_sequence_parallel_grads(self):
         """All-reduce gradients of tp-replicated parameters that saw token-sharded activations
-        (paddleformers/trainer/trainer_callback.py:936-963)."""
+        (paddleformers/trainer/trainer_callback.py:936-963): packed into one buffer, one all-reduce, unpacked."""
         if self.ps.degrees.mp <= 1:
             return
         g = self.ps.group("mp")
-        for dom in self.domains:
-            for _, p in dom.params:
-                if getattr(p, "sequence_parallel", False):
-                    dist.all_reduce(p.main_grad, group=g)
+        grads = [p.main_grad for dom in self.domains for _, p in dom.params if getattr(p, "sequence_parallel", False)]
+        if not grads:
+            return
+        if len(grads) == 1:
+            dist.all_reduce(grads[0], group=g)
+            return
+        flat = torch.cat([t.reshape(-1) for t in grads])
+        dist.all_reduce(flat, group=g)
+        torch._foreach_copy_([t.reshape(-1) for t in grads], list(flat.split([t.numel() for t in grads])))
+
+    def _replicated_slices(self, shards):
+        """Views of the local gradient shards that belong to parameters replicated over the tp group (the static list of
+        slice bounds is computed once)."""
+        if getattr(self, "_rep_bounds", None) is None:
+            ps = self.ps
+            bounds = []
+            for di, dom in enumerate(self.domains):
+                if dom.is_expert and ps.degrees.ep > 1:
+                    continue
+                n = dom.shard_numel
+                lo = dom.shard_rank * n
+                for name, p in dom.params:
+                    if getattr(p, "shard_spec", None) is None or getattr(p, "shard_spec")[0] != "tp":
+                        off, cnt = dom.offsets[name]
+                        a, b = max(off, lo), min(off + cnt, lo + n)
+                        if b > a:
+                            bounds.append((di, a - lo, b - lo))
+            self._rep_bounds = bounds
+        return [shards[di][a:b] for di, a, b in self._rep_bounds]
 
     def reduce_gradients(self):
         """Sum gradients over the data replicas: reduce-scatter inside the sharding group, all-reduce over dp.
@@ -254,19 +279,11 @@ class ShardedAdamW:
         # tp-replicated parameters appear on every tp rank: their share is counted once by dividing, which is exact
         # because replicated gradients are identical after the sequence-parallel sync.
         if ps.degrees.mp > 1:
-            rep = torch.zeros_like(acc_dense)
-            for dom, g in zip(self.domains, shards):
-                if dom.is_expert and ps.degrees.ep > 1:
-                    continue
-                n = dom.shard_numel
-                lo = dom.shard_rank * n
-                for name, p in dom.params:
-                    if getattr(p, "shard_spec", None) is None or getattr(p, "shard_spec")[0] != "tp":
-                        off, cnt = dom.offsets[name]
-                        a, b = max(off, lo), min(off + cnt, lo + n)
-                        if b > a:
-                            rep += g[a - lo:b - lo].double().pow(2).sum().float()
-            acc_dense = acc_dense - rep * (1.0 - 1.0 / ps.degrees.mp)  # experts with ep == 1 are folded in here too
+            views = self._replicated_slices(shards)
+            if views:
+                # one multi-tensor norm over all replicated slices instead of a launch per parameter
+                rep = torch.stack(torch._foreach_norm(views)).double().pow(2).sum().float().reshape(1)
+                acc_dense = acc_dense - rep * (1.0 - 1.0 / ps.degrees.mp)  # experts with ep == 1 are folded in here too
         total = torch.cat([acc_dense, acc_expert])
         if dist.is_initialized() and ps.world_size > 1:
             # dense shards: sum over sharding x mp x pp (x sep x cp hold identical copies -> not summed);

@@ -17,17 +17,29 @@ from .trainer_callback import TrainerCallback
 
 
 class EMACallback(TrainerCallback):
-    def __init__(self, decay: float = 0.999, start_step: int = 0):
+    def __init__(self, decay: float = 0.999, start_step: int = 0, interval: int = 1, loss_threshold: float = None):
+        """``interval``: average every that many optimizer steps; ``loss_threshold``: average only while the last logged
+        training loss is below it (``zcc_ema_interval`` / ``zcc_ema_loss_threshold`` of the reference's zero-cost
+        checkpoint EMA, paddleformers/trainer/training_args.py:1225-1238; the reference keeps the average in its
+        checkpoint worker's host memory, here it lives beside the master shard it averages)."""
         assert 0.0 < decay < 1.0
         self.decay, self.start_step = decay, start_step
+        self.interval, self.loss_threshold = max(int(interval or 1), 1), loss_threshold
         self.shadow: Dict[str, torch.Tensor] = {}
         self.num_updates = 0
+        self.last_loss = None
+
+    def on_log(self, args, state, control, logs=None, **kw):
+        if logs and "loss" in logs:
+            self.last_loss = float(logs["loss"])
 
     def _domains(self, optimizer) -> List:
         return list(getattr(optimizer, "domains", []))
 
     def on_optimizer_end(self, args, state, control, optimizer=None, **kw):
-        if optimizer is None or state.global_step + 1 < self.start_step:
+        if optimizer is None or state.global_step + 1 < self.start_step or (state.global_step + 1) % self.interval != 0:
+            return
+        if self.loss_threshold is not None and self.last_loss is not None and not self.last_loss < self.loss_threshold:
             return
         with torch.no_grad():
             for dom in self._domains(optimizer):

@@ -159,10 +159,14 @@ def callbacks_from_args(args) -> List[TrainerCallback]:
             out.append(VisualDLCallback())
         else:
             raise ValueError(f"report_to: unknown logger {n!r} (tensorboard, visualdl, jsonl, none)")
-    if float(getattr(args, "ema_decay", 0.0) or 0.0) > 0:
+    zcc_coef = getattr(args, "zcc_save_ema_coef", None) if getattr(args, "enable_zero_cost_checkpoint", False) else None
+    if float(getattr(args, "ema_decay", 0.0) or 0.0) > 0 or (zcc_coef is not None and 0.0 < float(zcc_coef) < 1.0):
         from .ema import EMACallback
 
-        out.append(EMACallback(float(args.ema_decay), int(getattr(args, "ema_start_step", 0) or 0)))
+        decay = float(args.ema_decay) if float(getattr(args, "ema_decay", 0.0) or 0.0) > 0 else float(zcc_coef)
+        out.append(EMACallback(decay, int(getattr(args, "ema_start_step", 0) or 0),
+                               interval=int(getattr(args, "zcc_ema_interval", 1) or 1),
+                               loss_threshold=getattr(args, "zcc_ema_loss_threshold", None)))
     if int(getattr(args, "internal_medicine_monitor_interval", 0) or 0) > 0:
         from .health_monitor import HealthMonitorCallback
 

@@ -91,6 +91,9 @@ class TrainingArguments:
     zcc_save_model_weights: bool = False        # also export HF weights at every save (collective and synchronous)
     nccl_comm_group_config: Optional[str] = None   # JSON file / string: per-group NCCL communicator options
     ema_decay: float = 0.0                      # > 0: keep an exponential moving average of the fp32 master shards
+    zcc_save_ema_coef: Optional[float] = None   # with enable_zero_cost_checkpoint: EMA coefficient (same average, saved with the checkpoint)
+    zcc_ema_interval: int = 1                   # average every that many optimizer steps
+    zcc_ema_loss_threshold: Optional[float] = None   # average only while the last logged loss is below this value
     ema_start_step: int = 0
     enable_timer: bool = False         # per-step read-data / forward-backward / optimizer-step timers in the log record
     log_loss_md5: bool = False         # md5 of the logged loss's fp32 bytes in the log record (also: LOG_LOSS_MD5=1)

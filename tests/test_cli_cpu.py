@@ -409,3 +409,22 @@ def test_vl_sft_stage_trains_paddleocr_vl(tmp_path):
         else:
             os.environ["CUDA_VISIBLE_DEVICES"] = env
     assert AutoModelForConditionalGeneration.from_pretrained(str(out), dtype=torch.float32).config.model_type == "paddleocr_vl"
+
+
+def test_reference_only_configuration_keys_are_translated_accepted_or_refused():
+    """A YAML written for the reference trainer starts a run here: aliases move to this package's fields, switches for
+    behaviour that is built in are accepted, and keys that ask for something that is not provided raise with a pointer."""
+    from paddleformers_b200.cli.hparams import parse_dict
+
+    base = dict(model_name_or_path="tiny", output_dir="/tmp/x", stage="PT")
+    args = parse_dict(dict(base, sharding_degree=1, evaluation_strategy="steps", use_async_save=True, unified_checkpoint=True,
+                           split_param=True, amp_master_grad=True, tensor_parallel_config="enable_mp_async_allreduce enable_sp_async_reduce_scatter",
+                           pipeline_parallel_config="enable_split_backward enable_overlap_p2p_comm", sharding_parallel_config="enable_stage1_overlap split_param",
+                           scale_loss=32768, to_static=False))
+    ta = args[-1]
+    assert ta.sharding_parallel_size == 1 and ta.eval_strategy == "steps" and ta.async_save is True
+    assert ta.save_checkpoint_format == "unified" and ta.pipeline_schedule == "zero_bubble" and ta.sharding_overlap is True
+    with pytest.raises(ValueError, match="tracing compiler"):
+        parse_dict(dict(base, to_static=True))
+    with pytest.raises(ValueError, match="unknown configuration keys"):
+        parse_dict(dict(base, definitely_not_a_flag=1))

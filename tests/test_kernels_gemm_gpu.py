@@ -147,3 +147,40 @@ def test_router_logits_fp32_accuracy_on_tensor_cores():
     assert rel(w.grad, wr.grad) < 2e-5
     assert rel(x.grad, xr.grad) < 5e-3          # dx is returned in bf16
     F.check_kernel_status()
+
+
+_REDUCE_WORKER = r'''
+import sys, torch
+sys.path.insert(0, sys.argv[1])
+from paddleformers_b200.ops import functional as F
+torch.manual_seed(0)
+bad = []
+for T, N, K in ((4096, 1024, 512), (2048, 768, 1280), (1000, 512, 264), (4096, 4096, 4096)):
+    dy = torch.randn(T, N, device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    acc = torch.randn(N, K, device="cuda")
+    ref = acc.double() + dy.double().t() @ x.double()
+    for _ in range(2):                       # two products into the same buffer: the second adds to the first
+        F.gemm(dy, x, out=acc, a_mn=True, b_mn=True, epi=F.EPI_ACCUM_F32)
+    ref = ref + dy.double().t() @ x.double()
+    err = ((acc.double() - ref).norm() / ref.norm()).item()
+    if not err < 2e-3:
+        bad.append((T, N, K, err))
+F.check_kernel_status()
+print("RESULT", "OK" if not bad else f"BAD {bad}")
+'''
+
+
+def test_weight_gradient_accumulates_through_tma_reduce_add(tmp_path):
+    """PFB_GEMM_TMA_REDUCE=1: the CTA-pair kernel adds its fp32 tiles to the gradient buffer with TMA reduce operations
+    (the sum is formed in L2). The switch is read once per process, so the check runs in a child process."""
+    import os
+    import subprocess
+    import sys
+
+    script = tmp_path / "w.py"
+    script.write_text(_REDUCE_WORKER)
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, str(script), repo], env=dict(os.environ, PFB_GEMM_TMA_REDUCE="1"), capture_output=True,
+                         text=True, timeout=600)
+    assert res.returncode == 0 and "RESULT OK" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]

@@ -144,6 +144,20 @@ def test_ema_tracks_master_weights_and_exports(tmp_path):
     assert max(diffs) > 0 and max(diffs) < 1e-2
 
 
+def test_zero_cost_checkpoint_ema_flags_average_on_an_interval_and_below_a_loss_threshold(tmp_path):
+    from paddleformers_b200.trainer.ema import EMACallback
+
+    _, tr = _make(tmp_path, 6, enable_zero_cost_checkpoint=True, zcc_save_ema_coef=0.5, zcc_ema_interval=2, save_strategy="no")
+    ema = next(cb for cb in tr.callback_handler.callbacks if isinstance(cb, EMACallback))
+    tr.train()
+    assert ema.decay == 0.5 and ema.num_updates == 3              # steps 2, 4, 6
+    _, tr = _make(tmp_path, 4, enable_zero_cost_checkpoint=True, zcc_save_ema_coef=0.5, zcc_ema_loss_threshold=1e-3,
+                  save_strategy="no")
+    ema = next(cb for cb in tr.callback_handler.callbacks if isinstance(cb, EMACallback))
+    tr.train()
+    assert ema.num_updates <= 1                                   # the loss never gets below the threshold once it is known
+
+
 def test_muon_orthogonalises_matrix_updates_and_trains(tmp_path):
     from paddleformers_b200.parallel.sharding import ShardedMuon, newton_schulz_orthogonalize
 
