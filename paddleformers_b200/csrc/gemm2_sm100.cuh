@@ -170,6 +170,17 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     mp = g * p.group_m + (r % gsz);
     nb = r / gsz;
   };
+  // Wave quantisation: with T tiles on C clusters the last round keeps only T mod C clusters busy. When that remainder is
+  // at most C / 2 the host asks for those tiles to be computed as two 128-column halves each (a unit of work half as
+  // long), so the last round takes half the time. Units [0, n_whole) are whole tiles, the rest are halves.
+  const int n_whole = num_tiles - p.split_tail;
+  const int num_units = n_whole + 2 * p.split_tail;
+  auto unit_coords = [&](int v, int& mp, int& nb, int& half) {
+    int t = v;
+    half = -1;
+    if (v >= n_whole) { const int h = v - n_whole; t = n_whole + (h >> 1); half = h & 1; }
+    tile_coords(t, mp, nb);
+  };
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs, each for its own halves) ----------------
@@ -177,18 +188,21 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       const uint32_t leader_full0 = mapa_shared(smem_u32(&full_bar[0]), 0);
-      for (int t = my_cluster; t < num_tiles && ok; t += n_clusters) {
-        int mp, nb; tile_coords(t, mp, nb);
+      for (int t = my_cluster; t < num_units && ok; t += n_clusters) {
+        int mp, nb, half; unit_coords(t, mp, nb, half);
         const int a_row0 = mp * 2 * GEMM_BM + static_cast<int>(cta) * GEMM_BM;
+        const int nbox = half >= 0 ? 1 : 2;                    // 64-row boxes of B per CTA and stage
         int b_row0;
-        if constexpr (EPI == EPI_SWIGLU_BF16) b_row0 = nb * G2_HALF + static_cast<int>(cta) * (p.N / 2);   // leader: gate rows, peer: up rows
-        else b_row0 = nb * G2_BN + static_cast<int>(cta) * G2_HALF;
+        if constexpr (EPI == EPI_SWIGLU_BF16)                  // leader: gate rows, peer: up rows
+          b_row0 = nb * G2_HALF + (half > 0 ? 64 : 0) + static_cast<int>(cta) * (p.N / 2);
+        else
+          b_row0 = nb * G2_BN + (half >= 0 ? half * G2_HALF + static_cast<int>(cta) * 64 : static_cast<int>(cta) * G2_HALF);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait_cluster(&empty_bar[stage], phase ^ 1, abort_flag, p.status, PFB_ERR_WAIT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + stage * S::STAGE_BYTES;
           uint8_t* sb = sa + S::A_BYTES;
           const uint32_t fb = leader_full0 + stage * 8;
-          if (leader) mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);   // this CTA's bytes and the peer's
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * (S::A_BYTES + nbox * (S::B_BYTES / 2)));   // this CTA's bytes and the peer's
           if constexpr (!A_MN) {
             tma_load_2d_pair(sa, &tmA, fb, kb * GEMM_BK, a_row0);
           } else {
@@ -196,12 +210,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             for (int j = 0; j < GEMM_BM / 64; ++j)
               tma_load_2d_pair(sa + j * (GEMM_BK * 128), &tmA, fb, a_row0 + j * 64, kb * GEMM_BK);
           }
-          if constexpr (!B_MN) {
-            tma_load_2d_pair(sb, &tmB, fb, kb * GEMM_BK, b_row0);
-          } else {
-            #pragma unroll
-            for (int j = 0; j < G2_HALF / 64; ++j)
-              tma_load_2d_pair(sb + j * (GEMM_BK * 128), &tmB, fb, b_row0 + j * 64, kb * GEMM_BK);
+          for (int j = 0; j < nbox; ++j) {
+            if constexpr (!B_MN) tma_load_2d_pair(sb + j * (64 * 128), &tmB, fb, kb * GEMM_BK, b_row0 + j * 64);
+            else tma_load_2d_pair(sb + j * (GEMM_BK * 128), &tmB, fb, b_row0 + j * 64, kb * GEMM_BK);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -213,11 +224,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       bool ok = true;
       if (leader) {
         // ---------------- leader: MMA issuer for the pair ----------------
-        constexpr uint32_t idesc = make_idesc(2 * GEMM_BM, G2_BN, A_MN, B_MN, 1);
+        constexpr uint32_t idesc_whole = make_idesc(2 * GEMM_BM, G2_BN, A_MN, B_MN, 1);
+        constexpr uint32_t idesc_half = make_idesc(2 * GEMM_BM, G2_HALF, A_MN, B_MN, 1);
         const uint32_t peer_empty0 = mapa_shared(smem_u32(&empty_bar[0]), 1);
         const uint32_t peer_tfull0 = mapa_shared(smem_u32(&tfull_bar[0]), 1);
         int acc = 0; uint32_t acc_phase = 0;
-        for (int t = my_cluster; t < num_tiles && ok; t += n_clusters) {
+        for (int t = my_cluster; t < num_units && ok; t += n_clusters) {
+          const uint32_t idesc = t >= n_whole ? idesc_half : idesc_whole;
           if (!mbar_wait_cluster(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, PFB_ERR_WAIT_TMEM_EMPTY)) break;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * G2_BN;
@@ -250,8 +263,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int quad = warp & 3;
     const uint32_t leader_tempty0 = mapa_shared(smem_u32(&tempty_bar[0]), 0);
     int acc = 0; uint32_t acc_phase = 0;
-    for (int t = my_cluster; t < num_tiles; t += n_clusters) {
-      int mp, nb; tile_coords(t, mp, nb);
+    for (int t = my_cluster; t < num_units; t += n_clusters) {
+      int mp, nb, half; unit_coords(t, mp, nb, half);
       if (!mbar_wait_cluster(&tfull_bar[acc], acc_phase, abort_flag, p.status, PFB_ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const int row = mp * 2 * GEMM_BM + static_cast<int>(cta) * GEMM_BM + quad * 32 + lane;
@@ -261,8 +274,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // row) and hands them to the TMA unit as reduce-add operations: D += tile is formed in L2
         uint8_t* my_stg = smem + S::STAGING_OFFSET + (warp - 2) * 8192;
         const int row0 = row - lane;
+        const int width = half >= 0 ? G2_HALF : G2_BN;
+        const int col0 = nb * G2_BN + (half > 0 ? G2_HALF : 0);
         #pragma unroll 1
-        for (int c = 0; c < G2_BN; c += 32) {
+        for (int c = 0; c < width; c += 32) {
           uint32_t v[32];
           tmem_ld_32x32(taddr + c, v);
           tmem_ld_wait();
@@ -275,11 +290,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0 && row0 < p.M && nb * G2_BN + c < p.N) {
-            tma_reduce_add_2d(&tmD, slab, nb * G2_BN + c, row0);
+          if (lane == 0 && row0 < p.M && col0 + c < p.N) {
+            tma_reduce_add_2d(&tmD, slab, col0 + c, row0);
             tma_store_commit();
           }
         }
+      } else if (half >= 0) {
+        gemm_store_tile<G2_HALF, EPI>(taddr, row, 2 * nb + half, p, 0);
       } else {
         gemm_store_tile<G2_BN, EPI>(taddr, row, nb, p, 0);
       }

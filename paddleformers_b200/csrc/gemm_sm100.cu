@@ -100,10 +100,19 @@ static bool pair_enabled() {
   return on;
 }
 
-// PFB_GEMM_TMA_REDUCE=1: the fp32-accumulating weight-gradient product adds its tiles through TMA reduce operations (the
-// sum is formed in L2) instead of reading the old values into the epilogue warps
+// The fp32-accumulating weight-gradient product adds its tiles through TMA reduce operations (the sum is formed in L2)
+// instead of reading the old values into the epilogue warps: +9-24 % on the model's weight-gradient shapes.
+// PFB_GEMM_TMA_REDUCE=0 restores the read-add-store epilogue.
 static bool tma_reduce_enabled() {
-  static const bool on = [] { const char* e = std::getenv("PFB_GEMM_TMA_REDUCE"); return e != nullptr && std::string(e) == "1"; }();
+  static const bool on = [] { const char* e = std::getenv("PFB_GEMM_TMA_REDUCE"); return e == nullptr || std::string(e) != "0"; }();
+  return on;
+}
+
+// When the last round of tiles would keep at most half of the CTA pairs busy, its tiles are computed as two 128-column
+// halves each, which halves the length of that round (+3-7 % on products with 256 or 384 tiles). PFB_GEMM_TAIL_SPLIT=0
+// switches it off.
+static bool tail_split_enabled() {
+  static const bool on = [] { const char* e = std::getenv("PFB_GEMM_TAIL_SPLIT"); return e == nullptr || std::string(e) != "0"; }();
   return on;
 }
 
@@ -214,9 +223,12 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, bool a_mn, 
       p2.group_m = 8;
       CUtensorMap tmA2 = a_mn ? make_tma_2d(a.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, a.stride(0), GEMM_BK, 64)
                               : make_tma_2d(a.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, a.stride(0), GEMM_BM, 64);
+      // B travels in 64-row boxes: two per CTA and stage for a whole tile, one for a half tile
       CUtensorMap tmB2 = b_mn ? make_tma_2d(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Kb, Nb_rows, b.stride(0), GEMM_BK, 64)
-                              : make_tma_2d(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Nb_rows, K, b.stride(0), G2_HALF, 64);
+                              : make_tma_2d(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Nb_rows, K, b.stride(0), 64, 64);
       const int n_clusters = static_cast<int>(std::min<long long>(tiles2, pairs));
+      const int tail = static_cast<int>(tiles2 % n_clusters);
+      if (tail_split_enabled() && tiles2 > n_clusters && tail > 0 && 2 * tail <= n_clusters) p2.split_tail = tail;
       int epi2 = static_cast<int>(epi);
       CUtensorMap tmD2 = tmA2;     // only the reduce-add epilogue reads it
       if (epi2 == EPI_ACCUM_F32 && a_mn && b_mn && tma_reduce_enabled() && out.stride(0) % 4 == 0 &&

@@ -44,6 +44,7 @@ struct GemmParams {
   int tiles_per_expert;     // k-grouped: m_blocks * n_blocks of one expert's [N, K] gradient
   long long d_expert_stride;  // k-grouped: elements between consecutive experts in D
   int* status;              // error word (0 = ok)
+  int split_tail = 0;       // CTA-pair kernel: this many tiles at the end of the tile list are computed as two 128-column halves
 };
 
 template <int BN, int STAGES>

@@ -60,6 +60,10 @@ def bench_gemm(rows):
         ("down dgrad", 4096, 14336, 4096, False, True, F.EPI_STORE_BF16),
         ("gate_up wgrad", 28672, 4096, 4096, True, True, F.EPI_ACCUM_F32),
         ("down wgrad", 4096, 14336, 4096, True, True, F.EPI_ACCUM_F32),
+        ("qkv dgrad", 4096, 4096, 6144, False, True, F.EPI_STORE_BF16),
+        ("qkv wgrad", 6144, 4096, 4096, True, True, F.EPI_ACCUM_F32),
+        ("o wgrad", 4096, 4096, 4096, True, True, F.EPI_ACCUM_F32),
+        ("o_proj 1/8 of K", 4096, 4096, 512, False, False, F.EPI_STORE_BF16),
         ("lm_head 2k", 2048, 128256, 4096, False, False, F.EPI_STORE_BF16),
         ("square 8k", 8192, 8192, 8192, False, False, F.EPI_STORE_BF16),
     ]

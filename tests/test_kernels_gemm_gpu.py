@@ -172,8 +172,8 @@ print("RESULT", "OK" if not bad else f"BAD {bad}")
 
 
 def test_weight_gradient_accumulates_through_tma_reduce_add(tmp_path):
-    """PFB_GEMM_TMA_REDUCE=1: the CTA-pair kernel adds its fp32 tiles to the gradient buffer with TMA reduce operations
-    (the sum is formed in L2). The switch is read once per process, so the check runs in a child process."""
+    """The CTA-pair kernel adds its fp32 tiles to the gradient buffer with TMA reduce operations (the sum is formed in L2;
+    PFB_GEMM_TMA_REDUCE, on by default). The switch is read once per process, so the check runs in a child process."""
     import os
     import subprocess
     import sys
@@ -183,4 +183,58 @@ def test_weight_gradient_accumulates_through_tma_reduce_add(tmp_path):
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     res = subprocess.run([sys.executable, str(script), repo], env=dict(os.environ, PFB_GEMM_TMA_REDUCE="1"), capture_output=True,
                          text=True, timeout=600)
+    assert res.returncode == 0 and "RESULT OK" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+_TAIL_WORKER = r'''
+import sys, torch
+sys.path.insert(0, sys.argv[1])
+from paddleformers_b200.ops import functional as F
+torch.manual_seed(0)
+def rel(a, b): return ((a.double() - b.double()).norm() / b.double().norm()).item()
+bad = []
+# 256 / 384 tiles of 256 x 256 on 74 CTA pairs: the last round (34 / 14 tiles) is computed as 128-column halves
+for M, N, K in ((4096, 4096, 512), (4096, 6144, 256), (4000, 4096, 320)):
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    y = F.gemm(x, w)                                              # forward: both operands K-major
+    if not rel(y, x.float() @ w.float().t()) < 6e-3: bad.append(("fwd", M, N, K))
+    dy = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    dx = F.gemm(dy, w, b_mn=True)                                 # input gradient: B read MN-major
+    if not rel(dx, dy.float() @ w.float()) < 6e-3: bad.append(("dgrad", M, N, K))
+    acc = torch.randn(N, K, device="cuda")
+    ref = acc.double() + dy.double().t() @ x.double()
+    F.gemm(dy, x, out=acc, a_mn=True, b_mn=True, epi=F.EPI_ACCUM_F32)    # weight gradient (few tiles here: whole tiles only)
+    if not rel(acc, ref) < 2e-3: bad.append(("wgrad", M, N, K))
+T, H, I = 4096, 512, 2048
+x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+wgu = (torch.randn(2 * I, H, device="cuda") * 0.05).to(torch.bfloat16)
+act = F.linear_swiglu(x, wgu) if hasattr(F, "linear_swiglu") else None
+if act is not None:
+    gu = x.float() @ wgu.float().t()
+    if not rel(act, torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]) < 8e-3: bad.append(("swiglu",))
+dy = torch.randn(4096, 4096, device="cuda", dtype=torch.bfloat16)
+xx = torch.randn(4096, 4096, device="cuda", dtype=torch.bfloat16)
+acc = torch.zeros(4096, 4096, device="cuda")
+F.gemm(dy, xx, out=acc, a_mn=True, b_mn=True, epi=F.EPI_ACCUM_F32)       # 256 tiles: split tail with the accumulate epilogue
+if not rel(acc, dy.float().t() @ xx.float()) < 2e-3: bad.append(("wgrad_tail",))
+F.check_kernel_status()
+print("RESULT", "OK" if not bad else f"BAD {bad}")
+'''
+
+
+@pytest.mark.parametrize("env", [dict(PFB_GEMM_TAIL_SPLIT="1", PFB_GEMM_TMA_REDUCE="0"), dict(PFB_GEMM_TAIL_SPLIT="1", PFB_GEMM_TMA_REDUCE="1"),
+                                 dict(PFB_GEMM_TAIL_SPLIT="0", PFB_GEMM_TMA_REDUCE="0")])
+def test_last_round_of_tiles_split_into_half_tiles(tmp_path, env):
+    """Tiles of the last, partly filled round are computed as two 128-column halves (PFB_GEMM_TAIL_SPLIT, on by default);
+    every epilogue and operand layout against fp32, with the switches on and off (they are read once per process, so the
+    check runs in a child process)."""
+    import os
+    import subprocess
+    import sys
+
+    script = tmp_path / "w.py"
+    script.write_text(_TAIL_WORKER)
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, str(script), repo], env=dict(os.environ, **env), capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and "RESULT OK" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
