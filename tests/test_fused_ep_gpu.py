@@ -85,8 +85,8 @@ def _run(tmp_path, nproc, port):
            f"--master-port={port}", str(script)]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
-    lines = [l for l in res.stdout.splitlines() if l.startswith("RESULT")]
-    assert len(lines) == nproc and all(l.startswith("RESULT OK") for l in lines), res.stdout[-3000:]
+    # the ranks write into one pipe at the same time, so two of their lines can interleave: count tokens, not lines
+    assert res.stdout.count("OK") >= nproc and res.stdout.count("RESULT") == nproc and "BAD" not in res.stdout, res.stdout[-3000:]
 
 
 def test_fused_ep_single_rank(tmp_path):

@@ -65,5 +65,5 @@ def test_fused_sharding_matches_nccl_path_bitwise(tmp_path):
            "--master-port=29547", str(script)]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
-    lines = [l for l in res.stdout.splitlines() if l.startswith("RESULT")]
-    assert len(lines) == 2 and all(l == "RESULT OK" for l in lines), res.stdout[-3000:]
+    # the ranks write into one pipe at the same time, so two of their lines can interleave: count tokens, not lines
+    assert res.stdout.count("OK") >= 2 and res.stdout.count("RESULT") == 2 and "BAD" not in res.stdout, res.stdout[-3000:]

@@ -122,8 +122,8 @@ def _run_workers(tmp_path, text, n, port):
            f"--master-port={port}", str(script)]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
-    lines = [l for l in res.stdout.splitlines() if l.startswith("RESULT")]
-    assert len(lines) == n and all(l == "RESULT OK" for l in lines), res.stdout[-3000:]
+    # the ranks write into one pipe at the same time, so two of their lines can interleave: count tokens, not lines
+    assert res.stdout.count("OK") >= n and res.stdout.count("RESULT") == n and "BAD" not in res.stdout, res.stdout[-3000:]
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
@@ -146,5 +146,5 @@ def test_fused_tp_linears_match_nccl_path(tmp_path):
            "--master-port=29541", str(script)]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
-    lines = [l for l in res.stdout.splitlines() if l.startswith("RESULT")]
-    assert len(lines) == 2 and all(l == "RESULT OK" for l in lines), res.stdout[-3000:]
+    # the ranks write into one pipe at the same time, so two of their lines can interleave: count tokens, not lines
+    assert res.stdout.count("OK") >= 2 and res.stdout.count("RESULT") == 2 and "BAD" not in res.stdout, res.stdout[-3000:]
