@@ -349,9 +349,84 @@ void ep_pull_rows(c10::optional<at::Tensor> out, const at::Tensor& idx, const at
   count_launch();
 }
 
+// ---- routing-weight gradient formed on the expert's side -----------------------------------------------------------
+// rowdots[slot] = <y[slot, :], dy[slot, :]> for the rows this rank's experts hold (one warp per row). dy rows are w * dout,
+// so the source rank recovers <y_row, dout> = rowdots / w and never re-reads the expert outputs across NVLink.
+__global__ void ep_row_dots_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ dy, float* __restrict__ rowdots,
+                                   const int* __restrict__ expert_rows, int EL, int H, int capacity_rows) {
+  const int lane = threadIdx.x & 31;
+  const int rows = min(capacity_rows, expert_rows[2 * (EL - 1)] + expert_rows[2 * (EL - 1) + 1]);
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int nv = H >> 3;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+    const uint4* a = reinterpret_cast<const uint4*>(y + static_cast<long long>(r) * H);
+    const uint4* b = reinterpret_cast<const uint4*>(dy + static_cast<long long>(r) * H);
+    float acc = 0.f;
+    for (int i = lane; i < nv; i += 32) {
+      const uint4 va = a[i], vb = b[i];
+      const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&va);
+      const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&vb);
+      #pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 fa = __bfloat1622float2(ha[q]), fb = __bfloat1622float2(hb[q]);
+        acc += fa.x * fb.x + fa.y * fb.y;
+      }
+    }
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) rowdots[r] = acc;
+  }
+}
+
+struct EpScalarPeers { const float* buf[EP_MAX_RANKS]; };
+
+// dots[p] = rowdots_of_destination[slot(p)] / w[p] (0 for dropped pairs and for w == 0): 4 bytes per pair across NVLink
+__global__ void ep_pull_scalars_kernel(float* __restrict__ dots, const long long* __restrict__ idx, const int* __restrict__ pair_slot,
+                                       const float* __restrict__ w, EpScalarPeers peers, int n_pairs, int EL, int capacity_rows) {
+  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += gridDim.x * blockDim.x) {
+    const int slot = pair_slot[p];
+    const float wp = w[p];
+    float v = 0.f;
+    if (slot < capacity_rows && wp != 0.f) v = peers.buf[static_cast<int>(idx[p] / EL)][slot] / wp;
+    dots[p] = v;
+  }
+}
+
+void ep_row_dots(const at::Tensor& y, const at::Tensor& dy, at::Tensor& rowdots, const at::Tensor& expert_rows, int64_t EL) {
+  TORCH_CHECK(y.is_cuda() && y.scalar_type() == at::kBFloat16 && dy.scalar_type() == at::kBFloat16 && y.is_contiguous() && dy.is_contiguous());
+  TORCH_CHECK(y.sizes() == dy.sizes() && y.size(1) % 8 == 0 && rowdots.scalar_type() == at::kFloat && rowdots.numel() >= y.size(0));
+  TORCH_CHECK(expert_rows.scalar_type() == at::kInt && expert_rows.numel() == 2 * EL);
+  const c10::cuda::CUDAGuard guard(y.device());
+  const int blocks = at::cuda::getCurrentDeviceProperties()->multiProcessorCount * 8;
+  ep_row_dots_kernel<<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const __nv_bfloat16*>(y.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(dy.data_ptr()), rowdots.data_ptr<float>(),
+      expert_rows.data_ptr<int>(), static_cast<int>(EL), static_cast<int>(y.size(1)), static_cast<int>(y.size(0)));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
+void ep_pull_scalars(at::Tensor& dots, const at::Tensor& idx, const at::Tensor& pair_slot, const at::Tensor& w,
+                     const at::Tensor& peer_rowdots_ptrs, int64_t EL, int64_t ep, int64_t capacity_rows) {
+  TORCH_CHECK(dots.is_cuda() && dots.scalar_type() == at::kFloat && w.scalar_type() == at::kFloat && dots.numel() == idx.numel() &&
+              w.numel() == idx.numel() && ep <= EP_MAX_RANKS && !peer_rowdots_ptrs.is_cuda());
+  const c10::cuda::CUDAGuard guard(dots.device());
+  EpScalarPeers peers{};
+  for (int q = 0; q < ep; ++q) peers.buf[q] = reinterpret_cast<const float*>(peer_rowdots_ptrs.data_ptr<int64_t>()[q]);
+  const int n = static_cast<int>(idx.numel());
+  if (n == 0) return;
+  ep_pull_scalars_kernel<<<std::min((n + 255) / 256, 148 * 8), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      dots.data_ptr<float>(), reinterpret_cast<const long long*>(idx.data_ptr<int64_t>()), pair_slot.data_ptr<int>(), w.data_ptr<float>(),
+      peers, n, static_cast<int>(EL), static_cast<int>(capacity_rows));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
 }  // namespace pfb
 
 TORCH_LIBRARY_FRAGMENT(pfb200, m) {
+  m.def("ep_row_dots(Tensor y, Tensor dy, Tensor(a!) rowdots, Tensor expert_rows, int EL) -> ()", &pfb::ep_row_dots);
+  m.def("ep_pull_scalars(Tensor(a!) dots, Tensor idx, Tensor pair_slot, Tensor w, Tensor peer_rowdots_ptrs, int EL, int ep, "
+        "int capacity_rows) -> ()", &pfb::ep_pull_scalars);
   m.def("ep_exchange(Tensor peer_tab_ptrs, Tensor my_counts, Tensor(a!) block_expert, Tensor(b!) expert_rows, Tensor(c!) total_rows, "
         "int rank, int ep, int EL, Tensor epoch) -> ()", &pfb::ep_exchange);
   m.def("ep_push_rows(Tensor x, Tensor idx, Tensor rank_in_expert, Tensor? scale, Tensor peer_tab_ptrs, Tensor(a!) pair_slot, "

@@ -391,4 +391,96 @@ __global__ void qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dout, 
   for (int i = threadIdx.x; i < D; i += blockDim.x) atomicAdd(&dnw[i], sdnw[i]);
 }
 
+// ---- 128-wide heads with full rotary (D == rot == 128): 8-byte accesses -------------------------------------------
+// Lane l holds elements 4l .. 4l+3 of the head; the rotation partner of element i (i + 64 or i - 64) lives in lane l ^ 16.
+__device__ __forceinline__ void ld_bf16x4(const __nv_bfloat16* p, float (&f)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ void st_bf16x4(__nv_bfloat16* p, const float (&f)[4]) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
+__global__ void qk_norm_rope_fwd128_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                                           const __nv_bfloat16* __restrict__ nw, float* __restrict__ rstd_out,
+                                           const int* __restrict__ pos, const float* __restrict__ cs, const float* __restrict__ sn,
+                                           int T, int n_heads, long long x_row_stride, long long out_row_stride, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(T) * n_heads;
+  const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  float w[4];
+  ld_bf16x4(nw + lane * 4, w);
+  const bool first = lane < 16;
+  for (long long wi = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; wi < total; wi += warps_total) {
+    const int t = static_cast<int>(wi / n_heads), h = static_cast<int>(wi - static_cast<long long>(t) * n_heads);
+    float v[4];
+    ld_bf16x4(x + t * x_row_stride + static_cast<long long>(h) * 128 + lane * 4, v);
+    float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss * (1.f / 128.f) + eps);
+    if (lane == 0 && rstd_out) rstd_out[wi] = rstd;
+    const int p = pos ? pos[t] : t;
+    const float4 c4 = *reinterpret_cast<const float4*>(cs + static_cast<long long>(p) * 64 + (lane & 15) * 4);
+    const float4 s4 = *reinterpret_cast<const float4*>(sn + static_cast<long long>(p) * 64 + (lane & 15) * 4);
+    const float c[4] = {c4.x, c4.y, c4.z, c4.w}, s[4] = {s4.x, s4.y, s4.z, s4.w};
+    float o[4];
+    #pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float y = v[j] * rstd * w[j];
+      const float other = __shfl_xor_sync(0xffffffffu, y, 16);
+      o[j] = first ? y * c[j] - other * s[j] : y * c[j] + other * s[j];
+    }
+    st_bf16x4(out + t * out_row_stride + static_cast<long long>(h) * 128 + lane * 4, o);
+  }
+}
+
+__global__ void qk_norm_rope_bwd128_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ x,
+                                           const __nv_bfloat16* __restrict__ nw, const float* __restrict__ rstd_in,
+                                           __nv_bfloat16* __restrict__ dx, float* __restrict__ dnw, const int* __restrict__ pos,
+                                           const float* __restrict__ cs, const float* __restrict__ sn, int T, int n_heads,
+                                           long long dout_row_stride, long long x_row_stride, long long dx_row_stride) {
+  __shared__ float sdnw[128];
+  for (int i = threadIdx.x; i < 128; i += blockDim.x) sdnw[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(T) * n_heads;
+  const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  float w[4], acc[4] = {0.f, 0.f, 0.f, 0.f};
+  ld_bf16x4(nw + lane * 4, w);
+  const bool first = lane < 16;
+  for (long long wi = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; wi < total; wi += warps_total) {
+    const int t = static_cast<int>(wi / n_heads), h = static_cast<int>(wi - static_cast<long long>(t) * n_heads);
+    float d[4], xv[4];
+    ld_bf16x4(dout + t * dout_row_stride + static_cast<long long>(h) * 128 + lane * 4, d);
+    ld_bf16x4(x + t * x_row_stride + static_cast<long long>(h) * 128 + lane * 4, xv);
+    const float rstd = rstd_in[wi];
+    const int p = pos ? pos[t] : t;
+    const float4 c4 = *reinterpret_cast<const float4*>(cs + static_cast<long long>(p) * 64 + (lane & 15) * 4);
+    const float4 s4 = *reinterpret_cast<const float4*>(sn + static_cast<long long>(p) * 64 + (lane & 15) * 4);
+    const float c[4] = {c4.x, c4.y, c4.z, c4.w}, s[4] = {s4.x, s4.y, s4.z, s4.w};
+    float dy[4], dot = 0.f;
+    #pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, d[j], 16);
+      const float g = first ? d[j] * c[j] + other * s[j] : d[j] * c[j] - other * s[j];   // gradient of the normed, weighted value
+      acc[j] += g * xv[j] * rstd;
+      dy[j] = g * w[j];
+      dot += dy[j] * xv[j];
+    }
+    dot = warp_sum(dot);
+    const float coef = dot * rstd * rstd * rstd * (1.f / 128.f);
+    float o[4];
+    #pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = rstd * dy[j] - coef * xv[j];
+    st_bf16x4(dx + t * dx_row_stride + static_cast<long long>(h) * 128 + lane * 4, o);
+  }
+  #pragma unroll
+  for (int j = 0; j < 4; ++j) atomicAdd(&sdnw[lane * 4 + j], acc[j]);
+  __syncthreads();
+  for (int i = threadIdx.x; i < 128; i += blockDim.x) atomicAdd(&dnw[i], sdnw[i]);
+}
+
 }  // namespace pfb

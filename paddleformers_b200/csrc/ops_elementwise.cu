@@ -154,6 +154,17 @@ at::Tensor qk_norm_rope_fwd(const at::Tensor& x, at::Tensor& out, const at::Tens
   const int* pp = pos.has_value() ? pos->data_ptr<int>() : nullptr;
   const long long warps = static_cast<long long>(T) * n_heads;
   const int threads = 256;
+  auto aligned8 = [](const at::Tensor& t) { return (reinterpret_cast<uintptr_t>(t.data_ptr()) & 7) == 0 && t.stride(0) % 4 == 0; };
+  if (D == 128 && rot == 128 && aligned8(x) && aligned8(out) && (reinterpret_cast<uintptr_t>(nw.data_ptr()) & 7) == 0) {
+    // 128-wide heads with full rotary: 8-byte accesses, warps stride over the (token, head) pairs
+    const int blocks = static_cast<int>(std::min<long long>((warps * 32 + threads - 1) / threads, static_cast<long long>(num_sms()) * 16));
+    qk_norm_rope_fwd128_kernel<<<blocks, threads, 0, cur_stream()>>>(
+        bf(x), bfm(out), bf(nw), rstd.data_ptr<float>(), pp, cos.data_ptr<float>(), sin.data_ptr<float>(), T,
+        static_cast<int>(n_heads), x.stride(0), out.stride(0), static_cast<float>(eps));
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    count_launch();
+    return rstd;
+  }
   qk_norm_rope_fwd_kernel<<<static_cast<int>((warps * 32 + threads - 1) / threads), threads, 0, cur_stream()>>>(
       bf(x), bfm(out), bf(nw), rstd.data_ptr<float>(), pp, cos.data_ptr<float>(), sin.data_ptr<float>(), T,
       static_cast<int>(n_heads), static_cast<int>(D), static_cast<int>(rot), x.stride(0), out.stride(0),
@@ -172,6 +183,15 @@ void qk_norm_rope_bwd(const at::Tensor& dout, const at::Tensor& x, const at::Ten
   const int T = x.size(0);
   if (T == 0) return;
   const int* pp = pos.has_value() ? pos->data_ptr<int>() : nullptr;
+  auto aligned8 = [](const at::Tensor& t) { return (reinterpret_cast<uintptr_t>(t.data_ptr()) & 7) == 0 && t.stride(0) % 4 == 0; };
+  if (D == 128 && rot == 128 && aligned8(dout) && aligned8(x) && aligned8(dx) && (reinterpret_cast<uintptr_t>(nw.data_ptr()) & 7) == 0) {
+    qk_norm_rope_bwd128_kernel<<<num_sms() * 8, 256, 0, cur_stream()>>>(
+        bf(dout), bf(x), bf(nw), rstd.data_ptr<float>(), bfm(dx), dnw.data_ptr<float>(), pp, cos.data_ptr<float>(),
+        sin.data_ptr<float>(), T, static_cast<int>(n_heads), dout.stride(0), x.stride(0), dx.stride(0));
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    count_launch();
+    return;
+  }
   qk_norm_rope_bwd_kernel<<<num_sms() * 4, 256, 0, cur_stream()>>>(
       bf(dout), bf(x), bf(nw), rstd.data_ptr<float>(), bfm(dx), dnw.data_ptr<float>(), pp, cos.data_ptr<float>(),
       sin.data_ptr<float>(), T, static_cast<int>(n_heads), static_cast<int>(D), static_cast<int>(rot), dout.stride(0),

@@ -164,6 +164,17 @@ def bench_elementwise(rows):
     rows.append(f"rope in place [{T}, 40 heads x 128]: {2 * T * 40 * 128 * 2 / ms / 1e6:7.1f} GB/s "
                 f"({2 * T * 40 * 128 * 2 / ms / 1e6 / peaks['hbm_gbs']:.2f} of measured copy)")
     print(rows[-1], flush=True)
+    # per-head RMSNorm + rotary on 32 heads of 128 (Qwen3), forward and backward
+    xq = torch.randn(T, 32 * 128, device="cuda", dtype=torch.bfloat16)
+    nw = torch.ones(128, device="cuda", dtype=torch.bfloat16)
+    oq = torch.empty_like(xq)
+    ms = timeit(lambda: ops.qk_norm_rope_fwd(xq, oq, nw, None, cos, sin, 32, 128, 128, 1e-6))
+    rstd_q = ops.qk_norm_rope_fwd(xq, oq, nw, None, cos, sin, 32, 128, 128, 1e-6)
+    dnw = torch.zeros(128, device="cuda")
+    ms_b = timeit(lambda: ops.qk_norm_rope_bwd(oq, xq, nw, rstd_q, xq.new_empty(xq.shape), dnw, None, cos, sin, 32, 128, 128))
+    rows.append(f"qk_norm + rope [{T}, 32 heads x 128]: forward {2 * xq.numel() * 2 / ms / 1e6:7.1f} GB/s, backward "
+                f"{3 * xq.numel() * 2 / ms_b / 1e6:7.1f} GB/s ({3 * xq.numel() * 2 / ms_b / 1e6 / peaks['hbm_gbs']:.2f} of measured copy)")
+    print(rows[-1], flush=True)
     gu = torch.randn(T, 2 * I, device="cuda", dtype=torch.bfloat16)
     ms = timeit(lambda: torch.ops.pfb200.swiglu_fwd(gu))
     rows.append(f"swiglu fwd [{T},{2 * I}]: {3 * T * I * 2 / ms / 1e6:7.1f} GB/s")
@@ -244,6 +255,7 @@ def main():
     ap.add_argument("--what", default="gemm,attn,elementwise")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
+    F._ops()                 # load the extension before the first torch.ops.pfb200 lookup
     rows = []
     for w in args.what.split(","):
         {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise, "fp8": bench_fp8}[w](rows)

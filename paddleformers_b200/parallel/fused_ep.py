@@ -11,8 +11,10 @@ reference, paddleformers/transformers/fused_a2a.py:81-178 and paddleformers/nn/m
 3. grouped expert GEMMs on the receive buffer, output written into a peer-visible buffer.
 4. ``ep_pull_rows``  each source reads its k rows back and forms the weighted sum.
 
-The backward pass mirrors it: the combine's backward pushes ``w * dout`` rows and reads the expert outputs again for
-the routing-weight gradient; the dispatch's backward pulls the expert input gradients.
+The backward pass mirrors it: the combine's backward pushes ``w * dout`` rows; the routing-weight gradient is formed on
+the expert's side (a dot product of each received gradient row with the expert output beside it, 4 bytes per pair
+fetched back; ``PFB_EP_LOCAL_DOTS=0`` re-reads the expert outputs remotely instead); the dispatch's backward pulls the
+expert input gradients.
 
 Buffers. Per MoE layer and micro-batch in flight: the receive buffer (it is the saved activation of the expert GEMMs) and
 the expert output buffer (read again in the backward pass). Without pipeline parallelism one micro-batch is in flight;
@@ -30,7 +32,7 @@ import torch
 
 from .fused_collectives import SymmetricArena, _Region
 
-FLAG_COUNTS, FLAG_OFFSETS, FLAG_ROWS, FLAG_Y, FLAG_DY, FLAG_DX = 0, 1, 2, 3, 4, 5
+FLAG_COUNTS, FLAG_OFFSETS, FLAG_ROWS, FLAG_Y, FLAG_DY, FLAG_DX, FLAG_RD = 0, 1, 2, 3, 4, 5, 6
 _MAX_RANKS = 8
 STATS = {"dispatch": 0, "combine": 0}
 
@@ -58,6 +60,8 @@ class EPWorkspace:
         self.table = _Region(self.arena, (2 * self.ep * num_local + 8 * _MAX_RANKS,), torch.int32)
         self.dy = _Region(self.arena, (self.cap, H), torch.bfloat16)
         self.dxr = _Region(self.arena, (self.cap, H), torch.bfloat16)
+        self.rowdots = _Region(self.arena, (self.cap,), torch.float32)     # <expert output row, weighted gradient row>
+        self.local_dots = os.environ.get("PFB_EP_LOCAL_DOTS", "1") != "0"
         self.fwd_epoch = torch.zeros(1, dtype=torch.int32, device=dev)
         self.bwd_epoch = torch.zeros(1, dtype=torch.int32, device=dev)
         self.done = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -215,8 +219,19 @@ class _Combine(torch.autograd.Function):
         ws.bwd_epoch.add_(1)
         ws.push(dout, plan, wf, ws.dy, FLAG_DY, ws.bwd_epoch, False)   # reuses the slots recorded in the forward pass
         dots = torch.empty(wf.numel(), dtype=torch.float32, device=dout.device)
-        ws.pull(None, plan, None, dout, dots, bufs["y"])
-        ws.wait(FLAG_DY, ws.bwd_epoch)
+        if ws.local_dots:
+            # Routing-weight gradient <expert output row, dout> formed where the rows are: once every peer's weighted
+            # gradient rows (w * dout) have landed, this rank takes the dot product of each of its rows with the expert
+            # output beside it (local memory) and the sources fetch 4 bytes per pair and divide by w, instead of reading
+            # the expert outputs (4 KB per pair) across NVLink a second time.
+            ws.wait(FLAG_DY, ws.bwd_epoch)
+            torch.ops.pfb200.ep_row_dots(bufs["y"].tensor, ws.dy.tensor, ws.rowdots.tensor, plan["expert_rows"], ws.EL)
+            ws.signal(FLAG_RD, ws.bwd_epoch)
+            ws.wait(FLAG_RD, ws.bwd_epoch)
+            torch.ops.pfb200.ep_pull_scalars(dots, plan["idx"], plan["pair_slot"], wf, ws.rowdots.peer_ptrs, ws.EL, ws.ep, ws.cap)
+        else:
+            ws.pull(None, plan, None, dout, dots, bufs["y"])
+            ws.wait(FLAG_DY, ws.bwd_epoch)
         return ws.dy.tensor.detach(), dots.view(ctx.w_shape).to(ctx.w_dtype), None, None, None
 
 

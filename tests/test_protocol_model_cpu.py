@@ -14,7 +14,7 @@ import random
 
 import pytest
 
-FLAG_COUNTS, FLAG_OFFSETS, FLAG_ROWS, FLAG_Y, FLAG_DY, FLAG_DX = range(6)
+FLAG_COUNTS, FLAG_OFFSETS, FLAG_ROWS, FLAG_Y, FLAG_DY, FLAG_DX, FLAG_RD = range(7)
 
 
 class Hazard(AssertionError):
@@ -121,9 +121,22 @@ def rank_program(w: World, me: int, layers: int, steps: int, broken: str = ""):
             for p in peers:                                       # combine backward: w * dout rows to the experts' ranks
                 yield from write(p, "dy", btag)
             yield from signal(FLAG_DY, bwd_epoch)
-            for p in peers:                                       # routing-weight gradient reads the expert outputs again
-                yield from read(p, f"y{L}", ftag, [p])
-            yield from wait(FLAG_DY, bwd_epoch)
+            if broken == "remote_dots":
+                for p in peers:                                   # older variant: re-read the expert outputs remotely
+                    yield from read(p, f"y{L}", ftag, [p])
+                yield from wait(FLAG_DY, bwd_epoch)
+            else:
+                # routing-weight gradient on the expert's side: row dots of (y, dy) into a shared scalar buffer, a flag,
+                # then every source fetches its pairs' scalars
+                yield from wait(FLAG_DY, bwd_epoch)
+                yield from read(me, f"y{L}", ftag, [me])
+                yield from read(me, "dy", btag, peers)
+                yield from write(me, "rowdots", btag)
+                yield from signal(FLAG_RD, bwd_epoch)
+                if broken != "no_wait_rd":
+                    yield from wait(FLAG_RD, bwd_epoch)
+                for p in peers:
+                    yield from read(p, "rowdots", btag, [p])
             yield from read(me, "dy", btag, peers)                # expert backward
             yield from read(me, f"x_recv{L}", ftag, peers)
             yield from write(me, "dxr", btag)
@@ -174,7 +187,7 @@ def test_dy_zero_fill_of_shared_buffer_is_ordered_before_the_next_push():
         run(2, layers=2, steps=2, seed=seed)
 
 
-@pytest.mark.parametrize("broken", ["no_wait_y", "no_wait_dx", "no_zero_order"])
+@pytest.mark.parametrize("broken", ["no_wait_y", "no_wait_dx", "no_zero_order", "no_wait_rd"])
 def test_checker_detects_a_removed_synchronisation(broken):
     caught = 0
     for seed in range(300):
