@@ -44,6 +44,7 @@ __device__ __forceinline__ int tab_flags(int ep, int EL) { return 2 * ep * EL; }
 
 __global__ void ep_exchange_kernel(EpTables tabs, const int* __restrict__ my_counts /*[ep*EL]*/, int* __restrict__ block_expert,
                                    int n_blocks, int* __restrict__ expert_rows /*[EL,2]*/, int* __restrict__ total_rows,
+                                   int* __restrict__ expert_tot /*[EL] rows received per expert before padding, or null*/,
                                    int rank, int ep, int EL, const int* __restrict__ epoch_ptr, int* status) {
   __shared__ int s_cnt[EP_MAX_RANKS * EP_MAX_LOCAL_EXPERTS];
   __shared__ int s_seg[EP_MAX_LOCAL_EXPERTS + 1];
@@ -84,6 +85,7 @@ __global__ void ep_exchange_kernel(EpTables tabs, const int* __restrict__ my_cou
       if (pos + padded > n_blocks * 128) padded = max(0, n_blocks * 128 - pos);
       expert_rows[2 * e] = pos;
       expert_rows[2 * e + 1] = padded;
+      if (expert_tot) expert_tot[e] = min(tot, padded);
       pos += padded;
     }
     s_seg[EL] = pos;
@@ -267,13 +269,15 @@ static EpPeers make_peers(const at::Tensor& peer_buf_ptrs, const at::Tensor& pee
 }
 
 void ep_exchange(const at::Tensor& peer_tab_ptrs, const at::Tensor& my_counts, at::Tensor& block_expert, at::Tensor& expert_rows,
-                 at::Tensor& total_rows, int64_t rank, int64_t ep, int64_t EL, const at::Tensor& epoch) {
+                 at::Tensor& total_rows, int64_t rank, int64_t ep, int64_t EL, const at::Tensor& epoch,
+                 c10::optional<at::Tensor> expert_tot) {
   TORCH_CHECK(ep <= EP_MAX_RANKS && EL <= EP_MAX_LOCAL_EXPERTS && my_counts.scalar_type() == at::kInt && my_counts.numel() == ep * EL);
   TORCH_CHECK(block_expert.scalar_type() == at::kInt && expert_rows.scalar_type() == at::kInt && expert_rows.numel() == 2 * EL);
   const c10::cuda::CUDAGuard guard(my_counts.device());
   ep_exchange_kernel<<<1, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
       make_tabs(peer_tab_ptrs, rank, ep), my_counts.data_ptr<int>(), block_expert.data_ptr<int>(), static_cast<int>(block_expert.numel()),
-      expert_rows.data_ptr<int>(), total_rows.data_ptr<int>(), rank, ep, EL, epoch.data_ptr<int>(), status_word());
+      expert_rows.data_ptr<int>(), total_rows.data_ptr<int>(), expert_tot.has_value() ? expert_tot->data_ptr<int>() : nullptr, rank, ep, EL,
+      epoch.data_ptr<int>(), status_word());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
 }
@@ -378,6 +382,37 @@ __global__ void ep_row_dots_kernel(const __nv_bfloat16* __restrict__ y, const __
   }
 }
 
+// Zero the padding rows of every expert segment (rows [start + received, start + padded)): the weight-gradient GEMMs read
+// whole 128-row blocks. One warp per row, 16-byte stores. Peers only ever write the received rows, so this may run while
+// their pushes for the same exchange arrive.
+__global__ void ep_zero_padding_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ expert_rows, const int* __restrict__ expert_tot,
+                                       int EL, int H, int capacity_rows) {
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, warps = (gridDim.x * blockDim.x) >> 5;
+  const int nv = H >> 3;
+  for (int w = warp; w < EL * 128; w += warps) {
+    const int e = w >> 7, r = w & 127;
+    const int start = expert_rows[2 * e], padded = expert_rows[2 * e + 1], tot = expert_tot[e];
+    const int row = start + tot + r;
+    if (tot + r >= padded || row >= capacity_rows) continue;
+    uint4* dst = reinterpret_cast<uint4*>(buf + static_cast<long long>(row) * H);
+    for (int i = lane; i < nv; i += 32) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+void ep_zero_padding(at::Tensor& buf, const at::Tensor& expert_rows, const at::Tensor& expert_tot, int64_t EL) {
+  TORCH_CHECK(buf.is_cuda() && buf.scalar_type() == at::kBFloat16 && buf.is_contiguous() && buf.size(1) % 8 == 0);
+  TORCH_CHECK(expert_rows.scalar_type() == at::kInt && expert_rows.numel() == 2 * EL && expert_tot.scalar_type() == at::kInt &&
+              expert_tot.numel() == EL);
+  const c10::cuda::CUDAGuard guard(buf.device());
+  const int blocks = static_cast<int>((EL * 128 * 32 + 255) / 256);
+  ep_zero_padding_kernel<<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<__nv_bfloat16*>(buf.data_ptr()), expert_rows.data_ptr<int>(), expert_tot.data_ptr<int>(), static_cast<int>(EL),
+      static_cast<int>(buf.size(1)), static_cast<int>(buf.size(0)));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
 struct EpScalarPeers { const float* buf[EP_MAX_RANKS]; };
 
 // dots[p] = rowdots_of_destination[slot(p)] / w[p] (0 for dropped pairs and for w == 0): 4 bytes per pair across NVLink
@@ -428,7 +463,8 @@ TORCH_LIBRARY_FRAGMENT(pfb200, m) {
   m.def("ep_pull_scalars(Tensor(a!) dots, Tensor idx, Tensor pair_slot, Tensor w, Tensor peer_rowdots_ptrs, int EL, int ep, "
         "int capacity_rows) -> ()", &pfb::ep_pull_scalars);
   m.def("ep_exchange(Tensor peer_tab_ptrs, Tensor my_counts, Tensor(a!) block_expert, Tensor(b!) expert_rows, Tensor(c!) total_rows, "
-        "int rank, int ep, int EL, Tensor epoch) -> ()", &pfb::ep_exchange);
+        "int rank, int ep, int EL, Tensor epoch, Tensor(d!)? expert_tot) -> ()", &pfb::ep_exchange);
+  m.def("ep_zero_padding(Tensor(a!) buf, Tensor expert_rows, Tensor expert_tot, int EL) -> ()", &pfb::ep_zero_padding);
   m.def("ep_push_rows(Tensor x, Tensor idx, Tensor rank_in_expert, Tensor? scale, Tensor peer_tab_ptrs, Tensor(a!) pair_slot, "
         "Tensor peer_buf_ptrs, int k, int EL, int ep, int capacity_rows, int rank, int flag_slot, Tensor epoch, Tensor(b!) done_counter, "
         "bool slots_from_table) -> ()",

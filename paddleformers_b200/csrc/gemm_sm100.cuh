@@ -99,8 +99,8 @@ __device__ __forceinline__ void gemm_store_tile(uint32_t taddr, int row, int nb,
         for (int j = 0; j < 16; ++j) {
           float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
           float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
-          float a0 = g0 / (1.f + __expf(-g0)) * u0;
-          float a1 = g1 / (1.f + __expf(-g1)) * u1;
+          float a0 = __fdividef(g0, 1.f + __expf(-g0)) * u0;     // fast division: the epilogue warps are latency-bound
+          float a1 = __fdividef(g1, 1.f + __expf(-g1)) * u1;
           o[j] = pack_bf16x2(a0, a1);
         }
         __nv_bfloat16* dst = Dp + static_cast<long long>(row) * p.ldd + col;

@@ -169,7 +169,8 @@ def make_plan(ws: EPWorkspace, idx: torch.Tensor, routed: dict = None) -> dict:
     return {"idx": flat, "counts": counts.to(torch.int32), "rank_in_expert": rank_in_expert.to(torch.int32),
             "pair_slot": torch.empty(flat.numel(), dtype=torch.int32, device=dev),
             "block_expert": torch.empty(ws.cap // 128, dtype=torch.int32, device=dev),
-            "expert_rows": torch.empty((ws.EL, 2), dtype=torch.int32, device=dev)}
+            "expert_rows": torch.empty((ws.EL, 2), dtype=torch.int32, device=dev),
+            "expert_tot": torch.empty(ws.EL, dtype=torch.int32, device=dev)}
 
 
 class _Dispatch(torch.autograd.Function):
@@ -188,7 +189,6 @@ class _Dispatch(torch.autograd.Function):
         # g: gradient of the receive buffer rows, produced by the expert backward which has consumed ws.dy by now
         if g.data_ptr() != ws.dxr.tensor.data_ptr():     # the expert backward normally writes straight into the buffer
             ws.dxr.tensor.copy_(g)
-        ws.dy.tensor.zero_()        # padding rows of the next exchange must read as zero in the weight-gradient GEMMs
         ws.signal(FLAG_DX, ws.bwd_epoch)
         ws.wait(FLAG_DX, ws.bwd_epoch)
         dx = torch.empty(ctx.shape, dtype=torch.bfloat16, device=g.device)
@@ -217,6 +217,9 @@ class _Combine(torch.autograd.Function):
         (wf,) = ctx.saved_tensors
         dout = dout.contiguous()
         ws.bwd_epoch.add_(1)
+        # the gradient buffer is shared by all layers: this layer's padding rows hold older rows and must read as zero in
+        # the weight-gradient GEMMs; only they are cleared (peers write the received rows only, so this may overlap their pushes)
+        torch.ops.pfb200.ep_zero_padding(ws.dy.tensor, plan["expert_rows"], plan["expert_tot"], ws.EL)
         ws.push(dout, plan, wf, ws.dy, FLAG_DY, ws.bwd_epoch, False)   # reuses the slots recorded in the forward pass
         dots = torch.empty(wf.numel(), dtype=torch.float32, device=dout.device)
         if ws.local_dots:
@@ -246,7 +249,7 @@ def moe_forward(ws: EPWorkspace, layer, x2d, idx, w):
     plan = make_plan(ws, idx, getattr(layer.gate, "last_plan", None))
     ws.fwd_epoch.add_(1)
     torch.ops.pfb200.ep_exchange(ws.table.peer_ptrs, plan["counts"], plan["block_expert"], plan["expert_rows"], ws.total_rows,
-                                 ws.rank, ws.ep, ws.EL, ws.fwd_epoch)
+                                 ws.rank, ws.ep, ws.EL, ws.fwd_epoch, plan["expert_tot"])
     x_recv = _Dispatch.apply(x2d, ws, bufs, plan)
     y_rows = layer.experts(x_recv, plan["block_expert"], None, out=bufs["y"].tensor.detach(), expert_rows=plan["expert_rows"],
                           grad_rows_out=ws.dxr.tensor)
