@@ -284,3 +284,27 @@ def test_image_processor_raster_order_matches_plain_patch_cutting():
     assert torch.equal(again, raster["pixel_values"])
     reordered = blocks["pixel_values"].view(gh // 2, gw // 2, 2, 2, -1).permute(0, 2, 1, 3, 4).reshape(gh * gw, -1)
     assert torch.equal(reordered, raster["pixel_values"])
+
+
+def test_model_files_resolve_from_the_cache_of_the_selected_hub(tmp_path, monkeypatch):
+    """DOWNLOAD_SOURCE picks whose cache is searched first; flat <org>/<name> layouts (ModelScope, AI Studio) and the
+    Hugging Face snapshot layout both resolve; nothing is downloaded."""
+    from paddleformers_b200.utils.download import resolve_dir, resolve_file_path
+
+    ms = tmp_path / "ms"
+    (ms / "hub" / "org" / "tiny").mkdir(parents=True)
+    (ms / "hub" / "org" / "tiny" / "config.json").write_text("{\"from\": \"modelscope\"}")
+    hf = tmp_path / "hf"
+    snap = hf / "hub" / "models--org--tiny" / "snapshots" / "abc"
+    snap.mkdir(parents=True)
+    (snap / "config.json").write_text("{\"from\": \"huggingface\"}")
+    monkeypatch.setenv("MODELSCOPE_CACHE", str(ms))
+    monkeypatch.setenv("HF_HOME", str(hf))
+    monkeypatch.setenv("HF_HUB_OFFLINE", "1")
+    monkeypatch.setenv("DOWNLOAD_SOURCE", "modelscope")
+    assert "modelscope" in open(resolve_file_path("org/tiny", "config.json")).read()
+    monkeypatch.setenv("DOWNLOAD_SOURCE", "huggingface")
+    assert "huggingface" in open(resolve_file_path("org/tiny", "config.json")).read()
+    assert resolve_dir("org/tiny") == str(snap)
+    with pytest.raises(FileNotFoundError):
+        resolve_file_path("org/absent", "config.json")
