@@ -1,6 +1,6 @@
 """Small fixed workloads of each hot kernel for profiler captures:
 
-    python -m paddleformers_b200.ops.profile_cases --case gemm|attn_fwd|attn_bwd|gemm_swiglu|gemm_wgrad|moe_layer|moe_layer_local
+    python -m paddleformers_b200.ops.profile_cases --case gemm|attn_fwd|attn_bwd|gemm_swiglu|gemm_wgrad|gemm_mxf8|moe_layer|moe_layer_local
 
 Each case launches its kernel a few times on inputs larger than the L2 cache but well under a few GB, so that an
 ``ncu --set full --clock-control none -k regex:<kernel> -s 1 -c 1`` capture finishes in about a minute (always pass
@@ -36,6 +36,20 @@ def case_gemm(kind: str):
         out = torch.zeros(N, K, device="cuda", dtype=torch.float32)
         for _ in range(3):
             F.gemm(dy, x, out=out, a_mn=True, b_mn=True, epi=F.EPI_ACCUM_F32)
+
+
+def case_gemm_mxf8():
+    """Block-scaled e4m3 product with the scales applied by the tensor core (kernel gemm_mxf8_kernel)."""
+    from ..quantization import fp8 as Q
+
+    M, N, K = 4096, 8192, 4096
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    xq, xs_t = Q.quant_act_kernel(x)
+    wq, ws = Q.quant_weight_kernel(w)
+    for _ in range(3):
+        Q.fp8_gemm(xq, xs_t, wq, ws, out=out)
 
 
 def case_attn(kind: str):
@@ -84,11 +98,13 @@ def case_moe_layer(kind: str):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["gemm", "gemm_swiglu", "gemm_wgrad", "attn_fwd", "attn_bwd", "moe_layer",
-                                                      "moe_layer_local"])
+    ap.add_argument("--case", required=True, choices=["gemm", "gemm_swiglu", "gemm_wgrad", "gemm_mxf8", "attn_fwd", "attn_bwd",
+                                                      "moe_layer", "moe_layer_local"])
     args = ap.parse_args()
     if args.case.startswith("moe"):
         case_moe_layer(args.case)
+    elif args.case == "gemm_mxf8":
+        case_gemm_mxf8()
     elif args.case.startswith("gemm"):
         case_gemm(args.case)
     else:
