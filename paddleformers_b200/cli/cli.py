@@ -43,8 +43,8 @@ def build_launch_command(argv: List[str], nproc: int) -> List[str]:
     master_port = os.environ.get("MASTER_PORT", "29533")
     cmd = [sys.executable, "-m", "torch.distributed.run", f"--nnodes={nnodes}", f"--node-rank={node_rank}",
            f"--nproc-per-node={nproc}", f"--master-addr={master_addr}", f"--master-port={master_port}"]
-    if os.environ.get("BIND_TRAINER_NUMA") == "1" and shutil.which("numactl"):
-        cmd = ["numactl", "--interleave=all"] + cmd
+    # BIND_TRAINER_NUMA=1: every trainer process pins itself to the NUMA node of its GPU (utils/numa.py); the launcher
+    # itself needs no wrapper
     return cmd + ["-m", "paddleformers_b200.cli.train"] + argv
 
 

@@ -163,6 +163,9 @@ def run_dpo(model_args, data_args, gen_args, train_args):
 
 
 def run_tuner(argv: Optional[list] = None):
+    from ..utils.numa import maybe_bind_trainer
+
+    maybe_bind_trainer()       # BIND_TRAINER_NUMA=1: CPUs and memory of the NUMA node next to this rank's GPU
     model_args, data_args, gen_args, export_args, train_args = get_train_args(argv)
     stage = model_args.stage.upper()
     if stage == "VL-SFT":

@@ -428,3 +428,32 @@ def test_reference_only_configuration_keys_are_translated_accepted_or_refused():
         parse_dict(dict(base, to_static=True))
     with pytest.raises(ValueError, match="unknown configuration keys"):
         parse_dict(dict(base, definitely_not_a_flag=1))
+
+
+def test_numa_binding_reads_the_gpu_node_from_sysfs(tmp_path, monkeypatch):
+    """BIND_TRAINER_NUMA: PCI address -> numa_node -> cpulist -> sched_setaffinity, against a fake sysfs tree."""
+    import os
+
+    from paddleformers_b200.utils import numa
+
+    assert numa.parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    pci, node = tmp_path / "pci", tmp_path / "node"
+    (pci / "0000:1b:00.0").mkdir(parents=True)
+    (pci / "0000:1b:00.0" / "numa_node").write_text("1\n")
+    (pci / "0000:9a:00.0").mkdir(parents=True)
+    (pci / "0000:9a:00.0" / "numa_node").write_text("-1\n")
+    allowed = sorted(os.sched_getaffinity(0))
+    (node / "node1").mkdir(parents=True)
+    (node / "node1" / "cpulist").write_text(f"{allowed[0]}-{allowed[0]},4000-4003\n")
+    assert numa.numa_node_of_pci("0000:1b:00.0", str(pci)) == 1 and numa.numa_node_of_pci("0000:9a:00.0", str(pci)) is None
+    assert numa.cpus_of_node(1, str(node))[0] == allowed[0]
+    monkeypatch.setattr(numa, "gpu_pci_address", lambda i: "0000:1b:00.0" if i == 0 else ("0000:9a:00.0" if i == 1 else None))
+    try:
+        res = numa.bind_to_gpu_node(0, str(pci), str(node), set_memory=False)
+        assert res["node"] == 1 and res["cpus"] == 1 and sorted(os.sched_getaffinity(0)) == [allowed[0]]
+    finally:
+        os.sched_setaffinity(0, allowed)
+    assert numa.bind_to_gpu_node(1, str(pci), str(node))["node"] is None          # the platform hides the node: no-op
+    assert numa.bind_to_gpu_node(2, str(pci), str(node))["reason"].startswith("no PCI")
+    monkeypatch.delenv("BIND_TRAINER_NUMA", raising=False)
+    assert numa.maybe_bind_trainer() is None
