@@ -57,6 +57,25 @@ class SymmetricArena:
         return ch, 0
 
 
+CANARY_BYTES = 1024
+CANARY_WORD = 0x5AA55AA5
+_CANARIES: List[torch.Tensor] = []       # int32 views of the guard words behind every region (PFB_DEBUG_CANARY=1)
+
+
+def canaries_enabled() -> bool:
+    return os.environ.get("PFB_DEBUG_CANARY", "0") == "1"
+
+
+def check_canaries() -> int:
+    """Debug aid for the peer-memory kernels (PFB_DEBUG_CANARY=1): every region of a symmetric arena is followed by 1 KB of
+    guard words that no kernel, local or remote, may touch. Returns the number of regions whose guard was overwritten
+    (one device synchronisation); 0 when the mode is off."""
+    if not _CANARIES:
+        return 0
+    bad = torch.stack([(c != CANARY_WORD).any() for c in _CANARIES]).sum()
+    return int(bad)
+
+
 class _Region:
     """A tensor inside the arena plus the table of its addresses on every peer."""
 
@@ -65,7 +84,13 @@ class _Region:
         for s in shape:
             n *= s
         nbytes = n * torch.empty((), dtype=dtype).element_size()
-        buf, off = arena.alloc(nbytes)
+        guard = canaries_enabled()
+        payload = (nbytes + 1023) // 1024 * 1024
+        buf, off = arena.alloc(payload + CANARY_BYTES if guard else nbytes)
+        if guard:
+            c = buf.tensor((CANARY_BYTES // 4,), torch.int32, off + payload)
+            c.fill_(CANARY_WORD)
+            _CANARIES.append(c)
         self.tensor = buf.tensor(shape, dtype, off)
         self.peer_ptrs = torch.tensor([p + off for p in buf.peer_ptrs], dtype=torch.int64)
         self.local_ptr = buf.local_ptr + off
@@ -135,6 +160,7 @@ def release_workspaces() -> None:
         ws.arena.used.clear()
     _WS.clear()
     fused_ep._WS.clear()
+    _CANARIES.clear()
 
 
 # ---------------------------------------------------------------------------------------------------------------

@@ -455,6 +455,12 @@ class Trainer:
                 from ..parallel.fused_ep import dropped_pairs
 
                 self._ep_dropped = dropped_pairs() if getattr(self.ps.degrees, "ep", 1) > 1 else 0
+                # PFB_DEBUG_CANARY=1: guard words behind every peer-visible buffer must be intact
+                from ..parallel.fused_collectives import check_canaries
+
+                n_bad = check_canaries()
+                if n_bad:
+                    raise RuntimeError(f"{n_bad} peer-memory regions were written past their end (PFB_DEBUG_CANARY guard words)")
             if not math.isfinite(loss_v):
                 raise FloatingPointError(f"LOSS_{'NAN' if math.isnan(loss_v) else 'INF'}_ERROR: loss is {loss_v} at "
                                          f"step {self.state.global_step}")

@@ -96,3 +96,24 @@ def test_fused_ep_single_rank(tmp_path):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fused_ep_matches_alltoall_two_ranks(tmp_path):
     _run(tmp_path, 2, 29552)
+
+
+def test_guard_words_behind_peer_memory_regions_catch_an_overrun(monkeypatch):
+    """PFB_DEBUG_CANARY=1 places 1 KB of guard words behind every region of a symmetric arena; a write past a region's end
+    (here made through a wider view of the same allocation, so nothing leaves the buffer) is reported."""
+    from paddleformers_b200.parallel import fused_collectives as fc
+
+    monkeypatch.setenv("PFB_DEBUG_CANARY", "1")
+    arena = fc.SymmetricArena(None)
+    a = fc._Region(arena, (300,), torch.float32)          # 1200 bytes -> payload rounded to 2048, guard behind it
+    b = fc._Region(arena, (64, 8), torch.bfloat16)
+    a.tensor.fill_(1.0)
+    b.tensor.fill_(2.0)
+    assert fc.check_canaries() == 0
+    buf = arena.chunks[0]
+    wide = buf.tensor((2048 // 4 + 4,), torch.float32, a.local_ptr - buf.local_ptr)
+    wide[2048 // 4 + 1] = 7.0                              # one word into a's guard
+    assert fc.check_canaries() == 1
+    fc._CANARIES.clear()
+    for ch in arena.chunks:
+        ch.close()
