@@ -424,3 +424,33 @@ def test_global_aux_loss_uses_the_statistics_of_all_data_ranks():
         assert abs(a - float(aux)) < 1e-6                              # every rank reports the loss of the whole batch
     # each rank differentiates through its own probabilities only: the ranks' gradients add up to the whole-batch gradient
     torch.testing.assert_close(res[0][1] + res[1][1], gate.weight.grad, rtol=1e-4, atol=1e-7)
+
+
+@pytest.mark.parametrize("name,P,M,V", [("1F1B", 4, 8, 1), ("interleaved", 2, 8, 2), ("zero_bubble", 4, 8, 1), ("FThenB", 2, 6, 1),
+                                        ("zbv", 2, 8, 2)])
+def test_expert_exchange_buffer_slots_follow_the_pipeline_schedule(name, P, M, V):
+    """Every micro-batch holds one buffer slot from its first forward to its last backward chunk on a stage; slots are
+    reused, so their number is the schedule's maximum of micro-batches in flight (P - stage for 1F1B, all of them for FThenB)."""
+    from paddleformers_b200.parallel.fused_ep import SlotAllocator
+    from paddleformers_b200.parallel.pipeline import make_schedule
+
+    for stage in range(P):
+        alloc = SlotAllocator(V)
+        live, peak = set(), 0
+        for a in make_schedule(name, stage, P, M, V):
+            if a.kind == "W":
+                continue
+            slot = alloc.acquire(a.mb)
+            # no two micro-batches in flight share a slot
+            assert all(alloc.slot_of[m] != slot for m in live if m != a.mb)
+            live.add(a.mb)
+            peak = max(peak, len(live))
+            if a.kind == "B":
+                alloc.backward_done(a.mb)
+                if a.mb not in alloc.slot_of:
+                    live.discard(a.mb)
+        assert not alloc.slot_of and alloc.high_water == peak
+        if name == "1F1B":
+            assert alloc.high_water == P - stage
+        if name == "FThenB":
+            assert alloc.high_water == M
