@@ -196,7 +196,7 @@ class Trainer:
         if self.lr_scheduler is None:
             min_ratio = a.min_lr / a.learning_rate if a.learning_rate > 0 else 0.0
             fn = get_scheduler_lambda(a.lr_scheduler_type, a.get_warmup_steps(num_training_steps), num_training_steps,
-                                      min_lr_ratio=min_ratio, decay_steps=a.decay_steps)
+                                      min_lr_ratio=min_ratio, num_cycles=a.num_cycles, power=a.power, decay_steps=a.decay_steps)
             self.lr_scheduler = LRScheduler(a.learning_rate, fn)
         self.callback_handler.optimizer, self.callback_handler.lr_scheduler = self.optimizer, self.lr_scheduler
         self.zcc = None
@@ -415,6 +415,13 @@ class Trainer:
         metrics = speed_metrics("train", train_start, num_samples=(self.state.global_step - start_step) * a.global_batch_size,
                                 num_steps=self.state.global_step - start_step, seq_length=a.max_seq_len,
                                 model_flops_per_token=flops_per_token, world_size=a.world_size)
+        if a.load_best_model_at_end and self.state.best_model_checkpoint and \
+                os.path.isdir(self.state.best_model_checkpoint):
+            ckpt.wait_for_pending_saves()
+            logger.info(f"loading the best checkpoint {self.state.best_model_checkpoint} (metric {self.state.best_metric})")
+            keep = (self.state.global_step, self.state.best_metric, self.state.best_model_checkpoint, self.state.log_history)
+            self._load_from_checkpoint(self.state.best_model_checkpoint)
+            self.state.global_step, self.state.best_metric, self.state.best_model_checkpoint, self.state.log_history = keep
         self.control = self.callback_handler.on_train_end(a, self.state, self.control)
         self.log(metrics)
         return metrics
@@ -495,11 +502,30 @@ class Trainer:
             self._last_log_time, self._last_log_step = now, self.state.global_step
             self.log(logs)
         if self.control.should_evaluate and self.eval_dataset is not None:
-            self.evaluate()
+            self._last_eval = (self.state.global_step, self.evaluate())
         if self.control.should_save:
+            last = getattr(self, "_last_eval", None)      # evaluation and save of one step may come in separate calls
+            self._track_best_checkpoint(last[1] if last and last[0] == self.state.global_step else None)   # before the state is written
             self._save_checkpoint()
             self.control = self.callback_handler.on_save(a, self.state, self.control)
         self.control._new_step()
+
+    def _track_best_checkpoint(self, metrics: Optional[Dict[str, float]]):
+        """Remember the checkpoint written at the step with the best evaluation metric (``metric_for_best_model``,
+        ``greater_is_better``; paddleformers/trainer/trainer.py best-model bookkeeping of the save path)."""
+        a = self.args
+        if not metrics or not (a.load_best_model_at_end or a.metric_for_best_model):
+            return
+        name = a.metric_for_best_model or "loss"
+        key = name if name.startswith("eval_") else f"eval_{name}"
+        if key not in metrics:
+            return
+        greater = a.greater_is_better if a.greater_is_better is not None else not key.endswith("loss")
+        value = float(metrics[key])
+        best = self.state.best_metric
+        if best is None or (value > best if greater else value < best):
+            self.state.best_metric = value
+            self.state.best_model_checkpoint = os.path.join(a.output_dir, f"{PREFIX_CHECKPOINT_DIR}-{self.state.global_step}")
 
     def log(self, logs: Dict[str, float]):
         for cb in self.callback_handler.callbacks:        # callbacks that add fields (timers, memory) run before the sinks
@@ -522,6 +548,8 @@ class Trainer:
         start = time.time()
         n_batches = 0
         for inputs in loader:
+            if 0 < self.args.max_evaluate_steps <= n_batches:
+                break
             inputs = self._prepare_inputs(inputs)
             out = model(**inputs)
             n = out.num_tokens.double() if out.num_tokens is not None else torch.ones_like(cnt)

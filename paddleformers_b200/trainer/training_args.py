@@ -49,6 +49,9 @@ class TrainingArguments:
     warmup_steps: int = 0
     warmup_ratio: float = 0.0
     decay_steps: Optional[int] = None
+    num_cycles: float = 0.5            # cosine: number of waves (0.5 = decay to the minimum once)
+    power: float = 1.0                 # polynomial: exponent of the decay
+    lr_end: Optional[float] = None     # polynomial: final learning rate (same role as min_lr; used when min_lr is 0)
     optim: str = field(default="adamw", metadata={"help": "adamw | adamw_mini (one second moment per row) | adamw_custom | muon"})
     use_lowprecision_moment: bool = False        # adamw_custom: Adam moments stored in bf16
     tensorwise_offload_optimizer: bool = False   # adamw_custom: Adam moments live in host memory, streamed through the device
@@ -85,6 +88,10 @@ class TrainingArguments:
     save_hf_steps: int = -1
     eval_strategy: str = "no"
     eval_steps: Optional[int] = None
+    max_evaluate_steps: int = -1       # > 0: evaluate on at most that many batches
+    load_best_model_at_end: bool = False        # reload the checkpoint with the best evaluation metric when training ends
+    metric_for_best_model: Optional[str] = None   # default "loss" (looked up as eval_<name>)
+    greater_is_better: Optional[bool] = None      # default: False for losses, True otherwise
     report_to: str = "none"            # none | comma-separated: tensorboard, visualdl, jsonl
     logging_dir: Optional[str] = None  # scalar logs (default <output_dir>/runs)
     enable_zero_cost_checkpoint: bool = False   # snapshot the optimizer shard on a side stream, persist in the background
@@ -135,6 +142,12 @@ class TrainingArguments:
 
     def __post_init__(self):
         self.lr_scheduler_type = SchedulerType(self.lr_scheduler_type).value
+        if self.lr_end is not None and not self.min_lr:
+            self.min_lr = float(self.lr_end)
+        # the reference's names for the same two layouts: per-rank shards / layout-independent state
+        fmt_alias = {"sharding_io": "sharded", "flex_checkpoint": "unified", "unified_checkpoint": "unified"}
+        self.save_checkpoint_format = fmt_alias.get(self.save_checkpoint_format, self.save_checkpoint_format)
+        self.load_checkpoint_format = fmt_alias.get(self.load_checkpoint_format, self.load_checkpoint_format)
         self.save_strategy = IntervalStrategy(self.save_strategy).value
         self.eval_strategy = IntervalStrategy(self.eval_strategy).value
         if self.bf16 and self.fp16:

@@ -243,3 +243,27 @@ def test_module_ranges_nest_and_balance_in_forward_and_backward():
     n = len(events)
     model(input_ids=ids)                      # hooks removed on exit
     assert len(events) == n
+
+
+def test_best_checkpoint_is_tracked_and_reloaded_at_the_end(tmp_path):
+    """load_best_model_at_end: the checkpoint of the step with the lowest evaluation loss is remembered and its weights are
+    back in the model when train() returns; max_evaluate_steps bounds the evaluation; the scheduler takes power / lr_end."""
+    torch.manual_seed(0)
+    cfg = named_config("tiny-llama")
+    model = AutoModelForCausalLM.from_config(cfg)
+    train = _Fixed(SyntheticCausalLMDataset(32000, 128, 8, seed=0), 64)
+    evals = _Fixed(SyntheticCausalLMDataset(32000, 128, 8, seed=0), 8)
+    args = TrainingArguments(output_dir=str(tmp_path), per_device_train_batch_size=2, max_steps=6, learning_rate=3e-4, logging_steps=1,
+                             save_steps=2, eval_strategy="steps", eval_steps=2, max_evaluate_steps=2, max_seq_len=128,
+                             lr_scheduler_type="polynomial", power=2.0, lr_end=1e-5, load_best_model_at_end=True)
+    assert args.min_lr == 1e-5
+    tr = Trainer(model=model, args=args, train_dataset=train, eval_dataset=evals)
+    tr.train()
+    evs = [h for h in tr.state.log_history if "eval_loss" in h]
+    assert len(evs) == 3 and all(h["eval_steps_per_second"] > 0 for h in evs)
+    best = min(range(3), key=lambda i: evs[i]["eval_loss"])
+    assert tr.state.best_metric == evs[best]["eval_loss"]
+    assert tr.state.best_model_checkpoint.endswith(f"checkpoint-{2 * (best + 1)}")
+    ref = AutoModelForCausalLM.from_pretrained(tr.state.best_model_checkpoint)
+    for (n1, p1), (n2, p2) in zip(model.state_dict().items(), ref.state_dict().items()):
+        assert torch.equal(p1, p2), n1
