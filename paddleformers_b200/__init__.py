@@ -38,6 +38,7 @@ _LAZY = {
     "AutoModel": ".transformers.auto", "SiglipVisionModel": ".models.siglip", "SiglipVisionConfig": ".models.siglip",
     "Qwen3VLForConditionalGeneration": ".models.vision_language", "Qwen3VLMoeForConditionalGeneration": ".models.vision_language",
     "Glm4vMoeForConditionalGeneration": ".models.vision_language", "FullyShardedOptimizer": ".parallel.fsdp",
+    "Gemma4ForCausalLM": ".models.gemma4", "Gemma4TextConfig": ".models.gemma4",
 }
 
 

@@ -1018,8 +1018,6 @@ CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Q
 # feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
 UNSUPPORTED_FAMILIES = {
     "deepseek_v4": "compressed sparse attention",
-    "gemma4_text": "per-layer-type head geometry (global layers with their own head size and shared key / value projection)",
-    "gemma4": "per-layer-type head geometry (global layers with their own head size and shared key / value projection)",
     "kimi_k3": "delta-rule linear attention with per-channel decay, vision tower", "kimi_linear": "delta-rule linear attention with per-channel decay",
     "kimi_k25": "vision tower", "hyperencoder": "encoder stack of its own",
     "phi4_multimodal": "vision and audio towers", "molmo": "vision tower with pooled multi-crop features",
@@ -1028,9 +1026,25 @@ UNSUPPORTED_FAMILIES = {
 }
 
 
+# causal-LM families that are models of their own (not the unified decoder): model_type -> (module, config class, model class)
+STANDALONE_FAMILIES = {
+    "gemma4_text": ("gemma4", "Gemma4TextConfig", "Gemma4ForCausalLM"),
+    "gemma4": ("gemma4", "Gemma4TextConfig", "Gemma4ForCausalLM"),          # the multimodal wrapper's text decoder
+}
+
+
+def _standalone(model_type: str, which: int):
+    import importlib
+
+    mod, *names = STANDALONE_FAMILIES[model_type]
+    return getattr(importlib.import_module(f"{__package__}.{mod}"), names[which])
+
+
 def resolve_config_class(model_type: str):
     if model_type in CONFIG_MAPPING:
         return CONFIG_MAPPING[model_type]
+    if model_type in STANDALONE_FAMILIES:
+        return _standalone(model_type, 0)
     if model_type in UNSUPPORTED_FAMILIES:
         raise NotImplementedError(f"model_type {model_type!r} is known but not implemented: it needs {UNSUPPORTED_FAMILIES[model_type]}")
     raise ValueError(f"unknown model_type {model_type!r}; supported: {sorted(CONFIG_MAPPING)}")

@@ -1128,7 +1128,24 @@ Qwen3NextForCausalLM = _family("Qwen3NextForCausalLM", Qwen3NextConfig)
 Qwen3_5ForCausalLM = _family("Qwen3_5ForCausalLM", Qwen3_5TextConfig)
 Qwen3_5MoeForCausalLM = _family("Qwen3_5MoeForCausalLM", Qwen3_5MoeTextConfig)
 
-MODEL_MAPPING = {
+class _ModelMapping(dict):
+    """model_type -> causal-LM class; families that are models of their own are imported on first use."""
+
+    def __missing__(self, key):
+        from .configuration import STANDALONE_FAMILIES, _standalone
+
+        if key not in STANDALONE_FAMILIES:
+            raise KeyError(key)
+        self[key] = _standalone(key, 1)
+        return self[key]
+
+    def __contains__(self, key):
+        from .configuration import STANDALONE_FAMILIES
+
+        return dict.__contains__(self, key) or key in STANDALONE_FAMILIES
+
+
+MODEL_MAPPING = _ModelMapping({
     "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
     "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "minicpm4_1": MiniCPM4_1ForCausalLM, "glm4": Glm4ForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma2": Gemma2ForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
     "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "minimax": MiniMaxForCausalLM, "diffllama": DiffLlamaForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "gpt_oss": GptOssForCausalLM, "llama4_text": Llama4ForCausalLM, "qwen3_next": Qwen3NextForCausalLM, "qwen3_5_text": Qwen3_5ForCausalLM, "qwen3_5_moe_text": Qwen3_5MoeForCausalLM,
@@ -1136,4 +1153,4 @@ MODEL_MAPPING = {
     "glm_moe_dsa": DeepseekV3ForCausalLM, "deepseek_v32": DeepseekV3ForCausalLM, "kimi_k2": DeepseekV3ForCausalLM, "ernie4_5": Ernie4_5ForCausalLM, "ernie4_5_moe": Ernie4_5MoeForCausalLM, "seed_oss": SeedOssForCausalLM, "internlm3": InternLM3ForCausalLM, "glm4_moe_lite": DeepseekV3ForCausalLM, "qwen2": Qwen2ForCausalLM, "qwen3": Qwen3ForCausalLM,
     "qwen3_moe": Qwen3MoeForCausalLM, "deepseek_v3": DeepseekV3ForCausalLM, "deepseek_v2": DeepseekV3ForCausalLM,
     "glm4_moe": Glm4MoeForCausalLM, "decoder": DecoderForCausalLM,
-}
+})

@@ -1009,3 +1009,90 @@ def test_classification_heads_match_hugging_face(tmp_path):
     with torch.no_grad():                            # the decoder really came from the causal-LM checkpoint
         hidden = lm.model(input_ids=ids).last_hidden_state
     assert (reward.hidden(ids) - hidden).abs().max() < 1e-4
+
+
+_G4_LAYERS = ["sliding_attention", "full_attention", "sliding_attention", "sliding_attention", "full_attention", "full_attention"]
+
+
+@pytest.mark.parametrize("variant", [
+    dict(),                                                                                 # dense with per-layer inputs
+    dict(num_kv_shared_layers=3, use_double_wide_mlp=True, layer_types=_G4_LAYERS),          # later layers reuse keys / values
+    dict(attention_k_eq_v=True, num_global_key_value_heads=1, hidden_size_per_layer_input=0),
+    dict(enable_moe_block=True, num_experts=8, top_k_experts=2, moe_intermediate_size=32, attention_k_eq_v=True,
+         num_global_key_value_heads=1, hidden_size_per_layer_input=0),                       # the 26B-A4B layout
+], ids=["dense_ple", "kv_shared_wide_mlp", "k_eq_v", "moe"])
+def test_gemma4_text_matches_hugging_face(tmp_path, variant):
+    """Per-layer-type head geometry, proportional rotary on the global layers, weightless value norm, unit score scale, the
+    dense + routed feed-forward sum with its five norms, per-layer inputs, shared keys / values, layer scalars, capped logits:
+    logits, loss and gradients against the ``transformers`` implementation; packed documents; greedy decoding; round trip."""
+    from transformers import Gemma4ForCausalLM as HFModel
+    from transformers.models.gemma4.configuration_gemma4 import Gemma4TextConfig as HFConfig
+
+    from paddleformers_b200.generation.utils import GenerationConfig
+
+    torch.manual_seed(0)
+    kw = dict(vocab_size=160, hidden_size=64, intermediate_size=96, num_hidden_layers=6, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=16, global_head_dim=32, sliding_window=8, vocab_size_per_layer_input=160, hidden_size_per_layer_input=8,
+              max_position_embeddings=128, final_logit_softcapping=30.0)
+    kw.update(variant)
+    cfg = HFConfig(**kw)
+    cfg._attn_implementation = "eager"
+    hf = HFModel(cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n or "scale" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+        for n, b in hf.named_buffers():
+            if n.endswith("layer_scalar"):
+                b.copy_(torch.rand(1) + 0.5)
+    hf.save_pretrained(tmp_path / "hf")
+    mine = AutoModelForCausalLM.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).eval()
+    assert type(mine).__name__ == "Gemma4ForCausalLM"
+    ids = torch.randint(3, 160, (2, 24))
+    with torch.no_grad():
+        want = hf(input_ids=ids).logits
+        got = mine(ids).logits
+    assert (want - got).abs().max() < 2e-4
+    # loss and gradients (labels here are already next-token targets)
+    labels = torch.cat([ids[:, 1:], torch.full((2, 1), -100)], dim=1)
+    mine.train()
+    mine(ids, labels=labels).loss.backward()
+    hf_loss = hf(input_ids=ids, labels=ids).loss
+    hf_loss.backward()
+    assert abs(mine(ids, labels=labels).loss.item() - hf_loss.item()) < 1e-4
+    ga, gb = mine.model.layers[1].self_attn.q_proj.weight.grad, hf.model.layers[1].self_attn.q_proj.weight.grad
+    assert (ga - gb).abs().max() < 1e-4 * max(1.0, gb.abs().max().item())
+    if variant.get("enable_moe_block"):
+        ga, gb = mine.model.layers[0].moe.experts.gate_up_proj.grad, hf.model.layers[0].experts.gate_up_proj.grad
+        assert (ga - gb).abs().max() < 1e-4 * max(1.0, gb.abs().max().item()) and ga.abs().sum() > 0
+        assert mine.model.layers[0].moe.router.per_expert_scale.grad.abs().sum() > 0
+    mine.eval()
+    # two packed documents: the second one's logits equal those of the document alone (positions restart)
+    kend = torch.full((2, 24), 24, dtype=torch.int32)
+    kend[:, :10] = 10
+    pos = torch.cat([torch.arange(10), torch.arange(14)])[None].expand(2, -1)
+    with torch.no_grad():
+        packed = mine(ids, position_ids=pos, kend=kend).logits
+        alone = mine(ids[:, 10:]).logits
+    assert (packed[:, 10:] - alone).abs().max() < 2e-4
+    # greedy decoding agrees with the argmax of a full forward
+    out = mine.generate(ids[:, :9], GenerationConfig(max_new_tokens=4, eos_token_id=-1))
+    with torch.no_grad():
+        step = hf(input_ids=out[:, :-1]).logits.argmax(-1)
+    assert out.shape == (2, 13) and torch.equal(step[:, 8:], out[:, 9:])
+    mine.save_pretrained(str(tmp_path / "mine"))
+    back = HFModel.from_pretrained(tmp_path / "mine").eval()
+    with torch.no_grad():
+        assert (back(input_ids=ids).logits - want).abs().max() < 1e-5
+
+
+def test_gemma4_reads_the_multimodal_wrapper_configuration_and_the_reference_field_names():
+    from paddleformers_b200.transformers.auto import AutoConfig
+
+    cfg = AutoConfig.for_model("gemma4", num_hidden_layers=12, interleaved_attn_pattern=(5, 1), full_attention_rope_base=5e5,
+                               hidden_act="gelu_pytorch_tanh", enable_moe_block=True, num_experts=8, top_k_experts=2)
+    assert cfg.model_type == "gemma4_text" and cfg.layer_types[5] == "full_attention" and cfg.layer_types[-1] == "full_attention"
+    assert cfg.rope_parameters["full_attention"] == {"rope_type": "proportional", "rope_theta": 5e5, "partial_rotary_factor": 0.25}
+    wrapped = type(cfg).from_dict({"model_type": "gemma4", "text_config": {"model_type": "gemma4_text", "num_hidden_layers": 3}})
+    assert wrapped.num_hidden_layers == 3 and wrapped.num_experts_per_tok is None
+    assert cfg.layer_head_geometry(0) == (256, 4, False) and cfg.layer_head_geometry(5)[0] == 512

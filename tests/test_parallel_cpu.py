@@ -10,6 +10,15 @@ from dist_utils import run_distributed
 def _tiny_cfg(moe=False, **kw):
     from paddleformers_b200.models.configuration import named_config
 
+    if moe == "gemma4":          # dense + routed feed-forward sum, two head geometries, per-layer inputs
+        from paddleformers_b200.transformers.auto import AutoConfig
+
+        base = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=2, head_dim=16, global_head_dim=32, sliding_window=8, vocab_size_per_layer_input=128,
+                    hidden_size_per_layer_input=8, enable_moe_block=True, num_experts=4, top_k_experts=2, moe_intermediate_size=32,
+                    attention_k_eq_v=True, num_global_key_value_heads=1)
+        base.update(kw)
+        return AutoConfig.for_model("gemma4_text", **base)
     if moe:
         base = dict(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
                     num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, vocab_size=128, router_aux_loss_coef=0.0)
@@ -89,6 +98,8 @@ def _reference(moe, steps, accum):
     ("dp2", 2, False, dict(gradient_accumulation_steps=1)),
     ("stage3_fsdp2", 2, False, dict(sharding="stage3", gradient_accumulation_steps=1)),
     ("ep2", 2, True, dict(expert_model_parallel_size=2, sharding="stage1", gradient_accumulation_steps=1, moe_token_dispatcher_type="alltoall")),
+    ("gemma4_ep2", 2, "gemma4", dict(expert_model_parallel_size=2, sharding="stage1", gradient_accumulation_steps=1,
+                                     moe_token_dispatcher_type="alltoall")),
     ("cp2", 2, False, dict(context_parallel_size=2, gradient_accumulation_steps=2)),
     ("cp2_contiguous", 2, False, dict(context_parallel_size=2, cp_balance_mode="contiguous_allgather", gradient_accumulation_steps=2)),
     ("cp2_ring", 2, False, dict(context_parallel_size=2, context_parallel_algo="ring", gradient_accumulation_steps=2)),
