@@ -267,6 +267,8 @@ def run_vl_sft(model_args, data_args, gen_args, train_args):
         for k in ("min_pixels", "max_pixels"):
             if getattr(data_args, k, None):
                 proc_kw[k] = getattr(data_args, k)
+        if model.config.model_type in ("ernie4_5_vl_moe", "ernie4_5_moe_vl"):      # single-frame patches; frames are paired later
+            proc_kw.update(temporal_patch_size=1)
         if model.config.model_type == "qwen3_vl":       # this generation normalises pixels to [-1, 1]
             proc_kw.update(image_mean=(0.5, 0.5, 0.5), image_std=(0.5, 0.5, 0.5))
         proc = Qwen2VLImageProcessor(**proc_kw)

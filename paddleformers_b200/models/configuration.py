@@ -1021,7 +1021,6 @@ UNSUPPORTED_FAMILIES = {
     "kimi_k3": "delta-rule linear attention with per-channel decay, vision tower", "kimi_linear": "delta-rule linear attention with per-channel decay",
     "kimi_k25": "vision tower", "hyperencoder": "encoder stack of its own",
     "phi4_multimodal": "vision and audio towers", "molmo": "vision tower with pooled multi-crop features",
-    "ernie4_5_vl": "vision tower, modality-aware experts", "ernie4_5_moe_vl": "vision tower, modality-aware experts",
     "qwen3_omni_moe": "audio / vision towers",
 }
 

@@ -467,7 +467,11 @@ class DecoderLayer(nn.Module):
             self.self_attn = self.linear_attn.forward
         else:
             self.self_attn = attn_cls(config, layer_idx, dtype=dtype, device=device)
-        if config.is_moe_layer(layer_idx):
+        if config.is_moe_layer(layer_idx) and getattr(config, "moe_modality_isolated", False):
+            from ..nn.moe import ModalityMoELayer
+
+            self.mlp = ModalityMoELayer(config, dtype=dtype, device=device)
+        elif config.is_moe_layer(layer_idx):
             self.mlp = MoELayer(config, dtype=dtype, device=device)
         else:
             self.mlp = DenseMLP(config.hidden_size, config.intermediate_size, config, bias=config.mlp_bias, dtype=dtype, device=device)
@@ -973,6 +977,23 @@ def build_weight_map(config: DecoderConfig) -> WeightMap:
             # the three expert projections (gate, up, down)
             src = f"model.layers.{i}." + (getattr(config, "moe_block_hf_name", None) or "mlp") + "."
             g_n, u_n, d_n = getattr(config, "expert_proj_hf_names", None) or ("gate_proj", "up_proj", "down_proj")
+            if getattr(config, "moe_modality_isolated", False):
+                # a text and a vision expert group: the checkpoint numbers the experts consecutively (text 0 .. E-1, vision
+                # E .. 2E-1), stores both routers transposed ([H, E]; the vision one as "weight_1") and both correction biases
+                # as the two rows of one tensor
+                tr = (lambda t: t.t().contiguous(), lambda t: t.t().contiguous())
+                for g, (part, wname) in enumerate((("text_moe.", "gate.weight"), ("vision_moe.", "gate.weight_1"))):
+                    rules.append(Rule(pre + part + "experts.gate_up_proj", [src + "experts.{E}." + g_n + ".weight", src + "experts.{E}." + u_n + ".weight"],
+                                      "stack_concat", 0, E, 2, expert_base=g * E))
+                    rules.append(Rule(pre + part + "experts.down_proj", [src + "experts.{E}." + d_n + ".weight"], "stack", 0, E, expert_base=g * E))
+                    rules.append(Rule(pre + part + "gate.weight", [src + wname], fn=tr))
+                    if config.topk_method == "noaux_tc":
+                        rules.append(Rule(pre + part + "gate.e_score_correction_bias", [src + "moe_statics.e_score_correction_bias"],
+                                          fn=(lambda t, g=g: t[g], lambda t: t[None])))
+                if config.n_shared_experts:
+                    rules.append(Rule(pre + "shared_experts.gate_up_proj.weight",
+                                      [src + "shared_experts.gate_proj.weight", src + "shared_experts.up_proj.weight"], "concat", 0))
+                continue
             if getattr(config, "hf_experts_style", None) == "llama4":
                 # stacked [E, H, 2I] ([in, out], gate columns then up columns) and [E, I, H]
                 tr = (lambda t: t.transpose(1, 2).contiguous(), lambda t: t.transpose(1, 2).contiguous())

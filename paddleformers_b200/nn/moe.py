@@ -693,3 +693,46 @@ class MoELayer(nn.Module):
         if aux is not None:
             y = AddAuxiliaryLoss.apply(y, aux)
         return y
+
+
+class ModalityMoELayer(nn.Module):
+    """Two isolated expert groups, one serving text tokens and one serving image / video tokens, each with its own router
+    and expert width, plus shared experts that see every token (ERNIE-4.5-VL;
+    paddleformers/transformers/ernie4_5_moe_vl/model/modeling_moe_vl.py). ``vision_rows`` (bool [tokens], set by the model
+    before the layers run; None = text only) says which rows go to the vision group."""
+
+    def __init__(self, config, dtype=None, device=None):
+        super().__init__()
+        import copy
+
+        text_cfg, vis_cfg = copy.copy(config), copy.copy(config)
+        text_cfg.n_shared_experts = vis_cfg.n_shared_experts = 0
+        vis_cfg.moe_intermediate_size = int(config.moe_vision_intermediate_size)
+        self.text_moe = MoELayer(text_cfg, dtype=dtype, device=device)
+        self.vision_moe = MoELayer(vis_cfg, dtype=dtype, device=device)
+        self.shared_experts = None
+        if config.n_shared_experts:
+            self.shared_experts = DenseMLP(config.hidden_size, config.moe_intermediate_size * config.n_shared_experts, config,
+                                           tp=False, dtype=dtype, device=device)
+        self.ep = get_parallel_state().degrees.ep
+        self.vision_rows: Optional[torch.Tensor] = None
+        self.last_aux_loss = None
+
+    def forward(self, x2d: torch.Tensor) -> torch.Tensor:
+        vis = self.vision_rows
+        if vis is None and self.ep == 1:
+            y = self.text_moe(x2d)
+        else:
+            if vis is None:
+                vis = torch.zeros(x2d.shape[0], dtype=torch.bool, device=x2d.device)
+            assert vis.numel() == x2d.shape[0], "one modality flag per token row"
+            y = torch.zeros_like(x2d)
+            for rows, moe in ((torch.nonzero(~vis)[:, 0], self.text_moe), (torch.nonzero(vis)[:, 0], self.vision_moe)):
+                # under expert parallelism both groups run on every rank (their exchanges are collective), also on no rows
+                if rows.numel() or self.ep > 1:
+                    y = y.index_add(0, rows, moe(x2d.index_select(0, rows)))
+        aux = [m.last_aux_loss for m in (self.text_moe, self.vision_moe) if m.last_aux_loss is not None]
+        self.last_aux_loss = torch.stack(aux).sum() if aux else None
+        if self.shared_experts is not None:
+            y = y + self.shared_experts(x2d)
+        return y

@@ -60,7 +60,11 @@ class AutoModelForConditionalGeneration:
 
         from ..models.paddleocr_vl import PaddleOCRVLConfig, PaddleOCRVLForConditionalGeneration
 
-        table = {"llama4": (Llama4Config, Llama4ForConditionalGeneration),
+        from ..models.ernie4_5_vl import Ernie4_5VLConfig, Ernie4_5VLForConditionalGeneration
+
+        table = {"ernie4_5_vl_moe": (Ernie4_5VLConfig, Ernie4_5VLForConditionalGeneration),
+                 "ernie4_5_moe_vl": (Ernie4_5VLConfig, Ernie4_5VLForConditionalGeneration),      # the reference's spelling
+                 "llama4": (Llama4Config, Llama4ForConditionalGeneration),
                  "paddleocr_vl": (PaddleOCRVLConfig, PaddleOCRVLForConditionalGeneration),
                  "paligemma": (PaliGemmaConfig, PaliGemmaForConditionalGeneration),
                  "paligemma2": (PaliGemma2Config, PaliGemmaForConditionalGeneration),

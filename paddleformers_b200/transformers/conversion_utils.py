@@ -128,6 +128,8 @@ class Rule:
     offset: float = 0.0                        # rename: internal = checkpoint + offset ((1 + w) norm weights)
     fn: Optional[Tuple[Callable, Callable]] = None      # rename: (checkpoint -> internal, internal -> checkpoint) for layouts
     #                                                     that no declarative field covers
+    expert_base: int = 0                                # stack rules: checkpoint index of this group's first expert (two expert
+    #                                                     groups of one layer numbered consecutively)
     qkv_groups: Optional[Tuple[int, int, int]] = None   # rename: (kv heads, q heads per kv head, head dim) of a checkpoint that
     #                                                     stores the fused projection grouped by kv head: [q.. q k v] per group
 
@@ -143,7 +145,7 @@ class Rule:
 
     def source_names(self) -> List[str]:
         if self.op in ("stack", "stack_concat"):
-            return [s.format(E=e) for e in range(self.num_experts) for s in self.sources]
+            return [s.format(E=self.expert_base + e) for e in range(self.num_experts) for s in self.sources]
         return list(self.sources)
 
     def forward(self, get: Callable[[str], torch.Tensor], expert_range: Optional[range] = None) -> torch.Tensor:
@@ -162,9 +164,9 @@ class Rule:
             return torch.cat([self._load(i, get(s)) for i, s in enumerate(self.sources)], dim=self.dim)
         er = expert_range if expert_range is not None else range(self.num_experts)
         if self.op == "stack":
-            return torch.stack([get(self.sources[0].format(E=e)) for e in er], dim=0)
+            return torch.stack([get(self.sources[0].format(E=self.expert_base + e)) for e in er], dim=0)
         if self.op == "stack_concat":
-            return torch.stack([torch.cat([get(s.format(E=e)) for s in self.sources], dim=self.dim) for e in er], dim=0)
+            return torch.stack([torch.cat([get(s.format(E=self.expert_base + e)) for s in self.sources], dim=self.dim) for e in er], dim=0)
         raise ValueError(self.op)
 
     def inverse(self, tensor: torch.Tensor, section_sizes: Optional[List[int]] = None, expert_offset: int = 0) -> Dict[str, torch.Tensor]:
@@ -185,7 +187,7 @@ class Rule:
                     for i, (s, p) in enumerate(zip(self.sources, torch.split(tensor, sizes, dim=self.dim)))}
         out = {}
         for i in range(tensor.shape[0]):
-            e = expert_offset + i
+            e = self.expert_base + expert_offset + i
             if self.op == "stack":
                 out[self.sources[0].format(E=e)] = tensor[i].contiguous()
             else:
@@ -224,5 +226,5 @@ def expand_layers(template_rules: List[Rule], layer_ids: Iterable[int]) -> List[
         for r in template_rules:
             out.append(Rule(r.target.replace("{L}", str(i)), [s.replace("{L}", str(i)) for s in r.sources], r.op, r.dim,
                             r.num_experts, r.expert_pairs, r.sizes, r.rope_deinterleave, r.flatten, r.reshape, r.source_shape, r.offset,
-                            r.fn, r.qkv_groups))
+                            r.fn, r.expert_base, r.qkv_groups))
     return out

@@ -1096,3 +1096,120 @@ def test_gemma4_reads_the_multimodal_wrapper_configuration_and_the_reference_fie
     wrapped = type(cfg).from_dict({"model_type": "gemma4", "text_config": {"model_type": "gemma4_text", "num_hidden_layers": 3}})
     assert wrapped.num_hidden_layers == 3 and wrapped.num_experts_per_tok is None
     assert cfg.layer_head_geometry(0) == (256, 4, False) and cfg.layer_head_geometry(5)[0] == 512
+
+
+def test_ernie4_5_vl_matches_hugging_face(tmp_path):
+    """Vision tower, spatial + temporal resampler (a still image paired with itself, video frames paired even / odd), three-axis
+    rotary positions on interleaved pairs, text / vision expert groups with their own routers and widths, shared experts:
+    logits for an image prompt, an image + video prompt and plain text; loss and gradients; the published checkpoint layout
+    (experts numbered text first, transposed routers, two-row correction bias) both ways."""
+    from transformers.models.ernie4_5_vl_moe.configuration_ernie4_5_vl_moe import Ernie4_5_VLMoeConfig as HFConfig
+    from transformers.models.ernie4_5_vl_moe.modeling_ernie4_5_vl_moe import Ernie4_5_VLMoeForConditionalGeneration as HFModel
+
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    torch.manual_seed(0)
+    cfg = HFConfig(
+        text_config=dict(vocab_size=200, hidden_size=64, intermediate_size=96, num_hidden_layers=3, num_attention_heads=4,
+                         num_key_value_heads=2, moe_intermediate_size=[32, 16], moe_k=2, moe_num_experts=4, moe_num_shared_experts=1,
+                         max_position_embeddings=256, mlp_layer_types=["dense", "sparse", "sparse"], router_aux_loss_coef=0.0,
+                         rope_parameters={"rope_theta": 10000.0, "rope_type": "default", "mrope_section": [3, 3, 2]}),
+        vision_config=dict(depth=2, hidden_size=32, num_heads=2, intermediate_size=64, patch_size=4, spatial_merge_size=2,
+                           temporal_merge_size=2),
+        image_token_id=190, video_token_id=191, image_start_token_id=192, image_end_token_id=193, video_start_token_id=194,
+        video_end_token_id=195)
+    cfg._attn_implementation = "eager"
+    hf = HFModel(cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "e_score_correction_bias" in n:
+                p.copy_(torch.randn_like(p) * 0.1)
+            if "norm" in n or ".ln." in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    hf.save_pretrained(tmp_path / "hf")
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).eval()
+    # an image of 4 x 6 patches (6 tokens after the 2 x 2 merge), then a video of 4 frames of 4 x 4 patches (2 frame pairs x 4)
+    ids = [5, 6, 192] + [190] * 6 + [193, 7, 8, 9]
+    mm = [0, 0, 0] + [1] * 6 + [0, 0, 0, 0]
+    moe = [0, 0, 1] + [1] * 6 + [1, 0, 0, 0]
+    img = dict(pixel_values=torch.randn(24, 48), image_grid_thw=torch.tensor([[1, 4, 6]]))
+    vid = dict(pixel_values_videos=torch.randn(64, 48), video_grid_thw=torch.tensor([[4, 4, 4]]))
+    ids2 = ids + [194] + [191] * 8 + [195, 10, 11]
+    mm2, moe2 = mm + [0] + [2] * 8 + [0, 0, 0], moe + [2] + [2] * 8 + [2, 0, 0]
+    t = lambda x: torch.tensor([x])          # noqa: E731
+    with torch.no_grad():
+        assert (hf(input_ids=t(ids), mm_token_type_ids=t(mm), moe_mm_token_type_ids=t(moe), **img).logits
+                - mine(t(ids), **img).logits).abs().max() < 1e-4
+        want = hf(input_ids=t(ids2), mm_token_type_ids=t(mm2), moe_mm_token_type_ids=t(moe2), **img, **vid).logits
+        assert (want - mine(t(ids2), **img, **vid).logits).abs().max() < 1e-4
+        text = torch.randint(0, 180, (2, 12))
+        assert (hf(input_ids=text).logits - mine(text).logits).abs().max() < 1e-4
+    pos = mine.forward.__globals__["multimodal_position_ids"](t(ids2), 190, 191, img["image_grid_thw"], torch.tensor([[2, 4, 4]]), 2)
+    assert pos[:, 0, 3:9].tolist() == [[3] * 6, [3, 3, 3, 4, 4, 4], [3, 4, 5] * 2]           # t fixed, rows, columns
+    assert pos[0, 0, 9].item() == 6 and pos[:, 0, 14:22].tolist()[0] == [11] * 8             # text resumes after max(rows, cols)
+    # loss and gradients; labels are next-token targets here, shifted inside the other implementation
+    lab = torch.tensor(ids2[1:] + [-100])[None]
+    lab[lab >= 190] = -100
+    hf_lab = torch.tensor(ids2)[None].clone()
+    hf_lab[hf_lab >= 190] = -100
+    mine.train()
+    out = mine(t(ids2), labels=lab, **img, **vid)
+    out.loss.backward()
+    ref = hf(input_ids=t(ids2), labels=hf_lab, mm_token_type_ids=t(mm2), moe_mm_token_type_ids=t(moe2), **img, **vid)
+    ref.loss.backward()
+    assert abs(out.loss.item() - ref.loss.item()) < 1e-4
+    ga = mine.language.model.layers["1"].mlp.vision_moe.experts.down_proj.grad
+    gb = hf.model.language_model.layers[1].mlp.vision_moe.experts.down_proj.grad
+    assert ga.abs().sum() > 0 and (ga - gb).abs().max() < 1e-4 * max(1.0, gb.abs().max().item())
+    ga, gb = mine.resampler.temporal_linear.fc1.weight.grad, hf.model.resampler_model.temporal_linear.fc1.weight.grad
+    assert (ga - gb).abs().max() < 1e-4 * max(1.0, gb.abs().max().item())
+    mine.eval()
+    mine.save_pretrained(str(tmp_path / "mine"))
+    back = HFModel.from_pretrained(tmp_path / "mine").eval()
+    with torch.no_grad():
+        again = back(input_ids=t(ids2), mm_token_type_ids=t(mm2), moe_mm_token_type_ids=t(moe2), **img, **vid).logits
+    assert (again - want).abs().max() < 1e-5
+
+
+def test_ernie4_5_vl_trains_on_a_padded_batch_of_images_of_different_sizes():
+    """The VL data path (single-frame patches in merge-block order, one placeholder per merged patch, padded batch) through the
+    model and an optimizer step; vision rows are found from the token ids."""
+    import numpy as np
+
+    from paddleformers_b200.models.ernie4_5_vl import Ernie4_5VLConfig, Ernie4_5VLForConditionalGeneration
+    from paddleformers_b200.models.vision_language import mm_collate_fn
+    from paddleformers_b200.transformers.image_processing import Qwen2VLImageProcessor
+
+    torch.manual_seed(0)
+    cfg = Ernie4_5VLConfig(
+        text_config=dict(vocab_size=200, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, moe_intermediate_size=[32, 16], moe_k=2, moe_num_experts=4, moe_num_shared_experts=1,
+                         mlp_layer_types=["dense", "sparse"], rope_parameters={"rope_theta": 10000.0, "mrope_section": [3, 3, 2]}),
+        vision_config=dict(depth=1, hidden_size=32, num_heads=2, intermediate_size=64, patch_size=4, spatial_merge_size=2),
+        image_token_id=190, video_token_id=191, image_start_token_id=192, image_end_token_id=193, video_start_token_id=194,
+        video_end_token_id=195)
+    assert cfg.vision_start_token_id == 192 and cfg.text_config.moe_layers == [1]
+    model = Ernie4_5VLForConditionalGeneration(cfg, dtype=torch.float32)
+    proc = Qwen2VLImageProcessor(patch_size=4, merge_size=2, temporal_patch_size=1, min_pixels=64, max_pixels=1024)
+    rng = np.random.default_rng(0)
+    examples = []
+    for hw in ((16, 24), (32, 16)):
+        pre = proc([rng.integers(0, 255, (*hw, 3), dtype=np.uint8)])
+        n = proc.num_image_tokens(pre["image_grid_thw"][0].tolist())
+        ids = [5, 192] + [190] * n + [193] + rng.integers(1, 180, 6).tolist()
+        lab = [-100] * (n + 2) + ids[n + 3:] + [-100]
+        examples.append({"input_ids": torch.tensor(ids), "labels": torch.tensor(lab), **pre})
+    batch = mm_collate_fn(examples, pad_token_id=0)
+    assert batch["input_ids"].shape[0] == 2 and batch["pixel_values"].shape[1] == 3 * 4 * 4
+    rows = model.vision_rows(batch["input_ids"])
+    assert rows.sum().item() == sum(int((e["input_ids"] >= 190).sum()) for e in examples)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+    losses = []
+    for _ in range(4):
+        out = model(**batch)
+        out.loss.backward()
+        opt.step()
+        opt.zero_grad()
+        losses.append(out.loss.item())
+    assert losses[-1] < losses[0]
+    assert all(m.mlp.vision_rows is None for m in model.language.model.layers.values() if hasattr(m.mlp, "vision_rows"))

@@ -465,3 +465,59 @@ def test_expert_exchange_buffer_slots_follow_the_pipeline_schedule(name, P, M, V
             assert alloc.high_water == P - stage
         if name == "FThenB":
             assert alloc.high_water == M
+
+
+def _modality_moe_worker(rank, world, full):
+    """Text / vision expert groups under expert parallelism: both groups' exchanges run on every rank, also on a rank
+    whose batch has no vision rows."""
+    from paddleformers_b200.models.ernie4_5_vl import Ernie4_5VLTextConfig
+    from paddleformers_b200.nn.moe import ModalityMoELayer
+    from paddleformers_b200.parallel.topology import ParallelDegrees, initialize_parallel
+    from paddleformers_b200.transformers.model_utils import param_shard_spec
+
+    ps = initialize_parallel(ParallelDegrees(sharding=world, ep=world), backend="gloo") if world > 1 else \
+        initialize_parallel(ParallelDegrees(), backend="gloo")
+    cfg = Ernie4_5VLTextConfig(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=1, num_attention_heads=2,
+                               moe_intermediate_size=[16, 8], moe_k=2, moe_num_experts=4, moe_num_shared_experts=1,
+                               router_aux_loss_coef=0.0, mlp_layer_types=["sparse"])
+    cfg.moe_token_dispatcher_type = "alltoall"
+    layer = ModalityMoELayer(cfg, dtype=torch.float32)
+    with torch.no_grad():
+        for name, p in layer.named_parameters():
+            p.copy_(param_shard_spec(p).shard(full[name], 0, 1, ps.rank_in("ep"), ps.degrees.ep))
+        for name, b in layer.named_buffers():
+            if name in full:
+                b.copy_(full[name])
+    outs = []
+    for r in (range(2) if world == 1 else [rank]):        # the single process plays both ranks' batches
+        g = torch.Generator().manual_seed(100 + r)
+        x = torch.randn(12, 32, generator=g, requires_grad=True)
+        vis = torch.zeros(12, dtype=torch.bool)
+        if r == 0:
+            vis[3:9] = True                                # rank 1 holds text only
+        layer.vision_rows = vis
+        y = layer(x)
+        y.square().sum().backward()
+        outs.append((y.detach(), x.grad.clone()))
+    return outs
+
+
+def test_modality_isolated_experts_under_expert_parallelism():
+    from paddleformers_b200.models.ernie4_5_vl import Ernie4_5VLTextConfig
+    from paddleformers_b200.nn.moe import ModalityMoELayer
+
+    torch.manual_seed(2)
+    cfg = Ernie4_5VLTextConfig(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=1, num_attention_heads=2,
+                               moe_intermediate_size=[16, 8], moe_k=2, moe_num_experts=4, moe_num_shared_experts=1,
+                               router_aux_loss_coef=0.0, mlp_layer_types=["sparse"])
+    layer = ModalityMoELayer(cfg, dtype=torch.float32)
+    full = {}
+    for name, p in layer.named_parameters():
+        full[name] = torch.randn_like(p) * 0.2
+    full["text_moe.gate.e_score_correction_bias"] = torch.randn(4) * 0.1
+    full["vision_moe.gate.e_score_correction_bias"] = torch.randn(4) * 0.1
+    ref = run_distributed(_modality_moe_worker, 1, full)[0]
+    got = run_distributed(_modality_moe_worker, 2, full)
+    for r in range(2):
+        y, gx = got[r][0]
+        assert (y - ref[r][0]).abs().max() < 1e-5 and (gx - ref[r][1]).abs().max() < 1e-5
