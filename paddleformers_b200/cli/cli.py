@@ -17,7 +17,7 @@ from typing import List, Optional
 USAGE = """usage: paddleformers-b200 <command> [args]
 
 commands:
-  train  <config.yaml|json> [key=value ...]   run a training stage (SFT | PT | DPO, with or without LoRA)
+  train  <config.yaml|json> [key=value ...]   run a training stage (SFT | PT | DPO | VL-SFT | VL-PT | VL-DPO | recipes; with or without LoRA)
   export <config.yaml|json> [key=value ...]   merge LoRA adapters into the base model and write an HF checkpoint
   version                                     print the package version
   help                                        this text

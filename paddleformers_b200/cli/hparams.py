@@ -22,7 +22,7 @@ from ..trainer.training_args import TrainingArguments
 class ModelArguments:
     model_name_or_path: Optional[str] = None
     model_type: Optional[str] = field(default=None, metadata={"help": "build from a named preset / model_type when no checkpoint is given"})
-    stage: str = field(default="SFT", metadata={"help": "SFT | PT | DPO | VL-SFT | auto-parallel"})
+    stage: str = field(default="SFT", metadata={"help": "SFT | PT | DPO | VL-SFT | VL-PT | VL-DPO | auto-parallel | dsv3_pretrain | ernie_pretrain"})
     from_scratch: bool = False
     lora: bool = False
     lora_rank: int = 8

@@ -172,15 +172,19 @@ def run_tuner(argv: Optional[list] = None):
         return run_vl_sft(model_args, data_args, gen_args, train_args)
     if stage == "SFT":
         return run_sft(model_args, data_args, gen_args, train_args)
-    if stage in ("PT", "CPT", "VL-PT"):
+    if stage == "VL-PT":
+        return run_vl_sft(model_args, data_args, gen_args, train_args, pretrain=True)
+    if stage == "VL-DPO":
+        return run_vl_dpo(model_args, data_args, gen_args, train_args)
+    if stage in ("PT", "CPT"):
         return run_sft(model_args, data_args, gen_args, train_args, pretrain=True)
-    if stage in ("DPO", "VL-DPO"):
+    if stage == "DPO":
         return run_dpo(model_args, data_args, gen_args, train_args)
     if stage in ("AUTO-PARALLEL", "AUTO_PARALLEL"):
         return run_auto_parallel(model_args, data_args, gen_args, train_args)
     if stage in RECIPES:
         return run_recipe_pretrain(stage, model_args, data_args, gen_args, train_args)
-    raise ValueError(f"unknown stage {model_args.stage!r}; expected SFT | PT | DPO | VL-SFT | auto-parallel | "
+    raise ValueError(f"unknown stage {model_args.stage!r}; expected SFT | PT | DPO | VL-SFT | VL-PT | VL-DPO | auto-parallel | "
                      f"{' | '.join(sorted(RECIPES)).lower()}")
 
 
@@ -231,14 +235,8 @@ def run_recipe_pretrain(stage, model_args, data_args, gen_args, train_args):
     return run_sft(model_args, data_args, gen_args, train_args, pretrain=True)
 
 
-def run_vl_sft(model_args, data_args, gen_args, train_args):
-    """Supervised fine-tuning of a vision-language model on conversations with images
-    (paddleformers/cli/train/tuner.py:33-68 routes VL-SFT to the same workflow with multimodal data plugins)."""
-    import functools as ft
-
-    from ..datasets.mm_dataset import MMSFTDataset
-    from ..models.vision_language import mm_collate_fn
-    from ..trainer.trainer import Trainer
+def _vl_model_and_processor(model_args, data_args, train_args):
+    """(model, tokenizer, image processor, placeholder token names) of a vision-language stage."""
     from ..transformers.auto import AutoModelForConditionalGeneration
     from ..transformers.image_processing import Qwen2VLImageProcessor
 
@@ -248,7 +246,7 @@ def run_vl_sft(model_args, data_args, gen_args, train_args):
                                                               device=torch.device(train_args.device))
     tokenizer = _tokenizer(model_args)
     if tokenizer is None:
-        raise ValueError("VL-SFT needs a tokenizer (model_name_or_path with tokenizer files)")
+        raise ValueError("vision-language stages need a tokenizer (model_name_or_path with tokenizer files)")
     vc = model.config.vision_config
     if not isinstance(vc, dict) or "spatial_merge_size" not in vc:    # fixed image size, a fixed number of tokens per image
         from ..transformers.image_processing import SiglipImageProcessor
@@ -275,10 +273,50 @@ def run_vl_sft(model_args, data_args, gen_args, train_args):
         names = dict(image_token=tokenizer.convert_ids_to_tokens(model.config.image_token_id),
                      vision_start_token=tokenizer.convert_ids_to_tokens(model.config.vision_start_token_id),
                      vision_end_token=tokenizer.convert_ids_to_tokens(model.config.vision_end_token_id))
-    train_ds = MMSFTDataset(data_args.train_dataset_path, tokenizer, proc, data_args.template, train_args.max_seq_len, **names)
+    return model, tokenizer, proc, names
+
+
+def run_vl_sft(model_args, data_args, gen_args, train_args, pretrain: bool = False):
+    """Supervised fine-tuning of a vision-language model on conversations with images, or (``pretrain``, stage VL-PT)
+    next-token training on ``{"text": "... <image> ...", "images": [...]}`` records where every text token is a target
+    (paddleformers/cli/train/tuner.py:33-68 routes VL-SFT / VL-PT to the same workflow with multimodal data plugins)."""
+    import functools as ft
+
+    from ..datasets.mm_dataset import MMSFTDataset
+    from ..models.vision_language import mm_collate_fn
+    from ..trainer.trainer import Trainer
+
+    model, tokenizer, proc, names = _vl_model_and_processor(model_args, data_args, train_args)
+    train_ds = MMSFTDataset(data_args.train_dataset_path, tokenizer, proc, data_args.template, train_args.max_seq_len,
+                            pretrain=pretrain, **names)
     pad = tokenizer.pad_token_id if tokenizer.pad_token_id is not None else 0
     trainer = Trainer(model=model, args=train_args, train_dataset=train_ds, data_collator=ft.partial(mm_collate_fn, pad_token_id=pad),
                       tokenizer=tokenizer)
+    metrics = trainer.train(resume_from_checkpoint=train_args.resume_from_checkpoint)
+    trainer.save_model(train_args.output_dir)
+    return trainer, metrics
+
+
+def run_vl_dpo(model_args, data_args, gen_args, train_args):
+    """Preference optimisation of a vision-language model: prompt (with images) + chosen and + rejected as two rows, a frozen
+    copy of the starting model as the reference (none for the reference-free losses)
+    (paddleformers/cli/train/dpo/workflow.py:65 with the multimodal plugins)."""
+    import functools as ft
+
+    from ..datasets.mm_dataset import MMDPODataset, mm_dpo_collate_fn
+    from ..trainer.dpo_trainer import DPOTrainer
+    from ..transformers.auto import AutoModelForConditionalGeneration
+
+    model, tokenizer, proc, names = _vl_model_and_processor(model_args, data_args, train_args)
+    ref = None
+    if train_args.dpo_loss_type not in ("or", "simpo"):
+        ref = AutoModelForConditionalGeneration.from_pretrained(train_args.ref_model_name_or_path or model_args.model_name_or_path,
+                                                                dtype=train_args.compute_dtype, device=torch.device(train_args.device))
+    ds = MMDPODataset(data_args.train_dataset_path, tokenizer, proc, data_args.template, train_args.max_seq_len, **names)
+    pad = tokenizer.pad_token_id if tokenizer.pad_token_id is not None else 0
+    trainer = DPOTrainer(model=model, args=train_args, data_collator=ft.partial(mm_dpo_collate_fn, pad_token_id=pad), train_dataset=ds,
+                         tokenizer=tokenizer, ref_model=ref, dpo_beta=train_args.dpo_beta, dpo_loss_type=train_args.dpo_loss_type,
+                         dpo_label_smoothing=train_args.dpo_label_smoothing, sft_loss_ratio=train_args.sft_loss_ratio)
     metrics = trainer.train(resume_from_checkpoint=train_args.resume_from_checkpoint)
     trainer.save_model(train_args.output_dir)
     return trainer, metrics

@@ -40,6 +40,16 @@ class DPOTrainer(Trainer):
         self.last_metrics: Dict[str, float] = {}
 
     def _logps(self, model, inputs):
+        if "preference_pairs" in inputs:
+            # multimodal pairs: rows 2b / 2b + 1 are example b's chosen / rejected sequence, targets on the response only
+            extra = {k: inputs[k] for k in ("pixel_values", "image_grid_thw", "pixel_values_videos", "video_grid_thw", "token_type_ids")
+                     if inputs.get(k) is not None}
+            out = model(input_ids=inputs["input_ids"], return_logits=True, **extra)
+            labels = inputs["labels"]
+            S = labels.shape[1]
+            lo, hi = torch.zeros(labels.shape[0], dtype=torch.long, device=labels.device), torch.full_like(labels[:, 0], S)
+            lp = _response_logps(out.logits, labels, lo, hi, self.dpo["loss_type"] in ("simpo", "ipo", "or"))
+            return lp[0::2], lp[1::2], out
         out = model(input_ids=inputs["input_ids"], position_ids=inputs.get("position_ids"),
                     attn_mask_startend_row_indices=inputs.get("attn_mask_startend_row_indices"), return_logits=True)
         idx = inputs["response_indexs"]
@@ -61,7 +71,10 @@ class DPOTrainer(Trainer):
                     with ctx:
                         rc, rr, _ = self._logps(model, inputs)
         nll = None
-        if self.dpo["sft_loss_ratio"] > 0:
+        if self.dpo["sft_loss_ratio"] > 0 and "preference_pairs" in inputs:
+            lab = inputs["labels"][0::2]
+            nll = -_response_logps(out.logits[0::2], lab, torch.zeros_like(lab[:, 0]), torch.full_like(lab[:, 0], lab.shape[1]), True).mean()
+        elif self.dpo["sft_loss_ratio"] > 0:
             idx = inputs["response_indexs"]
             nll = -_response_logps(out.logits, inputs["chosen_labels"], idx[:, 1], idx[:, 2], True).mean()
         loss, metrics = dpo_loss(pc, pr, rc, rr, chosen_nll=nll, **self.dpo)

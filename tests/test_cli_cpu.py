@@ -173,6 +173,75 @@ def test_vl_sft_stage_trains_on_images(tmp_path):
     assert model.visual.patch_embed.weight.shape == (16, 3 * 2 * 4 * 4) and os.path.exists(out / "tokenizer.json")
 
 
+def test_vl_pt_and_vl_dpo_stages(tmp_path):
+    """VL-PT: image-text records where every text token is a target. VL-DPO: preference pairs that share a prompt with an image;
+    the policy moves away from the frozen reference and the logged reward margin becomes positive."""
+    from PIL import Image
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    from paddleformers_b200.cli.cli import main
+    from paddleformers_b200.datasets.mm_dataset import MMDPODataset, MMSFTDataset, mm_dpo_collate_fn
+    from paddleformers_b200.models.vision_language import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+    from paddleformers_b200.transformers.image_processing import Qwen2VLImageProcessor
+
+    words = ["<pad>", "<s>", "</s>", "<unk>", "Human:", "Assistant:", "System:", "<image>", "<|image_pad|>", "<|vision_start|>",
+             "<|vision_end|>"] + [f"w{i}" for i in range(40)]
+    tok = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    fast = PreTrainedTokenizerFast(tokenizer_object=tok, pad_token="<pad>", bos_token="<s>", eos_token="</s>", unk_token="<unk>")
+    base = tmp_path / "base"
+    cfg = Qwen2VLConfig(text_config=dict(vocab_size=len(words), hidden_size=32, intermediate_size=48, num_hidden_layers=1,
+                                         num_attention_heads=2, num_key_value_heads=1, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}),
+                        vision_config=dict(depth=1, embed_dim=16, hidden_size=32, mlp_ratio=2, num_heads=2, patch_size=4),
+                        image_token_id=words.index("<|image_pad|>"), vision_start_token_id=words.index("<|vision_start|>"),
+                        vision_end_token_id=words.index("<|vision_end|>"))
+    torch.manual_seed(0)
+    Qwen2VLForConditionalGeneration(cfg, dtype=torch.float32).save_pretrained(str(base))
+    fast.save_pretrained(str(base))
+    rng = np.random.RandomState(0)
+    pt, dpo = tmp_path / "pt.jsonl", tmp_path / "dpo.jsonl"
+    with open(pt, "w") as f, open(dpo, "w") as g:
+        for i in range(8):
+            img = tmp_path / f"img{i}.png"
+            Image.fromarray((rng.rand(16 + 8 * (i % 2), 24, 3) * 255).astype("uint8")).save(img)
+            f.write(json.dumps({"images": [str(img)], "text": f"w1 <image> w{2 + i % 5} w7 w8"}) + "\n")
+            g.write(json.dumps({"images": [str(img)], "messages": [{"role": "user", "content": "<image> w1 w2"}],
+                                "chosen": "w5 w6 w7", "rejected": "w30 w31"}) + "\n")
+    proc = Qwen2VLImageProcessor(patch_size=4, merge_size=2, temporal_patch_size=2, min_pixels=256, max_pixels=4096)
+    names = dict(image_token="<|image_pad|>", vision_start_token="<|vision_start|>", vision_end_token="<|vision_end|>")
+    item = MMSFTDataset(str(pt), fast, proc, "default", 64, pretrain=True, **names)[0]
+    n_img = int((item["input_ids"] == words.index("<|image_pad|>")).sum())
+    assert n_img == proc.num_image_tokens(item["image_grid_thw"][0].tolist())
+    assert int((item["labels"] != -100).sum()) == 4            # w2 w7 w8 </s> after the image run; never an image token
+    pair = MMDPODataset(str(dpo), fast, proc, "default", 64, **names)[1]
+    assert len(pair["input_ids"]) == 2 and [int((x != -100).sum()) for x in pair["labels"]] == [4, 3]     # response + end token
+    batch = mm_dpo_collate_fn([pair, pair])
+    assert batch["input_ids"].shape[0] == 4 and batch["image_grid_thw"].shape[0] == 4 and int(batch["preference_pairs"]) == 2
+    common = {"model_name_or_path": str(base), "compute_type": "float32", "device": "cpu", "template": "default", "max_seq_len": 64,
+              "per_device_train_batch_size": 2, "logging_steps": 1, "save_strategy": "no", "min_pixels": 256, "max_pixels": 4096}
+    env = os.environ.get("CUDA_VISIBLE_DEVICES")
+    os.environ["CUDA_VISIBLE_DEVICES"] = ""
+    try:
+        f1 = tmp_path / "pt.json"
+        f1.write_text(json.dumps(dict(common, stage="VL-PT", train_dataset_path=str(pt), max_steps=3, learning_rate=5e-3,
+                                      output_dir=str(tmp_path / "out_pt"))))
+        assert main(["train", str(f1)]) == 0
+        f2 = tmp_path / "dpo.json"
+        f2.write_text(json.dumps(dict(common, stage="VL-DPO", train_dataset_path=str(dpo), max_steps=6, learning_rate=2e-2,
+                                      output_dir=str(tmp_path / "out_dpo"), dpo_beta=0.5, logging_dir=str(tmp_path / "logs"))))
+        from paddleformers_b200.cli.train import run_tuner
+
+        trainer, _ = run_tuner([str(f2)])
+    finally:
+        if env is None:
+            os.environ.pop("CUDA_VISIBLE_DEVICES", None)
+        else:
+            os.environ["CUDA_VISIBLE_DEVICES"] = env
+    assert os.path.exists(tmp_path / "out_pt" / "model.safetensors") and os.path.exists(tmp_path / "out_dpo" / "model.safetensors")
+    assert trainer.ref_model is not None and trainer.last_metrics["rewards/margins"] > 0 and trainer.last_metrics["rewards/accuracies"] == 1.0
+
+
 def test_example_configs_parse(monkeypatch):
     """Every file under examples/config is accepted by the argument parser (no unknown keys, right types, parallel
     degrees that divide a 64-GPU job)."""
