@@ -181,6 +181,12 @@ def translate(cfg: Dict[str, Any], known: set) -> Dict[str, Any]:
                     notes.append(f"{key}:{opt}: unknown option, ignored")
         elif key in REFERENCE_FLAGS:
             apply(key, out.pop(key), key)
+    if isinstance(out.get("recompute_modules"), dict):
+        # the reference's refined recompute: {operation: layers that recompute it}, applied on top of per-layer recompute
+        out.setdefault("refined_recompute", out.pop("recompute_modules"))
+        if not out.get("recompute_granularity"):
+            out["recompute_granularity"] = "full"
+        notes.append("recompute_modules (per-operation counts) -> refined_recompute with recompute_granularity=full")
     if notes:
         logger.info("reference configuration keys: " + "; ".join(notes))
     return out

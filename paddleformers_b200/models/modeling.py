@@ -23,6 +23,7 @@ import torch.utils.checkpoint
 
 from ..nn.moe import DenseMLP, MoELayer
 from ..ops import functional as F
+from ..utils.refined_recompute import checkpoint_keeping, keep, kept_ops_of_layer
 from ..parallel.tensor_parallel import (ColumnParallelLinear, GatherOp, RowParallelLinear, ScatterOp,
                                         VocabParallelEmbedding, mark_as_sequence_parallel_parameter)
 from ..parallel.topology import get_parallel_state
@@ -231,7 +232,7 @@ class Attention(nn.Module):
             gate = qg[..., self.D:].reshape(x2d.shape[0], self.Hq * self.D)
             qkv = torch.cat([qg[..., :self.D].reshape(x2d.shape[0], self.Hq * self.D), _apply(self.k_proj, x2d), _apply(self.v_proj, x2d)], dim=-1)
         else:
-            qkv = _apply(self.qkv_proj, x2d)
+            qkv = keep("attention_column_ln", _apply, self.qkv_proj, x2d)
         kend = ctx.kend_window if ((self.window or self.chunk) and ctx.kend_window is not None) else ctx.kend
         cos, sin = (ctx.cos_local, ctx.sin_local) if (self.local_rope and ctx.cos_local is not None) else (ctx.cos, ctx.sin)
         if self.qk_norm_full:
@@ -307,10 +308,10 @@ class Attention(nn.Module):
                                           v.reshape(B, S, self.Hkv, D), ctx, self.scale, self.config)
             out = out.reshape(B * S, self.Hq * D)
         else:
-            out = F.flash_attention_qkvpacked(qkv, ctx.B, ctx.S, self.Hq, self.Hkv, self.D, True, kend, self.scale)
+            out = keep("flash_attn", F.flash_attention_qkvpacked, qkv, ctx.B, ctx.S, self.Hq, self.Hkv, self.D, True, kend, self.scale)
         if gate is not None:
             out = out * torch.sigmoid(gate.float()).to(out.dtype)
-        return _apply(self.o_proj, out)
+        return keep("attention_row_ln", _apply, self.o_proj, out)
 
 
 class SparseIndexer(nn.Module):
@@ -648,6 +649,12 @@ class DecoderModel(nn.Module):
         method = getattr(cfg, "recompute_method", None) or "uniform"
         n_rc = int(getattr(cfg, "recompute_num_layers", 1) or 1)
         layer_ids = list(self.layer_range)
+        # refined_recompute = {operation: layers that recompute it}: the named operations of the other layers keep their saved
+        # tensors and are skipped when the layer is rebuilt (utils/refined_recompute.py)
+        refined = getattr(cfg, "refined_recompute", None) if recompute else None
+        if refined:
+            assert not getattr(cfg, "recompute_use_reentrant", False), "refined_recompute needs the non-reentrant checkpoint"
+            assert not (method == "uniform" and n_rc > 1), "refined_recompute works per layer (recompute_num_layers 1)"
         if recompute and method == "block":
             skip |= set(layer_ids[n_rc:])
         if recompute and method == "uniform" and n_rc > 1 and caches is None:
@@ -666,6 +673,10 @@ class DecoderModel(nn.Module):
             layer = self.layers[str(i)]
             cache = caches[i] if caches is not None else None
             if recompute and i not in skip and cache is None:
+                kept = kept_ops_of_layer(refined, i, cfg.num_hidden_layers, layer_ids) if refined else ()
+                if kept:
+                    hidden, residual = checkpoint_keeping(lambda h, r, layer=layer: layer(h, r, ctx, None), kept, hidden, residual)
+                    continue
                 hidden, residual = torch.utils.checkpoint.checkpoint(
                     layer, hidden, residual, ctx, None, use_reentrant=bool(getattr(cfg, "recompute_use_reentrant", False)))
             else:

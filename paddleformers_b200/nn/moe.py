@@ -606,16 +606,18 @@ class DenseMLP(nn.Module):
     def forward(self, x):
         if self.act_name not in ("silu", "swish"):
             return self._gated_generic(x)
+        from ..utils.refined_recompute import keep      # no-ops outside a refined-recompute frame
+
         if self._tp:
-            return self.down_proj(self.gate_up_proj(x))
+            return keep("mlp_row_ln", self.down_proj, keep("mlp_column_ln", self.gate_up_proj, x))
         gu, dn = self.gate_up_proj, self.down_proj
         if not isinstance(gu, nn.Linear):          # wrapped (e.g. LoRA): the wrapper owns the projection
-            act = F.swiglu(gu(x))
+            act = keep("mlp_column_ln", lambda t: F.swiglu(gu(t)), x)
         elif gu.bias is None:
-            act = F.linear_swiglu(x, gu.weight)
+            act = keep("mlp_column_ln", F.linear_swiglu, x, gu.weight)
         else:
-            act = F.swiglu(F.linear(x, gu.weight, gu.bias))
-        return F.linear(act, dn.weight, dn.bias) if isinstance(dn, nn.Linear) else dn(act)
+            act = keep("mlp_column_ln", lambda t: F.swiglu(F.linear(t, gu.weight, gu.bias)), x)
+        return keep("mlp_row_ln", F.linear, act, dn.weight, dn.bias) if isinstance(dn, nn.Linear) else keep("mlp_row_ln", dn, act)
 
 
 class MoELayer(nn.Module):

@@ -52,6 +52,9 @@ class LlmMetaConfig:
         ("recompute_num_layers", int, 1, "layers per recompute chunk"),
         ("recompute_modules", Optional[Any], None, "module names to recompute under selective granularity"),
         ("recompute_use_reentrant", bool, False, "use the reentrant checkpoint implementation"),
+        ("refined_recompute", Optional[Any], None, "with full recompute: {operation: number of layers that recompute it} for "
+         "attention_column_ln | flash_attn | attention_row_ln | mlp_column_ln | mlp_row_ln; the other layers keep that "
+         "operation's saved tensors (0: kept in every layer)"),
     ]
     loss_attributes = [
         ("use_fused_head_and_loss_fn", bool, False, "fused head + loss computing gradients in the forward"),

@@ -526,3 +526,12 @@ def test_numa_binding_reads_the_gpu_node_from_sysfs(tmp_path, monkeypatch):
     assert numa.bind_to_gpu_node(2, str(pci), str(node))["reason"].startswith("no PCI")
     monkeypatch.delenv("BIND_TRAINER_NUMA", raising=False)
     assert numa.maybe_bind_trainer() is None
+
+
+def test_per_operation_recompute_counts_become_refined_recompute():
+    from paddleformers_b200.cli.reference_flags import translate
+
+    out = translate({"recompute_modules": {"flash_attn": 0, "mlp_row_ln": 2}}, {"recompute_modules", "recompute_granularity", "refined_recompute"})
+    assert out == {"refined_recompute": {"flash_attn": 0, "mlp_row_ln": 2}, "recompute_granularity": "full"}
+    keep = translate({"recompute_modules": ["attn"], "recompute_granularity": "selective"}, {"recompute_modules", "recompute_granularity"})
+    assert keep["recompute_modules"] == ["attn"]
