@@ -92,6 +92,9 @@ def _reference(moe, steps, accum):
     ("tp2", 2, False, dict(tensor_model_parallel_size=2, gradient_accumulation_steps=2)),
     ("tp2_sp_filtered_loss", 2, False, dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2,
                                             use_filtered_label_loss=True)),
+    ("tp2_sp_refined_recompute", 2, False, dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2,
+                                                recompute_granularity="full",
+                                                refined_recompute={"flash_attn": 0, "attention_column_ln": 0, "mlp_row_ln": 1})),
     ("sharding2", 2, False, dict(sharding="stage1", gradient_accumulation_steps=1)),
     ("sharding2_custom_adamw", 2, False, dict(sharding="stage1", gradient_accumulation_steps=1, optim="adamw_custom",
                                               tensorwise_offload_optimizer=True)),
@@ -166,6 +169,11 @@ def _train_single4(rank, world, moe, targs, steps, full_state):
                              pipeline_schedule="interleaved")),
     ("pp2_zero_bubble", dict(pipeline_model_parallel_size=2, gradient_accumulation_steps=4, pipeline_schedule="zero_bubble")),
     ("pp2_zbv", dict(pipeline_model_parallel_size=2, gradient_accumulation_steps=4, pipeline_schedule="zbv")),
+    ("pp2_1f1b_refined_recompute", dict(pipeline_model_parallel_size=2, gradient_accumulation_steps=4, recompute_granularity="full",
+                                        refined_recompute={"flash_attn": 0, "mlp_column_ln": 2})),
+    ("pp2_zero_bubble_refined_recompute", dict(pipeline_model_parallel_size=2, gradient_accumulation_steps=4,
+                                               pipeline_schedule="zero_bubble", recompute_granularity="full",
+                                               refined_recompute={"attention_row_ln": 0, "mlp_row_ln": 0})),
 ])
 def test_pipeline_matches_single_process(name, targs):
     from paddleformers_b200.models.modeling import MODEL_MAPPING
