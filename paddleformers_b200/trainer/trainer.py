@@ -30,8 +30,8 @@ from . import checkpoint as ckpt
 from .trainer_callback import (CallbackHandler, DefaultFlowCallback, FP8QuantWeightCallback, MetricsDumpCallback,
                                MoECorrectionBiasAdjustCallback, PrinterCallback, ProfilerCallback, TrainerCallback,
                                TrainerControl, TrainerState)
-from .trainer_utils import (PREFIX_CHECKPOINT_DIR, LRScheduler, TrainerMemoryTracker, get_last_checkpoint, tensor_md5,
-                            get_scheduler_lambda, set_random_seed, speed_metrics)
+from .trainer_utils import (PREFIX_CHECKPOINT_DIR, EvalPrediction, EvalSampler, LRScheduler, PredictionOutput, TrainerMemoryTracker,
+                            get_last_checkpoint, tensor_md5, get_scheduler_lambda, set_random_seed, speed_metrics)
 from .training_args import TrainingArguments
 
 
@@ -67,7 +67,8 @@ class Trainer:
     def __init__(self, model: torch.nn.Module = None, args: TrainingArguments = None, data_collator: Callable = None,
                  train_dataset: Dataset = None, eval_dataset: Dataset = None, tokenizer=None,
                  callbacks: Optional[List[TrainerCallback]] = None, optimizers: Tuple[Any, Any] = (None, None),
-                 compute_metrics: Optional[Callable] = None, criterion: Optional[Callable] = None):
+                 compute_metrics: Optional[Callable] = None, criterion: Optional[Callable] = None,
+                 preprocess_logits_for_metrics: Optional[Callable] = None):
         self.args = args or TrainingArguments()
         self.ps = self.args.setup_parallel()
         set_random_seed(self.args.seed, self.ps)
@@ -76,6 +77,7 @@ class Trainer:
         self.train_dataset, self.eval_dataset = train_dataset, eval_dataset
         self.tokenizer = tokenizer
         self.compute_metrics = compute_metrics
+        self.preprocess_logits_for_metrics = preprocess_logits_for_metrics
         self.criterion = criterion
         self.optimizer, self.lr_scheduler = optimizers
         self.state = TrainerState(is_world_process_zero=self.args.process_index == 0)
@@ -537,53 +539,117 @@ class Trainer:
 
     @torch.no_grad()
     def evaluate(self, eval_dataset=None, metric_key_prefix: str = "eval") -> Dict[str, float]:
+        """Loss and perplexity over the WHOLE evaluation set (token-weighted, summed over the data ranks), plus whatever
+        ``compute_metrics`` returns for the gathered predictions. A dict of datasets is evaluated one by one, each under
+        ``<prefix>_<name>`` (paddleformers/trainer/trainer.py ``evaluate`` / ``evaluation_loop``)."""
+        ds = eval_dataset if eval_dataset is not None else self.eval_dataset
+        if isinstance(ds, dict):
+            metrics = {}
+            for name, one in ds.items():
+                metrics.update(self.evaluate(one, f"{metric_key_prefix}_{name}"))
+            return metrics
+        start = time.time()
+        loss, preds, labels, n_batches = self._evaluation_loop(ds, want_predictions=self.compute_metrics is not None)
+        metrics = {f"{metric_key_prefix}_loss": loss, f"{metric_key_prefix}_ppl": math.exp(min(loss, 50.0))}
+        if self.compute_metrics is not None:
+            extra = self.compute_metrics(EvalPrediction(predictions=preds, label_ids=labels)) or {}
+            metrics.update({(k if k.startswith(metric_key_prefix + "_") else f"{metric_key_prefix}_{k}"): float(v) for k, v in extra.items()})
+        metrics.update(speed_metrics(metric_key_prefix, start, num_samples=len(ds), num_steps=n_batches))
+        self.log(metrics)
+        self.control = self.callback_handler.on_evaluate(self.args, self.state, self.control, metrics=metrics)
+        return metrics
+
+    @torch.no_grad()
+    def _evaluation_loop(self, dataset, want_predictions: bool, with_labels: bool = True):
+        """(token-weighted mean loss, predictions, labels, batches per rank). Predictions are the arg-max token ids unless
+        ``preprocess_logits_for_metrics(logits, labels)`` says otherwise; rows that only fill up the last batch are left out."""
         model = self.model
+        was_training = model.training
         model.eval()
-        loader = self.get_eval_dataloader(eval_dataset)
+        a = self.args
+        sampler = EvalSampler(len(dataset), self.ps.dataset_rank, a.dataset_world_size, a.per_device_eval_batch_size)
+        loader = DataLoader(dataset, batch_size=a.per_device_eval_batch_size, sampler=sampler, collate_fn=self.data_collator,
+                            pin_memory=self.device.type == "cuda")
         tot = torch.zeros((), dtype=torch.float64, device=self.device)
         cnt = torch.zeros((), dtype=torch.float64, device=self.device)
         saved_accum = getattr(model, "loss_accumulation_steps", 1)
         if hasattr(model, "loss_accumulation_steps"):
             model.loss_accumulation_steps = 1
-        start = time.time()
-        n_batches = 0
-        for inputs in loader:
-            if 0 < self.args.max_evaluate_steps <= n_batches:
-                break
-            inputs = self._prepare_inputs(inputs)
-            out = model(**inputs)
-            n = out.num_tokens.double() if out.num_tokens is not None else torch.ones_like(cnt)
-            tot += out.loss.double() * n
-            cnt += n
-            n_batches += 1
-            self.control = self.callback_handler.on_prediction_step(self.args, self.state, self.control)
-        if hasattr(model, "loss_accumulation_steps"):
-            model.loss_accumulation_steps = saved_accum
+        rows_p, rows_l, n_batches = [], [], 0
+        try:
+            for b, inputs in enumerate(loader):
+                if 0 < a.max_evaluate_steps <= n_batches:
+                    break
+                inputs = self._prepare_inputs(inputs)
+                pad_rows = sampler.padding_rows(b)
+                has_labels = with_labels and inputs.get("labels") is not None
+                if not with_labels:
+                    inputs.pop("labels", None)
+                if pad_rows and has_labels:
+                    inputs["labels"] = inputs["labels"].clone()
+                    inputs["labels"][pad_rows] = -100
+                out = model(**inputs, return_logits=True) if want_predictions else model(**inputs)
+                if has_labels and out.loss is not None:
+                    n = out.num_tokens.double() if out.num_tokens is not None else torch.ones_like(cnt)
+                    if len(pad_rows) < a.per_device_eval_batch_size:        # a batch of fill-ins only has no valid token
+                        tot += out.loss.double() * n
+                        cnt += n
+                if want_predictions:
+                    keep = [i for i in range(out.logits.shape[0]) if i not in pad_rows]
+                    lab = inputs.get("labels")
+                    pre = getattr(self, "preprocess_logits_for_metrics", None)
+                    pred = pre(out.logits, lab) if pre is not None else out.logits.argmax(-1)
+                    rows_p += [pred[i].cpu() for i in keep]
+                    if lab is not None:
+                        rows_l += [lab[i].cpu() for i in keep]
+                n_batches += 1
+                self.control = self.callback_handler.on_prediction_step(a, self.state, self.control)
+        finally:
+            if hasattr(model, "loss_accumulation_steps"):
+                model.loss_accumulation_steps = saved_accum
+            model.train(was_training)
         if dist.is_initialized() and self.ps.size("data") > 1:
             both = torch.stack([tot, cnt])
             dist.all_reduce(both, group=self.ps.group("data"))
             tot, cnt = both[0], both[1]
+            if want_predictions:
+                gathered = [None] * self.ps.size("data")
+                dist.all_gather_object(gathered, (rows_p, rows_l), group=self.ps.group("data"))
+                # back to dataset order: global batch by global batch, rank by rank
+                per = a.per_device_eval_batch_size
+                rows_p, rows_l = [], []
+                for gb in range(n_batches):
+                    for rp, rl in gathered:
+                        rows_p += rp[gb * per:(gb + 1) * per]
+                        rows_l += rl[gb * per:(gb + 1) * per]
         loss = float(tot / cnt.clamp(min=1))
-        metrics = {f"{metric_key_prefix}_loss": loss, f"{metric_key_prefix}_ppl": math.exp(min(loss, 50.0))}
-        metrics.update(speed_metrics(metric_key_prefix, start, num_samples=n_batches * self.args.per_device_eval_batch_size *
-                                     self.args.dataset_world_size, num_steps=n_batches))
-        self.log(metrics)
-        self.control = self.callback_handler.on_evaluate(self.args, self.state, self.control, metrics=metrics)
-        model.train()
-        return metrics
 
-    @torch.no_grad()
-    def predict(self, test_dataset, metric_key_prefix: str = "test"):
-        self.model.eval()
-        loader = self.get_eval_dataloader(test_dataset)
-        preds = []
-        for inputs in loader:
-            inputs = self._prepare_inputs(inputs)
-            inputs.pop("labels", None)
-            out = self.model(**inputs, return_logits=True)
-            preds.append(out.logits.argmax(-1).cpu())
-        self.model.train()
-        return torch.cat(preds) if preds else None
+        def stack(rows):
+            if not rows:
+                return None
+            if rows[0].dim() == 0:
+                return torch.stack(rows).numpy()
+            width = max(r.shape[0] for r in rows)
+            outp = torch.full((len(rows), width) + tuple(rows[0].shape[1:]), -100, dtype=rows[0].dtype)
+            for i, r in enumerate(rows):
+                outp[i, :r.shape[0]] = r
+            return outp.numpy()
+
+        return loss, stack(rows_p), stack(rows_l), n_batches
+
+    def predict(self, test_dataset, metric_key_prefix: str = "test") -> PredictionOutput:
+        """Predictions (and, where the set has labels, loss and ``compute_metrics`` results) for every example of the set."""
+        start = time.time()
+        has_labels = len(test_dataset) > 0 and "labels" in test_dataset[0]
+        loss, preds, labels, n_batches = self._evaluation_loop(test_dataset, want_predictions=True, with_labels=has_labels)
+        metrics = {}
+        if has_labels:
+            metrics[f"{metric_key_prefix}_loss"] = loss
+            if self.compute_metrics is not None:
+                extra = self.compute_metrics(EvalPrediction(predictions=preds, label_ids=labels)) or {}
+                metrics.update({f"{metric_key_prefix}_{k}": float(v) for k, v in extra.items()})
+        metrics.update(speed_metrics(metric_key_prefix, start, num_samples=len(test_dataset), num_steps=n_batches))
+        return PredictionOutput(predictions=preds, label_ids=labels, metrics=metrics)
 
     # ------------------------------------------------------------------ checkpointing
     def save_model(self, output_dir: Optional[str] = None):

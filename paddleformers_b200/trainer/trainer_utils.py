@@ -11,7 +11,7 @@ import os
 import random
 import re
 import time
-from typing import Dict, Optional
+from typing import NamedTuple, Dict, Optional
 
 import numpy as np
 import torch
@@ -185,6 +185,46 @@ def set_random_seed(seed: int, parallel_state=None):
     if torch.cuda.is_available():
         torch.cuda.manual_seed(local)
     return local
+
+
+class EvalPrediction(NamedTuple):
+    """What ``compute_metrics`` receives: predictions and labels of the whole evaluation set, one row per example, padded
+    with -100 to the longest row (paddleformers/trainer/trainer_utils.py ``EvalPrediction``)."""
+
+    predictions: "np.ndarray"
+    label_ids: Optional["np.ndarray"]
+
+
+class PredictionOutput(NamedTuple):
+    predictions: "np.ndarray"
+    label_ids: Optional["np.ndarray"]
+    metrics: Optional[Dict[str, float]]
+
+
+class EvalSampler(torch.utils.data.Sampler):
+    """Sequential indices of ONE data rank covering the whole set: global batch b holds examples
+    [b * world * batch, (b + 1) * world * batch), rank r its r-th slice. The last global batch is filled up by wrapping
+    around, so that every rank runs the same number of batches (collectives inside the model stay matched);
+    ``padding_rows(b)`` tells which rows of this rank's batch b are such fill-ins and must not count."""
+
+    def __init__(self, n: int, rank: int, world: int, batch: int):
+        self.n, self.rank, self.world, self.batch = n, rank, world, batch
+        self.num_batches = (n + world * batch - 1) // (world * batch) if n > 0 else 0
+
+    def __len__(self):
+        return self.num_batches * self.batch
+
+    def _positions(self, b: int):
+        base = (b * self.world + self.rank) * self.batch
+        return range(base, base + self.batch)
+
+    def padding_rows(self, b: int):
+        return [i for i, p in enumerate(self._positions(b)) if p >= self.n]
+
+    def __iter__(self):
+        for b in range(self.num_batches):
+            for p in self._positions(b):
+                yield p % self.n
 
 
 def get_last_checkpoint(folder: str, require_complete: bool = True) -> Optional[str]:
