@@ -1020,7 +1020,7 @@ UNSUPPORTED_FAMILIES = {
     "deepseek_v4": "compressed sparse attention",
     "kimi_k3": "delta-rule linear attention with per-channel decay, vision tower", "kimi_linear": "delta-rule linear attention with per-channel decay",
     "kimi_k25": "vision tower", "hyperencoder": "encoder stack of its own",
-    "phi4_multimodal": "vision and audio towers", "molmo": "vision tower with pooled multi-crop features",
+    "molmo": "vision tower with pooled multi-crop features",
     "qwen3_omni_moe": "audio / vision towers",
 }
 

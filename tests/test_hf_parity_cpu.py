@@ -1213,3 +1213,90 @@ def test_ernie4_5_vl_trains_on_a_padded_batch_of_images_of_different_sizes():
         losses.append(out.loss.item())
     assert losses[-1] < losses[0]
     assert all(m.mlp.vision_rows is None for m in model.language.model.layers.values() if hasattr(m.mlp, "vision_rows"))
+
+
+def test_phi4_multimodal_matches_hugging_face(tmp_path):
+    """Image branch (fractional position buckets, partly filled crops, 2 x 2 pooling, row / image separators), audio branch
+    (convolutional time reduction, conformer blocks with relative-position bias, windows of 500 frames for long audio, the two
+    projector sets), placeholders replaced in the prompt, Phi-3 decoder: logits, loss and gradients; checkpoint both ways.
+    Padded audio frames must not influence the valid ones."""
+    from transformers.models.phi4_multimodal.configuration_phi4_multimodal import Phi4MultimodalConfig as HFConfig
+    from transformers.models.phi4_multimodal.modeling_phi4_multimodal import Phi4MultimodalForCausalLM as HFModel
+
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    torch.manual_seed(0)
+    cfg = HFConfig(vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                   num_key_value_heads=2, max_position_embeddings=2048, original_max_position_embeddings=2048, pad_token_id=0,
+                   bos_token_id=1, eos_token_id=2,
+                   vision_config=dict(hidden_size=32, intermediate_size=48, num_hidden_layers=3, num_attention_heads=2, image_size=56,
+                                      patch_size=14, crop_size=56, image_token_id=290),
+                   audio_config=dict(hidden_size=32, intermediate_size=48, num_blocks=2, num_attention_heads=2, ext_pw_out_channel=32,
+                                     depthwise_separable_out_channel=32, input_size=16, nemo_conv_channels=8, nemo_final_size=2,
+                                     time_reduction=8, bias_max_distance=20, audio_token_id=291))
+    for c in (cfg, cfg.vision_config, cfg.audio_config):
+        c._attn_implementation = "eager"
+    hf = HFModel(cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "extensor" in n or n.endswith((".b1", ".b2")) or "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+        for n, b in hf.named_buffers():
+            if "global_mean" in n:
+                b.copy_(torch.randn_like(b) * 0.1)
+            if "global_invstd" in n:
+                b.copy_(torch.rand_like(b) + 0.5)
+    hf.save_pretrained(tmp_path / "hf")
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).eval()
+    # image resized to 56 x 112: global view + 1 x 2 crops of 4 x 4 patches; the right crop shows the image in its two left
+    # patch columns only
+    pix = torch.randn(1, 3, 3, 56, 56)
+    sizes = torch.tensor([[56, 112]])
+    mask = torch.ones(1, 3, 4, 4)
+    mask[0, 2, :, 2:] = 0
+    n_img = 2 * (3 + 1) + 1 + 2 * (2 + 1)            # tiled crops: 2 rows of 3 useful columns + separator; separator; global 2 x (2 + 1)
+    feats = torch.randn(1, 40, 16)
+    n_aud = 5                                         # 40 frames / 8
+    ids = torch.tensor([[5, 6] + [290] * n_img + [7] + [291] * n_aud + [8, 9]])
+    kw = dict(image_pixel_values=pix, image_sizes=sizes, image_attention_mask=mask, audio_input_features=feats,
+              audio_embed_sizes=torch.tensor([n_aud]))
+    with torch.no_grad():
+        want = hf(input_ids=ids, **kw).logits
+        assert (want - mine(ids, **kw).logits).abs().max() < 1e-4
+        # audio only ("speech" projectors), longer than one window of 500 reduced frames
+        long = torch.randn(1, 8 * 520, 16)
+        ids2 = torch.tensor([[5] + [291] * 520 + [8, 9]])
+        a = hf(input_ids=ids2, audio_input_features=long, audio_embed_sizes=torch.tensor([520])).logits
+        b = mine(ids2, audio_input_features=long, audio_embed_sizes=torch.tensor([520])).logits
+        assert (a - b).abs().max() < 1e-4
+        # padding: frames beyond the valid length change nothing in the valid part
+        enc = mine.embed_tokens_extend.audio_embed.encoder
+        x = torch.randn(1, 64, 16)
+        fm = torch.zeros(1, 64, dtype=torch.bool)
+        fm[:, :40] = True
+        y1 = enc(x, fm)
+        x2 = x.clone()
+        x2[:, 48:] = 7.0                               # past the receptive field of the last valid reduced frame
+        y2 = enc(x2, fm)
+        assert (y1[:, :5] - y2[:, :5]).abs().max() < 1e-5 and (y1[:, 6:] - y2[:, 6:]).abs().max() > 1e-6
+    lab = torch.cat([ids[:, 1:], torch.full((1, 1), -100)], dim=1)
+    lab[lab >= 290] = -100
+    hf_lab = ids.clone()
+    hf_lab[hf_lab >= 290] = -100
+    mine.train()
+    out = mine(ids, labels=lab, **kw)
+    out.loss.backward()
+    ref = hf(input_ids=ids, labels=hf_lab, **kw)
+    ref.loss.backward()
+    assert abs(out.loss.item() - ref.loss.item()) < 1e-4
+    pairs = [(mine.embed_tokens_extend.image_embed.sub_img_feature_extensor, hf.model.embed_tokens_extend.image_embed.sub_img_feature_extensor),
+             (mine.embed_tokens_extend.audio_embed.encoder.encoders[0].conv.b1, hf.model.embed_tokens_extend.audio_embed.encoder.encoders[0].conv.glu.b1),
+             (mine.embed_tokens_extend.image_embed.img_processor.position_embedding.weight,
+              hf.model.embed_tokens_extend.image_embed.img_processor.embeddings.position_embedding.weight)]
+    for a, b in pairs:
+        assert a.grad.abs().sum() > 0 and (a.grad - b.grad).abs().max() < 1e-4 * max(1.0, b.grad.abs().max().item())
+    mine.eval()
+    mine.save_pretrained(str(tmp_path / "mine"))
+    back = HFModel.from_pretrained(tmp_path / "mine").eval()
+    with torch.no_grad():
+        assert (back(input_ids=ids, **kw).logits - want).abs().max() < 1e-5
