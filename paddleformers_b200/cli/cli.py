@@ -1,4 +1,4 @@
-"""``paddleformers-b200 {train|export|version|help}``: the user-facing command.
+"""``paddleformers-b200 {train|export|merge|preprocess|ckpt|env|version|help}``: the user-facing command.
 
 ``train cfg.yaml [key=value ...]`` starts one process per visible GPU with ``torch.distributed.run`` (rendezvous on
 MASTER_ADDR / 127.0.0.1), optionally under ``numactl`` binding, and kills the whole process tree if any rank fails;
@@ -19,6 +19,11 @@ USAGE = """usage: paddleformers-b200 <command> [args]
 commands:
   train  <config.yaml|json> [key=value ...]   run a training stage (SFT | PT | DPO | VL-SFT | VL-PT | VL-DPO | recipes; with or without LoRA)
   export <config.yaml|json> [key=value ...]   merge LoRA adapters into the base model and write an HF checkpoint
+  merge  <config.yaml|json> [key=value ...]   merge several checkpoints of one architecture (linear | slerp | ties, with
+                                              dare / magprune / trim sparsification of the task vectors)
+  preprocess --input F --tokenizer DIR --output-prefix P [...]   tokenise raw text into the .bin / .idx corpus format
+  ckpt   inspect|reshard ...                  look into a training checkpoint, or re-cut its optimizer shards
+  env                                         versions, GPUs and the state of the compiled extension
   version                                     print the package version
   help                                        this text
 """
@@ -94,6 +99,37 @@ def export(argv: List[str]) -> int:
     return 0
 
 
+def merge(argv: List[str]) -> int:
+    """``merge cfg.yaml [key=value ...]``: the fields of ``mergekit.MergeConfig`` from a YAML / JSON file and overrides
+    (paddleformers/mergekit/merge_model.py, examples/tools/merge.py)."""
+    import dataclasses
+    import json
+
+    from ..mergekit.merge import MergeConfig, MergeModel
+
+    cfg = {}
+    for a in argv:
+        if "=" in a and not os.path.exists(a):
+            k, v = a.split("=", 1)
+            try:
+                cfg[k] = json.loads(v)
+            except json.JSONDecodeError:
+                cfg[k] = v
+        elif a.endswith((".yaml", ".yml")):
+            import yaml
+
+            cfg.update(yaml.safe_load(open(a)) or {})
+        else:
+            cfg.update(json.load(open(a)))
+    known = {f.name for f in dataclasses.fields(MergeConfig)}
+    unknown = sorted(set(cfg) - known)
+    if unknown:
+        raise ValueError(f"unknown merge options {unknown}; known: {sorted(known)}")
+    out = MergeModel(MergeConfig(**cfg)).merge()
+    print(f"merged model written to {out}")
+    return 0
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     if not argv or argv[0] in ("help", "-h", "--help"):
@@ -109,6 +145,23 @@ def main(argv: Optional[List[str]] = None) -> int:
         return train(rest)
     if cmd == "export":
         return export(rest)
+    if cmd == "merge":
+        return merge(rest)
+    if cmd == "preprocess":
+        from ..data.preprocess import main as preprocess_main
+
+        return preprocess_main(rest) or 0
+    if cmd == "ckpt":
+        from ..trainer.ckpt_converter import main as ckpt_main
+
+        return ckpt_main(rest)
+    if cmd == "env":
+        import json
+
+        from ..utils.env_report import collect
+
+        print(json.dumps(collect(), indent=2, default=str))
+        return 0
     print(f"unknown command {cmd!r}\n\n{USAGE}", file=sys.stderr)
     return 2
 

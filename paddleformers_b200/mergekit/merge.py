@@ -28,6 +28,7 @@ class MergeConfig:
     output_path: str = "./merged"
     seed: int = 0
     rescale: bool = True
+    max_shard_size_gb: float = 5.0          # output files are cut at this size; several files come with an index
 
 
 def sparsify(delta: torch.Tensor, kind: Optional[str], keep: float, gen: torch.Generator, rescale: bool = True) -> torch.Tensor:
@@ -97,11 +98,24 @@ class MergeModel:
         gen = torch.Generator().manual_seed(cfg.seed)
         os.makedirs(cfg.output_path, exist_ok=True)
         out: Dict[str, torch.Tensor] = {}
+        shards: List[Dict[str, str]] = []          # one {tensor name: file} map per written file
+        limit = int(cfg.max_shard_size_gb * (1 << 30))
+        held = 0
+
+        def flush():
+            nonlocal out, held
+            if out:
+                fname = f"model-{len(shards) + 1:05d}.safetensors"
+                save_file(out, os.path.join(cfg.output_path, fname), metadata={"format": "pt"})
+                shards.append({k: fname for k in out})
+                out, held = {}, 0
+
         for name in sorted(readers[0].keys()):
             ts = [r.get(name) for r in readers]
             dtype = ts[0].dtype
             if not ts[0].is_floating_point():
                 out[name] = ts[0]
+                held += ts[0].numel() * ts[0].element_size()
                 continue
             if cfg.merge_method == "linear":
                 if cfg.sparsify_type and base is not None:
@@ -117,7 +131,23 @@ class MergeModel:
             else:
                 raise ValueError(cfg.merge_method)
             out[name] = m.to(dtype).contiguous()
-        save_file(out, os.path.join(cfg.output_path, "model.safetensors"), metadata={"format": "pt"})
+            held += out[name].numel() * out[name].element_size()
+            if held >= limit:                      # only one output file's worth of merged tensors is alive at a time
+                flush()
+        flush()
+        if len(shards) == 1:
+            os.replace(os.path.join(cfg.output_path, "model-00001.safetensors"), os.path.join(cfg.output_path, "model.safetensors"))
+        else:
+            total = len(shards)
+            weight_map = {}
+            for i, m in enumerate(shards):
+                final = f"model-{i + 1:05d}-of-{total:05d}.safetensors"
+                os.replace(os.path.join(cfg.output_path, f"model-{i + 1:05d}.safetensors"), os.path.join(cfg.output_path, final))
+                weight_map.update({k: final for k in m})
+            import json
+
+            with open(os.path.join(cfg.output_path, "model.safetensors.index.json"), "w") as f:
+                json.dump({"metadata": {}, "weight_map": weight_map}, f, indent=2, sort_keys=True)
         for fn in os.listdir(cfg.model_path_list[0]):
             if fn.endswith(".json") and "index" not in fn or fn.startswith("tokenizer") or fn.endswith(".model"):
                 shutil.copy(os.path.join(cfg.model_path_list[0], fn), os.path.join(cfg.output_path, fn))

@@ -257,6 +257,11 @@ def test_example_configs_parse(monkeypatch):
     assert len(files) >= 8
     for f in files:
         flat = read_args([f])
+        if os.path.basename(f).startswith("merge"):
+            from paddleformers_b200.mergekit.merge import MergeConfig
+
+            assert set(flat) <= {x.name for x in __import__("dataclasses").fields(MergeConfig)}, f
+            continue
         if "export" in os.path.basename(f):
             from paddleformers_b200.cli.hparams import ExportArguments
 
@@ -535,3 +540,38 @@ def test_per_operation_recompute_counts_become_refined_recompute():
     assert out == {"refined_recompute": {"flash_attn": 0, "mlp_row_ln": 2}, "recompute_granularity": "full"}
     keep = translate({"recompute_modules": ["attn"], "recompute_granularity": "selective"}, {"recompute_modules", "recompute_granularity"})
     assert keep["recompute_modules"] == ["attn"]
+
+
+def test_merge_preprocess_ckpt_and_env_commands(tmp_path, capsys):
+    """``merge``: two checkpoints averaged into several output files with an index that loads back; unknown options refused.
+    ``env`` prints the report; ``preprocess`` and ``ckpt`` reach their tools."""
+    from paddleformers_b200.cli.cli import main
+    from paddleformers_b200.models.configuration import named_config
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+    from paddleformers_b200.transformers.auto import AutoModelForCausalLM
+
+    cfg = named_config("tiny-llama", num_hidden_layers=2, hidden_size=32, intermediate_size=48, num_attention_heads=2,
+                       num_key_value_heads=2, head_dim=16, vocab_size=64)
+    models = []
+    for i in range(2):
+        torch.manual_seed(i)
+        m = MODEL_MAPPING[cfg.model_type](cfg)
+        m.save_pretrained(str(tmp_path / f"m{i}"))
+        models.append(m)
+    spec = tmp_path / "merge.json"
+    spec.write_text(json.dumps({"merge_method": "linear", "model_path_list": [str(tmp_path / "m0"), str(tmp_path / "m1")],
+                                "weight_list": [0.25, 0.75], "output_path": str(tmp_path / "merged")}))
+    assert main(["merge", str(spec), "max_shard_size_gb=0.00001"]) == 0          # ~10 KB per file: several files + index
+    files = sorted(os.listdir(tmp_path / "merged"))
+    assert "model.safetensors.index.json" in files and sum(f.endswith(".safetensors") for f in files) > 1
+    merged = AutoModelForCausalLM.from_pretrained(str(tmp_path / "merged"), dtype=torch.float32)
+    a, b = (dict(m.named_parameters()) for m in models)
+    for n, p in merged.named_parameters():
+        assert torch.allclose(p, 0.25 * a[n] + 0.75 * b[n], atol=1e-6), n
+    with pytest.raises(ValueError, match="unknown merge options"):
+        main(["merge", str(spec), "blend=1"])
+    capsys.readouterr()
+    assert main(["env"]) == 0
+    assert "torch" in capsys.readouterr().out
+    with pytest.raises(SystemExit):
+        main(["preprocess", "--help"])
