@@ -39,6 +39,7 @@ _LAZY = {
     "Qwen3VLForConditionalGeneration": ".models.vision_language", "Qwen3VLMoeForConditionalGeneration": ".models.vision_language",
     "Glm4vMoeForConditionalGeneration": ".models.vision_language", "FullyShardedOptimizer": ".parallel.fsdp",
     "Gemma4ForCausalLM": ".models.gemma4", "Gemma4TextConfig": ".models.gemma4",
+    "MolmoForCausalLM": ".models.molmo", "MolmoConfig": ".models.molmo",
     "Phi4MultimodalForCausalLM": ".models.phi4_multimodal", "Phi4MultimodalConfig": ".models.phi4_multimodal",
     "Ernie4_5VLForConditionalGeneration": ".models.ernie4_5_vl", "Ernie4_5VLConfig": ".models.ernie4_5_vl",
 }

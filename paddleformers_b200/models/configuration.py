@@ -1017,11 +1017,16 @@ CONFIG_MAPPING = {c.model_type: c for c in (Ernie4_5Config, Ernie4_5MoeConfig, Q
 # Families of the reference's registry (paddleformers/transformers/auto/modeling.py:55-112) whose blocks need a
 # feature the unified decoder does not have; the Auto classes name the missing piece instead of failing on a key error.
 UNSUPPORTED_FAMILIES = {
-    "deepseek_v4": "compressed sparse attention",
-    "kimi_k3": "delta-rule linear attention with per-channel decay, vision tower", "kimi_linear": "delta-rule linear attention with per-channel decay",
-    "kimi_k25": "vision tower", "hyperencoder": "encoder stack of its own",
-    "molmo": "vision tower with pooled multi-crop features",
-    "qwen3_omni_moe": "audio / vision towers",
+    # the reference holds a configuration and a checkpoint name map for these; the layers themselves come from its external
+    # PaddleFleet package
+    "deepseek_v4": "compressed sparse attention (the reference builds the layers from an external package)",
+    "kimi_k3": "delta-rule linear attention with per-channel decay and block attention residuals (the reference builds the "
+               "layers from an external package)",
+    "kimi_linear": "delta-rule linear attention with per-channel decay",
+    "hyperencoder": "an encoder stack of its own (the reference builds the layers from an external package)",
+    # the reference ships processors only for these; AutoProcessor hands them to the `transformers` package
+    "kimi_k25": "a vision tower (the reference ships its processor only)",
+    "qwen3_omni_moe": "audio / vision towers (the reference ships its processor only)",
 }
 
 

@@ -187,6 +187,7 @@ class Attention(nn.Module):
         self.o_proj = _linear(self.Hq_total * self.D, H, bool(getattr(config, "attention_out_bias", False)), "rowwise", config,
                               dtype=dtype, device=device)
         self.use_qk_norm = config.use_qk_norm
+        self.clip_qkv = float(getattr(config, "clip_qkv", 0.0) or 0.0)          # projections clamped to [-c, c] (Molmo / OLMo)
         self.qk_norm_full = bool(getattr(config, "qk_norm_full", False))      # one RMSNorm over all heads' features (OLMo2)
         if self.qk_norm_full:
             assert tp == 1, "full-width QK norm is implemented for tensor-parallel degree 1"
@@ -233,6 +234,8 @@ class Attention(nn.Module):
             qkv = torch.cat([qg[..., :self.D].reshape(x2d.shape[0], self.Hq * self.D), _apply(self.k_proj, x2d), _apply(self.v_proj, x2d)], dim=-1)
         else:
             qkv = keep("attention_column_ln", _apply, self.qkv_proj, x2d)
+        if self.clip_qkv:
+            qkv = qkv.clamp(-self.clip_qkv, self.clip_qkv)
         kend = ctx.kend_window if ((self.window or self.chunk) and ctx.kend_window is not None) else ctx.kend
         cos, sin = (ctx.cos_local, ctx.sin_local) if (self.local_rope and ctx.cos_local is not None) else (ctx.cos, ctx.sin)
         if self.qk_norm_full:

@@ -1300,3 +1300,129 @@ def test_phi4_multimodal_matches_hugging_face(tmp_path):
     back = HFModel.from_pretrained(tmp_path / "mine").eval()
     with torch.no_grad():
         assert (back(input_ids=ids, **kw).logits - want).abs().max() < 1e-5
+
+
+def test_molmo_decoder_and_tower_against_olmo2_and_clip_oracles(tmp_path):
+    """No other implementation of Molmo is at hand, so its parts are checked against the models they are built from: the
+    decoder (norms after the branches, full-width QK norm, fused [q | k | v] and [up | gate] projections, extended embedding
+    table, head over the base table) against ``transformers``' OLMo 2 through a checkpoint written in Molmo's tensor names; the
+    image tower against ``transformers``' CLIP vision encoder; pooling, padding embeddings and the scatter-add into the token
+    embeddings against a direct restatement."""
+    from safetensors.torch import save_file
+    from transformers import CLIPVisionConfig, CLIPVisionModel, Olmo2Config, Olmo2ForCausalLM
+
+    from paddleformers_b200.models.molmo import MolmoConfig, MolmoForCausalLM
+
+    torch.manual_seed(0)
+    E, A, H, I, L = 96, 8, 64, 80, 2
+    hf = Olmo2ForCausalLM(Olmo2Config(vocab_size=E, hidden_size=H, intermediate_size=I, num_hidden_layers=L, num_attention_heads=4,
+                                      num_key_value_heads=2, max_position_embeddings=128, rope_theta=10000.0, rms_norm_eps=1e-6,
+                                      tie_word_embeddings=False, pad_token_id=0)).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    clip = CLIPVisionModel(CLIPVisionConfig(hidden_size=32, intermediate_size=48, num_hidden_layers=4, num_attention_heads=2,
+                                            image_size=28, patch_size=14, hidden_act="quick_gelu", layer_norm_eps=1e-5)).eval()
+    sd, T, V = {}, "model.transformer.", "model.vision_backbone."
+    hs = hf.state_dict()
+    sd[T + "wte.embedding"] = hs["model.embed_tokens.weight"]
+    sd[T + "wte.new_embedding"] = torch.randn(A, H) * 0.02
+    sd[T + "ln_f.weight"] = hs["model.norm.weight"]
+    sd[T + "ff_out.weight"] = hs["lm_head.weight"]
+    for i in range(L):
+        a, b = f"model.layers.{i}.", f"{T}blocks.{i}."
+        sd[b + "att_proj.weight"] = torch.cat([hs[a + f"self_attn.{x}_proj.weight"] for x in "qkv"], dim=0)
+        sd[b + "attn_out.weight"] = hs[a + "self_attn.o_proj.weight"]
+        sd[b + "ff_proj.weight"] = torch.cat([hs[a + "mlp.up_proj.weight"], hs[a + "mlp.gate_proj.weight"]], dim=0)
+        sd[b + "ff_out.weight"] = hs[a + "mlp.down_proj.weight"]
+        sd[b + "attn_norm.weight"] = hs[a + "post_attention_layernorm.weight"]
+        sd[b + "ff_norm.weight"] = hs[a + "post_feedforward_layernorm.weight"]
+        sd[b + "q_norm.weight"], sd[b + "k_norm.weight"] = hs[a + "self_attn.q_norm.weight"], hs[a + "self_attn.k_norm.weight"]
+    cs = clip.state_dict()
+    pre = "vision_model."
+    sd[V + "image_vit.class_embedding"] = cs[pre + "embeddings.class_embedding"]
+    sd[V + "image_vit.positional_embedding"] = cs[pre + "embeddings.position_embedding.weight"]
+    sd[V + "image_vit.patch_embedding.weight"] = cs[pre + "embeddings.patch_embedding.weight"].permute(0, 2, 3, 1).reshape(32, -1)
+    sd[V + "image_vit.pre_ln.weight"], sd[V + "image_vit.pre_ln.bias"] = cs[pre + "pre_layrnorm.weight"], cs[pre + "pre_layrnorm.bias"]
+    for i in range(4):
+        a, b = f"{pre}encoder.layers.{i}.", f"{V}image_vit.transformer.resblocks.{i}."
+        for mine, theirs in (("attention.wq", "self_attn.q_proj"), ("attention.wk", "self_attn.k_proj"), ("attention.wv", "self_attn.v_proj"),
+                             ("attention.wo", "self_attn.out_proj"), ("feed_forward.w1", "mlp.fc1"), ("feed_forward.w2", "mlp.fc2"),
+                             ("attention_norm", "layer_norm1"), ("ffn_norm", "layer_norm2")):
+            for leaf in ("weight", "bias"):
+                sd[b + f"{mine}.{leaf}"] = cs[a + f"{theirs}.{leaf}"]
+    cfg = MolmoConfig(vocab_size=E - 6, embedding_size=E, hidden_size=H, intermediate_size=2 * I, num_hidden_layers=L, num_attention_heads=4,
+                      num_key_value_heads=2, additional_vocab_size=A, max_position_embeddings=128, rope_theta=10000.0, layer_norm_eps=1e-6,
+                      vision_backbone=dict(image_default_input_size=(28, 28), image_patch_size=14, image_emb_dim=32, image_num_heads=2,
+                                           image_num_key_value_heads=2, image_num_layers=4, image_head_dim=16, image_mlp_dim=48,
+                                           image_num_pos=5, image_norm_eps=1e-5), vit_layers=(-1, -3))
+    mine = MolmoForCausalLM(cfg, dtype=torch.float32)
+    for n, p in mine.model.vision_backbone.named_parameters():            # pooling, projector, padding embeddings: random
+        if ("model.vision_backbone." + n) not in sd:
+            sd["model.vision_backbone." + n] = torch.randn_like(p) * 0.1
+    ck = tmp_path / "molmo"
+    ck.mkdir()
+    save_file({k: v.contiguous() for k, v in sd.items()}, str(ck / "model.safetensors"))
+    cfg.save_pretrained(str(ck))
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    mine = AutoModelForConditionalGeneration.from_pretrained(str(ck), dtype=torch.float32).eval()
+    assert type(mine).__name__ == "MolmoForCausalLM"
+    ids = torch.randint(0, E, (2, 14))
+    with torch.no_grad():
+        assert (hf(input_ids=ids).logits - mine(ids).logits).abs().max() < 1e-4          # decoder, text only
+        extra = mine(torch.tensor([[E + 3, 5, 6]])).logits                                # a row of the extra table is reachable
+        assert extra.shape == (1, 3, E)
+        # tower: every block's output equals the CLIP encoder's hidden states
+        img = torch.randn(3, 3, 28, 28)
+        patches = img.reshape(3, 3, 2, 14, 2, 14).permute(0, 2, 4, 3, 5, 1).reshape(3, 4, 14 * 14 * 3)
+        outs = mine.model.vision_backbone.image_vit(patches, (2, 2))
+        want = clip(pixel_values=img, output_hidden_states=True).hidden_states
+        for i in range(4):
+            assert (outs[i] - want[i + 1]).abs().max() < 1e-4
+        # backbone after the tower, restated directly
+        vb = mine.model.vision_backbone
+        images = patches.reshape(1, 3, 4, -1).clone()
+        images[0, 2] = -1                                                                 # an unused crop
+        masks = torch.ones(1, 3, 4)
+        masks[0, 1, 2:] = 0.0
+        masks[0, 1, 1] = 0.25
+        got = vb(images, masks)
+        feats = torch.cat([outs[-1], outs[-3]], dim=-1)[:, 1:].clone()
+        feats[2] = 0
+        feats = feats + vb.pad_embed[0] * (masks[0] == 0)[..., None] + vb.pad_embed[1] * ((masks[0] < 1) & (masks[0] > 0))[..., None]
+        rows = []
+        for c in range(3):
+            blk = feats[c]                                                                # 2 x 2 patches = one pooled row
+            q = blk.mean(0, keepdim=True)
+            pa = vb.image_pooling_2d
+            qh = pa.wq(q).view(1, 2, 16).transpose(0, 1)
+            kh, vh = pa.wk(blk).view(4, 2, 16).transpose(0, 1), pa.wv(blk).view(4, 2, 16).transpose(0, 1)
+            att = torch.softmax(qh @ kh.transpose(1, 2) / 4.0, dim=-1) @ vh
+            o = pa.wo(att.transpose(0, 1).reshape(1, 32))
+            pr = vb.image_projector
+            rows.append(pr["w2"](torch.nn.functional.silu(pr["w1"](o)) * pr["w3"](o)))
+        assert (got[0, :, 0] - torch.cat(rows)).abs().max() < 1e-5
+        # the rows are added at image_input_idx; -1 rows are ignored
+        idx = torch.tensor([[[3], [7], [-1]]])
+        base = mine.language.model.embed(ids[:1]).clone()
+        with_img = mine(ids[:1], images=images, image_masks=masks, image_input_idx=idx).logits
+        h = base.clone()
+        h[3] += got[0, 0, 0]
+        h[7] += got[0, 1, 0]
+        lm = mine.language
+        ctx = lm.model.make_context(ids[:1])
+        hid, res = lm.model.run_layers(h, None, ctx)
+        hid = lm.model.norm(hid, res)[0] if res is not None else lm.model.norm(hid)
+        assert (with_img[0] - torch.nn.functional.linear(hid, mine.head_weight())).abs().max() < 1e-5
+    mine.train()
+    out = mine(ids[:1], images=images, image_masks=masks, image_input_idx=idx, labels=ids[:1])
+    out.loss.backward()
+    assert mine.model.vision_backbone.pad_embed.grad.abs().sum() > 0 and mine.lm_head.weight.grad.abs().sum() > 0
+    mine.save_pretrained(str(tmp_path / "again"))
+    from safetensors import safe_open
+
+    with safe_open(str(tmp_path / "again" / "model.safetensors"), "pt") as f:
+        assert set(f.keys()) == set(sd) and torch.equal(f.get_tensor(T + "blocks.1.ff_proj.weight"), sd[T + "blocks.1.ff_proj.weight"])
+        assert f.get_tensor(T + "wte.new_embedding").shape == (A, H)
