@@ -1022,7 +1022,6 @@ UNSUPPORTED_FAMILIES = {
     "deepseek_v4": "compressed sparse attention (the reference builds the layers from an external package)",
     "kimi_k3": "delta-rule linear attention with per-channel decay and block attention residuals (the reference builds the "
                "layers from an external package)",
-    "kimi_linear": "delta-rule linear attention with per-channel decay",
     "hyperencoder": "an encoder stack of its own (the reference builds the layers from an external package)",
     # the reference ships processors only for these; AutoProcessor hands them to the `transformers` package
     "kimi_k25": "a vision tower (the reference ships its processor only)",
@@ -1053,7 +1052,7 @@ def resolve_config_class(model_type: str):
         raise NotImplementedError(f"model_type {model_type!r} is known but not implemented: it needs {UNSUPPORTED_FAMILIES[model_type]}")
     raise ValueError(f"unknown model_type {model_type!r}; supported: {sorted(CONFIG_MAPPING)}")
 # families whose architecture is a strict subset of an implemented one load through it
-CONFIG_MAPPING.update({"glm4": Glm4Config, "minicpm4_1": MiniCPM4_1Config, "qwen3_5": Qwen3_5TextConfig, "qwen3_5_moe": Qwen3_5MoeTextConfig, "kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV2Config, "glm4_moe_lite": Glm4MoeLiteConfig, "glm_moe_dsa": GlmMoeDsaConfig, "deepseek_v32": DeepseekV32Config, "phi4": Phi3Config})
+CONFIG_MAPPING.update({"glm4": Glm4Config, "minicpm4_1": MiniCPM4_1Config, "qwen3_5": Qwen3_5TextConfig, "qwen3_5_moe": Qwen3_5MoeTextConfig, "kimi_k2": DeepseekV3Config, "deepseek_v2": DeepseekV2Config, "glm4_moe_lite": Glm4MoeLiteConfig, "glm_moe_dsa": GlmMoeDsaConfig, "deepseek_v32": DeepseekV32Config, "phi4": Phi3Config, "phi4flash": Phi3Config})
 
 
 def named_config(name: str, **overrides) -> DecoderConfig:

@@ -1181,7 +1181,7 @@ class _ModelMapping(dict):
 
 
 MODEL_MAPPING = _ModelMapping({
-    "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM,
+    "llama": LlamaForCausalLM, "mistral": MistralForCausalLM, "phi3": Phi3ForCausalLM, "phi4": Phi3ForCausalLM, "phi4flash": Phi3ForCausalLM,
     "qwen2_moe": Qwen2MoeForCausalLM, "granite": GraniteForCausalLM, "minicpm": MiniCPMForCausalLM, "minicpm4_1": MiniCPM4_1ForCausalLM, "glm4": Glm4ForCausalLM, "olmo2": Olmo2ForCausalLM, "gemma": GemmaForCausalLM, "gemma2": Gemma2ForCausalLM, "gemma3_text": Gemma3ForCausalLM, "cohere": CohereForCausalLM, "cohere2": Cohere2ForCausalLM,
     "stablelm": StableLmForCausalLM, "hunyuan_v1_dense": HunYuanDenseV1ForCausalLM, "hunyuan_v1_moe": HunYuanMoEV1ForCausalLM, "minimax_m2": MiniMaxM2ForCausalLM, "minimax": MiniMaxForCausalLM, "diffllama": DiffLlamaForCausalLM, "mixtral": MixtralForCausalLM, "minicpm3": MiniCPM3ForCausalLM, "internlm2": InternLM2ForCausalLM, "gpt_oss": GptOssForCausalLM, "llama4_text": Llama4ForCausalLM, "qwen3_next": Qwen3NextForCausalLM, "qwen3_5_text": Qwen3_5ForCausalLM, "qwen3_5_moe_text": Qwen3_5MoeForCausalLM,
     "qwen3_5": Qwen3_5ForCausalLM, "qwen3_5_moe": Qwen3_5MoeForCausalLM,

@@ -467,3 +467,40 @@ class Phi4MultimodalForCausalLM(PretrainedModel):
                 src = aud + name[len("audio_embed."):]
             rules.append(Rule("embed_tokens_extend." + name, [src]))
         return WeightMap(rules)
+
+
+class Phi4MultimodalProcessor:
+    """Prompt + images + audio clips -> model inputs: every image tag of the prompt is repeated once per feature row of the
+    corresponding image, every audio tag once per row of the corresponding clip (the job of
+    paddleformers/transformers/phi4_multimodal/processor.py). ``tokenizer`` must map ``image_token`` / ``audio_token`` to the
+    placeholder ids of the model configuration."""
+
+    def __init__(self, tokenizer, image_processor=None, audio_processor=None, image_token: str = "<|image|>", audio_token: str = "<|audio|>"):
+        from ..transformers.audio_processing import KaldiFbankFeatureExtractor
+        from ..transformers.image_processing import DynamicHDImageProcessor
+
+        self.tokenizer = tokenizer
+        self.image_processor = image_processor or DynamicHDImageProcessor()
+        self.audio_processor = audio_processor or KaldiFbankFeatureExtractor()
+        self.image_token, self.audio_token = image_token, audio_token
+
+    def __call__(self, text: str, images=None, audio=None, sampling_rate: Optional[int] = None) -> dict:
+        import re
+
+        out = {}
+        counts = {self.image_token: [], self.audio_token: []}
+        if images is not None:
+            pre = self.image_processor(list(images))
+            counts[self.image_token] = list(pre.pop("num_img_tokens"))
+            out.update(pre)
+        if audio is not None:
+            pre = self.audio_processor(list(audio), sampling_rate=sampling_rate)
+            counts[self.audio_token] = [int(n) for n in pre["audio_embed_sizes"]]
+            out.update(pre)
+        for tag, per in counts.items():
+            if text.count(tag) != len(per):
+                raise ValueError(f"the prompt has {text.count(tag)} {tag} tags for {len(per)} inputs of that kind")
+            it = iter(per)
+            text = re.sub(re.escape(tag), lambda _m, tag=tag, it=it: tag * next(it), text)
+        out["input_ids"] = torch.tensor([self.tokenizer.encode(text, add_special_tokens=False)])
+        return out

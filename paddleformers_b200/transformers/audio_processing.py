@@ -94,3 +94,71 @@ class LogMelFeatureExtractor:
 
 
 WhisperFeatureExtractor = LogMelFeatureExtractor
+
+
+def kaldi_mel_filter_bank(num_frequency_bins: int, num_mel_filters: int, min_frequency: float, max_frequency: float,
+                          sampling_rate: int) -> torch.Tensor:
+    """[num_frequency_bins, num_mel_filters] triangular filters on the Kaldi (HTK-formula) mel scale, mel = 1127 ln(1 + f / 700),
+    with the triangles drawn in MEL space (a bin's weight is linear in its mel value, not in its frequency) and no area
+    normalisation: the filter bank of Kaldi-compatible front ends."""
+    def to_mel(f):
+        return 1127.0 * torch.log(1.0 + f / 700.0)
+
+    edges = torch.linspace(float(to_mel(torch.tensor(float(min_frequency), dtype=torch.float64))),
+                           float(to_mel(torch.tensor(float(max_frequency), dtype=torch.float64))), num_mel_filters + 2, dtype=torch.float64)
+    bins = to_mel(torch.linspace(0, sampling_rate // 2, num_frequency_bins, dtype=torch.float64))          # bin centres in mel
+    widths = edges[1:] - edges[:-1]
+    slopes = edges[None, :] - bins[:, None]
+    down, up = -slopes[:, :-2] / widths[:-1], slopes[:, 2:] / widths[1:]
+    return torch.clamp(torch.minimum(down, up), min=0.0).to(torch.float32)
+
+
+class KaldiFbankFeatureExtractor:
+    """Log-mel features of the Phi-4-multimodal audio branch (paddleformers/transformers/phi4_multimodal/feature_extraction.py):
+    25 ms frames every 10 ms without padding at the edges, per-frame pre-emphasis (the first sample of a frame is paired with
+    its successor), 16-bit amplitude scale, symmetric Hamming window, 512-point power spectrum, 80 Kaldi-scale mel filters up
+    to 7690 Hz, natural log floored at 0. ``extractor(waveforms)`` returns ``audio_input_features`` [B, frames, 80],
+    ``audio_embed_sizes`` [B] (placeholders per clip: frames / compression rate, rounded up, then / downsample rate, rounded
+    up) and, for a batch of clips of different lengths, ``audio_attention_mask`` [B, frames]."""
+
+    def __init__(self, feature_size: int = 80, sampling_rate: int = 16000, hop_length: int = 160, n_fft: int = 512,
+                 win_length: int = 400, preemphasis: float = 0.97, audio_compression_rate: int = 8, audio_downsample_rate: int = 1,
+                 audio_feat_stride: int = 1, mel_min_frequency: float = 0.0, mel_max_frequency: float = 7690.0, **unused):
+        self.feature_size, self.sampling_rate, self.hop_length, self.n_fft, self.win_length = feature_size, sampling_rate, hop_length, n_fft, win_length
+        self.preemphasis, self.rate, self.down, self.stride = preemphasis, audio_compression_rate, audio_downsample_rate, audio_feat_stride
+        self.mel_filters = kaldi_mel_filter_bank(n_fft // 2 + 1, feature_size, mel_min_frequency, mel_max_frequency, sampling_rate)
+
+    @classmethod
+    def from_pretrained(cls, path: str):
+        with open(os.path.join(path, "preprocessor_config.json")) as f:
+            return cls(**json.load(f))
+
+    def num_frames(self, num_samples: int) -> int:
+        return ((num_samples - self.win_length) // self.hop_length + 1) * self.stride
+
+    def num_placeholders(self, frames: int) -> int:
+        return -(-(-(-frames // self.rate)) // self.down)
+
+    def features(self, wave: torch.Tensor) -> torch.Tensor:
+        """wave [samples] -> [frames, feature_size]."""
+        frames = wave.to(torch.float32).unfold(-1, self.win_length, self.hop_length)
+        prev = torch.roll(frames, 1, dims=-1)
+        prev[:, 0] = prev[:, 1]
+        frames = (frames - self.preemphasis * prev) * 32768
+        window = torch.hamming_window(self.win_length, periodic=False, dtype=torch.float64, device=wave.device)
+        spec = torch.fft.rfft(window * frames, n=self.n_fft, dim=1).to(torch.complex64).abs() ** 2
+        return torch.log(torch.clamp(spec @ self.mel_filters.to(wave.device), min=1.0))
+
+    def __call__(self, raw_speech, sampling_rate: int = None, **unused) -> Dict[str, torch.Tensor]:
+        if sampling_rate is not None and sampling_rate != self.sampling_rate:
+            raise ValueError(f"expected audio sampled at {self.sampling_rate} Hz, got {sampling_rate}")
+        clips = raw_speech if isinstance(raw_speech, (list, tuple)) else (list(raw_speech) if getattr(raw_speech, "ndim", 1) > 1 else [raw_speech])
+        feats = [self.features(torch.as_tensor(np.asarray(c) if not isinstance(c, torch.Tensor) else c)) for c in clips]
+        n = torch.tensor([f.shape[0] for f in feats])
+        out = torch.zeros(len(feats), int(n.max()), self.feature_size)
+        for i, f in enumerate(feats):
+            out[i, :f.shape[0]] = f
+        data = {"audio_input_features": out, "audio_embed_sizes": torch.tensor([self.num_placeholders(int(x)) for x in n])}
+        if len(feats) > 1:
+            data["audio_attention_mask"] = torch.arange(int(n.max()))[None] < n[:, None]
+        return data

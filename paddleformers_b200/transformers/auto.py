@@ -68,6 +68,7 @@ class AutoModelForConditionalGeneration:
 
         table = {"molmo": (MolmoConfig, MolmoForCausalLM),
                  "phi4_multimodal": (Phi4MultimodalConfig, Phi4MultimodalForCausalLM),
+                 "phi4mm": (Phi4MultimodalConfig, Phi4MultimodalForCausalLM),
                  "ernie4_5_vl_moe": (Ernie4_5VLConfig, Ernie4_5VLForConditionalGeneration),
                  "ernie4_5_moe_vl": (Ernie4_5VLConfig, Ernie4_5VLForConditionalGeneration),      # the reference's spelling
                  "llama4": (Llama4Config, Llama4ForConditionalGeneration),

@@ -176,3 +176,73 @@ class SiglipImageProcessor:
                                                 antialias=True).clamp(0.0, 255.0)
             out.append((t * self.rescale_factor - mean) / std)
         return {"pixel_values": torch.cat(out, dim=0)}
+
+
+class DynamicHDImageProcessor:
+    """Image pre-processing of Phi-4-multimodal (paddleformers/transformers/phi4_multimodal/image_processor.py): the image
+    is scaled (keeping its aspect ratio) into a grid of ``crop`` x ``crop`` tiles - as many as it covers, at most ``dynamic_hd``,
+    otherwise the grid whose aspect ratio is closest - and padded with white on the right / bottom; a bicubic down-scale of the
+    padded picture to one tile is the global view. Returns, per image: ``image_pixel_values`` [1 + tiles, 3, crop, crop] (global
+    view first, pixels in [-1, 1]), ``image_attention_mask`` [1 + tiles, crop / patch, crop / patch] (0 on patches that are
+    padding only), ``image_sizes`` (height, width of the padded picture) and the number of placeholder tokens the image needs;
+    a batch is padded to the largest tile count."""
+
+    def __init__(self, crop: int = 448, patch_size: int = 14, dynamic_hd: int = 36, image_mean=(0.5, 0.5, 0.5), image_std=(0.5, 0.5, 0.5)):
+        self.crop, self.patch, self.max_tiles = crop, patch_size, dynamic_hd
+        self.mean = torch.tensor(image_mean, dtype=torch.float32).view(3, 1, 1)
+        self.std = torch.tensor(image_std, dtype=torch.float32).view(3, 1, 1)
+
+    def grid(self, height: int, width: int):
+        """(tile columns, tile rows)."""
+        wc, hc = math.ceil(width / self.crop), math.ceil(height / self.crop)
+        if wc * hc <= self.max_tiles:
+            return wc, hc
+        aspect, area = width / height, width * height
+        best, best_diff = (1, 1), float("inf")
+        cands = sorted({(i, j) for i in range(1, self.max_tiles + 1) for j in range(1, self.max_tiles + 1) if i * j <= self.max_tiles},
+                       key=lambda x: x[0] * x[1])
+        for i, j in cands:
+            diff = abs(aspect - i / j)
+            if diff < best_diff:
+                best, best_diff = (i, j), diff
+            elif diff == best_diff and area > 0.5 * self.crop * self.crop * i * j:
+                best = (i, j)                      # a tie goes to the larger grid when the image has the pixels for it
+        return best
+
+    def preprocess_one(self, img: np.ndarray):
+        S, P = self.crop, self.patch
+        t = torch.from_numpy(np.ascontiguousarray(img)).permute(2, 0, 1)             # uint8 [3, H, W]
+        H, W = t.shape[-2:]
+        wc, hc = self.grid(H, W)
+        tw, th = S * wc, S * hc
+        if tw / W < th / H:
+            nw, nh = tw, int(H * (tw / W))
+        else:
+            nw, nh = int(W * (th / H)), th
+        if min(nw, nh) < 10:
+            raise ValueError(f"the aspect ratio is too extreme: scaled size {nw} x {nh}")
+        pad_w, pad_h = tw - nw, th - nh
+        m = S // P
+        mask = torch.ones(m * hc, m * wc)
+        if pad_w >= P:
+            mask[:, -(pad_w // P):] = 0
+        if pad_h >= P:
+            mask[-(pad_h // P):, :] = 0
+        t = torch.nn.functional.interpolate(t[None], size=(nh, nw), mode="bilinear", antialias=True)[0]
+        t = torch.nn.functional.pad(t, (0, pad_w, 0, pad_h), value=255)
+        x = (t.float() / 255.0 - self.mean) / self.std
+        glob = torch.nn.functional.interpolate(x[None], size=(S, S), mode="bicubic", antialias=False, align_corners=False)[0]
+        tiles = x.reshape(3, hc, S, wc, S).permute(1, 3, 0, 2, 4).reshape(hc * wc, 3, S, S)
+        tile_masks = mask.reshape(hc, m, wc, m).permute(0, 2, 1, 3).reshape(hc * wc, m, m)
+        f = (m + 1) // 2                                                             # pooled patches per tile side
+        pooled = tile_masks[:, 0::2, 0::2].reshape(hc, wc, f, f).permute(0, 2, 1, 3).reshape(hc * f, wc * f)
+        tokens = f * f + f + 1 + int(pooled.sum()) + int(pooled[:, 0].sum())         # global rows + separators, tiles + row ends
+        return torch.cat([glob[None], tiles]), torch.cat([torch.ones(1, m, m), tile_masks]), (th, tw), tokens
+
+    def __call__(self, images: List[np.ndarray], return_tensors: str = "pt"):
+        outs = [self.preprocess_one(np.asarray(im)) for im in images]
+        n = max(o[0].shape[0] for o in outs)
+        pix = torch.stack([torch.cat([o[0], o[0].new_zeros(n - o[0].shape[0], *o[0].shape[1:])]) for o in outs])
+        masks = torch.stack([torch.cat([o[1], o[1].new_ones(n - o[1].shape[0], *o[1].shape[1:])]) for o in outs])
+        return {"image_pixel_values": pix, "image_attention_mask": masks, "image_sizes": torch.tensor([o[2] for o in outs]),
+                "num_img_tokens": [o[3] for o in outs]}

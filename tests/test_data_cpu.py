@@ -308,3 +308,63 @@ def test_model_files_resolve_from_the_cache_of_the_selected_hub(tmp_path, monkey
     assert resolve_dir("org/tiny") == str(snap)
     with pytest.raises(FileNotFoundError):
         resolve_file_path("org/absent", "config.json")
+
+
+def test_phi4_processors_match_hugging_face_and_feed_the_model():
+    """Dynamic-HD image tiling (grid choice, white padding, global view, patch masks, placeholder count) and the Kaldi-style
+    log-mel front end (pre-emphasis, Hamming window, mel-space triangles) against ``transformers``; the combined processor
+    expands the prompt so that the model finds one placeholder per feature row."""
+    import numpy as np
+    from transformers.models.phi4_multimodal.feature_extraction_phi4_multimodal import Phi4MultimodalFeatureExtractor
+    from transformers.models.phi4_multimodal.image_processing_phi4_multimodal import Phi4MultimodalImageProcessor
+
+    from paddleformers_b200.models.phi4_multimodal import Phi4MultimodalConfig, Phi4MultimodalForCausalLM, Phi4MultimodalProcessor
+    from paddleformers_b200.transformers.audio_processing import KaldiFbankFeatureExtractor
+    from paddleformers_b200.transformers.image_processing import DynamicHDImageProcessor
+
+    rng = np.random.default_rng(0)
+    imgs = [rng.integers(0, 255, (300, 700, 3), dtype=np.uint8), rng.integers(0, 255, (900, 500, 3), dtype=np.uint8)]
+    want = Phi4MultimodalImageProcessor()(images=[torch.from_numpy(i).permute(2, 0, 1) for i in imgs], return_tensors="pt")
+    got = DynamicHDImageProcessor()(imgs)
+    for k in ("image_pixel_values", "image_attention_mask", "image_sizes"):
+        assert want[k].shape == got[k].shape and (want[k].float() - got[k].float()).abs().max() < 1e-5, k
+    assert want["num_img_tokens"].tolist() == got["num_img_tokens"] == [735, 1617]
+    assert DynamicHDImageProcessor(dynamic_hd=4).grid(2000, 3100) == (2, 1)             # more tiles than allowed: closest aspect ratio
+    a, b = rng.standard_normal(16000).astype(np.float32) * 0.1, rng.standard_normal(9000).astype(np.float32) * 0.1
+    w = Phi4MultimodalFeatureExtractor()([a, b], sampling_rate=16000, return_tensors="pt")
+    g = KaldiFbankFeatureExtractor()([a, b], sampling_rate=16000)
+    n_b = int(g["audio_attention_mask"][1].sum())
+    assert w["audio_embed_sizes"].tolist() == g["audio_embed_sizes"].tolist() == [13, 7] and n_b == int(w["audio_attention_mask"][1].sum())
+    assert (w["audio_input_features"][0] - g["audio_input_features"][0]).abs().max() < 1e-4
+    assert (w["audio_input_features"][1, :n_b] - g["audio_input_features"][1, :n_b]).abs().max() < 1e-4
+    with pytest.raises(ValueError, match="16000"):
+        KaldiFbankFeatureExtractor()(a, sampling_rate=8000)
+
+    class Tok:                                     # whitespace tokenizer that knows the two tags
+        vocab = {"<|image|>": 290, "<|audio|>": 291}
+
+        def encode(self, text, add_special_tokens=False):
+            import re
+
+            return [self.vocab.get(t, 5 + len(t) % 50) for t in re.findall(r"<\|image\|>|<\|audio\|>|\S+", text)]
+
+    cfg = Phi4MultimodalConfig(vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=1, num_attention_heads=4,
+                               num_key_value_heads=2, max_position_embeddings=4096,
+                               vision_config=dict(hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=2,
+                                                  image_size=56, patch_size=14, crop_size=56, image_token_id=290),
+                               audio_config=dict(hidden_size=32, intermediate_size=48, num_blocks=1, num_attention_heads=2,
+                                                 ext_pw_out_channel=32, depthwise_separable_out_channel=32, input_size=80,
+                                                 nemo_conv_channels=8, nemo_final_size=10, time_reduction=8, bias_max_distance=20,
+                                                 audio_token_id=291))
+    torch.manual_seed(0)
+    model = Phi4MultimodalForCausalLM(cfg, dtype=torch.float32).eval()
+    proc = Phi4MultimodalProcessor(Tok(), image_processor=DynamicHDImageProcessor(crop=56, patch_size=14, dynamic_hd=4))
+    batch = proc("look <|image|> and listen <|audio|> then answer", images=[imgs[0][:60, :130]], audio=[a], sampling_rate=16000)
+    # 60 x 130 pixels cover 2 x 3 tiles of 56, more than 4: the 1 x 2 grid is chosen; every tile pools to 2 x 2 rows
+    assert int((batch["input_ids"] == 290).sum()) == (2 * 4 + 2) + 1 + (2 * 2 + 2) == 17
+    assert int((batch["input_ids"] == 291).sum()) == 13
+    with torch.no_grad():
+        out = model(**batch)
+    assert out.logits.shape[:2] == batch["input_ids"].shape and torch.isfinite(out.logits).all()
+    with pytest.raises(ValueError, match="tags"):
+        proc("no tags here", images=[imgs[0]])
