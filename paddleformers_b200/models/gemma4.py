@@ -31,6 +31,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as TF
 
+from ..generation.utils import GenerationMixin
 from ..nn.attention import AttentionInterface
 from ..nn.moe import GroupedExperts, _PermuteFn, build_dispatch_plan, unpermute_combine
 from ..ops import functional as F
@@ -350,7 +351,7 @@ class Gemma4TextModel(nn.Module):
         return self.norm(x)
 
 
-class Gemma4ForCausalLM(PretrainedModel):
+class Gemma4ForCausalLM(PretrainedModel, GenerationMixin):
     config_class = Gemma4TextConfig
     base_model_prefix = "model"
 
@@ -404,11 +405,6 @@ class Gemma4ForCausalLM(PretrainedModel):
             out.loss = total / (count.clamp(min=1) * float(self.loss_accumulation_steps))
             out.num_tokens = count
         return out
-
-    def generate(self, input_ids, generation_config=None, **kw):
-        from ..generation.utils import generate
-
-        return generate(self, input_ids, generation_config, **kw)
 
     def weight_map(self) -> WeightMap:
         """Tensor names are the checkpoint's own, except the router / experts, which sit under ``moe.`` here."""

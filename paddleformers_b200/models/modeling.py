@@ -22,6 +22,7 @@ import torch.nn as nn
 import torch.utils.checkpoint
 
 from ..nn.moe import DenseMLP, MoELayer
+from ..generation.utils import GenerationMixin
 from ..ops import functional as F
 from ..utils.refined_recompute import checkpoint_keeping, keep, kept_ops_of_layer
 from ..parallel.tensor_parallel import (ColumnParallelLinear, GatherOp, RowParallelLinear, ScatterOp,
@@ -701,7 +702,7 @@ class DecoderModel(nn.Module):
         return hidden, ctx
 
 
-class DecoderForCausalLM(PretrainedModel):
+class DecoderForCausalLM(PretrainedModel, GenerationMixin):
     config_class = DecoderConfig
     base_model_prefix = "model"
 
