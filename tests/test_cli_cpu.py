@@ -575,3 +575,68 @@ def test_merge_preprocess_ckpt_and_env_commands(tmp_path, capsys):
     assert "torch" in capsys.readouterr().out
     with pytest.raises(SystemExit):
         main(["preprocess", "--help"])
+
+
+def test_vl_sft_stage_trains_ernie4_5_vl(tmp_path):
+    """ERNIE-4.5-VL through the VL-SFT stage: single-frame patches in merge-block order, image markers routed to the vision
+    experts, the published checkpoint layout written at the end."""
+    from PIL import Image
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    from paddleformers_b200.cli.train import run_tuner
+    from paddleformers_b200.models.ernie4_5_vl import Ernie4_5VLConfig
+    from paddleformers_b200.transformers.auto import AutoModelForConditionalGeneration
+
+    words = ["<pad>", "<s>", "</s>", "<unk>", "Human:", "Assistant:", "System:", "<image>", "<|IMAGE_PLACEHOLDER|>", "<|IMAGE_START|>",
+             "<|IMAGE_END|>", "<|VIDEO_PLACEHOLDER|>"] + [f"w{i}" for i in range(40)]
+    tok = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    fast = PreTrainedTokenizerFast(tokenizer_object=tok, pad_token="<pad>", bos_token="<s>", eos_token="</s>", unk_token="<unk>")
+    cfg = Ernie4_5VLConfig(
+        text_config=dict(vocab_size=len(words), hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=2,
+                         num_key_value_heads=1, moe_intermediate_size=[16, 8], moe_k=2, moe_num_experts=4, moe_num_shared_experts=1,
+                         mlp_layer_types=["dense", "sparse"], rope_parameters={"rope_theta": 10000.0, "mrope_section": [3, 3, 2]}),
+        vision_config=dict(depth=1, hidden_size=16, num_heads=2, intermediate_size=32, patch_size=4, spatial_merge_size=2),
+        image_token_id=words.index("<|IMAGE_PLACEHOLDER|>"), video_token_id=words.index("<|VIDEO_PLACEHOLDER|>"),
+        image_start_token_id=words.index("<|IMAGE_START|>"), image_end_token_id=words.index("<|IMAGE_END|>"),
+        video_start_token_id=None, video_end_token_id=None)
+    base = tmp_path / "base"
+    torch.manual_seed(0)
+    AutoModelForConditionalGeneration.from_config(cfg, dtype=torch.float32).save_pretrained(str(base))
+    fast.save_pretrained(str(base))
+    rng = np.random.RandomState(0)
+    data = tmp_path / "vl.jsonl"
+    with open(data, "w") as f:
+        for i in range(6):
+            img = tmp_path / f"img{i}.png"
+            Image.fromarray((rng.rand(16 + 8 * (i % 2), 24, 3) * 255).astype("uint8")).save(img)
+            f.write(json.dumps({"images": [str(img)], "messages": [{"role": "user", "content": "<image> w1 w2"},
+                                                                     {"role": "assistant", "content": f"w{3 + i % 5} w9"}]}) + "\n")
+    out = tmp_path / "out"
+    cfg_file = tmp_path / "vl.json"
+    cfg_file.write_text(json.dumps({
+        "stage": "VL-SFT", "model_name_or_path": str(base), "compute_type": "float32", "device": "cpu", "train_dataset_path": str(data),
+        "template": "default", "max_seq_len": 64, "max_steps": 4, "per_device_train_batch_size": 2, "learning_rate": 5e-3,
+        "logging_steps": 1, "save_strategy": "no", "output_dir": str(out), "min_pixels": 256, "max_pixels": 1024}))
+    env = os.environ.get("CUDA_VISIBLE_DEVICES")
+    os.environ["CUDA_VISIBLE_DEVICES"] = ""
+    try:
+        trainer, _ = run_tuner([str(cfg_file)])
+    finally:
+        if env is None:
+            os.environ.pop("CUDA_VISIBLE_DEVICES", None)
+        else:
+            os.environ["CUDA_VISIBLE_DEVICES"] = env
+    losses = [h["loss"] for h in trainer.state.log_history if "loss" in h]
+    assert len(losses) == 4 and losses[-1] < losses[0]
+    batch = next(iter(trainer.get_train_dataloader()))
+    assert batch["pixel_values"].shape[1] == 3 * 4 * 4 and int(trainer.model.vision_rows(batch["input_ids"]).sum()) > 0
+    from safetensors import safe_open
+
+    with safe_open(str(out / "model.safetensors"), "pt") as f:
+        keys = set(f.keys())
+    assert "model.layers.1.mlp.gate.weight_1" in keys and "model.layers.1.mlp.experts.7.down_proj.weight" in keys
+    assert "model.vision_model.patch_embed.proj.weight" in keys and "model.resampler_model.spatial_linear.0.weight" in keys
+    again = AutoModelForConditionalGeneration.from_pretrained(str(out), dtype=torch.float32)
+    assert again.config.model_type == "ernie4_5_vl_moe" and os.path.exists(out / "tokenizer.json")
