@@ -318,3 +318,43 @@ class MolmoForCausalLM(PretrainedModel):
             for name, _ in self.model.vision_backbone.named_parameters():
                 rules.append(Rule("model.vision_backbone." + name, ["model.vision_backbone." + name]))
         return WeightMap(rules)
+
+
+class MolmoProcessor:
+    """Prompt + images -> ``input_ids`` (start token, the images' token blocks, the prompt), ``images``, ``image_masks`` and
+    ``image_input_idx`` with positions counted in the final sequence (paddleformers/transformers/molmo/processing.py:99-190).
+    ``tokenizer`` must encode ``<im_start>``, ``<im_end>``, ``<im_patch>`` and ``<im_col>`` as single tokens."""
+
+    TOKENS = ("<im_start>", "<im_end>", "<im_patch>", "<im_col>")
+
+    def __init__(self, tokenizer, image_processor=None):
+        from ..transformers.image_processing import MolmoImageProcessor
+
+        self.tokenizer = tokenizer
+        self.image_processor = image_processor or MolmoImageProcessor()
+        ids = [tokenizer.encode(t, add_special_tokens=False) for t in self.TOKENS]
+        if any(len(i) != 1 for i in ids):
+            raise ValueError("the tokenizer must encode the Molmo image tokens as single tokens")
+        self.start_id, self.end_id, self.patch_id, self.col_id = (i[0] for i in ids)
+
+    def __call__(self, text: str, images=None, message_format: str = "role") -> dict:
+        import numpy as np
+
+        prompt = "" if text is None else text
+        if message_format == "role":
+            prompt = "User: " + prompt + " Assistant:"
+        ids = [self.tokenizer.bos_token_id if self.tokenizer.bos_token_id is not None else self.tokenizer.eos_token_id]
+        out = {}
+        if images:
+            crops, masks, idx = [], [], []
+            for img in images:
+                c, m, toks, ix = self.image_processor.preprocess_one(np.asarray(img), self.patch_id, self.col_id, self.start_id, self.end_id)
+                idx.append(np.where(ix >= 0, ix + len(ids), -1))
+                ids += toks.tolist()
+                crops.append(c)
+                masks.append(m)
+            out = {"images": torch.from_numpy(np.concatenate(crops))[None], "image_masks": torch.from_numpy(np.concatenate(masks))[None],
+                   "image_input_idx": torch.from_numpy(np.concatenate(idx))[None]}
+        ids += self.tokenizer.encode(" " + prompt, add_special_tokens=False)
+        out["input_ids"] = torch.tensor([ids])
+        return out

@@ -246,3 +246,99 @@ class DynamicHDImageProcessor:
         masks = torch.stack([torch.cat([o[1], o[1].new_ones(n - o[1].shape[0], *o[1].shape[1:])]) for o in outs])
         return {"image_pixel_values": pix, "image_attention_mask": masks, "image_sizes": torch.tensor([o[2] for o in outs]),
                 "num_img_tokens": [o[3] for o in outs]}
+
+
+class MolmoImageProcessor:
+    """Multi-crop pre-processing of Molmo (paddleformers/transformers/molmo/image_processing.py:45-318). The image is scaled
+    and centred (black padding) on a canvas of ``rows x cols`` overlapping crops: neighbouring crops share
+    ``overlap_margins`` patches, and every crop contributes only its inner window (plus the outer margin on the border of the
+    canvas) to the token grid, so the contributions tile the canvas exactly once. A down-scaled view of the whole image comes
+    first. Per image it returns
+
+    * ``images`` [1 + crops, patches, 3 p p]: flattened patches (pixel-major, channel last), CLIP-normalised;
+    * ``image_masks`` [1 + crops, patches]: fraction of every patch that shows the image; as in the published pipeline the
+      rows belong to the crops in order and a final row of -1 stands for the overview;
+    * ``tokens``: start, ``rows`` x (``<im_patch>`` x width, ``<im_col>``), end for the overview, then the same for the canvas
+      at pooled (2 x 2 patches) resolution;
+    * ``image_input_idx`` [1 + crops, pooled patches per crop]: for every pooled cell of every crop the position of its
+      ``<im_patch>`` token inside ``tokens``, or -1 where the cell lies in a margin that the neighbour provides."""
+
+    def __init__(self, max_crops: int = 12, overlap_margins=(4, 4), base_image_input_size=(336, 336), image_token_length_w: int = 12,
+                 image_token_length_h: int = 12, image_patch_size: int = 14, image_mean=OPENAI_CLIP_MEAN, image_std=OPENAI_CLIP_STD):
+        self.max_crops, self.margins, self.size = max_crops, tuple(overlap_margins), tuple(base_image_input_size)
+        self.tw, self.th, self.p = image_token_length_w, image_token_length_h, image_patch_size
+        self.mean, self.std = np.asarray(image_mean, dtype=np.float32), np.asarray(image_std, dtype=np.float32)
+        assert self.margins[0] % 2 == 0 and self.size[0] == self.size[1]
+        assert (self.size[0] // self.p + 1) // 2 == self.th == self.tw, "token grid = crop patches pooled 2 x 2"
+
+    def select_tiling(self, h: int, w: int, window: int) -> tuple:
+        """(rows, cols) with rows * cols <= max_crops: the grid that needs the least up-scaling, or, when every grid would
+        shrink the image, the one that shrinks it least."""
+        cands = sorted(((i, j) for i in range(1, self.max_crops + 1) for j in range(1, self.max_crops + 1) if i * j <= self.max_crops),
+                       key=lambda t: (t[0] * t[1], t[0]))
+        scale = np.asarray([min(np.float32(i * window) / np.float32(h), np.float32(j * window) / np.float32(w)) for i, j in cands], dtype=np.float32)
+        if (scale < 1).all():
+            return cands[int(np.argmax(scale))]
+        return cands[int(np.argmin(np.where(scale < 1.0, np.float32(10e9), scale)))]
+
+    def resize_and_pad(self, img: np.ndarray, out_hw) -> tuple:
+        H, W = out_hw
+        h, w = img.shape[:2]
+        s = min(np.float32(W) / np.float32(w), np.float32(H) / np.float32(h))
+        sh, sw = int(np.float32(h) * s), int(np.float32(w) * s)
+        t = torch.from_numpy(np.ascontiguousarray(img)).permute(2, 0, 1).float() / 255.0
+        t = torch.nn.functional.interpolate(t[None], size=(sh, sw), mode="bilinear", antialias=True, align_corners=False)[0].clamp(0, 1)
+        top, left = (H - sh) // 2, (W - sw) // 2
+        canvas = np.zeros((H, W, 3), dtype=np.float32)
+        canvas[top:top + sh, left:left + sw] = t.permute(1, 2, 0).numpy()
+        mask = np.zeros((H, W), dtype=bool)
+        mask[top:top + sh, left:left + sw] = True
+        return (canvas - self.mean) / self.std, mask
+
+    def _patchify(self, x: np.ndarray) -> np.ndarray:
+        """[n, S, S, c] -> [n, patches, p * p * c] (rows of patches, pixels row by row, channel last)."""
+        n, S, _, c = x.shape
+        g = S // self.p
+        return x.reshape(n, g, self.p, g, self.p, c).transpose(0, 1, 3, 2, 4, 5).reshape(n, g * g, self.p * self.p * c)
+
+    def preprocess_one(self, img: np.ndarray, patch_id: int, col_id: int, start_id: int, end_id: int):
+        p, S = self.p, self.size[0]
+        lm, rm = self.margins
+        g = S // p                                   # patches per crop side
+        window = g - (lm + rm)                       # patches that a crop in the middle contributes
+        rows, cols = self.select_tiling(img.shape[0] - p * (lm + rm), img.shape[1] - p * (lm + rm), window * p)
+        canvas, cmask = self.resize_and_pad(img, (rows * window * p + p * (lm + rm), cols * window * p + p * (lm + rm)))
+
+        def spans(n):                                # per crop along one axis: (first pooled cell used, pooled cells used)
+            out = []
+            for i in range(n):
+                size = window + (lm if i == 0 else 0) + (rm if i == n - 1 else 0)
+                out.append((0 if i == 0 else lm // 2, (size + 1) // 2))
+            return out
+
+        ys, xs = spans(rows), spans(cols)
+        Hp, Wp = (rows * window + lm + rm + 1) // 2, (cols * window + lm + rm + 1) // 2
+        assert sum(n for _, n in ys) == Hp and sum(n for _, n in xs) == Wp
+        low = [start_id] + ([patch_id] * self.tw + [col_id]) * self.th + [end_id]
+        high = [start_id] + ([patch_id] * Wp + [col_id]) * Hp + [end_id]
+        tokens = np.asarray(low + high, dtype=np.int64)
+        idx = np.full((1 + rows * cols, self.th * self.tw), -1, dtype=np.int64)
+        idx[0] = (1 + np.arange(self.th)[:, None] * (self.tw + 1) + np.arange(self.tw)[None]).reshape(-1)
+        base = len(low) + 1
+        crops, masks, r0 = [], [], 0
+        for i, (y0, nh) in enumerate(ys):
+            c0 = 0
+            for j, (x0, nw) in enumerate(xs):
+                cell = np.full((self.th, self.tw), -1, dtype=np.int64)
+                cell[y0:y0 + nh, x0:x0 + nw] = base + (r0 + np.arange(nh))[:, None] * (Wp + 1) + (c0 + np.arange(nw))[None]
+                idx[1 + i * cols + j] = cell.reshape(-1)
+                py, px = i * window * p, j * window * p
+                crops.append(canvas[py:py + S, px:px + S])
+                masks.append(cmask[py:py + S, px:px + S])
+                c0 += nw
+            r0 += nh
+        whole, _ = self.resize_and_pad(img, self.size)
+        images = self._patchify(np.stack([whole] + crops))
+        m = self._patchify(np.stack(masks)[..., None].astype(np.float32)).mean(-1)
+        image_masks = np.concatenate([m, np.full((1, m.shape[1]), -1.0, dtype=np.float32)], axis=0)
+        return images.astype(np.float32), image_masks, tokens, idx

@@ -368,3 +368,73 @@ def test_phi4_processors_match_hugging_face_and_feed_the_model():
     assert out.logits.shape[:2] == batch["input_ids"].shape and torch.isfinite(out.logits).all()
     with pytest.raises(ValueError, match="tags"):
         proc("no tags here", images=[imgs[0]])
+
+
+def test_molmo_multi_crop_processor_is_geometrically_consistent_and_feeds_the_model():
+    """Every ``<im_patch>`` token is claimed by exactly one pooled cell of one crop; the cell and the token describe the same
+    2 x 2 patches of the canvas; crops overlap by the margins; the overview comes first; masks give the visible fraction of a
+    patch; the model adds feature rows at the claimed positions only."""
+    import numpy as np
+
+    from paddleformers_b200.models.molmo import MolmoConfig, MolmoForCausalLM, MolmoProcessor
+    from paddleformers_b200.transformers.image_processing import MolmoImageProcessor
+
+    proc = MolmoImageProcessor()
+    rng = np.random.default_rng(0)
+    img = rng.integers(0, 255, (500, 900, 3), dtype=np.uint8)
+    PATCH, COL, START, END = 3, 4, 1, 2
+    images, masks, tokens, idx = proc.preprocess_one(img, PATCH, COL, START, END)
+    rows, cols = proc.select_tiling(500 - 112, 900 - 112, 224)
+    assert (rows, cols) == (2, 4) and images.shape == (1 + 8, 576, 588) and masks.shape == (9, 576) and idx.shape == (9, 144)
+    valid = idx[idx >= 0]
+    assert len(valid) == int((tokens == PATCH).sum()) == len(set(valid.tolist())) and (tokens[valid] == PATCH).all()
+    assert tokens[0] == START and tokens[12 * 13 + 1] == END and (idx[0] == np.flatnonzero(tokens == PATCH)[:144]).all()
+    # geometry: crop (i, j) starts 16 patches after its neighbour; cell (a, b) of it covers canvas patches (16 i + 2 a, 16 j + 2 b);
+    # the token at row R, column C of the pooled canvas grid covers canvas patches (2 R, 2 C)
+    Wp = (cols * 16 + 8 + 1) // 2
+    base = (1 + 12 * 13 + 1) + 1
+    for c in range(rows * cols):
+        i, j = divmod(c, cols)
+        for cell in np.flatnonzero(idx[1 + c] >= 0):
+            a, b = divmod(int(cell), 12)
+            R, C = divmod(int(idx[1 + c, cell]) - base, Wp + 1)
+            assert (16 * i + 2 * a, 16 * j + 2 * b) == (2 * R, 2 * C)
+    # neighbouring crops share 8 patch columns; the picture is centred with black (normalised zero) bars and masks say so
+    left, right = images[1].reshape(24, 24, 588), images[2].reshape(24, 24, 588)
+    assert np.allclose(left[:, 16:], right[:, :8])
+    assert masks[-1].min() == masks[-1].max() == -1 and 0 <= masks[:-1].min() and masks[:-1].max() == 1
+    _, m2, _, _ = proc.preprocess_one(rng.integers(0, 255, (333, 900, 3), dtype=np.uint8), PATCH, COL, START, END)
+    assert (m2[:-1] == 0).any() and ((m2[:-1] > 0) & (m2[:-1] < 1)).any() and (m2[:-1] == 1).any()    # bars, their edge, the picture
+    # a small image that fits one crop: one crop whose whole 12 x 12 grid is used
+    _, _, t1, i1 = proc.preprocess_one(rng.integers(0, 255, (200, 300, 3), dtype=np.uint8), PATCH, COL, START, END)
+    assert i1.shape == (2, 144) and (i1 >= 0).all() and int((t1 == PATCH).sum()) == 288
+
+    class Tok:
+        bos_token_id, eos_token_id = 0, 0
+        vocab = {"<im_start>": 91, "<im_end>": 92, "<im_patch>": 93, "<im_col>": 94}
+
+        def encode(self, text, add_special_tokens=False):
+            import re
+
+            return [self.vocab.get(t, 5 + len(t) % 50) for t in re.findall(r"<im_\w+>|\S+", text)]
+
+    small = MolmoImageProcessor(max_crops=4, overlap_margins=(2, 2), base_image_input_size=(56, 56), image_token_length_w=2,
+                                image_token_length_h=2, image_patch_size=14)
+    mp = MolmoProcessor(Tok(), small)
+    batch = mp("what is this", images=[rng.integers(0, 255, (60, 100, 3), dtype=np.uint8)])
+    cfg = MolmoConfig(vocab_size=90, embedding_size=96, hidden_size=32, intermediate_size=96, num_hidden_layers=1, num_attention_heads=2,
+                      additional_vocab_size=8, max_position_embeddings=256,
+                      vision_backbone=dict(image_default_input_size=(56, 56), image_patch_size=14, image_emb_dim=16, image_num_heads=2,
+                                           image_num_key_value_heads=2, image_num_layers=2, image_head_dim=8, image_mlp_dim=24,
+                                           image_num_pos=17), vit_layers=(-1, -2))
+    torch.manual_seed(0)
+    model = MolmoForCausalLM(cfg, dtype=torch.float32).eval()
+    ids = batch["input_ids"]
+    assert ids[0, 0] == 0 and ids[0, 1] == 91
+    with torch.no_grad():
+        with_img = model(**batch).logits
+        without = model(ids).logits
+    touched = (with_img - without).abs().amax(-1)[0] > 0
+    first = int(batch["image_input_idx"][batch["image_input_idx"] >= 0].min())
+    assert not touched[:first].any() and touched[first]                                   # causal: nothing before the first feature row moves
+    assert set(batch["image_input_idx"][batch["image_input_idx"] >= 0].tolist()) == set(torch.nonzero(ids[0] == 93)[:, 0].tolist())
