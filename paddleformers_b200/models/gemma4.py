@@ -20,7 +20,8 @@ What sets the family apart from the unified decoder, and why it is a model of it
 The routed experts go through the same dispatch plan / expert-parallel exchange as every other MoE layer of the package; their
 activation is tanh-GELU, which the grouped SwiGLU kernels do not fuse, so they run segment by segment in tensor
 operations. Attention runs through the flash kernel when a layer's head size is 128 and through the tensor-operation back-ends
-otherwise (256 / 512-wide heads). Tensor-parallel degree 1; functional support, not a tuned path.
+otherwise (256 / 512-wide heads). Attention and the dense MLP are tensor parallel (column / row split, no sequence
+parallelism); the routed experts are sharded by expert parallelism. Functional support, not a tuned path.
 """
 from __future__ import annotations
 
@@ -39,7 +40,7 @@ from ..parallel.topology import get_parallel_state
 from ..transformers.configuration_utils import PretrainedConfig
 from ..transformers.conversion_utils import Rule, WeightMap
 from ..transformers.model_utils import PretrainedModel
-from .modeling import CausalLMOutput, RMSNorm, _resolve_dtype
+from .modeling import CausalLMOutput, RMSNorm, _linear, _resolve_dtype
 
 _ACT = {"gelu_pytorch_tanh": lambda x: TF.gelu(x, approximate="tanh"), "gelu": TF.gelu, "silu": TF.silu}
 
@@ -149,17 +150,25 @@ class Gemma4Attention(nn.Module):
         super().__init__()
         self.layer_idx = layer_idx
         self.D, self.Hkv, self.k_eq_v = config.layer_head_geometry(layer_idx)
-        self.Hq = config.num_attention_heads
+        tp = get_parallel_state().degrees.mp
+        assert config.num_attention_heads % tp == 0 and self.Hkv % tp == 0, \
+            "Gemma 4: query heads and the key / value heads of every layer type must divide the tensor-parallel degree"
+        self.Hq, self.Hkv = config.num_attention_heads // tp, self.Hkv // tp          # heads of this rank
         self.sliding = config.layer_types[layer_idx] == "sliding_attention"
         self.kv_source = config.kv_source_layer(layer_idx)
         self.eps = config.rms_norm_eps
-        H, kw = config.hidden_size, dict(bias=bool(config.attention_bias), dtype=dtype, device=device)
-        self.q_proj = nn.Linear(H, self.Hq * self.D, **kw)
-        self.k_proj = nn.Linear(H, self.Hkv * self.D, **kw)
-        self.v_proj = None if self.k_eq_v else nn.Linear(H, self.Hkv * self.D, **kw)
-        self.o_proj = nn.Linear(self.Hq * self.D, H, **kw)
+        H, b, kw = config.hidden_size, bool(config.attention_bias), dict(dtype=dtype, device=device)
+        self.q_proj = _linear(H, self.Hq * tp * self.D, b, "colwise", config, **kw)
+        self.k_proj = _linear(H, self.Hkv * tp * self.D, b, "colwise", config, **kw)
+        self.v_proj = None if self.k_eq_v else _linear(H, self.Hkv * tp * self.D, b, "colwise", config, **kw)
+        self.o_proj = _linear(self.Hq * tp * self.D, H, b, "rowwise", config, **kw)
         self.q_norm = RMSNorm(self.D, self.eps, dtype=dtype, device=device)
         self.k_norm = RMSNorm(self.D, self.eps, dtype=dtype, device=device)
+        if tp > 1:                 # shared by all heads, seen by this rank's heads only: partial gradients, summed over the group
+            from ..parallel.tensor_parallel import mark_as_sequence_parallel_parameter
+
+            mark_as_sequence_parallel_parameter(self.q_norm.weight)
+            mark_as_sequence_parallel_parameter(self.k_norm.weight)
         self.impl = getattr(config, "_attn_implementation", None)
 
     def forward(self, x, cos, sin, kend, shared_kv: dict):
@@ -186,10 +195,10 @@ class Gemma4MLP(nn.Module):
         super().__init__()
         wide = bool(config.use_double_wide_mlp) and config.kv_source_layer(layer_idx) is not None
         I = config.intermediate_size * (2 if wide else 1)
-        kw = dict(bias=False, dtype=dtype, device=device)
-        self.gate_proj = nn.Linear(config.hidden_size, I, **kw)
-        self.up_proj = nn.Linear(config.hidden_size, I, **kw)
-        self.down_proj = nn.Linear(I, config.hidden_size, **kw)
+        kw = dict(dtype=dtype, device=device)
+        self.gate_proj = _linear(config.hidden_size, I, False, "colwise", config, **kw)
+        self.up_proj = _linear(config.hidden_size, I, False, "colwise", config, **kw)
+        self.down_proj = _linear(I, config.hidden_size, False, "rowwise", config, **kw)
         self.act = _ACT[config.hidden_activation]
 
     def forward(self, x):
@@ -357,7 +366,8 @@ class Gemma4ForCausalLM(PretrainedModel, GenerationMixin):
 
     def __init__(self, config: Gemma4TextConfig, dtype=None, device=None):
         super().__init__(config)
-        assert get_parallel_state().degrees.mp == 1, "Gemma 4 is implemented for tensor-parallel degree 1"
+        assert not (get_parallel_state().degrees.mp > 1 and getattr(config, "sequence_parallel", False)), \
+            "Gemma 4: tensor parallelism without sequence parallelism"
         dtype = dtype if dtype is not None else _resolve_dtype(config.dtype)
         self.model = Gemma4TextModel(config, dtype=dtype, device=device)
         self.lm_head = None if config.tie_word_embeddings else \

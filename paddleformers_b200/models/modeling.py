@@ -198,6 +198,11 @@ class Attention(nn.Module):
         elif self.use_qk_norm:
             self.q_norm = RMSNorm(self.D, config.rms_norm_eps, dtype=dtype, device=device)
             self.k_norm = RMSNorm(self.D, config.rms_norm_eps, dtype=dtype, device=device)
+            if tp > 1:
+                # one weight vector shared by all heads, but every tensor-parallel rank sees its own heads only: the
+                # gradients are partial sums and are added up over the group before the optimizer step
+                mark_as_sequence_parallel_parameter(self.q_norm.weight)
+                mark_as_sequence_parallel_parameter(self.k_norm.weight)
         self.qk_norm_after_rope = bool(self.use_qk_norm and getattr(config, "qk_norm_after_rope", False))   # Hunyuan
         self.scale = float(getattr(config, "attention_multiplier", None) or 1.0 / math.sqrt(self.D))
         # soft-capped attention scores and attention sinks are not in the flash kernels: such families run the eager back-end

@@ -16,7 +16,7 @@ def _tiny_cfg(moe=False, **kw):
         base = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
                     num_key_value_heads=2, head_dim=16, global_head_dim=32, sliding_window=8, vocab_size_per_layer_input=128,
                     hidden_size_per_layer_input=8, enable_moe_block=True, num_experts=4, top_k_experts=2, moe_intermediate_size=32,
-                    attention_k_eq_v=True, num_global_key_value_heads=1)
+                    attention_k_eq_v=True, num_global_key_value_heads=2)
         base.update(kw)
         return AutoConfig.for_model("gemma4_text", **base)
     if moe:
@@ -103,6 +103,10 @@ def _reference(moe, steps, accum):
     ("ep2", 2, True, dict(expert_model_parallel_size=2, sharding="stage1", gradient_accumulation_steps=1, moe_token_dispatcher_type="alltoall")),
     ("gemma4_ep2", 2, "gemma4", dict(expert_model_parallel_size=2, sharding="stage1", gradient_accumulation_steps=1,
                                      moe_token_dispatcher_type="alltoall")),
+    ("tp2_qk_norm_moe", 2, True, dict(tensor_model_parallel_size=2, gradient_accumulation_steps=2, moe_token_dispatcher_type="alltoall")),
+    ("tp2_sp_qk_norm_moe", 2, True, dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2,
+                                         moe_token_dispatcher_type="alltoall")),
+    ("gemma4_tp2", 2, "gemma4", dict(tensor_model_parallel_size=2, gradient_accumulation_steps=2, moe_token_dispatcher_type="alltoall")),
     ("cp2", 2, False, dict(context_parallel_size=2, gradient_accumulation_steps=2)),
     ("cp2_contiguous", 2, False, dict(context_parallel_size=2, cp_balance_mode="contiguous_allgather", gradient_accumulation_steps=2)),
     ("cp2_ring", 2, False, dict(context_parallel_size=2, context_parallel_algo="ring", gradient_accumulation_steps=2)),
@@ -529,3 +533,45 @@ def test_modality_isolated_experts_under_expert_parallelism():
     for r in range(2):
         y, gx = got[r][0]
         assert (y - ref[r][0]).abs().max() < 1e-5 and (gx - ref[r][1]).abs().max() < 1e-5
+
+
+def _qk_norm_weights_worker(rank, world, full):
+    from paddleformers_b200 import Trainer, TrainingArguments
+    from paddleformers_b200.models.configuration import named_config
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+    from paddleformers_b200.transformers.configuration_utils import LlmMetaConfig
+    from paddleformers_b200.transformers.model_utils import param_shard_spec
+
+    args = TrainingArguments(output_dir="/tmp/pfb_test_unused", per_device_train_batch_size=2, max_steps=2, learning_rate=5e-2,
+                             lr_scheduler_type="constant", logging_steps=1, save_strategy="no", max_seq_len=32, seed=3, device="cpu",
+                             tensor_model_parallel_size=world, max_grad_norm=0.0)
+    ps = args.setup_parallel()
+    cfg = named_config("qwen3-30b-a3b", num_hidden_layers=1, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                       num_experts=0, intermediate_size=96, vocab_size=128)
+    LlmMetaConfig.set_llm_config(cfg, args)
+    model = MODEL_MAPPING[cfg.model_type](cfg)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            p.copy_(param_shard_spec(p).shard(full[n], ps.coord["mp"], ps.degrees.mp, 0, 1))
+    tr = Trainer(model=model, args=args, train_dataset=_DS(_data(8)))
+    tr._sampler_shuffle = False
+    tr.train()
+    return {n: p.detach().clone() for n, p in model.named_parameters() if "q_norm" in n or "k_norm" in n}
+
+
+def test_per_head_norm_weights_get_the_gradient_of_all_heads_under_tensor_parallelism():
+    """One norm weight vector serves all heads, every tensor-parallel rank holds some of the heads: the partial gradients are
+    summed over the group, so the replicas stay equal and follow the single-process trajectory."""
+    from paddleformers_b200.models.configuration import named_config
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+
+    torch.manual_seed(0)
+    cfg = named_config("qwen3-30b-a3b", num_hidden_layers=1, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                       num_experts=0, intermediate_size=96, vocab_size=128)
+    full = {k: v.detach().clone() for k, v in MODEL_MAPPING[cfg.model_type](cfg).named_parameters()}
+    ref = run_distributed(_qk_norm_weights_worker, 1, full)[0]
+    got = run_distributed(_qk_norm_weights_worker, 2, full)
+    for n in ref:
+        assert (ref[n] - 1.0).abs().max() > 1e-3                                 # the weights moved
+        assert torch.equal(got[0][n], got[1][n]), n
+        assert (got[0][n] - ref[n]).abs().max() < 2e-3 * (ref[n] - 1.0).abs().max() + 1e-6, n
