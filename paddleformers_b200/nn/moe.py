@@ -640,6 +640,17 @@ class MoELayer(nn.Module):
             self.shared_expert_gate = nn.Linear(config.hidden_size, 1, bias=False, dtype=dtype, device=device)
         self.ep = get_parallel_state().degrees.ep
         self.last_aux_loss = None
+        if get_parallel_state().degrees.mp > 1 and getattr(config, "sequence_parallel", False):
+            # under sequence parallelism every tensor-parallel rank routes and computes ITS tokens with replicated router,
+            # shared-expert and (without expert parallelism) expert weights: their gradients are partial sums over the
+            # tokens and are added up over the group before the optimizer step
+            # (paddleformers/trainer/trainer_callback.py:918-963 does this for the gate and the norm weights)
+            from ..parallel.tensor_parallel import mark_as_sequence_parallel_parameter
+
+            mods = [self.gate, self.shared_experts, self.shared_expert_gate] + ([self.experts] if self.ep == 1 else [])
+            for mod in mods:
+                for p in (mod.parameters() if mod is not None else ()):
+                    mark_as_sequence_parallel_parameter(p)
 
     def forward(self, x2d: torch.Tensor) -> torch.Tensor:
         # moe_subbatch_token_num_before_dispatch > 0: route and run the experts on slices of the tokens, one after the other, which bounds

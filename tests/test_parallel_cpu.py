@@ -74,7 +74,9 @@ def _train(rank, world, moe, targs, steps, full_state):
     tr = Trainer(model=model, args=args, train_dataset=ds)
     tr._sampler_shuffle = False
     tr.train()
-    return [h["loss"] for h in tr.state.log_history if "loss" in h]
+    # the gradient norm of the first step rides along as a fourth number: it reacts to a wrong or missing gradient
+    # reduction long before the losses of a few steps do
+    return [h["loss"] for h in tr.state.log_history if "loss" in h] + [tr.state.log_history[0]["global_norm"]]
 
 
 def _reference(moe, steps, accum):
@@ -106,6 +108,10 @@ def _reference(moe, steps, accum):
     ("tp2_qk_norm_moe", 2, True, dict(tensor_model_parallel_size=2, gradient_accumulation_steps=2, moe_token_dispatcher_type="alltoall")),
     ("tp2_sp_qk_norm_moe", 2, True, dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2,
                                          moe_token_dispatcher_type="alltoall")),
+    ("tp2_sp_ep2_moe", 4, True, dict(tensor_model_parallel_size=2, sequence_parallel=True, expert_model_parallel_size=2, sharding="stage1",
+                                     gradient_accumulation_steps=1, moe_token_dispatcher_type="alltoall")),
+    ("tp2_ep2_moe", 4, True, dict(tensor_model_parallel_size=2, expert_model_parallel_size=2, sharding="stage1",
+                                  gradient_accumulation_steps=1, moe_token_dispatcher_type="alltoall")),
     ("gemma4_tp2", 2, "gemma4", dict(tensor_model_parallel_size=2, gradient_accumulation_steps=2, moe_token_dispatcher_type="alltoall")),
     ("cp2", 2, False, dict(context_parallel_size=2, gradient_accumulation_steps=2)),
     ("cp2_contiguous", 2, False, dict(context_parallel_size=2, cp_balance_mode="contiguous_allgather", gradient_accumulation_steps=2)),
@@ -121,7 +127,7 @@ def test_parallel_matches_single_process(name, world, moe, targs):
     ref = run_distributed(_train, 1, moe, single, steps, full)[0]
     got = run_distributed(_train, world, moe, targs, steps, full)
     for r in range(world):
-        assert len(got[r]) == steps
+        assert len(got[r]) == steps + 1
         for a, b in zip(ref, got[r]):
             assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (name, ref, got[r])
 
@@ -146,7 +152,7 @@ def _train_pp(rank, world, moe, targs, steps, full_state):
             p.copy_(spec.shard(full_state[g], ps.coord["mp"], ps.degrees.mp, ps.rank_in("ep"), ps.degrees.ep))
     tr = Trainer(model=model, args=args, train_dataset=_DS(_data(8 * steps)))
     tr.train()
-    return [h["loss"] for h in tr.state.log_history if "loss" in h]
+    return [h["loss"] for h in tr.state.log_history if "loss" in h] + [tr.state.log_history[0]["global_norm"]]
 
 
 def _train_single4(rank, world, moe, targs, steps, full_state):
@@ -164,7 +170,7 @@ def _train_single4(rank, world, moe, targs, steps, full_state):
             p.copy_(full_state[name])
     tr = Trainer(model=model, args=args, train_dataset=_DS(_data(8 * steps)))
     tr.train()
-    return [h["loss"] for h in tr.state.log_history if "loss" in h]
+    return [h["loss"] for h in tr.state.log_history if "loss" in h] + [tr.state.log_history[0]["global_norm"]]
 
 
 @pytest.mark.parametrize("name,targs", [
