@@ -110,12 +110,15 @@ class ShardedAdamW:
             key = (bool(getattr(p, "is_expert", False)), bool(no_decay_fn(name)), p.dtype, bool(self._is_muon_param(name, p)))
             groups.setdefault(key, []).append((name, p))
         # Expert gradients are summed over the moe_sharding group (all ranks that hold the same experts: mp x data / ep of
-        # them) and divided by its size; relative to dense parameters (averaged over the data ranks) that needs a factor.
-        # With sequence parallelism the tensor-parallel ranks of the group hold DIFFERENT tokens, so their sum is the
-        # gradient of all tokens once: factor mp * cp / ep (paddleformers/trainer/training_args.py:2808-2815). Without it
-        # they hold the SAME tokens and the sum counts every token mp times: factor cp / ep.
+        # them, context- and segment-parallel ranks counted as data ranks because dense gradients are averaged over them
+        # too) and divided by its size; relative to dense parameters, which are averaged over the data ranks, that needs a
+        # factor. With sequence parallelism the tensor-parallel ranks of the group hold DIFFERENT tokens, so the sum is the
+        # gradient of every token once: factor mp / ep. Without it they hold the SAME tokens and the sum counts every
+        # token mp times: factor 1 / ep. (The reference's factor tp * cp / ep, paddleformers/trainer/training_args.py:
+        # 2808-2815, is the same rule for a trainer that always runs MoE layers sequence parallel and does not average dense
+        # gradients over the context-parallel ranks.)
         sp = bool(getattr(getattr(model, "config", None), "sequence_parallel", False)) and d.mp > 1
-        expert_scale = float((d.mp if sp else 1) * d.cp) / float(d.ep) if d.ep > 1 else 1.0
+        expert_scale = float(d.mp if sp else 1) / float(d.ep) if d.ep > 1 else 1.0
         for (is_expert, no_decay, dtype, is_muon), plist in sorted(groups.items(),
                                                                    key=lambda kv: (kv[0][0], kv[0][1], str(kv[0][2]), kv[0][3])):
             if is_expert and d.ep > 1:

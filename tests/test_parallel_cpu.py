@@ -112,6 +112,11 @@ def _reference(moe, steps, accum):
                                      gradient_accumulation_steps=1, moe_token_dispatcher_type="alltoall")),
     ("tp2_ep2_moe", 4, True, dict(tensor_model_parallel_size=2, expert_model_parallel_size=2, sharding="stage1",
                                   gradient_accumulation_steps=1, moe_token_dispatcher_type="alltoall")),
+    ("ep2_cp2_moe", 4, True, dict(expert_model_parallel_size=2, context_parallel_size=2, sharding="stage1", gradient_accumulation_steps=1,
+                                  moe_token_dispatcher_type="alltoall")),
+    ("ep2_sep2_moe", 4, True, dict(expert_model_parallel_size=2, sep_parallel_size=2, sharding="stage1", gradient_accumulation_steps=1,
+                                   moe_token_dispatcher_type="alltoall")),
+    ("tp2_cp2", 4, False, dict(tensor_model_parallel_size=2, context_parallel_size=2, gradient_accumulation_steps=2)),
     ("gemma4_tp2", 2, "gemma4", dict(tensor_model_parallel_size=2, gradient_accumulation_steps=2, moe_token_dispatcher_type="alltoall")),
     ("cp2", 2, False, dict(context_parallel_size=2, gradient_accumulation_steps=2)),
     ("cp2_contiguous", 2, False, dict(context_parallel_size=2, cp_balance_mode="contiguous_allgather", gradient_accumulation_steps=2)),
