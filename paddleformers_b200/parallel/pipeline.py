@@ -431,12 +431,30 @@ class PipelineStageModel(PretrainedModel):
             return hidden
         return hidden + residual if residual is not None else hidden
 
+    def _head_loss(self, hidden, labels, scale, gather: bool = False):
+        """Head + cross entropy on this stage: under sequence parallelism the token slices are gathered first (every rank then
+        holds all rows; the backward pass keeps this rank's slice); a head that is a vocabulary shard (tied to a
+        vocabulary-parallel embedding) goes through the vocabulary-parallel loss."""
+        ps = get_parallel_state()
+        tp, w = ps.degrees.mp, self.head_weight()
+        if gather and tp > 1 and getattr(self.chunks[-1], "sp", False):
+            from .tensor_parallel import GatherOp
+
+            hidden = GatherOp.apply(hidden, ps.group("mp"))
+        if tp > 1 and w.shape[0] != self.config.vocab_size:
+            from .vocab_parallel_loss import vocab_parallel_linear_cross_entropy
+
+            return vocab_parallel_linear_cross_entropy(hidden, w, labels, self.ignore_index, scale)[0]
+        return F.fused_linear_cross_entropy(hidden, w, labels, self.ignore_index, 2048, scale)[0]
+
     def loss(self, hidden, batch, ctx):
         labels = batch["labels"].reshape(-1)
         count = (labels != self.ignore_index).sum()
         scale = 1.0 / (count.clamp(min=1).float() * float(self.loss_accumulation_steps))
-        loss, _ = F.fused_linear_cross_entropy(hidden, self.head_weight(), labels, self.ignore_index, 2048, scale)
+        loss = self._head_loss(hidden, labels, scale, gather=True)
         if len(self.mtp_layers) > 0:
+            if getattr(self.chunks[-1], "sp", False):
+                raise NotImplementedError("multi-token-prediction layers on a pipeline stage are implemented without sequence parallelism")
             ids, lab, h = batch["input_ids"], batch["labels"], hidden
             extra = []
             for layer in self.mtp_layers:
@@ -447,7 +465,7 @@ class PipelineStageModel(PretrainedModel):
                 flat = lab.reshape(-1)
                 cnt = (flat != self.ignore_index).sum()
                 sc = 1.0 / (cnt.clamp(min=1).float() * float(self.loss_accumulation_steps))
-                extra.append(F.fused_linear_cross_entropy(h, self.head_weight(), flat, self.ignore_index, 2048, sc)[0])
+                extra.append(self._head_loss(h, flat, sc))
             loss = loss + float(getattr(self.config, "mtp_loss_scaling_factor", 0.1)) * torch.stack(extra).mean()
         return loss
 
@@ -535,7 +553,9 @@ class PipelineEngine:
                     if src_stage == s:
                         x_in = local_fwd.pop((vs - 1, a.mb))
                     else:
-                        x_in = self._recv((B * S, H), dtype, dev, self.ranks[src_stage], self.fwd_group)
+                        # under sequence parallelism a stage hands over this rank's slice of the tokens
+                        rows = B * S // self.ps.degrees.mp if getattr(model.chunks[0], "sp", False) else B * S
+                        x_in = self._recv((rows, H), dtype, dev, self.ranks[src_stage], self.fwd_group)
                     x_in.requires_grad_(True)
                 out = model.forward_chunk(a.chunk, x_in, batch, ctx)
                 if vs == last_virtual:
@@ -591,6 +611,9 @@ class PipelineEngine:
             return
         for p in shared:
             g = getattr(p, "main_grad", None)
+            if g is not None and p.grad is not None:
+                g.add_(p.grad.to(g.dtype))          # what autograd left in .grad belongs to the sum as well
+                p.grad = None
             if g is None:
                 g = p.grad
             if g is not None:

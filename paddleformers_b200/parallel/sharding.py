@@ -239,6 +239,25 @@ class ShardedAdamW:
             self._rep_bounds = bounds
         return [shards[di][a:b] for di, a, b in self._rep_bounds]
 
+    def _pp_shared_slices(self, shards):
+        """Views of the local gradient shards of parameters that exist on two pipeline stages (a head tied to the input
+        embedding, the embedding copy of multi-token-prediction layers), on every stage but the first: both copies hold the
+        summed gradient, and the norm must count it once."""
+        if getattr(self, "_pp_shared_bounds", None) is None:
+            bounds = []
+            if self.ps.degrees.pp > 1 and self.ps.coord["pp"] != 0:
+                for di, dom in enumerate(self.domains):
+                    n = dom.shard_numel
+                    lo = dom.shard_rank * n
+                    for name, p in dom.params:
+                        if getattr(p, "pp_shared", None):
+                            off, cnt = dom.offsets[name]
+                            a, b = max(off, lo), min(off + cnt, lo + n)
+                            if b > a:
+                                bounds.append((di, a - lo, b - lo))
+            self._pp_shared_bounds = bounds
+        return [shards[di][a:b] for di, a, b in self._pp_shared_bounds]
+
     def reduce_gradients(self):
         """Sum gradients over the data replicas: reduce-scatter inside the sharding group, all-reduce over dp.
         Returns the local fp32 gradient shard of every domain (views of the flat gradient buffers)."""
@@ -293,6 +312,9 @@ class ShardedAdamW:
                 # one multi-tensor norm over all replicated slices instead of a launch per parameter
                 rep = torch.stack(torch._foreach_norm(views)).double().pow(2).sum().float().reshape(1)
                 acc_dense = acc_dense - rep * (1.0 - 1.0 / ps.degrees.mp)  # experts with ep == 1 are folded in here too
+        dup = self._pp_shared_slices(shards)
+        if dup:
+            acc_dense = acc_dense - torch.stack(torch._foreach_norm(dup)).double().pow(2).sum().float().reshape(1)
         total = torch.cat([acc_dense, acc_expert])
         if dist.is_initialized() and ps.world_size > 1:
             # dense shards: sum over sharding x mp x pp (x sep x cp hold identical copies -> not summed);

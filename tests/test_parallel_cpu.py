@@ -19,6 +19,9 @@ def _tiny_cfg(moe=False, **kw):
                     attention_k_eq_v=True, num_global_key_value_heads=2)
         base.update(kw)
         return AutoConfig.for_model("gemma4_text", **base)
+    if moe == "tied":            # dense, the head shares the embedding table
+        kw = dict(kw, tie_word_embeddings=True)
+        moe = False
     if moe:
         base = dict(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
                     num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, vocab_size=128, router_aux_loss_coef=0.0)
@@ -191,15 +194,44 @@ def _train_single4(rank, world, moe, targs, steps, full_state):
                                                refined_recompute={"attention_row_ln": 0, "mlp_row_ln": 0})),
 ])
 def test_pipeline_matches_single_process(name, targs):
+    _pipeline_case(name, 2, False, targs, 4)
+
+
+@pytest.mark.parametrize("name,world,kind,targs,single_accum", [
+    # stages hand over token slices under sequence parallelism; the last stage gathers them for the loss
+    ("pp2_tp2_sp", 4, False, dict(pipeline_model_parallel_size=2, tensor_model_parallel_size=2, sequence_parallel=True,
+                                  gradient_accumulation_steps=4), 4),
+    # a head tied to the input embedding: the gradients of both copies are summed, the norm counts them once
+    ("pp2_tied", 2, "tied", dict(pipeline_model_parallel_size=2, gradient_accumulation_steps=4), 4),
+    ("pp2_tied_zbv", 2, "tied", dict(pipeline_model_parallel_size=2, gradient_accumulation_steps=4, pipeline_schedule="zbv"), 4),
+    # ... and to a vocabulary-parallel embedding: the last stage holds a vocabulary shard
+    ("pp2_tp2_tied", 4, "tied", dict(pipeline_model_parallel_size=2, tensor_model_parallel_size=2, gradient_accumulation_steps=4), 4),
+    ("pp2_tp2_sp_tied", 4, "tied", dict(pipeline_model_parallel_size=2, tensor_model_parallel_size=2, sequence_parallel=True,
+                                        gradient_accumulation_steps=4), 4),
+    # experts sharded inside every stage
+    ("pp2_ep2_moe", 4, True, dict(pipeline_model_parallel_size=2, expert_model_parallel_size=2, sharding="stage1",
+                                  gradient_accumulation_steps=2, moe_token_dispatcher_type="alltoall"), 4),
+    ("pp2_ep2_moe_zero_bubble", 4, True, dict(pipeline_model_parallel_size=2, expert_model_parallel_size=2, sharding="stage1",
+                                              gradient_accumulation_steps=2, pipeline_schedule="zero_bubble",
+                                              moe_token_dispatcher_type="alltoall"), 4),
+])
+def test_pipeline_with_tensor_and_expert_parallelism(name, world, kind, targs, single_accum):
+    _pipeline_case(name, world, kind, targs, single_accum)
+
+
+def _pipeline_case(name, world, kind, targs, single_accum):
     from paddleformers_b200.models.modeling import MODEL_MAPPING
 
     steps = 2
     torch.manual_seed(5)
-    cfg = _tiny_cfg(False, num_hidden_layers=4)
+    cfg = _tiny_cfg(kind, num_hidden_layers=4)
     full = {k: v.detach().clone() for k, v in MODEL_MAPPING[cfg.model_type](cfg).named_parameters()}
-    ref = run_distributed(_train_single4, 1, False, dict(gradient_accumulation_steps=4), steps, full)[0]
-    got = run_distributed(_train_pp, 2, False, targs, steps, full)
-    for r in range(2):
+    single = dict(gradient_accumulation_steps=single_accum)
+    if kind is True:
+        single["moe_token_dispatcher_type"] = "alltoall"
+    ref = run_distributed(_train_single4, 1, kind, single, steps, full)[0]
+    got = run_distributed(_train_pp, world, kind, targs, steps, full)
+    for r in range(world):
         for a, b in zip(ref, got[r]):
             assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (name, ref, got[r])
 
