@@ -92,6 +92,17 @@ def _reference(moe, steps, accum):
     return full
 
 
+_REF_CACHE = {}
+
+
+def _single_process_run(worker, kind, single, steps, full):
+    """The single-process trajectory of a model kind is the same for every strategy that is compared with it: run it once."""
+    key = (worker.__name__, kind, tuple(sorted(single.items())), steps)
+    if key not in _REF_CACHE:
+        _REF_CACHE[key] = run_distributed(worker, 1, kind, single, steps, full)[0]
+    return _REF_CACHE[key]
+
+
 @pytest.mark.parametrize("name,world,moe,targs", [
     ("tp2_sp", 2, False, dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2)),
     ("tp2", 2, False, dict(tensor_model_parallel_size=2, gradient_accumulation_steps=2)),
@@ -132,7 +143,7 @@ def test_parallel_matches_single_process(name, world, moe, targs):
     single = dict(gradient_accumulation_steps=2)
     if moe:
         single["moe_token_dispatcher_type"] = "alltoall"
-    ref = run_distributed(_train, 1, moe, single, steps, full)[0]
+    ref = _single_process_run(_train, moe, single, steps, full)
     got = run_distributed(_train, world, moe, targs, steps, full)
     for r in range(world):
         assert len(got[r]) == steps + 1
@@ -229,7 +240,7 @@ def _pipeline_case(name, world, kind, targs, single_accum):
     single = dict(gradient_accumulation_steps=single_accum)
     if kind is True:
         single["moe_token_dispatcher_type"] = "alltoall"
-    ref = run_distributed(_train_single4, 1, kind, single, steps, full)[0]
+    ref = _single_process_run(_train_single4, kind, single, steps, full)
     got = run_distributed(_train_pp, world, kind, targs, steps, full)
     for r in range(world):
         for a, b in zip(ref, got[r]):
