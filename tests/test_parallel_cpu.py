@@ -629,3 +629,47 @@ def test_per_head_norm_weights_get_the_gradient_of_all_heads_under_tensor_parall
         assert (ref[n] - 1.0).abs().max() > 1e-3                                 # the weights moved
         assert torch.equal(got[0][n], got[1][n]), n
         assert (got[0][n] - ref[n]).abs().max() < 2e-3 * (ref[n] - 1.0).abs().max() + 1e-6, n
+
+
+def _train_and_save_pp(rank, world, kind, targs, steps, full_state, out_dir, resume):
+    from paddleformers_b200 import Trainer, TrainingArguments
+    from paddleformers_b200.parallel.pipeline import build_pipeline_model
+    from paddleformers_b200.transformers.configuration_utils import LlmMetaConfig
+    from paddleformers_b200.transformers.model_utils import param_shard_spec
+
+    args = TrainingArguments(output_dir=out_dir, per_device_train_batch_size=1, max_steps=steps, learning_rate=1e-2,
+                             lr_scheduler_type="constant", logging_steps=1, save_steps=2, max_seq_len=32, max_grad_norm=1.0,
+                             seed=3, device="cpu", **targs)
+    ps = args.setup_parallel()
+    cfg = _tiny_cfg(kind, num_hidden_layers=4)
+    LlmMetaConfig.set_llm_config(cfg, args)
+    model = build_pipeline_model(cfg)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            g = model.global_param_name(name)
+            p.copy_(param_shard_spec(p).shard(full_state[g], ps.coord["mp"], ps.degrees.mp, ps.rank_in("ep"), ps.degrees.ep))
+    tr = Trainer(model=model, args=args, train_dataset=_DS(_data(8 * 4)))
+    tr._sampler_shuffle = False
+    tr.train(resume_from_checkpoint="auto" if resume else None)
+    return [h["loss"] for h in tr.state.log_history if "loss" in h]
+
+
+@pytest.mark.parametrize("name,world,kind,targs", [
+    ("pp2_tied", 2, "tied", dict(pipeline_model_parallel_size=2, gradient_accumulation_steps=4)),
+    ("pp2_ep2", 4, True, dict(pipeline_model_parallel_size=2, expert_model_parallel_size=2, sharding="stage1",
+                              gradient_accumulation_steps=2, moe_token_dispatcher_type="alltoall")),
+])
+def test_checkpoint_resumes_under_pipeline_parallelism(tmp_path, name, world, kind, targs):
+    """Stages save and reload their own layers, optimizer shards and (tied head) shared tensors: the resumed run continues like
+    the uninterrupted one."""
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+
+    torch.manual_seed(5)
+    cfg = _tiny_cfg(kind, num_hidden_layers=4)
+    full = {k: v.detach().clone() for k, v in MODEL_MAPPING[cfg.model_type](cfg).named_parameters()}
+    ref = run_distributed(_train_and_save_pp, world, kind, dict(targs), 4, full, str(tmp_path / "ref"), False)[0]
+    run_distributed(_train_and_save_pp, world, kind, dict(targs), 2, full, str(tmp_path / "run"), False)
+    got = run_distributed(_train_and_save_pp, world, kind, dict(targs), 4, full, str(tmp_path / "run"), True)[0]
+    assert len(got) >= 2
+    for a, b in zip(ref[2:], got[-2:]):
+        assert abs(a - b) < 3e-4 * max(1.0, abs(a)), (name, ref, got)
