@@ -19,7 +19,7 @@ import torch
 import torch.nn as nn
 
 from ..ops import functional as F
-from ..parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear
+from ..parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear, mark_as_sequence_parallel_parameter
 
 LORA_CONFIG_NAME = "lora_config.json"
 LORA_WEIGHTS_NAME = "lora_model.safetensors"
@@ -68,10 +68,17 @@ class LoRALinear(nn.Module):
         self.lora_B = nn.Parameter(torch.zeros(out_f, cfg.r, dtype=w.dtype, device=w.device))
         nn.init.kaiming_uniform_(self.lora_A, a=math.sqrt(5))
         self.lora_B.lora_plus = True
+        # The factor that stays whole on every tensor-parallel rank meets only this rank's slice of the other factor, so its
+        # gradient is a partial sum: it is added up over the group before the optimizer step, like the norm weights under
+        # sequence parallelism.
         if isinstance(base, ColumnParallelLinear):
             self.lora_B.shard_spec = ("tp", 0, base.sections)
+            if base.tp > 1:
+                mark_as_sequence_parallel_parameter(self.lora_A)
         elif isinstance(base, RowParallelLinear):
             self.lora_A.shard_spec = ("tp", 1, None)
+            if base.tp > 1:
+                mark_as_sequence_parallel_parameter(self.lora_B)
         self.dropout = nn.Dropout(cfg.lora_dropout) if cfg.lora_dropout > 0 else None
         self.merged = False
         self.disabled = False
@@ -143,6 +150,8 @@ class LoRAMoeExperts(nn.Module):
         for p in (self.gu_A, self.gu_B, self.dn_A, self.dn_B):
             p.is_expert = True
             p.shard_spec = ("ep", 0, None)
+            if getattr(experts.gate_up_proj, "sequence_parallel", False):     # token slices per tensor-parallel rank: partial sums
+                mark_as_sequence_parallel_parameter(p)
         experts.gate_up_proj.requires_grad_(False)
         experts.down_proj.requires_grad_(False)
         self.num_local, self.expert_offset = experts.num_local, experts.expert_offset

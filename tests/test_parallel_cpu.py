@@ -673,3 +673,43 @@ def test_checkpoint_resumes_under_pipeline_parallelism(tmp_path, name, world, ki
     assert len(got) >= 2
     for a, b in zip(ref[2:], got[-2:]):
         assert abs(a - b) < 3e-4 * max(1.0, abs(a)), (name, ref, got)
+
+
+def _lora_tp_worker(rank, world, full, sp):
+    from paddleformers_b200 import Trainer, TrainingArguments
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+    from paddleformers_b200.peft.lora import LoRAConfig, LoRAModel
+    from paddleformers_b200.transformers.configuration_utils import LlmMetaConfig
+    from paddleformers_b200.transformers.model_utils import param_shard_spec
+
+    args = TrainingArguments(output_dir="/tmp/pfb_test_unused", per_device_train_batch_size=2, max_steps=3, learning_rate=1e-2,
+                             lr_scheduler_type="constant", logging_steps=1, save_strategy="no", max_seq_len=32, seed=3, device="cpu",
+                             tensor_model_parallel_size=world, sequence_parallel=sp and world > 1, max_grad_norm=1.0)
+    ps = args.setup_parallel()
+    cfg = _tiny_cfg(False)
+    LlmMetaConfig.set_llm_config(cfg, args)
+    model = LoRAModel(MODEL_MAPPING[cfg.model_type](cfg), LoRAConfig(r=4, lora_alpha=8))
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            p.copy_(param_shard_spec(p).shard(full[n], ps.coord["mp"], ps.degrees.mp, 0, 1))
+    tr = Trainer(model=model, args=args, train_dataset=_DS(_data(8)))
+    tr._sampler_shuffle = False
+    tr.train()
+    return [h["loss"] for h in tr.state.log_history if "loss" in h] + [tr.state.log_history[0]["global_norm"]]
+
+
+def test_lora_adapters_under_tensor_parallelism():
+    """The adapter factor that is whole on every rank (A beside a column-parallel layer, B beside a row-parallel one) gets its
+    gradient summed over the tensor-parallel group; losses and the gradient norm follow the single-process run."""
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+    from paddleformers_b200.peft.lora import LoRAConfig, LoRAModel
+
+    torch.manual_seed(5)
+    cfg = _tiny_cfg(False)
+    m = LoRAModel(MODEL_MAPPING[cfg.model_type](cfg), LoRAConfig(r=4, lora_alpha=8))
+    full = {k: (v.detach().clone() if "lora_B" not in k else torch.randn_like(v) * 0.05) for k, v in m.named_parameters()}
+    ref = run_distributed(_lora_tp_worker, 1, full, False)[0]
+    got = run_distributed(_lora_tp_worker, 2, full, True)
+    for r in range(2):
+        for a, b in zip(ref, got[r]):
+            assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (ref, got[r])
