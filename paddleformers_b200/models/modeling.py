@@ -25,7 +25,7 @@ from ..nn.moe import DenseMLP, MoELayer
 from ..generation.utils import GenerationMixin
 from ..ops import functional as F
 from ..utils.refined_recompute import checkpoint_keeping, keep, kept_ops_of_layer
-from ..parallel.tensor_parallel import (ColumnParallelLinear, GatherOp, RowParallelLinear, ScatterOp,
+from ..parallel.tensor_parallel import (AllGatherOp, ColumnParallelLinear, CopyToTP, GatherOp, RowParallelLinear, ScatterOp,
                                         VocabParallelEmbedding, mark_as_sequence_parallel_parameter)
 from ..parallel.topology import get_parallel_state
 from ..transformers.conversion_utils import Rule, WeightMap, expand_layers
@@ -388,8 +388,16 @@ class MLAAttention(nn.Module):
         if rs and rs.get("mscale_all_dim"):
             m = 0.1 * float(rs["mscale_all_dim"]) * math.log(float(rs.get("factor", 1.0))) + 1.0
             self.scale = self.scale * m * m
+        self.tp = tp
         self.sp = bool(getattr(config, "sequence_parallel", False)) and tp > 1
         self.group = get_parallel_state().group("mp")
+        if self.sp:
+            # the replicated low-rank projections and their norms see this rank's token slice only: partial gradients,
+            # summed over the group before the optimizer step
+            reps = [self.kv_a_proj_with_mqa.weight, self.kv_a_layernorm.weight]
+            reps += [self.q_a_proj.weight, self.q_a_layernorm.weight] if self.q_lora else []
+            for p in reps:
+                mark_as_sequence_parallel_parameter(p)
         self.indexer = None
         if getattr(config, "index_topk", None):
             assert tp == 1 and self.q_lora, "sparse (indexer) attention needs the latent query and tensor-parallel degree 1"
@@ -404,10 +412,13 @@ class MLAAttention(nn.Module):
         else:
             q = _apply(self.q_proj, x2d)
         ckv = _apply(self.kv_a_proj_with_mqa, x2d)
-        if self.sp:  # replicated projections ran on token shards: gather tokens for the per-head products
-            ckv = GatherOp.apply(ckv, self.group)
         kv_lat, k_pe = ckv[:, : self.kv_lora], ckv[:, self.kv_lora:]
+        # the latent goes through a column-parallel projection, which gathers token slices (sequence parallelism) and sums
+        # the heads' gradients over the ranks itself; the shared rotary key does not, so it gets the same treatment here:
+        # every rank's heads read it, and their gradients are added up on the way back
         kv = _apply(self.kv_b_proj, self.kv_a_layernorm(kv_lat.contiguous()))
+        if self.tp > 1:
+            k_pe = AllGatherOp.apply(k_pe.contiguous(), self.group) if self.sp else CopyToTP.apply(k_pe.contiguous(), self.group)
         q = q.view(T, self.Hq, self.qd)
         kv = kv.view(T, self.Hq, self.nope + self.vd)
         q_pe = F.rope_heads(q[..., self.nope:].reshape(T, self.Hq * self.rope), ctx.cos, ctx.sin, ctx.positions,
@@ -537,11 +548,16 @@ class MTPLayer(nn.Module):
 
     def __init__(self, config: DecoderConfig, layer_idx: int, dtype=None, device=None):
         super().__init__()
-        self.enorm = RMSNorm(config.hidden_size, config.rms_norm_eps, dtype=dtype, device=device)
-        self.hnorm = RMSNorm(config.hidden_size, config.rms_norm_eps, dtype=dtype, device=device)
+        # under sequence parallelism the layer works on this rank's token slice: its replicated weights collect partial
+        # gradients, which are summed over the group before the optimizer step
+        sp = bool(getattr(config, "sequence_parallel", False)) and get_parallel_state().degrees.mp > 1
+        self.enorm = RMSNorm(config.hidden_size, config.rms_norm_eps, sp, dtype=dtype, device=device)
+        self.hnorm = RMSNorm(config.hidden_size, config.rms_norm_eps, sp, dtype=dtype, device=device)
         self.eh_proj = nn.Linear(2 * config.hidden_size, config.hidden_size, bias=False, dtype=dtype, device=device)
+        if sp:
+            mark_as_sequence_parallel_parameter(self.eh_proj.weight)
         self.block = DecoderLayer(config, layer_idx, dtype=dtype, device=device)
-        self.final_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps, dtype=dtype, device=device)
+        self.final_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps, sp, dtype=dtype, device=device)
 
     def forward(self, h2d, shifted_emb2d, ctx):
         x = torch.cat([self.enorm(shifted_emb2d), self.hnorm(h2d)], dim=-1)
@@ -824,9 +840,12 @@ class DecoderForCausalLM(PretrainedModel, GenerationMixin):
 
     def forward(self, input_ids, labels=None, position_ids=None, attn_mask_startend_row_indices=None, kend=None,
                 caches=None, return_logits: Optional[bool] = None, cp_global_positions=None, cp_full_seq_len=None,
-                full_attn_mask_startend_row_indices=None, **unused):
+                full_attn_mask_startend_row_indices=None, full_input_ids=None, full_labels=None, mtp_global_positions=None,
+                **unused):
         """``labels`` are next-token targets aligned with ``input_ids`` (already shifted by the data pipeline, as in
-        the reference's collators). ``attn_mask_startend_row_indices`` / ``kend``: int [B, S] FlashMask start rows."""
+        the reference's collators). ``attn_mask_startend_row_indices`` / ``kend``: int [B, S] FlashMask start rows.
+        ``full_input_ids`` / ``full_labels`` / ``mtp_global_positions``: under context / segment parallelism the unsliced rows
+        and the global position of every local token, for the multi-token-prediction heads."""
         if kend is None and attn_mask_startend_row_indices is not None:
             kend = attn_mask_startend_row_indices.reshape(input_ids.shape[0], -1)
         kend_full = full_attn_mask_startend_row_indices
@@ -860,38 +879,50 @@ class DecoderForCausalLM(PretrainedModel, GenerationMixin):
                 loss, _ = self._loss(hidden, lab, scale)
             out.num_tokens = count
             if len(self.mtp_layers) > 0:
-                out.mtp_losses = self._mtp_losses(hidden, input_ids, labels, ctx, scale)
+                # The fused head + loss functions write the head's weight gradient (already multiplied by their ``scale``)
+                # into main_grad during the forward pass, so a factor applied to their result afterwards would reach dh but
+                # not dW: the weight of the multi-token-prediction term, lam / depth, goes into the scale instead.
                 lam = float(getattr(self.config, "mtp_loss_scaling_factor", 0.1))
-                loss = loss + lam * torch.stack(out.mtp_losses).mean()
+                w = lam / len(self.mtp_layers)
+                weighted = self._mtp_losses(hidden, input_ids, labels, ctx, scale, weight=w,
+                                            full=(full_input_ids, full_labels, mtp_global_positions))
+                out.mtp_losses = [l.detach() / w for l in weighted]
+                loss = loss + torch.stack(weighted).sum()
             aux = [m.mlp.last_aux_loss for m in self.model.layers.values() if isinstance(m.mlp, MoELayer) and m.mlp.last_aux_loss is not None]
             if aux:
                 out.aux_loss = torch.stack(aux).sum()
             out.loss = loss
         return out
 
-    def _mtp_losses(self, hidden, input_ids, labels, ctx, scale):
+    def _mtp_losses(self, hidden, input_ids, labels, ctx, scale, weight: float = 1.0, full=(None, None, None)):
         """Depth-k MTP head predicts token t+1+k from h_t and the embedding of token t+k; sequences are shifted left
-        and the tail positions are ignored (paddleformers/nn/criterion/sft_loss.py:188-247)."""
+        and the tail positions are ignored (paddleformers/nn/criterion/sft_loss.py:188-247). Every loss comes back already
+        multiplied by ``weight``."""
         losses = []
-        h = hidden
+        h = hidden                       # under sequence parallelism: this rank's token slice, like every layer input
         ids, lab = input_ids, labels
-        if self.sp:
-            h = GatherOp.apply(h, get_parallel_state().group("mp"))
+        full_ids, full_lab, gpos = full
         for k, layer in enumerate(self.mtp_layers, start=1):
-            ids = torch.cat([ids[:, 1:], ids[:, -1:]], dim=1)
-            lab = torch.cat([lab[:, 1:], torch.full_like(lab[:, -1:], self.ignore_index)], dim=1)
-            emb = F.embedding(ids, self.model.embed_tokens.weight).reshape(-1, self.config.hidden_size) \
-                if not isinstance(self.model.embed_tokens, VocabParallelEmbedding) else \
-                _full_tokens(self.model.embed_tokens(ids), self.sp)
+            if full_ids is not None and gpos is not None:
+                # this rank holds a slice of the sequence: token t + k and its label may live on another rank
+                ahead = gpos + k
+                inside = ahead < full_ids.shape[1]
+                ahead = ahead.clamp(max=full_ids.shape[1] - 1)
+                ids = full_ids.index_select(1, ahead)
+                lab = torch.where(inside[None], full_lab.index_select(1, ahead), torch.full_like(lab, self.ignore_index))
+            else:
+                ids = torch.cat([ids[:, 1:], ids[:, -1:]], dim=1)
+                lab = torch.cat([lab[:, 1:], torch.full_like(lab[:, -1:], self.ignore_index)], dim=1)
+            if isinstance(self.model.embed_tokens, VocabParallelEmbedding):
+                emb = self.model.embed_tokens(ids)          # token slices under sequence parallelism, whole rows otherwise
+                emb = emb.reshape(-1, emb.shape[-1])
+            else:
+                emb = F.embedding(ids, self.model.embed_tokens.weight).reshape(-1, self.config.hidden_size)
             h = layer(h, emb, ctx)
             flat = lab.reshape(-1)
             cnt = (flat != self.ignore_index).sum()
-            sc = 1.0 / (self._label_norm(cnt) * float(self.loss_accumulation_steps))
-            saved_sp, self.sp = self.sp, False  # h is already token-complete
-            try:
-                l, _ = self._loss(h, flat, sc)
-            finally:
-                self.sp = saved_sp
+            sc = weight / (self._label_norm(cnt) * float(self.loss_accumulation_steps))
+            l, _ = self._loss(h, flat, sc)                  # gathers the token slices itself under sequence parallelism
             losses.append(l)
         return losses
 

@@ -40,6 +40,13 @@ def cp_positions(S: int, cp: int, rank: int, mode: str, device) -> torch.Tensor:
     return _zigzag_index(S, cp, rank, device)
 
 
+def _keep_unsliced_for_mtp(batch, out, idx) -> None:
+    """Multi-token-prediction heads look k tokens ahead, across slice boundaries: the whole token and label rows (small
+    integer tensors) travel with the slice, together with the global position of every local token."""
+    if "labels" in batch:
+        out["full_input_ids"], out["full_labels"], out["mtp_global_positions"] = batch["input_ids"], batch["labels"], idx
+
+
 def get_batch_on_this_cp_rank(batch: Dict[str, torch.Tensor], ps: Optional[ParallelState] = None,
                               mode: str = "dualchunk_allgather") -> Dict[str, torch.Tensor]:
     ps = ps or get_parallel_state()
@@ -59,6 +66,7 @@ def get_batch_on_this_cp_rank(batch: Dict[str, torch.Tensor], ps: Optional[Paral
         out["position_ids"] = idx[None].expand(batch["input_ids"].shape[0], -1).contiguous()
     out["cp_global_positions"] = idx
     out["cp_full_seq_len"] = S
+    _keep_unsliced_for_mtp(batch, out, idx)
     return out
 
 
@@ -75,6 +83,7 @@ def split_inputs_sequence_dim(batch: Dict[str, torch.Tensor], ps: Optional[Paral
     if batch.get("attn_mask_startend_row_indices") is not None:
         out["full_attn_mask_startend_row_indices"] = batch["attn_mask_startend_row_indices"]
     out["cp_full_seq_len"] = S
+    _keep_unsliced_for_mtp(batch, out, torch.arange(r * per, (r + 1) * per, device=batch["input_ids"].device))
     for k in _SEQ_KEYS:
         if k in batch and isinstance(batch[k], torch.Tensor) and batch[k].dim() >= 2 and batch[k].shape[1] == S:
             out[k] = batch[k][:, r * per:(r + 1) * per].contiguous()

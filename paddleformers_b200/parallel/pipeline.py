@@ -456,6 +456,9 @@ class PipelineStageModel(PretrainedModel):
             if getattr(self.chunks[-1], "sp", False):
                 raise NotImplementedError("multi-token-prediction layers on a pipeline stage are implemented without sequence parallelism")
             ids, lab, h = batch["input_ids"], batch["labels"], hidden
+            # the weight of the term goes into the scale of the fused head + loss (its weight gradient is written during the
+            # forward pass and would not see a factor applied afterwards)
+            w = float(getattr(self.config, "mtp_loss_scaling_factor", 0.1)) / len(self.mtp_layers)
             extra = []
             for layer in self.mtp_layers:
                 ids = torch.cat([ids[:, 1:], ids[:, -1:]], 1)
@@ -464,9 +467,9 @@ class PipelineStageModel(PretrainedModel):
                 h = layer(h, emb, ctx)
                 flat = lab.reshape(-1)
                 cnt = (flat != self.ignore_index).sum()
-                sc = 1.0 / (cnt.clamp(min=1).float() * float(self.loss_accumulation_steps))
+                sc = w / (cnt.clamp(min=1).float() * float(self.loss_accumulation_steps))
                 extra.append(self._head_loss(h, flat, sc))
-            loss = loss + float(getattr(self.config, "mtp_loss_scaling_factor", 0.1)) * torch.stack(extra).mean()
+            loss = loss + torch.stack(extra).sum()
         return loss
 
 

@@ -19,6 +19,15 @@ def _tiny_cfg(moe=False, **kw):
                     attention_k_eq_v=True, num_global_key_value_heads=2)
         base.update(kw)
         return AutoConfig.for_model("gemma4_text", **base)
+    if moe == "mla":             # latent attention + sigmoid group-limited router + shared expert + one MTP layer
+        from paddleformers_b200.transformers.auto import AutoConfig
+
+        base = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=4, n_routed_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, n_shared_experts=1,
+                    first_k_dense_replace=1, q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                    n_group=2, topk_group=1, num_nextn_predict_layers=1, max_position_embeddings=128)
+        base.update(kw)
+        return AutoConfig.for_model("deepseek_v3", **base)
     if moe == "tied":            # dense, the head shares the embedding table
         kw = dict(kw, tie_word_embeddings=True)
         moe = False
@@ -131,6 +140,14 @@ def _single_process_run(worker, kind, single, steps, full):
     ("ep2_sep2_moe", 4, True, dict(expert_model_parallel_size=2, sep_parallel_size=2, sharding="stage1", gradient_accumulation_steps=1,
                                    moe_token_dispatcher_type="alltoall")),
     ("tp2_cp2", 4, False, dict(tensor_model_parallel_size=2, context_parallel_size=2, gradient_accumulation_steps=2)),
+    # latent attention (shared rotary key read by every rank's heads), multi-token prediction (weighted term, look-ahead across
+    # slices), sigmoid group-limited router with shared expert
+    ("mla_mtp_tp2", 2, "mla", dict(tensor_model_parallel_size=2, gradient_accumulation_steps=2, moe_token_dispatcher_type="alltoall")),
+    ("mla_mtp_tp2_sp", 2, "mla", dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2,
+                                      moe_token_dispatcher_type="alltoall")),
+    ("mla_mtp_cp2", 2, "mla", dict(context_parallel_size=2, gradient_accumulation_steps=2, moe_token_dispatcher_type="alltoall")),
+    ("mla_mtp_ep2", 2, "mla", dict(expert_model_parallel_size=2, sharding="stage1", gradient_accumulation_steps=1,
+                                   moe_token_dispatcher_type="alltoall")),
     ("gemma4_tp2", 2, "gemma4", dict(tensor_model_parallel_size=2, gradient_accumulation_steps=2, moe_token_dispatcher_type="alltoall")),
     ("cp2", 2, False, dict(context_parallel_size=2, gradient_accumulation_steps=2)),
     ("cp2_contiguous", 2, False, dict(context_parallel_size=2, cp_balance_mode="contiguous_allgather", gradient_accumulation_steps=2)),
