@@ -640,7 +640,9 @@ class MoELayer(nn.Module):
             self.shared_expert_gate = nn.Linear(config.hidden_size, 1, bias=False, dtype=dtype, device=device)
         self.ep = get_parallel_state().degrees.ep
         self.last_aux_loss = None
+        self._token_slices = 1
         if get_parallel_state().degrees.mp > 1 and getattr(config, "sequence_parallel", False):
+            self._token_slices = get_parallel_state().degrees.mp
             # under sequence parallelism every tensor-parallel rank routes and computes ITS tokens with replicated router,
             # shared-expert and (without expert parallelism) expert weights: their gradients are partial sums over the
             # tokens and are added up over the group before the optimizer step
@@ -702,6 +704,11 @@ class MoELayer(nn.Module):
             if self.shared_expert_gate is not None:
                 shared = shared * torch.sigmoid(TF.linear(x2d, self.shared_expert_gate.weight)).to(shared.dtype)
             y = y + shared
+        if aux is not None and self._token_slices > 1:
+            # under sequence parallelism every tensor-parallel rank adds the balance term of ITS token slice and the router
+            # gradients of the ranks are summed: each term counts 1 / tp, so that together they weigh as much as the one
+            # term of the unsplit batch
+            aux = aux / self._token_slices
         self.last_aux_loss = aux.detach() if aux is not None else None
         if aux is not None:
             y = AddAuxiliaryLoss.apply(y, aux)

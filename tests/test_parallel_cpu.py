@@ -19,6 +19,22 @@ def _tiny_cfg(moe=False, **kw):
                     attention_k_eq_v=True, num_global_key_value_heads=2)
         base.update(kw)
         return AutoConfig.for_model("gemma4_text", **base)
+    if isinstance(moe, str) and moe.startswith("fam:"):       # any family of the registry at tiny size
+        from paddleformers_b200.transformers.auto import AutoConfig
+
+        base = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=2, head_dim=16, max_position_embeddings=128)
+        extra = {"mixtral": dict(num_local_experts=4, num_experts_per_tok=2),
+                 "qwen2_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=48),
+                 "ernie4_5_moe": dict(moe_num_experts=4, moe_k=2, moe_intermediate_size=32, moe_num_shared_experts=1, moe_layer_start_index=1),
+                 "gpt_oss": dict(num_local_experts=4, num_experts_per_tok=2, sliding_window=8),
+                 "gemma3_text": dict(sliding_window=8, query_pre_attn_scalar=16)}.get(moe[4:].replace("+noaux", ""), {})
+        base.update(extra)
+        base.update(kw)
+        if moe.endswith("+noaux"):
+            base["router_aux_loss_coef"] = 0.0
+            return AutoConfig.for_model(moe[4:-6], **base)
+        return AutoConfig.for_model(moe[4:], **base)
     if moe == "mla":             # latent attention + sigmoid group-limited router + shared expert + one MTP layer
         from paddleformers_b200.transformers.auto import AutoConfig
 
@@ -730,3 +746,25 @@ def test_lora_adapters_under_tensor_parallelism():
     for r in range(2):
         for a, b in zip(ref, got[r]):
             assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (ref, got[r])
+
+
+def test_balance_loss_weighs_the_same_under_sequence_parallelism():
+    """Every tensor-parallel rank adds the balance term of its own token slice and the router gradients are summed over the
+    ranks: the terms count 1 / tp each. The statistics are per slice, so the run is close to the single-process one, not equal;
+    without the factor the gradient norm of this model (large balance coefficient) doubles."""
+    kind = "fam:gpt_oss"
+    full = _reference(kind, 3, 2)
+    single = dict(gradient_accumulation_steps=2, moe_token_dispatcher_type="alltoall")
+    ref = _single_process_run(_train, kind, single, 3, full)
+    got = run_distributed(_train, 2, kind, dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2,
+                                                moe_token_dispatcher_type="alltoall"), 3, full)[0]
+    assert abs(got[-1] - ref[-1]) < 0.02 * ref[-1], (ref, got)          # first-step gradient norm
+    assert abs(got[0] - ref[0]) < 1e-4 * ref[0]
+    # and exactly equal without the balance term
+    kind = "fam:mixtral+noaux"
+    full = _reference(kind, 3, 2)
+    ref = _single_process_run(_train, kind, single, 3, full)
+    got = run_distributed(_train, 2, kind, dict(tensor_model_parallel_size=2, sequence_parallel=True, gradient_accumulation_steps=2,
+                                                moe_token_dispatcher_type="alltoall"), 3, full)[0]
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (ref, got)
