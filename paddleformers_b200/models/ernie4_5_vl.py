@@ -234,7 +234,7 @@ class Ernie4_5VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
         hidden = lm.model.norm(hidden, residual)[0] if residual is not None else lm.model.norm(hidden)
         out = CausalLMOutput()
         if return_logits if return_logits is not None else labels is None:
-            out.logits = lm.compute_logits(hidden).view(ctx.B, ctx.S, -1)
+            out.logits = lm.full_logits(hidden).view(ctx.B, ctx.S, -1)
         if labels is not None:
             lab = labels.reshape(-1)
             count = (lab != lm.ignore_index).sum()

@@ -25,7 +25,7 @@ from ..nn.moe import DenseMLP, MoELayer
 from ..generation.utils import GenerationMixin
 from ..ops import functional as F
 from ..utils.refined_recompute import checkpoint_keeping, keep, kept_ops_of_layer
-from ..parallel.tensor_parallel import (AllGatherOp, ColumnParallelLinear, CopyToTP, GatherOp, RowParallelLinear, ScatterOp,
+from ..parallel.tensor_parallel import (AllGatherOp, ColumnParallelLinear, CopyToTP, GatherLastDimOp, GatherOp, RowParallelLinear, ScatterOp,
                                         VocabParallelEmbedding, mark_as_sequence_parallel_parameter)
 from ..parallel.topology import get_parallel_state
 from ..transformers.conversion_utils import Rule, WeightMap, expand_layers
@@ -783,6 +783,24 @@ class DecoderForCausalLM(PretrainedModel, GenerationMixin):
             logits = (torch.tanh(logits.float() / cap) * cap).to(logits.dtype)
         return logits
 
+    def full_logits(self, hidden2d):
+        """[tokens, vocabulary] logits on every rank, differentiable. ``hidden2d`` is this rank's token slice under sequence
+        parallelism, all tokens otherwise. Under tensor parallelism the head (or a tied vocabulary-parallel embedding) is a
+        vocabulary shard: the hidden states are gathered / copied with a backward pass that sums the shards' gradients, the
+        logit shards are concatenated with a backward pass that keeps this rank's shard."""
+        if self.tp == 1:
+            return self.compute_logits(hidden2d)
+        group = get_parallel_state().group("mp")
+        w = self.head_weight()
+        h = AllGatherOp.apply(hidden2d, group) if self.sp else CopyToTP.apply(hidden2d, group)
+        logits = F.linear(h, w)
+        if w.shape[0] != self.config.vocab_size:
+            logits = GatherLastDimOp.apply(logits, group)
+        cap = float(getattr(self.config, "final_logit_softcapping", None) or 0.0)
+        if cap:
+            logits = (torch.tanh(logits.float() / cap) * cap).to(logits.dtype)
+        return logits
+
     def _label_norm(self, count):
         """Number of labelled tokens the loss is divided by. Ranks of a context / segment parallel group hold slices of ONE
         sequence: they normalise by the labelled tokens of the whole sequence (their mean per rank), so that averaging the
@@ -858,15 +876,7 @@ class DecoderForCausalLM(PretrainedModel, GenerationMixin):
         out = CausalLMOutput()
         want_logits = return_logits if return_logits is not None else labels is None
         if want_logits:
-            h = hidden
-            if self.sp:
-                h = GatherOp.apply(h, get_parallel_state().group("mp"))
-            logits = self.compute_logits(h)
-            if self.tp > 1 and self.lm_head is not None:
-                parts = [torch.empty_like(logits) for _ in range(self.tp)]
-                torch.distributed.all_gather(parts, logits.contiguous(), group=get_parallel_state().group("mp"))
-                logits = torch.cat(parts, dim=-1)
-            out.logits = logits.view(ctx.B, ctx.S, -1)
+            out.logits = self.full_logits(hidden).view(ctx.B, ctx.S, -1)
         if labels is not None:
             lab = labels.reshape(-1)
             count = (lab != self.ignore_index).sum()

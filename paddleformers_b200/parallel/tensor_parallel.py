@@ -110,6 +110,29 @@ class GatherOp(torch.autograd.Function):
         return g[r * per:(r + 1) * per].contiguous(), None
 
 
+class GatherLastDimOp(torch.autograd.Function):
+    """Concatenate the ranks' feature shards (logits of a vocabulary-parallel head) along the last dimension. Every rank then
+    computes the same function of the full tensor, so the gradient of the full tensor is the same everywhere and the backward
+    pass keeps this rank's shard."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group, ctx.width = group, x.shape[-1]
+        n = _group_size(group)
+        if n == 1:
+            return x
+        parts = [torch.empty_like(x) for _ in range(n)]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        return torch.cat(parts, dim=-1)
+
+    @staticmethod
+    def backward(ctx, g):
+        if _group_size(ctx.group) == 1:
+            return g, None
+        r = dist.get_rank(ctx.group)
+        return g[..., r * ctx.width:(r + 1) * ctx.width].contiguous(), None
+
+
 class AllGatherVarlenOp(torch.autograd.Function):
     """All-gather of token rows when every rank holds a different number of them (the rows that survive a label filter):
     the counts are exchanged first, rows are padded to the largest count for the collective and the padding is dropped.

@@ -768,3 +768,61 @@ def test_balance_loss_weighs_the_same_under_sequence_parallelism():
                                                 moe_token_dispatcher_type="alltoall"), 3, full)[0]
     for a, b in zip(ref, got):
         assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (ref, got)
+
+
+class _PreferencePairs(torch.utils.data.Dataset):
+    def __len__(self):
+        return 16
+
+    def __getitem__(self, i):
+        g = torch.Generator().manual_seed(i)
+        return {"prompt_ids": torch.randint(10, 60, (6,), generator=g).tolist(), "chosen_ids": [7, 7, 7, 1],
+                "rejected_ids": [9, 9, 9, 1]}
+
+
+def _dpo_tp_worker(rank, world, full, kind, targs):
+    from paddleformers_b200 import TrainingArguments
+    from paddleformers_b200.datasets.collate import dpo_collate_fn
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+    from paddleformers_b200.trainer.dpo_trainer import DPOTrainer
+    from paddleformers_b200.transformers.configuration_utils import LlmMetaConfig
+    from paddleformers_b200.transformers.model_utils import param_shard_spec
+
+    args = TrainingArguments(output_dir="/tmp/pfb_test_unused", per_device_train_batch_size=2, max_steps=3, learning_rate=5e-3,
+                             lr_scheduler_type="constant", logging_steps=1, save_strategy="no", max_seq_len=32, seed=3,
+                             device="cpu", **targs)
+    ps = args.setup_parallel()
+    cfg = _tiny_cfg(kind)
+    LlmMetaConfig.set_llm_config(cfg, args)
+
+    def build():
+        m = MODEL_MAPPING[cfg.model_type](cfg)
+        with torch.no_grad():
+            for n, p in m.named_parameters():
+                p.copy_(param_shard_spec(p).shard(full[n], ps.coord["mp"], ps.degrees.mp, 0, 1))
+        return m
+
+    tr = DPOTrainer(model=build(), ref_model=build(), args=args, train_dataset=_PreferencePairs(),
+                    data_collator=lambda b: dpo_collate_fn(b, max_seq_len=32), dpo_beta=0.5)
+    tr._sampler_shuffle = False
+    tr.train()
+    return [h["loss"] for h in tr.state.log_history if "loss" in h] + [tr.state.log_history[0]["global_norm"]]
+
+
+@pytest.mark.parametrize("kind", [False, "tied"])
+def test_preference_training_under_tensor_parallelism(kind):
+    """DPO reads the full logits: under tensor parallelism the vocabulary shards are concatenated by an operation whose
+    backward pass keeps this rank's shard, and the hidden states' gradient is summed over the shards (reduce-scattered under
+    sequence parallelism). Losses and the first gradient norm follow the single-process run, also with a tied
+    vocabulary-parallel embedding as the head."""
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+
+    torch.manual_seed(5)
+    cfg = _tiny_cfg(kind)
+    full = {k: v.detach().clone() for k, v in MODEL_MAPPING[cfg.model_type](cfg).named_parameters()}
+    ref = run_distributed(_dpo_tp_worker, 1, full, kind, {})[0]
+    for targs in (dict(tensor_model_parallel_size=2), dict(tensor_model_parallel_size=2, sequence_parallel=True)):
+        got = run_distributed(_dpo_tp_worker, 2, full, kind, targs)
+        for r in range(2):
+            for a, b in zip(ref, got[r]):
+                assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (targs, ref, got[r])
