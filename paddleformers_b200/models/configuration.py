@@ -1023,9 +1023,11 @@ UNSUPPORTED_FAMILIES = {
     "kimi_k3": "delta-rule linear attention with per-channel decay and block attention residuals (the reference builds the "
                "layers from an external package)",
     "hyperencoder": "an encoder stack of its own (the reference builds the layers from an external package)",
-    # the reference ships processors only for these; AutoProcessor hands them to the `transformers` package
-    "kimi_k25": "a vision tower (the reference ships its processor only)",
-    "qwen3_omni_moe": "audio / vision towers (the reference ships its processor only)",
+    # the reference ships processors only for these, and so does this package: transformers/kimi_processing.py (+
+    # tool_declaration.py) and transformers/omni_processing.py
+    "kimi_k25": "a vision tower (the reference ships its processor only; the processor is transformers.kimi_processing.KimiProcessor)",
+    "qwen3_omni_moe": "audio / vision towers (the reference ships its processor only; the processor is "
+                      "transformers.omni_processing.Qwen3OmniProcessor)",
 }
 
 

@@ -81,16 +81,29 @@ class LogMelFeatureExtractor:
         peak = log_spec.amax(dim=(1, 2), keepdim=True)
         return (torch.maximum(log_spec, peak - 8.0) + 4.0) / 4.0
 
-    def __call__(self, raw_speech: Union[np.ndarray, torch.Tensor, Sequence], sampling_rate: int = None, device: str = "cpu") -> Dict[str, torch.Tensor]:
+    def __call__(self, raw_speech: Union[np.ndarray, torch.Tensor, Sequence], sampling_rate: int = None, device: str = "cpu",
+                 padding="max_length", truncation: bool = True, return_attention_mask: bool = False) -> Dict[str, torch.Tensor]:
+        """``padding="max_length"`` pads (and with ``truncation`` cuts) every clip to ``chunk_length`` seconds, the Whisper
+        encoder's fixed input; ``padding="longest"`` (or True) pads to the longest clip of the batch, for encoders that take
+        clips of any length. ``return_attention_mask`` adds ``attention_mask`` [B, frames]: 1 for frames that start inside
+        the clip."""
         if sampling_rate is not None and sampling_rate != self.sampling_rate:
             raise ValueError(f"the model expects audio sampled at {self.sampling_rate} Hz, got {sampling_rate} Hz: resample first")
         if isinstance(raw_speech, (np.ndarray, torch.Tensor)) and getattr(raw_speech, "ndim", 1) == 1:
             raw_speech = [raw_speech]
-        batch = torch.full((len(raw_speech), self.n_samples), self.padding_value, dtype=torch.float32, device=device)
-        for i, w in enumerate(raw_speech):
-            w = torch.as_tensor(np.asarray(w) if not isinstance(w, torch.Tensor) else w, dtype=torch.float32)[: self.n_samples]
+        clips = [torch.as_tensor(np.asarray(w) if not isinstance(w, torch.Tensor) else w, dtype=torch.float32) for w in raw_speech]
+        if truncation:
+            clips = [w[: self.n_samples] for w in clips]
+        width = self.n_samples if padding == "max_length" else max(w.numel() for w in clips)
+        batch = torch.full((len(clips), width), self.padding_value, dtype=torch.float32, device=device)
+        for i, w in enumerate(clips):
             batch[i, : w.numel()] = w.to(device)
-        return {"input_features": self.log_mel(batch)}
+        out = {"input_features": self.log_mel(batch)}
+        if return_attention_mask:
+            frames = out["input_features"].shape[-1]
+            starts = torch.arange(frames, device=device) * self.hop_length
+            out["attention_mask"] = (starts[None, :] < torch.tensor([w.numel() for w in clips], device=device)[:, None]).to(torch.int32)
+        return out
 
 
 WhisperFeatureExtractor = LogMelFeatureExtractor

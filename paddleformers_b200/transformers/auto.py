@@ -196,8 +196,22 @@ class AutoTokenizer:
 
 
 class AutoProcessor:
+    """Processors of this package for the directories that name them (Kimi-K2.5: ``KimiK25VisionProcessor`` in
+    ``preprocessor_config.json``); every other directory goes to the `transformers` package."""
+
     @staticmethod
     def from_pretrained(path: str, **kw):
+        import json
+        import os
+
+        pre = os.path.join(path, "preprocessor_config.json")
+        if os.path.isfile(pre):
+            with open(pre) as f:
+                kind = json.load(f).get("image_processor_type")
+            if kind == "KimiK25VisionProcessor":
+                from .kimi_processing import KimiProcessor
+
+                return KimiProcessor.from_pretrained(path)
         from transformers import AutoProcessor as HFAutoProcessor
 
         return HFAutoProcessor.from_pretrained(path, **kw)

@@ -438,3 +438,150 @@ def test_molmo_multi_crop_processor_is_geometrically_consistent_and_feeds_the_mo
     first = int(batch["image_input_idx"][batch["image_input_idx"] >= 0].min())
     assert not touched[:first].any() and touched[first]                                   # causal: nothing before the first feature row moves
     assert set(batch["image_input_idx"][batch["image_input_idx"] >= 0].tolist()) == set(torch.nonzero(ids[0] == 93)[:, 0].tolist())
+
+
+def test_qwen3_omni_processor_expands_and_interleaves_like_hugging_face():
+    """Audio-encoder row counts, longest-padding mel features with their frame mask, and the expanded prompt (plain tags, and a
+    clip's audio rows merged into its video rows by time stamp) against ``transformers``; the whole call on a toy tokenizer."""
+    import types
+
+    import numpy as np
+    from transformers import WhisperFeatureExtractor as HFExtractor
+    from transformers.models.qwen3_omni_moe import processing_qwen3_omni_moe as hf
+
+    from paddleformers_b200.transformers.audio_processing import LogMelFeatureExtractor
+    from paddleformers_b200.transformers.omni_processing import Qwen3OmniProcessor, audio_encoder_output_lengths, interleave_by_time
+
+    rng = np.random.default_rng(0)
+    clips = [rng.standard_normal(16000 * 3 + 77).astype(np.float32), rng.standard_normal(9000).astype(np.float32)]
+    want = HFExtractor(feature_size=128)(clips, sampling_rate=16000, padding=True, truncation=False, return_attention_mask=True,
+                                         return_tensors="pt")
+    got = LogMelFeatureExtractor(feature_size=128)(clips, sampling_rate=16000, padding="longest", truncation=False,
+                                                   return_attention_mask=True)
+    assert (want["input_features"] - got["input_features"]).abs().max() < 1e-5
+    assert want["attention_mask"].tolist() == got["attention_mask"].tolist()
+    n = np.arange(1, 3000)
+    assert (hf._get_feat_extract_output_lengths(torch.tensor(n)).numpy() == audio_encoder_output_lengths(n)).all()
+    assert interleave_by_time(np.array([0.0, 0.0, 2.5]), 4) == [True, True, False, False, False, True, False]
+
+    tok = _Tok()
+    tok.encode = lambda text, add_special_tokens=False: [tok.vocab.setdefault(w, len(tok.vocab)) for w in
+                                                         text.replace("<|", " <|").replace("|>", "|> ").split()]
+    proc = Qwen3OmniProcessor(tok)
+    stand_in = types.SimpleNamespace(image_processor=proc.image_processor, video_processor=proc.video_processor,
+                                     **{k: getattr(proc, k) for k in ("audio_token", "image_token", "video_token", "vision_bos_token",
+                                                                      "vision_eos_token", "audio_bos_token", "audio_eos_token")})
+    text = ("a <|audio_pad|> b <|vision_start|><|image_pad|><|vision_end|> c <|vision_start|><|video_pad|><|vision_end|> "
+            "d <|audio_pad|>")
+    for in_video, lengths in ((False, [7, 3]), (True, [7, 41, 3])):
+        ref = hf.Qwen3OmniMoeProcessor.replace_multimodal_special_tokens(
+            stand_in, [text], iter(torch.tensor(lengths)), iter([torch.tensor([1, 4, 6])]), iter([torch.tensor([3, 4, 4])]),
+            iter([2.0]), in_video, 13.0, 2.0)[0]
+        assert proc.expand_tags(text, lengths, [[1, 4, 6]], [[3, 4, 4]], [2.0], in_video) == ref
+    with pytest.raises(ValueError):
+        proc.expand_tags(text, [7], [[1, 4, 6]], [[3, 4, 4]], [2.0])                    # a tag without an input
+    with pytest.raises(ValueError):
+        proc.expand_tags("a <|audio_pad|>", [7, 3], [], [], [])                           # an input without a tag
+
+    image = rng.integers(0, 255, (90, 120, 3), dtype=np.uint8)
+    video = rng.integers(0, 255, (4, 64, 64, 3), dtype=np.uint8)
+    out = proc([text, "e <|audio_pad|>"], images=[image], videos=[video], audio=[clips[0], clips[1], clips[1]], sampling_rate=16000)
+    ids = out["input_ids"]
+    count = lambda tag: int((ids == tok.vocab[tag]).sum())
+    rows = audio_encoder_output_lengths(out["feature_attention_mask"].sum(-1).numpy())
+    assert count("<|audio_pad|>") == int(rows.sum())
+    assert count("<|image_pad|>") == int(out["image_grid_thw"].prod(-1).sum()) // 4 == out["pixel_values"].shape[0] // 4
+    assert count("<|video_pad|>") == int(out["video_grid_thw"].prod(-1).sum()) // 4
+    assert out["video_second_per_grid"].tolist() == [2.0]
+    assert ids.shape == out["attention_mask"].shape and out["attention_mask"][1, 0] == 0 and out["attention_mask"][0].all()
+
+
+def test_tool_declarations_render_as_the_typescript_like_text():
+    """Stored text for a tool list that exercises every schema form: constraints, defaults, enums with null, arrays with and
+    without item comments, nested objects with additional properties, anyOf, type unions, ``$defs`` references and a
+    reference to the root."""
+    import json
+    import os
+
+    from paddleformers_b200.transformers.tool_declaration import function_to_typescript, sort_keys_deep, tools_to_typescript
+
+    with open(os.path.join(os.path.dirname(__file__), "fixtures", "tool_declaration_golden.json")) as f:
+        golden = json.load(f)
+    assert tools_to_typescript(golden["tools"]) == golden["text"]
+    assert tools_to_typescript([]) == "" and tools_to_typescript([{"type": "_plugin"}]) == ""
+    assert function_to_typescript({"name": "f", "parameters": {"type": "object", "properties": {"a": True, "b": False}}}) == \
+        "type f = (_: {\n  a?: any,\n  b?: null\n}) => any;"
+    with pytest.raises(ValueError):
+        function_to_typescript({"name": "f", "parameters": {"type": "object", "properties": {"a": {"enum": [1], "type": "string"}}}})
+    with pytest.raises(ValueError):
+        function_to_typescript({"name": "f", "parameters": {"type": "object", "properties": {"a": {"$ref": "#/$defs/Nope"}}}})
+    assert list(sort_keys_deep({"b": [{"d": 1, "c": 2}], "a": 0})) == ["a", "b"]
+
+
+def test_kimi_processor_round_trip(tmp_path):
+    """Native-resolution geometry (the reference's own expectation for a 400 x 30 image), patch order, video chunking with
+    time-stamped prompts, the tiktoken tokenizer on a small rank file (special tokens in the text, save / load), the chat
+    template with the tool block, and the joined processor through ``AutoProcessor``."""
+    import base64
+
+    import numpy as np
+
+    from paddleformers_b200.transformers.auto import AutoProcessor
+    from paddleformers_b200.transformers.kimi_processing import (KimiProcessor, KimiVisionProcessor, TikTokenTokenizer,
+                                                                 native_resolution_geometry, timestamp_text)
+
+    assert native_resolution_geometry(400, 30, 14, 2, 16384, 512) == {
+        "num_tokens": 30, "new_width": 400, "new_height": 30, "pad_width": 20, "pad_height": 26, "sampled_nframes": 1}
+    g = native_resolution_geometry(4000, 3000, 14, 2, 1024, 512)                 # shrunk to the patch budget
+    assert (g["new_width"] // 14) * (g["new_height"] // 14) <= 1024 and g["new_width"] * 3 // 4 in (g["new_height"], g["new_height"] + 1)
+    assert native_resolution_geometry(20000, 100, 14, 2, 16384, 64)["new_width"] == 64 * 14       # side limit
+    assert timestamp_text(3723.25) == "01:02:03.250" and timestamp_text(75.5, "mm:ss") == "01:15"
+
+    vp = KimiVisionProcessor()
+    rng = np.random.default_rng(0)
+    img = rng.integers(0, 255, (30, 400, 3), dtype=np.uint8)
+    out = vp([{"type": "image", "image": img}])
+    assert out["pixel_values"].shape == (120, 3, 14, 14) and out["grid_thws"].tolist() == [[1, 4, 30]]
+    # no resize for this size: patch (row 1, column 2) is that block of the normalised image; the padding normalises to -1
+    want = torch.from_numpy(img[14:28, 28:42]).permute(2, 0, 1).float() / 255.0 * 2 - 1
+    assert torch.allclose(out["pixel_values"][30 + 2], want, atol=1e-6)
+    assert (out["pixel_values"][3 * 30] == -1).all()
+
+    video = rng.integers(0, 255, (40, 56, 84, 3), dtype=np.uint8)
+    chunks = vp.split_video_chunks(video, fps=10.0)                          # 4 s at 2 frames / s -> 8 frames -> 2 chunks
+    assert [c["video_chunk"].shape[0] for c in chunks] == [4, 4]
+    assert chunks[1]["prompt"].startswith("00:00:02.200<|media_begin|>video") and vp.media_tokens(chunks[0]) == 2 * 3
+
+    toks = [bytes([i]) for i in range(256)] + [b"he", b"ll", b"hell", b"hello", b" w", b"or", b" wor"]
+    with open(tmp_path / "tiktoken.model", "wb") as f:
+        f.write(b"\n".join(base64.b64encode(t) + b" " + str(i).encode() for i, t in enumerate(toks)))
+    n = len(toks)
+    template = ("{% if tools_ts_str %}{{ tools_ts_str }}{% endif %}{% for m in messages %}<|im_user|>{% for p in m['content'] %}"
+                "{% if p['type'] == 'text' %}{{ p['text'] }}{% elif p['type'] == 'image' %}<|media_pad|>{% else %}"
+                "<|kimi_k25_video_placeholder|>{% endif %}{% endfor %}<|im_end|>{% endfor %}")
+    tok = TikTokenTokenizer(str(tmp_path / "tiktoken.model"), {n: "[BOS]", n + 1: "[EOS]", n + 2: "<|im_end|>", n + 3: "<|media_pad|>",
+                                                              n + 4: "<|im_user|>"}, pad_token="[EOS]", chat_template=template)
+    ids = tok.encode("hello world<|im_end|>")
+    assert ids == [259, 262, ord("l"), ord("d"), n + 2] and tok.decode(ids) == "hello world<|im_end|>"
+    assert tok.decode(ids, skip_special_tokens=True) == "hello world" and tok.vocab_size == n + 256
+    assert tok.encode("<|im_end|>", allow_special_tokens=False) != [n + 2]
+    assert tok.special_tokens[f"<|reserved_token_{n + 200}|>"] == n + 200
+    assert list(TikTokenTokenizer._bounded_runs("a" * 7 + "  b", 3)) == ["aaa", "aaa", "a  b"]      # no run longer than 3
+    tools = [{"type": "function", "function": {"name": "now", "description": "Current time"}}]
+    text = tok.apply_chat_template([{"role": "user", "content": [{"type": "text", "text": "hello"}]}], tools=tools)
+    assert text.startswith("# Tools\n\n## functions\nnamespace functions {\n// Current time\ntype now = (_: {}) => any;\n}\n<|im_user|>hello")
+
+    KimiProcessor(vp, tok).save_pretrained(str(tmp_path))
+    proc = AutoProcessor.from_pretrained(str(tmp_path))
+    assert isinstance(proc, KimiProcessor) and proc.tokenizer.get_vocab() == tok.get_vocab()
+    out = proc(messages=[{"role": "user", "content": [{"type": "image", "image_url": img},
+                                                      {"type": "video", "video_url": video, "fps": 10.0}, {"type": "text", "text": "hello"}]}])
+    assert list(out) == proc.model_input_names and out["grid_thws"].tolist() == [[1, 4, 30], [4, 4, 6], [4, 4, 6]]
+    assert out["pixel_values"].shape[0] == 120 + 2 * 96 and int((out["input_ids"] == n + 3).sum()) == 3          # one pad per item
+    assert "00:00:02.200<|media_begin|>" in proc.decode(out["input_ids"][0])
+    again = proc(text="<|media_pad|>hello", medias=[{"type": "image", "image": img}])
+    assert again["pixel_values"].shape[0] == 120
+    with pytest.raises(ValueError):
+        proc(text="hello")
+    with pytest.raises(ValueError):
+        proc()
