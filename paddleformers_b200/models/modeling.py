@@ -723,6 +723,21 @@ class DecoderModel(nn.Module):
         return hidden, ctx
 
 
+def label_norm(count):
+    """Number of labelled tokens the loss is divided by. Ranks of a context / segment parallel group hold slices of ONE
+    sequence: they normalise by the labelled tokens of the whole sequence (their mean per rank), so that averaging the
+    ranks' losses and gradients gives the loss of the unsplit sequence even when labels are spread unevenly."""
+    norm = count.clamp(min=1).to(torch.float32)
+    ps = get_parallel_state()
+    for axis in ("cp", "sep"):
+        n_slices = getattr(ps.degrees, axis)
+        if n_slices > 1 and torch.distributed.is_initialized():
+            total = count.to(torch.float32)
+            torch.distributed.all_reduce(total, group=ps.group(axis))
+            norm = (total / n_slices).clamp(min=1.0)
+    return norm
+
+
 class DecoderForCausalLM(PretrainedModel, GenerationMixin):
     config_class = DecoderConfig
     base_model_prefix = "model"
@@ -802,18 +817,7 @@ class DecoderForCausalLM(PretrainedModel, GenerationMixin):
         return logits
 
     def _label_norm(self, count):
-        """Number of labelled tokens the loss is divided by. Ranks of a context / segment parallel group hold slices of ONE
-        sequence: they normalise by the labelled tokens of the whole sequence (their mean per rank), so that averaging the
-        ranks' losses and gradients gives the loss of the unsplit sequence even when labels are spread unevenly."""
-        norm = count.clamp(min=1).to(torch.float32)
-        ps = get_parallel_state()
-        for axis in ("cp", "sep"):
-            n_slices = getattr(ps.degrees, axis)
-            if n_slices > 1 and torch.distributed.is_initialized():
-                total = count.to(torch.float32)
-                torch.distributed.all_reduce(total, group=ps.group(axis))
-                norm = (total / n_slices).clamp(min=1.0)
-        return norm
+        return label_norm(count)
 
     def _filter_labelled_rows(self, hidden2d, labels_flat):
         """use_filtered_label_loss: only the rows whose label is not ignored go through the head GEMM and the loss (a large

@@ -373,8 +373,15 @@ class PipelineStageModel(PretrainedModel):
             n_mtp = int(getattr(config, "num_nextn_predict_layers", 0) or 0)
             self.mtp_layers = nn.ModuleList([MTPLayer(config, config.num_hidden_layers + i, dtype=dtype, device=device) for i in range(n_mtp)])
             if n_mtp and self.chunks[-1].embed_tokens is None and not self.v_shape:
-                # MTP needs token embeddings on the last stage: a tied copy of the input embedding
-                self.chunks[-1].embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size, dtype=dtype, device=device)
+                # MTP needs token embeddings on the last stage: a tied copy of the input embedding, of the same kind (a
+                # vocabulary shard under tensor parallelism) so that the two stages can sum their gradients
+                if ps.degrees.mp > 1:
+                    from .tensor_parallel import VocabParallelEmbedding
+
+                    self.chunks[-1].embed_tokens = VocabParallelEmbedding(config.vocab_size, config.hidden_size, False,
+                                                                          dtype=dtype, device=device)
+                else:
+                    self.chunks[-1].embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size, dtype=dtype, device=device)
                 self.chunks[-1].embed_tokens.weight.pp_shared = "embed_tokens"
         if not self.v_shape:
             if self.is_first and self.chunks[0].embed_tokens is not None and (config.tie_word_embeddings or getattr(config, "num_nextn_predict_layers", 0)):
@@ -448,13 +455,18 @@ class PipelineStageModel(PretrainedModel):
         return F.fused_linear_cross_entropy(hidden, w, labels, self.ignore_index, 2048, scale)[0]
 
     def loss(self, hidden, batch, ctx):
+        from ..models.modeling import label_norm
+
         labels = batch["labels"].reshape(-1)
         count = (labels != self.ignore_index).sum()
-        scale = 1.0 / (count.clamp(min=1).float() * float(self.loss_accumulation_steps))
+        # ranks of a context / segment parallel group divide by the labelled tokens of the whole sequence
+        scale = 1.0 / (label_norm(count) * float(self.loss_accumulation_steps))
         loss = self._head_loss(hidden, labels, scale, gather=True)
         if len(self.mtp_layers) > 0:
-            if getattr(self.chunks[-1], "sp", False):
-                raise NotImplementedError("multi-token-prediction layers on a pipeline stage are implemented without sequence parallelism")
+            ps = get_parallel_state()
+            if getattr(self.chunks[-1], "sp", False) or ps.degrees.cp > 1 or ps.degrees.sep > 1:
+                raise NotImplementedError("multi-token-prediction layers on a pipeline stage are implemented without sequence, "
+                                          "context and segment parallelism")
             ids, lab, h = batch["input_ids"], batch["labels"], hidden
             # the weight of the term goes into the scale of the fused head + loss (its weight gradient is written during the
             # forward pass and would not see a factor applied afterwards)
@@ -463,8 +475,9 @@ class PipelineStageModel(PretrainedModel):
             for layer in self.mtp_layers:
                 ids = torch.cat([ids[:, 1:], ids[:, -1:]], 1)
                 lab = torch.cat([lab[:, 1:], torch.full_like(lab[:, -1:], self.ignore_index)], 1)
-                emb = F.embedding(ids, self.chunks[-1].embed_tokens.weight).reshape(-1, self.config.hidden_size)
-                h = layer(h, emb, ctx)
+                table = self.chunks[-1].embed_tokens
+                emb = table(ids) if ps.degrees.mp > 1 else F.embedding(ids, table.weight)
+                h = layer(h, emb.reshape(-1, self.config.hidden_size), ctx)
                 flat = lab.reshape(-1)
                 cnt = (flat != self.ignore_index).sum()
                 sc = w / (cnt.clamp(min=1).float() * float(self.loss_accumulation_steps))
@@ -543,8 +556,11 @@ class PipelineEngine:
             B, S = batch["input_ids"].shape
             if a.mb not in ctxs:
                 kend = batch.get("attn_mask_startend_row_indices", batch.get("kend"))
+                kend_full = batch.get("full_attn_mask_startend_row_indices")
                 ctxs[a.mb] = model.chunks[0].make_context(batch["input_ids"], batch.get("position_ids"),
-                                                          kend.reshape(B, -1) if kend is not None else None)
+                                                          kend.reshape(B, -1) if kend is not None else None,
+                                                          batch.get("cp_global_positions"), batch.get("cp_full_seq_len"),
+                                                          kend_full.reshape(B, -1) if kend_full is not None else None)
             ctx = ctxs[a.mb]
             # neighbours in the model's layer order; with the V placement the turn at the last stage stays on this rank
             src_stage = self._owner(vs - 1) if vs > 0 else None

@@ -258,6 +258,12 @@ def test_pipeline_matches_single_process(name, targs):
     ("pp2_ep2_moe_zero_bubble", 4, True, dict(pipeline_model_parallel_size=2, expert_model_parallel_size=2, sharding="stage1",
                                               gradient_accumulation_steps=2, pipeline_schedule="zero_bubble",
                                               moe_token_dispatcher_type="alltoall"), 4),
+    # stages hold slices of one sequence: global positions and the labelled-token count of the whole sequence reach the stages
+    ("pp2_cp2", 4, False, dict(pipeline_model_parallel_size=2, context_parallel_size=2, gradient_accumulation_steps=4), 4),
+    ("pp2_sep2", 4, False, dict(pipeline_model_parallel_size=2, sep_parallel_size=2, gradient_accumulation_steps=4), 4),
+    # multi-token prediction on the last stage: its embedding copy is a vocabulary shard like the first stage's table
+    ("pp2_tp2_mla_mtp", 4, "mla", dict(pipeline_model_parallel_size=2, tensor_model_parallel_size=2, gradient_accumulation_steps=4,
+                                       moe_token_dispatcher_type="alltoall"), 4),
 ])
 def test_pipeline_with_tensor_and_expert_parallelism(name, world, kind, targs, single_accum):
     _pipeline_case(name, world, kind, targs, single_accum)
@@ -271,7 +277,7 @@ def _pipeline_case(name, world, kind, targs, single_accum):
     cfg = _tiny_cfg(kind, num_hidden_layers=4)
     full = {k: v.detach().clone() for k, v in MODEL_MAPPING[cfg.model_type](cfg).named_parameters()}
     single = dict(gradient_accumulation_steps=single_accum)
-    if kind is True:
+    if kind is True or kind == "mla":
         single["moe_token_dispatcher_type"] = "alltoall"
     ref = _single_process_run(_train_single4, kind, single, steps, full)
     got = run_distributed(_train_pp, world, kind, targs, steps, full)
