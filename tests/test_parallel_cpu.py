@@ -832,3 +832,57 @@ def test_preference_training_under_tensor_parallelism(kind):
         for r in range(2):
             for a, b in zip(ref, got[r]):
                 assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (targs, ref, got[r])
+
+
+def _packed_data(n, S=32, vocab=128):
+    """Two documents per row: positions restart, keys of the first document end at its last row."""
+    g = torch.Generator().manual_seed(11)
+    ids = torch.randint(0, vocab, (n, S + 1), generator=g)
+    out = []
+    for i in range(n):
+        cut = 9 + (i * 5) % 14
+        lab = ids[i, 1:].clone()
+        lab[:2], lab[cut - 1], lab[cut:cut + 2] = -100, -100, -100
+        out.append({"input_ids": ids[i, :-1], "labels": lab, "position_ids": torch.cat([torch.arange(cut), torch.arange(S - cut)]),
+                    "attn_mask_startend_row_indices": torch.cat([torch.full((cut,), cut), torch.full((S - cut,), S)]).to(torch.int32)})
+    return out
+
+
+def _train_packed(rank, world, kind, targs, steps, full, pipeline):
+    from paddleformers_b200 import Trainer, TrainingArguments
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+    from paddleformers_b200.parallel.pipeline import build_pipeline_model
+    from paddleformers_b200.transformers.configuration_utils import LlmMetaConfig
+    from paddleformers_b200.transformers.model_utils import param_shard_spec
+
+    args = TrainingArguments(output_dir="/tmp/pfb_test_unused", per_device_train_batch_size=1, max_steps=steps, learning_rate=1e-2,
+                             lr_scheduler_type="constant", logging_steps=1, save_strategy="no", max_seq_len=32, max_grad_norm=1.0,
+                             seed=3, device="cpu", **targs)
+    ps = args.setup_parallel()
+    cfg = _tiny_cfg(kind, num_hidden_layers=4)
+    LlmMetaConfig.set_llm_config(cfg, args)
+    model = build_pipeline_model(cfg) if pipeline else MODEL_MAPPING[cfg.model_type](cfg)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            g = model.global_param_name(name) if pipeline else name
+            p.copy_(param_shard_spec(p).shard(full[g], ps.coord["mp"], ps.degrees.mp, ps.rank_in("ep"), ps.degrees.ep))
+    tr = Trainer(model=model, args=args, train_dataset=_DS(_packed_data(8 * steps)))
+    tr._sampler_shuffle = False
+    tr.train()
+    return [h["loss"] for h in tr.state.log_history if "loss" in h] + [tr.state.log_history[0]["global_norm"]]
+
+
+def test_packed_documents_under_pipeline_and_context_parallelism():
+    """Rows that pack two documents (restarting positions, per-key visibility bounds) train the same on 2 stages x 2 sequence
+    slices as in one process: the bounds of the whole row and the global positions reach every stage."""
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+
+    torch.manual_seed(5)
+    cfg = _tiny_cfg(False, num_hidden_layers=4)
+    full = {k: v.detach().clone() for k, v in MODEL_MAPPING[cfg.model_type](cfg).named_parameters()}
+    ref = run_distributed(_train_packed, 1, False, dict(gradient_accumulation_steps=4), 2, full, False)[0]
+    got = run_distributed(_train_packed, 4, False, dict(pipeline_model_parallel_size=2, context_parallel_size=2,
+                                                        gradient_accumulation_steps=4), 2, full, True)
+    for r in range(4):
+        for a, b in zip(ref, got[r]):
+            assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (ref, got[r])
