@@ -817,7 +817,7 @@ def _dpo_tp_worker(rank, world, full, kind, targs):
 
 @pytest.mark.parametrize("kind", [False, "tied"])
 def test_preference_training_under_tensor_parallelism(kind):
-    """DPO reads the full logits: under tensor parallelism the vocabulary shards are concatenated by an operation whose
+    """(Also context and segment parallelism.) DPO reads the full logits: under tensor parallelism the vocabulary shards are concatenated by an operation whose
     backward pass keeps this rank's shard, and the hidden states' gradient is summed over the shards (reduce-scattered under
     sequence parallelism). Losses and the first gradient norm follow the single-process run, also with a tied
     vocabulary-parallel embedding as the head."""
@@ -827,7 +827,11 @@ def test_preference_training_under_tensor_parallelism(kind):
     cfg = _tiny_cfg(kind)
     full = {k: v.detach().clone() for k, v in MODEL_MAPPING[cfg.model_type](cfg).named_parameters()}
     ref = run_distributed(_dpo_tp_worker, 1, full, kind, {})[0]
-    for targs in (dict(tensor_model_parallel_size=2), dict(tensor_model_parallel_size=2, sequence_parallel=True)):
+    cases = [dict(tensor_model_parallel_size=2), dict(tensor_model_parallel_size=2, sequence_parallel=True)]
+    if kind is False:
+        # ranks that hold slices of one sequence add up their parts of every response's log-probability
+        cases += [dict(context_parallel_size=2), dict(sep_parallel_size=2)]
+    for targs in cases:
         got = run_distributed(_dpo_tp_worker, 2, full, kind, targs)
         for r in range(2):
             for a, b in zip(ref, got[r]):
