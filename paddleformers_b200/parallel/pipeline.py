@@ -620,6 +620,57 @@ class PipelineEngine:
             dist.broadcast(total_loss, src=src, group=self.ps.group("pp"))
         return total_loss
 
+    @torch.no_grad()
+    def forward_only(self, micro_batches: List[Dict[str, torch.Tensor]]):
+        """Evaluation: every micro-batch runs down the virtual stages in order, nothing is kept for a backward pass. Returns
+        (sum over micro-batches of mean loss x labelled tokens, labelled tokens), the same on every stage."""
+        model, P, V, s = self.model, self.P, self.V, self.stage
+        H = model.config.hidden_size
+        dev = next(model.parameters()).device
+        dtype = next((p.dtype for n, p in model.named_parameters() if "gate.weight" not in n), torch.float32)
+        last_virtual = P * V - 1
+        saved_accum, model.loss_accumulation_steps = model.loss_accumulation_steps, 1
+        both = torch.zeros(2, dtype=torch.float64, device=dev)
+        mine = sorted((virtual_stage(s, c, P, self.v_shape), c) for c in range(V))
+        try:
+            for batch in micro_batches:
+                B, S = batch["input_ids"].shape
+                kend = batch.get("attn_mask_startend_row_indices", batch.get("kend"))
+                kend_full = batch.get("full_attn_mask_startend_row_indices")
+                ctx = model.chunks[0].make_context(batch["input_ids"], batch.get("position_ids"),
+                                                   kend.reshape(B, -1) if kend is not None else None,
+                                                   batch.get("cp_global_positions"), batch.get("cp_full_seq_len"),
+                                                   kend_full.reshape(B, -1) if kend_full is not None else None)
+                handed = None
+                for vs, c in mine:
+                    x_in = None
+                    if vs > 0:
+                        if self._owner(vs - 1) == s:
+                            x_in = handed
+                        else:
+                            rows = B * S // self.ps.degrees.mp if getattr(model.chunks[0], "sp", False) else B * S
+                            x_in = self._recv((rows, H), dtype, dev, self.ranks[self._owner(vs - 1)], self.fwd_group)
+                    out = model.forward_chunk(c, x_in, batch, ctx)
+                    if vs == last_virtual:
+                        pair = torch.stack([model.loss(out, batch, ctx).double(), (batch["labels"] != model.ignore_index).sum().double()])
+                        for axis in ("cp", "sep"):      # slices of one sequence: the mean of their losses, the sum of their counts
+                            if getattr(self.ps.degrees, axis) > 1:
+                                dist.all_reduce(pair, group=self.ps.group(axis))
+                                pair[0] /= getattr(self.ps.degrees, axis)
+                        both += torch.stack([pair[0] * pair[1], pair[1]])
+                    elif self._owner(vs + 1) == s:
+                        handed = out
+                    else:
+                        pending: List[object] = []
+                        self._send(out, self.ranks[self._owner(vs + 1)], self.fwd_group, pending)
+                        for w in pending:
+                            w.wait()
+        finally:
+            model.loss_accumulation_steps = saved_accum
+        if P > 1:
+            dist.broadcast(both, src=self.ps.group_ranks["pp"][self._owner(last_virtual)], group=self.ps.group("pp"))
+        return both[0], both[1]
+
     def _sync_shared_embeddings(self):
         """Sum the gradients of parameters that exist on both the first and the last stage (tied embeddings, MTP
         embedding copy)."""

@@ -284,12 +284,16 @@ class Trainer:
         if torch.cuda.is_available():
             torch.cuda.synchronize()
 
-    def training_pipeline_step(self, model, micro_batches: List[Dict[str, Any]]) -> torch.Tensor:
+    def _pipeline_engine(self, model):
         if self.pipeline_engine is None:
             from ..parallel.pipeline import PipelineEngine
 
             self.pipeline_engine = PipelineEngine(model, self.ps, schedule=self.args.pipeline_schedule,
                                                   num_virtual_stages=self.args.virtual_pipeline_model_parallel_size)
+        return self.pipeline_engine
+
+    def training_pipeline_step(self, model, micro_batches: List[Dict[str, Any]]) -> torch.Tensor:
+        self._pipeline_engine(model)
         batches = [self._prepare_inputs(mb) for mb in micro_batches]
         loss = self.pipeline_engine.forward_backward(batches)
         self.optimizer.accumulate_grads()
@@ -560,6 +564,32 @@ class Trainer:
         return metrics
 
     @torch.no_grad()
+    def _whole_sequences(self, pred, lab, inputs):
+        """Under context / segment parallelism every rank predicted a slice of the sequence: gather the slices and put every
+        token at its global position (predictions with a sequence dimension only); the labels are the unsliced rows."""
+        ps = self.ps
+        local = inputs["input_ids"].shape[1]
+        for axis in ("cp", "sep"):
+            n = getattr(ps.degrees, axis)
+            if n == 1 or pred.dim() < 2 or pred.shape[1] != local:
+                continue
+            parts = [torch.empty_like(pred) for _ in range(n)]
+            dist.all_gather(parts, pred.contiguous(), group=ps.group(axis))
+            if axis == "sep":
+                pred = torch.cat(parts, dim=1)
+            else:
+                from ..parallel.context_parallel import cp_positions
+
+                mode = getattr(self.args, "cp_balance_mode", None) or "dualchunk_allgather"
+                whole = torch.empty((pred.shape[0], local * n) + tuple(pred.shape[2:]), dtype=pred.dtype, device=pred.device)
+                for r, part in enumerate(parts):
+                    whole[:, cp_positions(local * n, n, r, mode, pred.device)] = part
+                pred = whole
+            if lab is not None and inputs.get("full_labels") is not None:
+                lab = inputs["full_labels"]
+        return pred, lab
+
+    @torch.no_grad()
     def _evaluation_loop(self, dataset, want_predictions: bool, with_labels: bool = True):
         """(token-weighted mean loss, predictions, labels, batches per rank). Predictions are the arg-max token ids unless
         ``preprocess_logits_for_metrics(logits, labels)`` says otherwise; rows that only fill up the last batch are left out."""
@@ -588,17 +618,36 @@ class Trainer:
                 if pad_rows and has_labels:
                     inputs["labels"] = inputs["labels"].clone()
                     inputs["labels"][pad_rows] = -100
+                if self.ps.degrees.pp > 1:
+                    if want_predictions or not has_labels:
+                        raise NotImplementedError("under pipeline parallelism evaluation reports the loss only: predictions "
+                                                  "and compute_metrics need the logits, which the last stage does not keep")
+                    loss_sum, n = self._pipeline_engine(model).forward_only([inputs])
+                    tot += loss_sum
+                    cnt += n
+                    n_batches += 1
+                    self.control = self.callback_handler.on_prediction_step(a, self.state, self.control)
+                    continue
                 out = model(**inputs, return_logits=True) if want_predictions else model(**inputs)
                 if has_labels and out.loss is not None:
                     n = out.num_tokens.double() if out.num_tokens is not None else torch.ones_like(cnt)
+                    loss = out.loss.double()
+                    for axis in ("cp", "sep"):
+                        # ranks that hold slices of one sequence: each loss is this slice's sum over the mean count of a
+                        # slice, so their mean is the loss of the sequence; the counts add up
+                        if getattr(self.ps.degrees, axis) > 1:
+                            pair = torch.stack([loss, n])
+                            dist.all_reduce(pair, group=self.ps.group(axis))
+                            loss, n = pair[0] / getattr(self.ps.degrees, axis), pair[1]
                     if len(pad_rows) < a.per_device_eval_batch_size:        # a batch of fill-ins only has no valid token
-                        tot += out.loss.double() * n
+                        tot += loss * n
                         cnt += n
                 if want_predictions:
                     keep = [i for i in range(out.logits.shape[0]) if i not in pad_rows]
                     lab = inputs.get("labels")
                     pre = getattr(self, "preprocess_logits_for_metrics", None)
                     pred = pre(out.logits, lab) if pre is not None else out.logits.argmax(-1)
+                    pred, lab = self._whole_sequences(pred, lab, inputs)
                     rows_p += [pred[i].cpu() for i in keep]
                     if lab is not None:
                         rows_l += [lab[i].cpu() for i in keep]

@@ -114,3 +114,60 @@ def test_whole_set_loss_metrics_and_several_sets():
     for m2, shape in got:
         assert m2["eval_loss"] == pytest.approx(want, rel=1e-5) and m2["eval_rows"] == 10 and shape == ((10, 10), (10, 10))
     assert got[0][0]["eval_accuracy"] == got[1][0]["eval_accuracy"]
+
+
+def _strategy_worker(rank, world, kind, targs, full, pipeline):
+    import numpy as np
+
+    import test_parallel_cpu as T
+    from paddleformers_b200 import Trainer, TrainingArguments
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+    from paddleformers_b200.parallel.pipeline import build_pipeline_model
+    from paddleformers_b200.transformers.configuration_utils import LlmMetaConfig
+    from paddleformers_b200.transformers.model_utils import param_shard_spec
+
+    args = TrainingArguments(output_dir="/tmp/pfb_test_unused", per_device_train_batch_size=1, per_device_eval_batch_size=1,
+                             max_steps=1, logging_steps=1, save_strategy="no", max_seq_len=32, seed=3, device="cpu", **targs)
+    ps = args.setup_parallel()
+    cfg = T._tiny_cfg(kind, num_hidden_layers=4)
+    LlmMetaConfig.set_llm_config(cfg, args)
+    model = build_pipeline_model(cfg) if pipeline else MODEL_MAPPING[cfg.model_type](cfg)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            g = model.global_param_name(name) if pipeline else name
+            p.copy_(param_shard_spec(p).shard(full[g], ps.coord["mp"], ps.degrees.mp, ps.rank_in("ep"), ps.degrees.ep))
+
+    def metrics(p):
+        pred, lab = np.asarray(p.predictions), np.asarray(p.label_ids)
+        return {"hits": float(((pred == lab) & (lab != -100)).sum()), "labelled": float((lab != -100).sum()),
+                "checksum": float((pred * (lab != -100)).sum())}
+
+    data = T._DS(T._data(6))
+    tr = Trainer(model=model, args=args, train_dataset=data, eval_dataset=data, compute_metrics=None if pipeline else metrics)
+    return {k: round(float(v), 5) for k, v in tr.evaluate().items() if k in ("eval_loss", "eval_hits", "eval_labelled", "eval_checksum")}
+
+
+@pytest.mark.parametrize("name,world,kind,targs", [
+    ("tied_tp2_sp", 2, "tied", dict(tensor_model_parallel_size=2, sequence_parallel=True)),
+    ("cp2", 2, False, dict(context_parallel_size=2)),
+    ("sep2", 2, False, dict(sep_parallel_size=2)),
+    ("pp2_interleaved", 2, False, dict(pipeline_model_parallel_size=2, virtual_pipeline_model_parallel_size=2, gradient_accumulation_steps=2)),
+    ("pp2_zbv", 2, False, dict(pipeline_model_parallel_size=2, pipeline_schedule="zbv", gradient_accumulation_steps=2)),
+    ("pp2_cp2", 4, False, dict(pipeline_model_parallel_size=2, context_parallel_size=2, gradient_accumulation_steps=2)),
+])
+def test_evaluation_under_parallel_strategies(name, world, kind, targs):
+    """Loss, and where the logits exist the predictions, equal the single-process evaluation: vocabulary shards are
+    concatenated, sequence slices are put back at their global positions and their losses combined, pipeline stages run a
+    forward-only pass and report the loss."""
+    import test_parallel_cpu as T
+    from paddleformers_b200.models.modeling import MODEL_MAPPING
+
+    torch.manual_seed(5)
+    cfg = T._tiny_cfg(kind, num_hidden_layers=4)
+    full = {k: v.detach().clone() for k, v in MODEL_MAPPING[cfg.model_type](cfg).named_parameters()}
+    ref = run_distributed(_strategy_worker, 1, kind, {}, full, False)[0]
+    got = run_distributed(_strategy_worker, world, kind, targs, full, name.startswith("pp2"))
+    for r in range(world):
+        for k, v in got[r].items():
+            assert abs(v - ref[k]) < 1e-4 * max(1.0, abs(ref[k])), (name, r, ref, got[r])
+        assert ("eval_hits" in got[r]) == (not name.startswith("pp2"))
