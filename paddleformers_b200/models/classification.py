@@ -53,6 +53,13 @@ class _DecoderWithHead(PretrainedModel):
 
     def hidden(self, input_ids, position_ids=None, kend=None):
         hidden, ctx = self.model(input_ids, position_ids, kend)
+        if self.model.sp:
+            # every rank holds a slice of the token rows: gather them (all ranks then compute the same head and loss, so the
+            # backward pass keeps this rank's slice)
+            from ..parallel.tensor_parallel import GatherOp
+            from ..parallel.topology import get_parallel_state
+
+            hidden = GatherOp.apply(hidden, get_parallel_state().group("mp"))
         return hidden.view(ctx.B, ctx.S, -1)
 
     def weight_map(self) -> WeightMap:

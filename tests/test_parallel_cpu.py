@@ -890,3 +890,56 @@ def test_packed_documents_under_pipeline_and_context_parallelism():
     for r in range(4):
         for a, b in zip(ref, got[r]):
             assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (ref, got[r])
+
+
+def _classifier_worker(rank, world, targs, full, token_level):
+    from paddleformers_b200 import TrainingArguments
+    from paddleformers_b200.models.classification import DecoderForSequenceClassification, DecoderForTokenClassification
+    from paddleformers_b200.transformers.configuration_utils import LlmMetaConfig
+    from paddleformers_b200.transformers.model_utils import param_shard_spec
+
+    args = TrainingArguments(output_dir="/tmp/pfb_test_unused", per_device_train_batch_size=1, max_steps=1, save_strategy="no",
+                             max_seq_len=32, seed=3, device="cpu", **targs)
+    ps = args.setup_parallel()
+    cfg = _tiny_cfg(False)
+    cfg.num_labels = 3
+    LlmMetaConfig.set_llm_config(cfg, args)
+    model = (DecoderForTokenClassification if token_level else DecoderForSequenceClassification)(cfg)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            p.copy_(param_shard_spec(p).shard(full[name], ps.coord["mp"], ps.degrees.mp, 0, 1))
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(1, 120, (2, 16), generator=g)
+    labels = torch.randint(0, 3, (2, 16), generator=g) if token_level else torch.tensor([2, 0])
+    out = model(ids, labels=labels)
+    out.loss.backward()
+    square = 0.0
+    for name, p in model.named_parameters():
+        grad = p.grad if p.grad is not None else getattr(p, "main_grad", None)
+        if grad is None:
+            continue
+        grad = grad.double().clone()
+        if getattr(p, "sequence_parallel", False) and world > 1:         # partial per rank: what the optimizer sums
+            torch.distributed.all_reduce(grad)
+        v = grad.pow(2).sum()
+        if tuple(p.shape) != tuple(full[name].shape) and world > 1:      # a shard: the norm adds the ranks' parts
+            torch.distributed.all_reduce(v)
+        square += float(v)
+    return [float(out.loss), square ** 0.5]
+
+
+@pytest.mark.parametrize("token_level", [False, True])
+def test_classification_heads_under_tensor_and_sequence_parallelism(token_level):
+    """Sequence (last kept token) and token classification on a tensor-parallel decoder: under sequence parallelism the token
+    slices are gathered before the head; loss and the norm of all gradients equal the single-process values."""
+    from paddleformers_b200.models.classification import DecoderForSequenceClassification, DecoderForTokenClassification
+
+    torch.manual_seed(5)
+    cfg = _tiny_cfg(False)
+    cfg.num_labels = 3
+    cls = DecoderForTokenClassification if token_level else DecoderForSequenceClassification
+    full = {k: v.detach().clone() for k, v in cls(cfg).named_parameters()}
+    ref = run_distributed(_classifier_worker, 1, {}, full, token_level)[0]
+    for targs in (dict(tensor_model_parallel_size=2), dict(tensor_model_parallel_size=2, sequence_parallel=True)):
+        for got in run_distributed(_classifier_worker, 2, targs, full, token_level):
+            assert abs(got[0] - ref[0]) < 1e-5 and abs(got[1] - ref[1]) < 1e-4 * ref[1], (targs, ref, got)
