@@ -202,7 +202,10 @@ class Ernie4_5VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
     def forward(self, input_ids, pixel_values=None, image_grid_thw=None, pixel_values_videos=None, video_grid_thw=None, labels=None,
                 position_ids=None, moe_mm_token_type_ids=None, return_logits: Optional[bool] = None, **unused):
         cfg, lm = self.config, self.language
-        h = lm.model.embed(input_ids)
+        if lm.model.sp:
+            raise NotImplementedError("the vision rows of the modality-isolated experts are whole-sequence positions: this model "
+                                      "runs without sequence parallelism")
+        h = lm.model.embed(input_ids, whole=True)
         for pv, grid, tok in ((pixel_values, image_grid_thw, cfg.image_token_id), (pixel_values_videos, video_grid_thw, cfg.video_token_id)):
             if pv is not None:
                 feats = self.resampler(self.visual(pv, grid), grid).to(h.dtype)
@@ -227,7 +230,7 @@ class Ernie4_5VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
         for m in moes:
             m.vision_rows = vis
         try:
-            hidden, residual = lm.model.run_layers(h, None, ctx)
+            hidden, residual = lm.model.run_layers(lm.model.token_slice(h), None, ctx)
         finally:
             for m in moes:
                 m.vision_rows = None

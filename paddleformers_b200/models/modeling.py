@@ -656,10 +656,17 @@ class DecoderModel(nn.Module):
         return BatchContext(B, S, pos, kend, cos, sin, cp_positions if S_full else None, S_full, kend_full if S_full else None,
                             kend_window, window, cos_l, sin_l)
 
-    def embed(self, input_ids):
+    def token_slice(self, h):
+        """This rank's rows of whole-sequence embeddings under sequence parallelism (the backward pass gathers the slices'
+        gradients, so whatever produced the rows sees the gradient of all of them)."""
+        return ScatterOp.apply(h, get_parallel_state().group("mp")) if self.sp else h
+
+    def embed(self, input_ids, whole: bool = False):
+        """[tokens, hidden] embeddings: this rank's token slice under sequence parallelism unless ``whole`` (multimodal models
+        write feature rows over placeholder positions first and call ``token_slice`` afterwards)."""
         mult = float(getattr(self.config, "embedding_multiplier", 1.0) or 1.0)
         if isinstance(self.embed_tokens, VocabParallelEmbedding):
-            h = self.embed_tokens(input_ids)
+            h = self.embed_tokens(input_ids, whole=whole)
             h = h if h.dim() == 2 else h.reshape(-1, h.shape[-1])
         else:
             h = F.embedding(input_ids, self.embed_tokens.weight).reshape(-1, self.config.hidden_size)

@@ -254,7 +254,7 @@ class MolmoForCausalLM(PretrainedModel):
                 attn_mask_startend_row_indices=None, return_logits: Optional[bool] = None, **unused):
         lm = self.language
         B, S = input_ids.shape
-        h = lm.model.embed(input_ids)                                                      # [B * S, H]
+        h = lm.model.embed(input_ids, whole=True)                                                      # [B * S, H]
         if images is not None:
             if self.model.vision_backbone is None:
                 raise ValueError("this Molmo configuration has no vision backbone")
@@ -271,7 +271,7 @@ class MolmoForCausalLM(PretrainedModel):
             h = h.index_add(0, rows, add)
         kend = attn_mask_startend_row_indices.reshape(B, -1) if attn_mask_startend_row_indices is not None else None
         ctx = lm.model.make_context(input_ids, position_ids, kend)
-        hidden, residual = lm.model.run_layers(h, None, ctx)
+        hidden, residual = lm.model.run_layers(lm.model.token_slice(h), None, ctx)
         hidden = lm.model.norm(hidden, residual)[0] if residual is not None else lm.model.norm(hidden)
         out = CausalLMOutput()
         if return_logits if return_logits is not None else labels is None:

@@ -141,7 +141,7 @@ class PaliGemmaForConditionalGeneration(PretrainedModel):
         B, S = input_ids.shape
         is_image = input_ids == cfg.image_token_id
         ids = input_ids.masked_fill(is_image, 0) if cfg.image_token_id >= cfg.text_config.vocab_size else input_ids
-        h = lm.model.embed(ids)
+        h = lm.model.embed(ids, whole=True)
         if pixel_values is not None or image_embeds is not None:
             feats = (image_embeds if image_embeds is not None else self.image_features(pixel_values)).to(h.dtype)
             assert int(is_image.sum()) == feats.shape[0], "one placeholder token per image patch is required"
@@ -152,7 +152,7 @@ class PaliGemmaForConditionalGeneration(PretrainedModel):
             ctx.kstart = two_way_block_starts(two_way)
             if ctx.kend_window is not None:           # a window never cuts through a two-way block
                 ctx.kend_window = torch.maximum(ctx.kend_window, two_way_block_ends(two_way))
-        hidden, residual = lm.model.run_layers(h, None, ctx)
+        hidden, residual = lm.model.run_layers(lm.model.token_slice(h), None, ctx)
         hidden = lm.model.norm(hidden, residual)[0] if residual is not None else lm.model.norm(hidden)
         out = CausalLMOutput()
         if return_logits if return_logits is not None else labels is None:

@@ -373,7 +373,7 @@ class Phi4MultimodalForCausalLM(PretrainedModel):
                 audio_embed_sizes=None, audio_attention_mask=None, labels=None, position_ids=None,
                 return_logits: Optional[bool] = None, **unused):
         cfg, lm = self.config, self.language
-        h = lm.model.embed(input_ids)
+        h = lm.model.embed(input_ids, whole=True)
         flat = input_ids.reshape(-1)
         for tok, feats in ((cfg.image_token_id, None if image_pixel_values is None else
                             self.embed_tokens_extend.image_embed(image_pixel_values, image_sizes, image_attention_mask)),
@@ -385,7 +385,7 @@ class Phi4MultimodalForCausalLM(PretrainedModel):
                 assert int(mask.sum()) == feats.shape[0], "one placeholder token per image / audio feature row is required"
                 h = h.masked_scatter(mask[:, None], feats.to(h.dtype))
         ctx = lm.model.make_context(input_ids, position_ids)
-        hidden, residual = lm.model.run_layers(h, None, ctx)
+        hidden, residual = lm.model.run_layers(lm.model.token_slice(h), None, ctx)
         hidden = lm.model.norm(hidden, residual)[0] if residual is not None else lm.model.norm(hidden)
         out = CausalLMOutput()
         if return_logits if return_logits is not None else labels is None:

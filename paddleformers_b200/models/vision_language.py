@@ -330,7 +330,7 @@ class Qwen2VLForConditionalGeneration(PretrainedModel):
     def forward(self, input_ids, pixel_values=None, image_grid_thw=None, pixel_values_videos=None, video_grid_thw=None, labels=None,
                 position_ids=None, return_logits: Optional[bool] = None, **unused):
         cfg, lm = self.config, self.language
-        h = lm.model.embed(input_ids)
+        h = lm.model.embed(input_ids, whole=True)
         for pv, grid, tok in ((pixel_values, image_grid_thw, cfg.image_token_id), (pixel_values_videos, video_grid_thw, cfg.video_token_id)):
             if pv is not None:
                 feats = self.visual(pv, grid).to(h.dtype)
@@ -341,7 +341,7 @@ class Qwen2VLForConditionalGeneration(PretrainedModel):
             position_ids = multimodal_position_ids(input_ids, cfg.image_token_id, cfg.video_token_id, image_grid_thw, video_grid_thw,
                                                    cfg.vision_config["spatial_merge_size"])
         ctx = self._context(input_ids, position_ids)
-        hidden, residual = lm.model.run_layers(h, None, ctx)
+        hidden, residual = lm.model.run_layers(lm.model.token_slice(h), None, ctx)
         hidden = lm.model.norm(hidden, residual)[0] if residual is not None else lm.model.norm(hidden)
         out = CausalLMOutput()
         if return_logits if return_logits is not None else labels is None:
@@ -621,6 +621,9 @@ class Qwen3VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
     def forward(self, input_ids, pixel_values=None, image_grid_thw=None, pixel_values_videos=None, video_grid_thw=None, labels=None,
                 position_ids=None, return_logits: Optional[bool] = None, **unused):
         cfg, lm = self.config, self.language
+        if lm.model.sp:
+            raise NotImplementedError("deepstack features are added to whole-sequence hidden states: this model runs without "
+                                      "sequence parallelism")
         h = lm.model.embed(input_ids)
         flat_ids = input_ids.reshape(-1)
         visual_rows, deep_feats = [], None

@@ -305,11 +305,13 @@ class VocabParallelEmbedding(nn.Module):
         self.weight = nn.Parameter(torch.empty(self.per, embedding_dim, dtype=dtype, device=device))
         self.weight.shard_spec = ("tp", 0, None)
 
-    def forward(self, ids):
+    def forward(self, ids, whole: bool = False):
+        """``whole``: all token rows on every rank even under sequence parallelism (for callers that still edit rows by global
+        position, e.g. write image features over placeholders, before they cut the token slice)."""
         out = F.embedding(ids, self.weight, vocab_start=self.rank * self.per if self.tp > 1 else 0)
         if self.tp > 1:
             flat = out.reshape(-1, self.embedding_dim)
-            if self.sequence_parallel:
+            if self.sequence_parallel and not whole:
                 return ReduceScatterOp.apply(flat, self.group)
             return ReduceFromTP.apply(flat, self.group).view(*ids.shape, self.embedding_dim)
         return out

@@ -943,3 +943,64 @@ def test_classification_heads_under_tensor_and_sequence_parallelism(token_level)
     for targs in (dict(tensor_model_parallel_size=2), dict(tensor_model_parallel_size=2, sequence_parallel=True)):
         for got in run_distributed(_classifier_worker, 2, targs, full, token_level):
             assert abs(got[0] - ref[0]) < 1e-5 and abs(got[1] - ref[1]) < 1e-4 * ref[1], (targs, ref, got)
+
+
+def _tiny_vl_cfg():
+    from paddleformers_b200.models.vision_language import Qwen2VLConfig
+    return Qwen2VLConfig(text_config=dict(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=2,
+                                         num_key_value_heads=2, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]}),
+                        vision_config=dict(depth=1, embed_dim=16, hidden_size=32, mlp_ratio=2, num_heads=2, patch_size=4), image_token_id=60)
+def _vl_worker(rank, world, targs, full):
+    import numpy as np
+
+    from paddleformers_b200 import TrainingArguments
+    from paddleformers_b200.models.vision_language import Qwen2VLForConditionalGeneration
+    from paddleformers_b200.models.vision_language import mm_collate_fn
+    from paddleformers_b200.transformers.image_processing import Qwen2VLImageProcessor
+    from paddleformers_b200.transformers.configuration_utils import LlmMetaConfig
+    from paddleformers_b200.transformers.model_utils import param_shard_spec
+    args = TrainingArguments(output_dir="/tmp/pfb_test_unused", per_device_train_batch_size=1, max_steps=1, save_strategy="no", max_seq_len=32, seed=3, device="cpu", **targs)
+    ps = args.setup_parallel()
+    cfg = _tiny_vl_cfg()
+    LlmMetaConfig.set_llm_config(cfg.text_config, args)
+    model = Qwen2VLForConditionalGeneration(cfg, dtype=torch.float32)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            p.copy_(param_shard_spec(p).shard(full[name], ps.coord["mp"], ps.degrees.mp, 0, 1))
+    rng = np.random.default_rng(0)
+    proc = Qwen2VLImageProcessor(patch_size=4, min_pixels=64, max_pixels=1024)
+    out = proc([rng.integers(0, 255, (24, 32, 3), dtype=np.uint8)])
+    n = proc.num_image_tokens(out["image_grid_thw"][0])
+    ids = [1, 2] + [60] * n + [3, 4, 5, 6]
+    ids = ids + [7] * (-len(ids) % 2)
+    labels = [-100] * (2 + n) + [4, 5, 6, -100] + [-100] * (len(ids) - n - 6)
+    batch = mm_collate_fn([{"input_ids": ids, "labels": labels, **out}])
+    o = model(**batch)
+    o.loss.backward()
+    sq = 0.0
+    for name, p in model.named_parameters():
+        g = p.grad if p.grad is not None else getattr(p, "main_grad", None)
+        if g is None: continue
+        g = g.double().clone()
+        if getattr(p, "sequence_parallel", False) and world > 1: torch.distributed.all_reduce(g)
+        v = g.pow(2).sum()
+        if tuple(p.shape) != tuple(full[name].shape) and world > 1: torch.distributed.all_reduce(v)
+        sq += float(v)
+    vis = model.visual.patch_embed.weight
+    gv = vis.grad if vis.grad is not None else vis.main_grad
+    return [float(o.loss), sq ** 0.5, float(gv.double().norm())]
+
+
+def test_vision_language_model_under_tensor_and_sequence_parallelism():
+    """Qwen2-VL on a tensor-parallel decoder: the image features are written over the placeholder rows of the whole-sequence
+    embeddings, then every rank cuts its token slice; loss, the norm of all gradients and the vision tower's gradient equal the
+    single-process values."""
+    from paddleformers_b200.models.vision_language import Qwen2VLForConditionalGeneration
+
+    torch.manual_seed(5)
+    full = {k: v.detach().clone() for k, v in Qwen2VLForConditionalGeneration(_tiny_vl_cfg(), dtype=torch.float32).named_parameters()}
+    ref = run_distributed(_vl_worker, 1, {}, full)[0]
+    for targs in (dict(tensor_model_parallel_size=2), dict(tensor_model_parallel_size=2, sequence_parallel=True)):
+        for got in run_distributed(_vl_worker, 2, targs, full):
+            for a, b in zip(ref, got):
+                assert abs(a - b) < 1e-4 * max(1.0, abs(a)), (targs, ref, got)
