@@ -215,6 +215,15 @@ class LoRAModel(nn.Module):
         except AttributeError:
             return getattr(self.model, name)
 
+    @property
+    def loss_accumulation_steps(self):
+        return getattr(self.model, "loss_accumulation_steps", 1)
+
+    @loss_accumulation_steps.setter
+    def loss_accumulation_steps(self, n):
+        # the trainer sets this on the model it was given: the wrapped model is the one that divides its loss by it
+        self.model.loss_accumulation_steps = n
+
     def lora_modules(self):
         return [m for m in self.model.modules() if isinstance(m, (LoRALinear, LoRAMoeExperts))]
 
