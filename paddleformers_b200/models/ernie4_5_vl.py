@@ -251,6 +251,14 @@ class Ernie4_5VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
 
         PretrainedModel.load_hf_checkpoint(self, directory, strict)
 
+    @property
+    def loss_accumulation_steps(self):
+        return self.language.loss_accumulation_steps
+
+    @loss_accumulation_steps.setter
+    def loss_accumulation_steps(self, v):
+        self.language.loss_accumulation_steps = v
+
     def weight_map(self) -> WeightMap:
         rules = []
         for r in build_weight_map(self.config.text_config).rules.values():
